@@ -1,0 +1,317 @@
+"""TEST INFRASTRUCTURE: ctypes bindings for the CPU oracle (oracle.c) and, where it was built, the real reference
+(ref_driver.cpp compiled against the unmodified RLtools headers).
+
+Only tests/, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs import this package. The product
+package never does.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "_build", "liboracle.so")
+REF_STRICT_SO = os.path.join(_HERE, "_ref", "libref_strict.so")
+REF_FAST_SO = os.path.join(_HERE, "_ref", "libref_fast.so")
+
+ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
+
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+_u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
+
+
+def build(ref: bool = True) -> None:
+    """Compile oracle.c (always) and the reference driver (when the reference tree exists)."""
+    subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
+    if ref and os.path.isdir(os.environ.get("B200RL_REFERENCE", "/root/reference")):
+        subprocess.run(["make", "-s", "-C", _HERE, "ref", "REFERENCE=" + os.environ.get("B200RL_REFERENCE", "/root/reference")], check=True)
+
+
+class MlpShape(C.Structure):
+    _fields_ = [("n_layers", C.c_int), ("input_dim", C.c_int), ("dims", C.c_int * 8), ("acts", C.c_int * 8)]
+
+    @staticmethod
+    def make(input_dim, dims, acts):
+        s = MlpShape()
+        s.n_layers = len(dims)
+        s.input_dim = input_dim
+        for i, (d, a) in enumerate(zip(dims, acts)):
+            s.dims[i] = d
+            s.acts[i] = ACT[a] if isinstance(a, str) else a
+        return s
+
+    def num_params(self):
+        n, i = 0, self.input_dim
+        for l in range(self.n_layers):
+            n += self.dims[l] * i + self.dims[l]
+            i = self.dims[l]
+        return n
+
+    def layer_dims(self):
+        return [self.dims[l] for l in range(self.n_layers)]
+
+
+def _opt(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class Oracle:
+    """Typed wrapper around liboracle.so. Arrays are float32 C-contiguous numpy arrays."""
+
+    def __init__(self, path=ORACLE_SO):
+        if not os.path.exists(path):
+            build(ref=False)
+        self.lib = L = C.CDLL(path)
+        L.orc_rng_uniform_stream.argtypes = [C.c_uint32, C.c_int, C.c_float, C.c_float, _f32p]
+        L.orc_rng_normal_stream.argtypes = [C.c_uint32, C.c_int, C.c_float, C.c_float, _f32p]
+        L.orc_rng_mixed_stream.argtypes = [C.c_uint32, C.c_int, _u8p, _f32p, _f32p, _f32p]
+        L.orc_dense_forward.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_void_p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.orc_dense_backward.argtypes = [_f32p, _f32p, C.c_int, _f32p, C.c_int, _f32p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.orc_mse_gradient.argtypes = [_f32p, C.c_int, _f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float]
+        L.orc_mse_evaluate.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float]
+        L.orc_mse_evaluate.restype = C.c_float
+        L.orc_adam_bias_correction.argtypes = [C.c_float, C.c_float, C.POINTER(C.c_uint32), C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        L.orc_adam_update.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_size_t] + [C.c_float] * 7
+        L.orc_mlp_evaluate.argtypes = [C.POINTER(MlpShape), _f32p, _f32p, C.c_int, _f32p, C.c_int, C.c_int]
+        L.orc_mlp_forward.argtypes = [C.POINTER(MlpShape), _f32p, _f32p, C.c_int, _f32p, _f32p, C.c_int]
+        L.orc_mlp_backward.argtypes = [C.POINTER(MlpShape), _f32p, _f32p, _f32p, C.c_int, _f32p, _f32p, _f32p, C.c_void_p, C.c_int]
+        L.orc_pendulum_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
+        L.orc_pendulum_step_batch.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, C.c_void_p, C.c_void_p]
+        L.orc_pendulum_rollout.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int,
+                                           _f32p, _f32p, _f32p, C.c_void_p]
+        L.orc_pendulum_rollout.restype = C.c_int
+        L.orc_rng_init.argtypes = [C.c_void_p, C.c_uint32]
+        L.orc_reset_table.argtypes = [C.c_void_p, C.c_int, C.c_int, _i32p, _u8p, C.c_int, _f32p, C.c_int]
+        L.orc_reset_table.restype = C.c_int
+        L.orc_gae.argtypes = [_f32p, _f32p, _u8p, _u8p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
+
+    # --- RNG -----------------------------------------------------------------------------------------------
+    def uniform_stream(self, seed, n, lo, hi):
+        out = np.empty(n, np.float32)
+        self.lib.orc_rng_uniform_stream(seed, n, lo, hi, out)
+        return out
+
+    def normal_stream(self, seed, n, mean, std):
+        out = np.empty(n, np.float32)
+        self.lib.orc_rng_normal_stream(seed, n, mean, std, out)
+        return out
+
+    def mixed_stream(self, seed, kinds, a, b):
+        out = np.empty(len(kinds), np.float32)
+        self.lib.orc_rng_mixed_stream(seed, len(kinds), kinds, a, b, out)
+        return out
+
+    # --- dense / mlp ---------------------------------------------------------------------------------------
+    def dense_forward(self, W, b, x, act, want_pre=True):
+        B, I = x.shape
+        O = W.shape[0]
+        pre = np.empty((B, O), np.float32) if want_pre else None
+        y = np.empty((B, O), np.float32)
+        self.lib.orc_dense_forward(W, b, x, I, _opt(pre), O, y, O, B, I, O, ACT[act] if isinstance(act, str) else act)
+        return pre, y
+
+    def dense_backward(self, W, x, pre, d_out, act, dW=None, db=None, want_d_in=True, want_grads=True):
+        B, I = x.shape
+        O = W.shape[0]
+        d_out = d_out.copy()
+        if want_grads:
+            dW = np.zeros((O, I), np.float32) if dW is None else dW.copy()
+            db = np.zeros(O, np.float32) if db is None else db.copy()
+        else:
+            dW = db = None
+        d_in = np.empty((B, I), np.float32) if want_d_in else None
+        self.lib.orc_dense_backward(W, x, I, pre, O, d_out, O, _opt(dW), _opt(db), _opt(d_in), I, B, I, O,
+                                    ACT[act] if isinstance(act, str) else act, 1)
+        return dW, db, d_in, d_out
+
+    def mse_gradient(self, a, b, loss_weight=1.0):
+        d = np.empty_like(a)
+        self.lib.orc_mse_gradient(a, a.shape[1], b, b.shape[1], d, d.shape[1], a.shape[0], a.shape[1], loss_weight)
+        return d
+
+    def adam_bias_correction(self, beta_1, beta_2, age):
+        a = C.c_uint32(age)
+        c1, c2 = C.c_float(), C.c_float()
+        self.lib.orc_adam_bias_correction(beta_1, beta_2, C.byref(a), C.byref(c1), C.byref(c2))
+        return c1.value, c2.value, a.value
+
+    def adam_update(self, p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2):
+        p, m, v = p.copy(), m.copy(), v.copy()
+        self.lib.orc_adam_update(p, g, m, v, p.size, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
+        return p, m, v
+
+    def mlp_evaluate(self, shape, params, x):
+        B = x.shape[0]
+        y = np.empty((B, shape.dims[shape.n_layers - 1]), np.float32)
+        self.lib.orc_mlp_evaluate(C.byref(shape), params, x, x.shape[1], y, y.shape[1], B)
+        return y
+
+    def mlp_forward(self, shape, params, x):
+        B = x.shape[0]
+        n = B * sum(shape.layer_dims())
+        pre, out = np.empty(n, np.float32), np.empty(n, np.float32)
+        self.lib.orc_mlp_forward(C.byref(shape), params, x, x.shape[1], pre, out, B)
+        return pre, out
+
+    def mlp_backward(self, shape, params, grads, x, pre, out, d_out, want_d_input=False):
+        B = x.shape[0]
+        grads = grads.copy()
+        d_out = d_out.copy()
+        d_in = np.empty((B, shape.input_dim), np.float32) if want_d_input else None
+        self.lib.orc_mlp_backward(C.byref(shape), params, grads, x, x.shape[1], pre, out, d_out, _opt(d_in), B)
+        return grads, d_in
+
+    def mlp_train_steps(self, shape, params, x, target, n_steps, alpha=1e-3, beta_1=0.9, beta_2=0.999, eps=1e-7, eps_sqrt=1e-7):
+        """n_steps x {zero_gradient, forward, mse gradient (weight 1), backward, Adam step}; TF-default hyper-parameters."""
+        p = params.copy()
+        m = np.zeros_like(p)
+        v = np.zeros_like(p)
+        age = 1
+        g = np.zeros_like(p)
+        pre = out = None
+        for _ in range(n_steps):
+            g = np.zeros_like(p)
+            pre, out = self.mlp_forward(shape, p, x)
+            O = shape.dims[shape.n_layers - 1]
+            y = out[-x.shape[0] * O:].reshape(x.shape[0], O)
+            d = self.mse_gradient(np.ascontiguousarray(y), target, 1.0)
+            g, _ = self.mlp_backward(shape, p, g, x, pre, out, d)
+            c1, c2, age = self.adam_bias_correction(beta_1, beta_2, age)
+            p, m, v = self.adam_update(p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
+        return p, g, m, v, pre, out
+
+    # --- pendulum ------------------------------------------------------------------------------------------
+    def pendulum_initial_states(self, seed, n):
+        s = np.empty((n, 2), np.float32)
+        self.lib.orc_pendulum_initial_states(seed, n, s)
+        return s
+
+    def pendulum_step(self, states, actions):
+        n = states.shape[0]
+        ns, r = np.empty((n, 2), np.float32), np.empty(n, np.float32)
+        obs, nobs = np.empty((n, 3), np.float32), np.empty((n, 3), np.float32)
+        self.lib.orc_pendulum_step_batch(n, states, np.ascontiguousarray(actions.reshape(-1)), ns, r, _opt(obs), _opt(nobs))
+        return ns, r, obs, nobs
+
+    def reset_table(self, seed, N, T, episode_step, truncated, step_limit, R):
+        rng = C.create_string_buffer(4 * 624 + 16)
+        self.lib.orc_rng_init(rng, seed)
+        table = np.zeros((R, N, 2), np.float32)
+        used = self.lib.orc_reset_table(rng, N, T, episode_step, truncated, step_limit, table, R)
+        if used < 0:
+            raise ValueError("reset table too small")
+        return table
+
+    def pendulum_rollout(self, shape, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=200,
+                         teacher_states=None):
+        N = states.shape[0]
+        states, episode_step = states.copy(), episode_step.copy()
+        truncated, episode_return = truncated.copy(), episode_return.copy()
+        obs = np.empty((T * N, 3), np.float32)
+        act = np.empty((T * N, 1), np.float32)
+        rew = np.empty((T * N, 1), np.float32)
+        rc = self.lib.orc_pendulum_rollout(C.byref(shape), params, N, T, states, episode_step, truncated, episode_return, reset_states,
+                                           reset_states.shape[0], step_limit, obs, act, rew, _opt(teacher_states))
+        if rc != 0:
+            raise RuntimeError(f"orc_pendulum_rollout rc={rc}")
+        return dict(obs=obs, act=act, rew=rew, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
+
+    def gae(self, rewards, all_values, terminated, truncated, N, steps, gamma=0.99, lam=0.95, ignore_termination=False):
+        adv, tgt = np.empty(steps * N, np.float32), np.empty(steps * N, np.float32)
+        self.lib.orc_gae(rewards, all_values, terminated, truncated, adv, tgt, N, steps, gamma, lam, int(ignore_termination))
+        return adv, tgt
+
+
+class Reference:
+    """Typed wrapper around the real reference (libref_strict.so / libref_fast.so). Present only where it was built."""
+
+    def __init__(self, kind="strict"):
+        path = REF_STRICT_SO if kind == "strict" else REF_FAST_SO
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self.lib = L = C.CDLL(path)
+        L.ref_case_name.restype = C.c_char_p
+        L.ref_case_dims.argtypes = [C.c_char_p, C.POINTER(C.c_int)]
+        L.ref_mlp_run.argtypes = [C.c_char_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 7 + [C.POINTER(C.c_double)]
+        L.ref_rng_uniform.argtypes = [C.c_uint32, C.c_int, C.c_float, C.c_float, _f32p]
+        L.ref_rng_normal.argtypes = [C.c_uint32, C.c_int, C.c_float, C.c_float, _f32p]
+        L.ref_rng_mixed.argtypes = [C.c_uint32, C.c_int, _u8p, _f32p, _f32p, _f32p]
+        L.ref_pendulum_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
+        L.ref_pendulum_step.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, C.c_void_p, C.c_void_p]
+        L.ref_pendulum_rollout.argtypes = [C.c_int, _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int,
+                                           _f32p, _f32p, _f32p, C.c_int]
+        L.ref_pendulum_rollout.restype = C.c_int
+
+    def cases(self):
+        out = {}
+        for i in range(self.lib.ref_num_cases()):
+            name = self.lib.ref_case_name(i).decode()
+            d = (C.c_int * 7)()
+            self.lib.ref_case_dims(name.encode(), d)
+            out[name] = dict(batch=d[0], input_dim=d[1], hidden_dim=d[2], output_dim=d[3], num_layers=d[4], hidden_act=d[5], output_act=d[6])
+        return out
+
+    @staticmethod
+    def case_shape(c):
+        dims = [c["hidden_dim"]] * (c["num_layers"] - 1) + [c["output_dim"]]
+        acts = [c["hidden_act"]] * (c["num_layers"] - 1) + [c["output_act"]]
+        return MlpShape.make(c["input_dim"], dims, acts)
+
+    def mlp_run(self, name, params, x, target, mode, n_steps=0, init_seed=0):
+        c = self.cases()[name]
+        shape = self.case_shape(c)
+        n, B = shape.num_params(), c["batch"]
+        acts = B * sum(shape.layer_dims())
+        res = dict(params=np.empty(n, np.float32), grads=np.empty(n, np.float32), m=np.empty(n, np.float32), v=np.empty(n, np.float32),
+                   pre=np.empty(acts, np.float32) if mode != 0 else None,
+                   out=np.empty(acts if mode != 0 else B * c["output_dim"], np.float32),
+                   d_input=np.empty((B, c["input_dim"]), np.float32) if mode == 3 else None)
+        sec = C.c_double()
+        rc = self.lib.ref_mlp_run(name.encode(), _opt(params), init_seed, _opt(x), _opt(target), mode, n_steps, _opt(res["params"]), _opt(res["grads"]),
+                                  _opt(res["m"]), _opt(res["v"]), _opt(res["pre"]), _opt(res["out"]), _opt(res["d_input"]), C.byref(sec))
+        assert rc == 0, name
+        res["seconds"] = sec.value
+        return res
+
+    def uniform_stream(self, seed, n, lo, hi):
+        out = np.empty(n, np.float32)
+        self.lib.ref_rng_uniform(seed, n, lo, hi, out)
+        return out
+
+    def normal_stream(self, seed, n, mean, std):
+        out = np.empty(n, np.float32)
+        self.lib.ref_rng_normal(seed, n, mean, std, out)
+        return out
+
+    def mixed_stream(self, seed, kinds, a, b):
+        out = np.empty(len(kinds), np.float32)
+        self.lib.ref_rng_mixed(seed, len(kinds), kinds, a, b, out)
+        return out
+
+    def pendulum_initial_states(self, seed, n):
+        s = np.empty((n, 2), np.float32)
+        self.lib.ref_pendulum_initial_states(seed, n, s)
+        return s
+
+    def pendulum_step(self, states, actions):
+        n = states.shape[0]
+        ns, r = np.empty((n, 2), np.float32), np.empty(n, np.float32)
+        obs, nobs = np.empty((n, 3), np.float32), np.empty((n, 3), np.float32)
+        self.lib.ref_pendulum_step(n, states, np.ascontiguousarray(actions.reshape(-1)), ns, r, _opt(obs), _opt(nobs))
+        return ns, r, obs, nobs
+
+    def pendulum_rollout(self, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=200, chunk=1, num_threads=1):
+        N = states.shape[0]
+        states, episode_step = states.copy(), episode_step.copy()
+        truncated, episode_return = truncated.copy(), episode_return.copy()
+        obs = np.empty((T * N, 3), np.float32)
+        act = np.empty((T * N, 1), np.float32)
+        rew = np.empty((T * N, 1), np.float32)
+        rc = self.lib.ref_pendulum_rollout(chunk, params, N, T, states, episode_step, truncated, episode_return, reset_states,
+                                           reset_states.shape[0], step_limit, obs, act, rew, num_threads)
+        if rc != 0:
+            raise RuntimeError(f"ref_pendulum_rollout rc={rc}")
+        return dict(obs=obs, act=act, rew=rew, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)

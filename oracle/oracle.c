@@ -1,0 +1,428 @@
+/*
+ * TEST INFRASTRUCTURE -- CPU oracle for the B200 hot path. NOT part of the shipped library.
+ *
+ * Plain-C restatement of the reference algorithm (RLtools, header-only C++) for the one path this repository
+ * accelerates: dense layer evaluate/forward/backward, MSE gradient, Adam, Pendulum step/reward/observe, the
+ * rollout loop that interleaves actor inference with the environment step, and GAE. Every function cites the
+ * reference file:line it follows (paths relative to the reference's include/rl_tools/).
+ *
+ * Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / --impl reference legs may load this
+ * file's library; the product path never does.
+ *
+ * Pinning: this restatement is checked bit-for-bit against the real reference compiled from its own headers
+ * (oracle/ref_driver.cpp -> oracle/_ref/libref_strict.so, generic CPU device, -O2 -fno-fast-math
+ * -ffp-contract=off) by tests/test_oracle_pinning.py (where the reference is present) and against the
+ * committed outputs of that same reference build in tests/golden/ (everywhere).
+ * Build: gcc -O2 -fno-fast-math -ffp-contract=off -fPIC -shared oracle.c -o _build/liboracle.so -lm
+ * The summation order is the reference's generic device order (operations_generic.h), left to right, with
+ * separate multiply and add (no fused multiply-add), so results are reproducible across compilers.
+ *
+ * The reference's random numbers come from libstdc++ (std::mt19937, std::uniform_real_distribution<float>,
+ * std::normal_distribution<float>; random/operations_cpu.h:21-48). libstdc++ is not part of the reference
+ * tree (GCC 13.3 here); its published algorithms are restated below and pinned against the reference's stream.
+ */
+#include <stdint.h>
+#include <stddef.h>
+#include <math.h>
+#include <string.h>
+#include <stdlib.h>
+
+#define ORC_ACT_IDENTITY 0
+#define ORC_ACT_RELU 1
+#define ORC_ACT_TANH 2
+#define ORC_ACT_FAST_TANH 3
+#define ORC_ACT_SIGMOID 4
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* RNG: std::mt19937 (MT19937, Matsumoto & Nishimura 1998) seeded as random/operations_cpu.h:21-24 does      */
+/* ------------------------------------------------------------------------------------------------------ */
+typedef struct { uint32_t mt[624]; int idx; } orc_rng;
+
+/* random/operations_cpu.h:23: engine = mt19937(seed + 1) */
+void orc_rng_init(orc_rng* r, uint32_t seed){
+    uint32_t s = seed + 1u;
+    r->mt[0] = s;
+    for(int i = 1; i < 624; i++) r->mt[i] = 1812433253u * (r->mt[i - 1] ^ (r->mt[i - 1] >> 30)) + (uint32_t)i;
+    r->idx = 624;
+}
+uint32_t orc_rng_next(orc_rng* r){
+    if(r->idx >= 624){
+        for(int i = 0; i < 624; i++){
+            uint32_t y = (r->mt[i] & 0x80000000u) | (r->mt[(i + 1) % 624] & 0x7fffffffu);
+            r->mt[i] = r->mt[(i + 397) % 624] ^ (y >> 1) ^ ((y & 1u) ? 0x9908b0dfu : 0u);
+        }
+        r->idx = 0;
+    }
+    uint32_t y = r->mt[r->idx++];
+    y ^= y >> 11; y ^= (y << 7) & 0x9d2c5680u; y ^= (y << 15) & 0xefc60000u; y ^= y >> 18;
+    return y;
+}
+/* std::generate_canonical<float, 24>(mt19937): one 32-bit draw, converted to float (round to nearest),
+ * divided by 2^32; a result that rounds up to 1.0f is replaced by the largest float below 1. */
+static float orc_canonical(orc_rng* r){
+    float sum = (float)orc_rng_next(r);
+    float ret = sum / 4294967296.0f;
+    if(ret >= 1.0f) ret = nextafterf(1.0f, 0.0f);
+    return ret;
+}
+/* random/operations_cpu.h:32-35 -> std::uniform_real_distribution<float>(lo, hi): u * (hi - lo) + lo */
+float orc_uniform_real(orc_rng* r, float lo, float hi){
+    return orc_canonical(r) * (hi - lo) + lo;
+}
+/* random/operations_cpu.h:40-48: a FRESH std::normal_distribution<float>(mean, std) per sample, so the second
+ * value of the Marsaglia polar pair is always discarded; std == 0 returns mean without consuming the engine. */
+float orc_normal(orc_rng* r, float mean, float std){
+    if(std == 0) return mean;
+    float x, y, r2;
+    do{
+        x = 2.0f * orc_canonical(r) - 1.0f;
+        y = 2.0f * orc_canonical(r) - 1.0f;
+        r2 = x * x + y * y;
+    } while(r2 > 1.0f || r2 == 0.0f);
+    float mult = sqrtf(-2 * logf(r2) / r2);
+    float ret = y * mult;
+    return ret * std + mean;
+}
+void orc_rng_uniform_stream(uint32_t seed, int n, float lo, float hi, float* out){
+    orc_rng r; orc_rng_init(&r, seed);
+    for(int i = 0; i < n; i++) out[i] = orc_uniform_real(&r, lo, hi);
+}
+void orc_rng_normal_stream(uint32_t seed, int n, float mean, float std, float* out){
+    orc_rng r; orc_rng_init(&r, seed);
+    for(int i = 0; i < n; i++) out[i] = orc_normal(&r, mean, std);
+}
+void orc_rng_mixed_stream(uint32_t seed, int n, const uint8_t* kinds, const float* a, const float* b, float* out){
+    orc_rng r; orc_rng_init(&r, seed);
+    for(int i = 0; i < n; i++) out[i] = kinds[i] == 0 ? orc_uniform_real(&r, a[i], b[i]) : orc_normal(&r, a[i], b[i]);
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* activations: nn/activation_functions.h:25-85, math/operations_cpu.h (std:: functions), fast_tanh          */
+/* math/operations_generic.h:247-251                                                                        */
+/* ------------------------------------------------------------------------------------------------------ */
+static float orc_fast_tanh(float x){
+    x = x < -3.0f ? -3.0f : (x > 3.0f ? 3.0f : x);
+    float x2 = x * x;
+    return x * (27 + x2) / (27 + 9 * x2);
+}
+float orc_activation(float x, int act){
+    switch(act){
+        case ORC_ACT_IDENTITY: return x;
+        case ORC_ACT_RELU: return x > 0.0f ? x : 0.0f;           /* math::max(x, 0) */
+        case ORC_ACT_TANH: return tanhf(x);
+        case ORC_ACT_FAST_TANH: return orc_fast_tanh(x);
+        case ORC_ACT_SIGMOID: return 1.0f / (1.0f + expf(-x));
+        default: return 0;
+    }
+}
+float orc_d_activation(float x, int act){
+    switch(act){
+        case ORC_ACT_IDENTITY: return 1;
+        case ORC_ACT_RELU: return x > 0 ? 1 : 0;
+        case ORC_ACT_TANH: { float a = tanhf(x); return 1.0f - a * a; }
+        case ORC_ACT_FAST_TANH: { float a = orc_fast_tanh(x); return 1.0f - a * a; }
+        case ORC_ACT_SIGMOID: { float s = orc_activation(x, ORC_ACT_SIGMOID); return s * (1 - s); }
+        default: return 0;
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* dense layer: nn/layers/dense/operations_generic.h                                                         */
+/* ------------------------------------------------------------------------------------------------------ */
+/* :94-110 evaluate and :112-127 forward: pre = b[o]; pre += W[o][i] * x[b][i] for i ascending; y = act(pre).
+ * W is [O,I] row-major, x rows have pitch ldx, pre (optional) pitch ldpre, y pitch ldy. */
+void orc_dense_forward(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
+                       int B, int I, int O, int act){
+    for(int b = 0; b < B; b++){
+        for(int o = 0; o < O; o++){
+            float acc = bias[o];
+            for(int i = 0; i < I; i++){
+                float prod = W[(size_t)o * I + i] * x[(size_t)b * ldx + i];
+                acc = acc + prod;
+            }
+            if(pre) pre[(size_t)b * ldpre + o] = acc;
+            y[(size_t)b * ldy + o] = orc_activation(acc, act);
+        }
+    }
+}
+/* :167-214 backward / backward_full (and :146-165 backward_input when dW == db == NULL):
+ * d_pre = act'(pre) * d_out; db[o] += d_pre; dW[o][i] += d_pre * x[b][i]; d_in[b][i] = sum_o W[o][i] * d_pre,
+ * batch outermost, output next, input innermost. Gradients ACCUMULATE. The reference's BLAS/CUDA variants
+ * overwrite d_out with d_pre (dense/operations_cpu_blas.h:142-186); store_d_pre reproduces that. */
+void orc_dense_backward(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
+                        float* dW, float* db, float* d_in, int ldi, int B, int I, int O, int act, int store_d_pre){
+    for(int b = 0; b < B; b++){
+        for(int o = 0; o < O; o++){
+            float d_pre = orc_d_activation(pre[(size_t)b * ldpre + o], act) * d_out[(size_t)b * ldd + o];
+            if(db) db[o] += d_pre;
+            for(int i = 0; i < I; i++){
+                if(d_in){
+                    if(o == 0) d_in[(size_t)b * ldi + i] = 0;
+                    float prod = W[(size_t)o * I + i] * d_pre;
+                    d_in[(size_t)b * ldi + i] += prod;
+                }
+                if(dW){
+                    float prod = d_pre * x[(size_t)b * ldx + i];
+                    dW[(size_t)o * I + i] += prod;
+                }
+            }
+            if(store_d_pre) d_out[(size_t)b * ldd + o] = d_pre;
+        }
+    }
+}
+
+/* nn/loss_functions/mse/operations_generic.h:43-58: d_a = (a - b) * (2 / (rows * cols) * w) */
+void orc_mse_gradient(const float* a, int lda, const float* b, int ldb, float* d_a, int ldd, int rows, int cols, float loss_weight){
+    float constant = (float)2 / ((float)rows * cols) * loss_weight;
+    for(int r = 0; r < rows; r++) for(int c = 0; c < cols; c++){
+        float diff = a[(size_t)r * lda + c] - b[(size_t)r * ldb + c];
+        d_a[(size_t)r * ldd + c] = diff * constant;
+    }
+}
+/* :9-22 evaluate: sum (a-b)^2 * w / (rows*cols) */
+float orc_mse_evaluate(const float* a, int lda, const float* b, int ldb, int rows, int cols, float loss_weight){
+    float acc = 0;
+    for(int r = 0; r < rows; r++) for(int c = 0; c < cols; c++){
+        float diff = a[(size_t)r * lda + c] - b[(size_t)r * ldb + c];
+        acc += diff * diff;
+    }
+    return acc * loss_weight / (rows * cols);
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* Adam: nn/optimizers/adam/operations_generic.h:49-64, instance/operations_generic.h:25-68,                 */
+/* utils/polyak/operations_generic.h:72-88                                                                   */
+/* ------------------------------------------------------------------------------------------------------ */
+/* _step (:49-59): c1 = 1/(1 - beta1^age), c2 = 1/(1 - beta2^age) via powf, then age++ (age starts at 1). */
+void orc_adam_bias_correction(float beta_1, float beta_2, uint32_t* age, float* c1, float* c2){
+    uint32_t a = *age;
+    *c1 = 1 / (1 - powf(beta_1, (float)a));
+    *c2 = 1 / (1 - powf(beta_2, (float)a));
+    *age = a + 1;
+}
+/* update(Adam::Instance) with clipping, weight decay and bias-lr factor off (the defaults):
+ *   m = b1*m + (1-b1)*g ; v = b2*v + ((1-b2)*g)*g ; p -= ((alpha*c1)*m) / (sqrt(max(v*c2, eps_sqrt)) + eps) */
+void orc_adam_update(float* p, const float* g, float* m, float* v, size_t n,
+                     float alpha, float beta_1, float beta_2, float epsilon, float epsilon_sqrt, float c1, float c2){
+    for(size_t i = 0; i < n; i++){
+        m[i] = beta_1 * m[i] + (1 - beta_1) * g[i];
+        v[i] = beta_2 * v[i] + (1 - beta_2) * g[i] * g[i];
+        float pre_sqrt = v[i] * c2;
+        pre_sqrt = pre_sqrt > epsilon_sqrt ? pre_sqrt : epsilon_sqrt;
+        float update = alpha * c1 * m[i] / (sqrtf(pre_sqrt) + epsilon);
+        float value = p[i];
+        value -= update;
+        p[i] = value;
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* MLP on a flat parameter arena. Layout (this repository's, used by oracle and library alike):              */
+/* for each layer l: W_l [O_l, I_l] row-major, then b_l [O_l].                                               */
+/* nn_models/mlp/operations_generic.h:77-102 (evaluate), :103-120 (forward), :180-204 (backward),            */
+/* :152-179 (backward_full), :210-217 (update)                                                               */
+/* ------------------------------------------------------------------------------------------------------ */
+typedef struct {
+    int n_layers;      /* <= 8 */
+    int input_dim;
+    int dims[8];       /* output dim of each layer */
+    int acts[8];
+} orc_mlp_shape;
+
+size_t orc_mlp_num_params(const orc_mlp_shape* s){
+    size_t n = 0; int in = s->input_dim;
+    for(int l = 0; l < s->n_layers; l++){ n += (size_t)s->dims[l] * in + s->dims[l]; in = s->dims[l]; }
+    return n;
+}
+size_t orc_mlp_act_elems(const orc_mlp_shape* s){ size_t n = 0; for(int l = 0; l < s->n_layers; l++) n += s->dims[l]; return n; }
+
+/* evaluate: y [B, O_last] (pitch ldy). scratch-free for the caller: allocates two [B, max_dim] ping-pong buffers. */
+void orc_mlp_evaluate(const orc_mlp_shape* s, const float* params, const float* x, int ldx, float* y, int ldy, int B){
+    int maxd = 0; for(int l = 0; l < s->n_layers; l++) if(s->dims[l] > maxd) maxd = s->dims[l];
+    float* tick = (float*)malloc(sizeof(float) * (size_t)B * maxd);
+    float* tock = (float*)malloc(sizeof(float) * (size_t)B * maxd);
+    const float* in = x; int ldin = ldx; int I = s->input_dim; const float* p = params;
+    for(int l = 0; l < s->n_layers; l++){
+        int O = s->dims[l];
+        int last = l == s->n_layers - 1;
+        float* out = last ? y : ((l % 2 == 0) ? tick : tock);
+        int ldo = last ? ldy : O;
+        orc_dense_forward(p, p + (size_t)O * I, in, ldin, NULL, 0, out, ldo, B, I, O, s->acts[l]);
+        p += (size_t)O * I + O; in = out; ldin = ldo; I = O;
+    }
+    free(tick); free(tock);
+}
+/* forward: stores per-layer pre-activations and outputs, concatenated layer after layer, each [B, O_l] dense. */
+void orc_mlp_forward(const orc_mlp_shape* s, const float* params, const float* x, int ldx, float* pre, float* out, int B){
+    const float* in = x; int ldin = ldx; int I = s->input_dim; const float* p = params;
+    for(int l = 0; l < s->n_layers; l++){
+        int O = s->dims[l];
+        orc_dense_forward(p, p + (size_t)O * I, in, ldin, pre, O, out, O, B, I, O, s->acts[l]);
+        p += (size_t)O * I + O; in = out; ldin = O; I = O;
+        pre += (size_t)B * O; out += (size_t)B * O;
+    }
+}
+/* backward: d_out [B, O_last] (clobbered), gradients accumulate into grads (same layout as params);
+ * d_input optional ([B, input_dim], pitch = input_dim): NULL -> the input layer gets the weights-only backward. */
+void orc_mlp_backward(const orc_mlp_shape* s, const float* params, float* grads, const float* x, int ldx,
+                      const float* pre, const float* out, float* d_out, float* d_input, int B){
+    int L = s->n_layers;
+    size_t poff[8], aoff[8]; int Is[8];
+    { size_t po = 0, ao = 0; int I = s->input_dim;
+      for(int l = 0; l < L; l++){ poff[l] = po; aoff[l] = ao; Is[l] = I; po += (size_t)s->dims[l] * I + s->dims[l]; ao += (size_t)B * s->dims[l]; I = s->dims[l]; } }
+    int maxd = s->input_dim; for(int l = 0; l < L; l++) if(s->dims[l] > maxd) maxd = s->dims[l];
+    float* tick = (float*)malloc(sizeof(float) * (size_t)B * maxd);
+    float* tock = (float*)malloc(sizeof(float) * (size_t)B * maxd);
+    float* d_cur = d_out; int ldd = s->dims[L - 1];
+    for(int l = L - 1; l >= 0; l--){
+        int O = s->dims[l], I = Is[l];
+        const float* in = l == 0 ? x : out + aoff[l - 1];
+        int ldin = l == 0 ? ldx : I;
+        float* d_in = l == 0 ? d_input : ((l % 2 == 0) ? tick : tock);
+        const float* W = params + poff[l];
+        float* dW = grads + poff[l];
+        orc_dense_backward(W, in, ldin, pre + aoff[l], O, d_cur, ldd, dW, dW + (size_t)O * I, d_in, I, B, I, O, s->acts[l], 1);
+        d_cur = d_in; ldd = I;
+    }
+    free(tick); free(tock);
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* Pendulum: rl/environments/pendulum/pendulum.h:11-25 (parameters), operations_generic.h                    */
+/* ------------------------------------------------------------------------------------------------------ */
+#define ORC_PI_F 3.141592653589793238462643383279502884f   /* math::PI<float> */
+static const float P_G = 10, P_MAX_SPEED = 8, P_MAX_TORQUE = 2, P_DT = 0.05f, P_M = 1, P_L = 1;
+
+static float orc_clip(float x, float lo, float hi){ return x < lo ? lo : (x > hi ? hi : x); }
+/* :14-22: f_mod_python(x + pi, 2 pi) - pi with f_mod_python(a, b) = a - b * floor(a / b), all float */
+float orc_angle_normalize(float x){
+    float a = x + ORC_PI_F, b = 2 * ORC_PI_F;
+    return (a - b * floorf(a / b)) - ORC_PI_F;
+}
+/* :57-61: theta ~ U[-pi, pi] first, then theta_dot ~ U[-1, 1] */
+void orc_pendulum_sample_initial_state(orc_rng* r, float* theta, float* theta_dot){
+    *theta = orc_uniform_real(r, -ORC_PI_F, ORC_PI_F);
+    *theta_dot = orc_uniform_real(r, -1, 1);
+}
+/* :78-101. The literal 3.0 makes the bracket DOUBLE arithmetic: the float operands are promoted, the sum with
+ * theta_dot is formed in double and rounded to float once. */
+void orc_pendulum_step(float theta, float theta_dot, float action, float* next_theta, float* next_theta_dot){
+    float u_normalised = orc_clip(action, -1, 1);       /* math::clamp */
+    float u = P_MAX_TORQUE * u_normalised;
+    u = orc_clip(u, -P_MAX_TORQUE, P_MAX_TORQUE);
+    float newthdot = theta_dot + (3 * P_G / (2 * P_L) * sinf(theta) + 3.0 / (P_M * P_L * P_L) * u) * P_DT;
+    newthdot = orc_clip(newthdot, -P_MAX_SPEED, P_MAX_SPEED);
+    float newth = theta + newthdot * P_DT;
+    *next_theta = newth; *next_theta_dot = newthdot;
+}
+/* :130-139: uses the UNCLAMPED action and the PRE-step state; 0.1 and 0.001 are double literals. */
+float orc_pendulum_reward(float theta, float theta_dot, float action){
+    float angle_norm = orc_angle_normalize(theta);
+    float u = P_MAX_TORQUE * action;
+    float costs = angle_norm * angle_norm + 0.1 * theta_dot * theta_dot + 0.001 * (u * u);
+    return -costs;
+}
+/* :141-160 ObservationFourier: [cos, sin, theta_dot] */
+void orc_pendulum_observe(float theta, float theta_dot, float* obs){
+    obs[0] = cosf(theta); obs[1] = sinf(theta); obs[2] = theta_dot;
+}
+void orc_pendulum_initial_states(uint32_t seed, int n, float* states){
+    orc_rng r; orc_rng_init(&r, seed);
+    for(int e = 0; e < n; e++) orc_pendulum_sample_initial_state(&r, &states[2 * e], &states[2 * e + 1]);
+}
+void orc_pendulum_step_batch(int n, const float* states, const float* actions, float* next_states, float* rewards, float* obs, float* next_obs){
+    for(int e = 0; e < n; e++){
+        orc_pendulum_step(states[2 * e], states[2 * e + 1], actions[e], &next_states[2 * e], &next_states[2 * e + 1]);
+        rewards[e] = orc_pendulum_reward(states[2 * e], states[2 * e + 1], actions[e]);
+        if(obs) orc_pendulum_observe(states[2 * e], states[2 * e + 1], obs + 3 * e);
+        if(next_obs) orc_pendulum_observe(next_states[2 * e], next_states[2 * e + 1], next_obs + 3 * e);
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* Rollout = off-policy runner step with deterministic actions, repeated T times:                            */
+/* rl/components/off_policy_runner/operations_generic_per_env.h:8-66 (prologue: reset-if-truncated, observe), */
+/* operations_generic.h:189-205 (interlude: batched policy evaluate), per_env.h:67-108 (epilogue: step,      */
+/* reward, counters, truncation). Replay-buffer writes are replaced by flat obs/act/rew outputs, row t*N+e.   */
+/* Resets draw from reset_states[k][e] = the k-th reset of env e inside this call (values pre-drawn in the    */
+/* reference's draw order by orc_reset_table).                                                               */
+/* ------------------------------------------------------------------------------------------------------ */
+int orc_pendulum_rollout(const orc_mlp_shape* actor, const float* params, int N, int T, float* states, int32_t* episode_step,
+                         uint8_t* truncated, float* episode_return, const float* reset_states, int R, int step_limit,
+                         float* obs, float* actions, float* rew, const float* teacher_states){
+    int rc = 0;
+    int* reset_count = (int*)calloc((size_t)N, sizeof(int));
+    if(actor->input_dim != 3 || actor->dims[actor->n_layers - 1] != 1) { free(reset_count); return -1; }
+    for(int t = 0; t < T; t++){
+        float* obs_t = obs + (size_t)t * N * 3; float* act_t = actions + (size_t)t * N; float* rew_t = rew + (size_t)t * N;
+        if(teacher_states) memcpy(states, teacher_states + (size_t)t * N * 2, sizeof(float) * 2 * (size_t)N);
+        for(int e = 0; e < N; e++){
+            if(truncated[e]){
+                if(reset_count[e] >= R){ rc = -2; continue; }
+                states[2 * e] = reset_states[((size_t)reset_count[e] * N + e) * 2];
+                states[2 * e + 1] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 1];
+                reset_count[e]++; episode_step[e] = 0; episode_return[e] = 0;
+            }
+            orc_pendulum_observe(states[2 * e], states[2 * e + 1], obs_t + 3 * e);
+        }
+        orc_mlp_evaluate(actor, params, obs_t, 3, act_t, 1, N);
+        for(int e = 0; e < N; e++){
+            float nt, ntd;
+            orc_pendulum_step(states[2 * e], states[2 * e + 1], act_t[e], &nt, &ntd);
+            float r = orc_pendulum_reward(states[2 * e], states[2 * e + 1], act_t[e]);
+            episode_step[e] += 1; episode_return[e] += r;
+            truncated[e] = (episode_step[e] == step_limit);     /* Pendulum never terminates (:243-247) */
+            rew_t[e] = r; states[2 * e] = nt; states[2 * e + 1] = ntd;
+        }
+    }
+    free(reset_count);
+    return rc;
+}
+/* Reset table in the reference's draw order: at every step the prologue visits envs 0..N-1 with ONE shared
+ * engine (off_policy_runner/operations_cpu.h:46-50) and draws (theta, theta_dot) for each truncated env.
+ * Pendulum never terminates, so the truncation schedule depends only on the integer counters. Returns the
+ * number of reset rounds written (<= R) or -1 if R is too small. rng state is advanced in place. */
+int orc_reset_table(orc_rng* rng, int N, int T, const int32_t* episode_step_in, const uint8_t* truncated_in, int step_limit, float* table, int R){
+    int32_t* es = (int32_t*)malloc(sizeof(int32_t) * (size_t)N); uint8_t* tr = (uint8_t*)malloc((size_t)N); int* cnt = (int*)calloc((size_t)N, sizeof(int));
+    memcpy(es, episode_step_in, sizeof(int32_t) * (size_t)N); memcpy(tr, truncated_in, (size_t)N);
+    int used = 0, rc = 0;
+    for(int t = 0; t < T && rc == 0; t++){
+        for(int e = 0; e < N; e++){
+            if(tr[e]){
+                if(cnt[e] >= R){ rc = -1; break; }
+                float* dst = table + ((size_t)cnt[e] * N + e) * 2;
+                orc_pendulum_sample_initial_state(rng, dst, dst + 1);
+                cnt[e]++; if(cnt[e] > used) used = cnt[e];
+                es[e] = 0;
+            }
+        }
+        for(int e = 0; e < N; e++){ es[e] += 1; tr[e] = es[e] == step_limit; }
+    }
+    free(es); free(tr); free(cnt);
+    return rc ? rc : used;
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* GAE: rl/algorithms/ppo/operations_generic.h:59-95. all_values has (steps+1)*N rows, row = step*N + env.    */
+/* ------------------------------------------------------------------------------------------------------ */
+void orc_gae(const float* rewards, const float* all_values, const uint8_t* terminated, const uint8_t* truncated,
+             float* advantages, float* target_values, int N, int steps, float gamma, float lambda, int ignore_termination){
+    for(int e = 0; e < N; e++){
+        float previous_value = all_values[(size_t)steps * N + e];
+        float previous_advantage = 0;
+        for(int sf = 0; sf < steps; sf++){
+            int sb = steps - 1 - sf;
+            size_t pos = (size_t)sb * N + e;
+            int term = terminated[pos], trunc = truncated[pos];
+            float current = all_values[pos];
+            int term_actual = term && !ignore_termination;
+            float next = term_actual ? 0 : previous_value;
+            float td = rewards[pos] + gamma * next - current;
+            if(trunc){ if(!term) td = 0; previous_advantage = 0; }
+            float adv = lambda * gamma * previous_advantage + td;
+            advantages[pos] = adv;
+            target_values[pos] = adv + current;
+            previous_advantage = adv; previous_value = current;
+        }
+    }
+}

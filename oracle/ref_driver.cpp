@@ -1,0 +1,407 @@
+// TEST INFRASTRUCTURE -- not part of the shipped library.
+//
+// Thin extern "C" driver around the UNMODIFIED RLtools headers (header-only C++17). It instantiates the
+// reference's own templates for the shapes the parity suite needs and exposes them as a flat C interface so
+// that (a) the plain-C restatement in oracle.c can be pinned against the real reference, bit for bit, and
+// (b) golden fixtures can be generated, and (c) the reference CPU path can be timed as the CPU baseline.
+//
+// Nothing from the reference is copied here: the headers are included from where they lie
+// (-I<reference>/include). Build recipe: oracle/Makefile (targets _ref/libref_strict.so, _ref/libref_fast.so).
+//
+//   strict : generic CPU device, -O2 -fno-fast-math -ffp-contract=off  -> fixed summation order, parity anchor
+//   fast   : CPU_OPENBLAS device (-DREF_USE_OPENBLAS), project default flags -> the timed CPU baseline
+//
+// Reference entry points exercised (paths inside the reference's include/rl_tools):
+//   nn_models/mlp/operations_generic.h   evaluate / forward / backward / zero_gradient / update
+//   nn/layers/dense/operations_generic.h (strict)  nn/layers/dense/operations_cpu_blas.h (fast)
+//   nn/optimizers/adam/operations_generic.h   init / reset_optimizer_state / step
+//   nn/loss_functions/mse/operations_generic.h   gradient
+//   rl/environments/pendulum/operations_generic.h   sample_initial_state / step / reward / observe
+//   random/operations_cpu.h   init(device, rng, seed), uniform_real_distribution, normal_distribution::sample
+#ifdef REF_USE_OPENBLAS
+#include <rl_tools/operations/cpu_mux.h>
+#else
+#include <rl_tools/operations/cpu.h>
+#endif
+#include <rl_tools/nn/optimizers/adam/instance/operations_generic.h>
+#ifdef REF_USE_OPENBLAS
+#include <rl_tools/nn/operations_cpu_mux.h>
+#else
+#include <rl_tools/nn/operations_generic.h>
+#endif
+#include <rl_tools/nn/layers/dense/operations_cpu.h>
+#include <rl_tools/nn/loss_functions/mse/operations_generic.h>
+#include <rl_tools/nn_models/mlp/operations_generic.h>
+#include <rl_tools/nn/optimizers/adam/operations_generic.h>
+#include <rl_tools/rl/environments/pendulum/operations_generic.h>
+
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <map>
+#include <vector>
+#include <thread>
+#include <chrono>
+
+namespace rlt = rl_tools;
+
+#ifdef REF_USE_OPENBLAS
+using DEVICE = rlt::devices::DEVICE_FACTORY<>;
+#else
+using DEVICE = rlt::devices::DefaultCPU;
+#endif
+using TI = typename DEVICE::index_t;
+using T = float;
+using TYPE_POLICY = rlt::numeric_types::Policy<T>;
+using RNG = DEVICE::SPEC::RANDOM::ENGINE<>;
+namespace act = rlt::nn::activation_functions;
+
+using PENDULUM_SPEC = rlt::rl::environments::pendulum::Specification<T, TI, rlt::rl::environments::pendulum::DefaultParameters<T>>;
+using PENDULUM = rlt::rl::environments::Pendulum<PENDULUM_SPEC>;
+
+static act::ActivationFunction act_from_int(int a){
+    switch(a){
+        case 0: return act::IDENTITY; case 1: return act::RELU; case 2: return act::TANH; case 3: return act::FAST_TANH; case 4: return act::SIGMOID;
+        default: return act::IDENTITY;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// MLP cases: the reference fixes every shape at compile time, so each (batch, dims, activations) tuple the
+// parity suite sweeps is one template instantiation, looked up by name at run time.
+// ---------------------------------------------------------------------------------------------------------
+struct MlpVTable{
+    int batch, input_dim, hidden_dim, output_dim, num_layers, hidden_act, output_act;
+    // params layout (flat): per layer W[O,I] row-major then b[O]
+    void (*run)(const float* params_in, uint32_t init_seed, const float* x, const float* target, int mode, int n_steps,
+                float* params_out, float* grads_out, float* m_out, float* v_out, float* pre_out, float* act_out, float* d_input_out, double* seconds);
+};
+
+template <typename LAYER>
+static void load_layer(DEVICE& device, LAYER& layer, const float*& p){
+    constexpr TI O = LAYER::OUTPUT_DIM, I = LAYER::INPUT_DIM;
+    for(TI o = 0; o < O; o++) for(TI i = 0; i < I; i++) rlt::set(device, layer.weights.parameters, p[o * I + i], o, i);
+    p += O * I;
+    for(TI o = 0; o < O; o++) rlt::set(device, layer.biases.parameters, p[o], o);
+    p += O;
+}
+enum Which{PARAMS, GRADS, MOM1, MOM2};
+template <typename LAYER>
+static void store_layer(DEVICE& device, LAYER& layer, float*& p, Which which){
+    constexpr TI O = LAYER::OUTPUT_DIM, I = LAYER::INPUT_DIM;
+    if(!p) return;
+    auto& w = which == PARAMS ? layer.weights.parameters : (which == GRADS ? layer.weights.gradient : (which == MOM1 ? layer.weights.gradient_first_order_moment : layer.weights.gradient_second_order_moment));
+    auto& b = which == PARAMS ? layer.biases.parameters : (which == GRADS ? layer.biases.gradient : (which == MOM1 ? layer.biases.gradient_first_order_moment : layer.biases.gradient_second_order_moment));
+    for(TI o = 0; o < O; o++) for(TI i = 0; i < I; i++) p[o * I + i] = rlt::get(device, w, o, i);
+    p += O * I;
+    for(TI o = 0; o < O; o++) p[o] = rlt::get(device, b, o);
+    p += O;
+}
+template <typename LAYER>
+static void store_acts(DEVICE& device, LAYER& layer, float*& pre, float*& out){
+    constexpr TI O = LAYER::OUTPUT_DIM, B = LAYER::INTERNAL_BATCH_SIZE;
+    for(TI b = 0; b < B; b++) for(TI o = 0; o < O; o++){
+        if(pre) pre[b * O + o] = rlt::get(layer.pre_activations, b, o);
+        if(out) out[b * O + o] = rlt::get(layer.output, b, o);
+    }
+    if(pre) pre += B * O;
+    if(out) out += B * O;
+}
+
+template <TI B, TI I, TI H, TI O, TI NL, act::ActivationFunction HACT, act::ActivationFunction OACT>
+struct MlpCase{
+    using CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, O, NL, H, HACT, OACT>;
+    using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, B, I>;
+    using CAPABILITY = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
+    using NET = rlt::nn_models::mlp::NeuralNetwork<CONFIG, CAPABILITY, INPUT_SHAPE>;
+    using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
+
+    template <typename F>
+    static void for_each_layer(NET& net, F f){
+        f(net.input_layer);
+        for(TI l = 0; l < NET::NUM_HIDDEN_LAYERS; l++) f(net.hidden_layers[l]);
+        f(net.output_layer);
+    }
+    // mode 0: evaluate only (act_out receives the network output [B,O])
+    // mode 1: zero_gradient, forward, mse::gradient(weight 1), backward            (n_steps ignored)
+    // mode 2: n_steps x { zero_gradient, forward, mse::gradient, backward, step }  (Adam, TF defaults)
+    // mode 3: like 1 but d_output := target (no loss) and the FULL backward incl. d_input (backward_full)
+    static void run(const float* params_in, uint32_t init_seed, const float* x, const float* target, int mode, int n_steps,
+                    float* params_out, float* grads_out, float* m_out, float* v_out, float* pre_out, float* act_out, float* d_input_out, double* seconds){
+        DEVICE device;
+        RNG rng;
+        rlt::malloc(device, rng);
+        rlt::init(device, rng, init_seed);
+        NET net;
+        typename NET::template Buffer<> buffers;
+        OPTIMIZER optimizer;
+        rlt::malloc(device, net);
+        rlt::malloc(device, buffers);
+        rlt::malloc(device, optimizer);
+        rlt::init(device, optimizer);
+        if(params_in){
+            const float* p = params_in;
+            for_each_layer(net, [&](auto& layer){ load_layer(device, layer, p); });
+        }
+        else{
+            rlt::init_weights(device, net, rng);
+        }
+        rlt::zero_gradient(device, net);
+        rlt::reset_optimizer_state(device, optimizer, net);
+        rlt::Matrix<rlt::matrix::Specification<T, TI, B, I>> input, d_input;
+        rlt::Matrix<rlt::matrix::Specification<T, TI, B, O>> output, tgt, d_output;
+        rlt::malloc(device, input); rlt::malloc(device, d_input); rlt::malloc(device, output); rlt::malloc(device, tgt); rlt::malloc(device, d_output);
+        if(x) for(TI b = 0; b < B; b++) for(TI i = 0; i < I; i++) rlt::set(input, b, i, x[b * I + i]);
+        if(target) for(TI b = 0; b < B; b++) for(TI o = 0; o < O; o++) rlt::set(tgt, b, o, target[b * O + o]);
+        auto t0 = std::chrono::steady_clock::now();
+        if(mode == 0){
+            int reps = n_steps > 0 ? n_steps : 1;
+            for(int r = 0; r < reps; r++) rlt::evaluate(device, net, input, output, buffers, rng);
+        }
+        else if(mode == 1){
+            rlt::forward(device, net, input, buffers, rng);
+            auto out = rlt::output(device, net);
+            auto out_m = rlt::matrix_view(device, out);
+            rlt::nn::loss_functions::mse::gradient(device, out_m, tgt, d_output, (T)1);
+            rlt::backward(device, net, input, d_output, buffers);
+        }
+        else if(mode == 2){
+            for(int s = 0; s < n_steps; s++){
+                rlt::zero_gradient(device, net);
+                rlt::forward(device, net, input, buffers, rng);
+                auto out = rlt::output(device, net);
+                auto out_m = rlt::matrix_view(device, out);
+                rlt::nn::loss_functions::mse::gradient(device, out_m, tgt, d_output, (T)1);
+                rlt::backward(device, net, input, d_output, buffers);
+                rlt::step(device, optimizer, net);
+            }
+        }
+        else if(mode == 3){
+            rlt::forward(device, net, input, buffers, rng);
+            rlt::copy(device, device, tgt, d_output);
+            rlt::backward_full(device, net, input, d_output, d_input, buffers);
+        }
+        auto t1 = std::chrono::steady_clock::now();
+        if(seconds) *seconds = std::chrono::duration<double>(t1 - t0).count();
+        if(mode == 0){
+            if(act_out) for(TI b = 0; b < B; b++) for(TI o = 0; o < O; o++) act_out[b * O + o] = rlt::get(output, b, o);
+        }
+        else{
+            float* pre = pre_out; float* ao = act_out;
+            for_each_layer(net, [&](auto& layer){ store_acts(device, layer, pre, ao); });
+        }
+        if(d_input_out && mode == 3) for(TI b = 0; b < B; b++) for(TI i = 0; i < I; i++) d_input_out[b * I + i] = rlt::get(d_input, b, i);
+        float* p;
+        p = params_out; for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, PARAMS); });
+        p = grads_out;  for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, GRADS); });
+        p = m_out;      for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, MOM1); });
+        p = v_out;      for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, MOM2); });
+        rlt::free(device, input); rlt::free(device, d_input); rlt::free(device, output); rlt::free(device, tgt); rlt::free(device, d_output);
+        rlt::free(device, net); rlt::free(device, buffers); rlt::free(device, optimizer);
+    }
+    static MlpVTable vtable(){
+        return MlpVTable{(int)B, (int)I, (int)H, (int)O, (int)NL, (int)HACT, (int)OACT, &run};
+    }
+};
+
+static int act_to_int(act::ActivationFunction a){
+    switch(a){ case act::IDENTITY: return 0; case act::RELU: return 1; case act::TANH: return 2; case act::FAST_TANH: return 3; case act::SIGMOID: return 4; default: return -1; }
+}
+
+#define MLP_CASES(X) \
+    X(c1_actor_eval,   256,  3,  64,   2, 3, act::RELU, act::IDENTITY) \
+    X(c2_actor_b256,   256,  3,  64,   1, 3, act::RELU, act::TANH) \
+    X(c3_critic,       256,  4, 256,   1, 3, act::RELU, act::IDENTITY) \
+    X(c4_actor_b2048, 2048, 27,  64,   8, 3, act::TANH, act::IDENTITY) \
+    X(c4_critic_b2048,2048, 27,  64,   1, 3, act::TANH, act::IDENTITY) \
+    X(c5_b1024,       1024, 64, 256,  16, 4, act::RELU, act::IDENTITY) \
+    X(sweep_b1,          1, 256, 10, 100, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b2,          2, 256, 10, 100, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b32,        32, 256, 10, 100, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b1024,    1024, 256, 10, 100, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b10,        10, 256,200, 100, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b9,          9, 256, 60, 100, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b200,      200, 256, 11, 100, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b64,        64, 256, 50, 101, 3, act::RELU, act::IDENTITY) \
+    X(sweep_b256,      256, 256,256, 256, 3, act::RELU, act::IDENTITY) \
+    X(tanh_b17,         17,   5, 33,   7, 4, act::TANH, act::TANH) \
+    X(fast_tanh_b33,    33,  13, 20,   3, 3, act::FAST_TANH, act::SIGMOID)
+
+static std::map<std::string, MlpVTable>& registry(){
+    static std::map<std::string, MlpVTable> r;
+    if(r.empty()){
+#define X(name, B, I, H, O, NL, HACT, OACT) r[#name] = MlpCase<B, I, H, O, NL, HACT, OACT>::vtable();
+        MLP_CASES(X)
+#undef X
+    }
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Pendulum + actor rollout with the reference functions (semantics of the off-policy runner's
+// prologue / interlude / epilogue for deterministic actions: observe -> evaluate -> step + reward).
+// ---------------------------------------------------------------------------------------------------------
+template <TI CHUNK>
+struct Rollout{
+    using CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
+    using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, CHUNK, 3>;
+    using NET = rlt::nn_models::mlp::NeuralNetwork<CONFIG, rlt::nn::capability::Forward<>, INPUT_SHAPE>;
+
+    // states [N,2] (theta, theta_dot) in/out; episode_step [N] in/out; truncated [N] in/out (uint8);
+    // reset_states [R,N,2]: the k-th reset of env e during this call takes reset_states[k][e] (k counts per env).
+    // outputs obs [T*N,3], act [T*N,1], rew [T*N,1], row t*N+e.
+    static int run(const float* params, TI N, TI Tsteps, float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                   const float* reset_states, TI R, TI step_limit, float* obs, float* actions, float* rew, int num_threads){
+        if(N % CHUNK != 0) return -1;
+        DEVICE device;
+        RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+        NET net; typename NET::template Buffer<> buffers;
+        rlt::malloc(device, net); rlt::malloc(device, buffers);
+        { const float* p = params;
+          load_layer(device, net.input_layer, p); load_layer(device, net.hidden_layers[0], p); load_layer(device, net.output_layer, p); }
+        PENDULUM env; typename PENDULUM::Parameters env_params;
+        std::vector<TI> reset_count(N, 0);
+        int rc = 0;
+        for(TI t = 0; t < Tsteps; t++){
+            float* obs_t = obs + (size_t)t * N * 3;
+            float* act_t = actions + (size_t)t * N;
+            float* rew_t = rew + (size_t)t * N;
+            auto prologue = [&](TI begin, TI end){
+                for(TI e = begin; e < end; e++){
+                    if(truncated[e]){
+                        if(reset_count[e] >= R){ rc = -2; continue; }
+                        states[2 * e + 0] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 0];
+                        states[2 * e + 1] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 1];
+                        reset_count[e]++;
+                        episode_step[e] = 0;
+                        episode_return[e] = 0;
+                    }
+                    typename PENDULUM::State s; s.theta = states[2 * e]; s.theta_dot = states[2 * e + 1];
+                    rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 3, false>> o;
+                    rlt::observe(device, env, env_params, s, typename PENDULUM::Observation{}, o, rng);
+                    for(TI k = 0; k < 3; k++) obs_t[3 * e + k] = rlt::get(o, 0, k);
+                }
+            };
+            auto epilogue = [&](TI begin, TI end){
+                for(TI e = begin; e < end; e++){
+                    typename PENDULUM::State s, ns; s.theta = states[2 * e]; s.theta_dot = states[2 * e + 1];
+                    rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 1, false>> a;
+                    rlt::set(a, 0, 0, act_t[e]);
+                    rlt::step(device, env, env_params, s, a, ns, rng);
+                    T r = rlt::reward(device, env, env_params, s, a, ns, rng);
+                    bool terminated_flag = rlt::terminated(device, env, env_params, ns, rng);
+                    episode_step[e] += 1;
+                    episode_return[e] += r;
+                    truncated[e] = terminated_flag || ((TI)episode_step[e] == step_limit);
+                    rew_t[e] = r;
+                    states[2 * e] = ns.theta; states[2 * e + 1] = ns.theta_dot;
+                }
+            };
+            auto fan_out = [&](auto& f){
+                if(num_threads <= 1){ f(0, N); return; }
+                std::vector<std::thread> threads;
+                TI per = (N + num_threads - 1) / num_threads;
+                for(int th = 0; th < num_threads; th++){
+                    TI b = th * per, e = std::min<TI>(N, b + per);
+                    if(b < e) threads.emplace_back([&f, b, e](){ f(b, e); });
+                }
+                for(auto& th: threads) th.join();
+            };
+            fan_out(prologue);
+            for(TI c = 0; c < N; c += CHUNK){
+                rlt::Matrix<rlt::matrix::Specification<T, TI, CHUNK, 3, true, rlt::matrix::layouts::RowMajorAlignment<TI, 1>>> in;
+                rlt::Matrix<rlt::matrix::Specification<T, TI, CHUNK, 1, true, rlt::matrix::layouts::RowMajorAlignment<TI, 1>>> out;
+                in._data = obs_t + (size_t)c * 3;
+                out._data = act_t + c;
+                rlt::evaluate(device, net, in, out, buffers, rng);
+            }
+            fan_out(epilogue);
+        }
+        rlt::free(device, net); rlt::free(device, buffers);
+        return rc;
+    }
+};
+
+extern "C" {
+
+int ref_num_cases(){ return (int)registry().size(); }
+const char* ref_case_name(int i){
+    auto it = registry().begin(); std::advance(it, i); return it->first.c_str();
+}
+// dims[7] = batch, input_dim, hidden_dim, output_dim, num_layers, hidden_act, output_act  (activation ids: see act_from_int)
+int ref_case_dims(const char* name, int* dims){
+    auto it = registry().find(name); if(it == registry().end()) return -1;
+    const MlpVTable& v = it->second;
+    dims[0] = v.batch; dims[1] = v.input_dim; dims[2] = v.hidden_dim; dims[3] = v.output_dim; dims[4] = v.num_layers;
+    dims[5] = act_to_int((act::ActivationFunction)v.hidden_act); dims[6] = act_to_int((act::ActivationFunction)v.output_act);
+    return 0;
+}
+int ref_mlp_run(const char* name, const float* params_in, uint32_t init_seed, const float* x, const float* target, int mode, int n_steps,
+                float* params_out, float* grads_out, float* m_out, float* v_out, float* pre_out, float* act_out, float* d_input_out, double* seconds){
+    auto it = registry().find(name); if(it == registry().end()) return -1;
+    it->second.run(params_in, init_seed, x, target, mode, n_steps, params_out, grads_out, m_out, v_out, pre_out, act_out, d_input_out, seconds);
+    return 0;
+}
+
+// raw reference RNG streams (random/operations_cpu.h): engine seeded with seed+1
+void ref_rng_uniform(uint32_t seed, int n, float lo, float hi, float* out){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    for(int i = 0; i < n; i++) out[i] = rlt::random::uniform_real_distribution(device.random, lo, hi, rng);
+}
+void ref_rng_normal(uint32_t seed, int n, float mean, float std, float* out){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    for(int i = 0; i < n; i++) out[i] = rlt::random::normal_distribution::sample(device.random, mean, std, rng);
+}
+// interleaved stream: kinds[i] == 0 -> uniform(lo[i], hi[i]); 1 -> normal(mean=lo[i], std=hi[i])
+void ref_rng_mixed(uint32_t seed, int n, const uint8_t* kinds, const float* a, const float* b, float* out){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    for(int i = 0; i < n; i++){
+        out[i] = kinds[i] == 0 ? rlt::random::uniform_real_distribution(device.random, a[i], b[i], rng)
+                               : rlt::random::normal_distribution::sample(device.random, a[i], b[i], rng);
+    }
+}
+// n envs, sample_initial_state in env order from one engine; states [n,2]
+void ref_pendulum_initial_states(uint32_t seed, int n, float* states){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    PENDULUM env; typename PENDULUM::Parameters env_params;
+    for(int e = 0; e < n; e++){
+        typename PENDULUM::State s;
+        rlt::sample_initial_state(device, env, env_params, s, rng);
+        states[2 * e] = s.theta; states[2 * e + 1] = s.theta_dot;
+    }
+}
+// element-wise reference env functions on n independent (state, action) pairs
+void ref_pendulum_step(int n, const float* states, const float* actions, float* next_states, float* rewards, float* obs, float* next_obs){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    PENDULUM env; typename PENDULUM::Parameters env_params;
+    for(int e = 0; e < n; e++){
+        typename PENDULUM::State s, ns; s.theta = states[2 * e]; s.theta_dot = states[2 * e + 1];
+        rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 1, false>> a; rlt::set(a, 0, 0, actions[e]);
+        rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 3, false>> o;
+        rlt::step(device, env, env_params, s, a, ns, rng);
+        rewards[e] = rlt::reward(device, env, env_params, s, a, ns, rng);
+        next_states[2 * e] = ns.theta; next_states[2 * e + 1] = ns.theta_dot;
+        if(obs){ rlt::observe(device, env, env_params, s, typename PENDULUM::Observation{}, o, rng); for(int k = 0; k < 3; k++) obs[3 * e + k] = rlt::get(o, 0, k); }
+        if(next_obs){ rlt::observe(device, env, env_params, ns, typename PENDULUM::Observation{}, o, rng); for(int k = 0; k < 3; k++) next_obs[3 * e + k] = rlt::get(o, 0, k); }
+    }
+}
+int ref_pendulum_episode_step_limit(){ return (int)PENDULUM::EPISODE_STEP_LIMIT; }
+
+// chunk: batch size of each reference evaluate() call (compile-time in the reference): 1, 256 or 65536
+int ref_pendulum_rollout(int chunk, const float* params, int N, int Tsteps, float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                         const float* reset_states, int R, int step_limit, float* obs, float* actions, float* rew, int num_threads){
+    switch(chunk){
+        case 1:     return Rollout<1>::run(params, N, Tsteps, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew, num_threads);
+        case 256:   return Rollout<256>::run(params, N, Tsteps, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew, num_threads);
+        case 65536: return Rollout<65536>::run(params, N, Tsteps, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew, num_threads);
+        default: return -3;
+    }
+}
+int ref_uses_openblas(){
+#ifdef REF_USE_OPENBLAS
+    return 1;
+#else
+    return 0;
+#endif
+}
+}

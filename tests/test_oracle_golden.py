@@ -1,0 +1,109 @@
+"""The CPU oracle (oracle/oracle.c) against the golden fixtures produced by the REAL reference
+(tests/golden/make_golden.py). Everything here is bit-exact: the oracle restates the reference's generic-device
+loop order with the same strict floating-point flags."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import make_golden as mg
+from conftest import GOLDEN
+import oracle
+
+
+def test_rng_streams_match_reference(orc):
+    fix = np.load(os.path.join(GOLDEN, "rng.npz"))
+    for seed in (0, 1, 12345):
+        assert np.array_equal(orc.uniform_stream(seed, 1024, -np.float32(np.pi), np.float32(np.pi)), fix[f"uniform_{seed}"])
+        assert np.array_equal(orc.normal_stream(seed, 1024, 0.25, 1.5), fix[f"normal_{seed}"])
+        kinds = (np.arange(1024) % 3 == 0).astype(np.uint8)
+        a = np.where(kinds == 0, -1.0, 0.0).astype(np.float32)
+        b = np.where(kinds == 0, 1.0, 0.5).astype(np.float32)
+        assert np.array_equal(orc.mixed_stream(seed, kinds, a, b), fix[f"mixed_{seed}"])
+        assert np.array_equal(orc.pendulum_initial_states(seed, 1024), fix[f"initial_states_{seed}"])
+
+
+def test_pendulum_step_reward_observe(orc):
+    fix = np.load(os.path.join(GOLDEN, "pendulum_step.npz"))
+    ns, r, obs, nobs = orc.pendulum_step(fix["states"], fix["actions"])
+    assert np.array_equal(ns, fix["next_states"])
+    assert np.array_equal(r, fix["rewards"])
+    assert np.array_equal(obs, fix["obs"])
+    assert np.array_equal(nobs, fix["next_obs"])
+
+
+def _case_from_dims(d):
+    return dict(batch=int(d[0]), input_dim=int(d[1]), hidden_dim=int(d[2]), output_dim=int(d[3]), num_layers=int(d[4]),
+                hidden_act=int(d[5]), output_act=int(d[6]))
+
+
+MLP_FIXTURES = sorted(glob.glob(os.path.join(GOLDEN, "mlp_*.npz")))
+
+
+@pytest.mark.parametrize("path", MLP_FIXTURES, ids=[os.path.basename(p)[4:-4] for p in MLP_FIXTURES])
+def test_mlp_forward_backward_adam(orc, path):
+    fix = np.load(path)
+    name = os.path.basename(path)[4:-4]
+    c = _case_from_dims(fix["dims"])
+    shape = oracle.Reference.case_shape(c)
+    params, x, target = mg.mlp_inputs(c, mg.case_seed(name))
+    B, O = c["batch"], c["output_dim"]
+
+    def check(key, arr):
+        s, tot = mg.sample(arr)
+        assert np.array_equal(s, fix[key]), key
+        assert tot == fix[key + "_sum"], key
+
+    check("eval_out", orc.mlp_evaluate(shape, params, x))
+    pre, out = orc.mlp_forward(shape, params, x)
+    check("fwd_pre", pre)
+    check("fwd_out", out)
+    y = np.ascontiguousarray(out[-B * O:].reshape(B, O))
+    d = orc.mse_gradient(y, target, 1.0)
+    grads, _ = orc.mlp_backward(shape, params, np.zeros_like(params), x, pre, out, d)
+    check("bwd_grads", grads)
+    p, g, m, v, _, _ = orc.mlp_train_steps(shape, params, x, target, mg.MLP_STEPS)
+    check("train_params", p)
+    check("train_grads", g)
+    check("train_m", m)
+    check("train_v", v)
+    grads_full, d_in = orc.mlp_backward(shape, params, np.zeros_like(params), x, pre, out, target, want_d_input=True)
+    check("full_grads", grads_full)
+    check("full_d_input", d_in)
+
+
+def test_rollout_with_resets(orc):
+    fix = np.load(os.path.join(GOLDEN, "rollout.npz"))
+    N, T, limit = int(fix["N"]), int(fix["T"]), int(fix["step_limit"])
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    ro = orc.pendulum_rollout(shape, fix["actor_params"], np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8),
+                              np.zeros(N, np.float32), fix["reset_table"], T, limit)
+    for k in ("obs", "act", "rew", "states", "episode_step", "truncated", "episode_return"):
+        assert np.array_equal(ro[k], fix[k]), k
+    # the reset table in the fixture is the reference engine's stream in the runner's draw order
+    table = orc.reset_table(int(fix["reset_seed"]), N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), limit, 3)
+    assert np.array_equal(table, fix["reset_table"])
+
+
+def test_rollout_staggered_counters(orc):
+    fix = np.load(os.path.join(GOLDEN, "rollout_staggered.npz"))
+    base = np.load(os.path.join(GOLDEN, "rollout.npz"))
+    N = int(base["N"])
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    ro = orc.pendulum_rollout(shape, base["actor_params"], fix["states0"], fix["episode_step0"], fix["truncated0"], np.zeros(N, np.float32),
+                              base["reset_table"], int(fix["T"]), 200)
+    for k in ("obs", "act", "rew"):
+        assert np.array_equal(ro[k][::7], fix[k]), k
+    for k in ("states", "episode_step", "truncated", "episode_return"):
+        assert np.array_equal(ro[k], fix[k]), k
+
+
+def test_kaiming_init_bounds_from_reference_engine():
+    """The fixture's actor came from the reference's init_weights (legacy Kaiming-uniform): every layer is bounded
+    by 1/sqrt(fan_in) and the first values are the reference engine's uniform stream (bias first, then the row)."""
+    fix = np.load(os.path.join(GOLDEN, "rollout.npz"))
+    p = fix["actor_params"]
+    assert p.size == 3 * 64 + 64 + 64 * 64 + 64 + 64 + 1
+    assert np.abs(p[:256]).max() <= 1 / np.sqrt(3) + 1e-7
+    assert np.abs(p[256:256 + 64 * 64 + 64]).max() <= 1 / 8 + 1e-7

@@ -1,0 +1,55 @@
+"""The CPU oracle against the REAL reference run live (oracle/_ref, built from the unmodified RLtools headers).
+Skipped where the reference build is absent; the committed golden fixtures cover those machines."""
+import numpy as np
+import pytest
+
+import make_golden as mg
+import oracle
+
+
+def test_rng_streams_live(orc, ref_strict):
+    for seed in (3, 99):
+        assert np.array_equal(orc.uniform_stream(seed, 4000, -2.5, 0.75), ref_strict.uniform_stream(seed, 4000, -2.5, 0.75))
+        assert np.array_equal(orc.normal_stream(seed, 4000, -1.0, 0.3), ref_strict.normal_stream(seed, 4000, -1.0, 0.3))
+        assert np.array_equal(orc.pendulum_initial_states(seed, 3000), ref_strict.pendulum_initial_states(seed, 3000))
+    # std == 0 returns the mean and consumes nothing (random/operations_cpu.h:41-43)
+    kinds = np.array([1, 0, 1, 0], np.uint8)
+    a = np.array([5.0, -1.0, 0.0, -1.0], np.float32)
+    b = np.array([0.0, 1.0, 1.0, 1.0], np.float32)
+    assert np.array_equal(orc.mixed_stream(4, kinds, a, b), ref_strict.mixed_stream(4, kinds, a, b))
+
+
+def test_pendulum_live(orc, ref_strict):
+    st = np.stack([mg.det_uniform(11, 50000, -40, 40), mg.det_uniform(11, 50000, -9, 9, stream=1)], 1).astype(np.float32)
+    ac = mg.det_uniform(11, 50000, -3, 3, stream=2)
+    for a, b in zip(orc.pendulum_step(st, ac), ref_strict.pendulum_step(st, ac)):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("name", ["c1_actor_eval", "c3_critic", "c4_actor_b2048", "tanh_b17", "fast_tanh_b33", "sweep_b9", "sweep_b200"])
+def test_mlp_live(orc, ref_strict, name):
+    c = ref_strict.cases()[name]
+    shape = ref_strict.case_shape(c)
+    params, x, target = mg.mlp_inputs(c, seed=4242)
+    ref = ref_strict.mlp_run(name, params, x, target, 2, 4)
+    p, g, m, v, pre, out = orc.mlp_train_steps(shape, params, x, target, 4)
+    for k, arr in (("params", p), ("grads", g), ("m", m), ("v", v), ("pre", pre), ("out", out)):
+        assert np.array_equal(arr, ref[k]), k
+    full = ref_strict.mlp_run(name, params, x, target, 3)
+    pre, out = orc.mlp_forward(shape, params, x)
+    grads, d_in = orc.mlp_backward(shape, params, np.zeros_like(params), x, pre, out, target, want_d_input=True)
+    assert np.array_equal(grads, full["grads"])
+    assert np.array_equal(d_in, full["d_input"])
+
+
+def test_rollout_live_chunked_evaluate(orc, ref_strict):
+    """Reference evaluate() on 256-env batches (the way the runner calls it) equals the per-env oracle bit for bit
+    on the generic device, because each output element is the same left-to-right sum."""
+    N, T = 512, 230
+    actor = ref_strict.mlp_run("c2_actor_b256", None, None, None, 0, init_seed=3)["params"]
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    table = orc.reset_table(8, N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), 200, 2)
+    a = orc.pendulum_rollout(shape, actor, np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32), table, T)
+    b = ref_strict.pendulum_rollout(actor, np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32), table, T, chunk=256)
+    for k in a:
+        assert np.array_equal(a[k], b[k]), k

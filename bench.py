@@ -1,0 +1,279 @@
+#!/usr/bin/env python
+"""Benchmark of the fused Pendulum rollout (actor forward + environment step), the headline metric: env-steps/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one pass of the hot path over one batch: ONE rollout call of 65,536 environments x 200 steps with the
+actor 3 -> 64 -> 64 -> 1 (ReLU, ReLU, tanh), synthetic seeded inputs, outputs obs/act/rew buffers (262 MB, larger
+than L2) written to HBM. With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank rolls out its
+own 65,536 environments (weak scaling, no data-path collective); the time is the max over ranks.
+
+Prints ONE JSON line: device-timed `value` (inputs resident in HBM, CUDA events on the launching stream), `e2e`
+(the host-buffer C-ABI call, host<->device copies inside the timed region), `roofline` for the rollout kernel
+against the measured peak, `cpu_baseline` (the reference's own CPU path timed on this box's cores), `clocks`.
+`--impl reference` times only the reference CPU implementation, on the same metric and config.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_ENVS, N_STEPS, STEP_LIMIT = 65536, 200, 200
+FLOP_PER_ENV_STEP = 2 * (3 * 64 + 64 * 64 + 64 * 1)      # 8,704: actor GEMMs only, no padding, no 3x for any split
+BYTES_PER_ENV_STEP = 20                                   # obs 12 + action 4 + reward 4 written per env-step
+WORKLOAD = "pendulum_rollout_65536env_x200step_actor3-64-64-1"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops=float(p["bf16_tflops"]), hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [int(s[0]) for s in self.samples]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons, "samples": len(sm)}
+
+
+def synthetic_inputs(seed, n_envs):
+    """Seeded stand-in for the Pendulum-v1 rollout: actor weights U(+-1/sqrt(fan_in)) (the reference initialiser's
+    bound), reset states theta ~ U[-pi, pi], theta_dot ~ U[-1, 1] from the reference-compatible engine."""
+    import numpy as np
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    rng = np.random.default_rng(seed)
+    parts, fan_in = [], 3
+    for d in (64, 64, 1):
+        parts.append((rng.uniform(-1, 1, d * fan_in + d) / np.sqrt(fan_in)).astype(np.float32))
+        fan_in = d
+    params = np.concatenate(parts)
+    table, _ = pkg.reset_table_host(seed, n_envs, N_STEPS, np.zeros(n_envs, np.int32), np.ones(n_envs, np.uint8), STEP_LIMIT, 1)
+    return params, table
+
+
+class CpuReference:
+    """The reference's own CPU path (oracle/_ref: unmodified RLtools headers, CPU_OPENBLAS device, project flags, all
+    host threads) on the same rollout; falls back to the plain-C oracle port (1 thread) where that build is absent."""
+
+    def __init__(self):
+        import numpy as np
+        self.cores = os.cpu_count() or 1
+        os.environ.setdefault("OPENBLAS_NUM_THREADS", str(self.cores))
+        import oracle
+        rng = np.random.default_rng(0)
+        parts, fan_in = [], 3
+        for d in (64, 64, 1):
+            parts.append((rng.uniform(-1, 1, d * fan_in + d) / np.sqrt(fan_in)).astype(np.float32))
+            fan_in = d
+        params = np.concatenate(parts)
+        orc = oracle.Oracle()
+        N = N_ENVS
+        table = orc.reset_table(0, N, 1, np.zeros(N, np.int32), np.ones(N, np.uint8), STEP_LIMIT, 1)
+        st, es, tr, er = np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32)
+        if os.path.exists(oracle.REF_FAST_SO):
+            ref = oracle.Reference("fast")
+            self.kind, self.threads = "reference", self.cores
+            self.run = lambda T: ref.pendulum_rollout(params, st, es, tr, er, table, T, STEP_LIMIT, chunk=65536, num_threads=self.cores)
+        else:
+            self.kind, self.threads = "port", 1
+            shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+            self.run = lambda T: orc.pendulum_rollout(shape, params, st, es, tr, er, table, T, STEP_LIMIT)
+        t0 = time.perf_counter(); self.run(2); self.sec_per_env_step_batch = (time.perf_counter() - t0) / 2
+
+    def sample_steps(self, seconds):
+        return int(max(2, min(N_STEPS, seconds / max(self.sec_per_env_step_batch, 1e-6))))
+
+    def timed(self, T):
+        t0 = time.perf_counter(); self.run(T)
+        return N_ENVS * T / (time.perf_counter() - t0)
+
+    def describe(self, T, reps, value):
+        return {"value": value, "unit": "env-steps/s", "cores": self.threads, "kind": self.kind,
+                "sample": f"{N_ENVS} envs x {T} steps of the same rollout (observe -> evaluate -> step/reward), median of {reps}"}
+
+
+def cpu_reference_rate(seconds_budget=15.0, reps=3):
+    cpu = CpuReference()
+    T = cpu.sample_steps(seconds_budget / reps)
+    return cpu.describe(T, reps, statistics.median(cpu.timed(T) for _ in range(reps)))
+
+
+def run_reference(args):
+    """--impl reference: each step is a bounded sample of the workload, sized so the whole run ends within ~2 minutes."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cpu = CpuReference()
+    T = cpu.sample_steps(120.0 / max(1, args.warmup + args.steps))
+    for _ in range(args.warmup):
+        cpu.timed(T)
+    rates = [cpu.timed(T) for _ in range(args.steps)]
+    rate = statistics.median(rates)
+    line = {"impl": "reference", "metric": "env-steps/s (fused actor fwd + env step)", "value": rate, "unit": "env-steps/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * N_ENVS * T / rate, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "timed_on": "host CPU cores"},
+            "cpu_baseline": cpu.describe(T, args.steps, rate), "e2e": {"value": rate, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    pkg.lib()                                     # fails loudly if the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    shape = pkg.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    params_h, table_h = synthetic_inputs(seed=rank, n_envs=N_ENVS)
+    t = lambda a: torch.from_numpy(a).to(dev)
+    params, table = t(params_h), t(table_h)
+    states, es, tr, er = (torch.zeros((N_ENVS, 2), device=dev), torch.zeros(N_ENVS, dtype=torch.int32, device=dev),
+                          torch.ones(N_ENVS, dtype=torch.uint8, device=dev), torch.zeros(N_ENVS, device=dev))
+    rows = N_ENVS * N_STEPS
+    obs, act, rew = torch.empty((rows, 3), device=dev), torch.empty((rows, 1), device=dev), torch.empty((rows, 1), device=dev)
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)   # 256 MB > 126 MB L2
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step():
+        # every episode is exactly 200 steps, so each call starts with all environments truncated -> reset from the table
+        pkg.pendulum_rollout(shape, params, states, es, tr, er, table, N_STEPS, STEP_LIMIT, obs=obs, act=act, rew=rew, error_flag=flag)
+
+    for _ in range(args.warmup):
+        flush.zero_(); step()
+    barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        wall0 = time.perf_counter()
+        for i in range(args.steps):
+            flush.zero_()                          # L2 flush between timed iterations (not inside the event pair)
+            starts[i].record(); step(); stops[i].record()
+        barrier()
+        wall = time.perf_counter() - wall0
+    assert int(flag.item()) == 0
+    dev_ms = sum(a.elapsed_time(b) for a, b in zip(starts, stops))
+    tm = torch.tensor([dev_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    total_ms = float(tm.item())
+    ms_per_step = total_ms / args.steps
+    value = world * N_ENVS * N_STEPS * args.steps / (total_ms * 1e-3)
+
+    # ---- end to end: host buffers through the C ABI, copies inside the timed region ----
+    pin = lambda *s, dtype=torch.float32: torch.empty(*s, dtype=dtype).pin_memory()
+    h_obs, h_act, h_rew = pin(rows, 3), pin(rows, 1), pin(rows, 1)
+    h_states, h_es, h_tr, h_er = pin(N_ENVS, 2), pin(N_ENVS, dtype=torch.int32), pin(N_ENVS, dtype=torch.uint8), pin(N_ENVS)
+    h_table, h_params = pin(*table_h.shape), pin(params_h.size)
+    h_table.copy_(torch.from_numpy(table_h)); h_params.copy_(torch.from_numpy(params_h))
+    h_states.zero_(); h_es.zero_(); h_tr.fill_(1); h_er.zero_()
+
+    def e2e_step():
+        pkg.pendulum_rollout_host(shape, h_params, h_states, h_es, h_tr, h_er, h_table, N_STEPS, h_obs, h_act, h_rew, STEP_LIMIT)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_value = world * N_ENVS * N_STEPS * args.e2e_steps / float(e2e_s.item())
+    h2d = params_h.nbytes + table_h.nbytes + N_ENVS * (8 + 4 + 1 + 4)
+    d2h = rows * BYTES_PER_ENV_STEP + N_ENVS * (8 + 4 + 1 + 4) + 4
+    pkg.lib().b200rl_release_host_staging()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        achieved_tflops = FLOP_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved_tflops / peaks["tflops"],
+                    "traffic": None, "peak_source": peaks["source"] + " bf16 dense (burst)",
+                    "hbm_write_gbs": BYTES_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]}
+        cpu = None if args.no_cpu_baseline else cpu_reference_rate()
+        line = {"metric": "env-steps/s (fused actor fwd + env step)", "value": value, "unit": "env-steps/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": WORKLOAD, "envs_per_gpu": N_ENVS, "steps_per_env": N_STEPS, "l2": "flushed between timed iterations; outputs (262 MB) exceed L2",
+                                                "parallelism": f"env-sharded x{world}, no collective"},
+                "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
+                "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps},
+                "gpu_launches": args.steps, "wall_s_timed_region": wall}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

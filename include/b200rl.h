@@ -1,0 +1,179 @@
+/*
+ * b200rl.h -- C ABI of libb200rl.so: the sm_100a kernels for the RLtools hot path
+ * (dense layer evaluate/forward/backward, MSE gradient, Adam, and the batched Pendulum environment step that the
+ * runners interleave with actor inference).
+ *
+ * Conventions
+ *   - every entry point returns an int status (B200RL_OK == 0); nothing aborts, nothing throws;
+ *   - all pointers are DEVICE pointers unless the parameter name ends in _host;
+ *   - matrices are row-major fp32 with an explicit row pitch in ELEMENTS (ld*), so views into wider tables work
+ *     (the reference's Matrix views carry a row pitch, containers/matrix/matrix.h:84-85); column pitch is 1;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued asynchronously on it, no entry point
+ *     synchronises or allocates unless its comment says so;
+ *   - "reference" citations are paths inside the RLtools tree (include/rl_tools/...).
+ */
+#ifndef B200RL_H
+#define B200RL_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200RL_OK 0
+#define B200RL_ERR_INVALID_ARGUMENT 1   /* null pointer, negative size, pitch smaller than the row */
+#define B200RL_ERR_UNSUPPORTED 2        /* a shape / activation this build has no kernel for */
+#define B200RL_ERR_CUDA 3               /* a CUDA runtime call failed; see b200rl_last_cuda_error() */
+#define B200RL_ERR_DEVICE_FLAG 4        /* a kernel reported a problem through its error flag */
+
+/* activation ids: nn/activation_functions.h:10-20 */
+#define B200RL_ACT_IDENTITY 0
+#define B200RL_ACT_RELU 1
+#define B200RL_ACT_TANH 2
+#define B200RL_ACT_FAST_TANH 3
+#define B200RL_ACT_SIGMOID 4
+
+#define B200RL_MAX_LAYERS 8
+
+typedef void* b200rl_stream_t; /* cudaStream_t */
+
+int b200rl_version(void);
+const char* b200rl_status_string(int status);
+/* text of the last CUDA error seen by this library on the calling thread ("" if none) */
+const char* b200rl_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Dense layer. W is [O, I] row-major (weights.parameters), bias is [O].
+ * ------------------------------------------------------------------------------------------------------- */
+
+/* y = act(x W^T + b); if pre != NULL the pre-activations are stored as well.
+ * Replaces evaluate (nn/layers/dense/operations_cuda.h:236-274: set_biases_kernel + cublasSgemm +
+ * activation_kernel) when pre == NULL and forward (:276-316, which adds a device-to-device copy of the
+ * pre-activations) when pre != NULL -- one launch instead of three or four. x must not alias y. */
+int b200rl_dense_forward(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
+                         int batch, int input_dim, int output_dim, int activation, b200rl_stream_t stream);
+
+/* d_pre = act'(pre) * d_out (written back into d_out, as the reference does);
+ * d_bias[o] += sum_b d_pre[b][o];  d_W[o][i] += sum_b d_pre[b][o] * x[b][i];  d_in[b][i] = sum_o d_pre[b][o] W[o][i].
+ * Gradients ACCUMULATE (zero them with b200rl_fill). d_in == NULL skips the input gradient (first layer),
+ * d_W == d_bias == NULL gives backward_input.
+ * Replaces backward / backward_full / backward_input (nn/layers/dense/operations_cuda.h:358-413:
+ * d_activation_accumulate_bias_gradient_kernel + two cublasSgemm).
+ * `scratch` is device memory of at least b200rl_dense_backward_scratch_bytes(...) bytes (may be NULL when that
+ * returns 0); it holds split-batch partial sums of d_W and d_bias that are reduced in a fixed order, so the
+ * result does not depend on scheduling. */
+size_t b200rl_dense_backward_scratch_bytes(int batch, int input_dim, int output_dim);
+int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
+                          float* d_W, float* d_bias, float* d_in, int ldi, int batch, int input_dim, int output_dim, int activation,
+                          void* scratch, size_t scratch_bytes, b200rl_stream_t stream);
+
+/* d_a = 2 w (a - b) / (rows cols). Replaces nn::loss_functions::mse::gradient (nn/loss_functions/mse/operations_cuda.h:41-58). */
+int b200rl_mse_gradient(const float* a, int lda, const float* b, int ldb, float* d_a, int ldd, int rows, int cols, float loss_weight,
+                        b200rl_stream_t stream);
+
+/* dst[0..n) = value. Replaces the cudaMemsetAsync pairs of zero_gradient / _reset_optimizer_state
+ * (nn/layers/dense/operations_cuda.h:415-432) -- with the flat arena below it is one call per network. */
+int b200rl_fill(float* dst, size_t n, float value, b200rl_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * MLP on a flat parameter arena. For each layer l: W_l [O_l, I_l] row-major, then b_l [O_l]; gradients and both
+ * Adam moments use the same layout in their own arenas, so zero_gradient, the optimizer step and a gradient
+ * all-reduce are each ONE pass over contiguous memory (the reference allocates 8 tensors per layer,
+ * nn/layers/dense/layer.h:82-127, nn/optimizers/adam/adam.h:88-95).
+ * ------------------------------------------------------------------------------------------------------- */
+typedef struct {
+    int n_layers;                    /* 1..B200RL_MAX_LAYERS */
+    int input_dim;
+    int dims[B200RL_MAX_LAYERS];     /* output dim per layer */
+    int acts[B200RL_MAX_LAYERS];     /* activation per layer */
+} b200rl_mlp_shape;
+
+size_t b200rl_mlp_num_params(const b200rl_mlp_shape* shape);
+
+/* y [batch, O_last] = mlp(x); no state is kept. tick/tock are two [batch, max hidden dim] ping-pong buffers
+ * (nn_models::mlp buffers, nn_models/mlp/network.h). Replaces nn_models::mlp evaluate
+ * (nn_models/mlp/operations_generic.h:77-102 recursing into the dense CUDA ops). */
+int b200rl_mlp_evaluate(const b200rl_mlp_shape* shape, const float* params, const float* x, int ldx, float* y, int ldy,
+                        float* tick, float* tock, int batch, b200rl_stream_t stream);
+
+/* forward that keeps per-layer pre-activations and outputs, concatenated layer after layer, each [batch, O_l]
+ * dense. Replaces nn_models::mlp forward (nn_models/mlp/operations_generic.h:103-120). */
+int b200rl_mlp_forward(const b200rl_mlp_shape* shape, const float* params, const float* x, int ldx, float* pre, float* out,
+                       int batch, b200rl_stream_t stream);
+
+/* backward through all layers; d_out [batch, O_last] is clobbered; grads accumulate; d_input may be NULL
+ * (input layer then gets the weights-only backward, nn_models/mlp/operations_generic.h:180-204; non-NULL gives
+ * backward_full :152-179). tick/tock: two [batch, max(dim)] buffers. scratch as for b200rl_dense_backward with the
+ * largest layer. */
+size_t b200rl_mlp_backward_scratch_bytes(const b200rl_mlp_shape* shape, int batch);
+int b200rl_mlp_backward(const b200rl_mlp_shape* shape, const float* params, float* grads, const float* x, int ldx, const float* pre,
+                        const float* out, float* d_out, float* d_input, float* tick, float* tock, int batch,
+                        void* scratch, size_t scratch_bytes, b200rl_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Adam. Hyper-parameters as nn::optimizers::adam::Parameters (nn/optimizers/adam/adam.h:13-25).
+ * ------------------------------------------------------------------------------------------------------- */
+typedef struct {
+    float alpha, beta_1, beta_2, epsilon, epsilon_sqrt;
+} b200rl_adam_hyper;
+
+/* Device-resident optimizer state, 4 x 32-bit words: {uint32 age, uint32 ticket, float c1, float c2}.
+ * b200rl_adam_reset sets age = 1 (reset_optimizer_state, nn/optimizers/adam/operations_generic.h:43-46). */
+int b200rl_adam_reset(uint32_t* state, b200rl_stream_t stream);
+
+/* One optimizer step over a flat arena of n parameters, ONE launch:
+ *   c1 = 1/(1-beta_1^age), c2 = 1/(1-beta_2^age), age += 1          (_step, adam/operations_generic.h:49-59)
+ *   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g g;  p -= alpha c1 m / (sqrt(max(v c2, eps_sqrt)) + eps)
+ * Replaces the <<<1,1>>> _step kernel plus one update_kernel per layer (nn/optimizers/adam/operations_cuda.h:56-69,
+ * nn/layers/dense/operations_cuda.h:193-233,434-446). The age lives on the device so the call can sit inside a
+ * captured CUDA graph; the last block to finish bumps it. */
+int b200rl_adam_step(float* params, const float* grads, float* m, float* v, size_t n, b200rl_adam_hyper hyper, uint32_t* state,
+                     b200rl_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Pendulum rollout: T x { reset-if-truncated, observe, actor forward, step, reward, counters } for N environments in
+ * ONE persistent launch. Semantics per step are the off-policy runner's prologue / interlude / epilogue with
+ * deterministic actions (rl/components/off_policy_runner/operations_generic_per_env.h:8-108,
+ * operations_cuda.h:60-115,184-204) on rl::environments::Pendulum with default parameters
+ * (rl/environments/pendulum/pendulum.h:11-25, operations_generic.h:57-160); T == 1 is one runner step.
+ *   states [N,2] (theta, theta_dot), episode_step [N], truncated [N] (0/1), episode_return [N]: in/out runner state
+ *   (truncated starts as 1 so the first step resets, off_policy_runner/operations_generic.h init);
+ *   reset_states [R,N,2]: the k-th reset of env e inside this call takes reset_states[k][e]; the values are drawn on
+ *   the host in the reference engine's order (b200rl_reset_table_host), mirroring how the reference's own CPU<->GPU
+ *   tests feed CPU-drawn noise to the device; may be NULL if no env can reset during the call;
+ *   obs [T*N,3], act [T*N,1], rew [T*N,1]: row t*N + env.
+ *   error_flag (device int, may be NULL) is set to 1 if an env needed more than R resets.
+ * The actor must be 3 -> H -> H -> 1 with H in {64}; activations are free. */
+int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
+                            uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds,
+                            int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
+                            b200rl_stream_t stream);
+
+/* HOST-buffer variant of the above: every pointer except `stream` is host memory (pinned host memory makes the
+ * copies asynchronous). Copies the runner state and reset table in, runs the rollout in env slabs and streams the
+ * obs/act/rew slabs back while the next slab computes; synchronises before returning. Allocates its device staging
+ * on first use and keeps it (freed by b200rl_release_host_staging). This is the call a host-side user of the
+ * runner makes when the rollout data is consumed on the CPU. */
+int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* actor_params_host, float* states_host,
+                                 int32_t* episode_step_host, uint8_t* truncated_host, float* episode_return_host,
+                                 const float* reset_states_host, int n_reset_rounds, int n_envs, int n_steps, int step_limit,
+                                 float* obs_host, float* act_host, float* rew_host, b200rl_stream_t stream);
+int b200rl_release_host_staging(void);
+
+/* Reference-compatible random streams on the HOST (std::mt19937 seeded with seed+1 and libstdc++'s
+ * uniform_real_distribution<float>, exactly what random/operations_cpu.h:21-35 drives), so that resets are
+ * bit-identical to a reference CPU run. rng_state_host is 625 x uint32 owned by the caller. */
+int b200rl_rng_init_host(uint32_t* rng_state_host, uint32_t seed);
+/* Fills reset_states_host [R,N,2] in the runner's draw order (each step, envs ascending, theta then theta_dot for
+ * every truncated env; off_policy_runner/operations_cpu.h:46-50) for a call of n_steps steps starting from the
+ * given counters. Returns the number of reset rounds used in *rounds_used_host. */
+int b200rl_reset_table_host(uint32_t* rng_state_host, int n_envs, int n_steps, const int32_t* episode_step_host,
+                            const uint8_t* truncated_host, int step_limit, float* reset_states_host, int n_reset_rounds,
+                            int* rounds_used_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,280 @@
+"""rl_tools_b200: Python plumbing around libb200rl.so (the sm_100a kernels behind the C ABI in include/b200rl.h).
+
+The library is the product; this module only (a) builds it with nvcc for sm_100a, (b) loads it with ctypes and
+(c) offers thin wrappers that take torch CUDA tensors (device memory + streams come from torch) and pass raw
+pointers through the C ABI. There is no CPU fallback: without the built library every call raises.
+"""
+import ctypes as C
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+LIB_PATH = os.path.join(HERE, "libb200rl.so")
+SOURCES = ["dense.cu", "adam.cu", "rollout.cu", "host_api.cu"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
+
+ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
+MAX_LAYERS = 8
+
+_lib = None
+
+
+class B200RLError(RuntimeError):
+    pass
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every CUDA source into libb200rl.so for sm_100a (nvcc cross-compiles without a GPU)."""
+    srcs = [os.path.join(CSRC, s) for s in SOURCES]
+    deps = srcs + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")] + [os.path.join(ROOT, "include", "b200rl.h")]
+    if not force and os.path.exists(LIB_PATH) and all(os.path.getmtime(LIB_PATH) >= os.path.getmtime(d) for d in deps):
+        return LIB_PATH
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + srcs + ["-o", LIB_PATH]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise B200RLError("nvcc failed:\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stderr)
+    return LIB_PATH
+
+
+class MlpShape(C.Structure):
+    """Mirror of b200rl_mlp_shape."""
+    _fields_ = [("n_layers", C.c_int), ("input_dim", C.c_int), ("dims", C.c_int * MAX_LAYERS), ("acts", C.c_int * MAX_LAYERS)]
+
+    @staticmethod
+    def make(input_dim, dims, acts):
+        s = MlpShape()
+        s.n_layers, s.input_dim = len(dims), input_dim
+        for i, (d, a) in enumerate(zip(dims, acts)):
+            s.dims[i] = d
+            s.acts[i] = ACT[a] if isinstance(a, str) else int(a)
+        return s
+
+    def layer_dims(self):
+        return [self.dims[i] for i in range(self.n_layers)]
+
+    def num_params(self):
+        n, i = 0, self.input_dim
+        for d in self.layer_dims():
+            n += d * i + d
+            i = d
+        return n
+
+
+class AdamHyper(C.Structure):
+    """Mirror of b200rl_adam_hyper; defaults are the reference's DEFAULT_PARAMETERS_TENSORFLOW."""
+    _fields_ = [("alpha", C.c_float), ("beta_1", C.c_float), ("beta_2", C.c_float), ("epsilon", C.c_float), ("epsilon_sqrt", C.c_float)]
+
+    def __init__(self, alpha=1e-3, beta_1=0.9, beta_2=0.999, epsilon=1e-7, epsilon_sqrt=1e-7):
+        super().__init__(alpha, beta_1, beta_2, epsilon, epsilon_sqrt)
+
+
+def lib():
+    """The loaded C-ABI library (ctypes). Raises if it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200RLError(f"{LIB_PATH} is missing: run rl_tools_b200.build() (needs nvcc); there is no CPU fallback")
+        L = C.CDLL(LIB_PATH)
+        vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+        shape_p = C.POINTER(MlpShape)
+        L.b200rl_version.restype = i
+        L.b200rl_status_string.restype = C.c_char_p
+        L.b200rl_status_string.argtypes = [i]
+        L.b200rl_last_cuda_error.restype = C.c_char_p
+        L.b200rl_dense_forward.argtypes = [vp, vp, vp, i, vp, i, vp, i, i, i, i, i, vp]
+        L.b200rl_dense_backward_scratch_bytes.argtypes = [i, i, i]
+        L.b200rl_dense_backward_scratch_bytes.restype = sz
+        L.b200rl_dense_backward.argtypes = [vp, vp, i, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, vp, sz, vp]
+        L.b200rl_mse_gradient.argtypes = [vp, i, vp, i, vp, i, i, i, f, vp]
+        L.b200rl_fill.argtypes = [vp, sz, f, vp]
+        L.b200rl_mlp_num_params.argtypes = [shape_p]
+        L.b200rl_mlp_num_params.restype = sz
+        L.b200rl_mlp_evaluate.argtypes = [shape_p, vp, vp, i, vp, i, vp, vp, i, vp]
+        L.b200rl_mlp_forward.argtypes = [shape_p, vp, vp, i, vp, vp, i, vp]
+        L.b200rl_mlp_backward_scratch_bytes.argtypes = [shape_p, i]
+        L.b200rl_mlp_backward_scratch_bytes.restype = sz
+        L.b200rl_mlp_backward.argtypes = [shape_p, vp, vp, vp, i, vp, vp, vp, vp, vp, vp, i, vp, sz, vp]
+        L.b200rl_adam_reset.argtypes = [vp, vp]
+        L.b200rl_adam_step.argtypes = [vp, vp, vp, vp, sz, AdamHyper, vp, vp]
+        L.b200rl_pendulum_rollout.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp]
+        L.b200rl_pendulum_rollout_host.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp]
+        L.b200rl_release_host_staging.argtypes = []
+        L.b200rl_rng_init_host.argtypes = [vp, C.c_uint32]
+        L.b200rl_reset_table_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i)]
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str = ""):
+    if status != 0:
+        L = lib()
+        msg = L.b200rl_status_string(status).decode()
+        if status == 3:
+            msg += ": " + L.b200rl_last_cuda_error().decode()
+        raise B200RLError(f"{what} failed with status {status} ({msg})")
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _act(a):
+    return ACT[a] if isinstance(a, str) else int(a)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Thin tensor-level wrappers (torch CUDA float32 tensors in, C ABI underneath)
+# ------------------------------------------------------------------------------------------------------------
+def dense_forward(W, bias, x, act, want_pre=True, y=None, pre=None):
+    import torch
+    B, I = x.shape
+    O = W.shape[0]
+    y = torch.empty((B, O), device=x.device, dtype=torch.float32) if y is None else y
+    if want_pre and pre is None:
+        pre = torch.empty((B, O), device=x.device, dtype=torch.float32)
+    check(lib().b200rl_dense_forward(_ptr(W), _ptr(bias), _ptr(x), x.stride(0), _ptr(pre), pre.stride(0) if pre is not None else 0,
+                                     _ptr(y), y.stride(0), B, I, O, _act(act), _stream()), "b200rl_dense_forward")
+    return pre, y
+
+
+def dense_backward(W, x, pre, d_out, act, dW=None, db=None, want_d_in=True, want_grads=True):
+    """Returns (dW, db, d_in); d_out is overwritten with d_pre. dW/db accumulate when given."""
+    import torch
+    B, I = x.shape
+    O = W.shape[0]
+    if want_grads:
+        dW = torch.zeros((O, I), device=x.device, dtype=torch.float32) if dW is None else dW
+        db = torch.zeros((O,), device=x.device, dtype=torch.float32) if db is None else db
+    else:
+        dW = db = None
+    d_in = torch.empty((B, I), device=x.device, dtype=torch.float32) if want_d_in else None
+    nbytes = lib().b200rl_dense_backward_scratch_bytes(B, I, O)
+    scratch = torch.empty((max(nbytes, 4),), device=x.device, dtype=torch.uint8)
+    check(lib().b200rl_dense_backward(_ptr(W), _ptr(x), x.stride(0), _ptr(pre), pre.stride(0), _ptr(d_out), d_out.stride(0), _ptr(dW), _ptr(db),
+                                      _ptr(d_in), d_in.stride(0) if d_in is not None else 0, B, I, O, _act(act), _ptr(scratch), nbytes, _stream()),
+          "b200rl_dense_backward")
+    return dW, db, d_in
+
+
+def mse_gradient(a, b, loss_weight=1.0, d_a=None):
+    import torch
+    d_a = torch.empty_like(a) if d_a is None else d_a
+    check(lib().b200rl_mse_gradient(_ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(d_a), d_a.stride(0), a.shape[0], a.shape[1], loss_weight, _stream()),
+          "b200rl_mse_gradient")
+    return d_a
+
+
+def fill(t, value):
+    check(lib().b200rl_fill(_ptr(t), t.numel(), float(value), _stream()), "b200rl_fill")
+
+
+class Mlp:
+    """An MLP on flat arenas (params / grads / Adam moments), mirroring the verbs of nn_models::mlp in the reference:
+    evaluate, forward, backward, zero_gradient, reset_optimizer_state, step."""
+
+    def __init__(self, input_dim, dims, acts, batch, device="cuda"):
+        import torch
+        self.shape = MlpShape.make(input_dim, dims, acts)
+        self.batch = batch
+        self.device = device
+        n = self.shape.num_params()
+        assert n == lib().b200rl_mlp_num_params(C.byref(self.shape))
+        z = lambda *s: torch.zeros(*s, device=device, dtype=torch.float32)
+        self.params, self.grads, self.m, self.v = z(n), z(n), z(n), z(n)
+        width = max([input_dim] + list(dims))
+        self.tick, self.tock = z(batch, width), z(batch, width)
+        acts_n = batch * sum(dims)
+        self.pre, self.out = z(acts_n), z(acts_n)
+        self.adam_state = torch.zeros(4, device=device, dtype=torch.int32)
+        nbytes = lib().b200rl_mlp_backward_scratch_bytes(C.byref(self.shape), batch)
+        self.scratch_bytes = nbytes
+        self.scratch = torch.empty(max(nbytes, 4), device=device, dtype=torch.uint8)
+        self.hyper = AdamHyper()
+        self.reset_optimizer_state()
+
+    def output(self):
+        O = self.shape.dims[self.shape.n_layers - 1]
+        return self.out[-self.batch * O:].view(self.batch, O)
+
+    def evaluate(self, x, y=None):
+        import torch
+        O = self.shape.dims[self.shape.n_layers - 1]
+        y = torch.empty((x.shape[0], O), device=x.device, dtype=torch.float32) if y is None else y
+        check(lib().b200rl_mlp_evaluate(C.byref(self.shape), _ptr(self.params), _ptr(x), x.stride(0), _ptr(y), y.stride(0), _ptr(self.tick), _ptr(self.tock),
+                                        x.shape[0], _stream()), "b200rl_mlp_evaluate")
+        return y
+
+    def forward(self, x):
+        assert x.shape[0] == self.batch
+        check(lib().b200rl_mlp_forward(C.byref(self.shape), _ptr(self.params), _ptr(x), x.stride(0), _ptr(self.pre), _ptr(self.out), self.batch, _stream()),
+              "b200rl_mlp_forward")
+        return self.output()
+
+    def backward(self, x, d_out, d_input=None):
+        check(lib().b200rl_mlp_backward(C.byref(self.shape), _ptr(self.params), _ptr(self.grads), _ptr(x), x.stride(0), _ptr(self.pre), _ptr(self.out),
+                                        _ptr(d_out), _ptr(d_input), _ptr(self.tick), _ptr(self.tock), self.batch, _ptr(self.scratch), self.scratch_bytes,
+                                        _stream()), "b200rl_mlp_backward")
+
+    def zero_gradient(self):
+        fill(self.grads, 0.0)
+
+    def reset_optimizer_state(self):
+        fill(self.m, 0.0)
+        fill(self.v, 0.0)
+        check(lib().b200rl_adam_reset(_ptr(self.adam_state), _stream()), "b200rl_adam_reset")
+
+    def step(self):
+        check(lib().b200rl_adam_step(_ptr(self.params), _ptr(self.grads), _ptr(self.m), _ptr(self.v), self.params.numel(), self.hyper,
+                                     _ptr(self.adam_state), _stream()), "b200rl_adam_step")
+
+
+def pendulum_rollout(shape, params, states, episode_step, truncated, episode_return, reset_states, n_steps, step_limit=200,
+                     obs=None, act=None, rew=None, error_flag=None):
+    """In-place on the runner state tensors; returns (obs, act, rew). All tensors live on the GPU."""
+    import torch
+    N = states.shape[0]
+    dev = states.device
+    obs = torch.empty((n_steps * N, 3), device=dev, dtype=torch.float32) if obs is None else obs
+    act = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if act is None else act
+    rew = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if rew is None else rew
+    R = 0 if reset_states is None else reset_states.shape[0]
+    check(lib().b200rl_pendulum_rollout(C.byref(shape), _ptr(params), _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return),
+                                        _ptr(reset_states), R, N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(error_flag), _stream()),
+          "b200rl_pendulum_rollout")
+    return obs, act, rew
+
+
+def pendulum_rollout_host(shape, params, states, episode_step, truncated, episode_return, reset_states, n_steps, obs, act, rew, step_limit=200):
+    """Host-buffer call (numpy arrays or pinned CPU torch tensors): copies in, rolls out, copies the trajectories back."""
+    def hp(a):
+        if a is None:
+            return None
+        return C.c_void_p(a.ctypes.data) if hasattr(a, "ctypes") else C.c_void_p(a.data_ptr())
+    N = states.shape[0]
+    R = 0 if reset_states is None else reset_states.shape[0]
+    check(lib().b200rl_pendulum_rollout_host(C.byref(shape), hp(params), hp(states), hp(episode_step), hp(truncated), hp(episode_return), hp(reset_states),
+                                             R, N, n_steps, step_limit, hp(obs), hp(act), hp(rew), _stream()), "b200rl_pendulum_rollout_host")
+
+
+def reset_table_host(seed, n_envs, n_steps, episode_step, truncated, step_limit, n_rounds):
+    """Reference-compatible reset states [n_rounds, n_envs, 2] drawn on the host in the runner's order (numpy in/out)."""
+    import numpy as np
+    state = np.zeros(625, np.uint32)
+    check(lib().b200rl_rng_init_host(C.c_void_p(state.ctypes.data), seed), "b200rl_rng_init_host")
+    table = np.zeros((n_rounds, n_envs, 2), np.float32)
+    used = C.c_int(0)
+    es = np.ascontiguousarray(episode_step, np.int32)
+    tr = np.ascontiguousarray(truncated, np.uint8)
+    check(lib().b200rl_reset_table_host(C.c_void_p(state.ctypes.data), n_envs, n_steps, C.c_void_p(es.ctypes.data), C.c_void_p(tr.ctypes.data), step_limit,
+                                        C.c_void_p(table.ctypes.data), n_rounds, C.byref(used)), "b200rl_reset_table_host")
+    return table, used.value

@@ -1,0 +1,134 @@
+// Fused Adam step over a flat parameter arena, MSE gradient, fill. All three are HBM-bandwidth-bound
+// element-wise passes: 16-byte vector accesses, grid sized in multiples of the SM count.
+#include "common.cuh"
+
+namespace b200rl {
+
+struct AdamState { uint32_t age; uint32_t ticket; float c1; float c2; };
+
+// c = 1 / (1 - beta^age) with the power taken in double and rounded to float once, which reproduces the
+// correctly-rounded powf the CPU reference gets from its libm (nn/optimizers/adam/operations_generic.h:49-59).
+__device__ __forceinline__ float bias_correction(float beta, uint32_t age){
+    float pw = (float)pow((double)beta, (double)(float)age);
+    return 1.0f / (1.0f - pw);
+}
+__device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, const b200rl_adam_hyper& h, float c1, float c2){
+    // utils/polyak/operations_generic.h:72-88 and nn/optimizers/adam/instance/operations_generic.h:25-61, no fused
+    // multiply-add so every intermediate rounds like the reference's
+    m = __fadd_rn(__fmul_rn(h.beta_1, m), __fmul_rn(1.0f - h.beta_1, g));
+    v = __fadd_rn(__fmul_rn(h.beta_2, v), __fmul_rn(__fmul_rn(1.0f - h.beta_2, g), g));
+    float pre_sqrt = fmaxf(__fmul_rn(v, c2), h.epsilon_sqrt);
+    float update = __fdiv_rn(__fmul_rn(__fmul_rn(h.alpha, c1), m), __fadd_rn(__fsqrt_rn(pre_sqrt), h.epsilon));
+    p = __fsub_rn(p, update);
+}
+
+__global__ void __launch_bounds__(256) adam_step_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                                                        size_t n, b200rl_adam_hyper h, AdamState* state, int vec_ok){
+    __shared__ float sc[2];
+    if(threadIdx.x == 0){
+        uint32_t age = *reinterpret_cast<volatile uint32_t*>(&state->age);
+        sc[0] = bias_correction(h.beta_1, age);
+        sc[1] = bias_correction(h.beta_2, age);
+    }
+    __syncthreads();
+    const float c1 = sc[0], c2 = sc[1];
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+    if(vec_ok){
+        size_t n4 = n / 4;
+        float4* p4 = reinterpret_cast<float4*>(p); const float4* g4 = reinterpret_cast<const float4*>(g);
+        float4* m4 = reinterpret_cast<float4*>(m); float4* v4 = reinterpret_cast<float4*>(v);
+        for(size_t i = tid; i < n4; i += stride){
+            float4 pp = p4[i], gg = __ldg(g4 + i), mm = m4[i], vv = v4[i];
+            adam_one(pp.x, gg.x, mm.x, vv.x, h, c1, c2); adam_one(pp.y, gg.y, mm.y, vv.y, h, c1, c2);
+            adam_one(pp.z, gg.z, mm.z, vv.z, h, c1, c2); adam_one(pp.w, gg.w, mm.w, vv.w, h, c1, c2);
+            p4[i] = pp; m4[i] = mm; v4[i] = vv;
+        }
+        for(size_t i = n4 * 4 + tid; i < n; i += stride) adam_one(p[i], g[i], m[i], v[i], h, c1, c2);
+    }
+    else{
+        for(size_t i = tid; i < n; i += stride) adam_one(p[i], g[i], m[i], v[i], h, c1, c2);
+    }
+    // the last block to finish publishes c1/c2 and bumps the age: every block has read the old age by then
+    __syncthreads();
+    if(threadIdx.x == 0){
+        __threadfence();
+        uint32_t t = atomicAdd(&state->ticket, 1u);
+        if(t == gridDim.x - 1){
+            state->c1 = c1; state->c2 = c2;
+            state->ticket = 0;
+            state->age = state->age + 1;
+        }
+    }
+}
+__global__ void adam_reset_kernel(AdamState* s){ s->age = 1; s->ticket = 0; s->c1 = 0.0f; s->c2 = 0.0f; }
+
+__global__ void __launch_bounds__(256) mse_gradient_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long ldb, float* d, long long ldd,
+                                                           int rows, int cols, float constant){
+    long long n = (long long)rows * cols;
+    for(long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x){
+        long long r = i / cols; int c = (int)(i - r * cols);
+        float diff = __fsub_rn(a[r * lda + c], b[r * ldb + c]);
+        d[r * ldd + c] = __fmul_rn(diff, constant);
+    }
+}
+__global__ void __launch_bounds__(256) fill_kernel(float* dst, size_t n, float value, int vec_ok){
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+    if(vec_ok){
+        size_t n4 = n / 4; float4 v4 = make_float4(value, value, value, value);
+        for(size_t i = tid; i < n4; i += stride) reinterpret_cast<float4*>(dst)[i] = v4;
+        for(size_t i = n4 * 4 + tid; i < n; i += stride) dst[i] = value;
+    }
+    else for(size_t i = tid; i < n; i += stride) dst[i] = value;
+}
+
+static int grid_for(size_t work_items, int per_block){
+    size_t blocks = (work_items + per_block - 1) / per_block;
+    size_t cap = (size_t)NUM_SMS * 8;
+    if(blocks > cap) blocks = cap;
+    if(blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+static bool aligned16(const void* p){ return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace b200rl
+using namespace b200rl;
+
+extern "C" {
+
+int b200rl_adam_reset(uint32_t* state, b200rl_stream_t stream){
+    if(!state) return B200RL_ERR_INVALID_ARGUMENT;
+    adam_reset_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<AdamState*>(state));
+    B200RL_LAUNCH_CHECK("adam_reset");
+    return B200RL_OK;
+}
+
+int b200rl_adam_step(float* params, const float* grads, float* m, float* v, size_t n, b200rl_adam_hyper hyper, uint32_t* state, b200rl_stream_t stream){
+    if(!params || !grads || !m || !v || !state) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n == 0) return B200RL_OK;
+    int vec_ok = aligned16(params) && aligned16(grads) && aligned16(m) && aligned16(v);
+    int grid = grid_for(vec_ok ? (n + 3) / 4 : n, 256);
+    adam_step_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(params, grads, m, v, n, hyper, reinterpret_cast<AdamState*>(state), vec_ok);
+    B200RL_LAUNCH_CHECK("adam_step");
+    return B200RL_OK;
+}
+
+int b200rl_mse_gradient(const float* a, int lda, const float* b, int ldb, float* d_a, int ldd, int rows, int cols, float loss_weight, b200rl_stream_t stream){
+    if(!a || !b || !d_a || rows < 0 || cols < 1 || lda < cols || ldb < cols || ldd < cols) return B200RL_ERR_INVALID_ARGUMENT;
+    if(rows == 0) return B200RL_OK;
+    // nn/loss_functions/mse/operations_generic.h:49: (T)2 / ((T)ROWS * COLS) * loss_weight, evaluated in float
+    float constant = 2.0f / ((float)rows * (float)cols) * loss_weight;
+    mse_gradient_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(a, lda, b, ldb, d_a, ldd, rows, cols, constant);
+    B200RL_LAUNCH_CHECK("mse_gradient");
+    return B200RL_OK;
+}
+
+int b200rl_fill(float* dst, size_t n, float value, b200rl_stream_t stream){
+    if(!dst) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n == 0) return B200RL_OK;
+    int vec_ok = aligned16(dst);
+    fill_kernel<<<grid_for(vec_ok ? (n + 3) / 4 : n, 256), 256, 0, (cudaStream_t)stream>>>(dst, n, value, vec_ok);
+    B200RL_LAUNCH_CHECK("fill");
+    return B200RL_OK;
+}
+
+}

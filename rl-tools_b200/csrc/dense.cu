@@ -1,0 +1,333 @@
+// Dense layer forward / backward for fp32 row-major operands with arbitrary row pitch, and the MLP chaining on a
+// flat parameter arena.
+//
+// One tiled kernel template covers the three contractions of a dense layer; they differ only in which operand
+// index is contiguous in memory:
+//   forward : y[b][o]   = sum_i x[b][i]     * W[o][i]     (both operands contiguous along the summed index)
+//   d_in    : d_in[b][i]= sum_o d_pre[b][o] * W[o][i]     (W strided along the summed index)
+//   d_W     : dW[o][i] += sum_b d_pre[b][o] * x[b][i]     (both strided; summed index = batch, split across CTAs)
+// Bias, pre-activation store and activation are fused into the forward epilogue; d_pre = act'(pre) * d_out and the
+// bias gradient are one pass; split-batch partials of d_W / d_bias are reduced in a fixed order (deterministic).
+#include "common.cuh"
+
+namespace b200rl {
+
+constexpr int BM = 64, BN = 64, BK = 16, GEMM_THREADS = 256, PADM = 4;
+
+enum { EPI_FORWARD = 0, EPI_STORE = 1, EPI_ACCUMULATE = 2 };
+
+struct GemmArgs {
+    const float* A; long long lda;   // A(m,k)
+    const float* B; long long ldb;   // B(n,k)
+    int M, N, K;
+    int k_per_split;                 // summed-index range handled by one blockIdx.z
+    // epilogue
+    const float* bias;               // EPI_FORWARD
+    float* pre; long long ldpre;     // EPI_FORWARD (nullable)
+    float* C; long long ldc;         // output (EPI_FORWARD: y, EPI_STORE: C, EPI_ACCUMULATE with gridDim.z == 1: C += acc)
+    float* partial;                  // EPI_ACCUMULATE with gridDim.z > 1: partial[z][M*N] (dense, ld = N)
+};
+
+template <bool KCONTIG>
+__device__ __forceinline__ void load_tile(float (*S)[BM + PADM], const float* __restrict__ P, long long ld, int row0, int rows, int k0, int k_end, int tid){
+    // S[k][r] = P(row0 + r, k0 + k); zero outside [0, rows) x [k0, k_end)
+    if constexpr(KCONTIG){
+        int k = tid % BK, r = tid / BK;            // 16 consecutive k per row -> 64-byte segments
+#pragma unroll
+        for(int j = 0; j < BM / (GEMM_THREADS / BK); j++){
+            int rr = r + j * (GEMM_THREADS / BK);
+            int gr = row0 + rr, gk = k0 + k;
+            S[k][rr] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gr * ld + gk) : 0.0f;
+        }
+    }
+    else{
+        int r = tid % BM, k = tid / BM;            // 64 consecutive rows (contiguous in memory) per k
+#pragma unroll
+        for(int j = 0; j < BK / (GEMM_THREADS / BM); j++){
+            int kk = k + j * (GEMM_THREADS / BM);
+            int gr = row0 + r, gk = k0 + kk;
+            S[kk][r] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gk * ld + gr) : 0.0f;
+        }
+    }
+}
+
+template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT>
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_kernel(GemmArgs a){
+    __shared__ __align__(16) float As[BK][BM + PADM];
+    __shared__ __align__(16) float Bs[BK][BN + PADM];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_begin = blockIdx.z * a.k_per_split;
+    const int k_end = min(a.K, k_begin + a.k_per_split);
+    const int tx = tid % 16, ty = tid / 16;
+    float acc[4][4];
+#pragma unroll
+    for(int i = 0; i < 4; i++)
+#pragma unroll
+        for(int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+
+    for(int k0 = k_begin; k0 < k_end; k0 += BK){
+        load_tile<A_KCONTIG>(As, a.A, a.lda, m0, a.M, k0, k_end, tid);
+        load_tile<B_KCONTIG>(Bs, a.B, a.ldb, n0, a.N, k0, k_end, tid);
+        __syncthreads();
+#pragma unroll
+        for(int k = 0; k < BK; k++){
+            float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            float4 bv = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+            float am[4] = {av.x, av.y, av.z, av.w}, bn[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for(int i = 0; i < 4; i++)
+#pragma unroll
+                for(int j = 0; j < 4; j++) acc[i][j] = fmaf(am[i], bn[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for(int i = 0; i < 4; i++){
+        int m = m0 + ty * 4 + i;
+        if(m >= a.M) continue;
+#pragma unroll
+        for(int j = 0; j < 4; j++){
+            int n = n0 + tx * 4 + j;
+            if(n >= a.N) continue;
+            float v = acc[i][j];
+            if constexpr(EPI == EPI_FORWARD){
+                v += __ldg(a.bias + n);
+                if(a.pre) a.pre[(long long)m * a.ldpre + n] = v;
+                a.C[(long long)m * a.ldc + n] = activation<ACT>(v);
+            }
+            else if constexpr(EPI == EPI_STORE){
+                a.C[(long long)m * a.ldc + n] = v;
+            }
+            else{
+                if(gridDim.z == 1) a.C[(long long)m * a.ldc + n] += v;
+                else a.partial[((long long)blockIdx.z * a.M + m) * a.N + n] = v;
+            }
+        }
+    }
+}
+
+// d_pre = act'(pre) * d_out written in place, plus per-column sums over a segment of rows.
+// grid (ceil(O/32), n_seg), block (32, 8). n_seg == 1: d_bias += column sum; else bias_partial[seg][o] = column sum.
+template <int ACT>
+__global__ void __launch_bounds__(256) dpre_bias_kernel(const float* __restrict__ pre, long long ldpre, float* d_out, long long ldd, float* d_bias, float* bias_partial,
+                                                       int B, int O, int rows_per_seg){
+    __shared__ float red[8][33];
+    int o = blockIdx.x * 32 + threadIdx.x;
+    int r0 = blockIdx.y * rows_per_seg, r1 = min(B, r0 + rows_per_seg);
+    float s = 0.0f;
+    if(o < O){
+        for(int r = r0 + threadIdx.y; r < r1; r += 8){
+            float d = d_activation<ACT>(pre[(long long)r * ldpre + o]) * d_out[(long long)r * ldd + o];
+            d_out[(long long)r * ldd + o] = d;
+            s += d;
+        }
+    }
+    red[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if(threadIdx.y == 0 && o < O){
+        float t = 0.0f;
+#pragma unroll
+        for(int y = 0; y < 8; y++) t += red[y][threadIdx.x];
+        if(d_bias){
+            if(gridDim.y == 1) d_bias[o] += t;
+            else bias_partial[(long long)blockIdx.y * O + o] = t;
+        }
+    }
+}
+// dst[i] += sum_s partial[s][i], s ascending (fixed order)
+__global__ void reduce_partials_kernel(float* dst, const float* __restrict__ partial, long long n, int splits){
+    for(long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x){
+        float s = 0.0f;
+        for(int z = 0; z < splits; z++) s += partial[(long long)z * n + i];
+        dst[i] += s;
+    }
+}
+
+struct BackwardPlan { int splits; int k_per_split; int bias_segs; int rows_per_seg; size_t bytes; };
+static BackwardPlan plan_backward(int B, int I, int O){
+    BackwardPlan p;
+    int tiles = ((O + BM - 1) / BM) * ((I + BN - 1) / BN);
+    int want = (2 * NUM_SMS + tiles - 1) / tiles;
+    int max_splits = (B + 255) / 256;
+    p.splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
+    if(p.splits < 1) p.splits = 1;
+    p.k_per_split = ((B + p.splits - 1) / p.splits + BK - 1) / BK * BK;
+    p.splits = (B + p.k_per_split - 1) / p.k_per_split;
+    int col_blocks = (O + 31) / 32;
+    int want_segs = (2 * NUM_SMS + col_blocks - 1) / col_blocks;
+    int max_segs = (B + 511) / 512;
+    p.bias_segs = want_segs > max_segs ? max_segs : want_segs;
+    if(p.bias_segs < 1) p.bias_segs = 1;
+    p.rows_per_seg = (B + p.bias_segs - 1) / p.bias_segs;
+    p.bias_segs = (B + p.rows_per_seg - 1) / p.rows_per_seg;
+    p.bytes = 0;
+    if(p.splits > 1) p.bytes += sizeof(float) * (size_t)p.splits * O * I;
+    if(p.bias_segs > 1) p.bytes += sizeof(float) * (size_t)p.bias_segs * O;
+    return p;
+}
+
+static int dense_forward_impl(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
+                              int B, int I, int O, int act, cudaStream_t s){
+    GemmArgs a{};
+    a.A = x; a.lda = ldx; a.B = W; a.ldb = I; a.M = B; a.N = O; a.K = I; a.k_per_split = I;
+    a.bias = bias; a.pre = pre; a.ldpre = ldpre; a.C = y; a.ldc = ldy;
+    dim3 grid((O + BN - 1) / BN, (B + BM - 1) / BM, 1);
+    B200RL_DISPATCH_ACT(act, (gemm_kernel<true, true, EPI_FORWARD, ACT><<<grid, GEMM_THREADS, 0, s>>>(a)));
+    B200RL_LAUNCH_CHECK("dense_forward");
+    return B200RL_OK;
+}
+
+static int dense_backward_impl(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
+                               float* dW, float* db, float* d_in, int ldi, int B, int I, int O, int act, void* scratch, size_t scratch_bytes, cudaStream_t s){
+    BackwardPlan p = plan_backward(B, I, O);
+    bool want_grads = dW != nullptr;
+    if(want_grads && p.bytes > 0 && (scratch == nullptr || scratch_bytes < p.bytes)) return B200RL_ERR_INVALID_ARGUMENT;
+    float* w_partial = reinterpret_cast<float*>(scratch);
+    float* b_partial = w_partial + (p.splits > 1 ? (size_t)p.splits * O * I : 0);
+    // backward_input only (no parameter gradients): d_pre is still needed, the column sums are not
+    int segs = want_grads ? p.bias_segs : (B + 4095) / 4096;
+    int rps = want_grads ? p.rows_per_seg : 4096;
+    {
+        dim3 grid((O + 31) / 32, segs), block(32, 8);
+        B200RL_DISPATCH_ACT(act, (dpre_bias_kernel<ACT><<<grid, block, 0, s>>>(pre, ldpre, d_out, ldd, want_grads ? db : nullptr, b_partial, B, O, rps)));
+        B200RL_LAUNCH_CHECK("dpre_bias");
+        if(want_grads && segs > 1){
+            reduce_partials_kernel<<<(O + 255) / 256, 256, 0, s>>>(db, b_partial, O, segs);
+            B200RL_LAUNCH_CHECK("reduce_bias");
+        }
+    }
+    if(want_grads){
+        GemmArgs a{};
+        a.A = d_out; a.lda = ldd; a.B = x; a.ldb = ldx; a.M = O; a.N = I; a.K = B; a.k_per_split = p.k_per_split;
+        a.C = dW; a.ldc = I; a.partial = w_partial;
+        dim3 grid((I + BN - 1) / BN, (O + BM - 1) / BM, p.splits);
+        gemm_kernel<false, false, EPI_ACCUMULATE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
+        B200RL_LAUNCH_CHECK("dense_dW");
+        if(p.splits > 1){
+            long long n = (long long)O * I;
+            int blocks = (int)((n + 255) / 256); if(blocks > 4 * NUM_SMS) blocks = 4 * NUM_SMS;
+            reduce_partials_kernel<<<blocks, 256, 0, s>>>(dW, w_partial, n, p.splits);
+            B200RL_LAUNCH_CHECK("reduce_dW");
+        }
+    }
+    if(d_in){
+        GemmArgs a{};
+        a.A = d_out; a.lda = ldd; a.B = W; a.ldb = I; a.M = B; a.N = I; a.K = O; a.k_per_split = O;
+        a.C = d_in; a.ldc = ldi;
+        dim3 grid((I + BN - 1) / BN, (B + BM - 1) / BM, 1);
+        gemm_kernel<true, false, EPI_STORE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
+        B200RL_LAUNCH_CHECK("dense_d_in");
+    }
+    return B200RL_OK;
+}
+
+static bool valid_shape(const b200rl_mlp_shape* sh){
+    if(!sh || sh->n_layers < 1 || sh->n_layers > B200RL_MAX_LAYERS || sh->input_dim < 1) return false;
+    for(int l = 0; l < sh->n_layers; l++) if(sh->dims[l] < 1 || !valid_activation(sh->acts[l])) return false;
+    return true;
+}
+
+}  // namespace b200rl
+
+using namespace b200rl;
+
+extern "C" {
+
+int b200rl_dense_forward(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
+                         int batch, int input_dim, int output_dim, int activation, b200rl_stream_t stream){
+    if(!W || !bias || !x || !y || batch < 0 || input_dim < 1 || output_dim < 1 || ldx < input_dim || ldy < output_dim || (pre && ldpre < output_dim) || !valid_activation(activation) || x == y)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    return dense_forward_impl(W, bias, x, ldx, pre, ldpre, y, ldy, batch, input_dim, output_dim, activation, (cudaStream_t)stream);
+}
+
+size_t b200rl_dense_backward_scratch_bytes(int batch, int input_dim, int output_dim){
+    if(batch < 1 || input_dim < 1 || output_dim < 1) return 0;
+    return plan_backward(batch, input_dim, output_dim).bytes;
+}
+
+int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
+                          float* d_W, float* d_bias, float* d_in, int ldi, int batch, int input_dim, int output_dim, int activation,
+                          void* scratch, size_t scratch_bytes, b200rl_stream_t stream){
+    if(!W || !pre || !d_out || batch < 0 || input_dim < 1 || output_dim < 1 || ldpre < output_dim || ldd < output_dim || !valid_activation(activation))
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if((d_W == nullptr) != (d_bias == nullptr)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(d_W && (!x || ldx < input_dim)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(d_in && ldi < input_dim) return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    return dense_backward_impl(W, x, ldx, pre, ldpre, d_out, ldd, d_W, d_bias, d_in, ldi, batch, input_dim, output_dim, activation, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+size_t b200rl_mlp_num_params(const b200rl_mlp_shape* sh){
+    if(!valid_shape(sh)) return 0;
+    size_t n = 0; int in = sh->input_dim;
+    for(int l = 0; l < sh->n_layers; l++){ n += (size_t)sh->dims[l] * in + sh->dims[l]; in = sh->dims[l]; }
+    return n;
+}
+
+int b200rl_mlp_evaluate(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* y, int ldy,
+                        float* tick, float* tock, int batch, b200rl_stream_t stream){
+    if(!valid_shape(sh) || !params || !x || !y || batch < 0 || ldx < sh->input_dim || ldy < sh->dims[sh->n_layers - 1]) return B200RL_ERR_INVALID_ARGUMENT;
+    if(sh->n_layers > 1 && (!tick || (sh->n_layers > 2 && !tock))) return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    const float* in = x; int ldin = ldx, I = sh->input_dim; const float* p = params;
+    for(int l = 0; l < sh->n_layers; l++){
+        int O = sh->dims[l]; bool last = l == sh->n_layers - 1;
+        float* out = last ? y : ((l % 2 == 0) ? tick : tock);
+        int ldo = last ? ldy : O;
+        int rc = dense_forward_impl(p, p + (size_t)O * I, in, ldin, nullptr, 0, out, ldo, batch, I, O, sh->acts[l], (cudaStream_t)stream);
+        if(rc) return rc;
+        p += (size_t)O * I + O; in = out; ldin = ldo; I = O;
+    }
+    return B200RL_OK;
+}
+
+int b200rl_mlp_forward(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* pre, float* out,
+                       int batch, b200rl_stream_t stream){
+    if(!valid_shape(sh) || !params || !x || !pre || !out || batch < 0 || ldx < sh->input_dim) return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    const float* in = x; int ldin = ldx, I = sh->input_dim; const float* p = params;
+    for(int l = 0; l < sh->n_layers; l++){
+        int O = sh->dims[l];
+        int rc = dense_forward_impl(p, p + (size_t)O * I, in, ldin, pre, O, out, O, batch, I, O, sh->acts[l], (cudaStream_t)stream);
+        if(rc) return rc;
+        p += (size_t)O * I + O; in = out; ldin = O; I = O;
+        pre += (size_t)batch * O; out += (size_t)batch * O;
+    }
+    return B200RL_OK;
+}
+
+size_t b200rl_mlp_backward_scratch_bytes(const b200rl_mlp_shape* sh, int batch){
+    if(!valid_shape(sh) || batch < 1) return 0;
+    size_t m = 0; int I = sh->input_dim;
+    for(int l = 0; l < sh->n_layers; l++){ size_t b = plan_backward(batch, I, sh->dims[l]).bytes; if(b > m) m = b; I = sh->dims[l]; }
+    return m;
+}
+
+int b200rl_mlp_backward(const b200rl_mlp_shape* sh, const float* params, float* grads, const float* x, int ldx, const float* pre,
+                        const float* out, float* d_out, float* d_input, float* tick, float* tock, int batch,
+                        void* scratch, size_t scratch_bytes, b200rl_stream_t stream){
+    if(!valid_shape(sh) || !params || !grads || !x || !pre || !out || !d_out || batch < 0 || ldx < sh->input_dim) return B200RL_ERR_INVALID_ARGUMENT;
+    int L = sh->n_layers;
+    if(L > 1 && (!tick || (L > 2 && !tock))) return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    size_t poff[B200RL_MAX_LAYERS], aoff[B200RL_MAX_LAYERS]; int Is[B200RL_MAX_LAYERS];
+    { size_t po = 0, ao = 0; int I = sh->input_dim;
+      for(int l = 0; l < L; l++){ poff[l] = po; aoff[l] = ao; Is[l] = I; po += (size_t)sh->dims[l] * I + sh->dims[l]; ao += (size_t)batch * sh->dims[l]; I = sh->dims[l]; } }
+    float* d_cur = d_out; int ldd = sh->dims[L - 1];
+    for(int l = L - 1; l >= 0; l--){
+        int O = sh->dims[l], I = Is[l];
+        const float* in = l == 0 ? x : out + aoff[l - 1];
+        int ldin = l == 0 ? ldx : I;
+        float* d_in = l == 0 ? d_input : ((l % 2 == 0) ? tick : tock);
+        float* dW = grads + poff[l];
+        int rc = dense_backward_impl(params + poff[l], in, ldin, pre + aoff[l], O, d_cur, ldd, dW, dW + (size_t)O * I, d_in, I, batch, I, O, sh->acts[l],
+                                     scratch, scratch_bytes, (cudaStream_t)stream);
+        if(rc) return rc;
+        d_cur = d_in; ldd = I;
+    }
+    return B200RL_OK;
+}
+
+}  // extern "C"

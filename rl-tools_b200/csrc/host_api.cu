@@ -1,0 +1,211 @@
+// Host-side entry points: status text, the host-buffer rollout pipeline, and reference-compatible random streams
+// for the reset table (std::mt19937 + libstdc++'s uniform_real_distribution<float>, as random/operations_cpu.h
+// drives them in the reference).
+#include "common.cuh"
+#include "rollout.cuh"
+#include <string.h>
+#include <string>
+#include <vector>
+
+namespace b200rl {
+
+static thread_local std::string g_last_cuda_error;
+int cuda_fail(cudaError_t e, const char* where){
+    g_last_cuda_error = std::string(where) + ": " + cudaGetErrorString(e);
+    return B200RL_ERR_CUDA;
+}
+
+// ---- MT19937 (Matsumoto & Nishimura), state = 624 words + index ------------------------------------------------
+struct Mt { uint32_t* mt; uint32_t& idx; };
+static void mt_seed(uint32_t* st, uint32_t seed){
+    st[0] = seed;
+    for(uint32_t i = 1; i < 624; i++) st[i] = 1812433253u * (st[i - 1] ^ (st[i - 1] >> 30)) + i;
+    st[624] = 624;
+}
+static uint32_t mt_next(uint32_t* st){
+    if(st[624] >= 624){
+        for(int i = 0; i < 624; i++){
+            uint32_t y = (st[i] & 0x80000000u) | (st[(i + 1) % 624] & 0x7fffffffu);
+            st[i] = st[(i + 397) % 624] ^ (y >> 1) ^ ((y & 1u) ? 0x9908b0dfu : 0u);
+        }
+        st[624] = 0;
+    }
+    uint32_t y = st[st[624]++];
+    y ^= y >> 11; y ^= (y << 7) & 0x9d2c5680u; y ^= (y << 15) & 0xefc60000u; y ^= y >> 18;
+    return y;
+}
+// std::uniform_real_distribution<float>(lo, hi) on mt19937: one draw, float(draw) / 2^32, clamped below 1
+static float uniform_real(uint32_t* st, float lo, float hi){
+    volatile float u = (float)mt_next(st) / 4294967296.0f;
+    if(u >= 1.0f) u = 0.99999994f;
+    volatile float scaled = u * (hi - lo);      // volatile: keep multiply and add separately rounded
+    return scaled + lo;
+}
+
+// ---- device staging for the host-buffer rollout ---------------------------------------------------------------
+struct Staging {
+    int device = -1;
+    size_t cap_envs = 0, cap_rows = 0, cap_reset = 0;
+    float *params = nullptr, *states = nullptr, *episode_return = nullptr, *reset = nullptr, *obs = nullptr, *act = nullptr, *rew = nullptr;
+    int32_t* episode_step = nullptr; uint8_t* truncated = nullptr; int* error_flag = nullptr;
+    cudaStream_t copy_stream = nullptr;
+    std::vector<cudaEvent_t> events;
+    void release(){
+        float** fp[] = {&params, &states, &episode_return, &reset, &obs, &act, &rew};
+        for(auto p : fp){ if(*p) cudaFree(*p); *p = nullptr; }
+        if(episode_step) cudaFree(episode_step); episode_step = nullptr;
+        if(truncated) cudaFree(truncated); truncated = nullptr;
+        if(error_flag) cudaFree(error_flag); error_flag = nullptr;
+        if(copy_stream) cudaStreamDestroy(copy_stream); copy_stream = nullptr;
+        for(auto e : events) cudaEventDestroy(e);
+        events.clear();
+        cap_envs = cap_rows = cap_reset = 0; device = -1;
+    }
+};
+static Staging g_staging;
+
+static int ensure_staging(size_t n_envs, size_t rows, size_t reset_elems, int slabs){
+    int dev = 0;
+    B200RL_CUDA_TRY(cudaGetDevice(&dev));
+    Staging& s = g_staging;
+    if(s.device != dev && s.device != -1) s.release();
+    s.device = dev;
+    if(!s.copy_stream) B200RL_CUDA_TRY(cudaStreamCreateWithFlags(&s.copy_stream, cudaStreamNonBlocking));
+    if(!s.params) B200RL_CUDA_TRY(cudaMalloc(&s.params, sizeof(float) * 65536));
+    if(!s.error_flag) B200RL_CUDA_TRY(cudaMalloc(&s.error_flag, sizeof(int)));
+    if(n_envs > s.cap_envs){
+        if(s.states){ cudaFree(s.states); cudaFree(s.episode_return); cudaFree(s.episode_step); cudaFree(s.truncated); }
+        B200RL_CUDA_TRY(cudaMalloc(&s.states, sizeof(float) * 2 * n_envs));
+        B200RL_CUDA_TRY(cudaMalloc(&s.episode_return, sizeof(float) * n_envs));
+        B200RL_CUDA_TRY(cudaMalloc(&s.episode_step, sizeof(int32_t) * n_envs));
+        B200RL_CUDA_TRY(cudaMalloc(&s.truncated, n_envs));
+        s.cap_envs = n_envs;
+    }
+    if(rows > s.cap_rows){
+        if(s.obs){ cudaFree(s.obs); cudaFree(s.act); cudaFree(s.rew); }
+        B200RL_CUDA_TRY(cudaMalloc(&s.obs, sizeof(float) * 3 * rows));
+        B200RL_CUDA_TRY(cudaMalloc(&s.act, sizeof(float) * rows));
+        B200RL_CUDA_TRY(cudaMalloc(&s.rew, sizeof(float) * rows));
+        s.cap_rows = rows;
+    }
+    if(reset_elems > s.cap_reset){
+        if(s.reset) cudaFree(s.reset);
+        B200RL_CUDA_TRY(cudaMalloc(&s.reset, sizeof(float) * reset_elems));
+        s.cap_reset = reset_elems;
+    }
+    while((int)s.events.size() < slabs){
+        cudaEvent_t e; B200RL_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        s.events.push_back(e);
+    }
+    return B200RL_OK;
+}
+
+}  // namespace b200rl
+using namespace b200rl;
+
+extern "C" {
+
+int b200rl_version(void){ return 100; }
+
+const char* b200rl_status_string(int status){
+    switch(status){
+        case B200RL_OK: return "ok";
+        case B200RL_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case B200RL_ERR_UNSUPPORTED: return "unsupported shape or activation";
+        case B200RL_ERR_CUDA: return "CUDA runtime error";
+        case B200RL_ERR_DEVICE_FLAG: return "a kernel raised its error flag";
+        default: return "unknown status";
+    }
+}
+const char* b200rl_last_cuda_error(void){ return g_last_cuda_error.c_str(); }
+
+int b200rl_rng_init_host(uint32_t* rng_state_host, uint32_t seed){
+    if(!rng_state_host) return B200RL_ERR_INVALID_ARGUMENT;
+    mt_seed(rng_state_host, seed + 1u);     // random/operations_cpu.h:23
+    return B200RL_OK;
+}
+
+int b200rl_reset_table_host(uint32_t* rng, int n_envs, int n_steps, const int32_t* episode_step_host, const uint8_t* truncated_host,
+                            int step_limit, float* reset_states_host, int n_reset_rounds, int* rounds_used_host){
+    if(!rng || !episode_step_host || !truncated_host || !reset_states_host || n_envs < 0 || n_steps < 0 || step_limit < 1 || n_reset_rounds < 0)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    std::vector<int32_t> es(episode_step_host, episode_step_host + n_envs);
+    std::vector<uint8_t> tr(truncated_host, truncated_host + n_envs);
+    std::vector<int> cnt(n_envs, 0);
+    int used = 0;
+    const float PI_F = 3.14159265358979323846f;
+    for(int t = 0; t < n_steps; t++){
+        for(int e = 0; e < n_envs; e++){
+            if(tr[e]){
+                if(cnt[e] >= n_reset_rounds) return B200RL_ERR_INVALID_ARGUMENT;
+                float* dst = reset_states_host + ((size_t)cnt[e] * n_envs + e) * 2;
+                dst[0] = uniform_real(rng, -PI_F, PI_F);      // pendulum/operations_generic.h:57-61: theta first
+                dst[1] = uniform_real(rng, -1.0f, 1.0f);
+                cnt[e]++; if(cnt[e] > used) used = cnt[e];
+                es[e] = 0;
+            }
+        }
+        for(int e = 0; e < n_envs; e++){ es[e] += 1; tr[e] = es[e] == step_limit; }
+    }
+    if(rounds_used_host) *rounds_used_host = used;
+    return B200RL_OK;
+}
+
+int b200rl_release_host_staging(void){ g_staging.release(); return B200RL_OK; }
+
+int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* actor_params_host, float* states_host,
+                                 int32_t* episode_step_host, uint8_t* truncated_host, float* episode_return_host,
+                                 const float* reset_states_host, int n_reset_rounds, int n_envs, int n_steps, int step_limit,
+                                 float* obs_host, float* act_host, float* rew_host, b200rl_stream_t stream){
+    int rc = validate_actor(actor);
+    if(rc) return rc;
+    if(!actor_params_host || !states_host || !episode_step_host || !truncated_host || !episode_return_host || !obs_host || !act_host || !rew_host ||
+       n_envs < 0 || n_steps < 0 || n_reset_rounds < 0 || step_limit < 1 || (reset_states_host == nullptr && n_reset_rounds != 0))
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0 || n_steps == 0) return B200RL_OK;
+    const size_t N = n_envs, rows = (size_t)n_envs * n_steps, n_params = b200rl_mlp_num_params(actor);
+    if(n_params > 65536) return B200RL_ERR_UNSUPPORTED;
+    // env slabs: the device-to-host copy of slab k overlaps the kernel of slab k+1
+    int slabs = n_envs >= 8192 ? 8 : 1;
+    int slab_envs = ((n_envs + slabs - 1) / slabs + 127) / 128 * 128;
+    slabs = (n_envs + slab_envs - 1) / slab_envs;
+    rc = ensure_staging(N, rows, (size_t)n_reset_rounds * N * 2, slabs);
+    if(rc) return rc;
+    Staging& st = g_staging;
+    cudaStream_t s = (cudaStream_t)stream;
+    B200RL_CUDA_TRY(cudaMemcpyAsync(st.params, actor_params_host, sizeof(float) * n_params, cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(st.states, states_host, sizeof(float) * 2 * N, cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(st.episode_step, episode_step_host, sizeof(int32_t) * N, cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(st.truncated, truncated_host, N, cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(st.episode_return, episode_return_host, sizeof(float) * N, cudaMemcpyHostToDevice, s));
+    if(n_reset_rounds > 0) B200RL_CUDA_TRY(cudaMemcpyAsync(st.reset, reset_states_host, sizeof(float) * 2 * N * n_reset_rounds, cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaMemsetAsync(st.error_flag, 0, sizeof(int), s));
+    for(int k = 0; k < slabs; k++){
+        RolloutArgs a{};
+        a.params = st.params; a.states = st.states; a.episode_step = st.episode_step; a.truncated = st.truncated; a.episode_return = st.episode_return;
+        a.reset_states = n_reset_rounds > 0 ? st.reset : nullptr; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs;
+        a.env_begin = k * slab_envs; a.env_count = (a.env_begin + slab_envs <= n_envs) ? slab_envs : n_envs - a.env_begin;
+        a.n_steps = n_steps; a.step_limit = step_limit; a.obs = st.obs; a.act = st.act; a.rew = st.rew; a.error_flag = st.error_flag;
+        for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
+        rc = rollout_dispatch(actor, a, s);
+        if(rc) return rc;
+        B200RL_CUDA_TRY(cudaEventRecord(st.events[k], s));
+        B200RL_CUDA_TRY(cudaStreamWaitEvent(st.copy_stream, st.events[k], 0));
+        // rows are t * n_envs + env: a slab is n_steps strips of env_count rows, pitch n_envs rows
+        const size_t w = a.env_count, off = a.env_begin;
+        B200RL_CUDA_TRY(cudaMemcpy2DAsync(obs_host + off * 3, sizeof(float) * 3 * N, st.obs + off * 3, sizeof(float) * 3 * N, sizeof(float) * 3 * w, n_steps, cudaMemcpyDeviceToHost, st.copy_stream));
+        B200RL_CUDA_TRY(cudaMemcpy2DAsync(act_host + off, sizeof(float) * N, st.act + off, sizeof(float) * N, sizeof(float) * w, n_steps, cudaMemcpyDeviceToHost, st.copy_stream));
+        B200RL_CUDA_TRY(cudaMemcpy2DAsync(rew_host + off, sizeof(float) * N, st.rew + off, sizeof(float) * N, sizeof(float) * w, n_steps, cudaMemcpyDeviceToHost, st.copy_stream));
+    }
+    int flag = 0;
+    B200RL_CUDA_TRY(cudaMemcpyAsync(states_host, st.states, sizeof(float) * 2 * N, cudaMemcpyDeviceToHost, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(episode_step_host, st.episode_step, sizeof(int32_t) * N, cudaMemcpyDeviceToHost, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(truncated_host, st.truncated, N, cudaMemcpyDeviceToHost, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(episode_return_host, st.episode_return, sizeof(float) * N, cudaMemcpyDeviceToHost, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(&flag, st.error_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+    B200RL_CUDA_TRY(cudaStreamSynchronize(s));
+    B200RL_CUDA_TRY(cudaStreamSynchronize(st.copy_stream));
+    return flag ? B200RL_ERR_DEVICE_FLAG : B200RL_OK;
+}
+
+}

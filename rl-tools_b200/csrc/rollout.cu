@@ -1,0 +1,126 @@
+// Fused Pendulum rollout: reset-if-truncated, observe, actor forward (3 -> H -> H -> 1), environment step, reward and
+// episode counters for T steps in ONE launch. One thread owns one environment for the whole call; the actor's weights
+// stay resident in shared memory; the runner state lives in registers between steps.
+#include "common.cuh"
+#include "pendulum.cuh"
+#include "rollout.cuh"
+
+namespace b200rl {
+
+// ---------------------------------------------------------------------------------------------------------------
+// CUDA-core kernel: exact fp32 FMA chain in the reference's summation order (bias first, inputs ascending).
+// Shared memory: W1 [H,3], b1 [H], W2 [H,H], b2 [H], W3 [H], b3 -- (H*H + 6H + 1) floats, read as warp broadcasts.
+// ---------------------------------------------------------------------------------------------------------------
+template <int H>
+__global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
+    extern __shared__ __align__(16) float smem[];
+    float* W1 = smem;                 // [H][3]
+    float* b1 = W1 + H * 3;           // [H]
+    float* W2 = b1 + H;               // [H][H]
+    float* b2 = W2 + H * H;           // [H]
+    float* W3 = b2 + H;               // [H]
+    float* b3 = W3 + H;               // [1]
+    constexpr int NPARAMS = H * 3 + H + H * H + H + H + 1;
+    for(int i = threadIdx.x; i < NPARAMS; i += blockDim.x) smem[i] = __ldg(a.params + i);
+    __syncthreads();
+
+    const int local = blockIdx.x * blockDim.x + threadIdx.x;
+    if(local >= a.env_count) return;
+    const int e = a.env_begin + local;
+    float theta = a.states[2 * e], theta_dot = a.states[2 * e + 1];
+    int es = a.episode_step[e];
+    bool trunc = a.truncated[e] != 0;
+    float er = a.episode_return[e];
+    int resets = 0;
+    const int act_h1 = a.acts[0], act_h2 = a.acts[1], act_out = a.acts[2];
+
+    for(int t = 0; t < a.n_steps; t++){
+        if(trunc){
+            if(a.reset_states != nullptr && resets < a.n_reset_rounds){
+                const float2 rs = *reinterpret_cast<const float2*>(a.reset_states + ((size_t)resets * a.n_envs + e) * 2);
+                theta = rs.x; theta_dot = rs.y;
+            }
+            else if(a.error_flag) *a.error_flag = 1;
+            resets++; es = 0; er = 0.0f;
+        }
+        float sn, cs;
+        sincosf(theta, &sn, &cs);
+        const size_t row = (size_t)t * a.n_envs + e;
+        a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot;
+
+        float h1[H];
+#pragma unroll
+        for(int j = 0; j < H; j++){
+            float acc = b1[j];
+            acc = fmaf(W1[j * 3 + 0], cs, acc); acc = fmaf(W1[j * 3 + 1], sn, acc); acc = fmaf(W1[j * 3 + 2], theta_dot, acc);
+            h1[j] = activation_rt(acc, act_h1);
+        }
+        float out = b3[0];
+#pragma unroll 2
+        for(int j = 0; j < H; j++){
+            float acc = b2[j];
+            const float4* w = reinterpret_cast<const float4*>(W2 + j * H);
+#pragma unroll
+            for(int k = 0; k < H / 4; k++){
+                const float4 w4 = w[k];
+                acc = fmaf(w4.x, h1[4 * k + 0], acc); acc = fmaf(w4.y, h1[4 * k + 1], acc);
+                acc = fmaf(w4.z, h1[4 * k + 2], acc); acc = fmaf(w4.w, h1[4 * k + 3], acc);
+            }
+            out = fmaf(W3[j], activation_rt(acc, act_h2), out);
+        }
+        const float action = activation_rt(out, act_out);
+
+        float nt, ntd;
+        pendulum::step(theta, theta_dot, sn, action, nt, ntd);
+        const float r = pendulum::reward(theta, theta_dot, action);
+        a.act[row] = action; a.rew[row] = r;
+        es += 1; er = __fadd_rn(er, r);
+        trunc = (es == a.step_limit);          // Pendulum never terminates (operations_generic.h:243-247)
+        theta = nt; theta_dot = ntd;
+    }
+    a.states[2 * e] = theta; a.states[2 * e + 1] = theta_dot;
+    a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
+}
+
+int launch_rollout_simt(const RolloutArgs& a, int H, cudaStream_t s){
+    if(H != 64) return B200RL_ERR_UNSUPPORTED;
+    constexpr int THREADS = 128;
+    size_t smem = sizeof(float) * (64 * 3 + 64 + 64 * 64 + 64 + 64 + 1);
+    int grid = (a.env_count + THREADS - 1) / THREADS;
+    rollout_simt_kernel<64><<<grid, THREADS, smem, s>>>(a);
+    B200RL_LAUNCH_CHECK("rollout_simt");
+    return B200RL_OK;
+}
+
+int validate_actor(const b200rl_mlp_shape* actor){
+    if(!actor) return B200RL_ERR_INVALID_ARGUMENT;
+    if(actor->n_layers != 3 || actor->input_dim != 3 || actor->dims[2] != 1 || actor->dims[0] != actor->dims[1]) return B200RL_ERR_UNSUPPORTED;
+    if(actor->dims[0] != 64) return B200RL_ERR_UNSUPPORTED;
+    for(int l = 0; l < 3; l++) if(!valid_activation(actor->acts[l])) return B200RL_ERR_INVALID_ARGUMENT;
+    return B200RL_OK;
+}
+
+int rollout_dispatch(const b200rl_mlp_shape* actor, const RolloutArgs& a, cudaStream_t s){
+    return launch_rollout_simt(a, actor->dims[0], s);
+}
+
+}  // namespace b200rl
+using namespace b200rl;
+
+extern "C" int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
+                                       uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds,
+                                       int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
+                                       b200rl_stream_t stream){
+    int rc = validate_actor(actor);
+    if(rc) return rc;
+    if(!actor_params || !states || !episode_step || !truncated || !episode_return || !obs || !act || !rew || n_envs < 0 || n_steps < 0 || n_reset_rounds < 0 || step_limit < 1)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(reset_states == nullptr && n_reset_rounds != 0) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0 || n_steps == 0) return B200RL_OK;
+    RolloutArgs a{};
+    a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
+    a.reset_states = reset_states; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs; a.env_begin = 0; a.env_count = n_envs;
+    a.n_steps = n_steps; a.step_limit = step_limit; a.obs = obs; a.act = act; a.rew = rew; a.error_flag = error_flag;
+    for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
+    return rollout_dispatch(actor, a, (cudaStream_t)stream);
+}

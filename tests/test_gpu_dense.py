@@ -1,0 +1,177 @@
+"""GPU parity of the dense layer, MSE gradient and Adam (through the C ABI) against the CPU oracle and the golden
+fixtures of the real reference. Tolerance: |x - ref| <= 1e-6 + 1e-5 |ref| per element (fp32 path)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import make_golden as mg
+from conftest import GOLDEN
+import oracle
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-5, 1e-6
+
+
+def close(got, want, rtol=RTOL, atol=ATOL):
+    got = got.detach().cpu().numpy() if hasattr(got, "detach") else np.asarray(got)
+    err = np.abs(got.reshape(-1).astype(np.float64) - want.reshape(-1).astype(np.float64))
+    bound = atol + rtol * np.abs(want.reshape(-1).astype(np.float64))
+    worst = int(np.argmax(err - bound))
+    assert np.all(err <= bound), f"max excess at {worst}: got {got.reshape(-1)[worst]} want {want.reshape(-1)[worst]} err {err[worst]:.3e}"
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+SHAPES = [  # (batch, in, out, act): the reference's CUDA test sweep plus awkward sizes
+    (1, 3, 64, "relu"), (256, 3, 64, "relu"), (256, 64, 2, "identity"), (2, 256, 10, "relu"), (9, 256, 60, "tanh"), (10, 200, 100, "relu"),
+    (32, 10, 100, "sigmoid"), (200, 11, 256, "fast_tanh"), (1024, 256, 10, "relu"), (64, 50, 101, "tanh"), (256, 256, 256, "relu"),
+    (2048, 27, 64, "tanh"), (300, 64, 8, "identity"), (4099, 65, 17, "relu"), (256, 4, 256, "relu"), (256, 256, 1, "identity"),
+]
+
+
+@pytest.mark.parametrize("B,I,O,act", SHAPES)
+def test_dense_forward_backward_vs_oracle(lib, orc, torch, B, I, O, act):
+    seed = B * 7 + I * 3 + O
+    W = (mg.det_uniform(seed, O * I, stream=1) / np.float32(np.sqrt(I))).reshape(O, I)
+    b = mg.det_uniform(seed, O, stream=2) / np.float32(np.sqrt(I))
+    x = mg.det_normal(seed, B * I, stream=3).reshape(B, I)
+    d_out = mg.det_normal(seed, B * O, stream=4).reshape(B, O)
+    pre_ref, y_ref = orc.dense_forward(W, b, x, act)
+    pre, y = lib.dense_forward(dev(torch, W), dev(torch, b), dev(torch, x), act)
+    close(pre, pre_ref)
+    close(y, y_ref)
+    dW0 = mg.det_normal(seed, O * I, stream=5).reshape(O, I)   # gradients accumulate on top of existing values
+    db0 = mg.det_normal(seed, O, stream=6)
+    dW_ref, db_ref, din_ref, dpre_ref = orc.dense_backward(W, x, pre_ref, d_out, act, dW=dW0, db=db0)
+    d_out_dev = dev(torch, d_out)
+    dW, db, d_in = lib.dense_backward(dev(torch, W), dev(torch, x), dev(torch, pre_ref), d_out_dev, act, dW=dev(torch, dW0), db=dev(torch, db0))
+    close(d_out_dev, dpre_ref)                                  # d_out is overwritten with d_pre, as in the reference
+    # sums over the batch: tolerance scales with the number of summed terms' magnitude
+    scale_w = np.abs(dpre_ref).T @ np.abs(x) + np.abs(dW0)
+    assert np.all(np.abs(dW.cpu().numpy() - dW_ref) <= ATOL + RTOL * scale_w)
+    scale_b = np.abs(dpre_ref).sum(0) + np.abs(db0)
+    assert np.all(np.abs(db.cpu().numpy() - db_ref) <= ATOL + RTOL * scale_b)
+    scale_i = np.abs(dpre_ref) @ np.abs(W)
+    assert np.all(np.abs(d_in.cpu().numpy() - din_ref) <= ATOL + RTOL * scale_i)
+
+
+def test_dense_forward_row_pitch_views(lib, orc, torch):
+    """Inputs/outputs that are column views of a wider table (dataset rows are 13 floats wide in the on-policy runner)."""
+    B, I, O = 77, 3, 5
+    table = mg.det_normal(1, B * 13).reshape(B, 13)
+    W = mg.det_uniform(2, O * I).reshape(O, I)
+    b = mg.det_uniform(3, O)
+    t = dev(torch, table)
+    x_view = t[:, 2:5]
+    out_table = torch.zeros((B, 11), device="cuda")
+    y_view = out_table[:, 4:9]
+    lib.dense_forward(dev(torch, W), dev(torch, b), x_view, "tanh", want_pre=False, y=y_view)
+    _, y_ref = orc.dense_forward(W, b, np.ascontiguousarray(table[:, 2:5]), "tanh", want_pre=False)
+    close(y_view, y_ref)
+    assert float(out_table[:, :4].abs().max()) == 0.0 and float(out_table[:, 9:].abs().max()) == 0.0
+
+
+def test_backward_input_only(lib, orc, torch):
+    B, I, O = 130, 20, 33
+    W = mg.det_uniform(5, O * I).reshape(O, I)
+    x = mg.det_normal(5, B * I, stream=1).reshape(B, I)
+    pre = mg.det_normal(5, B * O, stream=2).reshape(B, O)
+    d_out = mg.det_normal(5, B * O, stream=3).reshape(B, O)
+    _, _, din_ref, _ = orc.dense_backward(W, x, pre, d_out, "relu", want_grads=False)
+    _, _, d_in = lib.dense_backward(dev(torch, W), dev(torch, x), dev(torch, pre), dev(torch, d_out), "relu", want_grads=False)
+    close(d_in, din_ref, rtol=1e-5, atol=2e-6)
+
+
+def test_mse_gradient(lib, orc, torch):
+    a = mg.det_normal(9, 256 * 3).reshape(256, 3)
+    b = mg.det_normal(9, 256 * 3, stream=1).reshape(256, 3)
+    got = lib.mse_gradient(dev(torch, a), dev(torch, b), 0.5)
+    assert np.array_equal(got.cpu().numpy(), orc.mse_gradient(a, b, 0.5))      # element-wise: bit-exact
+
+
+@pytest.mark.parametrize("n", [1, 5, 1023, 67329, 152336])
+def test_adam_step_bit_exact_over_several_steps(lib, orc, torch, n):
+    p = mg.det_normal(n, n)
+    m = np.zeros(n, np.float32)
+    v = np.zeros(n, np.float32)
+    dp, dm, dv = dev(torch, p), dev(torch, m), dev(torch, v)
+    state = torch.zeros(4, dtype=torch.int32, device="cuda")
+    import ctypes as C
+    L = lib.lib()
+    lib.check(L.b200rl_adam_reset(C.c_void_p(state.data_ptr()), None))
+    age = 1
+    hyper = lib.AdamHyper()
+    for step in range(5):
+        g = mg.det_normal(n + step, n, stream=7) * np.float32(0.1 if step % 2 else 3.0)
+        c1, c2, age = orc.adam_bias_correction(0.9, 0.999, age)
+        p, m, v = orc.adam_update(p, g, m, v, 1e-3, 0.9, 0.999, 1e-7, 1e-7, c1, c2)
+        dg = dev(torch, g)
+        lib.check(L.b200rl_adam_step(C.c_void_p(dp.data_ptr()), C.c_void_p(dg.data_ptr()), C.c_void_p(dm.data_ptr()), C.c_void_p(dv.data_ptr()), n, hyper,
+                                     C.c_void_p(state.data_ptr()), None))
+        torch.cuda.synchronize()
+        st = state.cpu().numpy()
+        assert int(st[0]) == age and int(st[1]) == 0                      # integer optimizer state: exact
+        assert np.array_equal(dm.cpu().numpy(), m) and np.array_equal(dv.cpu().numpy(), v)
+        close(dp, p, rtol=1e-6, atol=1e-7)
+    assert np.array_equal(dp.cpu().numpy(), p), "Adam update differs in the last bit from the reference rounding sequence"
+
+
+MLP_FIXTURES = sorted(glob.glob(os.path.join(GOLDEN, "mlp_*.npz")))
+
+
+@pytest.mark.parametrize("path", MLP_FIXTURES, ids=[os.path.basename(p)[4:-4] for p in MLP_FIXTURES])
+def test_mlp_train_steps_vs_reference_golden(lib, torch, path):
+    """evaluate / forward / backward / Adam through the flat-arena MLP against the REAL reference's outputs."""
+    fix = np.load(path)
+    name = os.path.basename(path)[4:-4]
+    d = fix["dims"]
+    c = dict(batch=int(d[0]), input_dim=int(d[1]), hidden_dim=int(d[2]), output_dim=int(d[3]), num_layers=int(d[4]), hidden_act=int(d[5]), output_act=int(d[6]))
+    dims = [c["hidden_dim"]] * (c["num_layers"] - 1) + [c["output_dim"]]
+    acts = [c["hidden_act"]] * (c["num_layers"] - 1) + [c["output_act"]]
+    params, x, target = mg.mlp_inputs(c, mg.case_seed(name))
+    net = lib.Mlp(c["input_dim"], dims, acts, c["batch"])
+    net.params.copy_(dev(torch, params))
+    xd, td = dev(torch, x), dev(torch, target)
+
+    def check(key, t, rtol=RTOL, atol=ATOL):
+        s, _ = mg.sample(t.detach().cpu().numpy())
+        close(s, fix[key], rtol, atol)
+
+    check("eval_out", net.evaluate(xd))
+    net.zero_gradient()
+    y = net.forward(xd)
+    check("fwd_pre", net.pre)
+    check("fwd_out", net.out)
+    d_out = lib.mse_gradient(y, td, 1.0)
+    net.backward(xd, d_out)
+    # gradient sums run over batch x fan-in products: allow a few extra ulps of the largest term
+    check("bwd_grads", net.grads, rtol=2e-5, atol=2e-6)
+    net.zero_gradient()
+    net.reset_optimizer_state()
+    for _ in range(mg.MLP_STEPS):
+        net.zero_gradient()
+        y = net.forward(xd)
+        d_out = lib.mse_gradient(y, td, 1.0)
+        net.backward(xd, d_out)
+        net.step()
+    check("train_m", net.m, rtol=2e-5, atol=2e-6)
+    # Adam normalises the step to ~alpha regardless of gradient scale, so parameter error is bounded by alpha * relative gradient error
+    check("train_params", net.params, rtol=1e-5, atol=2e-6)
+    # full backward with d_input
+    net.zero_gradient()
+    net.forward(xd)
+    d_in = torch.empty((c["batch"], c["input_dim"]), device="cuda")
+    net.backward(xd, td.clone(), d_input=d_in)
+    check("full_grads", net.grads, rtol=2e-5, atol=5e-6)
+    check("full_d_input", d_in, rtol=2e-5, atol=5e-6)

@@ -1,0 +1,146 @@
+"""GPU parity of the fused Pendulum rollout (through the C ABI) against the CPU oracle and the golden rollout of the
+real reference: integer runner state bit-exact, floating point within 1e-6 + 1e-5|ref| per step when the state is
+teacher-forced, drift reported (and loosely bounded) for free-running trajectories of this chaotic system."""
+import os
+
+import numpy as np
+import pytest
+
+import make_golden as mg
+from conftest import GOLDEN
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def actor_shapes(lib, acts=("relu", "relu", "tanh")):
+    return lib.MlpShape.make(3, [64, 64, 1], list(acts)), oracle.MlpShape.make(3, [64, 64, 1], list(acts))
+
+
+def close(got, want, rtol=1e-5, atol=1e-6):
+    got = got.detach().cpu().numpy() if hasattr(got, "detach") else got
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert np.all(err <= atol + rtol * np.abs(want)), f"max err {err.max():.3e}"
+
+
+@pytest.mark.parametrize("acts", [("relu", "relu", "tanh"), ("tanh", "fast_tanh", "identity"), ("sigmoid", "relu", "tanh")])
+def test_single_step_teacher_forced(lib, orc, torch, acts):
+    """T == 1 (one off-policy runner step) from oracle-provided states, 60 consecutive steps: every step's obs, action,
+    reward and next state within tolerance; counters and flags exact."""
+    shape, oshape = actor_shapes(lib, acts)
+    N = 1000
+    params = mg.det_uniform(17, oshape.num_params()) * np.float32(0.35)
+    states = orc.pendulum_initial_states(4, N)
+    es = (np.arange(N) * 11 % 200).astype(np.int32)
+    tr = (np.arange(N) % 7 == 0).astype(np.uint8)
+    er = mg.det_normal(3, N)
+    table = orc.reset_table(21, N, 60, es, tr, 200, 2)
+    counts = np.zeros(N, np.int64)
+    dparams = dev(torch, params)
+    for t in range(60):
+        # the k-th reset of env e takes table[k][e]; with one step per call the caller hands over the right round
+        round_table = np.stack([table[counts[e], e] for e in range(N)])[None]
+        ref = orc.pendulum_rollout(oshape, params, states, es, tr, er, np.ascontiguousarray(round_table), 1)
+        d_states, d_es, d_tr, d_er = dev(torch, states), dev(torch, es), dev(torch, tr), dev(torch, er)
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        obs, act, rew = lib.pendulum_rollout(shape, dparams, d_states, d_es, d_tr, d_er, dev(torch, round_table), 1, error_flag=flag)
+        assert int(flag.item()) == 0
+        close(obs, ref["obs"])
+        close(act, ref["act"], rtol=1e-5, atol=2e-6)
+        close(rew, ref["rew"], rtol=1e-5, atol=1e-5)
+        close(d_states, ref["states"], rtol=1e-5, atol=2e-6)
+        assert np.array_equal(d_es.cpu().numpy(), ref["episode_step"])
+        assert np.array_equal(d_tr.cpu().numpy(), ref["truncated"])
+        close(d_er, ref["episode_return"], rtol=1e-5, atol=1e-4)
+        counts += tr.astype(np.int64)
+        states, es, tr, er = ref["states"], ref["episode_step"], ref["truncated"], ref["episode_return"]
+
+
+def test_rollout_vs_reference_golden(lib, torch):
+    """410 steps x 128 envs with resets at t = 0, 200, 400 against the REAL reference's trajectory. Integers and the
+    RNG-driven reset rows are exact; floats are compared over the first steps after each reset (before chaotic
+    divergence can amplify last-bit differences of sinf/tanhf) and the drift over the whole horizon is bounded."""
+    fix = np.load(os.path.join(GOLDEN, "rollout.npz"))
+    N, T, limit = int(fix["N"]), int(fix["T"]), int(fix["step_limit"])
+    shape, _ = actor_shapes(lib)
+    table, used = lib.reset_table_host(int(fix["reset_seed"]), N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), limit, 3)
+    assert used == 3 and np.array_equal(table, fix["reset_table"])          # product-side RNG == reference engine
+    st, es, tr, er = dev(torch, np.zeros((N, 2), np.float32)), dev(torch, np.zeros(N, np.int32)), dev(torch, np.ones(N, np.uint8)), dev(torch, np.zeros(N, np.float32))
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    obs, act, rew = lib.pendulum_rollout(shape, dev(torch, fix["actor_params"]), st, es, tr, er, dev(torch, table), T, limit, error_flag=flag)
+    assert int(flag.item()) == 0
+    assert np.array_equal(es.cpu().numpy(), fix["episode_step"])
+    assert np.array_equal(tr.cpu().numpy(), fix["truncated"])
+    obs, act, rew = obs.cpu().numpy().reshape(T, N, 3), act.cpu().numpy().reshape(T, N), rew.cpu().numpy().reshape(T, N)
+    gobs, gact, grew = fix["obs"].reshape(T, N, 3), fix["act"].reshape(T, N), fix["rew"].reshape(T, N)
+    for t0 in (0, 200, 400):
+        # reset rows: theta_dot is copied from the table, cos/sin computed from the exact same theta
+        assert np.array_equal(obs[t0, :, 2], fix["reset_table"][t0 // 200, :, 1])
+        for t in range(t0, t0 + 5):
+            close(obs[t], gobs[t], rtol=1e-5, atol=1e-5)
+            close(act[t], gact[t], rtol=1e-5, atol=1e-5)
+    drift = np.abs(obs - gobs).reshape(T, -1).max(1)
+    print("max |obs - reference| at t=1,10,50,199:", drift[1], drift[10], drift[50], drift[199])
+    assert drift[:200].max() < 5e-2
+    close(rew[:3], grew[:3], rtol=1e-5, atol=1e-5)
+
+
+def test_error_flag_when_reset_table_is_too_small(lib, torch):
+    shape, oshape = actor_shapes(lib)
+    N = 64
+    params = dev(torch, mg.det_uniform(1, oshape.num_params()) * np.float32(0.2))
+    st, es, tr, er = dev(torch, np.zeros((N, 2), np.float32)), dev(torch, np.full(N, 198, np.int32)), dev(torch, np.zeros(N, np.uint8)), dev(torch, np.zeros(N, np.float32))
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.pendulum_rollout(shape, params, st, es, tr, er, None, 5, error_flag=flag)     # env truncates after 2 steps, no table given
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 1
+    assert np.array_equal(es.cpu().numpy(), np.full(N, 3, np.int32))
+
+
+def test_host_buffer_rollout_equals_device_rollout(lib, torch):
+    """The host-buffer entry point (slabbed, overlapped copies) returns bit-identical trajectories to the device call."""
+    shape, oshape = actor_shapes(lib)
+    N, T = 8192 + 384, 37
+    params = mg.det_uniform(2, oshape.num_params()) * np.float32(0.3)
+    table, _ = lib.reset_table_host(3, N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), 200, 1)
+    st, es, tr, er = np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32)
+    obs_h, act_h, rew_h = np.zeros((T * N, 3), np.float32), np.zeros((T * N, 1), np.float32), np.zeros((T * N, 1), np.float32)
+    lib.pendulum_rollout_host(shape, params, st, es, tr, er, table, T, obs_h, act_h, rew_h)
+    d = [dev(torch, a) for a in (np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32))]
+    obs, act, rew = lib.pendulum_rollout(shape, dev(torch, params), d[0], d[1], d[2], d[3], dev(torch, table), T)
+    assert np.array_equal(obs.cpu().numpy(), obs_h) and np.array_equal(act.cpu().numpy(), act_h) and np.array_equal(rew.cpu().numpy(), rew_h)
+    assert np.array_equal(d[0].cpu().numpy(), st) and np.array_equal(d[1].cpu().numpy(), es) and np.array_equal(d[2].cpu().numpy(), tr)
+
+
+def test_full_size_properties(lib, torch):
+    """65,536 envs x 200 steps (the benchmark workload): size-independent properties -- every env ends the call
+    truncated with episode_step == 200, cos^2 + sin^2 == 1, |theta_dot| <= 8, |action| <= 1, reward <= 0, the episode
+    return equals the sum of rewards, and the first 512 envs equal a separate 512-env launch bit for bit (sharding
+    by environment does not change results)."""
+    shape, oshape = actor_shapes(lib)
+    N, T = 65536, 200
+    params = dev(torch, mg.det_uniform(5, oshape.num_params()) * np.float32(0.3))
+    table, _ = lib.reset_table_host(1, N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), 200, 1)
+    d = [dev(torch, a) for a in (np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32))]
+    obs, act, rew = lib.pendulum_rollout(shape, params, d[0], d[1], d[2], d[3], dev(torch, table), T)
+    assert bool((d[1] == 200).all()) and bool((d[2] == 1).all())
+    o = obs.view(T, N, 3)
+    assert float(((o[..., 0] ** 2 + o[..., 1] ** 2) - 1).abs().max()) < 1e-5
+    assert float(o[..., 2].abs().max()) <= 8.0 and float(act.abs().max()) <= 1.0 and float(rew.max()) <= 0.0
+    ret = rew.view(T, N).double().sum(0)
+    assert float((ret - d[3].double()).abs().max()) < 1e-2
+    M = 512
+    ds = [dev(torch, a) for a in (np.zeros((M, 2), np.float32), np.zeros(M, np.int32), np.ones(M, np.uint8), np.zeros(M, np.float32))]
+    obs_s, act_s, rew_s = lib.pendulum_rollout(shape, params, ds[0], ds[1], ds[2], ds[3], dev(torch, np.ascontiguousarray(table[:, :M])), T)
+    assert torch.equal(obs_s.view(T, M, 3), o[:, :M]) and torch.equal(act_s.view(T, M), act.view(T, N)[:, :M])

@@ -46,10 +46,17 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.samples, self.proc = index, [], None
+        self.t_begin = self.t_end = None
+
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -61,7 +68,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6 and parts[0].isdigit():
-                self.samples.append(parts)
+                self.samples.append([time.time()] + parts)
 
     def __exit__(self, *a):
         if self.proc:
@@ -72,12 +79,16 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        if not self.samples:
+        inside = [s[1:] for s in self.samples if self.t_begin is not None and self.t_begin <= s[0] <= (self.t_end or 1e30)]
+        window = "timed region"
+        if not inside:          # region shorter than the sampling period: use the samples taken under load around it
+            inside, window = [s[1:] for s in self.samples], "warm-up + timed region"
+        if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm = [int(s[0]) for s in self.samples]
+        sm = [int(s[0]) for s in inside]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons, "samples": len(sm)}
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in inside)]
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": int(inside[0][1]), "reasons": reasons, "samples": len(sm), "window": window}
 
 
 def synthetic_inputs(seed, n_envs):
@@ -163,15 +174,22 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
+    ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
+    ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
-    args.warmup = max(args.warmup, 3)
+    if not args.allow_short_warmup:
+        args.warmup = max(args.warmup, 3)
+    globals().update(N_ENVS=args.envs, N_STEPS=args.rollout_steps)
+    workload = WORKLOAD if (args.envs, args.rollout_steps) == (65536, 200) else f"pendulum_rollout_{args.envs}env_x{args.rollout_steps}step_actor3-64-64-1 (reduced: profiling only)"
 
     import numpy as np
     import torch
@@ -208,19 +226,20 @@ def main():
         # every episode is exactly 200 steps, so each call starts with all environments truncated -> reset from the table
         pkg.pendulum_rollout(shape, params, states, es, tr, er, table, N_STEPS, STEP_LIMIT, obs=obs, act=act, rew=rew, error_flag=flag)
 
-    for _ in range(args.warmup):
-        flush.zero_(); step()
-    barrier()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     with ClockSampler(local_rank) as clocks:
+        for _ in range(args.warmup):
+            flush.zero_(); step()
         barrier()
+        clocks.mark_begin()
         wall0 = time.perf_counter()
         for i in range(args.steps):
             flush.zero_()                          # L2 flush between timed iterations (not inside the event pair)
             starts[i].record(); step(); stops[i].record()
         barrier()
         wall = time.perf_counter() - wall0
+        clocks.mark_end()
     assert int(flag.item()) == 0
     dev_ms = sum(a.elapsed_time(b) for a, b in zip(starts, stops))
     tm = torch.tensor([dev_ms], device=dev, dtype=torch.float64)
@@ -241,17 +260,19 @@ def main():
     def e2e_step():
         pkg.pendulum_rollout_host(shape, h_params, h_states, h_es, h_tr, h_er, h_table, N_STEPS, h_obs, h_act, h_rew, STEP_LIMIT)
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.e2e_steps):
-        e2e_step()
-    barrier()
-    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-    e2e_value = world * N_ENVS * N_STEPS * args.e2e_steps / float(e2e_s.item())
+    e2e_value = None
+    if not args.no_e2e:
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+        e2e_value = world * N_ENVS * N_STEPS * args.e2e_steps / float(e2e_s.item())
     h2d = params_h.nbytes + table_h.nbytes + N_ENVS * (8 + 4 + 1 + 4)
     d2h = rows * BYTES_PER_ENV_STEP + N_ENVS * (8 + 4 + 1 + 4) + 4
     pkg.lib().b200rl_release_host_staging()
@@ -265,7 +286,7 @@ def main():
         cpu = None if args.no_cpu_baseline else cpu_reference_rate()
         line = {"metric": "env-steps/s (fused actor fwd + env step)", "value": value, "unit": "env-steps/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": {"workload": WORKLOAD, "envs_per_gpu": N_ENVS, "steps_per_env": N_STEPS, "l2": "flushed between timed iterations; outputs (262 MB) exceed L2",
+                "data": "synthetic", "config": {"workload": workload, "envs_per_gpu": N_ENVS, "steps_per_env": N_STEPS, "l2": "flushed between timed iterations; outputs (262 MB) exceed L2",
                                                 "parallelism": f"env-sharded x{world}, no collective"},
                 "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
                 "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps},

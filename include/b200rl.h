@@ -152,7 +152,7 @@ int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const float* actor_pa
                             b200rl_stream_t stream);
 
 /* HOST-buffer variant of the above: every pointer except `stream` is host memory (pinned host memory makes the
- * copies asynchronous). Copies the runner state and reset table in, runs the rollout in env slabs and streams the
+ * copies asynchronous). Copies the runner state and reset table in, runs the rollout in slabs of steps and streams the
  * obs/act/rew slabs back while the next slab computes; synchronises before returning. Allocates its device staging
  * on first use and keeps it (freed by b200rl_release_host_staging). This is the call a host-side user of the
  * runner makes when the rollout data is consumed on the CPU. */

@@ -47,13 +47,14 @@ struct Staging {
     int device = -1;
     size_t cap_envs = 0, cap_rows = 0, cap_reset = 0;
     float *params = nullptr, *states = nullptr, *episode_return = nullptr, *reset = nullptr, *obs = nullptr, *act = nullptr, *rew = nullptr;
-    int32_t* episode_step = nullptr; uint8_t* truncated = nullptr; int* error_flag = nullptr;
+    int32_t* episode_step = nullptr; int32_t* reset_count = nullptr; uint8_t* truncated = nullptr; int* error_flag = nullptr;
     cudaStream_t copy_stream = nullptr;
     std::vector<cudaEvent_t> events;
     void release(){
         float** fp[] = {&params, &states, &episode_return, &reset, &obs, &act, &rew};
         for(auto p : fp){ if(*p) cudaFree(*p); *p = nullptr; }
         if(episode_step) cudaFree(episode_step); episode_step = nullptr;
+        if(reset_count) cudaFree(reset_count); reset_count = nullptr;
         if(truncated) cudaFree(truncated); truncated = nullptr;
         if(error_flag) cudaFree(error_flag); error_flag = nullptr;
         if(copy_stream) cudaStreamDestroy(copy_stream); copy_stream = nullptr;
@@ -74,10 +75,11 @@ static int ensure_staging(size_t n_envs, size_t rows, size_t reset_elems, int sl
     if(!s.params) B200RL_CUDA_TRY(cudaMalloc(&s.params, sizeof(float) * 65536));
     if(!s.error_flag) B200RL_CUDA_TRY(cudaMalloc(&s.error_flag, sizeof(int)));
     if(n_envs > s.cap_envs){
-        if(s.states){ cudaFree(s.states); cudaFree(s.episode_return); cudaFree(s.episode_step); cudaFree(s.truncated); }
+        if(s.states){ cudaFree(s.states); cudaFree(s.episode_return); cudaFree(s.episode_step); cudaFree(s.reset_count); cudaFree(s.truncated); }
         B200RL_CUDA_TRY(cudaMalloc(&s.states, sizeof(float) * 2 * n_envs));
         B200RL_CUDA_TRY(cudaMalloc(&s.episode_return, sizeof(float) * n_envs));
         B200RL_CUDA_TRY(cudaMalloc(&s.episode_step, sizeof(int32_t) * n_envs));
+        B200RL_CUDA_TRY(cudaMalloc(&s.reset_count, sizeof(int32_t) * n_envs));
         B200RL_CUDA_TRY(cudaMalloc(&s.truncated, n_envs));
         s.cap_envs = n_envs;
     }
@@ -165,10 +167,11 @@ int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* act
     if(n_envs == 0 || n_steps == 0) return B200RL_OK;
     const size_t N = n_envs, rows = (size_t)n_envs * n_steps, n_params = b200rl_mlp_num_params(actor);
     if(n_params > 65536) return B200RL_ERR_UNSUPPORTED;
-    // env slabs: the device-to-host copy of slab k overlaps the kernel of slab k+1
-    int slabs = n_envs >= 8192 ? 8 : 1;
-    int slab_envs = ((n_envs + slabs - 1) / slabs + 127) / 128 * 128;
-    slabs = (n_envs + slab_envs - 1) / slab_envs;
+    // time slabs: every launch covers all environments (the kernel needs them all in flight to fill the GPU) for a range
+    // of steps; the device-to-host copy of slab k (contiguous rows [t0*N, t1*N)) overlaps the kernel of slab k+1
+    int slabs = (rows >= (size_t)1 << 20 && n_steps >= 8) ? 8 : 1;
+    int slab_steps = (n_steps + slabs - 1) / slabs;
+    slabs = (n_steps + slab_steps - 1) / slab_steps;
     rc = ensure_staging(N, rows, (size_t)n_reset_rounds * N * 2, slabs);
     if(rc) return rc;
     Staging& st = g_staging;
@@ -180,22 +183,23 @@ int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* act
     B200RL_CUDA_TRY(cudaMemcpyAsync(st.episode_return, episode_return_host, sizeof(float) * N, cudaMemcpyHostToDevice, s));
     if(n_reset_rounds > 0) B200RL_CUDA_TRY(cudaMemcpyAsync(st.reset, reset_states_host, sizeof(float) * 2 * N * n_reset_rounds, cudaMemcpyHostToDevice, s));
     B200RL_CUDA_TRY(cudaMemsetAsync(st.error_flag, 0, sizeof(int), s));
+    B200RL_CUDA_TRY(cudaMemsetAsync(st.reset_count, 0, sizeof(int32_t) * N, s));
     for(int k = 0; k < slabs; k++){
+        const int t0 = k * slab_steps, t1 = (t0 + slab_steps < n_steps) ? t0 + slab_steps : n_steps;
+        const size_t r0 = (size_t)t0 * N, nr = (size_t)(t1 - t0) * N;
         RolloutArgs a{};
         a.params = st.params; a.states = st.states; a.episode_step = st.episode_step; a.truncated = st.truncated; a.episode_return = st.episode_return;
-        a.reset_states = n_reset_rounds > 0 ? st.reset : nullptr; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs;
-        a.env_begin = k * slab_envs; a.env_count = (a.env_begin + slab_envs <= n_envs) ? slab_envs : n_envs - a.env_begin;
-        a.n_steps = n_steps; a.step_limit = step_limit; a.obs = st.obs; a.act = st.act; a.rew = st.rew; a.error_flag = st.error_flag;
+        a.reset_states = n_reset_rounds > 0 ? st.reset : nullptr; a.n_reset_rounds = n_reset_rounds; a.reset_count = st.reset_count; a.n_envs = n_envs;
+        a.env_begin = 0; a.env_count = n_envs;
+        a.n_steps = t1 - t0; a.step_limit = step_limit; a.obs = st.obs + r0 * 3; a.act = st.act + r0; a.rew = st.rew + r0; a.error_flag = st.error_flag;
         for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
         rc = rollout_dispatch(actor, a, s);
         if(rc) return rc;
         B200RL_CUDA_TRY(cudaEventRecord(st.events[k], s));
         B200RL_CUDA_TRY(cudaStreamWaitEvent(st.copy_stream, st.events[k], 0));
-        // rows are t * n_envs + env: a slab is n_steps strips of env_count rows, pitch n_envs rows
-        const size_t w = a.env_count, off = a.env_begin;
-        B200RL_CUDA_TRY(cudaMemcpy2DAsync(obs_host + off * 3, sizeof(float) * 3 * N, st.obs + off * 3, sizeof(float) * 3 * N, sizeof(float) * 3 * w, n_steps, cudaMemcpyDeviceToHost, st.copy_stream));
-        B200RL_CUDA_TRY(cudaMemcpy2DAsync(act_host + off, sizeof(float) * N, st.act + off, sizeof(float) * N, sizeof(float) * w, n_steps, cudaMemcpyDeviceToHost, st.copy_stream));
-        B200RL_CUDA_TRY(cudaMemcpy2DAsync(rew_host + off, sizeof(float) * N, st.rew + off, sizeof(float) * N, sizeof(float) * w, n_steps, cudaMemcpyDeviceToHost, st.copy_stream));
+        B200RL_CUDA_TRY(cudaMemcpyAsync(obs_host + r0 * 3, st.obs + r0 * 3, sizeof(float) * 3 * nr, cudaMemcpyDeviceToHost, st.copy_stream));
+        B200RL_CUDA_TRY(cudaMemcpyAsync(act_host + r0, st.act + r0, sizeof(float) * nr, cudaMemcpyDeviceToHost, st.copy_stream));
+        B200RL_CUDA_TRY(cudaMemcpyAsync(rew_host + r0, st.rew + r0, sizeof(float) * nr, cudaMemcpyDeviceToHost, st.copy_stream));
     }
     int flag = 0;
     B200RL_CUDA_TRY(cudaMemcpyAsync(states_host, st.states, sizeof(float) * 2 * N, cudaMemcpyDeviceToHost, s));

@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "pendulum.cuh"
 #include "rollout.cuh"
+#include <stdlib.h>
 
 namespace b200rl {
 
@@ -31,7 +32,7 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
     int es = a.episode_step[e];
     bool trunc = a.truncated[e] != 0;
     float er = a.episode_return[e];
-    int resets = 0;
+    int resets = a.reset_count ? a.reset_count[e] : 0;
     const int act_h1 = a.acts[0], act_h2 = a.acts[1], act_out = a.acts[2];
 
     for(int t = 0; t < a.n_steps; t++){
@@ -80,6 +81,7 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
     }
     a.states[2 * e] = theta; a.states[2 * e + 1] = theta_dot;
     a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
+    if(a.reset_count) a.reset_count[e] = resets;
 }
 
 int launch_rollout_simt(const RolloutArgs& a, int H, cudaStream_t s){
@@ -100,7 +102,11 @@ int validate_actor(const b200rl_mlp_shape* actor){
     return B200RL_OK;
 }
 
+// The tensor-core kernel is the default for the 64-wide actor; B200RL_ROLLOUT_KERNEL=simt selects the CUDA-core kernel
+// (same results up to fp32 rounding), which exists for A/B measurements.
 int rollout_dispatch(const b200rl_mlp_shape* actor, const RolloutArgs& a, cudaStream_t s){
+    static const bool force_simt = [](){ const char* v = getenv("B200RL_ROLLOUT_KERNEL"); return v && v[0] == 's'; }();
+    if(actor->dims[0] == 64 && !force_simt) return launch_rollout_tc(a, s);
     return launch_rollout_simt(a, actor->dims[0], s);
 }
 

@@ -144,9 +144,11 @@ def test_mlp_train_steps_vs_reference_golden(lib, torch, path):
     net.params.copy_(dev(torch, params))
     xd, td = dev(torch, x), dev(torch, target)
 
-    def check(key, t, rtol=RTOL, atol=ATOL):
+    def check(key, t, rtol=RTOL, atol=ATOL, tensor_scale=0.0):
+        # tensor_scale > 0 adds tensor_scale * max|reference| to the absolute tolerance: sums over the batch are
+        # compared relative to the scale of the tensor (their summation order differs from the reference's)
         s, _ = mg.sample(t.detach().cpu().numpy())
-        close(s, fix[key], rtol, atol)
+        close(s, fix[key], rtol, atol + tensor_scale * float(np.abs(fix[key]).max()))
 
     check("eval_out", net.evaluate(xd))
     net.zero_gradient()
@@ -156,7 +158,7 @@ def test_mlp_train_steps_vs_reference_golden(lib, torch, path):
     d_out = lib.mse_gradient(y, td, 1.0)
     net.backward(xd, d_out)
     # gradient sums run over batch x fan-in products: allow a few extra ulps of the largest term
-    check("bwd_grads", net.grads, rtol=2e-5, atol=2e-6)
+    check("bwd_grads", net.grads, tensor_scale=1e-5)
     net.zero_gradient()
     net.reset_optimizer_state()
     for _ in range(mg.MLP_STEPS):
@@ -165,13 +167,14 @@ def test_mlp_train_steps_vs_reference_golden(lib, torch, path):
         d_out = lib.mse_gradient(y, td, 1.0)
         net.backward(xd, d_out)
         net.step()
-    check("train_m", net.m, rtol=2e-5, atol=2e-6)
+    check("train_m", net.m, tensor_scale=1e-5)
     # Adam normalises the step to ~alpha regardless of gradient scale, so parameter error is bounded by alpha * relative gradient error
     check("train_params", net.params, rtol=1e-5, atol=2e-6)
-    # full backward with d_input
+    # full backward with d_input, from the initial parameters again
+    net.params.copy_(dev(torch, params))
     net.zero_gradient()
     net.forward(xd)
     d_in = torch.empty((c["batch"], c["input_dim"]), device="cuda")
     net.backward(xd, td.clone(), d_input=d_in)
-    check("full_grads", net.grads, rtol=2e-5, atol=5e-6)
-    check("full_d_input", d_in, rtol=2e-5, atol=5e-6)
+    check("full_grads", net.grads, tensor_scale=1e-5)
+    check("full_d_input", d_in, tensor_scale=1e-5)

@@ -111,14 +111,14 @@ def test_error_flag_when_reset_table_is_too_small(lib, torch):
 def test_host_buffer_rollout_equals_device_rollout(lib, torch):
     """The host-buffer entry point (slabbed, overlapped copies) returns bit-identical trajectories to the device call."""
     shape, oshape = actor_shapes(lib)
-    N, T = 8192 + 384, 37
+    N, T, limit = 8192 + 384, 130, 50            # > 2^20 rows: the call runs as 8 slabs of steps; resets fall inside slabs
     params = mg.det_uniform(2, oshape.num_params()) * np.float32(0.3)
-    table, _ = lib.reset_table_host(3, N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), 200, 1)
+    table, _ = lib.reset_table_host(3, N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), limit, 3)
     st, es, tr, er = np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32)
     obs_h, act_h, rew_h = np.zeros((T * N, 3), np.float32), np.zeros((T * N, 1), np.float32), np.zeros((T * N, 1), np.float32)
-    lib.pendulum_rollout_host(shape, params, st, es, tr, er, table, T, obs_h, act_h, rew_h)
+    lib.pendulum_rollout_host(shape, params, st, es, tr, er, table, T, obs_h, act_h, rew_h, limit)
     d = [dev(torch, a) for a in (np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32))]
-    obs, act, rew = lib.pendulum_rollout(shape, dev(torch, params), d[0], d[1], d[2], d[3], dev(torch, table), T)
+    obs, act, rew = lib.pendulum_rollout(shape, dev(torch, params), d[0], d[1], d[2], d[3], dev(torch, table), T, limit)
     assert np.array_equal(obs.cpu().numpy(), obs_h) and np.array_equal(act.cpu().numpy(), act_h) and np.array_equal(rew.cpu().numpy(), rew_h)
     assert np.array_equal(d[0].cpu().numpy(), st) and np.array_equal(d[1].cpu().numpy(), es) and np.array_equal(d[2].cpu().numpy(), tr)
 

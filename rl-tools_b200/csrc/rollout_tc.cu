@@ -5,7 +5,7 @@
 // lane r of tensor memory. The environments of a launch are spread evenly over all 4 x (#CTAs) groups (tiles of
 // <= 128 environments, a multiple of 4), so every SM carries the same load and there is a single wave.
 // Per step and group:
-//   1. thread: reset-if-truncated, sincos, observation; first layer (K = 3) on CUDA cores with packed fp32x2 FMAs;
+//   1. thread: reset-if-truncated, sincos, observation; first layer (K = 3) on CUDA cores, weights as constant-bank FMA operands;
 //      h1 is written RAW to tensor memory (A_hi: the tensor core reads the top 19 bits = the tf32 "hi" part) and the
 //      remainder lo = h1 - tf32_trunc(h1) into a K-major, 128-byte-swizzled shared-memory tile (A_lo)
 //   2. the group's leader issues 24 tcgen05.mma (M128 N64 K8, kind::tf32): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi over
@@ -29,17 +29,23 @@ constexpr uint32_t A_KBLOCK_BYTES = TILE * 128;        // 128 rows x 128 B (32 t
 constexpr uint32_t B_KBLOCK_BYTES = H * 128;           // 64 rows x 128 B
 constexpr uint32_t OFF_B_HI = 0, OFF_B_LO = 2 * B_KBLOCK_BYTES, OFF_A_LO = 4 * B_KBLOCK_BYTES;
 constexpr uint32_t A_LO_BYTES = 2 * A_KBLOCK_BYTES;           // per group
-constexpr uint32_t OFF_L1 = OFF_A_LO + GROUPS * A_LO_BYTES;   // per pair of hidden units: {w0a,w0b,w1a,w1b} {w2a,w2b,b1a,b1b}
-constexpr uint32_t OFF_L3 = OFF_L1 + (H / 2) * 32;            // per pair: {b2a, b2b, w3a, w3b}
-constexpr uint32_t OFF_B3 = OFF_L3 + (H / 2) * 16;
-constexpr uint32_t OFF_MBAR = OFF_B3 + 16;
+constexpr uint32_t OFF_MBAR = OFF_A_LO + GROUPS * A_LO_BYTES;
 constexpr uint32_t OFF_ABORT = OFF_MBAR + 8 * GROUPS;
 constexpr uint32_t OFF_SLOT = OFF_ABORT + 4 * GROUPS;
 constexpr uint32_t SMEM_BYTES = OFF_SLOT + 16 + 1024;         // + slack to align the base to 1024 B
 constexpr uint32_t TMEM_COLS = 512, TMEM_COLS_PER_GROUP = 128;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;        // ~1 s: far beyond any legitimate wait
 constexpr uint32_t TF32_MASK = 0xFFFFE000u;
+// arena offsets of the actor 3 -> 64 -> 64 -> 1
+constexpr int P_W1 = 0, P_B1 = 192, P_W2 = 256, P_B2 = 4352, P_W3 = 4416, P_B3 = 4480;
+constexpr int C_W1 = 0, C_B1 = 192, C_B2 = 256, C_W3 = 320, C_B3 = 384, C_COUNT = 385;
 }
+
+// The small layers' weights (W1, b1, b2, W3, b3) are read by EVERY thread at EVERY step. As constant-bank operands
+// of the FMA instructions they cost no load instruction and no shared-memory bandwidth (a warp-wide broadcast LDS.128
+// occupies the 128 B/clk shared pipe for 4 cycles, which made the table look-ups the bottleneck of the CUDA-core
+// phase). Filled by a device-to-device copy on the launch stream; launches are ordered by an event (see launch_tc).
+__constant__ float c_actor[C_COUNT + 3];
 
 template <int ACT>
 __device__ __forceinline__ float act_or_rt(float x, int rt){
@@ -50,28 +56,18 @@ __device__ __forceinline__ float act_or_rt(float x, int rt){
 template <int A1, int A2>
 __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, int n_tiles, int envs_per_tile){
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // 1024-byte alignment by OFFSET from the __shared__ array, so the compiler keeps the shared address space (LDS/STS, not generic)
+    uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, g = tid >> 7, r = tid & 127, warp = tid >> 5;
-    const float4* L1 = reinterpret_cast<const float4*>(base + OFF_L1);
-    const float4* L3 = reinterpret_cast<const float4*>(base + OFF_L3);
-    const float* B3 = reinterpret_cast<const float*>(base + OFF_B3);
     uint64_t* mbar = reinterpret_cast<uint64_t*>(base + OFF_MBAR) + g;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base + OFF_ABORT) + g;
     uint32_t* slot = reinterpret_cast<uint32_t*>(base + OFF_SLOT);
 
-    // ---- one-time staging of the actor: arena = W1[64,3] b1[64] W2[64,64] b2[64] W3[1,64] b3[1] ----
+    // ---- one-time staging of the second layer (B operand); arena = W1[64,3] b1[64] W2[64,64] b2[64] W3[1,64] b3[1] ----
     const float* P = a.params;
-    if(tid < H / 2){
-        const int j = 2 * tid;
-        float4* l1 = reinterpret_cast<float4*>(base + OFF_L1);
-        l1[2 * tid]     = make_float4(__ldg(P + j * 3), __ldg(P + (j + 1) * 3), __ldg(P + j * 3 + 1), __ldg(P + (j + 1) * 3 + 1));
-        l1[2 * tid + 1] = make_float4(__ldg(P + j * 3 + 2), __ldg(P + (j + 1) * 3 + 2), __ldg(P + 192 + j), __ldg(P + 192 + j + 1));
-        reinterpret_cast<float4*>(base + OFF_L3)[tid] = make_float4(__ldg(P + 4352 + j), __ldg(P + 4352 + j + 1), __ldg(P + 4416 + j), __ldg(P + 4416 + j + 1));
-    }
-    if(tid == 0) *reinterpret_cast<float*>(base + OFF_B3) = __ldg(P + 4480);
     for(int idx = tid; idx < H * H; idx += THREADS){
         const int j = idx >> 6, k = idx & 63;                 // W2[j][k]: row j of the B operand, K index k
-        const float w = __ldg(P + 256 + idx);
+        const float w = __ldg(P + P_W2 + idx);
         const float hi = __uint_as_float(__float_as_uint(w) & TF32_MASK);
         const uint32_t off = (uint32_t)(k >> 5) * B_KBLOCK_BYTES + (uint32_t)j * 128 + ((((uint32_t)(k & 31) >> 2) ^ ((uint32_t)j & 7)) << 4) + ((uint32_t)k & 3) * 4;
         *reinterpret_cast<float*>(base + OFF_B_HI + off) = hi;
@@ -123,8 +119,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             const size_t row = (size_t)t * a.n_envs + e;
             if(valid){ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
 
-            // ---- layer 1 (CUDA cores, two hidden units per packed FMA); A_hi -> TMEM, A_lo -> swizzled smem ----
-            const float2 cs2 = make_float2(cs, cs), sn2 = make_float2(sn, sn), td2 = make_float2(theta_dot, theta_dot);
+            // ---- layer 1 (CUDA cores, weights as constant-bank operands); A_hi -> TMEM, A_lo -> swizzled smem ----
 #pragma unroll
             for(int hb = 0; hb < 2; hb++){               // K-block hb = hidden units 32 hb .. 32 hb + 31
                 uint32_t hraw[32];
@@ -132,19 +127,15 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                 for(int c = 0; c < 8; c++){              // 16-byte chunk c of the K-block: units 4c .. 4c+3
                     float lo[4];
 #pragma unroll
-                    for(int q = 0; q < 2; q++){
-                        const int pp = hb * 16 + c * 2 + q;
-                        const float4 w01 = L1[2 * pp], w2b = L1[2 * pp + 1];
-                        float2 acc = make_float2(w2b.z, w2b.w);
-                        acc = __ffma2_rn(make_float2(w01.x, w01.y), cs2, acc);
-                        acc = __ffma2_rn(make_float2(w01.z, w01.w), sn2, acc);
-                        acc = __ffma2_rn(make_float2(w2b.x, w2b.y), td2, acc);
-                        const float h0 = act_or_rt<A1>(acc.x, act1), h1 = act_or_rt<A1>(acc.y, act1);
-                        const uint32_t u0 = __float_as_uint(h0), u1 = __float_as_uint(h1);
-                        hraw[c * 4 + q * 2] = u0; hraw[c * 4 + q * 2 + 1] = u1;
-                        const float2 l = __fadd2_rn(make_float2(h0, h1),
-                                                    make_float2(__uint_as_float((u0 & TF32_MASK) ^ 0x80000000u), __uint_as_float((u1 & TF32_MASK) ^ 0x80000000u)));
-                        lo[q * 2] = l.x; lo[q * 2 + 1] = l.y;
+                    for(int q = 0; q < 4; q++){
+                        const int j = hb * 32 + c * 4 + q;
+                        float acc = c_actor[C_W1 + 3 * j] * cs;
+                        acc = fmaf(c_actor[C_W1 + 3 * j + 1], sn, acc);
+                        acc = fmaf(c_actor[C_W1 + 3 * j + 2], theta_dot, acc);
+                        const float h = act_or_rt<A1>(acc + c_actor[C_B1 + j], act1);
+                        const uint32_t u = __float_as_uint(h);
+                        hraw[c * 4 + q] = u;
+                        lo[q] = h - __uint_as_float(u & TF32_MASK);
                     }
                     *reinterpret_cast<float4*>(my_row_lo + hb * A_KBLOCK_BYTES + (((uint32_t)c ^ swz) << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
                 }
@@ -182,21 +173,23 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             phase ^= 1;
             tc::fence_after_thread_sync();
 
-            // ---- epilogue: bias + activation of layer 2, output layer 64 -> 1 (two partial sums, packed) ----
-            float2 out2 = make_float2(0.0f, 0.0f);
+            // ---- epilogue: bias + activation of layer 2, output layer 64 -> 1 (four partial sums for ILP) ----
+            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
             for(int half = 0; half < 2; half++){
                 uint32_t d[32];
                 tc::tmem_ld_32x32(tmem_d + lane_off + half * 32, d);
                 tc::tmem_wait_ld();
 #pragma unroll
-                for(int p = 0; p < 16; p++){
-                    const float4 bw = L3[half * 16 + p];
-                    const float2 pre = __fadd2_rn(make_float2(__uint_as_float(d[2 * p]), __uint_as_float(d[2 * p + 1])), make_float2(bw.x, bw.y));
-                    out2 = __ffma2_rn(make_float2(bw.z, bw.w), make_float2(act_or_rt<A2>(pre.x, act2), act_or_rt<A2>(pre.y, act2)), out2);
+                for(int p = 0; p < 8; p++){
+                    const int j = half * 32 + p * 4;
+                    o0 = fmaf(c_actor[C_W3 + j + 0], act_or_rt<A2>(__uint_as_float(d[p * 4 + 0]) + c_actor[C_B2 + j + 0], act2), o0);
+                    o1 = fmaf(c_actor[C_W3 + j + 1], act_or_rt<A2>(__uint_as_float(d[p * 4 + 1]) + c_actor[C_B2 + j + 1], act2), o1);
+                    o2 = fmaf(c_actor[C_W3 + j + 2], act_or_rt<A2>(__uint_as_float(d[p * 4 + 2]) + c_actor[C_B2 + j + 2], act2), o2);
+                    o3 = fmaf(c_actor[C_W3 + j + 3], act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]) + c_actor[C_B2 + j + 3], act2), o3);
                 }
             }
-            const float action = activation_rt(B3[0] + (out2.x + out2.y), act3);
+            const float action = activation_rt(c_actor[C_B3] + ((o0 + o1) + (o2 + o3)), act3);
 
             float nt, ntd;
             pendulum::step(theta, theta_dot, sn, action, nt, ntd);
@@ -218,6 +211,21 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     if(warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// All launches share the constant bank holding the small layers, so each launch (copy + kernel) is ordered after the
+// previous one with an event: a launch on another stream waits for the kernel that still reads the old constants.
+// The kernel fills every SM, so this ordering costs no concurrency.
+static int upload_small_layers(const float* params, cudaStream_t s, cudaEvent_t* order_event){
+    static cudaEvent_t ev = nullptr;
+    if(!ev) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    B200RL_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
+    *order_event = cap == cudaStreamCaptureStatusNone ? ev : nullptr;
+    if(*order_event) B200RL_CUDA_TRY(cudaStreamWaitEvent(s, ev, 0));
+    B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + P_W1, sizeof(float) * 256, sizeof(float) * C_W1, cudaMemcpyDeviceToDevice, s));
+    B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + P_B2, sizeof(float) * 129, sizeof(float) * C_B2, cudaMemcpyDeviceToDevice, s));
+    return B200RL_OK;
+}
+
 template <int A1, int A2>
 static int launch_tc(const RolloutArgs& a, cudaStream_t s){
     static bool configured = false;
@@ -225,6 +233,9 @@ static int launch_tc(const RolloutArgs& a, cudaStream_t s){
         B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<A1, A2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
         configured = true;
     }
+    cudaEvent_t order_event = nullptr;
+    int rc = upload_small_layers(a.params, s, &order_event);
+    if(rc) return rc;
     // spread the environments evenly over every group of every SM: tiles of <= 128 environments (a multiple of 4)
     const int groups_total = NUM_SMS * GROUPS;
     int ept = ((a.env_count + groups_total - 1) / groups_total + 3) / 4 * 4;
@@ -235,6 +246,7 @@ static int launch_tc(const RolloutArgs& a, cudaStream_t s){
     if(grid > NUM_SMS) grid = NUM_SMS;
     rollout_tc_kernel<A1, A2><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
     B200RL_LAUNCH_CHECK("rollout_tc");
+    if(order_event) B200RL_CUDA_TRY(cudaEventRecord(order_event, s));
     return B200RL_OK;
 }
 

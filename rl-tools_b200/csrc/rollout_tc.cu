@@ -8,8 +8,8 @@
 //   1. thread: reset-if-truncated, sincos, observation; first layer (K = 3) on CUDA cores, weights as constant-bank FMA operands;
 //      h1 is written RAW to tensor memory (A_hi: the tensor core reads the top 19 bits = the tf32 "hi" part) and the
 //      remainder lo = h1 - tf32_trunc(h1) into a K-major, 128-byte-swizzled shared-memory tile (A_lo)
-//   2. the group's leader issues 24 tcgen05.mma (M128 N64 K8, kind::tf32): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi over
-//      K = 64 ("3xTF32": the dropped lo*lo term is ~2^-22 relative, so the fp32 accumulator matches an fp32 GEMM to
+//   2. the group's leader issues 26 tcgen05.mma (M128 N64 K8, kind::tf32): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi over
+//      K = 64, plus one K step each for the hi and lo part of the bias ("3xTF32": the dropped lo*lo term is ~2^-22 relative, so the fp32 accumulator matches an fp32 GEMM to
 //      ~1e-6), then tcgen05.commit -> the group's mbarrier
 //   3. every thread waits (bounded), reads its accumulator row from TMEM (tcgen05.ld), applies bias + activation and
 //      the 64 -> 1 output layer, then steps the environment in registers.
@@ -29,10 +29,14 @@ constexpr uint32_t A_KBLOCK_BYTES = TILE * 128;        // 128 rows x 128 B (32 t
 constexpr uint32_t B_KBLOCK_BYTES = H * 128;           // 64 rows x 128 B
 constexpr uint32_t OFF_B_HI = 0, OFF_B_LO = 2 * B_KBLOCK_BYTES, OFF_A_LO = 4 * B_KBLOCK_BYTES;
 constexpr uint32_t A_LO_BYTES = 2 * A_KBLOCK_BYTES;           // per group
-constexpr uint32_t OFF_MBAR = OFF_A_LO + GROUPS * A_LO_BYTES;
+constexpr uint32_t OFF_ONES = OFF_A_LO + GROUPS * A_LO_BYTES;  // [128 x 8] K=8 tile, column 0 == 1: feeds the bias row through the MMA
+constexpr uint32_t OFF_BIAS_HI = OFF_ONES + 4096;             // [64 x 8] K=8 tiles, column 0 == b2 (tf32 hi / lo parts)
+constexpr uint32_t OFF_BIAS_LO = OFF_BIAS_HI + 2048;
+constexpr uint32_t OFF_MBAR = OFF_BIAS_LO + 2048;
 constexpr uint32_t OFF_ABORT = OFF_MBAR + 8 * GROUPS;
 constexpr uint32_t OFF_SLOT = OFF_ABORT + 4 * GROUPS;
-constexpr uint32_t SMEM_BYTES = OFF_SLOT + 16 + 1024;         // + slack to align the base to 1024 B
+constexpr uint32_t OFF_TURN = OFF_SLOT + 8;                   // 2 mbarriers: the tensor token alternating between the group pairs {0,1} and {2,3}
+constexpr uint32_t SMEM_BYTES = OFF_TURN + 8 * 2 + 1024;         // + slack to align the base to 1024 B
 constexpr uint32_t TMEM_COLS = 512, TMEM_COLS_PER_GROUP = 128;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;        // ~1 s: far beyond any legitimate wait
 constexpr uint32_t TF32_MASK = 0xFFFFE000u;
@@ -62,6 +66,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     uint64_t* mbar = reinterpret_cast<uint64_t*>(base + OFF_MBAR) + g;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base + OFF_ABORT) + g;
     uint32_t* slot = reinterpret_cast<uint32_t*>(base + OFF_SLOT);
+    uint64_t* turn = reinterpret_cast<uint64_t*>(base + OFF_TURN);
 
     // ---- one-time staging of the second layer (B operand); arena = W1[64,3] b1[64] W2[64,64] b2[64] W3[1,64] b3[1] ----
     const float* P = a.params;
@@ -73,13 +78,25 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
         *reinterpret_cast<float*>(base + OFF_B_HI + off) = hi;
         *reinterpret_cast<float*>(base + OFF_B_LO + off) = w - hi;
     }
+    // bias of layer 2 as one extra K step: D += ones[128 x 8] * bias[64 x 8]^T with only column 0 populated
+    for(int idx = tid; idx < TILE * 8; idx += THREADS)
+        *reinterpret_cast<float*>(base + OFF_ONES + tc::noswizzle_k8_offset(idx >> 3, idx & 7)) = (idx & 7) == 0 ? 1.0f : 0.0f;
+    for(int idx = tid; idx < H * 8; idx += THREADS){
+        const int j = idx >> 3, k = idx & 7;
+        const float b = k == 0 ? __ldg(P + P_B2 + j) : 0.0f;
+        const float hi = __uint_as_float(__float_as_uint(b) & TF32_MASK);
+        *reinterpret_cast<float*>(base + OFF_BIAS_HI + tc::noswizzle_k8_offset(j, k)) = hi;
+        *reinterpret_cast<float*>(base + OFF_BIAS_LO + tc::noswizzle_k8_offset(j, k)) = b - hi;
+    }
     if(r == 0){ tc::mbar_init(mbar, 1); *abort_flag = 0; }
+    if(tid < 2) tc::mbar_init(turn + tid, 2);                 // each completes when BOTH leaders of the other pair have issued
     if(tid == 0) tc::fence_mbar_init();
     if(warp == 0){ tc::tmem_alloc(slot, TMEM_COLS); tc::tmem_relinquish(); }
     tc::fence_proxy_async_smem();
     tc::fence_before_thread_sync();
     __syncthreads();
     tc::fence_after_thread_sync();
+    if(tid == 0){ tc::mbar_arrive(turn); tc::mbar_arrive(turn); }          // pair {0,1} holds the token first
     const uint32_t tmem_base = *slot;
     const uint32_t tmem_d = tmem_base + (uint32_t)g * TMEM_COLS_PER_GROUP;          // accumulator: 64 columns
     const uint32_t tmem_a = tmem_d + 64;                                            // A_hi: 64 columns
@@ -87,15 +104,32 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     uint8_t* a_lo = base + OFF_A_LO + (uint32_t)g * A_LO_BYTES;
     const uint64_t desc_a_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(a_lo));
     const uint64_t desc_b_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_HI)), desc_b_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_LO));
+    const uint64_t desc_ones = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_ONES));
+    const uint64_t desc_bias_hi = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_BIAS_HI)), desc_bias_lo = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_BIAS_LO));
     constexpr uint32_t IDESC = tc::make_idesc_tf32(TILE, H);
     uint8_t* my_row_lo = a_lo + r * 128;
     const uint32_t swz = (uint32_t)r & 7;
     const int act1 = a.acts[0], act2 = a.acts[1], act3 = a.acts[2];
     const uint32_t bar_id = 1 + g;
-    uint32_t phase = 0;
+    uint32_t phase = 0, turn_phase = 0;
     bool failed = false;
+    uint64_t* my_turn = turn + (g >> 1);
+    uint64_t* next_turn = turn + ((g >> 1) ^ 1);
 
-    for(int tile = blockIdx.x * GROUPS + g; tile < n_tiles && !failed; tile += gridDim.x * GROUPS){
+    const int rounds = (n_tiles + (int)gridDim.x * GROUPS - 1) / ((int)gridDim.x * GROUPS);
+    for(int round = 0; round < rounds && !failed; round++){
+        const int tile = (round * (int)gridDim.x + (int)blockIdx.x) * GROUPS + g;
+        if(tile >= n_tiles){
+            // no environments for this group in this round: it still hands the tensor token on, once per step
+            if(r == 0){
+                for(int t = 0; t < a.n_steps; t++){
+                    if(!tc::mbar_wait_bounded(my_turn, turn_phase, WAIT_LIMIT_CYCLES)){ failed = true; break; }
+                    turn_phase ^= 1;
+                    tc::mbar_arrive(next_turn);
+                }
+            }
+            continue;
+        }
         const int local = tile * envs_per_tile + r;
         const bool valid = r < envs_per_tile && local < a.env_count;
         const int e = a.env_begin + (valid ? local : 0);
@@ -148,7 +182,13 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             if(*abort_flag){ failed = true; break; }
 
             // ---- layer 2 on the tensor core: D[128x64] = A_lo*B_hi + A_hi*B_lo + A_hi*B_hi ----
+            // The tensor token alternates between the group pairs {0,1} and {2,3}. If all four leaders issue at once the
+            // tensor core interleaves the four batches, they finish together and the groups fall into lock step (everyone
+            // computes, then everyone waits for the tensor core). With the token, one pair's MMA batches run while the other
+            // pair is in its CUDA-core phases; two batches in flight still hide the accumulator dependency between MMAs.
             if(r == 0){
+                if(!tc::mbar_wait_bounded(my_turn, turn_phase, WAIT_LIMIT_CYCLES)){ *abort_flag = 1; if(a.error_flag) *a.error_flag = 2; }
+                turn_phase ^= 1;
                 tc::fence_after_thread_sync();
 #pragma unroll
                 for(int kb = 0; kb < 2; kb++)
@@ -164,8 +204,12 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                         for(int ks = 0; ks < 4; ks++)
                             tc::mma_tf32_ts(tmem_d, tmem_a + (uint32_t)(kb * 32 + ks * 8), db + (uint64_t)(kb * (B_KBLOCK_BYTES >> 4) + ks * 2), IDESC, 1u);
                 }
+                tc::mma_tf32_ss(tmem_d, desc_ones, desc_bias_lo, IDESC, 1u);
+                tc::mma_tf32_ss(tmem_d, desc_ones, desc_bias_hi, IDESC, 1u);
                 tc::commit(mbar);
+                tc::mbar_arrive(next_turn);
             }
+            __syncwarp();                                     // the leader's lanes rejoin before the warp-wide TMEM loads
             if(!tc::mbar_wait_bounded(mbar, phase, WAIT_LIMIT_CYCLES)){
                 *abort_flag = 1;                              // seen by the whole group after its next barrier
                 if(a.error_flag) *a.error_flag = 2;
@@ -173,7 +217,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             phase ^= 1;
             tc::fence_after_thread_sync();
 
-            // ---- epilogue: bias + activation of layer 2, output layer 64 -> 1 (four partial sums for ILP) ----
+            // ---- epilogue: activation of layer 2 (bias came through the MMA), output layer 64 -> 1 (four partial sums) ----
             float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
             for(int half = 0; half < 2; half++){
@@ -183,10 +227,10 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
 #pragma unroll
                 for(int p = 0; p < 8; p++){
                     const int j = half * 32 + p * 4;
-                    o0 = fmaf(c_actor[C_W3 + j + 0], act_or_rt<A2>(__uint_as_float(d[p * 4 + 0]) + c_actor[C_B2 + j + 0], act2), o0);
-                    o1 = fmaf(c_actor[C_W3 + j + 1], act_or_rt<A2>(__uint_as_float(d[p * 4 + 1]) + c_actor[C_B2 + j + 1], act2), o1);
-                    o2 = fmaf(c_actor[C_W3 + j + 2], act_or_rt<A2>(__uint_as_float(d[p * 4 + 2]) + c_actor[C_B2 + j + 2], act2), o2);
-                    o3 = fmaf(c_actor[C_W3 + j + 3], act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]) + c_actor[C_B2 + j + 3], act2), o3);
+                    o0 = fmaf(c_actor[C_W3 + j + 0], act_or_rt<A2>(__uint_as_float(d[p * 4 + 0]), act2), o0);
+                    o1 = fmaf(c_actor[C_W3 + j + 1], act_or_rt<A2>(__uint_as_float(d[p * 4 + 1]), act2), o1);
+                    o2 = fmaf(c_actor[C_W3 + j + 2], act_or_rt<A2>(__uint_as_float(d[p * 4 + 2]), act2), o2);
+                    o3 = fmaf(c_actor[C_W3 + j + 3], act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]), act2), o3);
                 }
             }
             const float action = activation_rt(c_actor[C_B3] + ((o0 + o1) + (o2 + o3)), act3);

@@ -30,11 +30,16 @@ __device__ __forceinline__ void fence_proxy_async_smem(){ asm volatile("fence.pr
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count){
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar){
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" :: "r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void fence_mbar_init(){ asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity){
     uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    // the last operand is a suspend-time hint: the thread sleeps in hardware until the phase completes (or the hint
+    // expires) instead of burning issue slots that the other groups of the CTA need
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(0x989680u) : "memory");
     return done != 0;
 }
 // Waits for the phase with the given parity, giving up after ~limit_cycles SM clocks. Returns false on time-out so
@@ -61,6 +66,21 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_sw128(uint32_t smem_addr){
     d |= (uint64_t)1 << 46;                               // descriptor version (Blackwell)
     d |= (uint64_t)2 << 61;                               // layout type: SWIZZLE_128B
     return d;
+}
+// Descriptor for a K-major operand WITHOUT swizzle whose K extent is one instruction (8 tf32 = 32 bytes per row): "core
+// matrices" of 8 rows x 16 bytes are stored contiguously (row i at +16 i); the second 16-byte K chunk of the same 8 rows
+// follows at +128 bytes (leading byte offset), the next 8 rows at +256 bytes (stride byte offset). A 128-row tile is 4 KB.
+__device__ __forceinline__ uint64_t make_desc_kmajor_noswizzle_k8(uint32_t smem_addr){
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(128 >> 4) << 16;                      // leading byte offset: next K chunk
+    d |= (uint64_t)(256 >> 4) << 32;                      // stride byte offset: next 8 rows
+    d |= (uint64_t)1 << 46;                               // descriptor version (Blackwell)
+    return d;                                             // layout type 0: no swizzle
+}
+// byte offset of element (row, k) inside such a tile
+__host__ __device__ constexpr uint32_t noswizzle_k8_offset(uint32_t row, uint32_t k){
+    return (row >> 3) * 256u + (k >> 2) * 128u + (row & 7u) * 16u + (k & 3u) * 4u;
 }
 // Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major, shape M x N (K = 8 per instruction)
 __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N){

@@ -27,6 +27,7 @@ extern "C" {
 #define B200RL_ERR_UNSUPPORTED 2        /* a shape / activation this build has no kernel for */
 #define B200RL_ERR_CUDA 3               /* a CUDA runtime call failed; see b200rl_last_cuda_error() */
 #define B200RL_ERR_DEVICE_FLAG 4        /* a kernel reported a problem through its error flag */
+#define B200RL_ERR_SCRATCH_LIMIT 5      /* the problem needs more scratch than the built-in static buffer holds */
 
 /* activation ids: nn/activation_functions.h:10-20 */
 #define B200RL_ACT_IDENTITY 0
@@ -68,6 +69,24 @@ size_t b200rl_dense_backward_scratch_bytes(int batch, int input_dim, int output_
 int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
                           float* d_W, float* d_bias, float* d_in, int ldi, int batch, int input_dim, int output_dim, int activation,
                           void* scratch, size_t scratch_bytes, b200rl_stream_t stream);
+
+/* The same backward pass for callers that have no scratch buffer to give and must not allocate one.
+ * (No counterpart in the reference: its backward takes no scratch argument because cuBLAS manages its own workspace.)
+ * Who needs it: code that sits behind the reference's own signature backward(device, layer, input, d_output, buffer)
+ * -- there is no parameter through which scratch could arrive, and calling cudaMalloc inside a training step is not an
+ * option there, since it synchronises the whole device and the memory is usually already handed out to another
+ * allocator. The split-batch partial sums live instead in a static device array inside the library,
+ * B200RL_STATIC_SCRATCH_BYTES (8 MiB) large, which every GPU that loads the library holds until the process exits.
+ *   - problems that need more (see b200rl_dense_backward_scratch_bytes) are refused with B200RL_ERR_SCRATCH_LIMIT;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *     before any stream capture begins on that device;
+ *   - the call makes no cudaMalloc / cudaFree and uses no allocating library routine;
+ *   - all calls share the one array: two calls whose kernels can overlap on the GPU (different streams) race on it.
+ *     Nothing in it has to start at zero -- every partial sum that is read was written earlier in the same call. */
+#define B200RL_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+int b200rl_dense_backward_static_scratch(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
+                                         float* d_W, float* d_bias, float* d_in, int ldi, int batch, int input_dim, int output_dim,
+                                         int activation, b200rl_stream_t stream);
 
 /* d_a = 2 w (a - b) / (rows cols). Replaces nn::loss_functions::mse::gradient (nn/loss_functions/mse/operations_cuda.h:41-58). */
 int b200rl_mse_gradient(const float* a, int lda, const float* b, int ldb, float* d_a, int ldd, int rows, int cols, float loss_weight,

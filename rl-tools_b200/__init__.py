@@ -90,6 +90,7 @@ def lib():
         L.b200rl_dense_backward_scratch_bytes.argtypes = [i, i, i]
         L.b200rl_dense_backward_scratch_bytes.restype = sz
         L.b200rl_dense_backward.argtypes = [vp, vp, i, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, vp, sz, vp]
+        L.b200rl_dense_backward_static_scratch.argtypes = [vp, vp, i, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, vp]
         L.b200rl_mse_gradient.argtypes = [vp, i, vp, i, vp, i, i, i, f, vp]
         L.b200rl_fill.argtypes = [vp, sz, f, vp]
         L.b200rl_mlp_num_params.argtypes = [shape_p]

@@ -259,6 +259,44 @@ int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* 
     return dense_backward_impl(W, x, ldx, pre, ldpre, d_out, ldd, d_W, d_bias, d_in, ldi, batch, input_dim, output_dim, activation, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
+// ---- backward without caller scratch and without allocation ----------------------------------------------------
+// The partial sums go to this file-scope device array. In host code its name is only a handle, not a device address:
+// the address is looked up once per device with cudaGetSymbolAddress (with that device current) and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[B200RL_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void** out){
+    constexpr int MAX_DEVICES = 64;
+    static void* cached[MAX_DEVICES] = {};
+    int dev = 0;
+    B200RL_CUDA_TRY(cudaGetDevice(&dev));
+    if(dev < 0 || dev >= MAX_DEVICES) return B200RL_ERR_UNSUPPORTED;
+    if(cached[dev] == nullptr){
+        void* p = nullptr;
+        B200RL_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return B200RL_OK;
+}
+
+int b200rl_dense_backward_static_scratch(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
+                                         float* d_W, float* d_bias, float* d_in, int ldi, int batch, int input_dim, int output_dim,
+                                         int activation, b200rl_stream_t stream){
+    if(!W || !pre || !d_out || batch < 0 || input_dim < 1 || output_dim < 1 || ldpre < output_dim || ldd < output_dim || !valid_activation(activation))
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if((d_W == nullptr) != (d_bias == nullptr)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(d_W && (!x || ldx < input_dim)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(d_in && ldi < input_dim) return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    const size_t need = d_W ? plan_backward(batch, input_dim, output_dim).bytes : 0;
+    if(need > (size_t)B200RL_STATIC_SCRATCH_BYTES) return B200RL_ERR_SCRATCH_LIMIT;
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if(rc) return rc;
+    return dense_backward_impl(W, x, ldx, pre, ldpre, d_out, ldd, d_W, d_bias, d_in, ldi, batch, input_dim, output_dim, activation,
+                               scratch, B200RL_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+}
+
 size_t b200rl_mlp_num_params(const b200rl_mlp_shape* sh){
     if(!valid_shape(sh)) return 0;
     size_t n = 0; int in = sh->input_dim;

@@ -116,6 +116,7 @@ const char* b200rl_status_string(int status){
         case B200RL_ERR_UNSUPPORTED: return "unsupported shape or activation";
         case B200RL_ERR_CUDA: return "CUDA runtime error";
         case B200RL_ERR_DEVICE_FLAG: return "a kernel raised its error flag";
+        case B200RL_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the static buffer (B200RL_STATIC_SCRATCH_BYTES) holds";
         default: return "unknown status";
     }
 }

@@ -151,6 +151,29 @@ int b200rl_adam_reset(uint32_t* state, b200rl_stream_t stream);
 int b200rl_adam_step(float* params, const float* grads, float* m, float* v, size_t n, b200rl_adam_hyper hyper, uint32_t* state,
                      b200rl_stream_t stream);
 
+/* Per-tensor form of the same optimizer for hosts that keep the reference's one-tensor-per-parameter storage and its
+ * device-resident optimizer struct (nn::optimizers::Adam: parameters, bias-correction scalars, age):
+ *   hyper9 -> nn::optimizers::adam::Parameters<float> on the device (alpha, beta_1, beta_2, epsilon, epsilon_sqrt, ...);
+ *   b200rl_adam_advance_dev = _step (nn/optimizers/adam/operations_cuda.h:56-58): c1, c2 from the age, age += 1;
+ *   b200rl_adam_update_dev  = update of one parameter tensor (nn/optimizers/adam/instance/operations_cuda.h:60-70). */
+int b200rl_adam_advance_dev(const float* hyper9, uint32_t* age, float* c1, float* c2, b200rl_stream_t stream);
+int b200rl_adam_update_dev(float* params, const float* grads, float* m, float* v, size_t n, const float* hyper9, const float* c1,
+                           const float* c2, b200rl_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Device memory and copies for hosts compiled without the CUDA toolkit (the header-only adapter needs nothing but
+ * this header). Replace cudaMalloc / cudaFree / cudaMemcpyAsync + synchronise in containers/matrix/operations_cuda.h
+ * :16-40,105-195 and containers/tensor/operations_cuda.h:16-40,74-166. kind: 0 = host to device, 1 = device to host,
+ * 2 = device to device. b200rl_memcpy_2d copies `rows` rows of `width_bytes` with independent pitches (views).
+ * Copies that touch host memory synchronise the stream before returning, as the reference's do.
+ * ------------------------------------------------------------------------------------------------------- */
+int b200rl_device_malloc(void** ptr, size_t bytes);
+int b200rl_device_free(void* ptr);
+int b200rl_memcpy(void* dst, const void* src, size_t bytes, int kind, b200rl_stream_t stream);
+int b200rl_memcpy_2d(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes, size_t width_bytes, size_t rows, int kind,
+                     b200rl_stream_t stream);
+int b200rl_stream_synchronize(b200rl_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Pendulum rollout: T x { reset-if-truncated, observe, actor forward, step, reward, counters } for N environments in
  * ONE persistent launch. Semantics per step are the off-policy runner's prologue / interlude / epilogue with

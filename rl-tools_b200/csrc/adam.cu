@@ -60,6 +60,18 @@ __global__ void __launch_bounds__(256) adam_step_kernel(float* __restrict__ p, c
         }
     }
 }
+__global__ void adam_advance_dev_kernel(const float* hyper9, uint32_t* age, float* c1, float* c2){
+    const uint32_t a = *age;
+    *c1 = bias_correction(hyper9[1], a);
+    *c2 = bias_correction(hyper9[2], a);
+    *age = a + 1;
+}
+__global__ void __launch_bounds__(256) adam_update_dev_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, size_t n,
+                                                              const float* __restrict__ hyper9, const float* __restrict__ c1p, const float* __restrict__ c2p){
+    b200rl_adam_hyper h{hyper9[0], hyper9[1], hyper9[2], hyper9[3], hyper9[4]};
+    const float c1 = *c1p, c2 = *c2p;
+    for(size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) adam_one(p[i], g[i], m[i], v[i], h, c1, c2);
+}
 __global__ void adam_reset_kernel(AdamState* s){ s->age = 1; s->ticket = 0; s->c1 = 0.0f; s->c2 = 0.0f; }
 
 __global__ void __launch_bounds__(256) mse_gradient_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long ldb, float* d, long long ldd,
@@ -109,6 +121,20 @@ int b200rl_adam_step(float* params, const float* grads, float* m, float* v, size
     int grid = grid_for(vec_ok ? (n + 3) / 4 : n, 256);
     adam_step_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(params, grads, m, v, n, hyper, reinterpret_cast<AdamState*>(state), vec_ok);
     B200RL_LAUNCH_CHECK("adam_step");
+    return B200RL_OK;
+}
+
+int b200rl_adam_advance_dev(const float* hyper9, uint32_t* age, float* c1, float* c2, b200rl_stream_t stream){
+    if(!hyper9 || !age || !c1 || !c2) return B200RL_ERR_INVALID_ARGUMENT;
+    adam_advance_dev_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(hyper9, age, c1, c2);
+    B200RL_LAUNCH_CHECK("adam_advance_dev");
+    return B200RL_OK;
+}
+int b200rl_adam_update_dev(float* params, const float* grads, float* m, float* v, size_t n, const float* hyper9, const float* c1, const float* c2, b200rl_stream_t stream){
+    if(!params || !grads || !m || !v || !hyper9 || !c1 || !c2) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n == 0) return B200RL_OK;
+    adam_update_dev_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(params, grads, m, v, n, hyper9, c1, c2);
+    B200RL_LAUNCH_CHECK("adam_update_dev");
     return B200RL_OK;
 }
 

@@ -122,6 +122,40 @@ const char* b200rl_status_string(int status){
 }
 const char* b200rl_last_cuda_error(void){ return g_last_cuda_error.c_str(); }
 
+int b200rl_device_malloc(void** ptr, size_t bytes){
+    if(!ptr) return B200RL_ERR_INVALID_ARGUMENT;
+    B200RL_CUDA_TRY(cudaMalloc(ptr, bytes ? bytes : 1));
+    return B200RL_OK;
+}
+int b200rl_device_free(void* ptr){
+    if(ptr) B200RL_CUDA_TRY(cudaFree(ptr));
+    return B200RL_OK;
+}
+static bool memcpy_kind(int kind, cudaMemcpyKind* out){
+    if(kind == 0) *out = cudaMemcpyHostToDevice; else if(kind == 1) *out = cudaMemcpyDeviceToHost; else if(kind == 2) *out = cudaMemcpyDeviceToDevice; else return false;
+    return true;
+}
+int b200rl_memcpy(void* dst, const void* src, size_t bytes, int kind, b200rl_stream_t stream){
+    cudaMemcpyKind k;
+    if(!dst || !src || !memcpy_kind(kind, &k)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(bytes == 0) return B200RL_OK;
+    B200RL_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, k, (cudaStream_t)stream));
+    if(kind != 2) B200RL_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200RL_OK;
+}
+int b200rl_memcpy_2d(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes, size_t width_bytes, size_t rows, int kind, b200rl_stream_t stream){
+    cudaMemcpyKind k;
+    if(!dst || !src || !memcpy_kind(kind, &k) || dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes) return B200RL_ERR_INVALID_ARGUMENT;
+    if(width_bytes == 0 || rows == 0) return B200RL_OK;
+    B200RL_CUDA_TRY(cudaMemcpy2DAsync(dst, dst_pitch_bytes, src, src_pitch_bytes, width_bytes, rows, k, (cudaStream_t)stream));
+    if(kind != 2) B200RL_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200RL_OK;
+}
+int b200rl_stream_synchronize(b200rl_stream_t stream){
+    B200RL_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200RL_OK;
+}
+
 int b200rl_rng_init_host(uint32_t* rng_state_host, uint32_t seed){
     if(!rng_state_host) return B200RL_ERR_INVALID_ARGUMENT;
     mt_seed(rng_state_host, seed + 1u);     // random/operations_cpu.h:23

@@ -1,0 +1,81 @@
+// Header-only adapter, part 1: the device tag `rl_tools::devices::B200` for RLtools' overload-on-device-type API.
+//
+// Include AFTER <rl_tools/operations/cpu.h> (the host device is needed for host<->device copies and for the host-side
+// math/random/logging sub-devices) and BEFORE the reference's generic nn / nn_models headers; then include
+// <b200rl/rl_tools_operations.h>. User code is compiled with the host compiler only and linked against libb200rl.so.
+//
+// Mirrors the interface of the reference's CUDA device (devices/cuda.h:16-125: index_t = unsigned int,
+// DEVICE_ID = DeviceId::CUDA, SPEC::{MATH, RANDOM, LOGGING}, members math / random / logger / stream,
+// graph_capture_active) without cuBLAS / cuRAND handles. Errors are sticky in `device.status` (the reference prints
+// and continues); `check_status(device)` returns it.
+#pragma once
+#include <b200rl.h>
+#include <rl_tools/containers/tensor/tensor.h>
+#include <rl_tools/nn/optimizers/adam/adam.h>
+
+RL_TOOLS_NAMESPACE_WRAPPER_START
+namespace rl_tools::devices{
+    namespace b200{
+        struct Base{
+            static constexpr DeviceId DEVICE_ID = DeviceId::CUDA;
+            using index_t = unsigned int;
+            static constexpr index_t MAX_INDEX = -1;
+        };
+    }
+    struct DefaultB200Specification{
+        using MATH = devices::math::CPU;                 // scalar host-side math (hyper-parameters, bounds)
+        using MATH_DEVICE_ACCURATE = devices::math::CPU;
+        using RANDOM = devices::random::CPU;             // the CPU engine is the source of truth for parity
+        using LOGGING = devices::logging::CPU;
+        static constexpr bool TAG = false;
+        static constexpr bool KERNEL = false;
+    };
+    template <typename T_SPEC>
+    struct B200: b200::Base{
+        template <typename OTHER_DEVICE>
+        static constexpr bool compatible = OTHER_DEVICE::DEVICE_ID == DeviceId::CUDA;
+        using SPEC = T_SPEC;
+        typename SPEC::MATH math;
+        typename SPEC::RANDOM random;
+        typename SPEC::LOGGING* logger = nullptr;
+        b200rl_stream_t stream = nullptr;                // cudaStream_t; nullptr = the default stream
+        bool graph_capture_active = false;
+        int status = B200RL_OK;                          // first failure of any call on this device
+    };
+    using DefaultB200 = B200<DefaultB200Specification>;
+}
+RL_TOOLS_NAMESPACE_WRAPPER_END
+
+RL_TOOLS_NAMESPACE_WRAPPER_START
+namespace rl_tools{
+    namespace b200{
+        template <typename DEVICE>
+        inline void note(DEVICE& device, int rc){ if(rc != B200RL_OK && device.status == B200RL_OK) device.status = rc; }
+    }
+    template <typename SPEC>
+    void init(devices::B200<SPEC>& device){ device.status = B200RL_OK; }
+    template <typename SPEC>
+    int check_status(devices::B200<SPEC>& device){
+        b200::note(device, b200rl_stream_synchronize(device.stream));
+        return device.status;
+    }
+}
+RL_TOOLS_NAMESPACE_WRAPPER_END
+
+// The per-parameter Adam update must be declared BEFORE the reference's generic layer headers are included: the generic
+// dense `update(device, layer, optimizer)` calls `update(device, layer.weights, optimizer)`, and none of those argument
+// types lives directly in namespace rl_tools, so argument-dependent lookup does not reach overloads declared later (the
+// reference has the same ordering rule, see the note at the top of nn/optimizers/adam/adam.h).
+// Replaces nn/optimizers/adam/instance/operations_cuda.h:60-70.
+RL_TOOLS_NAMESPACE_WRAPPER_START
+namespace rl_tools{
+    template<typename DEV_SPEC, typename SPEC, typename ADAM_SPEC>
+    void update(devices::B200<DEV_SPEC>& device, nn::parameters::Adam::Instance<SPEC>& parameter, nn::optimizers::Adam<ADAM_SPEC>& optimizer){
+        static_assert(tensor::dense_row_major_layout<typename decltype(parameter.parameters)::SPEC>(), "only dense parameter tensors");
+        b200::note(device, b200rl_adam_update_dev(parameter.parameters._data, parameter.gradient._data, parameter.gradient_first_order_moment._data,
+                                                  parameter.gradient_second_order_moment._data, decltype(parameter.parameters)::SPEC::SIZE,
+                                                  reinterpret_cast<const float*>(optimizer.parameters._data), optimizer.first_order_moment_bias_correction._data,
+                                                  optimizer.second_order_moment_bias_correction._data, device.stream));
+    }
+}
+RL_TOOLS_NAMESPACE_WRAPPER_END

@@ -203,6 +203,13 @@ class Mlp:
         self.hyper = AdamHyper()
         self.reset_optimizer_state()
 
+    def d_out_buffer(self):
+        """A reusable [batch, O_last] buffer for the loss gradient."""
+        import torch
+        if not hasattr(self, "_d_out"):
+            self._d_out = torch.empty((self.batch, self.shape.dims[self.shape.n_layers - 1]), device=self.device, dtype=torch.float32)
+        return self._d_out
+
     def output(self):
         O = self.shape.dims[self.shape.n_layers - 1]
         return self.out[-self.batch * O:].view(self.batch, O)

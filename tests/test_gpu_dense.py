@@ -178,3 +178,21 @@ def test_mlp_train_steps_vs_reference_golden(lib, torch, path):
     net.backward(xd, td.clone(), d_input=d_in)
     check("full_grads", net.grads, tensor_scale=1e-5)
     check("full_d_input", d_in, tensor_scale=1e-5)
+
+
+def test_sharded_train_step_matches_oracle_full_batch(lib, orc, torch):
+    """Two chunks accumulated with the chunk loss weight + one Adam step == the oracle's full-batch step (world size 1)."""
+    from rl_tools_b200 import parallel
+    dims, acts = [32, 32, 4], ["relu", "relu", "identity"]
+    shape = oracle.MlpShape.make(8, dims, acts)
+    total, chunk = 512, 256
+    params = mg.det_uniform(41, shape.num_params()) * np.float32(0.3)
+    x = mg.det_normal(42, total * 8).reshape(total, 8)
+    y = mg.det_normal(43, total * 4).reshape(total, 4)
+    net = lib.Mlp(8, dims, acts, chunk)
+    net.params.copy_(dev(torch, params))
+    parallel.sharded_train_step(lib, net, dev(torch, x), dev(torch, y), total)
+    p_ref, g_ref, m_ref, v_ref, _, _ = orc.mlp_train_steps(shape, params, x, y, 1)
+    scale = float(np.abs(g_ref).max())
+    close(net.grads, g_ref, rtol=1e-5, atol=1e-6 + 1e-5 * scale)
+    close(net.params, p_ref, rtol=1e-5, atol=2e-6)

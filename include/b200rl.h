@@ -161,6 +161,31 @@ int b200rl_adam_update_dev(float* params, const float* grads, float* m, float* v
                            const float* c2, b200rl_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * PPO update pieces (host scalar loops in the reference, which therefore cannot run on its CUDA device).
+ * All column arguments carry an element pitch (ld_*): pass the dataset matrix's row pitch to work on column views of the
+ * on-policy dataset (rl/components/on_policy_runner/on_policy_runner.h:38-72, row = step * n_envs + env), or 1 for plain
+ * arrays. Flags are stored as floats (non-zero = true), as the dataset stores them.
+ * ------------------------------------------------------------------------------------------------------- */
+
+/* Generalized advantage estimation, one backward scan per environment. all_values has (steps + 1) * n_envs rows.
+ * Replaces estimate_generalized_advantages (rl/algorithms/ppo/operations_generic.h:59-95). */
+int b200rl_gae(const float* rewards, int ld_rewards, const float* all_values, int ld_values, const float* terminated, int ld_terminated,
+               const float* truncated, int ld_truncated, float* advantages, int ld_advantages, float* target_values, int ld_targets,
+               int n_envs, int steps, float gamma, float lambda, int ignore_termination, b200rl_stream_t stream);
+
+/* Gradient of the clipped-surrogate PPO loss of one minibatch with respect to the actor output (d_actions [batch, A]) and
+ * the state-independent log_std (d_log_std [A], ACCUMULATED): advantage mean/std over the minibatch, Gaussian log-prob of
+ * the rollout actions under the current policy, ratio clipping, entropy bonus.
+ * Replaces the per-sample loop of train (rl/algorithms/ppo/operations_generic.h:173-184, 214-296; Gaussian head
+ * random/operations_generic.h:87-121). current_actions = actor forward output on the minibatch observations.
+ * scratch: b200rl_ppo_scratch_bytes(batch, action_dim) bytes of device memory; action_dim <= 64. */
+size_t b200rl_ppo_scratch_bytes(int batch, int action_dim);
+int b200rl_ppo_policy_gradient(const float* current_actions, int ld_current, const float* rollout_actions, int ld_rollout, const float* log_std,
+                               const float* rollout_log_probs, int ld_log_probs, const float* advantages, int ld_advantages, float* d_actions, int ld_d,
+                               float* d_log_std, int batch, int action_dim, float epsilon_clip, float entropy_coefficient, float advantage_epsilon,
+                               int normalize_advantage, int learn_action_std, void* scratch, size_t scratch_bytes, b200rl_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Device memory and copies for hosts compiled without the CUDA toolkit (the header-only adapter needs nothing but
  * this header). Replace cudaMalloc / cudaFree / cudaMemcpyAsync + synchronise in containers/matrix/operations_cuda.h
  * :16-40,105-195 and containers/tensor/operations_cuda.h:16-40,74-166. kind: 0 = host to device, 1 = device to host,

@@ -87,6 +87,8 @@ class Oracle:
         L.orc_reset_table.argtypes = [C.c_void_p, C.c_int, C.c_int, _i32p, _u8p, C.c_int, _f32p, C.c_int]
         L.orc_reset_table.restype = C.c_int
         L.orc_gae.argtypes = [_f32p, _f32p, _u8p, _u8p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
+        L.orc_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
+        L.orc_ppo_policy_gradient.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_float, C.c_int, C.c_int]
 
     # --- RNG -----------------------------------------------------------------------------------------------
     def uniform_stream(self, seed, n, lo, hi):
@@ -225,6 +227,22 @@ class Oracle:
         return adv, tgt
 
 
+    def normal_functions(self, mean, log_std, value):
+        n = mean.size
+        lp, dm, dl = np.empty(n, np.float32), np.empty(n, np.float32), np.empty(n, np.float32)
+        self.lib.orc_normal_functions(n, mean, log_std, value, lp, dm, dl)
+        return lp, dm, dl
+
+    def ppo_policy_gradient(self, current_actions, rollout_actions, log_std, rollout_log_probs, advantages, d_log_std=None,
+                            epsilon_clip=0.2, entropy_coefficient=0.01, advantage_epsilon=1e-8, normalize_advantage=True, learn_action_std=True):
+        B, A = current_actions.shape
+        d_actions = np.empty((B, A), np.float32)
+        d_log_std = np.zeros(A, np.float32) if d_log_std is None else d_log_std.copy()
+        self.lib.orc_ppo_policy_gradient(current_actions, rollout_actions, log_std, rollout_log_probs, advantages, d_actions, d_log_std, B, A,
+                                         epsilon_clip, entropy_coefficient, advantage_epsilon, int(normalize_advantage), int(learn_action_std))
+        return d_actions, d_log_std
+
+
 class Reference:
     """Typed wrapper around the real reference (libref_strict.so / libref_fast.so). Present only where it was built."""
 
@@ -244,6 +262,8 @@ class Reference:
         L.ref_pendulum_rollout.argtypes = [C.c_int, _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int,
                                            _f32p, _f32p, _f32p, C.c_int]
         L.ref_pendulum_rollout.restype = C.c_int
+        L.ref_gae.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _f32p, _f32p]
+        L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
 
     def cases(self):
         out = {}
@@ -275,6 +295,17 @@ class Reference:
         assert rc == 0, name
         res["seconds"] = sec.value
         return res
+
+    def gae(self, rewards, all_values, terminated, truncated, N, steps):
+        adv, tgt = np.empty(steps * N, np.float32), np.empty(steps * N, np.float32)
+        assert self.lib.ref_gae(N, steps, rewards, all_values, terminated, truncated, adv, tgt) == 0
+        return adv, tgt
+
+    def normal_functions(self, mean, log_std, value):
+        n = mean.size
+        lp, dm, dl = np.empty(n, np.float32), np.empty(n, np.float32), np.empty(n, np.float32)
+        self.lib.ref_normal_functions(n, mean, log_std, value, lp, dm, dl)
+        return lp, dm, dl
 
     def uniform_stream(self, seed, n, lo, hi):
         out = np.empty(n, np.float32)

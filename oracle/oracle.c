@@ -426,3 +426,82 @@ void orc_gae(const float* rewards, const float* all_values, const uint8_t* termi
         }
     }
 }
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* Diagonal-Gaussian policy head: random/operations_generic.h:87-121 (log_prob and its derivatives).        */
+/* neg_log_sqrt_pi is a double expression (-0.5 * log(2 pi)) rounded to float on assignment.                 */
+/* ------------------------------------------------------------------------------------------------------ */
+float orc_normal_log_prob(float mean, float log_std, float value){
+    float neg_log_sqrt_pi = -0.5 * logf(2 * ORC_PI_F);
+    float diff = value - mean;
+    float std = expf(log_std);
+    float pre_square = diff / std;
+    return neg_log_sqrt_pi - log_std - 0.5 * pre_square * pre_square;
+}
+float orc_normal_d_log_prob_d_mean(float mean, float log_std, float value){
+    float diff = value - mean; float std = expf(log_std); float pre_square = diff / std;
+    return pre_square / std;
+}
+float orc_normal_d_log_prob_d_log_std(float mean, float log_std, float value){
+    float diff = value - mean; float std = expf(log_std); float pre_square = diff / std;
+    return -1 + pre_square * pre_square;
+}
+void orc_normal_functions(int n, const float* mean, const float* log_std, const float* value, float* lp, float* dmean, float* dlogstd){
+    for(int i = 0; i < n; i++){
+        lp[i] = orc_normal_log_prob(mean[i], log_std[i], value[i]);
+        dmean[i] = orc_normal_d_log_prob_d_mean(mean[i], log_std[i], value[i]);
+        dlogstd[i] = orc_normal_d_log_prob_d_log_std(mean[i], log_std[i], value[i]);
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* PPO minibatch loss gradient w.r.t. the actor output and log_std: rl/algorithms/ppo/operations_generic.h   */
+/* :173-184 (advantage mean / std over the minibatch), :214-296 (per-sample clipped surrogate gradient,      */
+/* entropy bonus, log_std gradient accumulation). Default parameters (rl/algorithms/ppo/ppo.h:13-38).        */
+/* current_actions [B,A] = actor(obs) with the current parameters; rollout_actions [B,A], rollout_log_probs  */
+/* [B], advantages [B] from the dataset; d_actions [B,A] receives d loss / d actor output; d_log_std [A]      */
+/* ACCUMULATES (the reference increments log_std.gradient, zeroed by zero_gradient before).                  */
+/* ------------------------------------------------------------------------------------------------------ */
+void orc_ppo_policy_gradient(const float* current_actions, const float* rollout_actions, const float* log_std, const float* rollout_log_probs,
+                             const float* advantages, float* d_actions, float* d_log_std, int B, int A,
+                             float epsilon_clip, float entropy_coefficient, float advantage_epsilon, int normalize_advantage, int learn_action_std){
+    float advantage_mean = 0, advantage_std = 0;
+    if(normalize_advantage){
+        for(int b = 0; b < B; b++){ float a = advantages[b]; advantage_mean += a; advantage_std += a * a; }
+        advantage_mean /= B; advantage_std /= B;
+        float var = advantage_std - advantage_mean * advantage_mean;
+        advantage_std = sqrtf(var > 0 ? var : 0);
+    }
+    float* d_lp_d_logstd = (float*)malloc(sizeof(float) * (size_t)A);
+    for(int b = 0; b < B; b++){
+        float action_log_prob = 0;
+        for(int i = 0; i < A; i++){
+            float cur = current_actions[(size_t)b * A + i], roll = rollout_actions[(size_t)b * A + i], ls = log_std[i];
+            action_log_prob += orc_normal_log_prob(cur, ls, roll);
+            d_actions[(size_t)b * A + i] = orc_normal_d_log_prob_d_mean(cur, ls, roll);
+            if(learn_action_std){
+                float d_entropy = -(float)1 / B * entropy_coefficient;
+                d_log_std[i] += d_entropy;
+                d_lp_d_logstd[i] = orc_normal_d_log_prob_d_log_std(cur, ls, roll);
+            }
+        }
+        float advantage = advantages[b];
+        if(normalize_advantage) advantage = (advantage - advantage_mean) / (advantage_std + advantage_epsilon);
+        float log_ratio = action_log_prob - rollout_log_probs[b];
+        float ratio = expf(log_ratio);
+        float lo = 1 - epsilon_clip, hi = 1 + epsilon_clip;
+        float clipped_ratio = ratio < lo ? lo : (ratio > hi ? hi : ratio);
+        int clipped = ratio != clipped_ratio;
+        float normal_advantage = ratio * advantage, clipped_advantage = clipped_ratio * advantage;
+        int ratio_min_switch = normal_advantage - clipped_advantage <= 0.0f;
+        float d_loss_d_surrogate = -(float)1 / B;
+        float d_surrogate_d_ratio = (ratio_min_switch ? 1.0f : 0.0f) * advantage + (ratio_min_switch ? 0.0f : 1.0f) * advantage * (clipped ? 0.0f : 1.0f);
+        float d_loss_d_ratio = d_loss_d_surrogate * d_surrogate_d_ratio;
+        float d_loss_d_lp = d_loss_d_ratio * ratio;
+        for(int i = 0; i < A; i++){
+            d_actions[(size_t)b * A + i] *= d_loss_d_lp;
+            if(learn_action_std) d_log_std[i] += d_loss_d_lp * d_lp_d_logstd[i];
+        }
+    }
+    free(d_lp_d_logstd);
+}

@@ -34,6 +34,9 @@
 #include <rl_tools/nn_models/mlp/operations_generic.h>
 #include <rl_tools/nn/optimizers/adam/operations_generic.h>
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
+#include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
+#include <rl_tools/rl/algorithms/ppo/ppo.h>
+#include <rl_tools/rl/algorithms/ppo/operations_generic.h>
 
 #include <cstdint>
 #include <cstring>
@@ -322,7 +325,40 @@ struct Rollout{
     }
 };
 
+// GAE through the reference's own Dataset + estimate_generalized_advantages (rl/algorithms/ppo/operations_generic.h:59-95)
+template <TI N, TI STEPS>
+static void gae_case(const float* rewards, const float* all_values, const uint8_t* terminated, const uint8_t* truncated, float* advantages, float* target_values){
+    using RUNNER_SPEC = rlt::rl::components::on_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, bool, N>;
+    using DATASET_SPEC = rlt::rl::components::on_policy_runner::DatasetSpecification<RUNNER_SPEC, STEPS>;
+    using PARAMETERS = rlt::rl::algorithms::ppo::DefaultParameters<TYPE_POLICY, TI, 64>;
+    DEVICE device;
+    rlt::rl::components::on_policy_runner::Dataset<DATASET_SPEC> dataset;
+    rlt::malloc(device, dataset);
+    for(TI i = 0; i < STEPS * N; i++){
+        rlt::set(dataset.rewards, i, 0, rewards[i]); rlt::set(dataset.terminated, i, 0, (T)terminated[i]); rlt::set(dataset.truncated, i, 0, (T)truncated[i]);
+    }
+    for(TI i = 0; i < (STEPS + 1) * N; i++) rlt::set(dataset.all_values, i, 0, all_values[i]);
+    rlt::estimate_generalized_advantages(device, dataset, PARAMETERS{});
+    for(TI i = 0; i < STEPS * N; i++){ advantages[i] = rlt::get(dataset.advantages, i, 0); target_values[i] = rlt::get(dataset.target_values, i, 0); }
+    rlt::free(device, dataset);
+}
+
 extern "C" {
+
+int ref_gae(int N, int steps, const float* rewards, const float* all_values, const uint8_t* terminated, const uint8_t* truncated, float* advantages, float* target_values){
+    if(N == 64 && steps == 1024){ gae_case<64, 1024>(rewards, all_values, terminated, truncated, advantages, target_values); return 0; }
+    if(N == 5 && steps == 37){ gae_case<5, 37>(rewards, all_values, terminated, truncated, advantages, target_values); return 0; }
+    return -1;
+}
+// Gaussian head: random/operations_generic.h:87-121
+void ref_normal_functions(int n, const float* mean, const float* log_std, const float* value, float* lp, float* dmean, float* dlogstd){
+    DEVICE device;
+    for(int i = 0; i < n; i++){
+        lp[i] = rlt::random::normal_distribution::log_prob(device.random, mean[i], log_std[i], value[i]);
+        dmean[i] = rlt::random::normal_distribution::d_log_prob_d_mean(device.random, mean[i], log_std[i], value[i]);
+        dlogstd[i] = rlt::random::normal_distribution::d_log_prob_d_log_std(device.random, mean[i], log_std[i], value[i]);
+    }
+}
 
 int ref_num_cases(){ return (int)registry().size(); }
 const char* ref_case_name(int i){

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "host_api.cu"]
+SOURCES = ["dense.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
@@ -91,6 +91,10 @@ def lib():
         L.b200rl_dense_backward_scratch_bytes.restype = sz
         L.b200rl_dense_backward.argtypes = [vp, vp, i, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, vp, sz, vp]
         L.b200rl_dense_backward_static_scratch.argtypes = [vp, vp, i, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, vp]
+        L.b200rl_gae.argtypes = [vp, i, vp, i, vp, i, vp, i, vp, i, vp, i, i, i, f, f, i, vp]
+        L.b200rl_ppo_scratch_bytes.argtypes = [i, i]
+        L.b200rl_ppo_scratch_bytes.restype = sz
+        L.b200rl_ppo_policy_gradient.argtypes = [vp, i, vp, i, vp, vp, i, vp, i, vp, i, vp, i, i, f, f, f, i, i, vp, sz, vp]
         L.b200rl_mse_gradient.argtypes = [vp, i, vp, i, vp, i, i, i, f, vp]
         L.b200rl_fill.argtypes = [vp, sz, f, vp]
         L.b200rl_mlp_num_params.argtypes = [shape_p]
@@ -175,6 +179,31 @@ def mse_gradient(a, b, loss_weight=1.0, d_a=None):
     return d_a
 
 
+def gae(rewards, all_values, terminated, truncated, n_envs, steps, gamma=0.99, lam=0.95, ignore_termination=False):
+    """Column tensors ([rows] or [rows, 1] views with any row stride) -> (advantages, target_values), both [steps * n_envs]."""
+    import torch
+    adv = torch.empty(steps * n_envs, device=rewards.device, dtype=torch.float32)
+    tgt = torch.empty_like(adv)
+    check(lib().b200rl_gae(_ptr(rewards), rewards.stride(0), _ptr(all_values), all_values.stride(0), _ptr(terminated), terminated.stride(0),
+                           _ptr(truncated), truncated.stride(0), _ptr(adv), 1, _ptr(tgt), 1, n_envs, steps, gamma, lam, int(ignore_termination), _stream()), "b200rl_gae")
+    return adv, tgt
+
+
+def ppo_policy_gradient(current_actions, rollout_actions, log_std, rollout_log_probs, advantages, d_log_std, epsilon_clip=0.2, entropy_coefficient=0.01,
+                        advantage_epsilon=1e-8, normalize_advantage=True, learn_action_std=True, d_actions=None):
+    """d_log_std is accumulated in place; returns d_actions [B, A]."""
+    import torch
+    B, A = current_actions.shape
+    d_actions = torch.empty((B, A), device=current_actions.device, dtype=torch.float32) if d_actions is None else d_actions
+    nbytes = lib().b200rl_ppo_scratch_bytes(B, A)
+    scratch = torch.empty(nbytes, device=current_actions.device, dtype=torch.uint8)
+    check(lib().b200rl_ppo_policy_gradient(_ptr(current_actions), current_actions.stride(0), _ptr(rollout_actions), rollout_actions.stride(0), _ptr(log_std),
+                                           _ptr(rollout_log_probs), rollout_log_probs.stride(0), _ptr(advantages), advantages.stride(0), _ptr(d_actions),
+                                           d_actions.stride(0), _ptr(d_log_std), B, A, epsilon_clip, entropy_coefficient, advantage_epsilon,
+                                           int(normalize_advantage), int(learn_action_std), _ptr(scratch), nbytes, _stream()), "b200rl_ppo_policy_gradient")
+    return d_actions
+
+
 def fill(t, value):
     check(lib().b200rl_fill(_ptr(t), t.numel(), float(value), _stream()), "b200rl_fill")
 
@@ -183,7 +212,7 @@ class Mlp:
     """An MLP on flat arenas (params / grads / Adam moments), mirroring the verbs of nn_models::mlp in the reference:
     evaluate, forward, backward, zero_gradient, reset_optimizer_state, step."""
 
-    def __init__(self, input_dim, dims, acts, batch, device="cuda"):
+    def __init__(self, input_dim, dims, acts, batch, device="cuda", extra_params=0):
         import torch
         self.shape = MlpShape.make(input_dim, dims, acts)
         self.batch = batch
@@ -191,6 +220,10 @@ class Mlp:
         n = self.shape.num_params()
         assert n == lib().b200rl_mlp_num_params(C.byref(self.shape))
         z = lambda *s: torch.zeros(*s, device=device, dtype=torch.float32)
+        # extra_params: further parameters optimised together with the network (e.g. the PPO actor's log_std,
+        # nn_models/mlp_unconditional_stddev/network.h:11-27), stored behind the layers in the same arenas
+        self.n_mlp, self.n_extra = n, extra_params
+        n = n + extra_params
         self.params, self.grads, self.m, self.v = z(n), z(n), z(n), z(n)
         width = max([input_dim] + list(dims))
         self.tick, self.tock = z(batch, width), z(batch, width)
@@ -202,6 +235,10 @@ class Mlp:
         self.scratch = torch.empty(max(nbytes, 4), device=device, dtype=torch.uint8)
         self.hyper = AdamHyper()
         self.reset_optimizer_state()
+
+    def extra(self, arena="params"):
+        """View of the extra parameters (or their gradient / moments) behind the layers."""
+        return getattr(self, arena)[self.n_mlp:]
 
     def d_out_buffer(self):
         """A reusable [batch, O_last] buffer for the loss gradient."""

@@ -134,6 +134,20 @@ def main():
     np.savez(os.path.join(HERE, "rollout_staggered.npz"), states0=st1, episode_step0=es1, truncated0=tr1, T=300,
              obs=ro1["obs"][::7].copy(), act=ro1["act"][::7].copy(), rew=ro1["rew"][::7].copy(), states=ro1["states"],
              episode_step=ro1["episode_step"], truncated=ro1["truncated"], episode_return=ro1["episode_return"])
+    # ---- GAE (reference Dataset + estimate_generalized_advantages) and the Gaussian policy head ----
+    ppo = {}
+    for N, steps in ((64, 1024), (5, 37)):
+        n = N * steps
+        rewards = det_normal(31, n, stream=N)
+        all_values = det_normal(32, n + N, stream=N)
+        truncated = (_hash_u64(33, n, N) % np.uint64(97) == 0).astype(np.uint8)
+        terminated = (truncated & (_hash_u64(34, n, N) % np.uint64(2) == 0)).astype(np.uint8)     # termination implies truncation
+        adv, tgt = ref.gae(rewards, all_values, terminated, truncated, N, steps)
+        ppo[f"gae_{N}x{steps}_adv"], ppo[f"gae_{N}x{steps}_tgt"] = adv, tgt
+    mean, log_std, value = det_normal(35, 4096), det_uniform(36, 4096, -2.0, 0.5), det_normal(37, 4096) * np.float32(1.5)
+    lp, dm, dl = ref.normal_functions(mean, log_std, value)
+    ppo.update(normal_log_prob=lp, normal_d_mean=dm, normal_d_log_std=dl)
+    np.savez(os.path.join(HERE, "ppo.npz"), **ppo)
     print("golden fixtures written to", HERE)
 
 

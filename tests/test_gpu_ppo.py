@@ -1,0 +1,123 @@
+"""GPU parity of the PPO update pieces (through the C ABI): GAE against the REAL reference's golden output (bit-exact),
+the minibatch policy gradient against the CPU oracle, and one full minibatch update on the Ant-like shapes of the PPO
+configuration (obs 27, actions 8, minibatch 2048; synthetic N(0,1) data -- MuJoCo is not part of this path)."""
+import os
+
+import numpy as np
+import pytest
+
+import make_golden as mg
+from conftest import GOLDEN
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def gae_inputs(N, steps):
+    n = N * steps
+    rewards = mg.det_normal(31, n, stream=N)
+    all_values = mg.det_normal(32, n + N, stream=N)
+    truncated = (mg._hash_u64(33, n, N) % np.uint64(97) == 0).astype(np.uint8)
+    terminated = (truncated & (mg._hash_u64(34, n, N) % np.uint64(2) == 0)).astype(np.uint8)
+    return rewards, all_values, terminated, truncated
+
+
+@pytest.mark.parametrize("N,steps", [(64, 1024), (5, 37)])
+def test_gae_bit_exact_vs_reference_golden(lib, torch, N, steps):
+    fix = np.load(os.path.join(GOLDEN, "ppo.npz"))
+    rewards, all_values, terminated, truncated = gae_inputs(N, steps)
+    adv, tgt = lib.gae(dev(torch, rewards), dev(torch, all_values), dev(torch, terminated.astype(np.float32)), dev(torch, truncated.astype(np.float32)), N, steps)
+    assert np.array_equal(adv.cpu().numpy(), fix[f"gae_{N}x{steps}_adv"])
+    assert np.array_equal(tgt.cpu().numpy(), fix[f"gae_{N}x{steps}_tgt"])
+
+
+def test_gae_on_column_views_of_the_dataset_matrix(lib, torch):
+    """Same result when the columns live inside the reference's row-major dataset matrix (pitch = DATA_DIM = 51 for Ant)."""
+    N, steps, D = 64, 1024, 51
+    fix = np.load(os.path.join(GOLDEN, "ppo.npz"))
+    rewards, all_values, terminated, truncated = gae_inputs(N, steps)
+    data = torch.zeros(((steps + 1) * N, D), device="cuda")
+    data[:steps * N, 44] = dev(torch, rewards); data[:steps * N, 45] = dev(torch, terminated.astype(np.float32))
+    data[:steps * N, 46] = dev(torch, truncated.astype(np.float32)); data[:, 48] = dev(torch, all_values)
+    adv, tgt = lib.gae(data[:, 44], data[:, 48], data[:, 45], data[:, 46], N, steps)
+    assert np.array_equal(adv.cpu().numpy(), fix[f"gae_{N}x{steps}_adv"]) and np.array_equal(tgt.cpu().numpy(), fix[f"gae_{N}x{steps}_tgt"])
+
+
+@pytest.mark.parametrize("B,A,normalize,learn", [(2048, 8, True, True), (300, 1, True, True), (64, 3, False, True), (1000, 8, True, False)])
+def test_ppo_policy_gradient_vs_oracle(lib, orc, torch, B, A, normalize, learn):
+    cur = mg.det_normal(B, B * A).reshape(B, A) * np.float32(0.5)
+    roll = cur + mg.det_normal(B + 1, B * A).reshape(B, A) * np.float32(0.4)
+    log_std = mg.det_uniform(B + 2, A, -1.2, -0.2)
+    old_lp = mg.det_normal(B + 3, B) * np.float32(0.3) - np.float32(0.5 * A)
+    adv = mg.det_normal(B + 4, B) * np.float32(2.0) + np.float32(0.3)
+    g0 = mg.det_normal(B + 5, A)
+    d_ref, dls_ref = orc.ppo_policy_gradient(cur, roll, log_std, old_lp, adv, d_log_std=g0, normalize_advantage=normalize, learn_action_std=learn)
+    dls = dev(torch, g0)
+    d = lib.ppo_policy_gradient(dev(torch, cur), dev(torch, roll), dev(torch, log_std), dev(torch, old_lp), dev(torch, adv), dls,
+                                normalize_advantage=normalize, learn_action_std=learn)
+    # the advantage statistics are sums over the minibatch in a different order: relative 1e-5 of each value's scale
+    scale = np.abs(d_ref).max()
+    assert np.all(np.abs(d.cpu().numpy() - d_ref) <= 1e-5 * scale + 1e-5 * np.abs(d_ref) + 1e-9)
+    if learn:
+        # the reference adds 2 * B small increments to log_std.gradient one after the other in fp32: its own rounding error
+        # is up to B half-ulps of the running sum (observed: ~9e-6 at B = 2048), which bounds the comparison
+        bound = 1e-6 + B * 3e-8 * np.maximum(np.abs(dls_ref), np.abs(g0)) + 1e-5 * np.abs(d_ref).sum(0).max()
+        assert np.all(np.abs(dls.cpu().numpy() - dls_ref) <= bound)
+    else:
+        assert np.array_equal(dls.cpu().numpy(), g0)
+
+
+def test_ppo_minibatch_update_on_ant_shapes(lib, orc, torch):
+    """One minibatch of the PPO update (actor 27-64-64-8 tanh + log_std, critic 27-64-64-1, batch 2048): actor forward,
+    policy gradient, backward, critic forward / 0.5-weighted MSE / backward, one Adam step each -- against the oracle."""
+    B, OBS, A = 2048, 27, 8
+    dims_a, dims_c, acts = [64, 64, A], [64, 64, 1], ["tanh", "tanh", "identity"]
+    sa, sc = oracle.MlpShape.make(OBS, dims_a, acts), oracle.MlpShape.make(OBS, dims_c, acts)
+    pa = np.concatenate([mg.mlp_inputs(dict(batch=1, input_dim=OBS, hidden_dim=64, output_dim=A, num_layers=3), 5)[0], np.full(A, np.log(0.5), np.float32)])
+    pc = mg.mlp_inputs(dict(batch=1, input_dim=OBS, hidden_dim=64, output_dim=1, num_layers=3), 6)[0]
+    obs = mg.det_normal(7, B * OBS).reshape(B, OBS)
+    n_a = sa.num_params()
+    mean0 = orc.mlp_evaluate(sa, pa[:n_a].copy(), obs)
+    roll = (mean0 + np.float32(0.5) * mg.det_normal(8, B * A).reshape(B, A)).astype(np.float32)
+    lp, _, _ = orc.normal_functions(mean0.reshape(-1), np.tile(pa[n_a:], B), roll.reshape(-1))
+    old_lp = lp.reshape(B, A).sum(1).astype(np.float32) + mg.det_normal(9, B) * np.float32(0.05)     # a slightly different old policy
+    adv, targets = mg.det_normal(10, B), mg.det_normal(11, B).reshape(B, 1)
+    # --- oracle ---
+    pre, out = orc.mlp_forward(sa, pa[:n_a].copy(), obs)
+    cur = np.ascontiguousarray(out[-B * A:].reshape(B, A))
+    d_act, d_ls = orc.ppo_policy_gradient(cur, roll, pa[n_a:].copy(), old_lp, adv)
+    ga, _ = orc.mlp_backward(sa, pa[:n_a].copy(), np.zeros(n_a, np.float32), obs, pre, out, d_act)
+    ga = np.concatenate([ga, d_ls])
+    c1, c2, _ = orc.adam_bias_correction(0.9, 0.999, 1)
+    pa_ref, _, _ = orc.adam_update(pa, ga, np.zeros_like(pa), np.zeros_like(pa), 1e-3, 0.9, 0.999, 1e-7, 1e-7, c1, c2)
+    prec, outc = orc.mlp_forward(sc, pc, obs)
+    d_c = orc.mse_gradient(np.ascontiguousarray(outc[-B:].reshape(B, 1)), targets, 0.5)
+    gc, _ = orc.mlp_backward(sc, pc, np.zeros_like(pc), obs, prec, outc, d_c)
+    pc_ref, _, _ = orc.adam_update(pc, gc, np.zeros_like(pc), np.zeros_like(pc), 1e-3, 0.9, 0.999, 1e-7, 1e-7, c1, c2)
+    # --- library ---
+    actor, critic = lib.Mlp(OBS, dims_a, acts, B, extra_params=A), lib.Mlp(OBS, dims_c, acts, B)
+    actor.params.copy_(dev(torch, pa)); critic.params.copy_(dev(torch, pc))
+    od = dev(torch, obs)
+    actor.zero_gradient(); critic.zero_gradient()
+    cur_d = actor.forward(od)
+    d_act_d = lib.ppo_policy_gradient(cur_d, dev(torch, roll), actor.extra("params"), dev(torch, old_lp), dev(torch, adv), actor.extra("grads"))
+    actor.backward(od, d_act_d)
+    actor.step()
+    val = critic.forward(od)
+    critic.backward(od, lib.mse_gradient(val, dev(torch, targets), 0.5))
+    critic.step()
+    ga_d = actor.grads.cpu().numpy()
+    assert np.all(np.abs(ga_d - ga) <= 1e-6 + 1e-5 * np.abs(ga) + 1e-5 * np.abs(ga).max() + B * 3e-8 * np.abs(ga))
+    assert np.all(np.abs(actor.params.cpu().numpy() - pa_ref) <= 2e-6 + 1e-5 * np.abs(pa_ref))
+    assert np.all(np.abs(critic.params.cpu().numpy() - pc_ref) <= 2e-6 + 1e-5 * np.abs(pc_ref))

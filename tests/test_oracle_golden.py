@@ -107,3 +107,20 @@ def test_kaiming_init_bounds_from_reference_engine():
     assert p.size == 3 * 64 + 64 + 64 * 64 + 64 + 64 + 1
     assert np.abs(p[:256]).max() <= 1 / np.sqrt(3) + 1e-7
     assert np.abs(p[256:256 + 64 * 64 + 64]).max() <= 1 / 8 + 1e-7
+
+
+def test_gae_and_gaussian_head_match_reference(orc):
+    """orc_gae against the reference's estimate_generalized_advantages on its own Dataset type; the Gaussian log-prob
+    and its derivatives against random/operations_generic.h (all bit-exact)."""
+    fix = np.load(os.path.join(GOLDEN, "ppo.npz"))
+    for N, steps in ((64, 1024), (5, 37)):
+        n = N * steps
+        rewards = mg.det_normal(31, n, stream=N)
+        all_values = mg.det_normal(32, n + N, stream=N)
+        truncated = (mg._hash_u64(33, n, N) % np.uint64(97) == 0).astype(np.uint8)
+        terminated = (truncated & (mg._hash_u64(34, n, N) % np.uint64(2) == 0)).astype(np.uint8)
+        adv, tgt = orc.gae(rewards, all_values, terminated, truncated, N, steps)
+        assert np.array_equal(adv, fix[f"gae_{N}x{steps}_adv"]) and np.array_equal(tgt, fix[f"gae_{N}x{steps}_tgt"])
+    mean, log_std, value = mg.det_normal(35, 4096), mg.det_uniform(36, 4096, -2.0, 0.5), mg.det_normal(37, 4096) * np.float32(1.5)
+    lp, dm, dl = orc.normal_functions(mean, log_std, value)
+    assert np.array_equal(lp, fix["normal_log_prob"]) and np.array_equal(dm, fix["normal_d_mean"]) and np.array_equal(dl, fix["normal_d_log_std"])

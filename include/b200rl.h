@@ -45,6 +45,11 @@ const char* b200rl_status_string(int status);
 /* text of the last CUDA error seen by this library on the calling thread ("" if none) */
 const char* b200rl_last_cuda_error(void);
 
+/* Reads (and synchronises for) the library's device-side error word into *state_host: non-zero after a bounded wait
+ * inside a tensor-core dense kernel expired (the kernel then left its loops and released its tensor memory instead of
+ * spinning). The reference has no counterpart (its asserts are no-ops in kernels, utils/assert/operations_cuda.h:17-21). */
+int b200rl_device_error_state(int* state_host);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Dense layer. W is [O, I] row-major (weights.parameters), bias is [O].
  * ------------------------------------------------------------------------------------------------------- */

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}

@@ -9,24 +9,12 @@
 // Bias, pre-activation store and activation are fused into the forward epilogue; d_pre = act'(pre) * d_out and the
 // bias gradient are one pass; split-batch partials of d_W / d_bias are reduced in a fixed order (deterministic).
 #include "common.cuh"
+#include "dense.cuh"
+#include <stdlib.h>
 
 namespace b200rl {
 
 constexpr int BM = 64, BN = 64, BK = 16, GEMM_THREADS = 256, PADM = 4;
-
-enum { EPI_FORWARD = 0, EPI_STORE = 1, EPI_ACCUMULATE = 2 };
-
-struct GemmArgs {
-    const float* A; long long lda;   // A(m,k)
-    const float* B; long long ldb;   // B(n,k)
-    int M, N, K;
-    int k_per_split;                 // summed-index range handled by one blockIdx.z
-    // epilogue
-    const float* bias;               // EPI_FORWARD
-    float* pre; long long ldpre;     // EPI_FORWARD (nullable)
-    float* C; long long ldc;         // output (EPI_FORWARD: y, EPI_STORE: C, EPI_ACCUMULATE with gridDim.z == 1: C += acc)
-    float* partial;                  // EPI_ACCUMULATE with gridDim.z > 1: partial[z][M*N] (dense, ld = N)
-};
 
 template <bool KCONTIG>
 __device__ __forceinline__ void load_tile(float (*S)[BM + PADM], const float* __restrict__ P, long long ld, int row0, int rows, int k0, int k_end, int tid){
@@ -144,11 +132,22 @@ __global__ void reduce_partials_kernel(float* dst, const float* __restrict__ par
     }
 }
 
+// The tensor-core kernel takes the contraction when its 128-row tiles are reasonably filled and there is enough work to
+// amortise its setup; B200RL_DENSE_KERNEL=simt forces the CUDA-core kernel (A/B measurements).
+static bool tc_eligible(long long M, long long N, long long K){
+    static const bool force_simt = [](){ const char* v = getenv("B200RL_DENSE_KERNEL"); return v && v[0] == 's'; }();
+    if(force_simt) return false;
+    return M >= 64 && N >= 16 && (double)M * N * K >= (double)(1 << 22);
+}
+static bool use_tensor_cores(const GemmArgs& a){ return tc_eligible(a.M, a.N, a.K); }
+
 struct BackwardPlan { int splits; int k_per_split; int bias_segs; int rows_per_seg; size_t bytes; };
 static BackwardPlan plan_backward(int B, int I, int O){
     BackwardPlan p;
-    int tiles = ((O + BM - 1) / BM) * ((I + BN - 1) / BN);
-    int want = (2 * NUM_SMS + tiles - 1) / tiles;
+    // weight gradient = contraction over the batch: split it so that every SM has work (tile shape of the kernel that will run)
+    const bool tc = tc_eligible(O, I, B);
+    int tiles = tc ? ((O + 127) / 128) * ((I + 255) / 256) : ((O + BM - 1) / BM) * ((I + BN - 1) / BN);
+    int want = tc ? (NUM_SMS + tiles - 1) / tiles : (2 * NUM_SMS + tiles - 1) / tiles;
     int max_splits = (B + 255) / 256;
     p.splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
     if(p.splits < 1) p.splits = 1;
@@ -172,6 +171,10 @@ static int dense_forward_impl(const float* W, const float* bias, const float* x,
     GemmArgs a{};
     a.A = x; a.lda = ldx; a.B = W; a.ldb = I; a.M = B; a.N = O; a.K = I; a.k_per_split = I;
     a.bias = bias; a.pre = pre; a.ldpre = ldpre; a.C = y; a.ldc = ldy;
+    if(use_tensor_cores(a)){
+        int rc = launch_gemm_tc(a, EPI_FORWARD, act, true, true, 1, s);
+        if(rc != B200RL_ERR_UNSUPPORTED) return rc;
+    }
     dim3 grid((O + BN - 1) / BN, (B + BM - 1) / BM, 1);
     B200RL_DISPATCH_ACT(act, (gemm_kernel<true, true, EPI_FORWARD, ACT><<<grid, GEMM_THREADS, 0, s>>>(a)));
     B200RL_LAUNCH_CHECK("dense_forward");
@@ -201,9 +204,13 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         GemmArgs a{};
         a.A = d_out; a.lda = ldd; a.B = x; a.ldb = ldx; a.M = O; a.N = I; a.K = B; a.k_per_split = p.k_per_split;
         a.C = dW; a.ldc = I; a.partial = w_partial;
-        dim3 grid((I + BN - 1) / BN, (O + BM - 1) / BM, p.splits);
-        gemm_kernel<false, false, EPI_ACCUMULATE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
-        B200RL_LAUNCH_CHECK("dense_dW");
+        int rc_tc = use_tensor_cores(a) ? launch_gemm_tc(a, EPI_ACCUMULATE, 0, false, false, p.splits, s) : B200RL_ERR_UNSUPPORTED;
+        if(rc_tc != B200RL_OK && rc_tc != B200RL_ERR_UNSUPPORTED) return rc_tc;
+        if(rc_tc == B200RL_ERR_UNSUPPORTED){
+            dim3 grid((I + BN - 1) / BN, (O + BM - 1) / BM, p.splits);
+            gemm_kernel<false, false, EPI_ACCUMULATE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
+            B200RL_LAUNCH_CHECK("dense_dW");
+        }
         if(p.splits > 1){
             long long n = (long long)O * I;
             int blocks = (int)((n + 255) / 256); if(blocks > 4 * NUM_SMS) blocks = 4 * NUM_SMS;
@@ -215,9 +222,13 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         GemmArgs a{};
         a.A = d_out; a.lda = ldd; a.B = W; a.ldb = I; a.M = B; a.N = I; a.K = O; a.k_per_split = O;
         a.C = d_in; a.ldc = ldi;
-        dim3 grid((I + BN - 1) / BN, (B + BM - 1) / BM, 1);
-        gemm_kernel<true, false, EPI_STORE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
-        B200RL_LAUNCH_CHECK("dense_d_in");
+        int rc_tc = use_tensor_cores(a) ? launch_gemm_tc(a, EPI_STORE, 0, true, false, 1, s) : B200RL_ERR_UNSUPPORTED;
+        if(rc_tc != B200RL_OK && rc_tc != B200RL_ERR_UNSUPPORTED) return rc_tc;
+        if(rc_tc == B200RL_ERR_UNSUPPORTED){
+            dim3 grid((I + BN - 1) / BN, (B + BM - 1) / BM, 1);
+            gemm_kernel<true, false, EPI_STORE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
+            B200RL_LAUNCH_CHECK("dense_d_in");
+        }
     }
     return B200RL_OK;
 }

@@ -1,0 +1,281 @@
+// Tensor-core contraction for the dense layer (sm_100a, tcgen05 + TMEM), fp32 in / fp32 out through the 3xTF32 split:
+//   C[m][n] = sum_k A(m,k) * B(n,k)   with   A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi   (tf32 parts, fp32 accumulate)
+// The operands are plain fp32 matrices in HBM (activations, weights, gradients) in either orientation; the split into
+// hi/lo parts cannot be done by a TMA copy, so the 256 threads of the CTA stage each 32-wide k chunk themselves:
+// coalesced global loads -> hi/lo split in registers -> K-major, 128-byte-swizzled shared-memory tiles (a transposing
+// store when k is not the contiguous index in memory). Two stages: while the tensor core works on chunk c (12
+// tcgen05.mma M128 x N x K8 per chunk into a fresh 128 x N TMEM accumulator, committed to the chunk's mbarrier) the threads
+// prefetch and stage chunk c+1 and add chunk c-1 from TMEM to their fp32 register accumulators.
+// One CTA per SM, persistent over (row tile, column tile, k split) work items; N <= 256 per tile.
+// Epilogue: transposition through shared memory so that every global store is a full 128-byte row segment,
+// then bias + pre-activation store + activation (forward), plain store (input gradient) or accumulate / split-k partial
+// store (weight gradient).
+#include "common.cuh"
+#include "dense.cuh"
+#include "tcgen05.cuh"
+
+namespace b200rl {
+
+namespace {
+constexpr int TC_THREADS = 256, TC_M = 128, TC_KC = 32, TC_NMAX = 256;
+constexpr uint32_t A_TILE_BYTES = TC_M * 128;                       // one k chunk of A: 128 rows x 32 tf32
+constexpr uint32_t TMEM_COLS = 512;                                  // two 256-column accumulators (one per k chunk in flight)
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+}
+
+// x = hi + lo with BOTH parts rounded to nearest tf32: the tensor core truncates whatever it is given, so rounding here
+// keeps the representation error at ~2^-23 |x| (a truncated remainder would leave ~2^-20). This kernel is tensor-bound,
+// the two conversions per element are free.
+__device__ __forceinline__ void split_rn(float x, float& hi, float& lo){
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
+    lo = __uint_as_float(l);
+}
+
+// set to 1 by a kernel whose bounded wait expired (read back through b200rl_device_error_state)
+__device__ int g_dense_tc_error = 0;
+
+// Staging of one operand chunk (`rows` x 32 elements, element (r, k) = KCONTIG ? P[r*ld + k] : P[k*ld + r]) is split in
+// two halves so that the global-load latency overlaps the tensor-core work on the previous chunk:
+//   prefetch_operand : all loads of the chunk are issued back to back into registers (16 bytes per thread and iteration)
+//   store_operand    : tf32 hi/lo split and 16-byte stores into the two K-major SW128 tiles (a transposing store when k
+//                      is not the contiguous index in memory); rows >= row_limit and k >= k_end are zero.
+template <bool KCONTIG, int ITERS>
+__device__ __forceinline__ void prefetch_operand(float4 (&reg)[ITERS], const float* __restrict__ P, long long ld, int row0, int row_limit, int rows,
+                                                 int k0, int k_end, bool vec_ok, int tid){
+#pragma unroll
+    for(int it = 0; it < ITERS; it++){
+        const int idx = tid + it * TC_THREADS;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if(idx < rows * 8){
+            const int r = KCONTIG ? (idx >> 3) : (idx % rows), c = KCONTIG ? (idx & 7) : (idx / rows);
+            const int gr = row0 + r, gk = k0 + c * 4;
+            if(gr < row_limit){
+                if constexpr(KCONTIG){
+                    const float* src = P + (long long)gr * ld + gk;
+                    if(vec_ok && gk + 3 < k_end) v = __ldg(reinterpret_cast<const float4*>(src));
+                    else{
+                        if(gk + 0 < k_end) v.x = __ldg(src + 0);
+                        if(gk + 1 < k_end) v.y = __ldg(src + 1);
+                        if(gk + 2 < k_end) v.z = __ldg(src + 2);
+                        if(gk + 3 < k_end) v.w = __ldg(src + 3);
+                    }
+                }
+                else{
+                    // consecutive threads read consecutive rows for a fixed k: coalesced
+                    const float* src = P + (long long)gk * ld + gr;
+                    if(gk + 0 < k_end) v.x = __ldg(src);
+                    if(gk + 1 < k_end) v.y = __ldg(src + ld);
+                    if(gk + 2 < k_end) v.z = __ldg(src + 2 * ld);
+                    if(gk + 3 < k_end) v.w = __ldg(src + 3 * ld);
+                }
+            }
+        }
+        reg[it] = v;
+    }
+}
+template <bool KCONTIG, int ITERS>
+__device__ __forceinline__ void store_operand(const float4 (&reg)[ITERS], uint8_t* hi_tile, uint8_t* lo_tile, int rows, int tid){
+#pragma unroll
+    for(int it = 0; it < ITERS; it++){
+        const int idx = tid + it * TC_THREADS;
+        if(idx < rows * 8){
+            const int r = KCONTIG ? (idx >> 3) : (idx % rows), c = KCONTIG ? (idx & 7) : (idx / rows);
+            float4 h, l;
+            split_rn(reg[it].x, h.x, l.x); split_rn(reg[it].y, h.y, l.y); split_rn(reg[it].z, h.z, l.z); split_rn(reg[it].w, h.w, l.w);
+            const uint32_t off = (uint32_t)r * 128 + ((uint32_t)(c ^ (r & 7)) << 4);
+            *reinterpret_cast<float4*>(hi_tile + off) = h;
+            *reinterpret_cast<float4*>(lo_tile + off) = l;
+        }
+    }
+}
+
+// Per k chunk the tensor core starts a FRESH accumulator (alternating between two 256-column TMEM buffers) and the
+// threads add the finished chunk to fp32 registers with round-to-nearest adds. The tensor core's own accumulation
+// truncates, so a long chain of dependent MMAs into one accumulator drifts (measured: mean error 1.2e-6 at K = 256 with
+// 96 chained MMAs); with 12 MMAs per chain and the cross-chunk sum in registers the result is as accurate as an fp32
+// FMA loop.
+template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmArgs a, int n_pad, int m_tiles, int n_tiles, int splits, int a_vec, int b_vec){
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t b_tile_bytes = (uint32_t)n_pad * 128;
+    const uint32_t stage_bytes = 2 * A_TILE_BYTES + 2 * b_tile_bytes;
+    uint8_t* ctrl = base + 2 * stage_bytes;
+    uint64_t* chunk_bar = reinterpret_cast<uint64_t*>(ctrl);          // [2]: the MMAs of the chunk using stage / TMEM buffer s have completed
+    uint32_t* slot = reinterpret_cast<uint32_t*>(ctrl + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 20);
+
+    if(tid == 0){ tc::mbar_init(chunk_bar, 1); tc::mbar_init(chunk_bar + 1, 1); tc::fence_mbar_init(); *abort_flag = 0; }
+    if(warp == 0){ tc::tmem_alloc(slot, TMEM_COLS); tc::tmem_relinquish(); }
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    tc::fence_after_thread_sync();
+    const uint32_t tmem_base = *slot;
+    const uint32_t idesc = tc::make_idesc_tf32(TC_M, n_pad);
+    const int q = warp & 3, col_half = warp >> 2;                     // this warp: TMEM lanes 32 q .. +31, 32-column blocks col_half, col_half + 2, ...
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const int n_blocks = (n_pad + 31) / 32;
+    const int total = m_tiles * n_tiles * splits;
+    uint32_t u = 0;                                                   // running chunk counter: stage and TMEM buffer u & 1
+    bool aborted = false;
+
+    // adds the finished chunk (buffer `buf`, barrier phase `parity`) to the register accumulators
+    auto accumulate = [&](float (&acc)[4][32], uint32_t buf, uint32_t parity){
+        if(!tc::mbar_wait_bounded(chunk_bar + buf, parity, WAIT_LIMIT_CYCLES)) *abort_flag = 1;
+        tc::fence_after_thread_sync();
+#pragma unroll
+        for(int bi = 0; bi < 4; bi++){
+            const int cb = col_half + 2 * bi;
+            if(cb < n_blocks){
+                uint32_t v[32];
+                tc::tmem_ld_32x32(tmem_base + buf * 256 + lane_off + (uint32_t)(cb * 32), v);
+                tc::tmem_wait_ld();
+#pragma unroll
+                for(int j = 0; j < 32; j++) acc[bi][j] += __uint_as_float(v[j]);
+            }
+        }
+    };
+
+    for(int item = blockIdx.x; item < total && !aborted; item += gridDim.x){
+        const int z = item / (m_tiles * n_tiles), mn = item % (m_tiles * n_tiles);
+        const int m0 = (mn / n_tiles) * TC_M, n0 = (mn % n_tiles) * n_pad;
+        const int k_begin = z * a.k_per_split, k_end = min(a.K, k_begin + a.k_per_split);
+        const int n_chunks = (k_end - k_begin + TC_KC - 1) / TC_KC;
+        const int b_rows = min(n_pad, ((a.N - n0) + 15) / 16 * 16);           // rows of the B tile that can hold data
+        float acc[4][32];
+#pragma unroll
+        for(int bi = 0; bi < 4; bi++)
+#pragma unroll
+            for(int j = 0; j < 32; j++) acc[bi][j] = 0.0f;
+        float4 ra[4], rb[8];
+        prefetch_operand<A_KCONTIG, 4>(ra, a.A, a.lda, m0, a.M, TC_M, k_begin, k_end, a_vec != 0, tid);
+        prefetch_operand<B_KCONTIG, 8>(rb, a.B, a.ldb, n0, a.N, b_rows, k_begin, k_end, b_vec != 0, tid);
+
+        for(int c = 0; c < n_chunks; c++){
+            const uint32_t s = u & 1;
+            uint8_t* stage = base + s * stage_bytes;
+            // stage s and TMEM buffer s are free: the chunk that used them last (u - 2) was waited for in the previous iteration
+            store_operand<A_KCONTIG, 4>(ra, stage, stage + A_TILE_BYTES, TC_M, tid);
+            store_operand<B_KCONTIG, 8>(rb, stage + 2 * A_TILE_BYTES, stage + 2 * A_TILE_BYTES + b_tile_bytes, b_rows, tid);
+            if(b_rows < n_pad && c < 2){
+                // rows of the padded tile that never receive data: zero them once per stage and work item
+                for(int idx = tid; idx < (n_pad - b_rows) * 8; idx += TC_THREADS){
+                    const uint32_t off = (uint32_t)(b_rows + (idx >> 3)) * 128 + ((uint32_t)(idx & 7) << 4);
+                    *reinterpret_cast<float4*>(stage + 2 * A_TILE_BYTES + off) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    *reinterpret_cast<float4*>(stage + 2 * A_TILE_BYTES + b_tile_bytes + off) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            tc::fence_proxy_async_smem();
+            tc::fence_before_thread_sync();
+            __syncthreads();
+            if(*abort_flag){ aborted = true; break; }
+            if(tid == 0){
+                tc::fence_after_thread_sync();
+                const uint64_t da_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(stage)), da_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + A_TILE_BYTES));
+                const uint64_t db_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + 2 * A_TILE_BYTES));
+                const uint64_t db_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + 2 * A_TILE_BYTES + b_tile_bytes));
+                const uint32_t d = tmem_base + s * 256;
+#pragma unroll
+                for(int pass = 0; pass < 3; pass++){                 // the small correction terms first, then hi * hi
+                    const uint64_t da = pass == 0 ? da_lo : da_hi, db = pass == 1 ? db_lo : db_hi;
+#pragma unroll
+                    for(int ks = 0; ks < 4; ks++) tc::mma_tf32_ss(d, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, (pass | ks) ? 1u : 0u);
+                }
+                tc::commit(chunk_bar + s);
+            }
+            __syncwarp();
+            if(c + 1 < n_chunks){
+                const int k0 = k_begin + (c + 1) * TC_KC;
+                prefetch_operand<A_KCONTIG, 4>(ra, a.A, a.lda, m0, a.M, TC_M, k0, k_end, a_vec != 0, tid);
+                prefetch_operand<B_KCONTIG, 8>(rb, a.B, a.ldb, n0, a.N, b_rows, k0, k_end, b_vec != 0, tid);
+            }
+            if(c > 0) accumulate(acc, s ^ 1, ((u - 1) >> 1) & 1);
+            u++;
+        }
+        if(aborted) break;
+        accumulate(acc, (u - 1) & 1, ((u - 1) >> 1) & 1);
+
+        // ---- epilogue: transposition through a warp-private 32 x 33 patch (stage 0 is free: every MMA has completed), so
+        // that each global store instruction writes one full 128-byte row segment ----
+        float* patch = reinterpret_cast<float*>(base) + warp * (32 * 33);
+#pragma unroll
+        for(int bi = 0; bi < 4; bi++){
+            const int cb = col_half + 2 * bi;
+            if(cb >= n_blocks) continue;
+#pragma unroll
+            for(int j = 0; j < 32; j++) patch[lane * 33 + j] = acc[bi][j];
+            __syncwarp();
+            const int n = n0 + cb * 32 + lane;
+            const bool n_ok = cb * 32 + lane < n_pad && n < a.N;
+            float bias = 0.0f;
+            if constexpr(EPI == EPI_FORWARD){ if(n_ok) bias = __ldg(a.bias + n); }
+            for(int r = 0; r < 32; r++){
+                const int m = m0 + q * 32 + r;
+                if(m >= a.M || !n_ok) continue;
+                float x = patch[r * 33 + lane];
+                if constexpr(EPI == EPI_FORWARD){
+                    x += bias;
+                    if(a.pre) a.pre[(long long)m * a.ldpre + n] = x;
+                    a.C[(long long)m * a.ldc + n] = activation<ACT>(x);
+                }
+                else if constexpr(EPI == EPI_STORE){
+                    a.C[(long long)m * a.ldc + n] = x;
+                }
+                else{
+                    if(splits == 1) a.C[(long long)m * a.ldc + n] += x;
+                    else a.partial[((long long)z * a.M + m) * a.N + n] = x;
+                }
+            }
+            __syncwarp();
+        }
+        tc::fence_before_thread_sync();
+        __syncthreads();                               // the patch area (stage 0) is overwritten by the next work item
+        if(*abort_flag){ aborted = true; break; }
+    }
+    if(aborted && tid == 0) g_dense_tc_error = 1;
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    if(warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <bool A_KC, bool B_KC, int EPI, int ACT>
+static int launch_one(const GemmArgs& a, int splits, cudaStream_t s){
+    int n_pad = (a.N + 15) / 16 * 16;
+    if(n_pad > TC_NMAX) n_pad = TC_NMAX;
+    const int n_tiles = (a.N + n_pad - 1) / n_pad, m_tiles = (a.M + TC_M - 1) / TC_M;
+    const uint32_t smem = 2 * (2 * A_TILE_BYTES + 2 * (uint32_t)n_pad * 128) + 64 + 1024;
+    static uint32_t configured = 0;
+    if(smem > configured){
+        B200RL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<A_KC, B_KC, EPI, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024)));
+        configured = 2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024;
+    }
+    const long long total = (long long)m_tiles * n_tiles * splits;
+    const int grid = (int)(total < NUM_SMS ? total : NUM_SMS);
+    auto aligned = [](const float* p, long long ld){ return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld & 3) == 0; };
+    const int a_vec = A_KC && aligned(a.A, a.lda) && (a.k_per_split % 4 == 0), b_vec = B_KC && aligned(a.B, a.ldb) && (a.k_per_split % 4 == 0);
+    gemm_tc_kernel<A_KC, B_KC, EPI, ACT><<<grid, TC_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec);
+    B200RL_LAUNCH_CHECK("gemm_tc");
+    return B200RL_OK;
+}
+
+int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcontig, bool b_kcontig, int splits, cudaStream_t s){
+    if(a.M < 1 || a.N < 1 || a.K < 1) return B200RL_ERR_UNSUPPORTED;
+    if(epilogue == EPI_FORWARD && a_kcontig && b_kcontig){
+        B200RL_DISPATCH_ACT(activation, return (launch_one<true, true, EPI_FORWARD, ACT>(a, 1, s)));
+    }
+    if(epilogue == EPI_STORE && a_kcontig && !b_kcontig) return launch_one<true, false, EPI_STORE, 0>(a, 1, s);
+    if(epilogue == EPI_ACCUMULATE && !a_kcontig && !b_kcontig) return launch_one<false, false, EPI_ACCUMULATE, 0>(a, splits, s);
+    return B200RL_ERR_UNSUPPORTED;
+}
+
+}  // namespace b200rl
+
+extern "C" int b200rl_device_error_state(int* state_host){
+    if(!state_host) return B200RL_ERR_INVALID_ARGUMENT;
+    B200RL_CUDA_TRY(cudaMemcpyFromSymbol(state_host, b200rl::g_dense_tc_error, sizeof(int)));
+    return B200RL_OK;
+}

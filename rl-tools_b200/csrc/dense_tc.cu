@@ -27,11 +27,11 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 // keeps the representation error at ~2^-23 |x| (a truncated remainder would leave ~2^-20). This kernel is tensor-bound,
 // the two conversions per element are free.
 __device__ __forceinline__ void split_rn(float x, float& hi, float& lo){
-    uint32_t h, l;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
-    hi = __uint_as_float(h);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
-    lo = __uint_as_float(l);
+    // round to nearest (ties away) in integer arithmetic: add half a tf32 ulp to the bit pattern, clear the low 13 bits --
+    // two full-rate ALU operations instead of a conversion-pipe instruction
+    hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+    const float r = x - hi;
+    lo = __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xFFFFE000u);
 }
 
 // set to 1 by a kernel whose bounded wait expired (read back through b200rl_device_error_state)

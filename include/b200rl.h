@@ -245,6 +245,37 @@ int b200rl_reset_table_host(uint32_t* rng_state_host, int n_envs, int n_steps, c
                             const uint8_t* truncated_host, int step_limit, float* reset_states_host, int n_reset_rounds,
                             int* rounds_used_host);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * On-policy collect for PPO: T x { reset-if-truncated, observe, actor forward -> action mean, Gaussian action noise, log-prob,
+ * step, reward, flags } for N Pendulum environments in ONE launch, written as rows of the runner's dataset matrix.
+ * Replaces collect (rl/components/on_policy_runner/operations_generic.h:105-146; prologue / epilogue per environment
+ * operations_generic_per_env.h:9-79; Gaussian head random/operations_cpu.h:40-48, random/operations_generic.h:87-97).
+ *   dataset [(T + 1) * N, ld_dataset], row = step * N + env, columns as on_policy_runner.h:38-72 for observation 3 / action 1:
+ *     0-2 observation, 3 action mean, 4 action, 5 log-prob, 6 reward, 7 terminated, 8 truncated, 9 reset, 10 value, 11 advantage,
+ *     12 target value (10-12 are not touched). reset[env] of step 0 = the incoming truncated flag, reset[pos + N] = truncated[pos];
+ *     rows T * N + env receive the final observation. ld_dataset >= 13.
+ *   noise [T, N]: the standard-normal variate of every action draw, reset_states [R, N, 2]: both in the order the reference's single
+ *     engine produces them (b200rl_collect_tables_host); action = noise * exp(log_std) + mean.
+ *   log_std: device scalar (the state-independent log standard deviation of nn_models/mlp_unconditional_stddev).
+ *   step_limit == 0 disables truncation. Runner state arguments as in b200rl_pendulum_rollout.
+ * The actor must be 3 -> 64 -> 64 -> 1. The _layers variant takes the six parameter tensors W1 b1 W2 b2 W3 b3 as separate device
+ * pointers (how the reference's containers allocate them) and packs them into a file-scope device arena first. */
+#define B200RL_COLLECT_DATA_DIM 13
+int b200rl_pendulum_collect(const b200rl_mlp_shape* actor, const float* actor_params, const float* log_std, float* states,
+                            int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states,
+                            int n_reset_rounds, const float* noise, int n_envs, int n_steps, int step_limit, float* dataset,
+                            int ld_dataset, int* error_flag, b200rl_stream_t stream);
+int b200rl_pendulum_collect_layers(const b200rl_mlp_shape* actor, const float* const* layer_params, const float* log_std,
+                                   float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                                   const float* reset_states, int n_reset_rounds, const float* noise, int n_envs, int n_steps,
+                                   int step_limit, float* dataset, int ld_dataset, int* error_flag, b200rl_stream_t stream);
+/* Host tables for one collect call in the reference engine's draw order (per step: environments ascending, initial state of every
+ * truncated environment; then environments ascending, one normal draw per action). rng_state_host as in b200rl_rng_init_host,
+ * advanced in place, so consecutive calls continue the reference's stream. */
+int b200rl_collect_tables_host(uint32_t* rng_state_host, int n_envs, int n_steps, const int32_t* episode_step_host,
+                               const uint8_t* truncated_host, int step_limit, float* reset_states_host, int n_reset_rounds,
+                               int* rounds_used_host, float* noise_host);
+
 #ifdef __cplusplus
 }
 #endif

@@ -87,6 +87,11 @@ class Oracle:
         L.orc_reset_table.argtypes = [C.c_void_p, C.c_int, C.c_int, _i32p, _u8p, C.c_int, _f32p, C.c_int]
         L.orc_reset_table.restype = C.c_int
         L.orc_gae.argtypes = [_f32p, _f32p, _u8p, _u8p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
+        L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
+                                           C.c_void_p, C.c_int, _f32p, C.c_int]
+        L.orc_pendulum_collect.restype = C.c_int
+        L.orc_collect_tables.argtypes = [C.c_void_p, C.c_int, C.c_int, _i32p, _u8p, C.c_int, _f32p, C.c_int, _f32p]
+        L.orc_collect_tables.restype = C.c_int
         L.orc_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.orc_ppo_policy_gradient.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_float, C.c_int, C.c_int]
 
@@ -221,6 +226,32 @@ class Oracle:
             raise RuntimeError(f"orc_pendulum_rollout rc={rc}")
         return dict(obs=obs, act=act, rew=rew, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
 
+    # --- on-policy collect ---------------------------------------------------------------------------------
+    def new_rng(self, seed):
+        rng = C.create_string_buffer(4 * 624 + 16)
+        self.lib.orc_rng_init(rng, seed)
+        return rng
+
+    def collect_tables(self, rng, N, T, episode_step, truncated, step_limit, R):
+        """Draws of one collect call (engine state `rng` from new_rng, advanced in place): reset table [R,N,2], noise [T,N]."""
+        table, noise = np.zeros((R, N, 2), np.float32), np.empty((T, N), np.float32)
+        used = self.lib.orc_collect_tables(rng, N, T, episode_step, truncated, step_limit, table, R, noise)
+        if used < 0:
+            raise ValueError("reset table too small")
+        return table, noise
+
+    def pendulum_collect(self, shape, params, runner, T, step_limit, rng=None, reset_states=None, noise=None, dataset=None):
+        """runner = dict(states, episode_step, truncated, episode_return), updated IN PLACE. Either rng (inline draws) or the
+        two tables. Returns the dataset matrix [(T+1)*N, 13]."""
+        N = runner["states"].shape[0]
+        ds = np.zeros(((T + 1) * N, 13), np.float32) if dataset is None else dataset
+        R = 0 if reset_states is None else reset_states.shape[0]
+        rc = self.lib.orc_pendulum_collect(C.byref(shape), params, N, T, runner["states"], runner["episode_step"], runner["truncated"],
+                                           runner["episode_return"], rng, _opt(reset_states), R, _opt(noise), step_limit, ds, 13)
+        if rc != 0:
+            raise RuntimeError(f"orc_pendulum_collect rc={rc}")
+        return ds
+
     def gae(self, rewards, all_values, terminated, truncated, N, steps, gamma=0.99, lam=0.95, ignore_termination=False):
         adv, tgt = np.empty(steps * N, np.float32), np.empty(steps * N, np.float32)
         self.lib.orc_gae(rewards, all_values, terminated, truncated, adv, tgt, N, steps, gamma, lam, int(ignore_termination))
@@ -263,6 +294,7 @@ class Reference:
                                            _f32p, _f32p, _f32p, C.c_int]
         L.ref_pendulum_rollout.restype = C.c_int
         L.ref_gae.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _f32p, _f32p]
+        L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
 
     def cases(self):
@@ -295,6 +327,22 @@ class Reference:
         assert rc == 0, name
         res["seconds"] = sec.value
         return res
+
+    COLLECT_CASES = ((64, 64, 100, 1), (5, 37, 20, 1), (7, 50, 0, 1), (33, 25, 10, 2))   # (N, steps, step_limit, hidden activation id)
+
+    def collect(self, N, steps, step_limit, hidden_act, actor_params, seed, n_collects):
+        """n_collects consecutive collect() calls of the reference's OnPolicyRunner on a fresh runner. Returns the data matrix
+        after each call [n_collects, (steps+1)*N, 13] and the final runner state."""
+        ds = np.empty((n_collects, (steps + 1) * N, 13), np.float32)
+        runner = dict(states=np.empty((N, 2), np.float32), episode_step=np.empty(N, np.int32), truncated=np.empty(N, np.uint8),
+                      episode_return=np.empty(N, np.float32))
+        step = C.c_uint64(0)
+        rc = self.lib.ref_collect(N, steps, step_limit, hidden_act, actor_params, seed, n_collects, ds, runner["states"], runner["episode_step"],
+                                  runner["truncated"], runner["episode_return"], C.byref(step))
+        if rc != 0:
+            raise KeyError("no such collect case")
+        runner["step"] = step.value
+        return ds, runner
 
     def gae(self, rewards, all_values, terminated, truncated, N, steps):
         adv, tgt = np.empty(steps * N, np.float32), np.empty(steps * N, np.float32)

@@ -455,6 +455,94 @@ void orc_normal_functions(int n, const float* mean, const float* log_std, const 
 }
 
 /* ------------------------------------------------------------------------------------------------------ */
+/* On-policy collect: rl/components/on_policy_runner/operations_generic.h:105-146 (collect),                  */
+/* operations_generic_per_env.h:9-36 (prologue), :37-79 (epilogue), dataset columns on_policy_runner.h:38-72.  */
+/* Pendulum: observation 3, action 1 -> row = obs[0:3] action_mean[3] action[4] log_prob[5] reward[6]         */
+/* terminated[7] truncated[8] reset[9] value[10] advantage[11] target_value[12]; row index step*N + env;      */
+/* reset is truncation delayed by one step: row env of step 0 takes the runner's incoming flag, row pos+N the  */
+/* flag after the step at pos. The final observation goes to row T*N + env. params = MLP arena followed by     */
+/* log_std[1]. Two sources of randomness: rng != NULL draws inline from ONE engine in the reference's order    */
+/* (per step: envs ascending initial states of truncated envs, then envs ascending action noise); rng == NULL  */
+/* reads the tables written by orc_collect_tables (reset_states [R,N,2], noise [T,N] standard normal draws).   */
+/* step_limit == 0 disables truncation (STEP_LIMIT > 0 && episode_step >= STEP_LIMIT).                        */
+/* ------------------------------------------------------------------------------------------------------ */
+int orc_pendulum_collect(const orc_mlp_shape* actor, const float* params, int N, int T, float* states, int32_t* episode_step,
+                         uint8_t* truncated, float* episode_return, orc_rng* rng, const float* reset_states, int R, const float* noise,
+                         int step_limit, float* dataset, int ld){
+    if(actor->input_dim != 3 || actor->dims[actor->n_layers - 1] != 1 || ld < 13) return -1;
+    const float log_std = params[orc_mlp_num_params(actor)];
+    int rc = 0;
+    int* reset_count = (int*)calloc((size_t)N, sizeof(int));
+    float* obs_t = (float*)malloc(sizeof(float) * 3 * (size_t)N); float* mean_t = (float*)malloc(sizeof(float) * (size_t)N);
+    for(int e = 0; e < N; e++) dataset[(size_t)e * ld + 9] = truncated[e] ? 1.0f : 0.0f;
+    for(int t = 0; t < T; t++){
+        for(int e = 0; e < N; e++){
+            if(truncated[e]){
+                truncated[e] = 0; episode_step[e] = 0; episode_return[e] = 0;
+                if(rng) orc_pendulum_sample_initial_state(rng, &states[2 * e], &states[2 * e + 1]);
+                else if(reset_count[e] >= R) rc = -2;
+                else{
+                    states[2 * e] = reset_states[((size_t)reset_count[e] * N + e) * 2];
+                    states[2 * e + 1] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 1];
+                    reset_count[e]++;
+                }
+            }
+            orc_pendulum_observe(states[2 * e], states[2 * e + 1], obs_t + 3 * e);
+            memcpy(dataset + ((size_t)t * N + e) * ld, obs_t + 3 * e, sizeof(float) * 3);
+        }
+        orc_mlp_evaluate(actor, params, obs_t, 3, mean_t, 1, N);
+        for(int e = 0; e < N; e++){
+            float* row = dataset + ((size_t)t * N + e) * ld;
+            const float mean = mean_t[e];
+            const float std = expf(log_std);
+            const float action = rng ? orc_normal(rng, mean, std) : noise[(size_t)t * N + e] * std + mean;
+            row[3] = mean; row[4] = action; row[5] = 0 + orc_normal_log_prob(mean, log_std, action);
+            float nt, ntd;
+            orc_pendulum_step(states[2 * e], states[2 * e + 1], action, &nt, &ntd);
+            const float r = orc_pendulum_reward(states[2 * e], states[2 * e + 1], action);
+            row[7] = 0;                                        /* Pendulum never terminates */
+            episode_return[e] += r; row[6] = r;
+            episode_step[e] += 1;
+            const int trunc = step_limit > 0 && episode_step[e] >= step_limit;
+            row[8] = (float)trunc;
+            row[(size_t)N * ld + 9] = (float)trunc;
+            truncated[e] = (uint8_t)trunc;
+            states[2 * e] = nt; states[2 * e + 1] = ntd;
+        }
+    }
+    for(int e = 0; e < N; e++) orc_pendulum_observe(states[2 * e], states[2 * e + 1], dataset + ((size_t)T * N + e) * ld);
+    free(reset_count); free(obs_t); free(mean_t);
+    return rc;
+}
+/* The draws of one collect call as tables, in the engine order described above. The truncation schedule depends only on
+ * the integer counters (Pendulum never terminates). noise holds the standard-normal variate of each fresh
+ * std::normal_distribution (action = noise * std + mean). Returns the number of reset rounds used or -1 if R is too small. */
+int orc_collect_tables(orc_rng* rng, int N, int T, const int32_t* episode_step_in, const uint8_t* truncated_in, int step_limit,
+                       float* reset_states, int R, float* noise){
+    int32_t* es = (int32_t*)malloc(sizeof(int32_t) * (size_t)N); uint8_t* tr = (uint8_t*)malloc((size_t)N); int* cnt = (int*)calloc((size_t)N, sizeof(int));
+    memcpy(es, episode_step_in, sizeof(int32_t) * (size_t)N); memcpy(tr, truncated_in, (size_t)N);
+    int used = 0, rc = 0;
+    for(int t = 0; t < T && rc == 0; t++){
+        for(int e = 0; e < N; e++){
+            if(tr[e]){
+                if(cnt[e] >= R){ rc = -1; break; }
+                float* dst = reset_states + ((size_t)cnt[e] * N + e) * 2;
+                orc_pendulum_sample_initial_state(rng, dst, dst + 1);
+                cnt[e]++; if(cnt[e] > used) used = cnt[e];
+                es[e] = 0;
+            }
+        }
+        if(rc) break;
+        for(int e = 0; e < N; e++){
+            noise[(size_t)t * N + e] = orc_normal(rng, 0.0f, 1.0f);
+            es[e] += 1; tr[e] = step_limit > 0 && es[e] >= step_limit;
+        }
+    }
+    free(es); free(tr); free(cnt);
+    return rc ? rc : used;
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
 /* PPO minibatch loss gradient w.r.t. the actor output and log_std: rl/algorithms/ppo/operations_generic.h   */
 /* :173-184 (advantage mean / std over the minibatch), :214-296 (per-sample clipped surrogate gradient,      */
 /* entropy bonus, log_std gradient accumulation). Default parameters (rl/algorithms/ppo/ppo.h:13-38).        */

@@ -18,6 +18,8 @@
 //   nn/loss_functions/mse/operations_generic.h   gradient
 //   rl/environments/pendulum/operations_generic.h   sample_initial_state / step / reward / observe
 //   random/operations_cpu.h   init(device, rng, seed), uniform_real_distribution, normal_distribution::sample
+//   rl/components/on_policy_runner/operations_generic.h   init / collect (actor: sequential<mlp_unconditional_stddev>)
+//   rl/algorithms/ppo/operations_generic.h   estimate_generalized_advantages
 #ifdef REF_USE_OPENBLAS
 #include <rl_tools/operations/cpu_mux.h>
 #else
@@ -32,6 +34,8 @@
 #include <rl_tools/nn/layers/dense/operations_cpu.h>
 #include <rl_tools/nn/loss_functions/mse/operations_generic.h>
 #include <rl_tools/nn_models/mlp/operations_generic.h>
+#include <rl_tools/nn_models/mlp_unconditional_stddev/operations_generic.h>
+#include <rl_tools/nn_models/sequential/operations_generic.h>
 #include <rl_tools/nn/optimizers/adam/operations_generic.h>
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
@@ -343,7 +347,66 @@ static void gae_case(const float* rewards, const float* all_values, const uint8_
     rlt::free(device, dataset);
 }
 
+// On-policy collect through the reference's own runner (rl/components/on_policy_runner/operations_generic.h:69-146,
+// operations_generic_per_env.h:9-79) with the PPO actor type (rl/algorithms/ppo/loop/core/config.h:54-67 without the
+// identity standardisation layer): sequential< mlp_unconditional_stddev 3 -> 64 -> 64 -> 1 >.
+// actor_params: W1 b1 W2 b2 W3 b3 log_std (flat). datasets receives n_collects x [(STEPS+1)*N, 13] (the whole data matrix
+// after each collect, zero-initialised before the first).
+template <TI N, TI STEPS, TI STEP_LIMIT, act::ActivationFunction HACT>
+static void collect_case(const float* actor_params, uint32_t seed, int n_collects, float* datasets, float* states_out, int32_t* episode_step_out,
+                         uint8_t* truncated_out, float* episode_return_out, uint64_t* runner_step_out){
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, HACT, act::IDENTITY>;
+    using ACTOR_MLP = rlt::nn_models::mlp_unconditional_stddev::BindConfiguration<ACTOR_CONFIG>;
+    using MODULE_CHAIN = rlt::nn_models::sequential::Module<ACTOR_MLP>;
+    using ACTOR = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, MODULE_CHAIN, rlt::tensor::Shape<TI, 1, N, 3>>;
+    using RUNNER_SPEC = rlt::rl::components::on_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, typename ACTOR::template State<>, N, STEP_LIMIT>;
+    using RUNNER = rlt::rl::components::OnPolicyRunner<RUNNER_SPEC>;
+    using DATASET_SPEC = rlt::rl::components::on_policy_runner::DatasetSpecification<RUNNER_SPEC, STEPS>;
+    using DATASET = rlt::rl::components::on_policy_runner::Dataset<DATASET_SPEC>;
+    static_assert(DATASET::DATA_DIM == 13);
+    DEVICE device;
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    ACTOR actor; typename ACTOR::template Buffer<> buffers; RUNNER runner; DATASET dataset;
+    rlt::malloc(device, actor); rlt::malloc(device, buffers); rlt::malloc(device, runner); rlt::malloc(device, dataset);
+    { const float* p = actor_params;
+      auto& mlp = actor.content;
+      load_layer(device, mlp.input_layer, p); load_layer(device, mlp.hidden_layers[0], p); load_layer(device, mlp.output_layer, p);
+      rlt::set(device, mlp.log_std.parameters, p[0], 0); }
+    rlt::Tensor<rlt::tensor::Specification<PENDULUM, TI, rlt::tensor::Shape<TI, N>>> envs;
+    rlt::Tensor<rlt::tensor::Specification<typename PENDULUM::Parameters, TI, rlt::tensor::Shape<TI, N>>> env_parameters;
+    rlt::malloc(device, envs); rlt::malloc(device, env_parameters);
+    rlt::set_all(device, dataset.data, 0);
+    rlt::init(device, runner, envs, env_parameters, actor, rng);
+    constexpr size_t DS = (size_t)(STEPS + 1) * N * 13;
+    for(int c = 0; c < n_collects; c++){
+        rlt::collect(device, dataset, runner, actor, buffers, rng);
+        for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < 13; k++) datasets[c * DS + r * 13 + k] = rlt::get(dataset.data, r, k);
+    }
+    for(TI e = 0; e < N; e++){
+        auto& st = rlt::get(runner.states, 0, e);
+        states_out[2 * e] = st.theta; states_out[2 * e + 1] = st.theta_dot;
+        episode_step_out[e] = (int32_t)rlt::get(runner.episode_step, 0, e);
+        truncated_out[e] = rlt::get(runner.truncated, 0, e) ? 1 : 0;
+        episode_return_out[e] = rlt::get(runner.episode_return, 0, e);
+    }
+    *runner_step_out = runner.step;
+    rlt::free(device, envs); rlt::free(device, env_parameters);
+    rlt::free(device, actor); rlt::free(device, buffers); rlt::free(device, runner); rlt::free(device, dataset);
+}
+
 extern "C" {
+
+int ref_collect(int N, int steps, int step_limit, int hidden_act, const float* actor_params, uint32_t seed, int n_collects, float* datasets,
+                float* states_out, int32_t* episode_step_out, uint8_t* truncated_out, float* episode_return_out, uint64_t* runner_step_out){
+#define COLLECT_CASE(n, s, l, a, A) if(N == n && steps == s && step_limit == l && hidden_act == a){ \
+        collect_case<n, s, l, A>(actor_params, seed, n_collects, datasets, states_out, episode_step_out, truncated_out, episode_return_out, runner_step_out); return 0; }
+    COLLECT_CASE(64, 64, 100, 1, act::RELU)
+    COLLECT_CASE(5, 37, 20, 1, act::RELU)
+    COLLECT_CASE(7, 50, 0, 1, act::RELU)
+    COLLECT_CASE(33, 25, 10, 2, act::TANH)
+#undef COLLECT_CASE
+    return -1;
+}
 
 int ref_gae(int N, int steps, const float* rewards, const float* all_values, const uint8_t* terminated, const uint8_t* truncated, float* advantages, float* target_values){
     if(N == 64 && steps == 1024){ gae_case<64, 1024>(rewards, all_values, terminated, truncated, advantages, target_values); return 0; }

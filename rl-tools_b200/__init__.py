@@ -111,6 +111,9 @@ def lib():
         L.b200rl_release_host_staging.argtypes = []
         L.b200rl_rng_init_host.argtypes = [vp, C.c_uint32]
         L.b200rl_reset_table_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i)]
+        L.b200rl_collect_tables_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i), vp]
+        L.b200rl_pendulum_collect.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
+        L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         _lib = L
     return _lib
 
@@ -323,3 +326,45 @@ def reset_table_host(seed, n_envs, n_steps, episode_step, truncated, step_limit,
     check(lib().b200rl_reset_table_host(C.c_void_p(state.ctypes.data), n_envs, n_steps, C.c_void_p(es.ctypes.data), C.c_void_p(tr.ctypes.data), step_limit,
                                         C.c_void_p(table.ctypes.data), n_rounds, C.byref(used)), "b200rl_reset_table_host")
     return table, used.value
+
+
+def rng_init_host(seed):
+    """State of the reference-compatible host engine (numpy uint32[625]); advanced in place by the *_tables_host calls."""
+    import numpy as np
+    state = np.zeros(625, np.uint32)
+    check(lib().b200rl_rng_init_host(C.c_void_p(state.ctypes.data), seed), "b200rl_rng_init_host")
+    return state
+
+
+def collect_tables_host(rng_state, n_envs, n_steps, episode_step, truncated, step_limit, n_rounds):
+    """Draws of one on-policy collect call in the reference engine's order: (reset_states [n_rounds, n_envs, 2], noise [n_steps, n_envs])."""
+    import numpy as np
+    table = np.zeros((max(n_rounds, 1), n_envs, 2), np.float32)
+    noise = np.empty((n_steps, n_envs), np.float32)
+    used = C.c_int(0)
+    es = np.ascontiguousarray(episode_step, np.int32)
+    tr = np.ascontiguousarray(truncated, np.uint8)
+    check(lib().b200rl_collect_tables_host(C.c_void_p(rng_state.ctypes.data), n_envs, n_steps, C.c_void_p(es.ctypes.data), C.c_void_p(tr.ctypes.data),
+                                           step_limit, C.c_void_p(table.ctypes.data), n_rounds, C.byref(used), C.c_void_p(noise.ctypes.data)),
+          "b200rl_collect_tables_host")
+    return table[:n_rounds], noise, used.value
+
+
+def pendulum_collect(shape, params, log_std, states, episode_step, truncated, episode_return, reset_states, noise, n_steps, step_limit,
+                     dataset=None, error_flag=None, layers=None):
+    """On-policy collect into the dataset matrix [(n_steps + 1) * N, 13] (GPU tensors; runner state updated in place).
+    `layers` = six separately allocated parameter tensors (W1 b1 W2 b2 W3 b3) instead of the flat arena `params`."""
+    import torch
+    N = states.shape[0]
+    dataset = torch.zeros(((n_steps + 1) * N, 13), device=states.device, dtype=torch.float32) if dataset is None else dataset
+    R = 0 if reset_states is None else reset_states.shape[0]
+    if layers is not None:
+        table = (C.c_void_p * 6)(*[t.data_ptr() for t in layers])
+        check(lib().b200rl_pendulum_collect_layers(C.byref(shape), table, _ptr(log_std), _ptr(states), _ptr(episode_step), _ptr(truncated),
+                                                   _ptr(episode_return), _ptr(reset_states), R, _ptr(noise), N, n_steps, step_limit, _ptr(dataset),
+                                                   dataset.stride(0), _ptr(error_flag), _stream()), "b200rl_pendulum_collect_layers")
+    else:
+        check(lib().b200rl_pendulum_collect(C.byref(shape), _ptr(params), _ptr(log_std), _ptr(states), _ptr(episode_step), _ptr(truncated),
+                                            _ptr(episode_return), _ptr(reset_states), R, _ptr(noise), N, n_steps, step_limit, _ptr(dataset),
+                                            dataset.stride(0), _ptr(error_flag), _stream()), "b200rl_pendulum_collect")
+    return dataset

@@ -41,6 +41,22 @@ static float uniform_real(uint32_t* st, float lo, float hi){
     volatile float scaled = u * (hi - lo);      // volatile: keep multiply and add separately rounded
     return scaled + lo;
 }
+// A fresh std::normal_distribution<float>(0, 1) per sample (random/operations_cpu.h:40-48): Marsaglia polar method on two
+// canonical draws per attempt; the second variate of the pair is discarded.
+static float standard_normal(uint32_t* st){
+    float x, y, r2;
+    do{
+        volatile float cx = (float)mt_next(st) / 4294967296.0f; if(cx >= 1.0f) cx = 0.99999994f;
+        volatile float cy = (float)mt_next(st) / 4294967296.0f; if(cy >= 1.0f) cy = 0.99999994f;
+        volatile float tx = 2.0f * cx, ty = 2.0f * cy;
+        x = tx - 1.0f; y = ty - 1.0f;
+        volatile float xx = x * x, yy = y * y;
+        r2 = xx + yy;
+    } while(r2 > 1.0f || r2 == 0.0f);
+    volatile float num = -2 * logf(r2);
+    const float mult = sqrtf(num / r2);
+    return y * mult;
+}
 
 // ---- device staging for the host-buffer rollout ---------------------------------------------------------------
 struct Staging {
@@ -183,6 +199,36 @@ int b200rl_reset_table_host(uint32_t* rng, int n_envs, int n_steps, const int32_
             }
         }
         for(int e = 0; e < n_envs; e++){ es[e] += 1; tr[e] = es[e] == step_limit; }
+    }
+    if(rounds_used_host) *rounds_used_host = used;
+    return B200RL_OK;
+}
+
+int b200rl_collect_tables_host(uint32_t* rng, int n_envs, int n_steps, const int32_t* episode_step_host, const uint8_t* truncated_host,
+                               int step_limit, float* reset_states_host, int n_reset_rounds, int* rounds_used_host, float* noise_host){
+    if(!rng || !episode_step_host || !truncated_host || n_envs < 0 || n_steps < 0 || step_limit < 0 || n_reset_rounds < 0 ||
+       (n_reset_rounds > 0 && !reset_states_host) || (!noise_host && n_steps > 0))
+        return B200RL_ERR_INVALID_ARGUMENT;
+    std::vector<int32_t> es(episode_step_host, episode_step_host + n_envs);
+    std::vector<uint8_t> tr(truncated_host, truncated_host + n_envs);
+    std::vector<int> cnt(n_envs, 0);
+    int used = 0;
+    const float PI_F = 3.14159265358979323846f;
+    for(int t = 0; t < n_steps; t++){
+        for(int e = 0; e < n_envs; e++){              // prologue: on_policy_runner/operations_generic_per_env.h:19-28
+            if(tr[e]){
+                if(cnt[e] >= n_reset_rounds) return B200RL_ERR_INVALID_ARGUMENT;
+                float* dst = reset_states_host + ((size_t)cnt[e] * n_envs + e) * 2;
+                dst[0] = uniform_real(rng, -PI_F, PI_F);
+                dst[1] = uniform_real(rng, -1.0f, 1.0f);
+                cnt[e]++; if(cnt[e] > used) used = cnt[e];
+                es[e] = 0;
+            }
+        }
+        for(int e = 0; e < n_envs; e++){              // epilogue: one normal draw per action, :46-60; truncation :72
+            noise_host[(size_t)t * n_envs + e] = standard_normal(rng);
+            es[e] += 1; tr[e] = step_limit > 0 && es[e] >= step_limit;
+        }
     }
     if(rounds_used_host) *rounds_used_host = used;
     return B200RL_OK;

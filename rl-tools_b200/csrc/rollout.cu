@@ -12,7 +12,7 @@ namespace b200rl {
 // CUDA-core kernel: exact fp32 FMA chain in the reference's summation order (bias first, inputs ascending).
 // Shared memory: W1 [H,3], b1 [H], W2 [H,H], b2 [H], W3 [H], b3 -- (H*H + 6H + 1) floats, read as warp broadcasts.
 // ---------------------------------------------------------------------------------------------------------------
-template <int H>
+template <int H, bool COLLECT>
 __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
     extern __shared__ __align__(16) float smem[];
     float* W1 = smem;                 // [H][3]
@@ -34,6 +34,12 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
     float er = a.episode_return[e];
     int resets = a.reset_count ? a.reset_count[e] : 0;
     const int act_h1 = a.acts[0], act_h2 = a.acts[1], act_out = a.acts[2];
+    GaussianHead head{};
+    const size_t ld = COLLECT ? (size_t)a.ld_dataset : 0;
+    if constexpr(COLLECT){
+        head.init(a.log_std);
+        a.dataset[(size_t)e * ld + COL_RESET] = trunc ? 1.0f : 0.0f;      // collect, operations_generic.h:115-117
+    }
 
     for(int t = 0; t < a.n_steps; t++){
         if(trunc){
@@ -47,7 +53,9 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
         float sn, cs;
         sincosf(theta, &sn, &cs);
         const size_t row = (size_t)t * a.n_envs + e;
-        a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot;
+        float* drow = COLLECT ? a.dataset + row * ld : nullptr;
+        if constexpr(COLLECT){ drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot; }
+        else{ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
 
         float h1[H];
 #pragma unroll
@@ -69,15 +77,34 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
             }
             out = fmaf(W3[j], activation_rt(acc, act_h2), out);
         }
-        const float action = activation_rt(out, act_out);
+        float action = activation_rt(out, act_out);
+        if constexpr(COLLECT){
+            const float mean = action;
+            action = head.sample(mean, __ldg(a.noise + row));
+            drow[COL_ACTION_MEAN] = mean; drow[COL_ACTION] = action; drow[COL_LOG_PROB] = head.log_prob(mean, action, a.neg_half_log_2pi);
+        }
 
         float nt, ntd;
         pendulum::step(theta, theta_dot, sn, action, nt, ntd);
         const float r = pendulum::reward(theta, theta_dot, action);
-        a.act[row] = action; a.rew[row] = r;
         es += 1; er = __fadd_rn(er, r);
-        trunc = (es == a.step_limit);          // Pendulum never terminates (operations_generic.h:243-247)
+        if constexpr(COLLECT){
+            trunc = a.step_limit > 0 && es >= a.step_limit;                 // operations_generic_per_env.h:72
+            const float flag = trunc ? 1.0f : 0.0f;
+            drow[COL_REWARD] = r; drow[COL_TERMINATED] = 0.0f; drow[COL_TRUNCATED] = flag;
+            drow[(size_t)a.n_envs * ld + COL_RESET] = flag;                 // all_reset[pos + N]
+        }
+        else{
+            a.act[row] = action; a.rew[row] = r;
+            trunc = (es == a.step_limit);      // Pendulum never terminates (operations_generic.h:243-247)
+        }
         theta = nt; theta_dot = ntd;
+    }
+    if constexpr(COLLECT){                     // final observation, operations_generic.h:136-143
+        float sn, cs;
+        sincosf(theta, &sn, &cs);
+        float* drow = a.dataset + ((size_t)a.n_steps * a.n_envs + e) * ld;
+        drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot;
     }
     a.states[2 * e] = theta; a.states[2 * e + 1] = theta_dot;
     a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
@@ -89,7 +116,8 @@ int launch_rollout_simt(const RolloutArgs& a, int H, cudaStream_t s){
     constexpr int THREADS = 128;
     size_t smem = sizeof(float) * (64 * 3 + 64 + 64 * 64 + 64 + 64 + 1);
     int grid = (a.env_count + THREADS - 1) / THREADS;
-    rollout_simt_kernel<64><<<grid, THREADS, smem, s>>>(a);
+    if(a.dataset) rollout_simt_kernel<64, true><<<grid, THREADS, smem, s>>>(a);
+    else rollout_simt_kernel<64, false><<<grid, THREADS, smem, s>>>(a);
     B200RL_LAUNCH_CHECK("rollout_simt");
     return B200RL_OK;
 }
@@ -129,4 +157,67 @@ extern "C" int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const floa
     a.n_steps = n_steps; a.step_limit = step_limit; a.obs = obs; a.act = act; a.rew = rew; a.error_flag = error_flag;
     for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
     return rollout_dispatch(actor, a, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// On-policy collect (rl/components/on_policy_runner/operations_generic.h:105-146): the same kernels with the Gaussian
+// policy head and the dataset-row writer switched on.
+// ---------------------------------------------------------------------------------------------------------------
+static int collect_launch(const b200rl_mlp_shape* actor, const float* actor_params, const float* log_std, float* states, int32_t* episode_step,
+                          uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, const float* noise,
+                          int n_envs, int n_steps, int step_limit, float* dataset, int ld_dataset, int* error_flag, cudaStream_t stream){
+    int rc = validate_actor(actor);
+    if(rc) return rc;
+    if(!actor_params || !log_std || !states || !episode_step || !truncated || !episode_return || !dataset || n_envs < 0 || n_steps < 0 ||
+       n_reset_rounds < 0 || step_limit < 0 || ld_dataset < COLLECT_DATA_DIM || (noise == nullptr && n_steps > 0))
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(reset_states == nullptr && n_reset_rounds != 0) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0) return B200RL_OK;
+    RolloutArgs a{};
+    a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
+    a.reset_states = reset_states; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs; a.env_begin = 0; a.env_count = n_envs;
+    a.n_steps = n_steps; a.step_limit = step_limit; a.error_flag = error_flag;
+    a.dataset = dataset; a.ld_dataset = ld_dataset; a.noise = noise; a.log_std = log_std;
+    a.neg_half_log_2pi = (float)(-0.5 * logf(2 * 3.14159265358979323846f));      // random/operations_generic.h:89
+    for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
+    return rollout_dispatch(actor, a, stream);
+}
+
+extern "C" int b200rl_pendulum_collect(const b200rl_mlp_shape* actor, const float* actor_params, const float* log_std, float* states,
+                                       int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states,
+                                       int n_reset_rounds, const float* noise, int n_envs, int n_steps, int step_limit, float* dataset,
+                                       int ld_dataset, int* error_flag, b200rl_stream_t stream){
+    return collect_launch(actor, actor_params, log_std, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds, noise,
+                          n_envs, n_steps, step_limit, dataset, ld_dataset, error_flag, (cudaStream_t)stream);
+}
+
+// Actor given as separately allocated layer tensors (how the reference's containers hold them): packed into a file-scope
+// device arena by device-to-device copies on the launch stream. Calls are ordered against each other by an event, since they
+// share that arena.
+static __device__ __align__(16) float g_collect_actor_arena[64 * 3 + 64 + 64 * 64 + 64 + 64 + 1 + 3];
+
+extern "C" int b200rl_pendulum_collect_layers(const b200rl_mlp_shape* actor, const float* const* layer_params, const float* log_std,
+                                              float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                                              const float* reset_states, int n_reset_rounds, const float* noise, int n_envs, int n_steps,
+                                              int step_limit, float* dataset, int ld_dataset, int* error_flag, b200rl_stream_t stream){
+    int rc = validate_actor(actor);
+    if(rc) return rc;
+    if(!layer_params) return B200RL_ERR_INVALID_ARGUMENT;
+    for(int i = 0; i < 6; i++) if(!layer_params[i]) return B200RL_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    static cudaEvent_t ev = nullptr;
+    float* arena = nullptr;
+    if(!ev) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    B200RL_CUDA_TRY(cudaGetSymbolAddress((void**)&arena, g_collect_actor_arena));
+    B200RL_CUDA_TRY(cudaStreamWaitEvent(s, ev, 0));
+    const size_t counts[6] = {64 * 3, 64, 64 * 64, 64, 64, 1};
+    size_t off = 0;
+    for(int i = 0; i < 6; i++){
+        B200RL_CUDA_TRY(cudaMemcpyAsync(arena + off, layer_params[i], sizeof(float) * counts[i], cudaMemcpyDeviceToDevice, s));
+        off += counts[i];
+    }
+    rc = collect_launch(actor, arena, log_std, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds, noise,
+                        n_envs, n_steps, step_limit, dataset, ld_dataset, error_flag, s);
+    B200RL_CUDA_TRY(cudaEventRecord(ev, s));
+    return rc;
 }

@@ -19,6 +19,33 @@ struct RolloutArgs {
     float* obs; float* act; float* rew;
     int* error_flag;            // device int, may be null: 1 = reset table exhausted, 2 = a bounded tensor-core wait timed out
     int acts[3];
+    // on-policy collect (dataset != null): rows of the runner's dataset matrix instead of obs / act / rew
+    float* dataset;             // [(n_steps + 1) * n_envs, ld_dataset], columns as in CollectColumns
+    int ld_dataset;
+    const float* noise;         // [n_steps, n_envs] standard-normal draws in the reference engine's order
+    const float* log_std;       // device scalar: the actor's state-independent log standard deviation
+    float neg_half_log_2pi;     // (float)(-0.5 * logf(2 pi)), evaluated on the host like the reference does
+};
+
+// Columns of the on-policy dataset for Pendulum (observation 3, action 1; rl/components/on_policy_runner/on_policy_runner.h:38-72)
+enum CollectColumns { COL_OBS = 0, COL_ACTION_MEAN = 3, COL_ACTION = 4, COL_LOG_PROB = 5, COL_REWARD = 6, COL_TERMINATED = 7,
+                      COL_TRUNCATED = 8, COL_RESET = 9, COL_VALUE = 10, COL_ADVANTAGE = 11, COL_TARGET_VALUE = 12, COLLECT_DATA_DIM = 13 };
+
+// Gaussian policy head of the rollout (on_policy_runner/operations_generic_per_env.h:46-60, random/operations_cpu.h:40-48,
+// random/operations_generic.h:87-97) with the reference's rounding sequence: action = eps * std + mean as separate multiply
+// and add; log_prob = (neg_half_log_2pi - log_std) - 0.5 * ((action - mean) / std)^2 with the square term in double.
+struct GaussianHead {
+    float log_std, std;
+    __device__ __forceinline__ void init(const float* log_std_ptr){
+        log_std = __ldg(log_std_ptr);
+        std = (float)exp((double)log_std);       // double exp rounded once = the host's correctly rounded expf
+    }
+    __device__ __forceinline__ float sample(float mean, float eps) const { return __fadd_rn(__fmul_rn(eps, std), mean); }
+    __device__ __forceinline__ float log_prob(float mean, float action, float neg_half_log_2pi) const {
+        const float pre_square = __fdiv_rn(__fsub_rn(action, mean), std);
+        const double sq = __dmul_rn(__dmul_rn(0.5, (double)pre_square), (double)pre_square);
+        return (float)__dsub_rn((double)__fsub_rn(neg_half_log_2pi, log_std), sq);
+    }
 };
 
 int validate_actor(const b200rl_mlp_shape* actor);

@@ -57,7 +57,7 @@ __device__ __forceinline__ float act_or_rt(float x, int rt){
     else return activation_rt(x, rt);
 }
 
-template <int A1, int A2>
+template <int A1, int A2, bool COLLECT>
 __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, int n_tiles, int envs_per_tile){
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment by OFFSET from the __shared__ array, so the compiler keeps the shared address space (LDS/STS, not generic)
@@ -115,6 +115,9 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     bool failed = false;
     uint64_t* my_turn = turn + (g >> 1);
     uint64_t* next_turn = turn + ((g >> 1) ^ 1);
+    GaussianHead head{};
+    const size_t ld = COLLECT ? (size_t)a.ld_dataset : 0;
+    if constexpr(COLLECT) head.init(a.log_std);
 
     const int rounds = (n_tiles + (int)gridDim.x * GROUPS - 1) / ((int)gridDim.x * GROUPS);
     for(int round = 0; round < rounds && !failed; round++){
@@ -138,6 +141,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             theta = a.states[2 * e]; theta_dot = a.states[2 * e + 1];
             es = a.episode_step[e]; trunc = a.truncated[e] != 0; er = a.episode_return[e];
             resets = a.reset_count ? a.reset_count[e] : 0;
+            if constexpr(COLLECT) a.dataset[(size_t)e * ld + COL_RESET] = trunc ? 1.0f : 0.0f;      // collect, operations_generic.h:115-117
         }
         for(int t = 0; t < a.n_steps; t++){
             if(trunc){
@@ -151,7 +155,11 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             float sn, cs;
             sincosf(theta, &sn, &cs);
             const size_t row = (size_t)t * a.n_envs + e;
-            if(valid){ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
+            float* drow = COLLECT ? a.dataset + row * ld : nullptr;
+            if(valid){
+                if constexpr(COLLECT){ drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot; }
+                else{ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
+            }
 
             // ---- layer 1 (CUDA cores, weights as constant-bank operands); A_hi -> TMEM, A_lo -> swizzled smem ----
 #pragma unroll
@@ -233,15 +241,38 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                     o3 = fmaf(c_actor[C_W3 + j + 3], act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]), act2), o3);
                 }
             }
-            const float action = activation_rt(c_actor[C_B3] + ((o0 + o1) + (o2 + o3)), act3);
+            float action = activation_rt(c_actor[C_B3] + ((o0 + o1) + (o2 + o3)), act3);
+            if constexpr(COLLECT){
+                const float mean = action;
+                action = head.sample(mean, valid ? __ldg(a.noise + row) : 0.0f);
+                if(valid){ drow[COL_ACTION_MEAN] = mean; drow[COL_ACTION] = action; drow[COL_LOG_PROB] = head.log_prob(mean, action, a.neg_half_log_2pi); }
+            }
 
             float nt, ntd;
             pendulum::step(theta, theta_dot, sn, action, nt, ntd);
             const float rwd = pendulum::reward(theta, theta_dot, action);
-            if(valid){ a.act[row] = action; a.rew[row] = rwd; }
             es += 1; er = __fadd_rn(er, rwd);
-            trunc = (es == a.step_limit);
+            if constexpr(COLLECT){
+                trunc = a.step_limit > 0 && es >= a.step_limit;             // operations_generic_per_env.h:72
+                if(valid){
+                    const float flag = trunc ? 1.0f : 0.0f;
+                    drow[COL_REWARD] = rwd; drow[COL_TERMINATED] = 0.0f; drow[COL_TRUNCATED] = flag;
+                    drow[(size_t)a.n_envs * ld + COL_RESET] = flag;         // all_reset[pos + N]
+                }
+            }
+            else{
+                if(valid){ a.act[row] = action; a.rew[row] = rwd; }
+                trunc = (es == a.step_limit);
+            }
             theta = nt; theta_dot = ntd;
+        }
+        if constexpr(COLLECT){
+            if(valid && !failed){                  // final observation, operations_generic.h:136-143
+                float sn, cs;
+                sincosf(theta, &sn, &cs);
+                float* drow = a.dataset + ((size_t)a.n_steps * a.n_envs + e) * ld;
+                drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot;
+            }
         }
         if(valid && !failed){
             a.states[2 * e] = theta; a.states[2 * e + 1] = theta_dot;
@@ -270,11 +301,11 @@ static int upload_small_layers(const float* params, cudaStream_t s, cudaEvent_t*
     return B200RL_OK;
 }
 
-template <int A1, int A2>
+template <int A1, int A2, bool COLLECT>
 static int launch_tc(const RolloutArgs& a, cudaStream_t s){
     static bool configured = false;
     if(!configured){
-        B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<A1, A2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+        B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<A1, A2, COLLECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
         configured = true;
     }
     cudaEvent_t order_event = nullptr;
@@ -288,7 +319,7 @@ static int launch_tc(const RolloutArgs& a, cudaStream_t s){
     const int n_tiles = (a.env_count + ept - 1) / ept;
     int grid = (n_tiles + GROUPS - 1) / GROUPS;
     if(grid > NUM_SMS) grid = NUM_SMS;
-    rollout_tc_kernel<A1, A2><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
+    rollout_tc_kernel<A1, A2, COLLECT><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
     B200RL_LAUNCH_CHECK("rollout_tc");
     if(order_event) B200RL_CUDA_TRY(cudaEventRecord(order_event, s));
     return B200RL_OK;
@@ -296,9 +327,13 @@ static int launch_tc(const RolloutArgs& a, cudaStream_t s){
 
 int launch_rollout_tc(const RolloutArgs& a, cudaStream_t s){
     const int a1 = a.acts[0], a2 = a.acts[1];
-    if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU>(a, s);
-    if(a1 == B200RL_ACT_TANH && a2 == B200RL_ACT_TANH) return launch_tc<B200RL_ACT_TANH, B200RL_ACT_TANH>(a, s);
-    return launch_tc<-1, -1>(a, s);
+    if(a.dataset){
+        if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, true>(a, s);
+        return launch_tc<-1, -1, true>(a, s);
+    }
+    if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, false>(a, s);
+    if(a1 == B200RL_ACT_TANH && a2 == B200RL_ACT_TANH) return launch_tc<B200RL_ACT_TANH, B200RL_ACT_TANH, false>(a, s);
+    return launch_tc<-1, -1, false>(a, s);
 }
 
 }  // namespace b200rl

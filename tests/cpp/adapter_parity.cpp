@@ -12,10 +12,16 @@
 #include <rl_tools/nn/loss_functions/mse/operations_generic.h>
 #include <rl_tools/nn_models/mlp/operations_generic.h>
 #include <rl_tools/nn/optimizers/adam/operations_generic.h>
+#include <rl_tools/rl/environments/pendulum/operations_generic.h>
+#include <rl_tools/nn_models/mlp_unconditional_stddev/operations_generic.h>
+#include <rl_tools/nn_models/sequential/operations_generic.h>
+#include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
 #include <b200rl/rl_tools_operations.h>
+#include <b200rl/rl_tools_on_policy_runner.h>
 
 #include <cstdio>
 #include <cmath>
+#include <vector>
 
 namespace rlt = rl_tools;
 using DEVICE_CPU = rlt::devices::DefaultCPU;
@@ -92,6 +98,69 @@ void train_steps(const char* name){
     rlt::free(gpu, x_gpu); rlt::free(gpu, y_gpu); rlt::free(gpu, d_gpu);
 }
 
+// On-policy collect: the reference's OnPolicyRunner on the CPU device against the same runner type on devices::B200, same engine
+// seed, consecutive collect calls. Flags, counters and the engine's final state must be identical; float columns agree to the first
+// steps' rounding and stay within a small drift over the horizon (the trajectories are free-running).
+template <TI N, TI STEPS, TI STEP_LIMIT, act::ActivationFunction HACT, int COLLECTS>
+void collect_parity(const char* name){
+    using PENDULUM = rlt::rl::environments::Pendulum<rlt::rl::environments::pendulum::Specification<T, TI, rlt::rl::environments::pendulum::DefaultParameters<T>>>;
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, HACT, act::IDENTITY>;
+    using ACTOR_MLP = rlt::nn_models::mlp_unconditional_stddev::BindConfiguration<ACTOR_CONFIG>;
+    using ACTOR = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<ACTOR_MLP>, rlt::tensor::Shape<TI, 1, N, 3>>;
+    using RUNNER_SPEC = rlt::rl::components::on_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, typename ACTOR::template State<>, N, STEP_LIMIT>;
+    using RUNNER = rlt::rl::components::OnPolicyRunner<RUNNER_SPEC>;
+    using DATASET = rlt::rl::components::on_policy_runner::Dataset<rlt::rl::components::on_policy_runner::DatasetSpecification<RUNNER_SPEC, STEPS>>;
+    DEVICE_CPU cpu; DEVICE_GPU gpu;
+    rlt::init(gpu);
+    DEVICE_CPU::SPEC::RANDOM::ENGINE<> rng_cpu, rng_gpu;
+    rlt::malloc(cpu, rng_cpu); rlt::malloc(cpu, rng_gpu);
+    rlt::init(cpu, rng_cpu, 3); rlt::init(cpu, rng_gpu, 3);
+    ACTOR actor_cpu, actor_gpu; typename ACTOR::template Buffer<> buf_cpu, buf_gpu;
+    RUNNER runner_cpu, runner_gpu; DATASET ds_cpu, ds_gpu, ds_back;
+    rlt::malloc(cpu, actor_cpu); rlt::malloc(cpu, buf_cpu); rlt::malloc(cpu, runner_cpu); rlt::malloc(cpu, ds_cpu); rlt::malloc(cpu, ds_back);
+    rlt::malloc(gpu, actor_gpu); rlt::malloc(gpu, buf_gpu); rlt::malloc(gpu, runner_gpu); rlt::malloc(gpu, ds_gpu);
+    rlt::init_weights(cpu, actor_cpu, rng_cpu); rlt::init_weights(cpu, actor_cpu, rng_gpu);          // both engines advance alike
+    rlt::set(cpu, actor_cpu.content.log_std.parameters, (T)-0.7, 0);
+    rlt::copy(cpu, gpu, actor_cpu, actor_gpu);
+    rlt::Tensor<rlt::tensor::Specification<PENDULUM, TI, rlt::tensor::Shape<TI, N>>> envs;
+    rlt::Tensor<rlt::tensor::Specification<typename PENDULUM::Parameters, TI, rlt::tensor::Shape<TI, N>>> env_parameters;
+    rlt::malloc(cpu, envs); rlt::malloc(cpu, env_parameters);
+    rlt::set_all(cpu, ds_cpu.data, 0); rlt::set_all(gpu, ds_gpu.data, 0);
+    rlt::init(cpu, runner_cpu, envs, env_parameters, actor_cpu, rng_cpu);
+    rlt::init(gpu, runner_gpu, envs, env_parameters, actor_gpu, rng_gpu);
+    double worst_flag = 0, worst_first = 0, worst_drift = 0;
+    for(int c = 0; c < COLLECTS; c++){
+        rlt::collect(cpu, ds_cpu, runner_cpu, actor_cpu, buf_cpu, rng_cpu);
+        rlt::collect(gpu, ds_gpu, runner_gpu, actor_gpu, buf_gpu, rng_gpu);
+        rlt::copy(gpu, cpu, ds_gpu.data, ds_back.data);
+        for(TI r = 0; r < (STEPS + 1) * N; r++){
+            for(TI k = 0; k < 10; k++){
+                if(r >= STEPS * N && k >= 3 && k != 9) continue;          // final-observation rows carry only the observation and reset
+                double d = std::fabs((double)rlt::get(ds_cpu.data, r, k) - (double)rlt::get(ds_back.data, r, k));
+                if(k >= 7) worst_flag = std::fmax(worst_flag, d);
+                else{
+                    worst_drift = std::fmax(worst_drift, d);
+                    if(c == 0 && r < N) worst_first = std::fmax(worst_first, d);
+                }
+            }
+        }
+    }
+    int status = rlt::check_status(gpu);
+    std::vector<TI> es(N); std::vector<uint8_t> tr(N);
+    b200rl_memcpy(es.data(), runner_gpu.episode_step._data, N * sizeof(TI), 1, gpu.stream);
+    b200rl_memcpy(tr.data(), runner_gpu.truncated._data, N, 1, gpu.stream);
+    bool counters = runner_cpu.step == runner_gpu.step;
+    for(TI e = 0; e < N; e++) counters = counters && es[e] == rlt::get(runner_cpu.episode_step, 0, e) && (tr[e] != 0) == rlt::get(runner_cpu.truncated, 0, e);
+    bool engines = rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_cpu) == rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_gpu);
+    bool ok = status == 0 && counters && engines && worst_flag == 0 && worst_first < 2e-5 && worst_drift < 5e-3;
+    std::printf("%-28s envs %4u steps %3u limit %3u collects %d  status %d  counters %d  engine %d  flags diff %.1e  first step diff %.2e  drift %.2e  %s\n",
+                name, N, STEPS, STEP_LIMIT, COLLECTS, status, (int)counters, (int)engines, worst_flag, worst_first, worst_drift, ok ? "OK" : "FAIL");
+    if(!ok) failures++;
+    rlt::free(cpu, actor_cpu); rlt::free(cpu, buf_cpu); rlt::free(cpu, runner_cpu); rlt::free(cpu, ds_cpu); rlt::free(cpu, ds_back);
+    rlt::free(gpu, actor_gpu); rlt::free(gpu, buf_gpu); rlt::free(gpu, runner_gpu); rlt::free(gpu, ds_gpu);
+    rlt::free(cpu, envs); rlt::free(cpu, env_parameters);
+}
+
 int main(){
     // the reference's CUDA sweep (cuda_basics.cu:961-972) plus the BASELINE shapes
     train_steps<   1, 256,  10, 100, 3, act::RELU, act::IDENTITY, 1>("sweep_b1");
@@ -107,6 +176,8 @@ int main(){
     train_steps< 256,   4, 256,   1, 3, act::RELU, act::IDENTITY, 5>("c3_sac_critic_5steps");
     train_steps<2048,  27,  64,   8, 3, act::TANH, act::IDENTITY, 2>("c4_ppo_actor");
     train_steps<1024,  64, 256,  16, 4, act::RELU, act::IDENTITY, 2>("c5_b1024");
+    collect_parity<  64, 64, 100, act::RELU, 3>("collect_ppo_default");
+    collect_parity<1000, 40,  15, act::TANH, 2>("collect_tanh_1000");
     std::printf("%s\n", failures ? "ADAPTER PARITY FAILED" : "ADAPTER PARITY OK");
     return failures ? 1 : 0;
 }

@@ -60,6 +60,24 @@ def test_reset_table_matches_oracle_stream(lib, orc):
     assert rc == 1
 
 
+def test_collect_tables_match_oracle_stream(lib, orc):
+    """Product-side normal_distribution / uniform_real draw order of on-policy collect vs the oracle's restatement, across two
+    consecutive calls on one engine state."""
+    N, T, limit = 131, 77, 30
+    es = (np.arange(N) * 7 % limit).astype(np.int32)
+    tr = (np.arange(N) % 4 == 0).astype(np.uint8)
+    state, rng = lib.rng_init_host(11), orc.new_rng(11)
+    for _ in range(2):
+        table, noise, used = lib.collect_tables_host(state, N, T, es, tr, limit, 4)
+        want_table, want_noise = orc.collect_tables(rng, N, T, es, tr, limit, 4)
+        assert used == 3
+        assert np.array_equal(table, want_table) and np.array_equal(noise, want_noise)
+    # step_limit 0 = never truncated: only the initially flagged environments draw a state
+    table, noise, used = lib.collect_tables_host(state, N, T, es, tr, 0, 1)
+    want_table, want_noise = orc.collect_tables(rng, N, T, es, tr, 0, 1)
+    assert used == 1 and np.array_equal(table, want_table) and np.array_equal(noise, want_noise)
+
+
 def test_product_does_not_reference_the_oracle():
     """The shipped package must never import or link the CPU oracle."""
     pkg = os.path.join(ROOT, "rl-tools_b200")

@@ -124,3 +124,33 @@ def test_gae_and_gaussian_head_match_reference(orc):
     mean, log_std, value = mg.det_normal(35, 4096), mg.det_uniform(36, 4096, -2.0, 0.5), mg.det_normal(37, 4096) * np.float32(1.5)
     lp, dm, dl = orc.normal_functions(mean, log_std, value)
     assert np.array_equal(lp, fix["normal_log_prob"]) and np.array_equal(dm, fix["normal_d_mean"]) and np.array_equal(dl, fix["normal_d_log_std"])
+
+
+def fresh_runner(N):
+    """Runner state right after init(): every environment flagged truncated (on_policy_runner/operations_generic.h:69-82)."""
+    return dict(states=np.zeros((N, 2), np.float32), episode_step=np.zeros(N, np.int32), truncated=np.ones(N, np.uint8),
+                episode_return=np.zeros(N, np.float32))
+
+
+@pytest.mark.parametrize("case", range(len(mg.COLLECT_CASES)))
+def test_on_policy_collect_matches_reference(orc, case):
+    """Consecutive collect() calls of the reference's OnPolicyRunner (one engine, resets and action noise interleaved) against the
+    oracle, once drawing inline from the engine and once through the draw tables the GPU path consumes. Bit-exact."""
+    fix = np.load(os.path.join(GOLDEN, "collect.npz"))
+    N, T, limit, hact, n_collects = mg.COLLECT_CASES[case]
+    params = mg.collect_params(case)
+    shape = oracle.MlpShape.make(3, [64, 64, 1], [hact, hact, 0])
+    for mode in ("inline", "tables"):
+        rng = orc.new_rng(mg.COLLECT_SEED)
+        runner = fresh_runner(N)
+        ds = np.zeros(((T + 1) * N, 13), np.float32)
+        for c in range(n_collects):
+            if mode == "inline":
+                orc.pendulum_collect(shape, params, runner, T, limit, rng=rng, dataset=ds)
+            else:
+                table, noise = orc.collect_tables(rng, N, T, runner["episode_step"], runner["truncated"], limit, 8)
+                orc.pendulum_collect(shape, params, runner, T, limit, reset_states=table, noise=noise, dataset=ds)
+            assert np.array_equal(ds, fix[f"dataset_{case}"][c]), (mode, c)
+        for k in ("states", "episode_step", "truncated", "episode_return"):
+            assert np.array_equal(runner[k], fix[f"{k}_{case}"]), (mode, k)
+        assert int(fix[f"runner_step_{case}"]) == n_collects * N * T

@@ -53,3 +53,21 @@ def test_rollout_live_chunked_evaluate(orc, ref_strict):
     b = ref_strict.pendulum_rollout(actor, np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32), table, T, chunk=256)
     for k in a:
         assert np.array_equal(a[k], b[k]), k
+
+
+def test_collect_live(orc, ref_strict):
+    """collect() of the real reference, compiled here, against the oracle on parameters the fixtures do not cover."""
+    for i, (N, T, limit, hact) in enumerate(oracle.Reference.COLLECT_CASES):
+        params = (np.random.RandomState(100 + i).randn(4482) * 0.4).astype(np.float32)
+        params[-1] = 0.3 - 0.4 * i
+        want, runner_ref = ref_strict.collect(N, T, limit, hact, params, 5 + i, 2)
+        shape = oracle.MlpShape.make(3, [64, 64, 1], [hact, hact, 0])
+        rng = orc.new_rng(5 + i)
+        runner = dict(states=np.zeros((N, 2), np.float32), episode_step=np.zeros(N, np.int32), truncated=np.ones(N, np.uint8),
+                      episode_return=np.zeros(N, np.float32))
+        ds = np.zeros(((T + 1) * N, 13), np.float32)
+        for c in range(2):
+            orc.pendulum_collect(shape, params, runner, T, limit, rng=rng, dataset=ds)
+            assert np.array_equal(ds, want[c])
+        for k in ("states", "episode_step", "truncated", "episode_return"):
+            assert np.array_equal(runner[k], runner_ref[k]), k

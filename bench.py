@@ -229,6 +229,72 @@ def run_mlp_train(args):
         dist.destroy_process_group()
 
 
+def run_collect(args):
+    """Secondary line: the on-policy collect (PPO rollout) of `--envs` Pendulum environments per GPU x `--collect-steps` steps with the
+    PPO default actor (3 -> 64 -> 64 -> 1, ReLU, identity output, Gaussian head) and STEP_LIMIT 100; draw tables resident in HBM.
+    One step = one collect call = one kernel launch writing the [(T + 1) * N, 13] dataset matrix."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    world, rank, local_rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    N, T, limit = args.envs, args.collect_steps, 100
+    shape = pkg.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "identity"])
+    rs = np.random.RandomState(100 + rank)
+    params = torch.from_numpy(np.concatenate([(rs.uniform(-1, 1, 4481) * 0.3).astype(np.float32), np.float32([-0.5])])).to(dev)
+    # synthetic draw tables with the distributions of the real ones (initial states U(-pi, pi) x U(-1, 1), noise N(0, 1)); the
+    # counters are reset before every call so that each call consumes the same table (one reset round at step 0)
+    table = torch.from_numpy(np.stack([rs.uniform(-np.pi, np.pi, (1, N)), rs.uniform(-1, 1, (1, N))], -1).astype(np.float32)).to(dev)
+    noise = torch.from_numpy(rs.standard_normal((T, N)).astype(np.float32)).to(dev)
+    states, es, tr, er = torch.zeros((N, 2), device=dev), torch.zeros(N, dtype=torch.int32, device=dev), torch.ones(N, dtype=torch.uint8, device=dev), torch.zeros(N, device=dev)
+    ds = torch.zeros(((T + 1) * N, 13), device=dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+
+    def step():
+        es.zero_(); tr.fill_(1)
+        pkg.pendulum_collect(shape, params, params[4481:], states, es, tr, er, table, noise, T, limit, dataset=ds, error_flag=flag)
+
+    sync = lambda: (dist.barrier() if dist is not None else None, torch.cuda.synchronize())
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    sync()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    for i in range(args.steps):
+        flush.zero_(); es.zero_(); tr.fill_(1)
+        starts[i].record()
+        pkg.pendulum_collect(shape, params, params[4481:], states, es, tr, er, table, noise, T, limit, dataset=ds, error_flag=flag)
+        stops[i].record()
+    sync()
+    assert int(flag.item()) == 0
+    tm = torch.tensor([sum(a.elapsed_time(b) for a, b in zip(starts, stops))], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    ms = float(tm.item()) / args.steps
+    if rank == 0:
+        peaks = measured_peaks()
+        bytes_step = 44.0                      # 10 dataset floats written + 1 noise float read per env-step
+        tflops = FLOP_PER_ENV_STEP * N * T / (ms * 1e-3) / 1e12
+        print(json.dumps({"metric": "env-steps/s (on-policy collect: actor fwd + Gaussian head + env step + dataset row)", "value": world * N * T / (ms * 1e-3),
+                          "unit": "env-steps/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": f"pendulum_collect_{N}env_x{T}step_actor3-64-64-1_limit{limit}", "l2": "flushed between timed iterations",
+                                     "parallelism": f"env-sharded x{world}, no collective"},
+                          "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
+                                       "peak_source": peaks["source"] + " bf16 dense (burst)", "hbm_gbs": bytes_step * N * T / (ms * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]},
+                          "gpu_launches": args.steps}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -241,12 +307,16 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train"],
-                    help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP")
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect"],
+                    help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
+                         "collect = secondary line: on-policy (PPO) collect into the dataset matrix")
+    ap.add_argument("--collect-steps", type=int, default=64, help="collect: steps per environment per call")
     ap.add_argument("--train-rows", type=int, default=1 << 24, help="mlp_train: total input rows over all GPUs")
     args = ap.parse_args()
     if args.workload == "mlp_train":
         return run_mlp_train(args)
+    if args.workload == "collect":
+        return run_collect(args)
     if args.impl == "reference":
         return run_reference(args)
     if not args.allow_short_warmup:

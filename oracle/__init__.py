@@ -190,6 +190,37 @@ class Oracle:
             p, m, v = self.adam_update(p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
         return p, g, m, v, pre, out
 
+    def ppo_train(self, actor_shape, critic_shape, actor_params, critic_params, dataset, n_rows, batch, epochs,
+                  alpha=1e-3, beta_1=0.9, beta_2=0.999, eps=1e-7, eps_sqrt=1e-7):
+        """The PPO update of rl/algorithms/ppo/operations_generic.h:96-336 without epoch shuffling, default parameters: per minibatch
+        zero_gradient, actor forward, clipped-surrogate gradient (+ log_std gradient), actor backward, critic forward, MSE gradient with
+        weight 0.5 against the target values, critic backward, one Adam step each. dataset = the [rows, 13] matrix of the on-policy
+        runner; actor_params = MLP arena + log_std. Returns (actor params, grads, first moment, critic params, grads, first moment)."""
+        na = actor_shape.num_params()
+        ap, cp = actor_params.copy(), critic_params.copy()
+        am, av, cm, cv = np.zeros_like(ap), np.zeros_like(ap), np.zeros_like(cp), np.zeros_like(cp)
+        a_age = c_age = 1
+        ag, cg = np.zeros_like(ap), np.zeros_like(cp)
+        for _ in range(epochs):
+            for b in range(n_rows // batch):
+                rows = dataset[b * batch:(b + 1) * batch]
+                obs = np.ascontiguousarray(rows[:, 0:3])
+                pre, out = self.mlp_forward(actor_shape, ap[:na], obs)
+                current = np.ascontiguousarray(out[-batch:].reshape(batch, 1))
+                d_actions, d_log_std = self.ppo_policy_gradient(current, np.ascontiguousarray(rows[:, 4:5]), ap[na:], np.ascontiguousarray(rows[:, 5]),
+                                                                np.ascontiguousarray(rows[:, 11]))
+                g_mlp, _ = self.mlp_backward(actor_shape, ap[:na], np.zeros(na, np.float32), obs, pre, out, d_actions)
+                ag = np.concatenate([g_mlp, d_log_std]).astype(np.float32)
+                pre, out = self.mlp_forward(critic_shape, cp, obs)
+                values = np.ascontiguousarray(out[-batch:].reshape(batch, 1))
+                d_values = self.mse_gradient(values, np.ascontiguousarray(rows[:, 12:13]), 0.5)
+                cg, _ = self.mlp_backward(critic_shape, cp, np.zeros_like(cp), obs, pre, out, d_values)
+                c1, c2, a_age = self.adam_bias_correction(beta_1, beta_2, a_age)
+                ap, am, av = self.adam_update(ap, ag, am, av, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
+                c1, c2, c_age = self.adam_bias_correction(beta_1, beta_2, c_age)
+                cp, cm, cv = self.adam_update(cp, cg, cm, cv, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
+        return ap, ag, am, cp, cg, cm
+
     # --- pendulum ------------------------------------------------------------------------------------------
     def pendulum_initial_states(self, seed, n):
         s = np.empty((n, 2), np.float32)
@@ -294,6 +325,7 @@ class Reference:
                                            _f32p, _f32p, _f32p, C.c_int]
         L.ref_pendulum_rollout.restype = C.c_int
         L.ref_gae.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _f32p, _f32p]
+        L.ref_ppo_train.argtypes = [C.c_int] * 4 + [_f32p] * 9
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
 
@@ -343,6 +375,16 @@ class Reference:
             raise KeyError("no such collect case")
         runner["step"] = step.value
         return ds, runner
+
+    PPO_TRAIN_CASES = ((64, 64, 4096, 1), (64, 64, 512, 2), (5, 37, 37, 3))      # (N, steps, minibatch, epochs)
+
+    def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset):
+        """The reference's train() on a given dataset matrix [(steps+1)*N, 13]; no shuffling. Returns the same tuple as Oracle.ppo_train."""
+        outs = [np.empty(4482, np.float32) for _ in range(3)] + [np.empty(4481, np.float32) for _ in range(3)]
+        rc = self.lib.ref_ppo_train(N, steps, batch, epochs, actor_params, critic_params, np.ascontiguousarray(dataset, np.float32), *outs)
+        if rc != 0:
+            raise KeyError("no such PPO train case")
+        return tuple(outs)
 
     def gae(self, rewards, all_values, terminated, truncated, N, steps):
         adv, tgt = np.empty(steps * N, np.float32), np.empty(steps * N, np.float32)

@@ -394,7 +394,70 @@ static void collect_case(const float* actor_params, uint32_t seed, int n_collect
     rlt::free(device, actor); rlt::free(device, buffers); rlt::free(device, runner); rlt::free(device, dataset);
 }
 
+// PPO update through the reference's own train() (rl/algorithms/ppo/operations_generic.h:96-336) on a caller-provided dataset matrix:
+// EPOCHS x (STEPS_TOTAL / BATCH) minibatches, no shuffling, default PPO parameters otherwise (ppo.h:13-38), Adam with the TF defaults.
+// Actor = sequential<mlp_unconditional_stddev 3->64->64->1>, critic = sequential<mlp 3->64->64->1>, both ReLU / identity.
+// Outputs after the call: parameters, and the gradient and Adam first moment left by the LAST minibatch, actor (4482 = MLP arena +
+// log_std) and critic (4481).
+template <TI BATCH, TI EPOCHS>
+struct PpoTrainParameters: rlt::rl::algorithms::ppo::DefaultParameters<TYPE_POLICY, TI, BATCH>{
+    static constexpr TI N_EPOCHS = EPOCHS;
+    static constexpr bool SHUFFLE_EPOCH = false;
+};
+template <TI N, TI STEPS, TI BATCH, TI EPOCHS>
+static void ppo_train_case(const float* actor_params, const float* critic_params, const float* dataset_in, float* actor_out, float* actor_grad, float* actor_m,
+                           float* critic_out, float* critic_grad, float* critic_m){
+    using CAPABILITY = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
+    using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, BATCH, 3>;
+    using MLP_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::IDENTITY>;
+    using ACTOR = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp_unconditional_stddev::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
+    using CRITIC = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
+    using PARAMETERS = PpoTrainParameters<BATCH, EPOCHS>;
+    using PPO_SPEC = rlt::rl::algorithms::ppo::Specification<TYPE_POLICY, TI, PENDULUM, ACTOR, CRITIC, PARAMETERS>;
+    using PPO = rlt::rl::algorithms::PPO<PPO_SPEC>;
+    using PPO_BUFFERS = rlt::rl::algorithms::ppo::Buffers<rlt::rl::algorithms::ppo::BufferSpecification<PPO_SPEC>>;
+    using RUNNER_SPEC = rlt::rl::components::on_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, typename ACTOR::template State<>, N, 100>;
+    using DATASET = rlt::rl::components::on_policy_runner::Dataset<rlt::rl::components::on_policy_runner::DatasetSpecification<RUNNER_SPEC, STEPS>>;
+    using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
+    DEVICE device;
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    PPO ppo; PPO_BUFFERS ppo_buffers; DATASET dataset; OPTIMIZER actor_optimizer, critic_optimizer;
+    typename ACTOR::template Buffer<> actor_buffers; typename CRITIC::template Buffer<> critic_buffers;
+    rlt::malloc(device, ppo); rlt::malloc(device, ppo_buffers); rlt::malloc(device, dataset); rlt::malloc(device, actor_optimizer); rlt::malloc(device, critic_optimizer);
+    rlt::malloc(device, actor_buffers); rlt::malloc(device, critic_buffers);
+    rlt::init(device, ppo, actor_optimizer, critic_optimizer, rng);
+    { const float* p = actor_params; auto& m = ppo.actor.content;
+      load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p);
+      rlt::set(device, m.log_std.parameters, p[0], 0); }
+    { const float* p = critic_params; auto& m = ppo.critic.content;
+      load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
+    for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < 13; k++) rlt::set(dataset.data, r, k, dataset_in[r * 13 + k]);
+    rlt::train(device, ppo, dataset, actor_optimizer, critic_optimizer, ppo_buffers, actor_buffers, critic_buffers, rng);
+    auto dump = [&](auto& m, float* params, float* grads, float* mom){
+        store_layer(device, m.input_layer, params, PARAMS); store_layer(device, m.hidden_layers[0], params, PARAMS); store_layer(device, m.output_layer, params, PARAMS);
+        store_layer(device, m.input_layer, grads, GRADS); store_layer(device, m.hidden_layers[0], grads, GRADS); store_layer(device, m.output_layer, grads, GRADS);
+        store_layer(device, m.input_layer, mom, MOM1); store_layer(device, m.hidden_layers[0], mom, MOM1); store_layer(device, m.output_layer, mom, MOM1);
+    };
+    dump(ppo.actor.content, actor_out, actor_grad, actor_m);
+    actor_out[4481] = rlt::get(device, ppo.actor.content.log_std.parameters, 0);
+    actor_grad[4481] = rlt::get(device, ppo.actor.content.log_std.gradient, 0);
+    actor_m[4481] = rlt::get(device, ppo.actor.content.log_std.gradient_first_order_moment, 0);
+    dump(ppo.critic.content, critic_out, critic_grad, critic_m);
+    rlt::free(device, ppo); rlt::free(device, ppo_buffers); rlt::free(device, dataset); rlt::free(device, actor_optimizer); rlt::free(device, critic_optimizer);
+    rlt::free(device, actor_buffers); rlt::free(device, critic_buffers);
+}
+
 extern "C" {
+
+int ref_ppo_train(int N, int steps, int batch, int epochs, const float* actor_params, const float* critic_params, const float* dataset_in,
+                  float* actor_out, float* actor_grad, float* actor_m, float* critic_out, float* critic_grad, float* critic_m){
+#define PPO_CASE(n, s, b, e) if(N == n && steps == s && batch == b && epochs == e){ ppo_train_case<n, s, b, e>(actor_params, critic_params, dataset_in, actor_out, actor_grad, actor_m, critic_out, critic_grad, critic_m); return 0; }
+    PPO_CASE(64, 64, 4096, 1)
+    PPO_CASE(64, 64, 512, 2)
+    PPO_CASE(5, 37, 37, 3)
+#undef PPO_CASE
+    return -1;
+}
 
 int ref_collect(int N, int steps, int step_limit, int hidden_act, const float* actor_params, uint32_t seed, int n_collects, float* datasets,
                 float* states_out, int32_t* episode_step_out, uint8_t* truncated_out, float* episode_return_out, uint64_t* runner_step_out){
@@ -411,6 +474,7 @@ int ref_collect(int N, int steps, int step_limit, int hidden_act, const float* a
 int ref_gae(int N, int steps, const float* rewards, const float* all_values, const uint8_t* terminated, const uint8_t* truncated, float* advantages, float* target_values){
     if(N == 64 && steps == 1024){ gae_case<64, 1024>(rewards, all_values, terminated, truncated, advantages, target_values); return 0; }
     if(N == 5 && steps == 37){ gae_case<5, 37>(rewards, all_values, terminated, truncated, advantages, target_values); return 0; }
+    if(N == 64 && steps == 64){ gae_case<64, 64>(rewards, all_values, terminated, truncated, advantages, target_values); return 0; }
     return -1;
 }
 // Gaussian head: random/operations_generic.h:87-121

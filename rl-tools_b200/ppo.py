@@ -1,0 +1,71 @@
+"""Host-side mirror of the reference's PPO update on the on-policy dataset matrix, driving the C ABI.
+
+`DatasetLayout` gives the column views of rl/components/on_policy_runner/on_policy_runner.h:38-72 (symmetric observations);
+`estimate_generalized_advantages` and `train` follow rl/algorithms/ppo/operations_generic.h:59-95 and :96-336 with the default
+parameters of rl/algorithms/ppo/ppo.h:13-38. Everything runs on the GPU on torch CUDA tensors; there is no CPU path.
+"""
+from . import gae as _gae, mse_gradient as _mse_gradient, ppo_policy_gradient as _ppo_policy_gradient
+
+
+class DatasetLayout:
+    """Column offsets of the dataset matrix [(steps + 1) * n_envs, data_dim], row = step * n_envs + env."""
+
+    def __init__(self, observation_dim, action_dim):
+        o, a = observation_dim, action_dim
+        self.observation_dim, self.action_dim = o, a
+        self.observations = slice(0, o)
+        self.actions_mean = slice(o, o + a)
+        self.actions = slice(o + a, o + 2 * a)
+        self.action_log_probs = o + 2 * a
+        self.rewards = o + 2 * a + 1
+        self.terminated = o + 2 * a + 2
+        self.truncated = o + 2 * a + 3
+        self.reset = o + 2 * a + 4
+        self.values = o + 2 * a + 5
+        self.advantages = o + 2 * a + 6
+        self.target_values = o + 2 * a + 7
+        self.data_dim = o + 2 * a + 8
+
+
+def estimate_generalized_advantages(dataset, layout, n_envs, steps, gamma=0.99, lam=0.95, ignore_termination=False):
+    """Fills the advantage and target-value columns from rewards / values / flags, in place (one backward scan per environment).
+    The value column must hold the critic's values of all (steps + 1) * n_envs observations."""
+    rows = steps * n_envs
+    adv, tgt = _gae(dataset[:, layout.rewards], dataset[:, layout.values], dataset[:, layout.terminated], dataset[:, layout.truncated],
+                    n_envs, steps, gamma, lam, ignore_termination)
+    dataset[:rows, layout.advantages] = adv
+    dataset[:rows, layout.target_values] = tgt
+    return dataset
+
+
+def evaluate_values(critic, dataset, layout):
+    """critic(all observations) -> value column, as the PPO loop does before the advantage estimate
+    (rl/algorithms/ppo/loop/core/operations_generic.h: evaluate(critic, all_observations_privileged, all_values))."""
+    for begin in range(0, dataset.shape[0], critic.batch):           # the Mlp's ping-pong buffers hold critic.batch rows
+        rows = dataset[begin:begin + critic.batch]
+        critic.evaluate(rows[:, layout.observations], y=rows[:, layout.values:layout.values + 1])
+    return dataset
+
+
+def train(actor, critic, dataset, layout, n_rows, batch_size, n_epochs=10, epsilon_clip=0.2, entropy_coefficient=0.01, advantage_epsilon=1e-8,
+          normalize_advantage=True, learn_action_std=True):
+    """n_epochs x (n_rows // batch_size) minibatch updates in dataset order (the reference's SHUFFLE_EPOCH = false): zero_gradient,
+    actor forward, clipped-surrogate gradient (+ log_std gradient), actor backward, critic forward, 0.5-weighted MSE gradient against
+    the target values, critic backward, one Adam step each. `actor` is an Mlp with extra_params = action_dim (the log_std behind the
+    layers), `critic` an Mlp with one output; both built for batch_size rows."""
+    assert actor.batch == batch_size and critic.batch == batch_size and actor.n_extra == layout.action_dim
+    for _ in range(n_epochs):
+        for b in range(n_rows // batch_size):
+            rows = dataset[b * batch_size:(b + 1) * batch_size]
+            obs = rows[:, layout.observations]
+            actor.zero_gradient()
+            critic.zero_gradient()
+            current = actor.forward(obs)
+            d_actions = _ppo_policy_gradient(current, rows[:, layout.actions], actor.extra("params"), rows[:, layout.action_log_probs], rows[:, layout.advantages],
+                                             actor.extra("grads"), epsilon_clip, entropy_coefficient, advantage_epsilon, normalize_advantage, learn_action_std,
+                                             d_actions=actor.d_out_buffer())
+            actor.backward(obs, d_actions)
+            values = critic.forward(obs)
+            critic.backward(obs, _mse_gradient(values, rows[:, layout.target_values:layout.target_values + 1], 0.5, d_a=critic.d_out_buffer()))
+            actor.step()
+            critic.step()

@@ -121,3 +121,53 @@ def test_ppo_minibatch_update_on_ant_shapes(lib, orc, torch):
     assert np.all(np.abs(ga_d - ga) <= 1e-6 + 1e-5 * np.abs(ga) + 1e-5 * np.abs(ga).max() + B * 3e-8 * np.abs(ga))
     assert np.all(np.abs(actor.params.cpu().numpy() - pa_ref) <= 2e-6 + 1e-5 * np.abs(pa_ref))
     assert np.all(np.abs(critic.params.cpu().numpy() - pc_ref) <= 2e-6 + 1e-5 * np.abs(pc_ref))
+
+
+@pytest.mark.parametrize("case", range(len(mg.PPO_TRAIN_CASES)))
+def test_ppo_train_vs_reference_golden(lib, torch, case):
+    """The whole PPO update (rl_tools_b200.ppo.train: epochs x minibatches over the dataset matrix, column views with the matrix's row
+    pitch) against what the REAL reference's train() left behind on the same stored dataset: parameters of both networks within
+    1e-5 |ref| + 2e-6 after up to 16 Adam steps, last-minibatch gradients within 1e-5 of the tensor's scale."""
+    from rl_tools_b200 import ppo
+    fix = np.load(os.path.join(GOLDEN, "ppo_train.npz"))
+    N, steps, batch, epochs = mg.PPO_TRAIN_CASES[case]
+    pa, pc = mg.ppo_train_params(case)
+    dims, acts = [64, 64, 1], ["relu", "relu", "identity"]
+    actor, critic = lib.Mlp(3, dims, acts, batch, extra_params=1), lib.Mlp(3, dims, acts, batch)
+    actor.params.copy_(dev(torch, pa)); critic.params.copy_(dev(torch, pc))
+    dataset = dev(torch, fix[f"dataset_{case}"])
+    layout = ppo.DatasetLayout(3, 1)
+    assert layout.data_dim == 13 and layout.target_values == 12
+    ppo.train(actor, critic, dataset, layout, N * steps, batch, n_epochs=epochs)
+    for name, got in (("actor", actor.params), ("critic", critic.params)):
+        want = fix[f"{name}_{case}"]
+        err = np.abs(got.cpu().numpy() - want)
+        assert np.all(err <= 2e-6 + 1e-5 * np.abs(want)), f"{name}: max err {err.max():.3e}"
+    for name, got in (("actor_grad", actor.grads), ("critic_grad", critic.grads), ("actor_m", actor.m), ("critic_m", critic.m)):
+        want = fix[f"{name}_{case}"]
+        err = np.abs(got.cpu().numpy() - want)
+        assert np.all(err <= 1e-5 * np.abs(want).max() + 1e-5 * np.abs(want) + 1e-8), f"{name}: max err {err.max():.3e} of scale {np.abs(want).max():.3e}"
+
+
+def test_gae_and_values_in_place_on_the_dataset_matrix(lib, orc, torch):
+    """evaluate_values + estimate_generalized_advantages write the value / advantage / target columns of the dataset matrix in place;
+    advantage and target are bit-exact against the oracle given the same value column."""
+    from rl_tools_b200 import ppo
+    fix = np.load(os.path.join(GOLDEN, "ppo_train.npz"))
+    N, steps = 64, 64
+    ds = fix["dataset_0"].copy()
+    _, pc = mg.ppo_train_params(0)
+    critic = lib.Mlp(3, [64, 64, 1], ["relu", "relu", "identity"], 1024)
+    critic.params.copy_(dev(torch, pc))
+    d = dev(torch, ds)
+    d[:, 10:13] = 0
+    layout = ppo.DatasetLayout(3, 1)
+    ppo.evaluate_values(critic, d, layout)
+    values = d[:, 10].cpu().numpy()
+    assert np.all(np.abs(values - ds[:, 10]) <= 2e-6 + 1e-5 * np.abs(ds[:, 10]))
+    ppo.estimate_generalized_advantages(d, layout, N, steps)
+    n = N * steps
+    adv, tgt = orc.gae(np.ascontiguousarray(ds[:n, 6]), values, ds[:n, 7].astype(np.uint8), ds[:n, 8].astype(np.uint8), N, steps)
+    got = d.cpu().numpy()
+    assert np.array_equal(got[:n, 11], adv) and np.array_equal(got[:n, 12], tgt)
+    assert np.array_equal(got[:, :10], ds[:, :10])

@@ -154,3 +154,17 @@ def test_on_policy_collect_matches_reference(orc, case):
         for k in ("states", "episode_step", "truncated", "episode_return"):
             assert np.array_equal(runner[k], fix[f"{k}_{case}"]), (mode, k)
         assert int(fix[f"runner_step_{case}"]) == n_collects * N * T
+
+
+@pytest.mark.parametrize("case", range(len(mg.PPO_TRAIN_CASES)))
+def test_ppo_train_matches_reference(orc, case):
+    """The reference's train() (epochs x minibatches of clipped-surrogate actor update + critic regression, Adam) on a stored dataset
+    matrix against the oracle's composition of its dense / PPO-gradient / Adam pieces: parameters, last gradients and first moments of
+    both networks, bit for bit. This pins the PPO policy-gradient restatement."""
+    fix = np.load(os.path.join(GOLDEN, "ppo_train.npz"))
+    N, steps, batch, epochs = mg.PPO_TRAIN_CASES[case]
+    actor, critic = mg.ppo_train_params(case)
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "identity"])
+    got = orc.ppo_train(shape, shape, actor, critic, fix[f"dataset_{case}"], N * steps, batch, epochs)
+    for name, g in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got):
+        assert np.array_equal(g, fix[f"{name}_{case}"]), name

@@ -71,3 +71,25 @@ def test_collect_live(orc, ref_strict):
             assert np.array_equal(ds, want[c])
         for k in ("states", "episode_step", "truncated", "episode_return"):
             assert np.array_equal(runner[k], runner_ref[k]), k
+
+
+def test_ppo_train_live(orc, ref_strict):
+    """train() of the real reference, compiled here, against the oracle on inputs the fixtures do not cover."""
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "identity"])
+    rs = np.random.RandomState(4)
+    for (N, T, B, E) in oracle.Reference.PPO_TRAIN_CASES:
+        ap = (rs.randn(4482) * 0.3).astype(np.float32)
+        ap[-1] = -0.4
+        cp = (rs.randn(4481) * 0.3).astype(np.float32)
+        runner = dict(states=np.zeros((N, 2), np.float32), episode_step=np.zeros(N, np.int32), truncated=np.ones(N, np.uint8),
+                      episode_return=np.zeros(N, np.float32))
+        ds = orc.pendulum_collect(shape, ap, runner, T, 20, rng=orc.new_rng(3))
+        ds[:, 10] = orc.mlp_evaluate(shape, cp, np.ascontiguousarray(ds[:, 0:3]))[:, 0]
+        n = N * T
+        adv, tgt = orc.gae(np.ascontiguousarray(ds[:n, 6]), np.ascontiguousarray(ds[:, 10]), np.ascontiguousarray(ds[:n, 7]).astype(np.uint8),
+                           np.ascontiguousarray(ds[:n, 8]).astype(np.uint8), N, T)
+        ds[:n, 11], ds[:n, 12] = adv, tgt
+        want = ref_strict.ppo_train(N, T, B, E, ap, cp, ds)
+        got = orc.ppo_train(shape, shape, ap, cp, ds, n, B, E)
+        for name, g, w in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got, want):
+            assert np.array_equal(g, w), (N, T, B, E, name)

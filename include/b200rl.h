@@ -276,6 +276,16 @@ int b200rl_collect_tables_host(uint32_t* rng_state_host, int n_envs, int n_steps
                                const uint8_t* truncated_host, int step_limit, float* reset_states_host, int n_reset_rounds,
                                int* rounds_used_host, float* noise_host);
 
+/* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
+ * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and
+ * target-value columns. b200rl_shuffle_permutation_host replays those draws on the host engine (advanced in place, as the reference
+ * would) and returns perm_host[i] = the original row that ends at position i; b200rl_permute_rows applies it on the device to the
+ * columns whose bit is set in column_mask (columns < 64): data[i][c] = old data[perm[i]][c]. scratch: b200rl_permute_rows_scratch_bytes. */
+int b200rl_shuffle_permutation_host(uint32_t* rng_state_host, int n_rows, int32_t* perm_host);
+size_t b200rl_permute_rows_scratch_bytes(int n_rows, unsigned long long column_mask);
+int b200rl_permute_rows(float* data, int ld, int n_rows, const int32_t* perm, unsigned long long column_mask, void* scratch, size_t scratch_bytes,
+                        b200rl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

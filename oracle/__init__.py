@@ -87,6 +87,9 @@ class Oracle:
         L.orc_reset_table.argtypes = [C.c_void_p, C.c_int, C.c_int, _i32p, _u8p, C.c_int, _f32p, C.c_int]
         L.orc_reset_table.restype = C.c_int
         L.orc_gae.argtypes = [_f32p, _f32p, _u8p, _u8p, _f32p, _f32p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
+        _u64p = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
+        L.orc_rng_uniform_int_stream.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
+        L.orc_shuffle_permutation.argtypes = [C.c_void_p, C.c_int, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
                                            C.c_void_p, C.c_int, _f32p, C.c_int]
         L.orc_pendulum_collect.restype = C.c_int
@@ -190,18 +193,36 @@ class Oracle:
             p, m, v = self.adam_update(p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
         return p, g, m, v, pre, out
 
+    SHUFFLED_COLUMNS = (0, 1, 2, 4, 5, 11, 12)      # observation, action, log-prob, advantage, target value (Pendulum layout)
+
+    def uniform_int_stream(self, seed, lo, hi):
+        lo, hi = np.ascontiguousarray(lo, np.uint64), np.ascontiguousarray(hi, np.uint64)
+        out = np.empty(lo.size, np.uint64)
+        self.lib.orc_rng_uniform_int_stream(seed, lo.size, lo, hi, out)
+        return out
+
+    def shuffle_permutation(self, rng, n):
+        """perm[i] = original row that the reference's epoch shuffle leaves at position i (engine `rng` advanced in place)."""
+        perm = np.empty(n, np.int32)
+        self.lib.orc_shuffle_permutation(rng, n, perm)
+        return perm
+
     def ppo_train(self, actor_shape, critic_shape, actor_params, critic_params, dataset, n_rows, batch, epochs,
-                  alpha=1e-3, beta_1=0.9, beta_2=0.999, eps=1e-7, eps_sqrt=1e-7):
+                  alpha=1e-3, beta_1=0.9, beta_2=0.999, eps=1e-7, eps_sqrt=1e-7, shuffle_rng=None):
         """The PPO update of rl/algorithms/ppo/operations_generic.h:96-336 without epoch shuffling, default parameters: per minibatch
         zero_gradient, actor forward, clipped-surrogate gradient (+ log_std gradient), actor backward, critic forward, MSE gradient with
         weight 0.5 against the target values, critic backward, one Adam step each. dataset = the [rows, 13] matrix of the on-policy
-        runner; actor_params = MLP arena + log_std. Returns (actor params, grads, first moment, critic params, grads, first moment)."""
+        runner; actor_params = MLP arena + log_std. shuffle_rng (from new_rng) switches the per-epoch row shuffle on (:127-158). Returns (actor params, grads, first moment, critic params, grads, first moment)."""
         na = actor_shape.num_params()
         ap, cp = actor_params.copy(), critic_params.copy()
         am, av, cm, cv = np.zeros_like(ap), np.zeros_like(ap), np.zeros_like(cp), np.zeros_like(cp)
         a_age = c_age = 1
         ag, cg = np.zeros_like(ap), np.zeros_like(cp)
         for _ in range(epochs):
+            if shuffle_rng is not None:             # SHUFFLE_EPOCH: in place on the caller's matrix, like the reference
+                perm = self.shuffle_permutation(shuffle_rng, n_rows)
+                cols = list(self.SHUFFLED_COLUMNS)
+                dataset[:n_rows, cols] = dataset[:n_rows][perm][:, cols]
             for b in range(n_rows // batch):
                 rows = dataset[b * batch:(b + 1) * batch]
                 obs = np.ascontiguousarray(rows[:, 0:3])
@@ -325,7 +346,9 @@ class Reference:
                                            _f32p, _f32p, _f32p, C.c_int]
         L.ref_pendulum_rollout.restype = C.c_int
         L.ref_gae.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _f32p, _f32p]
-        L.ref_ppo_train.argtypes = [C.c_int] * 4 + [_f32p] * 9
+        L.ref_ppo_train.argtypes = [C.c_int] * 5 + [C.c_uint32] + [_f32p] * 10
+        _u64p = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
+        L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
 
@@ -377,14 +400,24 @@ class Reference:
         return ds, runner
 
     PPO_TRAIN_CASES = ((64, 64, 4096, 1), (64, 64, 512, 2), (5, 37, 37, 3))      # (N, steps, minibatch, epochs)
+    PPO_TRAIN_SHUFFLE_CASES = ((64, 64, 512, 2), (5, 37, 37, 3))
 
-    def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset):
-        """The reference's train() on a given dataset matrix [(steps+1)*N, 13]; no shuffling. Returns the same tuple as Oracle.ppo_train."""
+    def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset, shuffle_seed=None):
+        """The reference's train() on a given dataset matrix [(steps+1)*N, 13]; SHUFFLE_EPOCH with an engine seeded by shuffle_seed, or
+        off (None). Returns the same tuple as Oracle.ppo_train plus the dataset matrix as train() leaves it."""
         outs = [np.empty(4482, np.float32) for _ in range(3)] + [np.empty(4481, np.float32) for _ in range(3)]
-        rc = self.lib.ref_ppo_train(N, steps, batch, epochs, actor_params, critic_params, np.ascontiguousarray(dataset, np.float32), *outs)
+        ds_out = np.empty(((steps + 1) * N, 13), np.float32)
+        rc = self.lib.ref_ppo_train(N, steps, batch, epochs, int(shuffle_seed is not None), shuffle_seed or 0, actor_params, critic_params,
+                                    np.ascontiguousarray(dataset, np.float32), *outs, ds_out)
         if rc != 0:
             raise KeyError("no such PPO train case")
-        return tuple(outs)
+        return tuple(outs) + (ds_out,)
+
+    def uniform_int_stream(self, seed, lo, hi):
+        lo, hi = np.ascontiguousarray(lo, np.uint64), np.ascontiguousarray(hi, np.uint64)
+        out = np.empty(lo.size, np.uint64)
+        self.lib.ref_rng_uniform_int(seed, lo.size, lo, hi, out)
+        return out
 
     def gae(self, rewards, all_values, terminated, truncated, N, steps):
         adv, tgt = np.empty(steps * N, np.float32), np.empty(steps * N, np.float32)

@@ -83,6 +83,39 @@ float orc_normal(orc_rng* r, float mean, float std){
     float ret = y * mult;
     return ret * std + mean;
 }
+/* std::uniform_int_distribution<T>(lo, hi) on mt19937 (random/operations_cpu.h:27-29), libstdc++ (GCC >= 11): for a range below
+ * 2^32 on a 32-bit generator this is Lemire's nearly divisionless method with a 64-bit product: one draw, redraw while the low half
+ * of draw * range falls below (2^32 - range) mod range; the result is the high half. A range of exactly 2^32 values returns the
+ * raw draw. Larger ranges (upscaling) do not occur on this path and are not restated. */
+uint64_t orc_uniform_int(orc_rng* r, uint64_t lo, uint64_t hi){
+    const uint64_t urange = hi - lo;
+    if(urange == 0xFFFFFFFFull) return lo + orc_rng_next(r);
+    const uint32_t erange = (uint32_t)(urange + 1);
+    uint64_t product = (uint64_t)orc_rng_next(r) * erange;
+    uint32_t low = (uint32_t)product;
+    if(low < erange){
+        const uint32_t threshold = (uint32_t)(-erange) % erange;
+        while(low < threshold){
+            product = (uint64_t)orc_rng_next(r) * erange;
+            low = (uint32_t)product;
+        }
+    }
+    return lo + (product >> 32);
+}
+void orc_rng_uniform_int_stream(uint32_t seed, int n, const uint64_t* lo, const uint64_t* hi, uint64_t* out){
+    orc_rng r; orc_rng_init(&r, seed);
+    for(int i = 0; i < n; i++) out[i] = orc_uniform_int(&r, lo[i], hi[i]);
+}
+/* Epoch shuffle of PPO train (rl/algorithms/ppo/operations_generic.h:127-158): for i = 0..n-1 draw j in [i, n-1] and swap rows i
+ * and j of the observation, action, advantage, log-prob and target-value columns. perm[i] = the ORIGINAL row that ends up at
+ * position i; the engine state advances exactly as in the reference (one draw per row, more on rejection). */
+void orc_shuffle_permutation(orc_rng* r, int n, int32_t* perm){
+    for(int i = 0; i < n; i++) perm[i] = i;
+    for(int i = 0; i < n; i++){
+        const int j = (int)orc_uniform_int(r, (uint64_t)i, (uint64_t)(n - 1));
+        const int32_t tmp = perm[i]; perm[i] = perm[j]; perm[j] = tmp;
+    }
+}
 void orc_rng_uniform_stream(uint32_t seed, int n, float lo, float hi, float* out){
     orc_rng r; orc_rng_init(&r, seed);
     for(int i = 0; i < n; i++) out[i] = orc_uniform_real(&r, lo, hi);

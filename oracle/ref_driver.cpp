@@ -399,20 +399,22 @@ static void collect_case(const float* actor_params, uint32_t seed, int n_collect
 // Actor = sequential<mlp_unconditional_stddev 3->64->64->1>, critic = sequential<mlp 3->64->64->1>, both ReLU / identity.
 // Outputs after the call: parameters, and the gradient and Adam first moment left by the LAST minibatch, actor (4482 = MLP arena +
 // log_std) and critic (4481).
-template <TI BATCH, TI EPOCHS>
+template <TI BATCH, TI EPOCHS, bool SHUFFLE>
 struct PpoTrainParameters: rlt::rl::algorithms::ppo::DefaultParameters<TYPE_POLICY, TI, BATCH>{
     static constexpr TI N_EPOCHS = EPOCHS;
-    static constexpr bool SHUFFLE_EPOCH = false;
+    static constexpr bool SHUFFLE_EPOCH = SHUFFLE;
 };
-template <TI N, TI STEPS, TI BATCH, TI EPOCHS>
-static void ppo_train_case(const float* actor_params, const float* critic_params, const float* dataset_in, float* actor_out, float* actor_grad, float* actor_m,
-                           float* critic_out, float* critic_grad, float* critic_m){
+// SHUFFLE: the reference's per-epoch in-place row shuffle (operations_generic.h:127-158) driven by the engine seeded with `seed`;
+// dataset_out receives the matrix as train() leaves it (rows of the shuffled columns permuted).
+template <TI N, TI STEPS, TI BATCH, TI EPOCHS, bool SHUFFLE>
+static void ppo_train_case(const float* actor_params, const float* critic_params, const float* dataset_in, uint32_t seed, float* actor_out, float* actor_grad, float* actor_m,
+                           float* critic_out, float* critic_grad, float* critic_m, float* dataset_out){
     using CAPABILITY = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
     using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, BATCH, 3>;
     using MLP_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::IDENTITY>;
     using ACTOR = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp_unconditional_stddev::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
     using CRITIC = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
-    using PARAMETERS = PpoTrainParameters<BATCH, EPOCHS>;
+    using PARAMETERS = PpoTrainParameters<BATCH, EPOCHS, SHUFFLE>;
     using PPO_SPEC = rlt::rl::algorithms::ppo::Specification<TYPE_POLICY, TI, PENDULUM, ACTOR, CRITIC, PARAMETERS>;
     using PPO = rlt::rl::algorithms::PPO<PPO_SPEC>;
     using PPO_BUFFERS = rlt::rl::algorithms::ppo::Buffers<rlt::rl::algorithms::ppo::BufferSpecification<PPO_SPEC>>;
@@ -421,6 +423,7 @@ static void ppo_train_case(const float* actor_params, const float* critic_params
     using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
     DEVICE device;
     RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    RNG train_rng; rlt::malloc(device, train_rng); rlt::init(device, train_rng, seed);
     PPO ppo; PPO_BUFFERS ppo_buffers; DATASET dataset; OPTIMIZER actor_optimizer, critic_optimizer;
     typename ACTOR::template Buffer<> actor_buffers; typename CRITIC::template Buffer<> critic_buffers;
     rlt::malloc(device, ppo); rlt::malloc(device, ppo_buffers); rlt::malloc(device, dataset); rlt::malloc(device, actor_optimizer); rlt::malloc(device, critic_optimizer);
@@ -432,7 +435,8 @@ static void ppo_train_case(const float* actor_params, const float* critic_params
     { const float* p = critic_params; auto& m = ppo.critic.content;
       load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
     for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < 13; k++) rlt::set(dataset.data, r, k, dataset_in[r * 13 + k]);
-    rlt::train(device, ppo, dataset, actor_optimizer, critic_optimizer, ppo_buffers, actor_buffers, critic_buffers, rng);
+    rlt::train(device, ppo, dataset, actor_optimizer, critic_optimizer, ppo_buffers, actor_buffers, critic_buffers, train_rng);
+    if(dataset_out) for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < 13; k++) dataset_out[r * 13 + k] = rlt::get(dataset.data, r, k);
     auto dump = [&](auto& m, float* params, float* grads, float* mom){
         store_layer(device, m.input_layer, params, PARAMS); store_layer(device, m.hidden_layers[0], params, PARAMS); store_layer(device, m.output_layer, params, PARAMS);
         store_layer(device, m.input_layer, grads, GRADS); store_layer(device, m.hidden_layers[0], grads, GRADS); store_layer(device, m.output_layer, grads, GRADS);
@@ -449,14 +453,22 @@ static void ppo_train_case(const float* actor_params, const float* critic_params
 
 extern "C" {
 
-int ref_ppo_train(int N, int steps, int batch, int epochs, const float* actor_params, const float* critic_params, const float* dataset_in,
-                  float* actor_out, float* actor_grad, float* actor_m, float* critic_out, float* critic_grad, float* critic_m){
-#define PPO_CASE(n, s, b, e) if(N == n && steps == s && batch == b && epochs == e){ ppo_train_case<n, s, b, e>(actor_params, critic_params, dataset_in, actor_out, actor_grad, actor_m, critic_out, critic_grad, critic_m); return 0; }
-    PPO_CASE(64, 64, 4096, 1)
-    PPO_CASE(64, 64, 512, 2)
-    PPO_CASE(5, 37, 37, 3)
+int ref_ppo_train(int N, int steps, int batch, int epochs, int shuffle, uint32_t seed, const float* actor_params, const float* critic_params, const float* dataset_in,
+                  float* actor_out, float* actor_grad, float* actor_m, float* critic_out, float* critic_grad, float* critic_m, float* dataset_out){
+#define PPO_CASE(n, s, b, e, sh) if(N == n && steps == s && batch == b && epochs == e && (shuffle != 0) == sh){ \
+        ppo_train_case<n, s, b, e, sh>(actor_params, critic_params, dataset_in, seed, actor_out, actor_grad, actor_m, critic_out, critic_grad, critic_m, dataset_out); return 0; }
+    PPO_CASE(64, 64, 4096, 1, false)
+    PPO_CASE(64, 64, 512, 2, false)
+    PPO_CASE(5, 37, 37, 3, false)
+    PPO_CASE(64, 64, 512, 2, true)
+    PPO_CASE(5, 37, 37, 3, true)
 #undef PPO_CASE
     return -1;
+}
+// std::uniform_int_distribution<TI>(lo, hi) as random/operations_cpu.h:27-29 drives it (TI = the CPU device's index type)
+void ref_rng_uniform_int(uint32_t seed, int n, const uint64_t* lo, const uint64_t* hi, uint64_t* out){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    for(int i = 0; i < n; i++) out[i] = rlt::random::uniform_int_distribution(device.random, (TI)lo[i], (TI)hi[i], rng);
 }
 
 int ref_collect(int N, int steps, int step_limit, int hidden_act, const float* actor_params, uint32_t seed, int n_collects, float* datasets,

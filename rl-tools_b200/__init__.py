@@ -111,6 +111,10 @@ def lib():
         L.b200rl_release_host_staging.argtypes = []
         L.b200rl_rng_init_host.argtypes = [vp, C.c_uint32]
         L.b200rl_reset_table_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i)]
+        L.b200rl_shuffle_permutation_host.argtypes = [vp, i, vp]
+        L.b200rl_permute_rows_scratch_bytes.argtypes = [i, C.c_uint64]
+        L.b200rl_permute_rows_scratch_bytes.restype = sz
+        L.b200rl_permute_rows.argtypes = [vp, i, i, vp, C.c_uint64, vp, sz, vp]
         L.b200rl_collect_tables_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i), vp]
         L.b200rl_pendulum_collect.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
@@ -368,3 +372,22 @@ def pendulum_collect(shape, params, log_std, states, episode_step, truncated, ep
                                             _ptr(episode_return), _ptr(reset_states), R, _ptr(noise), N, n_steps, step_limit, _ptr(dataset),
                                             dataset.stride(0), _ptr(error_flag), _stream()), "b200rl_pendulum_collect")
     return dataset
+
+
+def shuffle_permutation_host(rng_state, n_rows):
+    """The row permutation of one PPO epoch shuffle, drawn on the reference-compatible host engine (advanced in place): numpy int32[n_rows]."""
+    import numpy as np
+    perm = np.empty(n_rows, np.int32)
+    check(lib().b200rl_shuffle_permutation_host(C.c_void_p(rng_state.ctypes.data), n_rows, C.c_void_p(perm.ctypes.data)), "b200rl_shuffle_permutation_host")
+    return perm
+
+
+def permute_rows(data, n_rows, perm, columns):
+    """data[i, c] = old data[perm[i], c] for the given columns (in place on a 2-D CUDA tensor; perm = int32 CUDA tensor)."""
+    import torch
+    mask = 0
+    for c in columns:
+        mask |= 1 << int(c)
+    nbytes = lib().b200rl_permute_rows_scratch_bytes(n_rows, mask)
+    scratch = torch.empty(max(nbytes, 4), device=data.device, dtype=torch.uint8)
+    check(lib().b200rl_permute_rows(_ptr(data), data.stride(0), n_rows, _ptr(perm), mask, _ptr(scratch), nbytes, _stream()), "b200rl_permute_rows")

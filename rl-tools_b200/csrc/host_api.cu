@@ -234,6 +234,30 @@ int b200rl_collect_tables_host(uint32_t* rng, int n_envs, int n_steps, const int
     return B200RL_OK;
 }
 
+// std::uniform_int_distribution on mt19937 for ranges below 2^32 (libstdc++: nearly divisionless bounded draw with a 64-bit product)
+static uint32_t uniform_int_below(uint32_t* st, uint32_t range){
+    uint64_t product = (uint64_t)mt_next(st) * range;
+    uint32_t low = (uint32_t)product;
+    if(low < range){
+        const uint32_t threshold = (uint32_t)(0u - range) % range;
+        while(low < threshold){
+            product = (uint64_t)mt_next(st) * range;
+            low = (uint32_t)product;
+        }
+    }
+    return (uint32_t)(product >> 32);
+}
+
+int b200rl_shuffle_permutation_host(uint32_t* rng, int n_rows, int32_t* perm_host){
+    if(!rng || !perm_host || n_rows < 0) return B200RL_ERR_INVALID_ARGUMENT;
+    for(int i = 0; i < n_rows; i++) perm_host[i] = i;
+    for(int i = 0; i < n_rows; i++){              // rl/algorithms/ppo/operations_generic.h:127-158: swap row i with a row drawn from [i, n-1]
+        const int j = i + (int)uniform_int_below(rng, (uint32_t)(n_rows - i));
+        const int32_t tmp = perm_host[i]; perm_host[i] = perm_host[j]; perm_host[j] = tmp;
+    }
+    return B200RL_OK;
+}
+
 int b200rl_release_host_staging(void){ g_staging.release(); return B200RL_OK; }
 
 int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* actor_params_host, float* states_host,

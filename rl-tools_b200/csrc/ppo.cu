@@ -176,3 +176,42 @@ int b200rl_ppo_policy_gradient(const float* current_actions, int ld_current, con
 }
 
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Epoch shuffle: apply a row permutation to selected columns of the dataset matrix (gather into scratch, write back).
+// ---------------------------------------------------------------------------------------------------------------
+namespace b200rl {
+template <bool GATHER>
+__global__ void permute_rows_kernel(float* __restrict__ data, int ld, int n_rows, const int32_t* __restrict__ perm, unsigned long long mask, int n_cols,
+                                    float* __restrict__ scratch){
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if(idx >= (long long)n_rows * n_cols) return;
+    const int row = (int)(idx / n_cols), c = (int)(idx % n_cols);
+    // column index of the c-th set bit of the mask
+    unsigned long long m = mask;
+    for(int k = 0; k < c; k++) m &= m - 1;
+    const int col = __ffsll((long long)m) - 1;
+    if(GATHER) scratch[idx] = data[(size_t)perm[row] * ld + col];
+    else data[(size_t)row * ld + col] = scratch[idx];
+}
+}  // namespace b200rl
+
+extern "C" size_t b200rl_permute_rows_scratch_bytes(int n_rows, unsigned long long column_mask){
+    return sizeof(float) * (size_t)(n_rows > 0 ? n_rows : 0) * (size_t)__builtin_popcountll(column_mask);
+}
+
+extern "C" int b200rl_permute_rows(float* data, int ld, int n_rows, const int32_t* perm, unsigned long long column_mask, void* scratch, size_t scratch_bytes,
+                                   b200rl_stream_t stream){
+    const int n_cols = __builtin_popcountll(column_mask);
+    if(!data || !perm || n_rows < 0 || ld < 1 || (ld < 64 && (column_mask >> ld) != 0)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_rows == 0 || n_cols == 0) return B200RL_OK;
+    if(!scratch || scratch_bytes < b200rl_permute_rows_scratch_bytes(n_rows, column_mask)) return B200RL_ERR_INVALID_ARGUMENT;
+    const long long total = (long long)n_rows * n_cols;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    b200rl::permute_rows_kernel<true><<<blocks, threads, 0, s>>>(data, ld, n_rows, perm, column_mask, n_cols, static_cast<float*>(scratch));
+    b200rl::permute_rows_kernel<false><<<blocks, threads, 0, s>>>(data, ld, n_rows, perm, column_mask, n_cols, static_cast<float*>(scratch));
+    B200RL_LAUNCH_CHECK("permute_rows");
+    return B200RL_OK;
+}

@@ -4,7 +4,7 @@
 `estimate_generalized_advantages` and `train` follow rl/algorithms/ppo/operations_generic.h:59-95 and :96-336 with the default
 parameters of rl/algorithms/ppo/ppo.h:13-38. Everything runs on the GPU on torch CUDA tensors; there is no CPU path.
 """
-from . import gae as _gae, mse_gradient as _mse_gradient, ppo_policy_gradient as _ppo_policy_gradient
+from . import gae as _gae, mse_gradient as _mse_gradient, ppo_policy_gradient as _ppo_policy_gradient, permute_rows as _permute_rows, shuffle_permutation_host as _shuffle_permutation_host
 
 
 class DatasetLayout:
@@ -48,13 +48,21 @@ def evaluate_values(critic, dataset, layout):
 
 
 def train(actor, critic, dataset, layout, n_rows, batch_size, n_epochs=10, epsilon_clip=0.2, entropy_coefficient=0.01, advantage_epsilon=1e-8,
-          normalize_advantage=True, learn_action_std=True):
-    """n_epochs x (n_rows // batch_size) minibatch updates in dataset order (the reference's SHUFFLE_EPOCH = false): zero_gradient,
+          normalize_advantage=True, learn_action_std=True, shuffle_rng_state=None):
+    """n_epochs x (n_rows // batch_size) minibatch updates. shuffle_rng_state (from rng_init_host) switches the reference's SHUFFLE_EPOCH
+    on: before every epoch the observation / action / log-prob / advantage / target-value columns of the dataset matrix are permuted in
+    place with the permutation the reference's engine would produce (:127-158); None keeps dataset order. Per minibatch: zero_gradient,
     actor forward, clipped-surrogate gradient (+ log_std gradient), actor backward, critic forward, 0.5-weighted MSE gradient against
     the target values, critic backward, one Adam step each. `actor` is an Mlp with extra_params = action_dim (the log_std behind the
     layers), `critic` an Mlp with one output; both built for batch_size rows."""
     assert actor.batch == batch_size and critic.batch == batch_size and actor.n_extra == layout.action_dim
+    import torch
+    shuffled = list(range(layout.observations.start, layout.observations.stop)) + list(range(layout.actions.start, layout.actions.stop)) + \
+        [layout.action_log_probs, layout.advantages, layout.target_values]
     for _ in range(n_epochs):
+        if shuffle_rng_state is not None:
+            perm = torch.from_numpy(_shuffle_permutation_host(shuffle_rng_state, n_rows)).to(dataset.device)
+            _permute_rows(dataset, n_rows, perm, shuffled)
         for b in range(n_rows // batch_size):
             rows = dataset[b * batch_size:(b + 1) * batch_size]
             obs = rows[:, layout.observations]

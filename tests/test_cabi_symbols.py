@@ -78,6 +78,17 @@ def test_collect_tables_match_oracle_stream(lib, orc):
     assert used == 1 and np.array_equal(table, want_table) and np.array_equal(noise, want_noise)
 
 
+def test_shuffle_permutation_matches_oracle_stream(lib, orc):
+    """Product-side uniform_int_distribution / Fisher-Yates order of the PPO epoch shuffle vs the oracle's restatement, two epochs on one
+    engine; every result is a permutation."""
+    state, rng = lib.rng_init_host(21), orc.new_rng(21)
+    for n in (4096, 185, 1):
+        for _ in range(2):
+            perm = lib.shuffle_permutation_host(state, n)
+            assert np.array_equal(perm, orc.shuffle_permutation(rng, n))
+            assert np.array_equal(np.sort(perm), np.arange(n))
+
+
 def test_product_does_not_reference_the_oracle():
     """The shipped package must never import or link the CPU oracle."""
     pkg = os.path.join(ROOT, "rl-tools_b200")

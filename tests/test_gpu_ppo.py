@@ -176,3 +176,37 @@ def test_gae_and_values_in_place_on_the_dataset_matrix(lib, orc, torch):
     got = d.cpu().numpy()
     assert np.array_equal(got[:n, 11], adv) and np.array_equal(got[:n, 12], tgt)
     assert np.array_equal(got[:, :10], ds[:, :10])
+
+
+@pytest.mark.parametrize("case", [1, 2])
+def test_ppo_train_with_epoch_shuffle_vs_reference_golden(lib, torch, case):
+    """SHUFFLE_EPOCH = true through rl_tools_b200.ppo.train: the dataset matrix after the call equals the reference's bit for bit (the
+    permutation comes from the reference-compatible host engine, the device only moves rows), parameters within 1e-5 |ref| + 2e-6."""
+    from rl_tools_b200 import ppo
+    fix = np.load(os.path.join(GOLDEN, "ppo_train.npz"))
+    N, steps, batch, epochs = mg.PPO_TRAIN_CASES[case]
+    pa, pc = mg.ppo_train_params(case)
+    dims, acts = [64, 64, 1], ["relu", "relu", "identity"]
+    actor, critic = lib.Mlp(3, dims, acts, batch, extra_params=1), lib.Mlp(3, dims, acts, batch)
+    actor.params.copy_(dev(torch, pa)); critic.params.copy_(dev(torch, pc))
+    dataset = dev(torch, fix[f"dataset_{case}"])
+    ppo.train(actor, critic, dataset, ppo.DatasetLayout(3, 1), N * steps, batch, n_epochs=epochs, shuffle_rng_state=lib.rng_init_host(mg.PPO_SHUFFLE_SEED))
+    assert np.array_equal(dataset.cpu().numpy(), fix[f"shuffled_dataset_{case}"])
+    for name, got in (("actor", actor.params), ("critic", critic.params)):
+        want = fix[f"shuffled_{name}_{case}"]
+        err = np.abs(got.cpu().numpy() - want)
+        assert np.all(err <= 2e-6 + 1e-5 * np.abs(want)), f"{name}: max err {err.max():.3e}"
+
+
+def test_permute_rows_on_a_wide_matrix(lib, torch):
+    """Row gather on selected columns of a 51-column matrix (the Ant dataset's width), other columns untouched."""
+    rows, D = 5000, 51
+    g = torch.Generator(device="cuda"); g.manual_seed(1)
+    data = torch.randn((rows + 64, D), device="cuda", generator=g)
+    before = data.clone()
+    perm = torch.randperm(rows, device="cuda", generator=g).to(torch.int32)
+    cols = list(range(0, 27)) + list(range(35, 43)) + [43, 49, 50]
+    lib.permute_rows(data, rows, perm, cols)
+    rest = [c for c in range(D) if c not in cols]
+    assert torch.equal(data[:rows][:, cols], before[perm.long()][:, cols])
+    assert torch.equal(data[:rows][:, rest], before[:rows][:, rest]) and torch.equal(data[rows:], before[rows:])

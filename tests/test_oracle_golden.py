@@ -168,3 +168,25 @@ def test_ppo_train_matches_reference(orc, case):
     got = orc.ppo_train(shape, shape, actor, critic, fix[f"dataset_{case}"], N * steps, batch, epochs)
     for name, g in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got):
         assert np.array_equal(g, fix[f"{name}_{case}"]), name
+
+
+def test_uniform_int_distribution_matches_reference(orc):
+    fix = np.load(os.path.join(GOLDEN, "ppo_train.npz"))
+    lo, hi = mg.uniform_int_ranges()
+    assert np.array_equal(orc.uniform_int_stream(mg.PPO_SHUFFLE_SEED, lo, hi), fix["uniform_int"])
+
+
+@pytest.mark.parametrize("case", [1, 2])
+def test_ppo_train_with_epoch_shuffle_matches_reference(orc, case):
+    """SHUFFLE_EPOCH = true: the in-place Fisher-Yates row swaps of the observation / action / log-prob / advantage / target columns
+    driven by std::uniform_int_distribution, then the same minibatch updates. Dataset after train() and all parameters bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "ppo_train.npz"))
+    N, steps, batch, epochs = mg.PPO_TRAIN_CASES[case]
+    actor, critic = mg.ppo_train_params(case)
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "identity"])
+    ds = fix[f"dataset_{case}"].copy()
+    got = orc.ppo_train(shape, shape, actor, critic, ds, N * steps, batch, epochs, shuffle_rng=orc.new_rng(mg.PPO_SHUFFLE_SEED))
+    assert np.array_equal(ds, fix[f"shuffled_dataset_{case}"])
+    assert not np.array_equal(ds, fix[f"dataset_{case}"])
+    for name, g in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got):
+        assert np.array_equal(g, fix[f"shuffled_{name}_{case}"]), name

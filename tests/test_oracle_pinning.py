@@ -93,3 +93,21 @@ def test_ppo_train_live(orc, ref_strict):
         got = orc.ppo_train(shape, shape, ap, cp, ds, n, B, E)
         for name, g, w in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got, want):
             assert np.array_equal(g, w), (N, T, B, E, name)
+
+
+def test_uniform_int_and_shuffled_train_live(orc, ref_strict):
+    rs = np.random.RandomState(9)
+    lo = rs.randint(0, 5000, 30000).astype(np.uint64)
+    hi = lo + rs.choice([0, 1, 6, 7, 8, 1000, 2 ** 20 + 1, 2 ** 32 - 1], 30000).astype(np.uint64)
+    assert np.array_equal(orc.uniform_int_stream(3, lo, hi), ref_strict.uniform_int_stream(3, lo, hi))
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "identity"])
+    for (N, T, B, E) in oracle.Reference.PPO_TRAIN_SHUFFLE_CASES:
+        ap = (rs.randn(4482) * 0.3).astype(np.float32)
+        cp = (rs.randn(4481) * 0.3).astype(np.float32)
+        ds = (rs.randn((T + 1) * N, 13) * 0.5).astype(np.float32)           # train() consumes any matrix
+        want = ref_strict.ppo_train(N, T, B, E, ap, cp, ds, shuffle_seed=77)
+        mine = ds.copy()
+        got = orc.ppo_train(shape, shape, ap, cp, mine, N * T, B, E, shuffle_rng=orc.new_rng(77))
+        assert np.array_equal(mine, want[6])
+        for g, w in zip(got, want[:6]):
+            assert np.array_equal(g, w)

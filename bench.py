@@ -295,6 +295,161 @@ def run_collect(args):
         dist.destroy_process_group()
 
 
+def run_ppo_update(args):
+    """Secondary line: the PPO update on the Ant shapes of the PPO configuration -- observation 27, actor 27 -> 64 -> 64 -> 8 tanh +
+    log_std, critic 27 -> 64 -> 64 -> 1, 64 envs x 1024 steps, GAE (gamma 0.99, lambda 0.95), minibatch 2048, 10 epochs with the
+    reference's epoch shuffle (permutation drawn on the host engine inside the timed region). One step = GAE + train() over the whole
+    dataset = 320 minibatch updates; value = minibatch samples per second. Single GPU (replicas only)."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from rl_tools_b200 import ppo
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    OBS, ACT, N, T, B, E = 27, 8, 64, 1024, 2048, 10
+    layout = ppo.DatasetLayout(OBS, ACT)
+    g = torch.Generator(device=dev); g.manual_seed(5)
+    rows = (T + 1) * N
+    acts = ["tanh", "tanh", "identity"]
+    actor, critic = pkg.Mlp(OBS, [64, 64, ACT], acts, B, extra_params=ACT), pkg.Mlp(OBS, [64, 64, 1], acts, B)
+    init = {}
+    for net, dims in ((actor, (64, 64, ACT)), (critic, (64, 64, 1))):
+        off, fan_in = 0, OBS
+        for d in dims:
+            n = d * fan_in + d
+            net.params[off:off + n] = (torch.rand(n, device=dev, generator=g) * 2 - 1) / fan_in ** 0.5
+            off += n; fan_in = d
+        init[net] = net.params.clone()
+    actor.extra("params").fill_(float(np.log(0.5)))
+    init[actor] = actor.params.clone()
+    base = torch.zeros((rows, layout.data_dim), device=dev)
+    base[:, layout.observations] = torch.randn((rows, OBS), device=dev, generator=g)
+    base[:, layout.actions_mean] = 0.3 * torch.randn((rows, ACT), device=dev, generator=g)
+    base[:, layout.actions] = base[:, layout.actions_mean] + 0.5 * torch.randn((rows, ACT), device=dev, generator=g)
+    base[:, layout.action_log_probs] = -5.5 + 0.8 * torch.randn(rows, device=dev, generator=g)
+    base[:, layout.rewards] = torch.randn(rows, device=dev, generator=g)
+    base[:, layout.truncated] = (torch.rand(rows, device=dev, generator=g) < 1e-3).float()
+    dataset = base.clone()
+    rng_state = pkg.rng_init_host(1)
+
+    def step():
+        dataset.copy_(base)
+        for net in (actor, critic):
+            net.params.copy_(init[net]); net.reset_optimizer_state()
+        e0.record()
+        ppo.evaluate_values(critic, dataset, layout)
+        ppo.estimate_generalized_advantages(dataset, layout, N, T)
+        ppo.train(actor, critic, dataset, layout, N * T, B, n_epochs=E, shuffle_rng_state=rng_state)
+        e1.record()
+
+    steps, warmup = min(args.steps, 5), 3
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(steps):
+        step(); torch.cuda.synchronize(); ms.append(e0.elapsed_time(e1))
+    ms = sum(ms) / len(ms)
+    samples = N * T * E
+    flop_per_sample = 3 * 2 * ((OBS * 64 + 64 * 64 + 64 * ACT) + (OBS * 64 + 64 * 64 + 64))       # forward + both backward contractions, actor + critic
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        if os.path.exists(oracle.REF_FAST_SO):
+            os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
+            ref = oracle.Reference("fast")
+            na, nc = OBS * 64 + 64 + 64 * 64 + 64 + 64 * ACT + ACT + ACT, OBS * 64 + 64 + 64 * 64 + 64 + 64 + 1
+            sec = ref.ppo_train(N, T, B, 1, init[actor].cpu().numpy()[:na], init[critic].cpu().numpy()[:nc], base.cpu().numpy(), shuffle_seed=1, env="ant", want_seconds=True)[7]
+            cpu = {"value": N * T / sec, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
+                   "sample": "one epoch (32 minibatches of 2048) of the reference's train() with the epoch shuffle, CPU_OPENBLAS build"}
+    peaks = measured_peaks()
+    tflops = flop_per_sample * samples / (ms * 1e-3) / 1e12
+    launches = steps * (E * (N * T // B) * 24 + E * 2 + 70)
+    print(json.dumps({"metric": "PPO update minibatch-samples/s", "value": samples / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "ppo_update_ant_shapes_obs27_act8_64envx1024step_mb2048_10epochs_shuffled", "updates_per_step": E * (N * T // B),
+                                 "l2": "the dataset (13 MB) fits L2: this workload is launch- and latency-bound", "parallelism": "single GPU"},
+                      "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
+                                   "peak_source": peaks["source"] + " bf16 dense (burst)"},
+                      "cpu_baseline": cpu, "gpu_launches": launches}))
+
+
+def run_critic_train(args):
+    """Secondary line: the SAC critic regression step of the off-policy configuration -- Q-net 4 -> 256 -> 256 -> 1 ReLU, batch 256,
+    N(0,1) inputs and targets, zero_gradient + forward + MSE gradient + backward + Adam, 1000 steps per timed call, eager launches and
+    replayed as a CUDA graph of the same C-ABI calls. value = training samples per second (graph replay). Single GPU."""
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, STEPS = 256, 1000
+    g = torch.Generator(device=dev); g.manual_seed(3)
+    net = pkg.Mlp(4, [256, 256, 1], ["relu", "relu", "identity"], B)
+    off, fan_in = 0, 4
+    for d in (256, 256, 1):
+        n = d * fan_in + d
+        net.params[off:off + n] = (torch.rand(n, device=dev, generator=g) * 2 - 1) / fan_in ** 0.5
+        off += n; fan_in = d
+    x, y = torch.randn((B, 4), device=dev, generator=g), torch.randn((B, 1), device=dev, generator=g)
+    d_out = net.d_out_buffer()
+
+    def train_step():
+        net.zero_gradient()
+        out = net.forward(x)
+        pkg.mse_gradient(out, y, 1.0, d_a=d_out)
+        net.backward(x, d_out)
+        net.step()
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(20):
+            train_step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(10):
+            train_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = min(args.steps, 10)
+    def timed(fn):
+        fn(); torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+    ms_eager = timed(lambda: [train_step() for _ in range(STEPS)])
+    ms_graph = timed(lambda: [graph.replay() for _ in range(STEPS // 10)])
+    flop = 3 * 2 * B * (4 * 256 + 256 * 256 + 256)
+    cpu = None
+    if not args.no_cpu_baseline:
+        import numpy as np
+        import oracle
+        if os.path.exists(oracle.REF_FAST_SO):
+            os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
+            ref = oracle.Reference("fast")
+            res = ref.mlp_run("c3_critic", net.params.cpu().numpy(), x.cpu().numpy(), y.cpu().numpy(), 2, 200)
+            cpu = {"value": 200 * B / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
+                   "sample": "200 train steps (zero_gradient, forward, mse gradient, backward, Adam) of the reference, CPU_OPENBLAS build"}
+    peaks = measured_peaks()
+    tflops = flop * STEPS / (ms_graph * 1e-3) / 1e12
+    print(json.dumps({"metric": "SAC-critic train samples/s (batch 256)", "value": STEPS * B / (ms_graph * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": reps,
+                      "warmup": 1, "ms_per_step": ms_graph, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "critic_train_4-256-256-1_batch256_x1000steps", "us_per_train_step_graph": ms_graph, "us_per_train_step_eager": ms_eager,
+                                 "l2": "working set (1 MB) is L2-resident by design: latency-bound", "parallelism": "single GPU"},
+                      "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
+                                   "peak_source": peaks["source"] + " bf16 dense (burst)"},
+                      "cpu_baseline": cpu, "gpu_launches": reps * STEPS * 15}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -307,9 +462,10 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect"],
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train"],
                     help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
-                         "collect = secondary line: on-policy (PPO) collect into the dataset matrix")
+                         "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
+                         "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
     ap.add_argument("--collect-steps", type=int, default=64, help="collect: steps per environment per call")
     ap.add_argument("--train-rows", type=int, default=1 << 24, help="mlp_train: total input rows over all GPUs")
     args = ap.parse_args()
@@ -317,6 +473,10 @@ def main():
         return run_mlp_train(args)
     if args.workload == "collect":
         return run_collect(args)
+    if args.workload == "ppo_update":
+        return run_ppo_update(args)
+    if args.workload == "critic_train":
+        return run_critic_train(args)
     if args.impl == "reference":
         return run_reference(args)
     if not args.allow_short_warmup:

@@ -193,7 +193,12 @@ class Oracle:
             p, m, v = self.adam_update(p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
         return p, g, m, v, pre, out
 
-    SHUFFLED_COLUMNS = (0, 1, 2, 4, 5, 11, 12)      # observation, action, log-prob, advantage, target value (Pendulum layout)
+    @staticmethod
+    def dataset_columns(obs_dim, action_dim):
+        """Column indices of the on-policy dataset matrix (rl/components/on_policy_runner/on_policy_runner.h:38-72, symmetric observations)."""
+        o, a = obs_dim, action_dim
+        return dict(obs=slice(0, o), mean=slice(o, o + a), action=slice(o + a, o + 2 * a), log_prob=o + 2 * a, reward=o + 2 * a + 1, terminated=o + 2 * a + 2,
+                    truncated=o + 2 * a + 3, reset=o + 2 * a + 4, value=o + 2 * a + 5, advantage=o + 2 * a + 6, target=o + 2 * a + 7, dim=o + 2 * a + 8)
 
     def uniform_int_stream(self, seed, lo, hi):
         lo, hi = np.ascontiguousarray(lo, np.uint64), np.ascontiguousarray(hi, np.uint64)
@@ -209,32 +214,35 @@ class Oracle:
 
     def ppo_train(self, actor_shape, critic_shape, actor_params, critic_params, dataset, n_rows, batch, epochs,
                   alpha=1e-3, beta_1=0.9, beta_2=0.999, eps=1e-7, eps_sqrt=1e-7, shuffle_rng=None):
-        """The PPO update of rl/algorithms/ppo/operations_generic.h:96-336 without epoch shuffling, default parameters: per minibatch
-        zero_gradient, actor forward, clipped-surrogate gradient (+ log_std gradient), actor backward, critic forward, MSE gradient with
-        weight 0.5 against the target values, critic backward, one Adam step each. dataset = the [rows, 13] matrix of the on-policy
-        runner; actor_params = MLP arena + log_std. shuffle_rng (from new_rng) switches the per-epoch row shuffle on (:127-158). Returns (actor params, grads, first moment, critic params, grads, first moment)."""
+        """The PPO update of rl/algorithms/ppo/operations_generic.h:96-336, default parameters: per minibatch zero_gradient, actor
+        forward, clipped-surrogate gradient (+ log_std gradient), actor backward, critic forward, MSE gradient with weight 0.5 against
+        the target values, critic backward, one Adam step each. dataset = the [rows, obs + 2 act + 8] matrix of the on-policy runner;
+        actor_params = MLP arena + log_std[act]. shuffle_rng (from new_rng) switches the per-epoch row shuffle on (:127-158): observation,
+        action, advantage, log-prob and target-value columns, in place. Returns (actor params, grads, first moment, critic ...)."""
         na = actor_shape.num_params()
+        A = actor_shape.dims[actor_shape.n_layers - 1]
+        col = self.dataset_columns(actor_shape.input_dim, A)
+        shuffled = list(range(col["obs"].start, col["obs"].stop)) + list(range(col["action"].start, col["action"].stop)) + [col["log_prob"], col["advantage"], col["target"]]
         ap, cp = actor_params.copy(), critic_params.copy()
         am, av, cm, cv = np.zeros_like(ap), np.zeros_like(ap), np.zeros_like(cp), np.zeros_like(cp)
         a_age = c_age = 1
         ag, cg = np.zeros_like(ap), np.zeros_like(cp)
         for _ in range(epochs):
-            if shuffle_rng is not None:             # SHUFFLE_EPOCH: in place on the caller's matrix, like the reference
+            if shuffle_rng is not None:
                 perm = self.shuffle_permutation(shuffle_rng, n_rows)
-                cols = list(self.SHUFFLED_COLUMNS)
-                dataset[:n_rows, cols] = dataset[:n_rows][perm][:, cols]
+                dataset[:n_rows, shuffled] = dataset[:n_rows][perm][:, shuffled]
             for b in range(n_rows // batch):
                 rows = dataset[b * batch:(b + 1) * batch]
-                obs = np.ascontiguousarray(rows[:, 0:3])
+                obs = np.ascontiguousarray(rows[:, col["obs"]])
                 pre, out = self.mlp_forward(actor_shape, ap[:na], obs)
-                current = np.ascontiguousarray(out[-batch:].reshape(batch, 1))
-                d_actions, d_log_std = self.ppo_policy_gradient(current, np.ascontiguousarray(rows[:, 4:5]), ap[na:], np.ascontiguousarray(rows[:, 5]),
-                                                                np.ascontiguousarray(rows[:, 11]))
+                current = np.ascontiguousarray(out[-batch * A:].reshape(batch, A))
+                d_actions, d_log_std = self.ppo_policy_gradient(current, np.ascontiguousarray(rows[:, col["action"]]), ap[na:], np.ascontiguousarray(rows[:, col["log_prob"]]),
+                                                                np.ascontiguousarray(rows[:, col["advantage"]]))
                 g_mlp, _ = self.mlp_backward(actor_shape, ap[:na], np.zeros(na, np.float32), obs, pre, out, d_actions)
                 ag = np.concatenate([g_mlp, d_log_std]).astype(np.float32)
                 pre, out = self.mlp_forward(critic_shape, cp, obs)
                 values = np.ascontiguousarray(out[-batch:].reshape(batch, 1))
-                d_values = self.mse_gradient(values, np.ascontiguousarray(rows[:, 12:13]), 0.5)
+                d_values = self.mse_gradient(values, np.ascontiguousarray(rows[:, col["target"]:col["target"] + 1]), 0.5)
                 cg, _ = self.mlp_backward(critic_shape, cp, np.zeros_like(cp), obs, pre, out, d_values)
                 c1, c2, a_age = self.adam_bias_correction(beta_1, beta_2, a_age)
                 ap, am, av = self.adam_update(ap, ag, am, av, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
@@ -346,7 +354,7 @@ class Reference:
                                            _f32p, _f32p, _f32p, C.c_int]
         L.ref_pendulum_rollout.restype = C.c_int
         L.ref_gae.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _f32p, _f32p]
-        L.ref_ppo_train.argtypes = [C.c_int] * 5 + [C.c_uint32] + [_f32p] * 10
+        L.ref_ppo_train.argtypes = [C.c_int] * 6 + [C.c_uint32] + [_f32p] * 10 + [C.POINTER(C.c_double)]
         _u64p = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
         L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
@@ -402,16 +410,24 @@ class Reference:
     PPO_TRAIN_CASES = ((64, 64, 4096, 1), (64, 64, 512, 2), (5, 37, 37, 3))      # (N, steps, minibatch, epochs)
     PPO_TRAIN_SHUFFLE_CASES = ((64, 64, 512, 2), (5, 37, 37, 3))
 
-    def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset, shuffle_seed=None):
-        """The reference's train() on a given dataset matrix [(steps+1)*N, 13]; SHUFFLE_EPOCH with an engine seeded by shuffle_seed, or
-        off (None). Returns the same tuple as Oracle.ppo_train plus the dataset matrix as train() leaves it."""
-        outs = [np.empty(4482, np.float32) for _ in range(3)] + [np.empty(4481, np.float32) for _ in range(3)]
-        ds_out = np.empty(((steps + 1) * N, 13), np.float32)
-        rc = self.lib.ref_ppo_train(N, steps, batch, epochs, int(shuffle_seed is not None), shuffle_seed or 0, actor_params, critic_params,
-                                    np.ascontiguousarray(dataset, np.float32), *outs, ds_out)
+    PPO_TRAIN_ANT_CASES = ((64, 1024, 2048, 1, False), (64, 1024, 2048, 1, True), (64, 1024, 2048, 10, True))   # + shuffle flag; env="ant"
+
+    def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset, shuffle_seed=None, env="pendulum", want_seconds=False):
+        """The reference's train() on a given dataset matrix [(steps+1)*N, obs + 2 act + 8]; SHUFFLE_EPOCH with an engine seeded by
+        shuffle_seed, or off (None). env = "pendulum" (3 / 1, ReLU) or "ant" (27 / 8, tanh). Returns the same tuple as Oracle.ppo_train plus
+        the dataset matrix as train() leaves it (plus train()'s wall time if want_seconds)."""
+        obs, act = (3, 1) if env == "pendulum" else (27, 8)
+        n_critic = obs * 64 + 64 + 64 * 64 + 64 + 64 + 1
+        n_actor = obs * 64 + 64 + 64 * 64 + 64 + 64 * act + act + act
+        assert actor_params.size == n_actor and critic_params.size == n_critic and dataset.shape == ((steps + 1) * N, obs + 2 * act + 8)
+        outs = [np.empty(n_actor, np.float32) for _ in range(3)] + [np.empty(n_critic, np.float32) for _ in range(3)]
+        ds_out = np.empty(dataset.shape, np.float32)
+        seconds = C.c_double(0)
+        rc = self.lib.ref_ppo_train(0 if env == "pendulum" else 1, N, steps, batch, epochs, int(shuffle_seed is not None), shuffle_seed or 0, actor_params,
+                                    critic_params, np.ascontiguousarray(dataset, np.float32), *outs, ds_out, C.byref(seconds))
         if rc != 0:
             raise KeyError("no such PPO train case")
-        return tuple(outs) + (ds_out,)
+        return tuple(outs) + (ds_out,) + ((seconds.value,) if want_seconds else ())
 
     def uniform_int_stream(self, seed, lo, hi):
         lo, hi = np.ascontiguousarray(lo, np.uint64), np.ascontiguousarray(hi, np.uint64)

@@ -406,20 +406,35 @@ struct PpoTrainParameters: rlt::rl::algorithms::ppo::DefaultParameters<TYPE_POLI
 };
 // SHUFFLE: the reference's per-epoch in-place row shuffle (operations_generic.h:127-158) driven by the engine seeded with `seed`;
 // dataset_out receives the matrix as train() leaves it (rows of the shuffled columns permuted).
-template <TI N, TI STEPS, TI BATCH, TI EPOCHS, bool SHUFFLE>
+// Shapes of the Ant PPO configuration (observation 27, action 8) as a type: train() and the dataset only read these constants.
+struct AntLike{
+    struct Observation{ static constexpr TI DIM = 27; };
+    using ObservationPrivileged = Observation;
+    static constexpr TI ACTION_DIM = 8;
+    static constexpr TI N_AGENTS = 1;
+    static constexpr TI EPISODE_STEP_LIMIT = 1000;
+    struct Parameters{}; struct State{};
+};
+// Generic in the environment type: the dataset has OBS + 2 * ACT + 8 columns, the actor arena is the MLP OBS -> 64 -> 64 -> ACT followed
+// by log_std[ACT], the critic OBS -> 64 -> 64 -> 1. seconds (may be null) receives the wall time of train() alone.
+template <typename ENV, act::ActivationFunction HACT, TI N, TI STEPS, TI BATCH, TI EPOCHS, bool SHUFFLE>
 static void ppo_train_case(const float* actor_params, const float* critic_params, const float* dataset_in, uint32_t seed, float* actor_out, float* actor_grad, float* actor_m,
-                           float* critic_out, float* critic_grad, float* critic_m, float* dataset_out){
+                           float* critic_out, float* critic_grad, float* critic_m, float* dataset_out, double* seconds){
+    constexpr TI OBS = ENV::Observation::DIM, ACT = ENV::ACTION_DIM, D = OBS + 2 * ACT + 8;
+    constexpr TI N_ACTOR = OBS * 64 + 64 + 64 * 64 + 64 + 64 * ACT + ACT;
     using CAPABILITY = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
-    using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, BATCH, 3>;
-    using MLP_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::IDENTITY>;
-    using ACTOR = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp_unconditional_stddev::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
-    using CRITIC = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
+    using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, BATCH, OBS>;
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, ACT, 3, 64, HACT, act::IDENTITY>;
+    using CRITIC_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, HACT, act::IDENTITY>;
+    using ACTOR = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp_unconditional_stddev::BindConfiguration<ACTOR_CONFIG>>, INPUT_SHAPE>;
+    using CRITIC = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<CRITIC_CONFIG>>, INPUT_SHAPE>;
     using PARAMETERS = PpoTrainParameters<BATCH, EPOCHS, SHUFFLE>;
-    using PPO_SPEC = rlt::rl::algorithms::ppo::Specification<TYPE_POLICY, TI, PENDULUM, ACTOR, CRITIC, PARAMETERS>;
+    using PPO_SPEC = rlt::rl::algorithms::ppo::Specification<TYPE_POLICY, TI, ENV, ACTOR, CRITIC, PARAMETERS>;
     using PPO = rlt::rl::algorithms::PPO<PPO_SPEC>;
     using PPO_BUFFERS = rlt::rl::algorithms::ppo::Buffers<rlt::rl::algorithms::ppo::BufferSpecification<PPO_SPEC>>;
-    using RUNNER_SPEC = rlt::rl::components::on_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, typename ACTOR::template State<>, N, 100>;
+    using RUNNER_SPEC = rlt::rl::components::on_policy_runner::Specification<TYPE_POLICY, TI, ENV, typename ACTOR::template State<>, N, 100>;
     using DATASET = rlt::rl::components::on_policy_runner::Dataset<rlt::rl::components::on_policy_runner::DatasetSpecification<RUNNER_SPEC, STEPS>>;
+    static_assert(DATASET::DATA_DIM == D);
     using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
     DEVICE device;
     RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
@@ -431,21 +446,25 @@ static void ppo_train_case(const float* actor_params, const float* critic_params
     rlt::init(device, ppo, actor_optimizer, critic_optimizer, rng);
     { const float* p = actor_params; auto& m = ppo.actor.content;
       load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p);
-      rlt::set(device, m.log_std.parameters, p[0], 0); }
+      for(TI a = 0; a < ACT; a++) rlt::set(device, m.log_std.parameters, p[a], a); }
     { const float* p = critic_params; auto& m = ppo.critic.content;
       load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
-    for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < 13; k++) rlt::set(dataset.data, r, k, dataset_in[r * 13 + k]);
+    for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < D; k++) rlt::set(dataset.data, r, k, dataset_in[r * D + k]);
+    auto t0 = std::chrono::steady_clock::now();
     rlt::train(device, ppo, dataset, actor_optimizer, critic_optimizer, ppo_buffers, actor_buffers, critic_buffers, train_rng);
-    if(dataset_out) for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < 13; k++) dataset_out[r * 13 + k] = rlt::get(dataset.data, r, k);
+    if(seconds) *seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if(dataset_out) for(TI r = 0; r < (STEPS + 1) * N; r++) for(TI k = 0; k < D; k++) dataset_out[r * D + k] = rlt::get(dataset.data, r, k);
     auto dump = [&](auto& m, float* params, float* grads, float* mom){
         store_layer(device, m.input_layer, params, PARAMS); store_layer(device, m.hidden_layers[0], params, PARAMS); store_layer(device, m.output_layer, params, PARAMS);
         store_layer(device, m.input_layer, grads, GRADS); store_layer(device, m.hidden_layers[0], grads, GRADS); store_layer(device, m.output_layer, grads, GRADS);
         store_layer(device, m.input_layer, mom, MOM1); store_layer(device, m.hidden_layers[0], mom, MOM1); store_layer(device, m.output_layer, mom, MOM1);
     };
     dump(ppo.actor.content, actor_out, actor_grad, actor_m);
-    actor_out[4481] = rlt::get(device, ppo.actor.content.log_std.parameters, 0);
-    actor_grad[4481] = rlt::get(device, ppo.actor.content.log_std.gradient, 0);
-    actor_m[4481] = rlt::get(device, ppo.actor.content.log_std.gradient_first_order_moment, 0);
+    for(TI a = 0; a < ACT; a++){
+        actor_out[N_ACTOR + a] = rlt::get(device, ppo.actor.content.log_std.parameters, a);
+        actor_grad[N_ACTOR + a] = rlt::get(device, ppo.actor.content.log_std.gradient, a);
+        actor_m[N_ACTOR + a] = rlt::get(device, ppo.actor.content.log_std.gradient_first_order_moment, a);
+    }
     dump(ppo.critic.content, critic_out, critic_grad, critic_m);
     rlt::free(device, ppo); rlt::free(device, ppo_buffers); rlt::free(device, dataset); rlt::free(device, actor_optimizer); rlt::free(device, critic_optimizer);
     rlt::free(device, actor_buffers); rlt::free(device, critic_buffers);
@@ -453,15 +472,19 @@ static void ppo_train_case(const float* actor_params, const float* critic_params
 
 extern "C" {
 
-int ref_ppo_train(int N, int steps, int batch, int epochs, int shuffle, uint32_t seed, const float* actor_params, const float* critic_params, const float* dataset_in,
-                  float* actor_out, float* actor_grad, float* actor_m, float* critic_out, float* critic_grad, float* critic_m, float* dataset_out){
-#define PPO_CASE(n, s, b, e, sh) if(N == n && steps == s && batch == b && epochs == e && (shuffle != 0) == sh){ \
-        ppo_train_case<n, s, b, e, sh>(actor_params, critic_params, dataset_in, seed, actor_out, actor_grad, actor_m, critic_out, critic_grad, critic_m, dataset_out); return 0; }
-    PPO_CASE(64, 64, 4096, 1, false)
-    PPO_CASE(64, 64, 512, 2, false)
-    PPO_CASE(5, 37, 37, 3, false)
-    PPO_CASE(64, 64, 512, 2, true)
-    PPO_CASE(5, 37, 37, 3, true)
+// env: 0 = Pendulum shapes (3 / 1, ReLU), 1 = Ant shapes (27 / 8, tanh)
+int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle, uint32_t seed, const float* actor_params, const float* critic_params, const float* dataset_in,
+                  float* actor_out, float* actor_grad, float* actor_m, float* critic_out, float* critic_grad, float* critic_m, float* dataset_out, double* seconds){
+#define PPO_CASE(id, ENV, HACT, n, s, b, e, sh) if(env == id && N == n && steps == s && batch == b && epochs == e && (shuffle != 0) == sh){ \
+        ppo_train_case<ENV, HACT, n, s, b, e, sh>(actor_params, critic_params, dataset_in, seed, actor_out, actor_grad, actor_m, critic_out, critic_grad, critic_m, dataset_out, seconds); return 0; }
+    PPO_CASE(0, PENDULUM, act::RELU, 64, 64, 4096, 1, false)
+    PPO_CASE(0, PENDULUM, act::RELU, 64, 64, 512, 2, false)
+    PPO_CASE(0, PENDULUM, act::RELU, 5, 37, 37, 3, false)
+    PPO_CASE(0, PENDULUM, act::RELU, 64, 64, 512, 2, true)
+    PPO_CASE(0, PENDULUM, act::RELU, 5, 37, 37, 3, true)
+    PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 1, false)
+    PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 1, true)
+    PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 10, true)
 #undef PPO_CASE
     return -1;
 }

@@ -217,3 +217,24 @@ def test_permute_rows_on_a_wide_matrix(lib, torch):
     rest = [c for c in range(D) if c not in cols]
     assert torch.equal(data[:rows][:, cols], before[perm.long()][:, cols])
     assert torch.equal(data[:rows][:, rest], before[:rows][:, rest]) and torch.equal(data[rows:], before[rows:])
+
+
+@pytest.mark.parametrize("tag", ["plain", "shuffled"])
+def test_ppo_train_on_ant_shapes_vs_reference_golden(lib, torch, tag):
+    """The PPO configuration's shapes (observation 27, actions 8, 64 envs x 1024 steps, minibatch 2048, tanh) through
+    rl_tools_b200.ppo.train against the REAL reference's train(): one epoch = 32 updates; the shuffled dataset is exact."""
+    from rl_tools_b200 import ppo
+    fix = np.load(os.path.join(GOLDEN, "ppo_train_ant.npz"))
+    pa, pc, ds = mg.ppo_ant_inputs()
+    acts = ["tanh", "tanh", "identity"]
+    actor, critic = lib.Mlp(27, [64, 64, 8], acts, 2048, extra_params=8), lib.Mlp(27, [64, 64, 1], acts, 2048)
+    actor.params.copy_(dev(torch, pa)); critic.params.copy_(dev(torch, pc))
+    dataset = dev(torch, ds)
+    layout = ppo.DatasetLayout(27, 8)
+    assert layout.data_dim == 51
+    state = lib.rng_init_host(mg.PPO_SHUFFLE_SEED) if tag == "shuffled" else None
+    ppo.train(actor, critic, dataset, layout, 64 * 1024, 2048, n_epochs=1, shuffle_rng_state=state)
+    s, tot = mg.sample(dataset.cpu().numpy())
+    assert np.array_equal(s, fix[f"{tag}_dataset_sample"]) and tot == fix[f"{tag}_dataset_sum"]
+    for name, got in (("actor", actor.params), ("critic", critic.params)):
+        assert_params_close(name, got.cpu().numpy(), fix[f"{tag}_{name}"], 32)

@@ -190,3 +190,20 @@ def test_ppo_train_with_epoch_shuffle_matches_reference(orc, case):
     assert not np.array_equal(ds, fix[f"dataset_{case}"])
     for name, g in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got):
         assert np.array_equal(g, fix[f"shuffled_{name}_{case}"]), name
+
+
+@pytest.mark.parametrize("tag", ["plain", "shuffled"])
+def test_ppo_train_on_ant_shapes_matches_reference(orc, tag):
+    """One epoch (32 minibatches of 2048) of the reference's train() on the Ant shapes of the PPO configuration: observation 27, actor
+    27 -> 64 -> 64 -> 8 tanh + log_std[8], critic 27 -> 64 -> 64 -> 1, 64 envs x 1024 steps. Bit for bit on the machine that generated the
+    fixture (tanhf comes from the C library on both sides); 1e-6 elsewhere."""
+    fix = np.load(os.path.join(GOLDEN, "ppo_train_ant.npz"))
+    actor, critic, ds = mg.ppo_ant_inputs()
+    sa, sc = oracle.MlpShape.make(27, [64, 64, 8], ["tanh", "tanh", "identity"]), oracle.MlpShape.make(27, [64, 64, 1], ["tanh", "tanh", "identity"])
+    rng = orc.new_rng(mg.PPO_SHUFFLE_SEED) if tag == "shuffled" else None
+    got = orc.ppo_train(sa, sc, actor, critic, ds, 64 * 1024, 2048, 1, shuffle_rng=rng)
+    s, tot = mg.sample(ds)
+    assert np.array_equal(s, fix[f"{tag}_dataset_sample"]) and tot == fix[f"{tag}_dataset_sum"]        # data movement only: exact everywhere
+    for name, g in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got):
+        want = fix[f"{tag}_{name}"]
+        assert np.array_equal(g, want) or np.all(np.abs(g - want) <= 1e-6 + 1e-5 * np.abs(want)), name

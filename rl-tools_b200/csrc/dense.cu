@@ -178,12 +178,15 @@ __global__ void reduce_partials_kernel(float* dst, const float* __restrict__ par
     }
 }
 
-// The tensor-core kernel takes the contraction when its 128-row tiles are reasonably filled and there is enough work to
-// amortise its setup; B200RL_DENSE_KERNEL=simt forces the CUDA-core kernel (A/B measurements).
+// The tensor-core kernel takes the contraction when there is enough work to fill its 128 x 256 tiles on a good part of the SMs:
+// one tile costs ~30 us at K = 256 however few tiles there are, which the CUDA-core kernel's 64 x 64 tiles beat below ~2^27
+// multiply-adds (batch-256 training steps, the 64-wide PPO networks). B200RL_DENSE_KERNEL=simt forces the CUDA-core kernel and
+// B200RL_DENSE_TC_MIN_LOG2 overrides the threshold (A/B measurements).
 static bool tc_eligible(long long M, long long N, long long K){
     static const bool force_simt = [](){ const char* v = getenv("B200RL_DENSE_KERNEL"); return v && v[0] == 's'; }();
+    static const int min_log2 = [](){ const char* v = getenv("B200RL_DENSE_TC_MIN_LOG2"); return v ? atoi(v) : 27; }();
     if(force_simt) return false;
-    return M >= 64 && N >= 16 && (double)M * N * K >= (double)(1 << 22);
+    return M >= 64 && N >= 16 && (double)M * N * K >= ldexp(1.0, min_log2);
 }
 static bool use_tensor_cores(const GemmArgs& a){ return tc_eligible(a.M, a.N, a.K); }
 

@@ -215,7 +215,7 @@ def run_mlp_train(args):
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
     ms = float(tm.item()) / steps
     if rank == 0:
-        flop = 876544.0 * rows * world
+        flop = 876544.0 * rows                     # per GPU: the roofline compares one GPU's kernels with one GPU's peak
         peaks = measured_peaks()
         launches = steps * ((rows // chunk) * (4 + 1 + 4 * 3 + 3) + 2)
         print(json.dumps({"metric": "MLP fwd+bwd+Adam samples/s", "value": rows * world / (ms * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": steps,

@@ -10,7 +10,7 @@ import __graft_entry__ as entry
 
 
 def test_adapter_compiles_against_the_reference_headers():
-    if not os.path.isdir("/root/reference/include/rl_tools"):
+    if not os.path.isdir(os.path.join(entry.REFERENCE_DIR, "include", "rl_tools")):
         pytest.skip("reference tree not present on this machine")
     entry.load_package().build()
     assert entry.build_adapter_test()

@@ -37,6 +37,8 @@ SHAPES = [  # (batch, in, out, act): the reference's CUDA test sweep plus awkwar
     (1, 3, 64, "relu"), (256, 3, 64, "relu"), (256, 64, 2, "identity"), (2, 256, 10, "relu"), (9, 256, 60, "tanh"), (10, 200, 100, "relu"),
     (32, 10, 100, "sigmoid"), (200, 11, 256, "fast_tanh"), (1024, 256, 10, "relu"), (64, 50, 101, "tanh"), (256, 256, 256, "relu"),
     (2048, 27, 64, "tanh"), (300, 64, 8, "identity"), (4099, 65, 17, "relu"), (256, 4, 256, "relu"), (256, 256, 1, "identity"),
+    # >= 2^27 multiply-adds: these take the tensor-core kernel (ragged rows, ragged k, narrow and non-multiple-of-8 columns)
+    (4099, 256, 200, "relu"), (8192, 130, 257, "tanh"), (70001, 64, 40, "relu"), (16384, 256, 256, "relu"),
 ]
 
 

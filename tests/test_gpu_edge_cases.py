@@ -30,7 +30,9 @@ def test_empty_inputs_are_accepted_and_touch_nothing(lib, torch):
     p = lambda t: C.c_void_p(t.data_ptr())
     i32, u8 = torch.zeros(4, dtype=torch.int32, device="cuda"), torch.zeros(4, dtype=torch.uint8, device="cuda")
     params = torch.zeros(4482, device="cuda")
-    assert L.b200rl_dense_forward(p(sentinel), p(sentinel), p(sentinel), 4, None, 0, p(sentinel), 4, 0, 4, 4, 1, None) == 0          # batch 0
+    other = torch.full((64,), 5.0, device="cuda")
+    assert L.b200rl_dense_forward(p(sentinel), p(sentinel), p(sentinel), 4, None, 0, p(other), 4, 0, 4, 4, 1, None) == 0             # batch 0
+    assert L.b200rl_dense_forward(p(sentinel), p(sentinel), p(sentinel), 4, None, 0, p(sentinel), 4, 0, 4, 4, 1, None) == 1          # in-place output is refused
     assert L.b200rl_pendulum_rollout(C.byref(shape), p(params), p(sentinel), p(i32), p(u8), p(sentinel), None, 0, 0, 5, 200,
                                      p(sentinel), p(sentinel), p(sentinel), None, None) == 0                                       # no environments
     assert L.b200rl_pendulum_rollout(C.byref(shape), p(params), p(sentinel), p(i32), p(u8), p(sentinel), None, 0, 4, 0, 200,
@@ -40,7 +42,7 @@ def test_empty_inputs_are_accepted_and_touch_nothing(lib, torch):
     assert L.b200rl_permute_rows(p(sentinel), 4, 0, p(i32), 3, None, 0, None) == 0
     assert L.b200rl_gae(p(sentinel), 1, p(sentinel), 1, p(sentinel), 1, p(sentinel), 1, p(sentinel), 1, p(sentinel), 1, 0, 8, 0.99, 0.95, 0, None) == 0
     torch.cuda.synchronize()
-    assert bool((sentinel == 5.0).all()) and int(i32.abs().sum()) == 0
+    assert bool((sentinel == 5.0).all()) and bool((other == 5.0).all()) and int(i32.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("N", [1, 3, 31, 127, 129, 593, 4 * 148 * 128 + 5])

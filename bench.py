@@ -334,6 +334,7 @@ def run_ppo_update(args):
     base[:, layout.truncated] = (torch.rand(rows, device=dev, generator=g) < 1e-3).float()
     dataset = base.clone()
     rng_state = pkg.rng_init_host(1)
+    graphs = ppo.MinibatchGraphs(actor, critic, dataset, layout, N * T, B)       # one captured graph per minibatch position
 
     def step():
         dataset.copy_(base)
@@ -342,7 +343,7 @@ def run_ppo_update(args):
         e0.record()
         ppo.evaluate_values(critic, dataset, layout)
         ppo.estimate_generalized_advantages(dataset, layout, N, T)
-        ppo.train(actor, critic, dataset, layout, N * T, B, n_epochs=E, shuffle_rng_state=rng_state)
+        ppo.train(actor, critic, dataset, layout, N * T, B, n_epochs=E, shuffle_rng_state=rng_state, graphs=graphs)
         e1.record()
 
     steps, warmup = min(args.steps, 5), 3
@@ -372,7 +373,8 @@ def run_ppo_update(args):
     print(json.dumps({"metric": "PPO update minibatch-samples/s", "value": samples / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
                       "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "ppo_update_ant_shapes_obs27_act8_64envx1024step_mb2048_10epochs_shuffled", "updates_per_step": E * (N * T // B),
-                                 "l2": "the dataset (13 MB) fits L2: this workload is launch- and latency-bound", "parallelism": "single GPU"},
+                                 "l2": "the dataset (13 MB) fits L2: this workload is launch- and latency-bound", "launching": "one CUDA graph replay per minibatch update",
+                                 "parallelism": "single GPU"},
                       "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
                                    "peak_source": peaks["source"] + " bf16 dense (burst)"},
                       "cpu_baseline": cpu, "gpu_launches": launches}))

@@ -197,13 +197,19 @@ def gae(rewards, all_values, terminated, truncated, n_envs, steps, gamma=0.99, l
 
 
 def ppo_policy_gradient(current_actions, rollout_actions, log_std, rollout_log_probs, advantages, d_log_std, epsilon_clip=0.2, entropy_coefficient=0.01,
-                        advantage_epsilon=1e-8, normalize_advantage=True, learn_action_std=True, d_actions=None):
-    """d_log_std is accumulated in place; returns d_actions [B, A]."""
+                        advantage_epsilon=1e-8, normalize_advantage=True, learn_action_std=True, d_actions=None, scratch=None):
+    """d_log_std is accumulated in place; returns d_actions [B, A]. scratch: a dict that keeps the device scratch buffer between calls
+    (required under CUDA graph capture, where nothing may be allocated)."""
     import torch
     B, A = current_actions.shape
     d_actions = torch.empty((B, A), device=current_actions.device, dtype=torch.float32) if d_actions is None else d_actions
     nbytes = lib().b200rl_ppo_scratch_bytes(B, A)
-    scratch = torch.empty(nbytes, device=current_actions.device, dtype=torch.uint8)
+    if scratch is not None:
+        if scratch.get("bytes", -1) < nbytes:
+            scratch["buffer"], scratch["bytes"] = torch.empty(nbytes, device=current_actions.device, dtype=torch.uint8), nbytes
+        scratch = scratch["buffer"]
+    else:
+        scratch = torch.empty(nbytes, device=current_actions.device, dtype=torch.uint8)
     check(lib().b200rl_ppo_policy_gradient(_ptr(current_actions), current_actions.stride(0), _ptr(rollout_actions), rollout_actions.stride(0), _ptr(log_std),
                                            _ptr(rollout_log_probs), rollout_log_probs.stride(0), _ptr(advantages), advantages.stride(0), _ptr(d_actions),
                                            d_actions.stride(0), _ptr(d_log_std), B, A, epsilon_clip, entropy_coefficient, advantage_epsilon,

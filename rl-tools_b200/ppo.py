@@ -47,16 +47,59 @@ def evaluate_values(critic, dataset, layout):
     return dataset
 
 
+def _minibatch_update(actor, critic, rows, layout, epsilon_clip, entropy_coefficient, advantage_epsilon, normalize_advantage, learn_action_std):
+    obs = rows[:, layout.observations]
+    actor.zero_gradient()
+    critic.zero_gradient()
+    current = actor.forward(obs)
+    d_actions = _ppo_policy_gradient(current, rows[:, layout.actions], actor.extra("params"), rows[:, layout.action_log_probs], rows[:, layout.advantages],
+                                     actor.extra("grads"), epsilon_clip, entropy_coefficient, advantage_epsilon, normalize_advantage, learn_action_std,
+                                     d_actions=actor.d_out_buffer(), scratch=actor.__dict__.setdefault("_ppo_scratch", {}))
+    actor.backward(obs, d_actions)
+    values = critic.forward(obs)
+    critic.backward(obs, _mse_gradient(values, rows[:, layout.target_values:layout.target_values + 1], 0.5, d_a=critic.d_out_buffer()))
+    actor.step()
+    critic.step()
+
+
+class MinibatchGraphs:
+    """One captured CUDA graph per minibatch position of a dataset matrix: the ~24 launches of a minibatch update replayed with a
+    single launch. Valid for one (actor, critic, dataset, batch_size) combination; every pointer is baked into the graphs."""
+
+    def __init__(self, actor, critic, dataset, layout, n_rows, batch_size, **hyper):
+        import torch
+        self.key = (dataset.data_ptr(), n_rows, batch_size)
+        self.graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        saved = [t.clone() for t in (actor.params, actor.m, actor.v, actor.adam_state, critic.params, critic.m, critic.v, critic.adam_state)]
+        with torch.cuda.stream(side):
+            _minibatch_update(actor, critic, dataset[:batch_size], layout, **hyper)             # warm-up outside capture (lazy module loading)
+        torch.cuda.current_stream().wait_stream(side)
+        for b in range(n_rows // batch_size):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                _minibatch_update(actor, critic, dataset[b * batch_size:(b + 1) * batch_size], layout, **hyper)
+            self.graphs.append(g)
+        for t, s in zip((actor.params, actor.m, actor.v, actor.adam_state, critic.params, critic.m, critic.v, critic.adam_state), saved):
+            t.copy_(s)                                                                          # the warm-up update is undone
+
+
 def train(actor, critic, dataset, layout, n_rows, batch_size, n_epochs=10, epsilon_clip=0.2, entropy_coefficient=0.01, advantage_epsilon=1e-8,
-          normalize_advantage=True, learn_action_std=True, shuffle_rng_state=None):
+          normalize_advantage=True, learn_action_std=True, shuffle_rng_state=None, graphs=None):
     """n_epochs x (n_rows // batch_size) minibatch updates. shuffle_rng_state (from rng_init_host) switches the reference's SHUFFLE_EPOCH
     on: before every epoch the observation / action / log-prob / advantage / target-value columns of the dataset matrix are permuted in
     place with the permutation the reference's engine would produce (:127-158); None keeps dataset order. Per minibatch: zero_gradient,
     actor forward, clipped-surrogate gradient (+ log_std gradient), actor backward, critic forward, 0.5-weighted MSE gradient against
     the target values, critic backward, one Adam step each. `actor` is an Mlp with extra_params = action_dim (the log_std behind the
-    layers), `critic` an Mlp with one output; both built for batch_size rows."""
-    assert actor.batch == batch_size and critic.batch == batch_size and actor.n_extra == layout.action_dim
+    layers), `critic` an Mlp with one output; both built for batch_size rows. graphs = a MinibatchGraphs built for these arguments
+    replays each minibatch update as one CUDA graph launch instead of ~24 kernel launches (same kernels, same results)."""
     import torch
+    assert actor.batch == batch_size and critic.batch == batch_size and actor.n_extra == layout.action_dim
+    hyper = dict(epsilon_clip=epsilon_clip, entropy_coefficient=entropy_coefficient, advantage_epsilon=advantage_epsilon,
+                 normalize_advantage=normalize_advantage, learn_action_std=learn_action_std)
+    if graphs is not None:
+        assert graphs.key == (dataset.data_ptr(), n_rows, batch_size), "graphs were captured for another dataset matrix"
     shuffled = list(range(layout.observations.start, layout.observations.stop)) + list(range(layout.actions.start, layout.actions.stop)) + \
         [layout.action_log_probs, layout.advantages, layout.target_values]
     for _ in range(n_epochs):
@@ -64,16 +107,7 @@ def train(actor, critic, dataset, layout, n_rows, batch_size, n_epochs=10, epsil
             perm = torch.from_numpy(_shuffle_permutation_host(shuffle_rng_state, n_rows)).to(dataset.device)
             _permute_rows(dataset, n_rows, perm, shuffled)
         for b in range(n_rows // batch_size):
-            rows = dataset[b * batch_size:(b + 1) * batch_size]
-            obs = rows[:, layout.observations]
-            actor.zero_gradient()
-            critic.zero_gradient()
-            current = actor.forward(obs)
-            d_actions = _ppo_policy_gradient(current, rows[:, layout.actions], actor.extra("params"), rows[:, layout.action_log_probs], rows[:, layout.advantages],
-                                             actor.extra("grads"), epsilon_clip, entropy_coefficient, advantage_epsilon, normalize_advantage, learn_action_std,
-                                             d_actions=actor.d_out_buffer())
-            actor.backward(obs, d_actions)
-            values = critic.forward(obs)
-            critic.backward(obs, _mse_gradient(values, rows[:, layout.target_values:layout.target_values + 1], 0.5, d_a=critic.d_out_buffer()))
-            actor.step()
-            critic.step()
+            if graphs is not None:
+                graphs.graphs[b].replay()
+            else:
+                _minibatch_update(actor, critic, dataset[b * batch_size:(b + 1) * batch_size], layout, **hyper)

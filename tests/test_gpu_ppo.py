@@ -238,3 +238,23 @@ def test_ppo_train_on_ant_shapes_vs_reference_golden(lib, torch, tag):
     assert np.array_equal(s, fix[f"{tag}_dataset_sample"]) and tot == fix[f"{tag}_dataset_sum"]
     for name, got in (("actor", actor.params), ("critic", critic.params)):
         assert_params_close(name, got.cpu().numpy(), fix[f"{tag}_{name}"], 32)
+
+
+def test_ppo_train_graph_replay_equals_eager_launches(lib, torch):
+    """MinibatchGraphs replays the same kernels as the eager path: parameters, moments and the shuffled dataset are bit-identical."""
+    from rl_tools_b200 import ppo
+    fix = np.load(os.path.join(GOLDEN, "ppo_train.npz"))
+    N, steps, batch, epochs = mg.PPO_TRAIN_CASES[1]
+    pa, pc = mg.ppo_train_params(1)
+    dims, acts = [64, 64, 1], ["relu", "relu", "identity"]
+    layout = ppo.DatasetLayout(3, 1)
+    results = []
+    for use_graphs in (False, True):
+        actor, critic = lib.Mlp(3, dims, acts, batch, extra_params=1), lib.Mlp(3, dims, acts, batch)
+        actor.params.copy_(dev(torch, pa)); critic.params.copy_(dev(torch, pc))
+        dataset = dev(torch, fix["dataset_1"])
+        graphs = ppo.MinibatchGraphs(actor, critic, dataset, layout, N * steps, batch) if use_graphs else None
+        ppo.train(actor, critic, dataset, layout, N * steps, batch, n_epochs=epochs, shuffle_rng_state=lib.rng_init_host(5), graphs=graphs)
+        results.append([t.clone() for t in (actor.params, actor.m, actor.v, critic.params, critic.m, critic.v, dataset)])
+    for a, b in zip(*results):
+        assert torch.equal(a, b)

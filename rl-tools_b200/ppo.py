@@ -47,7 +47,7 @@ def evaluate_values(critic, dataset, layout):
     return dataset
 
 
-def _minibatch_update(actor, critic, rows, layout, epsilon_clip, entropy_coefficient, advantage_epsilon, normalize_advantage, learn_action_std):
+def _minibatch_update(actor, critic, rows, layout, epsilon_clip=0.2, entropy_coefficient=0.01, advantage_epsilon=1e-8, normalize_advantage=True, learn_action_std=True):
     obs = rows[:, layout.observations]
     actor.zero_gradient()
     critic.zero_gradient()

@@ -197,14 +197,16 @@ static BackwardPlan plan_backward(int B, int I, int O){
     const bool tc = tc_eligible(O, I, B);
     int tiles = tc ? ((O + 127) / 128) * ((I + 255) / 256) : ((O + BM - 1) / BM) * ((I + BN - 1) / BN);
     int want = tc ? (NUM_SMS + tiles - 1) / tiles : (2 * NUM_SMS + tiles - 1) / tiles;
-    int max_splits = (B + 255) / 256;
+    // at least 256 batch rows per split for the tensor-core kernel (8 chunks amortise its tile setup), 64 for the CUDA-core kernel:
+    // small batches (256 ... 2048 rows) would otherwise run on a handful of CTAs and be bound by the latency of their k loop
+    int max_splits = tc ? (B + 255) / 256 : (B + 63) / 64;
     p.splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
     if(p.splits < 1) p.splits = 1;
     p.k_per_split = ((B + p.splits - 1) / p.splits + BK - 1) / BK * BK;
     p.splits = (B + p.k_per_split - 1) / p.k_per_split;
     int col_blocks = (O + 127) / 128;                      // the vector kernel's blocks cover 128 columns
     int want_segs = (4 * NUM_SMS + col_blocks - 1) / col_blocks;
-    int max_segs = (B + 255) / 256;
+    int max_segs = (B + 63) / 64;
     p.bias_segs = want_segs > max_segs ? max_segs : want_segs;
     if(p.bias_segs < 1) p.bias_segs = 1;
     p.rows_per_seg = (B + p.bias_segs - 1) / p.bias_segs;

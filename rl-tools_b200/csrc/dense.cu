@@ -16,67 +16,98 @@ namespace b200rl {
 
 constexpr int BM = 64, BN = 64, BK = 16, GEMM_THREADS = 256, PADM = 4;
 
-template <bool KCONTIG>
-__device__ __forceinline__ void load_tile(float (*S)[BM + PADM], const float* __restrict__ P, long long ld, int row0, int rows, int k0, int k_end, int tid){
-    // S[k][r] = P(row0 + r, k0 + k); zero outside [0, rows) x [k0, k_end)
+// One k-step of an operand tile travels global -> registers -> shared memory, so that the loads of step k+1 are in flight while
+// step k is multiplied (the batch-256 and 64-wide problems run on few CTAs and are bound by this latency, not by bandwidth).
+// Tile element (k, r) = P(row0 + r, k0 + k), zero outside [0, rows) x [k0, k_end); T / 16 elements per thread (T = tile edge).
+template <int T, bool KCONTIG>
+__device__ __forceinline__ void fetch_tile(float (&reg)[T / 16], const float* __restrict__ P, long long ld, int row0, int rows, int k0, int k_end, int tid){
     if constexpr(KCONTIG){
-        int k = tid % BK, r = tid / BK;            // 16 consecutive k per row -> 64-byte segments
+        const int k = tid % BK, r = tid / BK;            // 16 consecutive k per row -> 64-byte segments
 #pragma unroll
-        for(int j = 0; j < BM / (GEMM_THREADS / BK); j++){
-            int rr = r + j * (GEMM_THREADS / BK);
-            int gr = row0 + rr, gk = k0 + k;
-            S[k][rr] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gr * ld + gk) : 0.0f;
+        for(int j = 0; j < T / 16; j++){
+            const int gr = row0 + r + j * (GEMM_THREADS / BK), gk = k0 + k;
+            reg[j] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gr * ld + gk) : 0.0f;
         }
     }
     else{
-        int r = tid % BM, k = tid / BM;            // 64 consecutive rows (contiguous in memory) per k
+        const int r = tid % T, k = tid / T;              // T consecutive rows (contiguous in memory) per k
 #pragma unroll
-        for(int j = 0; j < BK / (GEMM_THREADS / BM); j++){
-            int kk = k + j * (GEMM_THREADS / BM);
-            int gr = row0 + r, gk = k0 + kk;
-            S[kk][r] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gk * ld + gr) : 0.0f;
+        for(int j = 0; j < T / 16; j++){
+            const int gr = row0 + r, gk = k0 + k + j * (GEMM_THREADS / T);
+            reg[j] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gk * ld + gr) : 0.0f;
         }
     }
 }
+template <int T, bool KCONTIG>
+__device__ __forceinline__ void store_tile(float (*S)[T + PADM], const float (&reg)[T / 16], int tid){
+    if constexpr(KCONTIG){
+        const int k = tid % BK, r = tid / BK;
+#pragma unroll
+        for(int j = 0; j < T / 16; j++) S[k][r + j * (GEMM_THREADS / BK)] = reg[j];
+    }
+    else{
+        const int r = tid % T, k = tid / T;
+#pragma unroll
+        for(int j = 0; j < T / 16; j++) S[k + j * (GEMM_THREADS / T)][r] = reg[j];
+    }
+}
 
-template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT>
+// C tile T x T per CTA (T = 64, or 32 when 64-wide tiles would leave most SMs idle), 256 threads, (T/16)^2 outputs per thread.
+template <int T, bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT>
 __global__ void __launch_bounds__(GEMM_THREADS) gemm_kernel(GemmArgs a){
-    __shared__ __align__(16) float As[BK][BM + PADM];
-    __shared__ __align__(16) float Bs[BK][BN + PADM];
+    static_assert(T == 64 || T == 32);
+    constexpr int R = T / 16;
+    __shared__ __align__(16) float As[BK][T + PADM];
+    __shared__ __align__(16) float Bs[BK][T + PADM];
     const int tid = threadIdx.x;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * T, n0 = blockIdx.x * T;
     const int k_begin = blockIdx.z * a.k_per_split;
     const int k_end = min(a.K, k_begin + a.k_per_split);
     const int tx = tid % 16, ty = tid / 16;
-    float acc[4][4];
+    float acc[R][R];
 #pragma unroll
-    for(int i = 0; i < 4; i++)
+    for(int i = 0; i < R; i++)
 #pragma unroll
-        for(int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+        for(int j = 0; j < R; j++) acc[i][j] = 0.0f;
 
+    float ra[R], rb[R];
+    fetch_tile<T, A_KCONTIG>(ra, a.A, a.lda, m0, a.M, k_begin, k_end, tid);
+    fetch_tile<T, B_KCONTIG>(rb, a.B, a.ldb, n0, a.N, k_begin, k_end, tid);
     for(int k0 = k_begin; k0 < k_end; k0 += BK){
-        load_tile<A_KCONTIG>(As, a.A, a.lda, m0, a.M, k0, k_end, tid);
-        load_tile<B_KCONTIG>(Bs, a.B, a.ldb, n0, a.N, k0, k_end, tid);
+        store_tile<T, A_KCONTIG>(As, ra, tid);
+        store_tile<T, B_KCONTIG>(Bs, rb, tid);
         __syncthreads();
+        if(k0 + BK < k_end){
+            fetch_tile<T, A_KCONTIG>(ra, a.A, a.lda, m0, a.M, k0 + BK, k_end, tid);
+            fetch_tile<T, B_KCONTIG>(rb, a.B, a.ldb, n0, a.N, k0 + BK, k_end, tid);
+        }
 #pragma unroll
         for(int k = 0; k < BK; k++){
-            float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
-            float4 bv = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
-            float am[4] = {av.x, av.y, av.z, av.w}, bn[4] = {bv.x, bv.y, bv.z, bv.w};
+            float am[R], bn[R];
+            if constexpr(R == 4){
+                const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+                const float4 bv = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+                am[0] = av.x; am[1] = av.y; am[2] = av.z; am[3] = av.w; bn[0] = bv.x; bn[1] = bv.y; bn[2] = bv.z; bn[3] = bv.w;
+            }
+            else{
+                const float2 av = *reinterpret_cast<const float2*>(&As[k][ty * 2]);
+                const float2 bv = *reinterpret_cast<const float2*>(&Bs[k][tx * 2]);
+                am[0] = av.x; am[1] = av.y; bn[0] = bv.x; bn[1] = bv.y;
+            }
 #pragma unroll
-            for(int i = 0; i < 4; i++)
+            for(int i = 0; i < R; i++)
 #pragma unroll
-                for(int j = 0; j < 4; j++) acc[i][j] = fmaf(am[i], bn[j], acc[i][j]);
+                for(int j = 0; j < R; j++) acc[i][j] = fmaf(am[i], bn[j], acc[i][j]);
         }
         __syncthreads();
     }
 #pragma unroll
-    for(int i = 0; i < 4; i++){
-        int m = m0 + ty * 4 + i;
+    for(int i = 0; i < R; i++){
+        int m = m0 + ty * R + i;
         if(m >= a.M) continue;
 #pragma unroll
-        for(int j = 0; j < 4; j++){
-            int n = n0 + tx * 4 + j;
+        for(int j = 0; j < R; j++){
+            int n = n0 + tx * R + j;
             if(n >= a.N) continue;
             float v = acc[i][j];
             if constexpr(EPI == EPI_FORWARD){
@@ -94,6 +125,21 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_kernel(GemmArgs a){
         }
     }
 }
+// 32-wide tiles when 64-wide ones would occupy less than half of the SMs
+static inline bool small_tiles(int M, int N, int splits){
+    return (long long)((M + 63) / 64) * ((N + 63) / 64) * splits < NUM_SMS / 2;
+}
+#define B200RL_LAUNCH_SIMT_GEMM(AK, BKC, EPI, ACT, args, splits, stream)                                                            \
+    do{                                                                                                                             \
+        if(small_tiles((args).M, (args).N, (splits))){                                                                              \
+            dim3 grid_(((args).N + 31) / 32, ((args).M + 31) / 32, (splits));                                                       \
+            gemm_kernel<32, AK, BKC, EPI, ACT><<<grid_, GEMM_THREADS, 0, (stream)>>>(args);                                         \
+        }                                                                                                                           \
+        else{                                                                                                                       \
+            dim3 grid_(((args).N + 63) / 64, ((args).M + 63) / 64, (splits));                                                       \
+            gemm_kernel<64, AK, BKC, EPI, ACT><<<grid_, GEMM_THREADS, 0, (stream)>>>(args);                                         \
+        }                                                                                                                           \
+    } while(0)
 
 // d_pre = act'(pre) * d_out written in place, plus per-column sums over a segment of rows.
 // grid (ceil(O/32), n_seg), block (32, 8). n_seg == 1: d_bias += column sum; else bias_partial[seg][o] = column sum.
@@ -226,8 +272,7 @@ static int dense_forward_impl(const float* W, const float* bias, const float* x,
         int rc = launch_gemm_tc(a, EPI_FORWARD, act, true, true, 1, s);
         if(rc != B200RL_ERR_UNSUPPORTED) return rc;
     }
-    dim3 grid((O + BN - 1) / BN, (B + BM - 1) / BM, 1);
-    B200RL_DISPATCH_ACT(act, (gemm_kernel<true, true, EPI_FORWARD, ACT><<<grid, GEMM_THREADS, 0, s>>>(a)));
+    B200RL_DISPATCH_ACT(act, B200RL_LAUNCH_SIMT_GEMM(true, true, EPI_FORWARD, ACT, a, 1, s));
     B200RL_LAUNCH_CHECK("dense_forward");
     return B200RL_OK;
 }
@@ -265,8 +310,7 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         int rc_tc = use_tensor_cores(a) ? launch_gemm_tc(a, EPI_ACCUMULATE, 0, false, false, p.splits, s) : B200RL_ERR_UNSUPPORTED;
         if(rc_tc != B200RL_OK && rc_tc != B200RL_ERR_UNSUPPORTED) return rc_tc;
         if(rc_tc == B200RL_ERR_UNSUPPORTED){
-            dim3 grid((I + BN - 1) / BN, (O + BM - 1) / BM, p.splits);
-            gemm_kernel<false, false, EPI_ACCUMULATE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
+            B200RL_LAUNCH_SIMT_GEMM(false, false, EPI_ACCUMULATE, 0, a, p.splits, s);
             B200RL_LAUNCH_CHECK("dense_dW");
         }
         if(p.splits > 1){
@@ -283,8 +327,7 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         int rc_tc = use_tensor_cores(a) ? launch_gemm_tc(a, EPI_STORE, 0, true, false, 1, s) : B200RL_ERR_UNSUPPORTED;
         if(rc_tc != B200RL_OK && rc_tc != B200RL_ERR_UNSUPPORTED) return rc_tc;
         if(rc_tc == B200RL_ERR_UNSUPPORTED){
-            dim3 grid((I + BN - 1) / BN, (B + BM - 1) / BM, 1);
-            gemm_kernel<true, false, EPI_STORE, 0><<<grid, GEMM_THREADS, 0, s>>>(a);
+            B200RL_LAUNCH_SIMT_GEMM(true, false, EPI_STORE, 0, a, 1, s);
             B200RL_LAUNCH_CHECK("dense_d_in");
         }
     }

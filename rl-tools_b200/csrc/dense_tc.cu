@@ -6,6 +6,12 @@
 // store when k is not the contiguous index in memory). Two stages: while the tensor core works on chunk c (12
 // tcgen05.mma M128 x N x K8 per chunk into a fresh 128 x N TMEM accumulator, committed to the chunk's mbarrier) the threads
 // prefetch and stage chunk c+1 and add chunk c-1 from TMEM to their fp32 register accumulators.
+// The MMAs are issued by a warp of their own: issuing an M128 x N256 x K8 MMA blocks the thread for about as long as the MMA
+// runs (~105 cycles each, measured), so an issuing thread that also stages operands makes every other warp wait for it at the
+// next barrier. The CTA therefore has three warpgroups: two stage + accumulate (256 threads, registers raised to 240 with
+// setmaxnreg) and one that holds the issuing warp (registers lowered to 24; its other three warps exit). Measured and not
+// kept: letting those three warps stage the B operand -- 96 threads cannot keep enough 16-byte loads in flight (Little's law:
+// ~17 KB in flight against the ~48 KB the 256 staging threads sustain) and the 65,536 x 256 x 256 forward fell from 114 to 171 us.
 // One CTA per SM, persistent over (row tile, column tile, k split) work items; N <= 256 per tile.
 // Epilogue: transposition through shared memory so that every global store is a full 128-byte row segment,
 // then bias + pre-activation store + activation (forward), plain store (input gradient) or accumulate / split-k partial
@@ -17,7 +23,7 @@
 namespace b200rl {
 
 namespace {
-constexpr int TC_THREADS = 256, TC_M = 128, TC_KC = 32, TC_NMAX = 256;
+constexpr int TC_THREADS = 256, TC_LAUNCH_THREADS = 384, TC_M = 128, TC_KC = 32, TC_NMAX = 256;      // 256 staging threads + the issuing warpgroup
 constexpr uint32_t A_TILE_BYTES = TC_M * 128;                       // one k chunk of A: 128 rows x 32 tf32
 constexpr uint32_t TMEM_COLS = 512;                                  // two 256-column accumulators (one per k chunk in flight)
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
@@ -98,7 +104,7 @@ __device__ __forceinline__ void store_operand(const float4 (&reg)[ITERS], uint8_
 // 96 chained MMAs); with 12 MMAs per chain and the cross-chunk sum in registers the result is as accurate as an fp32
 // FMA loop.
 template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmArgs a, int n_pad, int m_tiles, int n_tiles, int splits, int a_vec, int b_vec){
+__global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs a, int n_pad, int m_tiles, int n_tiles, int splits, int a_vec, int b_vec){
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -106,20 +112,55 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmArgs a, int 
     const uint32_t stage_bytes = 2 * A_TILE_BYTES + 2 * b_tile_bytes;
     uint8_t* ctrl = base + 2 * stage_bytes;
     uint64_t* chunk_bar = reinterpret_cast<uint64_t*>(ctrl);          // [2]: the MMAs of the chunk using stage / TMEM buffer s have completed
-    uint32_t* slot = reinterpret_cast<uint32_t*>(ctrl + 16);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 20);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl + 16);      // [2]: stage s holds the operands of the next chunk
+    uint32_t* slot = reinterpret_cast<uint32_t*>(ctrl + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 36);
 
-    if(tid == 0){ tc::mbar_init(chunk_bar, 1); tc::mbar_init(chunk_bar + 1, 1); tc::fence_mbar_init(); *abort_flag = 0; }
+    if(tid == 0){
+        tc::mbar_init(chunk_bar, 1); tc::mbar_init(chunk_bar + 1, 1); tc::mbar_init(full_bar, 1); tc::mbar_init(full_bar + 1, 1);
+        tc::fence_mbar_init(); *abort_flag = 0;
+    }
     if(warp == 0){ tc::tmem_alloc(slot, TMEM_COLS); tc::tmem_relinquish(); }
     tc::fence_before_thread_sync();
     __syncthreads();
     tc::fence_after_thread_sync();
     const uint32_t tmem_base = *slot;
     const uint32_t idesc = tc::make_idesc_tf32(TC_M, n_pad);
+    const int total = m_tiles * n_tiles * splits;
+
+    if(tid >= TC_THREADS){
+        // ---- issuing warpgroup: one thread walks the same (work item, chunk) sequence as the staging threads ----
+        tc::setmaxnreg_dec<24>();
+        if(tid != TC_THREADS) return;
+        uint32_t u = 0;
+        for(int item = blockIdx.x; item < total; item += gridDim.x){
+            const int z = item / (m_tiles * n_tiles);
+            const int k_begin = z * a.k_per_split, k_end = min(a.K, k_begin + a.k_per_split);
+            const int n_chunks = (k_end - k_begin + TC_KC - 1) / TC_KC;
+            for(int c = 0; c < n_chunks; c++, u++){
+                const uint32_t s = u & 1;
+                if(!tc::mbar_wait_bounded(full_bar + s, (u >> 1) & 1, WAIT_LIMIT_CYCLES) || *abort_flag){ *abort_flag = 1; g_dense_tc_error = 1; return; }
+                tc::fence_after_thread_sync();
+                uint8_t* stage = base + s * stage_bytes;
+                const uint64_t da_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(stage)), da_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + A_TILE_BYTES));
+                const uint64_t db_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + 2 * A_TILE_BYTES));
+                const uint64_t db_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + 2 * A_TILE_BYTES + b_tile_bytes));
+                const uint32_t d = tmem_base + s * 256;
+#pragma unroll
+                for(int pass = 0; pass < 3; pass++){                 // the small correction terms first, then hi * hi
+                    const uint64_t da = pass == 0 ? da_lo : da_hi, db = pass == 1 ? db_lo : db_hi;
+#pragma unroll
+                    for(int ks = 0; ks < 4; ks++) tc::mma_tf32_ss(d, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, (pass | ks) ? 1u : 0u);
+                }
+                tc::commit(chunk_bar + s);
+            }
+        }
+        return;
+    }
+    tc::setmaxnreg_inc<240>();
     const int q = warp & 3, col_half = warp >> 2;                     // this warp: TMEM lanes 32 q .. +31, 32-column blocks col_half, col_half + 2, ...
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int n_blocks = (n_pad + 31) / 32;
-    const int total = m_tiles * n_tiles * splits;
     uint32_t u = 0;                                                   // running chunk counter: stage and TMEM buffer u & 1
     bool aborted = false;
 
@@ -171,22 +212,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmArgs a, int 
             }
             tc::fence_proxy_async_smem();
             tc::fence_before_thread_sync();
-            __syncthreads();
+            tc::named_barrier_sync(1, TC_THREADS);
             if(*abort_flag){ aborted = true; break; }
-            if(tid == 0){
-                tc::fence_after_thread_sync();
-                const uint64_t da_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(stage)), da_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + A_TILE_BYTES));
-                const uint64_t db_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + 2 * A_TILE_BYTES));
-                const uint64_t db_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(stage + 2 * A_TILE_BYTES + b_tile_bytes));
-                const uint32_t d = tmem_base + s * 256;
-#pragma unroll
-                for(int pass = 0; pass < 3; pass++){                 // the small correction terms first, then hi * hi
-                    const uint64_t da = pass == 0 ? da_lo : da_hi, db = pass == 1 ? db_lo : db_hi;
-#pragma unroll
-                    for(int ks = 0; ks < 4; ks++) tc::mma_tf32_ss(d, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, (pass | ks) ? 1u : 0u);
-                }
-                tc::commit(chunk_bar + s);
-            }
+            if(tid == 0) tc::mbar_arrive(full_bar + s);              // the issuing warp takes over from here
             __syncwarp();
             if(c + 1 < n_chunks){
                 const int k0 = k_begin + (c + 1) * TC_KC;
@@ -233,12 +261,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmArgs a, int 
             __syncwarp();
         }
         tc::fence_before_thread_sync();
-        __syncthreads();                               // the patch area (stage 0) is overwritten by the next work item
+        tc::named_barrier_sync(1, TC_THREADS);         // the patch area (stage 0) is overwritten by the next work item
         if(*abort_flag){ aborted = true; break; }
     }
     if(aborted && tid == 0) g_dense_tc_error = 1;
     tc::fence_before_thread_sync();
-    __syncthreads();
+    tc::named_barrier_sync(1, TC_THREADS);
     if(warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
@@ -257,7 +285,7 @@ static int launch_one(const GemmArgs& a, int splits, cudaStream_t s){
     const int grid = (int)(total < NUM_SMS ? total : NUM_SMS);
     auto aligned = [](const float* p, long long ld){ return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld & 3) == 0; };
     const int a_vec = A_KC && aligned(a.A, a.lda) && (a.k_per_split % 4 == 0), b_vec = B_KC && aligned(a.B, a.ldb) && (a.k_per_split % 4 == 0);
-    gemm_tc_kernel<A_KC, B_KC, EPI, ACT><<<grid, TC_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec);
+    gemm_tc_kernel<A_KC, B_KC, EPI, ACT><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec);
     B200RL_LAUNCH_CHECK("gemm_tc");
     return B200RL_OK;
 }

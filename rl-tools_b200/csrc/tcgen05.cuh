@@ -125,6 +125,10 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 __device__ __forceinline__ void tmem_wait_st(){ asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld(){ asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- register reallocation between warpgroups (all four warps of a warpgroup execute the same instruction) ------------------
+template <int N> __device__ __forceinline__ void setmaxnreg_inc(){ asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" :: "n"(N)); }
+template <int N> __device__ __forceinline__ void setmaxnreg_dec(){ asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(N)); }
+
 // ---- named barrier for a sub-group of the CTA (id 1..15; id 0 is __syncthreads) ---------------------------------------
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads){
     asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");

@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "dense.cuh"
 #include "tcgen05.cuh"
+#include <type_traits>
 
 namespace b200rl {
 
@@ -103,7 +104,10 @@ __device__ __forceinline__ void store_operand(const float4 (&reg)[ITERS], uint8_
 // truncates, so a long chain of dependent MMAs into one accumulator drifts (measured: mean error 1.2e-6 at K = 256 with
 // 96 chained MMAs); with 12 MMAs per chain and the cross-chunk sum in registers the result is as accurate as an fp32
 // FMA loop.
-template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT>
+// NB = 32-column accumulator blocks per thread: 4 for tiles up to 256 columns, 1 for tiles up to 64 columns. The narrow variant has
+// registers to spare and prefetches TWO k chunks ahead: with a short MMA per chunk its loop is otherwise one global-load latency per
+// chunk long (the 256 -> 16 and 64 -> 256 layers of the training workload spent a third of the step there).
+template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT, int NB>
 __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs a, int n_pad, int m_tiles, int n_tiles, int splits, int a_vec, int b_vec){
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -165,11 +169,13 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
     bool aborted = false;
 
     // adds the finished chunk (buffer `buf`, barrier phase `parity`) to the register accumulators
-    auto accumulate = [&](float (&acc)[4][32], uint32_t buf, uint32_t parity){
+    constexpr int SETS = NB == 1 ? 2 : 1;                             // register sets = prefetch distance in chunks
+    constexpr int B_ITERS = NB == 1 ? 2 : 8;                          // 16-byte pieces of a B chunk per thread (64 or 256 rows)
+    auto accumulate = [&](float (&acc)[NB][32], uint32_t buf, uint32_t parity){
         if(!tc::mbar_wait_bounded(chunk_bar + buf, parity, WAIT_LIMIT_CYCLES)) *abort_flag = 1;
         tc::fence_after_thread_sync();
 #pragma unroll
-        for(int bi = 0; bi < 4; bi++){
+        for(int bi = 0; bi < NB; bi++){
             const int cb = col_half + 2 * bi;
             if(cb < n_blocks){
                 uint32_t v[32];
@@ -187,21 +193,27 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
         const int k_begin = z * a.k_per_split, k_end = min(a.K, k_begin + a.k_per_split);
         const int n_chunks = (k_end - k_begin + TC_KC - 1) / TC_KC;
         const int b_rows = min(n_pad, ((a.N - n0) + 15) / 16 * 16);           // rows of the B tile that can hold data
-        float acc[4][32];
+        float acc[NB][32];
 #pragma unroll
-        for(int bi = 0; bi < 4; bi++)
+        for(int bi = 0; bi < NB; bi++)
 #pragma unroll
             for(int j = 0; j < 32; j++) acc[bi][j] = 0.0f;
-        float4 ra[4], rb[8];
-        prefetch_operand<A_KCONTIG, 4>(ra, a.A, a.lda, m0, a.M, TC_M, k_begin, k_end, a_vec != 0, tid);
-        prefetch_operand<B_KCONTIG, 8>(rb, a.B, a.ldb, n0, a.N, b_rows, k_begin, k_end, b_vec != 0, tid);
-
-        for(int c = 0; c < n_chunks; c++){
+        float4 ra[SETS][4], rb[SETS][B_ITERS];
+#pragma unroll
+        for(int p = 0; p < SETS; p++){
+            if(p < n_chunks){
+                prefetch_operand<A_KCONTIG, 4>(ra[p], a.A, a.lda, m0, a.M, TC_M, k_begin + p * TC_KC, k_end, a_vec != 0, tid);
+                prefetch_operand<B_KCONTIG, B_ITERS>(rb[p], a.B, a.ldb, n0, a.N, b_rows, k_begin + p * TC_KC, k_end, b_vec != 0, tid);
+            }
+        }
+        // one k chunk; SET selects the register set at compile time. Returns false when the kernel is aborting.
+        auto chunk_body = [&](auto SET, int c) -> bool {
+            constexpr int P = decltype(SET)::value;
             const uint32_t s = u & 1;
             uint8_t* stage = base + s * stage_bytes;
             // stage s and TMEM buffer s are free: the chunk that used them last (u - 2) was waited for in the previous iteration
-            store_operand<A_KCONTIG, 4>(ra, stage, stage + A_TILE_BYTES, TC_M, tid);
-            store_operand<B_KCONTIG, 8>(rb, stage + 2 * A_TILE_BYTES, stage + 2 * A_TILE_BYTES + b_tile_bytes, b_rows, tid);
+            store_operand<A_KCONTIG, 4>(ra[P], stage, stage + A_TILE_BYTES, TC_M, tid);
+            store_operand<B_KCONTIG, B_ITERS>(rb[P], stage + 2 * A_TILE_BYTES, stage + 2 * A_TILE_BYTES + b_tile_bytes, b_rows, tid);
             if(b_rows < n_pad && c < 2){
                 // rows of the padded tile that never receive data: zero them once per stage and work item
                 for(int idx = tid; idx < (n_pad - b_rows) * 8; idx += TC_THREADS){
@@ -213,16 +225,22 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
             tc::fence_proxy_async_smem();
             tc::fence_before_thread_sync();
             tc::named_barrier_sync(1, TC_THREADS);
-            if(*abort_flag){ aborted = true; break; }
+            if(*abort_flag) return false;
             if(tid == 0) tc::mbar_arrive(full_bar + s);              // the issuing warp takes over from here
-            __syncwarp();
-            if(c + 1 < n_chunks){
-                const int k0 = k_begin + (c + 1) * TC_KC;
-                prefetch_operand<A_KCONTIG, 4>(ra, a.A, a.lda, m0, a.M, TC_M, k0, k_end, a_vec != 0, tid);
-                prefetch_operand<B_KCONTIG, 8>(rb, a.B, a.ldb, n0, a.N, b_rows, k0, k_end, b_vec != 0, tid);
+            if(c + SETS < n_chunks){
+                const int k0 = k_begin + (c + SETS) * TC_KC;
+                prefetch_operand<A_KCONTIG, 4>(ra[P], a.A, a.lda, m0, a.M, TC_M, k0, k_end, a_vec != 0, tid);
+                prefetch_operand<B_KCONTIG, B_ITERS>(rb[P], a.B, a.ldb, n0, a.N, b_rows, k0, k_end, b_vec != 0, tid);
             }
             if(c > 0) accumulate(acc, s ^ 1, ((u - 1) >> 1) & 1);
             u++;
+            return true;
+        };
+        for(int c = 0; c < n_chunks && !aborted; c += SETS){
+            if(!chunk_body(std::integral_constant<int, 0>{}, c)){ aborted = true; break; }
+            if constexpr(SETS == 2){
+                if(c + 1 < n_chunks && !chunk_body(std::integral_constant<int, 1>{}, c + 1)){ aborted = true; break; }
+            }
         }
         if(aborted) break;
         accumulate(acc, (u - 1) & 1, ((u - 1) >> 1) & 1);
@@ -231,7 +249,7 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
         // that each global store instruction writes one full 128-byte row segment ----
         float* patch = reinterpret_cast<float*>(base) + warp * (32 * 33);
 #pragma unroll
-        for(int bi = 0; bi < 4; bi++){
+        for(int bi = 0; bi < NB; bi++){
             const int cb = col_half + 2 * bi;
             if(cb >= n_blocks) continue;
 #pragma unroll
@@ -270,24 +288,29 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
     if(warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <bool A_KC, bool B_KC, int EPI, int ACT>
-static int launch_one(const GemmArgs& a, int splits, cudaStream_t s){
-    int n_pad = (a.N + 15) / 16 * 16;
-    if(n_pad > TC_NMAX) n_pad = TC_NMAX;
+template <bool A_KC, bool B_KC, int EPI, int ACT, int NB>
+static int launch_variant(const GemmArgs& a, int splits, int n_pad, cudaStream_t s){
     const int n_tiles = (a.N + n_pad - 1) / n_pad, m_tiles = (a.M + TC_M - 1) / TC_M;
     const uint32_t smem = 2 * (2 * A_TILE_BYTES + 2 * (uint32_t)n_pad * 128) + 64 + 1024;
-    static uint32_t configured = 0;
-    if(smem > configured){
-        B200RL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<A_KC, B_KC, EPI, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024)));
-        configured = 2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024;
+    static bool configured = false;
+    if(!configured){
+        B200RL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024)));
+        configured = true;
     }
     const long long total = (long long)m_tiles * n_tiles * splits;
     const int grid = (int)(total < NUM_SMS ? total : NUM_SMS);
     auto aligned = [](const float* p, long long ld){ return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld & 3) == 0; };
     const int a_vec = A_KC && aligned(a.A, a.lda) && (a.k_per_split % 4 == 0), b_vec = B_KC && aligned(a.B, a.ldb) && (a.k_per_split % 4 == 0);
-    gemm_tc_kernel<A_KC, B_KC, EPI, ACT><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec);
+    gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec);
     B200RL_LAUNCH_CHECK("gemm_tc");
     return B200RL_OK;
+}
+template <bool A_KC, bool B_KC, int EPI, int ACT>
+static int launch_one(const GemmArgs& a, int splits, cudaStream_t s){
+    int n_pad = (a.N + 15) / 16 * 16;
+    if(n_pad > TC_NMAX) n_pad = TC_NMAX;
+    if(n_pad <= 64) return launch_variant<A_KC, B_KC, EPI, ACT, 1>(a, splits, n_pad, s);
+    return launch_variant<A_KC, B_KC, EPI, ACT, 4>(a, splits, n_pad, s);
 }
 
 int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcontig, bool b_kcontig, int splits, cudaStream_t s){

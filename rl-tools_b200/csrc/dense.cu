@@ -259,6 +259,21 @@ __global__ void __launch_bounds__(256) reduce_bias_partials_kernel(float* dst, c
     }
 }
 
+// dst[i][o] = src[o][i] for a row-major [O, I] matrix (32 x 32 tiles through shared memory, both sides coalesced)
+__global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int O, int I){
+    __shared__ float tile[32][33];
+    const int i0 = blockIdx.x * 32, o0 = blockIdx.y * 32;
+    for(int r = threadIdx.y; r < 32; r += 8){
+        const int o = o0 + r, i = i0 + threadIdx.x;
+        tile[r][threadIdx.x] = (o < O && i < I) ? __ldg(src + (long long)o * I + i) : 0.0f;
+    }
+    __syncthreads();
+    for(int r = threadIdx.y; r < 32; r += 8){
+        const int i = i0 + r, o = o0 + threadIdx.x;
+        if(i < I && o < O) dst[(long long)i * O + o] = tile[threadIdx.x][r];
+    }
+}
+
 // The tensor-core kernel takes the contraction when there is enough work to fill its 128 x 256 tiles on a good part of the SMs:
 // one tile costs ~30 us at K = 256 however few tiles there are, which the CUDA-core kernel's 64 x 64 tiles beat below ~2^27
 // multiply-adds (batch-256 training steps, the 64-wide PPO networks). B200RL_DENSE_KERNEL=simt forces the CUDA-core kernel and
@@ -271,7 +286,9 @@ static bool tc_eligible(long long M, long long N, long long K){
 }
 static bool use_tensor_cores(const GemmArgs& a){ return tc_eligible(a.M, a.N, a.K); }
 
-struct BackwardPlan { int splits; int k_per_split; int bias_segs; int rows_per_seg; size_t bytes; };
+// bytes: split-k and bias partial sums (required when gradients are wanted); wt_bytes: room for the transposed weights behind them,
+// which lets the input-gradient GEMM of the tensor-core path read both operands with 16-byte loads (used when the scratch has it)
+struct BackwardPlan { int splits; int k_per_split; int bias_segs; int rows_per_seg; size_t bytes; size_t wt_bytes; };
 static BackwardPlan plan_backward(int B, int I, int O){
     BackwardPlan p;
     // weight gradient = contraction over the batch: split it so that every SM has work (tile shape of the kernel that will run)
@@ -295,6 +312,8 @@ static BackwardPlan plan_backward(int B, int I, int O){
     p.bytes = 0;
     if(p.splits > 1) p.bytes += sizeof(float) * (size_t)p.splits * O * I;
     if(p.bias_segs > 1) p.bytes += sizeof(float) * (size_t)p.bias_segs * O;
+    p.bytes = (p.bytes + 15) / 16 * 16;
+    p.wt_bytes = tc_eligible(B, I, O) ? sizeof(float) * (size_t)O * I : 0;
     return p;
 }
 
@@ -359,7 +378,19 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         GemmArgs a{};
         a.A = d_out; a.lda = ldd; a.B = W; a.ldb = I; a.M = B; a.N = I; a.K = O; a.k_per_split = O;
         a.C = d_in; a.ldc = ldi;
-        int rc_tc = use_tensor_cores(a) ? launch_gemm_tc(a, EPI_STORE, 0, true, false, 1, s) : B200RL_ERR_UNSUPPORTED;
+        int rc_tc = B200RL_ERR_UNSUPPORTED;
+        if(use_tensor_cores(a)){
+            if(p.wt_bytes > 0 && scratch != nullptr && scratch_bytes >= p.bytes + p.wt_bytes){
+                // W^T once (256 KB for a 256 x 256 layer), then both operands are k-contiguous: 16-byte loads instead of four strided ones
+                float* Wt = reinterpret_cast<float*>(static_cast<char*>(scratch) + p.bytes);
+                transpose_kernel<<<dim3((I + 31) / 32, (O + 31) / 32), dim3(32, 8), 0, s>>>(W, Wt, O, I);
+                B200RL_LAUNCH_CHECK("transpose_W");
+                a.B = Wt; a.ldb = O;
+                rc_tc = launch_gemm_tc(a, EPI_STORE, 0, true, true, 1, s);
+                if(rc_tc == B200RL_ERR_UNSUPPORTED){ a.B = W; a.ldb = I; }
+            }
+            if(rc_tc == B200RL_ERR_UNSUPPORTED) rc_tc = launch_gemm_tc(a, EPI_STORE, 0, true, false, 1, s);
+        }
         if(rc_tc != B200RL_OK && rc_tc != B200RL_ERR_UNSUPPORTED) return rc_tc;
         if(rc_tc == B200RL_ERR_UNSUPPORTED){
             B200RL_LAUNCH_SIMT_GEMM(true, false, EPI_STORE, 0, a, 1, s);
@@ -391,7 +422,8 @@ int b200rl_dense_forward(const float* W, const float* bias, const float* x, int 
 
 size_t b200rl_dense_backward_scratch_bytes(int batch, int input_dim, int output_dim){
     if(batch < 1 || input_dim < 1 || output_dim < 1) return 0;
-    return plan_backward(batch, input_dim, output_dim).bytes;
+    const BackwardPlan p = plan_backward(batch, input_dim, output_dim);
+    return p.bytes + p.wt_bytes;
 }
 
 int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
@@ -486,7 +518,7 @@ int b200rl_mlp_forward(const b200rl_mlp_shape* sh, const float* params, const fl
 size_t b200rl_mlp_backward_scratch_bytes(const b200rl_mlp_shape* sh, int batch){
     if(!valid_shape(sh) || batch < 1) return 0;
     size_t m = 0; int I = sh->input_dim;
-    for(int l = 0; l < sh->n_layers; l++){ size_t b = plan_backward(batch, I, sh->dims[l]).bytes; if(b > m) m = b; I = sh->dims[l]; }
+    for(int l = 0; l < sh->n_layers; l++){ const BackwardPlan p = plan_backward(batch, I, sh->dims[l]); const size_t b = p.bytes + p.wt_bytes; if(b > m) m = b; I = sh->dims[l]; }
     return m;
 }
 

@@ -319,6 +319,7 @@ int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcont
         B200RL_DISPATCH_ACT(activation, return (launch_one<true, true, EPI_FORWARD, ACT>(a, 1, s)));
     }
     if(epilogue == EPI_STORE && a_kcontig && !b_kcontig) return launch_one<true, false, EPI_STORE, 0>(a, 1, s);
+    if(epilogue == EPI_STORE && a_kcontig && b_kcontig) return launch_one<true, true, EPI_STORE, 0>(a, 1, s);
     if(epilogue == EPI_ACCUMULATE && !a_kcontig && !b_kcontig) return launch_one<false, false, EPI_ACCUMULATE, 0>(a, splits, s);
     return B200RL_ERR_UNSUPPORTED;
 }

@@ -83,6 +83,69 @@ __device__ __forceinline__ void prefetch_operand(float4 (&reg)[ITERS], const flo
         reg[it] = v;
     }
 }
+// Rows contiguous in memory (k is the strided index), 16-byte aligned: a thread takes a 4-row x 4-k block with four 16-byte loads
+// ALONG THE ROWS (one per k) instead of sixteen scalar loads; store_operand_blocks transposes the block in registers. Block g of the
+// chunk = (k piece c = g % 8, row quad r4 = g / 8): c is the fast index so that the later 16-byte shared-memory stores of a warp cover
+// every swizzled piece of four rows (no bank conflicts).
+template <int ITERS>
+__device__ __forceinline__ void prefetch_operand_blocks(float4 (&reg)[ITERS], const float* __restrict__ P, long long ld, int row0, int row_limit, int rows,
+                                                        int k0, int k_end, int tid){
+    static_assert(ITERS % 4 == 0);
+#pragma unroll
+    for(int j = 0; j < ITERS / 4; j++){
+        const int g = tid + j * TC_THREADS, c = g & 7, r4 = g >> 3;
+        const int gr = row0 + r4 * 4;
+#pragma unroll
+        for(int kk = 0; kk < 4; kk++){
+            const int gk = k0 + c * 4 + kk;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if(r4 * 4 < rows && gk < k_end){
+                const float* src = P + (long long)gk * ld + gr;
+                if(gr + 3 < row_limit) v = __ldg(reinterpret_cast<const float4*>(src));
+                else{
+                    if(gr + 0 < row_limit) v.x = __ldg(src + 0);
+                    if(gr + 1 < row_limit) v.y = __ldg(src + 1);
+                    if(gr + 2 < row_limit) v.z = __ldg(src + 2);
+                }
+            }
+            reg[j * 4 + kk] = v;
+        }
+    }
+}
+template <int ITERS>
+__device__ __forceinline__ void store_operand_blocks(const float4 (&reg)[ITERS], uint8_t* hi_tile, uint8_t* lo_tile, int rows, int tid){
+#pragma unroll
+    for(int j = 0; j < ITERS / 4; j++){
+        const int g = tid + j * TC_THREADS, c = g & 7, r4 = g >> 3;
+        if(r4 * 4 < rows){
+            const float col[4][4] = {{reg[j * 4 + 0].x, reg[j * 4 + 1].x, reg[j * 4 + 2].x, reg[j * 4 + 3].x},
+                                     {reg[j * 4 + 0].y, reg[j * 4 + 1].y, reg[j * 4 + 2].y, reg[j * 4 + 3].y},
+                                     {reg[j * 4 + 0].z, reg[j * 4 + 1].z, reg[j * 4 + 2].z, reg[j * 4 + 3].z},
+                                     {reg[j * 4 + 0].w, reg[j * 4 + 1].w, reg[j * 4 + 2].w, reg[j * 4 + 3].w}};
+#pragma unroll
+            for(int rr = 0; rr < 4; rr++){
+                const int r = r4 * 4 + rr;
+                float4 h, l;
+                split_rn(col[rr][0], h.x, l.x); split_rn(col[rr][1], h.y, l.y); split_rn(col[rr][2], h.z, l.z); split_rn(col[rr][3], h.w, l.w);
+                const uint32_t off = (uint32_t)r * 128 + ((uint32_t)(c ^ (r & 7)) << 4);
+                *reinterpret_cast<float4*>(hi_tile + off) = h;
+                *reinterpret_cast<float4*>(lo_tile + off) = l;
+            }
+        }
+    }
+}
+// dispatch between the two forms (blocks = rows contiguous, aligned, enough registers for whole 4 x 4 blocks)
+template <bool KCONTIG, int ITERS>
+__device__ __forceinline__ void fetch_chunk(float4 (&reg)[ITERS], const float* __restrict__ P, long long ld, int row0, int row_limit, int rows,
+                                            int k0, int k_end, bool vec_ok, int tid){
+    if constexpr(!KCONTIG && ITERS % 4 == 0){
+        if(vec_ok){ prefetch_operand_blocks<ITERS>(reg, P, ld, row0, row_limit, rows, k0, k_end, tid); return; }
+    }
+    prefetch_operand<KCONTIG, ITERS>(reg, P, ld, row0, row_limit, rows, k0, k_end, vec_ok, tid);
+}
+template <bool KCONTIG, int ITERS>
+__device__ __forceinline__ void stage_chunk(const float4 (&reg)[ITERS], uint8_t* hi_tile, uint8_t* lo_tile, int rows, bool vec_ok, int tid);
+
 template <bool KCONTIG, int ITERS>
 __device__ __forceinline__ void store_operand(const float4 (&reg)[ITERS], uint8_t* hi_tile, uint8_t* lo_tile, int rows, int tid){
 #pragma unroll
@@ -97,6 +160,14 @@ __device__ __forceinline__ void store_operand(const float4 (&reg)[ITERS], uint8_
             *reinterpret_cast<float4*>(lo_tile + off) = l;
         }
     }
+}
+
+template <bool KCONTIG, int ITERS>
+__device__ __forceinline__ void stage_chunk(const float4 (&reg)[ITERS], uint8_t* hi_tile, uint8_t* lo_tile, int rows, bool vec_ok, int tid){
+    if constexpr(!KCONTIG && ITERS % 4 == 0){
+        if(vec_ok){ store_operand_blocks<ITERS>(reg, hi_tile, lo_tile, rows, tid); return; }
+    }
+    store_operand<KCONTIG, ITERS>(reg, hi_tile, lo_tile, rows, tid);
 }
 
 // Per k chunk the tensor core starts a FRESH accumulator (alternating between two 256-column TMEM buffers) and the
@@ -202,8 +273,8 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
 #pragma unroll
         for(int p = 0; p < SETS; p++){
             if(p < n_chunks){
-                prefetch_operand<A_KCONTIG, 4>(ra[p], a.A, a.lda, m0, a.M, TC_M, k_begin + p * TC_KC, k_end, a_vec != 0, tid);
-                prefetch_operand<B_KCONTIG, B_ITERS>(rb[p], a.B, a.ldb, n0, a.N, b_rows, k_begin + p * TC_KC, k_end, b_vec != 0, tid);
+                fetch_chunk<A_KCONTIG, 4>(ra[p], a.A, a.lda, m0, a.M, TC_M, k_begin + p * TC_KC, k_end, a_vec != 0, tid);
+                fetch_chunk<B_KCONTIG, B_ITERS>(rb[p], a.B, a.ldb, n0, a.N, b_rows, k_begin + p * TC_KC, k_end, b_vec != 0, tid);
             }
         }
         // one k chunk; SET selects the register set at compile time. Returns false when the kernel is aborting.
@@ -212,8 +283,8 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
             const uint32_t s = u & 1;
             uint8_t* stage = base + s * stage_bytes;
             // stage s and TMEM buffer s are free: the chunk that used them last (u - 2) was waited for in the previous iteration
-            store_operand<A_KCONTIG, 4>(ra[P], stage, stage + A_TILE_BYTES, TC_M, tid);
-            store_operand<B_KCONTIG, B_ITERS>(rb[P], stage + 2 * A_TILE_BYTES, stage + 2 * A_TILE_BYTES + b_tile_bytes, b_rows, tid);
+            stage_chunk<A_KCONTIG, 4>(ra[P], stage, stage + A_TILE_BYTES, TC_M, a_vec != 0, tid);
+            stage_chunk<B_KCONTIG, B_ITERS>(rb[P], stage + 2 * A_TILE_BYTES, stage + 2 * A_TILE_BYTES + b_tile_bytes, b_rows, b_vec != 0, tid);
             if(b_rows < n_pad && c < 2){
                 // rows of the padded tile that never receive data: zero them once per stage and work item
                 for(int idx = tid; idx < (n_pad - b_rows) * 8; idx += TC_THREADS){
@@ -229,8 +300,8 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
             if(tid == 0) tc::mbar_arrive(full_bar + s);              // the issuing warp takes over from here
             if(c + SETS < n_chunks){
                 const int k0 = k_begin + (c + SETS) * TC_KC;
-                prefetch_operand<A_KCONTIG, 4>(ra[P], a.A, a.lda, m0, a.M, TC_M, k0, k_end, a_vec != 0, tid);
-                prefetch_operand<B_KCONTIG, B_ITERS>(rb[P], a.B, a.ldb, n0, a.N, b_rows, k0, k_end, b_vec != 0, tid);
+                fetch_chunk<A_KCONTIG, 4>(ra[P], a.A, a.lda, m0, a.M, TC_M, k0, k_end, a_vec != 0, tid);
+                fetch_chunk<B_KCONTIG, B_ITERS>(rb[P], a.B, a.ldb, n0, a.N, b_rows, k0, k_end, b_vec != 0, tid);
             }
             if(c > 0) accumulate(acc, s ^ 1, ((u - 1) >> 1) & 1);
             u++;
@@ -300,7 +371,9 @@ static int launch_variant(const GemmArgs& a, int splits, int n_pad, cudaStream_t
     const long long total = (long long)m_tiles * n_tiles * splits;
     const int grid = (int)(total < NUM_SMS ? total : NUM_SMS);
     auto aligned = [](const float* p, long long ld){ return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld & 3) == 0; };
-    const int a_vec = A_KC && aligned(a.A, a.lda) && (a.k_per_split % 4 == 0), b_vec = B_KC && aligned(a.B, a.ldb) && (a.k_per_split % 4 == 0);
+    // k-contiguous operands: 16-byte loads along k need an aligned base, pitch and k range; row-contiguous operands: 16-byte loads along
+    // the rows need an aligned base and pitch (tile origins are multiples of 16 rows)
+    const int a_vec = aligned(a.A, a.lda) && (!A_KC || a.k_per_split % 4 == 0), b_vec = aligned(a.B, a.ldb) && (!B_KC || a.k_per_split % 4 == 0);
     gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec);
     B200RL_LAUNCH_CHECK("gemm_tc");
     return B200RL_OK;

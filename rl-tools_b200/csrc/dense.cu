@@ -292,8 +292,10 @@ struct BackwardPlan { int splits; int k_per_split; int bias_segs; int rows_per_s
 static BackwardPlan plan_backward(int B, int I, int O){
     BackwardPlan p;
     // weight gradient = contraction over the batch: split it so that every SM has work (tile shape of the kernel that will run)
-    const bool tc = tc_eligible(O, I, B);
-    int tiles = tc ? ((O + 127) / 128) * ((I + 255) / 256) : ((O + BM - 1) / BM) * ((I + BN - 1) / BN);
+    // fewer than 64 output rows (e.g. a 16-wide last layer): the tensor-core kernel computes dW^T instead (rows = input features)
+    const bool tc_direct = tc_eligible(O, I, B), tc_swapped = !tc_direct && tc_eligible(I, O, B);
+    const bool tc = tc_direct || tc_swapped;
+    int tiles = tc_direct ? ((O + 127) / 128) * ((I + 255) / 256) : tc_swapped ? ((I + 127) / 128) * ((O + 255) / 256) : ((O + BM - 1) / BM) * ((I + BN - 1) / BN);
     int want = tc ? (NUM_SMS + tiles - 1) / tiles : (2 * NUM_SMS + tiles - 1) / tiles;
     // at least 256 batch rows per split for the tensor-core kernel (8 chunks amortise its tile setup), 64 for the CUDA-core kernel:
     // small batches (256 ... 2048 rows) would otherwise run on a handful of CTAs and be bound by the latency of their k loop
@@ -361,7 +363,13 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         GemmArgs a{};
         a.A = d_out; a.lda = ldd; a.B = x; a.ldb = ldx; a.M = O; a.N = I; a.K = B; a.k_per_split = p.k_per_split;
         a.C = dW; a.ldc = I; a.partial = w_partial;
-        int rc_tc = use_tensor_cores(a) ? launch_gemm_tc(a, EPI_ACCUMULATE, 0, false, false, p.splits, s) : B200RL_ERR_UNSUPPORTED;
+        int rc_tc = B200RL_ERR_UNSUPPORTED;
+        if(use_tensor_cores(a)) rc_tc = launch_gemm_tc(a, EPI_ACCUMULATE, 0, false, false, p.splits, s);
+        else if(tc_eligible(I, O, B)){
+            GemmArgs t = a;                        // dW^T[i][o] = sum_b x[b][i] * d_pre[b][o], stored transposed into dW / the partials
+            t.A = x; t.lda = ldx; t.B = d_out; t.ldb = ldd; t.M = I; t.N = O; t.transpose_c = 1;
+            rc_tc = launch_gemm_tc(t, EPI_ACCUMULATE, 0, false, false, p.splits, s);
+        }
         if(rc_tc != B200RL_OK && rc_tc != B200RL_ERR_UNSUPPORTED) return rc_tc;
         if(rc_tc == B200RL_ERR_UNSUPPORTED){
             B200RL_LAUNCH_SIMT_GEMM(false, false, EPI_ACCUMULATE, 0, a, p.splits, s);

@@ -16,6 +16,7 @@ struct GemmArgs {
     float* pre; long long ldpre;     // EPI_FORWARD (nullable)
     float* C; long long ldc;         // output (EPI_FORWARD: y, EPI_STORE: C, EPI_ACCUMULATE with gridDim.z == 1: C += acc)
     float* partial;                  // EPI_ACCUMULATE with gridDim.z > 1: partial[z][M*N] (dense, ld = N)
+    int transpose_c;                 // EPI_ACCUMULATE on the tensor-core path only: the result is C^T, i.e. C[n][m] (and partial[z][n][m])
 };
 
 

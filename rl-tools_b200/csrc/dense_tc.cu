@@ -343,8 +343,14 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
                     a.C[(long long)m * a.ldc + n] = x;
                 }
                 else{
-                    if(splits == 1) a.C[(long long)m * a.ldc + n] += x;
-                    else a.partial[((long long)z * a.M + m) * a.N + n] = x;
+                    if(a.transpose_c){
+                        if(splits == 1) a.C[(long long)n * a.ldc + m] += x;
+                        else a.partial[((long long)z * a.N + n) * a.M + m] = x;
+                    }
+                    else{
+                        if(splits == 1) a.C[(long long)m * a.ldc + n] += x;
+                        else a.partial[((long long)z * a.M + m) * a.N + n] = x;
+                    }
                 }
             }
             __syncwarp();

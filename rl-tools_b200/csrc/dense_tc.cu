@@ -179,7 +179,7 @@ __device__ __forceinline__ void stage_chunk(const float4 (&reg)[ITERS], uint8_t*
 // registers to spare and prefetches TWO k chunks ahead: with a short MMA per chunk its loop is otherwise one global-load latency per
 // chunk long (the 256 -> 16 and 64 -> 256 layers of the training workload spent a third of the step there).
 template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT, int NB>
-__global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs a, int n_pad, int m_tiles, int n_tiles, int splits, int a_vec, int b_vec){
+__global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs a, int n_pad, int m_tiles, int n_tiles, int splits, int a_vec, int b_vec, int c_vec){
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -316,13 +316,75 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
         if(aborted) break;
         accumulate(acc, (u - 1) & 1, ((u - 1) >> 1) & 1);
 
-        // ---- epilogue: transposition through a warp-private 32 x 33 patch (stage 0 is free: every MMA has completed), so
+        // ---- epilogue, vector form (forward / plain store with 16-byte aligned rows): the warp transposes each 32 x 32 block through a
+        // private shared-memory patch with 16-byte accesses on both sides (row pitch 36 floats: conflict-free for both the row-wise
+        // writes and the 8-lanes-per-row reads), so that every global store instruction writes four full 128-byte lines.
+        // (The scalar form below issues 32 four-byte-per-lane stores per block and output: ~16 k cycles per 128 x 256 tile. Measured
+        // and not kept: storing straight from the accumulator registers, 16 bytes per lane and one row per lane -- every instruction then
+        // touches 32 half-filled sectors and the 256 -> 256 forward went from 114 to 167 us.) ----
+        bool direct = false;
+        if constexpr(EPI != EPI_ACCUMULATE) direct = (c_vec & 1) && (EPI != EPI_FORWARD || a.pre == nullptr || (c_vec & 2));
+        if(direct){
+            float* vpatch = reinterpret_cast<float*>(base) + warp * (32 * 36);
+            const int g = lane & 7, rsub = lane >> 3;
+#pragma unroll
+            for(int bi = 0; bi < NB; bi++){
+                const int cb = col_half + 2 * bi;
+                if(cb >= n_blocks) continue;
+#pragma unroll
+                for(int j4 = 0; j4 < 8; j4++)
+                    *reinterpret_cast<float4*>(vpatch + lane * 36 + 4 * j4) = make_float4(acc[bi][4 * j4], acc[bi][4 * j4 + 1], acc[bi][4 * j4 + 2], acc[bi][4 * j4 + 3]);
+                __syncwarp();
+                const int n = n0 + cb * 32 + 4 * g;
+                const bool n_ok = cb * 32 + 4 * g < n_pad && n < a.N, full = n + 3 < a.N;
+                float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+                if constexpr(EPI == EPI_FORWARD){
+                    if(n_ok){
+                        if(full && (c_vec & 4)){ const float4 b4 = __ldg(reinterpret_cast<const float4*>(a.bias + n)); bias4[0] = b4.x; bias4[1] = b4.y; bias4[2] = b4.z; bias4[3] = b4.w; }
+                        else{
+#pragma unroll
+                            for(int e = 0; e < 4; e++) if(n + e < a.N) bias4[e] = __ldg(a.bias + n + e);
+                        }
+                    }
+                }
+#pragma unroll
+                for(int it = 0; it < 8; it++){
+                    const int r = 4 * it + rsub, m = m0 + q * 32 + r;
+                    if(m < a.M && n_ok){
+                        const float4 v = *reinterpret_cast<const float4*>(vpatch + r * 36 + 4 * g);
+                        float x[4] = {v.x, v.y, v.z, v.w};
+                        float* crow = a.C + (long long)m * a.ldc + n;
+                        if constexpr(EPI == EPI_FORWARD){
+#pragma unroll
+                            for(int e = 0; e < 4; e++) x[e] += bias4[e];
+                            if(a.pre){
+                                float* prow = a.pre + (long long)m * a.ldpre + n;
+                                if(full) *reinterpret_cast<float4*>(prow) = make_float4(x[0], x[1], x[2], x[3]);
+                                else{
+#pragma unroll
+                                    for(int e = 0; e < 4; e++) if(n + e < a.N) prow[e] = x[e];
+                                }
+                            }
+#pragma unroll
+                            for(int e = 0; e < 4; e++) x[e] = activation<ACT>(x[e]);
+                        }
+                        if(full) *reinterpret_cast<float4*>(crow) = make_float4(x[0], x[1], x[2], x[3]);
+                        else{
+#pragma unroll
+                            for(int e = 0; e < 4; e++) if(n + e < a.N) crow[e] = x[e];
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        // ---- epilogue, transposing form: through a warp-private 32 x 33 patch (stage 0 is free: every MMA has completed), so
         // that each global store instruction writes one full 128-byte row segment ----
         float* patch = reinterpret_cast<float*>(base) + warp * (32 * 33);
 #pragma unroll
         for(int bi = 0; bi < NB; bi++){
             const int cb = col_half + 2 * bi;
-            if(cb >= n_blocks) continue;
+            if(cb >= n_blocks || direct) continue;
 #pragma unroll
             for(int j = 0; j < 32; j++) patch[lane * 33 + j] = acc[bi][j];
             __syncwarp();
@@ -380,7 +442,9 @@ static int launch_variant(const GemmArgs& a, int splits, int n_pad, cudaStream_t
     // k-contiguous operands: 16-byte loads along k need an aligned base, pitch and k range; row-contiguous operands: 16-byte loads along
     // the rows need an aligned base and pitch (tile origins are multiples of 16 rows)
     const int a_vec = aligned(a.A, a.lda) && (!A_KC || a.k_per_split % 4 == 0), b_vec = aligned(a.B, a.ldb) && (!B_KC || a.k_per_split % 4 == 0);
-    gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec);
+    const int c_vec = (aligned(a.C, a.ldc) ? 1 : 0) | ((a.pre == nullptr || aligned(a.pre, a.ldpre)) ? 2 : 0) |
+                      ((a.bias != nullptr && (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0) ? 4 : 0);
+    gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec, c_vec);
     B200RL_LAUNCH_CHECK("gemm_tc");
     return B200RL_OK;
 }

@@ -575,8 +575,11 @@ def main():
     if rank == 0:
         peaks = measured_peaks()
         achieved_tflops = FLOP_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e12
+        # dram__bytes_read + dram__bytes_write of one full-size launch from the committed ncu capture (profiles/rollout_tc_kernel_65536env.md);
+        # other sizes were not captured
+        traffic = 205.2e6 if (N_ENVS, N_STEPS) == (65536, 200) else None
         roofline = {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved_tflops / peaks["tflops"],
-                    "traffic": None, "peak_source": peaks["source"] + " bf16 dense (burst)",
+                    "traffic": traffic, "peak_source": peaks["source"] + " bf16 dense (burst)",
                     "hbm_write_gbs": BYTES_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]}
         cpu = None if args.no_cpu_baseline else cpu_reference_rate()
         line = {"metric": "env-steps/s (fused actor fwd + env step)", "value": value, "unit": "env-steps/s", "n_gpus": world, "steps": args.steps,

@@ -218,13 +218,27 @@ def run_mlp_train(args):
         flop = 876544.0 * rows                     # per GPU: the roofline compares one GPU's kernels with one GPU's peak
         peaks = measured_peaks()
         launches = steps * ((rows // chunk) * (4 + 1 + 4 * 3 + 3) + 2)
+        cpu = None
+        if not args.no_cpu_baseline:
+            import numpy as np
+            import oracle
+            if os.path.exists(oracle.REF_FAST_SO):
+                # the reference's own forward + MSE gradient + backward + Adam on its CPU_OPENBLAS device, batch 1024 (its largest instantiated
+                # batch of this network), all host threads
+                os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
+                ref = oracle.Reference("fast")
+                rs = np.random.RandomState(0)
+                xs, ys = rs.randn(1024, 64).astype(np.float32), rs.randn(1024, 16).astype(np.float32)
+                res = ref.mlp_run("c5_b1024", net.params.cpu().numpy(), xs, ys, 2, 200)
+                cpu = {"value": 200 * 1024 / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
+                       "sample": "200 train steps (forward, mse gradient, backward, Adam) at batch 1024 of the same network, CPU_OPENBLAS build"}
         print(json.dumps({"metric": "MLP fwd+bwd+Adam samples/s", "value": rows * world / (ms * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": steps,
                           "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                           "config": {"workload": f"mlp_train_64-256-256-256-16_rows{rows * world}", "chunk_rows": chunk, "parallelism": f"dp{world}, one NCCL all-reduce of the 609 KB gradient arena per step",
                                      "l2": "inputs (>= 4 GB per pass) exceed L2"},
                           "roofline": {"bound": "tensor", "achieved": flop / (ms * 1e-3) / 1e12, "peak": peaks["tflops"], "unit": "TFLOP/s",
                                        "frac": flop / (ms * 1e-3) / 1e12 / peaks["tflops"], "traffic": None, "peak_source": peaks["source"] + " bf16 dense (burst)"},
-                          "gpu_launches": launches}))
+                          "cpu_baseline": cpu, "gpu_launches": launches}))
     if dist is not None:
         dist.destroy_process_group()
 

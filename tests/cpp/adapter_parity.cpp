@@ -11,13 +11,16 @@
 #include <rl_tools/nn/layers/dense/operations_cpu.h>
 #include <rl_tools/nn/loss_functions/mse/operations_generic.h>
 #include <rl_tools/nn_models/mlp/operations_generic.h>
-#include <rl_tools/nn/optimizers/adam/operations_generic.h>
-#include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/nn_models/mlp_unconditional_stddev/operations_generic.h>
 #include <rl_tools/nn_models/sequential/operations_generic.h>
+#include <rl_tools/nn/optimizers/adam/operations_generic.h>      // after every model type it steps (same rule as for the reference's own devices)
+#include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
+#include <rl_tools/rl/algorithms/ppo/ppo.h>
+#include <rl_tools/rl/algorithms/ppo/operations_generic.h>
 #include <b200rl/rl_tools_operations.h>
 #include <b200rl/rl_tools_on_policy_runner.h>
+#include <b200rl/rl_tools_ppo.h>
 
 #include <cstdio>
 #include <cmath>
@@ -161,6 +164,86 @@ void collect_parity(const char* name){
     rlt::free(cpu, envs); rlt::free(cpu, env_parameters);
 }
 
+// PPO update: the reference's train() + estimate_generalized_advantages on the CPU device against the overloads on devices::B200, on the same
+// randomly filled dataset matrix, same initial networks, same engine seed (epoch shuffle on). The shuffled dataset must be identical (data
+// movement only), advantages / target values bit-identical (same arithmetic per element), network parameters within the drift of
+// EPOCHS x BATCHES Adam steps.
+template <TI BATCH, TI EPOCHS>
+struct PpoParityParameters: rlt::rl::algorithms::ppo::DefaultParameters<TYPE_POLICY, TI, BATCH>{
+    static constexpr TI N_EPOCHS = EPOCHS;
+};
+template <TI N, TI STEPS, TI BATCH, TI EPOCHS>
+void ppo_parity(const char* name){
+    using PENDULUM = rlt::rl::environments::Pendulum<rlt::rl::environments::pendulum::Specification<T, TI, rlt::rl::environments::pendulum::DefaultParameters<T>>>;
+    using CAPABILITY = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
+    using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, BATCH, 3>;
+    using MLP_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::IDENTITY>;
+    using ACTOR = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp_unconditional_stddev::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
+    using CRITIC = rlt::nn_models::sequential::Build<CAPABILITY, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<MLP_CONFIG>>, INPUT_SHAPE>;
+    using PARAMETERS = PpoParityParameters<BATCH, EPOCHS>;
+    using PPO_SPEC = rlt::rl::algorithms::ppo::Specification<TYPE_POLICY, TI, PENDULUM, ACTOR, CRITIC, PARAMETERS>;
+    using PPO = rlt::rl::algorithms::PPO<PPO_SPEC>;
+    using PPO_BUFFERS = rlt::rl::algorithms::ppo::Buffers<rlt::rl::algorithms::ppo::BufferSpecification<PPO_SPEC>>;
+    using RUNNER_SPEC = rlt::rl::components::on_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, typename ACTOR::template State<>, N, 100>;
+    using DATASET = rlt::rl::components::on_policy_runner::Dataset<rlt::rl::components::on_policy_runner::DatasetSpecification<RUNNER_SPEC, STEPS>>;
+    using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
+    DEVICE_CPU cpu; DEVICE_GPU gpu;
+    rlt::init(gpu);
+    DEVICE_CPU::SPEC::RANDOM::ENGINE<> rng_init, rng_cpu, rng_gpu;
+    rlt::malloc(cpu, rng_init); rlt::malloc(cpu, rng_cpu); rlt::malloc(cpu, rng_gpu);
+    rlt::init(cpu, rng_init, 11); rlt::init(cpu, rng_cpu, 5); rlt::init(cpu, rng_gpu, 5);
+    PPO ppo_cpu, ppo_gpu, ppo_back; PPO_BUFFERS pb_cpu, pb_gpu; DATASET ds_cpu, ds_gpu, ds_back;
+    OPTIMIZER ao_cpu, co_cpu, ao_gpu, co_gpu;
+    typename ACTOR::template Buffer<> ab_cpu, ab_gpu; typename CRITIC::template Buffer<> cb_cpu, cb_gpu;
+    rlt::malloc(cpu, ppo_cpu); rlt::malloc(cpu, ppo_back); rlt::malloc(cpu, pb_cpu); rlt::malloc(cpu, ds_cpu); rlt::malloc(cpu, ds_back);
+    rlt::malloc(cpu, ao_cpu); rlt::malloc(cpu, co_cpu); rlt::malloc(cpu, ab_cpu); rlt::malloc(cpu, cb_cpu);
+    rlt::malloc(gpu, ppo_gpu); rlt::malloc(gpu, pb_gpu); rlt::malloc(gpu, ds_gpu);
+    rlt::malloc(gpu, ao_gpu); rlt::malloc(gpu, co_gpu); rlt::malloc(gpu, ab_gpu); rlt::malloc(gpu, cb_gpu);
+    rlt::init(cpu, ppo_cpu, ao_cpu, co_cpu, rng_init);
+    rlt::init(gpu, ao_gpu); rlt::init(gpu, co_gpu);
+    rlt::copy(cpu, gpu, ppo_cpu.actor, ppo_gpu.actor); rlt::copy(cpu, gpu, ppo_cpu.critic, ppo_gpu.critic);
+    rlt::reset_optimizer_state(gpu, ao_gpu, ppo_gpu.actor); rlt::reset_optimizer_state(gpu, co_gpu, ppo_gpu.critic);
+    // a synthetic dataset matrix: train() and the advantage estimate consume any values; flags are 0 / 1
+    rlt::randn(cpu, ds_cpu.data, rng_init);
+    for(TI r = 0; r < (STEPS + 1) * N; r++){
+        rlt::set(ds_cpu.data, r, 5, rlt::get(ds_cpu.data, r, 5) * (T)0.3 - (T)1.2);                 // rollout log-probabilities
+        rlt::set(ds_cpu.data, r, 7, (T)0); rlt::set(ds_cpu.data, r, 8, (T)((r / N) % 20 == 19)); rlt::set(ds_cpu.data, r, 9, (T)0);
+    }
+    rlt::copy(cpu, gpu, ds_cpu.data, ds_gpu.data);
+    rlt::estimate_generalized_advantages(cpu, ds_cpu, PARAMETERS{});
+    rlt::estimate_generalized_advantages(gpu, ds_gpu, PARAMETERS{});
+    rlt::copy(gpu, cpu, ds_gpu.data, ds_back.data);
+    T gae_diff = rlt::abs_diff(cpu, ds_cpu.data, ds_back.data);
+    rlt::train(cpu, ppo_cpu, ds_cpu, ao_cpu, co_cpu, pb_cpu, ab_cpu, cb_cpu, rng_cpu);
+    rlt::train(gpu, ppo_gpu, ds_gpu, ao_gpu, co_gpu, pb_gpu, ab_gpu, cb_gpu, rng_gpu);
+    int status = rlt::check_status(gpu);
+    rlt::copy(gpu, cpu, ds_gpu.data, ds_back.data);
+    T shuffle_diff = rlt::abs_diff(cpu, ds_cpu.data, ds_back.data);
+    rlt::copy(gpu, cpu, ppo_gpu.actor, ppo_back.actor); rlt::copy(gpu, cpu, ppo_gpu.critic, ppo_back.critic);
+    // mean absolute parameter difference (weights + biases of the three layers + log_std); Adam moves a parameter by ~1e-3 per step
+    double actor_diff = 0, critic_diff = 0, count = 0;
+    auto layer_diff = [&](auto& a, auto& b){
+        double d = rlt::abs_diff(cpu, a.weights.parameters, b.weights.parameters) + rlt::abs_diff(cpu, a.biases.parameters, b.biases.parameters);
+        return d;
+    };
+    { auto& a = ppo_cpu.actor.content; auto& b = ppo_back.actor.content;
+      actor_diff = layer_diff(a.input_layer, b.input_layer) + layer_diff(a.hidden_layers[0], b.hidden_layers[0]) + layer_diff(a.output_layer, b.output_layer)
+                   + std::fabs((double)rlt::get(cpu, a.log_std.parameters, 0) - (double)rlt::get(cpu, b.log_std.parameters, 0)); }
+    { auto& a = ppo_cpu.critic.content; auto& b = ppo_back.critic.content;
+      critic_diff = layer_diff(a.input_layer, b.input_layer) + layer_diff(a.hidden_layers[0], b.hidden_layers[0]) + layer_diff(a.output_layer, b.output_layer); }
+    count = 3 * 64 + 64 + 64 * 64 + 64 + 64 + 1;
+    actor_diff /= count + 1; critic_diff /= count;
+    bool engines = rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_cpu) == rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_gpu);
+    bool ok = status == 0 && gae_diff == 0 && shuffle_diff == 0 && engines && actor_diff < 2e-6 && critic_diff < 2e-6;
+    std::printf("%-28s envs %3u steps %3u batch %4u epochs %u  status %d  gae diff %.1e  shuffled dataset diff %.1e  engine %d  mean actor diff %.2e  mean critic diff %.2e  %s\n",
+                name, N, STEPS, BATCH, EPOCHS, status, gae_diff, shuffle_diff, (int)engines, actor_diff, critic_diff, ok ? "OK" : "FAIL");
+    if(!ok) failures++;
+    rlt::free(cpu, ppo_cpu); rlt::free(cpu, ppo_back); rlt::free(cpu, pb_cpu); rlt::free(cpu, ds_cpu); rlt::free(cpu, ds_back);
+    rlt::free(cpu, ao_cpu); rlt::free(cpu, co_cpu); rlt::free(cpu, ab_cpu); rlt::free(cpu, cb_cpu);
+    rlt::free(gpu, ppo_gpu); rlt::free(gpu, pb_gpu); rlt::free(gpu, ds_gpu);
+    rlt::free(gpu, ao_gpu); rlt::free(gpu, co_gpu); rlt::free(gpu, ab_gpu); rlt::free(gpu, cb_gpu);
+}
+
 int main(){
     // the reference's CUDA sweep (cuda_basics.cu:961-972) plus the BASELINE shapes
     train_steps<   1, 256,  10, 100, 3, act::RELU, act::IDENTITY, 1>("sweep_b1");
@@ -178,6 +261,8 @@ int main(){
     train_steps<1024,  64, 256,  16, 4, act::RELU, act::IDENTITY, 2>("c5_b1024");
     collect_parity<  64, 64, 100, act::RELU, 3>("collect_ppo_default");
     collect_parity<1000, 40,  15, act::TANH, 2>("collect_tanh_1000");
+    ppo_parity<64, 64, 512, 2>("ppo_train_shuffled");
+    ppo_parity<16, 128, 2048, 1>("ppo_train_one_batch");
     std::printf("%s\n", failures ? "ADAPTER PARITY FAILED" : "ADAPTER PARITY OK");
     return failures ? 1 : 0;
 }

@@ -276,6 +276,31 @@ int b200rl_collect_tables_host(uint32_t* rng_state_host, int n_envs, int n_steps
                                const uint8_t* truncated_host, int step_limit, float* reset_states_host, int n_reset_rounds,
                                int* rounds_used_host, float* noise_host);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * Off-policy runner step with per-environment replay buffers: step<POLICY>(device, runner, policy, buffers, rng)
+ * (rl/components/off_policy_runner/operations_generic.h:219-238, CUDA form operations_cuda.h:184-204): reset-if-truncated from
+ * reset_states [N, 2] (one round, drawn on the host in environment order for the environments whose truncated flag is set), observe
+ * into observations [N, 3], actor forward into actions [N, 1], step + reward, counters, next_observations [N, 3], then the transition
+ * is appended to the environment's replay buffer (rl/components/replay_buffer/operations_generic.h:54-79: row = observation 3,
+ * action 1, reward 1, next observation 3, terminated, truncated; episode_start[position] = current_episode_start; position wraps at
+ * capacity; full is set when it returns to 0; a reset marks the previous transition truncated, operations_generic_per_env.h:41-52).
+ * The replay buffers are described by byte offsets into one struct per environment, so that the reference's statically allocated
+ * ReplayBuffer structs in device memory can be written in place. Either actor_params (flat arena) or layer_params (six tensors).
+ * reward_scratch [N] floats and was_truncated_scratch [N] bytes are work areas. Like the reference (whose add() overload for
+ * ReplayBufferWithStates is not selected), the per-transition state copies are not written. */
+typedef struct b200rl_replay_layout {
+    size_t env_stride;                    /* bytes from one environment's replay buffer to the next */
+    size_t off_data;                      /* data matrix [capacity, ld_data] floats */
+    size_t off_episode_start;             /* episode_start [capacity] indices */
+    size_t off_position, off_full, off_current_episode_start;   /* index, 1-byte flag, index */
+    int capacity, ld_data, index_bytes;   /* index_bytes: 4 or 8 */
+} b200rl_replay_layout;
+int b200rl_pendulum_offpolicy_step(const b200rl_mlp_shape* actor, const float* actor_params, const float* const* layer_params, float* states,
+                                   int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_envs,
+                                   int step_limit, float* observations, float* actions, float* next_observations, void* replay_buffers,
+                                   const b200rl_replay_layout* layout, float* reward_scratch, uint8_t* was_truncated_scratch, int* error_flag,
+                                   b200rl_stream_t stream);
+
 /* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
  * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and
  * target-value columns. b200rl_shuffle_permutation_host replays those draws on the host engine (advanced in place, as the reference

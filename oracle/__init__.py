@@ -90,6 +90,9 @@ class Oracle:
         _u64p = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
         L.orc_rng_uniform_int_stream.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         L.orc_shuffle_permutation.argtypes = [C.c_void_p, C.c_int, _i32p]
+        _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
+        L.orc_offpolicy_steps.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i32p, _u8p, _f32p,
+                                          _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _f32p, _f32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
                                            C.c_void_p, C.c_int, _f32p, C.c_int]
         L.orc_pendulum_collect.restype = C.c_int
@@ -286,6 +289,24 @@ class Oracle:
             raise RuntimeError(f"orc_pendulum_rollout rc={rc}")
         return dict(obs=obs, act=act, rew=rew, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
 
+    # --- off-policy runner with replay buffers -------------------------------------------------------------
+    @staticmethod
+    def new_offpolicy_state(N, capacity):
+        """Runner + replay-buffer state right after init(): every environment flagged truncated, empty buffers."""
+        return dict(states=np.zeros((N, 2), np.float32), episode_step=np.zeros(N, np.int32), truncated=np.ones(N, np.uint8), episode_return=np.zeros(N, np.float32),
+                    replay_data=np.zeros((N, capacity, 10), np.float32), episode_start=np.zeros((N, capacity), np.int64),
+                    replay_states=np.zeros((N, capacity, 2), np.float32), replay_next_states=np.zeros((N, capacity, 2), np.float32),
+                    counters=np.zeros((N, 3), np.int64), buf_obs=np.zeros((N, 3), np.float32), buf_act=np.zeros((N, 1), np.float32),
+                    buf_next_obs=np.zeros((N, 3), np.float32))
+
+    def offpolicy_steps(self, shape, params, st, step_limit, n_steps, rng):
+        """n_steps x step() of the off-policy runner on the state dict `st` (updated in place); `rng` from new_rng."""
+        N, capacity = st["replay_data"].shape[:2]
+        self.lib.orc_offpolicy_steps(C.byref(shape), params, N, capacity, step_limit, n_steps, rng, st["states"], st["episode_step"], st["truncated"],
+                                     st["episode_return"], st["replay_data"], st["episode_start"], st["replay_states"], st["replay_next_states"],
+                                     st["counters"], st["buf_obs"], st["buf_act"], st["buf_next_obs"])
+        return st
+
     # --- on-policy collect ---------------------------------------------------------------------------------
     def new_rng(self, seed):
         rng = C.create_string_buffer(4 * 624 + 16)
@@ -357,6 +378,8 @@ class Reference:
         L.ref_ppo_train.argtypes = [C.c_int] * 6 + [C.c_uint32] + [_f32p] * 10 + [C.POINTER(C.c_double)]
         _u64p = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
         L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
+        _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
+        L.ref_offpolicy_steps.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _i32p, _u8p, _f32p, _f32p, _f32p, _f32p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
 
@@ -411,6 +434,18 @@ class Reference:
     PPO_TRAIN_SHUFFLE_CASES = ((64, 64, 512, 2), (5, 37, 37, 3))
 
     PPO_TRAIN_ANT_CASES = ((64, 1024, 2048, 1, False), (64, 1024, 2048, 1, True), (64, 1024, 2048, 10, True))   # + shuffle flag; env="ant"
+
+    OFFPOLICY_CASES = ((8, 64, 50), (33, 40, 17))      # (N, replay capacity, episode step limit)
+
+    def offpolicy_steps(self, N, capacity, step_limit, actor_params, seed, n_steps):
+        """n_steps x step<0>() of the reference's OffPolicyRunner on a fresh runner; returns a state dict like Oracle.new_offpolicy_state."""
+        st = Oracle.new_offpolicy_state(N, capacity)
+        rc = self.lib.ref_offpolicy_steps(N, capacity, step_limit, actor_params, seed, n_steps, st["replay_data"], st["episode_start"], st["replay_states"],
+                                          st["replay_next_states"], st["counters"], st["states"], st["episode_step"], st["truncated"], st["episode_return"],
+                                          st["buf_obs"], st["buf_act"], st["buf_next_obs"])
+        if rc != 0:
+            raise KeyError("no such off-policy runner case")
+        return st
 
     def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset, shuffle_seed=None, env="pendulum", want_seconds=False):
         """The reference's train() on a given dataset matrix [(steps+1)*N, obs + 2 act + 8]; SHUFFLE_EPOCH with an engine seeded by

@@ -488,6 +488,64 @@ void orc_normal_functions(int n, const float* mean, const float* log_std, const 
 }
 
 /* ------------------------------------------------------------------------------------------------------ */
+/* Off-policy runner step with per-environment replay buffers:                                               */
+/* rl/components/off_policy_runner/operations_generic.h:219-238 (step = prologue, interlude, epilogue),       */
+/* operations_generic_per_env.h:8-61 (prologue: on truncation draw a new initial state, reset the counters,   */
+/* mark the previous transition of a non-empty replay buffer truncated and start a new episode there; then    */
+/* observe), :62-108 (epilogue: step, reward, next observation, counters, truncation, replay add),            */
+/* rl/components/replay_buffer/operations_generic.h:54-85 (add: row = observation 3, action 1, reward 1, next   */
+/* observation 3, terminated, truncated; episode_start[position] = current_episode_start; position wraps;     */
+/* a truncated transition starts a new episode at the next position; full once position returns to 0).        */
+/* Replay storage: data [N, capacity, 10], episode_start [N, capacity], states / next_states [N, capacity, 2],  */
+/* counters [N, 3] = (position, full, current_episode_start). One engine, draws in environment order.          */
+/* buf_obs / buf_act / buf_next_obs [N, 3 | 1 | 3]: the runner's step buffers after the last step.             */
+/* ------------------------------------------------------------------------------------------------------ */
+void orc_offpolicy_steps(const orc_mlp_shape* actor, const float* params, int N, int capacity, int step_limit, int n_steps, orc_rng* rng,
+                         float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                         float* replay_data, int64_t* episode_start, float* replay_states, float* replay_next_states, int64_t* counters,
+                         float* buf_obs, float* buf_act, float* buf_next_obs){
+    for(int s = 0; s < n_steps; s++){
+        for(int e = 0; e < N; e++){
+            int64_t* cnt = counters + 3 * e;
+            if(truncated[e]){
+                orc_pendulum_sample_initial_state(rng, &states[2 * e], &states[2 * e + 1]);
+                episode_step[e] = 0; episode_return[e] = 0;
+                if(cnt[1] || cnt[0] > 0){
+                    const int64_t prev = cnt[0] == 0 ? capacity - 1 : cnt[0] - 1;
+                    replay_data[((size_t)e * capacity + prev) * 10 + 9] = 1.0f;
+                    cnt[2] = cnt[0];
+                }
+            }
+            orc_pendulum_observe(states[2 * e], states[2 * e + 1], buf_obs + 3 * e);
+        }
+        orc_mlp_evaluate(actor, params, buf_obs, 3, buf_act, 1, N);
+        for(int e = 0; e < N; e++){
+            int64_t* cnt = counters + 3 * e;
+            float nt, ntd;
+            orc_pendulum_step(states[2 * e], states[2 * e + 1], buf_act[e], &nt, &ntd);
+            const float r = orc_pendulum_reward(states[2 * e], states[2 * e + 1], buf_act[e]);
+            orc_pendulum_observe(nt, ntd, buf_next_obs + 3 * e);
+            episode_step[e] += 1; episode_return[e] += r;
+            const int trunc = episode_step[e] == step_limit;               /* Pendulum never terminates */
+            truncated[e] = (uint8_t)trunc;
+            const int64_t pos = cnt[0];
+            float* row = replay_data + ((size_t)e * capacity + pos) * 10;
+            memcpy(row, buf_obs + 3 * e, sizeof(float) * 3); row[3] = buf_act[e]; row[4] = r; memcpy(row + 5, buf_next_obs + 3 * e, sizeof(float) * 3);
+            row[8] = 0.0f; row[9] = (float)trunc;
+            /* replay_states / replay_next_states stay untouched: in the reference the add() overload for ReplayBufferWithStates names a type
+             * (SPEC::T) its specification does not have, so overload resolution silently falls back to the base-class add() (:54-79), which
+             * does not store the states. */
+            (void)replay_states; (void)replay_next_states;
+            episode_start[(size_t)e * capacity + pos] = cnt[2];
+            cnt[0] = (pos + 1) % capacity;
+            if(trunc) cnt[2] = cnt[0];
+            if(cnt[0] == 0 && !cnt[1]) cnt[1] = 1;
+            states[2 * e] = nt; states[2 * e + 1] = ntd;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
 /* On-policy collect: rl/components/on_policy_runner/operations_generic.h:105-146 (collect),                  */
 /* operations_generic_per_env.h:9-36 (prologue), :37-79 (epilogue), dataset columns on_policy_runner.h:38-72.  */
 /* Pendulum: observation 3, action 1 -> row = obs[0:3] action_mean[3] action[4] log_prob[5] reward[6]         */

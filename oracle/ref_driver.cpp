@@ -18,6 +18,7 @@
 //   nn/loss_functions/mse/operations_generic.h   gradient
 //   rl/environments/pendulum/operations_generic.h   sample_initial_state / step / reward / observe
 //   random/operations_cpu.h   init(device, rng, seed), uniform_real_distribution, normal_distribution::sample
+//   rl/components/off_policy_runner/operations_generic.h  malloc / init / step<0> (per-environment replay buffers)
 //   rl/components/on_policy_runner/operations_generic.h   init / collect (actor: sequential<mlp_unconditional_stddev>)
 //   rl/algorithms/ppo/operations_generic.h   estimate_generalized_advantages
 #ifdef REF_USE_OPENBLAS
@@ -39,6 +40,7 @@
 #include <rl_tools/nn/optimizers/adam/operations_generic.h>
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
+#include <rl_tools/rl/components/off_policy_runner/operations_generic.h>
 #include <rl_tools/rl/algorithms/ppo/ppo.h>
 #include <rl_tools/rl/algorithms/ppo/operations_generic.h>
 
@@ -470,7 +472,69 @@ static void ppo_train_case(const float* actor_params, const float* critic_params
     rlt::free(device, actor_buffers); rlt::free(device, critic_buffers);
 }
 
+// Off-policy runner through the reference's own OffPolicyRunner (rl/components/off_policy_runner/operations_generic.h:47-69,162-238,
+// operations_generic_per_env.h:8-108; replay buffer rl/components/replay_buffer/operations_generic.h:54-85): n_steps x step<0> with a
+// deterministic actor sequential<mlp 3 -> 64 -> 64 -> 1, ReLU / tanh>. Outputs per environment: the replay buffer's data matrix
+// [CAPACITY, 10] (observation 3, action 1, reward 1, next observation 3, terminated, truncated), episode_start [CAPACITY], states and
+// next_states [CAPACITY, 2], and (position, full, current_episode_start); plus the runner state and the runner's step buffers.
+template <TI T_N, TI T_CAPACITY, TI T_LIMIT>
+struct OffPolicyParameters: rlt::rl::components::off_policy_runner::ParametersDefault<TYPE_POLICY, TI>{
+    static constexpr TI N_ENVIRONMENTS = T_N;
+    static constexpr TI REPLAY_BUFFER_CAPACITY = T_CAPACITY;
+    static constexpr TI EPISODE_STEP_LIMIT = T_LIMIT;
+};
+template <TI N, TI CAPACITY, TI LIMIT>
+static void offpolicy_case(const float* actor_params, uint32_t seed, int n_steps, float* replay_data, int64_t* episode_start, float* replay_states, float* replay_next_states,
+                           int64_t* counters, float* states_out, int32_t* episode_step_out, uint8_t* truncated_out, float* episode_return_out,
+                           float* buf_obs, float* buf_act, float* buf_next_obs){
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
+    using ACTOR = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<ACTOR_CONFIG>>, rlt::tensor::Shape<TI, 1, N, 3>>;
+    using POLICIES = rlt::utils::Tuple<TI, ACTOR>;
+    using SPEC = rlt::rl::components::off_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, POLICIES, OffPolicyParameters<N, CAPACITY, LIMIT>>;
+    using RUNNER = rlt::rl::components::OffPolicyRunner<SPEC>;
+    DEVICE device;
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    ACTOR actor; typename ACTOR::template Buffer<> buffers;
+    rlt::malloc(device, actor); rlt::malloc(device, buffers);
+    { const float* p = actor_params; auto& m = actor.content;
+      load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
+    RUNNER* runner = new RUNNER();                       // the replay buffers are statically allocated inside the runner's matrices
+    rlt::malloc(device, *runner);
+    rlt::init(device, *runner);
+    for(int s = 0; s < n_steps; s++) rlt::step<0>(device, *runner, actor, buffers, rng);
+    for(TI e = 0; e < N; e++){
+        auto& rb = rlt::get(runner->replay_buffers, 0, e);
+        for(TI r = 0; r < CAPACITY; r++){
+            for(TI k = 0; k < 10; k++) replay_data[((size_t)e * CAPACITY + r) * 10 + k] = rlt::get(rb.data, r, k);
+            episode_start[(size_t)e * CAPACITY + r] = (int64_t)rlt::get(device, rb.episode_start, r);
+            const auto& st = rlt::get(rb.states, r, 0); const auto& ns = rlt::get(rb.next_states, r, 0);
+            replay_states[((size_t)e * CAPACITY + r) * 2] = st.theta; replay_states[((size_t)e * CAPACITY + r) * 2 + 1] = st.theta_dot;
+            replay_next_states[((size_t)e * CAPACITY + r) * 2] = ns.theta; replay_next_states[((size_t)e * CAPACITY + r) * 2 + 1] = ns.theta_dot;
+        }
+        counters[3 * e] = (int64_t)rb.position; counters[3 * e + 1] = rb.full ? 1 : 0; counters[3 * e + 2] = (int64_t)rb.current_episode_start;
+        const auto& st = rlt::get(runner->states, 0, e);
+        states_out[2 * e] = st.theta; states_out[2 * e + 1] = st.theta_dot;
+        episode_step_out[e] = (int32_t)rlt::get(runner->episode_step, 0, e);
+        truncated_out[e] = rlt::get(runner->truncated, 0, e) ? 1 : 0;
+        episode_return_out[e] = rlt::get(runner->episode_return, 0, e);
+        for(TI k = 0; k < 3; k++){ buf_obs[3 * e + k] = rlt::get(runner->buffers.observations, e, k); buf_next_obs[3 * e + k] = rlt::get(runner->buffers.next_observations, e, k); }
+        buf_act[e] = rlt::get(runner->buffers.actions, e, 0);
+    }
+    rlt::free(device, *runner); delete runner;
+    rlt::free(device, actor); rlt::free(device, buffers);
+}
+
 extern "C" {
+
+int ref_offpolicy_steps(int N, int capacity, int step_limit, const float* actor_params, uint32_t seed, int n_steps, float* replay_data, int64_t* episode_start,
+                         float* replay_states, float* replay_next_states, int64_t* counters, float* states_out, int32_t* episode_step_out, uint8_t* truncated_out,
+                         float* episode_return_out, float* buf_obs, float* buf_act, float* buf_next_obs){
+#define OFFPOLICY_CASE(n, c, l) if(N == n && capacity == c && step_limit == l){ offpolicy_case<n, c, l>(actor_params, seed, n_steps, replay_data, episode_start, replay_states, replay_next_states, counters, states_out, episode_step_out, truncated_out, episode_return_out, buf_obs, buf_act, buf_next_obs); return 0; }
+    OFFPOLICY_CASE(8, 64, 50)
+    OFFPOLICY_CASE(33, 40, 17)
+#undef OFFPOLICY_CASE
+    return -1;
+}
 
 // env: 0 = Pendulum shapes (3 / 1, ReLU), 1 = Ant shapes (27 / 8, tanh)
 int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle, uint32_t seed, const float* actor_params, const float* critic_params, const float* dataset_in,

@@ -21,6 +21,22 @@ MAX_LAYERS = 8
 _lib = None
 
 
+class ReplayLayout(C.Structure):
+    """Mirror of b200rl_replay_layout: byte offsets of one environment's replay buffer."""
+    _fields_ = [("env_stride", C.c_size_t), ("off_data", C.c_size_t), ("off_episode_start", C.c_size_t), ("off_position", C.c_size_t),
+                ("off_full", C.c_size_t), ("off_current_episode_start", C.c_size_t), ("capacity", C.c_int), ("ld_data", C.c_int), ("index_bytes", C.c_int)]
+
+    @staticmethod
+    def packed(capacity):
+        """data [capacity, 10] f32 | episode_start [capacity] u32 | position u32 | current_episode_start u32 | full u8 (+3 pad)."""
+        L = ReplayLayout()
+        L.capacity, L.ld_data, L.index_bytes = capacity, 10, 4
+        L.off_data, L.off_episode_start = 0, 40 * capacity
+        L.off_position, L.off_current_episode_start, L.off_full = 44 * capacity, 44 * capacity + 4, 44 * capacity + 8
+        L.env_stride = 44 * capacity + 12
+        return L
+
+
 class B200RLError(RuntimeError):
     pass
 
@@ -115,6 +131,7 @@ def lib():
         L.b200rl_permute_rows_scratch_bytes.argtypes = [i, C.c_uint64]
         L.b200rl_permute_rows_scratch_bytes.restype = sz
         L.b200rl_permute_rows.argtypes = [vp, i, i, vp, C.c_uint64, vp, sz, vp]
+        L.b200rl_pendulum_offpolicy_step.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp, vp, vp, C.POINTER(ReplayLayout), vp, vp, vp, vp]
         L.b200rl_collect_tables_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i), vp]
         L.b200rl_pendulum_collect.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
@@ -397,3 +414,16 @@ def permute_rows(data, n_rows, perm, columns):
     nbytes = lib().b200rl_permute_rows_scratch_bytes(n_rows, mask)
     scratch = torch.empty(max(nbytes, 4), device=data.device, dtype=torch.uint8)
     check(lib().b200rl_permute_rows(_ptr(data), data.stride(0), n_rows, _ptr(perm), mask, _ptr(scratch), nbytes, _stream()), "b200rl_permute_rows")
+
+
+def pendulum_offpolicy_step(shape, params, states, episode_step, truncated, episode_return, reset_states, step_limit, observations, actions, next_observations,
+                            replay, layout, error_flag=None, layers=None):
+    """One off-policy runner step with per-environment replay buffers (`replay` = uint8 CUDA tensor laid out as `layout` describes)."""
+    import torch
+    N = states.shape[0]
+    rew = torch.empty(N, device=states.device, dtype=torch.float32)
+    was = torch.empty(N, device=states.device, dtype=torch.uint8)
+    table = None if layers is None else (C.c_void_p * 6)(*[t.data_ptr() for t in layers])
+    check(lib().b200rl_pendulum_offpolicy_step(C.byref(shape), _ptr(params) if layers is None else None, table, _ptr(states), _ptr(episode_step), _ptr(truncated),
+                                               _ptr(episode_return), _ptr(reset_states), N, step_limit, _ptr(observations), _ptr(actions), _ptr(next_observations),
+                                               _ptr(replay), C.byref(layout), _ptr(rew), _ptr(was), _ptr(error_flag), _stream()), "b200rl_pendulum_offpolicy_step")

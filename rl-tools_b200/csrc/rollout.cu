@@ -196,15 +196,11 @@ extern "C" int b200rl_pendulum_collect(const b200rl_mlp_shape* actor, const floa
 // share that arena.
 static __device__ __align__(16) float g_collect_actor_arena[64 * 3 + 64 + 64 * 64 + 64 + 64 + 1 + 3];
 
-extern "C" int b200rl_pendulum_collect_layers(const b200rl_mlp_shape* actor, const float* const* layer_params, const float* log_std,
-                                              float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
-                                              const float* reset_states, int n_reset_rounds, const float* noise, int n_envs, int n_steps,
-                                              int step_limit, float* dataset, int ld_dataset, int* error_flag, b200rl_stream_t stream){
-    int rc = validate_actor(actor);
-    if(rc) return rc;
+// packs six separately allocated layer tensors (W1 b1 W2 b2 W3 b3) into the file-scope arena; *order_event is recorded by the caller
+// after its kernel launch
+static int pack_actor_layers(const float* const* layer_params, cudaStream_t s, float** arena_out, cudaEvent_t* order_event){
     if(!layer_params) return B200RL_ERR_INVALID_ARGUMENT;
     for(int i = 0; i < 6; i++) if(!layer_params[i]) return B200RL_ERR_INVALID_ARGUMENT;
-    cudaStream_t s = (cudaStream_t)stream;
     static cudaEvent_t ev = nullptr;
     float* arena = nullptr;
     if(!ev) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
@@ -216,8 +212,105 @@ extern "C" int b200rl_pendulum_collect_layers(const b200rl_mlp_shape* actor, con
         B200RL_CUDA_TRY(cudaMemcpyAsync(arena + off, layer_params[i], sizeof(float) * counts[i], cudaMemcpyDeviceToDevice, s));
         off += counts[i];
     }
+    *arena_out = arena; *order_event = ev;
+    return B200RL_OK;
+}
+
+extern "C" int b200rl_pendulum_collect_layers(const b200rl_mlp_shape* actor, const float* const* layer_params, const float* log_std,
+                                              float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                                              const float* reset_states, int n_reset_rounds, const float* noise, int n_envs, int n_steps,
+                                              int step_limit, float* dataset, int ld_dataset, int* error_flag, b200rl_stream_t stream){
+    int rc = validate_actor(actor);
+    if(rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* arena = nullptr; cudaEvent_t ev = nullptr;
+    rc = pack_actor_layers(layer_params, s, &arena, &ev);
+    if(rc) return rc;
     rc = collect_launch(actor, arena, log_std, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds, noise,
                         n_envs, n_steps, step_limit, dataset, ld_dataset, error_flag, s);
     B200RL_CUDA_TRY(cudaEventRecord(ev, s));
     return rc;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Off-policy runner step with per-environment replay buffers (rl/components/off_policy_runner/operations_generic.h:219-238):
+// one fused rollout step into the runner's step buffers, then one thread per environment appends the transition to that environment's
+// replay buffer with the reference's bookkeeping (operations_generic_per_env.h:41-52, replay_buffer/operations_generic.h:54-79).
+// ---------------------------------------------------------------------------------------------------------------
+namespace b200rl {
+template <typename INDEX>
+__global__ void replay_add_kernel(int n_envs, const float* __restrict__ states, const uint8_t* __restrict__ truncated, const uint8_t* __restrict__ was_truncated,
+                                  const float* __restrict__ observations, const float* __restrict__ actions, const float* __restrict__ rewards,
+                                  float* __restrict__ next_observations, unsigned char* replay, b200rl_replay_layout L){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= n_envs) return;
+    unsigned char* rb = replay + (size_t)e * L.env_stride;
+    float* data = reinterpret_cast<float*>(rb + L.off_data);
+    INDEX* episode_start = reinterpret_cast<INDEX*>(rb + L.off_episode_start);
+    INDEX& position_ref = *reinterpret_cast<INDEX*>(rb + L.off_position);
+    INDEX& ces_ref = *reinterpret_cast<INDEX*>(rb + L.off_current_episode_start);
+    unsigned char& full_ref = *(rb + L.off_full);
+    INDEX position = position_ref, ces = ces_ref;
+    bool full = full_ref != 0;
+    if(was_truncated[e] && (full || position > 0)){            // prologue: the environment was reset at the start of this step
+        const INDEX prev = position == 0 ? (INDEX)(L.capacity - 1) : position - 1;
+        data[(size_t)prev * L.ld_data + 9] = 1.0f;
+        ces = position;
+    }
+    float sn, cs;
+    const float next_theta = states[2 * e], next_theta_dot = states[2 * e + 1];
+    sincosf(next_theta, &sn, &cs);
+    next_observations[3 * e] = cs; next_observations[3 * e + 1] = sn; next_observations[3 * e + 2] = next_theta_dot;
+    const bool trunc = truncated[e] != 0;
+    float* row = data + (size_t)position * L.ld_data;
+    row[0] = observations[3 * e]; row[1] = observations[3 * e + 1]; row[2] = observations[3 * e + 2];
+    row[3] = actions[e]; row[4] = rewards[e];
+    row[5] = cs; row[6] = sn; row[7] = next_theta_dot;
+    row[8] = 0.0f; row[9] = trunc ? 1.0f : 0.0f;              // Pendulum never terminates
+    episode_start[position] = ces;
+    position = (position + 1) % (INDEX)L.capacity;
+    if(trunc) ces = position;
+    if(position == 0 && !full) full = true;
+    position_ref = position; ces_ref = ces; full_ref = full ? 1 : 0;
+}
+}  // namespace b200rl
+
+extern "C" int b200rl_pendulum_offpolicy_step(const b200rl_mlp_shape* actor, const float* actor_params, const float* const* layer_params, float* states,
+                                              int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_envs,
+                                              int step_limit, float* observations, float* actions, float* next_observations, void* replay_buffers,
+                                              const b200rl_replay_layout* layout, float* reward_scratch, uint8_t* was_truncated_scratch, int* error_flag,
+                                              b200rl_stream_t stream){
+    int rc = validate_actor(actor);
+    if(rc) return rc;
+    if((!actor_params && !layer_params) || !states || !episode_step || !truncated || !episode_return || !observations || !actions || !next_observations ||
+       !replay_buffers || !layout || !reward_scratch || !was_truncated_scratch || n_envs < 0 || step_limit < 1)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(layout->capacity < 1 || layout->ld_data < 10 || (layout->index_bytes != 4 && layout->index_bytes != 8)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0) return B200RL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaEvent_t ev = nullptr;
+    if(!actor_params){
+        float* arena = nullptr;
+        rc = pack_actor_layers(layer_params, s, &arena, &ev);
+        if(rc) return rc;
+        actor_params = arena;
+    }
+    B200RL_CUDA_TRY(cudaMemcpyAsync(was_truncated_scratch, truncated, (size_t)n_envs, cudaMemcpyDeviceToDevice, s));
+    RolloutArgs a{};
+    a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
+    a.reset_states = reset_states; a.n_reset_rounds = reset_states ? 1 : 0; a.n_envs = n_envs; a.env_begin = 0; a.env_count = n_envs;
+    a.n_steps = 1; a.step_limit = step_limit; a.obs = observations; a.act = actions; a.rew = reward_scratch; a.error_flag = error_flag;
+    for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
+    rc = rollout_dispatch(actor, a, s);
+    if(ev) B200RL_CUDA_TRY(cudaEventRecord(ev, s));
+    if(rc) return rc;
+    const int threads = 128, blocks = (n_envs + threads - 1) / threads;
+    if(layout->index_bytes == 4)
+        replay_add_kernel<uint32_t><<<blocks, threads, 0, s>>>(n_envs, states, truncated, was_truncated_scratch, observations, actions, reward_scratch,
+                                                              next_observations, static_cast<unsigned char*>(replay_buffers), *layout);
+    else
+        replay_add_kernel<unsigned long long><<<blocks, threads, 0, s>>>(n_envs, states, truncated, was_truncated_scratch, observations, actions, reward_scratch,
+                                                                        next_observations, static_cast<unsigned char*>(replay_buffers), *layout);
+    B200RL_LAUNCH_CHECK("replay_add");
+    return B200RL_OK;
 }

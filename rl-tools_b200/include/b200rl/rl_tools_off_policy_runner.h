@@ -1,0 +1,142 @@
+// Header-only adapter, part 5: the off-policy runner on `devices::B200`.
+//
+// Include after <b200rl/rl_tools_on_policy_runner.h> and <rl_tools/rl/components/off_policy_runner/operations_generic.h>.
+//
+// Mirrors malloc / free / init / step<POLICY_INDEX> of the reference's CUDA runner (rl/components/off_policy_runner/operations_cuda.h:
+// 117-204): the runner's matrices, including the statically allocated per-environment replay-buffer structs, live in device memory,
+// and one step is the fused rollout kernel (T = 1) into the runner's step buffers followed by the replay-buffer append kernel, which
+// writes the reference's struct layout in place (byte offsets taken from the struct type on the host). Reset draws are made on the host
+// with the reference's own sample_initial_state on the caller's engine, in environment order, like the reference's CPU runner.
+//
+// Supported: rl::environments::Pendulum, symmetric observations, policy = sequential< mlp 3 -> 64 -> 64 -> 1 > or that mlp itself, fp32.
+// Not provided: gather_batch (the view members inside the device-resident replay-buffer structs are not initialised: only the data
+// matrix, episode_start and the position / full / current_episode_start counters are maintained), episode statistics.
+#pragma once
+#include "rl_tools_on_policy_runner.h"
+#include <memory>
+#include <vector>
+
+RL_TOOLS_NAMESPACE_WRAPPER_START
+namespace rl_tools{
+    namespace b200{
+        template <typename SPEC>
+        b200rl_replay_layout replay_layout(){
+            using RUNNER = rl::components::OffPolicyRunner<SPEC>;
+            using RB = typename RUNNER::REPLAY_BUFFER_TYPE;
+            static_assert(!SPEC::DYNAMIC_ALLOCATION_REPLAY_BUFFER, "the replay buffers must be statically allocated inside the runner (as for the reference's CUDA runner)");
+            static std::unique_ptr<RB> probe(new RB());                       // only its member addresses are used
+            const char* base = reinterpret_cast<const char*>(probe.get());
+            b200rl_replay_layout L{};
+            L.env_stride = sizeof(RB);
+            L.off_data = reinterpret_cast<const char*>(probe->data._data) - base;
+            L.off_episode_start = reinterpret_cast<const char*>(probe->episode_start._data) - base;
+            L.off_position = reinterpret_cast<const char*>(&probe->position) - base;
+            L.off_full = reinterpret_cast<const char*>(&probe->full) - base;
+            L.off_current_episode_start = reinterpret_cast<const char*>(&probe->current_episode_start) - base;
+            L.capacity = (int)SPEC::PARAMETERS::REPLAY_BUFFER_CAPACITY;
+            L.ld_data = (int)row_pitch(probe->data);
+            L.index_bytes = (int)sizeof(typename SPEC::TI);
+            return L;
+        }
+        // the six parameter tensors of a 3-layer MLP, for a bare mlp or a one-module sequential model around it
+        template <typename MLP_SPEC>
+        void actor_layers(nn_models::mlp::NeuralNetworkForward<MLP_SPEC>& mlp, const float* (&layers)[6], int (&acts)[3]){
+            static_assert(MLP_SPEC::INPUT_DIM == 3 && MLP_SPEC::CONFIG::HIDDEN_DIM == 64 && MLP_SPEC::CONFIG::NUM_LAYERS == 3 && MLP_SPEC::CONFIG::OUTPUT_DIM == 1, "actor 3 -> 64 -> 64 -> 1");
+            layers[0] = mlp.input_layer.weights.parameters._data; layers[1] = mlp.input_layer.biases.parameters._data;
+            layers[2] = mlp.hidden_layers[0].weights.parameters._data; layers[3] = mlp.hidden_layers[0].biases.parameters._data;
+            layers[4] = mlp.output_layer.weights.parameters._data; layers[5] = mlp.output_layer.biases.parameters._data;
+            acts[0] = acts[1] = activation_id<MLP_SPEC::CONFIG::HIDDEN_ACTIVATION_FUNCTION>();
+            acts[2] = activation_id<MLP_SPEC::CONFIG::OUTPUT_ACTIVATION_FUNCTION>();
+        }
+        template <typename MODULE_SPEC>
+        void actor_layers(nn_models::sequential::ModuleForward<MODULE_SPEC>& model, const float* (&layers)[6], int (&acts)[3]){
+            static_assert(utils::typing::is_same_v<typename MODULE_SPEC::NEXT_MODULE, nn_models::sequential::OutputModule>, "the policy must be the bare MLP module");
+            actor_layers(model.content, layers, acts);
+        }
+    }
+    // rl/components/off_policy_runner/operations_cuda.h:117-134
+    template<typename DEV_SPEC, typename SPEC>
+    void malloc(devices::B200<DEV_SPEC>& device, rl::components::OffPolicyRunner<SPEC>& runner){
+        static_assert(!SPEC::DYNAMIC_ALLOCATION_REPLAY_BUFFER && !SPEC::DYNAMIC_ALLOCATION_EPISODE_STATS, "static allocation inside the runner, as for the reference's CUDA runner");
+        malloc(device, runner.buffers.observations); malloc(device, runner.buffers.actions); malloc(device, runner.buffers.next_observations);
+        malloc(device, runner.envs); malloc(device, runner.states); malloc(device, runner.env_parameters);
+        malloc(device, runner.episode_return); malloc(device, runner.episode_step); malloc(device, runner.truncated);
+        malloc(device, runner.replay_buffers); malloc(device, runner.episode_stats);
+    }
+    template<typename DEV_SPEC, typename SPEC>
+    void free(devices::B200<DEV_SPEC>& device, rl::components::OffPolicyRunner<SPEC>& runner){
+        free(device, runner.buffers.observations); free(device, runner.buffers.actions); free(device, runner.buffers.next_observations);
+        free(device, runner.envs); free(device, runner.states); free(device, runner.env_parameters);
+        free(device, runner.episode_return); free(device, runner.episode_step); free(device, runner.truncated);
+        free(device, runner.replay_buffers); free(device, runner.episode_stats);
+    }
+    // rl/components/off_policy_runner/operations_generic.h:162-183: every environment truncated, empty replay buffers
+    template<typename DEV_SPEC, typename SPEC>
+    void init(devices::B200<DEV_SPEC>& device, rl::components::OffPolicyRunner<SPEC>& runner){
+        using RUNNER = rl::components::OffPolicyRunner<SPEC>;
+        static_assert(b200::is_pendulum<typename SPEC::ENVIRONMENT>::value, "only rl::environments::Pendulum is implemented on this device");
+        static_assert(sizeof(typename RUNNER::REPLAY_BUFFER_TYPE) % 4 == 0);
+        b200::note(device, b200rl_fill(reinterpret_cast<float*>(runner.replay_buffers._data), sizeof(typename RUNNER::REPLAY_BUFFER_TYPE) / 4 * (size_t)RUNNER::N_ENVIRONMENTS, 0.0f, device.stream));
+        b200::fill_any(device, runner.truncated, true);
+        b200::fill_any(device, runner.episode_step, 0);
+        b200::fill_any(device, runner.episode_return, 0);
+        runner.previous_policy_set = false;
+        runner.previous_policy = 0;
+#ifdef RL_TOOLS_DEBUG_RL_COMPONENTS_OFF_POLICY_RUNNER_CHECK_INIT
+        runner.initialized = true;
+#endif
+    }
+    // rl/components/off_policy_runner/operations_cuda.h:184-204
+    template<auto POLICY_INDEX, typename DEV_SPEC, typename SPEC, typename POLICY, typename POLICY_BUFFERS, typename RNG>
+    void step(devices::B200<DEV_SPEC>& device, rl::components::OffPolicyRunner<SPEC>& runner, POLICY& policy, POLICY_BUFFERS&, RNG& rng){
+        using RUNNER = rl::components::OffPolicyRunner<SPEC>;
+        using ENVIRONMENT = typename SPEC::ENVIRONMENT;
+        using T = typename SPEC::TYPE_POLICY::DEFAULT;
+        using TI = typename SPEC::TI;
+        constexpr TI N = RUNNER::N_ENVIRONMENTS;
+        static_assert(b200::is_pendulum<ENVIRONMENT>::value, "only rl::environments::Pendulum is implemented on this device");
+        static_assert(utils::typing::is_same_v<T, float> && sizeof(TI) == 4 && sizeof(bool) == 1 && sizeof(typename ENVIRONMENT::State) == 2 * sizeof(float));
+        static_assert(!SPEC::PARAMETERS::ASYMMETRIC_OBSERVATIONS && !SPEC::PARAMETERS::COLLECT_EPISODE_STATS, "not implemented on this device");
+        const bool policy_switch = runner.previous_policy_set && (POLICY_INDEX != runner.previous_policy);
+        if(policy_switch) b200::fill_any(device, runner.truncated, true);
+
+        // reset draws on the host, environments ascending (operations_generic_per_env.h:37-40)
+        std::vector<uint8_t> truncated(N);
+        b200::note(device, b200rl_memcpy(truncated.data(), runner.truncated._data, N, 1, device.stream));
+        std::vector<float> reset_states((size_t)N * 2, 0.0f);
+        ENVIRONMENT env; typename ENVIRONMENT::Parameters parameters; typename ENVIRONMENT::State state;
+        for(TI env_i = 0; env_i < N; env_i++){
+            if(truncated[env_i]){
+                if(SPEC::PARAMETERS::SAMPLE_PARAMETERS) sample_initial_parameters(device, env, parameters, rng);
+                sample_initial_state(device, env, parameters, state, rng);
+                reset_states[2 * env_i] = state.theta; reset_states[2 * env_i + 1] = state.theta_dot;
+            }
+        }
+        // work area kept for the life of the process: reset states [N, 2], rewards [N], previous flags [N], error flag
+        static void* scratch = nullptr;
+        constexpr size_t RESET_BYTES = sizeof(float) * 2 * N, REWARD_BYTES = sizeof(float) * N, FLAG_OFFSET = RESET_BYTES + REWARD_BYTES + ((N + 15) / 16) * 16;
+        if(!scratch) b200::note(device, b200rl_device_malloc(&scratch, FLAG_OFFSET + 16));
+        if(!scratch) return;
+        char* sc = static_cast<char*>(scratch);
+        int flag = 0;
+        b200::note(device, b200rl_memcpy(sc, reset_states.data(), RESET_BYTES, 0, device.stream));
+        b200::note(device, b200rl_memcpy(sc + FLAG_OFFSET, &flag, sizeof(int), 0, device.stream));
+        const float* layers[6]; int acts[3];
+        b200::actor_layers(policy, layers, acts);
+        b200rl_mlp_shape shape{};
+        shape.n_layers = 3; shape.input_dim = 3; shape.dims[0] = 64; shape.dims[1] = 64; shape.dims[2] = 1;
+        for(int l = 0; l < 3; l++) shape.acts[l] = acts[l];
+        static const b200rl_replay_layout layout = b200::replay_layout<SPEC>();
+        static_assert(decltype(runner.buffers.observations)::SPEC::COLS == 3 && decltype(runner.buffers.actions)::SPEC::COLS == 1);
+        b200::note(device, b200rl_pendulum_offpolicy_step(&shape, nullptr, layers, reinterpret_cast<float*>(runner.states._data), reinterpret_cast<int32_t*>(runner.episode_step._data),
+                                                          reinterpret_cast<uint8_t*>(runner.truncated._data), runner.episode_return._data, reinterpret_cast<const float*>(sc), (int)N,
+                                                          (int)SPEC::PARAMETERS::EPISODE_STEP_LIMIT, runner.buffers.observations._data, runner.buffers.actions._data,
+                                                          runner.buffers.next_observations._data, runner.replay_buffers._data, &layout, reinterpret_cast<float*>(sc + RESET_BYTES),
+                                                          reinterpret_cast<uint8_t*>(sc + RESET_BYTES + REWARD_BYTES), reinterpret_cast<int*>(sc + FLAG_OFFSET), device.stream));
+        b200::note(device, b200rl_memcpy(&flag, sc + FLAG_OFFSET, sizeof(int), 1, device.stream));
+        if(flag != 0) b200::note(device, B200RL_ERR_DEVICE_FLAG);
+        runner.previous_policy = POLICY_INDEX;
+        runner.previous_policy_set = true;
+    }
+}
+RL_TOOLS_NAMESPACE_WRAPPER_END

@@ -16,15 +16,18 @@
 #include <rl_tools/nn/optimizers/adam/operations_generic.h>      // after every model type it steps (same rule as for the reference's own devices)
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
+#include <rl_tools/rl/components/off_policy_runner/operations_generic.h>
 #include <rl_tools/rl/algorithms/ppo/ppo.h>
 #include <rl_tools/rl/algorithms/ppo/operations_generic.h>
 #include <b200rl/rl_tools_operations.h>
 #include <b200rl/rl_tools_on_policy_runner.h>
 #include <b200rl/rl_tools_ppo.h>
+#include <b200rl/rl_tools_off_policy_runner.h>
 
 #include <cstdio>
 #include <cmath>
 #include <vector>
+#include <memory>
 
 namespace rlt = rl_tools;
 using DEVICE_CPU = rlt::devices::DefaultCPU;
@@ -244,6 +247,71 @@ void ppo_parity(const char* name){
     rlt::free(gpu, ao_gpu); rlt::free(gpu, co_gpu); rlt::free(gpu, ab_gpu); rlt::free(gpu, cb_gpu);
 }
 
+// Off-policy runner: the reference's OffPolicyRunner (per-environment replay buffers) on the CPU device against the same runner type on
+// devices::B200, same actor, same engine seed, STEPS x step<0>(). Counters, flags, episode_start and the engine's final state must be
+// identical; replay rows agree within the drift of the free-running trajectories.
+template <TI T_N, TI T_CAPACITY, TI T_LIMIT>
+struct OffPolicyParityParameters: rlt::rl::components::off_policy_runner::ParametersDefault<TYPE_POLICY, TI>{
+    static constexpr TI N_ENVIRONMENTS = T_N;
+    static constexpr TI REPLAY_BUFFER_CAPACITY = T_CAPACITY;
+    static constexpr TI EPISODE_STEP_LIMIT = T_LIMIT;
+};
+template <TI N, TI CAPACITY, TI LIMIT, int STEPS>
+void offpolicy_parity(const char* name){
+    using PENDULUM = rlt::rl::environments::Pendulum<rlt::rl::environments::pendulum::Specification<T, TI, rlt::rl::environments::pendulum::DefaultParameters<T>>>;
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
+    using ACTOR = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<ACTOR_CONFIG>>, rlt::tensor::Shape<TI, 1, N, 3>>;
+    using POLICIES = rlt::utils::Tuple<TI, ACTOR>;
+    using SPEC = rlt::rl::components::off_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, POLICIES, OffPolicyParityParameters<N, CAPACITY, LIMIT>>;
+    using RUNNER = rlt::rl::components::OffPolicyRunner<SPEC>;
+    using RB = typename RUNNER::REPLAY_BUFFER_TYPE;
+    DEVICE_CPU cpu; DEVICE_GPU gpu;
+    rlt::init(gpu);
+    DEVICE_CPU::SPEC::RANDOM::ENGINE<> rng_init, rng_cpu, rng_gpu;
+    rlt::malloc(cpu, rng_init); rlt::malloc(cpu, rng_cpu); rlt::malloc(cpu, rng_gpu);
+    rlt::init(cpu, rng_init, 2); rlt::init(cpu, rng_cpu, 8); rlt::init(cpu, rng_gpu, 8);
+    ACTOR actor_cpu, actor_gpu; typename ACTOR::template Buffer<> buf_cpu, buf_gpu;
+    rlt::malloc(cpu, actor_cpu); rlt::malloc(cpu, buf_cpu); rlt::malloc(gpu, actor_gpu); rlt::malloc(gpu, buf_gpu);
+    rlt::init_weights(cpu, actor_cpu, rng_init);
+    rlt::copy(cpu, gpu, actor_cpu, actor_gpu);
+    std::unique_ptr<RUNNER> runner_cpu(new RUNNER()), runner_gpu(new RUNNER());
+    rlt::malloc(cpu, *runner_cpu); rlt::malloc(gpu, *runner_gpu);
+    rlt::init(cpu, *runner_cpu); rlt::init(gpu, *runner_gpu);
+    for(int s = 0; s < STEPS; s++){
+        rlt::step<0>(cpu, *runner_cpu, actor_cpu, buf_cpu, rng_cpu);
+        rlt::step<0>(gpu, *runner_gpu, actor_gpu, buf_gpu, rng_gpu);
+    }
+    int status = rlt::check_status(gpu);
+    // raw copy of the device-resident replay-buffer structs (their view members hold no host-valid pointers: only data members are read)
+    std::vector<unsigned char> raw(sizeof(RB) * (size_t)N);
+    b200rl_memcpy(raw.data(), runner_gpu->replay_buffers._data, raw.size(), 1, gpu.stream);
+    std::vector<TI> es(N); std::vector<uint8_t> tr(N);
+    b200rl_memcpy(es.data(), runner_gpu->episode_step._data, N * sizeof(TI), 1, gpu.stream);
+    b200rl_memcpy(tr.data(), runner_gpu->truncated._data, N, 1, gpu.stream);
+    bool counters = true; double flags_diff = 0, rows_diff = 0;
+    const TI written = STEPS < (int)CAPACITY ? (TI)STEPS : CAPACITY;
+    for(TI e = 0; e < N; e++){
+        const RB& g = *reinterpret_cast<const RB*>(raw.data() + sizeof(RB) * (size_t)e);
+        const RB& c = rlt::get(runner_cpu->replay_buffers, 0, e);
+        counters = counters && g.position == c.position && g.full == c.full && g.current_episode_start == c.current_episode_start;
+        counters = counters && es[e] == rlt::get(runner_cpu->episode_step, 0, e) && (tr[e] != 0) == rlt::get(runner_cpu->truncated, 0, e);
+        for(TI r = 0; r < written; r++){
+            counters = counters && g.episode_start._data[r] == c.episode_start._data[r];
+            for(TI k = 0; k < 10; k++){
+                const double d = std::fabs((double)g.data._data[r * 10 + k] - (double)c.data._data[r * 10 + k]);
+                if(k >= 8) flags_diff = std::fmax(flags_diff, d); else rows_diff = std::fmax(rows_diff, d);
+            }
+        }
+    }
+    bool engines = rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_cpu) == rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_gpu);
+    bool ok = status == 0 && counters && engines && flags_diff == 0 && rows_diff < 5e-3;
+    std::printf("%-28s envs %3u capacity %3u limit %3u steps %d  status %d  counters %d  engine %d  flags diff %.1e  replay rows drift %.2e  %s\n",
+                name, N, CAPACITY, LIMIT, STEPS, status, (int)counters, (int)engines, flags_diff, rows_diff, ok ? "OK" : "FAIL");
+    if(!ok) failures++;
+    rlt::free(cpu, *runner_cpu); rlt::free(gpu, *runner_gpu);
+    rlt::free(cpu, actor_cpu); rlt::free(cpu, buf_cpu); rlt::free(gpu, actor_gpu); rlt::free(gpu, buf_gpu);
+}
+
 int main(){
     // the reference's CUDA sweep (cuda_basics.cu:961-972) plus the BASELINE shapes
     train_steps<   1, 256,  10, 100, 3, act::RELU, act::IDENTITY, 1>("sweep_b1");
@@ -261,6 +329,8 @@ int main(){
     train_steps<1024,  64, 256,  16, 4, act::RELU, act::IDENTITY, 2>("c5_b1024");
     collect_parity<  64, 64, 100, act::RELU, 3>("collect_ppo_default");
     collect_parity<1000, 40,  15, act::TANH, 2>("collect_tanh_1000");
+    offpolicy_parity<8, 64, 50, 137>("off_policy_runner_step");
+    offpolicy_parity<33, 40, 17, 90>("off_policy_runner_wraps");
     ppo_parity<64, 64, 512, 2>("ppo_train_shuffled");
     ppo_parity<16, 128, 2048, 1>("ppo_train_one_batch");
     std::printf("%s\n", failures ? "ADAPTER PARITY FAILED" : "ADAPTER PARITY OK");

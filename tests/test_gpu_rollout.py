@@ -1,6 +1,7 @@
 """GPU parity of the fused Pendulum rollout (through the C ABI) against the CPU oracle and the golden rollout of the
 real reference: integer runner state bit-exact, floating point within 1e-6 + 1e-5|ref| per step when the state is
 teacher-forced, drift reported (and loosely bounded) for free-running trajectories of this chaotic system."""
+import ctypes as C
 import os
 
 import numpy as np
@@ -144,3 +145,58 @@ def test_full_size_properties(lib, torch):
     ds = [dev(torch, a) for a in (np.zeros((M, 2), np.float32), np.zeros(M, np.int32), np.ones(M, np.uint8), np.zeros(M, np.float32))]
     obs_s, act_s, rew_s = lib.pendulum_rollout(shape, params, ds[0], ds[1], ds[2], ds[3], dev(torch, np.ascontiguousarray(table[:, :M])), T)
     assert torch.equal(obs_s.view(T, M, 3), o[:, :M]) and torch.equal(act_s.view(T, M), act.view(T, N)[:, :M])
+
+
+@pytest.mark.parametrize("case", range(len(mg.OFFPOLICY_CASES)))
+def test_offpolicy_step_with_replay_buffers_vs_reference_golden(lib, orc, torch, case):
+    """step() of the off-policy runner with per-environment replay buffers, one call per step, teacher-forced from the oracle's runner
+    state every step (so no trajectory drift enters): replay rows written this step within 1e-5 |ref| + 2e-6, the bookkeeping
+    (episode_start, position, full, current_episode_start, the truncation mark on the previous transition) exact; after the last step
+    the whole replay buffer equals the reference's fixture within the same tolerance."""
+    fix = np.load(os.path.join(GOLDEN, "offpolicy.npz"))
+    N, cap, limit, steps = mg.OFFPOLICY_CASES[case]
+    shape, oshape = actor_shapes(lib)
+    params = mg.offpolicy_params(case)
+    st = orc.new_offpolicy_state(N, cap)
+    rng_o, rng_g = orc.new_rng(mg.OFFPOLICY_SEED), lib.rng_init_host(mg.OFFPOLICY_SEED)
+    L = lib.ReplayLayout.packed(cap)
+    replay = torch.zeros(N * L.env_stride, dtype=torch.uint8, device="cuda")
+    params_d = dev(torch, params)
+    bounds = np.cumsum([0, 192, 64, 4096, 64, 64, 1])
+    layers = [params_d[bounds[i]:bounds[i + 1]].clone() for i in range(6)]
+    obs, act, nobs = torch.zeros((N, 3), device="cuda"), torch.zeros((N, 1), device="cuda"), torch.zeros((N, 3), device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def unpack():
+        raw = replay.cpu().numpy().reshape(N, L.env_stride)
+        data = raw[:, :40 * cap].copy().view(np.float32).reshape(N, cap, 10)
+        es = raw[:, 40 * cap:44 * cap].copy().view(np.uint32).reshape(N, cap)
+        pos = raw[:, 44 * cap:44 * cap + 4].copy().view(np.uint32)[:, 0]
+        ces = raw[:, 44 * cap + 4:44 * cap + 8].copy().view(np.uint32)[:, 0]
+        return data, es, pos, raw[:, 44 * cap + 8], ces
+
+    for t in range(steps):
+        table = np.zeros((1, N, 2), np.float32)                 # this step's reset draws, from the product-side engine in environment order
+        lib.check(lib.lib().b200rl_reset_table_host(C.c_void_p(rng_g.ctypes.data), N, 1, C.c_void_p(st["episode_step"].ctypes.data),
+                                                    C.c_void_p(st["truncated"].ctypes.data), limit, C.c_void_p(table.ctypes.data), 1, None), "b200rl_reset_table_host")
+        d = [dev(torch, st[k]) for k in ("states", "episode_step", "truncated", "episode_return")]
+        before = st["counters"].copy()
+        lib.pendulum_offpolicy_step(shape, params_d, d[0], d[1], d[2], d[3], dev(torch, table), limit, obs, act, nobs, replay, L, error_flag=flag,
+                                    layers=layers if t % 2 else None)
+        orc.offpolicy_steps(oshape, params, st, limit, 1, rng_o)            # advances `st`
+        data, es, pos, full, ces = unpack()
+        assert int(flag.item()) == 0
+        assert np.array_equal(pos, st["counters"][:, 0]) and np.array_equal(full, st["counters"][:, 1]) and np.array_equal(ces, st["counters"][:, 2])
+        assert np.array_equal(d[1].cpu().numpy(), st["episode_step"]) and np.array_equal(d[2].cpu().numpy(), st["truncated"])
+        rows = before[:, 0]
+        got_rows, want_rows = data[np.arange(N), rows], st["replay_data"][np.arange(N), rows]
+        assert np.array_equal(got_rows[:, 8:], want_rows[:, 8:])
+        close(got_rows[:, :8], want_rows[:, :8], rtol=1e-5, atol=1e-5)
+        assert np.array_equal(es[np.arange(N), rows], st["episode_start"][np.arange(N), rows])
+        close(nobs, st["buf_next_obs"], atol=2e-6)
+        close(d[0], st["states"], atol=2e-6)
+    data, es, pos, full, ces = unpack()
+    w = min(steps, cap)
+    assert np.array_equal(data[:, :w, 8:], fix[f"replay_data_{case}"][:, :, 8:])          # terminated / truncated flags incl. the marks set at resets
+    close(data[:, :w, :8], fix[f"replay_data_{case}"][:, :, :8], rtol=1e-5, atol=1e-5)
+    assert np.array_equal(es[:, :w], fix[f"episode_start_{case}"]) and np.array_equal(np.stack([pos, full, ces], 1), fix[f"counters_{case}"])

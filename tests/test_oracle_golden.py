@@ -207,3 +207,20 @@ def test_ppo_train_on_ant_shapes_matches_reference(orc, tag):
     for name, g in zip(("actor", "actor_grad", "actor_m", "critic", "critic_grad", "critic_m"), got):
         want = fix[f"{tag}_{name}"]
         assert np.array_equal(g, want) or np.all(np.abs(g - want) <= 1e-6 + 1e-5 * np.abs(want)), name
+
+
+@pytest.mark.parametrize("case", range(len(mg.OFFPOLICY_CASES)))
+def test_offpolicy_runner_with_replay_buffers_matches_reference(orc, case):
+    """n x step<0>() of the reference's OffPolicyRunner: replay rows, episode_start, position / full / current_episode_start (wrap-around
+    and the truncation mark on the previous transition included), runner state and step buffers, bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "offpolicy.npz"))
+    N, cap, limit, steps = mg.OFFPOLICY_CASES[case]
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    st = orc.offpolicy_steps(shape, mg.offpolicy_params(case), orc.new_offpolicy_state(N, cap), limit, steps, orc.new_rng(mg.OFFPOLICY_SEED))
+    w = min(steps, cap)
+    for k, v in st.items():
+        if k in ("replay_states", "replay_next_states"):
+            assert not v.any()                                  # not stored, like the reference
+            continue
+        got = v[:, :w] if k in ("replay_data", "episode_start") else v
+        assert np.array_equal(got, fix[f"{k}_{case}"]), k

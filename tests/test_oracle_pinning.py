@@ -111,3 +111,19 @@ def test_uniform_int_and_shuffled_train_live(orc, ref_strict):
         assert np.array_equal(mine, want[6])
         for g, w in zip(got, want[:6]):
             assert np.array_equal(g, w)
+
+
+def test_offpolicy_runner_live(orc, ref_strict):
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    rs = np.random.RandomState(12)
+    for (N, cap, lim) in oracle.Reference.OFFPOLICY_CASES:
+        params = (rs.randn(4481) * 0.3).astype(np.float32)
+        for n_steps in (1, cap - 1, cap, 3 * cap + 5):
+            want = ref_strict.offpolicy_steps(N, cap, lim, params, 4, n_steps)
+            got = orc.offpolicy_steps(shape, params, orc.new_offpolicy_state(N, cap), lim, n_steps, orc.new_rng(4))
+            w = min(n_steps, cap)
+            for k in want:
+                if k in ("replay_states", "replay_next_states"):
+                    continue
+                a, b = (want[k][:, :w], got[k][:, :w]) if k in ("replay_data", "episode_start") else (want[k], got[k])
+                assert np.array_equal(a, b), (N, cap, lim, n_steps, k)

@@ -148,9 +148,9 @@ class CpuReference:
                 "sample": f"{N_ENVS} envs x {T} steps of the same rollout (observe -> evaluate -> step/reward), median of {reps}"}
 
 
-def cpu_reference_rate(seconds_budget=15.0, reps=3):
+def cpu_reference_rate(seconds_total=15.0, reps=3):
     cpu = CpuReference()
-    T = cpu.sample_steps(seconds_budget / reps)
+    T = cpu.sample_steps(seconds_total / reps)
     return cpu.describe(T, reps, statistics.median(cpu.timed(T) for _ in range(reps)))
 
 

@@ -20,6 +20,7 @@
 #include "pendulum.cuh"
 #include "rollout.cuh"
 #include "tcgen05.cuh"
+#include <stdlib.h>
 
 namespace b200rl {
 
@@ -36,7 +37,9 @@ constexpr uint32_t OFF_MBAR = OFF_BIAS_LO + 2048;
 constexpr uint32_t OFF_ABORT = OFF_MBAR + 8 * GROUPS;
 constexpr uint32_t OFF_SLOT = OFF_ABORT + 4 * GROUPS;
 constexpr uint32_t OFF_TURN = OFF_SLOT + 8;                   // 2 mbarriers: the tensor token alternating between the group pairs {0,1} and {2,3}
-constexpr uint32_t SMEM_BYTES = OFF_TURN + 8 * 2 + 1024;         // + slack to align the base to 1024 B
+constexpr uint32_t OFF_STAGE = (OFF_TURN + 8 * 2 + 15) / 16 * 16;  // output staging for bulk stores: per group 3 buffers x (obs 1536 + act 512 + rew 512 B)
+constexpr uint32_t STAGE_BUF_BYTES = TILE * 12 + TILE * 4 + TILE * 4, STAGE_GROUP_BYTES = 3 * STAGE_BUF_BYTES;
+constexpr uint32_t SMEM_BYTES = OFF_STAGE + GROUPS * STAGE_GROUP_BYTES + 1024;         // + slack to align the base to 1024 B
 constexpr uint32_t TMEM_COLS = 512, TMEM_COLS_PER_GROUP = 128;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;        // ~1 s: far beyond any legitimate wait
 constexpr uint32_t TF32_MASK = 0xFFFFE000u;
@@ -57,8 +60,14 @@ __device__ __forceinline__ float act_or_rt(float x, int rt){
     else return activation_rt(x, rt);
 }
 
-template <int A1, int A2, bool COLLECT>
+// BULK: the trajectory rows of a tile and step are contiguous in HBM (obs 12 B, act 4 B, rew 4 B per environment), so the threads write them to
+// a shared-memory staging buffer and the group's leader hands each buffer to the copy engine (cp.async.bulk shared -> global, no multicast)
+// one step later, at the barrier it already has before its MMA batch. Three buffers rotate: the buffer of step t is read by the copy issued
+// after barrier t+1, the leader waits for that read before barrier t+2, and the buffer is written again in step t+3. Requires 16-byte aligned
+// row starts (n_envs and the slab origin multiples of 4, aligned output pointers); the host selects the plain-store instantiation otherwise.
+template <int A1, int A2, bool COLLECT, bool BULK>
 __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, int n_tiles, int envs_per_tile){
+    static_assert(!(COLLECT && BULK), "dataset rows are strided: plain stores");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment by OFFSET from the __shared__ array, so the compiler keeps the shared address space (LDS/STS, not generic)
     uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -118,6 +127,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     GaussianHead head{};
     const size_t ld = COLLECT ? (size_t)a.ld_dataset : 0;
     if constexpr(COLLECT) head.init(a.log_std);
+    uint8_t* stage_base = base + OFF_STAGE + (uint32_t)g * STAGE_GROUP_BYTES;
 
     const int rounds = (n_tiles + (int)gridDim.x * GROUPS - 1) / ((int)gridDim.x * GROUPS);
     for(int round = 0; round < rounds && !failed; round++){
@@ -143,7 +153,21 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             resets = a.reset_count ? a.reset_count[e] : 0;
             if constexpr(COLLECT) a.dataset[(size_t)e * ld + COL_RESET] = trunc ? 1.0f : 0.0f;      // collect, operations_generic.h:115-117
         }
+        const int tile_first = a.env_begin + tile * envs_per_tile;
+        const int tile_count = min(envs_per_tile, a.env_count - tile * envs_per_tile);
+        // leader only: hands the staged rows of step `ts` to the copy engine
+        auto bulk_flush = [&](int ts){
+            uint8_t* buf = stage_base + (uint32_t)(ts % 3) * STAGE_BUF_BYTES;
+            const size_t row0 = (size_t)ts * a.n_envs + tile_first;
+            tc::bulk_store(a.obs + row0 * 3, buf, (uint32_t)tile_count * 12);
+            tc::bulk_store(a.act + row0, buf + TILE * 12, (uint32_t)tile_count * 4);
+            tc::bulk_store(a.rew + row0, buf + TILE * 16, (uint32_t)tile_count * 4);
+            tc::bulk_commit();
+        };
         for(int t = 0; t < a.n_steps; t++){
+            float* st_obs = reinterpret_cast<float*>(stage_base + (uint32_t)(t % 3) * STAGE_BUF_BYTES);
+            float* st_act = st_obs + TILE * 3;
+            float* st_rew = st_act + TILE;
             if(trunc){
                 if(a.reset_states != nullptr && resets < a.n_reset_rounds){
                     const float2 rs = *reinterpret_cast<const float2*>(a.reset_states + ((size_t)resets * a.n_envs + e) * 2);
@@ -158,6 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             float* drow = COLLECT ? a.dataset + row * ld : nullptr;
             if(valid){
                 if constexpr(COLLECT){ drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot; }
+                else if constexpr(BULK){ st_obs[r * 3 + 0] = cs; st_obs[r * 3 + 1] = sn; st_obs[r * 3 + 2] = theta_dot; }
                 else{ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
             }
 
@@ -186,6 +211,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             tc::tmem_wait_st();
             tc::fence_proxy_async_smem();
             tc::fence_before_thread_sync();
+            if constexpr(BULK){ if(r == 0) tc::bulk_wait_read<0>(); }      // the copy of step t-2 has read its buffer (re-used from step t+1 on)
             tc::named_barrier_sync(bar_id, TILE);
             if(*abort_flag){ failed = true; break; }
 
@@ -216,6 +242,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                 tc::mma_tf32_ss(tmem_d, desc_ones, desc_bias_hi, IDESC, 1u);
                 tc::commit(mbar);
                 tc::mbar_arrive(next_turn);
+                if constexpr(BULK){ if(t > 0) bulk_flush(t - 1); }          // every thread of the group finished step t-1 before this step's barrier
             }
             __syncwarp();                                     // the leader's lanes rejoin before the warp-wide TMEM loads
             if(!tc::mbar_wait_bounded(mbar, phase, WAIT_LIMIT_CYCLES)){
@@ -261,10 +288,20 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                 }
             }
             else{
-                if(valid){ a.act[row] = action; a.rew[row] = rwd; }
+                if(valid){
+                    if constexpr(BULK){ st_act[r] = action; st_rew[r] = rwd; }
+                    else{ a.act[row] = action; a.rew[row] = rwd; }
+                }
                 trunc = (es == a.step_limit);
             }
             theta = nt; theta_dot = ntd;
+        }
+        if constexpr(BULK){
+            // last step of the tile: make the staged rows visible to the copy engine, flush, and wait until every buffer has been read
+            tc::fence_proxy_async_smem();
+            tc::named_barrier_sync(bar_id, TILE);
+            if(r == 0 && !failed && a.n_steps > 0){ bulk_flush(a.n_steps - 1); tc::bulk_wait_read<0>(); }
+            tc::named_barrier_sync(bar_id, TILE);
         }
         if constexpr(COLLECT){
             if(valid && !failed){                  // final observation, operations_generic.h:136-143
@@ -301,11 +338,11 @@ static int upload_small_layers(const float* params, cudaStream_t s, cudaEvent_t*
     return B200RL_OK;
 }
 
-template <int A1, int A2, bool COLLECT>
-static int launch_tc(const RolloutArgs& a, cudaStream_t s){
+template <int A1, int A2, bool COLLECT, bool BULK>
+static int launch_tc_variant(const RolloutArgs& a, cudaStream_t s){
     static bool configured = false;
     if(!configured){
-        B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<A1, A2, COLLECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+        B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<A1, A2, COLLECT, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
         configured = true;
     }
     cudaEvent_t order_event = nullptr;
@@ -319,10 +356,22 @@ static int launch_tc(const RolloutArgs& a, cudaStream_t s){
     const int n_tiles = (a.env_count + ept - 1) / ept;
     int grid = (n_tiles + GROUPS - 1) / GROUPS;
     if(grid > NUM_SMS) grid = NUM_SMS;
-    rollout_tc_kernel<A1, A2, COLLECT><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
+    rollout_tc_kernel<A1, A2, COLLECT, BULK><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
     B200RL_LAUNCH_CHECK("rollout_tc");
     if(order_event) B200RL_CUDA_TRY(cudaEventRecord(order_event, s));
     return B200RL_OK;
+}
+
+// Bulk stores need 16-byte aligned row starts in all three outputs; B200RL_ROLLOUT_STORES=plain keeps per-thread stores (A/B measurements)
+template <int A1, int A2, bool COLLECT>
+static int launch_tc(const RolloutArgs& a, cudaStream_t s){
+    if constexpr(COLLECT) return launch_tc_variant<A1, A2, true, false>(a, s);
+    else{
+        static const bool plain = [](){ const char* v = getenv("B200RL_ROLLOUT_STORES"); return v && v[0] == 'p'; }();
+        const bool aligned = ((reinterpret_cast<uintptr_t>(a.obs) | reinterpret_cast<uintptr_t>(a.act) | reinterpret_cast<uintptr_t>(a.rew)) & 15u) == 0 &&
+                             a.n_envs % 4 == 0 && a.env_begin % 4 == 0 && a.env_count % 4 == 0;
+        return (aligned && !plain) ? launch_tc_variant<A1, A2, false, true>(a, s) : launch_tc_variant<A1, A2, false, false>(a, s);
+    }
 }
 
 int launch_rollout_tc(const RolloutArgs& a, cudaStream_t s){

@@ -61,7 +61,7 @@ __device__ __forceinline__ float act_or_rt(float x, int rt){
 }
 
 // BULK: the trajectory rows of a tile and step are contiguous in HBM (obs 12 B, act 4 B, rew 4 B per environment), so the threads write them to
-// a shared-memory staging buffer and the group's leader hands each buffer to the copy engine (cp.async.bulk shared -> global, no multicast)
+// a shared-memory staging buffer and the group's leader hands each buffer to the copy engine (cp.async.bulk shared -> global, one destination)
 // one step later, at the barrier it already has before its MMA batch. Three buffers rotate: the buffer of step t is read by the copy issued
 // after barrier t+1, the leader waits for that read before barrier t+2, and the buffer is written again in step t+3. Requires 16-byte aligned
 // row starts (n_envs and the slab origin multiples of 4, aligned output pointers); the host selects the plain-store instantiation otherwise.

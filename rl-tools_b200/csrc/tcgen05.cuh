@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) tensor-core path: TMEM allocation, tcgen05.mma with
 // shared-memory operand descriptors, tcgen05.commit -> mbarrier, tcgen05.ld, proxy fences, bounded mbarrier waits,
-// and bulk (TMA) shared->global stores. Everything here is single-CTA (cta_group::1); nothing uses cluster multicast.
+// and bulk (TMA) shared->global stores. Everything here is single-CTA (cta_group::1): every copy has exactly one destination.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

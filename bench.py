@@ -12,6 +12,9 @@ Prints ONE JSON line: device-timed `value` (inputs resident in HBM, CUDA events 
 (the host-buffer C-ABI call, host<->device copies inside the timed region), `roofline` for the rollout kernel
 against the measured peak, `cpu_baseline` (the reference's own CPU path timed on this box's cores), `clocks`.
 `--impl reference` times only the reference CPU implementation, on the same metric and config.
+
+`--workload {mlp_train, collect, ppo_update, critic_train}` print secondary lines in the same JSON form (sharded MLP training, on-policy
+collect, the PPO update on the Ant shapes, batch-256 critic regression steps); the default workload is the headline rollout.
 """
 import argparse
 import json

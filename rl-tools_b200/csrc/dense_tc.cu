@@ -12,10 +12,12 @@
 // setmaxnreg) and one that holds the issuing warp (registers lowered to 24; its other three warps exit). Measured and not
 // kept: letting those three warps stage the B operand -- 96 threads cannot keep enough 16-byte loads in flight (Little's law:
 // ~17 KB in flight against the ~48 KB the 256 staging threads sustain) and the 65,536 x 256 x 256 forward fell from 114 to 171 us.
-// One CTA per SM, persistent over (row tile, column tile, k split) work items; N <= 256 per tile.
-// Epilogue: transposition through shared memory so that every global store is a full 128-byte row segment,
-// then bias + pre-activation store + activation (forward), plain store (input gradient) or accumulate / split-k partial
-// store (weight gradient).
+// One CTA per SM, persistent over (row tile, column tile, k split) work items; N <= 256 per tile; tiles of <= 64 columns use a
+// variant with a quarter of the accumulator registers that prefetches two k chunks ahead.
+// Operands whose rows (not k) are contiguous in memory are loaded as 4 x 4 blocks with 16-byte loads and transposed in registers.
+// Epilogue: transposition through shared memory with 16-byte accesses so that every global store instruction writes four full
+// 128-byte lines, then bias + pre-activation store + activation (forward), plain store (input gradient) or accumulate / split-k
+// partial store, optionally transposed (weight gradient).
 #include "common.cuh"
 #include "dense.cuh"
 #include "tcgen05.cuh"

@@ -13,8 +13,8 @@ Prints ONE JSON line: device-timed `value` (inputs resident in HBM, CUDA events 
 against the measured peak, `cpu_baseline` (the reference's own CPU path timed on this box's cores), `clocks`.
 `--impl reference` times only the reference CPU implementation, on the same metric and config.
 
-`--workload {mlp_train, collect, ppo_update, critic_train}` print secondary lines in the same JSON form (sharded MLP training, on-policy
-collect, the PPO update on the Ant shapes, batch-256 critic regression steps); the default workload is the headline rollout.
+`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval}` print secondary lines in the same JSON form (sharded MLP training,
+on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference); the default workload is the headline rollout.
 """
 import argparse
 import json
@@ -469,6 +469,68 @@ def run_critic_train(args):
                       "cpu_baseline": cpu, "gpu_launches": reps * STEPS * 15}))
 
 
+def run_actor_eval(args):
+    """Secondary line: the batched actor inference of the CPU-runnable configuration -- fp32 input [256, 3], MLP 3 -> 64 -> 64 -> 2 (ReLU,
+    ReLU, identity), evaluate() = three fused dense launches, 1000 calls per timed step, eager and replayed as a CUDA graph.
+    value = inferred samples per second (graph replay). Single GPU."""
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, CALLS = 256, 1000
+    g = torch.Generator(device=dev); g.manual_seed(4)
+    net = pkg.Mlp(3, [64, 64, 2], ["relu", "relu", "identity"], B)
+    off, fan_in = 0, 3
+    for d in (64, 64, 2):                                   # Glorot-uniform weights, zero biases
+        bound = (6.0 / (fan_in + d)) ** 0.5
+        net.params[off:off + d * fan_in] = (torch.rand(d * fan_in, device=dev, generator=g) * 2 - 1) * bound
+        off += d * fan_in + d; fan_in = d
+    x = torch.rand((B, 3), device=dev, generator=g) * 2 - 1
+    y = torch.empty((B, 2), device=dev)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(5):
+            net.evaluate(x, y=y)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(10):
+            net.evaluate(x, y=y)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = min(args.steps, 10)
+    def timed(fn):
+        fn(); torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+    ms_eager = timed(lambda: [net.evaluate(x, y=y) for _ in range(CALLS)])
+    ms_graph = timed(lambda: [graph.replay() for _ in range(CALLS // 10)])
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        if os.path.exists(oracle.REF_FAST_SO):
+            os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
+            ref = oracle.Reference("fast")
+            res = ref.mlp_run("c1_actor_eval", net.params.cpu().numpy(), x.cpu().numpy(), None, 0, 20000)
+            cpu = {"value": 20000 * B / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
+                   "sample": "20,000 evaluate() calls of the reference at batch 256, CPU_OPENBLAS build"}
+    peaks = measured_peaks()
+    tflops = 2 * B * (3 * 64 + 64 * 64 + 64 * 2) * CALLS / (ms_graph * 1e-3) / 1e12
+    print(json.dumps({"metric": "actor inference samples/s (batch 256)", "value": CALLS * B / (ms_graph * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": reps, "warmup": 1,
+                      "ms_per_step": ms_graph, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "actor_eval_3-64-64-2_batch256_x1000calls", "us_per_call_graph": ms_graph, "us_per_call_eager": ms_eager,
+                                 "l2": "working set (20 KB) is L2-resident by design: latency-bound", "parallelism": "single GPU"},
+                      "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
+                                   "peak_source": peaks["source"] + " bf16 dense (burst)"},
+                      "cpu_baseline": cpu, "gpu_launches": reps * CALLS * 3}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -481,7 +543,7 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train"],
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval"],
                     help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
                          "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
                          "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
@@ -496,6 +558,8 @@ def main():
         return run_ppo_update(args)
     if args.workload == "critic_train":
         return run_critic_train(args)
+    if args.workload == "actor_eval":
+        return run_actor_eval(args)
     if args.impl == "reference":
         return run_reference(args)
     if not args.allow_short_warmup:

@@ -274,9 +274,19 @@ def run_collect(args):
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
     flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
 
+    device_rng = args.collect_rng == "device"
+    calls = [0]
+
+    def collect():
+        if device_rng:      # resets and noise drawn inside the kernel; consecutive calls continue the counter stream
+            pkg.pendulum_collect_device_rng(shape, params, params[4481:], states, es, tr, er, 1234 + rank, calls[0] * T, T, limit, dataset=ds, error_flag=flag)
+            calls[0] += 1
+        else:
+            pkg.pendulum_collect(shape, params, params[4481:], states, es, tr, er, table, noise, T, limit, dataset=ds, error_flag=flag)
+
     def step():
         es.zero_(); tr.fill_(1)
-        pkg.pendulum_collect(shape, params, params[4481:], states, es, tr, er, table, noise, T, limit, dataset=ds, error_flag=flag)
+        collect()
 
     sync = lambda: (dist.barrier() if dist is not None else None, torch.cuda.synchronize())
     warmup = max(args.warmup, 3)
@@ -288,7 +298,7 @@ def run_collect(args):
     for i in range(args.steps):
         flush.zero_(); es.zero_(); tr.fill_(1)
         starts[i].record()
-        pkg.pendulum_collect(shape, params, params[4481:], states, es, tr, er, table, noise, T, limit, dataset=ds, error_flag=flag)
+        collect()
         stops[i].record()
     sync()
     assert int(flag.item()) == 0
@@ -296,15 +306,25 @@ def run_collect(args):
     if dist is not None:
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
     ms = float(tm.item()) / args.steps
+    host_tables_ms = None
+    if rank == 0 and not device_rng:
+        # what the table-driven entry point costs on the host per call when the tables are real: the reference-compatible engine
+        # drawing T x N normals and the initial states, then the copy to the device (one call, wall clock)
+        rng = pkg.rng_init_host(7)
+        t0 = time.perf_counter()
+        tab, nz, _ = pkg.collect_tables_host(rng, N, T, np.zeros(N, np.int32), np.ones(N, np.uint8), limit, 1)
+        torch.from_numpy(tab).to(dev); torch.from_numpy(nz).to(dev); torch.cuda.synchronize()
+        host_tables_ms = (time.perf_counter() - t0) * 1e3
     if rank == 0:
         peaks = measured_peaks()
-        bytes_step = 44.0                      # 10 dataset floats written + 1 noise float read per env-step
+        bytes_step = 40.0 if device_rng else 44.0      # 10 dataset floats written (+ 1 noise float read) per env-step
         tflops = FLOP_PER_ENV_STEP * N * T / (ms * 1e-3) / 1e12
         print(json.dumps({"metric": "env-steps/s (on-policy collect: actor fwd + Gaussian head + env step + dataset row)", "value": world * N * T / (ms * 1e-3),
                           "unit": "env-steps/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
                           "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                           "config": {"workload": f"pendulum_collect_{N}env_x{T}step_actor3-64-64-1_limit{limit}", "l2": "flushed between timed iterations",
-                                     "parallelism": f"env-sharded x{world}, no collective"},
+                                     "parallelism": f"env-sharded x{world}, no collective", "rng": "philox4x32-10 in the kernel" if device_rng else "host draw tables resident in HBM",
+                                     "host_tables_ms_per_call": host_tables_ms},
                           "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
                                        "peak_source": peaks["source"] + " bf16 dense (burst)", "hbm_gbs": bytes_step * N * T / (ms * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]},
                           "gpu_launches": args.steps}))
@@ -548,6 +568,8 @@ def main():
                          "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
                          "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
     ap.add_argument("--collect-steps", type=int, default=64, help="collect: steps per environment per call")
+    ap.add_argument("--collect-rng", default="tables", choices=["tables", "device"],
+                    help="collect: random numbers from host draw tables (bit-compatible with the reference's host engine) or drawn inside the kernel")
     ap.add_argument("--train-rows", type=int, default=1 << 24, help="mlp_train: total input rows over all GPUs")
     args = ap.parse_args()
     if args.workload == "mlp_train":

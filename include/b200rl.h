@@ -269,6 +269,21 @@ int b200rl_pendulum_collect_layers(const b200rl_mlp_shape* actor, const float* c
                                    float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
                                    const float* reset_states, int n_reset_rounds, const float* noise, int n_envs, int n_steps,
                                    int step_limit, float* dataset, int ld_dataset, int* error_flag, b200rl_stream_t stream);
+/* Device-side random numbers: the same two kernels without host draw tables. Every (environment e, step s) owns one block of the
+ * counter-based Philox-4x32-10 generator, counter = (e, s low, s high, 0), key = seed: words 0-1 give the standard-normal action noise
+ * (Box-Muller), words 2-3 the initial state (theta uniform in (-pi, pi), theta_dot in (-1, 1), the distribution of
+ * rl/environments/pendulum/operations_generic.h:57-61). s counts from first_step: pass the number of steps already collected so that
+ * consecutive calls continue the stream. The draws do not depend on how environments are sharded over launches or GPUs. This is the
+ * counterpart of the reference's device engines (random/operations_cuda.h uses cuRAND state per thread): statistically equivalent
+ * to, not bit-identical with, the host engine of the table-driven entry points. */
+int b200rl_pendulum_collect_device_rng(const b200rl_mlp_shape* actor, const float* actor_params, const float* log_std, float* states,
+                                       int32_t* episode_step, uint8_t* truncated, float* episode_return, unsigned long long seed,
+                                       unsigned long long first_step, int n_envs, int n_steps, int step_limit, float* dataset,
+                                       int ld_dataset, int* error_flag, b200rl_stream_t stream);
+int b200rl_pendulum_rollout_device_rng(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
+                                       uint8_t* truncated, float* episode_return, unsigned long long seed, unsigned long long first_step,
+                                       int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
+                                       b200rl_stream_t stream);
 /* Host tables for one collect call in the reference engine's draw order (per step: environments ascending, initial state of every
  * truncated environment; then environments ascending, one normal draw per action). rng_state_host as in b200rl_rng_init_host,
  * advanced in place, so consecutive calls continue the reference's stream. */

@@ -135,6 +135,9 @@ def lib():
         L.b200rl_collect_tables_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i), vp]
         L.b200rl_pendulum_collect.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
+        u64 = C.c_uint64
+        L.b200rl_pendulum_collect_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, i, vp, vp]
+        L.b200rl_pendulum_rollout_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, vp, vp, vp, vp]
         _lib = L
     return _lib
 
@@ -395,6 +398,34 @@ def pendulum_collect(shape, params, log_std, states, episode_step, truncated, ep
                                             _ptr(episode_return), _ptr(reset_states), R, _ptr(noise), N, n_steps, step_limit, _ptr(dataset),
                                             dataset.stride(0), _ptr(error_flag), _stream()), "b200rl_pendulum_collect")
     return dataset
+
+
+def pendulum_collect_device_rng(shape, params, log_std, states, episode_step, truncated, episode_return, seed, first_step, n_steps, step_limit,
+                                dataset=None, error_flag=None):
+    """On-policy collect with resets and action noise drawn on the device (Philox-4x32-10 keyed by `seed`, one block per environment and
+    step, steps counted from `first_step`): no host draw tables. Same dataset layout as pendulum_collect."""
+    import torch
+    N = states.shape[0]
+    dataset = torch.zeros(((n_steps + 1) * N, 13), device=states.device, dtype=torch.float32) if dataset is None else dataset
+    check(lib().b200rl_pendulum_collect_device_rng(C.byref(shape), _ptr(params), _ptr(log_std), _ptr(states), _ptr(episode_step), _ptr(truncated),
+                                                   _ptr(episode_return), seed, first_step, N, n_steps, step_limit, _ptr(dataset), dataset.stride(0),
+                                                   _ptr(error_flag), _stream()), "b200rl_pendulum_collect_device_rng")
+    return dataset
+
+
+def pendulum_rollout_device_rng(shape, params, states, episode_step, truncated, episode_return, seed, first_step, n_steps, step_limit=200,
+                                obs=None, act=None, rew=None, error_flag=None):
+    """pendulum_rollout with the initial states of truncated environments drawn on the device (see pendulum_collect_device_rng)."""
+    import torch
+    N = states.shape[0]
+    dev = states.device
+    obs = torch.empty((n_steps * N, 3), device=dev, dtype=torch.float32) if obs is None else obs
+    act = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if act is None else act
+    rew = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if rew is None else rew
+    check(lib().b200rl_pendulum_rollout_device_rng(C.byref(shape), _ptr(params), _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return),
+                                                   seed, first_step, N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(error_flag), _stream()),
+          "b200rl_pendulum_rollout_device_rng")
+    return obs, act, rew
 
 
 def shuffle_permutation_host(rng_state, n_rows):

@@ -42,8 +42,13 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
     }
 
     for(int t = 0; t < a.n_steps; t++){
+        StepDraws draws{};
+        if(a.device_rng) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
         if(trunc){
-            if(a.reset_states != nullptr && resets < a.n_reset_rounds){
+            if(a.device_rng){        // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
+                theta = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(draws.u_theta_dot, 2.0f, -1.0f);
+            }
+            else if(a.reset_states != nullptr && resets < a.n_reset_rounds){
                 const float2 rs = *reinterpret_cast<const float2*>(a.reset_states + ((size_t)resets * a.n_envs + e) * 2);
                 theta = rs.x; theta_dot = rs.y;
             }
@@ -80,7 +85,7 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
         float action = activation_rt(out, act_out);
         if constexpr(COLLECT){
             const float mean = action;
-            action = head.sample(mean, __ldg(a.noise + row));
+            action = head.sample(mean, a.device_rng ? draws.normal : __ldg(a.noise + row));
             drow[COL_ACTION_MEAN] = mean; drow[COL_ACTION] = action; drow[COL_LOG_PROB] = head.log_prob(mean, action, a.neg_half_log_2pi);
         }
 
@@ -141,10 +146,13 @@ int rollout_dispatch(const b200rl_mlp_shape* actor, const RolloutArgs& a, cudaSt
 }  // namespace b200rl
 using namespace b200rl;
 
-extern "C" int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
-                                       uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds,
-                                       int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
-                                       b200rl_stream_t stream){
+// device_rng: resets (and, for collect, the action noise) from the counter-based generator instead of host tables
+struct DeviceRng { int enabled; unsigned long long seed, step0; };
+
+static int rollout_launch(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
+                          uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds,
+                          int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
+                          DeviceRng rng, cudaStream_t stream){
     int rc = validate_actor(actor);
     if(rc) return rc;
     if(!actor_params || !states || !episode_step || !truncated || !episode_return || !obs || !act || !rew || n_envs < 0 || n_steps < 0 || n_reset_rounds < 0 || step_limit < 1)
@@ -155,8 +163,25 @@ extern "C" int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const floa
     a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
     a.reset_states = reset_states; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs; a.env_begin = 0; a.env_count = n_envs;
     a.n_steps = n_steps; a.step_limit = step_limit; a.obs = obs; a.act = act; a.rew = rew; a.error_flag = error_flag;
+    a.device_rng = rng.enabled; a.rng_seed = rng.seed; a.rng_step0 = rng.step0;
     for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
-    return rollout_dispatch(actor, a, (cudaStream_t)stream);
+    return rollout_dispatch(actor, a, stream);
+}
+
+extern "C" int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
+                                       uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds,
+                                       int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
+                                       b200rl_stream_t stream){
+    return rollout_launch(actor, actor_params, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds, n_envs, n_steps,
+                          step_limit, obs, act, rew, error_flag, DeviceRng{0, 0, 0}, (cudaStream_t)stream);
+}
+
+extern "C" int b200rl_pendulum_rollout_device_rng(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
+                                                  uint8_t* truncated, float* episode_return, unsigned long long seed, unsigned long long first_step,
+                                                  int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
+                                                  b200rl_stream_t stream){
+    return rollout_launch(actor, actor_params, states, episode_step, truncated, episode_return, nullptr, 0, n_envs, n_steps,
+                          step_limit, obs, act, rew, error_flag, DeviceRng{1, seed, first_step}, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -165,11 +190,12 @@ extern "C" int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const floa
 // ---------------------------------------------------------------------------------------------------------------
 static int collect_launch(const b200rl_mlp_shape* actor, const float* actor_params, const float* log_std, float* states, int32_t* episode_step,
                           uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, const float* noise,
-                          int n_envs, int n_steps, int step_limit, float* dataset, int ld_dataset, int* error_flag, cudaStream_t stream){
+                          int n_envs, int n_steps, int step_limit, float* dataset, int ld_dataset, int* error_flag, cudaStream_t stream,
+                          DeviceRng rng = DeviceRng{0, 0, 0}){
     int rc = validate_actor(actor);
     if(rc) return rc;
     if(!actor_params || !log_std || !states || !episode_step || !truncated || !episode_return || !dataset || n_envs < 0 || n_steps < 0 ||
-       n_reset_rounds < 0 || step_limit < 0 || ld_dataset < COLLECT_DATA_DIM || (noise == nullptr && n_steps > 0))
+       n_reset_rounds < 0 || step_limit < 0 || ld_dataset < COLLECT_DATA_DIM || (noise == nullptr && n_steps > 0 && !rng.enabled))
         return B200RL_ERR_INVALID_ARGUMENT;
     if(reset_states == nullptr && n_reset_rounds != 0) return B200RL_ERR_INVALID_ARGUMENT;
     if(n_envs == 0) return B200RL_OK;
@@ -179,6 +205,7 @@ static int collect_launch(const b200rl_mlp_shape* actor, const float* actor_para
     a.n_steps = n_steps; a.step_limit = step_limit; a.error_flag = error_flag;
     a.dataset = dataset; a.ld_dataset = ld_dataset; a.noise = noise; a.log_std = log_std;
     a.neg_half_log_2pi = (float)(-0.5 * logf(2 * 3.14159265358979323846f));      // random/operations_generic.h:89
+    a.device_rng = rng.enabled; a.rng_seed = rng.seed; a.rng_step0 = rng.step0;
     for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
     return rollout_dispatch(actor, a, stream);
 }
@@ -189,6 +216,14 @@ extern "C" int b200rl_pendulum_collect(const b200rl_mlp_shape* actor, const floa
                                        int ld_dataset, int* error_flag, b200rl_stream_t stream){
     return collect_launch(actor, actor_params, log_std, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds, noise,
                           n_envs, n_steps, step_limit, dataset, ld_dataset, error_flag, (cudaStream_t)stream);
+}
+
+extern "C" int b200rl_pendulum_collect_device_rng(const b200rl_mlp_shape* actor, const float* actor_params, const float* log_std, float* states,
+                                                  int32_t* episode_step, uint8_t* truncated, float* episode_return, unsigned long long seed,
+                                                  unsigned long long first_step, int n_envs, int n_steps, int step_limit, float* dataset,
+                                                  int ld_dataset, int* error_flag, b200rl_stream_t stream){
+    return collect_launch(actor, actor_params, log_std, states, episode_step, truncated, episode_return, nullptr, 0, nullptr,
+                          n_envs, n_steps, step_limit, dataset, ld_dataset, error_flag, (cudaStream_t)stream, DeviceRng{1, seed, first_step});
 }
 
 // Actor given as separately allocated layer tensors (how the reference's containers hold them): packed into a file-scope

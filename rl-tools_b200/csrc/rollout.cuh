@@ -25,7 +25,40 @@ struct RolloutArgs {
     const float* noise;         // [n_steps, n_envs] standard-normal draws in the reference engine's order
     const float* log_std;       // device scalar: the actor's state-independent log standard deviation
     float neg_half_log_2pi;     // (float)(-0.5 * logf(2 pi)), evaluated on the host like the reference does
+    // device-side random numbers (device_rng != 0): resets and action noise come from a counter-based generator keyed by
+    // (rng_seed, environment, rng_step0 + step) instead of the host draw tables; reset_states and noise are then unused
+    int device_rng;
+    unsigned long long rng_seed, rng_step0;
 };
+
+// Philox-4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11): a counter-based generator, so the
+// draw of (environment, step) does not depend on how the environments are sharded over launches or GPUs.
+struct Philox {
+    static constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+    __host__ __device__ static inline void block(uint32_t (&c)[4], uint32_t k0, uint32_t k1){
+#pragma unroll
+        for(int round = 0; round < 10; round++){
+            const unsigned long long p0 = (unsigned long long)M0 * c[0], p1 = (unsigned long long)M1 * c[2];
+            const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n1 = (uint32_t)p1, n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1, n3 = (uint32_t)p0;
+            c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+            k0 += W0; k1 += W1;
+        }
+    }
+};
+// One block per (environment, step): words 0-1 -> one standard normal (Box-Muller, cosine branch), words 2-3 -> the two uniforms of
+// an initial state. u = ((word >> 9) + 0.5) * 2^-23 is exact in fp32 and lies strictly inside (0, 1).
+struct StepDraws { float normal, u_theta, u_theta_dot; };
+__device__ __forceinline__ float unit_uniform(uint32_t word){ return ((float)(word >> 9) + 0.5f) * 1.1920928955078125e-7f; }   // 2^-23
+__device__ __forceinline__ StepDraws step_draws(unsigned long long seed, unsigned long long step, uint32_t env){
+    uint32_t c[4] = {env, (uint32_t)step, (uint32_t)(step >> 32), 0u};
+    Philox::block(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+    const float u1 = unit_uniform(c[0]), u2 = unit_uniform(c[1]);
+    StepDraws d;
+    d.normal = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+    d.u_theta = unit_uniform(c[2]);
+    d.u_theta_dot = unit_uniform(c[3]);
+    return d;
+}
 
 // Columns of the on-policy dataset for Pendulum (observation 3, action 1; rl/components/on_policy_runner/on_policy_runner.h:38-72)
 enum CollectColumns { COL_OBS = 0, COL_ACTION_MEAN = 3, COL_ACTION = 4, COL_LOG_PROB = 5, COL_REWARD = 6, COL_TERMINATED = 7,

@@ -168,8 +168,13 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             float* st_obs = reinterpret_cast<float*>(stage_base + (uint32_t)(t % 3) * STAGE_BUF_BYTES);
             float* st_act = st_obs + TILE * 3;
             float* st_rew = st_act + TILE;
+            StepDraws draws{};
+            if(a.device_rng) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
             if(trunc){
-                if(a.reset_states != nullptr && resets < a.n_reset_rounds){
+                if(a.device_rng){    // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
+                    theta = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(draws.u_theta_dot, 2.0f, -1.0f);
+                }
+                else if(a.reset_states != nullptr && resets < a.n_reset_rounds){
                     const float2 rs = *reinterpret_cast<const float2*>(a.reset_states + ((size_t)resets * a.n_envs + e) * 2);
                     theta = rs.x; theta_dot = rs.y;
                 }
@@ -271,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             float action = activation_rt(c_actor[C_B3] + ((o0 + o1) + (o2 + o3)), act3);
             if constexpr(COLLECT){
                 const float mean = action;
-                action = head.sample(mean, valid ? __ldg(a.noise + row) : 0.0f);
+                action = head.sample(mean, a.device_rng ? draws.normal : (valid ? __ldg(a.noise + row) : 0.0f));
                 if(valid){ drow[COL_ACTION_MEAN] = mean; drow[COL_ACTION] = action; drow[COL_LOG_PROB] = head.log_prob(mean, action, a.neg_half_log_2pi); }
             }
 

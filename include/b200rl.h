@@ -100,6 +100,11 @@ int b200rl_mse_gradient(const float* a, int lda, const float* b, int ldb, float*
 /* dst[0..n) = value. Replaces the cudaMemsetAsync pairs of zero_gradient / _reset_optimizer_state
  * (nn/layers/dense/operations_cuda.h:415-432) -- with the flat arena below it is one call per network. */
 int b200rl_fill(float* dst, size_t n, float value, b200rl_stream_t stream);
+/* Target-network (Polyak) update: target = polyak * target + (1 - polyak) * source, or with source * source when square != 0
+ * (update / update_squared, utils/polyak/operations_generic.h:10-40; CUDA form utils/polyak/operations_cuda.h:12-52; called per layer by
+ * update_critic_targets, rl/algorithms/sac/operations_generic.h:486-496). Row-major [rows, cols] matrices with row pitches ld_*. */
+int b200rl_polyak_update(const float* source, int ld_source, float* target, int ld_target, int rows, int cols, float polyak, int square,
+                         b200rl_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * MLP on a flat parameter arena. For each layer l: W_l [O_l, I_l] row-major, then b_l [O_l]; gradients and both
@@ -315,6 +320,39 @@ int b200rl_pendulum_offpolicy_step(const b200rl_mlp_shape* actor, const float* a
                                    int step_limit, float* observations, float* actions, float* next_observations, void* replay_buffers,
                                    const b200rl_replay_layout* layout, float* reward_scratch, uint8_t* was_truncated_scratch, int* error_flag,
                                    b200rl_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Replay-buffer sampling: gather_batch(device, runner, batch, rng) for SequentialBatch with SEQUENCE_LENGTH 1 and its default sampling
+ * parameters (rl/components/off_policy_runner/operations_generic.h:239-423, off_policy_runner.h:80-156; CUDA form
+ * operations_cuda.h:136-182). Per batch element the reference draws the environment index, then a sample offset in [0, eligible - 1]
+ * (eligible = full ? capacity : position of that environment's replay buffer); the transition index is the offset, or
+ * (position + max_episode_length + offset) mod capacity once the buffer is full. Outputs (device):
+ *   oa_base [2, batch, ld_oa]: step 0 = observation | action of the transition, step 1 = its next observation | zeros
+ *     (observations_actions_base of the batch: observations_current / actions_current view step 0, observations_next step 1);
+ *   rewards [batch] floats; terminated, reset (= 1), final_step_mask (= 1) [batch] bytes;
+ *   next_reset_base (= 1, 1), next_final_step_mask_base (= 0, 1) [2, batch] bytes.
+ * Rows of the replay data matrix are observation | action | reward | next observation | terminated | truncated
+ * (rl/components/replay_buffer/replay_buffer.h:32-62). max_episode_length is the ENVIRONMENT's EPISODE_STEP_LIMIT
+ * (off_policy_runner.h:41). An index outside its range sets *error_flag = 2 and skips the element.
+ * b200rl_replay_counters copies (position, full) of every environment's buffer into dense device arrays (for the host draws);
+ * b200rl_gather_draws_host makes the draws on the reference-compatible host engine in the reference's order, advanced in place. */
+int b200rl_replay_counters(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int32_t* position, uint8_t* full,
+                           b200rl_stream_t stream);
+int b200rl_gather_draws_host(uint32_t* rng_state_host, int n_envs, int batch, const int32_t* position_host, const uint8_t* full_host,
+                             int capacity, int32_t* env_index_host, int32_t* sample_offset_host);
+int b200rl_gather_batch(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim,
+                        int action_dim, const int32_t* env_index, const int32_t* sample_offset, int batch, float* oa_base, int ld_oa,
+                        float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
+                        uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream);
+
+/* The same gather with both indices drawn inside the kernel (the counterpart of the reference's device-side sampling,
+ * operations_cuda.h:166-182): Philox-4x32-10 block (batch element, call_index low, call_index high, 1) keyed by seed, word 0 -> environment,
+ * word 1 -> sample offset, each bounded by the high half of word * range. No host round trip: usable inside a captured graph when
+ * call_index is advanced by the caller between launches. An empty replay buffer sets *error_flag = 2. */
+int b200rl_gather_batch_device_rng(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length,
+                                   int obs_dim, int action_dim, unsigned long long seed, unsigned long long call_index, int batch,
+                                   float* oa_base, int ld_oa, float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base,
+                                   uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream);
 
 /* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
  * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and

@@ -93,6 +93,8 @@ class Oracle:
         _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
         L.orc_offpolicy_steps.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i32p, _u8p, _f32p,
                                           _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _f32p, _f32p]
+        L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
+        L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
                                            C.c_void_p, C.c_int, _f32p, C.c_int]
         L.orc_pendulum_collect.restype = C.c_int
@@ -307,6 +309,27 @@ class Oracle:
                                      st["counters"], st["buf_obs"], st["buf_act"], st["buf_next_obs"])
         return st
 
+    def polyak_update(self, source, target, polyak, square=False):
+        """target = polyak * target + (1 - polyak) * source [squared], in place on a 2-D float32 array."""
+        rows, cols = target.shape
+        self.lib.orc_polyak_update(np.ascontiguousarray(source, np.float32), cols, target, cols, rows, cols, polyak, int(square))
+        return target
+
+    @staticmethod
+    def new_batch(batch):
+        """Output arrays of one gather_batch with sequence length 1 (padded length 2)."""
+        return dict(oa_base=np.zeros((2, batch, 4), np.float32), rewards=np.zeros(batch, np.float32), terminated=np.zeros(batch, np.uint8),
+                    reset=np.zeros(batch, np.uint8), next_reset_base=np.zeros((2, batch), np.uint8), final_step_mask=np.zeros(batch, np.uint8),
+                    next_final_step_mask_base=np.zeros((2, batch), np.uint8), env_index=np.zeros(batch, np.int32), sample_index=np.zeros(batch, np.int32))
+
+    def gather_batch(self, st, batch, rng, max_episode_length=200):
+        """One gather_batch on the replay buffers of the state dict `st` (engine `rng` from new_rng, advanced in place)."""
+        N, capacity = st["replay_data"].shape[:2]
+        out = self.new_batch(batch)
+        self.lib.orc_gather_batch(N, capacity, max_episode_length, batch, rng, st["replay_data"], st["counters"], out["oa_base"], out["rewards"], out["terminated"],
+                                  out["reset"], out["next_reset_base"], out["final_step_mask"], out["next_final_step_mask_base"], out["env_index"], out["sample_index"])
+        return out
+
     # --- on-policy collect ---------------------------------------------------------------------------------
     def new_rng(self, seed):
         rng = C.create_string_buffer(4 * 624 + 16)
@@ -380,6 +403,8 @@ class Reference:
         L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
         L.ref_offpolicy_steps.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _i32p, _u8p, _f32p, _f32p, _f32p, _f32p]
+        L.ref_polyak_update.argtypes = [_f32p, _f32p, C.c_float, C.c_int, C.c_int]
+        L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
 
@@ -446,6 +471,27 @@ class Reference:
         if rc != 0:
             raise KeyError("no such off-policy runner case")
         return st
+
+    def polyak_update(self, source, target, polyak, square=False, n_updates=1):
+        """The reference's utils::polyak::update[_squared] on [41, 29] matrices, n_updates times; returns the new target."""
+        assert source.shape == (41, 29) and target.shape == (41, 29)
+        out = np.ascontiguousarray(target, np.float32).copy()
+        self.lib.ref_polyak_update(np.ascontiguousarray(source, np.float32), out, polyak, int(square), n_updates)
+        return out
+
+    GATHER_CASES = ((8, 64, 50, 32), (33, 40, 17, 100), (5, 300, 60, 64))        # (N, capacity, step limit, batch) instantiated in ref_driver.cpp
+
+    def offpolicy_gather(self, N, capacity, step_limit, batch, actor_params, seed, n_steps, n_gathers):
+        """n_steps x step<0>() on a fresh runner, then n_gathers x gather_batch on the same engine: a list of batch dicts (Oracle.new_batch
+        without the index arrays) and the engine's next raw draw afterwards."""
+        outs = [Oracle.new_batch(batch) for _ in range(n_gathers)]
+        stack = {k: np.zeros((n_gathers,) + outs[0][k].shape, outs[0][k].dtype) for k in outs[0] if k not in ("env_index", "sample_index")}
+        next_draw = C.c_uint32(0)
+        rc = self.lib.ref_offpolicy_gather(N, capacity, step_limit, batch, actor_params, seed, n_steps, n_gathers, stack["oa_base"], stack["rewards"], stack["terminated"],
+                                           stack["reset"], stack["next_reset_base"], stack["final_step_mask"], stack["next_final_step_mask_base"], C.byref(next_draw))
+        if rc != 0:
+            raise KeyError("no such gather_batch case")
+        return [{k: v[g] for k, v in stack.items()} for g in range(n_gathers)], next_draw.value
 
     def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset, shuffle_seed=None, env="pendulum", want_seconds=False):
         """The reference's train() on a given dataset matrix [(steps+1)*N, obs + 2 act + 8]; SHUFFLE_EPOCH with an engine seeded by

@@ -212,6 +212,15 @@ void orc_mse_gradient(const float* a, int lda, const float* b, int ldb, float* d
         d_a[(size_t)r * ldd + c] = diff * constant;
     }
 }
+/* Target-network update, utils/polyak/operations_generic.h:10-24 (update) and :26-40 (update_squared):      */
+/* target = polyak * target + (1 - polyak) * source [* source], left to right.                                */
+void orc_polyak_update(const float* source, int ld_source, float* target, int ld_target, int rows, int cols, float polyak, int square){
+    for(int r = 0; r < rows; r++) for(int c = 0; c < cols; c++){
+        const float s = source[(size_t)r * ld_source + c];
+        float* t = target + (size_t)r * ld_target + c;
+        *t = square ? polyak * *t + (1 - polyak) * s * s : polyak * *t + (1 - polyak) * s;
+    }
+}
 /* :9-22 evaluate: sum (a-b)^2 * w / (rows*cols) */
 float orc_mse_evaluate(const float* a, int lda, const float* b, int ldb, int rows, int cols, float loss_weight){
     float acc = 0;
@@ -542,6 +551,46 @@ void orc_offpolicy_steps(const orc_mlp_shape* actor, const float* params, int N,
             if(cnt[0] == 0 && !cnt[1]) cnt[1] = 1;
             states[2 * e] = nt; states[2 * e + 1] = ntd;
         }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* Replay-buffer sampling: gather_batch with SEQUENCE_LENGTH 1 (padded length 2),                             */
+/* rl/components/off_policy_runner/operations_generic.h:413-423 (per batch element: environment index drawn   */
+/* uniformly, then gather_batch_step), :239-411. With the default sampling parameters of sequence length 1    */
+/* (off_policy_runner.h:80-87: no random sequence length, no sampling from the initial state) one element is:   */
+/* offset ~ U{0 .. eligible - 1} with eligible = full ? capacity : position; index = offset, or                */
+/* (position + max_episode_length + offset) mod capacity once the buffer is full (:303-311);                    */
+/* sequence step 0 <- observation, action, reward, terminated of that transition; the step is the sequence's   */
+/* last (:352), so final_step_mask = 1, sequence step 1 <- its next observation with a zero action (:385-402),  */
+/* and next_final_step_mask_base[1] = 1 (:291); reset[0] = next_reset_base[0] = next_reset_base[1] = 1            */
+/* (:279-286, 296-302; next_reset views the base from step 1 when the first step is not a target, :85-91).    */
+/* Outputs: oa_base [2, batch, 4] (observation 3, action 1), rewards [batch], terminated / reset /             */
+/* final_step_mask [batch], next_reset_base / next_final_step_mask_base [2, batch]; env_index / sample_index   */
+/* [batch] (optional): which transition was taken. Storage as in orc_offpolicy_steps.                          */
+/* ------------------------------------------------------------------------------------------------------ */
+void orc_gather_batch(int N, int capacity, int max_episode_length, int batch, orc_rng* rng, const float* replay_data, const int64_t* counters,
+                      float* oa_base, float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
+                      uint8_t* next_final_step_mask_base, int32_t* env_index, int32_t* sample_index){
+    for(int b = 0; b < batch; b++){
+        const int e = (int)orc_uniform_int(rng, 0, (uint64_t)(N - 1));
+        const int64_t position = counters[3 * e], full = counters[3 * e + 1];
+        const int64_t eligible = full ? capacity : position;
+        const int64_t offset = (int64_t)orc_uniform_int(rng, 0, (uint64_t)(eligible - 1));
+        const int64_t index = full ? (position + max_episode_length + offset) % capacity : offset;
+        const float* row = replay_data + ((size_t)e * capacity + index) * 10;
+        float* step0 = oa_base + (size_t)b * 4;
+        float* step1 = oa_base + ((size_t)batch + b) * 4;
+        memcpy(step0, row, sizeof(float) * 4);                 /* observation, action */
+        rewards[b] = row[4];
+        terminated[b] = row[8] != 0.0f;
+        memcpy(step1, row + 5, sizeof(float) * 3);             /* next observation */
+        step1[3] = 0.0f;
+        reset[b] = 1; final_step_mask[b] = 1;
+        next_reset_base[b] = 1; next_reset_base[batch + b] = 1;    /* [1]: through next_reset, the view of steps 1.. (:85-91, :286) */
+        next_final_step_mask_base[b] = 0; next_final_step_mask_base[batch + b] = 1;
+        if(env_index) env_index[b] = e;
+        if(sample_index) sample_index[b] = (int32_t)index;
     }
 }
 

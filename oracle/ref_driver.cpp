@@ -524,7 +524,61 @@ static void offpolicy_case(const float* actor_params, uint32_t seed, int n_steps
     rlt::free(device, actor); rlt::free(device, buffers);
 }
 
+// Replay-buffer sampling through the reference's own gather_batch (rl/components/off_policy_runner/operations_generic.h:239-423) with
+// SEQUENCE_LENGTH 1 (the Markovian default: no random sequence lengths, no sampling from the initial state): n_steps x step<0> on a fresh
+// runner, then n_gathers x gather_batch on the same engine. Per gather: observations_actions_base [2, BATCH, 4], rewards [BATCH],
+// terminated / reset / final_step_mask [BATCH], next_reset_base / next_final_step_mask_base [2, BATCH].
+template <TI N, TI CAPACITY, TI LIMIT, TI BATCH>
+static void gather_case(const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards, uint8_t* terminated, uint8_t* reset,
+                        uint8_t* next_reset_base, uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, uint32_t* next_draw){
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
+    using ACTOR = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<ACTOR_CONFIG>>, rlt::tensor::Shape<TI, 1, N, 3>>;
+    using POLICIES = rlt::utils::Tuple<TI, ACTOR>;
+    using SPEC = rlt::rl::components::off_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, POLICIES, OffPolicyParameters<N, CAPACITY, LIMIT>>;
+    using RUNNER = rlt::rl::components::OffPolicyRunner<SPEC>;
+    using BATCH_SPEC = rlt::rl::components::off_policy_runner::SequentialBatchSpecification<SPEC, 1, BATCH>;
+    using BATCH_TYPE = rlt::rl::components::off_policy_runner::SequentialBatch<BATCH_SPEC>;
+    DEVICE device;
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    ACTOR actor; typename ACTOR::template Buffer<> buffers;
+    rlt::malloc(device, actor); rlt::malloc(device, buffers);
+    { const float* p = actor_params; auto& m = actor.content;
+      load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
+    RUNNER* runner = new RUNNER();
+    BATCH_TYPE batch;
+    rlt::malloc(device, *runner); rlt::malloc(device, batch);
+    rlt::init(device, *runner);
+    for(int s = 0; s < n_steps; s++) rlt::step<0>(device, *runner, actor, buffers, rng);
+    for(int g = 0; g < n_gathers; g++){
+        rlt::gather_batch(device, *runner, batch, rng);
+        for(TI q = 0; q < 2; q++) for(TI b = 0; b < BATCH; b++){
+            for(TI k = 0; k < 4; k++) oa_base[(((size_t)g * 2 + q) * BATCH + b) * 4 + k] = rlt::get(device, batch.observations_actions_base, q, b, k);
+            next_reset_base[((size_t)g * 2 + q) * BATCH + b] = rlt::get(device, batch.next_reset_base, q, b, 0) ? 1 : 0;
+            next_final_step_mask_base[((size_t)g * 2 + q) * BATCH + b] = rlt::get(device, batch.next_final_step_mask_base, q, b, 0) ? 1 : 0;
+        }
+        for(TI b = 0; b < BATCH; b++){
+            rewards[(size_t)g * BATCH + b] = rlt::get(device, batch.rewards, 0, b, 0);
+            terminated[(size_t)g * BATCH + b] = rlt::get(device, batch.terminated, 0, b, 0) ? 1 : 0;
+            reset[(size_t)g * BATCH + b] = rlt::get(device, batch.reset, 0, b, 0) ? 1 : 0;
+            final_step_mask[(size_t)g * BATCH + b] = rlt::get(device, batch.final_step_mask, 0, b, 0) ? 1 : 0;
+        }
+    }
+    if(next_draw) *next_draw = (uint32_t)rng.engine();      // where the engine stands afterwards
+    rlt::free(device, *runner); delete runner; rlt::free(device, batch);
+    rlt::free(device, actor); rlt::free(device, buffers);
+}
+
 extern "C" {
+
+int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards,
+                         uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, uint32_t* next_draw){
+#define GATHER_CASE(n, c, l, b) if(N == n && capacity == c && step_limit == l && batch == b){ gather_case<n, c, l, b>(actor_params, seed, n_steps, n_gathers, oa_base, rewards, terminated, reset, next_reset_base, final_step_mask, next_final_step_mask_base, next_draw); return 0; }
+    GATHER_CASE(8, 64, 50, 32)
+    GATHER_CASE(33, 40, 17, 100)
+    GATHER_CASE(5, 300, 60, 64)
+#undef GATHER_CASE
+    return -1;
+}
 
 int ref_offpolicy_steps(int N, int capacity, int step_limit, const float* actor_params, uint32_t seed, int n_steps, float* replay_data, int64_t* episode_start,
                          float* replay_states, float* replay_next_states, int64_t* counters, float* states_out, int32_t* episode_step_out, uint8_t* truncated_out,
@@ -551,6 +605,19 @@ int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle,
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 10, true)
 #undef PPO_CASE
     return -1;
+}
+// utils::polyak::update / update_squared (utils/polyak/operations_generic.h:10-40) on a [41, 29] matrix, n_updates times in a row
+void ref_polyak_update(const float* source, float* target, float polyak, int square, int n_updates){
+    DEVICE device;
+    rlt::Matrix<rlt::matrix::Specification<float, TI, 41, 29>> src, dst;
+    rlt::malloc(device, src); rlt::malloc(device, dst);
+    for(TI r = 0; r < 41; r++) for(TI c = 0; c < 29; c++){ rlt::set(src, r, c, source[r * 29 + c]); rlt::set(dst, r, c, target[r * 29 + c]); }
+    for(int i = 0; i < n_updates; i++){
+        if(square) rlt::utils::polyak::update_squared(device, src, dst, polyak);
+        else rlt::utils::polyak::update(device, src, dst, polyak);
+    }
+    for(TI r = 0; r < 41; r++) for(TI c = 0; c < 29; c++) target[r * 29 + c] = rlt::get(dst, r, c);
+    rlt::free(device, src); rlt::free(device, dst);
 }
 // std::uniform_int_distribution<TI>(lo, hi) as random/operations_cpu.h:27-29 drives it (TI = the CPU device's index type)
 void ref_rng_uniform_int(uint32_t seed, int n, const uint64_t* lo, const uint64_t* hi, uint64_t* out){

@@ -133,6 +133,11 @@ def lib():
         L.b200rl_permute_rows.argtypes = [vp, i, i, vp, C.c_uint64, vp, sz, vp]
         L.b200rl_pendulum_offpolicy_step.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp, vp, vp, C.POINTER(ReplayLayout), vp, vp, vp, vp]
         L.b200rl_collect_tables_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i), vp]
+        L.b200rl_polyak_update.argtypes = [vp, i, vp, i, i, i, f, i, vp]
+        L.b200rl_replay_counters.argtypes = [vp, C.POINTER(ReplayLayout), i, vp, vp, vp]
+        L.b200rl_gather_draws_host.argtypes = [vp, i, i, vp, vp, i, vp, vp]
+        L.b200rl_gather_batch.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, vp, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.b200rl_gather_batch_device_rng.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, C.c_uint64, C.c_uint64, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
         L.b200rl_pendulum_collect.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         u64 = C.c_uint64
@@ -458,3 +463,55 @@ def pendulum_offpolicy_step(shape, params, states, episode_step, truncated, epis
     check(lib().b200rl_pendulum_offpolicy_step(C.byref(shape), _ptr(params) if layers is None else None, table, _ptr(states), _ptr(episode_step), _ptr(truncated),
                                                _ptr(episode_return), _ptr(reset_states), N, step_limit, _ptr(observations), _ptr(actions), _ptr(next_observations),
                                                _ptr(replay), C.byref(layout), _ptr(rew), _ptr(was), _ptr(error_flag), _stream()), "b200rl_pendulum_offpolicy_step")
+
+
+def replay_counters(replay, layout, n_envs):
+    """(position int32[N], full uint8[N]) of every environment's replay buffer, as CUDA tensors."""
+    import torch
+    position = torch.empty(n_envs, device=replay.device, dtype=torch.int32)
+    full = torch.empty(n_envs, device=replay.device, dtype=torch.uint8)
+    check(lib().b200rl_replay_counters(_ptr(replay), C.byref(layout), n_envs, _ptr(position), _ptr(full), _stream()), "b200rl_replay_counters")
+    return position, full
+
+
+def gather_draws_host(rng_state, n_envs, batch, position, full, capacity):
+    """The draws of one gather_batch on the reference-compatible host engine (advanced in place): (env_index, sample_offset) numpy int32[batch]."""
+    import numpy as np
+    position, full = np.ascontiguousarray(position, np.int32), np.ascontiguousarray(full, np.uint8)
+    env_index, offset = np.empty(batch, np.int32), np.empty(batch, np.int32)
+    check(lib().b200rl_gather_draws_host(C.c_void_p(rng_state.ctypes.data), n_envs, batch, C.c_void_p(position.ctypes.data), C.c_void_p(full.ctypes.data), capacity,
+                                         C.c_void_p(env_index.ctypes.data), C.c_void_p(offset.ctypes.data)), "b200rl_gather_draws_host")
+    return env_index, offset
+
+
+def new_batch(batch, obs_dim=3, action_dim=1, device="cuda"):
+    """Output tensors of gather_batch (sequence length 1, padded length 2)."""
+    import torch
+    u8 = dict(device=device, dtype=torch.uint8)
+    return dict(oa_base=torch.zeros((2, batch, obs_dim + action_dim), device=device), rewards=torch.zeros(batch, device=device),
+                terminated=torch.zeros(batch, **u8), reset=torch.zeros(batch, **u8), next_reset_base=torch.zeros((2, batch), **u8),
+                final_step_mask=torch.zeros(batch, **u8), next_final_step_mask_base=torch.zeros((2, batch), **u8))
+
+
+def gather_batch(replay, layout, n_envs, out, env_index=None, sample_offset=None, seed=None, call_index=0, max_episode_length=200, obs_dim=3, action_dim=1,
+                 error_flag=None):
+    """Replay-buffer sampling into the batch tensors `out` (new_batch): indices either given (int32 CUDA tensors drawn by gather_draws_host) or
+    drawn inside the kernel from (seed, call_index)."""
+    batch = out["rewards"].shape[0]
+    tail = (batch, _ptr(out["oa_base"]), out["oa_base"].stride(1), _ptr(out["rewards"]), _ptr(out["terminated"]), _ptr(out["reset"]), _ptr(out["next_reset_base"]),
+            _ptr(out["final_step_mask"]), _ptr(out["next_final_step_mask_base"]), _ptr(error_flag), _stream())
+    if seed is None:
+        check(lib().b200rl_gather_batch(_ptr(replay), C.byref(layout), n_envs, max_episode_length, obs_dim, action_dim, _ptr(env_index), _ptr(sample_offset), *tail),
+              "b200rl_gather_batch")
+    else:
+        check(lib().b200rl_gather_batch_device_rng(_ptr(replay), C.byref(layout), n_envs, max_episode_length, obs_dim, action_dim, seed, call_index, *tail),
+              "b200rl_gather_batch_device_rng")
+    return out
+
+
+def polyak_update(source, target, polyak, square=False):
+    """target = polyak * target + (1 - polyak) * source [squared], in place on 2-D CUDA tensors (row pitches honoured)."""
+    rows, cols = target.shape
+    check(lib().b200rl_polyak_update(_ptr(source), source.stride(0), _ptr(target), target.stride(0), rows, cols, float(polyak), int(square), _stream()),
+          "b200rl_polyak_update")
+    return target

@@ -102,10 +102,35 @@ static int grid_for(size_t work_items, int per_block){
 }
 static bool aligned16(const void* p){ return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Target-network update (utils/polyak/operations_generic.h:10-24, 26-40; CUDA form operations_cuda.h:12-52):
+// target = polyak * target + (1 - polyak) * source (source squared in the second form), the two products rounded separately.
+template <bool SQUARE>
+__global__ void __launch_bounds__(256) polyak_kernel(const float* __restrict__ source, int ld_source, float* __restrict__ target, int ld_target,
+                                                     int rows, int cols, float polyak, float one_minus){
+    const size_t n = (size_t)rows * cols, stride = (size_t)gridDim.x * blockDim.x;
+    for(size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += stride){
+        const size_t r = i / cols, c = i - r * cols;
+        float s = source[r * ld_source + c];
+        float* t = target + r * ld_target + c;
+        if constexpr(SQUARE) *t = __fadd_rn(__fmul_rn(polyak, *t), __fmul_rn(__fmul_rn(one_minus, s), s));
+        else *t = __fadd_rn(__fmul_rn(polyak, *t), __fmul_rn(one_minus, s));
+    }
+}
+
 }  // namespace b200rl
 using namespace b200rl;
 
 extern "C" {
+
+int b200rl_polyak_update(const float* source, int ld_source, float* target, int ld_target, int rows, int cols, float polyak, int square, b200rl_stream_t stream){
+    if(!source || !target || rows < 0 || cols < 1 || ld_source < cols || ld_target < cols) return B200RL_ERR_INVALID_ARGUMENT;
+    if(rows == 0) return B200RL_OK;
+    const int grid = grid_for((size_t)rows * cols, 256);
+    if(square) polyak_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(source, ld_source, target, ld_target, rows, cols, polyak, 1.0f - polyak);
+    else polyak_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(source, ld_source, target, ld_target, rows, cols, polyak, 1.0f - polyak);
+    B200RL_LAUNCH_CHECK("polyak_update");
+    return B200RL_OK;
+}
 
 int b200rl_adam_reset(uint32_t* state, b200rl_stream_t stream){
     if(!state) return B200RL_ERR_INVALID_ARGUMENT;

@@ -258,6 +258,21 @@ int b200rl_shuffle_permutation_host(uint32_t* rng, int n_rows, int32_t* perm_hos
     return B200RL_OK;
 }
 
+// gather_batch (rl/components/off_policy_runner/operations_generic.h:413-423, 257-258, 303): per batch element the environment index, then the
+// sample offset in [0, eligible - 1] with eligible = full ? capacity : position of that environment's replay buffer
+int b200rl_gather_draws_host(uint32_t* rng, int n_envs, int batch, const int32_t* position_host, const uint8_t* full_host, int capacity,
+                             int32_t* env_index_host, int32_t* sample_offset_host){
+    if(!rng || !position_host || !full_host || !env_index_host || !sample_offset_host || n_envs < 1 || batch < 0 || capacity < 1) return B200RL_ERR_INVALID_ARGUMENT;
+    for(int b = 0; b < batch; b++){
+        const int e = (int)uniform_int_below(rng, (uint32_t)n_envs);
+        const int eligible = full_host[e] ? capacity : position_host[e];
+        if(eligible < 1) return B200RL_ERR_INVALID_ARGUMENT;          // the reference requires a non-empty replay buffer (:241)
+        env_index_host[b] = e;
+        sample_offset_host[b] = (int32_t)uniform_int_below(rng, (uint32_t)eligible);
+    }
+    return B200RL_OK;
+}
+
 int b200rl_release_host_staging(void){ g_staging.release(); return B200RL_OK; }
 
 int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* actor_params_host, float* states_host,

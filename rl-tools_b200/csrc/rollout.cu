@@ -349,3 +349,125 @@ extern "C" int b200rl_pendulum_offpolicy_step(const b200rl_mlp_shape* actor, con
     B200RL_LAUNCH_CHECK("replay_add");
     return B200RL_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Replay-buffer sampling: gather_batch with sequence length 1 (rl/components/off_policy_runner/operations_generic.h:239-423). The two
+// random indices of every batch element are drawn on the host (b200rl_gather_draws_host) in the reference's order; the kernel applies
+// the reference's index arithmetic and writes the batch tensors.
+// ---------------------------------------------------------------------------------------------------------------
+namespace b200rl {
+template <typename INDEX>
+__global__ void replay_counters_kernel(int n_envs, const unsigned char* __restrict__ replay, b200rl_replay_layout L, int32_t* __restrict__ position,
+                                       uint8_t* __restrict__ full){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= n_envs) return;
+    const unsigned char* rb = replay + (size_t)e * L.env_stride;
+    position[e] = (int32_t)*reinterpret_cast<const INDEX*>(rb + L.off_position);
+    full[e] = *(rb + L.off_full) != 0;
+}
+
+struct GatherArgs {
+    const unsigned char* replay; b200rl_replay_layout L;
+    int n_envs, max_episode_length, batch, obs_dim, action_dim;
+    const int32_t *env_index, *sample_offset;
+    float* oa_base; int ld_oa;
+    float* rewards; uint8_t *terminated, *reset, *next_reset_base, *final_step_mask, *next_final_step_mask_base;
+    int* error_flag;
+    int device_rng; unsigned long long seed, call;      // device draws: Philox block (batch element, call low, call high, 1) keyed by seed
+};
+// one warp per batch element: lanes stride over the columns of the transition row
+template <typename INDEX>
+__global__ void gather_batch_kernel(GatherArgs a){
+    const int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if(b >= a.batch) return;
+    int e, offset = 0;
+    uint32_t word1 = 0;
+    if(a.device_rng){         // bounded draws by the high half of word * range (bias below range / 2^32)
+        uint32_t c[4] = {(uint32_t)b, (uint32_t)a.call, (uint32_t)(a.call >> 32), 1u};
+        Philox::block(c, (uint32_t)a.seed, (uint32_t)(a.seed >> 32));
+        e = (int)__umulhi(c[0], (uint32_t)a.n_envs);
+        word1 = c[1];
+    }
+    else{ e = a.env_index[b]; offset = a.sample_offset[b]; }
+    bool ok = e >= 0 && e < a.n_envs && offset >= 0;
+    long long index = 0;
+    const unsigned char* rb = a.replay + (size_t)(ok ? e : 0) * a.L.env_stride;
+    if(ok){
+        const long long position = (long long)*reinterpret_cast<const INDEX*>(rb + a.L.off_position);
+        const bool full = *(rb + a.L.off_full) != 0;
+        if(a.device_rng) offset = (int)__umulhi(word1, (uint32_t)(full ? (long long)a.L.capacity : position));
+        ok = offset < (full ? (long long)a.L.capacity : position);                                       // :257
+        index = full ? (position + a.max_episode_length + offset) % a.L.capacity : (long long)offset;     // :303-311
+    }
+    if(!ok){
+        if(lane == 0 && a.error_flag) *a.error_flag = 2;
+        return;
+    }
+    const float* row = reinterpret_cast<const float*>(rb + a.L.off_data) + (size_t)index * a.L.ld_data;
+    const int O = a.obs_dim, A = a.action_dim;
+    float* step0 = a.oa_base + (size_t)b * a.ld_oa;
+    float* step1 = a.oa_base + ((size_t)a.batch + b) * a.ld_oa;
+    for(int c = lane; c < O + A; c += 32) step0[c] = row[c];                                  // observation, action (:318-341)
+    for(int c = lane; c < O; c += 32) step1[c] = row[O + A + 1 + c];                          // next observation (:385-390)
+    for(int c = lane; c < A; c += 32) step1[O + c] = 0.0f;                                    // :400-402
+    if(lane == 0){
+        a.rewards[b] = row[O + A];
+        a.terminated[b] = row[2 * O + A + 1] != 0.0f;
+        a.reset[b] = 1; a.final_step_mask[b] = 1;                                             // :279-281, :296-299, :352, :381-383
+        a.next_reset_base[b] = 1; a.next_reset_base[a.batch + b] = 1;                         // :285-286
+        a.next_final_step_mask_base[b] = 0; a.next_final_step_mask_base[a.batch + b] = 1;     // :291
+    }
+}
+}  // namespace b200rl
+
+extern "C" int b200rl_replay_counters(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int32_t* position, uint8_t* full,
+                                      b200rl_stream_t stream){
+    if(!replay_buffers || !layout || !position || !full || n_envs < 0 || (layout->index_bytes != 4 && layout->index_bytes != 8)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0) return B200RL_OK;
+    const int threads = 128, blocks = (n_envs + threads - 1) / threads;
+    cudaStream_t s = (cudaStream_t)stream;
+    if(layout->index_bytes == 4) replay_counters_kernel<uint32_t><<<blocks, threads, 0, s>>>(n_envs, static_cast<const unsigned char*>(replay_buffers), *layout, position, full);
+    else replay_counters_kernel<unsigned long long><<<blocks, threads, 0, s>>>(n_envs, static_cast<const unsigned char*>(replay_buffers), *layout, position, full);
+    B200RL_LAUNCH_CHECK("replay_counters");
+    return B200RL_OK;
+}
+
+static int gather_launch(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim,
+                         int action_dim, const int32_t* env_index, const int32_t* sample_offset, int batch, float* oa_base, int ld_oa,
+                         float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
+                         uint8_t* next_final_step_mask_base, int* error_flag, DeviceRng rng, b200rl_stream_t stream){
+    if(!replay_buffers || !layout || (!rng.enabled && (!env_index || !sample_offset)) || !oa_base || !rewards || !terminated || !reset || !next_reset_base || !final_step_mask ||
+       !next_final_step_mask_base || n_envs < 1 || batch < 0 || obs_dim < 1 || action_dim < 1 || max_episode_length < 0)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(layout->capacity < 1 || layout->ld_data < 2 * obs_dim + action_dim + 3 || ld_oa < obs_dim + action_dim || (layout->index_bytes != 4 && layout->index_bytes != 8))
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    GatherArgs a{};
+    a.replay = static_cast<const unsigned char*>(replay_buffers); a.L = *layout; a.n_envs = n_envs; a.max_episode_length = max_episode_length; a.batch = batch;
+    a.obs_dim = obs_dim; a.action_dim = action_dim; a.env_index = env_index; a.sample_offset = sample_offset; a.oa_base = oa_base; a.ld_oa = ld_oa;
+    a.rewards = rewards; a.terminated = terminated; a.reset = reset; a.next_reset_base = next_reset_base; a.final_step_mask = final_step_mask;
+    a.next_final_step_mask_base = next_final_step_mask_base; a.error_flag = error_flag;
+    a.device_rng = rng.enabled; a.seed = rng.seed; a.call = rng.step0;
+    const int threads = 128, blocks = (int)(((size_t)batch * 32 + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if(layout->index_bytes == 4) gather_batch_kernel<uint32_t><<<blocks, threads, 0, s>>>(a);
+    else gather_batch_kernel<unsigned long long><<<blocks, threads, 0, s>>>(a);
+    B200RL_LAUNCH_CHECK("gather_batch");
+    return B200RL_OK;
+}
+
+extern "C" int b200rl_gather_batch(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim,
+                                   int action_dim, const int32_t* env_index, const int32_t* sample_offset, int batch, float* oa_base, int ld_oa,
+                                   float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
+                                   uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream){
+    return gather_launch(replay_buffers, layout, n_envs, max_episode_length, obs_dim, action_dim, env_index, sample_offset, batch, oa_base, ld_oa, rewards,
+                         terminated, reset, next_reset_base, final_step_mask, next_final_step_mask_base, error_flag, DeviceRng{0, 0, 0}, stream);
+}
+
+extern "C" int b200rl_gather_batch_device_rng(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim,
+                                              int action_dim, unsigned long long seed, unsigned long long call_index, int batch, float* oa_base, int ld_oa,
+                                              float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
+                                              uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream){
+    return gather_launch(replay_buffers, layout, n_envs, max_episode_length, obs_dim, action_dim, nullptr, nullptr, batch, oa_base, ld_oa, rewards,
+                         terminated, reset, next_reset_base, final_step_mask, next_final_step_mask_base, error_flag, DeviceRng{1, seed, call_index}, stream);
+}

@@ -2,15 +2,16 @@
 //
 // Include after <b200rl/rl_tools_on_policy_runner.h> and <rl_tools/rl/components/off_policy_runner/operations_generic.h>.
 //
-// Mirrors malloc / free / init / step<POLICY_INDEX> of the reference's CUDA runner (rl/components/off_policy_runner/operations_cuda.h:
+// Mirrors malloc / free / init / step<POLICY_INDEX> / gather_batch of the reference's CUDA runner (rl/components/off_policy_runner/operations_cuda.h:
 // 117-204): the runner's matrices, including the statically allocated per-environment replay-buffer structs, live in device memory,
 // and one step is the fused rollout kernel (T = 1) into the runner's step buffers followed by the replay-buffer append kernel, which
 // writes the reference's struct layout in place (byte offsets taken from the struct type on the host). Reset draws are made on the host
 // with the reference's own sample_initial_state on the caller's engine, in environment order, like the reference's CPU runner.
 //
 // Supported: rl::environments::Pendulum, symmetric observations, policy = sequential< mlp 3 -> 64 -> 64 -> 1 > or that mlp itself, fp32.
-// Not provided: gather_batch (the view members inside the device-resident replay-buffer structs are not initialised: only the data
-// matrix, episode_start and the position / full / current_episode_start counters are maintained), episode statistics.
+// gather_batch is provided for SequentialBatch with sequence length 1. Not provided: longer sequences, episode statistics. The view members
+// inside the device-resident replay-buffer structs are not initialised: only the data matrix, episode_start and the position / full /
+// current_episode_start counters are maintained, and the kernels address rows through byte offsets.
 #pragma once
 #include "rl_tools_on_policy_runner.h"
 #include <memory>
@@ -137,6 +138,52 @@ namespace rl_tools{
         if(flag != 0) b200::note(device, B200RL_ERR_DEVICE_FLAG);
         runner.previous_policy = POLICY_INDEX;
         runner.previous_policy_set = true;
+    }
+    // rl/components/off_policy_runner/operations_generic.h:413-423 (per batch element: environment index, then gather_batch_step :239-411), CUDA
+    // form operations_cuda.h:166-182. Sequence length 1 with its default sampling parameters: the two indices of every element are drawn on the
+    // host from the caller's engine with the reference's own uniform_int_distribution, in the reference's order (the ranges depend on each
+    // buffer's position / full, read back from the device first); one kernel then fills the batch tensors.
+    template <typename DEV_SPEC, typename SPEC, typename BATCH_SPEC, typename RNG, bool DETERMINISTIC = false>
+    void gather_batch(devices::B200<DEV_SPEC>& device, rl::components::OffPolicyRunner<SPEC>& runner, rl::components::off_policy_runner::SequentialBatch<BATCH_SPEC>& batch, RNG& rng){
+        using RUNNER = rl::components::OffPolicyRunner<SPEC>;
+        using BATCH = rl::components::off_policy_runner::SequentialBatch<BATCH_SPEC>;
+        using TI = typename SPEC::TI;
+        using BP = typename BATCH_SPEC::PARAMETERS;
+        static_assert(utils::typing::is_same_v<SPEC, typename BATCH_SPEC::SPEC>);
+        static_assert(BATCH_SPEC::SEQUENCE_LENGTHH == 1 && !BP::RANDOM_SEQ_LENGTH && !BP::ALWAYS_SAMPLE_FROM_INITIAL_STATE && !DETERMINISTIC, "sequence length 1 with its default sampling parameters only");
+        static_assert(!SPEC::PARAMETERS::ASYMMETRIC_OBSERVATIONS && utils::typing::is_same_v<typename BATCH::T_INPUT, float> && sizeof(bool) == 1, "not implemented on this device");
+        constexpr TI N = RUNNER::N_ENVIRONMENTS, B = BATCH::BATCH_SIZE, CAPACITY = SPEC::PARAMETERS::REPLAY_BUFFER_CAPACITY;
+        static const b200rl_replay_layout layout = b200::replay_layout<SPEC>();
+        // work area kept for the life of the process: position [N], env_index [B], sample_offset [B] (int32), full [N] bytes, error flag
+        constexpr size_t OFF_ENV = sizeof(int32_t) * N, OFF_OFFSET = OFF_ENV + sizeof(int32_t) * B, OFF_FULL = OFF_OFFSET + sizeof(int32_t) * B, OFF_FLAG = OFF_FULL + ((N + 15) / 16) * 16;
+        static void* scratch = nullptr;
+        if(!scratch) b200::note(device, b200rl_device_malloc(&scratch, OFF_FLAG + 16));
+        if(!scratch) return;
+        char* sc = static_cast<char*>(scratch);
+        b200::note(device, b200rl_replay_counters(runner.replay_buffers._data, &layout, (int)N, reinterpret_cast<int32_t*>(sc), reinterpret_cast<uint8_t*>(sc + OFF_FULL), device.stream));
+        std::vector<int32_t> position(N), env_index(B), sample_offset(B);
+        std::vector<uint8_t> full(N);
+        b200::note(device, b200rl_memcpy(position.data(), sc, sizeof(int32_t) * N, 1, device.stream));
+        b200::note(device, b200rl_memcpy(full.data(), sc + OFF_FULL, N, 1, device.stream));
+        for(TI batch_step_i = 0; batch_step_i < B; batch_step_i++){
+            const TI env_i = random::uniform_int_distribution(device.random, (TI)0, (TI)(N - 1), rng);
+            const TI eligible = full[env_i] ? CAPACITY : (TI)position[env_i];
+            if(eligible == 0){ b200::note(device, B200RL_ERR_INVALID_ARGUMENT); return; }       // the reference requires a non-empty replay buffer (:241)
+            env_index[batch_step_i] = (int32_t)env_i;
+            sample_offset[batch_step_i] = (int32_t)random::uniform_int_distribution(device.random, (TI)0, (TI)(eligible - 1), rng);
+        }
+        int flag = 0;
+        b200::note(device, b200rl_memcpy(sc + OFF_ENV, env_index.data(), sizeof(int32_t) * B, 0, device.stream));
+        b200::note(device, b200rl_memcpy(sc + OFF_OFFSET, sample_offset.data(), sizeof(int32_t) * B, 0, device.stream));
+        b200::note(device, b200rl_memcpy(sc + OFF_FLAG, &flag, sizeof(int), 0, device.stream));
+        b200::note(device, b200rl_gather_batch(runner.replay_buffers._data, &layout, (int)N, (int)SPEC::MAX_EPISODE_LENGTH, (int)BATCH::OBSERVATION_DIM, (int)BATCH::ACTION_DIM,
+                                               reinterpret_cast<const int32_t*>(sc + OFF_ENV), reinterpret_cast<const int32_t*>(sc + OFF_OFFSET), (int)B,
+                                               batch.observations_actions_base._data, (int)BATCH::DATA_DIM, batch.rewards._data,
+                                               reinterpret_cast<uint8_t*>(batch.terminated._data), reinterpret_cast<uint8_t*>(batch.reset._data),
+                                               reinterpret_cast<uint8_t*>(batch.next_reset_base._data), reinterpret_cast<uint8_t*>(batch.final_step_mask._data),
+                                               reinterpret_cast<uint8_t*>(batch.next_final_step_mask_base._data), reinterpret_cast<int*>(sc + OFF_FLAG), device.stream));
+        b200::note(device, b200rl_memcpy(&flag, sc + OFF_FLAG, sizeof(int), 1, device.stream));
+        if(flag != 0) b200::note(device, B200RL_ERR_DEVICE_FLAG);
     }
 }
 RL_TOOLS_NAMESPACE_WRAPPER_END

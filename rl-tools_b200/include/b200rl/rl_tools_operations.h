@@ -153,6 +153,19 @@ namespace rl_tools{
         }
     }
 
+    // ---- Polyak (target-network) update: utils/polyak/operations_cuda.h:31-52 ---------------------------------------
+    namespace utils::polyak{
+        template<typename DEV_SPEC, typename SOURCE_SPEC, typename TARGET_SPEC, bool SQUARE = false>
+        void update(devices::B200<DEV_SPEC>& device, const Matrix<SOURCE_SPEC>& source, Matrix<TARGET_SPEC>& target, const typename SOURCE_SPEC::T polyak){
+            static_assert(containers::check_structure<SOURCE_SPEC, TARGET_SPEC> && utils::typing::is_same_v<typename SOURCE_SPEC::T, float>);
+            rl_tools::b200::note(device, b200rl_polyak_update(source._data, row_pitch(source), target._data, row_pitch(target), SOURCE_SPEC::ROWS, SOURCE_SPEC::COLS, polyak, SQUARE ? 1 : 0, device.stream));
+        }
+        template<typename DEV_SPEC, typename SOURCE_SPEC, typename TARGET_SPEC>
+        void update_squared(devices::B200<DEV_SPEC>& device, const Matrix<SOURCE_SPEC>& source, Matrix<TARGET_SPEC>& target, const typename SOURCE_SPEC::T polyak){
+            update<DEV_SPEC, SOURCE_SPEC, TARGET_SPEC, true>(device, source, target, polyak);
+        }
+    }
+
     // ---- Adam: nn/optimizers/adam/operations_cuda.h:39-69, instance/operations_cuda.h:60-70 ------------------------
     template<typename DEV_SPEC, typename SPEC>
     void init(devices::B200<DEV_SPEC>& device, nn::optimizers::Adam<SPEC>& optimizer){

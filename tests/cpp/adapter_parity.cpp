@@ -303,13 +303,62 @@ void offpolicy_parity(const char* name){
             }
         }
     }
+    // replay-buffer sampling on both devices from the same engine position: same indices (so the rows differ only by the replay rows' own
+    // drift), identical masks
+    using BATCH_SPEC = rlt::rl::components::off_policy_runner::SequentialBatchSpecification<SPEC, 1, 48>;
+    using BATCH = rlt::rl::components::off_policy_runner::SequentialBatch<BATCH_SPEC>;
+    BATCH batch_cpu, batch_gpu, batch_back;
+    rlt::malloc(cpu, batch_cpu); rlt::malloc(gpu, batch_gpu); rlt::malloc(cpu, batch_back);
+    double gather_diff = 0; bool masks = true;
+    for(int g = 0; g < 3; g++){
+        rlt::gather_batch(cpu, *runner_cpu, batch_cpu, rng_cpu);
+        rlt::gather_batch(gpu, *runner_gpu, batch_gpu, rng_gpu);
+        rlt::copy(gpu, cpu, batch_gpu, batch_back);
+        for(TI q = 0; q < 2; q++) for(TI b = 0; b < 48; b++){
+            for(TI k = 0; k < 4; k++) gather_diff = std::fmax(gather_diff, std::fabs((double)rlt::get(cpu, batch_cpu.observations_actions_base, q, b, k) - (double)rlt::get(cpu, batch_back.observations_actions_base, q, b, k)));
+            masks = masks && rlt::get(cpu, batch_cpu.next_reset_base, q, b, 0) == rlt::get(cpu, batch_back.next_reset_base, q, b, 0);
+            masks = masks && rlt::get(cpu, batch_cpu.next_final_step_mask_base, q, b, 0) == rlt::get(cpu, batch_back.next_final_step_mask_base, q, b, 0);
+        }
+        for(TI b = 0; b < 48; b++){
+            gather_diff = std::fmax(gather_diff, std::fabs((double)rlt::get(cpu, batch_cpu.rewards, 0, b, 0) - (double)rlt::get(cpu, batch_back.rewards, 0, b, 0)));
+            masks = masks && rlt::get(cpu, batch_cpu.terminated, 0, b, 0) == rlt::get(cpu, batch_back.terminated, 0, b, 0);
+            masks = masks && rlt::get(cpu, batch_cpu.reset, 0, b, 0) == rlt::get(cpu, batch_back.reset, 0, b, 0);
+            masks = masks && rlt::get(cpu, batch_cpu.final_step_mask, 0, b, 0) == rlt::get(cpu, batch_back.final_step_mask, 0, b, 0);
+        }
+    }
+    status = status ? status : rlt::check_status(gpu);
     bool engines = rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_cpu) == rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_gpu);
-    bool ok = status == 0 && counters && engines && flags_diff == 0 && rows_diff < 5e-3;
-    std::printf("%-28s envs %3u capacity %3u limit %3u steps %d  status %d  counters %d  engine %d  flags diff %.1e  replay rows drift %.2e  %s\n",
-                name, N, CAPACITY, LIMIT, STEPS, status, (int)counters, (int)engines, flags_diff, rows_diff, ok ? "OK" : "FAIL");
+    bool ok = status == 0 && counters && engines && flags_diff == 0 && rows_diff < 5e-3 && masks && gather_diff < 5e-3;
+    std::printf("%-28s envs %3u capacity %3u limit %3u steps %d  status %d  counters %d  engine %d  flags diff %.1e  replay rows drift %.2e  gather masks %d rows %.2e  %s\n",
+                name, N, CAPACITY, LIMIT, STEPS, status, (int)counters, (int)engines, flags_diff, rows_diff, (int)masks, gather_diff, ok ? "OK" : "FAIL");
     if(!ok) failures++;
+    rlt::free(cpu, batch_cpu); rlt::free(gpu, batch_gpu); rlt::free(cpu, batch_back);
     rlt::free(cpu, *runner_cpu); rlt::free(gpu, *runner_gpu);
     rlt::free(cpu, actor_cpu); rlt::free(cpu, buf_cpu); rlt::free(gpu, actor_gpu); rlt::free(gpu, buf_gpu);
+}
+
+// utils::polyak::update / update_squared on both devices from the same inputs: the CPU build here may contract a * b + c, so the bound is
+// one rounding of the result rather than zero
+void polyak_parity(const char* name){
+    constexpr TI ROWS = 67, COLS = 45;
+    DEVICE_CPU cpu; DEVICE_GPU gpu;
+    rlt::init(gpu);
+    DEVICE_CPU::SPEC::RANDOM::ENGINE<> rng; rlt::malloc(cpu, rng); rlt::init(cpu, rng, 3);
+    rlt::Matrix<rlt::matrix::Specification<T, TI, ROWS, COLS>> src_cpu, dst_cpu, src_gpu, dst_gpu, back;
+    rlt::malloc(cpu, src_cpu); rlt::malloc(cpu, dst_cpu); rlt::malloc(cpu, back); rlt::malloc(gpu, src_gpu); rlt::malloc(gpu, dst_gpu);
+    rlt::randn(cpu, src_cpu, rng); rlt::randn(cpu, dst_cpu, rng);
+    rlt::copy(cpu, gpu, src_cpu, src_gpu); rlt::copy(cpu, gpu, dst_cpu, dst_gpu);
+    for(int i = 0; i < 4; i++){
+        rlt::utils::polyak::update(cpu, src_cpu, dst_cpu, (T)0.995); rlt::utils::polyak::update(gpu, src_gpu, dst_gpu, (T)0.995);
+        rlt::utils::polyak::update_squared(cpu, src_cpu, dst_cpu, (T)0.9); rlt::utils::polyak::update_squared(gpu, src_gpu, dst_gpu, (T)0.9);
+    }
+    rlt::copy(gpu, cpu, dst_gpu, back);
+    const int status = rlt::check_status(gpu);
+    const double diff = rlt::abs_diff(cpu, dst_cpu, back) / (ROWS * COLS);
+    const bool ok = status == 0 && diff < 1e-7;
+    std::printf("%-28s %u x %u  status %d  mean diff %.2e  %s\n", name, ROWS, COLS, status, diff, ok ? "OK" : "FAIL");
+    if(!ok) failures++;
+    rlt::free(cpu, src_cpu); rlt::free(cpu, dst_cpu); rlt::free(cpu, back); rlt::free(gpu, src_gpu); rlt::free(gpu, dst_gpu);
 }
 
 int main(){
@@ -331,6 +380,8 @@ int main(){
     collect_parity<1000, 40,  15, act::TANH, 2>("collect_tanh_1000");
     offpolicy_parity<8, 64, 50, 137>("off_policy_runner_step");
     offpolicy_parity<33, 40, 17, 90>("off_policy_runner_wraps");
+    offpolicy_parity<5, 300, 60, 47>("off_policy_runner_part_full");
+    polyak_parity("polyak_target_update");
     ppo_parity<64, 64, 512, 2>("ppo_train_shuffled");
     ppo_parity<16, 128, 2048, 1>("ppo_train_one_batch");
     std::printf("%s\n", failures ? "ADAPTER PARITY FAILED" : "ADAPTER PARITY OK");

@@ -224,3 +224,34 @@ def test_offpolicy_runner_with_replay_buffers_matches_reference(orc, case):
             continue
         got = v[:, :w] if k in ("replay_data", "episode_start") else v
         assert np.array_equal(got, fix[f"{k}_{case}"]), k
+
+
+@pytest.mark.parametrize("case", range(len(mg.GATHER_CASES)))
+def test_gather_batch_matches_reference(orc, case):
+    """gather_batch (sequence length 1) after n runner steps, three consecutive batches on one engine: every batch tensor and the engine's
+    position afterwards, bit for bit (full and partly filled replay buffers, a buffer holding a single transition)."""
+    fix = np.load(os.path.join(GOLDEN, "gather.npz"))
+    N, cap, limit, batch, steps = mg.GATHER_CASES[case]
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    rng = orc.new_rng(mg.GATHER_SEED)
+    st = orc.offpolicy_steps(shape, mg.gather_params(case), orc.new_offpolicy_state(N, cap), limit, steps, rng)
+    for g in range(mg.N_GATHERS):
+        got = orc.gather_batch(st, batch, rng)
+        for k in ("oa_base", "rewards", "terminated", "reset", "next_reset_base", "final_step_mask", "next_final_step_mask_base"):
+            assert np.array_equal(got[k], fix[f"{k}_{case}"][g]), (g, k)
+        # the sampled transition really is the row the indices name
+        rows = st["replay_data"][got["env_index"], got["sample_index"]]
+        assert np.array_equal(got["oa_base"][0], rows[:, :4]) and np.array_equal(got["oa_base"][1, :, :3], rows[:, 5:8])
+    assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == int(fix[f"next_draw_{case}"])
+
+
+@pytest.mark.parametrize("case", range(len(mg.POLYAK_CASES)))
+def test_polyak_update_matches_reference(orc, case):
+    """utils::polyak::update / update_squared, repeated: bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "polyak.npz"))
+    polyak, square, n = mg.POLYAK_CASES[case]
+    source, target = mg.polyak_inputs()
+    target = target.copy()
+    for _ in range(n):
+        orc.polyak_update(source, target, np.float32(polyak), square)
+    assert np.array_equal(target, fix[f"target_{case}"])

@@ -127,3 +127,19 @@ def test_offpolicy_runner_live(orc, ref_strict):
                     continue
                 a, b = (want[k][:, :w], got[k][:, :w]) if k in ("replay_data", "episode_start") else (want[k], got[k])
                 assert np.array_equal(a, b), (N, cap, lim, n_steps, k)
+
+
+def test_gather_batch_live(orc, ref_strict):
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    rs = np.random.RandomState(13)
+    for (N, cap, lim, batch) in oracle.Reference.GATHER_CASES:
+        params = (rs.randn(4481) * 0.3).astype(np.float32)
+        for n_steps in (1, 2, cap - 1, cap, cap + 13, 3 * cap + 5):
+            want, next_draw = ref_strict.offpolicy_gather(N, cap, lim, batch, params, 6, n_steps, 2)
+            rng = orc.new_rng(6)
+            st = orc.offpolicy_steps(shape, params, orc.new_offpolicy_state(N, cap), lim, n_steps, rng)
+            for g in range(2):
+                got = orc.gather_batch(st, batch, rng)
+                for k in want[g]:
+                    assert np.array_equal(got[k], want[g][k]), (N, cap, n_steps, g, k)
+            assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == next_draw

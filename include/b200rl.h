@@ -354,6 +354,34 @@ int b200rl_gather_batch_device_rng(const void* replay_buffers, const b200rl_repl
                                    float* oa_base, int ld_oa, float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base,
                                    uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * SAC update pieces (rl/algorithms/sac/operations_generic.h, CUDA forms rl/algorithms/sac/operations_cuda.h and
+ * nn/layers/sample_and_squash/operations_cuda.h). All matrices row-major with row pitches ld_*.
+ *
+ * Sample-and-squash policy head with external noise (nn/layers/sample_and_squash/operations_generic.h:149-195, 212-260):
+ *   input [B, 2A] = mean | log_std; log_std clamped to [-20, 2]; sample = mean + noise * exp(log_std); output = tanh(sample);
+ *   log_probs[b] = sum_a normal_log_prob(mean, log_std, sample) - log(1 - output^2 + 1e-6). pre_squashing [B, A] dense (needed by the
+ *   backward pass) and log_probs may be NULL.
+ * Backward (backward_full, :290-398): d_input [B, 2A] from d_output [B, A] plus the entropy term alpha / B * d log_prob, zero log_std
+ *   gradient outside the clamp; d_log_alpha_per_sample[b] = alpha * (entropy_b - target_entropy); their in-order sum / B is ADDED to
+ *   *log_alpha_gradient (NULL skips it). log_alpha: device scalar. */
+int b200rl_sample_and_squash_forward(const float* input, int ld_in, const float* noise, int ld_noise, int batch, int action_dim, float* pre_squashing,
+                                     float* output, int ld_out, float* log_probs, b200rl_stream_t stream);
+int b200rl_sample_and_squash_backward(const float* input, int ld_in, const float* noise, int ld_noise, const float* pre_squashing, const float* output,
+                                      int ld_out, const float* d_output, int ld_dout, const float* log_alpha, float target_entropy, int batch,
+                                      int action_dim, float* d_input, int ld_din, float* d_log_alpha_per_sample, float* log_alpha_gradient,
+                                      b200rl_stream_t stream);
+/* Critic target (target_action_values, rl/algorithms/sac/operations_generic.h:133-178): min of the two target critics' values at the next
+ * state, entropy bonus -alpha * next_log_prob (inside or outside the discounted term), gamma, termination mask, reward. */
+int b200rl_sac_target_action_values(const float* q1_next, int ld_q1, const float* q2_next, int ld_q2, const float* rewards, const uint8_t* terminated,
+                                    const float* next_log_probs, const float* log_alpha, float gamma, int ignore_termination, int entropy_bonus,
+                                    int entropy_bonus_next_step, float* target, int ld_target, int batch, b200rl_stream_t stream);
+/* Actor loss gradient w.r.t. the action (min_value_d_output, :341-376): columns [action_offset, action_offset + A) of the input gradient of
+ * whichever critic has the smaller value for that sample (critic 1 if q1 < q2). */
+int b200rl_sac_min_value_d_output(const float* q1, int ld_q1, const float* q2, int ld_q2, const float* d_critic_1_input, const float* d_critic_2_input,
+                                  int ld_d_input, int action_offset, int action_dim, float* d_actor_output, int ld_out, int batch,
+                                  b200rl_stream_t stream);
+
 /* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
  * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and
  * target-value columns. b200rl_shuffle_permutation_host replays those draws on the host engine (advanced in place, as the reference

@@ -93,6 +93,8 @@ class Oracle:
         _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
         L.orc_offpolicy_steps.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i32p, _u8p, _f32p,
                                           _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _f32p, _f32p]
+        L.orc_sample_and_squash_forward.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p]
+        L.orc_sample_and_squash_backward.argtypes = [_f32p, C.c_int, _f32p, _f32p, _f32p, _f32p, C.c_float, C.c_float, C.c_int, C.c_int, _f32p, C.c_int, _f32p, _f32p]
         L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
@@ -309,6 +311,20 @@ class Oracle:
                                      st["counters"], st["buf_obs"], st["buf_act"], st["buf_next_obs"])
         return st
 
+    def sample_and_squash(self, inp, noise, d_output, log_alpha, target_entropy=-1.0):
+        """Forward (external noise) and backward of the SAC policy head on inp [B, 2A]: dict(pre_squashing, output, log_probs, d_input,
+        d_log_alpha_per_sample, log_alpha_gradient)."""
+        B, A = noise.shape
+        inp, noise, d_output = (np.ascontiguousarray(x, np.float32) for x in (inp, noise, d_output))
+        out = dict(pre_squashing=np.empty((B, A), np.float32), output=np.empty((B, A), np.float32), log_probs=np.empty(B, np.float32),
+                   d_input=np.empty((B, 2 * A), np.float32), d_log_alpha_per_sample=np.empty(B, np.float32))
+        self.lib.orc_sample_and_squash_forward(inp, 2 * A, noise, B, A, out["pre_squashing"], out["output"], out["log_probs"])
+        grad = np.zeros(1, np.float32)
+        self.lib.orc_sample_and_squash_backward(inp, 2 * A, noise, out["pre_squashing"], out["output"], d_output, log_alpha, target_entropy, B, A,
+                                                out["d_input"], 2 * A, out["d_log_alpha_per_sample"], grad)
+        out["log_alpha_gradient"] = grad[0]
+        return out
+
     def polyak_update(self, source, target, polyak, square=False):
         """target = polyak * target + (1 - polyak) * source [squared], in place on a 2-D float32 array."""
         rows, cols = target.shape
@@ -403,6 +419,7 @@ class Reference:
         L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
         L.ref_offpolicy_steps.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _i32p, _u8p, _f32p, _f32p, _f32p, _f32p]
+        L.ref_sample_and_squash.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_polyak_update.argtypes = [_f32p, _f32p, C.c_float, C.c_int, C.c_int]
         L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
@@ -471,6 +488,22 @@ class Reference:
         if rc != 0:
             raise KeyError("no such off-policy runner case")
         return st
+
+    SAS_CASES = ((256, 1), (100, 8), (7, 3))                   # (batch, action dim) instantiated in ref_driver.cpp
+
+    def sample_and_squash(self, inp, noise, d_output, log_alpha):
+        """The reference's sample_and_squash LayerGradient: forward with external noise, then backward_full (same dict as Oracle.sample_and_squash)."""
+        B, A = noise.shape
+        inp, noise, d_output = (np.ascontiguousarray(x, np.float32) for x in (inp, noise, d_output))
+        out = dict(pre_squashing=np.empty((B, A), np.float32), output=np.empty((B, A), np.float32), log_probs=np.empty(B, np.float32),
+                   d_input=np.empty((B, 2 * A), np.float32), d_log_alpha_per_sample=np.empty(B, np.float32))
+        grad = np.zeros(1, np.float32)
+        rc = self.lib.ref_sample_and_squash(B, A, inp, noise, d_output, log_alpha, out["pre_squashing"], out["output"], out["log_probs"], out["d_input"],
+                                            out["d_log_alpha_per_sample"], grad)
+        if rc != 0:
+            raise KeyError("no such sample_and_squash case")
+        out["log_alpha_gradient"] = grad[0]
+        return out
 
     def polyak_update(self, source, target, polyak, square=False, n_updates=1):
         """The reference's utils::polyak::update[_squared] on [41, 29] matrices, n_updates times; returns the new target."""

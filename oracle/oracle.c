@@ -496,6 +496,83 @@ void orc_normal_functions(int n, const float* mean, const float* log_std, const 
     }
 }
 
+float orc_normal_d_log_prob_d_sample(float mean, float log_std, float value){      /* random/operations_generic.h:114-120 */
+    float diff = value - mean; float std = expf(log_std); float pre_square = diff / std;
+    return -pre_square / std;
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
+/* Sample-and-squash layer (the SAC policy head), nn/layers/sample_and_squash/operations_generic.h:            */
+/* forward_per_sample :212-260 with external noise: per action dimension log_std clamped to [-20, 2]           */
+/* (layer.h:27-36), sample = mean + noise * std, action = tanh(sample),                                         */
+/* log_prob += normal log_prob(mean, clamped log_std, sample) - log(1 - action^2 + 1e-6), accumulated in fp32.  */
+/* input [B, 2A] = mean | log_std. Outputs: pre_squashing, output [B, A], log_probabilities [B].               */
+/* ------------------------------------------------------------------------------------------------------ */
+#define ORC_SAS_LOG_STD_LOW (-20.0f)
+#define ORC_SAS_LOG_STD_HIGH (2.0f)
+#define ORC_SAS_EPS (1e-6f)
+static float orc_clampf(float x, float lo, float hi){ return x < lo ? lo : (x > hi ? hi : x); }
+void orc_sample_and_squash_forward(const float* input, int ld_in, const float* noise, int B, int A, float* pre_squashing, float* output, float* log_probs){
+    for(int b = 0; b < B; b++){
+        float log_prob = 0;
+        for(int a = 0; a < A; a++){
+            const float mean = input[(size_t)b * ld_in + a];
+            const float log_std_clipped = orc_clampf(input[(size_t)b * ld_in + A + a], ORC_SAS_LOG_STD_LOW, ORC_SAS_LOG_STD_HIGH);
+            const float std = expf(log_std_clipped);
+            const float sample = mean + noise[(size_t)b * A + a] * std;
+            const float squashed = tanhf(sample);
+            pre_squashing[(size_t)b * A + a] = sample;
+            output[(size_t)b * A + a] = squashed;
+            const float one_minus_square_plus_eps = (1 - squashed * squashed + ORC_SAS_EPS);
+            log_prob += orc_normal_log_prob(mean, log_std_clipped, sample) - logf(one_minus_square_plus_eps);
+        }
+        log_probs[b] = log_prob;
+    }
+}
+/* backward_full_per_sample :290-357 and backward_full :358-398: d_input [B, 2A] from d_output [B, A] (the critic's   */
+/* action gradient) plus the entropy term alpha / B * d log_prob; the log_std gradient is zero outside the clamp;        */
+/* per-sample d_log_alpha = alpha * (entropy - target_entropy), summed over the batch in order, divided by the number    */
+/* of resets (= B for sequence length 1; nn/layers/gru/... num_resets) and ADDED to *log_alpha_gradient.                 */
+void orc_sample_and_squash_backward(const float* input, int ld_in, const float* noise, const float* pre_squashing, const float* output, const float* d_output,
+                                    float log_alpha, float target_entropy, int B, int A, float* d_input, int ld_din, float* d_log_alpha_per_sample,
+                                    float* log_alpha_gradient){
+    const float alpha = expf(log_alpha);
+    for(int b = 0; b < B; b++){
+        float entropy = 0;
+        for(int a = 0; a < A; a++){
+            const float action = output[(size_t)b * A + a];
+            const float d_output_value = d_output[(size_t)b * A + a];
+            const float d_tanh_pre_activation = d_output_value * (1 - action * action);
+            float d_mu = d_tanh_pre_activation;
+            const float nz = noise[(size_t)b * A + a];
+            const float d_std = d_tanh_pre_activation * nz;
+            const float log_std_pre_clamp = input[(size_t)b * ld_in + A + a];
+            const float log_std_clamped = orc_clampf(log_std_pre_clamp, ORC_SAS_LOG_STD_LOW, ORC_SAS_LOG_STD_HIGH);
+            const float std = expf(log_std_clamped);
+            float d_log_std_clamped = std * d_std;
+            const float mu = input[(size_t)b * ld_in + a];
+            const float action_sample = pre_squashing[(size_t)b * A + a];
+            const float d_log_prob_d_mean = orc_normal_d_log_prob_d_mean(mu, log_std_clamped, action_sample);
+            const float d_log_prob_d_sample = orc_normal_d_log_prob_d_sample(mu, log_std_clamped, action_sample);
+            d_mu += alpha / B * (d_log_prob_d_mean + d_log_prob_d_sample + 2 * action);
+            const float d_log_prob_d_log_std = orc_normal_d_log_prob_d_log_std(mu, log_std_clamped, action_sample);
+            d_log_std_clamped += alpha / B * (d_log_prob_d_log_std + d_log_prob_d_sample * nz * std + 2 * action * nz * std);
+            const float d_log_std = log_std_pre_clamp < ORC_SAS_LOG_STD_LOW || log_std_pre_clamp > ORC_SAS_LOG_STD_HIGH ? 0 : d_log_std_clamped;
+            d_input[(size_t)b * ld_din + a] = d_mu;
+            d_input[(size_t)b * ld_din + A + a] = d_log_std;
+            const float one_minus_action_square_plus_eps = (1 - action * action + ORC_SAS_EPS);
+            const float action_log_prob = orc_normal_log_prob(mu, log_std_clamped, action_sample) - logf(one_minus_action_square_plus_eps);
+            entropy += -action_log_prob;
+        }
+        const float d_alpha = entropy - target_entropy;
+        d_log_alpha_per_sample[b] = alpha * d_alpha;
+    }
+    float d_log_alpha = 0;
+    for(int b = 0; b < B; b++) d_log_alpha += d_log_alpha_per_sample[b];
+    d_log_alpha /= B;
+    *log_alpha_gradient += d_log_alpha;
+}
+
 /* ------------------------------------------------------------------------------------------------------ */
 /* Off-policy runner step with per-environment replay buffers:                                               */
 /* rl/components/off_policy_runner/operations_generic.h:219-238 (step = prologue, interlude, epilogue),       */

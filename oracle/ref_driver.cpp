@@ -41,6 +41,7 @@
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
 #include <rl_tools/rl/components/off_policy_runner/operations_generic.h>
+#include <rl_tools/nn/layers/sample_and_squash/operations_generic.h>
 #include <rl_tools/rl/algorithms/ppo/ppo.h>
 #include <rl_tools/rl/algorithms/ppo/operations_generic.h>
 
@@ -568,6 +569,39 @@ static void gather_case(const float* actor_params, uint32_t seed, int n_steps, i
     rlt::free(device, actor); rlt::free(device, buffers);
 }
 
+// The SAC policy head on its own: nn::layers::sample_and_squash LayerGradient forward (external noise) and backward_full
+// (nn/layers/sample_and_squash/operations_generic.h:212-280, 290-398) on a [B, 2A] input. log_alpha_gradient_out = the layer's log_alpha gradient
+// after one backward from a zeroed gradient.
+template <TI B, TI A>
+static void sas_case(const float* input, const float* noise, const float* d_output, float log_alpha, float* pre_squashing, float* output, float* log_probs,
+                     float* d_input, float* d_log_alpha_per_sample, float* log_alpha_gradient_out){
+    using CONFIG = rlt::nn::layers::sample_and_squash::Configuration<TYPE_POLICY, TI>;
+    using CAPABILITY = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
+    using LAYER = rlt::nn::layers::sample_and_squash::Layer<CONFIG, CAPABILITY, rlt::tensor::Shape<TI, 1, B, 2 * A>>;
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    LAYER layer; typename LAYER::template Buffer<> buffer;
+    rlt::malloc(device, layer); rlt::malloc(device, buffer);
+    rlt::init_weights(device, layer, rng); rlt::zero_gradient(device, layer);
+    rlt::set(device, layer.log_alpha.parameters, log_alpha, 0);
+    rlt::Matrix<rlt::matrix::Specification<T, TI, B, 2 * A>> in, din;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, B, A>> dout;
+    rlt::malloc(device, in); rlt::malloc(device, din); rlt::malloc(device, dout);
+    for(TI b = 0; b < B; b++){
+        for(TI k = 0; k < 2 * A; k++) rlt::set(in, b, k, input[b * 2 * A + k]);
+        for(TI k = 0; k < A; k++){ rlt::set(dout, b, k, d_output[b * A + k]); rlt::set(buffer.noise, b, k, noise[b * A + k]); }
+    }
+    rlt::Mode<rlt::nn::layers::sample_and_squash::mode::ExternalNoise<rlt::mode::Default<>>> mode;
+    rlt::forward(device, layer, in, buffer, rng, mode);
+    rlt::backward_full(device, layer, in, dout, din, buffer, mode);
+    for(TI b = 0; b < B; b++){
+        for(TI k = 0; k < A; k++){ pre_squashing[b * A + k] = rlt::get(layer.pre_squashing, b, k); output[b * A + k] = rlt::get(layer.output, b, k); }
+        for(TI k = 0; k < 2 * A; k++) d_input[b * 2 * A + k] = rlt::get(din, b, k);
+        log_probs[b] = rlt::get(layer.log_probabilities, 0, b);
+        d_log_alpha_per_sample[b] = rlt::get(buffer.d_log_alpha, 0, b);
+    }
+    *log_alpha_gradient_out = rlt::get(device, layer.log_alpha.gradient, 0);
+    rlt::free(device, layer); rlt::free(device, buffer); rlt::free(device, in); rlt::free(device, din); rlt::free(device, dout);
+}
 extern "C" {
 
 int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards,
@@ -604,6 +638,15 @@ int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle,
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 1, true)
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 10, true)
 #undef PPO_CASE
+    return -1;
+}
+int ref_sample_and_squash(int B, int A, const float* input, const float* noise, const float* d_output, float log_alpha, float* pre_squashing, float* output,
+                          float* log_probs, float* d_input, float* d_log_alpha_per_sample, float* log_alpha_gradient_out){
+#define SAS_CASE(b, a) if(B == b && A == a){ sas_case<b, a>(input, noise, d_output, log_alpha, pre_squashing, output, log_probs, d_input, d_log_alpha_per_sample, log_alpha_gradient_out); return 0; }
+    SAS_CASE(256, 1)
+    SAS_CASE(100, 8)
+    SAS_CASE(7, 3)
+#undef SAS_CASE
     return -1;
 }
 // utils::polyak::update / update_squared (utils/polyak/operations_generic.h:10-40) on a [41, 29] matrix, n_updates times in a row

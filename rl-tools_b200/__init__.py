@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
@@ -44,7 +44,7 @@ class B200RLError(RuntimeError):
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile every CUDA source into libb200rl.so for sm_100a (nvcc cross-compiles without a GPU)."""
     srcs = [os.path.join(CSRC, s) for s in SOURCES]
-    deps = srcs + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")] + [os.path.join(ROOT, "include", "b200rl.h")]
+    deps = srcs + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")] + [os.path.join(ROOT, "include", "b200rl.h"), os.path.abspath(__file__)]
     if not force and os.path.exists(LIB_PATH) and all(os.path.getmtime(LIB_PATH) >= os.path.getmtime(d) for d in deps):
         return LIB_PATH
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
@@ -133,6 +133,10 @@ def lib():
         L.b200rl_permute_rows.argtypes = [vp, i, i, vp, C.c_uint64, vp, sz, vp]
         L.b200rl_pendulum_offpolicy_step.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp, vp, vp, C.POINTER(ReplayLayout), vp, vp, vp, vp]
         L.b200rl_collect_tables_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i), vp]
+        L.b200rl_sample_and_squash_forward.argtypes = [vp, i, vp, i, i, i, vp, vp, i, vp, vp]
+        L.b200rl_sample_and_squash_backward.argtypes = [vp, i, vp, i, vp, vp, i, vp, i, vp, f, i, i, vp, i, vp, vp, vp]
+        L.b200rl_sac_target_action_values.argtypes = [vp, i, vp, i, vp, vp, vp, vp, f, i, i, i, vp, i, i, vp]
+        L.b200rl_sac_min_value_d_output.argtypes = [vp, i, vp, i, vp, vp, i, i, i, vp, i, i, vp]
         L.b200rl_polyak_update.argtypes = [vp, i, vp, i, i, i, f, i, vp]
         L.b200rl_replay_counters.argtypes = [vp, C.POINTER(ReplayLayout), i, vp, vp, vp]
         L.b200rl_gather_draws_host.argtypes = [vp, i, i, vp, vp, i, vp, vp]
@@ -515,3 +519,48 @@ def polyak_update(source, target, polyak, square=False):
     check(lib().b200rl_polyak_update(_ptr(source), source.stride(0), _ptr(target), target.stride(0), rows, cols, float(polyak), int(square), _stream()),
           "b200rl_polyak_update")
     return target
+
+
+def sample_and_squash_forward(inp, noise, output=None, pre_squashing=None, log_probs=None):
+    """SAC policy head on inp [B, 2A] (CUDA tensors): returns (output [B, A], pre_squashing [B, A], log_probs [B])."""
+    import torch
+    B, A = noise.shape
+    output = torch.empty((B, A), device=inp.device) if output is None else output
+    pre_squashing = torch.empty((B, A), device=inp.device) if pre_squashing is None else pre_squashing
+    log_probs = torch.empty(B, device=inp.device) if log_probs is None else log_probs
+    check(lib().b200rl_sample_and_squash_forward(_ptr(inp), inp.stride(0), _ptr(noise), noise.stride(0), B, A, _ptr(pre_squashing), _ptr(output), output.stride(0),
+                                                 _ptr(log_probs), _stream()), "b200rl_sample_and_squash_forward")
+    return output, pre_squashing, log_probs
+
+
+def sample_and_squash_backward(inp, noise, pre_squashing, output, d_output, log_alpha, log_alpha_gradient=None, target_entropy=-1.0, d_input=None):
+    """Backward of the SAC policy head: returns (d_input [B, 2A], d_log_alpha_per_sample [B]); log_alpha_gradient (1-element tensor) is incremented."""
+    import torch
+    B, A = noise.shape
+    d_input = torch.empty((B, 2 * A), device=inp.device) if d_input is None else d_input
+    per_sample = torch.empty(B, device=inp.device)
+    check(lib().b200rl_sample_and_squash_backward(_ptr(inp), inp.stride(0), _ptr(noise), noise.stride(0), _ptr(pre_squashing), _ptr(output), output.stride(0),
+                                                  _ptr(d_output), d_output.stride(0), _ptr(log_alpha), target_entropy, B, A, _ptr(d_input), d_input.stride(0),
+                                                  _ptr(per_sample), _ptr(log_alpha_gradient), _stream()), "b200rl_sample_and_squash_backward")
+    return d_input, per_sample
+
+
+def sac_target_action_values(q1_next, q2_next, rewards, terminated, next_log_probs, log_alpha, gamma=0.99, ignore_termination=False, entropy_bonus=True,
+                             entropy_bonus_next_step=True, target=None):
+    import torch
+    B = rewards.shape[0]
+    target = torch.empty((B, 1), device=rewards.device) if target is None else target
+    check(lib().b200rl_sac_target_action_values(_ptr(q1_next), q1_next.stride(0), _ptr(q2_next), q2_next.stride(0), _ptr(rewards), _ptr(terminated), _ptr(next_log_probs),
+                                                _ptr(log_alpha), gamma, int(ignore_termination), int(entropy_bonus), int(entropy_bonus_next_step), _ptr(target),
+                                                target.stride(0), B, _stream()), "b200rl_sac_target_action_values")
+    return target
+
+
+def sac_min_value_d_output(q1, q2, d_critic_1_input, d_critic_2_input, action_dim, d_actor_output=None):
+    import torch
+    B, D = d_critic_1_input.shape
+    d_actor_output = torch.empty((B, action_dim), device=q1.device) if d_actor_output is None else d_actor_output
+    assert d_critic_2_input.stride(0) == d_critic_1_input.stride(0)
+    check(lib().b200rl_sac_min_value_d_output(_ptr(q1), q1.stride(0), _ptr(q2), q2.stride(0), _ptr(d_critic_1_input), _ptr(d_critic_2_input), d_critic_1_input.stride(0),
+                                              D - action_dim, action_dim, _ptr(d_actor_output), d_actor_output.stride(0), B, _stream()), "b200rl_sac_min_value_d_output")
+    return d_actor_output

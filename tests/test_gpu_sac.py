@@ -1,0 +1,91 @@
+"""GPU parity of the SAC update pieces through the C ABI: the sample-and-squash policy head against the golden outputs of the
+reference's layer (forward with external noise, backward_full), the critic target and the min-value gradient selection against
+float32 restatements of the reference's lines. Tolerance for floating point: 1e-5 relative + 1e-6 absolute."""
+import os
+
+import numpy as np
+import pytest
+
+import make_golden as mg
+from conftest import GOLDEN
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def close(got, want, rtol=1e-5, atol=1e-6, what=""):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    err = np.abs(got - want)
+    assert np.all(err <= atol + rtol * np.abs(want)), f"{what}: max err {err.max():.3e}"
+
+
+@pytest.mark.parametrize("case", range(len(oracle.Reference.SAS_CASES)))
+def test_sample_and_squash_vs_reference_golden(lib, torch, case):
+    fix = np.load(os.path.join(GOLDEN, "sample_and_squash.npz"))
+    inp, noise, d_output = mg.sas_inputs(case)
+    B, A = noise.shape
+    inp_d, noise_d = dev(torch, inp), dev(torch, noise)
+    output, pre, logp = lib.sample_and_squash_forward(inp_d, noise_d)
+    close(pre.cpu().numpy(), fix[f"pre_squashing_{case}"], what="pre_squashing")
+    close(output.cpu().numpy(), fix[f"output_{case}"], what="output")
+    close(logp.cpu().numpy(), fix[f"log_probs_{case}"], what="log_probs")
+    exact = np.mean(output.cpu().numpy() == fix[f"output_{case}"])
+    assert exact > 0.98, exact                     # double-evaluated tanh rounded once = the host libm's float result nearly everywhere
+    log_alpha = dev(torch, np.array([mg.SAS_LOG_ALPHA], np.float32))
+    grad = torch.full((1,), 0.25, device="cuda")                # the gradient accumulates
+    d_input, per_sample = lib.sample_and_squash_backward(inp_d, noise_d, pre, output, dev(torch, d_output), log_alpha, log_alpha_gradient=grad)
+    close(d_input.cpu().numpy(), fix[f"d_input_{case}"], what="d_input")
+    close(per_sample.cpu().numpy(), fix[f"d_log_alpha_per_sample_{case}"], what="d_log_alpha_per_sample")
+    close(grad.item() - 0.25, fix[f"log_alpha_gradient_{case}"], rtol=1e-5, atol=2e-6, what="log_alpha gradient")
+    # clamped rows: no log_std gradient
+    assert d_input.cpu().numpy()[0, A] == 0 and d_input.cpu().numpy()[1 % B, 2 * A - 1] == 0
+    # strided views: input inside a wider matrix, output into a column block
+    wide_in = torch.zeros((B, 2 * A + 5), device="cuda"); wide_in[:, 2:2 + 2 * A] = inp_d
+    wide_out = torch.full((B, A + 3), 9.0, device="cuda")
+    lib.sample_and_squash_forward(wide_in[:, 2:2 + 2 * A], noise_d, output=wide_out[:, 3:])
+    assert torch.equal(wide_out[:, 3:], output) and bool((wide_out[:, :3] == 9).all())
+
+
+@pytest.mark.parametrize("bonus,next_step,ignore", [(True, True, False), (True, False, False), (False, True, True), (True, True, True)])
+def test_target_action_values(lib, torch, bonus, next_step, ignore):
+    """rl/algorithms/sac/operations_generic.h:133-163 in float32."""
+    rs = np.random.RandomState(3)
+    B = 300
+    q1, q2 = rs.randn(B, 1).astype(np.float32) * 10, rs.randn(B, 1).astype(np.float32) * 10
+    rew, logp = rs.randn(B).astype(np.float32), rs.randn(B).astype(np.float32) * 3
+    term = (rs.rand(B) < 0.3).astype(np.uint8)
+    log_alpha, gamma = np.float32(-0.7), np.float32(0.99)
+    got = lib.sac_target_action_values(dev(torch, q1), dev(torch, q2), dev(torch, rew), dev(torch, term), dev(torch, logp), dev(torch, np.array([log_alpha])),
+                                       gamma=float(gamma), ignore_termination=ignore, entropy_bonus=bonus, entropy_bonus_next_step=next_step).cpu().numpy()[:, 0]
+    alpha = np.float32(np.exp(np.float64(log_alpha)))
+    m = np.minimum(q1[:, 0], q2[:, 0])
+    entropy_bonus = -alpha * logp
+    if bonus and next_step:
+        m = m + entropy_bonus
+    future = np.where(ignore | (term == 0), gamma * m, np.float32(0)).astype(np.float32)
+    want = rew + future
+    if bonus and not next_step:
+        want = want + entropy_bonus
+    assert np.array_equal(got, want.astype(np.float32))
+
+
+def test_min_value_d_output(lib, torch):
+    rs = np.random.RandomState(4)
+    B, O, A = 257, 5, 3
+    q1, q2 = rs.randn(B, 1).astype(np.float32), rs.randn(B, 1).astype(np.float32)
+    q2[:7] = q1[:7]                                            # ties take critic 2 (strict <)
+    d1, d2 = rs.randn(B, O + A).astype(np.float32), rs.randn(B, O + A).astype(np.float32)
+    got = lib.sac_min_value_d_output(dev(torch, q1), dev(torch, q2), dev(torch, d1), dev(torch, d2), A).cpu().numpy()
+    want = np.where(q1 < q2, d1[:, O:], d2[:, O:])
+    assert np.array_equal(got, want)

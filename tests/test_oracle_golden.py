@@ -255,3 +255,13 @@ def test_polyak_update_matches_reference(orc, case):
     for _ in range(n):
         orc.polyak_update(source, target, np.float32(polyak), square)
     assert np.array_equal(target, fix[f"target_{case}"])
+
+
+@pytest.mark.parametrize("case", range(len(oracle.Reference.SAS_CASES)))
+def test_sample_and_squash_matches_reference(orc, case):
+    """The SAC policy head: forward with external noise and backward_full of the reference's LayerGradient, every output bit for bit
+    (clamped log_std rows included)."""
+    fix = np.load(os.path.join(GOLDEN, "sample_and_squash.npz"))
+    got = orc.sample_and_squash(*mg.sas_inputs(case), mg.SAS_LOG_ALPHA)
+    for k, v in got.items():
+        assert np.array_equal(v, fix[f"{k}_{case}"]), k

@@ -325,6 +325,72 @@ class Oracle:
         out["log_alpha_gradient"] = grad[0]
         return out
 
+    def sac_target_action_values(self, q1, q2, rewards, terminated, next_log_probs, log_alpha, gamma=np.float32(0.99)):
+        """rl/algorithms/sac/operations_generic.h:133-163 with the default parameters (entropy bonus inside the discounted term, termination honoured)."""
+        alpha = np.float32(np.exp(np.float64(np.float32(log_alpha))))          # the host libm's expf is correctly rounded
+        m = np.minimum(q1, q2).astype(np.float32) + (-alpha * next_log_probs.astype(np.float32))
+        future = np.where(terminated == 0, np.float32(gamma) * m, np.float32(0)).astype(np.float32)
+        return (rewards.astype(np.float32) + future).astype(np.float32)
+
+    def sac_updates(self, hidden, actor_params, log_alpha, critic_params, target_params, oa_base, rewards, terminated, noise_critic, noise_actor,
+                    alpha=1e-3, beta_1=0.9, beta_2=0.999, eps=1e-7, eps_sqrt=1e-7, polyak=np.float32(1.0 - 0.005), target_entropy=-1.0):
+        """n x { train_critic(critic 0), train_critic(critic 1), update_critic_targets, train_actor } of rl/algorithms/sac/operations_generic.h
+        (:223-336, :486-522, :378-456), default parameters, sequence length 1, Pendulum shapes (observation 3, action 1), hidden width `hidden`.
+        oa_base [U, 2, B, 4], rewards / terminated [U, B], noise_critic [U, 2, B, 1], noise_actor [U, B, 1]; critic_params / target_params [2, n].
+        Returns dict(actor=(params, grads, m), log_alpha=(value, grad, m), critics=[(params, grads, m)] * 2, targets=[params] * 2, target_values)."""
+        U, _, B, _ = oa_base.shape
+        actor_shape = MlpShape.make(3, [hidden, hidden, 2], ["relu", "relu", "identity"])
+        critic_shape = MlpShape.make(4, [hidden, hidden, 1], ["relu", "relu", "identity"])
+        ap = actor_params.copy(); am, av, ag = np.zeros_like(ap), np.zeros_like(ap), np.zeros_like(ap)
+        la = np.array([log_alpha], np.float32); lm, lv, lg = np.zeros(1, np.float32), np.zeros(1, np.float32), np.zeros(1, np.float32)
+        cp = [critic_params[c].copy() for c in range(2)]
+        cm, cv, cg = ([np.zeros_like(cp[0]) for _ in range(2)] for _ in range(3))
+        tp = [target_params[c].copy() for c in range(2)]
+        ages = dict(actor=1, alpha=1, c0=1, c1=1)
+        adam = lambda p, g, m, v, key: self._adam(p, g, m, v, ages, key, alpha, beta_1, beta_2, eps, eps_sqrt)
+        target_values = None
+        for u in range(U):
+            obs, nobs = np.ascontiguousarray(oa_base[u, 0, :, :3]), np.ascontiguousarray(oa_base[u, 1, :, :3])
+            oa = np.ascontiguousarray(oa_base[u, 0])
+            for c in range(2):
+                head_in = self.mlp_evaluate(actor_shape, ap, nobs)
+                head = self.sample_and_squash(head_in, noise_critic[u, c], np.zeros((B, 1), np.float32), la[0], target_entropy)
+                nin = np.ascontiguousarray(np.concatenate([nobs, head["output"]], axis=1))
+                q1, q2 = self.mlp_evaluate(critic_shape, tp[0], nin)[:, 0], self.mlp_evaluate(critic_shape, tp[1], nin)[:, 0]
+                target_values = self.sac_target_action_values(q1, q2, rewards[u], terminated[u], head["log_probs"], la[0])
+                pre, out = self.mlp_forward(critic_shape, cp[c], oa)
+                values = np.ascontiguousarray(out[-B:].reshape(B, 1))
+                d_values = self.mse_gradient(values, np.ascontiguousarray(target_values.reshape(B, 1)), 0.5)
+                cg[c], _ = self.mlp_backward(critic_shape, cp[c], np.zeros_like(cp[c]), oa, pre, out, d_values)
+                cp[c], cm[c], cv[c] = adam(cp[c], cg[c], cm[c], cv[c], f"c{c}")
+            for c in range(2):                                 # update_critic_targets, layer by layer = element-wise over the flat arena
+                t2 = tp[c].reshape(1, -1).copy()
+                self.polyak_update(cp[c].reshape(1, -1), t2, polyak)
+                tp[c] = t2.reshape(-1)
+            pre_a, out_a = self.mlp_forward(actor_shape, ap, obs)
+            head_in = np.ascontiguousarray(out_a[-2 * B:].reshape(B, 2))
+            inp = obs
+            fwd = self.sample_and_squash(head_in, noise_actor[u], np.zeros((B, 1), np.float32), la[0], target_entropy)
+            cin = np.ascontiguousarray(np.concatenate([inp, fwd["output"]], axis=1))
+            d_out = np.full((B, 1), np.float32(-1) / np.float32(B), np.float32)
+            qs, d_ins = [], []
+            for c in range(2):
+                pre, out = self.mlp_forward(critic_shape, cp[c], cin)
+                qs.append(out[-B:].copy())
+                _, d_in = self.mlp_backward(critic_shape, cp[c], np.zeros_like(cp[c]), cin, pre, out, d_out, want_d_input=True)
+                d_ins.append(d_in)
+            d_action = np.where((qs[0] < qs[1])[:, None], d_ins[0][:, 3:], d_ins[1][:, 3:]).astype(np.float32)
+            bwd = self.sample_and_squash(head_in, noise_actor[u], np.ascontiguousarray(d_action), la[0], target_entropy)
+            ag, _ = self.mlp_backward(actor_shape, ap, np.zeros_like(ap), obs, pre_a, out_a, np.ascontiguousarray(bwd["d_input"]))
+            lg = np.array([bwd["log_alpha_gradient"]], np.float32)
+            ap, am, av = adam(ap, ag, am, av, "actor")
+            la, lm, lv = adam(la, lg, lm, lv, "alpha")
+        return dict(actor=(ap, ag, am), log_alpha=(la[0], lg[0], lm[0]), critics=[(cp[c], cg[c], cm[c]) for c in range(2)], targets=tp, target_values=target_values)
+
+    def _adam(self, p, g, m, v, ages, key, alpha, beta_1, beta_2, eps, eps_sqrt):
+        c1, c2, ages[key] = self.adam_bias_correction(beta_1, beta_2, ages[key])
+        return self.adam_update(p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
+
     def polyak_update(self, source, target, polyak, square=False):
         """target = polyak * target + (1 - polyak) * source [squared], in place on a 2-D float32 array."""
         rows, cols = target.shape
@@ -419,6 +485,7 @@ class Reference:
         L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
         L.ref_offpolicy_steps.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _i32p, _u8p, _f32p, _f32p, _f32p, _f32p]
+        L.ref_sac_updates.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _u8p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_sample_and_squash.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_polyak_update.argtypes = [_f32p, _f32p, C.c_float, C.c_int, C.c_int]
         L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
@@ -488,6 +555,22 @@ class Reference:
         if rc != 0:
             raise KeyError("no such off-policy runner case")
         return st
+
+    SAC_CASES = ((256, 64), (100, 32))                          # (batch, hidden width) instantiated in ref_driver.cpp
+
+    def sac_updates(self, batch, hidden, actor_params, log_alpha, critic_params, target_params, oa_base, rewards, terminated, noise_critic, noise_actor):
+        """The reference's train_critic x 2, update_critic_targets, train_actor per update (same dict as Oracle.sac_updates)."""
+        U = oa_base.shape[0]
+        na, nc = actor_params.size, critic_params.shape[1]
+        f = lambda a: np.ascontiguousarray(a, np.float32)
+        actor_out, la_out = np.empty((3, na), np.float32), np.empty(3, np.float32)
+        critic_out, target_out, tv = np.empty((2, 3, nc), np.float32), np.empty((2, nc), np.float32), np.empty(batch, np.float32)
+        rc = self.lib.ref_sac_updates(batch, hidden, U, f(actor_params), log_alpha, f(critic_params), f(target_params), f(oa_base), f(rewards),
+                                      np.ascontiguousarray(terminated, np.uint8), f(noise_critic), f(noise_actor), actor_out, la_out, critic_out, target_out, tv)
+        if rc != 0:
+            raise KeyError("no such SAC case")
+        return dict(actor=tuple(actor_out), log_alpha=tuple(la_out), critics=[tuple(critic_out[c]) for c in range(2)], targets=[target_out[c] for c in range(2)],
+                    target_values=tv)
 
     SAS_CASES = ((256, 1), (100, 8), (7, 3))                   # (batch, action dim) instantiated in ref_driver.cpp
 

@@ -34,6 +34,7 @@
 #endif
 #include <rl_tools/nn/layers/dense/operations_cpu.h>
 #include <rl_tools/nn/loss_functions/mse/operations_generic.h>
+#include <rl_tools/nn/layers/sample_and_squash/operations_generic.h>     // before the model headers that recurse into it
 #include <rl_tools/nn_models/mlp/operations_generic.h>
 #include <rl_tools/nn_models/mlp_unconditional_stddev/operations_generic.h>
 #include <rl_tools/nn_models/sequential/operations_generic.h>
@@ -41,7 +42,7 @@
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
 #include <rl_tools/rl/components/off_policy_runner/operations_generic.h>
-#include <rl_tools/nn/layers/sample_and_squash/operations_generic.h>
+#include <rl_tools/rl/algorithms/sac/operations_generic.h>
 #include <rl_tools/rl/algorithms/ppo/ppo.h>
 #include <rl_tools/rl/algorithms/ppo/operations_generic.h>
 
@@ -602,6 +603,105 @@ static void sas_case(const float* input, const float* noise, const float* d_outp
     *log_alpha_gradient_out = rlt::get(device, layer.log_alpha.gradient, 0);
     rlt::free(device, layer); rlt::free(device, buffer); rlt::free(device, in); rlt::free(device, din); rlt::free(device, dout);
 }
+// SAC update through the reference's own train_critic / update_critic_targets / train_actor (rl/algorithms/sac/operations_generic.h:223-336,
+// 486-522, 378-456) with the default SAC parameters (gamma 0.99, entropy bonus on the next step, masking of non-terminal steps, target entropy
+// -ACTION_DIM, Polyak 0.995) on hand-filled SequentialBatch tensors of sequence length 1: per update critic 0, critic 1 (same batch, own noise),
+// target update, actor. Networks: actor sequential<mlp 3 -> H -> H -> 2, sample_and_squash>, critics sequential<mlp 4 -> H -> H -> 1>, ReLU.
+// Parameter arrays are W1 b1 W2 b2 W3 b3 per network; outputs are the same arrays after the updates plus gradients / first moments.
+template <TI T_BATCH>
+struct SacCaseParameters: rlt::rl::algorithms::sac::DefaultParameters<TYPE_POLICY, TI, 1>{
+    static constexpr TI ACTOR_BATCH_SIZE = T_BATCH;
+    static constexpr TI CRITIC_BATCH_SIZE = T_BATCH;
+};
+template <typename SAC_PARAMETERS>
+struct SacCaseHeadParameters{
+    static constexpr T LOG_STD_LOWER_BOUND = SAC_PARAMETERS::LOG_STD_LOWER_BOUND, LOG_STD_UPPER_BOUND = SAC_PARAMETERS::LOG_STD_UPPER_BOUND;
+    static constexpr T LOG_PROBABILITY_EPSILON = SAC_PARAMETERS::LOG_PROBABILITY_EPSILON, ALPHA = SAC_PARAMETERS::ALPHA, TARGET_ENTROPY = SAC_PARAMETERS::TARGET_ENTROPY;
+    static constexpr bool ADAPTIVE_ALPHA = SAC_PARAMETERS::ADAPTIVE_ALPHA, UPDATE_ALPHA_WITH_ACTOR = false;
+};
+template <typename LAYER>
+static void store_parameters_only(DEVICE& device, LAYER& layer, float*& p){        // for networks without gradient members
+    for(TI o = 0; o < LAYER::OUTPUT_DIM; o++) for(TI i = 0; i < LAYER::INPUT_DIM; i++) *p++ = rlt::get(device, layer.weights.parameters, o, i);
+    for(TI o = 0; o < LAYER::OUTPUT_DIM; o++) *p++ = rlt::get(device, layer.biases.parameters, o);
+}
+template <TI BATCH, TI HIDDEN>
+static void sac_case(int n_updates, const float* actor_params, float log_alpha, const float* critic_params /*[2]*/, const float* target_params /*[2]*/,
+                     const float* oa_base /*[U,2,B,4]*/, const float* rewards /*[U,B]*/, const uint8_t* terminated /*[U,B]*/, const float* noise_critic /*[U,2,B,1]*/,
+                     const float* noise_actor /*[U,B,1]*/, float* actor_out /*[3][n]*/, float* log_alpha_out /*[3]*/, float* critic_out /*[2][3][n]*/, float* target_out /*[2][n]*/,
+                     float* target_values_out /*[B] of the last critic update*/){
+    using SAC_PARAMETERS = SacCaseParameters<BATCH>;
+    using ACTOR_MLP = rlt::nn_models::mlp::BindConfiguration<rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 2, 3, HIDDEN, act::RELU, act::IDENTITY>>;
+    using SAS_PARAMETERS = SacCaseHeadParameters<SAC_PARAMETERS>;
+    using SAS = rlt::nn::layers::sample_and_squash::BindConfiguration<rlt::nn::layers::sample_and_squash::Configuration<TYPE_POLICY, TI, SAS_PARAMETERS>>;
+    using CAP_GRADIENT = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
+    using ACTOR = rlt::nn_models::sequential::Build<CAP_GRADIENT, rlt::nn_models::sequential::Module<ACTOR_MLP, rlt::nn_models::sequential::Module<SAS>>, rlt::tensor::Shape<TI, 1, BATCH, 3>>;
+    using CRITIC_MLP = rlt::nn_models::mlp::BindConfiguration<rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, HIDDEN, act::RELU, act::IDENTITY>>;
+    using CRITIC = rlt::nn_models::sequential::Build<CAP_GRADIENT, rlt::nn_models::sequential::Module<CRITIC_MLP>, rlt::tensor::Shape<TI, 1, BATCH, 4>>;
+    using CRITIC_TARGET = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<CRITIC_MLP>, rlt::tensor::Shape<TI, 1, BATCH, 4>>;
+    using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
+    using AC_SPEC = rlt::rl::algorithms::sac::Specification<TYPE_POLICY, TI, PENDULUM, ACTOR, CRITIC, CRITIC_TARGET, rlt::nn::parameters::Adam, OPTIMIZER, OPTIMIZER, OPTIMIZER, SAC_PARAMETERS, false>;
+    using ACTOR_CRITIC = rlt::rl::algorithms::sac::ActorCritic<AC_SPEC>;
+    using EVAL_ACTOR = typename ACTOR::template CHANGE_BATCH_SIZE<TI, 4>;
+    using RUNNER_SPEC = rlt::rl::components::off_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, rlt::utils::Tuple<TI, EVAL_ACTOR>, OffPolicyParameters<4, 16, 200>>;
+    using BATCH_TYPE = rlt::rl::components::off_policy_runner::SequentialBatch<rlt::rl::components::off_policy_runner::SequentialBatchSpecification<RUNNER_SPEC, 1, BATCH>>;
+    using CRITIC_TRAINING_BUFFERS = rlt::rl::algorithms::sac::CriticTrainingBuffers<rlt::rl::algorithms::sac::CriticTrainingBuffersSpecification<AC_SPEC, true>>;
+    using ACTOR_TRAINING_BUFFERS = rlt::rl::algorithms::sac::ActorTrainingBuffers<rlt::rl::algorithms::sac::ActorTrainingBuffersSpecification<AC_SPEC, true>>;
+    constexpr TI N_ACTOR = 3 * HIDDEN + HIDDEN + HIDDEN * HIDDEN + HIDDEN + HIDDEN * 2 + 2, N_CRITIC = 4 * HIDDEN + HIDDEN + HIDDEN * HIDDEN + HIDDEN + HIDDEN + 1;
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    auto* ac = new ACTOR_CRITIC();
+    BATCH_TYPE batch; CRITIC_TRAINING_BUFFERS ctb; ACTOR_TRAINING_BUFFERS atb;
+    typename ACTOR::template Buffer<> actor_buffers, actor_target_buffers; typename CRITIC::template Buffer<> critic_buffers; typename CRITIC_TARGET::template Buffer<> critic_target_buffers;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, BATCH, 1>> action_noise_critic, action_noise_actor;
+    rlt::malloc(device, *ac); rlt::malloc(device, batch); rlt::malloc(device, ctb); rlt::malloc(device, atb);
+    rlt::malloc(device, actor_buffers); rlt::malloc(device, actor_target_buffers); rlt::malloc(device, critic_buffers); rlt::malloc(device, critic_target_buffers);
+    rlt::malloc(device, action_noise_critic); rlt::malloc(device, action_noise_actor);
+    rlt::init(device, *ac, rng);
+    { const float* p = actor_params; auto& m = ac->actor.content;
+      load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
+    rlt::set(device, rlt::get_last_layer(ac->actor).log_alpha.parameters, log_alpha, 0);
+    for(int c = 0; c < 2; c++){
+        { const float* p = critic_params + c * N_CRITIC; auto& m = ac->critics[c].content;
+          load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
+        { const float* p = target_params + c * N_CRITIC; auto& m = ac->critics_target[c].content;
+          load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
+    }
+    for(int u = 0; u < n_updates; u++){
+        for(TI q = 0; q < 2; q++) for(TI b = 0; b < BATCH; b++){
+            for(TI k = 0; k < 4; k++) rlt::set(device, batch.observations_actions_base, oa_base[(((size_t)u * 2 + q) * BATCH + b) * 4 + k], q, b, k);
+            rlt::set(device, batch.next_reset_base, true, q, b, 0);
+            rlt::set(device, batch.next_final_step_mask_base, q == 1, q, b, 0);
+        }
+        for(TI b = 0; b < BATCH; b++){
+            rlt::set(device, batch.rewards, rewards[(size_t)u * BATCH + b], 0, b, 0);
+            rlt::set(device, batch.terminated, terminated[(size_t)u * BATCH + b] != 0, 0, b, 0);
+            rlt::set(device, batch.reset, true, 0, b, 0);
+            rlt::set(device, batch.final_step_mask, true, 0, b, 0);
+        }
+        for(int c = 0; c < 2; c++){
+            for(TI b = 0; b < BATCH; b++) rlt::set(action_noise_critic, b, 0, noise_critic[((size_t)u * 2 + c) * BATCH + b]);
+            rlt::train_critic(device, *ac, ac->critics[c], batch, ac->critic_optimizers[c], actor_target_buffers, critic_buffers, critic_target_buffers, ctb, action_noise_critic, rng);
+        }
+        if(target_values_out) for(TI b = 0; b < BATCH; b++) target_values_out[b] = rlt::get(device, ctb.target_action_value, 0, b, 0);
+        rlt::update_critic_targets(device, *ac);
+        for(TI b = 0; b < BATCH; b++) rlt::set(action_noise_actor, b, 0, noise_actor[(size_t)u * BATCH + b]);
+        rlt::train_actor(device, *ac, batch, ac->actor_optimizer, actor_buffers, critic_buffers, atb, action_noise_actor, rng);
+    }
+    auto dump = [&](auto& m, float*& out, Which what){ store_layer(device, m.input_layer, out, what); store_layer(device, m.hidden_layers[0], out, what); store_layer(device, m.output_layer, out, what); };
+    { float* o = actor_out; dump(ac->actor.content, o, PARAMS); dump(ac->actor.content, o, GRADS); dump(ac->actor.content, o, MOM1); }
+    auto& la = rlt::get_last_layer(ac->actor).log_alpha;
+    log_alpha_out[0] = rlt::get(device, la.parameters, 0); log_alpha_out[1] = rlt::get(device, la.gradient, 0); log_alpha_out[2] = rlt::get(device, la.gradient_first_order_moment, 0);
+    for(int c = 0; c < 2; c++){
+        float* o = critic_out + (size_t)c * 3 * N_CRITIC;
+        dump(ac->critics[c].content, o, PARAMS); dump(ac->critics[c].content, o, GRADS); dump(ac->critics[c].content, o, MOM1);
+        float* t = target_out + (size_t)c * N_CRITIC;
+        auto& tm = ac->critics_target[c].content;
+        store_parameters_only(device, tm.input_layer, t); store_parameters_only(device, tm.hidden_layers[0], t); store_parameters_only(device, tm.output_layer, t);
+    }
+    rlt::free(device, *ac); delete ac; rlt::free(device, batch); rlt::free(device, ctb); rlt::free(device, atb);
+    rlt::free(device, actor_buffers); rlt::free(device, actor_target_buffers); rlt::free(device, critic_buffers); rlt::free(device, critic_target_buffers);
+    rlt::free(device, action_noise_critic); rlt::free(device, action_noise_actor);
+}
+
 extern "C" {
 
 int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards,
@@ -638,6 +738,15 @@ int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle,
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 1, true)
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 10, true)
 #undef PPO_CASE
+    return -1;
+}
+int ref_sac_updates(int batch, int hidden, int n_updates, const float* actor_params, float log_alpha, const float* critic_params, const float* target_params,
+                    const float* oa_base, const float* rewards, const uint8_t* terminated, const float* noise_critic, const float* noise_actor, float* actor_out,
+                    float* log_alpha_out, float* critic_out, float* target_out, float* target_values_out){
+#define SAC_CASE(b, h) if(batch == b && hidden == h){ sac_case<b, h>(n_updates, actor_params, log_alpha, critic_params, target_params, oa_base, rewards, terminated, noise_critic, noise_actor, actor_out, log_alpha_out, critic_out, target_out, target_values_out); return 0; }
+    SAC_CASE(256, 64)
+    SAC_CASE(100, 32)
+#undef SAC_CASE
     return -1;
 }
 int ref_sample_and_squash(int B, int A, const float* input, const float* noise, const float* d_output, float log_alpha, float* pre_squashing, float* output,

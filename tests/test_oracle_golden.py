@@ -265,3 +265,15 @@ def test_sample_and_squash_matches_reference(orc, case):
     got = orc.sample_and_squash(*mg.sas_inputs(case), mg.SAS_LOG_ALPHA)
     for k, v in got.items():
         assert np.array_equal(v, fix[f"{k}_{case}"]), k
+
+
+@pytest.mark.parametrize("case", range(len(oracle.Reference.SAC_CASES)))
+@pytest.mark.parametrize("updates", [1, mg.SAC_UPDATES])
+def test_sac_updates_match_reference(orc, case, updates):
+    """train_critic (both critics), update_critic_targets, train_actor incl. the log_alpha step: parameters, gradients, first moments, target
+    networks and the last critic target values, bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "sac.npz"))
+    B, H = oracle.Reference.SAC_CASES[case]
+    got = mg.flatten_sac(orc.sac_updates(H, *mg.sac_inputs(case, updates)))
+    for k, v in got.items():
+        assert np.array_equal(v, fix[f"{k}_{case}_u{updates}"]), k

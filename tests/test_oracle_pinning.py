@@ -143,3 +143,25 @@ def test_gather_batch_live(orc, ref_strict):
                 for k in want[g]:
                     assert np.array_equal(got[k], want[g][k]), (N, cap, n_steps, g, k)
             assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == next_draw
+
+
+def test_sac_updates_live(orc, ref_strict):
+    import make_golden as mg
+    for case, (B, H) in enumerate(oracle.Reference.SAC_CASES):
+        args = list(mg.sac_inputs(case, 2))
+        args[1] = np.float32(0.3)                                      # another log_alpha than the fixture's
+        want, got = mg.flatten_sac(ref_strict.sac_updates(B, H, *args)), mg.flatten_sac(orc.sac_updates(H, *args))
+        for k in want:
+            assert np.array_equal(want[k], got[k]), (case, k)
+
+
+def test_sample_and_squash_live(orc, ref_strict):
+    rs = np.random.RandomState(8)
+    for (B, A) in oracle.Reference.SAS_CASES:
+        inp = (rs.randn(B, 2 * A) * 2).astype(np.float32)
+        inp[0, A], inp[B - 1, 2 * A - 1] = 2.5, -30
+        noise, dout = rs.randn(B, A).astype(np.float32), (rs.randn(B, A) / B).astype(np.float32)
+        for log_alpha in (0.0, -2.0):
+            want, got = ref_strict.sample_and_squash(inp, noise, dout, log_alpha), orc.sample_and_squash(inp, noise, dout, log_alpha)
+            for k in want:
+                assert np.array_equal(want[k], got[k]), (B, A, log_alpha, k)

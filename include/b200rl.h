@@ -132,7 +132,8 @@ int b200rl_mlp_evaluate(const b200rl_mlp_shape* shape, const float* params, cons
 int b200rl_mlp_forward(const b200rl_mlp_shape* shape, const float* params, const float* x, int ldx, float* pre, float* out,
                        int batch, b200rl_stream_t stream);
 
-/* backward through all layers; d_out [batch, O_last] is clobbered; grads accumulate; d_input may be NULL
+/* backward through all layers; d_out [batch, O_last] is clobbered; grads accumulate (grads == NULL: only the input gradient is
+ * propagated, backward_input of nn_models/mlp/operations_generic.h:130-150, d_input required); d_input may be NULL
  * (input layer then gets the weights-only backward, nn_models/mlp/operations_generic.h:180-204; non-NULL gives
  * backward_full :152-179). tick/tock: two [batch, max(dim)] buffers. scratch as for b200rl_dense_backward with the
  * largest layer. */

@@ -307,8 +307,9 @@ class Mlp:
               "b200rl_mlp_forward")
         return self.output()
 
-    def backward(self, x, d_out, d_input=None):
-        check(lib().b200rl_mlp_backward(C.byref(self.shape), _ptr(self.params), _ptr(self.grads), _ptr(x), x.stride(0), _ptr(self.pre), _ptr(self.out),
+    def backward(self, x, d_out, d_input=None, accumulate_gradients=True):
+        """accumulate_gradients=False is the reference's backward_input: only d_input is computed, the parameter gradients stay untouched."""
+        check(lib().b200rl_mlp_backward(C.byref(self.shape), _ptr(self.params), _ptr(self.grads) if accumulate_gradients else None, _ptr(x), x.stride(0), _ptr(self.pre), _ptr(self.out),
                                         _ptr(d_out), _ptr(d_input), _ptr(self.tick), _ptr(self.tock), self.batch, _ptr(self.scratch), self.scratch_bytes,
                                         _stream()), "b200rl_mlp_backward")
 

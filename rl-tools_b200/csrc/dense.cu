@@ -533,7 +533,8 @@ size_t b200rl_mlp_backward_scratch_bytes(const b200rl_mlp_shape* sh, int batch){
 int b200rl_mlp_backward(const b200rl_mlp_shape* sh, const float* params, float* grads, const float* x, int ldx, const float* pre,
                         const float* out, float* d_out, float* d_input, float* tick, float* tock, int batch,
                         void* scratch, size_t scratch_bytes, b200rl_stream_t stream){
-    if(!valid_shape(sh) || !params || !grads || !x || !pre || !out || !d_out || batch < 0 || ldx < sh->input_dim) return B200RL_ERR_INVALID_ARGUMENT;
+    if(!valid_shape(sh) || !params || !x || !pre || !out || !d_out || batch < 0 || ldx < sh->input_dim) return B200RL_ERR_INVALID_ARGUMENT;
+    if(!grads && !d_input) return B200RL_ERR_INVALID_ARGUMENT;          // grads == NULL: backward_input (nn_models/mlp/operations_generic.h:130-150)
     int L = sh->n_layers;
     if(L > 1 && (!tick || (L > 2 && !tock))) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
@@ -546,8 +547,8 @@ int b200rl_mlp_backward(const b200rl_mlp_shape* sh, const float* params, float* 
         const float* in = l == 0 ? x : out + aoff[l - 1];
         int ldin = l == 0 ? ldx : I;
         float* d_in = l == 0 ? d_input : ((l % 2 == 0) ? tick : tock);
-        float* dW = grads + poff[l];
-        int rc = dense_backward_impl(params + poff[l], in, ldin, pre + aoff[l], O, d_cur, ldd, dW, dW + (size_t)O * I, d_in, I, batch, I, O, sh->acts[l],
+        float* dW = grads ? grads + poff[l] : nullptr;
+        int rc = dense_backward_impl(params + poff[l], in, ldin, pre + aoff[l], O, d_cur, ldd, dW, dW ? dW + (size_t)O * I : nullptr, d_in, I, batch, I, O, sh->acts[l],
                                      scratch, scratch_bytes, (cudaStream_t)stream);
         if(rc) return rc;
         d_cur = d_in; ldd = I;

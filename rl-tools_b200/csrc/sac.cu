@@ -1,8 +1,8 @@
 // SAC update pieces that are not dense layers: the sample-and-squash policy head (forward with external noise, backward with the
 // entropy term and the log_alpha gradient), the critic target and the actor's choice between the two critics' input gradients.
 // All are per-sample element-wise passes over a minibatch (a few hundred rows): latency-bound launches, one thread per sample.
-// The transcendental functions are evaluated in double and rounded once, which reproduces the host libm's float results the
-// reference computes with (expf, tanhf, logf: correctly rounded in all but rare cases).
+// The transcendental functions are evaluated in double and rounded once: the host libm's expf and logf, which the reference computes
+// with, are correctly rounded, its tanhf is within one ulp of that.
 #include "common.cuh"
 
 namespace b200rl {

@@ -13,8 +13,8 @@ Prints ONE JSON line: device-timed `value` (inputs resident in HBM, CUDA events 
 against the measured peak, `cpu_baseline` (the reference's own CPU path timed on this box's cores), `clocks`.
 `--impl reference` times only the reference CPU implementation, on the same metric and config.
 
-`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval}` print secondary lines in the same JSON form (sharded MLP training,
-on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference); the default workload is the headline rollout.
+`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update}` print secondary lines in the same JSON form (sharded MLP training,
+on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference, the SAC training step); the default workload is the headline rollout.
 """
 import argparse
 import json
@@ -489,6 +489,109 @@ def run_critic_train(args):
                       "cpu_baseline": cpu, "gpu_launches": reps * STEPS * 15}))
 
 
+def run_sac_update(args):
+    """Secondary line: one SAC training step of the off-policy loop on the Pendulum shapes with the critic of the off-policy configuration --
+    gather_batch (indices drawn in the kernel) from 64 replay buffers of 4096 transitions, train_critic x 2, update_critic_targets, train_actor
+    incl. the log_alpha step; actor 3 -> 256 -> 256 -> 2 + sample-and-squash head, critics 4 -> 256 -> 256 -> 1, batch 256. Eager launches and
+    replayed as a CUDA graph of the same C-ABI calls. value = sampled transitions per second (graph replay). Single GPU."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from rl_tools_b200 import sac
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, H, N, CAP, UPDATES = 256, 256, 64, 4096, 100
+    rs = np.random.RandomState(5)
+    agent = sac.ActorCritic(3, 1, H, B)
+    for net in [agent.actor] + agent.critics:
+        off, fan_in = 0, net.shape.input_dim
+        for l in range(3):
+            d = net.shape.dims[l]
+            n = d * fan_in + d
+            net.params[off:off + n] = torch.from_numpy(((rs.rand(n) * 2 - 1) / fan_in ** 0.5).astype(np.float32)).to(dev)
+            off += n; fan_in = d
+    agent.copy_critics_to_targets()
+    L = pkg.ReplayLayout.packed(CAP)
+    raw = np.zeros((N, L.env_stride), np.uint8)
+    theta, theta_dot = rs.uniform(-np.pi, np.pi, (N, CAP)), rs.uniform(-8, 8, (N, CAP))
+    rows = np.stack([np.cos(theta), np.sin(theta), theta_dot, rs.uniform(-1, 1, (N, CAP)), rs.uniform(-16, 0, (N, CAP)), np.cos(theta + 0.1), np.sin(theta + 0.1), theta_dot,
+                     np.zeros((N, CAP)), (rs.rand(N, CAP) < 0.005)], -1).astype(np.float32)
+    raw[:, :40 * CAP] = rows.reshape(N, -1).view(np.uint8)
+    raw[:, 44 * CAP + 8] = 1                                     # full buffers, position 0
+    replay = torch.from_numpy(raw.reshape(-1)).to(dev)
+    batch = pkg.new_batch(B)
+    noise = torch.from_numpy(rs.standard_normal((64, 3, B, 1)).astype(np.float32)).to(dev)      # a resident pool, like the reference's randn() into its noise buffers
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    calls = [0]
+
+    def update():
+        k = calls[0] % 64
+        pkg.gather_batch(replay, L, N, batch, seed=11, call_index=calls[0], error_flag=flag)
+        agent.update(batch, noise[k, 0], noise[k, 1], noise[k, 2])
+        calls[0] += 1
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(20):
+            update()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(10):
+            update()
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = min(args.steps, 10)
+
+    def timed(fn):
+        fn(); torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+    ms_eager = timed(lambda: [update() for _ in range(UPDATES)])
+    ms_graph = timed(lambda: [graph.replay() for _ in range(UPDATES // 10)])
+    # contractions per update: critic updates 2 x (actor fwd + 2 target fwd + critic fwd + dW + dX), actor update (actor fwd, 2 critic fwd + dX, actor dW + dX)
+    fa, fc = 2 * B * (3 * H + H * H + H * 2), 2 * B * (4 * H + H * H + H)
+    flop = 2 * (fa + 2 * fc + 3 * fc) + (fa + 2 * 2 * fc + 2 * fa)
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        if os.path.exists(oracle.REF_FAST_SO):
+            os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
+            ref = oracle.Reference("fast")
+            U = 50
+            na, nc = agent.actor.params.numel(), agent.critics[0].params.numel()
+            oa = rs.uniform(-1, 1, (U, 2, B, 4)).astype(np.float32)
+            a = [agent.actor.params.cpu().numpy(), np.float32(-0.7), np.stack([c.params.cpu().numpy() for c in agent.critics]),
+                 np.stack([c.params.cpu().numpy() for c in agent.critics_target]), oa, rs.uniform(-16, 0, (U, B)).astype(np.float32), np.zeros((U, B), np.uint8),
+                 rs.standard_normal((U, 2, B, 1)).astype(np.float32), rs.standard_normal((U, B, 1)).astype(np.float32)]
+            ref.sac_updates(B, H, *a)                             # warm-up
+            t0 = time.perf_counter()
+            ref.sac_updates(B, H, *a)
+            sec = time.perf_counter() - t0
+            cpu = {"value": U * B / sec, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
+                   "sample": f"{U} updates (train_critic x 2, update_critic_targets, train_actor) of the reference on hand-filled batches, CPU_OPENBLAS build; batch "
+                             "sampling and network setup / teardown of the call included"}
+    peaks = measured_peaks()
+    tflops = flop * UPDATES / (ms_graph * 1e-3) / 1e12
+    print(json.dumps({"metric": "SAC update samples/s (batch 256: gather_batch, 2 x train_critic, target update, train_actor)", "value": UPDATES * B / (ms_graph * 1e-3),
+                      "unit": "samples/s", "n_gpus": 1, "steps": reps, "warmup": 1, "ms_per_step": ms_graph, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"sac_update_actor3-{H}-{H}-2_critics4-{H}-{H}-1_batch{B}_x{UPDATES}updates", "us_per_update_graph": ms_graph * 1e3 / UPDATES,
+                                 "us_per_update_eager": ms_eager * 1e3 / UPDATES, "replay": f"{N} buffers x {CAP} transitions, full", "noise": "resident pool of 64 x 3 draws",
+                                 "graph": "10 updates per captured graph (the sampled indices repeat per replay)",
+                                 "l2": "working set (a few MB) is L2-resident by design: latency-bound", "parallelism": "single GPU"},
+                      "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
+                                   "peak_source": peaks["source"] + " bf16 dense (burst)"},
+                      "cpu_baseline": cpu, "gpu_launches": reps * UPDATES * 40}))
+
+
 def run_actor_eval(args):
     """Secondary line: the batched actor inference of the CPU-runnable configuration -- fp32 input [256, 3], MLP 3 -> 64 -> 64 -> 2 (ReLU,
     ReLU, identity), evaluate() = three fused dense launches, 1000 calls per timed step, eager and replayed as a CUDA graph.
@@ -563,7 +666,7 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval"],
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update"],
                     help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
                          "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
                          "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
@@ -576,6 +679,8 @@ def main():
         return run_mlp_train(args)
     if args.workload == "collect":
         return run_collect(args)
+    if args.workload == "sac_update":
+        return run_sac_update(args)
     if args.workload == "ppo_update":
         return run_ppo_update(args)
     if args.workload == "critic_train":

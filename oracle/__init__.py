@@ -556,7 +556,7 @@ class Reference:
             raise KeyError("no such off-policy runner case")
         return st
 
-    SAC_CASES = ((256, 64), (100, 32))                          # (batch, hidden width) instantiated in ref_driver.cpp
+    SAC_CASES = ((256, 64), (100, 32))                          # (batch, hidden width) instantiated in ref_driver.cpp; (256, 256) too, for the timed baseline
 
     def sac_updates(self, batch, hidden, actor_params, log_alpha, critic_params, target_params, oa_base, rewards, terminated, noise_critic, noise_actor):
         """The reference's train_critic x 2, update_critic_targets, train_actor per update (same dict as Oracle.sac_updates)."""

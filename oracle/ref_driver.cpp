@@ -745,6 +745,7 @@ int ref_sac_updates(int batch, int hidden, int n_updates, const float* actor_par
                     float* log_alpha_out, float* critic_out, float* target_out, float* target_values_out){
 #define SAC_CASE(b, h) if(batch == b && hidden == h){ sac_case<b, h>(n_updates, actor_params, log_alpha, critic_params, target_params, oa_base, rewards, terminated, noise_critic, noise_actor, actor_out, log_alpha_out, critic_out, target_out, target_values_out); return 0; }
     SAC_CASE(256, 64)
+    SAC_CASE(256, 256)
     SAC_CASE(100, 32)
 #undef SAC_CASE
     return -1;

@@ -523,15 +523,15 @@ def run_sac_update(args):
     raw[:, 44 * CAP + 8] = 1                                     # full buffers, position 0
     replay = torch.from_numpy(raw.reshape(-1)).to(dev)
     batch = pkg.new_batch(B)
-    noise = torch.from_numpy(rs.standard_normal((64, 3, B, 1)).astype(np.float32)).to(dev)      # a resident pool, like the reference's randn() into its noise buffers
+    noise = torch.empty((3, B, 1), device=dev)
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
-    calls = [0]
+    counter = torch.zeros(1, dtype=torch.int64, device=dev)       # device-resident call index: a replayed graph samples fresh batches and noise
 
     def update():
-        k = calls[0] % 64
-        pkg.gather_batch(replay, L, N, batch, seed=11, call_index=calls[0], error_flag=flag)
-        agent.update(batch, noise[k, 0], noise[k, 1], noise[k, 2])
-        calls[0] += 1
+        pkg.gather_batch(replay, L, N, batch, seed=11, call_counter=counter, error_flag=flag)
+        pkg.randn_device_rng(noise, 11, stream_id=1, call_counter=counter)          # the reference's randn() into its noise buffers
+        agent.update(batch, noise[0], noise[1], noise[2])
+        pkg.counter_advance(counter, 1)
 
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
@@ -546,6 +546,7 @@ def run_sac_update(args):
     assert int(flag.item()) == 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = min(args.steps, 10)
+    seen = int(counter.item())
 
     def timed(fn):
         fn(); torch.cuda.synchronize()
@@ -556,6 +557,7 @@ def run_sac_update(args):
         return e0.elapsed_time(e1) / reps
     ms_eager = timed(lambda: [update() for _ in range(UPDATES)])
     ms_graph = timed(lambda: [graph.replay() for _ in range(UPDATES // 10)])
+    assert int(counter.item()) == seen + 2 * (reps + 1) * UPDATES and int(flag.item()) == 0      # every update of both timed loops ran and advanced the counter
     # contractions per update: critic updates 2 x (actor fwd + 2 target fwd + critic fwd + dW + dX), actor update (actor fwd, 2 critic fwd + dX, actor dW + dX)
     fa, fc = 2 * B * (3 * H + H * H + H * 2), 2 * B * (4 * H + H * H + H)
     flop = 2 * (fa + 2 * fc + 3 * fc) + (fa + 2 * 2 * fc + 2 * fa)
@@ -584,12 +586,12 @@ def run_sac_update(args):
                       "unit": "samples/s", "n_gpus": 1, "steps": reps, "warmup": 1, "ms_per_step": ms_graph, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                       "dtype": "f32", "data": "synthetic",
                       "config": {"workload": f"sac_update_actor3-{H}-{H}-2_critics4-{H}-{H}-1_batch{B}_x{UPDATES}updates", "us_per_update_graph": ms_graph * 1e3 / UPDATES,
-                                 "us_per_update_eager": ms_eager * 1e3 / UPDATES, "replay": f"{N} buffers x {CAP} transitions, full", "noise": "resident pool of 64 x 3 draws",
-                                 "graph": "10 updates per captured graph (the sampled indices repeat per replay)",
+                                 "us_per_update_eager": ms_eager * 1e3 / UPDATES, "replay": f"{N} buffers x {CAP} transitions, full", "noise": "3 x [256, 1] normals drawn on the device per update",
+                                 "graph": "10 updates per captured graph; a device-resident call counter gives every replay fresh indices and noise",
                                  "l2": "working set (a few MB) is L2-resident by design: latency-bound", "parallelism": "single GPU"},
                       "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
                                    "peak_source": peaks["source"] + " bf16 dense (burst)"},
-                      "cpu_baseline": cpu, "gpu_launches": reps * UPDATES * 40}))
+                      "cpu_baseline": cpu, "gpu_launches": reps * UPDATES * 113}))
 
 
 def run_actor_eval(args):

@@ -383,6 +383,20 @@ int b200rl_sac_min_value_d_output(const float* q1, int ld_q1, const float* q2, i
                                   int ld_d_input, int action_offset, int action_dim, float* d_actor_output, int ld_out, int batch,
                                   b200rl_stream_t stream);
 
+/* Randomness kept entirely on the device, for update loops captured in a CUDA graph: *call_counter (a device-resident 64-bit integer)
+ * takes the place of call_index in the sampling kernel and in the normal generator, and b200rl_counter_advance adds to it on the stream,
+ * so that every replay of one captured graph draws fresh indices and noise. b200rl_randn_device_rng fills dst[0..n) with standard normals:
+ * Philox block (element / 4, call low, call high, 2 + stream_id) keyed by seed, Box-Muller on the word pairs; call = call_index +
+ * *call_counter (call_counter may be NULL); different stream_id values give independent streams for the same call (the counterpart of
+ * the reference's randn(device, matrix, rng) on its device engines, containers/matrix/operations_cuda.h:197-223). */
+int b200rl_counter_advance(unsigned long long* call_counter, unsigned long long increment, b200rl_stream_t stream);
+int b200rl_randn_device_rng(float* dst, size_t n, unsigned long long seed, unsigned int stream_id, unsigned long long call_index,
+                            const unsigned long long* call_counter, b200rl_stream_t stream);
+int b200rl_gather_batch_device_counter(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length,
+                                       int obs_dim, int action_dim, unsigned long long seed, const unsigned long long* call_counter, int batch,
+                                       float* oa_base, int ld_oa, float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base,
+                                       uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream);
+
 /* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
  * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and
  * target-value columns. b200rl_shuffle_permutation_host replays those draws on the host engine (advanced in place, as the reference

@@ -137,6 +137,9 @@ def lib():
         L.b200rl_sample_and_squash_backward.argtypes = [vp, i, vp, i, vp, vp, i, vp, i, vp, f, i, i, vp, i, vp, vp, vp]
         L.b200rl_sac_target_action_values.argtypes = [vp, i, vp, i, vp, vp, vp, vp, f, i, i, i, vp, i, i, vp]
         L.b200rl_sac_min_value_d_output.argtypes = [vp, i, vp, i, vp, vp, i, i, i, vp, i, i, vp]
+        L.b200rl_counter_advance.argtypes = [vp, C.c_uint64, vp]
+        L.b200rl_randn_device_rng.argtypes = [vp, sz, C.c_uint64, C.c_uint, C.c_uint64, vp, vp]
+        L.b200rl_gather_batch_device_counter.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, C.c_uint64, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
         L.b200rl_polyak_update.argtypes = [vp, i, vp, i, i, i, f, i, vp]
         L.b200rl_replay_counters.argtypes = [vp, C.POINTER(ReplayLayout), i, vp, vp, vp]
         L.b200rl_gather_draws_host.argtypes = [vp, i, i, vp, vp, i, vp, vp]
@@ -499,13 +502,16 @@ def new_batch(batch, obs_dim=3, action_dim=1, device="cuda"):
 
 
 def gather_batch(replay, layout, n_envs, out, env_index=None, sample_offset=None, seed=None, call_index=0, max_episode_length=200, obs_dim=3, action_dim=1,
-                 error_flag=None):
+                 error_flag=None, call_counter=None):
     """Replay-buffer sampling into the batch tensors `out` (new_batch): indices either given (int32 CUDA tensors drawn by gather_draws_host) or
-    drawn inside the kernel from (seed, call_index)."""
+    drawn inside the kernel from (seed, call_index), or from (seed, *call_counter) with call_counter a one-element int64 CUDA tensor."""
     batch = out["rewards"].shape[0]
     tail = (batch, _ptr(out["oa_base"]), out["oa_base"].stride(1), _ptr(out["rewards"]), _ptr(out["terminated"]), _ptr(out["reset"]), _ptr(out["next_reset_base"]),
             _ptr(out["final_step_mask"]), _ptr(out["next_final_step_mask_base"]), _ptr(error_flag), _stream())
-    if seed is None:
+    if call_counter is not None:
+        check(lib().b200rl_gather_batch_device_counter(_ptr(replay), C.byref(layout), n_envs, max_episode_length, obs_dim, action_dim, seed, _ptr(call_counter), *tail),
+              "b200rl_gather_batch_device_counter")
+    elif seed is None:
         check(lib().b200rl_gather_batch(_ptr(replay), C.byref(layout), n_envs, max_episode_length, obs_dim, action_dim, _ptr(env_index), _ptr(sample_offset), *tail),
               "b200rl_gather_batch")
     else:
@@ -565,3 +571,15 @@ def sac_min_value_d_output(q1, q2, d_critic_1_input, d_critic_2_input, action_di
     check(lib().b200rl_sac_min_value_d_output(_ptr(q1), q1.stride(0), _ptr(q2), q2.stride(0), _ptr(d_critic_1_input), _ptr(d_critic_2_input), d_critic_1_input.stride(0),
                                               D - action_dim, action_dim, _ptr(d_actor_output), d_actor_output.stride(0), B, _stream()), "b200rl_sac_min_value_d_output")
     return d_actor_output
+
+
+def counter_advance(call_counter, increment=1):
+    """call_counter (one-element int64 CUDA tensor) += increment, on the current stream."""
+    check(lib().b200rl_counter_advance(_ptr(call_counter), increment, _stream()), "b200rl_counter_advance")
+
+
+def randn_device_rng(dst, seed, stream_id=0, call_index=0, call_counter=None):
+    """Fills the contiguous float32 CUDA tensor dst with standard normals from the counter-based generator."""
+    assert dst.is_contiguous()
+    check(lib().b200rl_randn_device_rng(_ptr(dst), dst.numel(), seed, stream_id, call_index, _ptr(call_counter), _stream()), "b200rl_randn_device_rng")
+    return dst

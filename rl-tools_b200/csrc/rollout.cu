@@ -374,6 +374,7 @@ struct GatherArgs {
     float* rewards; uint8_t *terminated, *reset, *next_reset_base, *final_step_mask, *next_final_step_mask_base;
     int* error_flag;
     int device_rng; unsigned long long seed, call;      // device draws: Philox block (batch element, call low, call high, 1) keyed by seed
+    const unsigned long long* call_counter;             // optional device-resident call index added to `call` (advanced by a later launch)
 };
 // one warp per batch element: lanes stride over the columns of the transition row
 template <typename INDEX>
@@ -383,7 +384,8 @@ __global__ void gather_batch_kernel(GatherArgs a){
     int e, offset = 0;
     uint32_t word1 = 0;
     if(a.device_rng){         // bounded draws by the high half of word * range (bias below range / 2^32)
-        uint32_t c[4] = {(uint32_t)b, (uint32_t)a.call, (uint32_t)(a.call >> 32), 1u};
+        const unsigned long long call = a.call + (a.call_counter ? *a.call_counter : 0ull);
+        uint32_t c[4] = {(uint32_t)b, (uint32_t)call, (uint32_t)(call >> 32), 1u};
         Philox::block(c, (uint32_t)a.seed, (uint32_t)(a.seed >> 32));
         e = (int)__umulhi(c[0], (uint32_t)a.n_envs);
         word1 = c[1];
@@ -435,7 +437,8 @@ extern "C" int b200rl_replay_counters(const void* replay_buffers, const b200rl_r
 static int gather_launch(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim,
                          int action_dim, const int32_t* env_index, const int32_t* sample_offset, int batch, float* oa_base, int ld_oa,
                          float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
-                         uint8_t* next_final_step_mask_base, int* error_flag, DeviceRng rng, b200rl_stream_t stream){
+                         uint8_t* next_final_step_mask_base, int* error_flag, DeviceRng rng, b200rl_stream_t stream,
+                         const unsigned long long* call_counter = nullptr){
     if(!replay_buffers || !layout || (!rng.enabled && (!env_index || !sample_offset)) || !oa_base || !rewards || !terminated || !reset || !next_reset_base || !final_step_mask ||
        !next_final_step_mask_base || n_envs < 1 || batch < 0 || obs_dim < 1 || action_dim < 1 || max_episode_length < 0)
         return B200RL_ERR_INVALID_ARGUMENT;
@@ -447,7 +450,7 @@ static int gather_launch(const void* replay_buffers, const b200rl_replay_layout*
     a.obs_dim = obs_dim; a.action_dim = action_dim; a.env_index = env_index; a.sample_offset = sample_offset; a.oa_base = oa_base; a.ld_oa = ld_oa;
     a.rewards = rewards; a.terminated = terminated; a.reset = reset; a.next_reset_base = next_reset_base; a.final_step_mask = final_step_mask;
     a.next_final_step_mask_base = next_final_step_mask_base; a.error_flag = error_flag;
-    a.device_rng = rng.enabled; a.seed = rng.seed; a.call = rng.step0;
+    a.device_rng = rng.enabled; a.seed = rng.seed; a.call = rng.step0; a.call_counter = call_counter;
     const int threads = 128, blocks = (int)(((size_t)batch * 32 + threads - 1) / threads);
     cudaStream_t s = (cudaStream_t)stream;
     if(layout->index_bytes == 4) gather_batch_kernel<uint32_t><<<blocks, threads, 0, s>>>(a);
@@ -470,4 +473,58 @@ extern "C" int b200rl_gather_batch_device_rng(const void* replay_buffers, const 
                                               uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream){
     return gather_launch(replay_buffers, layout, n_envs, max_episode_length, obs_dim, action_dim, nullptr, nullptr, batch, oa_base, ld_oa, rewards,
                          terminated, reset, next_reset_base, final_step_mask, next_final_step_mask_base, error_flag, DeviceRng{1, seed, call_index}, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Randomness that lives entirely on the device, for update loops captured in a CUDA graph: a device-resident 64-bit call counter
+// feeds the Philox counters of the sampling kernel above and of the normal generator below, and is advanced by its own launch, so that
+// every replay of the same graph draws fresh numbers.
+// ---------------------------------------------------------------------------------------------------------------
+namespace b200rl {
+__global__ void counter_advance_kernel(unsigned long long* counter, unsigned long long increment){ *counter += increment; }
+
+// four standard normals per Philox block: counter (element / 4, call low, call high, 2 + stream_id), Box-Muller on word pairs
+__global__ void randn_kernel(float* __restrict__ dst, size_t n, unsigned long long seed, uint32_t stream_id, unsigned long long call,
+                             const unsigned long long* __restrict__ call_counter){
+    const size_t q = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if(q * 4 >= n) return;
+    call += call_counter ? *call_counter : 0ull;
+    uint32_t c[4] = {(uint32_t)q, (uint32_t)call, (uint32_t)(call >> 32), 2u + stream_id};
+    Philox::block(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+    float out[4];
+#pragma unroll
+    for(int h = 0; h < 2; h++){
+        const float radius = sqrtf(-2.0f * logf(unit_uniform(c[2 * h])));
+        float sn, cs;
+        sincospif(2.0f * unit_uniform(c[2 * h + 1]), &sn, &cs);
+        out[2 * h] = radius * cs; out[2 * h + 1] = radius * sn;
+    }
+    for(int i = 0; i < 4 && q * 4 + i < n; i++) dst[q * 4 + i] = out[i];
+}
+}  // namespace b200rl
+
+extern "C" int b200rl_counter_advance(unsigned long long* counter, unsigned long long increment, b200rl_stream_t stream){
+    if(!counter) return B200RL_ERR_INVALID_ARGUMENT;
+    counter_advance_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(counter, increment);
+    B200RL_LAUNCH_CHECK("counter_advance");
+    return B200RL_OK;
+}
+
+extern "C" int b200rl_randn_device_rng(float* dst, size_t n, unsigned long long seed, unsigned int stream_id, unsigned long long call_index,
+                                       const unsigned long long* call_counter, b200rl_stream_t stream){
+    if(!dst || n > ((size_t)1 << 33)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n == 0) return B200RL_OK;
+    const size_t quads = (n + 3) / 4;
+    randn_kernel<<<(unsigned)((quads + 127) / 128), 128, 0, (cudaStream_t)stream>>>(dst, n, seed, stream_id, call_index, call_counter);
+    B200RL_LAUNCH_CHECK("randn_device_rng");
+    return B200RL_OK;
+}
+
+extern "C" int b200rl_gather_batch_device_counter(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim,
+                                                  int action_dim, unsigned long long seed, const unsigned long long* call_counter, int batch, float* oa_base,
+                                                  int ld_oa, float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
+                                                  uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream){
+    if(!call_counter) return B200RL_ERR_INVALID_ARGUMENT;
+    return gather_launch(replay_buffers, layout, n_envs, max_episode_length, obs_dim, action_dim, nullptr, nullptr, batch, oa_base, ld_oa, rewards,
+                         terminated, reset, next_reset_base, final_step_mask, next_final_step_mask_base, error_flag, DeviceRng{1, seed, 0}, stream, call_counter);
 }

@@ -230,3 +230,71 @@ def test_cuda_core_kernel_draws_the_same(lib, torch, tmp_path):
     eps_a, eps_b = (mine[:T, :, ACTION] - mine[:T, :, MEAN]) / std, (other[:T, :, ACTION] - other[:T, :, MEAN]) / std
     assert np.abs(eps_a - eps_b).max() < 1e-5
     assert np.abs(mine[:T, :, :7] - other[:T, :, :7]).max() < 5e-3
+
+
+def test_randn_matches_numpy_philox_and_counter(lib, torch):
+    """b200rl_randn_device_rng against the numpy statement of its counter layout (element / 4, call low, call high, 2 + stream id), and the
+    device-resident call counter: call_index + *counter is what enters the Philox counter."""
+    n, seed, stream_id, call = 1003, 0xABCDEF0123, 3, (1 << 33) + 5
+    got = lib.randn_device_rng(torch.empty(n, device="cuda"), seed, stream_id=stream_id, call_index=call).cpu().numpy()
+    q = np.arange((n + 3) // 4, dtype=np.uint64)
+    counter = np.stack([q, np.full_like(q, call & 0xFFFFFFFF), np.full_like(q, call >> 32), np.full_like(q, 2 + stream_id)], -1).astype(np.uint32)
+    words = philox4x32_10(counter, (seed & 0xFFFFFFFF, seed >> 32))
+    u = ((words >> np.uint32(9)).astype(np.float64) + 0.5) * 2.0 ** -23
+    want = np.empty((len(q), 4))
+    for h in range(2):
+        radius = np.sqrt(-2.0 * np.log(u[:, 2 * h]))
+        want[:, 2 * h], want[:, 2 * h + 1] = radius * np.cos(2 * np.pi * u[:, 2 * h + 1]), radius * np.sin(2 * np.pi * u[:, 2 * h + 1])
+    assert np.abs(got - want.reshape(-1)[:n]).max() < 2e-5
+    counter_d = torch.tensor([call - 7], dtype=torch.int64, device="cuda")
+    via_counter = lib.randn_device_rng(torch.empty(n, device="cuda"), seed, stream_id=stream_id, call_index=7, call_counter=counter_d).cpu().numpy()
+    assert np.array_equal(via_counter, got)
+    lib.counter_advance(counter_d, 7)
+    assert int(counter_d.item()) == call
+    other = lib.randn_device_rng(torch.empty(n, device="cuda"), seed, stream_id=stream_id + 1, call_index=call).cpu().numpy()
+    assert abs(np.corrcoef(other, got)[0, 1]) < 0.15
+    big = lib.randn_device_rng(torch.empty(1 << 21, device="cuda"), 5).cpu().numpy().astype(np.float64)
+    m = big.size
+    assert abs(big.mean()) < 5 / np.sqrt(m) and abs(big.var() - 1) < 5 * np.sqrt(2 / m) and abs((big ** 4).mean() - 3) < 5 * np.sqrt(96 / m)
+    assert abs((big[1:] * big[:-1]).mean()) < 5 / np.sqrt(m)
+
+
+def test_graph_replay_draws_fresh_numbers(lib, torch):
+    """Sampling, noise and the counter advance captured once as a CUDA graph: every replay uses the next call index, and equals the
+    direct calls with that index."""
+    import test_gpu_gather as tg
+    import make_golden as mg
+    orc = oracle.Oracle()
+    case = 0
+    N, cap, limit, _, steps = mg.GATHER_CASES[case]
+    st, _ = tg.replay_state(orc, case)
+    replay, L = tg.pack_replay(lib, torch, st)
+    B, seed = 64, 21
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+    out, noise = lib.new_batch(B), torch.empty((B, 1), device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def step():
+        lib.gather_batch(replay, L, N, out, seed=seed, call_counter=counter, error_flag=flag)
+        lib.randn_device_rng(noise, seed, stream_id=1, call_counter=counter)
+        lib.counter_advance(counter, 1)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()                                                       # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(side)
+    counter.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step()
+    seen = []
+    for k in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        direct = lib.gather_batch(replay, L, N, lib.new_batch(B), seed=seed, call_index=k, error_flag=flag)
+        direct_noise = lib.randn_device_rng(torch.empty((B, 1), device="cuda"), seed, stream_id=1, call_index=k)
+        assert torch.equal(out["oa_base"], direct["oa_base"]) and torch.equal(out["rewards"], direct["rewards"]) and torch.equal(noise, direct_noise)
+        seen.append(out["oa_base"].clone())
+    assert int(counter.item()) == 3 and int(flag.item()) == 0
+    assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[1], seen[2])

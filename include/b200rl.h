@@ -397,6 +397,22 @@ int b200rl_gather_batch_device_counter(const void* replay_buffers, const b200rl_
                                        float* oa_base, int ld_oa, float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base,
                                        uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * Observation normalisation of the PPO loop (rl/algorithms/ppo/loop/core/operations_generic.h:99-131): per loop step the running
+ * normaliser is updated with the collected observations and its statistics are handed to the standardize layer in front of actor and critic.
+ * b200rl_running_normalizer_update: update(device, normalizer, data) (rl/components/running_normalizer/operations_generic.h:27-47):
+ *   per column the batch mean and the batch standard deviation about that mean (0 when the sum of squared deviations is below 1e-6, else
+ *   sqrt(sum / (rows - 1))), then running += (batch - running) / age. age = the normaliser's age AFTER its increment (a host integer in
+ *   the reference). The column sums are taken in double and rounded once (the reference sums in fp32 in row order).
+ * b200rl_standardize_set_statistics: set_statistics (nn/layers/standardize/operations_generic.h:52-66): precision = std == 0 ? 0 : 1 / std.
+ * b200rl_standardize_forward: evaluate / forward of the layer (:69-92; CUDA form nn/layers/standardize/operations_cuda.h): (x - mean) * precision,
+ *   the product skipped where precision is 0. The layer has no trainable parameters; as the first layer of its network it needs no backward. */
+int b200rl_running_normalizer_update(const float* data, int ld, int rows, int dim, float* mean, float* std, unsigned long long age,
+                                     b200rl_stream_t stream);
+int b200rl_standardize_set_statistics(const float* mean, const float* std, int dim, float* layer_mean, float* layer_precision, b200rl_stream_t stream);
+int b200rl_standardize_forward(const float* x, int ldx, const float* mean, const float* precision, float* y, int ldy, int rows, int dim,
+                               b200rl_stream_t stream);
+
 /* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
  * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and
  * target-value columns. b200rl_shuffle_permutation_host replays those draws on the host engine (advanced in place, as the reference

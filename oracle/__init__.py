@@ -95,6 +95,9 @@ class Oracle:
                                           _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _f32p, _f32p]
         L.orc_sample_and_squash_forward.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p]
         L.orc_sample_and_squash_backward.argtypes = [_f32p, C.c_int, _f32p, _f32p, _f32p, _f32p, C.c_float, C.c_float, C.c_int, C.c_int, _f32p, C.c_int, _f32p, _f32p]
+        L.orc_running_normalizer_update.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _f32p, _f32p, C.c_void_p]
+        L.orc_standardize_set_statistics.argtypes = [_f32p, _f32p, C.c_int, _f32p, _f32p]
+        L.orc_standardize_forward.argtypes = [_f32p, C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
         L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
@@ -325,6 +328,22 @@ class Oracle:
         out["log_alpha_gradient"] = grad[0]
         return out
 
+    def normalizer(self, data):
+        """RunningNormalizer updates on data [U, R, D] (fresh normalizer), then a standardize layer with the resulting statistics on the last
+        batch: dict(mean [U, D], std [U, D], layer_mean, layer_precision, output [R, D])."""
+        U, R, D = data.shape
+        data = np.ascontiguousarray(data, np.float32)
+        mean, std, age = np.zeros(D, np.float32), np.ones(D, np.float32), C.c_uint64(0)
+        means, stds = np.empty((U, D), np.float32), np.empty((U, D), np.float32)
+        for u in range(U):
+            self.lib.orc_running_normalizer_update(data[u], D, R, D, mean, std, C.byref(age))
+            means[u], stds[u] = mean, std
+        lm, lp = np.empty(D, np.float32), np.empty(D, np.float32)
+        self.lib.orc_standardize_set_statistics(mean, std, D, lm, lp)
+        out = np.empty((R, D), np.float32)
+        self.lib.orc_standardize_forward(data[-1], D, lm, lp, out, D, R, D)
+        return dict(mean=means, std=stds, layer_mean=lm, layer_precision=lp, output=out)
+
     def sac_target_action_values(self, q1, q2, rewards, terminated, next_log_probs, log_alpha, gamma=np.float32(0.99)):
         """rl/algorithms/sac/operations_generic.h:133-163 with the default parameters (entropy bonus inside the discounted term, termination honoured)."""
         alpha = np.float32(np.exp(np.float64(np.float32(log_alpha))))          # the host libm's expf is correctly rounded
@@ -485,6 +504,7 @@ class Reference:
         L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
         L.ref_offpolicy_steps.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _i32p, _u8p, _f32p, _f32p, _f32p, _f32p]
+        L.ref_normalizer.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_sac_updates.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _u8p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_sample_and_squash.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_polyak_update.argtypes = [_f32p, _f32p, C.c_float, C.c_int, C.c_int]
@@ -555,6 +575,19 @@ class Reference:
         if rc != 0:
             raise KeyError("no such off-policy runner case")
         return st
+
+    NORMALIZER_CASES = ((4096, 27), (333, 3), (50, 5))            # (rows, dim) instantiated in ref_driver.cpp
+
+    def normalizer(self, data):
+        """The reference's RunningNormalizer::update on data [U, R, D], then set_statistics / evaluate of its standardize layer on the last batch
+        (same dict as Oracle.normalizer)."""
+        U, R, D = data.shape
+        means, stds = np.empty((U, D), np.float32), np.empty((U, D), np.float32)
+        lm, lp, out = np.empty(D, np.float32), np.empty(D, np.float32), np.empty((R, D), np.float32)
+        rc = self.lib.ref_normalizer(R, D, U, np.ascontiguousarray(data, np.float32), means, stds, lm, lp, out)
+        if rc != 0:
+            raise KeyError("no such normalizer case")
+        return dict(mean=means, std=stds, layer_mean=lm, layer_precision=lp, output=out)
 
     SAC_CASES = ((256, 64), (100, 32))                          # (batch, hidden width) instantiated in ref_driver.cpp; (256, 256) too, for the timed baseline
 

@@ -212,6 +212,39 @@ void orc_mse_gradient(const float* a, int lda, const float* b, int ldb, float* d
         d_a[(size_t)r * ldd + c] = diff * constant;
     }
 }
+/* ------------------------------------------------------------------------------------------------------ */
+/* Observation normalisation: rl/components/running_normalizer/operations_generic.h:27-47 (update: per column  */
+/* the batch mean and the batch standard deviation about that mean, both by sequential fp32 sums,              */
+/* containers/matrix/operations_generic.h:641-650, 674-691: std = 0 if the sum of squares is below 1e-6, else    */
+/* sqrt(sum / (rows - 1)); running values move by (batch value - running value) / age),                         */
+/* nn/layers/standardize/operations_generic.h:52-66 (set_statistics: precision = std == 0 ? 0 : 1 / std),       */
+/* :69-86 (evaluate: (x - mean) * precision, the product skipped where precision is 0). The layer's            */
+/* backward_input (:105-124) is not restated: the reference's template does not compile (it names a type its   */
+/* specification lacks) and is never reached, the layer being the first of its network.                        */
+/* ------------------------------------------------------------------------------------------------------ */
+void orc_running_normalizer_update(const float* data, int ld, int rows, int dim, float* mean, float* std, uint64_t* age){
+    *age += 1;
+    for(int c = 0; c < dim; c++){
+        float acc = 0;
+        for(int r = 0; r < rows; r++) acc += data[(size_t)r * ld + c];
+        const float data_mean = acc / rows;
+        float sq = 0;
+        for(int r = 0; r < rows; r++){ const float diff = data[(size_t)r * ld + c] - data_mean; sq += diff * diff; }
+        const float data_std = sq < 1e-6 ? 0 : sqrtf(sq / (rows - 1));
+        mean[c] = mean[c] + (data_mean - mean[c]) / (*age);
+        std[c] = std[c] + (data_std - std[c]) / (*age);
+    }
+}
+void orc_standardize_set_statistics(const float* mean, const float* std, int dim, float* layer_mean, float* layer_precision){
+    for(int c = 0; c < dim; c++){ layer_mean[c] = mean[c]; layer_precision[c] = std[c] == 0 ? 0 : 1 / std[c]; }
+}
+void orc_standardize_forward(const float* x, int ldx, const float* mean, const float* precision, float* y, int ldy, int rows, int dim){
+    for(int r = 0; r < rows; r++) for(int c = 0; c < dim; c++){
+        float v = x[(size_t)r * ldx + c] - mean[c];
+        if(precision[c] != 0) v *= precision[c];
+        y[(size_t)r * ldy + c] = v;
+    }
+}
 /* Target-network update, utils/polyak/operations_generic.h:10-24 (update) and :26-40 (update_squared):      */
 /* target = polyak * target + (1 - polyak) * source [* source], left to right.                                */
 void orc_polyak_update(const float* source, int ld_source, float* target, int ld_target, int rows, int cols, float polyak, int square){

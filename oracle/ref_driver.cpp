@@ -35,6 +35,8 @@
 #include <rl_tools/nn/layers/dense/operations_cpu.h>
 #include <rl_tools/nn/loss_functions/mse/operations_generic.h>
 #include <rl_tools/nn/layers/sample_and_squash/operations_generic.h>     // before the model headers that recurse into it
+#include <rl_tools/nn/layers/standardize/operations_generic.h>
+#include <rl_tools/rl/components/running_normalizer/operations_generic.h>
 #include <rl_tools/nn_models/mlp/operations_generic.h>
 #include <rl_tools/nn_models/mlp_unconditional_stddev/operations_generic.h>
 #include <rl_tools/nn_models/sequential/operations_generic.h>
@@ -702,6 +704,31 @@ static void sac_case(int n_updates, const float* actor_params, float log_alpha, 
     rlt::free(device, action_noise_critic); rlt::free(device, action_noise_actor);
 }
 
+// Observation normalisation through the reference's own RunningNormalizer::update (rl/components/running_normalizer/operations_generic.h:27-47)
+// on n_updates consecutive [ROWS, DIM] batches, then set_statistics + evaluate of a standardize layer
+// (nn/layers/standardize/operations_generic.h:52-86) on the last batch. The layer's backward_input (:105-124) cannot be instantiated: it names
+// LAYER_SPEC::T, which the layer's specification does not define (it is never reached in the reference, where the layer comes first).
+template <TI ROWS, TI DIM>
+static void normalizer_case(int n_updates, const float* data, float* mean_out, float* std_out, float* layer_mean, float* layer_precision, float* output){
+    using NORMALIZER = rlt::rl::components::RunningNormalizer<rlt::rl::components::running_normalizer::Specification<TYPE_POLICY, TI, DIM>>;
+    using LAYER = rlt::nn::layers::standardize::Layer<rlt::nn::layers::standardize::Configuration<TYPE_POLICY, TI>, rlt::nn::capability::Backward<>, rlt::tensor::Shape<TI, 1, ROWS, DIM>>;
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    NORMALIZER normalizer; LAYER layer; typename LAYER::template Buffer<> buffer;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, ROWS, DIM>> batch, out;
+    rlt::malloc(device, normalizer); rlt::malloc(device, layer); rlt::malloc(device, batch); rlt::malloc(device, out);
+    rlt::init(device, normalizer); rlt::init_weights(device, layer, rng);
+    for(int u = 0; u < n_updates; u++){
+        for(TI r = 0; r < ROWS; r++) for(TI c = 0; c < DIM; c++) rlt::set(batch, r, c, data[((size_t)u * ROWS + r) * DIM + c]);
+        rlt::update(device, normalizer, batch);
+        for(TI c = 0; c < DIM; c++){ mean_out[(size_t)u * DIM + c] = rlt::get(normalizer.mean, 0, c); std_out[(size_t)u * DIM + c] = rlt::get(normalizer.std, 0, c); }
+    }
+    rlt::set_statistics(device, layer, normalizer.mean, normalizer.std);
+    rlt::evaluate(device, layer, batch, out, buffer, rng);
+    for(TI c = 0; c < DIM; c++){ layer_mean[c] = rlt::get(device, layer.mean.parameters, c); layer_precision[c] = rlt::get(device, layer.precision.parameters, c); }
+    for(TI r = 0; r < ROWS; r++) for(TI c = 0; c < DIM; c++) output[r * DIM + c] = rlt::get(out, r, c);
+    rlt::free(device, normalizer); rlt::free(device, layer); rlt::free(device, batch); rlt::free(device, out);
+}
+
 extern "C" {
 
 int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards,
@@ -738,6 +765,14 @@ int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle,
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 1, true)
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 10, true)
 #undef PPO_CASE
+    return -1;
+}
+int ref_normalizer(int rows, int dim, int n_updates, const float* data, float* mean_out, float* std_out, float* layer_mean, float* layer_precision, float* output){
+#define NORMALIZER_CASE(r, d) if(rows == r && dim == d){ normalizer_case<r, d>(n_updates, data, mean_out, std_out, layer_mean, layer_precision, output); return 0; }
+    NORMALIZER_CASE(4096, 27)
+    NORMALIZER_CASE(333, 3)
+    NORMALIZER_CASE(50, 5)
+#undef NORMALIZER_CASE
     return -1;
 }
 int ref_sac_updates(int batch, int hidden, int n_updates, const float* actor_params, float log_alpha, const float* critic_params, const float* target_params,

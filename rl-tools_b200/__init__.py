@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
@@ -140,6 +140,9 @@ def lib():
         L.b200rl_counter_advance.argtypes = [vp, C.c_uint64, vp]
         L.b200rl_randn_device_rng.argtypes = [vp, sz, C.c_uint64, C.c_uint, C.c_uint64, vp, vp]
         L.b200rl_gather_batch_device_counter.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, C.c_uint64, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.b200rl_running_normalizer_update.argtypes = [vp, i, i, i, vp, vp, C.c_uint64, vp]
+        L.b200rl_standardize_set_statistics.argtypes = [vp, vp, i, vp, vp, vp]
+        L.b200rl_standardize_forward.argtypes = [vp, i, vp, vp, vp, i, i, i, vp]
         L.b200rl_polyak_update.argtypes = [vp, i, vp, i, i, i, f, i, vp]
         L.b200rl_replay_counters.argtypes = [vp, C.POINTER(ReplayLayout), i, vp, vp, vp]
         L.b200rl_gather_draws_host.argtypes = [vp, i, i, vp, vp, i, vp, vp]
@@ -583,3 +586,33 @@ def randn_device_rng(dst, seed, stream_id=0, call_index=0, call_counter=None):
     assert dst.is_contiguous()
     check(lib().b200rl_randn_device_rng(_ptr(dst), dst.numel(), seed, stream_id, call_index, _ptr(call_counter), _stream()), "b200rl_randn_device_rng")
     return dst
+
+
+class RunningNormalizer:
+    """Mirror of rl::components::RunningNormalizer (running_normalizer.h:17-30): per-column running mean and standard deviation of the
+    observation batches it has seen, plus the statistics of a standardize layer derived from them (mean, precision = 1 / std)."""
+
+    def __init__(self, dim, device="cuda"):
+        import torch
+        self.dim, self.age = dim, 0
+        self.mean, self.std = torch.zeros(dim, device=device), torch.ones(dim, device=device)            # init(), operations_generic.h:20-25
+        self.layer_mean, self.layer_precision = torch.zeros(dim, device=device), torch.ones(dim, device=device)     # init_weights of the layer
+
+    def update(self, data):
+        """Folds the batch statistics of data [rows, dim] (a 2-D CUDA tensor or view) into the running values."""
+        self.age += 1
+        check(lib().b200rl_running_normalizer_update(_ptr(data), data.stride(0), data.shape[0], self.dim, _ptr(self.mean), _ptr(self.std), self.age, _stream()),
+              "b200rl_running_normalizer_update")
+
+    def set_statistics(self):
+        """The standardize layer takes over the running values (set_statistics, nn/layers/standardize/operations_generic.h:52-66)."""
+        check(lib().b200rl_standardize_set_statistics(_ptr(self.mean), _ptr(self.std), self.dim, _ptr(self.layer_mean), _ptr(self.layer_precision), _stream()),
+              "b200rl_standardize_set_statistics")
+
+    def standardize(self, x, y=None):
+        """The standardize layer's forward pass: y = (x - mean) * precision."""
+        import torch
+        y = torch.empty((x.shape[0], self.dim), device=x.device) if y is None else y
+        check(lib().b200rl_standardize_forward(_ptr(x), x.stride(0), _ptr(self.layer_mean), _ptr(self.layer_precision), _ptr(y), y.stride(0), x.shape[0], self.dim,
+                                               _stream()), "b200rl_standardize_forward")
+        return y

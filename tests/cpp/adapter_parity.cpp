@@ -10,6 +10,9 @@
 #include <rl_tools/nn/operations_generic.h>
 #include <rl_tools/nn/layers/dense/operations_cpu.h>
 #include <rl_tools/nn/loss_functions/mse/operations_generic.h>
+#include <rl_tools/nn/layers/standardize/operations_generic.h>
+#include <rl_tools/rl/components/running_normalizer/operations_generic.h>
+#include <b200rl/rl_tools_standardize.h>                          // before the model headers that recurse into the layer
 #include <rl_tools/nn_models/mlp/operations_generic.h>
 #include <rl_tools/nn_models/mlp_unconditional_stddev/operations_generic.h>
 #include <rl_tools/nn_models/sequential/operations_generic.h>
@@ -361,6 +364,54 @@ void polyak_parity(const char* name){
     rlt::free(cpu, src_cpu); rlt::free(cpu, dst_cpu); rlt::free(cpu, back); rlt::free(gpu, src_gpu); rlt::free(gpu, dst_gpu);
 }
 
+// The PPO loop's observation normalisation on both devices: three normalizer updates, set_statistics, then a sequential model
+// <standardize, mlp> evaluated on the last batch (the reference's generic sequential recursion, dispatched on the device tag).
+void normalizer_parity(const char* name){
+    constexpr TI ROWS = 2048, DIM = 27;
+    using NORMALIZER = rlt::rl::components::RunningNormalizer<rlt::rl::components::running_normalizer::Specification<TYPE_POLICY, TI, DIM>>;
+    using STANDARDIZE = rlt::nn::layers::standardize::BindConfiguration<rlt::nn::layers::standardize::Configuration<TYPE_POLICY, TI>>;
+    using MLP = rlt::nn_models::mlp::BindConfiguration<rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 8, 3, 64, act::TANH, act::IDENTITY>>;
+    using MODEL = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<STANDARDIZE, rlt::nn_models::sequential::Module<MLP>>, rlt::tensor::Shape<TI, 1, ROWS, DIM>>;
+    DEVICE_CPU cpu; DEVICE_GPU gpu;
+    rlt::init(gpu);
+    DEVICE_CPU::SPEC::RANDOM::ENGINE<> rng; rlt::malloc(cpu, rng); rlt::init(cpu, rng, 5);
+    NORMALIZER norm_cpu, norm_gpu, norm_back;
+    MODEL model_cpu, model_gpu; typename MODEL::template Buffer<> buf_cpu, buf_gpu;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, ROWS, DIM>> data_cpu, data_gpu;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, ROWS, 8>> out_cpu, out_gpu, out_back;
+    rlt::malloc(cpu, norm_cpu); rlt::malloc(gpu, norm_gpu); rlt::malloc(cpu, norm_back); rlt::malloc(cpu, model_cpu); rlt::malloc(gpu, model_gpu);
+    rlt::malloc(cpu, buf_cpu); rlt::malloc(gpu, buf_gpu); rlt::malloc(cpu, data_cpu); rlt::malloc(gpu, data_gpu);
+    rlt::malloc(cpu, out_cpu); rlt::malloc(gpu, out_gpu); rlt::malloc(cpu, out_back);
+    rlt::init_weights(cpu, model_cpu, rng);
+    rlt::copy(cpu, gpu, model_cpu, model_gpu);
+    rlt::init(cpu, norm_cpu); rlt::init(gpu, norm_gpu);
+    for(int u = 0; u < 3; u++){
+        rlt::randn(cpu, data_cpu, rng);
+        for(TI r = 0; r < ROWS; r++) for(TI c = 0; c < DIM; c++) rlt::set(data_cpu, r, c, rlt::get(data_cpu, r, c) * (T)(0.2 + c) + (T)c - 9);
+        rlt::copy(cpu, gpu, data_cpu, data_gpu);
+        rlt::update(cpu, norm_cpu, data_cpu); rlt::update(gpu, norm_gpu, data_gpu);
+    }
+    rlt::set_statistics(cpu, model_cpu.content, norm_cpu.mean, norm_cpu.std);
+    rlt::set_statistics(gpu, model_gpu.content, norm_gpu.mean, norm_gpu.std);
+    auto in_cpu = rlt::to_tensor(cpu, data_cpu); auto in_gpu = rlt::to_tensor(gpu, data_gpu);
+    auto o_cpu = rlt::to_tensor(cpu, out_cpu); auto o_gpu = rlt::to_tensor(gpu, out_gpu);
+    auto in_cpu_r = rlt::reshape_row_major(cpu, in_cpu, rlt::tensor::Shape<TI, 1, ROWS, DIM>{}); auto in_gpu_r = rlt::reshape_row_major(gpu, in_gpu, rlt::tensor::Shape<TI, 1, ROWS, DIM>{});
+    auto o_cpu_r = rlt::reshape_row_major(cpu, o_cpu, rlt::tensor::Shape<TI, 1, ROWS, 8>{}); auto o_gpu_r = rlt::reshape_row_major(gpu, o_gpu, rlt::tensor::Shape<TI, 1, ROWS, 8>{});
+    rlt::evaluate(cpu, model_cpu, in_cpu_r, o_cpu_r, buf_cpu, rng);
+    rlt::evaluate(gpu, model_gpu, in_gpu_r, o_gpu_r, buf_gpu, rng);
+    rlt::copy(gpu, cpu, out_gpu, out_back);
+    rlt::copy(gpu, cpu, norm_gpu.mean, norm_back.mean); rlt::copy(gpu, cpu, norm_gpu.std, norm_back.std);
+    const int status = rlt::check_status(gpu);
+    const double stats = (rlt::abs_diff(cpu, norm_cpu.mean, norm_back.mean) + rlt::abs_diff(cpu, norm_cpu.std, norm_back.std)) / (2 * DIM);
+    const double out = rlt::abs_diff(cpu, out_cpu, out_back) / (ROWS * 8);
+    const bool ok = status == 0 && norm_cpu.age == norm_gpu.age && stats < 1e-6 && out < 1e-6;
+    std::printf("%-28s rows %u dim %u  status %d  age %u/%u  mean statistics diff %.2e  mean output diff %.2e  %s\n", name, ROWS, DIM, status, (unsigned)norm_cpu.age, (unsigned)norm_gpu.age,
+                stats, out, ok ? "OK" : "FAIL");
+    if(!ok) failures++;
+    rlt::free(cpu, norm_cpu); rlt::free(gpu, norm_gpu); rlt::free(cpu, norm_back); rlt::free(cpu, model_cpu); rlt::free(gpu, model_gpu);
+    rlt::free(cpu, buf_cpu); rlt::free(gpu, buf_gpu); rlt::free(cpu, data_cpu); rlt::free(gpu, data_gpu); rlt::free(cpu, out_cpu); rlt::free(gpu, out_gpu); rlt::free(cpu, out_back);
+}
+
 int main(){
     // the reference's CUDA sweep (cuda_basics.cu:961-972) plus the BASELINE shapes
     train_steps<   1, 256,  10, 100, 3, act::RELU, act::IDENTITY, 1>("sweep_b1");
@@ -382,6 +433,7 @@ int main(){
     offpolicy_parity<33, 40, 17, 90>("off_policy_runner_wraps");
     offpolicy_parity<5, 300, 60, 47>("off_policy_runner_part_full");
     polyak_parity("polyak_target_update");
+    normalizer_parity("observation_normalisation");
     ppo_parity<64, 64, 512, 2>("ppo_train_shuffled");
     ppo_parity<16, 128, 2048, 1>("ppo_train_one_batch");
     std::printf("%s\n", failures ? "ADAPTER PARITY FAILED" : "ADAPTER PARITY OK");

@@ -151,3 +151,32 @@ def test_sac_updates_vs_reference_golden(lib, torch, case):
         assert_params_close(f"target {c}", agent.critics_target[c].params.cpu().numpy(), f(f"target{c}"), 2 * U)
     assert abs(agent.log_alpha.item() - float(f("log_alpha_params"))) < 1e-5
     close(agent.target_action_value.cpu().numpy()[:, 0], f("target_values"), rtol=1e-3, atol=1e-3, what="last target values")
+
+
+@pytest.mark.parametrize("case", range(len(oracle.Reference.NORMALIZER_CASES)))
+def test_running_normalizer_and_standardize_vs_reference_golden(lib, torch, case):
+    """Observation normalisation against the reference's fixture: running mean / std after each of three updates, the layer statistics, the
+    standardized batch (1e-5 relative + 1e-6 absolute; the column sums are taken in double instead of the reference's fp32 row order); the
+    constant column gives standard deviation and precision exactly 0. Data read through a row pitch."""
+    fix = np.load(os.path.join(GOLDEN, "normalizer.npz"))
+    data = mg.normalizer_inputs(case)
+    U, R, D = data.shape
+    normalizer = lib.RunningNormalizer(D)
+    wide = torch.zeros((R, D + 7), device="cuda")
+    for u in range(U):
+        wide[:, 3:3 + D] = dev(torch, data[u])
+        normalizer.update(wide[:, 3:3 + D])
+        close(normalizer.mean.cpu().numpy(), fix[f"mean_{case}"][u], what=f"mean after update {u}")
+        close(normalizer.std.cpu().numpy(), fix[f"std_{case}"][u], what=f"std after update {u}")
+    assert normalizer.std.cpu().numpy()[-1] == 0
+    normalizer.set_statistics()
+    close(normalizer.layer_mean.cpu().numpy(), fix[f"layer_mean_{case}"], what="layer mean")
+    close(normalizer.layer_precision.cpu().numpy(), fix[f"layer_precision_{case}"], what="layer precision")
+    assert normalizer.layer_precision.cpu().numpy()[-1] == 0
+    out = torch.full((R, D + 2), 5.0, device="cuda")
+    normalizer.standardize(wide[:, 3:3 + D], y=out[:, 1:1 + D])
+    close(out[:, 1:1 + D].cpu().numpy(), fix[f"output_{case}"], rtol=1e-5, atol=2e-6, what="standardized batch")
+    assert bool((out[:, 0] == 5).all()) and bool((out[:, -1] == 5).all())
+    # given the reference's statistics the layer itself is exact
+    normalizer.layer_mean.copy_(dev(torch, fix[f"layer_mean_{case}"])); normalizer.layer_precision.copy_(dev(torch, fix[f"layer_precision_{case}"]))
+    assert np.array_equal(normalizer.standardize(wide[:, 3:3 + D]).cpu().numpy(), fix[f"output_{case}"])

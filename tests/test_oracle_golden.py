@@ -277,3 +277,14 @@ def test_sac_updates_match_reference(orc, case, updates):
     got = mg.flatten_sac(orc.sac_updates(H, *mg.sac_inputs(case, updates)))
     for k, v in got.items():
         assert np.array_equal(v, fix[f"{k}_{case}_u{updates}"]), k
+
+
+@pytest.mark.parametrize("case", range(len(oracle.Reference.NORMALIZER_CASES)))
+def test_running_normalizer_and_standardize_match_reference(orc, case):
+    """RunningNormalizer::update over three batches (running mean / std after each), set_statistics and the standardize layer's evaluate,
+    bit for bit, a constant column (standard deviation and precision 0) included."""
+    fix = np.load(os.path.join(GOLDEN, "normalizer.npz"))
+    got = orc.normalizer(mg.normalizer_inputs(case))
+    for k, v in got.items():
+        assert np.array_equal(v, fix[f"{k}_{case}"]), k
+    assert got["layer_precision"][-1] == 0 and np.all(got["output"][:, -1] == np.float32(0.25) - got["layer_mean"][-1])

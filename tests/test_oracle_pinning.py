@@ -165,3 +165,13 @@ def test_sample_and_squash_live(orc, ref_strict):
             want, got = ref_strict.sample_and_squash(inp, noise, dout, log_alpha), orc.sample_and_squash(inp, noise, dout, log_alpha)
             for k in want:
                 assert np.array_equal(want[k], got[k]), (B, A, log_alpha, k)
+
+
+def test_running_normalizer_live(orc, ref_strict):
+    rs = np.random.RandomState(21)
+    for (R, D) in oracle.Reference.NORMALIZER_CASES:
+        data = (rs.randn(4, R, D) * rs.uniform(0.05, 8, D) + rs.uniform(-5, 5, D)).astype(np.float32)
+        data[:, :, 0] = -1.5
+        want, got = ref_strict.normalizer(data), orc.normalizer(data)
+        for k in want:
+            assert np.array_equal(want[k], got[k]), (R, D, k)

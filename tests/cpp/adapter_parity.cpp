@@ -404,7 +404,8 @@ void normalizer_parity(const char* name){
     const int status = rlt::check_status(gpu);
     const double stats = (rlt::abs_diff(cpu, norm_cpu.mean, norm_back.mean) + rlt::abs_diff(cpu, norm_cpu.std, norm_back.std)) / (2 * DIM);
     const double out = rlt::abs_diff(cpu, out_cpu, out_back) / (ROWS * 8);
-    const bool ok = status == 0 && norm_cpu.age == norm_gpu.age && stats < 1e-6 && out < 1e-6;
+    // columns reach |x| ~ 80 (scale 0.2 .. 26, offset -9 .. 17): 1e-5 absolute is ~1e-6 of the data's scale
+    const bool ok = status == 0 && norm_cpu.age == norm_gpu.age && stats < 1e-5 && out < 1e-5;
     std::printf("%-28s rows %u dim %u  status %d  age %u/%u  mean statistics diff %.2e  mean output diff %.2e  %s\n", name, ROWS, DIM, status, (unsigned)norm_cpu.age, (unsigned)norm_gpu.age,
                 stats, out, ok ? "OK" : "FAIL");
     if(!ok) failures++;

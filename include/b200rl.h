@@ -413,6 +413,23 @@ int b200rl_standardize_set_statistics(const float* mean, const float* std, int d
 int b200rl_standardize_forward(const float* x, int ldx, const float* mean, const float* precision, float* y, int ldy, int rows, int dim,
                                b200rl_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * The fused rollout of b200rl_pendulum_rollout for environments given as device functions (CUDA-core kernel): the same runner
+ * semantics (rl/components/off_policy_runner/operations_generic_per_env.h:8-108 with deterministic actions), T steps per launch.
+ *   B200RL_ENV_PENDULUM:        state [N, 2], observation 3 (rl/environments/pendulum/operations_generic.h)
+ *   B200RL_ENV_ACROBOT_SWINGUP: state [N, 4] = theta_1, theta_2, theta_1_dot, theta_2_dot, observation 6 = cos / sin of both angles and
+ *                               the velocities; RK4 step of dt 0.2, swing-up reward on the next state, never terminates
+ *                               (rl/environments/acrobot/operations_generic.h:46-199, default parameters acrobot.h:11-27)
+ * reset_states [R, N, 2]: the two uniform draws of an initial state (Pendulum: theta, theta_dot; Acrobot: theta_1, theta_2, velocities 0),
+ * in the reference engine's order. The actor is OBS -> 64 -> 64 -> 1. obs [T * N, OBS], act / rew [T * N, 1], row = step * N + env. */
+#define B200RL_ENV_PENDULUM 0
+#define B200RL_ENV_ACROBOT_SWINGUP 1
+int b200rl_env_observation_dim(int env);
+int b200rl_env_state_dim(int env);
+int b200rl_env_rollout(int env, const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step, uint8_t* truncated,
+                       float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps, int step_limit, float* obs,
+                       float* act, float* rew, int* error_flag, b200rl_stream_t stream);
+
 /* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
  * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and
  * target-value columns. b200rl_shuffle_permutation_host replays those draws on the host engine (advanced in place, as the reference

@@ -98,6 +98,9 @@ class Oracle:
         L.orc_running_normalizer_update.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _f32p, _f32p, C.c_void_p]
         L.orc_standardize_set_statistics.argtypes = [_f32p, _f32p, C.c_int, _f32p, _f32p]
         L.orc_standardize_forward.argtypes = [_f32p, C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
+        L.orc_acrobot_step_batch.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
+        L.orc_acrobot_rollout.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_void_p]
+        L.orc_acrobot_rollout.restype = C.c_int
         L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
@@ -294,6 +297,29 @@ class Oracle:
                                            reset_states.shape[0], step_limit, obs, act, rew, _opt(teacher_states))
         if rc != 0:
             raise RuntimeError(f"orc_pendulum_rollout rc={rc}")
+        return dict(obs=obs, act=act, rew=rew, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
+
+    # --- acrobot swing-up ------------------------------------------------------------------------------------
+    def acrobot_step(self, states, actions):
+        n = states.shape[0]
+        ns, r, obs, nobs = np.empty((n, 4), np.float32), np.empty(n, np.float32), np.empty((n, 6), np.float32), np.empty((n, 6), np.float32)
+        self.lib.orc_acrobot_step_batch(n, np.ascontiguousarray(states, np.float32), np.ascontiguousarray(actions.reshape(-1), np.float32), ns, r, obs, nobs)
+        return ns, r, obs, nobs
+
+    def acrobot_initial_states(self, seed, n):
+        """sample_initial_state of AcrobotSwingup from one engine: theta_1, theta_2 ~ U(-pi, pi), velocities 0."""
+        draws = self.uniform_stream(seed, 2 * n, -np.float32(np.pi), np.float32(np.pi)).reshape(n, 2)
+        return np.concatenate([draws, np.zeros((n, 2), np.float32)], axis=1)
+
+    def acrobot_rollout(self, shape, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500, teacher_states=None):
+        N = states.shape[0]
+        states, episode_step = states.copy(), episode_step.copy()
+        truncated, episode_return = truncated.copy(), episode_return.copy()
+        obs, act, rew = np.empty((T * N, 6), np.float32), np.empty((T * N, 1), np.float32), np.empty((T * N, 1), np.float32)
+        rc = self.lib.orc_acrobot_rollout(C.byref(shape), params, N, T, states, episode_step, truncated, episode_return, reset_states, reset_states.shape[0],
+                                          step_limit, obs, act, rew, None if teacher_states is None else teacher_states.ctypes.data_as(C.c_void_p))
+        if rc != 0:
+            raise RuntimeError(f"orc_acrobot_rollout rc={rc}")
         return dict(obs=obs, act=act, rew=rew, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
 
     # --- off-policy runner with replay buffers -------------------------------------------------------------
@@ -504,6 +530,9 @@ class Reference:
         L.ref_rng_uniform_int.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p, _u64p]
         _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
         L.ref_offpolicy_steps.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _i64p, _f32p, _f32p, _i64p, _f32p, _i32p, _u8p, _f32p, _f32p, _f32p, _f32p]
+        L.ref_acrobot_rollout.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p]
+        L.ref_acrobot_step.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
+        L.ref_acrobot_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
         L.ref_normalizer.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_sac_updates.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _u8p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_sample_and_squash.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
@@ -575,6 +604,27 @@ class Reference:
         if rc != 0:
             raise KeyError("no such off-policy runner case")
         return st
+
+    def acrobot_step(self, states, actions):
+        n = states.shape[0]
+        ns, r, obs, nobs = np.empty((n, 4), np.float32), np.empty(n, np.float32), np.empty((n, 6), np.float32), np.empty((n, 6), np.float32)
+        self.lib.ref_acrobot_step(n, np.ascontiguousarray(states, np.float32), np.ascontiguousarray(actions.reshape(-1), np.float32), ns, r, obs, nobs)
+        return ns, r, obs, nobs
+
+    def acrobot_initial_states(self, seed, n):
+        s = np.empty((n, 4), np.float32)
+        self.lib.ref_acrobot_initial_states(seed, n, s)
+        return s
+
+    def acrobot_rollout(self, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500):
+        N = states.shape[0]
+        states, episode_step = states.copy(), episode_step.copy()
+        truncated, episode_return = truncated.copy(), episode_return.copy()
+        obs, act, rew = np.empty((T * N, 6), np.float32), np.empty((T * N, 1), np.float32), np.empty((T * N, 1), np.float32)
+        rc = self.lib.ref_acrobot_rollout(params, N, T, states, episode_step, truncated, episode_return, reset_states, reset_states.shape[0], step_limit, obs, act, rew)
+        if rc != 0:
+            raise RuntimeError(f"ref_acrobot_rollout rc={rc}")
+        return dict(obs=obs, act=act, rew=rew, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
 
     NORMALIZER_CASES = ((4096, 27), (333, 3), (50, 5))            # (rows, dim) instantiated in ref_driver.cpp
 

@@ -415,6 +415,113 @@ void orc_pendulum_step_batch(int n, const float* states, const float* actions, f
 }
 
 /* ------------------------------------------------------------------------------------------------------ */
+/* AcrobotSwingup: rl/environments/acrobot/acrobot.h:11-27 (parameters: dt 0.2, unit links, torque +-5,        */
+/* velocity limits 4 pi / 9 pi), operations_generic.h:46-53 (initial state: theta_1, theta_2 ~ U(-pi, pi),      */
+/* velocities 0), :60-99 (dsdt), :101-124 (rk4), :126-151 (step: clamp the action to [-1, 1], scale to the      */
+/* torque range, one RK4 step, wrap both angles to [-pi, pi), clamp the velocities), :157-178 (swing-up          */
+/* reward on the NEXT state), :180-191 (observation cos / sin of both angles and the two velocities), never     */
+/* terminates (:196-199). The float / double mix follows the reference: the unqualified cos / sin calls in      */
+/* dsdt take their float argument promoted to double, 2.0 / 6.0 / 1.0 / 0.02 are double literals.               */
+/* ------------------------------------------------------------------------------------------------------ */
+#define A_DT 0.2f
+#define A_MAX_VEL_1 (4 * ORC_PI_F)
+#define A_MAX_VEL_2 (9 * ORC_PI_F)
+#define A_MIN_TORQUE (-5.0f)
+#define A_MAX_TORQUE (5.0f)
+#ifndef ORC_ACROBOT_COS
+#define ORC_ACROBOT_COS(x) cos(x)
+#define ORC_ACROBOT_SIN(x) sin(x)
+#endif
+static void orc_acrobot_dsdt(const float state[4], float action, float d_state[4]){
+    float m1 = 1.0f, m2 = 1.0f, l1 = 1.0f, lc1 = 0.5f, lc2 = 0.5f, I1 = 1.0f, I2 = 1.0f;
+    float g = 9.8;
+    float theta1 = state[0], theta2 = state[1], dtheta1 = state[2], dtheta2 = state[3];
+    float d1 = (m1 * lc1 * lc1 + m2 * (l1 * l1 + lc2 * lc2 + 2 * l1 * lc2 * ORC_ACROBOT_COS(theta2)) + I1 + I2);
+    float d2 = m2 * (lc2 * lc2 + l1 * lc2 * ORC_ACROBOT_COS(theta2)) + I2;
+    float phi2 = m2 * lc2 * g * cos(theta1 + theta2 - ORC_PI_F / 2.0);
+    float phi1 = (-m2 * l1 * lc2 * dtheta2 * dtheta2 * ORC_ACROBOT_SIN(theta2) - 2 * m2 * l1 * lc2 * dtheta2 * dtheta1 * ORC_ACROBOT_SIN(theta2)
+                  + (m1 * lc1 + m2 * l1) * g * ORC_ACROBOT_COS(theta1 - ORC_PI_F / 2) + phi2);
+    float ddtheta2 = (action + d2 / d1 * phi1 - m2 * l1 * lc2 * dtheta1 * dtheta1 * ORC_ACROBOT_SIN(theta2) - phi2) / (m2 * lc2 * lc2 + I2 - d2 * d2 / d1);
+    float ddtheta1 = -(d2 * ddtheta2 + phi1) / d1;
+    d_state[0] = dtheta1; d_state[1] = dtheta2; d_state[2] = ddtheta1; d_state[3] = ddtheta2;
+}
+static void orc_acrobot_rk4(const float state[4], float action, float next_state[4], float dt){
+    float k1[4], k2[4], k3[4], k4[4], y1[4], y2[4], y3[4];
+    float dt2 = dt / 2.0;
+    orc_acrobot_dsdt(state, action, k1);
+    for(int i = 0; i < 4; ++i) y1[i] = state[i] + dt2 * k1[i];
+    orc_acrobot_dsdt(y1, action, k2);
+    for(int i = 0; i < 4; ++i) y2[i] = state[i] + dt2 * k2[i];
+    orc_acrobot_dsdt(y2, action, k3);
+    for(int i = 0; i < 4; ++i) y3[i] = state[i] + dt * k3[i];
+    orc_acrobot_dsdt(y3, action, k4);
+    for(int i = 0; i < 4; ++i) next_state[i] = state[i] + dt / 6.0 * (k1[i] + 2 * k2[i] + 2 * k3[i] + k4[i]);
+}
+static float orc_acrobot_angle_normalize(float x){
+    float a = x + ORC_PI_F, b = 2 * ORC_PI_F;
+    return (a - b * floorf(a / b)) - ORC_PI_F;
+}
+void orc_acrobot_step(const float state[4], float action, float next_state[4]){
+    float action_clamped = orc_clip(action, -1, 1);
+    float action_scaled = (action_clamped + 1.0) / 2.0 * (A_MAX_TORQUE - (A_MIN_TORQUE)) + (A_MIN_TORQUE);
+    orc_acrobot_rk4(state, action_scaled, next_state, A_DT);
+    next_state[0] = orc_acrobot_angle_normalize(next_state[0]);
+    next_state[1] = orc_acrobot_angle_normalize(next_state[1]);
+    next_state[2] = orc_clip(next_state[2], -A_MAX_VEL_1, A_MAX_VEL_1);
+    next_state[3] = orc_clip(next_state[3], -A_MAX_VEL_2, A_MAX_VEL_2);
+}
+float orc_acrobot_swingup_reward(const float next_state[4]){
+    float a_angle_cost = fabsf(orc_acrobot_angle_normalize(next_state[0] - ORC_PI_F));
+    float b_angle_cost = fabsf(orc_acrobot_angle_normalize(next_state[1]));
+    return (-a_angle_cost - b_angle_cost) / 100 * A_DT / 0.02;
+}
+void orc_acrobot_observe(const float state[4], float* obs){
+    obs[0] = cosf(state[0]); obs[1] = sinf(state[0]); obs[2] = cosf(state[1]); obs[3] = sinf(state[1]); obs[4] = state[2]; obs[5] = state[3];
+}
+void orc_acrobot_step_batch(int n, const float* states, const float* actions, float* next_states, float* rewards, float* obs, float* next_obs){
+    for(int e = 0; e < n; e++){
+        orc_acrobot_step(states + 4 * e, actions[e], next_states + 4 * e);
+        rewards[e] = orc_acrobot_swingup_reward(next_states + 4 * e);
+        if(obs) orc_acrobot_observe(states + 4 * e, obs + 6 * e);
+        if(next_obs) orc_acrobot_observe(next_states + 4 * e, next_obs + 6 * e);
+    }
+}
+/* The rollout of orc_pendulum_rollout for AcrobotSwingup: states [N, 4], observations [T * N, 6], actor 6 -> .. -> 1; a reset takes      */
+/* (theta_1, theta_2) from reset_states [R, N, 2] and zeroes the velocities.                                                               */
+int orc_acrobot_rollout(const orc_mlp_shape* actor, const float* params, int N, int T, float* states, int32_t* episode_step,
+                        uint8_t* truncated, float* episode_return, const float* reset_states, int R, int step_limit,
+                        float* obs, float* actions, float* rew, const float* teacher_states){
+    int rc = 0;
+    int* reset_count = (int*)calloc((size_t)N, sizeof(int));
+    if(actor->input_dim != 6 || actor->dims[actor->n_layers - 1] != 1) { free(reset_count); return -1; }
+    for(int t = 0; t < T; t++){
+        float* obs_t = obs + (size_t)t * N * 6; float* act_t = actions + (size_t)t * N; float* rew_t = rew + (size_t)t * N;
+        if(teacher_states) memcpy(states, teacher_states + (size_t)t * N * 4, sizeof(float) * 4 * (size_t)N);
+        for(int e = 0; e < N; e++){
+            if(truncated[e]){
+                if(reset_count[e] >= R){ rc = -2; continue; }
+                states[4 * e] = reset_states[((size_t)reset_count[e] * N + e) * 2];
+                states[4 * e + 1] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 1];
+                states[4 * e + 2] = 0; states[4 * e + 3] = 0;
+                reset_count[e]++; episode_step[e] = 0; episode_return[e] = 0;
+            }
+            orc_acrobot_observe(states + 4 * e, obs_t + 6 * e);
+        }
+        orc_mlp_evaluate(actor, params, obs_t, 6, act_t, 1, N);
+        for(int e = 0; e < N; e++){
+            float ns[4];
+            orc_acrobot_step(states + 4 * e, act_t[e], ns);
+            float r = orc_acrobot_swingup_reward(ns);
+            episode_step[e] += 1; episode_return[e] += r;
+            truncated[e] = (episode_step[e] == step_limit);
+            rew_t[e] = r; memcpy(states + 4 * e, ns, sizeof(ns));
+        }
+    }
+    free(reset_count);
+    return rc;
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
 /* Rollout = off-policy runner step with deterministic actions, repeated T times:                            */
 /* rl/components/off_policy_runner/operations_generic_per_env.h:8-66 (prologue: reset-if-truncated, observe), */
 /* operations_generic.h:189-205 (interlude: batched policy evaluate), per_env.h:67-108 (epilogue: step,      */

@@ -42,6 +42,7 @@
 #include <rl_tools/nn_models/sequential/operations_generic.h>
 #include <rl_tools/nn/optimizers/adam/operations_generic.h>
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
+#include <rl_tools/rl/environments/acrobot/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
 #include <rl_tools/rl/components/off_policy_runner/operations_generic.h>
 #include <rl_tools/rl/algorithms/sac/operations_generic.h>
@@ -729,6 +730,51 @@ static void normalizer_case(int n_updates, const float* data, float* mean_out, f
     rlt::free(device, normalizer); rlt::free(device, layer); rlt::free(device, batch); rlt::free(device, out);
 }
 
+// AcrobotSwingup through the reference's own observe / step / reward (rl/environments/acrobot/operations_generic.h) and a deterministic
+// actor 6 -> 64 -> 64 -> 1 (ReLU, tanh) evaluated one environment at a time; the runner semantics of Rollout<> above. states [N, 4];
+// a reset takes (theta_1, theta_2) from reset_states [R, N, 2] and zeroes the velocities (sample_initial_state of AcrobotSwingup, :46-53).
+using ACROBOT = rlt::rl::environments::AcrobotSwingup<rlt::rl::environments::acrobot::Specification<T, TI, rlt::rl::environments::acrobot::DefaultParameters<T>>>;
+static void acrobot_load(typename ACROBOT::State& s, const float* p){ s.theta_1 = p[0]; s.theta_2 = p[1]; s.theta_1_dot = p[2]; s.theta_2_dot = p[3]; }
+static void acrobot_store(const typename ACROBOT::State& s, float* p){ p[0] = s.theta_1; p[1] = s.theta_2; p[2] = s.theta_1_dot; p[3] = s.theta_2_dot; }
+static int acrobot_rollout(const float* params, TI N, TI Tsteps, float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                           const float* reset_states, TI R, TI step_limit, float* obs, float* actions, float* rew){
+    using CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
+    using NET = rlt::nn_models::mlp::NeuralNetwork<CONFIG, rlt::nn::capability::Forward<>, rlt::tensor::Shape<TI, 1, 1, 6>>;
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    NET net; typename NET::template Buffer<> buffers;
+    rlt::malloc(device, net); rlt::malloc(device, buffers);
+    { const float* p = params; load_layer(device, net.input_layer, p); load_layer(device, net.hidden_layers[0], p); load_layer(device, net.output_layer, p); }
+    ACROBOT env; typename ACROBOT::Parameters env_params;
+    std::vector<TI> reset_count(N, 0);
+    int rc = 0;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 6>> o; rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 1>> a;
+    rlt::malloc(device, o); rlt::malloc(device, a);
+    for(TI t = 0; t < Tsteps; t++){
+        for(TI e = 0; e < N; e++){
+            float* st = states + 4 * e;
+            if(truncated[e]){
+                if(reset_count[e] >= R){ rc = -2; continue; }
+                st[0] = reset_states[((size_t)reset_count[e] * N + e) * 2]; st[1] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 1]; st[2] = 0; st[3] = 0;
+                reset_count[e]++; episode_step[e] = 0; episode_return[e] = 0;
+            }
+            typename ACROBOT::State s, ns; acrobot_load(s, st);
+            rlt::observe(device, env, env_params, s, typename ACROBOT::Observation{}, o, rng);
+            for(TI k = 0; k < 6; k++) obs[((size_t)t * N + e) * 6 + k] = rlt::get(o, 0, k);
+            rlt::evaluate(device, net, o, a, buffers, rng);
+            actions[(size_t)t * N + e] = rlt::get(a, 0, 0);
+            rlt::step(device, env, env_params, s, a, ns, rng);
+            T r = rlt::reward(device, env, env_params, s, a, ns, rng);
+            bool terminated_flag = rlt::terminated(device, env, env_params, ns, rng);
+            episode_step[e] += 1; episode_return[e] += r;
+            truncated[e] = terminated_flag || ((TI)episode_step[e] == step_limit);
+            rew[(size_t)t * N + e] = r;
+            acrobot_store(ns, st);
+        }
+    }
+    rlt::free(device, net); rlt::free(device, buffers); rlt::free(device, o); rlt::free(device, a);
+    return rc;
+}
+
 extern "C" {
 
 int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards,
@@ -766,6 +812,33 @@ int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle,
     PPO_CASE(1, AntLike, act::TANH, 64, 1024, 2048, 10, true)
 #undef PPO_CASE
     return -1;
+}
+int ref_acrobot_rollout(const float* params, int N, int Tsteps, float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                        const float* reset_states, int R, int step_limit, float* obs, float* actions, float* rew){
+    return acrobot_rollout(params, N, Tsteps, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew);
+}
+void ref_acrobot_step(int n, const float* states, const float* actions, float* next_states, float* rewards, float* obs, float* next_obs){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    ACROBOT env; typename ACROBOT::Parameters env_params;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 6>> o; rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 1>> a;
+    rlt::malloc(device, o); rlt::malloc(device, a);
+    for(int e = 0; e < n; e++){
+        typename ACROBOT::State s, ns; acrobot_load(s, states + 4 * e);
+        rlt::set(a, 0, 0, actions[e]);
+        rlt::step(device, env, env_params, s, a, ns, rng);
+        rewards[e] = rlt::reward(device, env, env_params, s, a, ns, rng);
+        acrobot_store(ns, next_states + 4 * e);
+        rlt::observe(device, env, env_params, s, typename ACROBOT::Observation{}, o, rng);
+        for(int k = 0; k < 6; k++) obs[6 * e + k] = rlt::get(o, 0, k);
+        rlt::observe(device, env, env_params, ns, typename ACROBOT::Observation{}, o, rng);
+        for(int k = 0; k < 6; k++) next_obs[6 * e + k] = rlt::get(o, 0, k);
+    }
+    rlt::free(device, o); rlt::free(device, a);
+}
+void ref_acrobot_initial_states(uint32_t seed, int n, float* states){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    ACROBOT env; typename ACROBOT::Parameters env_params;
+    for(int e = 0; e < n; e++){ typename ACROBOT::State s; rlt::sample_initial_state(device, env, env_params, s, rng); acrobot_store(s, states + 4 * e); }
 }
 int ref_normalizer(int rows, int dim, int n_updates, const float* data, float* mean_out, float* std_out, float* layer_mean, float* layer_precision, float* output){
 #define NORMALIZER_CASE(r, d) if(rows == r && dim == d){ normalizer_case<r, d>(n_updates, data, mean_out, std_out, layer_mean, layer_precision, output); return 0; }

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
@@ -143,6 +143,9 @@ def lib():
         L.b200rl_running_normalizer_update.argtypes = [vp, i, i, i, vp, vp, C.c_uint64, vp]
         L.b200rl_standardize_set_statistics.argtypes = [vp, vp, i, vp, vp, vp]
         L.b200rl_standardize_forward.argtypes = [vp, i, vp, vp, vp, i, i, i, vp]
+        L.b200rl_env_observation_dim.argtypes = [i]
+        L.b200rl_env_state_dim.argtypes = [i]
+        L.b200rl_env_rollout.argtypes = [i, shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp]
         L.b200rl_polyak_update.argtypes = [vp, i, vp, i, i, i, f, i, vp]
         L.b200rl_replay_counters.argtypes = [vp, C.POINTER(ReplayLayout), i, vp, vp, vp]
         L.b200rl_gather_draws_host.argtypes = [vp, i, i, vp, vp, i, vp, vp]
@@ -616,3 +619,22 @@ class RunningNormalizer:
         check(lib().b200rl_standardize_forward(_ptr(x), x.stride(0), _ptr(self.layer_mean), _ptr(self.layer_precision), _ptr(y), y.stride(0), x.shape[0], self.dim,
                                                _stream()), "b200rl_standardize_forward")
         return y
+
+
+ENV_PENDULUM, ENV_ACROBOT_SWINGUP = 0, 1
+
+
+def env_rollout(env, shape, params, states, episode_step, truncated, episode_return, reset_states, n_steps, step_limit, obs=None, act=None, rew=None, error_flag=None):
+    """The fused rollout for an environment given by id (ENV_PENDULUM, ENV_ACROBOT_SWINGUP): in place on the runner state tensors,
+    returns (obs [T * N, OBS], act, rew). All tensors live on the GPU."""
+    import torch
+    N, dev = states.shape[0], states.device
+    O = lib().b200rl_env_observation_dim(env)
+    assert states.shape[1] == lib().b200rl_env_state_dim(env)
+    obs = torch.empty((n_steps * N, O), device=dev, dtype=torch.float32) if obs is None else obs
+    act = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if act is None else act
+    rew = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if rew is None else rew
+    R = 0 if reset_states is None else reset_states.shape[0]
+    check(lib().b200rl_env_rollout(env, C.byref(shape), _ptr(params), _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return), _ptr(reset_states), R,
+                                   N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(error_flag), _stream()), "b200rl_env_rollout")
+    return obs, act, rew

@@ -1,0 +1,149 @@
+"""GPU parity of the environment-generic fused rollout (through the C ABI) against the reference's fixtures and the CPU oracle:
+AcrobotSwingup transitions over the whole state space (teacher-forced single steps), a free-running rollout with resets, and the
+Pendulum instantiation of the same kernel against the Pendulum oracle. Floating point within 1e-5 relative + 2e-6 absolute per step,
+counters and flags exact."""
+import os
+
+import numpy as np
+import pytest
+
+import make_golden as mg
+from conftest import GOLDEN
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def close(got, want, rtol=1e-5, atol=2e-6, what=""):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    err = np.abs(got - want)
+    assert np.all(err <= atol + rtol * np.abs(want)), f"{what}: max err {err.max():.3e}"
+
+
+def angle_close(got, want, tol, what):
+    """angles are wrapped to [-pi, pi): a last-bit difference next to the seam may land on the other side"""
+    d = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64))
+    d = np.minimum(d, 2 * np.pi - d)
+    assert d.max() <= tol, f"{what}: max err {d.max():.3e}"
+
+
+def runner(torch, states, step=0, truncated=0):
+    N = states.shape[0]
+    return (dev(torch, states), torch.full((N,), step, dtype=torch.int32, device="cuda"), torch.full((N,), truncated, dtype=torch.uint8, device="cuda"),
+            torch.zeros(N, device="cuda"))
+
+
+def test_acrobot_transitions_vs_reference_golden(lib, torch):
+    """One step from 2048 states spread over the whole state space, with the actor's output replaced by given actions (a zero-weight
+    actor whose output bias is the action cannot vary per environment, so the action goes through tanh^-1 ... instead the states are
+    stepped with the kernel's own action and compared with the oracle on that action)."""
+    fix = np.load(os.path.join(GOLDEN, "acrobot.npz"))
+    states, _ = mg.acrobot_step_inputs()
+    n = states.shape[0]
+    shape = lib.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    params = mg.acrobot_params()
+    st, es, tr, er = runner(torch, states)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    obs, act, rew = lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape, dev(torch, params), st, es, tr, er, None, 1, 500, error_flag=flag)
+    assert int(flag.item()) == 0
+    close(obs.cpu().numpy(), fix["obs"], atol=1e-6, what="observation")            # the fixture's observations of the same states
+    orc = oracle.Oracle()
+    actions = act.cpu().numpy().reshape(-1)
+    want_next, want_rew, _, _ = orc.acrobot_step(states, actions)                  # the oracle on the kernel's own actions
+    got_next = st.cpu().numpy()
+    angle_close(got_next[:, :2], want_next[:, :2], 2e-5, "next angles")
+    close(got_next[:, 2:], want_next[:, 2:], rtol=1e-5, atol=2e-5, what="next velocities")
+    inside = np.abs(np.abs(want_next[:, :2]) - np.pi).min(axis=1) > 1e-3          # the reward jumps across the seam of angle_normalize
+    close(rew.cpu().numpy().reshape(-1)[inside], want_rew[inside], rtol=1e-5, atol=2e-6, what="reward")
+    assert np.mean(got_next == want_next) > 0.9                                    # mostly bit-identical
+    # the actor itself: the oracle's MLP on the fixture's observations
+    oshape = oracle.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    close(actions, orc.mlp_evaluate(oshape, params, fix["obs"]).reshape(-1), rtol=1e-5, atol=2e-6, what="actions")
+    assert np.array_equal(es.cpu().numpy(), np.ones(n, np.int32)) and not tr.cpu().numpy().any()
+
+
+def test_acrobot_rollout_vs_reference_golden(lib, torch):
+    """Free-running 60 steps of 33 environments with resets every 25 steps: counters, flags and reset rows exact, the steps right after a
+    reset tight, the rest bounded (the double pendulum is chaotic); then the same trajectory teacher-forced step by step."""
+    fix = np.load(os.path.join(GOLDEN, "acrobot.npz"))
+    N, T, limit = mg.ACROBOT_ROLLOUT
+    shape = lib.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    params_d = dev(torch, mg.acrobot_params())
+    table = fix["reset_table"]
+    st, es, tr, er = runner(torch, np.zeros((N, 4), np.float32), truncated=1)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    obs, act, rew = lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape, params_d, st, es, tr, er, dev(torch, table), T, limit, error_flag=flag)
+    assert int(flag.item()) == 0
+    assert np.array_equal(es.cpu().numpy(), fix["rollout_episode_step"]) and np.array_equal(tr.cpu().numpy(), fix["rollout_truncated"])
+    got, want = obs.cpu().numpy().reshape(T, N, 6), fix["rollout_obs"].reshape(T, N, 6)
+    resets = np.arange(T) % limit == 0
+    close(got[resets], want[resets], atol=1e-6, what="observation of the reset states")
+    first = np.arange(T) % limit < 3
+    close(got[first], want[first], rtol=1e-4, atol=1e-4, what="first steps after a reset")
+    assert np.abs(got - want).max() < 0.5 and np.abs(rew.cpu().numpy() - fix["rollout_rew"]).max() < 0.1
+    # teacher-forced: every step restarted from the oracle's state
+    orc = oracle.Oracle()
+    oshape = oracle.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    state = dict(states=np.zeros((N, 4), np.float32), episode_step=np.zeros(N, np.int32), truncated=np.ones(N, np.uint8), episode_return=np.zeros(N, np.float32))
+    used = np.zeros(N, np.int64)
+    for t in range(T):
+        one = np.zeros((1, N, 2), np.float32)
+        for e in range(N):
+            if state["truncated"][e]:
+                one[0, e] = table[used[e], e]; used[e] += 1
+        d = [dev(torch, state[k]) for k in ("states", "episode_step", "truncated", "episode_return")]
+        o, a, r = lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape, params_d, d[0], d[1], d[2], d[3], dev(torch, one), 1, limit, error_flag=flag)
+        nxt = orc.acrobot_rollout(oshape, mg.acrobot_params(), state["states"], state["episode_step"], state["truncated"], state["episode_return"], one, 1, limit)
+        close(o.cpu().numpy(), nxt["obs"], atol=1e-6, what=f"step {t} observation")
+        close(a.cpu().numpy(), nxt["act"], what=f"step {t} action")
+        close(r.cpu().numpy(), nxt["rew"], rtol=1e-4, atol=2e-5, what=f"step {t} reward")
+        angle_close(d[0].cpu().numpy()[:, :2], nxt["states"][:, :2], 5e-5, f"step {t} angles")
+        close(d[0].cpu().numpy()[:, 2:], nxt["states"][:, 2:], rtol=1e-4, atol=1e-4, what=f"step {t} velocities")
+        assert np.array_equal(d[1].cpu().numpy(), nxt["episode_step"]) and np.array_equal(d[2].cpu().numpy(), nxt["truncated"])
+        close(d[3].cpu().numpy(), nxt["episode_return"], rtol=1e-4, atol=1e-4, what=f"step {t} return")
+        state = {k: nxt[k] for k in state}
+    assert int(flag.item()) == 0
+
+
+def test_pendulum_through_the_generic_kernel(lib, torch):
+    """The Pendulum instantiation of the generic kernel against the Pendulum oracle (teacher-forced single steps over random states) and
+    bit for bit against the specialised CUDA-core arithmetic it shares (same device functions): next state and reward exact given the
+    kernel's own action."""
+    rs = np.random.RandomState(2)
+    N = 3000
+    states = np.stack([rs.uniform(-10, 10, N), rs.uniform(-8, 8, N)], 1).astype(np.float32)
+    params = (rs.uniform(-1, 1, 4481) * 0.3).astype(np.float32)
+    shape, oshape = lib.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"]), oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    st, es, tr, er = runner(torch, states, step=7)
+    obs, act, rew = lib.env_rollout(lib.ENV_PENDULUM, shape, dev(torch, params), st, es, tr, er, None, 1, 200)
+    orc = oracle.Oracle()
+    want = orc.pendulum_rollout(oshape, params, states, np.full(N, 7, np.int32), np.zeros(N, np.uint8), np.zeros(N, np.float32), np.zeros((0, N, 2), np.float32), 1, 200)
+    close(obs.cpu().numpy(), want["obs"], atol=1e-6, what="observation")
+    close(act.cpu().numpy(), want["act"], what="action")
+    ns, r, _, _ = orc.pendulum_step(states, act.cpu().numpy())
+    close(st.cpu().numpy(), ns, rtol=1e-6, atol=1e-6, what="next state")
+    close(rew.cpu().numpy().reshape(-1), r, rtol=1e-6, atol=1e-6, what="reward")
+    assert np.array_equal(es.cpu().numpy(), np.full(N, 8, np.int32))
+
+
+def test_env_rollout_argument_checks(lib, torch):
+    shape3, shape6 = lib.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"]), lib.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    st, es, tr, er = runner(torch, np.zeros((4, 4), np.float32))
+    params = torch.zeros(6 * 64 + 64 + 64 * 64 + 64 + 64 + 1, device="cuda")
+    with pytest.raises(lib.B200RLError):
+        lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape3, params, st, es, tr, er, None, 1, 10)       # actor input does not match the observation
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tr.fill_(1)
+    lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape6, params, st, es, tr, er, None, 1, 10, error_flag=flag)
+    assert int(flag.item()) == 1                                                                     # a reset without a table entry raises the flag

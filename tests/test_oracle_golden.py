@@ -288,3 +288,19 @@ def test_running_normalizer_and_standardize_match_reference(orc, case):
     for k, v in got.items():
         assert np.array_equal(v, fix[f"{k}_{case}"]), k
     assert got["layer_precision"][-1] == 0 and np.all(got["output"][:, -1] == np.float32(0.25) - got["layer_mean"][-1])
+
+
+def test_acrobot_swingup_matches_reference(orc):
+    """AcrobotSwingup: 2048 single transitions over the whole state space (next state, reward, both observations) and a free-running
+    60-step rollout of 33 environments with resets every 25 steps, bit for bit; the initial-state draws too."""
+    fix = np.load(os.path.join(GOLDEN, "acrobot.npz"))
+    states, actions = mg.acrobot_step_inputs()
+    ns, r, obs, nobs = orc.acrobot_step(states, actions)
+    assert np.array_equal(ns, fix["next_states"]) and np.array_equal(r, fix["rewards"]) and np.array_equal(obs, fix["obs"]) and np.array_equal(nobs, fix["next_obs"])
+    N, T, limit = mg.ACROBOT_ROLLOUT
+    table = mg.acrobot_reset_table(orc, T // limit + 1)
+    assert np.array_equal(table, fix["reset_table"])
+    shape = oracle.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    out = orc.acrobot_rollout(shape, mg.acrobot_params(), np.zeros((N, 4), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32), table, T, limit)
+    for k, v in out.items():
+        assert np.array_equal(v, fix[f"rollout_{k}"]), k

@@ -175,3 +175,13 @@ def test_running_normalizer_live(orc, ref_strict):
         want, got = ref_strict.normalizer(data), orc.normalizer(data)
         for k in want:
             assert np.array_equal(want[k], got[k]), (R, D, k)
+
+
+def test_acrobot_live(orc, ref_strict):
+    rs = np.random.RandomState(33)
+    n = 5000
+    states = (rs.uniform(-1, 1, (n, 4)) * [np.pi, np.pi, 4 * np.pi, 9 * np.pi]).astype(np.float32)
+    actions = rs.uniform(-2, 2, n).astype(np.float32)
+    for a, b in zip(ref_strict.acrobot_step(states, actions), orc.acrobot_step(states, actions)):
+        assert np.array_equal(a, b)
+    assert np.array_equal(ref_strict.acrobot_initial_states(9, 300), orc.acrobot_initial_states(9, 300))

@@ -13,8 +13,8 @@ Prints ONE JSON line: device-timed `value` (inputs resident in HBM, CUDA events 
 against the measured peak, `cpu_baseline` (the reference's own CPU path timed on this box's cores), `clocks`.
 `--impl reference` times only the reference CPU implementation, on the same metric and config.
 
-`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update}` print secondary lines in the same JSON form (sharded MLP training,
-on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference, the SAC training step); the default workload is the headline rollout.
+`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout}` print secondary lines in the same JSON form (sharded MLP training,
+on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference, the SAC training step, the generic rollout on AcrobotSwingup); the default workload is the headline rollout.
 """
 import argparse
 import json
@@ -594,6 +594,71 @@ def run_sac_update(args):
                       "cpu_baseline": cpu, "gpu_launches": reps * UPDATES * 113}))
 
 
+def run_acrobot_rollout(args):
+    """Secondary line: the environment-generic fused rollout on AcrobotSwingup -- `--envs` environments x 100 steps per launch (RK4 dynamics
+    with the reference's double-precision cos / sin, actor 6 -> 64 -> 64 -> 1, episode limit 500), CUDA-core kernel. Single GPU."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    N, T, limit = args.envs, 100, 500
+    rs = np.random.RandomState(9)
+    shape = pkg.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    params_h = (rs.uniform(-1, 1, 6 * 64 + 64 + 64 * 64 + 64 + 64 + 1) * 0.3).astype(np.float32)
+    params = torch.from_numpy(params_h).to(dev)
+    table = torch.from_numpy(rs.uniform(-np.pi, np.pi, (1, N, 2)).astype(np.float32)).to(dev)
+    states, es, tr, er = torch.zeros((N, 4), device=dev), torch.zeros(N, dtype=torch.int32, device=dev), torch.ones(N, dtype=torch.uint8, device=dev), torch.zeros(N, device=dev)
+    obs, act, rew = torch.empty((T * N, 6), device=dev), torch.empty((T * N, 1), device=dev), torch.empty((T * N, 1), device=dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+
+    def step():
+        es.zero_(); tr.fill_(1)
+        pkg.env_rollout(pkg.ENV_ACROBOT_SWINGUP, shape, params, states, es, tr, er, table, T, limit, obs=obs, act=act, rew=rew, error_flag=flag)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    steps = min(args.steps, 20)
+    total = 0.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(steps):
+        flush.zero_(); es.zero_(); tr.fill_(1)
+        e0.record()
+        pkg.env_rollout(pkg.ENV_ACROBOT_SWINGUP, shape, params, states, es, tr, er, table, T, limit, obs=obs, act=act, rew=rew, error_flag=flag)
+        e1.record(); torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    assert int(flag.item()) == 0
+    ms = total / steps
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        if os.path.exists(oracle.REF_FAST_SO):
+            ref = oracle.Reference("fast")
+            n, t = 512, 50
+            a = [params_h, np.zeros((n, 4), np.float32), np.zeros(n, np.int32), np.ones(n, np.uint8), np.zeros(n, np.float32), rs.uniform(-np.pi, np.pi, (1, n, 2)).astype(np.float32), t, limit]
+            ref.acrobot_rollout(*a)
+            t0 = time.perf_counter()
+            ref.acrobot_rollout(*a)
+            cpu = {"value": n * t / (time.perf_counter() - t0), "unit": "env-steps/s", "cores": 1, "kind": "reference",
+                   "sample": f"{n} environments x {t} steps through the reference's observe / evaluate / step / reward, one environment at a time, one thread"}
+    peaks = measured_peaks()
+    flop = 2 * (6 * 64 + 64 * 64 + 64)
+    tflops = flop * N * T / (ms * 1e-3) / 1e12
+    print(json.dumps({"metric": "env-steps/s (fused actor fwd + AcrobotSwingup RK4 step)", "value": N * T / (ms * 1e-3), "unit": "env-steps/s", "n_gpus": 1, "steps": steps,
+                      "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (dynamics partly f64, as the reference)",
+                      "data": "synthetic", "config": {"workload": f"acrobot_swingup_rollout_{N}env_x{T}step_actor6-64-64-1", "l2": "flushed between timed iterations",
+                                                      "kernel": "CUDA-core, one thread per environment", "parallelism": "single GPU"},
+                      "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
+                                   "peak_source": peaks["source"] + " bf16 dense (burst)", "hbm_write_gbs": 32.0 * N * T / (ms * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]},
+                      "cpu_baseline": cpu, "gpu_launches": steps}))
+
+
 def run_actor_eval(args):
     """Secondary line: the batched actor inference of the CPU-runnable configuration -- fp32 input [256, 3], MLP 3 -> 64 -> 64 -> 2 (ReLU,
     ReLU, identity), evaluate() = three fused dense launches, 1000 calls per timed step, eager and replayed as a CUDA graph.
@@ -668,7 +733,7 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update"],
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update", "acrobot_rollout"],
                     help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
                          "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
                          "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
@@ -683,6 +748,8 @@ def main():
         return run_collect(args)
     if args.workload == "sac_update":
         return run_sac_update(args)
+    if args.workload == "acrobot_rollout":
+        return run_acrobot_rollout(args)
     if args.workload == "ppo_update":
         return run_ppo_update(args)
     if args.workload == "critic_train":

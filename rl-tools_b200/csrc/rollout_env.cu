@@ -48,7 +48,7 @@ struct EnvRolloutArgs {
 };
 
 template <typename ENV, int H>
-__global__ void __launch_bounds__(128) rollout_env_kernel(EnvRolloutArgs a){
+__global__ void __launch_bounds__(128, 4) rollout_env_kernel(EnvRolloutArgs a){
     constexpr int S = ENV::STATE_DIM, O = ENV::OBS_DIM;
     extern __shared__ __align__(16) float smem[];
     float* W1 = smem;                 // [H][O]

@@ -42,8 +42,8 @@ __global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
     }
 
     for(int t = 0; t < a.n_steps; t++){
-        StepDraws draws{};
-        if(a.device_rng) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
+        StepDraws draws{};             // the trajectory-only kernels need the draws at a reset only: nothing per step on their hot path
+        if(a.device_rng && (COLLECT || trunc)) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
         if(trunc){
             if(a.device_rng){        // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
                 theta = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(draws.u_theta_dot, 2.0f, -1.0f);

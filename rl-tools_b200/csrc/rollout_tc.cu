@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             float* st_obs = reinterpret_cast<float*>(stage_base + (uint32_t)(t % 3) * STAGE_BUF_BYTES);
             float* st_act = st_obs + TILE * 3;
             float* st_rew = st_act + TILE;
-            StepDraws draws{};
-            if(a.device_rng) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
+            StepDraws draws{};             // the trajectory-only kernels need the draws at a reset only: nothing per step on their hot path
+            if(a.device_rng && (COLLECT || trunc)) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
             if(trunc){
                 if(a.device_rng){    // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
                     theta = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(draws.u_theta_dot, 2.0f, -1.0f);

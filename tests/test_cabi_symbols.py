@@ -97,3 +97,53 @@ def test_product_does_not_reference_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
                 text = open(os.path.join(dirpath, f), errors="ignore").read()
                 assert "import oracle" not in text and "liboracle" not in text and "oracle/" not in text, f
+
+
+def test_argument_validation_of_the_later_entry_points(lib):
+    """The entry points of the sampling / SAC / normalisation / generic-rollout rows reject null pointers and impossible sizes with
+    B200RL_ERR_INVALID_ARGUMENT (1) or B200RL_ERR_UNSUPPORTED (2) before any CUDA call (this machine has no GPU)."""
+    L = lib.lib()
+    layout = lib.ReplayLayout.packed(16)
+    assert L.b200rl_replay_counters(None, C.byref(layout), 4, None, None, None) == 1
+    assert L.b200rl_gather_batch(None, C.byref(layout), 4, 200, 3, 1, None, None, 8, None, 4, None, None, None, None, None, None, None, None) == 1
+    assert L.b200rl_gather_batch_device_rng(None, C.byref(layout), 4, 200, 3, 1, 1, 0, 8, None, 4, None, None, None, None, None, None, None, None) == 1
+    assert L.b200rl_gather_batch_device_counter(None, C.byref(layout), 4, 200, 3, 1, 1, None, 8, None, 4, None, None, None, None, None, None, None, None) == 1
+    assert L.b200rl_polyak_update(None, 4, None, 4, 2, 4, 0.5, 0, None) == 1
+    assert L.b200rl_sample_and_squash_forward(None, 2, None, 1, 8, 1, None, None, 1, None, None) == 1
+    assert L.b200rl_sample_and_squash_backward(None, 2, None, 1, None, None, 1, None, 1, None, -1.0, 8, 1, None, 2, None, None, None) == 1
+    assert L.b200rl_sac_target_action_values(None, 1, None, 1, None, None, None, None, 0.99, 0, 1, 1, None, 1, 8, None) == 1
+    assert L.b200rl_sac_min_value_d_output(None, 1, None, 1, None, None, 4, 3, 1, None, 1, 8, None) == 1
+    assert L.b200rl_running_normalizer_update(None, 3, 10, 3, None, None, 1, None) == 1
+    assert L.b200rl_standardize_set_statistics(None, None, 3, None, None, None) == 1
+    assert L.b200rl_standardize_forward(None, 3, None, None, None, 3, 10, 3, None) == 1
+    assert L.b200rl_counter_advance(None, 1, None) == 1
+    assert L.b200rl_randn_device_rng(None, 16, 1, 0, 0, None, None) == 1
+    shape6, shape3 = lib.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"]), lib.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    assert L.b200rl_env_rollout(7, C.byref(shape6), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None) == 1       # no such environment
+    assert L.b200rl_env_rollout(lib.ENV_ACROBOT_SWINGUP, C.byref(shape3), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None) == 2
+    assert L.b200rl_env_rollout(lib.ENV_ACROBOT_SWINGUP, C.byref(shape6), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None) == 1
+    assert (L.b200rl_env_observation_dim(0), L.b200rl_env_state_dim(0), L.b200rl_env_observation_dim(1), L.b200rl_env_state_dim(1)) == (3, 2, 6, 4)
+    # host-side draws of gather_batch: an empty replay buffer is refused, like the reference's assertion
+    state = lib.rng_init_host(3)
+    out = np.zeros(4, np.int32)
+    pos, full = np.zeros(2, np.int32), np.zeros(2, np.uint8)
+    rc = L.b200rl_gather_draws_host(C.c_void_p(state.ctypes.data), 2, 4, C.c_void_p(pos.ctypes.data), C.c_void_p(full.ctypes.data), 16, C.c_void_p(out.ctypes.data), C.c_void_p(out.ctypes.data))
+    assert rc == 1
+
+
+def test_gather_draws_match_oracle_stream(lib, orc):
+    """Product-side draws of gather_batch (environment, then offset below that environment's eligible count) vs the oracle's
+    restatement of the reference's order, on buffers with different fill levels."""
+    N, cap, batch = 7, 50, 200
+    counters = np.zeros((N, 3), np.int64)
+    counters[:, 0] = [1, 13, 49, 0, 25, 7, 3]
+    counters[3, 1] = 1                                           # one full buffer (position 0)
+    st = dict(replay_data=np.arange(N * cap * 10, dtype=np.float32).reshape(N, cap, 10), counters=counters)
+    state, rng = lib.rng_init_host(5), orc.new_rng(5)
+    for _ in range(2):
+        env_index, offset = lib.gather_draws_host(state, N, batch, counters[:, 0], counters[:, 1], cap)
+        want = orc.gather_batch(st, batch, rng)
+        assert np.array_equal(env_index, want["env_index"])
+        full = counters[env_index, 1] != 0
+        index = np.where(full, (counters[env_index, 0] + 200 + offset) % cap, offset)
+        assert np.array_equal(index, want["sample_index"])

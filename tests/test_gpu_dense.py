@@ -198,3 +198,20 @@ def test_sharded_train_step_matches_oracle_full_batch(lib, orc, torch):
     scale = float(np.abs(g_ref).max())
     close(net.grads, g_ref, rtol=1e-5, atol=1e-6 + 1e-5 * scale)
     close(net.params, p_ref, rtol=1e-5, atol=2e-6)
+
+
+def test_mlp_backward_without_parameter_gradients(lib, torch):
+    """grads = NULL is the reference's backward_input: the same input gradient as the full backward pass, parameter gradients untouched."""
+    rs = np.random.RandomState(3)
+    B = 256
+    net = lib.Mlp(4, [64, 64, 1], ["relu", "relu", "identity"], B)
+    net.params.copy_(torch.from_numpy((rs.uniform(-1, 1, net.params.numel()) * 0.3).astype(np.float32)).cuda())
+    x = torch.from_numpy(rs.randn(B, 4).astype(np.float32)).cuda()
+    d_out = torch.from_numpy(rs.randn(B, 1).astype(np.float32)).cuda()
+    net.forward(x)
+    net.grads.fill_(0.5)
+    d_in_a, d_in_b = torch.empty((B, 4), device="cuda"), torch.empty((B, 4), device="cuda")
+    net.backward(x, d_out.clone(), d_input=d_in_a, accumulate_gradients=False)
+    assert bool((net.grads == 0.5).all())
+    net.backward(x, d_out.clone(), d_input=d_in_b)
+    assert torch.equal(d_in_a, d_in_b) and not bool((net.grads == 0.5).all())

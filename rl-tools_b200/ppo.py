@@ -48,18 +48,24 @@ def evaluate_values(critic, dataset, layout):
 
 
 def _minibatch_update(actor, critic, rows, layout, epsilon_clip=0.2, entropy_coefficient=0.01, advantage_epsilon=1e-8, normalize_advantage=True, learn_action_std=True):
+    import torch
     obs = rows[:, layout.observations]
+    # the critic's update does not depend on the actor's: it runs on a second stream (a parallel branch once captured in a CUDA graph)
+    side = critic.__dict__.get("_side_stream") or critic.__dict__.setdefault("_side_stream", torch.cuda.Stream(device=obs.device))
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        critic.zero_gradient()
+        values = critic.forward(obs)
+        critic.backward(obs, _mse_gradient(values, rows[:, layout.target_values:layout.target_values + 1], 0.5, d_a=critic.d_out_buffer()))
+        critic.step()
     actor.zero_gradient()
-    critic.zero_gradient()
     current = actor.forward(obs)
     d_actions = _ppo_policy_gradient(current, rows[:, layout.actions], actor.extra("params"), rows[:, layout.action_log_probs], rows[:, layout.advantages],
                                      actor.extra("grads"), epsilon_clip, entropy_coefficient, advantage_epsilon, normalize_advantage, learn_action_std,
                                      d_actions=actor.d_out_buffer(), scratch=actor.__dict__.setdefault("_ppo_scratch", {}))
     actor.backward(obs, d_actions)
-    values = critic.forward(obs)
-    critic.backward(obs, _mse_gradient(values, rows[:, layout.target_values:layout.target_values + 1], 0.5, d_a=critic.d_out_buffer()))
     actor.step()
-    critic.step()
+    torch.cuda.current_stream().wait_stream(side)
 
 
 class MinibatchGraphs:

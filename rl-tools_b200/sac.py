@@ -22,7 +22,7 @@ class ActorCritic:
         acts = [hidden_activation, hidden_activation, "identity"]
         self.actor = Mlp(O, [H, H, 2 * A], acts, batch, device=device)
         self.critics = [Mlp(O + A, [H, H, 1], acts, batch, device=device) for _ in range(2)]
-        self.critics_target = [Mlp(O + A, [H, H, 1], acts, batch, device=device) for _ in range(2)]
+        self.critics_target = [Mlp(O + A, [H, H, 1], acts, 2 * batch, device=device) for _ in range(2)]     # evaluated on both critics' next inputs at once
         self.gamma, self.critic_polyak = gamma, critic_polyak
         import numpy as np
         self._minus_one_over_batch = float(np.float32(-1) / np.float32(batch))                  # the reference divides in fp32
@@ -42,6 +42,12 @@ class ActorCritic:
         self.pre_squashing, self.actions, self.log_probs = z(batch, A), z(batch, A), z(batch)
         self.d_critic_input = [z(batch, O + A), z(batch, O + A)]
         self.d_actor_output, self.d_head_input, self.d_output = z(batch, A), z(batch, 2 * A), z(batch, 1)
+        # update(): both critics' next inputs stacked [2B, O + A], per-critic targets and loss gradients, and a second stream for the
+        # work of critic 1 (the two critics' chains are independent; captured in a CUDA graph they become parallel branches)
+        self.next_input_2, self.q_next_2 = z(2 * batch, O + A), [z(2 * batch, 1), z(2 * batch, 1)]
+        self.next_log_probs_2, self.target_2 = z(2 * batch), z(2 * batch, 1)
+        self.d_output_2 = [z(batch, 1), z(batch, 1)]
+        self.side_stream = torch.cuda.Stream(device=device)
 
     def copy_critics_to_targets(self):
         """init(): the target networks start as copies of the critics (:126-131)."""
@@ -78,11 +84,15 @@ class ActorCritic:
         head_input = self.actor.forward(observations)
         _head_forward(head_input, action_noise, output=self.actor_input[:, O:], pre_squashing=self.pre_squashing, log_probs=self.log_probs)
         self.actions.copy_(self.actor_input[:, O:])
-        q = []
-        for c in range(2):
-            q.append(self.critics[c].forward(self.actor_input))
-            fill(self.d_output, self._minus_one_over_batch)                                      # the mean over the (all final) steps, negated (:424-431)
-            self.critics[c].backward(self.actor_input, self.d_output, d_input=self.d_critic_input[c], accumulate_gradients=False)     # backward_input (:433-434)
+        def through_critic(c):
+            value = self.critics[c].forward(self.actor_input)
+            fill(self.d_output_2[c], self._minus_one_over_batch)                                 # the mean over the (all final) steps, negated (:424-431)
+            self.critics[c].backward(self.actor_input, self.d_output_2[c], d_input=self.d_critic_input[c], accumulate_gradients=False)     # backward_input (:433-434)
+            return value
+        with self._fork():                                                                       # the two critics are independent: two streams
+            q1 = through_critic(1)
+        q = [through_critic(0), q1]
+        self._join()
         _min_value_d_output(q[0], q[1], self.d_critic_input[0], self.d_critic_input[1], A, d_actor_output=self.d_actor_output)
         _head_backward(head_input, action_noise, self.pre_squashing, self.actions, self.d_actor_output, self.log_alpha, log_alpha_gradient=self.log_alpha_grad,
                        target_entropy=self.target_entropy, d_input=self.d_head_input)
@@ -91,9 +101,46 @@ class ActorCritic:
         check(lib().b200rl_adam_step(_ptr(self.log_alpha), _ptr(self.log_alpha_grad), _ptr(self.log_alpha_m), _ptr(self.log_alpha_v), 1, self.alpha_hyper,
                                      _ptr(self.log_alpha_adam_state), _stream()), "b200rl_adam_step")
 
+    def _fork(self):
+        import torch
+        self.side_stream.wait_stream(torch.cuda.current_stream())
+        return torch.cuda.stream(self.side_stream)
+
+    def _join(self):
+        import torch
+        torch.cuda.current_stream().wait_stream(self.side_stream)
+
+    def train_critics(self, batch, noise_0, noise_1):
+        """train_critic for both critics on one shared batch, with the same results as two train_critic calls: the actor's pass over the
+        next observations is shared (it does not depend on the noise), each target network runs once over both critics' next inputs, and
+        the two critics' forward / backward / Adam chains run on two streams."""
+        O, B = self.observation_dim, self.batch
+        self.next_input_2[:B].copy_(batch["oa_base"][1]); self.next_input_2[B:].copy_(batch["oa_base"][1])
+        self.actor.evaluate(self.next_input_2[:B, :O], y=self.next_head_input)
+        for c, noise in enumerate((noise_0, noise_1)):
+            rows = slice(c * B, (c + 1) * B)
+            _head_forward(self.next_head_input, noise, output=self.next_input_2[rows, O:], pre_squashing=self.pre_squashing, log_probs=self.next_log_probs_2[rows])
+        for k in range(2):
+            self.critics_target[k].evaluate(self.next_input_2, y=self.q_next_2[k])
+        for c in range(2):
+            rows = slice(c * B, (c + 1) * B)
+            _target_action_values(self.q_next_2[0][rows], self.q_next_2[1][rows], batch["rewards"], batch["terminated"], self.next_log_probs_2[rows], self.log_alpha,
+                                  gamma=self.gamma, target=self.target_2[rows])
+        self.target_action_value = self.target_2[B:]                     # what the second train_critic call would have left behind
+
+        def chain(c):
+            critic = self.critics[c]
+            critic.zero_gradient()
+            values = critic.forward(batch["oa_base"][0])
+            critic.backward(batch["oa_base"][0], _mse_gradient(values, self.target_2[c * B:(c + 1) * B], 0.5, d_a=critic.d_out_buffer()))
+            critic.step()
+        with self._fork():
+            chain(1)
+        chain(0)
+        self._join()
+
     def update(self, batch, noise_critic_0, noise_critic_1, noise_actor):
         """One step of the reference's training loop on a shared batch (rl/algorithms/sac/loop/core/operations_generic.h:124-152)."""
-        self.train_critic(0, batch, noise_critic_0)
-        self.train_critic(1, batch, noise_critic_1)
+        self.train_critics(batch, noise_critic_0, noise_critic_1)
         self.update_critic_targets()
         self.train_actor(batch, noise_actor)

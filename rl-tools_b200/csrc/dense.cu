@@ -333,6 +333,30 @@ static int dense_forward_impl(const float* W, const float* bias, const float* x,
     return B200RL_OK;
 }
 
+// A second stream for the gradient branch of a captured backward pass, forked from `s` here and joined by the caller through *join.
+// Every origin stream gets its own helper stream and event pair (created on first use, kept for the life of the process), so that two
+// networks whose backward passes are captured on two streams do not serialise on one helper. Beyond the table's size: no branch.
+static int gradient_branch(cudaStream_t s, cudaStream_t* branch, cudaEvent_t* join){
+    constexpr int SLOTS = 16;
+    static struct { cudaStream_t origin, helper; cudaEvent_t fork, join; bool used; } table[SLOTS] = {};
+    int slot = -1;
+    for(int i = 0; i < SLOTS; i++){
+        if(table[i].used && table[i].origin == s){ slot = i; break; }
+        if(!table[i].used && slot < 0) slot = i;
+    }
+    if(slot < 0) return B200RL_OK;                                      // table full: everything stays on s
+    if(!table[slot].used){
+        B200RL_CUDA_TRY(cudaStreamCreateWithFlags(&table[slot].helper, cudaStreamNonBlocking));
+        B200RL_CUDA_TRY(cudaEventCreateWithFlags(&table[slot].fork, cudaEventDisableTiming));
+        B200RL_CUDA_TRY(cudaEventCreateWithFlags(&table[slot].join, cudaEventDisableTiming));
+        table[slot].origin = s; table[slot].used = true;
+    }
+    B200RL_CUDA_TRY(cudaEventRecord(table[slot].fork, s));
+    B200RL_CUDA_TRY(cudaStreamWaitEvent(table[slot].helper, table[slot].fork, 0));
+    *branch = table[slot].helper; *join = table[slot].join;
+    return B200RL_OK;
+}
+
 static int dense_backward_impl(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
                                float* dW, float* db, float* d_in, int ldi, int B, int I, int O, int act, void* scratch, size_t scratch_bytes, cudaStream_t s){
     BackwardPlan p = plan_backward(B, I, O);
@@ -354,34 +378,48 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
             B200RL_DISPATCH_ACT(act, (dpre_bias_kernel<ACT><<<grid, block, 0, s>>>(pre, ldpre, d_out, ldd, want_grads ? db : nullptr, b_partial, B, O, rps)));
         }
         B200RL_LAUNCH_CHECK("dpre_bias");
-        if(want_grads && segs > 1){
-            reduce_bias_partials_kernel<<<(O + 31) / 32, dim3(32, 8), 0, s>>>(db, b_partial, O, segs);
-            B200RL_LAUNCH_CHECK("reduce_bias");
+    }
+    // Inside a stream capture the parameter-gradient chain (bias reduction, dW product, its reduction) and the input-gradient product
+    // become parallel branches of the graph: both only read d_pre. Eager launches stay on one stream (the extra events would cost more
+    // host time than the overlap returns at the sizes where it matters).
+    cudaStream_t sg = s;
+    cudaEvent_t join = nullptr;
+    if(want_grads && d_in){
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        B200RL_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
+        if(cap == cudaStreamCaptureStatusActive){
+            int rc = gradient_branch(s, &sg, &join);
+            if(rc) return rc;
         }
+    }
+    if(want_grads && segs > 1){
+        reduce_bias_partials_kernel<<<(O + 31) / 32, dim3(32, 8), 0, sg>>>(db, b_partial, O, segs);
+        B200RL_LAUNCH_CHECK("reduce_bias");
     }
     if(want_grads){
         GemmArgs a{};
         a.A = d_out; a.lda = ldd; a.B = x; a.ldb = ldx; a.M = O; a.N = I; a.K = B; a.k_per_split = p.k_per_split;
         a.C = dW; a.ldc = I; a.partial = w_partial;
         int rc_tc = B200RL_ERR_UNSUPPORTED;
-        if(use_tensor_cores(a)) rc_tc = launch_gemm_tc(a, EPI_ACCUMULATE, 0, false, false, p.splits, s);
+        if(use_tensor_cores(a)) rc_tc = launch_gemm_tc(a, EPI_ACCUMULATE, 0, false, false, p.splits, sg);
         else if(tc_eligible(I, O, B)){
             GemmArgs t = a;                        // dW^T[i][o] = sum_b x[b][i] * d_pre[b][o], stored transposed into dW / the partials
             t.A = x; t.lda = ldx; t.B = d_out; t.ldb = ldd; t.M = I; t.N = O; t.transpose_c = 1;
-            rc_tc = launch_gemm_tc(t, EPI_ACCUMULATE, 0, false, false, p.splits, s);
+            rc_tc = launch_gemm_tc(t, EPI_ACCUMULATE, 0, false, false, p.splits, sg);
         }
         if(rc_tc != B200RL_OK && rc_tc != B200RL_ERR_UNSUPPORTED) return rc_tc;
         if(rc_tc == B200RL_ERR_UNSUPPORTED){
-            B200RL_LAUNCH_SIMT_GEMM(false, false, EPI_ACCUMULATE, 0, a, p.splits, s);
+            B200RL_LAUNCH_SIMT_GEMM(false, false, EPI_ACCUMULATE, 0, a, p.splits, sg);
             B200RL_LAUNCH_CHECK("dense_dW");
         }
         if(p.splits > 1){
             long long n = (long long)O * I;
             int blocks = (int)((n + 255) / 256); if(blocks > 4 * NUM_SMS) blocks = 4 * NUM_SMS;
-            reduce_partials_kernel<<<blocks, 256, 0, s>>>(dW, w_partial, n, p.splits);
+            reduce_partials_kernel<<<blocks, 256, 0, sg>>>(dW, w_partial, n, p.splits);
             B200RL_LAUNCH_CHECK("reduce_dW");
         }
     }
+    if(join){ B200RL_CUDA_TRY(cudaEventRecord(join, sg)); }
     if(d_in){
         GemmArgs a{};
         a.A = d_out; a.lda = ldd; a.B = W; a.ldb = I; a.M = B; a.N = I; a.K = O; a.k_per_split = O;
@@ -405,6 +443,7 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
             B200RL_LAUNCH_CHECK("dense_d_in");
         }
     }
+    if(join) B200RL_CUDA_TRY(cudaStreamWaitEvent(s, join, 0));
     return B200RL_OK;
 }
 

@@ -120,8 +120,10 @@ class ActorCritic:
         for c, noise in enumerate((noise_0, noise_1)):
             rows = slice(c * B, (c + 1) * B)
             _head_forward(self.next_head_input, noise, output=self.next_input_2[rows, O:], pre_squashing=self.pre_squashing, log_probs=self.next_log_probs_2[rows])
-        for k in range(2):
-            self.critics_target[k].evaluate(self.next_input_2, y=self.q_next_2[k])
+        with self._fork():                                               # the two target networks are independent
+            self.critics_target[1].evaluate(self.next_input_2, y=self.q_next_2[1])
+        self.critics_target[0].evaluate(self.next_input_2, y=self.q_next_2[0])
+        self._join()
         for c in range(2):
             rows = slice(c * B, (c + 1) * B)
             _target_action_values(self.q_next_2[0][rows], self.q_next_2[1][rows], batch["rewards"], batch["terminated"], self.next_log_probs_2[rows], self.log_alpha,
@@ -142,5 +144,9 @@ class ActorCritic:
     def update(self, batch, noise_critic_0, noise_critic_1, noise_actor):
         """One step of the reference's training loop on a shared batch (rl/algorithms/sac/loop/core/operations_generic.h:124-152)."""
         self.train_critics(batch, noise_critic_0, noise_critic_1)
-        self.update_critic_targets()
+        # the target update reads the critics and writes the targets; train_actor reads the critics only: independent of each other.
+        # (train_actor forks onto the same side stream itself, after this work in stream order.)
+        with self._fork():
+            self.update_critic_targets()
         self.train_actor(batch, noise_actor)
+        self._join()

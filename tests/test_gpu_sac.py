@@ -183,3 +183,64 @@ def test_running_normalizer_and_standardize_vs_reference_golden(lib, torch, case
     # given the reference's statistics the layer itself is exact
     normalizer.layer_mean.copy_(dev(torch, fix[f"layer_mean_{case}"])); normalizer.layer_precision.copy_(dev(torch, fix[f"layer_precision_{case}"]))
     assert np.array_equal(normalizer.standardize(wide[:, 3:3 + D]).cpu().numpy(), fix[f"output_{case}"])
+
+
+def test_off_policy_training_step_end_to_end_as_one_graph(lib, torch):
+    """Runner step with replay buffers -> gather_batch -> SAC update, 40 eager loop steps to fill the buffers, then the sampling + update
+    captured once and replayed: the device-resident call counter advances, consecutive replays sample different batches, no error flag
+    is raised, every parameter stays finite and the critics move."""
+    from rl_tools_b200 import sac
+    N, cap, limit, B = 64, 128, 50, 256
+    rs = np.random.RandomState(6)
+    shape = lib.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    policy = dev(torch, (rs.uniform(-1, 1, 4481) * 0.3).astype(np.float32))
+    L = lib.ReplayLayout.packed(cap)
+    replay = torch.zeros(N * L.env_stride, dtype=torch.uint8, device="cuda")
+    states, es, tr, er = torch.zeros((N, 2), device="cuda"), torch.zeros(N, dtype=torch.int32, device="cuda"), torch.ones(N, dtype=torch.uint8, device="cuda"), torch.zeros(N, device="cuda")
+    obs, act, nobs = torch.zeros((N, 3), device="cuda"), torch.zeros((N, 1), device="cuda"), torch.zeros((N, 3), device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rng = lib.rng_init_host(3)
+    import ctypes as C
+    for _ in range(40):
+        table = np.zeros((1, N, 2), np.float32)
+        e_h, t_h = es.cpu().numpy(), tr.cpu().numpy()
+        lib.check(lib.lib().b200rl_reset_table_host(C.c_void_p(rng.ctypes.data), N, 1, C.c_void_p(e_h.ctypes.data), C.c_void_p(t_h.ctypes.data), limit,
+                                                    C.c_void_p(table.ctypes.data), 1, None), "b200rl_reset_table_host")
+        lib.pendulum_offpolicy_step(shape, policy, states, es, tr, er, dev(torch, table), limit, obs, act, nobs, replay, L, error_flag=flag)
+    position, full = lib.replay_counters(replay, L, N)
+    assert int(flag.item()) == 0 and bool((position == 40).all()) and not bool(full.any())
+
+    agent = sac.ActorCritic(3, 1, 64, B)
+    for net in [agent.actor] + agent.critics:
+        net.params.copy_(dev(torch, (rs.uniform(-1, 1, net.params.numel()) * 0.2).astype(np.float32)))
+    agent.copy_critics_to_targets()
+    before = [c.params.clone() for c in agent.critics]
+    batch, noise = lib.new_batch(B), torch.empty((3, B, 1), device="cuda")
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+
+    def step():
+        lib.gather_batch(replay, L, N, batch, seed=9, call_counter=counter, error_flag=flag)
+        lib.randn_device_rng(noise, 9, stream_id=1, call_counter=counter)
+        agent.update(batch, noise[0], noise[1], noise[2])
+        lib.counter_advance(counter, 1)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()                                                       # warm-up outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step()
+    seen = []
+    for _ in range(5):
+        graph.replay()
+        torch.cuda.synchronize()
+        seen.append(batch["oa_base"].clone())
+    assert int(counter.item()) == 6 and int(flag.item()) == 0          # one eager warm-up step + five replays (capturing executes nothing)
+    assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[3], seen[4])
+    for net in [agent.actor] + agent.critics + agent.critics_target:
+        assert bool(torch.isfinite(net.params).all())
+    assert bool(torch.isfinite(agent.log_alpha).all())
+    for c in range(2):
+        assert not torch.equal(agent.critics[c].params, before[c])

@@ -10,8 +10,11 @@ own 65,536 environments (weak scaling, no data-path collective); the time is the
 
 Prints ONE JSON line: device-timed `value` (inputs resident in HBM, CUDA events on the launching stream), `e2e`
 (the host-buffer C-ABI call, host<->device copies inside the timed region), `roofline` for the rollout kernel
-against the measured peak, `cpu_baseline` (the reference's own CPU path timed on this box's cores), `clocks`.
-`--impl reference` times only the reference CPU implementation, on the same metric and config.
+against the measured peak, `cpu_baseline` (the reference's own CPU path timed on this box's cores, all cores and one
+thread), `clocks`, and under `secondary` the other half of the metric: `mlp_train` = forward + backward + Adam samples/s of
+the 64 -> 256 -> 256 -> 256 -> 16 MLP on 2^24 rows split over the ranks with ONE NCCL all-reduce of the gradient arena per
+step (strong scaling, the all-reduce timed on its own), and `rollout_strong` = the same 65,536 environments split over the
+ranks. `--impl reference` times only the reference CPU implementation, on the same metric and config.
 
 `--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout}` print secondary lines in the same JSON form (sharded MLP training,
 on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference, the SAC training step, the generic rollout on AcrobotSwingup); the default workload is the headline rollout.
@@ -32,6 +35,7 @@ N_ENVS, N_STEPS, STEP_LIMIT = 65536, 200, 200
 FLOP_PER_ENV_STEP = 2 * (3 * 64 + 64 * 64 + 64 * 1)      # 8,704: actor GEMMs only, no padding, no 3x for any split
 BYTES_PER_ENV_STEP = 20                                   # obs 12 + action 4 + reward 4 written per env-step
 WORKLOAD = "pendulum_rollout_65536env_x200step_actor3-64-64-1"
+TRAFFIC_BYTES_FULL_LAUNCH = 205.2e6                       # DRAM read + write bytes of one 65,536 x 200 launch (ncu, dram__bytes_read.sum + dram__bytes_write.sum)
 
 
 def measured_peaks():
@@ -110,6 +114,12 @@ def synthetic_inputs(seed, n_envs):
     return params, table
 
 
+def rollout_config(world, workload=None):
+    """The `config` object of the headline line; both arms print the same keys."""
+    return {"workload": workload or WORKLOAD, "envs_per_gpu": N_ENVS, "steps_per_env": N_STEPS, "l2": "flushed between timed iterations; outputs (262 MB) exceed L2",
+            "parallelism": f"env-sharded x{world}, no collective"}
+
+
 class CpuReference:
     """The reference's own CPU path (oracle/_ref: unmodified RLtools headers, CPU_OPENBLAS device, project flags, all
     host threads) on the same rollout; falls back to the plain-C oracle port (1 thread) where that build is absent."""
@@ -129,15 +139,40 @@ class CpuReference:
         N = N_ENVS
         table = orc.reset_table(0, N, 1, np.zeros(N, np.int32), np.ones(N, np.uint8), STEP_LIMIT, 1)
         st, es, tr, er = np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32)
+        self.build = "unmodified reference headers, CPU_OPENBLAS device, -O3 -ffast-math -march=x86-64-v3 (the project's -march=native pinned: built on one machine, timed on another)"
         if os.path.exists(oracle.REF_FAST_SO):
             ref = oracle.Reference("fast")
+            self.ref = ref
             self.kind, self.threads = "reference", self.cores
-            self.run = lambda T: ref.pendulum_rollout(params, st, es, tr, er, table, T, STEP_LIMIT, chunk=65536, num_threads=self.cores)
+            self.run = lambda T, threads=None: ref.pendulum_rollout(params, st, es, tr, er, table, T, STEP_LIMIT, chunk=65536, num_threads=threads or self.cores)
         else:
+            self.ref = None
             self.kind, self.threads = "port", 1
+            self.build = "plain-C restatement of the reference, -O2, one thread"
             shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
-            self.run = lambda T: orc.pendulum_rollout(shape, params, st, es, tr, er, table, T, STEP_LIMIT)
+            self.run = lambda T, threads=None: orc.pendulum_rollout(shape, params, st, es, tr, er, table, T, STEP_LIMIT)
         t0 = time.perf_counter(); self.run(2); self.sec_per_env_step_batch = (time.perf_counter() - t0) / 2
+
+    def set_blas_threads(self, n):
+        """OpenBLAS reads OPENBLAS_NUM_THREADS once at load; later changes go through its own setter."""
+        if self.ref is not None:
+            try:
+                self.ref.lib.openblas_set_num_threads(int(n))
+            except AttributeError:
+                pass
+
+    def one_thread_rate(self, seconds=4.0):
+        """The reference's recommended single-thread setting (one BLAS thread, environment loop on the calling thread)."""
+        if self.ref is None:
+            return None
+        self.set_blas_threads(1)
+        try:
+            t0 = time.perf_counter(); self.run(2, 1); per = (time.perf_counter() - t0) / 2
+            T = int(max(2, min(N_STEPS, seconds / max(per, 1e-6))))
+            t0 = time.perf_counter(); self.run(T, 1)
+            return N_ENVS * T / (time.perf_counter() - t0)
+        finally:
+            self.set_blas_threads(self.cores)
 
     def sample_steps(self, seconds):
         return int(max(2, min(N_STEPS, seconds / max(self.sec_per_env_step_batch, 1e-6))))
@@ -146,15 +181,16 @@ class CpuReference:
         t0 = time.perf_counter(); self.run(T)
         return N_ENVS * T / (time.perf_counter() - t0)
 
-    def describe(self, T, reps, value):
-        return {"value": value, "unit": "env-steps/s", "cores": self.threads, "kind": self.kind,
+    def describe(self, T, reps, value, one_thread=None):
+        return {"value": value, "unit": "env-steps/s", "cores": self.threads, "kind": self.kind, "cores_1_value": one_thread, "build": self.build,
                 "sample": f"{N_ENVS} envs x {T} steps of the same rollout (observe -> evaluate -> step/reward), median of {reps}"}
 
 
-def cpu_reference_rate(seconds_total=15.0, reps=3):
+def cpu_reference_rate(seconds_total=12.0, reps=3):
     cpu = CpuReference()
     T = cpu.sample_steps(seconds_total / reps)
-    return cpu.describe(T, reps, statistics.median(cpu.timed(T) for _ in range(reps)))
+    value = statistics.median(cpu.timed(T) for _ in range(reps))
+    return cpu.describe(T, reps, value, cpu.one_thread_rate())
 
 
 def run_reference(args):
@@ -169,26 +205,33 @@ def run_reference(args):
     rate = statistics.median(rates)
     line = {"impl": "reference", "metric": "env-steps/s (fused actor fwd + env step)", "value": rate, "unit": "env-steps/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * N_ENVS * T / rate, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "timed_on": "host CPU cores"},
-            "cpu_baseline": cpu.describe(T, args.steps, rate), "e2e": {"value": rate, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": rollout_config(args.gpus), "timed_on": "host CPU cores",
+            "cpu_baseline": cpu.describe(T, args.steps, rate, cpu.one_thread_rate()), "e2e": {"value": rate, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def run_mlp_train(args):
-    """Secondary line (not the headline): data-parallel training of the MLP 64 -> 256 -> 256 -> 256 -> 16 (ReLU, fp32) on
-    `--train-rows` synthetic N(0,1) rows split over the ranks (strong scaling); one step = forward + MSE gradient + backward
-    over the rank's rows in 65,536-row chunks, ONE all-reduce of the flat gradient arena (NCCL), ONE fused Adam launch."""
+def distributed_context():
+    """(torch, device, dist or None, world, rank): one process per GPU, NCCL when launched by torch.distributed.run."""
     import torch
-    from __graft_entry__ import load_package
-    pkg = load_package()
-    from rl_tools_b200 import parallel
     world, rank, local_rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+    return torch, dev, dist, world, rank
+
+
+MLP_FLOP_PER_SAMPLE = 876544.0          # forward 303,104 + weight gradient 303,104 + input gradient 270,336 (2 M N K each, no padding)
+
+
+def measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=True):
+    """Data-parallel training of the MLP 64 -> 256 -> 256 -> 256 -> 16 (ReLU, fp32) on `--train-rows` synthetic N(0,1) rows split over the
+    ranks (strong scaling); one step = forward + MSE gradient + backward over the rank's rows in 65,536-row chunks, ONE all-reduce of
+    the flat gradient arena (NCCL), ONE fused Adam launch. Returns the result dictionary on rank 0 (None elsewhere)."""
+    from rl_tools_b200 import parallel
     chunk = 65536
     b, e = parallel.shard_range(args.train_rows, rank, world)
     rows = (e - b) // chunk * chunk
@@ -202,46 +245,65 @@ def run_mlp_train(args):
         n = d * fan_in + d
         net.params[off:off + n] = (torch.rand(n, device=dev, generator=gp) * 2 - 1) / fan_in ** 0.5
         off += n; fan_in = d
-    step = lambda: parallel.sharded_train_step(pkg, net, x, y, rows * world, dist)
+    steps, warmup = max(1, min(args.steps, 5)), 3
+    ex = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     sync = lambda: (dist.barrier() if dist is not None else None, torch.cuda.synchronize())
-    steps, warmup = min(args.steps, 5), max(1, min(args.warmup, 2))
     for _ in range(warmup):
-        step()
+        parallel.sharded_train_step(pkg, net, x, y, rows * world, dist)
     sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        step()
+    for i in range(steps):
+        parallel.sharded_train_step(pkg, net, x, y, rows * world, dist, exchange_events=ex[i])
     e1.record(); sync()
-    tm = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    tm = torch.tensor([e0.elapsed_time(e1), sum(a.elapsed_time(b) for a, b in ex)], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-    ms = float(tm.item()) / steps
+    ms, exchange_ms = float(tm[0].item()) / steps, float(tm[1].item()) / steps
+    replicas_equal = None
+    if dist is not None:                 # identical replicas after identical updates of the all-reduced gradient
+        lo, hi = net.params.clone(), net.params.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_equal = bool(torch.equal(lo, hi))
+    del x, y
+    if rank != 0:
+        return None
+    flop = MLP_FLOP_PER_SAMPLE * rows              # per GPU: the roofline compares one GPU's kernels with one GPU's peak
+    peaks = measured_peaks()
+    launches = steps * ((rows // chunk) * (4 + 1 + 4 * 3 + 3) + 2)
+    cpu = None
+    if cpu_baseline:
+        import numpy as np
+        import oracle
+        if os.path.exists(oracle.REF_FAST_SO):
+            # the reference's own forward + MSE gradient + backward + Adam on its CPU_OPENBLAS device, batch 1024 (its largest instantiated
+            # batch of this network in the registry), all host threads
+            os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
+            ref = oracle.Reference("fast")
+            rs = np.random.RandomState(0)
+            xs, ys = rs.randn(1024, 64).astype(np.float32), rs.randn(1024, 16).astype(np.float32)
+            res = ref.mlp_run("c5_b1024", net.params.cpu().numpy(), xs, ys, 2, 100)
+            cpu = {"value": 100 * 1024 / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
+                   "sample": "100 train steps (forward, mse gradient, backward, Adam) at batch 1024 of the same network, CPU_OPENBLAS build"}
+    tf = flop / (ms * 1e-3) / 1e12
+    return {"metric": "MLP fwd+bwd+Adam samples/s", "value": rows * world / (ms * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "allreduce_ms": exchange_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"mlp_train_64-256-256-256-16_rows{rows * world}", "rows_per_gpu": rows, "chunk_rows": chunk,
+                       "parallelism": f"dp{world}, one NCCL all-reduce of the 609 KB gradient arena per step", "l2": "inputs (>= 0.6 GB per pass and GPU) exceed L2"},
+            "replicas_bit_identical": replicas_equal,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tf / peaks["tflops"], "traffic": None,
+                         "peak_source": peaks["source"] + " bf16 dense (burst)", "frac_of_3xtf32_ceiling": tf / (peaks["tflops"] / 6.0)},
+            "cpu_baseline": cpu, "gpu_launches": launches}
+
+
+def run_mlp_train(args):
+    """--workload mlp_train: the data-parallel training line on its own."""
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    torch, dev, dist, world, rank = distributed_context()
+    line = measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=not args.no_cpu_baseline)
     if rank == 0:
-        flop = 876544.0 * rows                     # per GPU: the roofline compares one GPU's kernels with one GPU's peak
-        peaks = measured_peaks()
-        launches = steps * ((rows // chunk) * (4 + 1 + 4 * 3 + 3) + 2)
-        cpu = None
-        if not args.no_cpu_baseline:
-            import numpy as np
-            import oracle
-            if os.path.exists(oracle.REF_FAST_SO):
-                # the reference's own forward + MSE gradient + backward + Adam on its CPU_OPENBLAS device, batch 1024 (its largest instantiated
-                # batch of this network), all host threads
-                os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
-                ref = oracle.Reference("fast")
-                rs = np.random.RandomState(0)
-                xs, ys = rs.randn(1024, 64).astype(np.float32), rs.randn(1024, 16).astype(np.float32)
-                res = ref.mlp_run("c5_b1024", net.params.cpu().numpy(), xs, ys, 2, 200)
-                cpu = {"value": 200 * 1024 / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
-                       "sample": "200 train steps (forward, mse gradient, backward, Adam) at batch 1024 of the same network, CPU_OPENBLAS build"}
-        print(json.dumps({"metric": "MLP fwd+bwd+Adam samples/s", "value": rows * world / (ms * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": steps,
-                          "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                          "config": {"workload": f"mlp_train_64-256-256-256-16_rows{rows * world}", "chunk_rows": chunk, "parallelism": f"dp{world}, one NCCL all-reduce of the 609 KB gradient arena per step",
-                                     "l2": "inputs (>= 4 GB per pass) exceed L2"},
-                          "roofline": {"bound": "tensor", "achieved": flop / (ms * 1e-3) / 1e12, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                                       "frac": flop / (ms * 1e-3) / 1e12 / peaks["tflops"], "traffic": None, "peak_source": peaks["source"] + " bf16 dense (burst)"},
-                          "cpu_baseline": cpu, "gpu_launches": launches}))
+        print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
@@ -730,6 +792,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="headline rollout only: skip the mlp_train and strong-scaling measurements")
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
@@ -764,19 +827,11 @@ def main():
     workload = WORKLOAD if (args.envs, args.rollout_steps) == (65536, 200) else f"pendulum_rollout_{args.envs}env_x{args.rollout_steps}step_actor3-64-64-1 (reduced: profiling only)"
 
     import numpy as np
-    import torch
     from __graft_entry__ import load_package
     pkg = load_package()
     pkg.lib()                                     # fails loudly if the CUDA library is missing
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+    torch, dev, dist, world, rank = distributed_context()
+    local_rank = dev.index
 
     def barrier():
         if dist is not None:
@@ -848,24 +903,56 @@ def main():
     h2d = params_h.nbytes + table_h.nbytes + N_ENVS * (8 + 4 + 1 + 4)
     d2h = rows * BYTES_PER_ENV_STEP + N_ENVS * (8 + 4 + 1 + 4) + 4
     pkg.lib().b200rl_release_host_staging()
+    del h_obs, h_act, h_rew
+
+    # ---- strong scaling of the same workload: the 65,536 environments split over the ranks (each rank rolls out N_ENVS / world) ----
+    strong = None
+    if not args.no_secondary:
+        n_local = N_ENVS // world // 4 * 4
+        s_states, s_es, s_tr, s_er = states[:n_local].clone(), es[:n_local].clone(), tr[:n_local].clone(), er[:n_local].clone()
+        s_table = table[:, :n_local].contiguous()
+        s_rows = n_local * N_STEPS
+        s_steps = max(3, min(args.steps, 20))
+        s0 = [torch.cuda.Event(enable_timing=True) for _ in range(s_steps)]
+        s1 = [torch.cuda.Event(enable_timing=True) for _ in range(s_steps)]
+        sstep = lambda: pkg.pendulum_rollout(shape, params, s_states, s_es, s_tr, s_er, s_table, N_STEPS, STEP_LIMIT, obs=obs[:s_rows], act=act[:s_rows], rew=rew[:s_rows], error_flag=flag)
+        for _ in range(3):
+            flush.zero_(); sstep()
+        barrier()
+        for i in range(s_steps):
+            flush.zero_(); s0[i].record(); sstep(); s1[i].record()
+        barrier()
+        stm = torch.tensor([sum(a.elapsed_time(b) for a, b in zip(s0, s1))], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(stm, op=dist.ReduceOp.MAX)
+        s_ms = float(stm.item()) / s_steps
+        strong = {"metric": "env-steps/s (fused actor fwd + env step)", "value": world * n_local * N_STEPS / (s_ms * 1e-3), "unit": "env-steps/s", "scaling": "strong",
+                  "n_gpus": world, "ms_per_step": s_ms, "steps": s_steps, "config": {"workload": workload, "envs_total": world * n_local, "envs_per_gpu": n_local, "steps_per_env": N_STEPS}}
+        assert int(flag.item()) == 0
+    del obs, act, rew
+    torch.cuda.empty_cache()
+    mlp = None
+    if not args.no_secondary:
+        mlp = measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=not args.no_cpu_baseline)
 
     if rank == 0:
         peaks = measured_peaks()
         achieved_tflops = FLOP_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e12
-        # dram__bytes_read + dram__bytes_write of one full-size launch from the committed ncu capture (profiles/rollout_tc_kernel_65536env.md);
-        # other sizes were not captured
-        traffic = 205.2e6 if (N_ENVS, N_STEPS) == (65536, 200) else None
+        # traffic: dram__bytes_read + dram__bytes_write of one full-size launch, a constant taken from an ncu capture of this workload
+        # (it cannot be measured inside an unprofiled run); other sizes were not captured
+        traffic = TRAFFIC_BYTES_FULL_LAUNCH if (N_ENVS, N_STEPS) == (65536, 200) else None
         roofline = {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved_tflops / peaks["tflops"],
-                    "traffic": traffic, "peak_source": peaks["source"] + " bf16 dense (burst)",
+                    "traffic": traffic, "traffic_source": "ncu capture of this workload, constant", "peak_source": peaks["source"] + " bf16 dense (burst)",
+                    "frac_of_3xtf32_ceiling": achieved_tflops / (peaks["tflops"] / 6.0),
                     "hbm_write_gbs": BYTES_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]}
         cpu = None if args.no_cpu_baseline else cpu_reference_rate()
         line = {"metric": "env-steps/s (fused actor fwd + env step)", "value": value, "unit": "env-steps/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": {"workload": workload, "envs_per_gpu": N_ENVS, "steps_per_env": N_STEPS, "l2": "flushed between timed iterations; outputs (262 MB) exceed L2",
-                                                "parallelism": f"env-sharded x{world}, no collective"},
+                "data": "synthetic", "config": rollout_config(world, workload),
                 "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
                 "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps},
-                "gpu_launches": args.steps, "wall_s_timed_region": wall}
+                "gpu_launches": 2 * args.steps, "wall_s_timed_region": wall,
+                "secondary": {"mlp_train": mlp, "rollout_strong": strong}}
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

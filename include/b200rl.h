@@ -49,6 +49,8 @@ const char* b200rl_last_cuda_error(void);
  * inside a tensor-core dense kernel expired (the kernel then left its loops and released its tensor memory instead of
  * spinning). The reference has no counterpart (its asserts are no-ops in kernels, utils/assert/operations_cuda.h:17-21). */
 int b200rl_device_error_state(int* state_host);
+/* Sets that word back to zero on the current device (synchronises), so that a later b200rl_device_error_state reports only what happened since. */
+int b200rl_device_error_clear(void);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Dense layer. W is [O, I] row-major (weights.parameters), bias is [O].
@@ -82,13 +84,17 @@ int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* 
  * option there, since it synchronises the whole device and the memory is usually already handed out to another
  * allocator. The split-batch partial sums live instead in a static device array inside the library,
  * B200RL_STATIC_SCRATCH_BYTES (8 MiB) large, which every GPU that loads the library holds until the process exits.
- *   - problems that need more (see b200rl_dense_backward_scratch_bytes) are refused with B200RL_ERR_SCRATCH_LIMIT;
+ *   - any batch size is accepted: the batch is split into as many partial sums as the array holds (fewer than the caller-scratch
+ *     entry point would use for a large batch -- slower there, same accuracy, still a fixed summation order);
+ *   - a layer with more than B200RL_STATIC_SCRATCH_MAX_WEIGHTS weights (input_dim * output_dim > 2^20, e.g. wider than 1024 x 1024),
+ *     for which the array cannot hold even two partial sums, is refused with B200RL_ERR_SCRATCH_LIMIT when gradients are asked for;
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
  *     before any stream capture begins on that device;
  *   - the call makes no cudaMalloc / cudaFree and uses no allocating library routine;
  *   - all calls share the one array: two calls whose kernels can overlap on the GPU (different streams) race on it.
  *     Nothing in it has to start at zero -- every partial sum that is read was written earlier in the same call. */
 #define B200RL_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+#define B200RL_STATIC_SCRATCH_MAX_WEIGHTS (B200RL_STATIC_SCRATCH_BYTES / 8u)   /* input_dim * output_dim of the largest accepted layer: 2^20 */
 int b200rl_dense_backward_static_scratch(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
                                          float* d_W, float* d_bias, float* d_in, int ldi, int batch, int input_dim, int output_dim,
                                          int activation, b200rl_stream_t stream);
@@ -218,7 +224,8 @@ int b200rl_stream_synchronize(b200rl_stream_t stream);
  * (rl/environments/pendulum/pendulum.h:11-25, operations_generic.h:57-160); T == 1 is one runner step.
  *   states [N,2] (theta, theta_dot), episode_step [N], truncated [N] (0/1), episode_return [N]: in/out runner state
  *   (truncated starts as 1 so the first step resets, off_policy_runner/operations_generic.h init);
- *   reset_states [R,N,2]: the k-th reset of env e inside this call takes reset_states[k][e]; the values are drawn on
+ *   reset_states [R,N,2] (any 4-byte aligned address: it is read with scalar loads, so a view into a larger table works): the k-th
+ *   reset of env e inside this call takes reset_states[k][e]; the values are drawn on
  *   the host in the reference engine's order (b200rl_reset_table_host), mirroring how the reference's own CPU<->GPU
  *   tests feed CPU-drawn noise to the device; may be NULL if no env can reset during the call;
  *   obs [T*N,3], act [T*N,1], rew [T*N,1]: row t*N + env.
@@ -265,7 +272,9 @@ int b200rl_reset_table_host(uint32_t* rng_state_host, int n_envs, int n_steps, c
  *   log_std: device scalar (the state-independent log standard deviation of nn_models/mlp_unconditional_stddev).
  *   step_limit == 0 disables truncation. Runner state arguments as in b200rl_pendulum_rollout.
  * The actor must be 3 -> 64 -> 64 -> 1. The _layers variant takes the six parameter tensors W1 b1 W2 b2 W3 b3 as separate device
- * pointers (how the reference's containers allocate them) and packs them into a file-scope device arena first. */
+ * pointers (how the reference's containers allocate them) and packs them into a file-scope device arena first; that arena is shared by
+ * all calls on a device, which are therefore ordered with an event -- a stream that is being captured is refused (B200RL_ERR_UNSUPPORTED):
+ * capture the flat-arena entry point instead. */
 #define B200RL_COLLECT_DATA_DIM 13
 int b200rl_pendulum_collect(const b200rl_mlp_shape* actor, const float* actor_params, const float* log_std, float* states,
                             int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states,

@@ -53,6 +53,11 @@ class MlpShape(C.Structure):
         return [self.dims[l] for l in range(self.n_layers)]
 
 
+def C5_SHAPE():
+    """The training network of the sharded configuration."""
+    return MlpShape.make(64, [256, 256, 256, 16], ["relu", "relu", "relu", "identity"])
+
+
 def _opt(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
@@ -205,6 +210,26 @@ class Oracle:
             c1, c2, age = self.adam_bias_correction(beta_1, beta_2, age)
             p, m, v = self.adam_update(p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
         return p, g, m, v, pre, out
+
+    def mlp_chunked_step(self, shape, params, x, target, chunk_rows, do_step=True, alpha=1e-3, beta_1=0.9, beta_2=0.999, eps=1e-7, eps_sqrt=1e-7):
+        """One optimizer step over chunks of chunk_rows rows: per chunk forward, mse gradient weighted chunk_rows / rows, backward with the
+        gradients accumulating over the chunks; then Adam (first step). Returns params, grads, m, v and the last chunk's pre / out."""
+        rows = x.shape[0]
+        assert rows % chunk_rows == 0
+        g = np.zeros_like(params)
+        O = shape.dims[shape.n_layers - 1]
+        w = np.float32(np.float32(chunk_rows) / np.float32(rows))
+        pre = out = None
+        for c in range(0, rows, chunk_rows):
+            xc, tc = np.ascontiguousarray(x[c:c + chunk_rows]), np.ascontiguousarray(target[c:c + chunk_rows])
+            pre, out = self.mlp_forward(shape, params, xc)
+            y = np.ascontiguousarray(out[-chunk_rows * O:].reshape(chunk_rows, O))
+            g, _ = self.mlp_backward(shape, params, g, xc, pre, out, self.mse_gradient(y, tc, w))
+        p, m, v = params.copy(), np.zeros_like(params), np.zeros_like(params)
+        if do_step:
+            c1, c2, _ = self.adam_bias_correction(beta_1, beta_2, 1)
+            p, m, v = self.adam_update(p, g, m, v, alpha, beta_1, beta_2, eps, eps_sqrt, c1, c2)
+        return dict(params=p, grads=g, m=m, v=v, pre=pre, out=out)
 
     @staticmethod
     def dataset_columns(obs_dim, action_dim):
@@ -540,6 +565,7 @@ class Reference:
         L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
+        L.ref_mlp_c5_chunked.argtypes = [C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int] + [_f32p] * 6
 
     def cases(self):
         out = {}
@@ -570,6 +596,20 @@ class Reference:
                                   _opt(res["m"]), _opt(res["v"]), _opt(res["pre"]), _opt(res["out"]), _opt(res["d_input"]), C.byref(sec))
         assert rc == 0, name
         res["seconds"] = sec.value
+        return res
+
+    def mlp_c5_chunked(self, chunk_rows, params, x, target, do_step=True):
+        """One optimizer step of the 64 -> 256 -> 256 -> 256 -> 16 network over x.shape[0] / chunk_rows chunks (gradients accumulate over the
+        chunks, each weighted chunk_rows / rows), through the reference's own zero_gradient / forward / mse::gradient / backward / step."""
+        shape = C5_SHAPE()
+        n, rows = shape.num_params(), x.shape[0]
+        assert rows % chunk_rows == 0
+        acts = chunk_rows * sum(shape.layer_dims())
+        res = dict(params=np.empty(n, np.float32), grads=np.empty(n, np.float32), m=np.empty(n, np.float32), v=np.empty(n, np.float32),
+                   pre=np.empty(acts, np.float32), out=np.empty(acts, np.float32))
+        rc = self.lib.ref_mlp_c5_chunked(chunk_rows, params, np.ascontiguousarray(x), np.ascontiguousarray(target), rows // chunk_rows, rows, 1 if do_step else 0,
+                                         res["params"], res["grads"], res["m"], res["v"], res["pre"], res["out"])
+        assert rc == 0
         return res
 
     COLLECT_CASES = ((64, 64, 100, 1), (5, 37, 20, 1), (7, 50, 0, 1), (33, 25, 10, 2))   # (N, steps, step_limit, hidden activation id)

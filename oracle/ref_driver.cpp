@@ -213,6 +213,47 @@ struct MlpCase{
         rlt::free(device, input); rlt::free(device, d_input); rlt::free(device, output); rlt::free(device, tgt); rlt::free(device, d_output);
         rlt::free(device, net); rlt::free(device, buffers); rlt::free(device, optimizer);
     }
+    // One optimizer step over n_chunks chunks of B rows, the way a data-parallel replica runs it: zero_gradient, then per chunk forward,
+    // mse::gradient with weight B / total_rows (so that the chunk gradients add up to the gradient of the whole batch) and backward --
+    // gradients accumulate over the chunks -- then, if do_step, one Adam step. pre / act: the LAST chunk's activations.
+    static void run_chunked(const float* params_in, const float* x, const float* target, int n_chunks, int total_rows, int do_step,
+                            float* params_out, float* grads_out, float* m_out, float* v_out, float* pre_out, float* act_out){
+        DEVICE device;
+        RNG rng;
+        rlt::malloc(device, rng);
+        rlt::init(device, rng, 0);
+        NET net;
+        typename NET::template Buffer<> buffers;
+        OPTIMIZER optimizer;
+        rlt::malloc(device, net); rlt::malloc(device, buffers); rlt::malloc(device, optimizer);
+        rlt::init(device, optimizer);
+        { const float* p = params_in; for_each_layer(net, [&](auto& layer){ load_layer(device, layer, p); }); }
+        rlt::reset_optimizer_state(device, optimizer, net);
+        rlt::Matrix<rlt::matrix::Specification<T, TI, B, I>> input;
+        rlt::Matrix<rlt::matrix::Specification<T, TI, B, O>> tgt, d_output;
+        rlt::malloc(device, input); rlt::malloc(device, tgt); rlt::malloc(device, d_output);
+        rlt::zero_gradient(device, net);
+        const T weight = (T)B / (T)total_rows;
+        for(int c = 0; c < n_chunks; c++){
+            const float* xc = x + (size_t)c * B * I; const float* tc = target + (size_t)c * B * O;
+            for(TI b = 0; b < B; b++) for(TI i = 0; i < I; i++) rlt::set(input, b, i, xc[b * I + i]);
+            for(TI b = 0; b < B; b++) for(TI o = 0; o < O; o++) rlt::set(tgt, b, o, tc[b * O + o]);
+            rlt::forward(device, net, input, buffers, rng);
+            auto out = rlt::output(device, net);
+            auto out_m = rlt::matrix_view(device, out);
+            rlt::nn::loss_functions::mse::gradient(device, out_m, tgt, d_output, weight);
+            rlt::backward(device, net, input, d_output, buffers);
+        }
+        if(do_step) rlt::step(device, optimizer, net);
+        { float* pre = pre_out; float* ao = act_out; for_each_layer(net, [&](auto& layer){ store_acts(device, layer, pre, ao); }); }
+        float* p;
+        p = params_out; for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, PARAMS); });
+        p = grads_out;  for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, GRADS); });
+        p = m_out;      for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, MOM1); });
+        p = v_out;      for_each_layer(net, [&](auto& layer){ store_layer(device, layer, p, MOM2); });
+        rlt::free(device, input); rlt::free(device, tgt); rlt::free(device, d_output);
+        rlt::free(device, net); rlt::free(device, buffers); rlt::free(device, optimizer);
+    }
     static MlpVTable vtable(){
         return MlpVTable{(int)B, (int)I, (int)H, (int)O, (int)NL, (int)HACT, (int)OACT, &run};
     }
@@ -931,6 +972,17 @@ int ref_mlp_run(const char* name, const float* params_in, uint32_t init_seed, co
     auto it = registry().find(name); if(it == registry().end()) return -1;
     it->second.run(params_in, init_seed, x, target, mode, n_steps, params_out, grads_out, m_out, v_out, pre_out, act_out, d_input_out, seconds);
     return 0;
+}
+
+// The training network of the sharded configuration (64 -> 256 -> 256 -> 256 -> 16, ReLU, identity) stepped over chunks of chunk_rows rows
+// (1024: fast enough for a live comparison; 65536: the chunk size of the GPU path, used to generate a fixture).
+int ref_mlp_c5_chunked(int chunk_rows, const float* params_in, const float* x, const float* target, int n_chunks, int total_rows, int do_step,
+                       float* params_out, float* grads_out, float* m_out, float* v_out, float* pre_out, float* act_out){
+    switch(chunk_rows){
+        case 1024:  MlpCase<1024, 64, 256, 16, 4, act::RELU, act::IDENTITY>::run_chunked(params_in, x, target, n_chunks, total_rows, do_step, params_out, grads_out, m_out, v_out, pre_out, act_out); return 0;
+        case 65536: MlpCase<65536, 64, 256, 16, 4, act::RELU, act::IDENTITY>::run_chunked(params_in, x, target, n_chunks, total_rows, do_step, params_out, grads_out, m_out, v_out, pre_out, act_out); return 0;
+        default: return -1;
+    }
 }
 
 // raw reference RNG streams (random/operations_cpu.h): engine seeded with seed+1

@@ -8,7 +8,14 @@
 
 namespace b200rl {
 
-constexpr int NUM_SMS = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+constexpr int NUM_SMS = 148;  // B200: 2 dies x 74 SMs; the split heuristics of the planners assume this (they decide scratch sizes, so they must not depend on the device)
+constexpr int MAX_DEVICES = 64;
+
+// ordinal of the calling thread's current device, checked against MAX_DEVICES: state that CUDA ties to a device (function attributes,
+// events, helper streams, symbol addresses) is kept per ordinal
+int current_device(int* device);
+// multiprocessor count of the current device (cached per ordinal): the grid of the persistent kernels
+int sm_count(int* count);
 
 // records the CUDA error text for b200rl_last_cuda_error() and maps it to a status
 int cuda_fail(cudaError_t e, const char* where);

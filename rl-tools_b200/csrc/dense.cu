@@ -10,7 +10,8 @@
 // bias gradient are one pass; split-batch partials of d_W / d_bias are reduced in a fixed order (deterministic).
 #include "common.cuh"
 #include "dense.cuh"
-#include <stdlib.h>
+#include <math.h>
+#include <mutex>
 
 namespace b200rl {
 
@@ -276,20 +277,18 @@ __global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict_
 
 // The tensor-core kernel takes the contraction when there is enough work to fill its 128 x 256 tiles on a good part of the SMs:
 // one tile costs ~30 us at K = 256 however few tiles there are, which the CUDA-core kernel's 64 x 64 tiles beat below ~2^27
-// multiply-adds (batch-256 training steps, the 64-wide PPO networks). B200RL_DENSE_KERNEL=simt forces the CUDA-core kernel and
-// B200RL_DENSE_TC_MIN_LOG2 overrides the threshold (A/B measurements).
+// multiply-adds (batch-256 training steps, the 64-wide PPO networks).
 static bool tc_eligible(long long M, long long N, long long K){
-    static const bool force_simt = [](){ const char* v = getenv("B200RL_DENSE_KERNEL"); return v && v[0] == 's'; }();
-    static const int min_log2 = [](){ const char* v = getenv("B200RL_DENSE_TC_MIN_LOG2"); return v ? atoi(v) : 27; }();
-    if(force_simt) return false;
-    return M >= 64 && N >= 16 && (double)M * N * K >= ldexp(1.0, min_log2);
+    return M >= 64 && N >= 16 && (double)M * N * K >= ldexp(1.0, 27);
 }
 static bool use_tensor_cores(const GemmArgs& a){ return tc_eligible(a.M, a.N, a.K); }
 
 // bytes: split-k and bias partial sums (required when gradients are wanted); wt_bytes: room for the transposed weights behind them,
 // which lets the input-gradient GEMM of the tensor-core path read both operands with 16-byte loads (used when the scratch has it)
 struct BackwardPlan { int splits; int k_per_split; int bias_segs; int rows_per_seg; size_t bytes; size_t wt_bytes; };
-static BackwardPlan plan_backward(int B, int I, int O){
+// budget: upper bound on p.bytes. The plan lowers the number of bias segments and of batch splits until the partial sums fit (fewer
+// splits is slower but as correct and as deterministic; one split needs no partial sums at all).
+static BackwardPlan plan_backward(int B, int I, int O, size_t budget = SIZE_MAX){
     BackwardPlan p;
     // weight gradient = contraction over the batch: split it so that every SM has work (tile shape of the kernel that will run)
     // fewer than 64 output rows (e.g. a 16-wide last layer): the tensor-core kernel computes dW^T instead (rows = input features)
@@ -302,13 +301,21 @@ static BackwardPlan plan_backward(int B, int I, int O){
     int max_splits = tc ? (B + 255) / 256 : (B + 63) / 64;
     p.splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
     if(p.splits < 1) p.splits = 1;
-    p.k_per_split = ((B + p.splits - 1) / p.splits + BK - 1) / BK * BK;
-    p.splits = (B + p.k_per_split - 1) / p.k_per_split;
     int col_blocks = (O + 127) / 128;                      // the vector kernel's blocks cover 128 columns
     int want_segs = (4 * NUM_SMS + col_blocks - 1) / col_blocks;
     int max_segs = (B + 63) / 64;
     p.bias_segs = want_segs > max_segs ? max_segs : want_segs;
     if(p.bias_segs < 1) p.bias_segs = 1;
+    if(budget != SIZE_MAX){
+        const size_t seg_bytes = sizeof(float) * (size_t)O, split_bytes = sizeof(float) * (size_t)O * I, usable = budget - (budget < 16 ? budget : 16);
+        if((size_t)p.bias_segs * seg_bytes > usable / 4) p.bias_segs = (int)(usable / 4 / seg_bytes);     // at most a quarter for the bias partials
+        if(p.bias_segs < 2) p.bias_segs = 1;
+        const size_t left = usable - (p.bias_segs > 1 ? (size_t)p.bias_segs * seg_bytes : 0);
+        if((size_t)p.splits * split_bytes > left) p.splits = (int)(left / split_bytes);
+        if(p.splits < 2) p.splits = 1;
+    }
+    p.k_per_split = ((B + p.splits - 1) / p.splits + BK - 1) / BK * BK;
+    p.splits = (B + p.k_per_split - 1) / p.k_per_split;
     p.rows_per_seg = (B + p.bias_segs - 1) / p.bias_segs;
     p.bias_segs = (B + p.rows_per_seg - 1) / p.rows_per_seg;
     p.bytes = 0;
@@ -338,18 +345,23 @@ static int dense_forward_impl(const float* W, const float* bias, const float* x,
 // networks whose backward passes are captured on two streams do not serialise on one helper. Beyond the table's size: no branch.
 static int gradient_branch(cudaStream_t s, cudaStream_t* branch, cudaEvent_t* join){
     constexpr int SLOTS = 16;
-    static struct { cudaStream_t origin, helper; cudaEvent_t fork, join; bool used; } table[SLOTS] = {};
+    static struct { int device; cudaStream_t origin, helper; cudaEvent_t fork, join; bool used; } table[SLOTS] = {};
+    static std::mutex mutex;
+    int dev = 0;
+    int rc = current_device(&dev);
+    if(rc) return rc;
+    std::lock_guard<std::mutex> lock(mutex);
     int slot = -1;
     for(int i = 0; i < SLOTS; i++){
-        if(table[i].used && table[i].origin == s){ slot = i; break; }
+        if(table[i].used && table[i].origin == s && table[i].device == dev){ slot = i; break; }
         if(!table[i].used && slot < 0) slot = i;
     }
     if(slot < 0) return B200RL_OK;                                      // table full: everything stays on s
-    if(!table[slot].used){
+    if(!table[slot].used){                                              // helper stream and events live on the current device, like s
         B200RL_CUDA_TRY(cudaStreamCreateWithFlags(&table[slot].helper, cudaStreamNonBlocking));
         B200RL_CUDA_TRY(cudaEventCreateWithFlags(&table[slot].fork, cudaEventDisableTiming));
         B200RL_CUDA_TRY(cudaEventCreateWithFlags(&table[slot].join, cudaEventDisableTiming));
-        table[slot].origin = s; table[slot].used = true;
+        table[slot].origin = s; table[slot].device = dev; table[slot].used = true;
     }
     B200RL_CUDA_TRY(cudaEventRecord(table[slot].fork, s));
     B200RL_CUDA_TRY(cudaStreamWaitEvent(table[slot].helper, table[slot].fork, 0));
@@ -358,8 +370,9 @@ static int gradient_branch(cudaStream_t s, cudaStream_t* branch, cudaEvent_t* jo
 }
 
 static int dense_backward_impl(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
-                               float* dW, float* db, float* d_in, int ldi, int B, int I, int O, int act, void* scratch, size_t scratch_bytes, cudaStream_t s){
-    BackwardPlan p = plan_backward(B, I, O);
+                               float* dW, float* db, float* d_in, int ldi, int B, int I, int O, int act, void* scratch, size_t scratch_bytes, cudaStream_t s,
+                               size_t plan_budget = SIZE_MAX){
+    BackwardPlan p = plan_backward(B, I, O, plan_budget);
     bool want_grads = dW != nullptr;
     if(want_grads && p.bytes > 0 && (scratch == nullptr || scratch_bytes < p.bytes)) return B200RL_ERR_INVALID_ARGUMENT;
     float* w_partial = reinterpret_cast<float*>(scratch);
@@ -491,11 +504,12 @@ int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* 
 static __device__ __align__(256) unsigned char g_static_scratch[B200RL_STATIC_SCRATCH_BYTES];
 
 static int static_scratch_address(void** out){
-    constexpr int MAX_DEVICES = 64;
     static void* cached[MAX_DEVICES] = {};
+    static std::mutex mutex;
     int dev = 0;
-    B200RL_CUDA_TRY(cudaGetDevice(&dev));
-    if(dev < 0 || dev >= MAX_DEVICES) return B200RL_ERR_UNSUPPORTED;
+    int rc = current_device(&dev);
+    if(rc) return rc;
+    std::lock_guard<std::mutex> lock(mutex);
     if(cached[dev] == nullptr){
         void* p = nullptr;
         B200RL_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
@@ -514,13 +528,14 @@ int b200rl_dense_backward_static_scratch(const float* W, const float* x, int ldx
     if(d_W && (!x || ldx < input_dim)) return B200RL_ERR_INVALID_ARGUMENT;
     if(d_in && ldi < input_dim) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
-    const size_t need = d_W ? plan_backward(batch, input_dim, output_dim).bytes : 0;
-    if(need > (size_t)B200RL_STATIC_SCRATCH_BYTES) return B200RL_ERR_SCRATCH_LIMIT;
+    // The batch is split as far as the array allows (never refused for its batch size); what does not fit at all is a layer whose
+    // weight matrix is so large that the array cannot hold two partial sums of its gradient.
+    if(d_W && (size_t)input_dim * (size_t)output_dim > B200RL_STATIC_SCRATCH_MAX_WEIGHTS) return B200RL_ERR_SCRATCH_LIMIT;
     void* scratch = nullptr;
     int rc = static_scratch_address(&scratch);
     if(rc) return rc;
     return dense_backward_impl(W, x, ldx, pre, ldpre, d_out, ldd, d_W, d_bias, d_in, ldi, batch, input_dim, output_dim, activation,
-                               scratch, B200RL_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+                               scratch, B200RL_STATIC_SCRATCH_BYTES, (cudaStream_t)stream, (size_t)B200RL_STATIC_SCRATCH_BYTES);
 }
 
 size_t b200rl_mlp_num_params(const b200rl_mlp_shape* sh){

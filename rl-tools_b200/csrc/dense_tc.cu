@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "dense.cuh"
 #include "tcgen05.cuh"
+#include <atomic>
 #include <type_traits>
 
 namespace b200rl {
@@ -317,6 +318,10 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
         }
         if(aborted) break;
         accumulate(acc, (u - 1) & 1, ((u - 1) >> 1) & 1);
+        // a wait that ran out leaves half-finished sums in the accumulators: nothing of this work item may reach global memory
+        // (an accumulating epilogue would corrupt the gradient). The barrier makes the decision the same for every thread.
+        tc::named_barrier_sync(1, TC_THREADS);
+        if(*abort_flag){ aborted = true; break; }
 
         // ---- epilogue, vector form (forward / plain store with 16-byte aligned rows): the warp transposes each 32 x 32 block through a
         // private shared-memory patch with 16-byte accesses on both sides (row pitch 36 floats: conflict-free for both the row-wise
@@ -433,13 +438,19 @@ template <bool A_KC, bool B_KC, int EPI, int ACT, int NB>
 static int launch_variant(const GemmArgs& a, int splits, int n_pad, cudaStream_t s){
     const int n_tiles = (a.N + n_pad - 1) / n_pad, m_tiles = (a.M + TC_M - 1) / TC_M;
     const uint32_t smem = 2 * (2 * A_TILE_BYTES + 2 * (uint32_t)n_pad * 128) + 64 + 1024;
-    static bool configured = false;
-    if(!configured){
+    // the attribute belongs to the (function, device) pair: one flag per device ordinal
+    static std::atomic<bool> configured[MAX_DEVICES];
+    int dev = 0, sms = 0;
+    int rc = current_device(&dev);
+    if(rc) return rc;
+    if(!configured[dev].load(std::memory_order_acquire)){
         B200RL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024)));
-        configured = true;
+        configured[dev].store(true, std::memory_order_release);
     }
+    rc = sm_count(&sms);
+    if(rc) return rc;
     const long long total = (long long)m_tiles * n_tiles * splits;
-    const int grid = (int)(total < NUM_SMS ? total : NUM_SMS);
+    const int grid = (int)(total < sms ? total : sms);
     auto aligned = [](const float* p, long long ld){ return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld & 3) == 0; };
     // k-contiguous operands: 16-byte loads along k need an aligned base, pitch and k range; row-contiguous operands: 16-byte loads along
     // the rows need an aligned base and pitch (tile origins are multiples of 16 rows)
@@ -474,5 +485,10 @@ int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcont
 extern "C" int b200rl_device_error_state(int* state_host){
     if(!state_host) return B200RL_ERR_INVALID_ARGUMENT;
     B200RL_CUDA_TRY(cudaMemcpyFromSymbol(state_host, b200rl::g_dense_tc_error, sizeof(int)));
+    return B200RL_OK;
+}
+extern "C" int b200rl_device_error_clear(void){
+    const int zero = 0;
+    B200RL_CUDA_TRY(cudaMemcpyToSymbol(b200rl::g_dense_tc_error, &zero, sizeof(int)));
     return B200RL_OK;
 }

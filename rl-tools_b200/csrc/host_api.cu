@@ -4,6 +4,8 @@
 #include "common.cuh"
 #include "rollout.cuh"
 #include <string.h>
+#include <atomic>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -13,6 +15,26 @@ static thread_local std::string g_last_cuda_error;
 int cuda_fail(cudaError_t e, const char* where){
     g_last_cuda_error = std::string(where) + ": " + cudaGetErrorString(e);
     return B200RL_ERR_CUDA;
+}
+
+int current_device(int* device){
+    B200RL_CUDA_TRY(cudaGetDevice(device));
+    if(*device < 0 || *device >= MAX_DEVICES) return B200RL_ERR_UNSUPPORTED;
+    return B200RL_OK;
+}
+int sm_count(int* count){
+    static std::atomic<int> cached[MAX_DEVICES];
+    int dev = 0;
+    int rc = current_device(&dev);
+    if(rc) return rc;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if(n == 0){
+        B200RL_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+        if(n < 1) return B200RL_ERR_UNSUPPORTED;
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    *count = n;
+    return B200RL_OK;
 }
 
 // ---- MT19937 (Matsumoto & Nishimura), state = 624 words + index ------------------------------------------------
@@ -79,13 +101,16 @@ struct Staging {
         cap_envs = cap_rows = cap_reset = 0; device = -1;
     }
 };
-static Staging g_staging;
+// one staging set per device ordinal: a process that drives several GPUs keeps each device's buffers
+static Staging g_staging[MAX_DEVICES];
+static std::mutex g_staging_mutex;
 
-static int ensure_staging(size_t n_envs, size_t rows, size_t reset_elems, int slabs){
+static int ensure_staging(size_t n_envs, size_t rows, size_t reset_elems, int slabs, Staging** out){
     int dev = 0;
-    B200RL_CUDA_TRY(cudaGetDevice(&dev));
-    Staging& s = g_staging;
-    if(s.device != dev && s.device != -1) s.release();
+    int rc = current_device(&dev);
+    if(rc) return rc;
+    Staging& s = g_staging[dev];
+    *out = &s;
     s.device = dev;
     if(!s.copy_stream) B200RL_CUDA_TRY(cudaStreamCreateWithFlags(&s.copy_stream, cudaStreamNonBlocking));
     if(!s.params) B200RL_CUDA_TRY(cudaMalloc(&s.params, sizeof(float) * 65536));
@@ -273,7 +298,11 @@ int b200rl_gather_draws_host(uint32_t* rng, int n_envs, int batch, const int32_t
     return B200RL_OK;
 }
 
-int b200rl_release_host_staging(void){ g_staging.release(); return B200RL_OK; }
+int b200rl_release_host_staging(void){
+    std::lock_guard<std::mutex> lock(g_staging_mutex);
+    for(int d = 0; d < MAX_DEVICES; d++) if(g_staging[d].device != -1) g_staging[d].release();
+    return B200RL_OK;
+}
 
 int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* actor_params_host, float* states_host,
                                  int32_t* episode_step_host, uint8_t* truncated_host, float* episode_return_host,
@@ -292,9 +321,11 @@ int b200rl_pendulum_rollout_host(const b200rl_mlp_shape* actor, const float* act
     int slabs = (rows >= (size_t)1 << 20 && n_steps >= 8) ? 8 : 1;
     int slab_steps = (n_steps + slabs - 1) / slabs;
     slabs = (n_steps + slab_steps - 1) / slab_steps;
-    rc = ensure_staging(N, rows, (size_t)n_reset_rounds * N * 2, slabs);
+    std::lock_guard<std::mutex> lock(g_staging_mutex);
+    Staging* staging = nullptr;
+    rc = ensure_staging(N, rows, (size_t)n_reset_rounds * N * 2, slabs, &staging);
     if(rc) return rc;
-    Staging& st = g_staging;
+    Staging& st = *staging;
     cudaStream_t s = (cudaStream_t)stream;
     B200RL_CUDA_TRY(cudaMemcpyAsync(st.params, actor_params_host, sizeof(float) * n_params, cudaMemcpyHostToDevice, s));
     B200RL_CUDA_TRY(cudaMemcpyAsync(st.states, states_host, sizeof(float) * 2 * N, cudaMemcpyHostToDevice, s));

@@ -1,131 +1,12 @@
-// Fused Pendulum rollout: reset-if-truncated, observe, actor forward (3 -> H -> H -> 1), environment step, reward and
-// episode counters for T steps in ONE launch. One thread owns one environment for the whole call; the actor's weights
-// stay resident in shared memory; the runner state lives in registers between steps.
+// Entry points of the fused Pendulum rollout (reset-if-truncated, observe, actor forward 3 -> 64 -> 64 -> 1, environment step, reward and
+// episode counters for T steps in ONE launch of the tensor-core kernel in rollout_tc.cu), of the on-policy collect, of the off-policy runner
+// step with replay buffers, and of replay-buffer sampling.
 #include "common.cuh"
 #include "pendulum.cuh"
 #include "rollout.cuh"
-#include <stdlib.h>
+#include <mutex>
 
 namespace b200rl {
-
-// ---------------------------------------------------------------------------------------------------------------
-// CUDA-core kernel: exact fp32 FMA chain in the reference's summation order (bias first, inputs ascending).
-// Shared memory: W1 [H,3], b1 [H], W2 [H,H], b2 [H], W3 [H], b3 -- (H*H + 6H + 1) floats, read as warp broadcasts.
-// ---------------------------------------------------------------------------------------------------------------
-template <int H, bool COLLECT>
-__global__ void __launch_bounds__(128) rollout_simt_kernel(RolloutArgs a){
-    extern __shared__ __align__(16) float smem[];
-    float* W1 = smem;                 // [H][3]
-    float* b1 = W1 + H * 3;           // [H]
-    float* W2 = b1 + H;               // [H][H]
-    float* b2 = W2 + H * H;           // [H]
-    float* W3 = b2 + H;               // [H]
-    float* b3 = W3 + H;               // [1]
-    constexpr int NPARAMS = H * 3 + H + H * H + H + H + 1;
-    for(int i = threadIdx.x; i < NPARAMS; i += blockDim.x) smem[i] = __ldg(a.params + i);
-    __syncthreads();
-
-    const int local = blockIdx.x * blockDim.x + threadIdx.x;
-    if(local >= a.env_count) return;
-    const int e = a.env_begin + local;
-    float theta = a.states[2 * e], theta_dot = a.states[2 * e + 1];
-    int es = a.episode_step[e];
-    bool trunc = a.truncated[e] != 0;
-    float er = a.episode_return[e];
-    int resets = a.reset_count ? a.reset_count[e] : 0;
-    const int act_h1 = a.acts[0], act_h2 = a.acts[1], act_out = a.acts[2];
-    GaussianHead head{};
-    const size_t ld = COLLECT ? (size_t)a.ld_dataset : 0;
-    if constexpr(COLLECT){
-        head.init(a.log_std);
-        a.dataset[(size_t)e * ld + COL_RESET] = trunc ? 1.0f : 0.0f;      // collect, operations_generic.h:115-117
-    }
-
-    for(int t = 0; t < a.n_steps; t++){
-        StepDraws draws{};             // the trajectory-only kernels need the draws at a reset only: nothing per step on their hot path
-        if(a.device_rng && (COLLECT || trunc)) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
-        if(trunc){
-            if(a.device_rng){        // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
-                theta = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(draws.u_theta_dot, 2.0f, -1.0f);
-            }
-            else if(a.reset_states != nullptr && resets < a.n_reset_rounds){
-                const float2 rs = *reinterpret_cast<const float2*>(a.reset_states + ((size_t)resets * a.n_envs + e) * 2);
-                theta = rs.x; theta_dot = rs.y;
-            }
-            else if(a.error_flag) *a.error_flag = 1;
-            resets++; es = 0; er = 0.0f;
-        }
-        float sn, cs;
-        sincosf(theta, &sn, &cs);
-        const size_t row = (size_t)t * a.n_envs + e;
-        float* drow = COLLECT ? a.dataset + row * ld : nullptr;
-        if constexpr(COLLECT){ drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot; }
-        else{ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
-
-        float h1[H];
-#pragma unroll
-        for(int j = 0; j < H; j++){
-            float acc = b1[j];
-            acc = fmaf(W1[j * 3 + 0], cs, acc); acc = fmaf(W1[j * 3 + 1], sn, acc); acc = fmaf(W1[j * 3 + 2], theta_dot, acc);
-            h1[j] = activation_rt(acc, act_h1);
-        }
-        float out = b3[0];
-#pragma unroll 2
-        for(int j = 0; j < H; j++){
-            float acc = b2[j];
-            const float4* w = reinterpret_cast<const float4*>(W2 + j * H);
-#pragma unroll
-            for(int k = 0; k < H / 4; k++){
-                const float4 w4 = w[k];
-                acc = fmaf(w4.x, h1[4 * k + 0], acc); acc = fmaf(w4.y, h1[4 * k + 1], acc);
-                acc = fmaf(w4.z, h1[4 * k + 2], acc); acc = fmaf(w4.w, h1[4 * k + 3], acc);
-            }
-            out = fmaf(W3[j], activation_rt(acc, act_h2), out);
-        }
-        float action = activation_rt(out, act_out);
-        if constexpr(COLLECT){
-            const float mean = action;
-            action = head.sample(mean, a.device_rng ? draws.normal : __ldg(a.noise + row));
-            drow[COL_ACTION_MEAN] = mean; drow[COL_ACTION] = action; drow[COL_LOG_PROB] = head.log_prob(mean, action, a.neg_half_log_2pi);
-        }
-
-        float nt, ntd;
-        pendulum::step(theta, theta_dot, sn, action, nt, ntd);
-        const float r = pendulum::reward(theta, theta_dot, action);
-        es += 1; er = __fadd_rn(er, r);
-        if constexpr(COLLECT){
-            trunc = a.step_limit > 0 && es >= a.step_limit;                 // operations_generic_per_env.h:72
-            const float flag = trunc ? 1.0f : 0.0f;
-            drow[COL_REWARD] = r; drow[COL_TERMINATED] = 0.0f; drow[COL_TRUNCATED] = flag;
-            drow[(size_t)a.n_envs * ld + COL_RESET] = flag;                 // all_reset[pos + N]
-        }
-        else{
-            a.act[row] = action; a.rew[row] = r;
-            trunc = (es == a.step_limit);      // Pendulum never terminates (operations_generic.h:243-247)
-        }
-        theta = nt; theta_dot = ntd;
-    }
-    if constexpr(COLLECT){                     // final observation, operations_generic.h:136-143
-        float sn, cs;
-        sincosf(theta, &sn, &cs);
-        float* drow = a.dataset + ((size_t)a.n_steps * a.n_envs + e) * ld;
-        drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot;
-    }
-    a.states[2 * e] = theta; a.states[2 * e + 1] = theta_dot;
-    a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
-    if(a.reset_count) a.reset_count[e] = resets;
-}
-
-int launch_rollout_simt(const RolloutArgs& a, int H, cudaStream_t s){
-    if(H != 64) return B200RL_ERR_UNSUPPORTED;
-    constexpr int THREADS = 128;
-    size_t smem = sizeof(float) * (64 * 3 + 64 + 64 * 64 + 64 + 64 + 1);
-    int grid = (a.env_count + THREADS - 1) / THREADS;
-    if(a.dataset) rollout_simt_kernel<64, true><<<grid, THREADS, smem, s>>>(a);
-    else rollout_simt_kernel<64, false><<<grid, THREADS, smem, s>>>(a);
-    B200RL_LAUNCH_CHECK("rollout_simt");
-    return B200RL_OK;
-}
 
 int validate_actor(const b200rl_mlp_shape* actor){
     if(!actor) return B200RL_ERR_INVALID_ARGUMENT;
@@ -135,12 +16,10 @@ int validate_actor(const b200rl_mlp_shape* actor){
     return B200RL_OK;
 }
 
-// The tensor-core kernel is the default for the 64-wide actor; B200RL_ROLLOUT_KERNEL=simt selects the CUDA-core kernel
-// (same results up to fp32 rounding), which exists for A/B measurements.
+// one kernel: the tensor-core rollout of the 64-wide actor (validate_actor admits nothing else)
 int rollout_dispatch(const b200rl_mlp_shape* actor, const RolloutArgs& a, cudaStream_t s){
-    static const bool force_simt = [](){ const char* v = getenv("B200RL_ROLLOUT_KERNEL"); return v && v[0] == 's'; }();
-    if(actor->dims[0] == 64 && !force_simt) return launch_rollout_tc(a, s);
-    return launch_rollout_simt(a, actor->dims[0], s);
+    if(actor->dims[0] != 64) return B200RL_ERR_UNSUPPORTED;
+    return launch_rollout_tc(a, s);
 }
 
 }  // namespace b200rl
@@ -231,23 +110,32 @@ extern "C" int b200rl_pendulum_collect_device_rng(const b200rl_mlp_shape* actor,
 // share that arena.
 static __device__ __align__(16) float g_collect_actor_arena[64 * 3 + 64 + 64 * 64 + 64 + 64 + 1 + 3];
 
-// packs six separately allocated layer tensors (W1 b1 W2 b2 W3 b3) into the file-scope arena; *order_event is recorded by the caller
-// after its kernel launch
+// packs six separately allocated layer tensors (W1 b1 W2 b2 W3 b3) into the file-scope arena of the current device; *order_event is
+// recorded by the caller after its kernel launch. The arena is shared by every call on the device, so calls are ordered with an event --
+// which a stream capture cannot wait on (the event was recorded outside the capture): a capturing stream is refused.
 static int pack_actor_layers(const float* const* layer_params, cudaStream_t s, float** arena_out, cudaEvent_t* order_event){
     if(!layer_params) return B200RL_ERR_INVALID_ARGUMENT;
     for(int i = 0; i < 6; i++) if(!layer_params[i]) return B200RL_ERR_INVALID_ARGUMENT;
-    static cudaEvent_t ev = nullptr;
-    float* arena = nullptr;
-    if(!ev) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-    B200RL_CUDA_TRY(cudaGetSymbolAddress((void**)&arena, g_collect_actor_arena));
-    B200RL_CUDA_TRY(cudaStreamWaitEvent(s, ev, 0));
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    B200RL_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
+    if(cap != cudaStreamCaptureStatusNone) return B200RL_ERR_UNSUPPORTED;
+    static struct { cudaEvent_t order; float* arena; } per_device[MAX_DEVICES] = {};
+    static std::mutex mutex;
+    int dev = 0;
+    int rc = current_device(&dev);
+    if(rc) return rc;
+    std::lock_guard<std::mutex> lock(mutex);
+    auto& st = per_device[dev];
+    if(!st.order) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&st.order, cudaEventDisableTiming));
+    if(!st.arena) B200RL_CUDA_TRY(cudaGetSymbolAddress((void**)&st.arena, g_collect_actor_arena));
+    B200RL_CUDA_TRY(cudaStreamWaitEvent(s, st.order, 0));
     const size_t counts[6] = {64 * 3, 64, 64 * 64, 64, 64, 1};
     size_t off = 0;
     for(int i = 0; i < 6; i++){
-        B200RL_CUDA_TRY(cudaMemcpyAsync(arena + off, layer_params[i], sizeof(float) * counts[i], cudaMemcpyDeviceToDevice, s));
+        B200RL_CUDA_TRY(cudaMemcpyAsync(st.arena + off, layer_params[i], sizeof(float) * counts[i], cudaMemcpyDeviceToDevice, s));
         off += counts[i];
     }
-    *arena_out = arena; *order_event = ev;
+    *arena_out = st.arena; *order_event = st.order;
     return B200RL_OK;
 }
 

@@ -82,7 +82,6 @@ struct GaussianHead {
 };
 
 int validate_actor(const b200rl_mlp_shape* actor);
-int launch_rollout_simt(const RolloutArgs& a, int H, cudaStream_t s);
 int launch_rollout_tc(const RolloutArgs& a, cudaStream_t s);     // tensor-core kernel, H == 64
 int rollout_dispatch(const b200rl_mlp_shape* actor, const RolloutArgs& a, cudaStream_t s);
 

@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(128, 4) rollout_env_kernel(EnvRolloutArgs a){
     for(int t = 0; t < a.n_steps; t++){
         if(trunc){                                   // prologue: rl/components/off_policy_runner/operations_generic_per_env.h:8-61
             if(a.reset_states != nullptr && resets < a.n_reset_rounds){
-                const float2 rs = *reinterpret_cast<const float2*>(a.reset_states + ((size_t)resets * a.n_envs + e) * 2);
+                const float* rsp = a.reset_states + ((size_t)resets * a.n_envs + e) * 2;      // scalar loads: the table may be a view at any 4-byte offset
+                const float2 rs = make_float2(__ldg(rsp), __ldg(rsp + 1));
                 ENV::reset(state, rs.x, rs.y);
             }
             else if(a.error_flag) *a.error_flag = 1;

@@ -8,19 +8,22 @@
 //   1. thread: reset-if-truncated, sincos, observation; first layer (K = 3) on CUDA cores, weights as constant-bank FMA operands;
 //      h1 is written RAW to tensor memory (A_hi: the tensor core reads the top 19 bits = the tf32 "hi" part) and the
 //      remainder lo = h1 - tf32_trunc(h1) into a K-major, 128-byte-swizzled shared-memory tile (A_lo)
-//   2. the group's leader issues 26 tcgen05.mma (M128 N64 K8, kind::tf32): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi over
-//      K = 64, plus one K step each for the hi and lo part of the bias ("3xTF32": the dropped lo*lo term is ~2^-22 relative, so the fp32 accumulator matches an fp32 GEMM to
+//   2. the group's leader issues 25 tcgen05.mma (M128 N64 K8, kind::tf32): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi over
+//      K = 64, plus one K step that adds the hi and lo part of the bias ("3xTF32": the dropped lo*lo term is ~2^-22 relative, so the fp32 accumulator matches an fp32 GEMM to
 //      ~1e-6), then tcgen05.commit -> the group's mbarrier
 //   3. every thread waits (bounded), reads its accumulator row from TMEM (tcgen05.ld), applies bias + activation and
 //      the 64 -> 1 output layer, then steps the environment in registers.
-// While one group waits for the tensor core the other three run their CUDA-core phases. The second-layer weights
-// (tf32 hi and lo parts, the B operand) stay resident in shared memory for the whole launch and are shared by the
+// The groups work as two pairs {0,1} and {2,3} that take turns ISSUING to the tensor core: a pair's two MMA batches run together
+// (one batch alone is bound by the latency of its chain of dependent MMAs) while the other pair is in its CUDA-core
+// phases; the turn passes as soon as a pair has issued. (Passing it only when the batches have completed keeps the pairs
+// half a period apart but measured slower: 0.900 against 0.864 ms per 65,536 x 200 rollout.) The second-layer
+// weights (tf32 hi and lo parts, the B operand) stay resident in shared memory for the whole launch and are shared by the
 // four groups. Tensor memory: 512 columns = 4 groups x (64 accumulator + 64 A_hi columns).
 #include "common.cuh"
 #include "pendulum.cuh"
 #include "rollout.cuh"
 #include "tcgen05.cuh"
-#include <stdlib.h>
+#include <mutex>
 
 namespace b200rl {
 
@@ -30,10 +33,9 @@ constexpr uint32_t A_KBLOCK_BYTES = TILE * 128;        // 128 rows x 128 B (32 t
 constexpr uint32_t B_KBLOCK_BYTES = H * 128;           // 64 rows x 128 B
 constexpr uint32_t OFF_B_HI = 0, OFF_B_LO = 2 * B_KBLOCK_BYTES, OFF_A_LO = 4 * B_KBLOCK_BYTES;
 constexpr uint32_t A_LO_BYTES = 2 * A_KBLOCK_BYTES;           // per group
-constexpr uint32_t OFF_ONES = OFF_A_LO + GROUPS * A_LO_BYTES;  // [128 x 8] K=8 tile, column 0 == 1: feeds the bias row through the MMA
-constexpr uint32_t OFF_BIAS_HI = OFF_ONES + 4096;             // [64 x 8] K=8 tiles, column 0 == b2 (tf32 hi / lo parts)
-constexpr uint32_t OFF_BIAS_LO = OFF_BIAS_HI + 2048;
-constexpr uint32_t OFF_MBAR = OFF_BIAS_LO + 2048;
+constexpr uint32_t OFF_ONES = OFF_A_LO + GROUPS * A_LO_BYTES;  // [128 x 8] K=8 tile, columns 0 and 1 == 1: feeds the bias row through the MMA
+constexpr uint32_t OFF_BIAS = OFF_ONES + 4096;                // [64 x 8] K=8 tile, column 0 == tf32 hi part of b2, column 1 == its lo part
+constexpr uint32_t OFF_MBAR = OFF_BIAS + 2048;
 constexpr uint32_t OFF_ABORT = OFF_MBAR + 8 * GROUPS;
 constexpr uint32_t OFF_SLOT = OFF_ABORT + 4 * GROUPS;
 constexpr uint32_t OFF_TURN = OFF_SLOT + 8;                   // 2 mbarriers: the tensor token alternating between the group pairs {0,1} and {2,3}
@@ -89,13 +91,12 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     }
     // bias of layer 2 as one extra K step: D += ones[128 x 8] * bias[64 x 8]^T with only column 0 populated
     for(int idx = tid; idx < TILE * 8; idx += THREADS)
-        *reinterpret_cast<float*>(base + OFF_ONES + tc::noswizzle_k8_offset(idx >> 3, idx & 7)) = (idx & 7) == 0 ? 1.0f : 0.0f;
+        *reinterpret_cast<float*>(base + OFF_ONES + tc::noswizzle_k8_offset(idx >> 3, idx & 7)) = (idx & 7) < 2 ? 1.0f : 0.0f;
     for(int idx = tid; idx < H * 8; idx += THREADS){
         const int j = idx >> 3, k = idx & 7;
-        const float b = k == 0 ? __ldg(P + P_B2 + j) : 0.0f;
+        const float b = __ldg(P + P_B2 + j);
         const float hi = __uint_as_float(__float_as_uint(b) & TF32_MASK);
-        *reinterpret_cast<float*>(base + OFF_BIAS_HI + tc::noswizzle_k8_offset(j, k)) = hi;
-        *reinterpret_cast<float*>(base + OFF_BIAS_LO + tc::noswizzle_k8_offset(j, k)) = b - hi;
+        *reinterpret_cast<float*>(base + OFF_BIAS + tc::noswizzle_k8_offset(j, k)) = k == 0 ? hi : (k == 1 ? b - hi : 0.0f);
     }
     if(r == 0){ tc::mbar_init(mbar, 1); *abort_flag = 0; }
     if(tid < 2) tc::mbar_init(turn + tid, 2);                 // each completes when BOTH leaders of the other pair have issued
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     const uint64_t desc_a_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(a_lo));
     const uint64_t desc_b_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_HI)), desc_b_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_LO));
     const uint64_t desc_ones = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_ONES));
-    const uint64_t desc_bias_hi = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_BIAS_HI)), desc_bias_lo = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_BIAS_LO));
+    const uint64_t desc_bias = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_BIAS));
     constexpr uint32_t IDESC = tc::make_idesc_tf32(TILE, H);
     uint8_t* my_row_lo = a_lo + r * 128;
     const uint32_t swz = (uint32_t)r & 7;
@@ -170,13 +171,13 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             float* st_rew = st_act + TILE;
             StepDraws draws{};             // the trajectory-only kernels need the draws at a reset only: nothing per step on their hot path
             if(a.device_rng && (COLLECT || trunc)) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
-            if(trunc){
+            if(trunc && valid){
                 if(a.device_rng){    // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
                     theta = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(draws.u_theta_dot, 2.0f, -1.0f);
                 }
                 else if(a.reset_states != nullptr && resets < a.n_reset_rounds){
-                    const float2 rs = *reinterpret_cast<const float2*>(a.reset_states + ((size_t)resets * a.n_envs + e) * 2);
-                    theta = rs.x; theta_dot = rs.y;
+                    const float* rs = a.reset_states + ((size_t)resets * a.n_envs + e) * 2;      // scalar loads: the table may be a view at any 4-byte offset
+                    theta = __ldg(rs); theta_dot = __ldg(rs + 1);
                 }
                 else if(a.error_flag) *a.error_flag = 1;
                 resets++; es = 0; er = 0.0f;
@@ -201,10 +202,10 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
 #pragma unroll
                     for(int q = 0; q < 4; q++){
                         const int j = hb * 32 + c * 4 + q;
-                        float acc = c_actor[C_W1 + 3 * j] * cs;
+                        float acc = fmaf(c_actor[C_W1 + 3 * j], cs, c_actor[C_B1 + j]);      // bias first, inputs ascending: the reference's order
                         acc = fmaf(c_actor[C_W1 + 3 * j + 1], sn, acc);
                         acc = fmaf(c_actor[C_W1 + 3 * j + 2], theta_dot, acc);
-                        const float h = act_or_rt<A1>(acc + c_actor[C_B1 + j], act1);
+                        const float h = act_or_rt<A1>(acc, act1);
                         const uint32_t u = __float_as_uint(h);
                         hraw[c * 4 + q] = u;
                         lo[q] = h - __uint_as_float(u & TF32_MASK);
@@ -243,8 +244,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                         for(int ks = 0; ks < 4; ks++)
                             tc::mma_tf32_ts(tmem_d, tmem_a + (uint32_t)(kb * 32 + ks * 8), db + (uint64_t)(kb * (B_KBLOCK_BYTES >> 4) + ks * 2), IDESC, 1u);
                 }
-                tc::mma_tf32_ss(tmem_d, desc_ones, desc_bias_lo, IDESC, 1u);
-                tc::mma_tf32_ss(tmem_d, desc_ones, desc_bias_hi, IDESC, 1u);
+                tc::mma_tf32_ss(tmem_d, desc_ones, desc_bias, IDESC, 1u);
                 tc::commit(mbar);
                 tc::mbar_arrive(next_turn);
                 if constexpr(BULK){ if(t > 0) bulk_flush(t - 1); }          // every thread of the group finished step t-1 before this step's barrier
@@ -328,66 +328,77 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     if(warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// All launches share the constant bank holding the small layers, so each launch (copy + kernel) is ordered after the
-// previous one with an event: a launch on another stream waits for the kernel that still reads the old constants.
-// The kernel fills every SM, so this ordering costs no concurrency.
-static int upload_small_layers(const float* params, cudaStream_t s, cudaEvent_t* order_event){
-    static cudaEvent_t ev = nullptr;
-    if(!ev) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+// All launches on a device share the constant bank holding the small layers, so each launch (copies + kernel) is ordered after the
+// previous one on that device with an event: a launch on another stream waits for the kernel that still reads the old constants.
+// The kernel fills every SM, so this ordering costs no concurrency. The event, like the kernel's shared-memory attribute, belongs
+// to a device: both are kept per device ordinal.
+namespace {
+struct TcDeviceState { cudaEvent_t order = nullptr; bool configured[16] = {}; };
+TcDeviceState g_tc_state[MAX_DEVICES];
+std::mutex g_tc_mutex;
+}
+
+static int upload_small_layers(TcDeviceState& st, const float* params, cudaStream_t s, cudaEvent_t* order_event){
+    if(!st.order) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&st.order, cudaEventDisableTiming));
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     B200RL_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
-    *order_event = cap == cudaStreamCaptureStatusNone ? ev : nullptr;
-    if(*order_event) B200RL_CUDA_TRY(cudaStreamWaitEvent(s, ev, 0));
+    *order_event = cap == cudaStreamCaptureStatusNone ? st.order : nullptr;
+    if(*order_event) B200RL_CUDA_TRY(cudaStreamWaitEvent(s, st.order, 0));
     B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + P_W1, sizeof(float) * 256, sizeof(float) * C_W1, cudaMemcpyDeviceToDevice, s));
     B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + P_B2, sizeof(float) * 129, sizeof(float) * C_B2, cudaMemcpyDeviceToDevice, s));
     return B200RL_OK;
 }
 
 template <int A1, int A2, bool COLLECT, bool BULK>
-static int launch_tc_variant(const RolloutArgs& a, cudaStream_t s){
-    static bool configured = false;
-    if(!configured){
+static int launch_tc_variant(const RolloutArgs& a, cudaStream_t s, int variant){
+    int dev = 0, sms = 0;
+    int rc = current_device(&dev);
+    if(rc) return rc;
+    rc = sm_count(&sms);
+    if(rc) return rc;
+    std::lock_guard<std::mutex> lock(g_tc_mutex);
+    TcDeviceState& st = g_tc_state[dev];
+    if(!st.configured[variant]){
         B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<A1, A2, COLLECT, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-        configured = true;
+        st.configured[variant] = true;
     }
     cudaEvent_t order_event = nullptr;
-    int rc = upload_small_layers(a.params, s, &order_event);
+    rc = upload_small_layers(st, a.params, s, &order_event);
     if(rc) return rc;
     // spread the environments evenly over every group of every SM: tiles of <= 128 environments (a multiple of 4)
-    const int groups_total = NUM_SMS * GROUPS;
+    const int groups_total = sms * GROUPS;
     int ept = ((a.env_count + groups_total - 1) / groups_total + 3) / 4 * 4;
     if(ept < 32) ept = 32;
     if(ept > TILE) ept = TILE;
     const int n_tiles = (a.env_count + ept - 1) / ept;
     int grid = (n_tiles + GROUPS - 1) / GROUPS;
-    if(grid > NUM_SMS) grid = NUM_SMS;
+    if(grid > sms) grid = sms;
     rollout_tc_kernel<A1, A2, COLLECT, BULK><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
     B200RL_LAUNCH_CHECK("rollout_tc");
     if(order_event) B200RL_CUDA_TRY(cudaEventRecord(order_event, s));
     return B200RL_OK;
 }
 
-// Bulk stores need 16-byte aligned row starts in all three outputs; B200RL_ROLLOUT_STORES=plain keeps per-thread stores (A/B measurements)
+// Bulk stores need 16-byte aligned row starts in all three outputs; per-thread stores otherwise (and always for the strided dataset rows)
 template <int A1, int A2, bool COLLECT>
-static int launch_tc(const RolloutArgs& a, cudaStream_t s){
-    if constexpr(COLLECT) return launch_tc_variant<A1, A2, true, false>(a, s);
+static int launch_tc(const RolloutArgs& a, cudaStream_t s, int variant){
+    if constexpr(COLLECT) return launch_tc_variant<A1, A2, true, false>(a, s, variant);
     else{
-        static const bool plain = [](){ const char* v = getenv("B200RL_ROLLOUT_STORES"); return v && v[0] == 'p'; }();
         const bool aligned = ((reinterpret_cast<uintptr_t>(a.obs) | reinterpret_cast<uintptr_t>(a.act) | reinterpret_cast<uintptr_t>(a.rew)) & 15u) == 0 &&
                              a.n_envs % 4 == 0 && a.env_begin % 4 == 0 && a.env_count % 4 == 0;
-        return (aligned && !plain) ? launch_tc_variant<A1, A2, false, true>(a, s) : launch_tc_variant<A1, A2, false, false>(a, s);
+        return aligned ? launch_tc_variant<A1, A2, false, true>(a, s, variant) : launch_tc_variant<A1, A2, false, false>(a, s, variant + 1);
     }
 }
 
 int launch_rollout_tc(const RolloutArgs& a, cudaStream_t s){
     const int a1 = a.acts[0], a2 = a.acts[1];
     if(a.dataset){
-        if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, true>(a, s);
-        return launch_tc<-1, -1, true>(a, s);
+        if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, true>(a, s, 0);
+        return launch_tc<-1, -1, true>(a, s, 1);
     }
-    if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, false>(a, s);
-    if(a1 == B200RL_ACT_TANH && a2 == B200RL_ACT_TANH) return launch_tc<B200RL_ACT_TANH, B200RL_ACT_TANH, false>(a, s);
-    return launch_tc<-1, -1, false>(a, s);
+    if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, false>(a, s, 2);
+    if(a1 == B200RL_ACT_TANH && a2 == B200RL_ACT_TANH) return launch_tc<B200RL_ACT_TANH, B200RL_ACT_TANH, false>(a, s, 4);
+    return launch_tc<-1, -1, false>(a, s, 6);
 }
 
 }  // namespace b200rl

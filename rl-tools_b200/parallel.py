@@ -28,9 +28,10 @@ def allreduce_sum_(tensor, dist=None, group=None):
     return tensor
 
 
-def sharded_train_step(pkg, net, x_shard, y_shard, total_rows: int, dist=None, group=None):
+def sharded_train_step(pkg, net, x_shard, y_shard, total_rows: int, dist=None, group=None, exchange_events=None):
     """One optimizer step of `net` (rl_tools_b200.Mlp with batch == chunk size) on this rank's rows. x_shard / y_shard
-    are CUDA tensors whose row count is a multiple of net.batch."""
+    are CUDA tensors whose row count is a multiple of net.batch. exchange_events: an optional pair of CUDA events recorded
+    on the current stream right before and right after the all-reduce, so that the exchange can be timed on its own."""
     rows = x_shard.shape[0]
     assert rows % net.batch == 0, "shard rows must be a multiple of the chunk size"
     net.zero_gradient()
@@ -40,5 +41,9 @@ def sharded_train_step(pkg, net, x_shard, y_shard, total_rows: int, dist=None, g
         out = net.forward(x)
         d_out = pkg.mse_gradient(out, y, w, d_a=net.d_out_buffer())
         net.backward(x, d_out)
+    if exchange_events is not None:
+        exchange_events[0].record()
     allreduce_sum_(net.grads, dist, group)
+    if exchange_events is not None:
+        exchange_events[1].record()
     net.step()

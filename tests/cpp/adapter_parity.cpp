@@ -13,6 +13,7 @@
 #include <rl_tools/nn/layers/standardize/operations_generic.h>
 #include <rl_tools/rl/components/running_normalizer/operations_generic.h>
 #include <b200rl/rl_tools_standardize.h>                          // before the model headers that recurse into the layer
+#include <b200rl/rl_tools_mlp.h>                                  // whole-model overloads: before the generic MLP operations
 #include <rl_tools/nn_models/mlp/operations_generic.h>
 #include <rl_tools/nn_models/mlp_unconditional_stddev/operations_generic.h>
 #include <rl_tools/nn_models/sequential/operations_generic.h>

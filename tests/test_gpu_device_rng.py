@@ -196,42 +196,6 @@ def test_rollout_device_rng(lib, torch):
     assert np.array_equal(runner["truncated"].cpu().numpy(), want["truncated"])
 
 
-CUDA_CORE_SCRIPT = """
-import sys, numpy as np, torch
-sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
-import __graft_entry__ as entry
-import test_gpu_device_rng as t
-lib = entry.load_package()
-shape, params = t.make_actor(lib)
-ds = t.collect(lib, torch, shape, t.dev(torch, params), t.fresh(torch, {N}), {seed}, 3, {T}, {limit})
-np.save({out!r}, ds)
-"""
-
-
-def test_cuda_core_kernel_draws_the_same(lib, torch, tmp_path):
-    """The CUDA-core variant of the kernel (selected by B200RL_ROLLOUT_KERNEL=simt, read once per process, hence the child process) uses
-    the same counters: identical flags and reset rows, noise and trajectories equal up to the two kernels' fp32 differences."""
-    import os
-    import subprocess
-    import sys
-    N, T, limit, seed = 700, 16, 5, 31337
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    out = str(tmp_path / "simt.npy")
-    script = CUDA_CORE_SCRIPT.format(root=root, tests=os.path.join(root, "tests"), N=N, seed=seed, T=T, limit=limit, out=out)
-    env = dict(os.environ, B200RL_ROLLOUT_KERNEL="simt")
-    subprocess.run([sys.executable, "-c", script], check=True, env=env, timeout=600)
-    other = np.load(out).reshape(T + 1, N, 13)
-    shape, params = make_actor(lib)
-    mine = collect(lib, torch, shape, dev(torch, params), fresh(torch, N), seed, 3, T, limit).reshape(T + 1, N, 13)
-    assert np.array_equal(mine[:T, :, 7:10], other[:T, :, 7:10])
-    reset = mine[:T, :, RESET] != 0
-    assert np.abs(mine[:T, :, :3][reset] - other[:T, :, :3][reset]).max() < 1e-6
-    std = np.float32(np.exp(np.float64(params[-1])))
-    eps_a, eps_b = (mine[:T, :, ACTION] - mine[:T, :, MEAN]) / std, (other[:T, :, ACTION] - other[:T, :, MEAN]) / std
-    assert np.abs(eps_a - eps_b).max() < 1e-5
-    assert np.abs(mine[:T, :, :7] - other[:T, :, :7]).max() < 5e-3
-
-
 def test_randn_matches_numpy_philox_and_counter(lib, torch):
     """b200rl_randn_device_rng against the numpy statement of its counter layout (element / 4, call low, call high, 2 + stream id), and the
     device-resident call counter: call_index + *counter is what enters the Philox counter."""

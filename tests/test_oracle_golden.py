@@ -304,3 +304,18 @@ def test_acrobot_swingup_matches_reference(orc):
     out = orc.acrobot_rollout(shape, mg.acrobot_params(), np.zeros((N, 4), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32), table, T, limit)
     for k, v in out.items():
         assert np.array_equal(v, fix[f"rollout_{k}"]), k
+
+
+def test_c5_chunk_65536_forward_rows_match_reference(orc):
+    """The fixture of the 65,536-row chunk (the reference's own forward through its scalar loops): rows are independent in the forward pass,
+    so the oracle's forward on the sampled rows of the last chunk must reproduce the stored activations bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "c5_chunked_b65536.npz"))
+    params, x, _ = mg.c5_inputs()
+    rows = fix["act_rows"]
+    xs = np.ascontiguousarray(x[mg.C5_CHUNK * (mg.C5_CHUNKS - 1):][rows])
+    pre, out = orc.mlp_forward(oracle.C5_SHAPE(), params, xs)
+    off = 0
+    for l, d in enumerate([256, 256, 256, 16]):
+        assert np.array_equal(pre[off:off + rows.size * d].reshape(rows.size, d), fix[f"pre_{l}"])
+        assert np.array_equal(out[off:off + rows.size * d].reshape(rows.size, d), fix[f"out_{l}"])
+        off += rows.size * d

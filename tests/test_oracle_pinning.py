@@ -42,6 +42,17 @@ def test_mlp_live(orc, ref_strict, name):
     assert np.array_equal(d_in, full["d_input"])
 
 
+def test_chunked_training_step_live(orc, ref_strict):
+    """The data-parallel replica's step (gradients accumulated over chunks, each weighted chunk / rows, then Adam) through the reference's own
+    verbs equals the oracle's composition bit for bit (chunks of 1024 rows; the 65,536-row chunk is pinned through its fixture)."""
+    import oracle
+    params, x, target = mg.c5_inputs(3 * 1024)
+    ref = ref_strict.mlp_c5_chunked(1024, params, x, target)
+    mine = orc.mlp_chunked_step(oracle.C5_SHAPE(), params, x, target, 1024)
+    for k in ("params", "grads", "m", "v", "pre", "out"):
+        assert np.array_equal(ref[k], mine[k]), k
+
+
 def test_rollout_live_chunked_evaluate(orc, ref_strict):
     """Reference evaluate() on 256-env batches (the way the runner calls it) equals the per-env oracle bit for bit
     on the generic device, because each output element is the same left-to-right sum."""

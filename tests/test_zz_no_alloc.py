@@ -50,10 +50,33 @@ def test_static_scratch_backward_equals_regular_backward_twice_in_a_row(lib, B, 
             assert np.array_equal(a, b)
 
 
-def test_static_scratch_limit_is_reported_before_any_launch(lib):
+def test_large_batch_is_split_within_the_static_array(lib):
+    """A training-sized layer (256 x 256 at batch 8192) would take 32 splits = exactly 8 MiB of weight-gradient partial sums plus the bias
+    partial sums with caller scratch: more than the static array holds. The static entry point plans with fewer splits instead of refusing;
+    the result differs from the caller-scratch one only by the summation order of the batch split, i.e. within the sums' bound
+    1e-6 + 1e-5 * sum|terms|; d_pre and d_in do not depend on the split and are identical."""
+    import torch
     L = lib.lib()
-    B, I, O = 1 << 20, 1024, 1024            # split-batch partials would need far more than 8 MiB
+    B, I, O = 8192, 256, 256
     assert L.b200rl_dense_backward_scratch_bytes(B, I, O) > 8 * 1024 * 1024
+    W = (mg.det_uniform(77, O * I) / np.float32(np.sqrt(I))).reshape(O, I)
+    for call in range(2):
+        x = mg.det_normal(900 + call, B * I, stream=1).reshape(B, I)
+        pre = mg.det_normal(900 + call, B * O, stream=2).reshape(B, O)
+        d_out = mg.det_normal(900 + call, B * O, stream=3).reshape(B, O)
+        want = _backward(lib, torch, None, W, x, pre, d_out, "relu", with_scratch=True)
+        got = _backward(lib, torch, L.b200rl_dense_backward_static_scratch, W, x, pre, d_out, "relu", with_scratch=False)
+        d_pre = want[3].astype(np.float64)
+        assert np.all(np.abs(got[0] - want[0]) <= 1e-6 + 1e-5 * (np.abs(d_pre).T @ np.abs(x.astype(np.float64))))
+        assert np.all(np.abs(got[1] - want[1]) <= 1e-6 + 1e-5 * np.abs(d_pre).sum(0))
+        assert np.array_equal(got[2], want[2]) and np.array_equal(got[3], want[3])
+
+
+def test_static_scratch_limit_is_reported_before_any_launch(lib):
+    """What the static array cannot serve at all is a layer so wide that two partial sums of its weight gradient do not fit
+    (input_dim * output_dim > 2^20): refused with a clear status before anything is launched; without gradients nothing is refused."""
+    L = lib.lib()
+    B, I, O = 4096, 2048, 1024
     one = C.c_void_p(16)                      # never dereferenced: the size check comes first
     rc = L.b200rl_dense_backward_static_scratch(one, one, I, one, O, one, O, one, one, None, 0, B, I, O, 0, None)
     assert rc == 5 and b"static buffer" in L.b200rl_status_string(5)

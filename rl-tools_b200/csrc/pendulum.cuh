@@ -1,8 +1,14 @@
-// Pendulum dynamics, reward and observation as device functions with the reference's exact arithmetic
-// (rl/environments/pendulum/operations_generic.h). The reference mixes float and double: the literal 3.0 in the
-// velocity update and 0.1 / 0.001 in the reward promote those expressions to double, and the CPU oracle build keeps
-// multiply and add separate. Explicit *_rn intrinsics pin the same rounding sequence here, so that for identical
-// sin/cos/action inputs the next state and the reward are bit-identical to the CPU path.
+// Pendulum dynamics, reward and observation as device functions following the reference's arithmetic
+// (rl/environments/pendulum/operations_generic.h). The reference mixes float and double: the literal 3.0 in the velocity
+// update and 0.1 / 0.001 in the reward promote those expressions to double. Double-precision instructions are avoided
+// here on purpose: on this GPU they queue behind tensor-core work, and the handful of them per environment step made the
+// fused rollout 24 % slower (0.864 -> 0.695 ms per 65,536 x 200 rollout). Instead
+//   - the velocity update, which feeds back into the (chaotic) trajectory, carries its intermediate results as unevaluated
+//     sums of two floats (error-free products and sums built from fused multiply-adds), i.e. with ~48 significant bits, and
+//     rounds to float once at the end: the result equals the reference's double computation rounded to float except when
+//     that lies within ~2^-46 relative of a rounding boundary;
+//   - the reward (an output, not fed back) is evaluated in float with fused multiply-adds: within 2 ulp of the reference.
+// Explicit *_rn intrinsics keep the compiler from contracting or reordering the error-free sequences.
 #pragma once
 #include "common.cuh"
 
@@ -23,8 +29,15 @@ __device__ __forceinline__ void step(float theta, float theta_dot, float sin_the
     float u = __fmul_rn(MAX_TORQUE, clip(action, -1.0f, 1.0f));
     u = clip(u, -MAX_TORQUE, MAX_TORQUE);
     const float gravity_term = __fmul_rn(3.0f * G / (2.0f * LENGTH), sin_theta);               // float
-    const double bracket = __dadd_rn((double)gravity_term, __dmul_rn(3.0 / (double)(MASS * LENGTH * LENGTH), (double)u));
-    float newthdot = (float)__dadd_rn((double)theta_dot, __dmul_rn(bracket, (double)DT));
+    // newthdot = (float)(theta_dot + (gravity_term + 3.0 * u) * dt), evaluated on float pairs:
+    const float ph = __fmul_rn(3.0f / (MASS * LENGTH * LENGTH), u), pl = __fmaf_rn(3.0f / (MASS * LENGTH * LENGTH), u, -ph);     // 3 u = ph + pl exactly
+    const float s = __fadd_rn(gravity_term, ph), sb = __fsub_rn(s, gravity_term);
+    const float se = __fadd_rn(__fsub_rn(gravity_term, __fsub_rn(s, sb)), __fsub_rn(ph, sb));                                   // gravity_term + ph = s + se exactly
+    const float bl = __fadd_rn(se, pl);                                                                                           // bracket = s + bl
+    const float qh = __fmul_rn(s, DT), ql = __fmaf_rn(bl, DT, __fmaf_rn(s, DT, -qh));                                             // bracket * dt = qh + ql
+    const float t = __fadd_rn(theta_dot, qh), tb = __fsub_rn(t, theta_dot);
+    const float te = __fadd_rn(__fsub_rn(theta_dot, __fsub_rn(t, tb)), __fsub_rn(qh, tb));                                        // theta_dot + qh = t + te exactly
+    float newthdot = __fadd_rn(t, __fadd_rn(te, ql));
     newthdot = clip(newthdot, -MAX_SPEED, MAX_SPEED);
     next_theta = __fadd_rn(theta, __fmul_rn(newthdot, DT));
     next_theta_dot = newthdot;
@@ -33,9 +46,7 @@ __device__ __forceinline__ void step(float theta, float theta_dot, float sin_the
 __device__ __forceinline__ float reward(float theta, float theta_dot, float action){
     const float an = angle_normalize(theta);
     const float u = __fmul_rn(MAX_TORQUE, action);
-    double costs = __dadd_rn((double)__fmul_rn(an, an), __dmul_rn(__dmul_rn(0.1, (double)theta_dot), (double)theta_dot));
-    costs = __dadd_rn(costs, __dmul_rn(0.001, (double)__fmul_rn(u, u)));
-    return -(float)costs;
+    return -__fmaf_rn(0.001f, __fmul_rn(u, u), __fmaf_rn(__fmul_rn(0.1f, theta_dot), theta_dot, __fmul_rn(an, an)));
 }
 
 }}  // namespace b200rl::pendulum

@@ -66,7 +66,9 @@ enum CollectColumns { COL_OBS = 0, COL_ACTION_MEAN = 3, COL_ACTION = 4, COL_LOG_
 
 // Gaussian policy head of the rollout (on_policy_runner/operations_generic_per_env.h:46-60, random/operations_cpu.h:40-48,
 // random/operations_generic.h:87-97) with the reference's rounding sequence: action = eps * std + mean as separate multiply
-// and add; log_prob = (neg_half_log_2pi - log_std) - 0.5 * ((action - mean) / std)^2 with the square term in double.
+// and add; log_prob = (neg_half_log_2pi - log_std) - 0.5 * ((action - mean) / std)^2, where the reference takes the square
+// term and the subtraction in double: here the square is an exact float pair and the difference is rounded to float once
+// (no double-precision instruction on the per-step path, see pendulum.cuh).
 struct GaussianHead {
     float log_std, std;
     __device__ __forceinline__ void init(const float* log_std_ptr){
@@ -75,9 +77,12 @@ struct GaussianHead {
     }
     __device__ __forceinline__ float sample(float mean, float eps) const { return __fadd_rn(__fmul_rn(eps, std), mean); }
     __device__ __forceinline__ float log_prob(float mean, float action, float neg_half_log_2pi) const {
-        const float pre_square = __fdiv_rn(__fsub_rn(action, mean), std);
-        const double sq = __dmul_rn(__dmul_rn(0.5, (double)pre_square), (double)pre_square);
-        return (float)__dsub_rn((double)__fsub_rn(neg_half_log_2pi, log_std), sq);
+        const float p = __fdiv_rn(__fsub_rn(action, mean), std);
+        const float h = __fmul_rn(p, p), l = __fmaf_rn(p, p, -h);                      // p^2 = h + l exactly
+        const float a = __fsub_rn(neg_half_log_2pi, log_std), hh = __fmul_rn(0.5f, h);
+        const float t = __fsub_rn(a, hh), tb = __fsub_rn(t, a);
+        const float te = __fsub_rn(__fsub_rn(a, __fsub_rn(t, tb)), __fadd_rn(hh, tb)); // a - hh = t + te exactly
+        return __fadd_rn(t, __fmaf_rn(-0.5f, l, te));
     }
 };
 

@@ -174,7 +174,11 @@ def test_collect_full_size_properties(lib, torch):
     ps = (body[:, :, ACTION] - body[:, :, MEAN]) / std
     c0 = np.float32(-0.5 * np.float32(np.log(np.float64(np.float32(2 * np.float32(np.pi))))))      # the host's logf, correctly rounded
     lp = (c0 - params[-1]).astype(np.float64) - 0.5 * ps.astype(np.float64) * ps.astype(np.float64)
-    assert np.array_equal(body[:, :, LOGP], lp.astype(np.float32))
+    # the kernel carries the square as an exact float pair and rounds the difference once, where the reference rounds to double and then to
+    # float: the two agree except where the double result lies next to a float rounding boundary, and then they are neighbouring floats
+    got_lp, want_lp = body[:, :, LOGP], lp.astype(np.float32)
+    differs = got_lp != want_lp
+    assert differs.mean() < 1e-5 and np.all(np.abs(got_lp - want_lp)[differs] <= np.spacing(np.abs(want_lp[differs])))
     obs = ds[:, OBS]
     assert np.abs(obs[:, 0].astype(np.float64) ** 2 + obs[:, 1].astype(np.float64) ** 2 - 1).max() < 1e-6
     assert np.abs(obs[:, 2]).max() <= 8.0 and body[:, :, REWARD].max() <= 0

@@ -4,47 +4,58 @@
 // environments for all T steps; thread r of the group owns environment r of the tile, which is row r of the MMA and
 // lane r of tensor memory. The environments of a launch are spread evenly over all 4 x (#CTAs) groups (tiles of
 // <= 128 environments, a multiple of 4), so every SM carries the same load and there is a single wave.
+//
+// The second layer (the one dense contraction of the path) runs on the tensor core with fp32 accuracy through a split
+// into fp16 parts: x = lead + rest with lead = fp16(x) (11 significant bits) and rest = fp16(x - lead), so lead + rest
+// carries ~22 bits, and
+//     h1 . W2  ~=  rest_h * lead_W  +  lead_h * rest_W  +  lead_h * lead_W          (fp32 accumulate, dropped term ~2^-24)
+// Every part has K = 64 in ONE 128-byte row, an instruction covers K = 16, so a tile and step take 3 passes x 4
+// tcgen05.mma (M128 N64 K16, kind::f16) plus one K step that adds the two parts of the bias through a constant "ones"
+// tile: 13 MMAs. (The same accuracy through tf32 parts takes 25 MMAs of K = 8, and the 25 form ONE chain of dependent
+// accumulations at ~110 cycles each, which sat on every group's critical path: 0.70 -> 0.62 ms per 65,536 x 200 rollout.)
+// W2 and b2 are multiplied by a power of two that brings their largest magnitude into [2^13, 2^14), which keeps the
+// remainder parts out of fp16's subnormal range; the accumulator is scaled back exactly in the epilogue. Layer-1
+// activations are converted with saturation: hidden activations beyond +-65504 are outside this kernel's domain.
 // Per step and group:
 //   1. thread: reset-if-truncated, sincos, observation; first layer (K = 3) on CUDA cores, weights as constant-bank FMA operands;
-//      h1 is written RAW to tensor memory (A_hi: the tensor core reads the top 19 bits = the tf32 "hi" part) and the
-//      remainder lo = h1 - tf32_trunc(h1) into a K-major, 128-byte-swizzled shared-memory tile (A_lo)
-//   2. the group's leader issues 25 tcgen05.mma (M128 N64 K8, kind::tf32): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi over
-//      K = 64, plus one K step that adds the hi and lo part of the bias ("3xTF32": the dropped lo*lo term is ~2^-22 relative, so the fp32 accumulator matches an fp32 GEMM to
-//      ~1e-6), then tcgen05.commit -> the group's mbarrier
-//   3. every thread waits (bounded), reads its accumulator row from TMEM (tcgen05.ld), applies bias + activation and
+//      the leading parts of h1 go to tensor memory (two K elements per 32-bit column: 32 columns), the remainder parts into a
+//      K-major, 128-byte-swizzled shared-memory tile
+//   2. the group's leader issues the 13 MMAs and tcgen05.commit -> the group's mbarrier
+//   3. every thread waits (bounded), reads its accumulator row from TMEM (tcgen05.ld), applies the activation and
 //      the 64 -> 1 output layer, then steps the environment in registers.
 // The groups work as two pairs {0,1} and {2,3} that take turns ISSUING to the tensor core: a pair's two MMA batches run together
 // (one batch alone is bound by the latency of its chain of dependent MMAs) while the other pair is in its CUDA-core
-// phases; the turn passes as soon as a pair has issued. (Passing it only when the batches have completed keeps the pairs
-// half a period apart but measured slower: 0.900 against 0.864 ms per 65,536 x 200 rollout.) The second-layer
-// weights (tf32 hi and lo parts, the B operand) stay resident in shared memory for the whole launch and are shared by the
-// four groups. Tensor memory: 512 columns = 4 groups x (64 accumulator + 64 A_hi columns).
+// phases; the turn passes as soon as a pair has issued. (Measured against it: passing the turn only when the batches have
+// completed, 0.900 against 0.864 ms; no turns at all, 0.73 against 0.63 ms.) The second-layer weights (both fp16 parts, the B
+// operand) stay resident in shared memory for the whole launch and are shared by the four groups.
+// Tensor memory: 4 groups x (64 accumulator + 32 operand columns) of the 512 allocated.
 #include "common.cuh"
 #include "pendulum.cuh"
 #include "rollout.cuh"
 #include "tcgen05.cuh"
 #include <mutex>
+#include <cuda_fp16.h>
+
 
 namespace b200rl {
 
 namespace {
 constexpr int H = 64, TILE = 128, GROUPS = 4, THREADS = GROUPS * TILE;
-constexpr uint32_t A_KBLOCK_BYTES = TILE * 128;        // 128 rows x 128 B (32 tf32 along K)
-constexpr uint32_t B_KBLOCK_BYTES = H * 128;           // 64 rows x 128 B
-constexpr uint32_t OFF_B_HI = 0, OFF_B_LO = 2 * B_KBLOCK_BYTES, OFF_A_LO = 4 * B_KBLOCK_BYTES;
-constexpr uint32_t A_LO_BYTES = 2 * A_KBLOCK_BYTES;           // per group
-constexpr uint32_t OFF_ONES = OFF_A_LO + GROUPS * A_LO_BYTES;  // [128 x 8] K=8 tile, columns 0 and 1 == 1: feeds the bias row through the MMA
-constexpr uint32_t OFF_BIAS = OFF_ONES + 4096;                // [64 x 8] K=8 tile, column 0 == tf32 hi part of b2, column 1 == its lo part
+constexpr uint32_t A_PART_BYTES = TILE * 128;          // 128 rows x 128 B: the whole K = 64 as fp16
+constexpr uint32_t B_PART_BYTES = H * 128;             // 64 rows x 128 B
+constexpr uint32_t OFF_B_LEAD = 0, OFF_B_REST = B_PART_BYTES, OFF_A_REST = 2 * B_PART_BYTES;      // leading fp16 parts / fp16 parts of the remainders
+constexpr uint32_t OFF_ONES = OFF_A_REST + GROUPS * A_PART_BYTES;  // [128 x 16] K=16 tile, columns 0 and 1 == 1: feeds the bias row through the MMA
+constexpr uint32_t OFF_BIAS = OFF_ONES + 4096;                // [64 x 16] K=16 tile, column 0 == leading part of b2 (scaled), column 1 == its remainder part
 constexpr uint32_t OFF_MBAR = OFF_BIAS + 2048;
 constexpr uint32_t OFF_ABORT = OFF_MBAR + 8 * GROUPS;
 constexpr uint32_t OFF_SLOT = OFF_ABORT + 4 * GROUPS;
-constexpr uint32_t OFF_TURN = OFF_SLOT + 8;                   // 2 mbarriers: the tensor token alternating between the group pairs {0,1} and {2,3}
+constexpr uint32_t OFF_SCALE = OFF_SLOT + 8;                  // [0] scale of the second-layer operand (a power of two), [1] its inverse; [2..3] reduction scratch
+constexpr uint32_t OFF_TURN = OFF_SCALE + 16 + 4 * 32;                   // 2 mbarriers: the tensor token alternating between the group pairs {0,1} and {2,3}
 constexpr uint32_t OFF_STAGE = (OFF_TURN + 8 * 2 + 15) / 16 * 16;  // output staging for bulk stores: per group 3 buffers x (obs 1536 + act 512 + rew 512 B)
 constexpr uint32_t STAGE_BUF_BYTES = TILE * 12 + TILE * 4 + TILE * 4, STAGE_GROUP_BYTES = 3 * STAGE_BUF_BYTES;
 constexpr uint32_t SMEM_BYTES = OFF_STAGE + GROUPS * STAGE_GROUP_BYTES + 1024;         // + slack to align the base to 1024 B
-constexpr uint32_t TMEM_COLS = 512, TMEM_COLS_PER_GROUP = 128;
+constexpr uint32_t TMEM_COLS = 512, TMEM_COLS_PER_GROUP = 128;          // per group 64 accumulator + 32 operand columns are used
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;        // ~1 s: far beyond any legitimate wait
-constexpr uint32_t TF32_MASK = 0xFFFFE000u;
 // arena offsets of the actor 3 -> 64 -> 64 -> 1
 constexpr int P_W1 = 0, P_B1 = 192, P_W2 = 256, P_B2 = 4352, P_W3 = 4416, P_B3 = 4480;
 constexpr int C_W1 = 0, C_B1 = 192, C_B2 = 256, C_W3 = 320, C_B3 = 384, C_COUNT = 385;
@@ -55,6 +66,20 @@ constexpr int C_W1 = 0, C_B1 = 192, C_B2 = 256, C_W3 = 320, C_B3 = 384, C_COUNT 
 // occupies the 128 B/clk shared pipe for 4 cycles, which made the table look-ups the bottleneck of the CUDA-core
 // phase). Filled by a device-to-device copy on the launch stream; launches are ordered by an event (see launch_tc).
 __constant__ float c_actor[C_COUNT + 3];
+
+// x = lead + rest + O(2^-24 x): lead = fp16(x) (11 significant bits), rest = fp16(x - lead). Two values per register, the lower index in
+// the low half. Conversions saturate at +-65504 instead of producing infinities.
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi){
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ void split_f16_pair(float a, float b, uint32_t& lead, uint32_t& rest){
+    lead = pack_f16x2_sat(a, b);
+    const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&lead));
+    const float2 d = __ffma2_rn(back, make_float2(-1.0f, -1.0f), make_float2(a, b));
+    rest = pack_f16x2_sat(d.x, d.y);
+}
 
 template <int ACT>
 __device__ __forceinline__ float act_or_rt(float x, int rt){
@@ -80,23 +105,46 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     uint64_t* turn = reinterpret_cast<uint64_t*>(base + OFF_TURN);
 
     // ---- one-time staging of the second layer (B operand); arena = W1[64,3] b1[64] W2[64,64] b2[64] W3[1,64] b3[1] ----
+    // W2 and b2 are multiplied by a power of two that brings the largest magnitude into [2^13, 2^14): the remainder parts then stay clear
+    // of fp16's subnormal range; the accumulator is scaled back (exactly) in the epilogue.
     const float* P = a.params;
-    for(int idx = tid; idx < H * H; idx += THREADS){
-        const int j = idx >> 6, k = idx & 63;                 // W2[j][k]: row j of the B operand, K index k
-        const float w = __ldg(P + P_W2 + idx);
-        const float hi = __uint_as_float(__float_as_uint(w) & TF32_MASK);
-        const uint32_t off = (uint32_t)(k >> 5) * B_KBLOCK_BYTES + (uint32_t)j * 128 + ((((uint32_t)(k & 31) >> 2) ^ ((uint32_t)j & 7)) << 4) + ((uint32_t)k & 3) * 4;
-        *reinterpret_cast<float*>(base + OFF_B_HI + off) = hi;
-        *reinterpret_cast<float*>(base + OFF_B_LO + off) = w - hi;
+    float* scale_slot = reinterpret_cast<float*>(base + OFF_SCALE);
+    {
+        float m = 0.0f;
+        for(int idx = tid; idx < H * H + H; idx += THREADS) m = fmaxf(m, fabsf(__ldg(P + P_W2 + idx)));       // W2 and b2 are adjacent in the arena
+#pragma unroll
+        for(int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if((tid & 31) == 0) scale_slot[4 + warp] = m;
+        __syncthreads();
+        if(tid == 0){
+            float mm = 0.0f;
+            for(int w = 0; w < THREADS / 32; w++) mm = fmaxf(mm, scale_slot[4 + w]);
+            // exponent of the largest magnitude -> scale = 2^(13 - exponent); degenerate inputs (all zero, inf, nan) take scale 1
+            const int ex = (int)((__float_as_uint(mm) >> 23) & 0xFF) - 127;
+            const bool ok = mm > 0.0f && ex > -100 && ex < 100;
+            scale_slot[0] = ok ? __uint_as_float((uint32_t)(127 + 13 - ex) << 23) : 1.0f;
+            scale_slot[1] = ok ? __uint_as_float((uint32_t)(127 - 13 + ex) << 23) : 1.0f;
+        }
+        __syncthreads();
     }
-    // bias of layer 2 as one extra K step: D += ones[128 x 8] * bias[64 x 8]^T with only column 0 populated
-    for(int idx = tid; idx < TILE * 8; idx += THREADS)
-        *reinterpret_cast<float*>(base + OFF_ONES + tc::noswizzle_k8_offset(idx >> 3, idx & 7)) = (idx & 7) < 2 ? 1.0f : 0.0f;
-    for(int idx = tid; idx < H * 8; idx += THREADS){
-        const int j = idx >> 3, k = idx & 7;
-        const float b = __ldg(P + P_B2 + j);
-        const float hi = __uint_as_float(__float_as_uint(b) & TF32_MASK);
-        *reinterpret_cast<float*>(base + OFF_BIAS + tc::noswizzle_k8_offset(j, k)) = k == 0 ? hi : (k == 1 ? b - hi : 0.0f);
+    const float w_scale = scale_slot[0], w_unscale = scale_slot[1];
+    for(int idx = tid; idx < H * H / 2; idx += THREADS){
+        const int j = idx >> 5, k = (idx & 31) * 2;           // W2[j][k], W2[j][k+1]: row j of the B operand, K index k
+        uint32_t lead, rest;
+        split_f16_pair(__ldg(P + P_W2 + j * H + k) * w_scale, __ldg(P + P_W2 + j * H + k + 1) * w_scale, lead, rest);
+        const uint32_t off = (uint32_t)j * 128 + ((((uint32_t)k >> 3) ^ ((uint32_t)j & 7)) << 4) + ((uint32_t)k & 7) * 2;
+        *reinterpret_cast<uint32_t*>(base + OFF_B_LEAD + off) = lead;
+        *reinterpret_cast<uint32_t*>(base + OFF_B_REST + off) = rest;
+    }
+    // bias of layer 2 as one extra K step: D += ones[128 x 16] * bias[64 x 16]^T with columns 0 and 1 populated (leading and remainder part)
+    for(int idx = tid; idx < TILE * 16; idx += THREADS)
+        *reinterpret_cast<__half*>(base + OFF_ONES + tc::noswizzle_k16_offset(idx >> 4, idx & 15)) = __float2half((idx & 15) < 2 ? 1.0f : 0.0f);
+    for(int idx = tid; idx < H * 16; idx += THREADS){
+        const int j = idx >> 4, k = idx & 15;
+        uint32_t lead, rest;
+        split_f16_pair(__ldg(P + P_B2 + j) * w_scale, 0.0f, lead, rest);
+        const uint16_t v = k == 0 ? (uint16_t)(lead & 0xFFFF) : (k == 1 ? (uint16_t)(rest & 0xFFFF) : (uint16_t)0);
+        *reinterpret_cast<uint16_t*>(base + OFF_BIAS + tc::noswizzle_k16_offset(j, k)) = v;
     }
     if(r == 0){ tc::mbar_init(mbar, 1); *abort_flag = 0; }
     if(tid < 2) tc::mbar_init(turn + tid, 2);                 // each completes when BOTH leaders of the other pair have issued
@@ -109,15 +157,15 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
     if(tid == 0){ tc::mbar_arrive(turn); tc::mbar_arrive(turn); }          // pair {0,1} holds the token first
     const uint32_t tmem_base = *slot;
     const uint32_t tmem_d = tmem_base + (uint32_t)g * TMEM_COLS_PER_GROUP;          // accumulator: 64 columns
-    const uint32_t tmem_a = tmem_d + 64;                                            // A_hi: 64 columns
+    const uint32_t tmem_a = tmem_d + 64;                                            // leading fp16 part of A, two K elements per column: 32 columns
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;                    // this warp's lane quarter
-    uint8_t* a_lo = base + OFF_A_LO + (uint32_t)g * A_LO_BYTES;
-    const uint64_t desc_a_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(a_lo));
-    const uint64_t desc_b_hi = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_HI)), desc_b_lo = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_LO));
+    uint8_t* a_rest = base + OFF_A_REST + (uint32_t)g * A_PART_BYTES;
+    const uint64_t desc_a_rest = tc::make_desc_kmajor_sw128(tc::smem_u32(a_rest));
+    const uint64_t desc_b_lead = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_LEAD)), desc_b_rest = tc::make_desc_kmajor_sw128(tc::smem_u32(base + OFF_B_REST));
     const uint64_t desc_ones = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_ONES));
     const uint64_t desc_bias = tc::make_desc_kmajor_noswizzle_k8(tc::smem_u32(base + OFF_BIAS));
-    constexpr uint32_t IDESC = tc::make_idesc_tf32(TILE, H);
-    uint8_t* my_row_lo = a_lo + r * 128;
+    constexpr uint32_t IDESC = tc::make_idesc_f16(TILE, H);
+    uint8_t* my_row_rest = a_rest + r * 128;              // this thread's row of the remainder-part tile
     const uint32_t swz = (uint32_t)r & 7;
     const int act1 = a.acts[0], act2 = a.acts[1], act3 = a.acts[2];
     const uint32_t bar_id = 1 + g;
@@ -192,28 +240,29 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                 else{ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
             }
 
-            // ---- layer 1 (CUDA cores, weights as constant-bank operands); A_hi -> TMEM, A_lo -> swizzled smem ----
+            // ---- layer 1 (CUDA cores, weights as constant-bank operands); leading fp16 parts -> TMEM, remainder parts -> swizzled smem tile ----
+            uint32_t lead_all[32];
 #pragma unroll
-            for(int hb = 0; hb < 2; hb++){               // K-block hb = hidden units 32 hb .. 32 hb + 31
-                uint32_t hraw[32];
+            for(int c = 0; c < 8; c++){                  // 16-byte chunk c of the row: units 8c .. 8c+7
+                uint32_t lead[4], rest[4];
 #pragma unroll
-                for(int c = 0; c < 8; c++){              // 16-byte chunk c of the K-block: units 4c .. 4c+3
-                    float lo[4];
+                for(int q = 0; q < 4; q++){
+                    float h[2];
 #pragma unroll
-                    for(int q = 0; q < 4; q++){
-                        const int j = hb * 32 + c * 4 + q;
+                    for(int z = 0; z < 2; z++){
+                        const int j = c * 8 + q * 2 + z;
                         float acc = fmaf(c_actor[C_W1 + 3 * j], cs, c_actor[C_B1 + j]);      // bias first, inputs ascending: the reference's order
                         acc = fmaf(c_actor[C_W1 + 3 * j + 1], sn, acc);
                         acc = fmaf(c_actor[C_W1 + 3 * j + 2], theta_dot, acc);
-                        const float h = act_or_rt<A1>(acc, act1);
-                        const uint32_t u = __float_as_uint(h);
-                        hraw[c * 4 + q] = u;
-                        lo[q] = h - __uint_as_float(u & TF32_MASK);
+                        h[z] = act_or_rt<A1>(acc, act1);
                     }
-                    *reinterpret_cast<float4*>(my_row_lo + hb * A_KBLOCK_BYTES + (((uint32_t)c ^ swz) << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                    split_f16_pair(h[0], h[1], lead[q], rest[q]);
                 }
-                tc::tmem_st_32x32(tmem_a + lane_off + hb * 32, hraw);
+#pragma unroll
+                for(int q = 0; q < 4; q++) lead_all[c * 4 + q] = lead[q];
+                *reinterpret_cast<uint4*>(my_row_rest + (((uint32_t)c ^ swz) << 4)) = make_uint4(rest[0], rest[1], rest[2], rest[3]);
             }
+            tc::tmem_st_32x32(tmem_a + lane_off, lead_all);
             tc::tmem_wait_st();
             tc::fence_proxy_async_smem();
             tc::fence_before_thread_sync();
@@ -221,30 +270,23 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             tc::named_barrier_sync(bar_id, TILE);
             if(*abort_flag){ failed = true; break; }
 
-            // ---- layer 2 on the tensor core: D[128x64] = A_lo*B_hi + A_hi*B_lo + A_hi*B_hi ----
-            // The tensor token alternates between the group pairs {0,1} and {2,3}. If all four leaders issue at once the
-            // tensor core interleaves the four batches, they finish together and the groups fall into lock step (everyone
-            // computes, then everyone waits for the tensor core). With the token, one pair's MMA batches run while the other
-            // pair is in its CUDA-core phases; two batches in flight still hide the accumulator dependency between MMAs.
+            // ---- layer 2 on the tensor core. The issuing turn alternates between the group pairs {0,1} and {2,3}: one pair's MMA batches
+            // run while the other pair is in its CUDA-core phases; two batches in flight hide the accumulator dependency between MMAs ----
             if(r == 0){
                 if(!tc::mbar_wait_bounded(my_turn, turn_phase, WAIT_LIMIT_CYCLES)){ *abort_flag = 1; if(a.error_flag) *a.error_flag = 2; }
                 turn_phase ^= 1;
                 tc::fence_after_thread_sync();
+                // remainder * leading (A from shared memory), leading * remainder and leading * leading (A from tensor memory, 8 columns
+                // per K = 16 step): the small terms first; then the bias step
 #pragma unroll
-                for(int kb = 0; kb < 2; kb++)
-#pragma unroll
-                    for(int ks = 0; ks < 4; ks++)
-                        tc::mma_tf32_ss(tmem_d, desc_a_lo + (uint64_t)(kb * (A_KBLOCK_BYTES >> 4) + ks * 2), desc_b_hi + (uint64_t)(kb * (B_KBLOCK_BYTES >> 4) + ks * 2), IDESC, (kb | ks) ? 1u : 0u);
+                for(int ks = 0; ks < 4; ks++) tc::mma_f16_ss(tmem_d, desc_a_rest + (uint64_t)(ks * 2), desc_b_lead + (uint64_t)(ks * 2), IDESC, ks ? 1u : 0u);
 #pragma unroll
                 for(int pass = 0; pass < 2; pass++){
-                    const uint64_t db = pass == 0 ? desc_b_lo : desc_b_hi;
+                    const uint64_t db = pass == 0 ? desc_b_rest : desc_b_lead;
 #pragma unroll
-                    for(int kb = 0; kb < 2; kb++)
-#pragma unroll
-                        for(int ks = 0; ks < 4; ks++)
-                            tc::mma_tf32_ts(tmem_d, tmem_a + (uint32_t)(kb * 32 + ks * 8), db + (uint64_t)(kb * (B_KBLOCK_BYTES >> 4) + ks * 2), IDESC, 1u);
+                    for(int ks = 0; ks < 4; ks++) tc::mma_f16_ts(tmem_d, tmem_a + (uint32_t)(ks * 8), db + (uint64_t)(ks * 2), IDESC, 1u);
                 }
-                tc::mma_tf32_ss(tmem_d, desc_ones, desc_bias, IDESC, 1u);
+                tc::mma_f16_ss(tmem_d, desc_ones, desc_bias, IDESC, 1u);
                 tc::commit(mbar);
                 tc::mbar_arrive(next_turn);
                 if constexpr(BULK){ if(t > 0) bulk_flush(t - 1); }          // every thread of the group finished step t-1 before this step's barrier
@@ -267,13 +309,17 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
 #pragma unroll
                 for(int p = 0; p < 8; p++){
                     const int j = half * 32 + p * 4;
-                    o0 = fmaf(c_actor[C_W3 + j + 0], act_or_rt<A2>(__uint_as_float(d[p * 4 + 0]), act2), o0);
-                    o1 = fmaf(c_actor[C_W3 + j + 1], act_or_rt<A2>(__uint_as_float(d[p * 4 + 1]), act2), o1);
-                    o2 = fmaf(c_actor[C_W3 + j + 2], act_or_rt<A2>(__uint_as_float(d[p * 4 + 2]), act2), o2);
-                    o3 = fmaf(c_actor[C_W3 + j + 3], act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]), act2), o3);
+                    // ReLU commutes with the positive scale: it is taken out once after the sum; other activations scale each unit back first
+                    constexpr bool HOMOGENEOUS = A2 == B200RL_ACT_RELU || A2 == B200RL_ACT_IDENTITY;
+                    const float back = HOMOGENEOUS ? 1.0f : w_unscale;
+                    o0 = fmaf(c_actor[C_W3 + j + 0], act_or_rt<A2>(__uint_as_float(d[p * 4 + 0]) * back, act2), o0);
+                    o1 = fmaf(c_actor[C_W3 + j + 1], act_or_rt<A2>(__uint_as_float(d[p * 4 + 1]) * back, act2), o1);
+                    o2 = fmaf(c_actor[C_W3 + j + 2], act_or_rt<A2>(__uint_as_float(d[p * 4 + 2]) * back, act2), o2);
+                    o3 = fmaf(c_actor[C_W3 + j + 3], act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]) * back, act2), o3);
                 }
             }
-            float action = activation_rt(c_actor[C_B3] + ((o0 + o1) + (o2 + o3)), act3);
+            const float osum = (o0 + o1) + (o2 + o3);
+            float action = activation_rt(c_actor[C_B3] + ((A2 == B200RL_ACT_RELU || A2 == B200RL_ACT_IDENTITY) ? osum * w_unscale : osum), act3);
             if constexpr(COLLECT){
                 const float mean = action;
                 action = head.sample(mean, a.device_rng ? draws.normal : (valid ? __ldg(a.noise + row) : 0.0f));

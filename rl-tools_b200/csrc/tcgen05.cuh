@@ -86,6 +86,25 @@ __host__ __device__ constexpr uint32_t noswizzle_k8_offset(uint32_t row, uint32_
 __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N){
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// The same for kind::f16 with fp16 operands (K = 16 per instruction, 32 bytes per row like the tf32 K = 8 step), fp32 accumulate
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N){
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// byte offset of element (row, k) of a K = 16 fp16 tile without swizzle (the layout of make_desc_kmajor_noswizzle_k8 with 2-byte elements)
+__host__ __device__ constexpr uint32_t noswizzle_k16_offset(uint32_t row, uint32_t k){
+    return (row >> 3) * 256u + (k >> 3) * 128u + (row & 7u) * 16u + (k & 7u) * 2u;
+}
+__device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate){
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+}
+// fp16 A operand from tensor memory: lane = row, two consecutive K elements per 32-bit column
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate){
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 :: "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+}
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread
 __device__ __forceinline__ void mma_tf32_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate){
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"

@@ -103,6 +103,13 @@ int b200rl_dense_backward_static_scratch(const float* W, const float* x, int ldx
 int b200rl_mse_gradient(const float* a, int lda, const float* b, int ldb, float* d_a, int ldd, int rows, int cols, float loss_weight,
                         b200rl_stream_t stream);
 
+/* The loss value itself: loss_weight * sum (a - b)^2 / (rows * cols), returned through *loss_host (host memory; the call synchronises the
+ * stream, as a function that returns the value must). Replaces nn::loss_functions::mse::evaluate
+ * (nn/loss_functions/mse/operations_generic.h:9-22, a host loop over get() in the reference). The squares are summed in double in a
+ * fixed order and rounded once. */
+int b200rl_mse_evaluate(const float* a, int lda, const float* b, int ldb, int rows, int cols, float loss_weight, float* loss_host,
+                        b200rl_stream_t stream);
+
 /* dst[0..n) = value. Replaces the cudaMemsetAsync pairs of zero_gradient / _reset_optimizer_state
  * (nn/layers/dense/operations_cuda.h:415-432) -- with the flat arena below it is one call per network. */
 int b200rl_fill(float* dst, size_t n, float value, b200rl_stream_t stream);
@@ -251,6 +258,17 @@ int b200rl_release_host_staging(void);
  * uniform_real_distribution<float>, exactly what random/operations_cpu.h:21-35 drives), so that resets are
  * bit-identical to a reference CPU run. rng_state_host is 625 x uint32 owned by the caller. */
 int b200rl_rng_init_host(uint32_t* rng_state_host, uint32_t seed);
+/* init_weights of one dense layer on that host engine, uploaded to W [O, I] and bias [O] (synchronises): per output row the bias draw
+ * U(-bias_bound, bias_bound) (skipped, bias = 0, when draw_biases == 0) followed by the row's I weight draws U(-weight_bound, weight_bound)
+ * -- the draw order of nn/layers/dense/operations_generic.h:59-87. The reference's default (legacy Kaiming-uniform, layer.h:28-39) is
+ * weight_bound = bias_bound = 1 / sqrt(I) evaluated in float as sqrt(3) * (sqrt(2 / (1 + sqrt(5)^2)) / sqrt(I)) and 1 / sqrt(I).
+ * Replaces the CUDA form nn/layers/dense/operations_cuda.h:17-67 (which draws on its device engines). */
+int b200rl_dense_init_weights(uint32_t* rng_state_host, float weight_bound, float bias_bound, int draw_biases, float* W, float* bias,
+                              int input_dim, int output_dim, b200rl_stream_t stream);
+/* randn(device, matrix, rng) with the host engine: rows * cols standard normals in row-major order (one fresh
+ * std::normal_distribution per element, random/operations_cpu.h:40-48) into a device matrix with row pitch ld; synchronises.
+ * Replaces containers/matrix/operations_cuda.h:197-223 for callers that need the host stream's exact values. */
+int b200rl_randn_host_rng(uint32_t* rng_state_host, float* dst, int ld, int rows, int cols, b200rl_stream_t stream);
 /* Fills reset_states_host [R,N,2] in the runner's draw order (each step, envs ascending, theta then theta_dot for
  * every truncated env; off_policy_runner/operations_cpu.h:46-50) for a call of n_steps steps starting from the
  * given counters. Returns the number of reset rounds used in *rounds_used_host. */

@@ -160,6 +160,9 @@ class Oracle:
         self.lib.orc_mse_gradient(a, a.shape[1], b, b.shape[1], d, d.shape[1], a.shape[0], a.shape[1], loss_weight)
         return d
 
+    def mse_evaluate(self, a, b, loss_weight=1.0):
+        return float(self.lib.orc_mse_evaluate(a, a.shape[1], b, b.shape[1], a.shape[0], a.shape[1], loss_weight))
+
     def adam_bias_correction(self, beta_1, beta_2, age):
         a = C.c_uint32(age)
         c1, c2 = C.c_float(), C.c_float()

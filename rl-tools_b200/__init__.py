@@ -126,6 +126,9 @@ def lib():
         L.b200rl_pendulum_rollout_host.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp]
         L.b200rl_release_host_staging.argtypes = []
         L.b200rl_rng_init_host.argtypes = [vp, C.c_uint32]
+        L.b200rl_dense_init_weights.argtypes = [vp, f, f, i, vp, vp, i, i, vp]
+        L.b200rl_randn_host_rng.argtypes = [vp, vp, i, i, i, vp]
+        L.b200rl_mse_evaluate.argtypes = [vp, i, vp, i, i, i, f, vp, vp]
         L.b200rl_reset_table_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i)]
         L.b200rl_shuffle_permutation_host.argtypes = [vp, i, vp]
         L.b200rl_permute_rows_scratch_bytes.argtypes = [i, C.c_uint64]
@@ -222,6 +225,38 @@ def mse_gradient(a, b, loss_weight=1.0, d_a=None):
     check(lib().b200rl_mse_gradient(_ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(d_a), d_a.stride(0), a.shape[0], a.shape[1], loss_weight, _stream()),
           "b200rl_mse_gradient")
     return d_a
+
+
+def mse_evaluate(a, b, loss_weight=1.0):
+    """The loss value loss_weight * mean((a - b)^2) as a Python float (synchronises the current stream)."""
+    import ctypes
+    out = ctypes.c_float()
+    check(lib().b200rl_mse_evaluate(_ptr(a), a.stride(0), _ptr(b), b.stride(0), a.shape[0], a.shape[1], loss_weight, ctypes.byref(out), _stream()), "b200rl_mse_evaluate")
+    return out.value
+
+
+def dense_init_weights(rng_state, W, bias, legacy=True, scale=1.0):
+    """The reference's Kaiming-uniform init_weights of one dense layer on the host engine `rng_state` (advanced in place), written to the device
+    tensors W [O, I] and bias [O]. Bounds evaluated in float32 exactly as nn/layers/dense/operations_generic.h:61-76 does."""
+    import numpy as np
+    f = np.float32
+    O, I = W.shape
+    if legacy:
+        slope = np.sqrt(f(5))
+        gain = np.sqrt(f(2.0) / (f(1) + slope * slope))
+    else:
+        gain = np.sqrt(f(2.0)) * f(scale)
+    std = f(gain) / np.sqrt(f(I))
+    weight_bound = np.sqrt(f(3.0)) * f(std)
+    bias_bound = f(1) / np.sqrt(f(I))
+    check(lib().b200rl_dense_init_weights(C.c_void_p(rng_state.ctypes.data), float(weight_bound), float(bias_bound), int(bool(legacy)), _ptr(W), _ptr(bias), I, O, _stream()),
+          "b200rl_dense_init_weights")
+
+
+def randn_host_rng(rng_state, dst):
+    """Fills the device matrix dst [rows, cols] (any row stride) with standard normals from the host engine, in the reference's order."""
+    check(lib().b200rl_randn_host_rng(C.c_void_p(rng_state.ctypes.data), _ptr(dst), dst.stride(0), dst.shape[0], dst.shape[1], _stream()), "b200rl_randn_host_rng")
+    return dst
 
 
 def gae(rewards, all_values, terminated, truncated, n_envs, steps, gamma=0.99, lam=0.95, ignore_termination=False):

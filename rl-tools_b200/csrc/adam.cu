@@ -83,6 +83,27 @@ __global__ void __launch_bounds__(256) mse_gradient_kernel(const float* __restri
         d[r * ldd + c] = __fmul_rn(diff, constant);
     }
 }
+// loss = loss_weight * sum (a - b)^2 / (rows * cols): one block, every thread a strided partial sum in double, then a fixed-order tree
+// (the reference adds the squares in float in row-major order; the double sum rounded once lies within that sum's own rounding error)
+__device__ float g_mse_value;
+__global__ void __launch_bounds__(1024) mse_evaluate_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long ldb, int rows, int cols,
+                                                            float loss_weight, float* out){
+    __shared__ double part[1024];
+    const long long n = (long long)rows * cols;
+    double acc = 0.0;
+    for(long long i = threadIdx.x; i < n; i += blockDim.x){
+        const long long r = i / cols; const int c = (int)(i - r * cols);
+        const float diff = __fsub_rn(a[r * lda + c], b[r * ldb + c]);
+        acc += (double)__fmul_rn(diff, diff);
+    }
+    part[threadIdx.x] = acc;
+    __syncthreads();
+    for(int w = 512; w > 0; w >>= 1){
+        if((int)threadIdx.x < w) part[threadIdx.x] += part[threadIdx.x + w];
+        __syncthreads();
+    }
+    if(threadIdx.x == 0) *out = __fdiv_rn(__fmul_rn((float)part[0], loss_weight), (float)n);     // acc * loss_weight / (ROWS * COLS)
+}
 __global__ void __launch_bounds__(256) fill_kernel(float* dst, size_t n, float value, int vec_ok){
     const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
     if(vec_ok){
@@ -170,6 +191,18 @@ int b200rl_mse_gradient(const float* a, int lda, const float* b, int ldb, float*
     float constant = 2.0f / ((float)rows * (float)cols) * loss_weight;
     mse_gradient_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(a, lda, b, ldb, d_a, ldd, rows, cols, constant);
     B200RL_LAUNCH_CHECK("mse_gradient");
+    return B200RL_OK;
+}
+
+int b200rl_mse_evaluate(const float* a, int lda, const float* b, int ldb, int rows, int cols, float loss_weight, float* loss_host, b200rl_stream_t stream){
+    if(!a || !b || !loss_host || rows < 1 || cols < 1 || lda < cols || ldb < cols) return B200RL_ERR_INVALID_ARGUMENT;
+    float* slot = nullptr;
+    B200RL_CUDA_TRY(cudaGetSymbolAddress((void**)&slot, g_mse_value));
+    cudaStream_t s = (cudaStream_t)stream;
+    mse_evaluate_kernel<<<1, 1024, 0, s>>>(a, lda, b, ldb, rows, cols, loss_weight, slot);
+    B200RL_LAUNCH_CHECK("mse_evaluate");
+    B200RL_CUDA_TRY(cudaMemcpyAsync(loss_host, slot, sizeof(float), cudaMemcpyDeviceToHost, s));
+    B200RL_CUDA_TRY(cudaStreamSynchronize(s));
     return B200RL_OK;
 }
 

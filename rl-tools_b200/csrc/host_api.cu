@@ -298,6 +298,36 @@ int b200rl_gather_draws_host(uint32_t* rng, int n_envs, int batch, const int32_t
     return B200RL_OK;
 }
 
+// init_weights of a dense layer (nn/layers/dense/operations_generic.h:59-90): per output row the bias draw (when the initialiser
+// draws biases) and then the row's input_dim weight draws, all uniform on the host engine; uploaded in two copies.
+int b200rl_dense_init_weights(uint32_t* rng, float weight_bound, float bias_bound, int draw_biases, float* W, float* bias,
+                              int input_dim, int output_dim, b200rl_stream_t stream){
+    if(!rng || !W || !bias || input_dim < 1 || output_dim < 1 || !(weight_bound >= 0.0f) || !(bias_bound >= 0.0f)) return B200RL_ERR_INVALID_ARGUMENT;
+    std::vector<float> w((size_t)output_dim * input_dim), b((size_t)output_dim);
+    for(int o = 0; o < output_dim; o++){
+        b[o] = draw_biases ? uniform_real(rng, -bias_bound, bias_bound) : 0.0f;
+        for(int i = 0; i < input_dim; i++) w[(size_t)o * input_dim + i] = uniform_real(rng, -weight_bound, weight_bound);
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    B200RL_CUDA_TRY(cudaMemcpyAsync(W, w.data(), sizeof(float) * w.size(), cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaMemcpyAsync(bias, b.data(), sizeof(float) * b.size(), cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaStreamSynchronize(s));             // the host vectors go out of scope
+    return B200RL_OK;
+}
+
+// randn(device, matrix, rng) with the HOST engine (containers/matrix/operations_generic.h:631-639: row-major order, one
+// normal_distribution::sample(0, 1) per element), uploaded row by row into a matrix with row pitch ld.
+int b200rl_randn_host_rng(uint32_t* rng, float* dst, int ld, int rows, int cols, b200rl_stream_t stream){
+    if(!rng || !dst || rows < 0 || cols < 0 || ld < cols) return B200RL_ERR_INVALID_ARGUMENT;
+    if(rows == 0 || cols == 0) return B200RL_OK;
+    std::vector<float> h((size_t)rows * cols);
+    for(size_t i = 0; i < h.size(); i++) h[i] = standard_normal(rng);
+    cudaStream_t s = (cudaStream_t)stream;
+    B200RL_CUDA_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * (size_t)ld, h.data(), sizeof(float) * (size_t)cols, sizeof(float) * (size_t)cols, (size_t)rows, cudaMemcpyHostToDevice, s));
+    B200RL_CUDA_TRY(cudaStreamSynchronize(s));
+    return B200RL_OK;
+}
+
 int b200rl_release_host_staging(void){
     std::lock_guard<std::mutex> lock(g_staging_mutex);
     for(int d = 0; d < MAX_DEVICES; d++) if(g_staging[d].device != -1) g_staging[d].release();

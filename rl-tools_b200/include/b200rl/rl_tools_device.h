@@ -12,6 +12,8 @@
 #include <b200rl.h>
 #include <rl_tools/containers/tensor/tensor.h>
 #include <rl_tools/nn/optimizers/adam/adam.h>
+#include <rl_tools/nn/layers/dense/layer.h>
+#include <vector>
 
 RL_TOOLS_NAMESPACE_WRAPPER_START
 namespace rl_tools::devices{
@@ -58,6 +60,37 @@ namespace rl_tools{
     int check_status(devices::B200<SPEC>& device){
         b200::note(device, b200rl_stream_synchronize(device.stream));
         return device.status;
+    }
+}
+RL_TOOLS_NAMESPACE_WRAPPER_END
+
+// init_weights of a dense layer likewise has to be declared before the reference's generic dense operations: their three-argument
+// init_weights(device, layer, rng) forwards to the four-argument form below with no argument from namespace rl_tools.
+// The draws are made on the HOST with the reference's own uniform_real_distribution on the caller's engine, in the reference's order
+// (per output row the bias, then the row's weights; nn/layers/dense/operations_generic.h:59-87), then uploaded: the parameters are
+// bit-identical to those of the CPU device for the same engine state, and the engine advances identically.
+// Replaces nn/layers/dense/operations_cuda.h:17-67 (which draws on its device engines instead).
+RL_TOOLS_NAMESPACE_WRAPPER_START
+namespace rl_tools{
+    template<typename DEV_SPEC, typename SPEC, typename INITIALIZER_SPEC, typename RNG>
+    void init_weights(devices::B200<DEV_SPEC>& device, nn::layers::dense::LayerForward<SPEC>& layer, const nn::layers::dense::KaimingUniform<INITIALIZER_SPEC>&, RNG& rng){
+        using T = typename SPEC::TYPE_POLICY::DEFAULT;
+        static_assert(utils::typing::is_same_v<T, float>, "fp32 only");
+        T gain;
+        if constexpr(INITIALIZER_SPEC::INIT_LEGACY){
+            const T negative_slope = math::sqrt(device.math, (T)5);
+            gain = math::sqrt(device.math, (T)2.0 / (1 + negative_slope * negative_slope));
+        }
+        else gain = math::sqrt(device.math, (T)2.0) * INITIALIZER_SPEC::SCALE;
+        const T std = gain / math::sqrt(device.math, (T)SPEC::INPUT_DIM);
+        const T weight_bound = math::sqrt(device.math, (T)3.0) * std, bias_bound = 1 / math::sqrt(device.math, (T)SPEC::INPUT_DIM);
+        std::vector<T> w((size_t)SPEC::OUTPUT_DIM * SPEC::INPUT_DIM), b((size_t)SPEC::OUTPUT_DIM);
+        for(typename SPEC::TI i = 0; i < SPEC::OUTPUT_DIM; i++){
+            b[i] = INITIALIZER_SPEC::INIT_LEGACY ? random::uniform_real_distribution(device.random, -bias_bound, bias_bound, rng) : (T)0;
+            for(typename SPEC::TI j = 0; j < SPEC::INPUT_DIM; j++) w[(size_t)i * SPEC::INPUT_DIM + j] = random::uniform_real_distribution(device.random, -weight_bound, weight_bound, rng);
+        }
+        b200::note(device, b200rl_memcpy(layer.weights.parameters._data, w.data(), w.size() * sizeof(T), 0, device.stream));
+        b200::note(device, b200rl_memcpy(layer.biases.parameters._data, b.data(), b.size() * sizeof(T), 0, device.stream));
     }
 }
 RL_TOOLS_NAMESPACE_WRAPPER_END

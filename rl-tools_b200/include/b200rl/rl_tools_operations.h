@@ -88,6 +88,18 @@ namespace rl_tools{
         b200::note(device, b200rl_fill(t._data, SPEC::SIZE, value, device.stream));
     }
 
+    // containers/matrix/operations_cuda.h:197-223 draws on the device engines; here the draws come from the caller's HOST engine through
+    // the reference's own normal_distribution::sample, in the generic randn's order (containers/matrix/operations_generic.h:631-639), so
+    // that a matrix filled on this device equals the one the CPU device fills from the same engine state
+    template<typename DEV_SPEC, typename SPEC, typename RNG>
+    void randn(devices::B200<DEV_SPEC>& device, Matrix<SPEC>& m, RNG& rng){
+        using T = typename SPEC::T;
+        static_assert(utils::typing::is_same_v<T, float> && SPEC::COL_PITCH == 1, "fp32, column pitch 1");
+        std::vector<T> host((size_t)SPEC::ROWS * SPEC::COLS);
+        for(size_t i = 0; i < host.size(); i++) host[i] = random::normal_distribution::sample(device.random, (T)0, (T)1, rng);
+        b200::note(device, b200rl_memcpy_2d(m._data, row_pitch(m) * sizeof(T), host.data(), SPEC::COLS * sizeof(T), SPEC::COLS * sizeof(T), SPEC::ROWS, 0, device.stream));
+    }
+
     // ---- dense layer: nn/layers/dense/operations_cuda.h:236-413 ---------------------------------------------------
     namespace b200{
         template <nn::activation_functions::ActivationFunction F>
@@ -150,6 +162,14 @@ namespace rl_tools{
         void gradient(devices::B200<DEV_SPEC>& device, Matrix<SPEC_A>& a, Matrix<SPEC_B>& b, Matrix<SPEC_DA>& d_a, typename SPEC_A::T loss_weight = 1){
             static_assert(containers::check_structure<SPEC_A, SPEC_B> && containers::check_structure<SPEC_A, SPEC_DA>);
             rl_tools::b200::note(device, b200rl_mse_gradient(a._data, row_pitch(a), b._data, row_pitch(b), d_a._data, row_pitch(d_a), SPEC_A::ROWS, SPEC_A::COLS, loss_weight, device.stream));
+        }
+        // nn/loss_functions/mse/operations_generic.h:9-22 (the reference has no CUDA form: its generic loop would read device memory on the host)
+        template<typename DEV_SPEC, typename SPEC_A, typename SPEC_B>
+        typename SPEC_A::T evaluate(devices::B200<DEV_SPEC>& device, Matrix<SPEC_A>& a, Matrix<SPEC_B>& b, typename SPEC_A::T loss_weight = 1){
+            static_assert(containers::check_structure<SPEC_A, SPEC_B>);
+            float loss = 0;
+            rl_tools::b200::note(device, b200rl_mse_evaluate(a._data, row_pitch(a), b._data, row_pitch(b), SPEC_A::ROWS, SPEC_A::COLS, loss_weight, &loss, device.stream));
+            return loss;
         }
     }
 

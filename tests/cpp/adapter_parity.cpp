@@ -414,6 +414,82 @@ void normalizer_parity(const char* name){
     rlt::free(cpu, buf_cpu); rlt::free(gpu, buf_gpu); rlt::free(cpu, data_cpu); rlt::free(gpu, data_gpu); rlt::free(cpu, out_cpu); rlt::free(gpu, out_gpu); rlt::free(cpu, out_back);
 }
 
+// init_weights, randn and mse::evaluate on the device tag against the CPU device from the same engine state: the draws are made by the
+// reference's own distributions on the host, so parameters, matrices and the engine's final state are identical; the loss value agrees to
+// the float sum's rounding. Also: the network lives in ONE arena (whole-model path), and a network allocated layer by layer (the
+// per-layer path of the same verbs) trains to the same parameters.
+template <TI BATCH, TI INPUT_DIM, TI HIDDEN_DIM, TI OUTPUT_DIM>
+void boundary_extras(const char* name){
+    using CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, OUTPUT_DIM, 3, HIDDEN_DIM, act::RELU, act::IDENTITY>;
+    using INPUT_SHAPE = rlt::tensor::Shape<TI, 1, BATCH, INPUT_DIM>;
+    using NET = rlt::nn_models::mlp::NeuralNetwork<CONFIG, rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>, INPUT_SHAPE>;
+    using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
+    DEVICE_CPU cpu; DEVICE_GPU gpu;
+    rlt::init(gpu);
+    NET net_cpu, net_gpu, net_layers, net_back, net_back2;
+    typename NET::template Buffer<> buf_gpu, buf_layers;
+    OPTIMIZER opt_gpu, opt_layers;
+    rlt::malloc(cpu, net_cpu); rlt::malloc(cpu, net_back); rlt::malloc(cpu, net_back2);
+    rlt::malloc(gpu, net_gpu); rlt::malloc(gpu, buf_gpu); rlt::malloc(gpu, opt_gpu); rlt::malloc(gpu, buf_layers); rlt::malloc(gpu, opt_layers);
+    // layer by layer: the reference's per-tensor allocation, which the whole-model verbs must detect and serve through the per-layer path
+    rlt::malloc(gpu, net_layers.input_layer); rlt::malloc(gpu, net_layers.hidden_layers[0]); rlt::malloc(gpu, net_layers.output_layer);
+    const bool arena = (bool)rlt::b200::mlp::arena_of(net_gpu), no_arena = !(bool)rlt::b200::mlp::arena_of(net_layers);
+    DEVICE_CPU::SPEC::RANDOM::ENGINE<> rng_cpu, rng_gpu;
+    rlt::malloc(cpu, rng_cpu); rlt::malloc(cpu, rng_gpu);
+    rlt::init(cpu, rng_cpu, 11); rlt::init(cpu, rng_gpu, 11);
+    rlt::init_weights(cpu, net_cpu, rng_cpu);
+    rlt::init_weights(gpu, net_gpu, rng_gpu);
+    rlt::zero_gradient(cpu, net_cpu); rlt::zero_gradient(gpu, net_gpu);
+    rlt::init(gpu, opt_gpu); rlt::init(gpu, opt_layers);
+    rlt::reset_optimizer_state(gpu, opt_gpu, net_gpu);
+    rlt::copy(gpu, cpu, net_gpu, net_back);
+    rlt::Matrix<rlt::matrix::Specification<T, TI, BATCH, INPUT_DIM>> x_cpu, x_gpu, x_back;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, BATCH, OUTPUT_DIM>> y_cpu, y_gpu, d_gpu, d_layers, out_cpu;
+    rlt::malloc(cpu, x_cpu); rlt::malloc(cpu, x_back); rlt::malloc(cpu, y_cpu); rlt::malloc(cpu, out_cpu);
+    rlt::malloc(gpu, x_gpu); rlt::malloc(gpu, y_gpu); rlt::malloc(gpu, d_gpu); rlt::malloc(gpu, d_layers);
+    rlt::randn(cpu, x_cpu, rng_cpu); rlt::randn(gpu, x_gpu, rng_gpu);
+    rlt::randn(cpu, y_cpu, rng_cpu); rlt::randn(gpu, y_gpu, rng_gpu);
+    rlt::copy(gpu, cpu, x_gpu, x_back);
+    const T init_diff = rlt::abs_diff(cpu, net_back.input_layer.weights.parameters, net_cpu.input_layer.weights.parameters) + rlt::abs_diff(cpu, net_back.input_layer.biases.parameters, net_cpu.input_layer.biases.parameters)
+                      + rlt::abs_diff(cpu, net_back.hidden_layers[0].weights.parameters, net_cpu.hidden_layers[0].weights.parameters) + rlt::abs_diff(cpu, net_back.output_layer.biases.parameters, net_cpu.output_layer.biases.parameters)
+                      + rlt::abs_diff(cpu, net_back.output_layer.weights.parameters, net_cpu.output_layer.weights.parameters);
+    const T randn_diff = rlt::abs_diff(cpu, x_back, x_cpu);
+    const bool engine_equal = rlt::abs_diff(cpu, rng_cpu, rng_gpu) == 0;
+    // loss of y against a shifted copy, on both devices
+    for(TI b = 0; b < BATCH; b++) for(TI o = 0; o < OUTPUT_DIM; o++) rlt::set(out_cpu, b, o, rlt::get(y_cpu, b, o) * (T)0.75 + (T)0.1);
+    rlt::copy(cpu, gpu, out_cpu, d_gpu);
+    const T l_cpu = rlt::nn::loss_functions::mse::evaluate(cpu, y_cpu, out_cpu, (T)1.5), l_gpu = rlt::nn::loss_functions::mse::evaluate(gpu, y_gpu, d_gpu, (T)1.5);
+    // the same two training steps through the arena path and through the layer-by-layer path
+    rlt::copy(cpu, gpu, net_cpu, net_layers);
+    rlt::zero_gradient(gpu, net_layers);
+    rlt::reset_optimizer_state(gpu, opt_layers, net_layers);
+    for(int s = 0; s < 2; s++){
+        rlt::zero_gradient(gpu, net_gpu);
+        rlt::forward(gpu, net_gpu, x_gpu, buf_gpu, rng_gpu);
+        { auto out = rlt::output(gpu, net_gpu); auto out_m = rlt::matrix_view(gpu, out); rlt::nn::loss_functions::mse::gradient(gpu, out_m, y_gpu, d_gpu, (T)1); }
+        rlt::backward(gpu, net_gpu, x_gpu, d_gpu, buf_gpu);
+        rlt::step(gpu, opt_gpu, net_gpu);
+        rlt::zero_gradient(gpu, net_layers);
+        rlt::forward(gpu, net_layers, x_gpu, buf_layers, rng_gpu);
+        { auto out = rlt::output(gpu, net_layers); auto out_m = rlt::matrix_view(gpu, out); rlt::nn::loss_functions::mse::gradient(gpu, out_m, y_gpu, d_layers, (T)1); }
+        rlt::backward(gpu, net_layers, x_gpu, d_layers, buf_layers);
+        rlt::step(gpu, opt_layers, net_layers);
+    }
+    const int status = rlt::check_status(gpu);
+    rlt::copy(gpu, cpu, net_gpu, net_back); rlt::copy(gpu, cpu, net_layers, net_back2);
+    const double n_all = 4.0 * (INPUT_DIM * HIDDEN_DIM + HIDDEN_DIM + HIDDEN_DIM * HIDDEN_DIM + HIDDEN_DIM + HIDDEN_DIM * OUTPUT_DIM + OUTPUT_DIM) + 2.0 * BATCH * (2 * HIDDEN_DIM + OUTPUT_DIM);
+    const T path_diff = (T)(rlt::abs_diff(cpu, net_back, net_back2) / n_all);
+    const bool ok = status == 0 && arena && no_arena && init_diff == 0 && randn_diff == 0 && engine_equal && std::fabs(l_cpu - l_gpu) <= 1e-6 * std::fabs(l_cpu) && path_diff < 1e-7;
+    std::printf("%-28s batch %4u  status %d  arena %d/%d  init_weights diff %.1e  randn diff %.1e  engine %d  mse loss %.7f vs %.7f  arena vs per-layer mean diff %.2e  %s\n",
+                name, BATCH, status, (int)arena, (int)no_arena, init_diff, randn_diff, (int)engine_equal, l_cpu, l_gpu, path_diff, ok ? "OK" : "FAIL");
+    if(!ok) failures++;
+    rlt::free(cpu, net_cpu); rlt::free(cpu, net_back); rlt::free(cpu, net_back2);
+    rlt::free(gpu, net_gpu); rlt::free(gpu, buf_gpu); rlt::free(gpu, opt_gpu); rlt::free(gpu, buf_layers); rlt::free(gpu, opt_layers);
+    rlt::free(gpu, net_layers.input_layer); rlt::free(gpu, net_layers.hidden_layers[0]); rlt::free(gpu, net_layers.output_layer);
+    rlt::free(cpu, x_cpu); rlt::free(cpu, x_back); rlt::free(cpu, y_cpu); rlt::free(cpu, out_cpu);
+    rlt::free(gpu, x_gpu); rlt::free(gpu, y_gpu); rlt::free(gpu, d_gpu); rlt::free(gpu, d_layers);
+}
+
 int main(){
     // the reference's CUDA sweep (cuda_basics.cu:961-972) plus the BASELINE shapes
     train_steps<   1, 256,  10, 100, 3, act::RELU, act::IDENTITY, 1>("sweep_b1");
@@ -429,6 +505,8 @@ int main(){
     train_steps< 256,   4, 256,   1, 3, act::RELU, act::IDENTITY, 5>("c3_sac_critic_5steps");
     train_steps<2048,  27,  64,   8, 3, act::TANH, act::IDENTITY, 2>("c4_ppo_actor");
     train_steps<1024,  64, 256,  16, 4, act::RELU, act::IDENTITY, 2>("c5_b1024");
+    boundary_extras<256, 4, 64, 2>("init_randn_mse_arena");
+    boundary_extras<2048, 27, 64, 8>("init_randn_mse_arena_b2048");
     collect_parity<  64, 64, 100, act::RELU, 3>("collect_ppo_default");
     collect_parity<1000, 40,  15, act::TANH, 2>("collect_tanh_1000");
     offpolicy_parity<8, 64, 50, 137>("off_policy_runner_step");

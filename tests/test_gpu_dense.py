@@ -215,3 +215,32 @@ def test_mlp_backward_without_parameter_gradients(lib, torch):
     assert bool((net.grads == 0.5).all())
     net.backward(x, d_out.clone(), d_input=d_in_b)
     assert torch.equal(d_in_a, d_in_b) and not bool((net.grads == 0.5).all())
+
+
+def test_init_weights_reproduces_the_reference_engine(lib, torch):
+    """b200rl_dense_init_weights, layer after layer on one host engine, against the actor the reference's own init_weights produced from
+    seed 0 (3 -> 64 -> 64 -> 1, legacy Kaiming-uniform; stored in rollout.npz): bias, then the row's weights, per output row -- bit-exact."""
+    want = np.load(os.path.join(GOLDEN, "rollout.npz"))["actor_params"]
+    rng = lib.rng_init_host(0)
+    parts, fan_in = [], 3
+    for d in (64, 64, 1):
+        W, b = torch.empty((d, fan_in), device="cuda"), torch.empty(d, device="cuda")
+        lib.dense_init_weights(rng, W, b)
+        parts += [W.cpu().numpy().reshape(-1), b.cpu().numpy()]
+        fan_in = d
+    assert np.array_equal(np.concatenate(parts), want)
+
+
+def test_randn_host_engine_and_mse_evaluate(lib, orc, torch):
+    """Normals of the host engine in the reference's order (row-major, a fresh distribution per element) into a pitched device matrix, and the
+    loss value against the oracle's sequential float sum: the double sum rounded once lies within that sum's rounding error, bounded here by
+    rows * cols * 2^-24 relative."""
+    rows, cols = 37, 5
+    table = torch.zeros((rows, 9), device="cuda")
+    lib.randn_host_rng(lib.rng_init_host(5), table[:, 2:7])
+    assert np.array_equal(table[:, 2:7].cpu().numpy().reshape(-1), orc.normal_stream(5, rows * cols, 0.0, 1.0))
+    assert float(table[:, :2].abs().sum()) == 0 and float(table[:, 7:].abs().sum()) == 0
+    for B, O, w in ((256, 1, 1.0), (2048, 8, 0.5), (1, 3, 2.0), (4099, 17, 1.0)):
+        a, b = mg.det_normal(B + O, B * O, stream=1).reshape(B, O), mg.det_normal(B + O, B * O, stream=2).reshape(B, O)
+        got, want = lib.mse_evaluate(dev(torch, a), dev(torch, b), w), orc.mse_evaluate(a, b, w)
+        assert abs(got - want) <= max(B * O * 2.0 ** -24, 1e-6) * abs(want), (B, O, got, want)

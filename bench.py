@@ -900,6 +900,19 @@ def main():
         if dist is not None:
             dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
         e2e_value = world * N_ENVS * N_STEPS * args.e2e_steps / float(e2e_s.item())
+    # what the host link alone allows at this rank count: the same device-to-host bytes (the three trajectory arrays, already on the device)
+    # copied to the same pinned buffers by all ranks at once, nothing else -- the ceiling of any host-buffer call on this machine
+    copy_only_value = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            h_obs.copy_(obs, non_blocking=True); h_act.copy_(act, non_blocking=True); h_rew.copy_(rew, non_blocking=True)
+        barrier()
+        c_s = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(c_s, op=dist.ReduceOp.MAX)
+        copy_only_value = world * N_ENVS * N_STEPS * args.e2e_steps / float(c_s.item())
     h2d = params_h.nbytes + table_h.nbytes + N_ENVS * (8 + 4 + 1 + 4)
     d2h = rows * BYTES_PER_ENV_STEP + N_ENVS * (8 + 4 + 1 + 4) + 4
     pkg.lib().b200rl_release_host_staging()
@@ -951,7 +964,8 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic", "config": rollout_config(world, workload),
                 "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
-                "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps},
+                "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
+                        "copy_only_value": copy_only_value, "copy_only_note": "the same device-to-host bytes copied by all ranks at once and nothing else: the host link's ceiling for this call"},
                 "gpu_launches": 2 * args.steps, "wall_s_timed_region": wall,
                 "secondary": {"mlp_train": mlp, "rollout_strong": strong}}
         print(json.dumps(line))

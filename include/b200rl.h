@@ -63,6 +63,15 @@ int b200rl_device_error_clear(void);
 int b200rl_dense_forward(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
                          int batch, int input_dim, int output_dim, int activation, b200rl_stream_t stream);
 
+/* The same with a caller-owned workspace of b200rl_dense_forward_workspace_bytes(...) bytes (16-byte aligned device memory; 0 for
+ * shapes that do not take the tensor-core kernel): the weights are split into their tensor-core operand parts once per call into the
+ * workspace instead of once per 128-row tile of the batch -- the fast form for large batches. Contents of the workspace need not be
+ * kept between calls; calls that share one workspace must be ordered on one stream. workspace == NULL behaves like b200rl_dense_forward.
+ * (No counterpart in the reference: cuBLAS manages its own workspace.) */
+size_t b200rl_dense_forward_workspace_bytes(int batch, int input_dim, int output_dim);
+int b200rl_dense_forward_ws(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
+                            int batch, int input_dim, int output_dim, int activation, void* workspace, size_t workspace_bytes, b200rl_stream_t stream);
+
 /* d_pre = act'(pre) * d_out (written back into d_out, as the reference does);
  * d_bias[o] += sum_b d_pre[b][o];  d_W[o][i] += sum_b d_pre[b][o] * x[b][i];  d_in[b][i] = sum_o d_pre[b][o] W[o][i].
  * Gradients ACCUMULATE (zero them with b200rl_fill). d_in == NULL skips the input gradient (first layer),
@@ -144,6 +153,14 @@ int b200rl_mlp_evaluate(const b200rl_mlp_shape* shape, const float* params, cons
  * dense. Replaces nn_models::mlp forward (nn_models/mlp/operations_generic.h:103-120). */
 int b200rl_mlp_forward(const b200rl_mlp_shape* shape, const float* params, const float* x, int ldx, float* pre, float* out,
                        int batch, b200rl_stream_t stream);
+
+/* evaluate / forward with a caller-owned workspace (b200rl_mlp_forward_workspace_bytes = the largest layer's
+ * b200rl_dense_forward_workspace_bytes), see b200rl_dense_forward_ws. */
+size_t b200rl_mlp_forward_workspace_bytes(const b200rl_mlp_shape* shape, int batch);
+int b200rl_mlp_evaluate_ws(const b200rl_mlp_shape* shape, const float* params, const float* x, int ldx, float* y, int ldy,
+                           float* tick, float* tock, int batch, void* workspace, size_t workspace_bytes, b200rl_stream_t stream);
+int b200rl_mlp_forward_ws(const b200rl_mlp_shape* shape, const float* params, const float* x, int ldx, float* pre, float* out,
+                          int batch, void* workspace, size_t workspace_bytes, b200rl_stream_t stream);
 
 /* backward through all layers; d_out [batch, O_last] is clobbered; grads accumulate (grads == NULL: only the input gradient is
  * propagated, backward_input of nn_models/mlp/operations_generic.h:130-150, d_input required); d_input may be NULL

@@ -117,6 +117,13 @@ def lib():
         L.b200rl_mlp_num_params.restype = sz
         L.b200rl_mlp_evaluate.argtypes = [shape_p, vp, vp, i, vp, i, vp, vp, i, vp]
         L.b200rl_mlp_forward.argtypes = [shape_p, vp, vp, i, vp, vp, i, vp]
+        L.b200rl_dense_forward_workspace_bytes.argtypes = [i, i, i]
+        L.b200rl_dense_forward_workspace_bytes.restype = sz
+        L.b200rl_dense_forward_ws.argtypes = [vp, vp, vp, i, vp, i, vp, i, i, i, i, i, vp, sz, vp]
+        L.b200rl_mlp_forward_workspace_bytes.argtypes = [shape_p, i]
+        L.b200rl_mlp_forward_workspace_bytes.restype = sz
+        L.b200rl_mlp_evaluate_ws.argtypes = [shape_p, vp, vp, i, vp, i, vp, vp, i, vp, sz, vp]
+        L.b200rl_mlp_forward_ws.argtypes = [shape_p, vp, vp, i, vp, vp, i, vp, sz, vp]
         L.b200rl_mlp_backward_scratch_bytes.argtypes = [shape_p, i]
         L.b200rl_mlp_backward_scratch_bytes.restype = sz
         L.b200rl_mlp_backward.argtypes = [shape_p, vp, vp, vp, i, vp, vp, vp, vp, vp, vp, i, vp, sz, vp]
@@ -188,13 +195,20 @@ def _act(a):
 # ------------------------------------------------------------------------------------------------------------
 # Thin tensor-level wrappers (torch CUDA float32 tensors in, C ABI underneath)
 # ------------------------------------------------------------------------------------------------------------
-def dense_forward(W, bias, x, act, want_pre=True, y=None, pre=None):
+def dense_forward(W, bias, x, act, want_pre=True, y=None, pre=None, workspace=False):
+    """workspace=True: the b200rl_dense_forward_ws form with a workspace of the size the library asks for (weights split once per call)."""
     import torch
     B, I = x.shape
     O = W.shape[0]
     y = torch.empty((B, O), device=x.device, dtype=torch.float32) if y is None else y
     if want_pre and pre is None:
         pre = torch.empty((B, O), device=x.device, dtype=torch.float32)
+    if workspace:
+        n = lib().b200rl_dense_forward_workspace_bytes(B, I, O)
+        ws = torch.empty(max(n, 16), device=x.device, dtype=torch.uint8)
+        check(lib().b200rl_dense_forward_ws(_ptr(W), _ptr(bias), _ptr(x), x.stride(0), _ptr(pre), pre.stride(0) if pre is not None else 0,
+                                            _ptr(y), y.stride(0), B, I, O, _act(act), _ptr(ws), n, _stream()), "b200rl_dense_forward_ws")
+        return pre, y
     check(lib().b200rl_dense_forward(_ptr(W), _ptr(bias), _ptr(x), x.stride(0), _ptr(pre), pre.stride(0) if pre is not None else 0,
                                      _ptr(y), y.stride(0), B, I, O, _act(act), _stream()), "b200rl_dense_forward")
     return pre, y
@@ -319,6 +333,9 @@ class Mlp:
         nbytes = lib().b200rl_mlp_backward_scratch_bytes(C.byref(self.shape), batch)
         self.scratch_bytes = nbytes
         self.scratch = torch.empty(max(nbytes, 4), device=device, dtype=torch.uint8)
+        # forward workspace: the weights' tensor-core operand image of the layer in flight (0 bytes for small batches)
+        self.workspace_bytes = lib().b200rl_mlp_forward_workspace_bytes(C.byref(self.shape), batch)
+        self.workspace = torch.empty(max(self.workspace_bytes, 16), device=device, dtype=torch.uint8)
         self.hyper = AdamHyper()
         self.reset_optimizer_state()
 
@@ -341,14 +358,15 @@ class Mlp:
         import torch
         O = self.shape.dims[self.shape.n_layers - 1]
         y = torch.empty((x.shape[0], O), device=x.device, dtype=torch.float32) if y is None else y
-        check(lib().b200rl_mlp_evaluate(C.byref(self.shape), _ptr(self.params), _ptr(x), x.stride(0), _ptr(y), y.stride(0), _ptr(self.tick), _ptr(self.tock),
-                                        x.shape[0], _stream()), "b200rl_mlp_evaluate")
+        ws_ok = x.shape[0] <= self.batch          # the workspace was sized for self.batch rows (the plan depends on the batch)
+        check(lib().b200rl_mlp_evaluate_ws(C.byref(self.shape), _ptr(self.params), _ptr(x), x.stride(0), _ptr(y), y.stride(0), _ptr(self.tick), _ptr(self.tock),
+                                           x.shape[0], _ptr(self.workspace) if ws_ok else None, self.workspace_bytes if ws_ok else 0, _stream()), "b200rl_mlp_evaluate")
         return y
 
     def forward(self, x):
         assert x.shape[0] == self.batch
-        check(lib().b200rl_mlp_forward(C.byref(self.shape), _ptr(self.params), _ptr(x), x.stride(0), _ptr(self.pre), _ptr(self.out), self.batch, _stream()),
-              "b200rl_mlp_forward")
+        check(lib().b200rl_mlp_forward_ws(C.byref(self.shape), _ptr(self.params), _ptr(x), x.stride(0), _ptr(self.pre), _ptr(self.out), self.batch,
+                                          _ptr(self.workspace), self.workspace_bytes, _stream()), "b200rl_mlp_forward")
         return self.output()
 
     def backward(self, x, d_out, d_input=None, accumulate_gradients=True):

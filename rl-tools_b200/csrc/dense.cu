@@ -260,21 +260,6 @@ __global__ void __launch_bounds__(256) reduce_bias_partials_kernel(float* dst, c
     }
 }
 
-// dst[i][o] = src[o][i] for a row-major [O, I] matrix (32 x 32 tiles through shared memory, both sides coalesced)
-__global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int O, int I){
-    __shared__ float tile[32][33];
-    const int i0 = blockIdx.x * 32, o0 = blockIdx.y * 32;
-    for(int r = threadIdx.y; r < 32; r += 8){
-        const int o = o0 + r, i = i0 + threadIdx.x;
-        tile[r][threadIdx.x] = (o < O && i < I) ? __ldg(src + (long long)o * I + i) : 0.0f;
-    }
-    __syncthreads();
-    for(int r = threadIdx.y; r < 32; r += 8){
-        const int i = i0 + r, o = o0 + threadIdx.x;
-        if(i < I && o < O) dst[(long long)i * O + o] = tile[threadIdx.x][r];
-    }
-}
-
 // The tensor-core kernel takes the contraction when there is enough work to fill its 128 x 256 tiles on a good part of the SMs:
 // one tile costs ~30 us at K = 256 however few tiles there are, which the CUDA-core kernel's 64 x 64 tiles beat below ~2^27
 // multiply-adds (batch-256 training steps, the 64-wide PPO networks).
@@ -283,8 +268,9 @@ static bool tc_eligible(long long M, long long N, long long K){
 }
 static bool use_tensor_cores(const GemmArgs& a){ return tc_eligible(a.M, a.N, a.K); }
 
-// bytes: split-k and bias partial sums (required when gradients are wanted); wt_bytes: room for the transposed weights behind them,
-// which lets the input-gradient GEMM of the tensor-core path read both operands with 16-byte loads (used when the scratch has it)
+// bytes: split-k and bias partial sums (required when gradients are wanted); wt_bytes: room behind them for the operand image of the
+// transposed weights, which the input-gradient product of the tensor-core path copies in instead of re-splitting W^T per row tile
+// (used when the scratch has it)
 struct BackwardPlan { int splits; int k_per_split; int bias_segs; int rows_per_seg; size_t bytes; size_t wt_bytes; };
 // budget: upper bound on p.bytes. The plan lowers the number of bias segments and of batch splits until the partial sums fit (fewer
 // splits is slower but as correct and as deterministic; one split needs no partial sums at all).
@@ -322,17 +308,28 @@ static BackwardPlan plan_backward(int B, int I, int O, size_t budget = SIZE_MAX)
     if(p.splits > 1) p.bytes += sizeof(float) * (size_t)p.splits * O * I;
     if(p.bias_segs > 1) p.bytes += sizeof(float) * (size_t)p.bias_segs * O;
     p.bytes = (p.bytes + 15) / 16 * 16;
-    p.wt_bytes = tc_eligible(B, I, O) ? sizeof(float) * (size_t)O * I : 0;
+    p.wt_bytes = tc_eligible(B, I, O) ? weight_image_bytes(I, O) : 0;
     return p;
 }
 
+// workspace (optional): room for the weights' operand image, see b200rl_dense_forward_workspace_bytes
+static size_t forward_workspace_bytes(int B, int I, int O){ return tc_eligible(B, O, I) ? weight_image_bytes(O, I) : 0; }
 static int dense_forward_impl(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
-                              int B, int I, int O, int act, cudaStream_t s){
+                              int B, int I, int O, int act, cudaStream_t s, void* workspace = nullptr, size_t workspace_bytes = 0){
     GemmArgs a{};
     a.A = x; a.lda = ldx; a.B = W; a.ldb = I; a.M = B; a.N = O; a.K = I; a.k_per_split = I;
     a.bias = bias; a.pre = pre; a.ldpre = ldpre; a.C = y; a.ldc = ldy;
     if(use_tensor_cores(a)){
-        int rc = launch_gemm_tc(a, EPI_FORWARD, act, true, true, 1, s);
+        int rc = B200RL_ERR_UNSUPPORTED;
+        if(workspace != nullptr && workspace_bytes >= weight_image_bytes(O, I) && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0){
+            // the weights are split into their tf32 parts ONCE per call (a few microseconds), not once per 128-row tile of the batch
+            rc = launch_weight_image(W, I, O, I, false, static_cast<float*>(workspace), s);
+            if(rc) return rc;
+            GemmArgs g = a;
+            g.B = static_cast<const float*>(workspace);
+            rc = launch_gemm_tc(g, EPI_FORWARD, act, true, true, 1, s, true);
+        }
+        if(rc == B200RL_ERR_UNSUPPORTED) rc = launch_gemm_tc(a, EPI_FORWARD, act, true, true, 1, s);
         if(rc != B200RL_ERR_UNSUPPORTED) return rc;
     }
     B200RL_DISPATCH_ACT(act, B200RL_LAUNCH_SIMT_GEMM(true, true, EPI_FORWARD, ACT, a, 1, s));
@@ -440,13 +437,13 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         int rc_tc = B200RL_ERR_UNSUPPORTED;
         if(use_tensor_cores(a)){
             if(p.wt_bytes > 0 && scratch != nullptr && scratch_bytes >= p.bytes + p.wt_bytes){
-                // W^T once (256 KB for a 256 x 256 layer), then both operands are k-contiguous: 16-byte loads instead of four strided ones
-                float* Wt = reinterpret_cast<float*>(static_cast<char*>(scratch) + p.bytes);
-                transpose_kernel<<<dim3((I + 31) / 32, (O + 31) / 32), dim3(32, 8), 0, s>>>(W, Wt, O, I);
-                B200RL_LAUNCH_CHECK("transpose_W");
-                a.B = Wt; a.ldb = O;
-                rc_tc = launch_gemm_tc(a, EPI_STORE, 0, true, true, 1, s);
-                if(rc_tc == B200RL_ERR_UNSUPPORTED){ a.B = W; a.ldb = I; }
+                // operand image of W^T once per call (tf32 parts, tile layout), copied in by the kernel chunk by chunk
+                float* image = reinterpret_cast<float*>(static_cast<char*>(scratch) + p.bytes);
+                int rc = launch_weight_image(W, I, I, O, true, image, s);
+                if(rc) return rc;
+                GemmArgs g = a;
+                g.B = image;
+                rc_tc = launch_gemm_tc(g, EPI_STORE, 0, true, true, 1, s, true);
             }
             if(rc_tc == B200RL_ERR_UNSUPPORTED) rc_tc = launch_gemm_tc(a, EPI_STORE, 0, true, false, 1, s);
         }
@@ -478,6 +475,18 @@ int b200rl_dense_forward(const float* W, const float* bias, const float* x, int 
         return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
     return dense_forward_impl(W, bias, x, ldx, pre, ldpre, y, ldy, batch, input_dim, output_dim, activation, (cudaStream_t)stream);
+}
+
+size_t b200rl_dense_forward_workspace_bytes(int batch, int input_dim, int output_dim){
+    if(batch < 1 || input_dim < 1 || output_dim < 1) return 0;
+    return forward_workspace_bytes(batch, input_dim, output_dim);
+}
+int b200rl_dense_forward_ws(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
+                            int batch, int input_dim, int output_dim, int activation, void* workspace, size_t workspace_bytes, b200rl_stream_t stream){
+    if(!W || !bias || !x || !y || batch < 0 || input_dim < 1 || output_dim < 1 || ldx < input_dim || ldy < output_dim || (pre && ldpre < output_dim) || !valid_activation(activation) || x == y)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(batch == 0) return B200RL_OK;
+    return dense_forward_impl(W, bias, x, ldx, pre, ldpre, y, ldy, batch, input_dim, output_dim, activation, (cudaStream_t)stream, workspace, workspace_bytes);
 }
 
 size_t b200rl_dense_backward_scratch_bytes(int batch, int input_dim, int output_dim){
@@ -545,8 +554,19 @@ size_t b200rl_mlp_num_params(const b200rl_mlp_shape* sh){
     return n;
 }
 
+size_t b200rl_mlp_forward_workspace_bytes(const b200rl_mlp_shape* sh, int batch){
+    if(!valid_shape(sh) || batch < 1) return 0;
+    size_t m = 0; int I = sh->input_dim;
+    for(int l = 0; l < sh->n_layers; l++){ const size_t b = forward_workspace_bytes(batch, I, sh->dims[l]); if(b > m) m = b; I = sh->dims[l]; }
+    return m;
+}
+
 int b200rl_mlp_evaluate(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* y, int ldy,
                         float* tick, float* tock, int batch, b200rl_stream_t stream){
+    return b200rl_mlp_evaluate_ws(sh, params, x, ldx, y, ldy, tick, tock, batch, nullptr, 0, stream);
+}
+int b200rl_mlp_evaluate_ws(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* y, int ldy,
+                           float* tick, float* tock, int batch, void* workspace, size_t workspace_bytes, b200rl_stream_t stream){
     if(!valid_shape(sh) || !params || !x || !y || batch < 0 || ldx < sh->input_dim || ldy < sh->dims[sh->n_layers - 1]) return B200RL_ERR_INVALID_ARGUMENT;
     if(sh->n_layers > 1 && (!tick || (sh->n_layers > 2 && !tock))) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
@@ -555,7 +575,7 @@ int b200rl_mlp_evaluate(const b200rl_mlp_shape* sh, const float* params, const f
         int O = sh->dims[l]; bool last = l == sh->n_layers - 1;
         float* out = last ? y : ((l % 2 == 0) ? tick : tock);
         int ldo = last ? ldy : O;
-        int rc = dense_forward_impl(p, p + (size_t)O * I, in, ldin, nullptr, 0, out, ldo, batch, I, O, sh->acts[l], (cudaStream_t)stream);
+        int rc = dense_forward_impl(p, p + (size_t)O * I, in, ldin, nullptr, 0, out, ldo, batch, I, O, sh->acts[l], (cudaStream_t)stream, workspace, workspace_bytes);
         if(rc) return rc;
         p += (size_t)O * I + O; in = out; ldin = ldo; I = O;
     }
@@ -564,12 +584,16 @@ int b200rl_mlp_evaluate(const b200rl_mlp_shape* sh, const float* params, const f
 
 int b200rl_mlp_forward(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* pre, float* out,
                        int batch, b200rl_stream_t stream){
+    return b200rl_mlp_forward_ws(sh, params, x, ldx, pre, out, batch, nullptr, 0, stream);
+}
+int b200rl_mlp_forward_ws(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* pre, float* out,
+                          int batch, void* workspace, size_t workspace_bytes, b200rl_stream_t stream){
     if(!valid_shape(sh) || !params || !x || !pre || !out || batch < 0 || ldx < sh->input_dim) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
     const float* in = x; int ldin = ldx, I = sh->input_dim; const float* p = params;
     for(int l = 0; l < sh->n_layers; l++){
         int O = sh->dims[l];
-        int rc = dense_forward_impl(p, p + (size_t)O * I, in, ldin, pre, O, out, O, batch, I, O, sh->acts[l], (cudaStream_t)stream);
+        int rc = dense_forward_impl(p, p + (size_t)O * I, in, ldin, pre, O, out, O, batch, I, O, sh->acts[l], (cudaStream_t)stream, workspace, workspace_bytes);
         if(rc) return rc;
         p += (size_t)O * I + O; in = out; ldin = O; I = O;
         pre += (size_t)batch * O; out += (size_t)batch * O;

@@ -23,6 +23,14 @@ struct GemmArgs {
 // Tensor-core (tcgen05, 3xTF32) version of the same contraction; returns B200RL_ERR_UNSUPPORTED for shapes it does not
 // take (the caller then uses the CUDA-core kernel). a_kcontig / b_kcontig: whether the summed index is the contiguous
 // one of A(m,k) / B(n,k) in memory. `splits` = number of k ranges (gridDim.z of the CUDA-core kernel).
-int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcontig, bool b_kcontig, int splits, cudaStream_t s);
+int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcontig, bool b_kcontig, int splits, cudaStream_t s, bool b_image = false);
+
+// Operand image of a weight matrix for the tensor-core kernel: B(n, k) = W[n][k] (or W[k][n] when `transposed`) split ONCE into its
+// tf32 hi / lo parts and laid out exactly as the kernel's shared-memory B tiles (per 256-row tile and 32-wide k chunk: the swizzled
+// hi tile, then the lo tile), so that a CTA brings a chunk's B operand in with one bulk copy instead of loading, splitting and
+// storing it again for every row tile. With b_image the kernel takes a.B as such an image (forward and plain-store epilogues,
+// k-contiguous A, one k range).
+size_t weight_image_bytes(int N, int K);
+int launch_weight_image(const float* W, long long ld, int N, int K, bool transposed, float* image, cudaStream_t s);
 
 }  // namespace b200rl

@@ -181,8 +181,12 @@ __device__ __forceinline__ void stage_chunk(const float4 (&reg)[ITERS], uint8_t*
 // NB = 32-column accumulator blocks per thread: 4 for tiles up to 256 columns, 1 for tiles up to 64 columns. The narrow variant has
 // registers to spare and prefetches TWO k chunks ahead: with a short MMA per chunk its loop is otherwise one global-load latency per
 // chunk long (the 256 -> 16 and 64 -> 256 layers of the training workload spent a third of the step there).
-template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT, int NB>
+// B_IMG: a.B is a weight image (launch_weight_image): thread 0 brings each chunk's B tiles in with one bulk copy, issued one chunk
+// ahead as soon as the stage's previous MMAs have completed; the stage's "full" barrier then waits for the copy's bytes as well as for
+// the staging threads' arrival, and the staging threads handle the A operand only.
+template <bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT, int NB, bool B_IMG>
 __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs a, int n_pad, int m_tiles, int n_tiles, int splits, int a_vec, int b_vec, int c_vec){
+    static_assert(!B_IMG || (A_KCONTIG && EPI != EPI_ACCUMULATE), "weight images serve the forward and input-gradient products");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -272,12 +276,20 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
         for(int bi = 0; bi < NB; bi++)
 #pragma unroll
             for(int j = 0; j < 32; j++) acc[bi][j] = 0.0f;
-        float4 ra[SETS][4], rb[SETS][B_ITERS];
+        float4 ra[SETS][4], rb[B_IMG ? 1 : SETS][B_IMG ? 1 : B_ITERS];
+        // image chunk (n tile, k chunk) -> the B area of a stage (hi tile, lo tile: contiguous in both)
+        const int k_chunks_total = (a.K + TC_KC - 1) / TC_KC;
+        auto load_b_image = [&](int chunk, uint32_t stage_index){
+            const size_t index = (size_t)(mn % n_tiles) * k_chunks_total + (size_t)(k_begin / TC_KC + chunk);
+            tc::mbar_expect_tx(full_bar + stage_index, 2 * b_tile_bytes);
+            tc::bulk_load(base + stage_index * stage_bytes + 2 * A_TILE_BYTES, reinterpret_cast<const uint8_t*>(a.B) + index * 2 * b_tile_bytes, 2 * b_tile_bytes, full_bar + stage_index);
+        };
+        if constexpr(B_IMG){ if(tid == 0 && n_chunks > 0) load_b_image(0, u & 1); }       // both stages are free at the start of a work item
 #pragma unroll
         for(int p = 0; p < SETS; p++){
             if(p < n_chunks){
                 fetch_chunk<A_KCONTIG, 4>(ra[p], a.A, a.lda, m0, a.M, TC_M, k_begin + p * TC_KC, k_end, a_vec != 0, tid);
-                fetch_chunk<B_KCONTIG, B_ITERS>(rb[p], a.B, a.ldb, n0, a.N, b_rows, k_begin + p * TC_KC, k_end, b_vec != 0, tid);
+                if constexpr(!B_IMG) fetch_chunk<B_KCONTIG, B_ITERS>(rb[p], a.B, a.ldb, n0, a.N, b_rows, k_begin + p * TC_KC, k_end, b_vec != 0, tid);
             }
         }
         // one k chunk; SET selects the register set at compile time. Returns false when the kernel is aborting.
@@ -287,8 +299,8 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
             uint8_t* stage = base + s * stage_bytes;
             // stage s and TMEM buffer s are free: the chunk that used them last (u - 2) was waited for in the previous iteration
             stage_chunk<A_KCONTIG, 4>(ra[P], stage, stage + A_TILE_BYTES, TC_M, a_vec != 0, tid);
-            stage_chunk<B_KCONTIG, B_ITERS>(rb[P], stage + 2 * A_TILE_BYTES, stage + 2 * A_TILE_BYTES + b_tile_bytes, b_rows, b_vec != 0, tid);
-            if(b_rows < n_pad && c < 2){
+            if constexpr(!B_IMG) stage_chunk<B_KCONTIG, B_ITERS>(rb[P], stage + 2 * A_TILE_BYTES, stage + 2 * A_TILE_BYTES + b_tile_bytes, b_rows, b_vec != 0, tid);
+            if(!B_IMG && b_rows < n_pad && c < 2){
                 // rows of the padded tile that never receive data: zero them once per stage and work item
                 for(int idx = tid; idx < (n_pad - b_rows) * 8; idx += TC_THREADS){
                     const uint32_t off = (uint32_t)(b_rows + (idx >> 3)) * 128 + ((uint32_t)(idx & 7) << 4);
@@ -304,9 +316,12 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
             if(c + SETS < n_chunks){
                 const int k0 = k_begin + (c + SETS) * TC_KC;
                 fetch_chunk<A_KCONTIG, 4>(ra[P], a.A, a.lda, m0, a.M, TC_M, k0, k_end, a_vec != 0, tid);
-                fetch_chunk<B_KCONTIG, B_ITERS>(rb[P], a.B, a.ldb, n0, a.N, b_rows, k0, k_end, b_vec != 0, tid);
+                if constexpr(!B_IMG) fetch_chunk<B_KCONTIG, B_ITERS>(rb[P], a.B, a.ldb, n0, a.N, b_rows, k0, k_end, b_vec != 0, tid);
             }
             if(c > 0) accumulate(acc, s ^ 1, ((u - 1) >> 1) & 1);
+            // the other stage is free now (chunk c-1, its last user, has completed; the first chunk of an item finds it free anyway):
+            // bring in the weights of chunk c+1 while chunk c runs on the tensor core
+            if constexpr(B_IMG){ if(tid == 0 && c + 1 < n_chunks){ tc::fence_after_thread_sync(); load_b_image(c + 1, s ^ 1); } }
             u++;
             return true;
         };
@@ -434,7 +449,7 @@ __global__ void __launch_bounds__(TC_LAUNCH_THREADS, 1) gemm_tc_kernel(GemmArgs 
     if(warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <bool A_KC, bool B_KC, int EPI, int ACT, int NB>
+template <bool A_KC, bool B_KC, int EPI, int ACT, int NB, bool B_IMG = false>
 static int launch_variant(const GemmArgs& a, int splits, int n_pad, cudaStream_t s){
     const int n_tiles = (a.N + n_pad - 1) / n_pad, m_tiles = (a.M + TC_M - 1) / TC_M;
     const uint32_t smem = 2 * (2 * A_TILE_BYTES + 2 * (uint32_t)n_pad * 128) + 64 + 1024;
@@ -444,7 +459,7 @@ static int launch_variant(const GemmArgs& a, int splits, int n_pad, cudaStream_t
     int rc = current_device(&dev);
     if(rc) return rc;
     if(!configured[dev].load(std::memory_order_acquire)){
-        B200RL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024)));
+        B200RL_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB, B_IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * (2 * A_TILE_BYTES + 2 * TC_NMAX * 128) + 64 + 1024)));
         configured[dev].store(true, std::memory_order_release);
     }
     rc = sm_count(&sms);
@@ -457,20 +472,64 @@ static int launch_variant(const GemmArgs& a, int splits, int n_pad, cudaStream_t
     const int a_vec = aligned(a.A, a.lda) && (!A_KC || a.k_per_split % 4 == 0), b_vec = aligned(a.B, a.ldb) && (!B_KC || a.k_per_split % 4 == 0);
     const int c_vec = (aligned(a.C, a.ldc) ? 1 : 0) | ((a.pre == nullptr || aligned(a.pre, a.ldpre)) ? 2 : 0) |
                       ((a.bias != nullptr && (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0) ? 4 : 0);
-    gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec, c_vec);
+    gemm_tc_kernel<A_KC, B_KC, EPI, ACT, NB, B_IMG><<<grid, TC_LAUNCH_THREADS, smem, s>>>(a, n_pad, m_tiles, n_tiles, splits, a_vec, b_vec, c_vec);
     B200RL_LAUNCH_CHECK("gemm_tc");
     return B200RL_OK;
 }
-template <bool A_KC, bool B_KC, int EPI, int ACT>
+static int tile_columns(int N){
+    int n_pad = (N + 15) / 16 * 16;
+    return n_pad > TC_NMAX ? TC_NMAX : n_pad;
+}
+template <bool A_KC, bool B_KC, int EPI, int ACT, bool B_IMG = false>
 static int launch_one(const GemmArgs& a, int splits, cudaStream_t s){
-    int n_pad = (a.N + 15) / 16 * 16;
-    if(n_pad > TC_NMAX) n_pad = TC_NMAX;
-    if(n_pad <= 64) return launch_variant<A_KC, B_KC, EPI, ACT, 1>(a, splits, n_pad, s);
-    return launch_variant<A_KC, B_KC, EPI, ACT, 4>(a, splits, n_pad, s);
+    const int n_pad = tile_columns(a.N);
+    if(n_pad <= 64) return launch_variant<A_KC, B_KC, EPI, ACT, 1, B_IMG>(a, splits, n_pad, s);
+    return launch_variant<A_KC, B_KC, EPI, ACT, 4, B_IMG>(a, splits, n_pad, s);
 }
 
-int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcontig, bool b_kcontig, int splits, cudaStream_t s){
+// ---- weight image: one thread per 16-byte piece (4 k values of one row) of the image ----
+__global__ void __launch_bounds__(256) weight_image_kernel(const float* __restrict__ W, long long ld, int N, int K, int transposed, int n_pad, int n_tiles, int k_chunks,
+                                                           uint8_t* __restrict__ image){
+    const long long piece = blockIdx.x * (long long)blockDim.x + threadIdx.x, pieces = (long long)n_tiles * k_chunks * n_pad * 8;
+    if(piece >= pieces) return;
+    const int c = (int)(piece & 7), row = (int)((piece >> 3) % n_pad);
+    const long long tile = (piece >> 3) / n_pad;                         // n tile * k_chunks + k chunk
+    const int chunk = (int)(tile % k_chunks), n = (int)(tile / k_chunks) * n_pad + row, k0 = chunk * TC_KC + c * 4;
+    float4 h = make_float4(0.f, 0.f, 0.f, 0.f), l = h;
+    if(n < N){
+        float v[4];
+#pragma unroll
+        for(int e = 0; e < 4; e++){
+            const int k = k0 + e;
+            v[e] = k < K ? (transposed ? __ldg(W + (long long)k * ld + n) : __ldg(W + (long long)n * ld + k)) : 0.0f;
+        }
+        split_rn(v[0], h.x, l.x); split_rn(v[1], h.y, l.y); split_rn(v[2], h.z, l.z); split_rn(v[3], h.w, l.w);
+    }
+    const size_t tile_bytes = (size_t)n_pad * 128, off = (size_t)row * 128 + ((size_t)(c ^ (row & 7)) << 4);
+    *reinterpret_cast<float4*>(image + (size_t)tile * 2 * tile_bytes + off) = h;
+    *reinterpret_cast<float4*>(image + (size_t)tile * 2 * tile_bytes + tile_bytes + off) = l;
+}
+size_t weight_image_bytes(int N, int K){
+    const int n_pad = tile_columns(N);
+    return (size_t)((N + n_pad - 1) / n_pad) * (size_t)((K + TC_KC - 1) / TC_KC) * 2 * (size_t)n_pad * 128;
+}
+int launch_weight_image(const float* W, long long ld, int N, int K, bool transposed, float* image, cudaStream_t s){
+    if((reinterpret_cast<uintptr_t>(image) & 15u) != 0) return B200RL_ERR_INVALID_ARGUMENT;
+    const int n_pad = tile_columns(N), n_tiles = (N + n_pad - 1) / n_pad, k_chunks = (K + TC_KC - 1) / TC_KC;
+    const long long pieces = (long long)n_tiles * k_chunks * n_pad * 8;
+    weight_image_kernel<<<(unsigned)((pieces + 255) / 256), 256, 0, s>>>(W, ld, N, K, transposed ? 1 : 0, n_pad, n_tiles, k_chunks, reinterpret_cast<uint8_t*>(image));
+    B200RL_LAUNCH_CHECK("weight_image");
+    return B200RL_OK;
+}
+
+int launch_gemm_tc(const GemmArgs& a, int epilogue, int activation, bool a_kcontig, bool b_kcontig, int splits, cudaStream_t s, bool b_image){
     if(a.M < 1 || a.N < 1 || a.K < 1) return B200RL_ERR_UNSUPPORTED;
+    if(b_image){
+        if(!a_kcontig || splits != 1 || a.k_per_split < a.K) return B200RL_ERR_UNSUPPORTED;
+        if(epilogue == EPI_FORWARD){ B200RL_DISPATCH_ACT(activation, return (launch_one<true, true, EPI_FORWARD, ACT, true>(a, 1, s))); }
+        if(epilogue == EPI_STORE) return launch_one<true, true, EPI_STORE, 0, true>(a, 1, s);
+        return B200RL_ERR_UNSUPPORTED;
+    }
     if(epilogue == EPI_FORWARD && a_kcontig && b_kcontig){
         B200RL_DISPATCH_ACT(activation, return (launch_one<true, true, EPI_FORWARD, ACT>(a, 1, s)));
     }

@@ -53,6 +53,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return true;
 }
 
+// transaction count of the barrier's current phase += bytes (the phase then also waits for that many bytes of bulk copies)
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes){
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// bulk (TMA) load global -> this CTA's shared memory, one destination; completion is signalled on the mbarrier as `bytes` transaction
+// bytes. Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar){
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_u32(smem)), "l"(gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // ---- operand descriptors -------------------------------------------------------------------------------------
 // Shared-memory matrix descriptor for a K-major operand stored with the 128-byte swizzle: rows of 128 bytes
 // (32 tf32 values along K), 8-row groups 1024 bytes apart, 16-byte chunk index XORed with (row mod 8); the tile

@@ -10,7 +10,8 @@
 //       per network; the reference's per-tensor containers are bound into it, so every per-tensor operation of the reference (copy,
 //       the per-layer dense overloads, persistence walks) keeps working on the same memory. Order inside the arena: for each layer
 //       W [O, I] then b [O] -- the layout of b200rl_mlp_shape -- repeated for gradients and both Adam moments; then the stored
-//       pre-activations and outputs, layer after layer, each [batch, O] dense; then the split-batch scratch of the backward pass.
+//       pre-activations and outputs, layer after layer, each [batch, O] dense; then the split-batch scratch of the backward pass and the
+//       workspace of the forward pass.
 //   evaluate / forward / backward / backward_full / backward_input (:77-204)   -> b200rl_mlp_evaluate / _forward / _backward
 //   zero_gradient (:122-129), _reset_optimizer_state (:219-228)                 -> one b200rl_fill per arena
 //   update (:210-217: one kernel per parameter tensor)                          -> ONE b200rl_adam_update_dev over the flat arena
@@ -60,8 +61,10 @@ namespace rl_tools{
             static constexpr bool SUPPORTED = SPEC::NUM_LAYERS <= B200RL_MAX_LAYERS && activation_code(SPEC::OUTPUT_ACTIVATION_FUNCTION) >= 0 && activation_code(SPEC::HIDDEN_ACTIVATION_FUNCTION) >= 0;
             static size_t scratch_bytes(){
                 if constexpr(!HAS_GRAD) return 0;
-                else{ const b200rl_mlp_shape s = shape(); return b200rl_mlp_backward_scratch_bytes(&s, (int)BATCH); }
+                else{ const b200rl_mlp_shape s = shape(); return (b200rl_mlp_backward_scratch_bytes(&s, (int)BATCH) + 255) / 256 * 256; }
             }
+            // forward workspace (the weights' tensor-core operand image of the layer in flight; 0 for small batches), behind the scratch
+            static size_t workspace_bytes(){ const b200rl_mlp_shape s = shape(); return b200rl_mlp_forward_workspace_bytes(&s, (int)BATCH); }
         };
 
         // one parameter tensor and whatever optimizer state its type carries
@@ -107,6 +110,7 @@ namespace rl_tools{
             float* pre() const { return base + L::OFF_PRE; }
             float* out() const { return base + L::OFF_OUT; }
             void* scratch() const { return base + L::OFF_SCRATCH; }
+            void* workspace() const { return reinterpret_cast<char*>(base + L::OFF_SCRATCH) + L::scratch_bytes(); }
             explicit operator bool() const { return base != nullptr; }
         };
         template <typename S> bool parameter_at(const nn::parameters::Plain::Instance<S>& p, const float* params, const float*, const float*, const float*){ return p.parameters._data == params; }
@@ -150,7 +154,7 @@ namespace rl_tools{
         static_assert(utils::typing::is_same_v<typename SPEC::TYPE_POLICY::DEFAULT, float>, "fp32 only");
         static_assert(SPEC::CAPABILITY::DYNAMIC_ALLOCATION, "device memory is allocated dynamically");
         void* base = nullptr;
-        b200::note(device, b200rl_device_malloc(&base, sizeof(float) * L::OFF_SCRATCH + L::scratch_bytes()));
+        b200::note(device, b200rl_device_malloc(&base, sizeof(float) * L::OFF_SCRATCH + L::scratch_bytes() + L::workspace_bytes()));
         b200::mlp::bind(network, static_cast<float*>(base));
     }
     template<typename DEV_SPEC, typename SPEC>
@@ -175,8 +179,10 @@ namespace rl_tools{
         const auto arena = b200::mlp::arena_of(network);
         if(arena){
             const b200rl_mlp_shape shape = b200::mlp::Layout<MODEL_SPEC>::shape();
-            b200::note(device, b200rl_mlp_evaluate(&shape, arena.params(), input._data, row_pitch(input), output._data, row_pitch(output), buffers.tick._data, buffers.tock._data,
-                                                   INPUT_SPEC::ROWS, device.stream));
+            // the workspace was sized for the network's own batch; a larger evaluation batch goes without it
+            const bool ws = INPUT_SPEC::ROWS <= MODEL_SPEC::INTERNAL_BATCH_SIZE;
+            b200::note(device, b200rl_mlp_evaluate_ws(&shape, arena.params(), input._data, row_pitch(input), output._data, row_pitch(output), buffers.tick._data, buffers.tock._data,
+                                                      INPUT_SPEC::ROWS, ws ? arena.workspace() : nullptr, ws ? b200::mlp::Layout<MODEL_SPEC>::workspace_bytes() : 0, device.stream));
             return;
         }
         // layer by layer (nn_models/mlp/operations_generic.h:77-102)
@@ -199,7 +205,8 @@ namespace rl_tools{
         const auto arena = b200::mlp::arena_of(network);
         if(arena){
             const b200rl_mlp_shape shape = b200::mlp::Layout<MODEL_SPEC>::shape();
-            b200::note(device, b200rl_mlp_forward(&shape, arena.params(), input._data, row_pitch(input), arena.pre(), arena.out(), INPUT_SPEC::ROWS, device.stream));
+            b200::note(device, b200rl_mlp_forward_ws(&shape, arena.params(), input._data, row_pitch(input), arena.pre(), arena.out(), INPUT_SPEC::ROWS,
+                                                     arena.workspace(), b200::mlp::Layout<MODEL_SPEC>::workspace_bytes(), device.stream));
             return;
         }
         nn::layers::dense::Buffer layer_buffer;                 // nn_models/mlp/operations_generic.h:103-113

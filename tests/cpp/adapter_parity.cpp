@@ -459,6 +459,9 @@ void boundary_extras(const char* name){
     for(TI b = 0; b < BATCH; b++) for(TI o = 0; o < OUTPUT_DIM; o++) rlt::set(out_cpu, b, o, rlt::get(y_cpu, b, o) * (T)0.75 + (T)0.1);
     rlt::copy(cpu, gpu, out_cpu, d_gpu);
     const T l_cpu = rlt::nn::loss_functions::mse::evaluate(cpu, y_cpu, out_cpu, (T)1.5), l_gpu = rlt::nn::loss_functions::mse::evaluate(gpu, y_gpu, d_gpu, (T)1.5);
+    // the CPU device adds BATCH * OUTPUT_DIM squares in float, one after the other: its own rounding error grows like sqrt(n) * 2^-24 (the device
+    // sums in double and rounds once); four standard deviations of that random walk bound the difference
+    const double loss_tolerance = 4.0 * std::sqrt((double)BATCH * OUTPUT_DIM) * 5.96e-8 + 1e-7;
     // the same two training steps through the arena path and through the layer-by-layer path
     rlt::copy(cpu, gpu, net_cpu, net_layers);
     rlt::zero_gradient(gpu, net_layers);
@@ -479,7 +482,7 @@ void boundary_extras(const char* name){
     rlt::copy(gpu, cpu, net_gpu, net_back); rlt::copy(gpu, cpu, net_layers, net_back2);
     const double n_all = 4.0 * (INPUT_DIM * HIDDEN_DIM + HIDDEN_DIM + HIDDEN_DIM * HIDDEN_DIM + HIDDEN_DIM + HIDDEN_DIM * OUTPUT_DIM + OUTPUT_DIM) + 2.0 * BATCH * (2 * HIDDEN_DIM + OUTPUT_DIM);
     const T path_diff = (T)(rlt::abs_diff(cpu, net_back, net_back2) / n_all);
-    const bool ok = status == 0 && arena && no_arena && init_diff == 0 && randn_diff == 0 && engine_equal && std::fabs(l_cpu - l_gpu) <= 1e-6 * std::fabs(l_cpu) && path_diff < 1e-7;
+    const bool ok = status == 0 && arena && no_arena && init_diff == 0 && randn_diff == 0 && engine_equal && std::fabs(l_cpu - l_gpu) <= loss_tolerance * std::fabs(l_cpu) && path_diff < 1e-7;
     std::printf("%-28s batch %4u  status %d  arena %d/%d  init_weights diff %.1e  randn diff %.1e  engine %d  mse loss %.7f vs %.7f  arena vs per-layer mean diff %.2e  %s\n",
                 name, BATCH, status, (int)arena, (int)no_arena, init_diff, randn_diff, (int)engine_equal, l_cpu, l_gpu, path_diff, ok ? "OK" : "FAIL");
     if(!ok) failures++;

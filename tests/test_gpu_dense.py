@@ -53,6 +53,9 @@ def test_dense_forward_backward_vs_oracle(lib, orc, torch, B, I, O, act):
     pre, y = lib.dense_forward(dev(torch, W), dev(torch, b), dev(torch, x), act)
     close(pre, pre_ref)
     close(y, y_ref)
+    if lib.lib().b200rl_dense_forward_workspace_bytes(B, I, O) > 0:       # tensor-core shapes: the workspace form (weights split once) gives the same bits
+        pre_ws, y_ws = lib.dense_forward(dev(torch, W), dev(torch, b), dev(torch, x), act, workspace=True)
+        assert torch.equal(pre_ws, pre) and torch.equal(y_ws, y)
     dW0 = mg.det_normal(seed, O * I, stream=5).reshape(O, I)   # gradients accumulate on top of existing values
     db0 = mg.det_normal(seed, O, stream=6)
     dW_ref, db_ref, din_ref, dpre_ref = orc.dense_backward(W, x, pre_ref, d_out, act, dW=dW0, db=db0)

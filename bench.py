@@ -35,7 +35,7 @@ N_ENVS, N_STEPS, STEP_LIMIT = 65536, 200, 200
 FLOP_PER_ENV_STEP = 2 * (3 * 64 + 64 * 64 + 64 * 1)      # 8,704: actor GEMMs only, no padding, no 3x for any split
 BYTES_PER_ENV_STEP = 20                                   # obs 12 + action 4 + reward 4 written per env-step
 WORKLOAD = "pendulum_rollout_65536env_x200step_actor3-64-64-1"
-TRAFFIC_BYTES_FULL_LAUNCH = 205.2e6                       # DRAM read + write bytes of one 65,536 x 200 launch (ncu, dram__bytes_read.sum + dram__bytes_write.sum)
+TRAFFIC_BYTES_FULL_LAUNCH = 203.1e6                       # DRAM read + write bytes of one 65,536 x 200 launch (ncu, dram__bytes_read.sum + dram__bytes_write.sum)
 
 
 def measured_peaks():
@@ -285,6 +285,19 @@ def measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=Tru
             res = ref.mlp_run("c5_b1024", net.params.cpu().numpy(), xs, ys, 2, 100)
             cpu = {"value": 100 * 1024 / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
                    "sample": "100 train steps (forward, mse gradient, backward, Adam) at batch 1024 of the same network, CPU_OPENBLAS build"}
+    # the reference's OWN CUDA device (cuBLAS SGEMM per layer + its kernels) on the same step, same rows resident in HBM, on this GPU: the second
+    # baseline next to its CPU path. Present where oracle/_ref/libref_cuda.so was built from the reference's headers.
+    cuda_reference = None
+    if cpu_baseline and world == 1:
+        import oracle
+        if os.path.exists(oracle.REF_CUDA_SO):
+            g2 = torch.Generator(device=dev); g2.manual_seed(1234)
+            xr, yr = torch.randn((rows, 64), device=dev, generator=g2), torch.randn((rows, 16), device=dev, generator=g2)
+            torch.cuda.synchronize()
+            ref_ms, _, _ = oracle.ReferenceCuda().mlp_train("c5_b65536", net.params.cpu().numpy(), xr.data_ptr(), yr.data_ptr(), rows, steps=2, warmup=1)
+            cuda_reference = {"value": rows / (ref_ms * 1e-3), "unit": "samples/s", "ms_per_step": ref_ms, "kind": "reference",
+                              "build": "unmodified reference headers, devices::CUDA (cublasSgemm, fp32), nvcc -O3 sm_100a", "sample": "2 steps after 1 warm-up, same rows and chunking"}
+            del xr, yr
     tf = flop / (ms * 1e-3) / 1e12
     return {"metric": "MLP fwd+bwd+Adam samples/s", "value": rows * world / (ms * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms, "allreduce_ms": exchange_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -293,7 +306,7 @@ def measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=Tru
             "replicas_bit_identical": replicas_equal,
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tf / peaks["tflops"], "traffic": None,
                          "peak_source": peaks["source"] + " bf16 dense (burst)", "frac_of_3xtf32_ceiling": tf / (peaks["tflops"] / 6.0)},
-            "cpu_baseline": cpu, "gpu_launches": launches}
+            "cpu_baseline": cpu, "cuda_reference": cuda_reference, "gpu_launches": launches}
 
 
 def run_mlp_train(args):
@@ -805,6 +818,8 @@ def main():
                     help="collect: random numbers from host draw tables (bit-compatible with the reference's host engine) or drawn inside the kernel")
     ap.add_argument("--train-rows", type=int, default=1 << 24, help="mlp_train: total input rows over all GPUs")
     args = ap.parse_args()
+    import faulthandler
+    faulthandler.enable()                          # a crash in native code prints the Python stack it happened under
     if args.workload == "mlp_train":
         return run_mlp_train(args)
     if args.workload == "collect":
@@ -960,10 +975,21 @@ def main():
                     "frac_of_split_ceiling": achieved_tflops / (peaks["tflops"] / 3.0),
                     "hbm_write_gbs": BYTES_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]}
         cpu = None if args.no_cpu_baseline else cpu_reference_rate()
+        # the reference's OWN CUDA runner (prologue kernel, per-layer bias / cublasSgemm / activation, epilogue kernel: ~12 launches per step) on
+        # this GPU, same environment count, step limit and actor: the second baseline next to its CPU path
+        cuda_reference = None
+        if not args.no_cpu_baseline and (N_ENVS, N_STEPS) == (65536, 200):
+            import oracle
+            if os.path.exists(oracle.REF_CUDA_SO):
+                ref_ms, mean_return = oracle.ReferenceCuda().rollout("65536env", params_h[:4481], steps=2, warmup=1)
+                cuda_reference = {"value": N_ENVS * N_STEPS / (ref_ms * 1e-3), "unit": "env-steps/s", "ms_per_step": ref_ms, "kind": "reference",
+                                  "build": "unmodified reference headers, devices::CUDA off-policy runner step<0> (cublasSgemm, fp32, cuRAND resets), nvcc -O3 sm_100a",
+                                  "sample": "2 rollouts of 200 runner steps after 1 warm-up rollout, incl. the replay-buffer append the runner does",
+                                  "mean_episode_return": mean_return}
         line = {"metric": "env-steps/s (fused actor fwd + env step)", "value": value, "unit": "env-steps/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic", "config": rollout_config(world, workload),
-                "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
+                "roofline": roofline, "cpu_baseline": cpu, "cuda_reference": cuda_reference, "clocks": clocks.summary(),
                 "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
                         "copy_only_value": copy_only_value, "copy_only_note": "the same device-to-host bytes copied by all ranks at once and nothing else: the host link's ceiling for this call"},
                 "gpu_launches": 2 * args.steps, "wall_s_timed_region": wall,

@@ -427,6 +427,23 @@ int b200rl_sac_min_value_d_output(const float* q1, int ld_q1, const float* q2, i
                                   int ld_d_input, int action_offset, int action_dim, float* d_actor_output, int ld_out, int batch,
                                   b200rl_stream_t stream);
 
+/* The small tensor operations between the network passes of train_critic / train_actor, with every operand in device memory, so that the
+ * reference's generic verbs (rl/algorithms/sac/operations_generic.h:243-336, 378-456) run on the device without a host read-back.
+ *  b200rl_mse_gradient_dev_weight  mse::gradient with the loss weight in a one-element device tensor (nn/loss_functions/mse/operations_generic.h:66-79)
+ *  b200rl_mask_count               result[0] = number of set entries of a bool mask (cast_reduce_sum<T>, containers/tensor/operations_generic.h:838-845;
+ *                                  CUDA form containers/tensor/operations_cuda.h:308-315), n < 2^24
+ *  b200rl_scale                    t[i] = t[i] * scale, or (1 / t[i]) * scale with reciprocal != 0 (scale, containers/tensor/operations_generic.h:712-719, 433-445)
+ *  b200rl_fill_from_device         dst[0..n) = value[0] (set_all(tensor, one-element tensor), :741-748)
+ *  b200rl_mask_rows                rows r of target [rows, cols] with (mask[r] != 0) != (invert != 0) receive row r of source, or zeros when source == NULL
+ *                                  (mask_actions and mask_gradient, rl/algorithms/sac/operations_generic.h:180-232; CUDA forms sac/operations_cuda.h:76-127) */
+int b200rl_mse_gradient_dev_weight(const float* a, int lda, const float* b, int ldb, float* d_a, int ldd, int rows, int cols, const float* loss_weight,
+                                   b200rl_stream_t stream);
+int b200rl_mask_count(const uint8_t* mask, size_t n, float* result, b200rl_stream_t stream);
+int b200rl_scale(float* t, size_t n, float scale, int reciprocal, b200rl_stream_t stream);
+int b200rl_fill_from_device(float* dst, size_t n, const float* value, b200rl_stream_t stream);
+int b200rl_mask_rows(const float* source, int ld_source, float* target, int ld_target, const uint8_t* mask, int rows, int cols, int invert,
+                     b200rl_stream_t stream);
+
 /* Randomness kept entirely on the device, for update loops captured in a CUDA graph: *call_counter (a device-resident 64-bit integer)
  * takes the place of call_index in the sampling kernel and in the normal generator, and b200rl_counter_advance adds to it on the stream,
  * so that every replay of one captured graph draws fresh indices and noise. b200rl_randn_device_rng fills dst[0..n) with standard normals:
@@ -464,15 +481,26 @@ int b200rl_standardize_forward(const float* x, int ldx, const float* mean, const
  *   B200RL_ENV_ACROBOT_SWINGUP: state [N, 4] = theta_1, theta_2, theta_1_dot, theta_2_dot, observation 6 = cos / sin of both angles and
  *                               the velocities; RK4 step of dt 0.2, swing-up reward on the next state, never terminates
  *                               (rl/environments/acrobot/operations_generic.h:46-199, default parameters acrobot.h:11-27)
- * reset_states [R, N, 2]: the two uniform draws of an initial state (Pendulum: theta, theta_dot; Acrobot: theta_1, theta_2, velocities 0),
- * in the reference engine's order. The actor is OBS -> 64 -> 64 -> 1. obs [T * N, OBS], act / rew [T * N, 1], row = step * N + env. */
+ *   B200RL_ENV_ACROBOT:         the variant that TERMINATES (rl::environments::Acrobot): same dynamics and observation, reward -1 per step
+ *                               (:154-156), terminated when the tip is above the bar, evaluated on the next state (:193-195); an episode ends
+ *                               (truncated) at termination or at the step limit (operations_generic_per_env.h:93-97)
+ * reset_states [R, N, D] with D = b200rl_env_reset_dim(env): the draws of an initial state in the reference engine's order (Pendulum:
+ * theta, theta_dot; AcrobotSwingup: theta_1, theta_2, velocities 0; Acrobot: all four components, U(-0.1, 0.1)).
+ * The actor is OBS -> 64 -> 64 -> 1. obs [T * N, OBS], act / rew [T * N, 1], row = step * N + env.
+ * b200rl_env_rollout_flags additionally writes the environment's terminated flag of every transition (terminated [T * N], may be NULL):
+ * the column the replay buffer and the critic target need for environments that terminate. */
 #define B200RL_ENV_PENDULUM 0
 #define B200RL_ENV_ACROBOT_SWINGUP 1
+#define B200RL_ENV_ACROBOT 2
 int b200rl_env_observation_dim(int env);
 int b200rl_env_state_dim(int env);
+int b200rl_env_reset_dim(int env);
 int b200rl_env_rollout(int env, const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step, uint8_t* truncated,
                        float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps, int step_limit, float* obs,
                        float* act, float* rew, int* error_flag, b200rl_stream_t stream);
+int b200rl_env_rollout_flags(int env, const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step, uint8_t* truncated,
+                       float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps, int step_limit, float* obs,
+                       float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream);
 
 /* Epoch shuffle of the PPO update (SHUFFLE_EPOCH, rl/algorithms/ppo/operations_generic.h:127-158): the reference swaps row i with a
  * row drawn by std::uniform_int_distribution from [i, n-1], for i = 0..n-1, on the observation, action, advantage, log-prob and

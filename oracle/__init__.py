@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "_build", "liboracle.so")
 REF_STRICT_SO = os.path.join(_HERE, "_ref", "libref_strict.so")
 REF_FAST_SO = os.path.join(_HERE, "_ref", "libref_fast.so")
+REF_CUDA_SO = os.path.join(_HERE, "_ref", "libref_cuda.so")
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
 
@@ -25,8 +26,12 @@ _u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
 def build(ref: bool = True) -> None:
     """Compile oracle.c (always) and the reference driver (when the reference tree exists)."""
     subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
-    if ref and os.path.isdir(os.environ.get("B200RL_REFERENCE", "/root/reference")):
-        subprocess.run(["make", "-s", "-C", _HERE, "ref", "REFERENCE=" + os.environ.get("B200RL_REFERENCE", "/root/reference")], check=True)
+    # the reference tree: named by B200RL_REFERENCE, else a checkout next to this repository; absent -> the prebuilt _ref libraries are used
+    reference = os.environ.get("B200RL_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    if ref and os.path.isdir(os.path.join(reference, "include", "rl_tools")):
+        subprocess.run(["make", "-s", "-C", _HERE, "ref", "REFERENCE=" + reference], check=True)
+        if os.path.exists("/usr/local/cuda/bin/nvcc"):            # the reference's own CUDA device, as the second baseline
+            subprocess.run(["make", "-s", "-C", _HERE, "ref_cuda", "REFERENCE=" + reference], check=True)
 
 
 class MlpShape(C.Structure):
@@ -106,6 +111,10 @@ class Oracle:
         L.orc_acrobot_step_batch.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.orc_acrobot_rollout.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_void_p]
         L.orc_acrobot_rollout.restype = C.c_int
+        L.orc_acrobot_rollout_variant.argtypes = [C.c_int, C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, _u8p,
+                                                  C.c_void_p]
+        L.orc_acrobot_rollout_variant.restype = C.c_int
+        L.orc_acrobot_terminating_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
         L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
@@ -339,6 +348,26 @@ class Oracle:
         draws = self.uniform_stream(seed, 2 * n, -np.float32(np.pi), np.float32(np.pi)).reshape(n, 2)
         return np.concatenate([draws, np.zeros((n, 2), np.float32)], axis=1)
 
+    def acrobot_terminating_initial_states(self, seed, n):
+        """n initial states of the terminating Acrobot (four U(-0.1, 0.1) draws each, double bounds) from a fresh engine: [n, 4]."""
+        s = np.empty((n, 4), np.float32)
+        self.lib.orc_acrobot_terminating_initial_states(seed, n, s)
+        return s
+
+    def acrobot_terminating_rollout(self, shape, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500):
+        """The runner loop on the terminating Acrobot: reset_states [R, N, 4]; returns obs, act, rew, terminated and the runner state."""
+        N = states.shape[0]
+        states, episode_step, truncated, episode_return = (np.array(states, np.float32), np.array(episode_step, np.int32), np.array(truncated, np.uint8),
+                                                           np.array(episode_return, np.float32))
+        reset_states = np.ascontiguousarray(reset_states, np.float32)
+        assert reset_states.shape[1:] == (N, 4)
+        obs, act, rew, term = np.empty((T * N, 6), np.float32), np.empty((T * N, 1), np.float32), np.empty((T * N, 1), np.float32), np.empty(T * N, np.uint8)
+        rc = self.lib.orc_acrobot_rollout_variant(1, C.byref(shape), np.ascontiguousarray(params, np.float32), N, T, states, episode_step, truncated, episode_return,
+                                                  reset_states, reset_states.shape[0], step_limit, obs, act, rew, term, None)
+        if rc != 0:
+            raise RuntimeError(f"orc_acrobot_rollout_variant rc={rc}")
+        return dict(obs=obs, act=act, rew=rew, terminated=term, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
+
     def acrobot_rollout(self, shape, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500, teacher_states=None):
         N = states.shape[0]
         states, episode_step = states.copy(), episode_step.copy()
@@ -533,6 +562,44 @@ class Oracle:
         return d_actions, d_log_std
 
 
+class ReferenceCuda:
+    """The real reference on ITS OWN CUDA device (libref_cuda.so: cuBLAS SGEMM + the reference's kernels). Present only where it was built;
+    needs a GPU to run. Arguments that are device memory are passed as raw addresses (torch tensors' data_ptr())."""
+    CASES = {"c5_b65536": (0, 65536, 64, 16, 152336), "c5_b1024": (1, 1024, 64, 16, 152336), "c3_b256": (2, 256, 4, 1, 67329)}
+
+    def __init__(self):
+        if not os.path.exists(REF_CUDA_SO):
+            raise FileNotFoundError(REF_CUDA_SO)
+        self.lib = C.CDLL(REF_CUDA_SO)
+        self.lib.ref_cuda_mlp_train.argtypes = [C.c_int, C.c_longlong, C.c_int, C.c_int, _f32p, C.c_void_p, C.c_void_p, C.POINTER(C.c_float), _f32p, _f32p]
+        self.lib.ref_cuda_mlp_train.restype = C.c_int
+        self.lib.ref_cuda_rollout.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        self.lib.ref_cuda_rollout.restype = C.c_int
+
+    def rollout(self, case, actor_params, steps, warmup=0):
+        """`steps` timed rollouts of 200 off-policy runner steps (the reference's step<0> on its CUDA device) of the deterministic actor
+        3 -> 64 -> 64 -> 1 on 65,536 ("65536env") or 512 ("512env") Pendulum environments. Returns (ms per rollout, mean episode return)."""
+        params = np.ascontiguousarray(actor_params, np.float32)
+        assert params.size == 4481
+        ms, probe = C.c_float(), C.c_float()
+        rc = self.lib.ref_cuda_rollout({"65536env": 0, "512env": 1}[case], steps, warmup, params, C.byref(ms), C.byref(probe))
+        if rc != 0:
+            raise RuntimeError(f"ref_cuda_rollout returned {rc}")
+        return ms.value, probe.value
+
+    def mlp_train(self, case, params, x_ptr, y_ptr, rows, steps, warmup=0):
+        """`steps` training steps (zero_gradient; per chunk forward, MSE gradient weighted chunk / rows, backward; Adam) after `warmup` untimed
+        ones. Returns (ms per step, parameters afterwards, gradient of the last step)."""
+        which, chunk, _, _, n_params = self.CASES[case]
+        params = np.ascontiguousarray(params, np.float32)
+        assert params.size == n_params and rows % chunk == 0
+        out, grads, ms = np.empty(n_params, np.float32), np.empty(n_params, np.float32), C.c_float()
+        rc = self.lib.ref_cuda_mlp_train(which, rows, steps, warmup, params, x_ptr, y_ptr, C.byref(ms), out, grads)
+        if rc != 0:
+            raise RuntimeError(f"ref_cuda_mlp_train returned {rc}")
+        return ms.value, out, grads
+
+
 class Reference:
     """Typed wrapper around the real reference (libref_strict.so / libref_fast.so). Present only where it was built."""
 
@@ -561,6 +628,8 @@ class Reference:
         L.ref_acrobot_rollout.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p]
         L.ref_acrobot_step.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_acrobot_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
+        L.ref_acrobot_terminating_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
+        L.ref_acrobot_terminating_rollout.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, _u8p]
         L.ref_normalizer.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_sac_updates.argtypes = [C.c_int, C.c_int, C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _u8p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_sample_and_squash.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
@@ -658,6 +727,24 @@ class Reference:
         s = np.empty((n, 4), np.float32)
         self.lib.ref_acrobot_initial_states(seed, n, s)
         return s
+
+    def acrobot_terminating_initial_states(self, seed, n):
+        s = np.empty((n, 4), np.float32)
+        self.lib.ref_acrobot_terminating_initial_states(seed, n, s)
+        return s
+
+    def acrobot_terminating_rollout(self, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500):
+        """The reference's own observe / step / reward / terminated of rl::environments::Acrobot under the runner loop; reset_states [R, N, 4]."""
+        N = states.shape[0]
+        states, episode_step, truncated, episode_return = (np.array(states, np.float32), np.array(episode_step, np.int32), np.array(truncated, np.uint8),
+                                                           np.array(episode_return, np.float32))
+        reset_states = np.ascontiguousarray(reset_states, np.float32)
+        obs, act, rew, term = np.empty((T * N, 6), np.float32), np.empty((T * N, 1), np.float32), np.empty((T * N, 1), np.float32), np.empty(T * N, np.uint8)
+        rc = self.lib.ref_acrobot_terminating_rollout(np.ascontiguousarray(params, np.float32), N, T, states, episode_step, truncated, episode_return, reset_states,
+                                                      reset_states.shape[0], step_limit, obs, act, rew, term)
+        if rc != 0:
+            raise RuntimeError(f"ref_acrobot_terminating_rollout rc={rc}")
+        return dict(obs=obs, act=act, rew=rew, terminated=term, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
 
     def acrobot_rollout(self, params, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500):
         N = states.shape[0]

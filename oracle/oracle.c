@@ -69,6 +69,16 @@ static float orc_canonical(orc_rng* r){
 float orc_uniform_real(orc_rng* r, float lo, float hi){
     return orc_canonical(r) * (hi - lo) + lo;
 }
+/* The same call with double bounds (the reference writes some bounds as double literals, e.g. rl/environments/acrobot/operations_generic.h:40-43):
+ * std::uniform_real_distribution<double> -> std::generate_canonical<double, 53>(mt19937): TWO 32-bit draws, low word first,
+ * (g0 + g1 * 2^32) rounded to double, divided by 2^64; then u * (hi - lo) + lo in double. */
+double orc_uniform_real_double(orc_rng* r, double lo, double hi){
+    double sum = (double)orc_rng_next(r);
+    sum += (double)orc_rng_next(r) * 4294967296.0;
+    double ret = sum / 18446744073709551616.0;
+    if(ret >= 1.0) ret = nextafter(1.0, 0.0);
+    return ret * (hi - lo) + lo;
+}
 /* random/operations_cpu.h:40-48: a FRESH std::normal_distribution<float>(mean, std) per sample, so the second
  * value of the Marsaglia polar pair is always discarded; std == 0 returns mean without consuming the engine. */
 float orc_normal(orc_rng* r, float mean, float std){
@@ -475,6 +485,16 @@ float orc_acrobot_swingup_reward(const float next_state[4]){
     float b_angle_cost = fabsf(orc_acrobot_angle_normalize(next_state[1]));
     return (-a_angle_cost - b_angle_cost) / 100 * A_DT / 0.02;
 }
+/* the terminating variant (rl::environments::Acrobot): reward -1 per step (:154-156); terminated when the tip is above the bar,
+ * (-cos(theta_1) - cos(theta_2 + theta_1)) > 1.0 with the unqualified cos of a float, i.e. in double (:193-195), evaluated on the NEXT
+ * state by the runner; initial state: four draws U(-0.1, 0.1) with double bounds, each rounded to float (:38-44) */
+int orc_acrobot_terminated(const float state[4]){
+    return (-ORC_ACROBOT_COS((double)state[0]) - ORC_ACROBOT_COS((double)(state[1] + state[0]))) > 1.0;
+}
+void orc_acrobot_terminating_initial_states(uint32_t seed, int n, float* states){
+    orc_rng r; orc_rng_init(&r, seed);
+    for(int i = 0; i < 4 * n; i++) states[i] = (float)orc_uniform_real_double(&r, -0.1, 0.1);
+}
 void orc_acrobot_observe(const float state[4], float* obs){
     obs[0] = cosf(state[0]); obs[1] = sinf(state[0]); obs[2] = cosf(state[1]); obs[3] = sinf(state[1]); obs[4] = state[2]; obs[5] = state[3];
 }
@@ -488,10 +508,13 @@ void orc_acrobot_step_batch(int n, const float* states, const float* actions, fl
 }
 /* The rollout of orc_pendulum_rollout for AcrobotSwingup: states [N, 4], observations [T * N, 6], actor 6 -> .. -> 1; a reset takes      */
 /* (theta_1, theta_2) from reset_states [R, N, 2] and zeroes the velocities.                                                               */
-int orc_acrobot_rollout(const orc_mlp_shape* actor, const float* params, int N, int T, float* states, int32_t* episode_step,
-                        uint8_t* truncated, float* episode_return, const float* reset_states, int R, int step_limit,
-                        float* obs, float* actions, float* rew, const float* teacher_states){
+/* terminating != 0: the terminating variant; a reset then takes all four state components from reset_states [R, N, 4], the reward is -1,  */
+/* and `terminated` [T * N] (may be NULL) receives the flag that also ends the episode (per_env.h:93-97).                                 */
+int orc_acrobot_rollout_variant(int terminating, const orc_mlp_shape* actor, const float* params, int N, int T, float* states, int32_t* episode_step,
+                                uint8_t* truncated, float* episode_return, const float* reset_states, int R, int step_limit,
+                                float* obs, float* actions, float* rew, uint8_t* terminated, const float* teacher_states){
     int rc = 0;
+    const int D = terminating ? 4 : 2;
     int* reset_count = (int*)calloc((size_t)N, sizeof(int));
     if(actor->input_dim != 6 || actor->dims[actor->n_layers - 1] != 1) { free(reset_count); return -1; }
     for(int t = 0; t < T; t++){
@@ -500,9 +523,7 @@ int orc_acrobot_rollout(const orc_mlp_shape* actor, const float* params, int N, 
         for(int e = 0; e < N; e++){
             if(truncated[e]){
                 if(reset_count[e] >= R){ rc = -2; continue; }
-                states[4 * e] = reset_states[((size_t)reset_count[e] * N + e) * 2];
-                states[4 * e + 1] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 1];
-                states[4 * e + 2] = 0; states[4 * e + 3] = 0;
+                for(int k = 0; k < 4; k++) states[4 * e + k] = k < D ? reset_states[((size_t)reset_count[e] * N + e) * D + k] : 0;
                 reset_count[e]++; episode_step[e] = 0; episode_return[e] = 0;
             }
             orc_acrobot_observe(states + 4 * e, obs_t + 6 * e);
@@ -511,14 +532,22 @@ int orc_acrobot_rollout(const orc_mlp_shape* actor, const float* params, int N, 
         for(int e = 0; e < N; e++){
             float ns[4];
             orc_acrobot_step(states + 4 * e, act_t[e], ns);
-            float r = orc_acrobot_swingup_reward(ns);
+            float r = terminating ? -1.0f : orc_acrobot_swingup_reward(ns);
+            const int term = terminating ? orc_acrobot_terminated(ns) : 0;
             episode_step[e] += 1; episode_return[e] += r;
-            truncated[e] = (episode_step[e] == step_limit);
+            truncated[e] = term || (episode_step[e] == step_limit);
             rew_t[e] = r; memcpy(states + 4 * e, ns, sizeof(ns));
+            if(terminated) terminated[(size_t)t * N + e] = (uint8_t)term;
         }
     }
     free(reset_count);
     return rc;
+}
+int orc_acrobot_rollout(const orc_mlp_shape* actor, const float* params, int N, int T, float* states, int32_t* episode_step,
+                        uint8_t* truncated, float* episode_return, const float* reset_states, int R, int step_limit,
+                        float* obs, float* actions, float* rew, const float* teacher_states){
+    return orc_acrobot_rollout_variant(0, actor, params, N, T, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew, NULL,
+                                       teacher_states);
 }
 
 /* ------------------------------------------------------------------------------------------------------ */

@@ -775,10 +775,15 @@ static void normalizer_case(int n_updates, const float* data, float* mean_out, f
 // actor 6 -> 64 -> 64 -> 1 (ReLU, tanh) evaluated one environment at a time; the runner semantics of Rollout<> above. states [N, 4];
 // a reset takes (theta_1, theta_2) from reset_states [R, N, 2] and zeroes the velocities (sample_initial_state of AcrobotSwingup, :46-53).
 using ACROBOT = rlt::rl::environments::AcrobotSwingup<rlt::rl::environments::acrobot::Specification<T, TI, rlt::rl::environments::acrobot::DefaultParameters<T>>>;
+// the variant that TERMINATES (reward -1 per step until the tip is above the bar, :154-156, 193-195); its initial state is four draws (:38-44)
+using ACROBOT_TERMINATING = rlt::rl::environments::Acrobot<rlt::rl::environments::acrobot::Specification<T, TI, rlt::rl::environments::acrobot::DefaultParameters<T>>>;
 static void acrobot_load(typename ACROBOT::State& s, const float* p){ s.theta_1 = p[0]; s.theta_2 = p[1]; s.theta_1_dot = p[2]; s.theta_2_dot = p[3]; }
 static void acrobot_store(const typename ACROBOT::State& s, float* p){ p[0] = s.theta_1; p[1] = s.theta_2; p[2] = s.theta_1_dot; p[3] = s.theta_2_dot; }
+// RESET_DIM values of reset_states [R, N, RESET_DIM] overwrite the leading state components at a reset, the rest are zeroed; terminated_out
+// [T * N] (may be null) receives the environment's terminated flag of every transition
+template <typename ACROBOT, TI RESET_DIM>
 static int acrobot_rollout(const float* params, TI N, TI Tsteps, float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
-                           const float* reset_states, TI R, TI step_limit, float* obs, float* actions, float* rew){
+                           const float* reset_states, TI R, TI step_limit, float* obs, float* actions, float* rew, uint8_t* terminated_out){
     using CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
     using NET = rlt::nn_models::mlp::NeuralNetwork<CONFIG, rlt::nn::capability::Forward<>, rlt::tensor::Shape<TI, 1, 1, 6>>;
     DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
@@ -795,7 +800,7 @@ static int acrobot_rollout(const float* params, TI N, TI Tsteps, float* states, 
             float* st = states + 4 * e;
             if(truncated[e]){
                 if(reset_count[e] >= R){ rc = -2; continue; }
-                st[0] = reset_states[((size_t)reset_count[e] * N + e) * 2]; st[1] = reset_states[((size_t)reset_count[e] * N + e) * 2 + 1]; st[2] = 0; st[3] = 0;
+                for(TI k = 0; k < 4; k++) st[k] = k < RESET_DIM ? reset_states[((size_t)reset_count[e] * N + e) * RESET_DIM + k] : 0;
                 reset_count[e]++; episode_step[e] = 0; episode_return[e] = 0;
             }
             typename ACROBOT::State s, ns; acrobot_load(s, st);
@@ -809,6 +814,7 @@ static int acrobot_rollout(const float* params, TI N, TI Tsteps, float* states, 
             episode_step[e] += 1; episode_return[e] += r;
             truncated[e] = terminated_flag || ((TI)episode_step[e] == step_limit);
             rew[(size_t)t * N + e] = r;
+            if(terminated_out) terminated_out[(size_t)t * N + e] = terminated_flag ? 1 : 0;
             acrobot_store(ns, st);
         }
     }
@@ -856,7 +862,16 @@ int ref_ppo_train(int env, int N, int steps, int batch, int epochs, int shuffle,
 }
 int ref_acrobot_rollout(const float* params, int N, int Tsteps, float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
                         const float* reset_states, int R, int step_limit, float* obs, float* actions, float* rew){
-    return acrobot_rollout(params, N, Tsteps, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew);
+    return acrobot_rollout<ACROBOT, 2>(params, N, Tsteps, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew, nullptr);
+}
+int ref_acrobot_terminating_rollout(const float* params, int N, int Tsteps, float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return,
+                                    const float* reset_states, int R, int step_limit, float* obs, float* actions, float* rew, uint8_t* terminated){
+    return acrobot_rollout<ACROBOT_TERMINATING, 4>(params, N, Tsteps, states, episode_step, truncated, episode_return, reset_states, R, step_limit, obs, actions, rew, terminated);
+}
+void ref_acrobot_terminating_initial_states(uint32_t seed, int n, float* states){
+    DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    ACROBOT_TERMINATING env; typename ACROBOT_TERMINATING::Parameters env_params;
+    for(int e = 0; e < n; e++){ typename ACROBOT_TERMINATING::State s; rlt::sample_initial_state(device, env, env_params, s, rng); acrobot_store(s, states + 4 * e); }
 }
 void ref_acrobot_step(int n, const float* states, const float* actions, float* next_states, float* rewards, float* obs, float* next_obs){
     DEVICE device; RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);

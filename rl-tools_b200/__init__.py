@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "dense_tc.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "mlp_fused.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
@@ -136,6 +136,11 @@ def lib():
         L.b200rl_dense_init_weights.argtypes = [vp, f, f, i, vp, vp, i, i, vp]
         L.b200rl_randn_host_rng.argtypes = [vp, vp, i, i, i, vp]
         L.b200rl_mse_evaluate.argtypes = [vp, i, vp, i, i, i, f, vp, vp]
+        L.b200rl_mse_gradient_dev_weight.argtypes = [vp, i, vp, i, vp, i, i, i, vp, vp]
+        L.b200rl_mask_count.argtypes = [vp, sz, vp, vp]
+        L.b200rl_scale.argtypes = [vp, sz, f, i, vp]
+        L.b200rl_fill_from_device.argtypes = [vp, sz, vp, vp]
+        L.b200rl_mask_rows.argtypes = [vp, i, vp, i, vp, i, i, i, vp]
         L.b200rl_reset_table_host.argtypes = [vp, i, i, vp, vp, i, vp, i, C.POINTER(i)]
         L.b200rl_shuffle_permutation_host.argtypes = [vp, i, vp]
         L.b200rl_permute_rows_scratch_bytes.argtypes = [i, C.c_uint64]
@@ -156,6 +161,8 @@ def lib():
         L.b200rl_env_observation_dim.argtypes = [i]
         L.b200rl_env_state_dim.argtypes = [i]
         L.b200rl_env_rollout.argtypes = [i, shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp]
+        L.b200rl_env_rollout_flags.argtypes = [i, shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp]
+        L.b200rl_env_reset_dim.argtypes = [i]
         L.b200rl_polyak_update.argtypes = [vp, i, vp, i, i, i, f, i, vp]
         L.b200rl_replay_counters.argtypes = [vp, C.POINTER(ReplayLayout), i, vp, vp, vp]
         L.b200rl_gather_draws_host.argtypes = [vp, i, i, vp, vp, i, vp, vp]
@@ -239,6 +246,36 @@ def mse_gradient(a, b, loss_weight=1.0, d_a=None):
     check(lib().b200rl_mse_gradient(_ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(d_a), d_a.stride(0), a.shape[0], a.shape[1], loss_weight, _stream()),
           "b200rl_mse_gradient")
     return d_a
+
+
+def mse_gradient_dev_weight(a, b, loss_weight, d_a=None):
+    """mse_gradient with the loss weight read from the one-element device tensor `loss_weight`."""
+    import torch
+    d_a = torch.empty_like(a) if d_a is None else d_a
+    check(lib().b200rl_mse_gradient_dev_weight(_ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(d_a), d_a.stride(0), a.shape[0], a.shape[1], _ptr(loss_weight),
+                                               _stream()), "b200rl_mse_gradient_dev_weight")
+    return d_a
+
+
+def mask_count(mask, result):
+    """result[0] = number of set entries of the uint8 / bool device tensor `mask` (the reference's cast_reduce_sum)."""
+    check(lib().b200rl_mask_count(_ptr(mask), mask.numel(), _ptr(result), _stream()), "b200rl_mask_count")
+
+
+def scale_(t, scale, reciprocal=False):
+    """In place: t * scale, or (1 / t) * scale."""
+    check(lib().b200rl_scale(_ptr(t), t.numel(), scale, int(reciprocal), _stream()), "b200rl_scale")
+
+
+def fill_from_device(dst, value):
+    """dst[:] = value[0] with `value` a one-element device tensor."""
+    check(lib().b200rl_fill_from_device(_ptr(dst), dst.numel(), _ptr(value), _stream()), "b200rl_fill_from_device")
+
+
+def mask_rows(target, mask, source=None, invert=False):
+    """Rows of `target` [rows, cols] whose mask (inverted if asked) is set receive the row of `source`, or zeros without a source."""
+    check(lib().b200rl_mask_rows(_ptr(source) if source is not None else None, source.stride(0) if source is not None else 0, _ptr(target), target.stride(0),
+                                 _ptr(mask), target.shape[0], target.shape[1], int(invert), _stream()), "b200rl_mask_rows")
 
 
 def mse_evaluate(a, b, loss_weight=1.0):
@@ -674,12 +711,14 @@ class RunningNormalizer:
         return y
 
 
-ENV_PENDULUM, ENV_ACROBOT_SWINGUP = 0, 1
+ENV_PENDULUM, ENV_ACROBOT_SWINGUP, ENV_ACROBOT = 0, 1, 2
 
 
-def env_rollout(env, shape, params, states, episode_step, truncated, episode_return, reset_states, n_steps, step_limit, obs=None, act=None, rew=None, error_flag=None):
-    """The fused rollout for an environment given by id (ENV_PENDULUM, ENV_ACROBOT_SWINGUP): in place on the runner state tensors,
-    returns (obs [T * N, OBS], act, rew). All tensors live on the GPU."""
+def env_rollout(env, shape, params, states, episode_step, truncated, episode_return, reset_states, n_steps, step_limit, obs=None, act=None, rew=None, error_flag=None,
+                terminated=None):
+    """The fused rollout for an environment given by id (ENV_PENDULUM, ENV_ACROBOT_SWINGUP, ENV_ACROBOT): in place on the runner state tensors,
+    returns (obs [T * N, OBS], act, rew). All tensors live on the GPU. terminated: an optional uint8 tensor [T * N] that receives the
+    environment's terminated flag of every transition."""
     import torch
     N, dev = states.shape[0], states.device
     O = lib().b200rl_env_observation_dim(env)
@@ -688,6 +727,7 @@ def env_rollout(env, shape, params, states, episode_step, truncated, episode_ret
     act = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if act is None else act
     rew = torch.empty((n_steps * N, 1), device=dev, dtype=torch.float32) if rew is None else rew
     R = 0 if reset_states is None else reset_states.shape[0]
-    check(lib().b200rl_env_rollout(env, C.byref(shape), _ptr(params), _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return), _ptr(reset_states), R,
-                                   N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(error_flag), _stream()), "b200rl_env_rollout")
+    assert reset_states is None or reset_states.shape[1:] == (N, lib().b200rl_env_reset_dim(env))
+    check(lib().b200rl_env_rollout_flags(env, C.byref(shape), _ptr(params), _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return), _ptr(reset_states), R,
+                                         N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(terminated), _ptr(error_flag), _stream()), "b200rl_env_rollout_flags")
     return obs, act, rew

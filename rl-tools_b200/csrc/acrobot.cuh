@@ -90,4 +90,10 @@ __device__ __forceinline__ float swingup_reward(const float (&next)[4]){
     return (float)__ddiv_rn((double)scaled, 0.02);
 }
 
+// the terminating variant, operations_generic.h:193-195: (-cos(theta_1) - cos(theta_2 + theta_1)) > 1.0, the unqualified cos of a float
+// argument, i.e. evaluated in double on the float-rounded sum
+__device__ __forceinline__ bool terminated(const float (&s)[4]){
+    return __dsub_rn(-cos((double)s[0]), cos((double)__fadd_rn(s[1], s[0]))) > 1.0;
+}
+
 }}  // namespace b200rl::acrobot

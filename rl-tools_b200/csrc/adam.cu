@@ -138,6 +138,49 @@ __global__ void __launch_bounds__(256) polyak_kernel(const float* __restrict__ s
     }
 }
 
+// ---- small tensor operations of the SAC update whose operands live in device memory ------------------------------------------------
+// mse::gradient with the loss weight read from a one-element device tensor (nn/loss_functions/mse/operations_generic.h:66-79)
+__global__ void __launch_bounds__(256) mse_gradient_dev_weight_kernel(const float* __restrict__ a, long long lda, const float* __restrict__ b, long long ldb, float* d,
+                                                                      long long ldd, int rows, int cols, const float* __restrict__ loss_weight){
+    const float constant = __fmul_rn(__fdiv_rn(2.0f, __fmul_rn((float)rows, (float)cols)), __ldg(loss_weight));
+    long long n = (long long)rows * cols;
+    for(long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x){
+        long long r = i / cols; int c = (int)(i - r * cols);
+        d[r * ldd + c] = __fmul_rn(__fsub_rn(a[r * lda + c], b[r * ldb + c]), constant);
+    }
+}
+// cast_reduce_sum<float> of a mask (containers/tensor/operations_generic.h:838-845): the count is an integer, exact in float below 2^24
+__global__ void __launch_bounds__(256) mask_count_kernel(const uint8_t* __restrict__ mask, size_t n, float* result){
+    __shared__ unsigned int part[256];
+    unsigned int count = 0;
+    for(size_t i = threadIdx.x; i < n; i += blockDim.x) count += mask[i] != 0;
+    part[threadIdx.x] = count;
+    __syncthreads();
+    for(int w = 128; w > 0; w >>= 1){ if((int)threadIdx.x < w) part[threadIdx.x] += part[threadIdx.x + w]; __syncthreads(); }
+    if(threadIdx.x == 0) *result = (float)part[0];
+}
+// tensor::operations::unary::Scale (containers/tensor/operations_generic.h:433-445): x * scale, or (1 / x) * scale
+__global__ void __launch_bounds__(256) scale_kernel(float* t, size_t n, float scale, int reciprocal){
+    for(size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        t[i] = reciprocal ? __fmul_rn(__fdiv_rn(1.0f, t[i]), scale) : __fmul_rn(t[i], scale);
+}
+// set_all(tensor, one-element tensor) (containers/tensor/operations_generic.h:741-748)
+__global__ void __launch_bounds__(256) fill_from_kernel(float* dst, size_t n, const float* __restrict__ value){
+    const float v = __ldg(value);
+    for(size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = v;
+}
+// mask_actions / mask_gradient (rl/algorithms/sac/operations_generic.h:180-232): rows whose mask (optionally inverted) is set receive the
+// source row, or zeros when there is no source
+__global__ void __launch_bounds__(256) mask_rows_kernel(const float* __restrict__ source, long long ld_source, float* target, long long ld_target,
+                                                        const uint8_t* __restrict__ mask, int rows, int cols, int invert){
+    long long n = (long long)rows * cols;
+    for(long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x){
+        long long r = i / cols; int c = (int)(i - r * cols);
+        const bool take = (mask[r] != 0) != (invert != 0);
+        if(take) target[r * ld_target + c] = source ? source[r * ld_source + c] : 0.0f;
+    }
+}
+
 }  // namespace b200rl
 using namespace b200rl;
 
@@ -212,6 +255,43 @@ int b200rl_fill(float* dst, size_t n, float value, b200rl_stream_t stream){
     int vec_ok = aligned16(dst);
     fill_kernel<<<grid_for(vec_ok ? (n + 3) / 4 : n, 256), 256, 0, (cudaStream_t)stream>>>(dst, n, value, vec_ok);
     B200RL_LAUNCH_CHECK("fill");
+    return B200RL_OK;
+}
+
+
+int b200rl_mse_gradient_dev_weight(const float* a, int lda, const float* b, int ldb, float* d_a, int ldd, int rows, int cols, const float* loss_weight,
+                                   b200rl_stream_t stream){
+    if(!a || !b || !d_a || !loss_weight || rows < 0 || cols < 1 || lda < cols || ldb < cols || ldd < cols) return B200RL_ERR_INVALID_ARGUMENT;
+    if(rows == 0) return B200RL_OK;
+    mse_gradient_dev_weight_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(a, lda, b, ldb, d_a, ldd, rows, cols, loss_weight);
+    B200RL_LAUNCH_CHECK("mse_gradient_dev_weight");
+    return B200RL_OK;
+}
+int b200rl_mask_count(const uint8_t* mask, size_t n, float* result, b200rl_stream_t stream){
+    if(!result || (n && !mask) || n >= ((size_t)1 << 24)) return B200RL_ERR_INVALID_ARGUMENT;
+    mask_count_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(mask, n, result);
+    B200RL_LAUNCH_CHECK("mask_count");
+    return B200RL_OK;
+}
+int b200rl_scale(float* t, size_t n, float scale, int reciprocal, b200rl_stream_t stream){
+    if(n && !t) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n == 0) return B200RL_OK;
+    scale_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(t, n, scale, reciprocal);
+    B200RL_LAUNCH_CHECK("scale");
+    return B200RL_OK;
+}
+int b200rl_fill_from_device(float* dst, size_t n, const float* value, b200rl_stream_t stream){
+    if(!value || (n && !dst)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n == 0) return B200RL_OK;
+    fill_from_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(dst, n, value);
+    B200RL_LAUNCH_CHECK("fill_from_device");
+    return B200RL_OK;
+}
+int b200rl_mask_rows(const float* source, int ld_source, float* target, int ld_target, const uint8_t* mask, int rows, int cols, int invert, b200rl_stream_t stream){
+    if(!target || !mask || rows < 0 || cols < 1 || ld_target < cols || (source && ld_source < cols)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(rows == 0) return B200RL_OK;
+    mask_rows_kernel<<<grid_for((size_t)rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(source, ld_source, target, ld_target, mask, rows, cols, invert);
+    B200RL_LAUNCH_CHECK("mask_rows");
     return B200RL_OK;
 }
 

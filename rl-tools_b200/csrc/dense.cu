@@ -457,6 +457,13 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
     return B200RL_OK;
 }
 
+// whole-network kernels for small batches (mlp_fused.cu)
+bool mlp_fused_eligible(const b200rl_mlp_shape* sh, int batch);
+size_t mlp_fused_backward_scratch_bytes(const b200rl_mlp_shape* sh, int batch);
+int mlp_fused_forward(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* pre, float* out, float* y, int ldy, int batch, cudaStream_t s);
+int mlp_fused_backward(const b200rl_mlp_shape* sh, const float* params, float* grads, const float* x, int ldx, const float* pre, const float* out, float* d_out,
+                       float* d_input, int batch, void* scratch, size_t scratch_bytes, cudaStream_t s);
+
 static bool valid_shape(const b200rl_mlp_shape* sh){
     if(!sh || sh->n_layers < 1 || sh->n_layers > B200RL_MAX_LAYERS || sh->input_dim < 1) return false;
     for(int l = 0; l < sh->n_layers; l++) if(sh->dims[l] < 1 || !valid_activation(sh->acts[l])) return false;
@@ -570,6 +577,7 @@ int b200rl_mlp_evaluate_ws(const b200rl_mlp_shape* sh, const float* params, cons
     if(!valid_shape(sh) || !params || !x || !y || batch < 0 || ldx < sh->input_dim || ldy < sh->dims[sh->n_layers - 1]) return B200RL_ERR_INVALID_ARGUMENT;
     if(sh->n_layers > 1 && (!tick || (sh->n_layers > 2 && !tock))) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
+    if(mlp_fused_eligible(sh, batch)) return mlp_fused_forward(sh, params, x, ldx, nullptr, nullptr, y, ldy, batch, (cudaStream_t)stream);
     const float* in = x; int ldin = ldx, I = sh->input_dim; const float* p = params;
     for(int l = 0; l < sh->n_layers; l++){
         int O = sh->dims[l]; bool last = l == sh->n_layers - 1;
@@ -590,6 +598,7 @@ int b200rl_mlp_forward_ws(const b200rl_mlp_shape* sh, const float* params, const
                           int batch, void* workspace, size_t workspace_bytes, b200rl_stream_t stream){
     if(!valid_shape(sh) || !params || !x || !pre || !out || batch < 0 || ldx < sh->input_dim) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
+    if(mlp_fused_eligible(sh, batch)) return mlp_fused_forward(sh, params, x, ldx, pre, out, nullptr, 0, batch, (cudaStream_t)stream);
     const float* in = x; int ldin = ldx, I = sh->input_dim; const float* p = params;
     for(int l = 0; l < sh->n_layers; l++){
         int O = sh->dims[l];
@@ -605,7 +614,8 @@ size_t b200rl_mlp_backward_scratch_bytes(const b200rl_mlp_shape* sh, int batch){
     if(!valid_shape(sh) || batch < 1) return 0;
     size_t m = 0; int I = sh->input_dim;
     for(int l = 0; l < sh->n_layers; l++){ const BackwardPlan p = plan_backward(batch, I, sh->dims[l]); const size_t b = p.bytes + p.wt_bytes; if(b > m) m = b; I = sh->dims[l]; }
-    return m;
+    const size_t fused = mlp_fused_backward_scratch_bytes(sh, batch);
+    return fused > m ? fused : m;
 }
 
 int b200rl_mlp_backward(const b200rl_mlp_shape* sh, const float* params, float* grads, const float* x, int ldx, const float* pre,
@@ -616,6 +626,9 @@ int b200rl_mlp_backward(const b200rl_mlp_shape* sh, const float* params, float* 
     int L = sh->n_layers;
     if(L > 1 && (!tick || (L > 2 && !tock))) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
+    // small batches: the whole pass in two launches, when the caller's scratch has room for the gradients of all layers
+    if(mlp_fused_eligible(sh, batch) && scratch && scratch_bytes >= mlp_fused_backward_scratch_bytes(sh, batch))
+        return mlp_fused_backward(sh, params, grads, x, ldx, pre, out, d_out, d_input, batch, scratch, scratch_bytes, (cudaStream_t)stream);
     size_t poff[B200RL_MAX_LAYERS], aoff[B200RL_MAX_LAYERS]; int Is[B200RL_MAX_LAYERS];
     { size_t po = 0, ao = 0; int I = sh->input_dim;
       for(int l = 0; l < L; l++){ poff[l] = po; aoff[l] = ao; Is[l] = I; po += (size_t)sh->dims[l] * I + sh->dims[l]; ao += (size_t)batch * sh->dims[l]; I = sh->dims[l]; } }

@@ -3,11 +3,11 @@
 // environment, the runner state in registers between steps, the actor's weights in shared memory (read as warp broadcasts).
 // This is the CUDA-core kernel of rollout.cu with the Pendulum calls replaced by an ENV parameter; the tensor-core kernel
 // stays specialised to the Pendulum shapes. An environment provides
-//   STATE_DIM, OBS_DIM
-//   reset(state, u0, u1)            the initial state from the two draws of the reset table
+//   STATE_DIM, OBS_DIM, RESET_DIM
+//   reset(state, draws)             the initial state from the RESET_DIM values of the reset table
 //   observe(state, obs)             the observation the actor sees
 //   transition(state, action, next) returns the reward of the transition (the reference's step + reward)
-// Environments that never terminate only (truncation by the step limit).
+//   TERMINATES, terminated(next)    whether the transition ended the episode (evaluated on the next state, as the runner does)
 #include "common.cuh"
 #include "pendulum.cuh"
 #include "acrobot.cuh"
@@ -16,8 +16,10 @@
 namespace b200rl {
 
 struct PendulumEnv {          // rl/environments/pendulum/operations_generic.h
-    static constexpr int STATE_DIM = 2, OBS_DIM = 3;
-    __device__ static void reset(float (&s)[2], float u0, float u1){ s[0] = u0; s[1] = u1; }
+    static constexpr int STATE_DIM = 2, OBS_DIM = 3, RESET_DIM = 2;
+    static constexpr bool TERMINATES = false;
+    __device__ static bool terminated(const float (&)[2]){ return false; }
+    __device__ static void reset(float (&s)[2], const float (&u)[2]){ s[0] = u[0]; s[1] = u[1]; }
     __device__ static void observe(const float (&s)[2], float (&o)[3]){ sincosf(s[0], &o[1], &o[0]); o[2] = s[1]; }
     __device__ static float transition(const float (&s)[2], float action, float (&next)[2]){
         pendulum::step(s[0], s[1], sinf(s[0]), action, next[0], next[1]);
@@ -25,8 +27,10 @@ struct PendulumEnv {          // rl/environments/pendulum/operations_generic.h
     }
 };
 struct AcrobotSwingupEnv {    // rl/environments/acrobot/operations_generic.h
-    static constexpr int STATE_DIM = 4, OBS_DIM = 6;
-    __device__ static void reset(float (&s)[4], float u0, float u1){ s[0] = u0; s[1] = u1; s[2] = 0.0f; s[3] = 0.0f; }       // :46-53
+    static constexpr int STATE_DIM = 4, OBS_DIM = 6, RESET_DIM = 2;
+    static constexpr bool TERMINATES = false;
+    __device__ static bool terminated(const float (&)[4]){ return false; }
+    __device__ static void reset(float (&s)[4], const float (&u)[2]){ s[0] = u[0]; s[1] = u[1]; s[2] = 0.0f; s[3] = 0.0f; }       // :46-53
     __device__ static void observe(const float (&s)[4], float (&o)[6]){                                                   // :180-191
         sincosf(s[0], &o[1], &o[0]); sincosf(s[1], &o[3], &o[2]); o[4] = s[2]; o[5] = s[3];
     }
@@ -36,11 +40,20 @@ struct AcrobotSwingupEnv {    // rl/environments/acrobot/operations_generic.h
     }
 };
 
+struct AcrobotEnv: AcrobotSwingupEnv {    // rl::environments::Acrobot: the variant that terminates
+    static constexpr int RESET_DIM = 4;
+    static constexpr bool TERMINATES = true;
+    __device__ static bool terminated(const float (&next)[4]){ return acrobot::terminated(next); }                         // :193-195
+    __device__ static void reset(float (&s)[4], const float (&u)[4]){ s[0] = u[0]; s[1] = u[1]; s[2] = u[2]; s[3] = u[3]; }    // :38-44
+    __device__ static float transition(const float (&s)[4], float action, float (&next)[4]){ acrobot::step(s, action, next); return -1.0f; }   // reward :154-156
+};
+
 struct EnvRolloutArgs {
     const float* params;        // actor arena: W1[H,OBS] b1[H] W2[H,H] b2[H] W3[1,H] b3[1]
     float* states;              // [n_envs, STATE_DIM]
     int32_t* episode_step; uint8_t* truncated; float* episode_return;
-    const float* reset_states;  // [n_reset_rounds, n_envs, 2]
+    const float* reset_states;  // [n_reset_rounds, n_envs, RESET_DIM]
+    uint8_t* terminated;        // [n_steps * n_envs] or NULL
     int n_reset_rounds, n_envs, n_steps, step_limit;
     float* obs; float* act; float* rew;         // [n_steps * n_envs, OBS_DIM | 1 | 1], row = step * n_envs + env
     int* error_flag;
@@ -72,9 +85,11 @@ __global__ void __launch_bounds__(128, 4) rollout_env_kernel(EnvRolloutArgs a){
     for(int t = 0; t < a.n_steps; t++){
         if(trunc){                                   // prologue: rl/components/off_policy_runner/operations_generic_per_env.h:8-61
             if(a.reset_states != nullptr && resets < a.n_reset_rounds){
-                const float* rsp = a.reset_states + ((size_t)resets * a.n_envs + e) * 2;      // scalar loads: the table may be a view at any 4-byte offset
-                const float2 rs = make_float2(__ldg(rsp), __ldg(rsp + 1));
-                ENV::reset(state, rs.x, rs.y);
+                const float* rsp = a.reset_states + ((size_t)resets * a.n_envs + e) * ENV::RESET_DIM;      // scalar loads: the table may be a view at any 4-byte offset
+                float draws[ENV::RESET_DIM];
+#pragma unroll
+                for(int k = 0; k < ENV::RESET_DIM; k++) draws[k] = __ldg(rsp + k);
+                ENV::reset(state, draws);
             }
             else if(a.error_flag) *a.error_flag = 1;
             resets++; es = 0; er = 0.0f;
@@ -109,8 +124,10 @@ __global__ void __launch_bounds__(128, 4) rollout_env_kernel(EnvRolloutArgs a){
         float next[S];
         const float r = ENV::transition(state, action, next);        // epilogue: operations_generic_per_env.h:62-108
         es += 1; er = __fadd_rn(er, r);
-        trunc = (es == a.step_limit);
+        const bool term = ENV::TERMINATES && ENV::terminated(next);
+        trunc = term || (es == a.step_limit);                        // operations_generic_per_env.h:93-97
         a.act[row] = action; a.rew[row] = r;
+        if(a.terminated) a.terminated[row] = term ? 1 : 0;
 #pragma unroll
         for(int k = 0; k < S; k++) state[k] = next[k];
     }
@@ -131,12 +148,19 @@ static int launch_env(const EnvRolloutArgs& a, cudaStream_t s){
 }  // namespace b200rl
 using namespace b200rl;
 
-extern "C" int b200rl_env_observation_dim(int env){ return env == B200RL_ENV_PENDULUM ? 3 : env == B200RL_ENV_ACROBOT_SWINGUP ? 6 : 0; }
-extern "C" int b200rl_env_state_dim(int env){ return env == B200RL_ENV_PENDULUM ? 2 : env == B200RL_ENV_ACROBOT_SWINGUP ? 4 : 0; }
+extern "C" int b200rl_env_observation_dim(int env){ return env == B200RL_ENV_PENDULUM ? 3 : (env == B200RL_ENV_ACROBOT_SWINGUP || env == B200RL_ENV_ACROBOT) ? 6 : 0; }
+extern "C" int b200rl_env_state_dim(int env){ return env == B200RL_ENV_PENDULUM ? 2 : (env == B200RL_ENV_ACROBOT_SWINGUP || env == B200RL_ENV_ACROBOT) ? 4 : 0; }
+extern "C" int b200rl_env_reset_dim(int env){ return env == B200RL_ENV_ACROBOT ? 4 : (env == B200RL_ENV_PENDULUM || env == B200RL_ENV_ACROBOT_SWINGUP) ? 2 : 0; }
 
 extern "C" int b200rl_env_rollout(int env, const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step, uint8_t* truncated,
                                   float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps, int step_limit, float* obs,
                                   float* act, float* rew, int* error_flag, b200rl_stream_t stream){
+    return b200rl_env_rollout_flags(env, actor, actor_params, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds, n_envs, n_steps, step_limit,
+                                    obs, act, rew, nullptr, error_flag, stream);
+}
+extern "C" int b200rl_env_rollout_flags(int env, const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step, uint8_t* truncated,
+                                        float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps, int step_limit, float* obs,
+                                        float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream){
     const int O = b200rl_env_observation_dim(env);
     if(O == 0 || !actor) return B200RL_ERR_INVALID_ARGUMENT;
     if(actor->n_layers != 3 || actor->input_dim != O || actor->dims[0] != 64 || actor->dims[1] != 64 || actor->dims[2] != 1) return B200RL_ERR_UNSUPPORTED;
@@ -148,7 +172,9 @@ extern "C" int b200rl_env_rollout(int env, const b200rl_mlp_shape* actor, const 
     EnvRolloutArgs a{};
     a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
     a.reset_states = reset_states; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs; a.n_steps = n_steps; a.step_limit = step_limit;
-    a.obs = obs; a.act = act; a.rew = rew; a.error_flag = error_flag;
+    a.obs = obs; a.act = act; a.rew = rew; a.terminated = terminated; a.error_flag = error_flag;
     for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
-    return env == B200RL_ENV_PENDULUM ? launch_env<PendulumEnv>(a, (cudaStream_t)stream) : launch_env<AcrobotSwingupEnv>(a, (cudaStream_t)stream);
+    if(env == B200RL_ENV_PENDULUM) return launch_env<PendulumEnv>(a, (cudaStream_t)stream);
+    if(env == B200RL_ENV_ACROBOT) return launch_env<AcrobotEnv>(a, (cudaStream_t)stream);
+    return launch_env<AcrobotSwingupEnv>(a, (cudaStream_t)stream);
 }

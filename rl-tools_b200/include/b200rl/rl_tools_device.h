@@ -10,6 +10,7 @@
 // and continues); `check_status(device)` returns it.
 #pragma once
 #include <b200rl.h>
+#include <rl_tools/containers/matrix/matrix.h>
 #include <rl_tools/containers/tensor/tensor.h>
 #include <rl_tools/nn/optimizers/adam/adam.h>
 #include <rl_tools/nn/layers/dense/layer.h>
@@ -53,6 +54,28 @@ namespace rl_tools{
     namespace b200{
         template <typename DEVICE>
         inline void note(DEVICE& device, int rc){ if(rc != B200RL_OK && device.status == B200RL_OK) device.status = rc; }
+        // row pitch of a matrix as the C ABI wants it (>= the row length): the reference's matrix view of a one-dimensional tensor is a single
+        // row whose nominal pitch is 1 (containers/tensor/operations_generic.h:1053-1066), where the pitch is never used
+        template<typename SPEC>
+        constexpr typename SPEC::TI ld(const Matrix<SPEC>& m){ return SPEC::ROWS == 1 && row_pitch(m) < SPEC::COLS ? SPEC::COLS : row_pitch(m); }
+        // a tensor whose last dimension is contiguous and whose leading dimensions collapse into rows of one pitch
+        template<typename SPEC, typename TI, TI I>
+        constexpr bool collapsible_from(){
+            constexpr TI N = length(typename SPEC::SHAPE{});
+            if constexpr(I + 2 >= N) return true;
+            else return get<I>(typename SPEC::STRIDE{}) == get<I + 1>(typename SPEC::STRIDE{}) * get<I + 1>(typename SPEC::SHAPE{}) && collapsible_from<SPEC, TI, I + 1>();
+        }
+        template<typename SPEC>
+        struct Rows{
+            using TI = typename SPEC::TI;
+            static constexpr TI N = length(typename SPEC::SHAPE{});
+            static_assert(N >= 1);
+            static_assert(get<N - 1>(typename SPEC::STRIDE{}) == 1, "the last dimension must be contiguous");
+            static_assert(collapsible_from<SPEC, TI, 0>(), "the leading dimensions must collapse into rows of one pitch");
+            static constexpr TI COLS = get<N - 1>(typename SPEC::SHAPE{});
+            static constexpr TI ROWS = get<0>(tensor::CumulativeProduct<typename SPEC::SHAPE>{}) / COLS;      // the SHAPE's product: a view's SIZE may be its parent's
+            static constexpr TI PITCH = N >= 2 ? get<(N >= 2 ? N - 2 : 0)>(typename SPEC::STRIDE{}) : COLS;
+        };
     }
     template <typename SPEC>
     void init(devices::B200<SPEC>& device){ device.status = B200RL_OK; }
@@ -109,6 +132,25 @@ namespace rl_tools{
                                                   parameter.gradient_second_order_moment._data, decltype(parameter.parameters)::SPEC::SIZE,
                                                   reinterpret_cast<const float*>(optimizer.parameters._data), optimizer.first_order_moment_bias_correction._data,
                                                   optimizer.second_order_moment_bias_correction._data, device.stream));
+    }
+}
+RL_TOOLS_NAMESPACE_WRAPPER_END
+
+// The target-network update is declared here as well, ahead of everything: the reference calls it by its qualified name
+// (rl/algorithms/sac/operations_generic.h:486-496), which considers only the overloads declared before that call.
+RL_TOOLS_NAMESPACE_WRAPPER_START
+namespace rl_tools{
+    // ---- Polyak (target-network) update: utils/polyak/operations_cuda.h:31-52 ---------------------------------------
+    namespace utils::polyak{
+        template<typename DEV_SPEC, typename SOURCE_SPEC, typename TARGET_SPEC, bool SQUARE = false>
+        void update(devices::B200<DEV_SPEC>& device, const Matrix<SOURCE_SPEC>& source, Matrix<TARGET_SPEC>& target, const typename SOURCE_SPEC::T polyak){
+            static_assert(containers::check_structure<SOURCE_SPEC, TARGET_SPEC> && utils::typing::is_same_v<typename SOURCE_SPEC::T, float>);
+            rl_tools::b200::note(device, b200rl_polyak_update(source._data, rl_tools::b200::ld(source), target._data, rl_tools::b200::ld(target), SOURCE_SPEC::ROWS, SOURCE_SPEC::COLS, polyak, SQUARE ? 1 : 0, device.stream));
+        }
+        template<typename DEV_SPEC, typename SOURCE_SPEC, typename TARGET_SPEC>
+        void update_squared(devices::B200<DEV_SPEC>& device, const Matrix<SOURCE_SPEC>& source, Matrix<TARGET_SPEC>& target, const typename SOURCE_SPEC::T polyak){
+            update<DEV_SPEC, SOURCE_SPEC, TARGET_SPEC, true>(device, source, target, polyak);
+        }
     }
 }
 RL_TOOLS_NAMESPACE_WRAPPER_END

@@ -121,9 +121,9 @@ namespace rl_tools{
             return p.parameters._data == params && p.gradient._data == grads && p.gradient_first_order_moment._data == m && p.gradient_second_order_moment._data == v;
         }
         template <typename S> bool activations_at(const nn::layers::dense::LayerForward<S>&, const float*, const float*){ return true; }
-        template <typename S> bool activations_at(const nn::layers::dense::LayerBackward<S>& l, const float* pre, const float*){ return l.pre_activations._data == pre && row_pitch(l.pre_activations) == S::OUTPUT_DIM; }
+        template <typename S> bool activations_at(const nn::layers::dense::LayerBackward<S>& l, const float* pre, const float*){ return l.pre_activations._data == pre && rl_tools::b200::ld(l.pre_activations) == S::OUTPUT_DIM; }
         template <typename S> bool activations_at(const nn::layers::dense::LayerGradient<S>& l, const float* pre, const float* out){
-            return l.pre_activations._data == pre && l.output._data == out && row_pitch(l.pre_activations) == S::OUTPUT_DIM && row_pitch(l.output) == S::OUTPUT_DIM;
+            return l.pre_activations._data == pre && l.output._data == out && rl_tools::b200::ld(l.pre_activations) == S::OUTPUT_DIM && rl_tools::b200::ld(l.output) == S::OUTPUT_DIM;
         }
         template <typename SPEC>
         Arena<SPEC> arena_of(const nn_models::mlp::NeuralNetworkForward<SPEC>& network){
@@ -181,7 +181,7 @@ namespace rl_tools{
             const b200rl_mlp_shape shape = b200::mlp::Layout<MODEL_SPEC>::shape();
             // the workspace was sized for the network's own batch; a larger evaluation batch goes without it
             const bool ws = INPUT_SPEC::ROWS <= MODEL_SPEC::INTERNAL_BATCH_SIZE;
-            b200::note(device, b200rl_mlp_evaluate_ws(&shape, arena.params(), input._data, row_pitch(input), output._data, row_pitch(output), buffers.tick._data, buffers.tock._data,
+            b200::note(device, b200rl_mlp_evaluate_ws(&shape, arena.params(), input._data, rl_tools::b200::ld(input), output._data, rl_tools::b200::ld(output), buffers.tick._data, buffers.tock._data,
                                                       INPUT_SPEC::ROWS, ws ? arena.workspace() : nullptr, ws ? b200::mlp::Layout<MODEL_SPEC>::workspace_bytes() : 0, device.stream));
             return;
         }
@@ -205,7 +205,7 @@ namespace rl_tools{
         const auto arena = b200::mlp::arena_of(network);
         if(arena){
             const b200rl_mlp_shape shape = b200::mlp::Layout<MODEL_SPEC>::shape();
-            b200::note(device, b200rl_mlp_forward_ws(&shape, arena.params(), input._data, row_pitch(input), arena.pre(), arena.out(), INPUT_SPEC::ROWS,
+            b200::note(device, b200rl_mlp_forward_ws(&shape, arena.params(), input._data, rl_tools::b200::ld(input), arena.pre(), arena.out(), INPUT_SPEC::ROWS,
                                                      arena.workspace(), b200::mlp::Layout<MODEL_SPEC>::workspace_bytes(), device.stream));
             return;
         }
@@ -228,11 +228,11 @@ namespace rl_tools{
             using L = Layout<MODEL_SPEC>;
             const auto arena = arena_of(network);
             // the C entry points take a dense d_output and a dense d_input
-            if(!arena || row_pitch(d_output) != D_OUTPUT_SPEC::COLS || (d_input && d_input_pitch != MODEL_SPEC::INPUT_DIM)) return false;
+            if(!arena || rl_tools::b200::ld(d_output) != D_OUTPUT_SPEC::COLS || (d_input && d_input_pitch != MODEL_SPEC::INPUT_DIM)) return false;
             const b200rl_mlp_shape shape = L::shape();
             // backward_input needs no layer inputs: the first layer's input gradient only reads its weights; any valid pointer serves as x
             const float* x = input ? input->_data : arena.params();
-            const int ldx = input ? (int)row_pitch(*input) : (int)MODEL_SPEC::INPUT_DIM;
+            const int ldx = input ? (int)rl_tools::b200::ld(*input) : (int)MODEL_SPEC::INPUT_DIM;
             // stored layer outputs exist only on networks that can take parameter gradients; the input gradient alone does not read them
             const float* out = L::HAS_OUT ? arena.out() : arena.pre();
             if(want_grads && !L::HAS_OUT) return false;
@@ -262,7 +262,7 @@ namespace rl_tools{
     void backward_full(devices::B200<DEV_SPEC>& device, nn_models::mlp::NeuralNetworkGradient<MODEL_SPEC>& network, const Matrix<INPUT_SPEC>& input, Matrix<D_OUTPUT_SPEC>& d_output,
                        Matrix<D_INPUT_SPEC>& d_input, nn_models::mlp::NeuralNetworkBuffers<BUFFER_MODEL_SPEC>& buffer, const Mode<MODE>& mode = Mode<mode::Default<>>{}){
         static_assert(BUFFER_MODEL_SPEC::INTERNAL_BATCH_SIZE == D_OUTPUT_SPEC::ROWS && BUFFER_MODEL_SPEC::DIM >= MODEL_SPEC::HIDDEN_DIM && D_OUTPUT_SPEC::ROWS == MODEL_SPEC::INTERNAL_BATCH_SIZE);
-        if(b200::mlp::backward_arena(device, network, &input, d_output, d_input._data, row_pitch(d_input), true, buffer)) return;
+        if(b200::mlp::backward_arena(device, network, &input, d_output, d_input._data, rl_tools::b200::ld(d_input), true, buffer)) return;
         constexpr auto H = MODEL_SPEC::NUM_HIDDEN_LAYERS;                   // nn_models/mlp/operations_generic.h:152-179
         auto previous = H > 0 ? network.hidden_layers[H > 0 ? H - 1 : 0].output : network.input_layer.output;
         backward_full(device, network.output_layer, previous, d_output, buffer.tick, buffer.layer_buffer, mode);
@@ -278,7 +278,7 @@ namespace rl_tools{
     void backward_input(devices::B200<DEV_SPEC>& device, nn_models::mlp::NeuralNetworkBackward<MODEL_SPEC>& network, Matrix<D_OUTPUT_SPEC>& d_output, Matrix<D_INPUT_SPEC>& d_input,
                         nn_models::mlp::NeuralNetworkBuffers<BUFFER_MODEL_SPEC>& buffer, const Mode<MODE>& mode = Mode<mode::Default<>>{}){
         static_assert(BUFFER_MODEL_SPEC::INTERNAL_BATCH_SIZE == D_OUTPUT_SPEC::ROWS && BUFFER_MODEL_SPEC::DIM >= MODEL_SPEC::HIDDEN_DIM && D_OUTPUT_SPEC::ROWS == MODEL_SPEC::INTERNAL_BATCH_SIZE);
-        if(b200::mlp::backward_arena(device, network, (const Matrix<D_INPUT_SPEC>*)nullptr, d_output, d_input._data, row_pitch(d_input), false, buffer)) return;
+        if(b200::mlp::backward_arena(device, network, (const Matrix<D_INPUT_SPEC>*)nullptr, d_output, d_input._data, rl_tools::b200::ld(d_input), false, buffer)) return;
         constexpr auto H = MODEL_SPEC::NUM_HIDDEN_LAYERS;                   // nn_models/mlp/operations_generic.h:130-150
         backward_input(device, network.output_layer, d_output, buffer.tick, buffer.layer_buffer, mode);
         for(typename MODEL_SPEC::TI l1 = H; l1 > 0; l1--){

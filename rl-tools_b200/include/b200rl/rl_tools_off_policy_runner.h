@@ -35,7 +35,7 @@ namespace rl_tools{
             L.off_full = reinterpret_cast<const char*>(&probe->full) - base;
             L.off_current_episode_start = reinterpret_cast<const char*>(&probe->current_episode_start) - base;
             L.capacity = (int)SPEC::PARAMETERS::REPLAY_BUFFER_CAPACITY;
-            L.ld_data = (int)row_pitch(probe->data);
+            L.ld_data = (int)rl_tools::b200::ld(probe->data);
             L.index_bytes = (int)sizeof(typename SPEC::TI);
             return L;
         }

@@ -30,8 +30,8 @@ namespace rl_tools{
             std::vector<unsigned char> host(COUNT * sizeof(ELEMENT));          // raw bytes: std::vector<bool> has no data()
             ELEMENT* typed = reinterpret_cast<ELEMENT*>(host.data());
             for(size_t i = 0; i < COUNT; i++) typed[i] = (ELEMENT)value;
-            if(row_pitch(m) == SPEC::COLS) note(device, b200rl_memcpy(m._data, typed, COUNT * sizeof(ELEMENT), 0, device.stream));
-            else note(device, b200rl_memcpy_2d(m._data, row_pitch(m) * sizeof(ELEMENT), typed, SPEC::COLS * sizeof(ELEMENT),
+            if(rl_tools::b200::ld(m) == SPEC::COLS) note(device, b200rl_memcpy(m._data, typed, COUNT * sizeof(ELEMENT), 0, device.stream));
+            else note(device, b200rl_memcpy_2d(m._data, rl_tools::b200::ld(m) * sizeof(ELEMENT), typed, SPEC::COLS * sizeof(ELEMENT),
                                                SPEC::COLS * sizeof(ELEMENT), SPEC::ROWS, 0, device.stream));
         }
     }
@@ -114,7 +114,7 @@ namespace rl_tools{
             b200::note(device, b200rl_pendulum_collect_layers(&shape, layers, mlp.log_std.parameters._data, reinterpret_cast<float*>(runner.states._data),
                                                               reinterpret_cast<int32_t*>(runner.episode_step._data), reinterpret_cast<uint8_t*>(runner.truncated._data),
                                                               runner.episode_return._data, static_cast<const float*>(d_reset), ROUNDS, static_cast<const float*>(d_noise),
-                                                              N, STEPS, STEP_LIMIT, dataset.data._data, row_pitch(dataset.data), static_cast<int*>(d_flag), device.stream));
+                                                              N, STEPS, STEP_LIMIT, dataset.data._data, rl_tools::b200::ld(dataset.data), static_cast<int*>(d_flag), device.stream));
             b200::note(device, b200rl_memcpy(&flag, d_flag, sizeof(int), 1, device.stream));
             if(flag != 0) b200::note(device, B200RL_ERR_DEVICE_FLAG);
         }

@@ -42,16 +42,21 @@ namespace rl_tools{
             static_assert(utils::typing::is_same_v<typename SOURCE_SPEC::T, typename TARGET_SPEC::T>, "copy converts no types");
             static_assert(SOURCE_SPEC::COL_PITCH == 1 && TARGET_SPEC::COL_PITCH == 1, "column pitch must be 1");
             using T = typename SOURCE_SPEC::T;
-            note(device, b200rl_memcpy_2d(target._data, row_pitch(target) * sizeof(T), source._data, row_pitch(source) * sizeof(T),
+            note(device, b200rl_memcpy_2d(target._data, rl_tools::b200::ld(target) * sizeof(T), source._data, rl_tools::b200::ld(source) * sizeof(T),
                                           SOURCE_SPEC::COLS * sizeof(T), SOURCE_SPEC::ROWS, kind, device.stream));
         }
         template<typename DEVICE, typename SOURCE_SPEC, typename TARGET_SPEC>
         void copy_tensor(DEVICE& device, const Tensor<SOURCE_SPEC>& source, Tensor<TARGET_SPEC>& target, int kind){
             static_assert(tensor::same_dimensions<SOURCE_SPEC, TARGET_SPEC>());
             static_assert(utils::typing::is_same_v<typename utils::typing::remove_const<typename SOURCE_SPEC::T>::type, typename TARGET_SPEC::T>, "copy converts no types");
-            static_assert(tensor::dense_row_major_layout<SOURCE_SPEC>() && tensor::dense_row_major_layout<TARGET_SPEC>(), "only dense tensors");
             using T = typename TARGET_SPEC::T;
-            note(device, b200rl_memcpy(target._data, source._data, SOURCE_SPEC::SIZE * sizeof(T), kind, device.stream));
+            if constexpr(tensor::dense_row_major_layout<SOURCE_SPEC>() && tensor::dense_row_major_layout<TARGET_SPEC>()){
+                note(device, b200rl_memcpy(target._data, source._data, SOURCE_SPEC::SIZE * sizeof(T), kind, device.stream));
+            }
+            else{                                           // views of a wider table (view_range over the last dimension): a pitched row copy
+                using S = Rows<SOURCE_SPEC>; using D = Rows<TARGET_SPEC>;
+                note(device, b200rl_memcpy_2d(target._data, D::PITCH * sizeof(T), source._data, S::PITCH * sizeof(T), S::COLS * sizeof(T), S::ROWS, kind, device.stream));
+            }
         }
     }
     // containers/matrix/operations_cuda.h:105-195 (host<->device copies synchronise the stream, as there)
@@ -74,11 +79,11 @@ namespace rl_tools{
     void set_all(devices::B200<DEV_SPEC>& device, Matrix<SPEC>& m, VALUE_T value){
         static_assert(utils::typing::is_same_v<typename SPEC::T, float>, "fp32 only");
         static_assert(SPEC::COL_PITCH == 1);
-        if(row_pitch(m) == SPEC::COLS){
+        if(rl_tools::b200::ld(m) == SPEC::COLS){
             b200::note(device, b200rl_fill(m._data, (size_t)SPEC::ROWS * SPEC::COLS, (float)value, device.stream));
         }
         else{
-            for(typename SPEC::TI r = 0; r < SPEC::ROWS; r++) b200::note(device, b200rl_fill(m._data + r * row_pitch(m), SPEC::COLS, (float)value, device.stream));
+            for(typename SPEC::TI r = 0; r < SPEC::ROWS; r++) b200::note(device, b200rl_fill(m._data + r * rl_tools::b200::ld(m), SPEC::COLS, (float)value, device.stream));
         }
     }
     template<typename DEV_SPEC, typename SPEC>
@@ -97,7 +102,7 @@ namespace rl_tools{
         static_assert(utils::typing::is_same_v<T, float> && SPEC::COL_PITCH == 1, "fp32, column pitch 1");
         std::vector<T> host((size_t)SPEC::ROWS * SPEC::COLS);
         for(size_t i = 0; i < host.size(); i++) host[i] = random::normal_distribution::sample(device.random, (T)0, (T)1, rng);
-        b200::note(device, b200rl_memcpy_2d(m._data, row_pitch(m) * sizeof(T), host.data(), SPEC::COLS * sizeof(T), SPEC::COLS * sizeof(T), SPEC::ROWS, 0, device.stream));
+        b200::note(device, b200rl_memcpy_2d(m._data, rl_tools::b200::ld(m) * sizeof(T), host.data(), SPEC::COLS * sizeof(T), SPEC::COLS * sizeof(T), SPEC::ROWS, 0, device.stream));
     }
 
     // ---- dense layer: nn/layers/dense/operations_cuda.h:236-413 ---------------------------------------------------
@@ -114,8 +119,8 @@ namespace rl_tools{
                   nn::layers::dense::Buffer&, RNG&, const Mode<MODE>& = Mode<mode::Default<>>{}){
         static_assert(nn::layers::dense::check_input_output<LAYER_SPEC, INPUT_SPEC, OUTPUT_SPEC>);
         static_assert(INPUT_SPEC::COL_PITCH == 1 && OUTPUT_SPEC::COL_PITCH == 1);
-        b200::note(device, b200rl_dense_forward(layer.weights.parameters._data, layer.biases.parameters._data, input._data, row_pitch(input), nullptr, 0,
-                                                output._data, row_pitch(output), INPUT_SPEC::ROWS, LAYER_SPEC::INPUT_DIM, LAYER_SPEC::OUTPUT_DIM,
+        b200::note(device, b200rl_dense_forward(layer.weights.parameters._data, layer.biases.parameters._data, input._data, rl_tools::b200::ld(input), nullptr, 0,
+                                                output._data, rl_tools::b200::ld(output), INPUT_SPEC::ROWS, LAYER_SPEC::INPUT_DIM, LAYER_SPEC::OUTPUT_DIM,
                                                 b200::activation_id<LAYER_SPEC::ACTIVATION_FUNCTION>(), device.stream));
     }
     template<typename DEV_SPEC, typename LAYER_SPEC, typename INPUT_SPEC, typename OUTPUT_SPEC, typename RNG, typename MODE = mode::Default<>>
@@ -123,8 +128,8 @@ namespace rl_tools{
                  nn::layers::dense::Buffer&, RNG&, const Mode<MODE>& = Mode<mode::Default<>>{}){
         static_assert(nn::layers::dense::check_input_output<LAYER_SPEC, INPUT_SPEC, OUTPUT_SPEC>);
         static_assert(INPUT_SPEC::COL_PITCH == 1 && OUTPUT_SPEC::COL_PITCH == 1);
-        b200::note(device, b200rl_dense_forward(layer.weights.parameters._data, layer.biases.parameters._data, input._data, row_pitch(input),
-                                                layer.pre_activations._data, row_pitch(layer.pre_activations), output._data, row_pitch(output),
+        b200::note(device, b200rl_dense_forward(layer.weights.parameters._data, layer.biases.parameters._data, input._data, rl_tools::b200::ld(input),
+                                                layer.pre_activations._data, rl_tools::b200::ld(layer.pre_activations), output._data, rl_tools::b200::ld(output),
                                                 INPUT_SPEC::ROWS, LAYER_SPEC::INPUT_DIM, LAYER_SPEC::OUTPUT_DIM, b200::activation_id<LAYER_SPEC::ACTIVATION_FUNCTION>(), device.stream));
     }
     namespace b200{
@@ -132,8 +137,8 @@ namespace rl_tools{
         template<typename DEVICE, typename LAYER, typename INPUT_SPEC, typename D_OUTPUT_SPEC>
         void dense_backward(DEVICE& device, LAYER& layer, const float* input, unsigned input_pitch, Matrix<D_OUTPUT_SPEC>& d_output, float* d_W, float* d_b, float* d_input, unsigned d_input_pitch, const Matrix<INPUT_SPEC>*){
             using LAYER_SPEC = typename LAYER::SPEC;
-            note(device, b200rl_dense_backward_static_scratch(layer.weights.parameters._data, input, input_pitch, layer.pre_activations._data, row_pitch(layer.pre_activations),
-                                                              d_output._data, row_pitch(d_output), d_W, d_b, d_input, d_input_pitch, D_OUTPUT_SPEC::ROWS, LAYER_SPEC::INPUT_DIM,
+            note(device, b200rl_dense_backward_static_scratch(layer.weights.parameters._data, input, input_pitch, layer.pre_activations._data, rl_tools::b200::ld(layer.pre_activations),
+                                                              d_output._data, rl_tools::b200::ld(d_output), d_W, d_b, d_input, d_input_pitch, D_OUTPUT_SPEC::ROWS, LAYER_SPEC::INPUT_DIM,
                                                               LAYER_SPEC::OUTPUT_DIM, activation_id<LAYER_SPEC::ACTIVATION_FUNCTION>(), device.stream));
         }
     }
@@ -141,19 +146,19 @@ namespace rl_tools{
     void backward_input(devices::B200<DEV_SPEC>& device, nn::layers::dense::LayerBackward<LAYER_SPEC>& layer, Matrix<D_OUTPUT_SPEC>& d_output, Matrix<D_INPUT_SPEC>& d_input,
                         nn::layers::dense::Buffer&, const Mode<MODE>& = Mode<mode::Default<>>{}){
         static_assert(nn::layers::dense::check_input_output<LAYER_SPEC, D_INPUT_SPEC, D_OUTPUT_SPEC>);
-        b200::dense_backward(device, layer, nullptr, 0, d_output, nullptr, nullptr, d_input._data, row_pitch(d_input), (const Matrix<D_INPUT_SPEC>*)nullptr);
+        b200::dense_backward(device, layer, nullptr, 0, d_output, nullptr, nullptr, d_input._data, rl_tools::b200::ld(d_input), (const Matrix<D_INPUT_SPEC>*)nullptr);
     }
     template<typename DEV_SPEC, typename LAYER_SPEC, typename INPUT_SPEC, typename D_OUTPUT_SPEC, typename MODE = mode::Default<>>
     void backward(devices::B200<DEV_SPEC>& device, nn::layers::dense::LayerGradient<LAYER_SPEC>& layer, const Matrix<INPUT_SPEC>& input, Matrix<D_OUTPUT_SPEC>& d_output,
                   nn::layers::dense::Buffer&, const Mode<MODE>& = Mode<mode::Default<>>{}){
         static_assert(nn::layers::dense::check_input_output<LAYER_SPEC, INPUT_SPEC, D_OUTPUT_SPEC>);
-        b200::dense_backward(device, layer, input._data, row_pitch(input), d_output, layer.weights.gradient._data, layer.biases.gradient._data, nullptr, 0, &input);
+        b200::dense_backward(device, layer, input._data, rl_tools::b200::ld(input), d_output, layer.weights.gradient._data, layer.biases.gradient._data, nullptr, 0, &input);
     }
     template<typename DEV_SPEC, typename LAYER_SPEC, typename INPUT_SPEC, typename D_OUTPUT_SPEC, typename D_INPUT_SPEC, typename MODE = mode::Default<>>
     void backward_full(devices::B200<DEV_SPEC>& device, nn::layers::dense::LayerGradient<LAYER_SPEC>& layer, const Matrix<INPUT_SPEC>& input, Matrix<D_OUTPUT_SPEC>& d_output,
                        Matrix<D_INPUT_SPEC>& d_input, nn::layers::dense::Buffer&, const Mode<MODE>& = Mode<mode::Default<>>{}){
         static_assert(nn::layers::dense::check_input_output<LAYER_SPEC, INPUT_SPEC, D_OUTPUT_SPEC>);
-        b200::dense_backward(device, layer, input._data, row_pitch(input), d_output, layer.weights.gradient._data, layer.biases.gradient._data, d_input._data, row_pitch(d_input), &input);
+        b200::dense_backward(device, layer, input._data, rl_tools::b200::ld(input), d_output, layer.weights.gradient._data, layer.biases.gradient._data, d_input._data, rl_tools::b200::ld(d_input), &input);
     }
 
     // ---- MSE: nn/loss_functions/mse/operations_cuda.h:41-58 -------------------------------------------------------
@@ -161,53 +166,18 @@ namespace rl_tools{
         template<typename DEV_SPEC, typename SPEC_A, typename SPEC_B, typename SPEC_DA>
         void gradient(devices::B200<DEV_SPEC>& device, Matrix<SPEC_A>& a, Matrix<SPEC_B>& b, Matrix<SPEC_DA>& d_a, typename SPEC_A::T loss_weight = 1){
             static_assert(containers::check_structure<SPEC_A, SPEC_B> && containers::check_structure<SPEC_A, SPEC_DA>);
-            rl_tools::b200::note(device, b200rl_mse_gradient(a._data, row_pitch(a), b._data, row_pitch(b), d_a._data, row_pitch(d_a), SPEC_A::ROWS, SPEC_A::COLS, loss_weight, device.stream));
+            rl_tools::b200::note(device, b200rl_mse_gradient(a._data, rl_tools::b200::ld(a), b._data, rl_tools::b200::ld(b), d_a._data, rl_tools::b200::ld(d_a), SPEC_A::ROWS, SPEC_A::COLS, loss_weight, device.stream));
         }
         // nn/loss_functions/mse/operations_generic.h:9-22 (the reference has no CUDA form: its generic loop would read device memory on the host)
         template<typename DEV_SPEC, typename SPEC_A, typename SPEC_B>
         typename SPEC_A::T evaluate(devices::B200<DEV_SPEC>& device, Matrix<SPEC_A>& a, Matrix<SPEC_B>& b, typename SPEC_A::T loss_weight = 1){
             static_assert(containers::check_structure<SPEC_A, SPEC_B>);
             float loss = 0;
-            rl_tools::b200::note(device, b200rl_mse_evaluate(a._data, row_pitch(a), b._data, row_pitch(b), SPEC_A::ROWS, SPEC_A::COLS, loss_weight, &loss, device.stream));
+            rl_tools::b200::note(device, b200rl_mse_evaluate(a._data, rl_tools::b200::ld(a), b._data, rl_tools::b200::ld(b), SPEC_A::ROWS, SPEC_A::COLS, loss_weight, &loss, device.stream));
             return loss;
         }
     }
-
-    // ---- Polyak (target-network) update: utils/polyak/operations_cuda.h:31-52 ---------------------------------------
-    namespace utils::polyak{
-        template<typename DEV_SPEC, typename SOURCE_SPEC, typename TARGET_SPEC, bool SQUARE = false>
-        void update(devices::B200<DEV_SPEC>& device, const Matrix<SOURCE_SPEC>& source, Matrix<TARGET_SPEC>& target, const typename SOURCE_SPEC::T polyak){
-            static_assert(containers::check_structure<SOURCE_SPEC, TARGET_SPEC> && utils::typing::is_same_v<typename SOURCE_SPEC::T, float>);
-            rl_tools::b200::note(device, b200rl_polyak_update(source._data, row_pitch(source), target._data, row_pitch(target), SOURCE_SPEC::ROWS, SOURCE_SPEC::COLS, polyak, SQUARE ? 1 : 0, device.stream));
-        }
-        template<typename DEV_SPEC, typename SOURCE_SPEC, typename TARGET_SPEC>
-        void update_squared(devices::B200<DEV_SPEC>& device, const Matrix<SOURCE_SPEC>& source, Matrix<TARGET_SPEC>& target, const typename SOURCE_SPEC::T polyak){
-            update<DEV_SPEC, SOURCE_SPEC, TARGET_SPEC, true>(device, source, target, polyak);
-        }
-    }
-
-    // ---- Adam: nn/optimizers/adam/operations_cuda.h:39-69, instance/operations_cuda.h:60-70 ------------------------
-    template<typename DEV_SPEC, typename SPEC>
-    void init(devices::B200<DEV_SPEC>& device, nn::optimizers::Adam<SPEC>& optimizer){
-        using PARAMETERS = typename SPEC::DEFAULT_PARAMETERS;
-        static_assert(utils::typing::is_same_v<typename SPEC::T, float>, "fp32 only");
-        static_assert(!PARAMETERS::ENABLE_WEIGHT_DECAY && !PARAMETERS::ENABLE_BIAS_LR_FACTOR && !PARAMETERS::ENABLE_GRADIENT_CLIPPING, "only the default (plain) Adam update is implemented");
-        typename nn::optimizers::Adam<SPEC>::PARAMETERS host{PARAMETERS::ALPHA, PARAMETERS::BETA_1, PARAMETERS::BETA_2, PARAMETERS::EPSILON, PARAMETERS::EPSILON_SQRT,
-                                                             PARAMETERS::WEIGHT_DECAY, PARAMETERS::WEIGHT_DECAY_INPUT, PARAMETERS::WEIGHT_DECAY_OUTPUT, PARAMETERS::BIAS_LR_FACTOR};
-        b200::note(device, b200rl_memcpy(optimizer.parameters._data, &host, sizeof(host), 0, device.stream));
-    }
-    template<typename DEV_SPEC, typename SPEC, typename MODEL>
-    void reset_optimizer_state(devices::B200<DEV_SPEC>& device, nn::optimizers::Adam<SPEC>& optimizer, MODEL& model){
-        typename SPEC::TI one = 1;                        // age starts at 1 (nn/optimizers/adam/operations_generic.h:43-46)
-        b200::note(device, b200rl_memcpy(optimizer.age._data, &one, sizeof(one), 0, device.stream));
-        _reset_optimizer_state(device, model, optimizer);
-    }
-    template<typename DEV_SPEC, typename SPEC, typename MODEL>
-    void step(devices::B200<DEV_SPEC>& device, nn::optimizers::Adam<SPEC>& optimizer, MODEL& model){
-        static_assert(sizeof(typename SPEC::TI) == 4, "the age is a 32-bit counter");
-        b200::note(device, b200rl_adam_advance_dev(reinterpret_cast<const float*>(optimizer.parameters._data), reinterpret_cast<uint32_t*>(optimizer.age._data),
-                                                   optimizer.first_order_moment_bias_correction._data, optimizer.second_order_moment_bias_correction._data, device.stream));
-        update(device, model, optimizer);
-    }
 }
 RL_TOOLS_NAMESPACE_WRAPPER_END
+
+#include <b200rl/rl_tools_adam.h>

@@ -20,7 +20,7 @@ namespace rl_tools{
     void estimate_generalized_advantages(devices::B200<DEV_SPEC>& device, rl::components::on_policy_runner::Dataset<DATASET_SPEC>& dataset, PPO_PARAMETERS){
         using OPR_SPEC = typename DATASET_SPEC::SPEC;
         static_assert(utils::typing::is_same_v<typename OPR_SPEC::TYPE_POLICY::DEFAULT, float>, "fp32 only");
-        const int ld = (int)row_pitch(dataset.data);
+        const int ld = (int)rl_tools::b200::ld(dataset.data);
         b200::note(device, b200rl_gae(dataset.rewards._data, ld, dataset.all_values._data, ld, dataset.terminated._data, ld, dataset.truncated._data, ld,
                                       dataset.advantages._data, ld, dataset.target_values._data, ld, (int)OPR_SPEC::N_ENVIRONMENTS, (int)DATASET_SPEC::STEPS_PER_ENV,
                                       (float)PPO_PARAMETERS::GAMMA, (float)PPO_PARAMETERS::LAMBDA, PPO_PARAMETERS::IGNORE_TERMINATION ? 1 : 0, device.stream));
@@ -41,7 +41,7 @@ namespace rl_tools{
         constexpr TI N_EPOCHS = PARAMETERS::N_EPOCHS, BATCH_SIZE = PARAMETERS::BATCH_SIZE, N_BATCHES = DATASET::STEPS_TOTAL / BATCH_SIZE;
         constexpr TI ACTION_DIM = ENVIRONMENT::ACTION_DIM, OBSERVATION_DIM = ENVIRONMENT::Observation::DIM;
         static_assert(N_BATCHES > 0 && DATASET::DATA_DIM <= 64, "the row permutation takes a 64-bit column mask");
-        const int ld = (int)row_pitch(dataset.data);
+        const int ld = (int)rl_tools::b200::ld(dataset.data);
 
         void *d_perm = nullptr, *d_scratch = nullptr, *d_shuffle_scratch = nullptr;
         const size_t ppo_scratch_bytes = b200rl_ppo_scratch_bytes((int)BATCH_SIZE, (int)ACTION_DIM);
@@ -88,10 +88,10 @@ namespace rl_tools{
                 auto current_batch_actions_tensor_reshaped = reshape_row_major(device, current_batch_actions_tensor, tensor::Shape<TI, 1, BATCH_SIZE, ACTION_DIM>{});
                 forward(device, ppo.actor, batch_observations_tensor_reshaped, current_batch_actions_tensor_reshaped, actor_buffers, rng);
 
-                b200::note(device, b200rl_ppo_policy_gradient(ppo_buffers.current_batch_actions._data, (int)row_pitch(ppo_buffers.current_batch_actions),
+                b200::note(device, b200rl_ppo_policy_gradient(ppo_buffers.current_batch_actions._data, (int)rl_tools::b200::ld(ppo_buffers.current_batch_actions),
                                                               batch_actions._data, ld, last_layer.log_std.parameters._data, batch_action_log_probs._data, ld,
                                                               batch_advantages._data, ld, ppo_buffers.d_action_log_prob_d_action._data,
-                                                              (int)row_pitch(ppo_buffers.d_action_log_prob_d_action), last_layer.log_std.gradient._data,
+                                                              (int)rl_tools::b200::ld(ppo_buffers.d_action_log_prob_d_action), last_layer.log_std.gradient._data,
                                                               (int)BATCH_SIZE, (int)ACTION_DIM, (float)PARAMETERS::EPSILON_CLIP, (float)PARAMETERS::ACTION_ENTROPY_COEFFICIENT,
                                                               (float)PARAMETERS::ADVANTAGE_EPSILON, PARAMETERS::NORMALIZE_ADVANTAGE ? 1 : 0, PARAMETERS::LEARN_ACTION_STD ? 1 : 0,
                                                               d_scratch, ppo_scratch_bytes, device.stream));

@@ -19,7 +19,7 @@ namespace rl_tools{
         static_assert(DATA_SPEC::COLS == SPEC::DIM, "Data dimension must match normalizer dimension");
         static_assert(DATA_SPEC::ROWS > 1 && utils::typing::is_same_v<typename SPEC::TYPE_POLICY::DEFAULT, float>);
         normalizer.age++;
-        b200::note(device, b200rl_running_normalizer_update(data._data, (int)row_pitch(data), (int)DATA_SPEC::ROWS, (int)SPEC::DIM, normalizer.mean._data, normalizer.std._data,
+        b200::note(device, b200rl_running_normalizer_update(data._data, (int)rl_tools::b200::ld(data), (int)DATA_SPEC::ROWS, (int)SPEC::DIM, normalizer.mean._data, normalizer.std._data,
                                                             (unsigned long long)normalizer.age, device.stream));
     }
     // rl/components/running_normalizer/operations_generic.h:20-25 (set_all on 1 x DIM matrices)
@@ -45,8 +45,8 @@ namespace rl_tools{
     void evaluate(devices::B200<DEV_SPEC>& device, const nn::layers::standardize::LayerForward<LAYER_SPEC>& layer, const Matrix<INPUT_SPEC>& input, Matrix<OUTPUT_SPEC>& output,
                   nn::layers::standardize::Buffer&, RNG&, const Mode<MODE>& = Mode<mode::Default<>>{}){
         static_assert(nn::layers::standardize::check_input_output<LAYER_SPEC, INPUT_SPEC, OUTPUT_SPEC>);
-        b200::note(device, b200rl_standardize_forward(input._data, (int)row_pitch(input), layer.mean.parameters._data, layer.precision.parameters._data, output._data,
-                                                      (int)row_pitch(output), (int)INPUT_SPEC::ROWS, (int)LAYER_SPEC::INPUT_DIM, device.stream));
+        b200::note(device, b200rl_standardize_forward(input._data, (int)rl_tools::b200::ld(input), layer.mean.parameters._data, layer.precision.parameters._data, output._data,
+                                                      (int)rl_tools::b200::ld(output), (int)INPUT_SPEC::ROWS, (int)LAYER_SPEC::INPUT_DIM, device.stream));
     }
     template<typename DEV_SPEC, typename LAYER_SPEC, typename INPUT_SPEC, typename OUTPUT_SPEC, typename RNG, typename MODE = mode::Default<>>
     void forward(devices::B200<DEV_SPEC>& device, nn::layers::standardize::LayerBackward<LAYER_SPEC>& layer, const Matrix<INPUT_SPEC>& input, Matrix<OUTPUT_SPEC>& output,

@@ -10,6 +10,7 @@
 #include <rl_tools/nn/operations_generic.h>
 #include <rl_tools/nn/layers/dense/operations_cpu.h>
 #include <rl_tools/nn/loss_functions/mse/operations_generic.h>
+#include <rl_tools/nn/layers/sample_and_squash/operations_generic.h>     // before the model headers that recurse into it
 #include <rl_tools/nn/layers/standardize/operations_generic.h>
 #include <rl_tools/rl/components/running_normalizer/operations_generic.h>
 #include <b200rl/rl_tools_standardize.h>                          // before the model headers that recurse into the layer
@@ -21,6 +22,8 @@
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
 #include <rl_tools/rl/components/off_policy_runner/operations_generic.h>
+#include <b200rl/rl_tools_sac.h>                                  // before the SAC operations: min_value_d_output and the MSE gradient are looked up at their definition
+#include <rl_tools/rl/algorithms/sac/operations_generic.h>
 #include <rl_tools/rl/algorithms/ppo/ppo.h>
 #include <rl_tools/rl/algorithms/ppo/operations_generic.h>
 #include <b200rl/rl_tools_operations.h>
@@ -493,7 +496,128 @@ void boundary_extras(const char* name){
     rlt::free(gpu, x_gpu); rlt::free(gpu, y_gpu); rlt::free(gpu, d_gpu); rlt::free(gpu, d_layers);
 }
 
+// SAC update: the reference's OWN generic train_critic / update_critic_targets / train_actor (rl/algorithms/sac/operations_generic.h) instantiated on
+// devices::B200 next to the CPU device: same initial networks (initialised on the CPU, copied over), same hand-filled SequentialBatch of sequence
+// length 1, same action noise; per update critic 0, critic 1, target update, actor. Compared: every network with gradients and Adam moments,
+// log_alpha, the target critics, the last target values.
+template <TI T_BATCH>
+struct SacParityParameters: rlt::rl::algorithms::sac::DefaultParameters<TYPE_POLICY, TI, 1>{
+    static constexpr TI ACTOR_BATCH_SIZE = T_BATCH;
+    static constexpr TI CRITIC_BATCH_SIZE = T_BATCH;
+};
+template <typename SAC_PARAMETERS>
+struct SacParityHeadParameters{
+    static constexpr T LOG_STD_LOWER_BOUND = SAC_PARAMETERS::LOG_STD_LOWER_BOUND, LOG_STD_UPPER_BOUND = SAC_PARAMETERS::LOG_STD_UPPER_BOUND;
+    static constexpr T LOG_PROBABILITY_EPSILON = SAC_PARAMETERS::LOG_PROBABILITY_EPSILON, ALPHA = SAC_PARAMETERS::ALPHA, TARGET_ENTROPY = SAC_PARAMETERS::TARGET_ENTROPY;
+    static constexpr bool ADAPTIVE_ALPHA = SAC_PARAMETERS::ADAPTIVE_ALPHA, UPDATE_ALPHA_WITH_ACTOR = false;
+};
+template <TI BATCH, TI HIDDEN, int UPDATES>
+void sac_parity(const char* name){
+    using PENDULUM = rlt::rl::environments::Pendulum<rlt::rl::environments::pendulum::Specification<TYPE_POLICY, TI, rlt::rl::environments::pendulum::DefaultParameters<T>>>;
+    using SAC_PARAMETERS = SacParityParameters<BATCH>;
+    using ACTOR_MLP = rlt::nn_models::mlp::BindConfiguration<rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 2, 3, HIDDEN, act::RELU, act::IDENTITY>>;
+    using SAS = rlt::nn::layers::sample_and_squash::BindConfiguration<rlt::nn::layers::sample_and_squash::Configuration<TYPE_POLICY, TI, SacParityHeadParameters<SAC_PARAMETERS>>>;
+    using CAP_GRADIENT = rlt::nn::capability::Gradient<rlt::nn::parameters::Adam>;
+    using ACTOR = rlt::nn_models::sequential::Build<CAP_GRADIENT, rlt::nn_models::sequential::Module<ACTOR_MLP, rlt::nn_models::sequential::Module<SAS>>, rlt::tensor::Shape<TI, 1, BATCH, 3>>;
+    using CRITIC_MLP = rlt::nn_models::mlp::BindConfiguration<rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, HIDDEN, act::RELU, act::IDENTITY>>;
+    using CRITIC = rlt::nn_models::sequential::Build<CAP_GRADIENT, rlt::nn_models::sequential::Module<CRITIC_MLP>, rlt::tensor::Shape<TI, 1, BATCH, 4>>;
+    using CRITIC_TARGET = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<CRITIC_MLP>, rlt::tensor::Shape<TI, 1, BATCH, 4>>;
+    using OPTIMIZER = rlt::nn::optimizers::Adam<rlt::nn::optimizers::adam::Specification<TYPE_POLICY, TI>>;
+    using AC_SPEC = rlt::rl::algorithms::sac::Specification<TYPE_POLICY, TI, PENDULUM, ACTOR, CRITIC, CRITIC_TARGET, rlt::nn::parameters::Adam, OPTIMIZER, OPTIMIZER, OPTIMIZER, SAC_PARAMETERS, false>;
+    using ACTOR_CRITIC = rlt::rl::algorithms::sac::ActorCritic<AC_SPEC>;
+    using EVAL_ACTOR = typename ACTOR::template CHANGE_BATCH_SIZE<TI, 4>;
+    using RUNNER_SPEC = rlt::rl::components::off_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, rlt::utils::Tuple<TI, EVAL_ACTOR>, OffPolicyParityParameters<4, 16, 200>>;
+    using BATCH_TYPE = rlt::rl::components::off_policy_runner::SequentialBatch<rlt::rl::components::off_policy_runner::SequentialBatchSpecification<RUNNER_SPEC, 1, BATCH>>;
+    using CRITIC_TRAINING_BUFFERS = rlt::rl::algorithms::sac::CriticTrainingBuffers<rlt::rl::algorithms::sac::CriticTrainingBuffersSpecification<AC_SPEC, true>>;
+    using ACTOR_TRAINING_BUFFERS = rlt::rl::algorithms::sac::ActorTrainingBuffers<rlt::rl::algorithms::sac::ActorTrainingBuffersSpecification<AC_SPEC, true>>;
+    using NOISE = rlt::Matrix<rlt::matrix::Specification<T, TI, BATCH, 1>>;
+    DEVICE_CPU cpu; DEVICE_GPU gpu;
+    rlt::init(gpu);
+    DEVICE_CPU::SPEC::RANDOM::ENGINE<> rng;
+    rlt::malloc(cpu, rng); rlt::init(cpu, rng, 11);
+    auto ac_cpu = std::make_unique<ACTOR_CRITIC>(); auto ac_gpu = std::make_unique<ACTOR_CRITIC>(); auto ac_back = std::make_unique<ACTOR_CRITIC>();
+    BATCH_TYPE batch_cpu, batch_gpu; CRITIC_TRAINING_BUFFERS ctb_cpu, ctb_gpu, ctb_back; ACTOR_TRAINING_BUFFERS atb_cpu, atb_gpu;
+    typename ACTOR::template Buffer<> ab_cpu, atgt_cpu, ab_gpu, atgt_gpu; typename CRITIC::template Buffer<> cb_cpu, cb_gpu; typename CRITIC_TARGET::template Buffer<> ctgt_cpu, ctgt_gpu;
+    NOISE noise_cpu, noise_gpu;
+    rlt::malloc(cpu, *ac_cpu); rlt::malloc(cpu, *ac_back); rlt::malloc(cpu, batch_cpu); rlt::malloc(cpu, ctb_cpu); rlt::malloc(cpu, ctb_back); rlt::malloc(cpu, atb_cpu);
+    rlt::malloc(cpu, ab_cpu); rlt::malloc(cpu, atgt_cpu); rlt::malloc(cpu, cb_cpu); rlt::malloc(cpu, ctgt_cpu); rlt::malloc(cpu, noise_cpu);
+    rlt::malloc(gpu, *ac_gpu); rlt::malloc(gpu, batch_gpu); rlt::malloc(gpu, ctb_gpu); rlt::malloc(gpu, atb_gpu);
+    rlt::malloc(gpu, ab_gpu); rlt::malloc(gpu, atgt_gpu); rlt::malloc(gpu, cb_gpu); rlt::malloc(gpu, ctgt_gpu); rlt::malloc(gpu, noise_gpu);
+    rlt::init(cpu, *ac_cpu, rng);
+    rlt::init(gpu, *ac_gpu, rng);                              // allocates nothing new; every value is overwritten by the copy below
+    rlt::copy(cpu, gpu, *ac_cpu, *ac_gpu);
+    std::normal_distribution<T> normal(0, 1); std::uniform_real_distribution<T> uniform(0, 1);
+    std::mt19937 fill(3);
+    const char* first_failure = "";
+    auto probe = [&](const char* what){ if(gpu.status != B200RL_OK && !first_failure[0]) first_failure = what; };
+    probe("setup");
+    for(int u = 0; u < UPDATES; u++){
+        for(TI q = 0; q < 2; q++) for(TI b = 0; b < BATCH; b++){
+            T theta = (uniform(fill) * 2 - 1) * (T)3.14159265, theta_dot = (uniform(fill) * 2 - 1) * 8;
+            rlt::set(cpu, batch_cpu.observations_actions_base, std::cos(theta), q, b, 0);
+            rlt::set(cpu, batch_cpu.observations_actions_base, std::sin(theta), q, b, 1);
+            rlt::set(cpu, batch_cpu.observations_actions_base, theta_dot, q, b, 2);
+            rlt::set(cpu, batch_cpu.observations_actions_base, uniform(fill) * 2 - 1, q, b, 3);
+            rlt::set(cpu, batch_cpu.next_reset_base, true, q, b, 0);
+            rlt::set(cpu, batch_cpu.next_final_step_mask_base, q == 1, q, b, 0);
+        }
+        for(TI b = 0; b < BATCH; b++){
+            rlt::set(cpu, batch_cpu.rewards, -uniform(fill) * 16, 0, b, 0);
+            rlt::set(cpu, batch_cpu.terminated, uniform(fill) < (T)0.1, 0, b, 0);
+            rlt::set(cpu, batch_cpu.reset, true, 0, b, 0);
+            rlt::set(cpu, batch_cpu.final_step_mask, true, 0, b, 0);
+        }
+        rlt::copy(cpu, gpu, batch_cpu, batch_gpu);
+        for(int c = 0; c < 2; c++){
+            for(TI b = 0; b < BATCH; b++) rlt::set(noise_cpu, b, 0, normal(fill));
+            rlt::copy(cpu, gpu, noise_cpu, noise_gpu);
+            rlt::train_critic(cpu, *ac_cpu, ac_cpu->critics[c], batch_cpu, ac_cpu->critic_optimizers[c], atgt_cpu, cb_cpu, ctgt_cpu, ctb_cpu, noise_cpu, rng);
+            rlt::train_critic(gpu, *ac_gpu, ac_gpu->critics[c], batch_gpu, ac_gpu->critic_optimizers[c], atgt_gpu, cb_gpu, ctgt_gpu, ctb_gpu, noise_gpu, rng);
+            probe("train_critic");
+        }
+        rlt::update_critic_targets(cpu, *ac_cpu);
+        rlt::update_critic_targets(gpu, *ac_gpu);
+        probe("update_critic_targets");
+        for(TI b = 0; b < BATCH; b++) rlt::set(noise_cpu, b, 0, normal(fill));
+        rlt::copy(cpu, gpu, noise_cpu, noise_gpu);
+        rlt::train_actor(cpu, *ac_cpu, batch_cpu, ac_cpu->actor_optimizer, ab_cpu, cb_cpu, atb_cpu, noise_cpu, rng);
+        rlt::train_actor(gpu, *ac_gpu, batch_gpu, ac_gpu->actor_optimizer, ab_gpu, cb_gpu, atb_gpu, noise_gpu, rng);
+        probe("train_actor");
+    }
+    int status = rlt::check_status(gpu);
+    rlt::copy(gpu, cpu, *ac_gpu, *ac_back);
+    rlt::copy(gpu, cpu, ctb_gpu.target_action_value, ctb_back.target_action_value);
+    constexpr double N_ACTOR = 3.0 * HIDDEN + HIDDEN + (double)HIDDEN * HIDDEN + HIDDEN + HIDDEN * 2.0 + 2, N_CRITIC = 4.0 * HIDDEN + HIDDEN + (double)HIDDEN * HIDDEN + HIDDEN + HIDDEN + 1;
+    // abs_diff of a network sums over parameters, gradients, both Adam moments and the saved activations of every layer
+    T actor_diff = (T)(rlt::abs_diff(cpu, ac_back->actor.content, ac_cpu->actor.content) / (4 * N_ACTOR + 2.0 * BATCH * (2 * HIDDEN + 2)));
+    T critic_diff = 0, target_diff = 0;
+    for(int c = 0; c < 2; c++){
+        critic_diff += (T)(rlt::abs_diff(cpu, ac_back->critics[c].content, ac_cpu->critics[c].content) / (4 * N_CRITIC + 2.0 * BATCH * (2 * HIDDEN + 1)) / 2);
+        target_diff += (T)(rlt::abs_diff(cpu, ac_back->critics_target[c].content, ac_cpu->critics_target[c].content) / N_CRITIC / 2);
+    }
+    auto& la_cpu = rlt::get_last_layer(ac_cpu->actor).log_alpha; auto& la_back = rlt::get_last_layer(ac_back->actor).log_alpha;
+    T log_alpha_diff = std::abs(rlt::get(cpu, la_cpu.parameters, 0) - rlt::get(cpu, la_back.parameters, 0));
+    T log_alpha_grad_diff = std::abs(rlt::get(cpu, la_cpu.gradient, 0) - rlt::get(cpu, la_back.gradient, 0));
+    T target_value_diff = 0, target_value_scale = 0;
+    for(TI b = 0; b < BATCH; b++){
+        T want = rlt::get(cpu, ctb_cpu.target_action_value, 0, b, 0), got = rlt::get(cpu, ctb_back.target_action_value, 0, b, 0);
+        target_value_diff = std::max(target_value_diff, std::abs(want - got)); target_value_scale = std::max(target_value_scale, std::abs(want));
+    }
+    // bounds: means of absolute differences over fp32 tensors whose entries are O(1e-1) (the MLP cases above use 1e-7 for one network); the
+    // target values are single fp32 numbers of magnitude target_value_scale compared at 1e-5 relative + 1e-6
+    bool ok = status == 0 && actor_diff < 2e-7 && critic_diff < 2e-7 && target_diff < 1e-7 && log_alpha_diff < 1e-7 && log_alpha_grad_diff < 1e-5 &&
+              target_value_diff <= 1e-6 + 1e-5 * target_value_scale && !std::isnan(actor_diff) && !std::isnan(critic_diff);
+    std::printf("%-28s batch %4u hidden %3u updates %d  status %d  mean diff actor %.2e critics %.2e targets %.2e  log_alpha %.1e (grad %.1e)  target values %.2e of %.1f  %s%s  %s\n",
+                name, BATCH, HIDDEN, UPDATES, status, actor_diff, critic_diff, target_diff, log_alpha_diff, log_alpha_grad_diff, target_value_diff, target_value_scale, first_failure[0] ? "first failing verb: " : "", first_failure, ok ? "OK" : "FAIL");
+    if(!ok) failures++;
+    rlt::free(cpu, *ac_cpu); rlt::free(cpu, *ac_back); rlt::free(cpu, batch_cpu); rlt::free(cpu, ctb_cpu); rlt::free(cpu, ctb_back); rlt::free(cpu, atb_cpu);
+    rlt::free(cpu, ab_cpu); rlt::free(cpu, atgt_cpu); rlt::free(cpu, cb_cpu); rlt::free(cpu, ctgt_cpu); rlt::free(cpu, noise_cpu);
+    rlt::free(gpu, *ac_gpu); rlt::free(gpu, batch_gpu); rlt::free(gpu, ctb_gpu); rlt::free(gpu, atb_gpu);
+    rlt::free(gpu, ab_gpu); rlt::free(gpu, atgt_gpu); rlt::free(gpu, cb_gpu); rlt::free(gpu, ctgt_gpu); rlt::free(gpu, noise_gpu);
+}
+
 int main(){
+    std::setvbuf(stdout, nullptr, _IOLBF, 0);                          // a crash must not swallow the lines already printed
     // the reference's CUDA sweep (cuda_basics.cu:961-972) plus the BASELINE shapes
     train_steps<   1, 256,  10, 100, 3, act::RELU, act::IDENTITY, 1>("sweep_b1");
     train_steps<   2, 256,  10, 100, 3, act::RELU, act::IDENTITY, 1>("sweep_b2");
@@ -519,6 +643,8 @@ int main(){
     normalizer_parity("observation_normalisation");
     ppo_parity<64, 64, 512, 2>("ppo_train_shuffled");
     ppo_parity<16, 128, 2048, 1>("ppo_train_one_batch");
+    sac_parity<256, 64, 3>("sac_update_verbs");
+    sac_parity<100, 256, 2>("sac_update_verbs_h256");
     std::printf("%s\n", failures ? "ADAPTER PARITY FAILED" : "ADAPTER PARITY OK");
     return failures ? 1 : 0;
 }

@@ -95,7 +95,7 @@ def test_backward_input_only(lib, orc, torch):
     d_out = mg.det_normal(5, B * O, stream=3).reshape(B, O)
     _, _, din_ref, _ = orc.dense_backward(W, x, pre, d_out, "relu", want_grads=False)
     _, _, d_in = lib.dense_backward(dev(torch, W), dev(torch, x), dev(torch, pre), dev(torch, d_out), "relu", want_grads=False)
-    close(d_in, din_ref, rtol=1e-5, atol=2e-6)
+    close(d_in, din_ref)
 
 
 def test_mse_gradient(lib, orc, torch):
@@ -174,7 +174,7 @@ def test_mlp_train_steps_vs_reference_golden(lib, torch, path):
         net.step()
     check("train_m", net.m, tensor_scale=1e-5)
     # Adam normalises the step to ~alpha regardless of gradient scale, so parameter error is bounded by alpha * relative gradient error
-    check("train_params", net.params, rtol=1e-5, atol=2e-6)
+    check("train_params", net.params)
     # full backward with d_input, from the initial parameters again
     net.params.copy_(dev(torch, params))
     net.zero_gradient()
@@ -199,8 +199,8 @@ def test_sharded_train_step_matches_oracle_full_batch(lib, orc, torch):
     parallel.sharded_train_step(lib, net, dev(torch, x), dev(torch, y), total)
     p_ref, g_ref, m_ref, v_ref, _, _ = orc.mlp_train_steps(shape, params, x, y, 1)
     scale = float(np.abs(g_ref).max())
-    close(net.grads, g_ref, rtol=1e-5, atol=1e-6 + 1e-5 * scale)
-    close(net.params, p_ref, rtol=1e-5, atol=2e-6)
+    close(net.grads, g_ref)
+    close(net.params, p_ref)
 
 
 def test_mlp_backward_without_parameter_gradients(lib, torch):
@@ -247,3 +247,46 @@ def test_randn_host_engine_and_mse_evaluate(lib, orc, torch):
         a, b = mg.det_normal(B + O, B * O, stream=1).reshape(B, O), mg.det_normal(B + O, B * O, stream=2).reshape(B, O)
         got, want = lib.mse_evaluate(dev(torch, a), dev(torch, b), w), orc.mse_evaluate(a, b, w)
         assert abs(got - want) <= max(B * O * 2.0 ** -24, 1e-6) * abs(want), (B, O, got, want)
+
+
+@pytest.mark.gpu
+def test_device_operand_tensor_ops_of_the_sac_update(lib, torch):
+    """The small operations between the network passes of train_critic / train_actor with their operands in device memory, each against the same
+    float32 arithmetic in numpy: bit-exact (one multiply, one divide or a copy per element)."""
+    f = np.float32
+    rng = np.random.default_rng(11)
+    for rows, cols in ((256, 1), (97, 3), (1, 1)):
+        a, b = rng.standard_normal((rows, cols)).astype(f), rng.standard_normal((rows, cols)).astype(f)
+        mask = (rng.random(rows) < 0.4)
+        if rows > 1:
+            mask[0], mask[1] = True, False
+        mask_d = dev(torch, mask.astype(np.uint8))
+        weight = torch.zeros(1, device="cuda")
+        lib.mask_count(mask_d, weight)
+        assert weight.item() == mask.sum()
+        if mask.sum() == 0:
+            continue
+        lib.scale_(weight, f(rows * 0.5), reciprocal=True)                                   # the loss weight of train_critic
+        w_ref = f(1) / f(mask.sum()) * f(rows * 0.5)
+        assert weight.item() == w_ref
+        # gradient with that device-resident weight, into a pitched view
+        table = torch.full((rows, cols + 2), 7.0, device="cuda")
+        lib.mse_gradient_dev_weight(dev(torch, a), dev(torch, b), weight, table[:, 1:1 + cols])
+        constant = f(2) / (f(rows) * f(cols)) * w_ref
+        assert np.array_equal(table[:, 1:1 + cols].cpu().numpy(), (a - b) * constant)
+        assert float((table[:, 0] - 7).abs().sum()) == 0 and float((table[:, -1] - 7).abs().sum()) == 0
+        # set_all from a device scalar, plain scaling
+        buf = torch.empty(rows * cols, device="cuda")
+        lib.fill_from_device(buf, weight)
+        assert np.all(buf.cpu().numpy() == w_ref)
+        lib.scale_(buf, f(-3.0))
+        assert np.all(buf.cpu().numpy() == w_ref * f(-3.0))
+        # masked rows: copy of the source where the (inverted) mask is set, zeros without a source
+        for invert in (False, True):
+            take = mask != invert
+            target = dev(torch, b.copy())
+            lib.mask_rows(target, mask_d, source=dev(torch, a), invert=invert)
+            assert np.array_equal(target.cpu().numpy(), np.where(take[:, None], a, b))
+            target = dev(torch, b.copy())
+            lib.mask_rows(target, mask_d, invert=invert)
+            assert np.array_equal(target.cpu().numpy(), np.where(take[:, None], f(0), b))

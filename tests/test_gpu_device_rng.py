@@ -79,7 +79,7 @@ def test_draws_match_numpy_philox(lib, torch, N, T, limit, seed, first):
     normal, theta, theta_dot = expected_draws(seed, first, T, N)
     std = np.float32(np.exp(np.float64(params[-1])))
     eps = (got[..., ACTION].astype(np.float64) - got[..., MEAN]) / std
-    assert np.abs(eps - normal).max() < 2e-5 * (1 + np.abs(normal).max())
+    assert np.abs(eps - normal).max() < 4e-6 * (1 + np.abs(normal).max())
     # every row flagged as reset starts from the drawn initial state
     reset = got[..., RESET] != 0
     assert reset[0].all() and (limit == 0 or reset.sum() > N)
@@ -142,8 +142,8 @@ def test_same_arithmetic_as_table_driven_collect(lib, torch):
     assert np.array_equal(got[:T, :, 7:10], want[:T, :, 7:10])
     std = np.float32(np.exp(np.float64(params[-1])))
     assert np.array_equal(got[:T, :, ACTION], noise * std + got[:T, :, MEAN])
-    assert np.abs(got[..., :3] - want[..., :3]).max() < 5e-5
-    assert np.abs(got[:T, :, 3:7] - want[:T, :, 3:7]).max() < 2e-3
+    assert np.abs(got[..., :3] - want[..., :3]).max() < 1e-5
+    assert np.abs(got[:T, :, 3:7] - want[:T, :, 3:7]).max() < 4e-4
 
 
 def test_moments(lib, torch):
@@ -190,8 +190,8 @@ def test_rollout_device_rng(lib, torch):
     want = oracle.Oracle().pendulum_rollout(oshape, params[:4481], np.zeros((N, 2), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8),
                                             np.zeros(N, np.float32), table, T, limit)
     first = np.arange(T) % limit < 3                       # tight right after a reset, chaotic divergence later
-    assert np.abs(obs[first] - want["obs"].reshape(T, N, 3)[first]).max() < 2e-4
-    assert np.abs(act.cpu().numpy().reshape(T, N)[first] - want["act"].reshape(T, N)[first]).max() < 2e-4
+    assert np.abs(obs[first] - want["obs"].reshape(T, N, 3)[first]).max() < 4e-5
+    assert np.abs(act.cpu().numpy().reshape(T, N)[first] - want["act"].reshape(T, N)[first]).max() < 4e-5
     assert np.array_equal(runner["episode_step"].cpu().numpy(), want["episode_step"])
     assert np.array_equal(runner["truncated"].cpu().numpy(), want["truncated"])
 
@@ -209,7 +209,7 @@ def test_randn_matches_numpy_philox_and_counter(lib, torch):
     for h in range(2):
         radius = np.sqrt(-2.0 * np.log(u[:, 2 * h]))
         want[:, 2 * h], want[:, 2 * h + 1] = radius * np.cos(2 * np.pi * u[:, 2 * h + 1]), radius * np.sin(2 * np.pi * u[:, 2 * h + 1])
-    assert np.abs(got - want.reshape(-1)[:n]).max() < 2e-5
+    assert np.abs(got - want.reshape(-1)[:n]).max() < 1e-5      # fp32 Box-Muller against float64: a few ulp of sqrt(-2 log u) <= 5.6, amplified where log u is small
     counter_d = torch.tensor([call - 7], dtype=torch.int64, device="cuda")
     via_counter = lib.randn_device_rng(torch.empty(n, device="cuda"), seed, stream_id=stream_id, call_index=7, call_counter=counter_d).cpu().numpy()
     assert np.array_equal(via_counter, got)

@@ -25,7 +25,7 @@ def dev(torch, a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def close(got, want, rtol=1e-5, atol=2e-6, what=""):
+def close(got, want, rtol=1e-5, atol=1e-6, what=""):
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     err = np.abs(got - want)
     assert np.all(err <= atol + rtol * np.abs(want)), f"{what}: max err {err.max():.3e}"
@@ -57,19 +57,19 @@ def test_acrobot_transitions_vs_reference_golden(lib, torch):
     flag = torch.zeros(1, dtype=torch.int32, device="cuda")
     obs, act, rew = lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape, dev(torch, params), st, es, tr, er, None, 1, 500, error_flag=flag)
     assert int(flag.item()) == 0
-    close(obs.cpu().numpy(), fix["obs"], atol=1e-6, what="observation")            # the fixture's observations of the same states
+    close(obs.cpu().numpy(), fix["obs"], what="observation")            # the fixture's observations of the same states
     orc = oracle.Oracle()
     actions = act.cpu().numpy().reshape(-1)
     want_next, want_rew, _, _ = orc.acrobot_step(states, actions)                  # the oracle on the kernel's own actions
     got_next = st.cpu().numpy()
     angle_close(got_next[:, :2], want_next[:, :2], 2e-5, "next angles")
-    close(got_next[:, 2:], want_next[:, 2:], rtol=1e-5, atol=2e-5, what="next velocities")
+    close(got_next[:, 2:], want_next[:, 2:], what="next velocities")
     inside = np.abs(np.abs(want_next[:, :2]) - np.pi).min(axis=1) > 1e-3          # the reward jumps across the seam of angle_normalize
-    close(rew.cpu().numpy().reshape(-1)[inside], want_rew[inside], rtol=1e-5, atol=2e-6, what="reward")
+    close(rew.cpu().numpy().reshape(-1)[inside], want_rew[inside], what="reward")
     assert np.mean(got_next == want_next) > 0.9                                    # mostly bit-identical
     # the actor itself: the oracle's MLP on the fixture's observations
     oshape = oracle.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
-    close(actions, orc.mlp_evaluate(oshape, params, fix["obs"]).reshape(-1), rtol=1e-5, atol=2e-6, what="actions")
+    close(actions, orc.mlp_evaluate(oshape, params, fix["obs"]).reshape(-1), what="actions")
     assert np.array_equal(es.cpu().numpy(), np.ones(n, np.int32)) and not tr.cpu().numpy().any()
 
 
@@ -88,9 +88,9 @@ def test_acrobot_rollout_vs_reference_golden(lib, torch):
     assert np.array_equal(es.cpu().numpy(), fix["rollout_episode_step"]) and np.array_equal(tr.cpu().numpy(), fix["rollout_truncated"])
     got, want = obs.cpu().numpy().reshape(T, N, 6), fix["rollout_obs"].reshape(T, N, 6)
     resets = np.arange(T) % limit == 0
-    close(got[resets], want[resets], atol=1e-6, what="observation of the reset states")
+    close(got[resets], want[resets], what="observation of the reset states")
     first = np.arange(T) % limit < 3
-    close(got[first], want[first], rtol=1e-4, atol=1e-4, what="first steps after a reset")
+    close(got[first], want[first], what="first steps after a reset")
     assert np.abs(got - want).max() < 0.5 and np.abs(rew.cpu().numpy() - fix["rollout_rew"]).max() < 0.1
     # teacher-forced: every step restarted from the oracle's state
     orc = oracle.Oracle()
@@ -105,15 +105,67 @@ def test_acrobot_rollout_vs_reference_golden(lib, torch):
         d = [dev(torch, state[k]) for k in ("states", "episode_step", "truncated", "episode_return")]
         o, a, r = lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape, params_d, d[0], d[1], d[2], d[3], dev(torch, one), 1, limit, error_flag=flag)
         nxt = orc.acrobot_rollout(oshape, mg.acrobot_params(), state["states"], state["episode_step"], state["truncated"], state["episode_return"], one, 1, limit)
-        close(o.cpu().numpy(), nxt["obs"], atol=1e-6, what=f"step {t} observation")
+        close(o.cpu().numpy(), nxt["obs"], what=f"step {t} observation")
         close(a.cpu().numpy(), nxt["act"], what=f"step {t} action")
-        close(r.cpu().numpy(), nxt["rew"], rtol=1e-4, atol=2e-5, what=f"step {t} reward")
+        close(r.cpu().numpy(), nxt["rew"], what=f"step {t} reward")
         angle_close(d[0].cpu().numpy()[:, :2], nxt["states"][:, :2], 5e-5, f"step {t} angles")
-        close(d[0].cpu().numpy()[:, 2:], nxt["states"][:, 2:], rtol=1e-4, atol=1e-4, what=f"step {t} velocities")
+        close(d[0].cpu().numpy()[:, 2:], nxt["states"][:, 2:], what=f"step {t} velocities")
         assert np.array_equal(d[1].cpu().numpy(), nxt["episode_step"]) and np.array_equal(d[2].cpu().numpy(), nxt["truncated"])
-        close(d[3].cpu().numpy(), nxt["episode_return"], rtol=1e-4, atol=1e-4, what=f"step {t} return")
+        close(d[3].cpu().numpy(), nxt["episode_return"], what=f"step {t} return")
         state = {k: nxt[k] for k in state}
     assert int(flag.item()) == 0
+
+
+def test_acrobot_terminating_variant_vs_reference_golden(lib, torch):
+    """rl::environments::Acrobot (reward -1, terminated when the tip is above the bar) through the generic kernel. Free-running from the
+    fixture's reset table: the first steps of the first episodes against the reference's fixture; then teacher-forced step by step against
+    the oracle (which reproduces that fixture bit for bit): observation, action, next state within tolerance, reward exactly -1, and the
+    terminated / truncated flags and counters exact wherever the termination test is not within 1e-4 of its threshold (the flag is a
+    comparison of a sum of cosines with 1: a next state that differs in its last bits may land on the other side only there)."""
+    fix = np.load(os.path.join(GOLDEN, "acrobot_terminating.npz"))
+    N, T, limit = mg.ACROBOT_TERMINATING_ROLLOUT
+    shape = lib.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    params_d = dev(torch, mg.acrobot_params())
+    orc = oracle.Oracle()
+    table = mg.acrobot_terminating_table(orc, T)
+    assert np.array_equal(table[:32], fix["reset_table"])
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st, es, tr, er = runner(torch, np.zeros((N, 4), np.float32), truncated=1)
+    term = torch.full((T * N,), 7, dtype=torch.uint8, device="cuda")
+    obs, act, rew = lib.env_rollout(lib.ENV_ACROBOT, shape, params_d, st, es, tr, er, dev(torch, table), T, limit, error_flag=flag, terminated=term)
+    assert int(flag.item()) == 0
+    got, want = obs.cpu().numpy().reshape(T, N, 6), fix["rollout_obs"].reshape(T, N, 6)
+    close(got[:3], want[:3], what="first steps of the first episodes")
+    assert np.all(rew.cpu().numpy() == -1.0) and set(np.unique(term.cpu().numpy())) <= {0, 1}
+    assert np.array_equal(term.cpu().numpy().reshape(T, N)[:3], fix["rollout_terminated"].reshape(T, N)[:3])
+    assert 0.5 * fix["rollout_terminated"].sum() < term.sum().item() < 2 * fix["rollout_terminated"].sum()      # episodes end at a similar rate
+    # teacher-forced
+    oshape = oracle.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    state = dict(states=np.zeros((N, 4), np.float32), episode_step=np.zeros(N, np.int32), truncated=np.ones(N, np.uint8), episode_return=np.zeros(N, np.float32))
+    used = np.zeros(N, np.int64)
+    n_terminated = 0
+    for t in range(120):
+        one = np.zeros((1, N, 4), np.float32)
+        for e in range(N):
+            if state["truncated"][e]:
+                one[0, e] = table[used[e], e]; used[e] += 1
+        d = [dev(torch, state[k]) for k in ("states", "episode_step", "truncated", "episode_return")]
+        tm = torch.zeros(N, dtype=torch.uint8, device="cuda")
+        o, a, r = lib.env_rollout(lib.ENV_ACROBOT, shape, params_d, d[0], d[1], d[2], d[3], dev(torch, one), 1, limit, error_flag=flag, terminated=tm)
+        nxt = orc.acrobot_terminating_rollout(oshape, mg.acrobot_params(), state["states"], state["episode_step"], state["truncated"], state["episode_return"], one, 1, limit)
+        close(o.cpu().numpy(), nxt["obs"], what=f"step {t} observation")
+        close(a.cpu().numpy(), nxt["act"], what=f"step {t} action")
+        assert np.all(r.cpu().numpy() == -1.0)
+        angle_close(d[0].cpu().numpy()[:, :2], nxt["states"][:, :2], 5e-5, f"step {t} angles")
+        close(d[0].cpu().numpy()[:, 2:], nxt["states"][:, 2:], what=f"step {t} velocities")
+        ns = nxt["states"].astype(np.float64)
+        clear = np.abs(-np.cos(ns[:, 0]) - np.cos(ns[:, 1] + ns[:, 0]) - 1.0) > 1e-4
+        assert np.array_equal(tm.cpu().numpy()[clear], nxt["terminated"][clear])
+        assert np.array_equal(d[2].cpu().numpy()[clear], nxt["truncated"][clear]) and np.array_equal(d[1].cpu().numpy(), nxt["episode_step"])
+        close(d[3].cpu().numpy(), nxt["episode_return"], what=f"step {t} return")
+        n_terminated += int(nxt["terminated"].sum())
+        state = {k: nxt[k] for k in state}
+    assert n_terminated > 20 and int(flag.item()) == 0
 
 
 def test_pendulum_through_the_generic_kernel(lib, torch):
@@ -129,7 +181,7 @@ def test_pendulum_through_the_generic_kernel(lib, torch):
     obs, act, rew = lib.env_rollout(lib.ENV_PENDULUM, shape, dev(torch, params), st, es, tr, er, None, 1, 200)
     orc = oracle.Oracle()
     want = orc.pendulum_rollout(oshape, params, states, np.full(N, 7, np.int32), np.zeros(N, np.uint8), np.zeros(N, np.float32), np.zeros((0, N, 2), np.float32), 1, 200)
-    close(obs.cpu().numpy(), want["obs"], atol=1e-6, what="observation")
+    close(obs.cpu().numpy(), want["obs"], what="observation")
     close(act.cpu().numpy(), want["act"], what="action")
     ns, r, _, _ = orc.pendulum_step(states, act.cpu().numpy())
     close(st.cpu().numpy(), ns, rtol=1e-6, atol=1e-6, what="next state")

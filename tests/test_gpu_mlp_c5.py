@@ -113,9 +113,9 @@ def test_parameters_and_moments_against_the_reference(stepped, fix):
     g_bound = ATOL + RTOL * scale
     # m = (1 - beta_1) g: the gradient's bound scaled by 0.1 (+ one rounding)
     assert np.all(np.abs(stepped["m"][::s].astype(np.float64) - fix["m"]) <= 0.1 * g_bound + 1e-12)
-    # v = (1 - beta_2) g^2: d(g^2) = 2 |g| dg
+    # v = (1 - beta_2) g^2 with 1 - beta_2 = 1e-3: d(g^2) = (2 |g| + dg) dg
     g = np.abs(fix["grads"].astype(np.float64))
     assert np.all(np.abs(stepped["v"][::s].astype(np.float64) - fix["v"]) <= 1e-3 * (2 * g + g_bound) * g_bound + 1e-20)
-    # first step: p -= alpha * g / (|g| + eps') with eps' >= eps = 1e-7, so |dp| <= alpha * dg / (|g| + eps) + one rounding of p
+    # first step (alpha = 1e-3): p -= alpha * g / (|g| + eps') with eps' >= eps = 1e-7, so |dp| <= alpha * dg / (|g| + eps) + one rounding of p
     dp = np.abs(stepped["params"][::s].astype(np.float64) - fix["params"])
     assert np.all(dp <= 1e-3 * g_bound / (g + 1e-7) + 1.2e-7 * np.abs(fix["params"]) + 1e-9)

@@ -68,7 +68,7 @@ def test_ppo_policy_gradient_vs_oracle(lib, orc, torch, B, A, normalize, learn):
                                 normalize_advantage=normalize, learn_action_std=learn)
     # the advantage statistics are sums over the minibatch in a different order: relative 1e-5 of each value's scale
     scale = np.abs(d_ref).max()
-    assert np.all(np.abs(d.cpu().numpy() - d_ref) <= 1e-5 * scale + 1e-5 * np.abs(d_ref) + 1e-9)
+    assert np.all(np.abs(d.cpu().numpy() - d_ref) <= 2e-6 * scale + 1e-5 * np.abs(d_ref) + 1e-9)
     if learn:
         # the reference adds 2 * B small increments to log_std.gradient one after the other in fp32: its own rounding error
         # is up to B half-ulps of the running sum (observed: ~9e-6 at B = 2048), which bounds the comparison
@@ -118,18 +118,18 @@ def test_ppo_minibatch_update_on_ant_shapes(lib, orc, torch):
     critic.backward(od, lib.mse_gradient(val, dev(torch, targets), 0.5))
     critic.step()
     ga_d = actor.grads.cpu().numpy()
-    assert np.all(np.abs(ga_d - ga) <= 1e-6 + 1e-5 * np.abs(ga) + 1e-5 * np.abs(ga).max() + B * 3e-8 * np.abs(ga))
-    assert np.all(np.abs(actor.params.cpu().numpy() - pa_ref) <= 2e-6 + 1e-5 * np.abs(pa_ref))
-    assert np.all(np.abs(critic.params.cpu().numpy() - pc_ref) <= 2e-6 + 1e-5 * np.abs(pc_ref))
+    assert np.all(np.abs(ga_d - ga) <= 1e-6 + 1e-5 * np.abs(ga) + 2e-6 * np.abs(ga).max())
+    assert np.all(np.abs(actor.params.cpu().numpy() - pa_ref) <= 1e-6 + 1e-5 * np.abs(pa_ref))
+    assert np.all(np.abs(critic.params.cpu().numpy() - pc_ref) <= 1e-6 + 1e-5 * np.abs(pc_ref))
 
 
 def assert_params_close(name, got, want, n_updates, alpha=1e-3):
-    """Parameters after n_updates Adam steps: within 2e-6 + 1e-5 |ref| everywhere, except that Adam divides by sqrt(v): where a gradient
+    """Parameters after n_updates Adam steps: within 1e-6 + 1e-5 |ref| everywhere, except that Adam divides by sqrt(v): where a gradient
     is ~0 a last-bit difference of the gradient moves the parameter by a visible fraction of alpha, and a sample whose probability ratio
     sits on the clipping boundary can take the other branch of the clipped surrogate (a discontinuous gradient), so up to 1 % of the
     elements may deviate, by at most 5 % of the distance Adam can move a parameter in n_updates steps (the drift is printed)."""
     err = np.abs(got - want)
-    loose = err > 2e-6 + 1e-5 * np.abs(want)
+    loose = err > 1e-6 + 1e-5 * np.abs(want)
     print(f"{name}: max err {err.max():.3e} after {n_updates} updates, {int(loose.sum())} of {err.size} elements beyond 1e-5")
     assert loose.mean() <= 1e-2 and err.max() <= 0.05 * alpha * n_updates, f"{name}: max err {err.max():.3e}, {int(loose.sum())} elements beyond tolerance"
 
@@ -178,7 +178,7 @@ def test_gae_and_values_in_place_on_the_dataset_matrix(lib, orc, torch):
     layout = ppo.DatasetLayout(3, 1)
     ppo.evaluate_values(critic, d, layout)
     values = d[:, 10].cpu().numpy()
-    assert np.all(np.abs(values - ds[:, 10]) <= 2e-6 + 1e-5 * np.abs(ds[:, 10]))
+    assert np.all(np.abs(values - ds[:, 10]) <= 1e-6 + 1e-5 * np.abs(ds[:, 10]))
     ppo.estimate_generalized_advantages(d, layout, N, steps)
     n = N * steps
     adv, tgt = orc.gae(np.ascontiguousarray(ds[:n, 6]), values, ds[:n, 7].astype(np.uint8), ds[:n, 8].astype(np.uint8), N, steps)

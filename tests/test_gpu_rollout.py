@@ -58,12 +58,12 @@ def test_single_step_teacher_forced(lib, orc, torch, acts):
         obs, act, rew = lib.pendulum_rollout(shape, dparams, d_states, d_es, d_tr, d_er, dev(torch, round_table), 1, error_flag=flag)
         assert int(flag.item()) == 0
         close(obs, ref["obs"])
-        close(act, ref["act"], rtol=1e-5, atol=2e-6)
-        close(rew, ref["rew"], rtol=1e-5, atol=1e-5)
-        close(d_states, ref["states"], rtol=1e-5, atol=2e-6)
+        close(act, ref["act"])
+        close(rew, ref["rew"])
+        close(d_states, ref["states"])
         assert np.array_equal(d_es.cpu().numpy(), ref["episode_step"])
         assert np.array_equal(d_tr.cpu().numpy(), ref["truncated"])
-        close(d_er, ref["episode_return"], rtol=1e-5, atol=1e-4)
+        close(d_er, ref["episode_return"])
         counts += tr.astype(np.int64)
         states, es, tr, er = ref["states"], ref["episode_step"], ref["truncated"], ref["episode_return"]
 
@@ -89,12 +89,12 @@ def test_rollout_vs_reference_golden(lib, torch):
         # reset rows: theta_dot is copied from the table, cos/sin computed from the exact same theta
         assert np.array_equal(obs[t0, :, 2], fix["reset_table"][t0 // 200, :, 1])
         for t in range(t0, t0 + 5):
-            close(obs[t], gobs[t], rtol=1e-5, atol=1e-5)
-            close(act[t], gact[t], rtol=1e-5, atol=1e-5)
+            close(obs[t], gobs[t])
+            close(act[t], gact[t])
     drift = np.abs(obs - gobs).reshape(T, -1).max(1)
     print("max |obs - reference| at t=1,10,50,199:", drift[1], drift[10], drift[50], drift[199])
-    assert drift[:200].max() < 5e-2
-    close(rew[:3], grew[:3], rtol=1e-5, atol=1e-5)
+    assert drift[:200].max() < 1e-2
+    close(rew[:3], grew[:3])
 
 
 def test_error_flag_when_reset_table_is_too_small(lib, torch):
@@ -140,6 +140,7 @@ def test_full_size_properties(lib, torch):
     assert float(((o[..., 0] ** 2 + o[..., 1] ** 2) - 1).abs().max()) < 1e-5
     assert float(o[..., 2].abs().max()) <= 8.0 and float(act.abs().max()) <= 1.0 and float(rew.max()) <= 0.0
     ret = rew.view(T, N).double().sum(0)
+    # the device adds 200 rewards in fp32 at |sum| <= 2000: at most 200 * 2^-24 * 2000 = 2.4e-2 from the exact sum, ~sqrt(200) of an ulp typically
     assert float((ret - d[3].double()).abs().max()) < 1e-2
     M = 512
     ds = [dev(torch, a) for a in (np.zeros((M, 2), np.float32), np.zeros(M, np.int32), np.ones(M, np.uint8), np.zeros(M, np.float32))]
@@ -191,12 +192,12 @@ def test_offpolicy_step_with_replay_buffers_vs_reference_golden(lib, orc, torch,
         rows = before[:, 0]
         got_rows, want_rows = data[np.arange(N), rows], st["replay_data"][np.arange(N), rows]
         assert np.array_equal(got_rows[:, 8:], want_rows[:, 8:])
-        close(got_rows[:, :8], want_rows[:, :8], rtol=1e-5, atol=1e-5)
+        close(got_rows[:, :8], want_rows[:, :8])
         assert np.array_equal(es[np.arange(N), rows], st["episode_start"][np.arange(N), rows])
-        close(nobs, st["buf_next_obs"], atol=2e-6)
-        close(d[0], st["states"], atol=2e-6)
+        close(nobs, st["buf_next_obs"])
+        close(d[0], st["states"])
     data, es, pos, full, ces = unpack()
     w = min(steps, cap)
     assert np.array_equal(data[:, :w, 8:], fix[f"replay_data_{case}"][:, :, 8:])          # terminated / truncated flags incl. the marks set at resets
-    close(data[:, :w, :8], fix[f"replay_data_{case}"][:, :, :8], rtol=1e-5, atol=1e-5)
+    close(data[:, :w, :8], fix[f"replay_data_{case}"][:, :, :8])
     assert np.array_equal(es[:, :w], fix[f"episode_start_{case}"]) and np.array_equal(np.stack([pos, full, ces], 1), fix[f"counters_{case}"])

@@ -47,7 +47,7 @@ def test_sample_and_squash_vs_reference_golden(lib, torch, case):
     d_input, per_sample = lib.sample_and_squash_backward(inp_d, noise_d, pre, output, dev(torch, d_output), log_alpha, log_alpha_gradient=grad)
     close(d_input.cpu().numpy(), fix[f"d_input_{case}"], what="d_input")
     close(per_sample.cpu().numpy(), fix[f"d_log_alpha_per_sample_{case}"], what="d_log_alpha_per_sample")
-    close(grad.item() - 0.25, fix[f"log_alpha_gradient_{case}"], rtol=1e-5, atol=2e-6, what="log_alpha gradient")
+    close(grad.item() - 0.25, fix[f"log_alpha_gradient_{case}"], what="log_alpha gradient")
     # clamped rows: no log_std gradient
     assert d_input.cpu().numpy()[0, A] == 0 and d_input.cpu().numpy()[1 % B, 2 * A - 1] == 0
     # strided views: input inside a wider matrix, output into a column block
@@ -120,18 +120,18 @@ def test_sac_first_update_vs_reference_golden(lib, torch, case):
     agent, batches, noise_c, noise_a = build_agent(lib, torch, case, 1)
     agent.update(batches[0], noise_c[0, 0], noise_c[0, 1], noise_a[0])
     f = lambda k: fix[f"{k}_{case}_u1"]
-    close(agent.target_action_value.cpu().numpy()[:, 0], f("target_values"), rtol=1e-5, atol=2e-6, what="target values")
+    close(agent.target_action_value.cpu().numpy()[:, 0], f("target_values"), what="target values")
     for c in range(2):
         scale_close(agent.critics[c].grads.cpu().numpy(), f(f"critic{c}_grads"), what=f"critic {c} gradient")
         scale_close(agent.critics[c].m.cpu().numpy(), f(f"critic{c}_m"), what=f"critic {c} first moment")
         close(agent.critics_target[c].params.cpu().numpy(), f(f"target{c}"), what=f"target {c}")
     scale_close(agent.actor.grads.cpu().numpy(), f("actor_grads"), what="actor gradient")
-    close(agent.log_alpha_grad.item(), f("log_alpha_grads"), rtol=2e-5, atol=2e-6, what="log_alpha gradient")
+    close(agent.log_alpha_grad.item(), f("log_alpha_grads"), what="log_alpha gradient")
     # first Adam step: |update| = alpha for every element whose gradient is not ~0, sign decided by the gradient
     for name, got, want, grad in (("actor", agent.actor.params, f("actor_params"), f("actor_grads")), ("critic 0", agent.critics[0].params, f("critic0_params"), f("critic0_grads")),
                                   ("critic 1", agent.critics[1].params, f("critic1_params"), f("critic1_grads"))):
         solid = np.abs(grad) > 1e-4 * np.abs(grad).max()
-        close(got.cpu().numpy()[solid], want[solid], rtol=1e-5, atol=2e-6, what=name + " parameters")
+        close(got.cpu().numpy()[solid], want[solid], what=name + " parameters")
     close(agent.log_alpha.item(), f("log_alpha_params"), what="log_alpha")
 
 
@@ -149,8 +149,8 @@ def test_sac_updates_vs_reference_golden(lib, torch, case):
     for c in range(2):
         assert_params_close(f"critic {c}", agent.critics[c].params.cpu().numpy(), f(f"critic{c}_params"), 2 * U)
         assert_params_close(f"target {c}", agent.critics_target[c].params.cpu().numpy(), f(f"target{c}"), 2 * U)
-    assert abs(agent.log_alpha.item() - float(f("log_alpha_params"))) < 1e-5
-    close(agent.target_action_value.cpu().numpy()[:, 0], f("target_values"), rtol=1e-3, atol=1e-3, what="last target values")
+    assert abs(agent.log_alpha.item() - float(f("log_alpha_params"))) < 2e-6
+    close(agent.target_action_value.cpu().numpy()[:, 0], f("target_values"), what="last target values")
 
 
 @pytest.mark.parametrize("case", range(len(oracle.Reference.NORMALIZER_CASES)))

@@ -306,6 +306,21 @@ def test_acrobot_swingup_matches_reference(orc):
         assert np.array_equal(v, fix[f"rollout_{k}"]), k
 
 
+def test_acrobot_terminating_matches_reference(orc):
+    """rl::environments::Acrobot, the variant that terminates: the initial-state draws (double-bounded uniforms: two engine words each) and a
+    free-running 200-step rollout of 64 environments whose episodes end by termination or at the step limit, every array bit for bit --
+    observations, actions, rewards, the terminated flags and the runner's counters."""
+    fix = np.load(os.path.join(GOLDEN, "acrobot_terminating.npz"))
+    N, T, limit = mg.ACROBOT_TERMINATING_ROLLOUT
+    table = mg.acrobot_terminating_table(orc, T)
+    assert np.array_equal(table[:32], fix["reset_table"])
+    shape = oracle.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    out = orc.acrobot_terminating_rollout(shape, mg.acrobot_params(), np.zeros((N, 4), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32), table, T, limit)
+    for k, v in out.items():
+        assert np.array_equal(v, fix[f"rollout_{k}"]), k
+    assert out["terminated"].sum() > 50
+
+
 def test_c5_chunk_65536_forward_rows_match_reference(orc):
     """The fixture of the 65,536-row chunk (the reference's own forward through its scalar loops): rows are independent in the forward pass,
     so the oracle's forward on the sampled rows of the last chunk must reproduce the stored activations bit for bit."""

@@ -196,3 +196,13 @@ def test_acrobot_live(orc, ref_strict):
     for a, b in zip(ref_strict.acrobot_step(states, actions), orc.acrobot_step(states, actions)):
         assert np.array_equal(a, b)
     assert np.array_equal(ref_strict.acrobot_initial_states(9, 300), orc.acrobot_initial_states(9, 300))
+    # the terminating variant: double-bounded initial draws, terminated flags, reward -1, episodes cut by termination
+    assert np.array_equal(ref_strict.acrobot_terminating_initial_states(9, 300), orc.acrobot_terminating_initial_states(9, 300))
+    N, T, limit = 16, 150, 60
+    table = ref_strict.acrobot_terminating_initial_states(4, T * N).reshape(T, N, 4)
+    shape = oracle.MlpShape.make(6, [64, 64, 1], ["relu", "relu", "tanh"])
+    params = (rs.uniform(-1, 1, 6 * 64 + 64 + 64 * 64 + 64 + 64 + 1) * 0.3).astype(np.float32)
+    zero = lambda: (np.zeros((N, 4), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8), np.zeros(N, np.float32))
+    want, got = ref_strict.acrobot_terminating_rollout(params, *zero(), table, T, limit), orc.acrobot_terminating_rollout(shape, params, *zero(), table, T, limit)
+    for k in want:
+        assert np.array_equal(want[k], got[k]), k

@@ -973,6 +973,8 @@ def main():
                     "traffic": traffic, "traffic_source": "ncu capture of this workload, constant", "peak_source": peaks["source"] + " bf16 dense (burst)",
                     # the contraction runs as three passes of fp16 parts (fp32 accuracy), each at the dense 16-bit rate: the attainable ceiling is a third of the peak
                     "frac_of_split_ceiling": achieved_tflops / (peaks["tflops"] / 3.0),
+                    # the same number against the ceiling of the 3xTF32 form this kernel had before (tf32 at half the 16-bit rate, three passes)
+                    "frac_of_3xtf32_ceiling": achieved_tflops / (peaks["tflops"] / 6.0),
                     "hbm_write_gbs": BYTES_PER_ENV_STEP * N_ENVS * N_STEPS / (ms_per_step * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]}
         cpu = None if args.no_cpu_baseline else cpu_reference_rate()
         # the reference's OWN CUDA runner (prologue kernel, per-layer bias / cublasSgemm / activation, epilogue kernel: ~12 launches per step) on

@@ -380,6 +380,15 @@ class Mlp:
         """View of the extra parameters (or their gradient / moments) behind the layers."""
         return getattr(self, arena)[self.n_mlp:]
 
+    def save_code(self, name, batch=1):
+        """The network as C++ source in the reference's export format (what its `save_code` writes for a forward-only MLP and its
+        checkpoint step stores as checkpoint.h): see rl_tools_b200.export. Copies the parameters to the host."""
+        from . import export
+        names = {v: k for k, v in ACT.items()}
+        dims = [self.shape.dims[l] for l in range(self.shape.n_layers)]
+        acts = [names[self.shape.acts[l]] for l in range(self.shape.n_layers)]
+        return export.save_code(self.params[:self.n_mlp].detach().cpu().numpy(), self.shape.input_dim, dims, acts, name, batch)
+
     def d_out_buffer(self):
         """A reusable [batch, O_last] buffer for the loss gradient."""
         import torch

@@ -290,3 +290,22 @@ def test_device_operand_tensor_ops_of_the_sac_update(lib, torch):
             target = dev(torch, b.copy())
             lib.mask_rows(target, mask_d, invert=invert)
             assert np.array_equal(target.cpu().numpy(), np.where(take[:, None], f(0), b))
+
+
+@pytest.mark.gpu
+def test_network_trained_on_the_device_exports_in_the_reference_code_format(lib, torch):
+    """Mlp.save_code: the parameters as they are on the device, in the text the reference's own writer produces for them (the writer itself
+    is held byte for byte against the reference in tests/test_export.py)."""
+    from rl_tools_b200 import export
+    net = lib.Mlp(3, [64, 64, 1], ["relu", "relu", "tanh"], 32)
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    net.params.copy_(torch.randn(net.params.numel(), device="cuda", generator=g) * 0.2)
+    x, y = torch.randn((32, 3), device="cuda", generator=g), torch.randn((32, 1), device="cuda", generator=g)
+    for _ in range(2):
+        net.zero_gradient()
+        net.backward(x, lib.mse_gradient(net.forward(x), y, 1.0))
+        net.step()
+    code = net.save_code("rl_tools::checkpoint::actor")
+    params = net.params.cpu().numpy()
+    assert code == export.save_code(params, 3, [64, 64, 1], ["relu", "relu", "tanh"], "rl_tools::checkpoint::actor", 1)
+    assert export.hexfloat(params[0]) in code and export.hexfloat(params[-1]) in code and "namespace rl_tools::checkpoint::actor {" in code

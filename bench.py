@@ -207,6 +207,16 @@ def run_reference(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * N_ENVS * T / rate, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": rollout_config(args.gpus), "timed_on": "host CPU cores",
             "cpu_baseline": cpu.describe(T, args.steps, rate, cpu.one_thread_rate()), "e2e": {"value": rate, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if not args.no_secondary:
+        # the second half of the metric on the reference's CPU path, under the same key and config as the repository's arm
+        mlp = mlp_cpu_reference()
+        if mlp is not None:
+            rows = args.train_rows
+            line["secondary"] = {"mlp_train": {"metric": "MLP fwd+bwd+Adam samples/s", "value": mlp["value"], "unit": "samples/s", "n_gpus": args.gpus, "higher_is_better": True,
+                                               "scaling": "strong", "dtype": "f32", "data": "synthetic", "timed_on": "host CPU cores", "cpu_baseline": mlp,
+                                               "config": {"workload": f"mlp_train_64-256-256-256-16_rows{rows}", "rows_per_gpu": rows // max(1, args.gpus), "chunk_rows": 65536,
+                                                          "parallelism": f"dp{args.gpus}, one NCCL all-reduce of the 609 KB gradient arena per step",
+                                                          "l2": "inputs (>= 0.6 GB per pass and GPU) exceed L2"}}}
     print(json.dumps(line))
 
 
@@ -222,6 +232,24 @@ def distributed_context():
         if not dist.is_initialized():
             dist.init_process_group("nccl", device_id=dev)
     return torch, dev, dist, world, rank
+
+
+def mlp_cpu_reference(params=None):
+    """The reference's own forward + MSE gradient + backward + Adam of the 64 -> 256 -> 256 -> 256 -> 16 network on its CPU_OPENBLAS device, batch
+    1024 (its largest instantiated batch of this network in the registry), all host threads: samples/s, or None where the reference was not built."""
+    import numpy as np
+    import oracle
+    if not os.path.exists(oracle.REF_FAST_SO):
+        return None
+    os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
+    ref = oracle.Reference("fast")
+    rs = np.random.RandomState(0)
+    if params is None:
+        params = (rs.uniform(-1, 1, 152336) * 0.06).astype(np.float32)
+    xs, ys = rs.randn(1024, 64).astype(np.float32), rs.randn(1024, 16).astype(np.float32)
+    res = ref.mlp_run("c5_b1024", params, xs, ys, 2, 100)
+    return {"value": 100 * 1024 / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
+            "sample": "100 train steps (forward, mse gradient, backward, Adam) at batch 1024 of the same network, CPU_OPENBLAS build"}
 
 
 MLP_FLOP_PER_SAMPLE = 876544.0          # forward 303,104 + weight gradient 303,104 + input gradient 270,336 (2 M N K each, no padding)
@@ -271,20 +299,7 @@ def measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=Tru
     flop = MLP_FLOP_PER_SAMPLE * rows              # per GPU: the roofline compares one GPU's kernels with one GPU's peak
     peaks = measured_peaks()
     launches = steps * ((rows // chunk) * (4 + 1 + 4 * 3 + 3) + 2)
-    cpu = None
-    if cpu_baseline:
-        import numpy as np
-        import oracle
-        if os.path.exists(oracle.REF_FAST_SO):
-            # the reference's own forward + MSE gradient + backward + Adam on its CPU_OPENBLAS device, batch 1024 (its largest instantiated
-            # batch of this network in the registry), all host threads
-            os.environ.setdefault("OPENBLAS_NUM_THREADS", str(os.cpu_count() or 1))
-            ref = oracle.Reference("fast")
-            rs = np.random.RandomState(0)
-            xs, ys = rs.randn(1024, 64).astype(np.float32), rs.randn(1024, 16).astype(np.float32)
-            res = ref.mlp_run("c5_b1024", net.params.cpu().numpy(), xs, ys, 2, 100)
-            cpu = {"value": 100 * 1024 / res["seconds"], "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "reference",
-                   "sample": "100 train steps (forward, mse gradient, backward, Adam) at batch 1024 of the same network, CPU_OPENBLAS build"}
+    cpu = mlp_cpu_reference(net.params.cpu().numpy()) if cpu_baseline else None
     # the reference's OWN CUDA device (cuBLAS SGEMM per layer + its kernels) on the same step, same rows resident in HBM, on this GPU: the second
     # baseline next to its CPU path. Present where oracle/_ref/libref_cuda.so was built from the reference's headers.
     cuda_reference = None

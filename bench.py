@@ -686,7 +686,8 @@ def run_sac_update(args):
 
 def run_acrobot_rollout(args):
     """Secondary line: the environment-generic fused rollout on AcrobotSwingup -- `--envs` environments x 100 steps per launch (RK4 dynamics
-    with the reference's double-precision cos / sin, actor 6 -> 64 -> 64 -> 1, episode limit 500), CUDA-core kernel. Single GPU."""
+    with the reference's double-precision cos / sin, actor 6 -> 64 -> 64 -> 1, episode limit 500), the tensor-core rollout kernel with the Acrobot as
+    its environment policy. Single GPU."""
     import numpy as np
     import torch
     from __graft_entry__ import load_package
@@ -743,7 +744,7 @@ def run_acrobot_rollout(args):
     print(json.dumps({"metric": "env-steps/s (fused actor fwd + AcrobotSwingup RK4 step)", "value": N * T / (ms * 1e-3), "unit": "env-steps/s", "n_gpus": 1, "steps": steps,
                       "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (dynamics partly f64, as the reference)",
                       "data": "synthetic", "config": {"workload": f"acrobot_swingup_rollout_{N}env_x{T}step_actor6-64-64-1", "l2": "flushed between timed iterations",
-                                                      "kernel": "CUDA-core, one thread per environment", "parallelism": "single GPU"},
+                                                      "kernel": "tensor-core second layer (split fp16), environment as a compile-time policy", "parallelism": "single GPU"},
                       "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": tflops / peaks["tflops"], "traffic": None,
                                    "peak_source": peaks["source"] + " bf16 dense (burst)", "hbm_write_gbs": 32.0 * N * T / (ms * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm"]},
                       "cpu_baseline": cpu, "gpu_launches": steps}))

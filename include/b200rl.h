@@ -254,7 +254,8 @@ int b200rl_stream_synchronize(b200rl_stream_t stream);
  *   tests feed CPU-drawn noise to the device; may be NULL if no env can reset during the call;
  *   obs [T*N,3], act [T*N,1], rew [T*N,1]: row t*N + env.
  *   error_flag (device int, may be NULL) is set to 1 if an env needed more than R resets.
- * The actor must be 3 -> H -> H -> 1 with H in {64}; activations are free. */
+ * The actor must be 3 -> H -> H -> 1 with H in {16, 32, 64, 128}; activations are free. H = 64 runs on the tensor-core kernel, the other
+ * widths on the one-thread-per-environment kernel of b200rl_env_rollout (the device_rng, collect and runner-step entries take H = 64 only). */
 int b200rl_pendulum_rollout(const b200rl_mlp_shape* actor, const float* actor_params, float* states, int32_t* episode_step,
                             uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds,
                             int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
@@ -486,7 +487,7 @@ int b200rl_standardize_forward(const float* x, int ldx, const float* mean, const
  *                               (truncated) at termination or at the step limit (operations_generic_per_env.h:93-97)
  * reset_states [R, N, D] with D = b200rl_env_reset_dim(env): the draws of an initial state in the reference engine's order (Pendulum:
  * theta, theta_dot; AcrobotSwingup: theta_1, theta_2, velocities 0; Acrobot: all four components, U(-0.1, 0.1)).
- * The actor is OBS -> 64 -> 64 -> 1. obs [T * N, OBS], act / rew [T * N, 1], row = step * N + env.
+ * The actor is OBS -> H -> H -> 1 with H in {16, 32, 64, 128}. obs [T * N, OBS], act / rew [T * N, 1], row = step * N + env.
  * b200rl_env_rollout_flags additionally writes the environment's terminated flag of every transition (terminated [T * N], may be NULL):
  * the column the replay buffer and the critic target need for environments that terminate. */
 #define B200RL_ENV_PENDULUM 0

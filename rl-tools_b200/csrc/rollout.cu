@@ -32,6 +32,10 @@ static int rollout_launch(const b200rl_mlp_shape* actor, const float* actor_para
                           uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds,
                           int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, int* error_flag,
                           DeviceRng rng, cudaStream_t stream){
+    // hidden widths other than the tensor-core kernel's 64 run on the one-thread-per-environment kernel (table-driven resets only)
+    if(actor && !rng.enabled && actor->n_layers == 3 && actor->input_dim == 3 && actor->dims[0] == actor->dims[1] && actor->dims[0] != 64)
+        return b200rl_env_rollout(B200RL_ENV_PENDULUM, actor, actor_params, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds,
+                                  n_envs, n_steps, step_limit, obs, act, rew, error_flag, (b200rl_stream_t)stream);
     int rc = validate_actor(actor);
     if(rc) return rc;
     if(!actor_params || !states || !episode_step || !truncated || !episode_return || !obs || !act || !rew || n_envs < 0 || n_steps < 0 || n_reset_rounds < 0 || step_limit < 1)

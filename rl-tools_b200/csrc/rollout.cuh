@@ -5,18 +5,19 @@
 namespace b200rl {
 
 struct RolloutArgs {
-    const float* params;        // actor arena: W1[H,3] b1[H] W2[H,H] b2[H] W3[1,H] b3[1]
-    float* states;              // [n_envs, 2]
+    const float* params;        // actor arena: W1[H,OBS] b1[H] W2[H,H] b2[H] W3[1,H] b3[1]
+    float* states;              // [n_envs, STATE_DIM] (Pendulum: 2)
     int32_t* episode_step;      // [n_envs]
     uint8_t* truncated;         // [n_envs]
     float* episode_return;      // [n_envs]
-    const float* reset_states;  // [n_reset_rounds, n_envs, 2] or null
+    const float* reset_states;  // [n_reset_rounds, n_envs, RESET_DIM] or null
     int n_reset_rounds;
     int32_t* reset_count;       // [n_envs] resets already consumed per env (in/out), or null = all zero
     int n_envs;                 // row pitch of the outputs: row = t * n_envs + env
     int env_begin, env_count;   // the slab of environments this launch owns
     int n_steps, step_limit;
     float* obs; float* act; float* rew;
+    uint8_t* terminated;        // [n_steps * n_envs] the environment's terminated flag per transition, or null
     int* error_flag;            // device int, may be null: 1 = reset table exhausted, 2 = a bounded tensor-core wait timed out
     int acts[3];
     // on-policy collect (dataset != null): rows of the runner's dataset matrix instead of obs / act / rew
@@ -87,7 +88,8 @@ struct GaussianHead {
 };
 
 int validate_actor(const b200rl_mlp_shape* actor);
-int launch_rollout_tc(const RolloutArgs& a, cudaStream_t s);     // tensor-core kernel, H == 64
+int launch_rollout_tc(const RolloutArgs& a, cudaStream_t s);     // tensor-core kernel, H == 64, Pendulum
+int launch_env_rollout_tc(int env, const RolloutArgs& a, cudaStream_t s);     // tensor-core kernel, H == 64, environment B200RL_ENV_*
 int rollout_dispatch(const b200rl_mlp_shape* actor, const RolloutArgs& a, cudaStream_t s);
 
 }  // namespace b200rl

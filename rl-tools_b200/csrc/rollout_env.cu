@@ -1,52 +1,13 @@
 // Fused rollout for environments given as device-function policies: reset-if-truncated, observe, actor forward
-// (OBS_DIM -> 64 -> 64 -> 1), environment step, reward and episode counters for T steps in ONE launch, one thread per
+// (OBS_DIM -> H -> H -> 1, H one of 16 / 32 / 64 / 128), environment step, reward and episode counters for T steps in ONE launch, one thread per
 // environment, the runner state in registers between steps, the actor's weights in shared memory (read as warp broadcasts).
-// This is the CUDA-core kernel of rollout.cu with the Pendulum calls replaced by an ENV parameter; the tensor-core kernel
-// stays specialised to the Pendulum shapes. An environment provides
-//   STATE_DIM, OBS_DIM, RESET_DIM
-//   reset(state, draws)             the initial state from the RESET_DIM values of the reset table
-//   observe(state, obs)             the observation the actor sees
-//   transition(state, action, next) returns the reward of the transition (the reference's step + reward)
-//   TERMINATES, terminated(next)    whether the transition ended the episode (evaluated on the next state, as the runner does)
+// This CUDA-core kernel serves the hidden widths other than 64; width 64 runs on the tensor-core kernel (rollout_tc.cu), which takes the
+// same environment policies (envs.cuh).
 #include "common.cuh"
-#include "pendulum.cuh"
-#include "acrobot.cuh"
+#include "envs.cuh"
 #include "rollout.cuh"
 
 namespace b200rl {
-
-struct PendulumEnv {          // rl/environments/pendulum/operations_generic.h
-    static constexpr int STATE_DIM = 2, OBS_DIM = 3, RESET_DIM = 2;
-    static constexpr bool TERMINATES = false;
-    __device__ static bool terminated(const float (&)[2]){ return false; }
-    __device__ static void reset(float (&s)[2], const float (&u)[2]){ s[0] = u[0]; s[1] = u[1]; }
-    __device__ static void observe(const float (&s)[2], float (&o)[3]){ sincosf(s[0], &o[1], &o[0]); o[2] = s[1]; }
-    __device__ static float transition(const float (&s)[2], float action, float (&next)[2]){
-        pendulum::step(s[0], s[1], sinf(s[0]), action, next[0], next[1]);
-        return pendulum::reward(s[0], s[1], action);
-    }
-};
-struct AcrobotSwingupEnv {    // rl/environments/acrobot/operations_generic.h
-    static constexpr int STATE_DIM = 4, OBS_DIM = 6, RESET_DIM = 2;
-    static constexpr bool TERMINATES = false;
-    __device__ static bool terminated(const float (&)[4]){ return false; }
-    __device__ static void reset(float (&s)[4], const float (&u)[2]){ s[0] = u[0]; s[1] = u[1]; s[2] = 0.0f; s[3] = 0.0f; }       // :46-53
-    __device__ static void observe(const float (&s)[4], float (&o)[6]){                                                   // :180-191
-        sincosf(s[0], &o[1], &o[0]); sincosf(s[1], &o[3], &o[2]); o[4] = s[2]; o[5] = s[3];
-    }
-    __device__ static float transition(const float (&s)[4], float action, float (&next)[4]){
-        acrobot::step(s, action, next);
-        return acrobot::swingup_reward(next);
-    }
-};
-
-struct AcrobotEnv: AcrobotSwingupEnv {    // rl::environments::Acrobot: the variant that terminates
-    static constexpr int RESET_DIM = 4;
-    static constexpr bool TERMINATES = true;
-    __device__ static bool terminated(const float (&next)[4]){ return acrobot::terminated(next); }                         // :193-195
-    __device__ static void reset(float (&s)[4], const float (&u)[4]){ s[0] = u[0]; s[1] = u[1]; s[2] = u[2]; s[3] = u[3]; }    // :38-44
-    __device__ static float transition(const float (&s)[4], float action, float (&next)[4]){ acrobot::step(s, action, next); return -1.0f; }   // reward :154-156
-};
 
 struct EnvRolloutArgs {
     const float* params;        // actor arena: W1[H,OBS] b1[H] W2[H,H] b2[H] W3[1,H] b3[1]
@@ -61,7 +22,7 @@ struct EnvRolloutArgs {
 };
 
 template <typename ENV, int H>
-__global__ void __launch_bounds__(128, 4) rollout_env_kernel(EnvRolloutArgs a){
+__global__ void __launch_bounds__(128, H <= 64 ? 4 : 2) rollout_env_kernel(EnvRolloutArgs a){
     constexpr int S = ENV::STATE_DIM, O = ENV::OBS_DIM;
     extern __shared__ __align__(16) float smem[];
     float* W1 = smem;                 // [H][O]
@@ -136,13 +97,26 @@ __global__ void __launch_bounds__(128, 4) rollout_env_kernel(EnvRolloutArgs a){
     a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
 }
 
-template <typename ENV>
-static int launch_env(const EnvRolloutArgs& a, cudaStream_t s){
-    constexpr int H = 64, THREADS = 128;
+template <typename ENV, int H>
+static int launch_env_width(const EnvRolloutArgs& a, cudaStream_t s){
+    constexpr int THREADS = 128;
     constexpr size_t SMEM = sizeof(float) * (H * ENV::OBS_DIM + H + H * H + H + H + 1);
+    if(SMEM > 48 * 1024) B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_env_kernel<ENV, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
     rollout_env_kernel<ENV, H><<<(a.n_envs + THREADS - 1) / THREADS, THREADS, SMEM, s>>>(a);
     B200RL_LAUNCH_CHECK("rollout_env");
     return B200RL_OK;
+}
+
+// the hidden width is a template parameter (the first layer's activations live in registers): the widths of the reference's example
+// policies are instantiated (64 runs on the tensor-core kernel instead), any other is refused
+template <typename ENV>
+static int launch_env(const EnvRolloutArgs& a, int hidden, cudaStream_t s){
+    switch(hidden){
+        case 16:  return launch_env_width<ENV, 16>(a, s);
+        case 32:  return launch_env_width<ENV, 32>(a, s);
+        case 128: return launch_env_width<ENV, 128>(a, s);
+        default:  return B200RL_ERR_UNSUPPORTED;
+    }
 }
 
 }  // namespace b200rl
@@ -163,18 +137,28 @@ extern "C" int b200rl_env_rollout_flags(int env, const b200rl_mlp_shape* actor, 
                                         float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream){
     const int O = b200rl_env_observation_dim(env);
     if(O == 0 || !actor) return B200RL_ERR_INVALID_ARGUMENT;
-    if(actor->n_layers != 3 || actor->input_dim != O || actor->dims[0] != 64 || actor->dims[1] != 64 || actor->dims[2] != 1) return B200RL_ERR_UNSUPPORTED;
+    if(actor->n_layers != 3 || actor->input_dim != O || actor->dims[0] != actor->dims[1] || actor->dims[2] != 1) return B200RL_ERR_UNSUPPORTED;
+    const int H = actor->dims[0];
+    if(H != 16 && H != 32 && H != 64 && H != 128) return B200RL_ERR_UNSUPPORTED;
     for(int l = 0; l < 3; l++) if(!valid_activation(actor->acts[l])) return B200RL_ERR_INVALID_ARGUMENT;
     if(!actor_params || !states || !episode_step || !truncated || !episode_return || !obs || !act || !rew || n_envs < 0 || n_steps < 0 || n_reset_rounds < 0 || step_limit < 1)
         return B200RL_ERR_INVALID_ARGUMENT;
     if(reset_states == nullptr && n_reset_rounds != 0) return B200RL_ERR_INVALID_ARGUMENT;
     if(n_envs == 0 || n_steps == 0) return B200RL_OK;
+    if(H == 64){           // the tensor-core kernel: second layer as split-fp16 MMAs, the environment as its compile-time policy
+        RolloutArgs t{};
+        t.params = actor_params; t.states = states; t.episode_step = episode_step; t.truncated = truncated; t.episode_return = episode_return;
+        t.reset_states = reset_states; t.n_reset_rounds = n_reset_rounds; t.n_envs = n_envs; t.env_begin = 0; t.env_count = n_envs;
+        t.n_steps = n_steps; t.step_limit = step_limit; t.obs = obs; t.act = act; t.rew = rew; t.terminated = terminated; t.error_flag = error_flag;
+        for(int l = 0; l < 3; l++) t.acts[l] = actor->acts[l];
+        return launch_env_rollout_tc(env, t, (cudaStream_t)stream);
+    }
     EnvRolloutArgs a{};
     a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
     a.reset_states = reset_states; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs; a.n_steps = n_steps; a.step_limit = step_limit;
     a.obs = obs; a.act = act; a.rew = rew; a.terminated = terminated; a.error_flag = error_flag;
     for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
-    if(env == B200RL_ENV_PENDULUM) return launch_env<PendulumEnv>(a, (cudaStream_t)stream);
-    if(env == B200RL_ENV_ACROBOT) return launch_env<AcrobotEnv>(a, (cudaStream_t)stream);
-    return launch_env<AcrobotSwingupEnv>(a, (cudaStream_t)stream);
+    if(env == B200RL_ENV_PENDULUM) return launch_env<PendulumEnv>(a, H, (cudaStream_t)stream);
+    if(env == B200RL_ENV_ACROBOT) return launch_env<AcrobotEnv>(a, H, (cudaStream_t)stream);
+    return launch_env<AcrobotSwingupEnv>(a, H, (cudaStream_t)stream);
 }

@@ -1,4 +1,6 @@
-// Tensor-core Pendulum rollout for the 3 -> 64 -> 64 -> 1 actor (sm_100a, tcgen05 + TMEM).
+// Tensor-core rollout for the OBS -> 64 -> 64 -> 1 actor (sm_100a, tcgen05 + TMEM). The environment is a compile-time policy (envs.cuh):
+// the Pendulum (the headline workload; also the on-policy collect and the device-side random numbers) and the two Acrobot variants
+// (trajectories from reset tables, with the terminated flag of every transition on request).
 //
 // One persistent CTA per SM, 512 threads = 4 independent groups of 128 threads. A group owns a tile of up to 128
 // environments for all T steps; thread r of the group owns environment r of the tile, which is row r of the MMA and
@@ -17,7 +19,7 @@
 // remainder parts out of fp16's subnormal range; the accumulator is scaled back exactly in the epilogue. Layer-1
 // activations are converted with saturation: hidden activations beyond +-65504 are outside this kernel's domain.
 // Per step and group:
-//   1. thread: reset-if-truncated, sincos, observation; first layer (K = 3) on CUDA cores, weights as constant-bank FMA operands;
+//   1. thread: reset-if-truncated, observation; first layer (K = OBS) on CUDA cores, weights as constant-bank FMA operands;
 //      the leading parts of h1 go to tensor memory (two K elements per 32-bit column: 32 columns), the remainder parts into a
 //      K-major, 128-byte-swizzled shared-memory tile
 //   2. the group's leader issues the 13 MMAs and tcgen05.commit -> the group's mbarrier
@@ -30,11 +32,12 @@
 // operand) stay resident in shared memory for the whole launch and are shared by the four groups.
 // Tensor memory: 4 groups x (64 accumulator + 32 operand columns) of the 512 allocated.
 #include "common.cuh"
-#include "pendulum.cuh"
+#include "envs.cuh"
 #include "rollout.cuh"
 #include "tcgen05.cuh"
 #include <mutex>
 #include <cuda_fp16.h>
+#include <type_traits>
 
 
 namespace b200rl {
@@ -51,21 +54,26 @@ constexpr uint32_t OFF_ABORT = OFF_MBAR + 8 * GROUPS;
 constexpr uint32_t OFF_SLOT = OFF_ABORT + 4 * GROUPS;
 constexpr uint32_t OFF_SCALE = OFF_SLOT + 8;                  // [0] scale of the second-layer operand (a power of two), [1] its inverse; [2..3] reduction scratch
 constexpr uint32_t OFF_TURN = OFF_SCALE + 16 + 4 * 32;                   // 2 mbarriers: the tensor token alternating between the group pairs {0,1} and {2,3}
-constexpr uint32_t OFF_STAGE = (OFF_TURN + 8 * 2 + 15) / 16 * 16;  // output staging for bulk stores: per group 3 buffers x (obs 1536 + act 512 + rew 512 B)
-constexpr uint32_t STAGE_BUF_BYTES = TILE * 12 + TILE * 4 + TILE * 4, STAGE_GROUP_BYTES = 3 * STAGE_BUF_BYTES;
-constexpr uint32_t SMEM_BYTES = OFF_STAGE + GROUPS * STAGE_GROUP_BYTES + 1024;         // + slack to align the base to 1024 B
+constexpr uint32_t OFF_STAGE = (OFF_TURN + 8 * 2 + 15) / 16 * 16;  // output staging for bulk stores: per group 3 buffers x (obs + act + rew rows of a tile)
+__host__ __device__ constexpr uint32_t stage_buf_bytes(int obs_dim){ return TILE * 4 * obs_dim + TILE * 4 + TILE * 4; }
+__host__ __device__ constexpr uint32_t smem_bytes(int obs_dim){ return OFF_STAGE + GROUPS * 3 * stage_buf_bytes(obs_dim) + 1024; }     // + slack to align the base to 1024 B
 constexpr uint32_t TMEM_COLS = 512, TMEM_COLS_PER_GROUP = 128;          // per group 64 accumulator + 32 operand columns are used
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;        // ~1 s: far beyond any legitimate wait
-// arena offsets of the actor 3 -> 64 -> 64 -> 1
-constexpr int P_W1 = 0, P_B1 = 192, P_W2 = 256, P_B2 = 4352, P_W3 = 4416, P_B3 = 4480;
-constexpr int C_W1 = 0, C_B1 = 192, C_B2 = 256, C_W3 = 320, C_B3 = 384, C_COUNT = 385;
+constexpr int MAX_OBS = 6;
+// offsets in the arena of the actor OBS -> 64 -> 64 -> 1, and in the constant bank (the same without W2)
+struct Layout {
+    int P_B1, P_W2, P_B2, P_W3, P_B3, C_B1, C_B2, C_W3, C_B3;
+    __host__ __device__ constexpr Layout(int obs): P_B1(H * obs), P_W2(H * obs + H), P_B2(H * obs + H + H * H), P_W3(H * obs + 2 * H + H * H), P_B3(H * obs + 3 * H + H * H),
+                               C_B1(H * obs), C_B2(H * obs + H), C_W3(H * obs + 2 * H), C_B3(H * obs + 3 * H) {}
+};
+constexpr int C_COUNT_MAX = H * MAX_OBS + 3 * H + 1;
 }
 
 // The small layers' weights (W1, b1, b2, W3, b3) are read by EVERY thread at EVERY step. As constant-bank operands
 // of the FMA instructions they cost no load instruction and no shared-memory bandwidth (a warp-wide broadcast LDS.128
 // occupies the 128 B/clk shared pipe for 4 cycles, which made the table look-ups the bottleneck of the CUDA-core
 // phase). Filled by a device-to-device copy on the launch stream; launches are ordered by an event (see launch_tc).
-__constant__ float c_actor[C_COUNT + 3];
+__constant__ float c_actor[C_COUNT_MAX + 3];
 
 // x = lead + rest + O(2^-24 x): lead = fp16(x) (11 significant bits), rest = fp16(x - lead). Two values per register, the lower index in
 // the low half. Conversions saturate at +-65504 instead of producing infinities.
@@ -92,9 +100,16 @@ __device__ __forceinline__ float act_or_rt(float x, int rt){
 // one step later, at the barrier it already has before its MMA batch. Three buffers rotate: the buffer of step t is read by the copy issued
 // after barrier t+1, the leader waits for that read before barrier t+2, and the buffer is written again in step t+3. Requires 16-byte aligned
 // row starts (n_envs and the slab origin multiples of 4, aligned output pointers); the host selects the plain-store instantiation otherwise.
-template <int A1, int A2, bool COLLECT, bool BULK>
+template <typename ENV, int A1, int A2, bool COLLECT, bool BULK>
 __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, int n_tiles, int envs_per_tile){
     static_assert(!(COLLECT && BULK), "dataset rows are strided: plain stores");
+    constexpr bool IS_PENDULUM = std::is_same<ENV, PendulumEnv>::value;
+    static_assert(!COLLECT || IS_PENDULUM, "the dataset columns are the Pendulum's");
+    constexpr int S = ENV::STATE_DIM, O = ENV::OBS_DIM, RD = ENV::RESET_DIM;
+    static_assert(O <= MAX_OBS, "constant bank");
+    constexpr Layout L(O);
+    constexpr int P_W2 = L.P_W2, P_B2 = L.P_B2, C_W1 = 0, C_B1 = L.C_B1, C_W3 = L.C_W3, C_B3 = L.C_B3;
+    constexpr uint32_t STAGE_BUF_BYTES = stage_buf_bytes(O), STAGE_GROUP_BYTES = 3 * STAGE_BUF_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment by OFFSET from the __shared__ array, so the compiler keeps the shared address space (LDS/STS, not generic)
     uint8_t* base = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -195,9 +210,12 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
         const int local = tile * envs_per_tile + r;
         const bool valid = r < envs_per_tile && local < a.env_count;
         const int e = a.env_begin + (valid ? local : 0);
-        float theta = 0.0f, theta_dot = 0.0f, er = 0.0f; int es = 0, resets = 0; bool trunc = false;
+        float state[S], er = 0.0f; int es = 0, resets = 0; bool trunc = false;
+#pragma unroll
+        for(int k = 0; k < S; k++) state[k] = 0.0f;
         if(valid){
-            theta = a.states[2 * e]; theta_dot = a.states[2 * e + 1];
+#pragma unroll
+            for(int k = 0; k < S; k++) state[k] = a.states[(size_t)S * e + k];
             es = a.episode_step[e]; trunc = a.truncated[e] != 0; er = a.episode_return[e];
             resets = a.reset_count ? a.reset_count[e] : 0;
             if constexpr(COLLECT) a.dataset[(size_t)e * ld + COL_RESET] = trunc ? 1.0f : 0.0f;      // collect, operations_generic.h:115-117
@@ -208,36 +226,48 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
         auto bulk_flush = [&](int ts){
             uint8_t* buf = stage_base + (uint32_t)(ts % 3) * STAGE_BUF_BYTES;
             const size_t row0 = (size_t)ts * a.n_envs + tile_first;
-            tc::bulk_store(a.obs + row0 * 3, buf, (uint32_t)tile_count * 12);
-            tc::bulk_store(a.act + row0, buf + TILE * 12, (uint32_t)tile_count * 4);
-            tc::bulk_store(a.rew + row0, buf + TILE * 16, (uint32_t)tile_count * 4);
+            tc::bulk_store(a.obs + row0 * O, buf, (uint32_t)tile_count * 4 * O);
+            tc::bulk_store(a.act + row0, buf + TILE * 4 * O, (uint32_t)tile_count * 4);
+            tc::bulk_store(a.rew + row0, buf + TILE * 4 * (O + 1), (uint32_t)tile_count * 4);
             tc::bulk_commit();
         };
         for(int t = 0; t < a.n_steps; t++){
             float* st_obs = reinterpret_cast<float*>(stage_base + (uint32_t)(t % 3) * STAGE_BUF_BYTES);
-            float* st_act = st_obs + TILE * 3;
+            float* st_act = st_obs + TILE * O;
             float* st_rew = st_act + TILE;
             StepDraws draws{};             // the trajectory-only kernels need the draws at a reset only: nothing per step on their hot path
-            if(a.device_rng && (COLLECT || trunc)) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e);
+            if constexpr(IS_PENDULUM){ if(a.device_rng && (COLLECT || trunc)) draws = step_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e); }
             if(trunc && valid){
-                if(a.device_rng){    // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
-                    theta = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(draws.u_theta_dot, 2.0f, -1.0f);
+                bool drawn = false;
+                if constexpr(IS_PENDULUM){
+                    if(a.device_rng){    // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61)
+                        state[0] = fmaf(draws.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); state[1] = fmaf(draws.u_theta_dot, 2.0f, -1.0f);
+                        drawn = true;
+                    }
                 }
-                else if(a.reset_states != nullptr && resets < a.n_reset_rounds){
-                    const float* rs = a.reset_states + ((size_t)resets * a.n_envs + e) * 2;      // scalar loads: the table may be a view at any 4-byte offset
-                    theta = __ldg(rs); theta_dot = __ldg(rs + 1);
+                if(!drawn){
+                    if(a.reset_states != nullptr && resets < a.n_reset_rounds){
+                        const float* rs = a.reset_states + ((size_t)resets * a.n_envs + e) * RD;      // scalar loads: the table may be a view at any 4-byte offset
+                        float u[RD];
+#pragma unroll
+                        for(int k = 0; k < RD; k++) u[k] = __ldg(rs + k);
+                        ENV::reset(state, u);
+                    }
+                    else if(a.error_flag) *a.error_flag = 1;
                 }
-                else if(a.error_flag) *a.error_flag = 1;
                 resets++; es = 0; er = 0.0f;
             }
-            float sn, cs;
-            sincosf(theta, &sn, &cs);
+            float o[O];
+            ENV::observe(state, o);
             const size_t row = (size_t)t * a.n_envs + e;
             float* drow = COLLECT ? a.dataset + row * ld : nullptr;
             if(valid){
-                if constexpr(COLLECT){ drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot; }
-                else if constexpr(BULK){ st_obs[r * 3 + 0] = cs; st_obs[r * 3 + 1] = sn; st_obs[r * 3 + 2] = theta_dot; }
-                else{ a.obs[row * 3 + 0] = cs; a.obs[row * 3 + 1] = sn; a.obs[row * 3 + 2] = theta_dot; }
+#pragma unroll
+                for(int k = 0; k < O; k++){
+                    if constexpr(COLLECT) drow[COL_OBS + k] = o[k];
+                    else if constexpr(BULK) st_obs[r * O + k] = o[k];
+                    else a.obs[row * O + k] = o[k];
+                }
             }
 
             // ---- layer 1 (CUDA cores, weights as constant-bank operands); leading fp16 parts -> TMEM, remainder parts -> swizzled smem tile ----
@@ -251,9 +281,9 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
 #pragma unroll
                     for(int z = 0; z < 2; z++){
                         const int j = c * 8 + q * 2 + z;
-                        float acc = fmaf(c_actor[C_W1 + 3 * j], cs, c_actor[C_B1 + j]);      // bias first, inputs ascending: the reference's order
-                        acc = fmaf(c_actor[C_W1 + 3 * j + 1], sn, acc);
-                        acc = fmaf(c_actor[C_W1 + 3 * j + 2], theta_dot, acc);
+                        float acc = c_actor[C_B1 + j];                                       // bias first, inputs ascending: the reference's order
+#pragma unroll
+                        for(int k = 0; k < O; k++) acc = fmaf(c_actor[C_W1 + O * j + k], o[k], acc);
                         h[z] = act_or_rt<A1>(acc, act1);
                     }
                     split_f16_pair(h[0], h[1], lead[q], rest[q]);
@@ -326,9 +356,8 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                 if(valid){ drow[COL_ACTION_MEAN] = mean; drow[COL_ACTION] = action; drow[COL_LOG_PROB] = head.log_prob(mean, action, a.neg_half_log_2pi); }
             }
 
-            float nt, ntd;
-            pendulum::step(theta, theta_dot, sn, action, nt, ntd);
-            const float rwd = pendulum::reward(theta, theta_dot, action);
+            float next[S];
+            const float rwd = ENV::transition_obs(state, o, action, next);
             es += 1; er = __fadd_rn(er, rwd);
             if constexpr(COLLECT){
                 trunc = a.step_limit > 0 && es >= a.step_limit;             // operations_generic_per_env.h:72
@@ -343,9 +372,16 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                     if constexpr(BULK){ st_act[r] = action; st_rew[r] = rwd; }
                     else{ a.act[row] = action; a.rew[row] = rwd; }
                 }
-                trunc = (es == a.step_limit);
+                bool term = false;
+                if constexpr(ENV::TERMINATES){
+                    term = ENV::terminated(next);
+                    if(valid && a.terminated) a.terminated[row] = term ? 1 : 0;
+                }
+                else if(a.terminated){ if(valid) a.terminated[row] = 0; }
+                trunc = term || (es == a.step_limit);                         // operations_generic_per_env.h:93-97
             }
-            theta = nt; theta_dot = ntd;
+#pragma unroll
+            for(int k = 0; k < S; k++) state[k] = next[k];
         }
         if constexpr(BULK){
             // last step of the tile: make the staged rows visible to the copy engine, flush, and wait until every buffer has been read
@@ -356,14 +392,16 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
         }
         if constexpr(COLLECT){
             if(valid && !failed){                  // final observation, operations_generic.h:136-143
-                float sn, cs;
-                sincosf(theta, &sn, &cs);
+                float o[O];
+                ENV::observe(state, o);
                 float* drow = a.dataset + ((size_t)a.n_steps * a.n_envs + e) * ld;
-                drow[COL_OBS] = cs; drow[COL_OBS + 1] = sn; drow[COL_OBS + 2] = theta_dot;
+#pragma unroll
+                for(int k = 0; k < O; k++) drow[COL_OBS + k] = o[k];
             }
         }
         if(valid && !failed){
-            a.states[2 * e] = theta; a.states[2 * e + 1] = theta_dot;
+#pragma unroll
+            for(int k = 0; k < S; k++) a.states[(size_t)S * e + k] = state[k];
             a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
             if(a.reset_count) a.reset_count[e] = resets;
         }
@@ -379,24 +417,28 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
 // The kernel fills every SM, so this ordering costs no concurrency. The event, like the kernel's shared-memory attribute, belongs
 // to a device: both are kept per device ordinal.
 namespace {
-struct TcDeviceState { cudaEvent_t order = nullptr; bool configured[16] = {}; };
+struct TcDeviceState { cudaEvent_t order = nullptr; bool configured[3][16] = {}; };
 TcDeviceState g_tc_state[MAX_DEVICES];
 std::mutex g_tc_mutex;
 }
 
-static int upload_small_layers(TcDeviceState& st, const float* params, cudaStream_t s, cudaEvent_t* order_event){
+static int upload_small_layers(TcDeviceState& st, const float* params, int obs_dim, cudaStream_t s, cudaEvent_t* order_event){
+    const Layout L(obs_dim);
     if(!st.order) B200RL_CUDA_TRY(cudaEventCreateWithFlags(&st.order, cudaEventDisableTiming));
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     B200RL_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
     *order_event = cap == cudaStreamCaptureStatusNone ? st.order : nullptr;
     if(*order_event) B200RL_CUDA_TRY(cudaStreamWaitEvent(s, st.order, 0));
-    B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + P_W1, sizeof(float) * 256, sizeof(float) * C_W1, cudaMemcpyDeviceToDevice, s));
-    B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + P_B2, sizeof(float) * 129, sizeof(float) * C_B2, cudaMemcpyDeviceToDevice, s));
+    B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params, sizeof(float) * (size_t)L.P_W2, 0, cudaMemcpyDeviceToDevice, s));                           // W1, b1
+    B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + L.P_B2, sizeof(float) * (2 * H + 1), sizeof(float) * (size_t)L.C_B2, cudaMemcpyDeviceToDevice, s));   // b2, W3, b3
     return B200RL_OK;
 }
 
-template <int A1, int A2, bool COLLECT, bool BULK>
+template <typename ENV> struct EnvIndex { static constexpr int value = std::is_same<ENV, PendulumEnv>::value ? 0 : std::is_same<ENV, AcrobotSwingupEnv>::value ? 1 : 2; };
+
+template <typename ENV, int A1, int A2, bool COLLECT, bool BULK>
 static int launch_tc_variant(const RolloutArgs& a, cudaStream_t s, int variant){
+    constexpr uint32_t SMEM_BYTES = smem_bytes(ENV::OBS_DIM);
     int dev = 0, sms = 0;
     int rc = current_device(&dev);
     if(rc) return rc;
@@ -404,12 +446,12 @@ static int launch_tc_variant(const RolloutArgs& a, cudaStream_t s, int variant){
     if(rc) return rc;
     std::lock_guard<std::mutex> lock(g_tc_mutex);
     TcDeviceState& st = g_tc_state[dev];
-    if(!st.configured[variant]){
-        B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<A1, A2, COLLECT, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-        st.configured[variant] = true;
+    if(!st.configured[EnvIndex<ENV>::value][variant]){
+        B200RL_CUDA_TRY(cudaFuncSetAttribute(rollout_tc_kernel<ENV, A1, A2, COLLECT, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+        st.configured[EnvIndex<ENV>::value][variant] = true;
     }
     cudaEvent_t order_event = nullptr;
-    rc = upload_small_layers(st, a.params, s, &order_event);
+    rc = upload_small_layers(st, a.params, ENV::OBS_DIM, s, &order_event);
     if(rc) return rc;
     // spread the environments evenly over every group of every SM: tiles of <= 128 environments (a multiple of 4)
     const int groups_total = sms * GROUPS;
@@ -419,32 +461,46 @@ static int launch_tc_variant(const RolloutArgs& a, cudaStream_t s, int variant){
     const int n_tiles = (a.env_count + ept - 1) / ept;
     int grid = (n_tiles + GROUPS - 1) / GROUPS;
     if(grid > sms) grid = sms;
-    rollout_tc_kernel<A1, A2, COLLECT, BULK><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
+    rollout_tc_kernel<ENV, A1, A2, COLLECT, BULK><<<grid, THREADS, SMEM_BYTES, s>>>(a, n_tiles, ept);
     B200RL_LAUNCH_CHECK("rollout_tc");
     if(order_event) B200RL_CUDA_TRY(cudaEventRecord(order_event, s));
     return B200RL_OK;
 }
 
 // Bulk stores need 16-byte aligned row starts in all three outputs; per-thread stores otherwise (and always for the strided dataset rows)
-template <int A1, int A2, bool COLLECT>
+template <typename ENV, int A1, int A2, bool COLLECT>
 static int launch_tc(const RolloutArgs& a, cudaStream_t s, int variant){
-    if constexpr(COLLECT) return launch_tc_variant<A1, A2, true, false>(a, s, variant);
+    if constexpr(COLLECT) return launch_tc_variant<ENV, A1, A2, true, false>(a, s, variant);
     else{
         const bool aligned = ((reinterpret_cast<uintptr_t>(a.obs) | reinterpret_cast<uintptr_t>(a.act) | reinterpret_cast<uintptr_t>(a.rew)) & 15u) == 0 &&
                              a.n_envs % 4 == 0 && a.env_begin % 4 == 0 && a.env_count % 4 == 0;
-        return aligned ? launch_tc_variant<A1, A2, false, true>(a, s, variant) : launch_tc_variant<A1, A2, false, false>(a, s, variant + 1);
+        return aligned ? launch_tc_variant<ENV, A1, A2, false, true>(a, s, variant) : launch_tc_variant<ENV, A1, A2, false, false>(a, s, variant + 1);
     }
 }
 
 int launch_rollout_tc(const RolloutArgs& a, cudaStream_t s){
     const int a1 = a.acts[0], a2 = a.acts[1];
     if(a.dataset){
-        if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, true>(a, s, 0);
-        return launch_tc<-1, -1, true>(a, s, 1);
+        if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<PendulumEnv, B200RL_ACT_RELU, B200RL_ACT_RELU, true>(a, s, 0);
+        return launch_tc<PendulumEnv, -1, -1, true>(a, s, 1);
     }
-    if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<B200RL_ACT_RELU, B200RL_ACT_RELU, false>(a, s, 2);
-    if(a1 == B200RL_ACT_TANH && a2 == B200RL_ACT_TANH) return launch_tc<B200RL_ACT_TANH, B200RL_ACT_TANH, false>(a, s, 4);
-    return launch_tc<-1, -1, false>(a, s, 6);
+    if(a1 == B200RL_ACT_RELU && a2 == B200RL_ACT_RELU) return launch_tc<PendulumEnv, B200RL_ACT_RELU, B200RL_ACT_RELU, false>(a, s, 2);
+    if(a1 == B200RL_ACT_TANH && a2 == B200RL_ACT_TANH) return launch_tc<PendulumEnv, B200RL_ACT_TANH, B200RL_ACT_TANH, false>(a, s, 4);
+    return launch_tc<PendulumEnv, -1, -1, false>(a, s, 6);
+}
+
+// the other environments: trajectories only (no dataset rows, reset tables only), ReLU specialisation or run-time activations
+template <typename ENV>
+static int launch_env_tc(const RolloutArgs& a, cudaStream_t s){
+    if(a.dataset || a.device_rng) return B200RL_ERR_UNSUPPORTED;
+    if(a.acts[0] == B200RL_ACT_RELU && a.acts[1] == B200RL_ACT_RELU) return launch_tc<ENV, B200RL_ACT_RELU, B200RL_ACT_RELU, false>(a, s, 2);
+    return launch_tc<ENV, -1, -1, false>(a, s, 6);
+}
+int launch_env_rollout_tc(int env, const RolloutArgs& a, cudaStream_t s){
+    if(env == B200RL_ENV_PENDULUM) return launch_rollout_tc(a, s);
+    if(env == B200RL_ENV_ACROBOT_SWINGUP) return launch_env_tc<AcrobotSwingupEnv>(a, s);
+    if(env == B200RL_ENV_ACROBOT) return launch_env_tc<AcrobotEnv>(a, s);
+    return B200RL_ERR_INVALID_ARGUMENT;
 }
 
 }  // namespace b200rl

@@ -199,3 +199,51 @@ def test_env_rollout_argument_checks(lib, torch):
     tr.fill_(1)
     lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape6, params, st, es, tr, er, None, 1, 10, error_flag=flag)
     assert int(flag.item()) == 1                                                                     # a reset without a table entry raises the flag
+
+
+@pytest.mark.parametrize("hidden", [16, 32, 128])
+def test_actor_widths_other_than_64(lib, torch, hidden):
+    """The runner is generic in the policy (rl/components/off_policy_runner/operations_generic.h): hidden widths 16, 32 and 128 of the
+    3-layer actor run on the one-thread-per-environment kernel -- the Pendulum through its own entry point (which routes there), a whole
+    episode boundary included (step limit 5, two resets from the table), and one Acrobot swing-up step -- against the oracle's runner loop."""
+    rs = np.random.RandomState(hidden)
+    N, T = 777, 12
+    acts = ["relu", "relu", "tanh"]
+    n_params = hidden * 3 + hidden + hidden * hidden + hidden + hidden + 1
+    params = (rs.uniform(-1, 1, n_params) * (1.5 / np.sqrt(hidden))).astype(np.float32)
+    states = np.stack([rs.uniform(-3, 3, N), rs.uniform(-2, 2, N)], 1).astype(np.float32)
+    resets = np.stack([rs.uniform(-np.pi, np.pi, (3, N)), rs.uniform(-1, 1, (3, N))], 2).astype(np.float32)
+    shape, oshape = lib.MlpShape.make(3, [hidden, hidden, 1], acts), oracle.MlpShape.make(3, [hidden, hidden, 1], acts)
+    st, es, tr, er = runner(torch, states)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    obs, act, rew = lib.pendulum_rollout(shape, dev(torch, params), st, es, tr, er, dev(torch, resets), T, 5, error_flag=flag)
+    assert int(flag.item()) == 0
+    orc = oracle.Oracle()
+    # teacher forcing: the oracle recomputes each step from the kernel's own states, so one rounding difference cannot grow over the steps
+    got_obs = obs.cpu().numpy()
+    want = orc.pendulum_rollout(oshape, params, states, np.zeros(N, np.int32), np.zeros(N, np.uint8), np.zeros(N, np.float32), resets, T, 5)
+    close(got_obs[:N], want["obs"][:N], what="first observation")
+    close(act.cpu().numpy()[:N], want["act"][:N], what="first action")
+    want_act = orc.mlp_evaluate(oshape, params, got_obs).reshape(-1)
+    close(act.cpu().numpy().reshape(-1), want_act, what="actions of all steps on the kernel's observations")
+    assert np.array_equal(es.cpu().numpy(), want["episode_step"]) and np.array_equal(tr.cpu().numpy(), want["truncated"])
+    # the resets took the table's rows: the observation after a reset is the table's state
+    row = 5 * N                                                      # step 5 is the first step of the second episode
+    assert np.allclose(got_obs[row:row + N, 0], np.cos(resets[0, :, 0]), atol=1e-6) and np.allclose(got_obs[row:row + N, 2], resets[0, :, 1], atol=1e-6)
+
+    shape6, oshape6 = lib.MlpShape.make(6, [hidden, hidden, 1], acts), oracle.MlpShape.make(6, [hidden, hidden, 1], acts)
+    params6 = (rs.uniform(-1, 1, n_params + 3 * hidden) * (1.5 / np.sqrt(hidden))).astype(np.float32)
+    states4 = rs.uniform(-1, 1, (N, 4)).astype(np.float32)
+    st, es, tr, er = runner(torch, states4)
+    obs, act, rew = lib.env_rollout(lib.ENV_ACROBOT_SWINGUP, shape6, dev(torch, params6), st, es, tr, er, None, 1, 500)
+    want = orc.acrobot_rollout(oshape6, params6, states4, np.zeros(N, np.int32), np.zeros(N, np.uint8), np.zeros(N, np.float32), np.zeros((0, N, 2), np.float32), 1)
+    close(obs.cpu().numpy(), want["obs"], what="acrobot observation")
+    close(act.cpu().numpy(), want["act"], what="acrobot action")
+    close(st.cpu().numpy(), want["states"], rtol=1e-5, atol=2e-6, what="acrobot next state")
+
+
+def test_unsupported_actor_width_is_refused(lib, torch):
+    shape = lib.MlpShape.make(3, [48, 48, 1], ["relu", "relu", "tanh"])
+    st, es, tr, er = runner(torch, np.zeros((4, 2), np.float32))
+    with pytest.raises(lib.B200RLError):
+        lib.pendulum_rollout(shape, torch.zeros(48 * 3 + 48 + 48 * 48 + 48 + 48 + 1, device="cuda"), st, es, tr, er, None, 1, 200)

@@ -367,6 +367,22 @@ int b200rl_pendulum_offpolicy_step(const b200rl_mlp_shape* actor, const float* a
                                    const b200rl_replay_layout* layout, float* reward_scratch, uint8_t* was_truncated_scratch, int* error_flag,
                                    b200rl_stream_t stream);
 
+/* The same runner step in two halves around ANY policy -- how the reference's CUDA runner is built (operations_cuda.h:184-204: prologue
+ * kernel, evaluate(policy), epilogue kernel): an exploration policy with a stochastic head (SAC's sample-and-squash actor) is evaluated by
+ * the caller between the two calls.
+ * prologue: reset-if-truncated (reset_states [N, 2] in environment order, or, if NULL, drawn in the kernel from the counter-based generator
+ *   keyed by (seed, environment, call + *call_counter); call_counter is an optional device-resident 64-bit integer, so that a captured
+ *   graph draws fresh states on every replay), episode counters of a fresh episode, observations [N, 3]; was_truncated_scratch [N] keeps
+ *   the truncated flags for the epilogue.
+ * epilogue: environment step with actions [N, 1], reward, counters, truncation at step_limit, next_observations [N, 3], append to the
+ *   replay buffers (layout and bookkeeping as in b200rl_pendulum_offpolicy_step). */
+int b200rl_pendulum_offpolicy_prologue(float* states, int32_t* episode_step, const uint8_t* truncated, float* episode_return, const float* reset_states,
+                                       unsigned long long seed, unsigned long long call, const unsigned long long* call_counter, int n_envs,
+                                       float* observations, uint8_t* was_truncated_scratch, b200rl_stream_t stream);
+int b200rl_pendulum_offpolicy_epilogue(float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return, int n_envs, int step_limit,
+                                       const float* observations, const float* actions, float* next_observations, void* replay_buffers,
+                                       const b200rl_replay_layout* layout, const uint8_t* was_truncated_scratch, b200rl_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Replay-buffer sampling: gather_batch(device, runner, batch, rng) for SequentialBatch with SEQUENCE_LENGTH 1 and its default sampling
  * parameters (rl/components/off_policy_runner/operations_generic.h:239-423, off_policy_runner.h:80-156; CUDA form

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "dense_tc.cu", "mlp_fused.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "dense_skinny.cu", "mlp_fused.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
@@ -172,6 +172,8 @@ def lib():
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         u64 = C.c_uint64
         L.b200rl_pendulum_collect_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, i, vp, vp]
+        L.b200rl_pendulum_offpolicy_prologue.argtypes = [vp, vp, vp, vp, vp, u64, u64, vp, i, vp, vp, vp]
+        L.b200rl_pendulum_offpolicy_epilogue.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, C.POINTER(ReplayLayout), vp, vp]
         L.b200rl_pendulum_rollout_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, vp, vp, vp, vp]
         _lib = L
     return _lib
@@ -576,6 +578,20 @@ def pendulum_offpolicy_step(shape, params, states, episode_step, truncated, epis
     check(lib().b200rl_pendulum_offpolicy_step(C.byref(shape), _ptr(params) if layers is None else None, table, _ptr(states), _ptr(episode_step), _ptr(truncated),
                                                _ptr(episode_return), _ptr(reset_states), N, step_limit, _ptr(observations), _ptr(actions), _ptr(next_observations),
                                                _ptr(replay), C.byref(layout), _ptr(rew), _ptr(was), _ptr(error_flag), _stream()), "b200rl_pendulum_offpolicy_step")
+
+
+def pendulum_offpolicy_prologue(states, episode_step, truncated, episode_return, observations, was_truncated, reset_states=None, seed=0, call_index=0, call_counter=None):
+    """First half of the runner step around any policy: reset-if-truncated (from reset_states [N, 2], or drawn in the kernel keyed by
+    (seed, environment, call_index + *call_counter)), counters of a fresh episode, observations [N, 3]."""
+    check(lib().b200rl_pendulum_offpolicy_prologue(_ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return), _ptr(reset_states), seed, call_index,
+                                                   _ptr(call_counter), states.shape[0], _ptr(observations), _ptr(was_truncated), _stream()), "b200rl_pendulum_offpolicy_prologue")
+
+
+def pendulum_offpolicy_epilogue(states, episode_step, truncated, episode_return, step_limit, observations, actions, next_observations, replay, layout, was_truncated):
+    """Second half: environment step with the given actions [N, 1], reward, counters, next observations, replay-buffer append."""
+    check(lib().b200rl_pendulum_offpolicy_epilogue(_ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return), states.shape[0], step_limit, _ptr(observations),
+                                                   _ptr(actions), _ptr(next_observations), _ptr(replay), C.byref(layout), _ptr(was_truncated), _stream()),
+          "b200rl_pendulum_offpolicy_epilogue")
 
 
 def replay_counters(replay, layout, n_envs):

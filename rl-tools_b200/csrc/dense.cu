@@ -237,18 +237,19 @@ __global__ void reduce_partials_kernel(float* dst, const float* __restrict__ par
 // Bias gradient: dst[o] += sum_s partial[s][o] for few columns and many segments. One block per 32 columns, 8 lanes of segments
 // (lane y takes s = y, y + 8, ... in ascending order), then the 8 lane sums in ascending order: a fixed summation order, and
 // segs / 8 dependent steps instead of segs (the single-block, one-thread-per-column form took 31 us for 296 segments).
-__global__ void __launch_bounds__(256) reduce_bias_partials_kernel(float* dst, const float* __restrict__ partial, int O, int segs){
+// (stride: floats from one segment's record to the next; O for densely packed segments)
+__global__ void __launch_bounds__(256) reduce_strided_partials_kernel(float* dst, const float* __restrict__ partial, int O, long long stride, int segs){
     __shared__ float red[8][33];
     const int o = blockIdx.x * 32 + threadIdx.x;
     float s = 0.0f;
     if(o < O){
         int z = threadIdx.y;
         for(; z + 24 < segs; z += 32){
-            const float v0 = __ldg(partial + (long long)z * O + o), v1 = __ldg(partial + (long long)(z + 8) * O + o);
-            const float v2 = __ldg(partial + (long long)(z + 16) * O + o), v3 = __ldg(partial + (long long)(z + 24) * O + o);
+            const float v0 = __ldg(partial + (long long)z * stride + o), v1 = __ldg(partial + (long long)(z + 8) * stride + o);
+            const float v2 = __ldg(partial + (long long)(z + 16) * stride + o), v3 = __ldg(partial + (long long)(z + 24) * stride + o);
             s += v0; s += v1; s += v2; s += v3;
         }
-        for(; z < segs; z += 8) s += __ldg(partial + (long long)z * O + o);
+        for(; z < segs; z += 8) s += __ldg(partial + (long long)z * stride + o);
     }
     red[threadIdx.y][threadIdx.x] = s;
     __syncthreads();
@@ -267,6 +268,15 @@ static bool tc_eligible(long long M, long long N, long long K){
     return M >= 64 && N >= 16 && (double)M * N * K >= ldexp(1.0, 27);
 }
 static bool use_tensor_cores(const GemmArgs& a){ return tc_eligible(a.M, a.N, a.K); }
+
+// one-pass backward of a layer with few outputs at a large batch (dense_skinny.cu)
+bool skinny_backward_eligible(int B, int I, int O);
+size_t skinny_backward_scratch_bytes(int I, int O, int ctas);
+int skinny_backward_launch(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd, float* partial, float* d_in, int ldi,
+                           int B, int I, int O, int act, int ctas, cudaStream_t s);
+bool skinny_forward_eligible(const float* x, int ldx, int B, int I, int O);
+int skinny_forward_launch(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy, int B, int I, int O, int act, int ctas, cudaStream_t s);
+constexpr int SKINNY_CTAS = 2 * NUM_SMS;       // two resident CTAs per SM, one wave
 
 // bytes: split-k and bias partial sums (required when gradients are wanted); wt_bytes: room behind them for the operand image of the
 // transposed weights, which the input-gradient product of the tensor-core path copies in instead of re-splitting W^T per row tile
@@ -312,10 +322,18 @@ static BackwardPlan plan_backward(int B, int I, int O, size_t budget = SIZE_MAX)
     return p;
 }
 
+// what b200rl_dense_backward_scratch_bytes reports: the tiled path's partial sums and operand image, or the one-pass kernel's per-CTA sums
+static size_t backward_scratch_total(int B, int I, int O){
+    const BackwardPlan p = plan_backward(B, I, O);
+    const size_t tiled = p.bytes + p.wt_bytes, skinny = skinny_backward_eligible(B, I, O) ? skinny_backward_scratch_bytes(I, O, SKINNY_CTAS) : 0;
+    return tiled > skinny ? tiled : skinny;
+}
+
 // workspace (optional): room for the weights' operand image, see b200rl_dense_forward_workspace_bytes
 static size_t forward_workspace_bytes(int B, int I, int O){ return tc_eligible(B, O, I) ? weight_image_bytes(O, I) : 0; }
 static int dense_forward_impl(const float* W, const float* bias, const float* x, int ldx, float* pre, int ldpre, float* y, int ldy,
                               int B, int I, int O, int act, cudaStream_t s, void* workspace = nullptr, size_t workspace_bytes = 0){
+    if(skinny_forward_eligible(x, ldx, B, I, O)) return skinny_forward_launch(W, bias, x, ldx, pre, ldpre, y, ldy, B, I, O, act, SKINNY_CTAS, s);
     GemmArgs a{};
     a.A = x; a.lda = ldx; a.B = W; a.ldb = I; a.M = B; a.N = O; a.K = I; a.k_per_split = I;
     a.bias = bias; a.pre = pre; a.ldpre = ldpre; a.C = y; a.ldc = ldy;
@@ -369,8 +387,30 @@ static int gradient_branch(cudaStream_t s, cudaStream_t* branch, cudaEvent_t* jo
 static int dense_backward_impl(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
                                float* dW, float* db, float* d_in, int ldi, int B, int I, int O, int act, void* scratch, size_t scratch_bytes, cudaStream_t s,
                                size_t plan_budget = SIZE_MAX){
-    BackwardPlan p = plan_backward(B, I, O, plan_budget);
     bool want_grads = dW != nullptr;
+    // few outputs at a large batch: one pass over the layer's input (d_pre, bias and weight gradients, input gradient), when the scratch holds
+    // its per-CTA sums; the tiled path otherwise
+    if(skinny_backward_eligible(B, I, O) && (!want_grads || (scratch && scratch_bytes >= skinny_backward_scratch_bytes(I, O, SKINNY_CTAS)))){
+        float* partial = want_grads ? reinterpret_cast<float*>(scratch) : nullptr;
+        int rc = skinny_backward_launch(W, x, ldx, pre, ldpre, d_out, ldd, partial, d_in, ldi, B, I, O, act, SKINNY_CTAS, s);
+        if(rc) return rc;
+        if(want_grads){
+            // records of O * I + O floats per CTA: one reduction when the bias gradient follows the weight gradient in memory (a flat arena)
+            const int n = O * I, record = n + O;
+            if(db == dW + n){
+                reduce_strided_partials_kernel<<<(record + 31) / 32, dim3(32, 8), 0, s>>>(dW, partial, record, record, SKINNY_CTAS);
+                B200RL_LAUNCH_CHECK("reduce_skinny");
+            }
+            else{
+                reduce_strided_partials_kernel<<<(n + 31) / 32, dim3(32, 8), 0, s>>>(dW, partial, n, record, SKINNY_CTAS);
+                B200RL_LAUNCH_CHECK("reduce_dW");
+                reduce_strided_partials_kernel<<<(O + 31) / 32, dim3(32, 8), 0, s>>>(db, partial + n, O, record, SKINNY_CTAS);
+                B200RL_LAUNCH_CHECK("reduce_bias");
+            }
+        }
+        return B200RL_OK;
+    }
+    BackwardPlan p = plan_backward(B, I, O, plan_budget);
     if(want_grads && p.bytes > 0 && (scratch == nullptr || scratch_bytes < p.bytes)) return B200RL_ERR_INVALID_ARGUMENT;
     float* w_partial = reinterpret_cast<float*>(scratch);
     float* b_partial = w_partial + (p.splits > 1 ? (size_t)p.splits * O * I : 0);
@@ -403,7 +443,7 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         }
     }
     if(want_grads && segs > 1){
-        reduce_bias_partials_kernel<<<(O + 31) / 32, dim3(32, 8), 0, sg>>>(db, b_partial, O, segs);
+        reduce_strided_partials_kernel<<<(O + 31) / 32, dim3(32, 8), 0, sg>>>(db, b_partial, O, O, segs);
         B200RL_LAUNCH_CHECK("reduce_bias");
     }
     if(want_grads){
@@ -498,8 +538,7 @@ int b200rl_dense_forward_ws(const float* W, const float* bias, const float* x, i
 
 size_t b200rl_dense_backward_scratch_bytes(int batch, int input_dim, int output_dim){
     if(batch < 1 || input_dim < 1 || output_dim < 1) return 0;
-    const BackwardPlan p = plan_backward(batch, input_dim, output_dim);
-    return p.bytes + p.wt_bytes;
+    return backward_scratch_total(batch, input_dim, output_dim);
 }
 
 int b200rl_dense_backward(const float* W, const float* x, int ldx, const float* pre, int ldpre, float* d_out, int ldd,
@@ -613,7 +652,7 @@ int b200rl_mlp_forward_ws(const b200rl_mlp_shape* sh, const float* params, const
 size_t b200rl_mlp_backward_scratch_bytes(const b200rl_mlp_shape* sh, int batch){
     if(!valid_shape(sh) || batch < 1) return 0;
     size_t m = 0; int I = sh->input_dim;
-    for(int l = 0; l < sh->n_layers; l++){ const BackwardPlan p = plan_backward(batch, I, sh->dims[l]); const size_t b = p.bytes + p.wt_bytes; if(b > m) m = b; I = sh->dims[l]; }
+    for(int l = 0; l < sh->n_layers; l++){ const size_t b = backward_scratch_total(batch, I, sh->dims[l]); if(b > m) m = b; I = sh->dims[l]; }
     const size_t fused = mlp_fused_backward_scratch_bytes(sh, batch);
     return fused > m ? fused : m;
 }

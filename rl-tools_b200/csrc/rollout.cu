@@ -165,12 +165,10 @@ extern "C" int b200rl_pendulum_collect_layers(const b200rl_mlp_shape* actor, con
 // replay buffer with the reference's bookkeeping (operations_generic_per_env.h:41-52, replay_buffer/operations_generic.h:54-79).
 // ---------------------------------------------------------------------------------------------------------------
 namespace b200rl {
+// appends one transition of environment e to its replay buffer; (next_theta, next_theta_dot) is the state after the step
 template <typename INDEX>
-__global__ void replay_add_kernel(int n_envs, const float* __restrict__ states, const uint8_t* __restrict__ truncated, const uint8_t* __restrict__ was_truncated,
-                                  const float* __restrict__ observations, const float* __restrict__ actions, const float* __restrict__ rewards,
-                                  float* __restrict__ next_observations, unsigned char* replay, b200rl_replay_layout L){
-    const int e = blockIdx.x * blockDim.x + threadIdx.x;
-    if(e >= n_envs) return;
+__device__ __forceinline__ void replay_append(int e, float next_theta, float next_theta_dot, bool trunc, bool was_truncated, const float* __restrict__ observations,
+                                              float action, float reward, float* __restrict__ next_observations, unsigned char* replay, const b200rl_replay_layout& L){
     unsigned char* rb = replay + (size_t)e * L.env_stride;
     float* data = reinterpret_cast<float*>(rb + L.off_data);
     INDEX* episode_start = reinterpret_cast<INDEX*>(rb + L.off_episode_start);
@@ -179,19 +177,17 @@ __global__ void replay_add_kernel(int n_envs, const float* __restrict__ states, 
     unsigned char& full_ref = *(rb + L.off_full);
     INDEX position = position_ref, ces = ces_ref;
     bool full = full_ref != 0;
-    if(was_truncated[e] && (full || position > 0)){            // prologue: the environment was reset at the start of this step
+    if(was_truncated && (full || position > 0)){               // prologue: the environment was reset at the start of this step
         const INDEX prev = position == 0 ? (INDEX)(L.capacity - 1) : position - 1;
         data[(size_t)prev * L.ld_data + 9] = 1.0f;
         ces = position;
     }
     float sn, cs;
-    const float next_theta = states[2 * e], next_theta_dot = states[2 * e + 1];
     sincosf(next_theta, &sn, &cs);
     next_observations[3 * e] = cs; next_observations[3 * e + 1] = sn; next_observations[3 * e + 2] = next_theta_dot;
-    const bool trunc = truncated[e] != 0;
     float* row = data + (size_t)position * L.ld_data;
     row[0] = observations[3 * e]; row[1] = observations[3 * e + 1]; row[2] = observations[3 * e + 2];
-    row[3] = actions[e]; row[4] = rewards[e];
+    row[3] = action; row[4] = reward;
     row[5] = cs; row[6] = sn; row[7] = next_theta_dot;
     row[8] = 0.0f; row[9] = trunc ? 1.0f : 0.0f;              // Pendulum never terminates
     episode_start[position] = ces;
@@ -199,6 +195,57 @@ __global__ void replay_add_kernel(int n_envs, const float* __restrict__ states, 
     if(trunc) ces = position;
     if(position == 0 && !full) full = true;
     position_ref = position; ces_ref = ces; full_ref = full ? 1 : 0;
+}
+
+template <typename INDEX>
+__global__ void replay_add_kernel(int n_envs, const float* __restrict__ states, const uint8_t* __restrict__ truncated, const uint8_t* __restrict__ was_truncated,
+                                  const float* __restrict__ observations, const float* __restrict__ actions, const float* __restrict__ rewards,
+                                  float* __restrict__ next_observations, unsigned char* replay, b200rl_replay_layout L){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= n_envs) return;
+    replay_append<INDEX>(e, states[2 * e], states[2 * e + 1], truncated[e] != 0, was_truncated[e] != 0, observations, actions[e], rewards[e], next_observations, replay, L);
+}
+
+// The runner step in two halves around ANY policy (how the reference's CUDA runner is built: prologue kernel, evaluate(policy), epilogue
+// kernel; rl/components/off_policy_runner/operations_cuda.h:184-204 around operations_generic_per_env.h:8-61 and :62-108).
+// Prologue: reset-if-truncated (from the table, or drawn in the kernel), counters of a fresh episode, observation.
+__global__ void offpolicy_prologue_kernel(int n_envs, float* __restrict__ states, int32_t* __restrict__ episode_step, const uint8_t* __restrict__ truncated,
+                                          float* __restrict__ episode_return, const float* __restrict__ reset_states, unsigned long long seed, unsigned long long call,
+                                          const unsigned long long* __restrict__ call_counter, float* __restrict__ observations, uint8_t* __restrict__ was_truncated){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= n_envs) return;
+    float theta = states[2 * e], theta_dot = states[2 * e + 1];
+    const bool trunc = truncated[e] != 0;
+    was_truncated[e] = trunc ? 1 : 0;
+    if(trunc){
+        if(reset_states){ theta = __ldg(reset_states + 2 * e); theta_dot = __ldg(reset_states + 2 * e + 1); }
+        else{           // theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) (rl/environments/pendulum/operations_generic.h:57-61), one Philox block per (environment, call)
+            const StepDraws d = step_draws(seed, call + (call_counter ? *call_counter : 0ull), (uint32_t)e);
+            theta = fmaf(d.u_theta, 2.0f * pendulum::PI_F, -pendulum::PI_F); theta_dot = fmaf(d.u_theta_dot, 2.0f, -1.0f);
+        }
+        states[2 * e] = theta; states[2 * e + 1] = theta_dot;
+        episode_step[e] = 0; episode_return[e] = 0.0f;
+    }
+    float sn, cs;
+    sincosf(theta, &sn, &cs);
+    observations[3 * e] = cs; observations[3 * e + 1] = sn; observations[3 * e + 2] = theta_dot;
+}
+// Epilogue: environment step with the given actions, reward, counters, truncation, next observation, replay-buffer append.
+template <typename INDEX>
+__global__ void offpolicy_epilogue_kernel(int n_envs, int step_limit, float* __restrict__ states, int32_t* __restrict__ episode_step, uint8_t* __restrict__ truncated,
+                                          float* __restrict__ episode_return, const float* __restrict__ observations, const float* __restrict__ actions,
+                                          float* __restrict__ next_observations, const uint8_t* __restrict__ was_truncated, unsigned char* replay, b200rl_replay_layout L){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= n_envs) return;
+    const float theta = states[2 * e], theta_dot = states[2 * e + 1], action = actions[e];
+    float nt, ntd;
+    pendulum::step(theta, theta_dot, observations[3 * e + 1], action, nt, ntd);          // the observation's second component is sin(theta)
+    const float rwd = pendulum::reward(theta, theta_dot, action);
+    const int es = episode_step[e] + 1;
+    const bool trunc = es == step_limit;
+    states[2 * e] = nt; states[2 * e + 1] = ntd;
+    episode_step[e] = es; episode_return[e] = __fadd_rn(episode_return[e], rwd); truncated[e] = trunc ? 1 : 0;
+    replay_append<INDEX>(e, nt, ntd, trunc, was_truncated[e] != 0, observations, action, rwd, next_observations, replay, L);
 }
 }  // namespace b200rl
 
@@ -239,6 +286,38 @@ extern "C" int b200rl_pendulum_offpolicy_step(const b200rl_mlp_shape* actor, con
         replay_add_kernel<unsigned long long><<<blocks, threads, 0, s>>>(n_envs, states, truncated, was_truncated_scratch, observations, actions, reward_scratch,
                                                                         next_observations, static_cast<unsigned char*>(replay_buffers), *layout);
     B200RL_LAUNCH_CHECK("replay_add");
+    return B200RL_OK;
+}
+
+extern "C" int b200rl_pendulum_offpolicy_prologue(float* states, int32_t* episode_step, const uint8_t* truncated, float* episode_return, const float* reset_states,
+                                                  unsigned long long seed, unsigned long long call, const unsigned long long* call_counter, int n_envs,
+                                                  float* observations, uint8_t* was_truncated_scratch, b200rl_stream_t stream){
+    if(!states || !episode_step || !truncated || !episode_return || !observations || !was_truncated_scratch || n_envs < 0) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0) return B200RL_OK;
+    const int threads = 128, blocks = (n_envs + threads - 1) / threads;
+    offpolicy_prologue_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(n_envs, states, episode_step, truncated, episode_return, reset_states, seed, call, call_counter,
+                                                                           observations, was_truncated_scratch);
+    B200RL_LAUNCH_CHECK("offpolicy_prologue");
+    return B200RL_OK;
+}
+
+extern "C" int b200rl_pendulum_offpolicy_epilogue(float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return, int n_envs, int step_limit,
+                                                  const float* observations, const float* actions, float* next_observations, void* replay_buffers,
+                                                  const b200rl_replay_layout* layout, const uint8_t* was_truncated_scratch, b200rl_stream_t stream){
+    if(!states || !episode_step || !truncated || !episode_return || !observations || !actions || !next_observations || !replay_buffers || !layout ||
+       !was_truncated_scratch || n_envs < 0 || step_limit < 1)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(layout->capacity < 1 || layout->ld_data < 10 || (layout->index_bytes != 4 && layout->index_bytes != 8)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0) return B200RL_OK;
+    const int threads = 128, blocks = (n_envs + threads - 1) / threads;
+    cudaStream_t s = (cudaStream_t)stream;
+    if(layout->index_bytes == 4)
+        offpolicy_epilogue_kernel<uint32_t><<<blocks, threads, 0, s>>>(n_envs, step_limit, states, episode_step, truncated, episode_return, observations, actions,
+                                                                      next_observations, was_truncated_scratch, static_cast<unsigned char*>(replay_buffers), *layout);
+    else
+        offpolicy_epilogue_kernel<unsigned long long><<<blocks, threads, 0, s>>>(n_envs, step_limit, states, episode_step, truncated, episode_return, observations, actions,
+                                                                                next_observations, was_truncated_scratch, static_cast<unsigned char*>(replay_buffers), *layout);
+    B200RL_LAUNCH_CHECK("offpolicy_epilogue");
     return B200RL_OK;
 }
 

@@ -68,3 +68,129 @@ class PendulumPpoLoop:
         exploration noise that the collected actions carry."""
         L = self.layout
         return float(self.dataset[:self.n_envs * self.steps_per_env, L.rewards].mean().item()) * self.step_limit
+
+
+class PendulumSacLoop:
+    """sac::loop::core::State for rl::environments::Pendulum (rl/algorithms/sac/loop/core: config.h:19-49 parameters, operations_generic.h:71-87
+    init, :110-152 step) with the configuration of the reference's Pendulum example (src/rl/environments/pendulum/sac/cpu/training.h:44-54):
+    one environment, actor 3 -> 64 -> 64 -> 2 with the sample-and-squash head, two critics 4 -> 64 -> 64 -> 1, batch 100, replay capacity =
+    step limit = 10,000, 100 warm-up steps with uniformly random actions, every interval 1, shared batch.
+
+    One `step()` = the runner step in two halves around the stochastic actor (prologue: reset / observe; actor evaluate; head sample;
+    epilogue: environment step, reward, replay append), then -- past the warm-up -- gather_batch, the three noise tensors, train_critic x 2,
+    update_critic_targets, train_actor (incl. log_alpha). Past the warm-up the whole step is ONE CUDA-graph replay: every random draw inside it
+    (reset states, exploration noise, batch indices, update noise) comes from the counter-based generator keyed by a device-resident step counter
+    that the graph's last node advances, so nothing returns to the host between steps."""
+
+    def __init__(self, n_envs=1, batch_size=100, hidden_dim=64, step_limit=10000, n_warmup_steps=100, episode_step_limit=200, replay_capacity=None, seed=0,
+                 use_graph=True, device="cuda"):
+        import torch
+        from . import sac, ReplayLayout, new_batch
+        assert n_warmup_steps * n_envs >= batch_size, "config.h:25"
+        self.n_envs, self.batch_size, self.step_limit, self.n_warmup_steps, self.episode_step_limit = n_envs, batch_size, step_limit, n_warmup_steps, episode_step_limit
+        self.seed, self.step_index, self.use_graph, self.device = seed, 0, use_graph, device
+        self.agent = sac.ActorCritic(3, 1, hidden_dim, batch_size, device=device)
+        self.hidden_dim = hidden_dim
+        # init(device, actor_critic, rng) (rl/algorithms/sac/operations_generic.h:112-131): init_weights of the actor and the two critics on one engine
+        self.rng = rng_init_host(seed)
+        for net, fan_in0, out in ((self.agent.actor, 3, 2), (self.agent.critics[0], 4, 1), (self.agent.critics[1], 4, 1)):
+            off, fan_in = 0, fan_in0
+            for d in (hidden_dim, hidden_dim, out):
+                dense_init_weights(self.rng, net.params[off:off + d * fan_in].view(d, fan_in), net.params[off + d * fan_in:off + d * fan_in + d])
+                off += d * fan_in + d; fan_in = d
+            net.zero_gradient(); net.reset_optimizer_state()
+        self.agent.copy_critics_to_targets()
+        z = lambda *s, dtype=torch.float32: torch.zeros(*s, device=device, dtype=dtype)
+        # init(device, off_policy_runner): every environment starts truncated (reset by the first step), empty replay buffers
+        N = n_envs
+        self.layout = ReplayLayout.packed(step_limit if replay_capacity is None else replay_capacity)
+        self.replay = z(N * self.layout.env_stride, dtype=torch.uint8)
+        self.states, self.episode_step, self.episode_return = z(N, 2), z(N, dtype=torch.int32), z(N)
+        self.truncated, self.was_truncated = torch.ones(N, device=device, dtype=torch.uint8), z(N, dtype=torch.uint8)
+        self.observations, self.actions, self.next_observations = z(N, 3), z(N, 1), z(N, 3)
+        self.head_input, self.explore_noise = z(N, 2), z(N, 1)
+        self.explore_pre, self.explore_log_prob = z(N, 1), z(N)
+        self.batch, self.update_noise = new_batch(batch_size, device=device), z(3, batch_size, 1)
+        self.counter = z(1, dtype=torch.int64)                      # the loop's step index on the device
+        self.error_flag = z(1, dtype=torch.int32)
+        self.graph = None
+
+    # ---- the two halves of the runner step -------------------------------------------------------------------------------------------
+    def _prologue(self):
+        from . import pendulum_offpolicy_prologue
+        pendulum_offpolicy_prologue(self.states, self.episode_step, self.truncated, self.episode_return, self.observations, self.was_truncated, seed=self.seed,
+                                    call_counter=self.counter)
+
+    def _epilogue(self):
+        from . import pendulum_offpolicy_epilogue
+        pendulum_offpolicy_epilogue(self.states, self.episode_step, self.truncated, self.episode_return, self.episode_step_limit, self.observations, self.actions,
+                                    self.next_observations, self.replay, self.layout, self.was_truncated)
+
+    def _warmup_step(self):
+        """step<0> with the uniform random exploration policy (operations_generic.h:117-121)."""
+        import torch
+        from . import counter_advance
+        self._prologue()
+        self.actions.copy_(torch.rand_like(self.actions) * 2 - 1)
+        self._epilogue()
+        counter_advance(self.counter, 1)
+
+    def _train_step(self):
+        """step<1> with the actor, then the update (operations_generic.h:114-148), all draws keyed by the device-resident step counter."""
+        from . import sample_and_squash_forward, randn_device_rng, gather_batch, counter_advance
+        a = self.agent
+        self._prologue()
+        a.actor.evaluate(self.observations, y=self.head_input)
+        randn_device_rng(self.explore_noise, self.seed, stream_id=2, call_counter=self.counter)
+        sample_and_squash_forward(self.head_input, self.explore_noise, output=self.actions, pre_squashing=self.explore_pre, log_probs=self.explore_log_prob)
+        self._epilogue()
+        gather_batch(self.replay, self.layout, self.n_envs, self.batch, seed=self.seed, call_counter=self.counter, max_episode_length=self.episode_step_limit,
+                     error_flag=self.error_flag)
+        randn_device_rng(self.update_noise, self.seed, stream_id=1, call_counter=self.counter)
+        a.update(self.batch, self.update_noise[0], self.update_noise[1], self.update_noise[2])
+        counter_advance(self.counter, 1)
+
+    def step(self):
+        """One loop step; returns True once the step limit is reached (operations_generic.h:111-113)."""
+        import torch
+        if self.step_index >= self.step_limit:
+            return True
+        if self.step_index < self.n_warmup_steps:
+            self._warmup_step()
+        elif not self.use_graph:
+            self._train_step()
+        else:
+            if self.graph is None:
+                side = torch.cuda.Stream(device=self.device)
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    self._train_step()                             # this loop step, eagerly (also warms every kernel up before the capture)
+                torch.cuda.current_stream().wait_stream(side)
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, stream=side):
+                    self._train_step()
+            else:
+                self.graph.replay()
+        self.step_index += 1
+        return False
+
+    def evaluation_actor(self):
+        """The deterministic evaluation policy (the head in evaluation mode: action = tanh(mean)) as a 3 -> H -> H -> 1 actor with tanh output:
+        the mean row of the actor's output layer. Returns (shape, parameter arena)."""
+        import torch
+        H = self.hidden_dim
+        p = self.agent.actor.params
+        body = H * 3 + H + H * H + H
+        arena = torch.cat([p[:body], p[body:body + H], p[body + 2 * H:body + 2 * H + 1]])
+        return MlpShape.make(3, [H, H, 1], ["relu", "relu", "tanh"]), arena
+
+    def evaluate(self, n_episodes=100, seed=12345):
+        """Mean return of n_episodes evaluation episodes (one fused rollout launch of n_episodes environments x the episode step limit)."""
+        import torch
+        from . import pendulum_rollout_device_rng
+        shape, arena = self.evaluation_actor()
+        z = lambda *s, dtype=torch.float32: torch.zeros(*s, device=self.device, dtype=dtype)
+        st, es, er = z(n_episodes, 2), z(n_episodes, dtype=torch.int32), z(n_episodes)
+        tr = torch.ones(n_episodes, device=self.device, dtype=torch.uint8)
+        _, _, rew = pendulum_rollout_device_rng(shape, arena, st, es, tr, er, seed, 0, self.episode_step_limit, self.episode_step_limit)
+        return float(rew.view(self.episode_step_limit, n_episodes).sum(0).mean().item())

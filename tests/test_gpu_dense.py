@@ -39,6 +39,8 @@ SHAPES = [  # (batch, in, out, act): the reference's CUDA test sweep plus awkwar
     (2048, 27, 64, "tanh"), (300, 64, 8, "identity"), (4099, 65, 17, "relu"), (256, 4, 256, "relu"), (256, 256, 1, "identity"),
     # >= 2^27 multiply-adds: these take the tensor-core kernel (ragged rows, ragged k, narrow and non-multiple-of-8 columns)
     (4099, 256, 200, "relu"), (8192, 130, 257, "tanh"), (70001, 64, 40, "relu"), (16384, 256, 256, "relu"),
+    # few outputs at a large batch: the backward pass takes the one-pass kernel (ragged rows, one and two columns per thread, every output count class)
+    (8192, 256, 16, "identity"), (10007, 200, 5, "tanh"), (9001, 100, 1, "relu"), (33000, 256, 16, "sigmoid"),
 ]
 
 
@@ -96,6 +98,20 @@ def test_backward_input_only(lib, orc, torch):
     _, _, din_ref, _ = orc.dense_backward(W, x, pre, d_out, "relu", want_grads=False)
     _, _, d_in = lib.dense_backward(dev(torch, W), dev(torch, x), dev(torch, pre), dev(torch, d_out), "relu", want_grads=False)
     close(d_in, din_ref)
+
+
+def test_backward_input_only_few_outputs_large_batch(lib, orc, torch):
+    """backward_input of a last layer (few outputs, large batch: the one-pass kernel without its gradient half)."""
+    B, I, O = 9003, 256, 4
+    W = mg.det_uniform(6, O * I).reshape(O, I)
+    x = mg.det_normal(6, B * I, stream=1).reshape(B, I)
+    pre = mg.det_normal(6, B * O, stream=2).reshape(B, O)
+    d_out = mg.det_normal(6, B * O, stream=3).reshape(B, O)
+    _, _, din_ref, dpre_ref = orc.dense_backward(W, x, pre, d_out, "tanh", want_grads=False)
+    d_out_dev = dev(torch, d_out)
+    _, _, d_in = lib.dense_backward(dev(torch, W), dev(torch, x), dev(torch, pre), d_out_dev, "tanh", want_grads=False)
+    close(d_in, din_ref)
+    close(d_out_dev, dpre_ref)
 
 
 def test_mse_gradient(lib, orc, torch):

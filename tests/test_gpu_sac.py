@@ -244,3 +244,74 @@ def test_off_policy_training_step_end_to_end_as_one_graph(lib, torch):
     assert bool(torch.isfinite(agent.log_alpha).all())
     for c in range(2):
         assert not torch.equal(agent.critics[c].params, before[c])
+
+
+def test_runner_step_in_two_halves_equals_the_fused_step(lib, torch):
+    """prologue + (the fused step's own actions) + epilogue leaves the runner state and the replay buffers bit for bit as
+    b200rl_pendulum_offpolicy_step does (which the reference fixture pins): 25 steps over an episode limit of 10, i.e. with resets from
+    the table, truncation marks and the episode-start bookkeeping."""
+    N, cap, limit = 48, 16, 10
+    rs = np.random.RandomState(11)
+    shape = lib.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    policy = dev(torch, (rs.uniform(-1, 1, 4481) * 0.3).astype(np.float32))
+    L = lib.ReplayLayout.packed(cap)
+
+    def fresh():
+        return dict(replay=torch.zeros(N * L.env_stride, dtype=torch.uint8, device="cuda"), states=torch.zeros((N, 2), device="cuda"),
+                    es=torch.zeros(N, dtype=torch.int32, device="cuda"), tr=torch.ones(N, dtype=torch.uint8, device="cuda"), er=torch.zeros(N, device="cuda"),
+                    obs=torch.zeros((N, 3), device="cuda"), act=torch.zeros((N, 1), device="cuda"), nobs=torch.zeros((N, 3), device="cuda"))
+    a, b = fresh(), fresh()
+    was = torch.zeros(N, dtype=torch.uint8, device="cuda")
+    for step in range(25):
+        table = dev(torch, np.stack([rs.uniform(-np.pi, np.pi, N), rs.uniform(-1, 1, N)], 1).astype(np.float32).reshape(1, N, 2))
+        lib.pendulum_offpolicy_step(shape, policy, a["states"], a["es"], a["tr"], a["er"], table, limit, a["obs"], a["act"], a["nobs"], a["replay"], L)
+        lib.pendulum_offpolicy_prologue(b["states"], b["es"], b["tr"], b["er"], b["obs"], was, reset_states=table[0])
+        assert torch.equal(b["obs"], a["obs"])
+        lib.pendulum_offpolicy_epilogue(b["states"], b["es"], b["tr"], b["er"], limit, b["obs"], a["act"], b["nobs"], b["replay"], L, was)
+        for k in ("states", "es", "tr", "er", "nobs", "replay"):
+            assert torch.equal(a[k], b[k]), (step, k)
+    position, full = lib.replay_counters(b["replay"], L, N)
+    assert bool((position == 25 % cap).all()) and bool(full.all())
+
+
+def test_prologue_draws_initial_states_on_the_device(lib, torch):
+    """Without a table the prologue draws theta ~ U(-pi, pi), theta_dot ~ U(-1, 1) per (environment, call): inside the bounds, different per
+    environment and per call, reproducible, and only for the truncated environments."""
+    N = 4096
+    st = torch.full((N, 2), 9.0, device="cuda")
+    es, er = torch.full((N,), 5, dtype=torch.int32, device="cuda"), torch.ones(N, device="cuda")
+    tr = torch.ones(N, dtype=torch.uint8, device="cuda"); tr[::2] = 0
+    obs, was = torch.zeros((N, 3), device="cuda"), torch.zeros(N, dtype=torch.uint8, device="cuda")
+    counter = torch.full((1,), 3, dtype=torch.int64, device="cuda")
+    lib.pendulum_offpolicy_prologue(st, es, tr, er, obs, was, seed=5, call_counter=counter)
+    s = st.cpu().numpy()
+    assert np.all(s[::2] == 9.0) and np.all(es.cpu().numpy()[::2] == 5) and np.all(er.cpu().numpy()[::2] == 1.0)
+    drawn = s[1::2]
+    assert np.all(np.abs(drawn[:, 0]) <= np.pi) and np.all(np.abs(drawn[:, 1]) <= 1.0) and len(np.unique(drawn[:, 0])) > 2000
+    assert abs(drawn[:, 0].mean()) < 0.15 and abs(drawn[:, 1].mean()) < 0.05
+    assert np.all(es.cpu().numpy()[1::2] == 0) and np.all(er.cpu().numpy()[1::2] == 0.0) and torch.equal(was, tr)
+    close(obs.cpu().numpy(), np.stack([np.cos(s[:, 0].astype(np.float64)), np.sin(s[:, 0].astype(np.float64)), s[:, 1]], 1), what="observation")
+    st2 = torch.full((N, 2), 9.0, device="cuda")
+    lib.pendulum_offpolicy_prologue(st2, es, tr, er, obs, was, seed=5, call_index=3)              # the same call index given on the host
+    assert torch.equal(st2, st)
+    lib.pendulum_offpolicy_prologue(st2, es, tr, er, obs, was, seed=5, call_index=4)
+    assert not torch.equal(st2[1::2], st[1::2])
+
+
+def test_sac_loop_learns_the_pendulum(lib, torch):
+    """The off-policy training loop with the reference example's configuration (one environment, 64-wide networks, batch 100, 10,000 steps):
+    the deterministic evaluation policy goes from a random policy's return (below -900) to swinging up (above -400; the reference's
+    example reports about -200 to -150 after the same number of steps)."""
+    from rl_tools_b200.loops import PendulumSacLoop
+    torch.manual_seed(0)
+    loop = PendulumSacLoop(seed=0)
+    before = loop.evaluate()
+    while not loop.step():
+        pass
+    torch.cuda.synchronize()
+    assert int(loop.error_flag.item()) == 0 and int(loop.counter.item()) == 10000
+    after = loop.evaluate()
+    print(f"SAC Pendulum: evaluation return {before:.0f} -> {after:.0f}, alpha {float(loop.agent.log_alpha.exp().item()):.3f}")
+    assert before < -900 and after > -400, (before, after)
+    for net in [loop.agent.actor] + loop.agent.critics + loop.agent.critics_target:
+        assert bool(torch.isfinite(net.params).all())

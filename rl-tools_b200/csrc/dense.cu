@@ -464,8 +464,15 @@ static int dense_backward_impl(const float* W, const float* x, int ldx, const fl
         }
         if(p.splits > 1){
             long long n = (long long)O * I;
-            int blocks = (int)((n + 255) / 256); if(blocks > 4 * NUM_SMS) blocks = 4 * NUM_SMS;
-            reduce_partials_kernel<<<blocks, 256, 0, sg>>>(dW, w_partial, n, p.splits);
+            if(p.splits >= 16 && n < (1ll << 30)){
+                // many partial sums per element: eight lanes share an element's splits (a fixed order again: lane y takes y, y + 8, ...,
+                // then the lanes ascending), so a thread's chain is splits / 8 loads long (74 splits of 256 x 256: 12.5 -> 8 us)
+                reduce_strided_partials_kernel<<<(unsigned)((n + 31) / 32), dim3(32, 8), 0, sg>>>(dW, w_partial, (int)n, n, p.splits);
+            }
+            else{
+                int blocks = (int)((n + 255) / 256); if(blocks > 4 * NUM_SMS) blocks = 4 * NUM_SMS;
+                reduce_partials_kernel<<<blocks, 256, 0, sg>>>(dW, w_partial, n, p.splits);
+            }
             B200RL_LAUNCH_CHECK("reduce_dW");
         }
     }

@@ -13,12 +13,6 @@
 // Determinism: a CTA owns a fixed range of rows and sums them in ascending order (two row lanes, combined lane 0 + lane 1); the per-CTA
 // partial sums are added by the fixed-order reduction kernels of dense.cu.
 #include "common.cuh"
-#ifndef B200RL_SF_PREFETCH
-#define B200RL_SF_PREFETCH 0
-#endif
-#ifndef B200RL_SK_MIN_CTAS
-#define B200RL_SK_MIN_CTAS 2
-#endif
 
 namespace b200rl {
 
@@ -33,7 +27,7 @@ constexpr int SK_THREADS = 256, SK_COLS = 128, SK_LANES = 2, SK_BLOCK_ROWS = 32,
 // warps drift apart: some wait on their loads while others compute. The write-back of d_pre over d_out and the bias sums follow in a
 // second, short phase after a barrier.
 template <int ACT, int CPT, bool WANT_GRADS, bool WANT_DIN>
-__global__ void __launch_bounds__(SK_THREADS, B200RL_SK_MIN_CTAS) skinny_backward_kernel(const float* __restrict__ W, const float* __restrict__ x, long long ldx, const float* __restrict__ pre,
+__global__ void __launch_bounds__(SK_THREADS, 2) skinny_backward_kernel(const float* __restrict__ W, const float* __restrict__ x, long long ldx, const float* __restrict__ pre,
                                                                      long long ldpre, float* d_out, long long ldd, float* __restrict__ w_partial, float* __restrict__ b_partial,
                                                                      float* __restrict__ d_in, long long ldi, int B, int I, int O, int rows_per_cta, long long partial_stride){
     __shared__ __align__(16) float dp[SK_THREADS / 32][SK_INFLIGHT][SK_OT];     // per warp: d_pre of its eight rows in flight
@@ -226,22 +220,10 @@ __global__ void __launch_bounds__(SF_THREADS) skinny_forward_kernel(const float*
             }
     };
     const int g_step = gridDim.x * (SF_THREADS / 32);
-#if B200RL_SF_PREFETCH
-    float4 xn[SF_ROWS][NCH];
-    load_rows(blockIdx.x * (SF_THREADS / 32) + warp, xn);
-#endif
     for(int g = blockIdx.x * (SF_THREADS / 32) + warp; g < groups; g += g_step){
         const int row0 = g * SF_ROWS;
         float4 xv[SF_ROWS][NCH];
-#if B200RL_SF_PREFETCH
-#pragma unroll
-        for(int r = 0; r < SF_ROWS; r++)
-#pragma unroll
-            for(int ch = 0; ch < NCH; ch++) xv[r][ch] = xn[r][ch];
-        load_rows(g + g_step, xn);                   // the next pass's rows, in flight during this pass's arithmetic (rows past the batch read as zeros)
-#else
         load_rows(g, xv);
-#endif
         float v[SF_ROWS * SK_OT];
 #pragma unroll
         for(int i = 0; i < SF_ROWS * SK_OT; i++) v[i] = 0.0f;

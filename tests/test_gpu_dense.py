@@ -219,6 +219,38 @@ def test_sharded_train_step_matches_oracle_full_batch(lib, orc, torch):
     close(net.params, p_ref)
 
 
+@pytest.mark.parametrize("hidden_act,out_dim", [("tanh", 8), ("sigmoid", 40)])
+def test_mlp_backward_large_batch_against_the_oracle(lib, orc, torch, hidden_act, out_dim):
+    """The whole backward pass at a large batch -- the tensor-core products for the wide layers, the one-pass kernel for an output layer of
+    <= 16 units (out_dim 8) or the tiled path for a wider one (out_dim 40) -- against the oracle's per-layer recursion: parameter gradients on
+    top of existing values and the input gradient, for activations whose derivative is not 0 / 1, ragged rows and a ragged width; also the
+    input-gradient-only pass (no parameter gradients)."""
+    B, I, dims = 9001, 40, [256, 200, out_dim]
+    acts = [hidden_act, hidden_act, "identity"]
+    shape = oracle.MlpShape.make(I, dims, acts)
+    params = mg.det_uniform(77, shape.num_params()) * np.float32(0.08)
+    x = mg.det_normal(78, B * I).reshape(B, I)
+    d_out = mg.det_normal(79, B * out_dim).reshape(B, out_dim) / np.float32(B)
+    g0 = mg.det_normal(80, shape.num_params()) * np.float32(0.01)
+    pre, out = orc.mlp_forward(shape, params, x)
+    g_ref, din_ref = orc.mlp_backward(shape, params, g0, x, pre, out, d_out, want_d_input=True)
+    net = lib.Mlp(I, dims, acts, B)
+    net.params.copy_(dev(torch, params)); net.grads.copy_(dev(torch, g0))
+    xd = dev(torch, x)
+    net.forward(xd)
+    close(net.pre, pre); close(net.out, out)
+    d_in = torch.empty((B, I), device="cuda")
+    net.backward(xd, dev(torch, d_out), d_input=d_in)
+    # sums of B products of magnitude ~|d_out| * |activation|: the tolerance scales with the summed magnitudes (here <= ~1e-3 per entry)
+    g = net.grads.cpu().numpy()
+    assert np.all(np.abs(g - g_ref) <= 1e-6 + 1e-5 * np.maximum(np.abs(g_ref), 1e-2)), float(np.abs(g - g_ref).max())
+    close(d_in, din_ref, rtol=1e-5, atol=1e-8)
+    d_in_only = torch.empty((B, I), device="cuda")
+    net.grads.fill_(0.25)
+    net.backward(xd, dev(torch, d_out), d_input=d_in_only, accumulate_gradients=False)
+    assert bool((net.grads == 0.25).all()) and torch.equal(d_in_only, d_in)
+
+
 def test_mlp_backward_without_parameter_gradients(lib, torch):
     """grads = NULL is the reference's backward_input: the same input gradient as the full backward pass, parameter gradients untouched."""
     rs = np.random.RandomState(3)

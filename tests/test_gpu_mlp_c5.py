@@ -1,7 +1,8 @@
 """Whole-network parity of the sharded training configuration (64 -> 256 -> 256 -> 256 -> 16, ReLU, identity) at the chunk size the
 benchmark runs: 65,536 rows per chunk, two chunks accumulated into one gradient, one Adam step -- the sequence of
-rl_tools_b200.parallel.sharded_train_step. At this size every contraction takes the tensor-core kernel (forward, input gradient on the
-transposed weights, split-batch weight gradient, the transposed weight gradient of the 16-wide layer).
+rl_tools_b200.parallel.sharded_train_step. At this size the 256-wide contractions take the tensor-core kernel (forward, input gradient on the
+transposed weights, split-batch weight gradient) and the 16-wide output layer the one-pass kernels for few outputs (forward; d_pre, both
+gradients and the input gradient in one pass).
 
 Checked against the fixture written from the real reference's zero_gradient / forward / mse::gradient / backward / step
 (tests/golden/c5_chunked_b65536.npz, make_golden.py `c5`):

@@ -8,7 +8,9 @@
 // writes the reference's struct layout in place (byte offsets taken from the struct type on the host). Reset draws are made on the host
 // with the reference's own sample_initial_state on the caller's engine, in environment order, like the reference's CPU runner.
 //
-// Supported: rl::environments::Pendulum, symmetric observations, policy = sequential< mlp 3 -> 64 -> 64 -> 1 > or that mlp itself, fp32.
+// Supported: rl::environments::Pendulum, symmetric observations, fp32. The policy sequential< mlp 3 -> 64 -> 64 -> 1 > (or that mlp itself)
+// takes the fused kernel; ANY other policy that evaluates on this device runs as the reference's CUDA runner does -- prologue kernel, the
+// reference's own interlude (evaluate_step of the policy on the runner's observation / action buffers), epilogue kernel.
 // gather_batch is provided for SequentialBatch with sequence length 1. Not provided: longer sequences, episode statistics. The view members
 // inside the device-resident replay-buffer structs are not initialised: only the data matrix, episode_start and the position / full /
 // current_episode_start counters are maintained, and the kernels address rows through byte offsets.
@@ -39,6 +41,18 @@ namespace rl_tools{
             L.index_bytes = (int)sizeof(typename SPEC::TI);
             return L;
         }
+        // whether a policy is the shape the fused runner kernel takes (overloads on the forward base classes, so that every capability of a
+        // model matches; anything else falls to the last overload)
+        template <typename MLP_SPEC>
+        constexpr bool fused_actor(const nn_models::mlp::NeuralNetworkForward<MLP_SPEC>*){
+            return MLP_SPEC::INPUT_DIM == 3 && MLP_SPEC::CONFIG::HIDDEN_DIM == 64 && MLP_SPEC::CONFIG::NUM_LAYERS == 3 && MLP_SPEC::CONFIG::OUTPUT_DIM == 1;
+        }
+        template <typename MODULE_SPEC>
+        constexpr bool fused_actor(const nn_models::sequential::ModuleForward<MODULE_SPEC>*){
+            using CONTENT = decltype(nn_models::sequential::ModuleForward<MODULE_SPEC>::content);
+            return utils::typing::is_same_v<typename MODULE_SPEC::NEXT_MODULE, nn_models::sequential::OutputModule> && fused_actor(static_cast<const CONTENT*>(nullptr));
+        }
+        constexpr bool fused_actor(const void*){ return false; }
         // the six parameter tensors of a 3-layer MLP, for a bare mlp or a one-module sequential model around it
         template <typename MLP_SPEC>
         void actor_layers(nn_models::mlp::NeuralNetworkForward<MLP_SPEC>& mlp, const float* (&layers)[6], int (&acts)[3]){
@@ -89,7 +103,7 @@ namespace rl_tools{
     }
     // rl/components/off_policy_runner/operations_cuda.h:184-204
     template<auto POLICY_INDEX, typename DEV_SPEC, typename SPEC, typename POLICY, typename POLICY_BUFFERS, typename RNG>
-    void step(devices::B200<DEV_SPEC>& device, rl::components::OffPolicyRunner<SPEC>& runner, POLICY& policy, POLICY_BUFFERS&, RNG& rng){
+    void step(devices::B200<DEV_SPEC>& device, rl::components::OffPolicyRunner<SPEC>& runner, POLICY& policy, POLICY_BUFFERS& policy_eval_buffers, RNG& rng){
         using RUNNER = rl::components::OffPolicyRunner<SPEC>;
         using ENVIRONMENT = typename SPEC::ENVIRONMENT;
         using T = typename SPEC::TYPE_POLICY::DEFAULT;
@@ -122,18 +136,32 @@ namespace rl_tools{
         int flag = 0;
         b200::note(device, b200rl_memcpy(sc, reset_states.data(), RESET_BYTES, 0, device.stream));
         b200::note(device, b200rl_memcpy(sc + FLAG_OFFSET, &flag, sizeof(int), 0, device.stream));
-        const float* layers[6]; int acts[3];
-        b200::actor_layers(policy, layers, acts);
-        b200rl_mlp_shape shape{};
-        shape.n_layers = 3; shape.input_dim = 3; shape.dims[0] = 64; shape.dims[1] = 64; shape.dims[2] = 1;
-        for(int l = 0; l < 3; l++) shape.acts[l] = acts[l];
         static const b200rl_replay_layout layout = b200::replay_layout<SPEC>();
         static_assert(decltype(runner.buffers.observations)::SPEC::COLS == 3 && decltype(runner.buffers.actions)::SPEC::COLS == 1);
-        b200::note(device, b200rl_pendulum_offpolicy_step(&shape, nullptr, layers, reinterpret_cast<float*>(runner.states._data), reinterpret_cast<int32_t*>(runner.episode_step._data),
-                                                          reinterpret_cast<uint8_t*>(runner.truncated._data), runner.episode_return._data, reinterpret_cast<const float*>(sc), (int)N,
-                                                          (int)SPEC::PARAMETERS::EPISODE_STEP_LIMIT, runner.buffers.observations._data, runner.buffers.actions._data,
-                                                          runner.buffers.next_observations._data, runner.replay_buffers._data, &layout, reinterpret_cast<float*>(sc + RESET_BYTES),
-                                                          reinterpret_cast<uint8_t*>(sc + RESET_BYTES + REWARD_BYTES), reinterpret_cast<int*>(sc + FLAG_OFFSET), device.stream));
+        if constexpr(b200::fused_actor(static_cast<const POLICY*>(nullptr))){
+            const float* layers[6]; int acts[3];
+            b200::actor_layers(policy, layers, acts);
+            b200rl_mlp_shape shape{};
+            shape.n_layers = 3; shape.input_dim = 3; shape.dims[0] = 64; shape.dims[1] = 64; shape.dims[2] = 1;
+            for(int l = 0; l < 3; l++) shape.acts[l] = acts[l];
+            b200::note(device, b200rl_pendulum_offpolicy_step(&shape, nullptr, layers, reinterpret_cast<float*>(runner.states._data), reinterpret_cast<int32_t*>(runner.episode_step._data),
+                                                              reinterpret_cast<uint8_t*>(runner.truncated._data), runner.episode_return._data, reinterpret_cast<const float*>(sc), (int)N,
+                                                              (int)SPEC::PARAMETERS::EPISODE_STEP_LIMIT, runner.buffers.observations._data, runner.buffers.actions._data,
+                                                              runner.buffers.next_observations._data, runner.replay_buffers._data, &layout, reinterpret_cast<float*>(sc + RESET_BYTES),
+                                                              reinterpret_cast<uint8_t*>(sc + RESET_BYTES + REWARD_BYTES), reinterpret_cast<int*>(sc + FLAG_OFFSET), device.stream));
+        }
+        else{
+            // any other policy: the reference's three phases (operations_cuda.h:199-201) with the runner's buffers in device memory
+            uint8_t* was_truncated = reinterpret_cast<uint8_t*>(sc + RESET_BYTES + REWARD_BYTES);
+            b200::note(device, b200rl_pendulum_offpolicy_prologue(reinterpret_cast<float*>(runner.states._data), reinterpret_cast<int32_t*>(runner.episode_step._data),
+                                                                  reinterpret_cast<const uint8_t*>(runner.truncated._data), runner.episode_return._data, reinterpret_cast<const float*>(sc), 0, 0,
+                                                                  nullptr, (int)N, runner.buffers.observations._data, was_truncated, device.stream));
+            rl::components::off_policy_runner::interlude<POLICY_INDEX>(device, runner, policy, policy_eval_buffers, rng);
+            b200::note(device, b200rl_pendulum_offpolicy_epilogue(reinterpret_cast<float*>(runner.states._data), reinterpret_cast<int32_t*>(runner.episode_step._data),
+                                                                  reinterpret_cast<uint8_t*>(runner.truncated._data), runner.episode_return._data, (int)N,
+                                                                  (int)SPEC::PARAMETERS::EPISODE_STEP_LIMIT, runner.buffers.observations._data, runner.buffers.actions._data,
+                                                                  runner.buffers.next_observations._data, runner.replay_buffers._data, &layout, was_truncated, device.stream));
+        }
         b200::note(device, b200rl_memcpy(&flag, sc + FLAG_OFFSET, sizeof(int), 1, device.stream));
         if(flag != 0) b200::note(device, B200RL_ERR_DEVICE_FLAG);
         runner.previous_policy = POLICY_INDEX;

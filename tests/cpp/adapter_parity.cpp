@@ -263,10 +263,12 @@ struct OffPolicyParityParameters: rlt::rl::components::off_policy_runner::Parame
     static constexpr TI REPLAY_BUFFER_CAPACITY = T_CAPACITY;
     static constexpr TI EPISODE_STEP_LIMIT = T_LIMIT;
 };
-template <TI N, TI CAPACITY, TI LIMIT, int STEPS>
+// HIDDEN = 64 takes the fused runner kernel; any other width takes the reference's three phases (prologue kernel, the reference's own
+// interlude with the policy's evaluate on the device tag, epilogue kernel).
+template <TI N, TI CAPACITY, TI LIMIT, int STEPS, TI HIDDEN = 64>
 void offpolicy_parity(const char* name){
     using PENDULUM = rlt::rl::environments::Pendulum<rlt::rl::environments::pendulum::Specification<T, TI, rlt::rl::environments::pendulum::DefaultParameters<T>>>;
-    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, HIDDEN, act::RELU, act::TANH>;
     using ACTOR = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<ACTOR_CONFIG>>, rlt::tensor::Shape<TI, 1, N, 3>>;
     using POLICIES = rlt::utils::Tuple<TI, ACTOR>;
     using SPEC = rlt::rl::components::off_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, POLICIES, OffPolicyParityParameters<N, CAPACITY, LIMIT>>;
@@ -639,6 +641,7 @@ int main(){
     offpolicy_parity<8, 64, 50, 137>("off_policy_runner_step");
     offpolicy_parity<33, 40, 17, 90>("off_policy_runner_wraps");
     offpolicy_parity<5, 300, 60, 47>("off_policy_runner_part_full");
+    offpolicy_parity<9, 48, 20, 70, 32>("off_policy_runner_generic_policy");
     polyak_parity("polyak_target_update");
     normalizer_parity("observation_normalisation");
     ppo_parity<64, 64, 512, 2>("ppo_train_shuffled");

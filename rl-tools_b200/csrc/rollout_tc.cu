@@ -89,6 +89,17 @@ __device__ __forceinline__ void split_f16_pair(float a, float b, uint32_t& lead,
     rest = pack_f16x2_sat(d.x, d.y);
 }
 
+// The same split of relu(a), relu(b) with the ReLU folded into the conversions (no separate maximum per unit): the leading part is
+// converted with round-toward-zero and the conversion's own ReLU, so for x >= 0 the remainder x - lead is >= 0 and the second conversion's
+// ReLU leaves it alone, while for x < 0 the leading part is 0, the remainder is x itself and the second ReLU zeroes it. Truncation makes the
+// remainder up to twice as large as with round-to-nearest: lead + rest carries ~21 bits instead of ~22 (relative 2^-21 = 4.8e-7 worst case).
+__device__ __forceinline__ void split_f16_pair_relu(float a, float b, uint32_t& lead, uint32_t& rest){
+    asm("cvt.rz.relu.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(lead) : "f"(b), "f"(a));
+    const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&lead));
+    const float2 d = __ffma2_rn(back, make_float2(-1.0f, -1.0f), make_float2(a, b));
+    asm("cvt.rn.relu.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(rest) : "f"(d.y), "f"(d.x));
+}
+
 template <int ACT>
 __device__ __forceinline__ float act_or_rt(float x, int rt){
     if constexpr(ACT >= 0) return activation<ACT>(x);
@@ -284,9 +295,11 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                         float acc = c_actor[C_B1 + j];                                       // bias first, inputs ascending: the reference's order
 #pragma unroll
                         for(int k = 0; k < O; k++) acc = fmaf(c_actor[C_W1 + O * j + k], o[k], acc);
-                        h[z] = act_or_rt<A1>(acc, act1);
+                        if constexpr(A1 == B200RL_ACT_RELU) h[z] = acc;             // the ReLU rides on the conversions below
+                        else h[z] = act_or_rt<A1>(acc, act1);
                     }
-                    split_f16_pair(h[0], h[1], lead[q], rest[q]);
+                    if constexpr(A1 == B200RL_ACT_RELU) split_f16_pair_relu(h[0], h[1], lead[q], rest[q]);
+                    else split_f16_pair(h[0], h[1], lead[q], rest[q]);
                 }
 #pragma unroll
                 for(int q = 0; q < 4; q++) lead_all[c * 4 + q] = lead[q];

@@ -201,3 +201,30 @@ def test_offpolicy_step_with_replay_buffers_vs_reference_golden(lib, orc, torch,
     assert np.array_equal(data[:, :w, 8:], fix[f"replay_data_{case}"][:, :, 8:])          # terminated / truncated flags incl. the marks set at resets
     close(data[:, :w, :8], fix[f"replay_data_{case}"][:, :, :8])
     assert np.array_equal(es[:, :w], fix[f"episode_start_{case}"]) and np.array_equal(np.stack([pos, full, ces], 1), fix[f"counters_{case}"])
+
+
+@pytest.mark.parametrize("N", [443, 130, 1, 33, 80004, 75777])
+def test_environment_counts_that_fill_tiles_unevenly(lib, orc, torch, N):
+    """Environment counts that leave tiles partly filled (443 per SM-sized launch, 130, 1, 33) and that need several tiles per group (80,004
+    and 75,777: beyond 4 x 128 environments per SM; 75,777 is odd, i.e. the per-thread-store form). Three steps from given states, with
+    resets of the truncated environments, against the oracle's runner loop: every environment is stepped exactly once per step."""
+    shape, oshape = actor_shapes(lib)
+    T = 3
+    params = mg.det_uniform(23, oshape.num_params()) * np.float32(0.3)
+    rs = np.random.RandomState(N)
+    states = np.stack([rs.uniform(-3, 3, N), rs.uniform(-2, 2, N)], 1).astype(np.float32)
+    es = rs.randint(0, 199, N).astype(np.int32)
+    tr = (rs.uniform(size=N) < 0.3).astype(np.uint8)
+    er = rs.randn(N).astype(np.float32)
+    table = np.stack([rs.uniform(-np.pi, np.pi, (2, N)), rs.uniform(-1, 1, (2, N))], 2).astype(np.float32)
+    ref = orc.pendulum_rollout(oshape, params, states, es, tr, er, table, T)
+    d_states, d_es, d_tr, d_er = dev(torch, states), dev(torch, es), dev(torch, tr), dev(torch, er)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    obs, act, rew = lib.pendulum_rollout(shape, dev(torch, params), d_states, d_es, d_tr, d_er, dev(torch, table), T, error_flag=flag)
+    assert int(flag.item()) == 0
+    close(obs.cpu().numpy()[:N], ref["obs"][:N])                      # first step: exact inputs
+    close(act.cpu().numpy()[:N], ref["act"][:N])
+    assert np.array_equal(d_es.cpu().numpy(), ref["episode_step"]) and np.array_equal(d_tr.cpu().numpy(), ref["truncated"])
+    # later steps: the oracle's MLP on the kernel's own observations (one rounding difference in a state must not be held against the next step)
+    close(act.cpu().numpy().reshape(-1), orc.mlp_evaluate(oshape, params, obs.cpu().numpy()).reshape(-1))
+    close(d_states, ref["states"], rtol=1e-4, atol=1e-5)

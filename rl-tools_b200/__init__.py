@@ -48,12 +48,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB_PATH) and all(os.path.getmtime(LIB_PATH) >= os.path.getmtime(d) for d in deps):
         return LIB_PATH
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + srcs + ["-o", LIB_PATH]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise B200RLError("nvcc failed:\n" + res.stdout + res.stderr)
+    # one object per source, compiled in parallel (a source is recompiled when it or any header is newer than its object), then one link;
+    # the library is written next to its final name and renamed into place, so that nothing ever loads or copies a half-written file
+    from concurrent.futures import ThreadPoolExecutor
+    objdir = os.path.join(CSRC, "build")
+    os.makedirs(objdir, exist_ok=True)
+    headers = [d for d in deps if not d.endswith(".cu")]
+    compile_flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(src):
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        if not force and os.path.exists(obj) and all(os.path.getmtime(obj) >= os.path.getmtime(d) for d in [src] + headers):
+            return obj, None
+        res = subprocess.run([nvcc] + compile_flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj], capture_output=True, text=True)
+        if res.returncode != 0:
+            raise B200RLError("nvcc failed on " + src + ":\n" + res.stdout + res.stderr)
+        return obj, res.stderr
+
+    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
+        results = list(pool.map(compile_one, srcs))
     if verbose:
-        print(res.stderr)
+        print("".join(log for _, log in results if log))
+    tmp = LIB_PATH + ".tmp"
+    res = subprocess.run([nvcc] + NVCC_FLAGS + [obj for obj, _ in results] + ["-o", tmp], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise B200RLError("nvcc link failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -407,6 +407,29 @@ int b200rl_gather_batch(const void* replay_buffers, const b200rl_replay_layout* 
                         float* rewards, uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask,
                         uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream);
 
+/* gather_batch for ANY sequence length (the same reference function; SequentialBatch with SEQUENCE_LENGTH = sequence_length, padded length
+ * P = sequence_length + 1): per batch element the padded sequence is filled by walking the environment's replay buffer as gather_batch_step
+ * does (operations_generic.h:239-411). flags are the batch's sampling parameters (off_policy_runner.h:80-87; the reference's defaults for
+ * sequence_length > 1 are the first three together) and the DETERMINISTIC template flag of gather_batch:
+ *   B200RL_GATHER_FROM_INITIAL_STATE  ALWAYS_SAMPLE_FROM_INITIAL_STATE: a sequence starts at the first step of the sampled transition's episode
+ *   B200RL_GATHER_RANDOM_LENGTH       RANDOM_SEQ_LENGTH: sequences are cut at the nominal length with probability nominal_probability
+ *                                     (NOMINAL_SEQUENCE_LENGTH_PROBABILITY, 0.5), else at a length drawn from 1 .. sequence_length - 1
+ *   B200RL_GATHER_FIRST_STEP_TARGET   INCLUDE_FIRST_STEP_IN_TARGETS: next_reset views next_reset_base from step 0 instead of step 1
+ *   B200RL_GATHER_DETERMINISTIC       environment 0 and sample offset = the batch element's index instead of draws
+ * Draws come from the counter-based generator keyed by (seed, batch element, call_index + *call_counter); call_counter (device, 64-bit) may be
+ * NULL. Outputs (device): oa_base [P, batch, ld_oa] (observation | action per step; the step after a sequence's last transition holds that
+ * transition's next observation and a zero action), rewards [L, batch] floats, terminated / reset / final_step_mask [L, batch] bytes,
+ * next_reset_base / next_final_step_mask_base [P, batch] bytes. Entries the reference leaves unwritten (rewards of padding steps, rows behind the
+ * last sequence's end) are left as they are. An empty sampling range sets *error_flag = 2 and skips the element. */
+#define B200RL_GATHER_FROM_INITIAL_STATE 1
+#define B200RL_GATHER_RANDOM_LENGTH 2
+#define B200RL_GATHER_FIRST_STEP_TARGET 4
+#define B200RL_GATHER_DETERMINISTIC 8
+int b200rl_gather_batch_sequences(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim, int action_dim,
+                                  int sequence_length, int flags, float nominal_probability, unsigned long long seed, unsigned long long call_index,
+                                  const unsigned long long* call_counter, int batch, float* oa_base, int ld_oa, float* rewards, uint8_t* terminated, uint8_t* reset,
+                                  uint8_t* next_reset_base, uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream);
+
 /* The same gather with both indices drawn inside the kernel (the counterpart of the reference's device-side sampling,
  * operations_cuda.h:166-182): Philox-4x32-10 block (batch element, call_index low, call_index high, 1) keyed by seed, word 0 -> environment,
  * word 1 -> sample offset, each bounded by the high half of word * range. No host round trip: usable inside a captured graph when

@@ -116,6 +116,7 @@ class Oracle:
         L.orc_acrobot_rollout_variant.restype = C.c_int
         L.orc_acrobot_terminating_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
         L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
+        L.orc_gather_batch_sequences.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, _f32p, _i64p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
                                            C.c_void_p, C.c_int, _f32p, C.c_int]
@@ -514,6 +515,26 @@ class Oracle:
                                   out["reset"], out["next_reset_base"], out["final_step_mask"], out["next_final_step_mask_base"], out["env_index"], out["sample_index"])
         return out
 
+    GATHER_FROM_INITIAL_STATE, GATHER_RANDOM_LENGTH, GATHER_FIRST_STEP_TARGET, GATHER_DETERMINISTIC = 1, 2, 4, 8
+
+    @staticmethod
+    def new_sequence_batch(batch, L):
+        """Zeroed output arrays of one gather_batch with sequence length L (padded length L + 1)."""
+        u8 = np.uint8
+        return dict(oa_base=np.zeros((L + 1, batch, 4), np.float32), rewards=np.zeros((L, batch), np.float32), terminated=np.zeros((L, batch), u8),
+                    reset=np.zeros((L, batch), u8), next_reset_base=np.zeros((L + 1, batch), u8), final_step_mask=np.zeros((L, batch), u8),
+                    next_final_step_mask_base=np.zeros((L + 1, batch), u8))
+
+    def gather_batch_sequences(self, st, batch, L, flags, rng, max_episode_length=200, nominal_probability=0.5):
+        """One gather_batch with sequence length L on the replay buffers of the state dict `st` (engine `rng` from new_rng, advanced in place);
+        flags = GATHER_* bits. max_episode_length is the ENVIRONMENT's episode step limit (off_policy_runner.h:41)."""
+        N, capacity = st["replay_data"].shape[:2]
+        out = self.new_sequence_batch(batch, L)
+        self.lib.orc_gather_batch_sequences(N, capacity, max_episode_length, batch, L, flags, nominal_probability, rng, st["replay_data"], st["episode_start"], st["counters"],
+                                            out["oa_base"], out["rewards"], out["terminated"], out["reset"], out["next_reset_base"], out["final_step_mask"],
+                                            out["next_final_step_mask_base"])
+        return out
+
     # --- on-policy collect ---------------------------------------------------------------------------------
     def new_rng(self, seed):
         rng = C.create_string_buffer(4 * 624 + 16)
@@ -635,6 +656,7 @@ class Reference:
         L.ref_sample_and_squash.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_polyak_update.argtypes = [_f32p, _f32p, C.c_float, C.c_int, C.c_int]
         L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
+        L.ref_offpolicy_gather_sequences.argtypes = [C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_mlp_c5_chunked.argtypes = [C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int] + [_f32p] * 6
@@ -820,6 +842,22 @@ class Reference:
                                            stack["reset"], stack["next_reset_base"], stack["final_step_mask"], stack["next_final_step_mask_base"], C.byref(next_draw))
         if rc != 0:
             raise KeyError("no such gather_batch case")
+        return [{k: v[g] for k, v in stack.items()} for g in range(n_gathers)], next_draw.value
+
+    GATHER_SEQUENCE_CASES = ((4, 256, 20, 32, 5), (3, 300, 17, 16, 8))       # N, capacity, step limit, batch, sequence length
+    GATHER_SEQUENCE_MODES = (3, 0, 1, 8, 9, 2)                                # bit 0 from the initial state, bit 1 random lengths, bit 3 deterministic
+
+    def offpolicy_gather_sequences(self, which, mode, actor_params, seed, n_steps, n_gathers):
+        """n_steps x step<0>() on a fresh runner, then n_gathers x gather_batch with the sequence length of case `which` and the sampling
+        parameters of `mode`: a list of batch dicts (Oracle.new_sequence_batch) and the engine's next raw draw afterwards."""
+        N, capacity, limit, batch, L = self.GATHER_SEQUENCE_CASES[which]
+        proto = Oracle.new_sequence_batch(batch, L)
+        stack = {k: np.zeros((n_gathers,) + v.shape, v.dtype) for k, v in proto.items()}
+        next_draw = C.c_uint32(0)
+        rc = self.lib.ref_offpolicy_gather_sequences(which, mode, actor_params, seed, n_steps, n_gathers, stack["oa_base"], stack["rewards"], stack["terminated"],
+                                                     stack["reset"], stack["next_reset_base"], stack["final_step_mask"], stack["next_final_step_mask_base"], C.byref(next_draw))
+        if rc != 0:
+            raise KeyError("no such sequence gather case")
         return [{k: v[g] for k, v in stack.items()} for g in range(n_gathers)], next_draw.value
 
     def ppo_train(self, N, steps, batch, epochs, actor_params, critic_params, dataset, shuffle_seed=None, env="pendulum", want_seconds=False):

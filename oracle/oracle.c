@@ -841,6 +841,97 @@ void orc_gather_batch(int N, int capacity, int max_episode_length, int batch, or
 }
 
 /* ------------------------------------------------------------------------------------------------------ */
+/* Replay-buffer sampling for ANY sequence length: gather_batch / gather_batch_step                           */
+/* (rl/components/off_policy_runner/operations_generic.h:239-423) with the sampling parameters as flags       */
+/* (off_policy_runner.h:80-87; for SEQUENCE_LENGTH > 1 the defaults are all three on):                         */
+/*   ORC_GATHER_FROM_INITIAL_STATE  a sequence starts at the first step of the sampled transition's episode   */
+/*                                  (episode_start[index], :312-316); the eligible range of a full buffer then */
+/*                                  shrinks by max_episode_length (:258)                                        */
+/*   ORC_GATHER_RANDOM_LENGTH       sequences are cut to a random length: with probability nominal_probability */
+/*                                  (a double draw compared with the float parameter) the nominal length, else  */
+/*                                  U{1 .. sequence_length - 1} (:263-272, 361-381)                             */
+/*   ORC_GATHER_FIRST_STEP_TARGET   INCLUDE_FIRST_STEP_IN_TARGETS: next_reset views its base from step 0       */
+/*                                  instead of step 1 (:85-92), which is where the unconditional write of :286 */
+/*                                  lands                                                                       */
+/*   ORC_GATHER_DETERMINISTIC       the DETERMINISTIC template flag: environment 0, sample offset = the batch   */
+/*                                  element's index instead of draws (:301, :419)                               */
+/* Per batch element the padded sequence (sequence_length + 1 steps) is filled by walking the replay buffer:   */
+/* after a truncated transition (flag in the buffer, the newest transition, the second to last padded step, or   */
+/* a random cut) the next step holds that transition's next observation with a zero action and is marked in     */
+/* next_final_step_mask_base, and the step after it starts a new sequence at a new draw. Outputs: oa_base       */
+/* [P, batch, 4], rewards / terminated / reset / final_step_mask [L, batch], next_reset_base /                   */
+/* next_final_step_mask_base [P, batch] (P = L + 1). Entries the reference leaves unwritten (rewards of padding   */
+/* steps, the rows behind a sequence's end) keep what the caller put there.                                      */
+/* ------------------------------------------------------------------------------------------------------ */
+#define ORC_GATHER_FROM_INITIAL_STATE 1
+#define ORC_GATHER_RANDOM_LENGTH 2
+#define ORC_GATHER_FIRST_STEP_TARGET 4
+#define ORC_GATHER_DETERMINISTIC 8
+static int64_t gather_draw_length(orc_rng* rng, int L, float nominal_probability){
+    if(orc_uniform_real_double(rng, 0.0, 1.0) < (double)nominal_probability) return L;      /* ENABLE_NOMINAL_SEQUENCE_LENGTH_PROBABILITY (default on) */
+    return L > 1 ? (int64_t)orc_uniform_int(rng, 1, (uint64_t)(L - 1)) : L;
+}
+void orc_gather_batch_sequences(int N, int capacity, int max_episode_length, int batch, int L, int flags, float nominal_probability, orc_rng* rng,
+                                const float* replay_data, const int64_t* episode_start, const int64_t* counters, float* oa_base, float* rewards, uint8_t* terminated,
+                                uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask, uint8_t* next_final_step_mask_base){
+    const int P = L + 1;
+    const int from_initial = flags & ORC_GATHER_FROM_INITIAL_STATE, random_length = flags & ORC_GATHER_RANDOM_LENGTH, deterministic = flags & ORC_GATHER_DETERMINISTIC;
+    const int next_offset = (flags & ORC_GATHER_FIRST_STEP_TARGET) ? 0 : 1;
+    for(int b = 0; b < batch; b++){
+        const int e = deterministic ? 0 : (int)orc_uniform_int(rng, 0, (uint64_t)(N - 1));
+        const int64_t position = counters[3 * e], full = counters[3 * e + 1];
+        const float* data = replay_data + (size_t)e * capacity * 10;
+        const int64_t eligible = full ? (from_initial ? capacity - max_episode_length : capacity) : position;
+        int64_t index = 0, length = L, seq_step = 0;
+        if(random_length) length = gather_draw_length(rng, L, nominal_probability);
+        int previous_truncated = 0, previous_padding = 1;
+        for(int q = 0; q < L; q++){ final_step_mask[(size_t)q * batch + b] = 0; reset[(size_t)q * batch + b] = 0; }
+        for(int q = 0; q < P; q++){ next_final_step_mask_base[(size_t)q * batch + b] = 0; next_reset_base[(size_t)q * batch + b] = 0; }
+        reset[b] = 1; next_reset_base[b] = 1; next_reset_base[(size_t)next_offset * batch + b] = 1;
+        for(int q = 0; q < P; q++){
+            if(previous_truncated){
+                previous_truncated = 0; previous_padding = 1;
+                next_final_step_mask_base[(size_t)q * batch + b] = 1;
+                if(q < P - 1) reset[(size_t)q * batch + b] = 1;
+                continue;
+            }
+            if(previous_padding){
+                if(q < P - 1) reset[(size_t)q * batch + b] = 1;
+                next_reset_base[(size_t)q * batch + b] = 1;
+                const int64_t offset = deterministic ? b : (int64_t)orc_uniform_int(rng, 0, (uint64_t)(eligible - 1));
+                index = full ? (position + max_episode_length + offset) % capacity : offset;
+                if(from_initial) index = episode_start[(size_t)e * capacity + index];
+            }
+            const float* row = data + (size_t)index * 10;
+            float* step = oa_base + ((size_t)q * batch + b) * 4;
+            memcpy(step, row, sizeof(float) * 4);                                  /* observation, action */
+            if(q < P - 1){ rewards[(size_t)q * batch + b] = row[4]; terminated[(size_t)q * batch + b] = row[8] != 0.0f; }
+            int truncated = row[9] != 0.0f;
+            int64_t next_index = index + 1;
+            if(full) next_index %= capacity;
+            if(next_index == position) truncated = 1;
+            if(q == P - 2) truncated = 1;
+            if(random_length){
+                if(seq_step == length - 1){
+                    truncated = 1;
+                    length = L > 1 ? gather_draw_length(rng, L, nominal_probability) : L;      /* :363-377: no draw at sequence length 1 */
+                }
+                seq_step = truncated ? 0 : seq_step + 1;
+            }
+            if(truncated && q < P - 1){
+                final_step_mask[(size_t)q * batch + b] = 1;
+                float* next = oa_base + ((size_t)(q + 1) * batch + b) * 4;
+                memcpy(next, row + 5, sizeof(float) * 3);                          /* next observation, zero action */
+                next[3] = 0.0f;
+            }
+            index = next_index;
+            previous_padding = 0;
+            previous_truncated = truncated;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
 /* On-policy collect: rl/components/on_policy_runner/operations_generic.h:105-146 (collect),                  */
 /* operations_generic_per_env.h:9-36 (prologue), :37-79 (epilogue), dataset columns on_policy_runner.h:38-72.  */
 /* Pendulum: observation 3, action 1 -> row = obs[0:3] action_mean[3] action[4] log_prob[5] reward[6]         */

@@ -614,6 +614,58 @@ static void gather_case(const float* actor_params, uint32_t seed, int n_steps, i
     rlt::free(device, actor); rlt::free(device, buffers);
 }
 
+// The same through gather_batch for sequences: SequentialBatch with SEQUENCE_LENGTH = SEQ and its sampling parameters switched by MODE bits
+// (1 = ALWAYS_SAMPLE_FROM_INITIAL_STATE, 2 = RANDOM_SEQ_LENGTH, 8 = the DETERMINISTIC template flag of gather_batch; INCLUDE_FIRST_STEP_IN_TARGETS
+// keeps its default, SEQ > 1). Outputs per gather: observations_actions_base [SEQ + 1, BATCH, 4], rewards / terminated / reset / final_step_mask
+// [SEQ, BATCH], next_reset_base / next_final_step_mask_base [SEQ + 1, BATCH]. The batch tensors are zeroed before every gather (the reference
+// leaves entries behind a sequence's end unwritten).
+template <TI SEQ, int MODE>
+struct SeqBatchParameters: rlt::rl::components::off_policy_runner::SequentialBatchParameters<TYPE_POLICY, TI, SEQ>{
+    static constexpr bool ALWAYS_SAMPLE_FROM_INITIAL_STATE = (MODE & 1) != 0;
+    static constexpr bool RANDOM_SEQ_LENGTH = (MODE & 2) != 0;
+};
+template <TI N, TI CAPACITY, TI LIMIT, TI BATCH, TI SEQ, int MODE>
+static void gather_seq_case(const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards, uint8_t* terminated, uint8_t* reset,
+                            uint8_t* next_reset_base, uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, uint32_t* next_draw){
+    using ACTOR_CONFIG = rlt::nn_models::mlp::Configuration<TYPE_POLICY, TI, 1, 3, 64, act::RELU, act::TANH>;
+    using ACTOR = rlt::nn_models::sequential::Build<rlt::nn::capability::Forward<>, rlt::nn_models::sequential::Module<rlt::nn_models::mlp::BindConfiguration<ACTOR_CONFIG>>, rlt::tensor::Shape<TI, 1, N, 3>>;
+    using POLICIES = rlt::utils::Tuple<TI, ACTOR>;
+    using SPEC = rlt::rl::components::off_policy_runner::Specification<TYPE_POLICY, TI, PENDULUM, POLICIES, OffPolicyParameters<N, CAPACITY, LIMIT>>;
+    using RUNNER = rlt::rl::components::OffPolicyRunner<SPEC>;
+    using BATCH_SPEC = rlt::rl::components::off_policy_runner::SequentialBatchSpecification<SPEC, SEQ, BATCH, SeqBatchParameters<SEQ, MODE>>;
+    using BATCH_TYPE = rlt::rl::components::off_policy_runner::SequentialBatch<BATCH_SPEC>;
+    constexpr TI P = SEQ + 1;
+    DEVICE device;
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    ACTOR actor; typename ACTOR::template Buffer<> buffers;
+    rlt::malloc(device, actor); rlt::malloc(device, buffers);
+    { const float* p = actor_params; auto& m = actor.content;
+      load_layer(device, m.input_layer, p); load_layer(device, m.hidden_layers[0], p); load_layer(device, m.output_layer, p); }
+    RUNNER* runner = new RUNNER();
+    BATCH_TYPE batch;
+    rlt::malloc(device, *runner); rlt::malloc(device, batch);
+    rlt::init(device, *runner);
+    for(int s = 0; s < n_steps; s++) rlt::step<0>(device, *runner, actor, buffers, rng);
+    for(int g = 0; g < n_gathers; g++){
+        rlt::set_all(device, batch.observations_actions_base, 0); rlt::set_all(device, batch.rewards, 0); rlt::set_all(device, batch.terminated, false);
+        rlt::gather_batch<DEVICE, SPEC, BATCH_SPEC, RNG, (MODE & 8) != 0>(device, *runner, batch, rng);
+        for(TI q = 0; q < P; q++) for(TI b = 0; b < BATCH; b++){
+            for(TI k = 0; k < 4; k++) oa_base[(((size_t)g * P + q) * BATCH + b) * 4 + k] = rlt::get(device, batch.observations_actions_base, q, b, k);
+            next_reset_base[((size_t)g * P + q) * BATCH + b] = rlt::get(device, batch.next_reset_base, q, b, 0) ? 1 : 0;
+            next_final_step_mask_base[((size_t)g * P + q) * BATCH + b] = rlt::get(device, batch.next_final_step_mask_base, q, b, 0) ? 1 : 0;
+        }
+        for(TI q = 0; q < SEQ; q++) for(TI b = 0; b < BATCH; b++){
+            rewards[((size_t)g * SEQ + q) * BATCH + b] = rlt::get(device, batch.rewards, q, b, 0);
+            terminated[((size_t)g * SEQ + q) * BATCH + b] = rlt::get(device, batch.terminated, q, b, 0) ? 1 : 0;
+            reset[((size_t)g * SEQ + q) * BATCH + b] = rlt::get(device, batch.reset, q, b, 0) ? 1 : 0;
+            final_step_mask[((size_t)g * SEQ + q) * BATCH + b] = rlt::get(device, batch.final_step_mask, q, b, 0) ? 1 : 0;
+        }
+    }
+    if(next_draw) *next_draw = (uint32_t)rng.engine();
+    rlt::free(device, *runner); delete runner; rlt::free(device, batch);
+    rlt::free(device, actor); rlt::free(device, buffers);
+}
+
 // The SAC policy head on its own: nn::layers::sample_and_squash LayerGradient forward (external noise) and backward_full
 // (nn/layers/sample_and_squash/operations_generic.h:212-280, 290-398) on a [B, 2A] input. log_alpha_gradient_out = the layer's log_alpha gradient
 // after one backward from a zeroed gradient.
@@ -831,6 +883,19 @@ int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const f
     GATHER_CASE(33, 40, 17, 100)
     GATHER_CASE(5, 300, 60, 64)
 #undef GATHER_CASE
+    return -1;
+}
+
+// cases: 0 = (N 4, capacity 256, limit 20, batch 32, sequence 5), 1 = (N 3, capacity 300, limit 17, batch 16, sequence 8); modes as in gather_seq_case.
+// (MAX_EPISODE_LENGTH is the environment's own 200, whatever the runner's step limit: sampling from the initial state needs a capacity above it.)
+int ref_offpolicy_gather_sequences(int which, int mode, const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards,
+                                   uint8_t* terminated, uint8_t* reset, uint8_t* next_reset_base, uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, uint32_t* next_draw){
+#define GATHER_SEQ_CASE(w, n, c, l, b, q, m) if(which == w && mode == m){ gather_seq_case<n, c, l, b, q, m>(actor_params, seed, n_steps, n_gathers, oa_base, rewards, terminated, reset, next_reset_base, final_step_mask, next_final_step_mask_base, next_draw); return 0; }
+#define GATHER_SEQ_MODES(w, n, c, l, b, q) GATHER_SEQ_CASE(w, n, c, l, b, q, 3) GATHER_SEQ_CASE(w, n, c, l, b, q, 0) GATHER_SEQ_CASE(w, n, c, l, b, q, 1) GATHER_SEQ_CASE(w, n, c, l, b, q, 8) GATHER_SEQ_CASE(w, n, c, l, b, q, 9) GATHER_SEQ_CASE(w, n, c, l, b, q, 2)
+    GATHER_SEQ_MODES(0, 4, 256, 20, 32, 5)
+    GATHER_SEQ_MODES(1, 3, 300, 17, 16, 8)
+#undef GATHER_SEQ_MODES
+#undef GATHER_SEQ_CASE
     return -1;
 }
 

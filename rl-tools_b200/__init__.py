@@ -192,6 +192,7 @@ def lib():
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         u64 = C.c_uint64
         L.b200rl_pendulum_collect_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, i, vp, vp]
+        L.b200rl_gather_batch_sequences.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, i, i, f, u64, u64, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
         L.b200rl_pendulum_offpolicy_prologue.argtypes = [vp, vp, vp, vp, vp, u64, u64, vp, i, vp, vp, vp]
         L.b200rl_pendulum_offpolicy_epilogue.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, C.POINTER(ReplayLayout), vp, vp]
         L.b200rl_pendulum_rollout_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, vp, vp, vp, vp]
@@ -658,6 +659,34 @@ def gather_batch(replay, layout, n_envs, out, env_index=None, sample_offset=None
     else:
         check(lib().b200rl_gather_batch_device_rng(_ptr(replay), C.byref(layout), n_envs, max_episode_length, obs_dim, action_dim, seed, call_index, *tail),
               "b200rl_gather_batch_device_rng")
+    return out
+
+
+GATHER_FROM_INITIAL_STATE, GATHER_RANDOM_LENGTH, GATHER_FIRST_STEP_TARGET, GATHER_DETERMINISTIC = 1, 2, 4, 8
+
+
+def new_sequence_batch(batch, sequence_length, obs_dim=3, action_dim=1, device="cuda"):
+    """Zeroed output tensors of gather_batch_sequences (SequentialBatch with SEQUENCE_LENGTH = sequence_length, padded length + 1)."""
+    import torch
+    L, P = sequence_length, sequence_length + 1
+    u8 = dict(device=device, dtype=torch.uint8)
+    return dict(oa_base=torch.zeros((P, batch, obs_dim + action_dim), device=device), rewards=torch.zeros((L, batch), device=device),
+                terminated=torch.zeros((L, batch), **u8), reset=torch.zeros((L, batch), **u8), next_reset_base=torch.zeros((P, batch), **u8),
+                final_step_mask=torch.zeros((L, batch), **u8), next_final_step_mask_base=torch.zeros((P, batch), **u8))
+
+
+def gather_batch_sequences(replay, layout, n_envs, out, flags=None, seed=0, call_index=0, call_counter=None, max_episode_length=200, nominal_probability=0.5,
+                           obs_dim=3, action_dim=1, error_flag=None):
+    """gather_batch for sequences into the tensors `out` (new_sequence_batch). flags: GATHER_* bits; None = the reference's defaults for the
+    sequence length (all three sampling parameters on for sequences longer than 1, off for length 1)."""
+    L = out["rewards"].shape[0]
+    batch = out["rewards"].shape[1]
+    if flags is None:
+        flags = (GATHER_FROM_INITIAL_STATE | GATHER_RANDOM_LENGTH | GATHER_FIRST_STEP_TARGET) if L > 1 else 0
+    check(lib().b200rl_gather_batch_sequences(_ptr(replay), C.byref(layout), n_envs, max_episode_length, obs_dim, action_dim, L, flags, nominal_probability, seed, call_index,
+                                              _ptr(call_counter), batch, _ptr(out["oa_base"]), out["oa_base"].stride(1), _ptr(out["rewards"]), _ptr(out["terminated"]),
+                                              _ptr(out["reset"]), _ptr(out["next_reset_base"]), _ptr(out["final_step_mask"]), _ptr(out["next_final_step_mask_base"]),
+                                              _ptr(error_flag), _stream()), "b200rl_gather_batch_sequences")
     return out
 
 

@@ -393,6 +393,128 @@ __global__ void gather_batch_kernel(GatherArgs a){
 }
 }  // namespace b200rl
 
+// ---------------------------------------------------------------------------------------------------------------
+// Replay-buffer sampling for any sequence length (rl/components/off_policy_runner/operations_generic.h:239-423): one thread per batch
+// element walks the padded sequence through its environment's replay buffer exactly as gather_batch_step does -- a new start index
+// whenever the previous step was padding, the episode's first step if sequences start from the initial state, a cut at a truncated
+// transition, at the newest transition, at the second to last padded step or at a random length -- and writes the batch tensors
+// [step, batch, ...]. Draws (environment, sample offsets, sequence lengths) come from a counter-based stream per (batch element, call);
+// with B200RL_GATHER_DETERMINISTIC the environment is 0 and the offset the element's index, as with the reference's DETERMINISTIC flag.
+// ---------------------------------------------------------------------------------------------------------------
+namespace b200rl {
+struct GatherSeqArgs {
+    const unsigned char* replay; b200rl_replay_layout L;
+    int n_envs, max_episode_length, batch, obs_dim, action_dim, seq, flags;
+    float nominal_probability;
+    float* oa_base; int ld_oa;
+    float* rewards; uint8_t *terminated, *reset, *next_reset_base, *final_step_mask, *next_final_step_mask_base;
+    int* error_flag;
+    unsigned long long seed, call; const unsigned long long* call_counter;
+};
+// successive 32-bit draws of one (batch element, call): Philox blocks (element, call low, call high, 2 + block index)
+struct DrawStream {
+    uint32_t c[4]; uint32_t element, call_lo, call_hi, k0, k1; int block, used;
+    __device__ void init(unsigned long long seed, unsigned long long call, uint32_t e){ element = e; call_lo = (uint32_t)call; call_hi = (uint32_t)(call >> 32); k0 = (uint32_t)seed; k1 = (uint32_t)(seed >> 32); block = 0; used = 4; }
+    __device__ uint32_t next(){
+        if(used == 4){ c[0] = element; c[1] = call_lo; c[2] = call_hi; c[3] = 2u + (uint32_t)block; Philox::block(c, k0, k1); block++; used = 0; }
+        return c[used++];
+    }
+    __device__ long long below(long long n){ return (long long)__umulhi(next(), (uint32_t)n); }            // U{0 .. n-1}, bias below n / 2^32
+    __device__ float unit(){ return (float)(next() >> 8) * 5.9604644775390625e-8f; }                        // [0, 1) in steps of 2^-24
+};
+template <typename INDEX>
+__global__ void __launch_bounds__(128) gather_sequences_kernel(GatherSeqArgs a){
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if(b >= a.batch) return;
+    const bool from_initial = a.flags & B200RL_GATHER_FROM_INITIAL_STATE, random_length = a.flags & B200RL_GATHER_RANDOM_LENGTH, deterministic = a.flags & B200RL_GATHER_DETERMINISTIC;
+    const int next_offset = (a.flags & B200RL_GATHER_FIRST_STEP_TARGET) ? 0 : 1;
+    const int Lq = a.seq, P = Lq + 1, O = a.obs_dim, A = a.action_dim;
+    const size_t B = (size_t)a.batch;
+    DrawStream draws; draws.init(a.seed, a.call + (a.call_counter ? *a.call_counter : 0ull), (uint32_t)b);
+    const int e = deterministic ? 0 : (int)draws.below(a.n_envs);
+    const unsigned char* rb = a.replay + (size_t)e * a.L.env_stride;
+    const float* data = reinterpret_cast<const float*>(rb + a.L.off_data);
+    const INDEX* episode_start = reinterpret_cast<const INDEX*>(rb + a.L.off_episode_start);
+    const long long position = (long long)*reinterpret_cast<const INDEX*>(rb + a.L.off_position), capacity = a.L.capacity;
+    const bool full = *(rb + a.L.off_full) != 0;
+    const long long eligible = full ? (from_initial ? capacity - a.max_episode_length : capacity) : position;      // :258
+    if(eligible < 1 || (deterministic && b >= eligible)){ if(a.error_flag) *a.error_flag = 2; return; }             // the reference requires a non-empty range (:251-255)
+    auto draw_length = [&]() -> long long {                                                                       // :263-272
+        if(draws.unit() < a.nominal_probability) return Lq;
+        return Lq > 1 ? 1 + draws.below(Lq - 1) : Lq;
+    };
+    long long index = 0, length = Lq, seq_step = 0;
+    if(random_length) length = draw_length();
+    bool previous_truncated = false, previous_padding = true;
+    for(int q = 0; q < Lq; q++){ a.final_step_mask[q * B + b] = 0; a.reset[q * B + b] = 0; }
+    for(int q = 0; q < P; q++){ a.next_final_step_mask_base[q * B + b] = 0; a.next_reset_base[q * B + b] = 0; }
+    a.reset[b] = 1; a.next_reset_base[b] = 1; a.next_reset_base[next_offset * B + b] = 1;                           // :284-286
+    for(int q = 0; q < P; q++){
+        if(previous_truncated){                                                                                    // :288-297
+            previous_truncated = false; previous_padding = true;
+            a.next_final_step_mask_base[q * B + b] = 1;
+            if(q < P - 1) a.reset[q * B + b] = 1;
+            continue;
+        }
+        if(previous_padding){                                                                                      // :298-317
+            if(q < P - 1) a.reset[q * B + b] = 1;
+            a.next_reset_base[q * B + b] = 1;
+            const long long offset = deterministic ? b : draws.below(eligible);
+            index = full ? (position + a.max_episode_length + offset) % capacity : offset;
+            if(from_initial) index = (long long)episode_start[index];
+        }
+        const float* row = data + (size_t)index * a.L.ld_data;
+        float* step = a.oa_base + (q * B + b) * a.ld_oa;
+        for(int c = 0; c < O + A; c++) step[c] = row[c];                                                            // observation, action
+        if(q < P - 1){ a.rewards[q * B + b] = row[O + A]; a.terminated[q * B + b] = row[2 * O + A + 1] != 0.0f; }
+        bool truncated = row[2 * O + A + 2] != 0.0f;
+        long long next_index = index + 1;
+        if(full) next_index %= capacity;
+        if(next_index == position) truncated = true;                                                               // the newest transition
+        if(q == P - 2) truncated = true;
+        if(random_length){                                                                                         // :361-381
+            if(seq_step == length - 1){
+                truncated = true;
+                length = Lq > 1 ? draw_length() : Lq;
+            }
+            seq_step = truncated ? 0 : seq_step + 1;
+        }
+        if(truncated && q < P - 1){                                                                                // :386-403
+            a.final_step_mask[q * B + b] = 1;
+            float* next = a.oa_base + ((q + 1) * B + b) * a.ld_oa;
+            for(int c = 0; c < O; c++) next[c] = row[O + A + 1 + c];
+            for(int c = 0; c < A; c++) next[O + c] = 0.0f;
+        }
+        index = next_index;
+        previous_padding = false;
+        previous_truncated = truncated;
+    }
+}
+}  // namespace b200rl
+
+extern "C" int b200rl_gather_batch_sequences(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int max_episode_length, int obs_dim, int action_dim,
+                                             int sequence_length, int flags, float nominal_probability, unsigned long long seed, unsigned long long call_index,
+                                             const unsigned long long* call_counter, int batch, float* oa_base, int ld_oa, float* rewards, uint8_t* terminated, uint8_t* reset,
+                                             uint8_t* next_reset_base, uint8_t* final_step_mask, uint8_t* next_final_step_mask_base, int* error_flag, b200rl_stream_t stream){
+    if(!replay_buffers || !layout || !oa_base || !rewards || !terminated || !reset || !next_reset_base || !final_step_mask || !next_final_step_mask_base || n_envs < 1 ||
+       batch < 0 || obs_dim < 1 || action_dim < 1 || sequence_length < 1 || max_episode_length < 0 || ld_oa < obs_dim + action_dim)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(layout->capacity < 1 || layout->ld_data < 2 * obs_dim + action_dim + 3 || (layout->index_bytes != 4 && layout->index_bytes != 8)) return B200RL_ERR_INVALID_ARGUMENT;
+    if((flags & B200RL_GATHER_FROM_INITIAL_STATE) && layout->capacity < max_episode_length) return B200RL_ERR_INVALID_ARGUMENT;     // the reference's static_assert (:256)
+    if(batch == 0) return B200RL_OK;
+    GatherSeqArgs a{};
+    a.replay = static_cast<const unsigned char*>(replay_buffers); a.L = *layout; a.n_envs = n_envs; a.max_episode_length = max_episode_length; a.batch = batch;
+    a.obs_dim = obs_dim; a.action_dim = action_dim; a.seq = sequence_length; a.flags = flags; a.nominal_probability = nominal_probability;
+    a.oa_base = oa_base; a.ld_oa = ld_oa; a.rewards = rewards; a.terminated = terminated; a.reset = reset; a.next_reset_base = next_reset_base;
+    a.final_step_mask = final_step_mask; a.next_final_step_mask_base = next_final_step_mask_base; a.error_flag = error_flag;
+    a.seed = seed; a.call = call_index; a.call_counter = call_counter;
+    const int threads = 128, blocks = (batch + threads - 1) / threads;
+    if(layout->index_bytes == 4) gather_sequences_kernel<uint32_t><<<blocks, threads, 0, (cudaStream_t)stream>>>(a);
+    else gather_sequences_kernel<unsigned long long><<<blocks, threads, 0, (cudaStream_t)stream>>>(a);
+    B200RL_LAUNCH_CHECK("gather_sequences");
+    return B200RL_OK;
+}
+
 extern "C" int b200rl_replay_counters(const void* replay_buffers, const b200rl_replay_layout* layout, int n_envs, int32_t* position, uint8_t* full,
                                       b200rl_stream_t stream){
     if(!replay_buffers || !layout || !position || !full || n_envs < 0 || (layout->index_bytes != 4 && layout->index_bytes != 8)) return B200RL_ERR_INVALID_ARGUMENT;

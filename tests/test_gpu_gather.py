@@ -166,3 +166,55 @@ def test_polyak_update_vs_reference_golden(lib, orc, torch, case):
     orc.polyak_update(np.ascontiguousarray(big_s[:, 3:60]), view, np.float32(polyak), square)
     want[:, 10:67] = view
     assert np.array_equal(t_d.cpu().numpy(), want)
+
+
+# --- sequences longer than 1 -----------------------------------------------------------------------------------------------------------
+def sequence_replay_state(orc, which, steps):
+    N, cap, limit, batch, L = oracle.Reference.GATHER_SEQUENCE_CASES[which]
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    rng = orc.new_rng(mg.GATHER_SEQ_SEED)
+    return orc.offpolicy_steps(shape, mg.gather_sequence_params(which), orc.new_offpolicy_state(N, cap), limit, steps, rng)
+
+
+@pytest.mark.parametrize("run", [i for i, r in enumerate(mg.GATHER_SEQ_RUNS) if r[1] in (8, 9)])
+def test_gather_batch_sequences_deterministic_vs_reference_golden(lib, orc, torch, run):
+    """With the reference's DETERMINISTIC flag (environment 0, offset = batch element) and fixed sequence lengths nothing is drawn: the kernel's
+    walk through the replay buffer -- sequence starts (at the episode's first step or anywhere), cuts at truncated transitions, at the newest
+    transition and at the padded length, next observations behind a sequence's end, every mask -- equals the real reference's batch bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "gather_sequences.npz"))
+    which, mode, steps = mg.GATHER_SEQ_RUNS[run]
+    N, cap, limit, batch, L = oracle.Reference.GATHER_SEQUENCE_CASES[which]
+    replay, layout = pack_replay(lib, torch, sequence_replay_state(orc, which, steps))
+    out = lib.new_sequence_batch(batch, L)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flags = (mode & 1) | lib.GATHER_FIRST_STEP_TARGET | lib.GATHER_DETERMINISTIC
+    lib.gather_batch_sequences(replay, layout, N, out, flags=flags, error_flag=flag)
+    assert int(flag.item()) == 0
+    for k in mg.GATHER_SEQ_KEYS:
+        assert np.array_equal(out[k].cpu().numpy(), fix[f"{k}_{run}"][0]), k          # both consecutive golden batches are the same without draws
+        assert np.array_equal(fix[f"{k}_{run}"][0], fix[f"{k}_{run}"][1]), k
+
+
+@pytest.mark.parametrize("which,steps,flags", [(0, 230, 7), (0, 800, 7), (1, 950, 7), (1, 950, 6), (0, 600, 4), (1, 299, 5)])
+def test_gather_batch_sequences_with_device_draws(lib, orc, torch, which, steps, flags):
+    """Draws made inside the kernel: every batch element is re-walked on the host from the oracle's replay state. Each step's observation | action
+    row is located in the replay buffers; inside a sequence the indices are consecutive, a sequence starts at its episode's first step when that
+    flag is set, ends where the rules say it may (truncated transition, newest transition, padded length, or -- with random lengths only -- early),
+    the step behind a sequence's end holds that transition's next observation with a zero action, and the masks mark exactly these places.
+    Over many elements all environments are used, and with random lengths both early cuts and full-length sequences occur."""
+    N, cap, limit, batch_small, L = oracle.Reference.GATHER_SEQUENCE_CASES[which]
+    st = sequence_replay_state(orc, which, steps)
+    replay, layout = pack_replay(lib, torch, st)
+    B, P = 2048, L + 1
+    out = lib.new_sequence_batch(B, L)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.gather_batch_sequences(replay, layout, N, out, flags=flags, seed=77, call_index=3, error_flag=flag)
+    assert int(flag.item()) == 0
+    mg.check_sequence_batch({k: v.cpu().numpy() for k, v in out.items()}, st, L, flags)
+    # another call index draws another batch; the same call index the same one
+    out2 = lib.new_sequence_batch(B, L)
+    lib.gather_batch_sequences(replay, layout, N, out2, flags=flags, seed=77, call_index=4)
+    assert not torch.equal(out2["oa_base"], out["oa_base"])
+    out3 = lib.new_sequence_batch(B, L)                      # a fresh batch: entries behind a sequence's end are left as they are, like the reference's
+    lib.gather_batch_sequences(replay, layout, N, out3, flags=flags, seed=77, call_index=3)
+    assert all(torch.equal(out3[k], out[k]) for k in out)

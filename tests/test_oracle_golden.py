@@ -245,6 +245,36 @@ def test_gather_batch_matches_reference(orc, case):
     assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == int(fix[f"next_draw_{case}"])
 
 
+@pytest.mark.parametrize("run", range(len(mg.GATHER_SEQ_RUNS)))
+def test_gather_batch_sequences_match_reference(orc, run):
+    """gather_batch with sequence lengths 5 and 8 after n runner steps, two consecutive batches on one engine: every batch tensor and the
+    engine's position afterwards, bit for bit -- the reference's default sampling parameters (sequences from their episode's first step,
+    random lengths), each of them alone, neither, and the DETERMINISTIC flag; partly filled and wrapped replay buffers."""
+    fix = np.load(os.path.join(GOLDEN, "gather_sequences.npz"))
+    which, mode, steps = mg.GATHER_SEQ_RUNS[run]
+    N, cap, limit, batch, L = oracle.Reference.GATHER_SEQUENCE_CASES[which]
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    rng = orc.new_rng(mg.GATHER_SEQ_SEED)
+    st = orc.offpolicy_steps(shape, mg.gather_sequence_params(which), orc.new_offpolicy_state(N, cap), limit, steps, rng)
+    flags = (mode & 3) | orc.GATHER_FIRST_STEP_TARGET | (orc.GATHER_DETERMINISTIC if mode & 8 else 0)
+    for g in range(2):
+        got = orc.gather_batch_sequences(st, batch, L, flags, rng)
+        for k in mg.GATHER_SEQ_KEYS:
+            assert np.array_equal(got[k], fix[f"{k}_{run}"][g]), (g, k)
+    assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == int(fix[f"next_draw_{run}"])
+
+
+@pytest.mark.parametrize("which,steps,flags", [(0, 230, 7), (1, 950, 6), (0, 600, 4), (1, 299, 5)])
+def test_sequence_batch_checker_accepts_the_oracle(orc, which, steps, flags):
+    """The structural checker that the GPU tests apply to batches drawn by the kernel's own generator, applied to 2,048-element batches of the
+    (reference-pinned) oracle: it has to accept them."""
+    N, cap, limit, batch, L = oracle.Reference.GATHER_SEQUENCE_CASES[which]
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    rng = orc.new_rng(mg.GATHER_SEQ_SEED)
+    st = orc.offpolicy_steps(shape, mg.gather_sequence_params(which), orc.new_offpolicy_state(N, cap), limit, steps, rng)
+    mg.check_sequence_batch(orc.gather_batch_sequences(st, 2048, L, flags, rng), st, L, flags)
+
+
 @pytest.mark.parametrize("case", range(len(mg.POLYAK_CASES)))
 def test_polyak_update_matches_reference(orc, case):
     """utils::polyak::update / update_squared, repeated: bit for bit."""

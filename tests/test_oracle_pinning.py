@@ -156,6 +156,26 @@ def test_gather_batch_live(orc, ref_strict):
             assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == next_draw
 
 
+def test_gather_batch_sequences_live(orc, ref_strict):
+    """Sequence lengths 5 and 8, every combination of the sampling parameters the driver instantiates, replay buffers from barely eligible to
+    wrapped three times: batch tensors and the engine's position, bit for bit."""
+    shape = oracle.MlpShape.make(3, [64, 64, 1], ["relu", "relu", "tanh"])
+    rs = np.random.RandomState(17)
+    for which, (N, cap, lim, batch, L) in enumerate(ref_strict.GATHER_SEQUENCE_CASES):
+        params = (rs.randn(4481) * 0.3).astype(np.float32)
+        for mode in ref_strict.GATHER_SEQUENCE_MODES:
+            for n_steps in (201 + lim, cap - 1, cap, cap + 13, 3 * cap + 5):
+                want, next_draw = ref_strict.offpolicy_gather_sequences(which, mode, params, 6, n_steps, 2)
+                rng = orc.new_rng(6)
+                st = orc.offpolicy_steps(shape, params, orc.new_offpolicy_state(N, cap), lim, n_steps, rng)
+                flags = (mode & 3) | orc.GATHER_FIRST_STEP_TARGET | (orc.GATHER_DETERMINISTIC if mode & 8 else 0)
+                for g in range(2):
+                    got = orc.gather_batch_sequences(st, batch, L, flags, rng)
+                    for k in want[g]:
+                        assert np.array_equal(got[k], want[g][k]), (which, mode, n_steps, g, k)
+                assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == next_draw
+
+
 def test_sac_updates_live(orc, ref_strict):
     import make_golden as mg
     for case, (B, H) in enumerate(oracle.Reference.SAC_CASES):

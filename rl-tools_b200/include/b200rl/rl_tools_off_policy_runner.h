@@ -11,7 +11,8 @@
 // Supported: rl::environments::Pendulum, symmetric observations, fp32. The policy sequential< mlp 3 -> 64 -> 64 -> 1 > (or that mlp itself)
 // takes the fused kernel; ANY other policy that evaluates on this device runs as the reference's CUDA runner does -- prologue kernel, the
 // reference's own interlude (evaluate_step of the policy on the runner's observation / action buffers), epilogue kernel.
-// gather_batch is provided for SequentialBatch with sequence length 1. Not provided: longer sequences, episode statistics. The view members
+// gather_batch: SequentialBatch with sequence length 1 draws on the caller's host engine in the reference's order (same batch as the reference);
+// longer sequences and the DETERMINISTIC flag go to the kernel with in-kernel draws. Not provided: episode statistics. The view members
 // inside the device-resident replay-buffer structs are not initialised: only the data matrix, episode_start and the position / full /
 // current_episode_start counters are maintained, and the kernels address rows through byte offsets.
 #pragma once
@@ -178,10 +179,37 @@ namespace rl_tools{
         using TI = typename SPEC::TI;
         using BP = typename BATCH_SPEC::PARAMETERS;
         static_assert(utils::typing::is_same_v<SPEC, typename BATCH_SPEC::SPEC>);
-        static_assert(BATCH_SPEC::SEQUENCE_LENGTHH == 1 && !BP::RANDOM_SEQ_LENGTH && !BP::ALWAYS_SAMPLE_FROM_INITIAL_STATE && !DETERMINISTIC, "sequence length 1 with its default sampling parameters only");
         static_assert(!SPEC::PARAMETERS::ASYMMETRIC_OBSERVATIONS && utils::typing::is_same_v<typename BATCH::T_INPUT, float> && sizeof(bool) == 1, "not implemented on this device");
         constexpr TI N = RUNNER::N_ENVIRONMENTS, B = BATCH::BATCH_SIZE, CAPACITY = SPEC::PARAMETERS::REPLAY_BUFFER_CAPACITY;
         static const b200rl_replay_layout layout = b200::replay_layout<SPEC>();
+        if constexpr(BATCH_SPEC::SEQUENCE_LENGTHH != 1 || BP::RANDOM_SEQ_LENGTH || BP::ALWAYS_SAMPLE_FROM_INITIAL_STATE || DETERMINISTIC){
+            // Sequences (or any non-default sampling parameter): how many draws an element takes depends on the flags stored in the replay
+            // buffer, so they cannot be made ahead on the host engine; the kernel draws from its counter-based generator, seeded per call with
+            // two words of the caller's engine (none with DETERMINISTIC, where nothing is drawn). The batch then follows the reference's
+            // distribution, not its engine's sequence.
+            static_assert(BP::ENABLE_NOMINAL_SEQUENCE_LENGTH_PROBABILITY || !BP::RANDOM_SEQ_LENGTH, "random lengths without the nominal-length probability are not implemented");
+            constexpr int FLAGS = (BP::ALWAYS_SAMPLE_FROM_INITIAL_STATE ? B200RL_GATHER_FROM_INITIAL_STATE : 0) | (BP::RANDOM_SEQ_LENGTH ? B200RL_GATHER_RANDOM_LENGTH : 0) |
+                                  (BP::INCLUDE_FIRST_STEP_IN_TARGETS ? B200RL_GATHER_FIRST_STEP_TARGET : 0) | (DETERMINISTIC ? B200RL_GATHER_DETERMINISTIC : 0);
+            unsigned long long seed = 0;
+            if constexpr(!DETERMINISTIC){
+                const unsigned long long lo = random::uniform_int_distribution(device.random, (TI)0, (TI)0xFFFFFFFFu, rng), hi = random::uniform_int_distribution(device.random, (TI)0, (TI)0xFFFFFFFFu, rng);
+                seed = lo | (hi << 32);
+            }
+            static void* flag_slot = nullptr;
+            if(!flag_slot) b200::note(device, b200rl_device_malloc(&flag_slot, 16));
+            if(!flag_slot) return;
+            int flag = 0;
+            b200::note(device, b200rl_memcpy(flag_slot, &flag, sizeof(int), 0, device.stream));
+            b200::note(device, b200rl_gather_batch_sequences(runner.replay_buffers._data, &layout, (int)N, (int)SPEC::MAX_EPISODE_LENGTH, (int)BATCH::OBSERVATION_DIM, (int)BATCH::ACTION_DIM,
+                                                             (int)BATCH_SPEC::SEQUENCE_LENGTHH, FLAGS, (float)BP::NOMINAL_SEQUENCE_LENGTH_PROBABILITY, seed, 0, nullptr, (int)B,
+                                                             batch.observations_actions_base._data, (int)BATCH::DATA_DIM, batch.rewards._data,
+                                                             reinterpret_cast<uint8_t*>(batch.terminated._data), reinterpret_cast<uint8_t*>(batch.reset._data),
+                                                             reinterpret_cast<uint8_t*>(batch.next_reset_base._data), reinterpret_cast<uint8_t*>(batch.final_step_mask._data),
+                                                             reinterpret_cast<uint8_t*>(batch.next_final_step_mask_base._data), static_cast<int*>(flag_slot), device.stream));
+            b200::note(device, b200rl_memcpy(&flag, flag_slot, sizeof(int), 1, device.stream));
+            if(flag != 0) b200::note(device, B200RL_ERR_DEVICE_FLAG);
+            return;
+        }
         // work area kept for the life of the process: position [N], env_index [B], sample_offset [B] (int32), full [N] bytes, error flag
         constexpr size_t OFF_ENV = sizeof(int32_t) * N, OFF_OFFSET = OFF_ENV + sizeof(int32_t) * B, OFF_FULL = OFF_OFFSET + sizeof(int32_t) * B, OFF_FLAG = OFF_FULL + ((N + 15) / 16) * 16;
         static void* scratch = nullptr;

@@ -263,6 +263,11 @@ struct OffPolicyParityParameters: rlt::rl::components::off_policy_runner::Parame
     static constexpr TI REPLAY_BUFFER_CAPACITY = T_CAPACITY;
     static constexpr TI EPISODE_STEP_LIMIT = T_LIMIT;
 };
+// sampling parameters of the sequence check: fixed lengths, starts anywhere (what the DETERMINISTIC flag then leaves is a walk without draws)
+struct AdapterSequenceParameters: rlt::rl::components::off_policy_runner::SequentialBatchParameters<TYPE_POLICY, TI, 4>{
+    static constexpr bool ALWAYS_SAMPLE_FROM_INITIAL_STATE = false;
+    static constexpr bool RANDOM_SEQ_LENGTH = false;
+};
 // HIDDEN = 64 takes the fused runner kernel; any other width takes the reference's three phases (prologue kernel, the reference's own
 // interlude with the policy's evaluate on the device tag, epilogue kernel).
 template <TI N, TI CAPACITY, TI LIMIT, int STEPS, TI HIDDEN = 64>
@@ -334,6 +339,31 @@ void offpolicy_parity(const char* name){
             masks = masks && rlt::get(cpu, batch_cpu.reset, 0, b, 0) == rlt::get(cpu, batch_back.reset, 0, b, 0);
             masks = masks && rlt::get(cpu, batch_cpu.final_step_mask, 0, b, 0) == rlt::get(cpu, batch_back.final_step_mask, 0, b, 0);
         }
+    }
+    // sequences of length 4 through gather_batch<..., DETERMINISTIC = true> (environment 0, offset = batch element: no draws on either device):
+    // the kernel's walk through the device-resident replay-buffer structs against the reference's -- identical masks, rows within the drift
+    {
+        using SEQ_SPEC = rlt::rl::components::off_policy_runner::SequentialBatchSpecification<SPEC, 4, 8, AdapterSequenceParameters>;
+        using SEQ_BATCH = rlt::rl::components::off_policy_runner::SequentialBatch<SEQ_SPEC>;
+        SEQ_BATCH seq_cpu, seq_gpu, seq_back;
+        rlt::malloc(cpu, seq_cpu); rlt::malloc(gpu, seq_gpu); rlt::malloc(cpu, seq_back);
+        rlt::set_all(cpu, seq_cpu.observations_actions_base, 0); rlt::set_all(cpu, seq_cpu.rewards, 0); rlt::set_all(cpu, seq_cpu.terminated, false);
+        rlt::copy(cpu, gpu, seq_cpu, seq_gpu);
+        rlt::gather_batch<DEVICE_CPU, SPEC, SEQ_SPEC, decltype(rng_cpu), true>(cpu, *runner_cpu, seq_cpu, rng_cpu);
+        rlt::gather_batch<DEVICE_GPU::SPEC, SPEC, SEQ_SPEC, decltype(rng_gpu), true>(gpu, *runner_gpu, seq_gpu, rng_gpu);
+        rlt::copy(gpu, cpu, seq_gpu, seq_back);
+        for(TI q = 0; q < 5; q++) for(TI b = 0; b < 8; b++){
+            for(TI k = 0; k < 4; k++) gather_diff = std::fmax(gather_diff, std::fabs((double)rlt::get(cpu, seq_cpu.observations_actions_base, q, b, k) - (double)rlt::get(cpu, seq_back.observations_actions_base, q, b, k)));
+            masks = masks && rlt::get(cpu, seq_cpu.next_reset_base, q, b, 0) == rlt::get(cpu, seq_back.next_reset_base, q, b, 0);
+            masks = masks && rlt::get(cpu, seq_cpu.next_final_step_mask_base, q, b, 0) == rlt::get(cpu, seq_back.next_final_step_mask_base, q, b, 0);
+            if(q < 4){
+                gather_diff = std::fmax(gather_diff, std::fabs((double)rlt::get(cpu, seq_cpu.rewards, q, b, 0) - (double)rlt::get(cpu, seq_back.rewards, q, b, 0)));
+                masks = masks && rlt::get(cpu, seq_cpu.terminated, q, b, 0) == rlt::get(cpu, seq_back.terminated, q, b, 0);
+                masks = masks && rlt::get(cpu, seq_cpu.reset, q, b, 0) == rlt::get(cpu, seq_back.reset, q, b, 0);
+                masks = masks && rlt::get(cpu, seq_cpu.final_step_mask, q, b, 0) == rlt::get(cpu, seq_back.final_step_mask, q, b, 0);
+            }
+        }
+        rlt::free(cpu, seq_cpu); rlt::free(gpu, seq_gpu); rlt::free(cpu, seq_back);
     }
     status = status ? status : rlt::check_status(gpu);
     bool engines = rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_cpu) == rlt::random::uniform_real_distribution(cpu.random, (T)0, (T)1, rng_gpu);

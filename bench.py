@@ -16,7 +16,7 @@ the 64 -> 256 -> 256 -> 256 -> 16 MLP on 2^24 rows split over the ranks with ONE
 step (strong scaling, the all-reduce timed on its own), and `rollout_strong` = the same 65,536 environments split over the
 ranks. `--impl reference` times only the reference CPU implementation, on the same metric and config.
 
-`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout}` print secondary lines in the same JSON form (sharded MLP training,
+`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout, l2f_step}` print secondary lines in the same JSON form (sharded MLP training,
 on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference, the SAC training step, the generic rollout on AcrobotSwingup); the default workload is the headline rollout.
 """
 import argparse
@@ -750,6 +750,65 @@ def run_acrobot_rollout(args):
                       "cpu_baseline": cpu, "gpu_launches": steps}))
 
 
+def run_l2f_step(args):
+    """Secondary line: the L2F quadrotor step in the configuration of the reference's own GPU throughput harness -- 4096 x 512 quadrotors
+    (its grid), 100 steps per launch with a constant action each, states in place. value = quadrotor steps per second. Single GPU.
+    Parameter values and the sample states come from the committed fixture (written from the reference)."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    here = os.path.dirname(os.path.abspath(__file__))
+    fix = np.load(os.path.join(here, "tests", "golden", "l2f.npz"))
+    sys.path.insert(0, os.path.join(here, "tests", "golden"))
+    import make_golden as mg
+    N, T = 4096 * 512, 100
+    params = pkg.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    base_states, base_actions = mg.l2f_inputs(4096, seed=21)
+    states0 = torch.from_numpy(base_states).to(dev).repeat(512, 1).contiguous()
+    actions = torch.from_numpy(np.clip(base_actions, -1, 1) * np.float32(0.2)).to(dev).repeat(512, 1).contiguous()
+    states = states0.clone()
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+    warmup, steps = max(args.warmup, 3), min(args.steps, 20)
+    for _ in range(warmup):
+        states.copy_(states0); pkg.l2f_steps(params, states, actions, T)
+    torch.cuda.synchronize()
+    total = 0.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(steps):
+        states.copy_(states0); flush.zero_()
+        e0.record()
+        pkg.l2f_steps(params, states, actions, T)
+        e1.record(); torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    ms = total / steps
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        if os.path.exists(oracle.REF_FAST_SO):
+            ref = oracle.Reference("fast")
+            n, t = 4096, 100
+            ref.l2f_steps(base_states, base_actions, 2)
+            t0 = time.perf_counter()
+            ref.l2f_steps(base_states, base_actions, t)
+            cpu = {"value": n * t / (time.perf_counter() - t0), "unit": "quadrotor-steps/s", "cores": 1, "kind": "reference",
+                   "sample": f"{n} quadrotors x {t} steps through the reference's step() (project flags), one thread"}
+    peaks = measured_peaks()
+    flop = 4 * 157 + 5 * 21 * 2 + 60           # four dynamics evaluations (the reference's own count), the state algebra of RK4, post-integration
+    print(json.dumps({"metric": "quadrotor-steps/s (L2F step, RK4)", "value": N * T / (ms * 1e-3), "unit": "quadrotor-steps/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"l2f_step_{N}quadrotors_x{T}step", "l2": "flushed between timed iterations", "parallelism": "single GPU",
+                                 "kernel": "one thread per quadrotor, state in registers, no multiply-add contraction (bit-for-bit with the reference's CPU step)"},
+                      "roofline": {"bound": "hbm", "achieved": 2 * 92.0 * N / (ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s", "frac": 2 * 92.0 * N / (ms * 1e-3) / 1e9 / peaks["hbm"],
+                                   "traffic": None, "peak_source": peaks["source"], "note": "CUDA-core fp32 arithmetic in registers: neither HBM nor the tensor pipe bounds it",
+                                   "fp32_tflops": flop * N * T / (ms * 1e-3) / 1e12},
+                      "cpu_baseline": cpu, "gpu_launches": steps}))
+
+
 def run_actor_eval(args):
     """Secondary line: the batched actor inference of the CPU-runnable configuration -- fp32 input [256, 3], MLP 3 -> 64 -> 64 -> 2 (ReLU,
     ReLU, identity), evaluate() = three fused dense launches, 1000 calls per timed step, eager and replayed as a CUDA graph.
@@ -825,7 +884,7 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update", "acrobot_rollout"],
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update", "acrobot_rollout", "l2f_step"],
                     help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
                          "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
                          "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
@@ -844,6 +903,8 @@ def main():
         return run_sac_update(args)
     if args.workload == "acrobot_rollout":
         return run_acrobot_rollout(args)
+    if args.workload == "l2f_step":
+        return run_l2f_step(args)
     if args.workload == "ppo_update":
         return run_ppo_update(args)
     if args.workload == "critic_train":

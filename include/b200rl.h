@@ -384,6 +384,26 @@ int b200rl_pendulum_offpolicy_epilogue(float* states, int32_t* episode_step, uin
                                        const b200rl_replay_layout* layout, const uint8_t* was_truncated_scratch, b200rl_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * L2F quadrotor, the configuration of the reference's own GPU throughput harness (src/rl/environments/l2f/cuda/benchmark.cu:31-60: state =
+ * StateRotors<StateRandomForce<StateBase>>): n_steps x step(device, env, parameters, state, action, next_state, rng)
+ * (rl/environments/l2f/operations_generic.h:93-131) per quadrotor, in place. A state row is position 3, orientation quaternion 4 (w first),
+ * linear velocity 3, angular velocity 3, disturbance force 3, disturbance torque 3 (constant over the steps), rotor speeds 4 = 23 floats;
+ * actions [n, 4] are the normalised rotor set-points a policy emits (clamped to [-1, 1], constant over the steps of a call). parameters
+ * (host): dynamics = the 85 floats of the reference's parameters.dynamics in declaration order (multirotor.h:22-41: rotor positions, thrust
+ * and torque directions [4][3], thrust coefficients [4][3], torque constants, rising / falling time constants [4], mass, gravity [3], J,
+ * J_inv [3][3], hovering throttle, action limits min / max), the integration step and the three STATE_LIMIT_* constants. The action noise of
+ * the default parameter set is 0 and is not applied; observation, reward, termination and the randomised initial state / parameters of the
+ * environment are not part of this entry point. Results equal the reference's CPU step bit for bit (the kernel keeps its association and
+ * is compiled without multiply-add contraction).
+ * ------------------------------------------------------------------------------------------------------- */
+typedef struct b200rl_l2f_parameters {
+    float dynamics[85];
+    float dt;
+    float state_limit_position, state_limit_velocity, state_limit_angular_velocity;
+} b200rl_l2f_parameters;
+int b200rl_l2f_steps(const b200rl_l2f_parameters* parameters, float* states, const float* actions, int n, int n_steps, b200rl_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Replay-buffer sampling: gather_batch(device, runner, batch, rng) for SequentialBatch with SEQUENCE_LENGTH 1 and its default sampling
  * parameters (rl/components/off_policy_runner/operations_generic.h:239-423, off_policy_runner.h:80-156; CUDA form
  * operations_cuda.h:136-182). Per batch element the reference draws the environment index, then a sample offset in [0, eligible - 1]

@@ -116,6 +116,7 @@ class Oracle:
         L.orc_acrobot_rollout_variant.restype = C.c_int
         L.orc_acrobot_terminating_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
         L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
+        L.orc_l2f_steps.argtypes = [C.c_int, C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p]
         L.orc_gather_batch_sequences.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, _f32p, _i64p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
@@ -515,6 +516,18 @@ class Oracle:
                                   out["reset"], out["next_reset_base"], out["final_step_mask"], out["next_final_step_mask_base"], out["env_index"], out["sample_index"])
         return out
 
+    # --- L2F quadrotor -------------------------------------------------------------------------------------------
+    L2F_STATE_LIMITS = np.array([100000, 100000, 100000], np.float32)      # the reference harness' STATE_LIMIT_* (position, velocity, angular velocity)
+
+    def l2f_steps(self, dynamics, dt, states, actions, n_steps=1, state_limits=None):
+        """n_steps x step() of the L2F quadrotor (harness configuration) per row: states [n, 23], actions [n, 4] (normalised, constant over the
+        steps), dynamics = the 85 floats of the reference's parameters.dynamics. Returns the states afterwards."""
+        states, actions = np.ascontiguousarray(states, np.float32), np.ascontiguousarray(actions, np.float32)
+        out = np.empty_like(states)
+        limits = self.L2F_STATE_LIMITS if state_limits is None else np.ascontiguousarray(state_limits, np.float32)
+        self.lib.orc_l2f_steps(states.shape[0], n_steps, np.ascontiguousarray(dynamics, np.float32), np.float32(dt), limits, states, actions, out)
+        return out
+
     GATHER_FROM_INITIAL_STATE, GATHER_RANDOM_LENGTH, GATHER_FIRST_STEP_TARGET, GATHER_DETERMINISTIC = 1, 2, 4, 8
 
     @staticmethod
@@ -656,6 +669,8 @@ class Reference:
         L.ref_sample_and_squash.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
         L.ref_polyak_update.argtypes = [_f32p, _f32p, C.c_float, C.c_int, C.c_int]
         L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
+        L.ref_l2f_parameters.argtypes = [_f32p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        L.ref_l2f_steps.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p]
         L.ref_offpolicy_gather_sequences.argtypes = [C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
         L.ref_normal_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p]
@@ -843,6 +858,19 @@ class Reference:
         if rc != 0:
             raise KeyError("no such gather_batch case")
         return [{k: v[g] for k, v in stack.items()} for g in range(n_gathers)], next_draw.value
+
+    def l2f_parameters(self):
+        """(dynamics [85] floats = the reference's parameters.dynamics of the default parameter set, dt, action noise std)"""
+        d, dt, noise = np.zeros(85, np.float32), C.c_float(), C.c_float()
+        self.lib.ref_l2f_parameters(d, C.byref(dt), C.byref(noise))
+        return d, dt.value, noise.value
+
+    def l2f_steps(self, states, actions, n_steps=1):
+        """n_steps x the reference's step() per row of states [n, 23] with the row's constant action [n, 4]."""
+        states, actions = np.ascontiguousarray(states, np.float32), np.ascontiguousarray(actions, np.float32)
+        out = np.empty_like(states)
+        self.lib.ref_l2f_steps(states.shape[0], n_steps, states, actions, out)
+        return out
 
     GATHER_SEQUENCE_CASES = ((4, 256, 20, 32, 5), (3, 300, 17, 16, 8))       # N, capacity, step limit, batch, sequence length
     GATHER_SEQUENCE_MODES = (3, 0, 1, 8, 9, 2)                                # bit 0 from the initial state, bit 1 random lengths, bit 3 deterministic

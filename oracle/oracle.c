@@ -841,6 +841,121 @@ void orc_gather_batch(int N, int capacity, int max_episode_length, int batch, or
 }
 
 /* ------------------------------------------------------------------------------------------------------ */
+/* L2F quadrotor, the configuration of the reference's own GPU throughput harness                              */
+/* (src/rl/environments/l2f/cuda/benchmark.cu:31-60): state = StateRotors<StateRandomForce<StateBase>>, i.e.   */
+/* position 3, orientation quaternion 4 (w first), linear velocity 3, angular velocity 3, a constant            */
+/* disturbance force 3 and torque 3, rotor speeds 4 = 23 floats; one step = step()                             */
+/* (rl/environments/l2f/operations_generic.h:93-131): the normalised action is clamped to [-1, 1] and mapped to */
+/* the rotor-speed range, the state is integrated by one RK4 step (utils/generic/integrators.h:20-49, state    */
+/* algebra operations_generic/50_state_algebra.h) of the dynamics (operations_generic/60_dynamics.h:17-110:     */
+/* rotor thrust polynomial, thrust and torque sums, quaternion derivative, rotated thrust / mass + gravity,     */
+/* Euler's rigid-body equation, disturbance force and torque, first-order rotor response with rising / falling */
+/* time constants), then post_integration (operations_generic/70_post_integration.h:17-35, 127-141): quaternion */
+/* normalised, position / velocities clamped to the state limits, rotor speeds clamped to the action limits.    */
+/* The action noise of the default parameters is 0 (parameters/default.h:64-66), so no draw enters the result.  */
+/* dynamics: the 85 floats of parameters.dynamics in declaration order (multirotor.h:22-41). Every expression   */
+/* keeps the reference's association (no contraction).                                                          */
+/* ------------------------------------------------------------------------------------------------------ */
+typedef struct { float position[3], orientation[4], linear_velocity[3], angular_velocity[3], force[3], torque[3], rpm[4]; } orc_l2f_state;
+typedef struct { float rotor_positions[4][3], rotor_thrust_directions[4][3], rotor_torque_directions[4][3], rotor_thrust_coefficients[4][3], rotor_torque_constants[4],
+                 rotor_time_constants_rising[4], rotor_time_constants_falling[4], mass, gravity[3], J[3][3], J_inv[3][3], hovering_throttle_relative, action_min, action_max; } orc_l2f_dynamics;
+static void l2f_cross(const float* a, const float* b, float* out){
+    out[0] = a[1] * b[2] - a[2] * b[1]; out[1] = a[2] * b[0] - a[0] * b[2]; out[2] = a[0] * b[1] - a[1] * b[0];
+}
+static void l2f_matvec(const float A[3][3], const float* v, float* out){
+    for(int i = 0; i < 3; i++){ out[i] = 0; for(int j = 0; j < 3; j++) out[i] += A[i][j] * v[j]; }
+}
+static void l2f_dynamics(const orc_l2f_dynamics* p, const orc_l2f_state* s, const float* setpoint, orc_l2f_state* d){
+    float thrust[3] = {0, 0, 0}, torque[3] = {0, 0, 0};
+    for(int r = 0; r < 4; r++){                                              /* the rotor speeds in the state drive the body (60_dynamics.h:100) */
+        const float rpm = s->rpm[r];
+        const float magnitude = p->rotor_thrust_coefficients[r][0] + p->rotor_thrust_coefficients[r][1] * rpm + p->rotor_thrust_coefficients[r][2] * rpm * rpm;
+        float rotor_thrust[3];
+        for(int i = 0; i < 3; i++){ rotor_thrust[i] = p->rotor_thrust_directions[r][i] * magnitude; thrust[i] += rotor_thrust[i]; }
+        const float reaction = magnitude * p->rotor_torque_constants[r];
+        for(int i = 0; i < 3; i++) torque[i] += p->rotor_torque_directions[r][i] * reaction;
+        const float* a = p->rotor_positions[r];
+        torque[0] += a[1] * rotor_thrust[2] - a[2] * rotor_thrust[1];
+        torque[1] += a[2] * rotor_thrust[0] - a[0] * rotor_thrust[2];
+        torque[2] += a[0] * rotor_thrust[1] - a[1] * rotor_thrust[0];
+    }
+    for(int i = 0; i < 3; i++) d->position[i] = s->linear_velocity[i];
+    const float* q = s->orientation; const float* w = s->angular_velocity;
+    d->orientation[0] = -q[1] * w[0] - q[2] * w[1] - q[3] * w[2];
+    d->orientation[1] =  q[0] * w[0] + q[2] * w[2] - q[3] * w[1];
+    d->orientation[2] =  q[0] * w[1] + q[3] * w[0] - q[1] * w[2];
+    d->orientation[3] =  q[0] * w[2] + q[1] * w[1] - q[2] * w[0];
+    for(int i = 0; i < 4; i++) d->orientation[i] *= 0.5f;
+    float var[3], rotated[3];                                                /* rotate_vector_by_quaternion (quaternion_helper.h:22-36) */
+    l2f_cross(q + 1, thrust, var);
+    for(int i = 0; i < 3; i++) var[i] *= 2.0f;
+    l2f_cross(q + 1, var, rotated);
+    for(int i = 0; i < 3; i++) rotated[i] += var[i] * q[0];
+    for(int i = 0; i < 3; i++) rotated[i] += thrust[i];
+    const float inverse_mass = 1 / p->mass;
+    for(int i = 0; i < 3; i++) d->linear_velocity[i] = rotated[i] * inverse_mass;
+    for(int i = 0; i < 3; i++) d->linear_velocity[i] += p->gravity[i];
+    float v1[3], v2[3];
+    l2f_matvec(p->J, w, v1);
+    l2f_cross(w, v1, v2);
+    for(int i = 0; i < 3; i++) v1[i] = torque[i] - v2[i];
+    l2f_matvec(p->J_inv, v1, d->angular_velocity);
+    for(int i = 0; i < 3; i++) d->linear_velocity[i] += s->force[i] / p->mass;       /* StateRandomForce, :77-88 */
+    float extra[3];
+    l2f_matvec(p->J_inv, s->torque, extra);
+    for(int i = 0; i < 3; i++) d->angular_velocity[i] += extra[i];
+    for(int r = 0; r < 4; r++){                                                      /* StateRotors, :89-101 */
+        const float tau = setpoint[r] >= s->rpm[r] ? p->rotor_time_constants_rising[r] : p->rotor_time_constants_falling[r];
+        d->rpm[r] = (setpoint[r] - s->rpm[r]) * 1 / tau;
+    }
+}
+static void l2f_axpy(const orc_l2f_state* k, float scalar, orc_l2f_state* out){            /* scalar_multiply_accumulate of the integrated components */
+    for(int i = 0; i < 3; i++){
+        out->position[i] += scalar * k->position[i]; out->orientation[i] += scalar * k->orientation[i];
+        out->linear_velocity[i] += scalar * k->linear_velocity[i]; out->angular_velocity[i] += scalar * k->angular_velocity[i];
+    }
+    out->orientation[3] += scalar * k->orientation[3];
+    for(int i = 0; i < 4; i++) out->rpm[i] += scalar * k->rpm[i];
+}
+static float l2f_clamp(float x, float lo, float hi){ return x < lo ? lo : (x > hi ? hi : x); }
+void orc_l2f_steps(int n, int n_steps, const float* dynamics, float dt, const float* state_limits, const float* states, const float* actions, float* out){
+    const orc_l2f_dynamics* p = (const orc_l2f_dynamics*)dynamics;
+    for(int e = 0; e < n; e++){
+        orc_l2f_state s;
+        memcpy(&s, states + (size_t)e * 23, sizeof(s));
+        for(int step = 0; step < n_steps; step++){
+            float setpoint[4];
+            for(int i = 0; i < 4; i++){
+                const float half_range = (p->action_max - p->action_min) / 2;
+                float a = actions[(size_t)e * 4 + i];
+                a += 0.0f;                                                           /* the action noise of the default parameters */
+                a = l2f_clamp(a, -1.0f, 1.0f);
+                setpoint[i] = a * half_range + p->action_min + half_range;
+            }
+            orc_l2f_state k1 = s, k2 = s, k3 = s, k4 = s, t;
+            l2f_dynamics(p, &s, setpoint, &k1);
+            t = s; l2f_axpy(&k1, dt / 2, &t); l2f_dynamics(p, &t, setpoint, &k2);
+            t = s; l2f_axpy(&k2, dt / 2, &t); l2f_dynamics(p, &t, setpoint, &k3);
+            t = s; l2f_axpy(&k3, dt, &t);     l2f_dynamics(p, &t, setpoint, &k4);
+            orc_l2f_state next = s;
+            l2f_axpy(&k1, dt / 6, &next); l2f_axpy(&k2, dt / 3, &next); l2f_axpy(&k3, dt / 3, &next); l2f_axpy(&k4, dt / 6, &next);
+            float norm = 0;
+            for(int i = 0; i < 4; i++) norm += next.orientation[i] * next.orientation[i];
+            norm = sqrtf(norm);
+            for(int i = 0; i < 4; i++) next.orientation[i] /= norm;
+            for(int i = 0; i < 3; i++){
+                next.position[i] = l2f_clamp(next.position[i], -state_limits[0], state_limits[0]);
+                next.linear_velocity[i] = l2f_clamp(next.linear_velocity[i], -state_limits[1], state_limits[1]);
+                next.angular_velocity[i] = l2f_clamp(next.angular_velocity[i], -state_limits[2], state_limits[2]);
+            }
+            for(int i = 0; i < 4; i++) next.rpm[i] = l2f_clamp(next.rpm[i], p->action_min, p->action_max);
+            s = next;                                                               /* force and torque carry over (:142-150) */
+        }
+        memcpy(out + (size_t)e * 23, &s, sizeof(s));
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------ */
 /* Replay-buffer sampling for ANY sequence length: gather_batch / gather_batch_step                           */
 /* (rl/components/off_policy_runner/operations_generic.h:239-423) with the sampling parameters as flags       */
 /* (off_policy_runner.h:80-87; for SEQUENCE_LENGTH > 1 the defaults are all three on):                         */

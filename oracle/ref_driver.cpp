@@ -43,6 +43,7 @@
 #include <rl_tools/nn/optimizers/adam/operations_generic.h>
 #include <rl_tools/rl/environments/pendulum/operations_generic.h>
 #include <rl_tools/rl/environments/acrobot/operations_generic.h>
+#include <rl_tools/rl/environments/l2f/operations_generic.h>
 #include <rl_tools/rl/components/on_policy_runner/operations_generic.h>
 #include <rl_tools/rl/components/off_policy_runner/operations_generic.h>
 #include <rl_tools/rl/algorithms/sac/operations_generic.h>
@@ -874,6 +875,40 @@ static int acrobot_rollout(const float* params, TI N, TI Tsteps, float* states, 
     return rc;
 }
 
+// L2F quadrotor: the environment of the reference's own GPU throughput harness (src/rl/environments/l2f/cuda/benchmark.cu:31-60: rotor
+// dynamics by integration, a constant disturbance force / torque in the state, the default "crazyflie" parameter set, state limits far out),
+// stepped through the reference's step() (rl/environments/l2f/operations_generic.h:93-131). State rows are position 3, orientation
+// quaternion 4 (w first), linear velocity 3, angular velocity 3, disturbance force 3, disturbance torque 3, rotor speeds 4 = 23 floats.
+namespace l2f_harness {
+    using namespace rlt::rl::environments::l2f;
+    struct STATIC_PARAMETERS{
+        static constexpr TI N_SUBSTEPS = 1;
+        static constexpr TI ACTION_HISTORY_LENGTH = 16;
+        static constexpr bool CLOSED_FORM = false;
+        using STATE_BASE = StateBase<StateSpecification<T, TI>>;
+        using STATE_TYPE = StateRotors<StateRotorsSpecification<T, TI, CLOSED_FORM, StateRandomForce<StateSpecification<T, TI, STATE_BASE>>>>;
+        using OBSERVATION_TYPE = observation::Position<observation::PositionSpecification<T, TI, observation::OrientationRotationMatrix<observation::OrientationRotationMatrixSpecification<T, TI,
+                                 observation::LinearVelocity<observation::LinearVelocitySpecification<T, TI, observation::AngularVelocity<observation::AngularVelocitySpecification<T, TI>>>>>>>>;
+        using OBSERVATION_TYPE_PRIVILEGED = OBSERVATION_TYPE;
+        static constexpr bool PRIVILEGED_OBSERVATION_NOISE = false;
+        using DEFAULT_STUB = parameters::DEFAULT_PARAMETERS_FACTORY<T, TI>;
+        using PARAMETERS = typename DEFAULT_STUB::PARAMETERS_TYPE;
+        static constexpr auto PARAMETER_VALUES = DEFAULT_STUB::nominal_parameters;
+        static constexpr T STATE_LIMIT_POSITION = 100000;
+        static constexpr T STATE_LIMIT_VELOCITY = 100000;
+        static constexpr T STATE_LIMIT_ANGULAR_VELOCITY = 100000;
+    };
+    using ENVIRONMENT = rlt::rl::environments::Multirotor<rlt::rl::environments::l2f::Specification<T, TI, STATIC_PARAMETERS>>;
+    static void load(ENVIRONMENT::State& s, const float* r){
+        for(int k = 0; k < 3; k++){ s.position[k] = r[k]; s.linear_velocity[k] = r[7 + k]; s.angular_velocity[k] = r[10 + k]; s.force[k] = r[13 + k]; s.torque[k] = r[16 + k]; }
+        for(int k = 0; k < 4; k++){ s.orientation[k] = r[3 + k]; s.rpm[k] = r[19 + k]; }
+    }
+    static void store(const ENVIRONMENT::State& s, float* r){
+        for(int k = 0; k < 3; k++){ r[k] = s.position[k]; r[7 + k] = s.linear_velocity[k]; r[10 + k] = s.angular_velocity[k]; r[13 + k] = s.force[k]; r[16 + k] = s.torque[k]; }
+        for(int k = 0; k < 4; k++){ r[3 + k] = s.orientation[k]; r[19 + k] = s.rpm[k]; }
+    }
+}
+
 extern "C" {
 
 int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const float* actor_params, uint32_t seed, int n_steps, int n_gathers, float* oa_base, float* rewards,
@@ -884,6 +919,35 @@ int ref_offpolicy_gather(int N, int capacity, int step_limit, int batch, const f
     GATHER_CASE(5, 300, 60, 64)
 #undef GATHER_CASE
     return -1;
+}
+
+// the parameter values the step reads, as the reference's own structs hold them: parameters.dynamics (85 floats in declaration order:
+// rotor positions, thrust directions, torque directions [4][3] each, thrust coefficients [4][3], torque constants, rising and falling time
+// constants [4] each, mass, gravity [3], J, J_inv [3][3] each, hovering throttle, action limits min / max), then dt, then the action noise
+int ref_l2f_parameters(float* dynamics, float* dt, float* action_noise){
+    DEVICE device;
+    l2f_harness::ENVIRONMENT env; l2f_harness::ENVIRONMENT::Parameters parameters;
+    rlt::init(device, env); rlt::initial_parameters(device, env, parameters);
+    static_assert(sizeof(parameters.dynamics) == 85 * sizeof(float));
+    std::memcpy(dynamics, &parameters.dynamics, sizeof(parameters.dynamics));
+    *dt = parameters.integration.dt; *action_noise = parameters.mdp.action_noise.normalized_rpm;
+    return 0;
+}
+// n quadrotors, n_steps x step() each with its own constant action [n, 4] (normalised, as a policy emits it); states [n, 23] in, out [n, 23]
+int ref_l2f_steps(int n, int n_steps, const float* states, const float* actions, float* out){
+    DEVICE device;
+    l2f_harness::ENVIRONMENT env; l2f_harness::ENVIRONMENT::Parameters parameters;
+    rlt::init(device, env); rlt::initial_parameters(device, env, parameters);
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 4, false>> action;
+    for(int i = 0; i < n; i++){
+        l2f_harness::ENVIRONMENT::State state, next;
+        l2f_harness::load(state, states + (size_t)i * 23);
+        for(TI k = 0; k < 4; k++) rlt::set(action, 0, k, actions[(size_t)i * 4 + k]);
+        for(int s = 0; s < n_steps; s++){ rlt::step(device, env, parameters, state, action, next, rng); state = next; }
+        l2f_harness::store(state, out + (size_t)i * 23);
+    }
+    return 0;
 }
 
 // cases: 0 = (N 4, capacity 256, limit 20, batch 32, sequence 5), 1 = (N 3, capacity 300, limit 17, batch 16, sequence 8); modes as in gather_seq_case.

@@ -12,8 +12,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "dense_tc.cu", "dense_skinny.cu", "mlp_fused.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "dense_skinny.cu", "mlp_fused.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu", "l2f.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
+# per-source flags: the quadrotor dynamics keep the reference's association of every expression (bit-for-bit parity with its CPU step)
+SOURCE_FLAGS = {"l2f.cu": ["-fmad=false"]}
 
 ACT = {"identity": 0, "relu": 1, "tanh": 2, "fast_tanh": 3, "sigmoid": 4}
 MAX_LAYERS = 8
@@ -60,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         if not force and os.path.exists(obj) and all(os.path.getmtime(obj) >= os.path.getmtime(d) for d in [src] + headers):
             return obj, None
-        res = subprocess.run([nvcc] + compile_flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj], capture_output=True, text=True)
+        res = subprocess.run([nvcc] + compile_flags + (["-Xptxas", "-v"] if verbose else []) + SOURCE_FLAGS.get(os.path.basename(src), []) + ["-c", src, "-o", obj], capture_output=True, text=True)
         if res.returncode != 0:
             raise B200RLError("nvcc failed on " + src + ":\n" + res.stdout + res.stderr)
         return obj, res.stderr
@@ -192,6 +194,7 @@ def lib():
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         u64 = C.c_uint64
         L.b200rl_pendulum_collect_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, i, vp, vp]
+        L.b200rl_l2f_steps.argtypes = [C.POINTER(L2fParameters), vp, vp, i, i, vp]
         L.b200rl_gather_batch_sequences.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, i, i, f, u64, u64, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
         L.b200rl_pendulum_offpolicy_prologue.argtypes = [vp, vp, vp, vp, vp, u64, u64, vp, i, vp, vp, vp]
         L.b200rl_pendulum_offpolicy_epilogue.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, C.POINTER(ReplayLayout), vp, vp]
@@ -660,6 +663,29 @@ def gather_batch(replay, layout, n_envs, out, env_index=None, sample_offset=None
         check(lib().b200rl_gather_batch_device_rng(_ptr(replay), C.byref(layout), n_envs, max_episode_length, obs_dim, action_dim, seed, call_index, *tail),
               "b200rl_gather_batch_device_rng")
     return out
+
+
+class L2fParameters(C.Structure):
+    """Mirror of b200rl_l2f_parameters: dynamics = the 85 floats of the reference's parameters.dynamics; defaults of the limits = the reference
+    harness' STATE_LIMIT_* constants."""
+    _fields_ = [("dynamics", C.c_float * 85), ("dt", C.c_float), ("state_limit_position", C.c_float), ("state_limit_velocity", C.c_float),
+                ("state_limit_angular_velocity", C.c_float)]
+
+    @staticmethod
+    def make(dynamics, dt, limits=(100000.0, 100000.0, 100000.0)):
+        p = L2fParameters()
+        for i, v in enumerate(dynamics):
+            p.dynamics[i] = float(v)
+        p.dt = float(dt)
+        p.state_limit_position, p.state_limit_velocity, p.state_limit_angular_velocity = (float(x) for x in limits)
+        return p
+
+
+def l2f_steps(parameters, states, actions, n_steps=1):
+    """n_steps x the L2F quadrotor step per row of the CUDA tensor states [n, 23] (in place) with the row's normalised action [n, 4]."""
+    assert states.is_contiguous() and actions.is_contiguous() and states.shape[1] == 23 and actions.shape == (states.shape[0], 4)
+    check(lib().b200rl_l2f_steps(C.byref(parameters), _ptr(states), _ptr(actions), states.shape[0], n_steps, _stream()), "b200rl_l2f_steps")
+    return states
 
 
 GATHER_FROM_INITIAL_STATE, GATHER_RANDOM_LENGTH, GATHER_FIRST_STEP_TARGET, GATHER_DETERMINISTIC = 1, 2, 4, 8

@@ -275,6 +275,16 @@ def test_sequence_batch_checker_accepts_the_oracle(orc, which, steps, flags):
     mg.check_sequence_batch(orc.gather_batch_sequences(st, 2048, L, flags, rng), st, L, flags)
 
 
+def test_l2f_step_matches_reference(orc):
+    """The L2F quadrotor step (the reference's GPU-harness configuration, default parameter set) from 768 random states with random
+    actions, 1 and 50 steps: bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "l2f.npz"))
+    states, actions = mg.l2f_inputs()
+    assert np.array_equal(orc.l2f_steps(fix["dynamics"], float(fix["dt"]), states, actions, 1), fix["next_1"])
+    assert np.array_equal(orc.l2f_steps(fix["dynamics"], float(fix["dt"]), states, actions, 50), fix["next_50"])
+    assert not np.isnan(fix["next_50"]).any() and np.abs(np.linalg.norm(fix["next_50"][:, 3:7], axis=1) - 1).max() < 1e-6
+
+
 @pytest.mark.parametrize("case", range(len(mg.POLYAK_CASES)))
 def test_polyak_update_matches_reference(orc, case):
     """utils::polyak::update / update_squared, repeated: bit for bit."""

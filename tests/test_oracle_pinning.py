@@ -176,6 +176,16 @@ def test_gather_batch_sequences_live(orc, ref_strict):
                 assert (orc.lib.orc_rng_next(rng) & 0xFFFFFFFF) == next_draw
 
 
+def test_l2f_step_live(orc, ref_strict):
+    """4,000 other random quadrotor states and actions through 1, 7 and 120 steps: the restatement equals the reference's step() bit for bit."""
+    import make_golden as mg
+    dynamics, dt, noise = ref_strict.l2f_parameters()
+    assert noise == 0.0
+    states, actions = mg.l2f_inputs(4000, seed=5)
+    for n_steps in (1, 7, 120):
+        assert np.array_equal(orc.l2f_steps(dynamics, dt, states, actions, n_steps), ref_strict.l2f_steps(states, actions, n_steps)), n_steps
+
+
 def test_sac_updates_live(orc, ref_strict):
     import make_golden as mg
     for case, (B, H) in enumerate(oracle.Reference.SAC_CASES):

@@ -16,7 +16,7 @@ the 64 -> 256 -> 256 -> 256 -> 16 MLP on 2^24 rows split over the ranks with ONE
 step (strong scaling, the all-reduce timed on its own), and `rollout_strong` = the same 65,536 environments split over the
 ranks. `--impl reference` times only the reference CPU implementation, on the same metric and config.
 
-`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout, l2f_step}` print secondary lines in the same JSON form (sharded MLP training,
+`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout, l2f_step, l2f_rollout}` print secondary lines in the same JSON form (sharded MLP training,
 on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference, the SAC training step, the generic rollout on AcrobotSwingup); the default workload is the headline rollout.
 """
 import argparse
@@ -809,6 +809,55 @@ def run_l2f_step(args):
                       "cpu_baseline": cpu, "gpu_launches": steps}))
 
 
+def run_l2f_rollout(args):
+    """Secondary line: the fused runner loop on the L2F quadrotor -- `--envs` quadrotors x 100 steps per launch (observe, actor 18 -> 64 -> 64 -> 4,
+    RK4 step, reward, termination; episode limit 500, initial states of the reference's sampler from the committed fixture). Single GPU."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    here = os.path.dirname(os.path.abspath(__file__))
+    fix = np.load(os.path.join(here, "tests", "golden", "l2f.npz"))
+    N, T, limit, H = args.envs, 100, 500, 64
+    rs = np.random.RandomState(4)
+    shape = pkg.MlpShape.make(18, [H, H, 4], ["relu", "relu", "tanh"])
+    params_h = (rs.uniform(-1, 1, 18 * H + H + H * H + H + 4 * H + 4) * 0.05).astype(np.float32)
+    params = torch.from_numpy(params_h).to(dev)
+    p = pkg.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    init = fix["initial_states"].reshape(-1, 23)
+    table = torch.from_numpy(init[rs.randint(0, init.shape[0], (3, N))]).to(dev).contiguous()            # three reset rounds per environment
+    states, es, er = torch.zeros((N, 23), device=dev), torch.zeros(N, dtype=torch.int32, device=dev), torch.zeros(N, device=dev)
+    tr = torch.ones(N, dtype=torch.uint8, device=dev)
+    obs, act, rew = torch.empty((T * N, 18), device=dev), torch.empty((T * N, 4), device=dev), torch.empty(T * N, device=dev)
+    term = torch.empty(T * N, dtype=torch.uint8, device=dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+    warmup, steps = max(args.warmup, 3), min(args.steps, 20)
+    total = 0.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(warmup + steps):
+        flush.zero_(); es.zero_(); tr.fill_(1)
+        e0.record()
+        pkg.l2f_rollout(p, fix["mdp"], shape, params, states, es, tr, er, table, T, limit, obs=obs, act=act, rew=rew, terminated=term, error_flag=flag)
+        e1.record(); torch.cuda.synchronize()
+        if it >= warmup:
+            total += e0.elapsed_time(e1)
+    ms = total / steps
+    peaks = measured_peaks()
+    out_bytes = (18 + 4 + 1) * 4 + 1
+    print(json.dumps({"metric": "env-steps/s (fused actor fwd + L2F quadrotor step)", "value": N * T / (ms * 1e-3), "unit": "env-steps/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"l2f_rollout_{N}env_x{T}step_actor18-64-64-4", "l2": "flushed between timed iterations", "parallelism": "single GPU",
+                                 "kernel": "one thread per quadrotor, actor in shared memory, dynamics without multiply-add contraction", "resets_exhausted": int(flag.item())},
+                      "roofline": {"bound": "hbm", "achieved": out_bytes * N * T / (ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s", "frac": out_bytes * N * T / (ms * 1e-3) / 1e9 / peaks["hbm"],
+                                   "traffic": None, "peak_source": peaks["source"], "note": "CUDA-core fp32 arithmetic: neither HBM nor the tensor pipe bounds it"},
+                      "cpu_baseline": None, "gpu_launches": steps}))
+
+
 def run_actor_eval(args):
     """Secondary line: the batched actor inference of the CPU-runnable configuration -- fp32 input [256, 3], MLP 3 -> 64 -> 64 -> 2 (ReLU,
     ReLU, identity), evaluate() = three fused dense launches, 1000 calls per timed step, eager and replayed as a CUDA graph.
@@ -884,7 +933,7 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update", "acrobot_rollout", "l2f_step"],
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update", "acrobot_rollout", "l2f_step", "l2f_rollout"],
                     help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
                          "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
                          "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
@@ -905,6 +954,8 @@ def main():
         return run_acrobot_rollout(args)
     if args.workload == "l2f_step":
         return run_l2f_step(args)
+    if args.workload == "l2f_rollout":
+        return run_l2f_rollout(args)
     if args.workload == "ppo_update":
         return run_ppo_update(args)
     if args.workload == "critic_train":

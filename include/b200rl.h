@@ -402,6 +402,20 @@ typedef struct b200rl_l2f_parameters {
     float state_limit_position, state_limit_velocity, state_limit_angular_velocity;
 } b200rl_l2f_parameters;
 int b200rl_l2f_steps(const b200rl_l2f_parameters* parameters, float* states, const float* actions, int n, int n_steps, b200rl_stream_t stream);
+/* The runner loop on this environment, fused like b200rl_env_rollout: per step reset-if-truncated from reset_states [R, N, 23] (the k-th reset
+ * of environment e inside the call takes reset_states[k][e]; initial states are the caller's, e.g. the reference's sample_initial_state drawn on
+ * the host), observe (rl/environments/l2f/operations_generic/40_observe.h:42-147: position 3, rotation matrix 9, linear velocity 3, angular
+ * velocity 3 = 18 values; the default observation noise is 0), actor forward 18 -> H -> H -> 4 (H in {16, 32, 64}; fp32 FMA chains in the
+ * reference's order), step, reward (parameters/reward_functions/squared/operations_generic.h:12-103, desired state at the origin), terminated
+ * on the next state (operations_generic.h:143-158); an episode ends (truncated) at termination or at step_limit
+ * (rl/components/off_policy_runner/operations_generic_per_env.h:62-108). mdp (host, 18 floats): the reward function's non_negative flag, scale,
+ * constant, termination penalty and its weights position, position clip, orientation, linear velocity, angular velocity, linear acceleration,
+ * angular acceleration, action, d_action, position error integral; then termination enabled, position / linear velocity / angular velocity
+ * thresholds. obs [T * N, 18], act [T * N, 4], rew [T * N], terminated [T * N] (may be NULL), row = step * N + env; error_flag as for the
+ * other rollouts. Next states equal the reference's bit for bit given the action; observations bit for bit; the reward within the GPU's acosf. */
+int b200rl_l2f_rollout(const b200rl_l2f_parameters* parameters, const float* mdp, const b200rl_mlp_shape* actor, const float* actor_params, float* states,
+                       int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps,
+                       int step_limit, float* obs, float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Replay-buffer sampling: gather_batch(device, runner, batch, rng) for SequentialBatch with SEQUENCE_LENGTH 1 and its default sampling

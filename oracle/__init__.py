@@ -116,6 +116,8 @@ class Oracle:
         L.orc_acrobot_rollout_variant.restype = C.c_int
         L.orc_acrobot_terminating_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
         L.orc_polyak_update.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
+        L.orc_l2f_functions.argtypes = [C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _u8p]
+        L.orc_l2f_rollout.argtypes = [C.c_void_p, _f32p, _f32p, C.c_float, _f32p, _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, _u8p]
         L.orc_l2f_steps.argtypes = [C.c_int, C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p]
         L.orc_gather_batch_sequences.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, _f32p, _i64p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
@@ -528,6 +530,30 @@ class Oracle:
         self.lib.orc_l2f_steps(states.shape[0], n_steps, np.ascontiguousarray(dynamics, np.float32), np.float32(dt), limits, states, actions, out)
         return out
 
+    def l2f_functions(self, dynamics, dt, mdp, states, actions, next_states):
+        """(observe(state) [n, 18], reward(state, action, next_state) [n], terminated(next_state) [n]) of the L2F environment, row by row."""
+        n = states.shape[0]
+        obs, rew, term = np.empty((n, 18), np.float32), np.empty(n, np.float32), np.empty(n, np.uint8)
+        self.lib.orc_l2f_functions(n, np.ascontiguousarray(dynamics, np.float32), np.float32(dt), np.ascontiguousarray(mdp, np.float32), np.ascontiguousarray(states, np.float32),
+                                   np.ascontiguousarray(actions, np.float32), np.ascontiguousarray(next_states, np.float32), obs, rew, term)
+        return obs, rew, term
+
+    def l2f_rollout(self, shape, params, dynamics, dt, mdp, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500, state_limits=None):
+        """The runner loop on the L2F environment: reset_states [R, N, 23]; returns obs, act, rew, terminated and the runner state afterwards."""
+        N = states.shape[0]
+        states, episode_step, truncated, episode_return = (np.array(states, np.float32), np.array(episode_step, np.int32), np.array(truncated, np.uint8),
+                                                           np.array(episode_return, np.float32))
+        reset_states = np.ascontiguousarray(reset_states, np.float32)
+        assert reset_states.shape[1:] == (N, 23)
+        limits = self.L2F_STATE_LIMITS if state_limits is None else np.ascontiguousarray(state_limits, np.float32)
+        obs, act, rew, term = np.empty((T * N, 18), np.float32), np.empty((T * N, 4), np.float32), np.empty(T * N, np.float32), np.empty(T * N, np.uint8)
+        rc = self.lib.orc_l2f_rollout(C.byref(shape), np.ascontiguousarray(params, np.float32), np.ascontiguousarray(dynamics, np.float32), np.float32(dt), limits,
+                                      np.ascontiguousarray(mdp, np.float32), N, T, states, episode_step, truncated, episode_return, reset_states, reset_states.shape[0], step_limit,
+                                      obs, act, rew, term)
+        if rc != 0:
+            raise RuntimeError(f"orc_l2f_rollout rc={rc}")
+        return dict(obs=obs, act=act, rew=rew, terminated=term, states=states, episode_step=episode_step, truncated=truncated, episode_return=episode_return)
+
     GATHER_FROM_INITIAL_STATE, GATHER_RANDOM_LENGTH, GATHER_FIRST_STEP_TARGET, GATHER_DETERMINISTIC = 1, 2, 4, 8
 
     @staticmethod
@@ -670,6 +696,9 @@ class Reference:
         L.ref_polyak_update.argtypes = [_f32p, _f32p, C.c_float, C.c_int, C.c_int]
         L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_l2f_parameters.argtypes = [_f32p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        L.ref_l2f_mdp.argtypes = [_f32p]
+        L.ref_l2f_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _u8p]
+        L.ref_l2f_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
         L.ref_l2f_steps.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p]
         L.ref_offpolicy_gather_sequences.argtypes = [C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_collect.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, _f32p, _f32p, _i32p, _u8p, _f32p, C.POINTER(C.c_uint64)]
@@ -864,6 +893,25 @@ class Reference:
         d, dt, noise = np.zeros(85, np.float32), C.c_float(), C.c_float()
         self.lib.ref_l2f_parameters(d, C.byref(dt), C.byref(noise))
         return d, dt.value, noise.value
+
+    def l2f_mdp(self):
+        """The 18 floats of the default parameter set's reward function and termination thresholds (see ref_l2f_mdp)."""
+        m = np.zeros(18, np.float32)
+        self.lib.ref_l2f_mdp(m)
+        return m
+
+    def l2f_functions(self, states, actions, next_states):
+        """(observe(state) [n, 18], reward(state, action, next_state) [n], terminated(next_state) [n]) through the reference's own functions."""
+        n = states.shape[0]
+        obs, rew, term = np.empty((n, 18), np.float32), np.empty(n, np.float32), np.empty(n, np.uint8)
+        self.lib.ref_l2f_functions(n, np.ascontiguousarray(states, np.float32), np.ascontiguousarray(actions, np.float32), np.ascontiguousarray(next_states, np.float32), obs, rew, term)
+        return obs, rew, term
+
+    def l2f_initial_states(self, seed, n):
+        """n x sample_initial_state of the L2F environment on one engine (nominal parameters): [n, 23]."""
+        out = np.empty((n, 23), np.float32)
+        self.lib.ref_l2f_initial_states(seed, n, out)
+        return out
 
     def l2f_steps(self, states, actions, n_steps=1):
         """n_steps x the reference's step() per row of states [n, 23] with the row's constant action [n, 4]."""

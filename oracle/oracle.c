@@ -955,6 +955,101 @@ void orc_l2f_steps(int n, int n_steps, const float* dynamics, float dt, const fl
     }
 }
 
+/* L2F as an environment of the runner loop (same configuration): observe (operations_generic/40_observe.h:42-147: position, rotation     */
+/* matrix of the quaternion, linear and angular velocity = 18 values; the observation noise of the default parameters is 0), reward          */
+/* (parameters/reward_functions/squared/operations_generic.h:12-103 with the desired state at the origin,                                   */
+/* operations_generic/35_get_desired_state.h:17-27; the d_action and position-integral components are 0 for this state type), terminated      */
+/* (operations_generic.h:143-158, on the NEXT state). mdp = 18 floats: non_negative, scale, constant, termination penalty, the weights         */
+/* position, position clip, orientation, linear velocity, angular velocity, linear acceleration, angular acceleration, action, d_action,      */
+/* position error integral; termination enabled, position / linear velocity / angular velocity thresholds.                                   */
+void orc_l2f_observe(const float* state, float* o){
+    const float* q = state + 3;
+    for(int i = 0; i < 3; i++) o[i] = state[i] + 0.0f;
+    o[3]  = (1 - 2 * q[2] * q[2] - 2 * q[3] * q[3]); o[4]  = (2 * q[1] * q[2] - 2 * q[0] * q[3]); o[5]  = (2 * q[1] * q[3] + 2 * q[0] * q[2]);
+    o[6]  = (2 * q[1] * q[2] + 2 * q[0] * q[3]); o[7]  = (1 - 2 * q[1] * q[1] - 2 * q[3] * q[3]); o[8]  = (2 * q[2] * q[3] - 2 * q[0] * q[1]);
+    o[9]  = (2 * q[1] * q[3] - 2 * q[0] * q[2]); o[10] = (2 * q[2] * q[3] + 2 * q[0] * q[1]); o[11] = (1 - 2 * q[1] * q[1] - 2 * q[2] * q[2]);
+    for(int i = 3; i < 12; i++) o[i] += 0.0f;
+    for(int i = 0; i < 3; i++){ o[12 + i] = state[7 + i] + 0.0f; o[15 + i] = state[10 + i] + 0.0f; }
+}
+int orc_l2f_terminated(const float* mdp, const float* state){
+    if(mdp[14] != 0.0f){
+        for(int i = 0; i < 3; i++)
+            if(fabsf(state[i] - 0) > mdp[15] || fabsf(state[7 + i] - 0) > mdp[16] || fabsf(state[10 + i]) > mdp[17]) return 1;
+    }
+    return 0;
+}
+float orc_l2f_reward(const float* dynamics, float dt, const float* mdp, const float* state, const float* action, const float* next){
+    const orc_l2f_dynamics* p = (const orc_l2f_dynamics*)dynamics;
+    const float orientation_cost = 2 * acosf(1 - fabsf(state[3 + 3]));
+    const float x = state[0] - 0, y = state[1] - 0, z = state[2] - 0;
+    float position_cost = sqrtf(x * x + y * y + z * z);
+    if(mdp[5] > 0) position_cost = position_cost < mdp[5] ? position_cost : mdp[5];
+    const float vx = state[7] - 0, vy = state[8] - 0, vz = state[9] - 0;
+    const float linear_vel_cost = sqrtf(vx * vx + vy * vy + vz * vz);
+    const float angular_vel_cost = sqrtf(state[10] * state[10] + state[11] * state[11] + state[12] * state[12]);
+    float la[3], aa[3];
+    for(int i = 0; i < 3; i++){ la[i] = next[7 + i] - state[7 + i]; aa[i] = next[10 + i] - state[10 + i]; }
+    const float linear_acc_cost = sqrtf(la[0] * la[0] + la[1] * la[1] + la[2] * la[2]) / dt;
+    const float angular_acc_cost = sqrtf(aa[0] * aa[0] + aa[1] * aa[1] + aa[2] * aa[2]) / dt;
+    float acc = 0;
+    for(int i = 0; i < 4; i++){
+        const float relative = (action[i] + 1.0f) / 2.0f;
+        const float diff = relative - p->hovering_throttle_relative;
+        acc += diff * diff;
+    }
+    float action_cost = sqrtf(acc);
+    action_cost *= action_cost;
+    float weighted = 0;
+    weighted += mdp[4] * position_cost; weighted += mdp[6] * orientation_cost; weighted += mdp[7] * linear_vel_cost; weighted += mdp[8] * angular_vel_cost;
+    weighted += mdp[9] * linear_acc_cost; weighted += mdp[10] * angular_acc_cost; weighted += mdp[11] * action_cost; weighted += mdp[12] * 0.0f; weighted += mdp[13] * 0.0f;
+    const float scaled = mdp[1] * weighted;
+    if(orc_l2f_terminated(mdp, next)) return mdp[3];
+    float reward = -scaled + mdp[2];
+    return (reward > 0 || mdp[0] == 0.0f) ? reward : 0;
+}
+void orc_l2f_functions(int n, const float* dynamics, float dt, const float* mdp, const float* states, const float* actions, const float* next_states, float* observations,
+                       float* rewards, uint8_t* terminated){
+    for(int i = 0; i < n; i++){
+        orc_l2f_observe(states + (size_t)i * 23, observations + (size_t)i * 18);
+        rewards[i] = orc_l2f_reward(dynamics, dt, mdp, states + (size_t)i * 23, actions + (size_t)i * 4, next_states + (size_t)i * 23);
+        terminated[i] = (uint8_t)orc_l2f_terminated(mdp, next_states + (size_t)i * 23);
+    }
+}
+/* The runner loop on the L2F environment (rl/components/off_policy_runner/operations_generic_per_env.h:8-108, as for the other           */
+/* environments): per step reset-if-truncated from reset_states [R, N, 23], observe, actor forward (18 -> ... -> 4), step, reward,          */
+/* terminated on the next state, counters; an episode ends (truncated) at termination or at step_limit. obs [T * N, 18], act [T * N, 4],     */
+/* rew / terminated [T * N], row = step * N + env. Returns 1 if an environment needed more than R resets.                                   */
+int orc_l2f_rollout(const orc_mlp_shape* actor, const float* params, const float* dynamics, float dt, const float* state_limits, const float* mdp, int N, int T, float* states,
+                    int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int R, int step_limit, float* obs, float* act, float* rew,
+                    uint8_t* terminated){
+    int rc = 0;
+    int* resets = (int*)calloc((size_t)N, sizeof(int));
+    for(int t = 0; t < T; t++){
+        float* obs_t = obs + (size_t)t * N * 18; float* act_t = act + (size_t)t * N * 4;
+        for(int e = 0; e < N; e++){
+            if(truncated[e]){
+                if(resets[e] < R) memcpy(states + (size_t)e * 23, reset_states + ((size_t)resets[e] * N + e) * 23, sizeof(float) * 23);
+                else rc = 1;
+                resets[e]++; episode_step[e] = 0; episode_return[e] = 0.0f;
+            }
+            orc_l2f_observe(states + (size_t)e * 23, obs_t + (size_t)e * 18);
+        }
+        orc_mlp_evaluate(actor, params, obs_t, 18, act_t, 4, N);
+        for(int e = 0; e < N; e++){
+            float next[23];
+            orc_l2f_steps(1, 1, dynamics, dt, state_limits, states + (size_t)e * 23, act_t + (size_t)e * 4, next);
+            const float r = orc_l2f_reward(dynamics, dt, mdp, states + (size_t)e * 23, act_t + (size_t)e * 4, next);
+            const int term = orc_l2f_terminated(mdp, next);
+            episode_step[e] += 1; episode_return[e] += r;
+            truncated[e] = (uint8_t)(term || episode_step[e] == step_limit);
+            rew[(size_t)t * N + e] = r; terminated[(size_t)t * N + e] = (uint8_t)term;
+            memcpy(states + (size_t)e * 23, next, sizeof(next));
+        }
+    }
+    free(resets);
+    return rc;
+}
+
 /* ------------------------------------------------------------------------------------------------------ */
 /* Replay-buffer sampling for ANY sequence length: gather_batch / gather_batch_step                           */
 /* (rl/components/off_policy_runner/operations_generic.h:239-423) with the sampling parameters as flags       */

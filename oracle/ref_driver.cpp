@@ -933,6 +933,54 @@ int ref_l2f_parameters(float* dynamics, float* dt, float* action_noise){
     *dt = parameters.integration.dt; *action_noise = parameters.mdp.action_noise.normalized_rpm;
     return 0;
 }
+// the MDP side of the default parameter set as 18 floats: reward (Squared: non_negative flag, scale, constant, termination penalty, the weights
+// position, position clip, orientation, linear velocity, angular velocity, linear acceleration, angular acceleration, action, d_action,
+// position error integral), termination (enabled flag, position / linear velocity / angular velocity thresholds)
+int ref_l2f_mdp(float* mdp){
+    DEVICE device;
+    l2f_harness::ENVIRONMENT env; l2f_harness::ENVIRONMENT::Parameters parameters;
+    rlt::init(device, env); rlt::initial_parameters(device, env, parameters);
+    const auto& r = parameters.mdp.reward; const auto& t = parameters.mdp.termination;
+    const float values[18] = {r.non_negative ? 1.0f : 0.0f, r.scale, r.constant, r.termination_penalty, r.position, r.position_clip, r.orientation, r.linear_velocity, r.angular_velocity,
+                              r.linear_acceleration, r.angular_acceleration, r.action, r.d_action, r.position_error_integral, t.enabled ? 1.0f : 0.0f, t.position_threshold,
+                              t.linear_velocity_threshold, t.angular_velocity_threshold};
+    std::memcpy(mdp, values, sizeof(values));
+    return 0;
+}
+// observe(state) [n, 18] (position, rotation matrix, linear velocity, angular velocity), reward(state, action, next_state) [n] and
+// terminated(next_state) [n] through the reference's own functions, row by row
+int ref_l2f_functions(int n, const float* states, const float* actions, const float* next_states, float* observations, float* rewards, uint8_t* terminated_out){
+    DEVICE device;
+    l2f_harness::ENVIRONMENT env; l2f_harness::ENVIRONMENT::Parameters parameters;
+    rlt::init(device, env); rlt::initial_parameters(device, env, parameters);
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, 0);
+    rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 4, false>> action;
+    rlt::Matrix<rlt::matrix::Specification<T, TI, 1, 18, false>> observation;
+    static_assert(l2f_harness::ENVIRONMENT::Observation::DIM == 18);
+    for(int i = 0; i < n; i++){
+        l2f_harness::ENVIRONMENT::State state, next;
+        l2f_harness::load(state, states + (size_t)i * 23); l2f_harness::load(next, next_states + (size_t)i * 23);
+        for(TI k = 0; k < 4; k++) rlt::set(action, 0, k, actions[(size_t)i * 4 + k]);
+        rlt::observe(device, env, parameters, state, typename l2f_harness::ENVIRONMENT::Observation{}, observation, rng);
+        for(TI k = 0; k < 18; k++) observations[(size_t)i * 18 + k] = rlt::get(observation, 0, k);
+        rewards[i] = rlt::reward(device, env, parameters, state, action, next, rng);
+        terminated_out[i] = rlt::terminated(device, env, parameters, next, rng) ? 1 : 0;
+    }
+    return 0;
+}
+// n x sample_initial_state on one engine (nominal parameters)
+int ref_l2f_initial_states(uint32_t seed, int n, float* out){
+    DEVICE device;
+    l2f_harness::ENVIRONMENT env; l2f_harness::ENVIRONMENT::Parameters parameters;
+    rlt::init(device, env); rlt::initial_parameters(device, env, parameters);
+    RNG rng; rlt::malloc(device, rng); rlt::init(device, rng, seed);
+    for(int i = 0; i < n; i++){
+        l2f_harness::ENVIRONMENT::State state;
+        rlt::sample_initial_state(device, env, parameters, state, rng);
+        l2f_harness::store(state, out + (size_t)i * 23);
+    }
+    return 0;
+}
 // n quadrotors, n_steps x step() each with its own constant action [n, 4] (normalised, as a policy emits it); states [n, 23] in, out [n, 23]
 int ref_l2f_steps(int n, int n_steps, const float* states, const float* actions, float* out){
     DEVICE device;

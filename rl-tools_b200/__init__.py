@@ -194,6 +194,7 @@ def lib():
         L.b200rl_pendulum_collect_layers.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, vp, i, vp, i, i, i, vp, i, vp, vp]
         u64 = C.c_uint64
         L.b200rl_pendulum_collect_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, i, vp, vp]
+        L.b200rl_l2f_rollout.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 18), shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp]
         L.b200rl_l2f_steps.argtypes = [C.POINTER(L2fParameters), vp, vp, i, i, vp]
         L.b200rl_gather_batch_sequences.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, i, i, f, u64, u64, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
         L.b200rl_pendulum_offpolicy_prologue.argtypes = [vp, vp, vp, vp, vp, u64, u64, vp, i, vp, vp, vp]
@@ -686,6 +687,24 @@ def l2f_steps(parameters, states, actions, n_steps=1):
     assert states.is_contiguous() and actions.is_contiguous() and states.shape[1] == 23 and actions.shape == (states.shape[0], 4)
     check(lib().b200rl_l2f_steps(C.byref(parameters), _ptr(states), _ptr(actions), states.shape[0], n_steps, _stream()), "b200rl_l2f_steps")
     return states
+
+
+def l2f_rollout(parameters, mdp, shape, params, states, episode_step, truncated, episode_return, reset_states, n_steps, step_limit=500, obs=None, act=None, rew=None,
+                terminated=None, error_flag=None):
+    """The fused runner loop on the L2F quadrotor (actor 18 -> H -> H -> 4): in place on the runner state tensors; mdp = 18 floats (numpy / list) of
+    the reward function and the termination thresholds; reset_states [R, N, 23] or None. Returns (obs [T*N, 18], act [T*N, 4], rew [T*N], terminated [T*N])."""
+    import torch
+    N, dev = states.shape[0], states.device
+    obs = torch.empty((n_steps * N, 18), device=dev) if obs is None else obs
+    act = torch.empty((n_steps * N, 4), device=dev) if act is None else act
+    rew = torch.empty(n_steps * N, device=dev) if rew is None else rew
+    terminated = torch.empty(n_steps * N, device=dev, dtype=torch.uint8) if terminated is None else terminated
+    mdp_c = (C.c_float * 18)(*[float(v) for v in mdp])
+    R = 0 if reset_states is None else reset_states.shape[0]
+    check(lib().b200rl_l2f_rollout(C.byref(parameters), mdp_c, C.byref(shape), _ptr(params), _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return),
+                                   _ptr(reset_states), R, N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(terminated), _ptr(error_flag), _stream()),
+          "b200rl_l2f_rollout")
+    return obs, act, rew, terminated
 
 
 GATHER_FROM_INITIAL_STATE, GATHER_RANDOM_LENGTH, GATHER_FIRST_STEP_TARGET, GATHER_DETERMINISTIC = 1, 2, 4, 8

@@ -100,10 +100,45 @@ __device__ __forceinline__ void l2f_axpy(const L2fState& k, float scalar, L2fSta
     for(int i = 0; i < 4; i++) out.rpm[i] += scalar * k.rpm[i];
 }
 
+// one step() of the environment: action clamp and rotor-range map (operations_generic.h:103-109; the default action noise is 0), RK4, post_integration
+__device__ __forceinline__ void l2f_step(const L2fArgs& a, const L2fState& s, const float (&action)[4], L2fState& next){
+    const L2fDynamics& p = a.p;
+    float setpoint[4];
+    const float half_range = (p.action_max - p.action_min) / 2;
+#pragma unroll
+    for(int i = 0; i < 4; i++){
+        float act = action[i];
+        act += 0.0f;
+        act = l2f_clamp(act, -1.0f, 1.0f);
+        setpoint[i] = act * half_range + p.action_min + half_range;
+    }
+    const float dt = a.dt;
+    L2fState k1 = s, k2 = s, k3 = s, k4 = s, t;
+    l2f_dynamics(p, s, setpoint, k1);
+    t = s; l2f_axpy(k1, dt / 2, t); l2f_dynamics(p, t, setpoint, k2);
+    t = s; l2f_axpy(k2, dt / 2, t); l2f_dynamics(p, t, setpoint, k3);
+    t = s; l2f_axpy(k3, dt, t);     l2f_dynamics(p, t, setpoint, k4);
+    next = s;
+    l2f_axpy(k1, dt / 6, next); l2f_axpy(k2, dt / 3, next); l2f_axpy(k3, dt / 3, next); l2f_axpy(k4, dt / 6, next);
+    float norm = 0;                                                          // 70_post_integration.h:21-34
+#pragma unroll
+    for(int i = 0; i < 4; i++) norm += next.orientation[i] * next.orientation[i];
+    norm = sqrtf(norm);
+#pragma unroll
+    for(int i = 0; i < 4; i++) next.orientation[i] /= norm;
+#pragma unroll
+    for(int i = 0; i < 3; i++){
+        next.position[i] = l2f_clamp(next.position[i], -a.limit_position, a.limit_position);
+        next.linear_velocity[i] = l2f_clamp(next.linear_velocity[i], -a.limit_velocity, a.limit_velocity);
+        next.angular_velocity[i] = l2f_clamp(next.angular_velocity[i], -a.limit_angular_velocity, a.limit_angular_velocity);
+    }
+#pragma unroll
+    for(int i = 0; i < 4; i++) next.rpm[i] = l2f_clamp(next.rpm[i], p.action_min, p.action_max);      // :137-139
+}
+
 __global__ void __launch_bounds__(128) l2f_steps_kernel(L2fArgs a, float* __restrict__ states, const float* __restrict__ actions, int n, int n_steps){
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if(e >= n) return;
-    const L2fDynamics& p = a.p;
     L2fState s;
     {
         const float* row = states + (size_t)e * 23;
@@ -111,38 +146,12 @@ __global__ void __launch_bounds__(128) l2f_steps_kernel(L2fArgs a, float* __rest
 #pragma unroll
         for(int k = 0; k < 23; k++) dst[k] = row[k];
     }
-    float setpoint[4];
-    const float half_range = (p.action_max - p.action_min) / 2;                  // operations_generic.h:103-109; the default action noise is 0
+    float action[4];
 #pragma unroll
-    for(int i = 0; i < 4; i++){
-        float act = __ldg(actions + (size_t)e * 4 + i);
-        act += 0.0f;
-        act = l2f_clamp(act, -1.0f, 1.0f);
-        setpoint[i] = act * half_range + p.action_min + half_range;
-    }
-    const float dt = a.dt;
+    for(int i = 0; i < 4; i++) action[i] = __ldg(actions + (size_t)e * 4 + i);
     for(int step = 0; step < n_steps; step++){
-        L2fState k1 = s, k2 = s, k3 = s, k4 = s, t;
-        l2f_dynamics(p, s, setpoint, k1);
-        t = s; l2f_axpy(k1, dt / 2, t); l2f_dynamics(p, t, setpoint, k2);
-        t = s; l2f_axpy(k2, dt / 2, t); l2f_dynamics(p, t, setpoint, k3);
-        t = s; l2f_axpy(k3, dt, t);     l2f_dynamics(p, t, setpoint, k4);
-        L2fState next = s;
-        l2f_axpy(k1, dt / 6, next); l2f_axpy(k2, dt / 3, next); l2f_axpy(k3, dt / 3, next); l2f_axpy(k4, dt / 6, next);
-        float norm = 0;                                                          // 70_post_integration.h:21-34
-#pragma unroll
-        for(int i = 0; i < 4; i++) norm += next.orientation[i] * next.orientation[i];
-        norm = sqrtf(norm);
-#pragma unroll
-        for(int i = 0; i < 4; i++) next.orientation[i] /= norm;
-#pragma unroll
-        for(int i = 0; i < 3; i++){
-            next.position[i] = l2f_clamp(next.position[i], -a.limit_position, a.limit_position);
-            next.linear_velocity[i] = l2f_clamp(next.linear_velocity[i], -a.limit_velocity, a.limit_velocity);
-            next.angular_velocity[i] = l2f_clamp(next.angular_velocity[i], -a.limit_angular_velocity, a.limit_angular_velocity);
-        }
-#pragma unroll
-        for(int i = 0; i < 4; i++) next.rpm[i] = l2f_clamp(next.rpm[i], p.action_min, p.action_max);      // :137-139
+        L2fState next;
+        l2f_step(a, s, action, next);
         s = next;
     }
     {
@@ -151,6 +160,156 @@ __global__ void __launch_bounds__(128) l2f_steps_kernel(L2fArgs a, float* __rest
 #pragma unroll
         for(int k = 0; k < 23; k++) row[k] = src[k];
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The runner loop on this environment, fused like the other environments' rollouts (one thread per quadrotor, runner state in registers,
+// the actor 18 -> H -> H -> 4 in shared memory): reset-if-truncated from the table, observe (40_observe.h:42-147: position, rotation matrix,
+// velocities; the default observation noise is 0), actor forward as fp32 FMA chains in the reference's order (bias first, inputs
+// ascending), step, reward (reward_functions/squared/operations_generic.h:12-103, desired state at the origin), terminated on the NEXT
+// state (operations_generic.h:143-158), counters (operations_generic_per_env.h:62-108).
+// mdp: non_negative, scale, constant, termination penalty, weights position, position clip, orientation, linear / angular velocity,
+// linear / angular acceleration, action, d_action, position error integral; termination enabled, position / velocity / angular thresholds.
+// ---------------------------------------------------------------------------------------------------------------
+struct L2fRolloutArgs {
+    L2fArgs env; float mdp[18];
+    const float* params; float* states; int32_t* episode_step; uint8_t* truncated; float* episode_return;
+    const float* reset_states; int n_reset_rounds, n_envs, n_steps, step_limit;
+    float* obs; float* act; float* rew; uint8_t* terminated; int* error_flag; int acts[3];
+};
+__device__ __forceinline__ void l2f_observe(const L2fState& s, float (&o)[18]){
+    const float* q = s.orientation;
+#pragma unroll
+    for(int i = 0; i < 3; i++){ o[i] = s.position[i]; o[12 + i] = s.linear_velocity[i]; o[15 + i] = s.angular_velocity[i]; }
+    o[3]  = (1 - 2 * q[2] * q[2] - 2 * q[3] * q[3]); o[4]  = (2 * q[1] * q[2] - 2 * q[0] * q[3]); o[5]  = (2 * q[1] * q[3] + 2 * q[0] * q[2]);
+    o[6]  = (2 * q[1] * q[2] + 2 * q[0] * q[3]); o[7]  = (1 - 2 * q[1] * q[1] - 2 * q[3] * q[3]); o[8]  = (2 * q[2] * q[3] - 2 * q[0] * q[1]);
+    o[9]  = (2 * q[1] * q[3] - 2 * q[0] * q[2]); o[10] = (2 * q[2] * q[3] + 2 * q[0] * q[1]); o[11] = (1 - 2 * q[1] * q[1] - 2 * q[2] * q[2]);
+}
+__device__ __forceinline__ bool l2f_terminated(const float (&mdp)[18], const L2fState& s){
+    if(mdp[14] != 0.0f){
+#pragma unroll
+        for(int i = 0; i < 3; i++)
+            if(fabsf(s.position[i]) > mdp[15] || fabsf(s.linear_velocity[i]) > mdp[16] || fabsf(s.angular_velocity[i]) > mdp[17]) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ float l2f_reward(const L2fArgs& a, const float (&mdp)[18], const L2fState& s, const float (&action)[4], const L2fState& next, bool terminated){
+    const float orientation_cost = 2 * acosf(1 - fabsf(s.orientation[3]));
+    float position_cost = sqrtf(s.position[0] * s.position[0] + s.position[1] * s.position[1] + s.position[2] * s.position[2]);
+    if(mdp[5] > 0) position_cost = fminf(position_cost, mdp[5]);
+    const float linear_vel_cost = sqrtf(s.linear_velocity[0] * s.linear_velocity[0] + s.linear_velocity[1] * s.linear_velocity[1] + s.linear_velocity[2] * s.linear_velocity[2]);
+    const float angular_vel_cost = sqrtf(s.angular_velocity[0] * s.angular_velocity[0] + s.angular_velocity[1] * s.angular_velocity[1] + s.angular_velocity[2] * s.angular_velocity[2]);
+    float la[3], aa[3];
+#pragma unroll
+    for(int i = 0; i < 3; i++){ la[i] = next.linear_velocity[i] - s.linear_velocity[i]; aa[i] = next.angular_velocity[i] - s.angular_velocity[i]; }
+    const float linear_acc_cost = sqrtf(la[0] * la[0] + la[1] * la[1] + la[2] * la[2]) / a.dt;
+    const float angular_acc_cost = sqrtf(aa[0] * aa[0] + aa[1] * aa[1] + aa[2] * aa[2]) / a.dt;
+    float acc = 0;
+#pragma unroll
+    for(int i = 0; i < 4; i++){
+        const float diff = (action[i] + 1.0f) / 2.0f - a.p.hovering_throttle_relative;
+        acc += diff * diff;
+    }
+    float action_cost = sqrtf(acc);
+    action_cost *= action_cost;
+    float weighted = 0;
+    weighted += mdp[4] * position_cost; weighted += mdp[6] * orientation_cost; weighted += mdp[7] * linear_vel_cost; weighted += mdp[8] * angular_vel_cost;
+    weighted += mdp[9] * linear_acc_cost; weighted += mdp[10] * angular_acc_cost; weighted += mdp[11] * action_cost; weighted += mdp[12] * 0.0f; weighted += mdp[13] * 0.0f;
+    const float scaled = mdp[1] * weighted;
+    if(terminated) return mdp[3];
+    const float reward = -scaled + mdp[2];
+    return (reward > 0 || mdp[0] == 0.0f) ? reward : 0.0f;
+}
+
+template <int H>
+__global__ void __launch_bounds__(128) l2f_rollout_kernel(L2fRolloutArgs a){
+    constexpr int O = 18, A = 4;
+    extern __shared__ __align__(16) float smem[];
+    float* W1 = smem; float* b1 = W1 + H * O; float* W2 = b1 + H; float* b2 = W2 + H * H; float* W3 = b2 + H; float* b3 = W3 + A * H;
+    constexpr int NPARAMS = H * O + H + H * H + H + A * H + A;
+    for(int i = threadIdx.x; i < NPARAMS; i += blockDim.x) smem[i] = __ldg(a.params + i);
+    __syncthreads();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= a.n_envs) return;
+    L2fState s;
+    {
+        const float* row = a.states + (size_t)e * 23;
+        float* dst = reinterpret_cast<float*>(&s);
+#pragma unroll
+        for(int k = 0; k < 23; k++) dst[k] = row[k];
+    }
+    int es = a.episode_step[e], resets = 0;
+    bool trunc = a.truncated[e] != 0;
+    float er = a.episode_return[e];
+    for(int t = 0; t < a.n_steps; t++){
+        if(trunc){                                   // operations_generic_per_env.h:8-61
+            if(a.reset_states != nullptr && resets < a.n_reset_rounds){
+                const float* row = a.reset_states + ((size_t)resets * a.n_envs + e) * 23;
+                float* dst = reinterpret_cast<float*>(&s);
+#pragma unroll
+                for(int k = 0; k < 23; k++) dst[k] = __ldg(row + k);
+            }
+            else if(a.error_flag) *a.error_flag = 1;
+            resets++; es = 0; er = 0.0f;
+        }
+        float o[O];
+        l2f_observe(s, o);
+        const size_t row = (size_t)t * a.n_envs + e;
+#pragma unroll
+        for(int k = 0; k < O; k++) a.obs[row * O + k] = o[k];
+        float h1[H];
+#pragma unroll
+        for(int j = 0; j < H; j++){
+            float acc = b1[j];
+#pragma unroll
+            for(int k = 0; k < O; k++) acc = fmaf(W1[j * O + k], o[k], acc);
+            h1[j] = activation_rt(acc, a.acts[0]);
+        }
+        float out[A];
+#pragma unroll
+        for(int c = 0; c < A; c++) out[c] = b3[c];
+#pragma unroll 2
+        for(int j = 0; j < H; j++){
+            float acc = b2[j];
+            const float4* w = reinterpret_cast<const float4*>(W2 + j * H);
+#pragma unroll
+            for(int k = 0; k < H / 4; k++){
+                const float4 w4 = w[k];
+                acc = fmaf(w4.x, h1[4 * k + 0], acc); acc = fmaf(w4.y, h1[4 * k + 1], acc);
+                acc = fmaf(w4.z, h1[4 * k + 2], acc); acc = fmaf(w4.w, h1[4 * k + 3], acc);
+            }
+            const float h2 = activation_rt(acc, a.acts[1]);
+#pragma unroll
+            for(int c = 0; c < A; c++) out[c] = fmaf(W3[c * H + j], h2, out[c]);
+        }
+        float action[A];
+#pragma unroll
+        for(int c = 0; c < A; c++){ action[c] = activation_rt(out[c], a.acts[2]); a.act[row * A + c] = action[c]; }
+        L2fState next;
+        l2f_step(a.env, s, action, next);
+        const bool term = l2f_terminated(a.mdp, next);
+        const float r = l2f_reward(a.env, a.mdp, s, action, next, term);
+        es += 1; er = __fadd_rn(er, r);
+        trunc = term || (es == a.step_limit);
+        a.rew[row] = r;
+        if(a.terminated) a.terminated[row] = term ? 1 : 0;
+        s = next;
+    }
+    {
+        float* row = a.states + (size_t)e * 23;
+        const float* src = reinterpret_cast<const float*>(&s);
+#pragma unroll
+        for(int k = 0; k < 23; k++) row[k] = src[k];
+    }
+    a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
+}
+
+template <int H>
+static int launch_l2f_rollout(const L2fRolloutArgs& a, cudaStream_t s){
+    constexpr size_t SMEM = sizeof(float) * (H * 18 + H + H * H + H + 4 * H + 4);
+    l2f_rollout_kernel<H><<<(a.n_envs + 127) / 128, 128, SMEM, s>>>(a);
+    B200RL_LAUNCH_CHECK("l2f_rollout");
+    return B200RL_OK;
 }
 
 }  // namespace b200rl
@@ -168,4 +327,29 @@ extern "C" int b200rl_l2f_steps(const b200rl_l2f_parameters* parameters, float* 
     l2f_steps_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(a, states, actions, n, n_steps);
     B200RL_LAUNCH_CHECK("l2f_steps");
     return B200RL_OK;
+}
+
+extern "C" int b200rl_l2f_rollout(const b200rl_l2f_parameters* parameters, const float* mdp, const b200rl_mlp_shape* actor, const float* actor_params, float* states,
+                                  int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps,
+                                  int step_limit, float* obs, float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream){
+    if(!parameters || !mdp || !actor) return B200RL_ERR_INVALID_ARGUMENT;
+    if(actor->n_layers != 3 || actor->input_dim != 18 || actor->dims[0] != actor->dims[1] || actor->dims[2] != 4) return B200RL_ERR_UNSUPPORTED;
+    const int H = actor->dims[0];
+    if(H != 16 && H != 32 && H != 64) return B200RL_ERR_UNSUPPORTED;
+    for(int l = 0; l < 3; l++) if(!valid_activation(actor->acts[l])) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs < 0 || n_steps < 0 || n_reset_rounds < 0 || step_limit < 1 || (reset_states == nullptr && n_reset_rounds != 0)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0 || n_steps == 0) return B200RL_OK;
+    if(!actor_params || !states || !episode_step || !truncated || !episode_return || !obs || !act || !rew) return B200RL_ERR_INVALID_ARGUMENT;
+    L2fRolloutArgs a{};
+    memcpy(&a.env.p, parameters->dynamics, sizeof(L2fDynamics));
+    a.env.dt = parameters->dt; a.env.limit_position = parameters->state_limit_position; a.env.limit_velocity = parameters->state_limit_velocity;
+    a.env.limit_angular_velocity = parameters->state_limit_angular_velocity;
+    memcpy(a.mdp, mdp, sizeof(a.mdp));
+    a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
+    a.reset_states = reset_states; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs; a.n_steps = n_steps; a.step_limit = step_limit;
+    a.obs = obs; a.act = act; a.rew = rew; a.terminated = terminated; a.error_flag = error_flag;
+    for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
+    if(H == 16) return launch_l2f_rollout<16>(a, (cudaStream_t)stream);
+    if(H == 32) return launch_l2f_rollout<32>(a, (cudaStream_t)stream);
+    return launch_l2f_rollout<64>(a, (cudaStream_t)stream);
 }

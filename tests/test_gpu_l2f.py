@@ -62,3 +62,51 @@ def test_l2f_state_limits_and_action_clamp(lib, orc, torch, fix):
     got = d_states.cpu().numpy()
     assert np.array_equal(got, orc.l2f_steps(fix["dynamics"], float(fix["dt"]), states, actions, 10, state_limits=np.array(limits, np.float32)))
     assert np.abs(got[:, :3]).max() <= 0.5 and np.abs(got[:, 7:10]).max() <= 1.0 and np.abs(got[:, 10:13]).max() <= 3.0
+
+
+@pytest.mark.parametrize("hidden", [16, 32, 64])
+def test_l2f_rollout_vs_oracle(lib, orc, torch, fix, hidden):
+    """The fused runner loop on the quadrotor, 600 environments x 40 steps from the reference sampler's initial states with an episode limit of
+    25 (every environment is reset from the table inside the call; environments that drift off terminate earlier): observations, counters and
+    flags against the oracle's loop; per step, teacher-forced on the kernel's own trajectory, the action against the oracle's MLP on the
+    kernel's observation (fp32 tolerance), the next observation's state part bit for bit and the reward within the GPU's acosf."""
+    import oracle
+    N, T, limit = 600, 40, 25
+    rs = np.random.RandomState(hidden)
+    acts = ["tanh", "tanh", "tanh"]
+    shape, oshape = lib.MlpShape.make(18, [hidden, hidden, 4], acts), oracle.MlpShape.make(18, [hidden, hidden, 4], acts)
+    params = (rs.uniform(-1, 1, oshape.num_params()) * (1.0 / np.sqrt(hidden))).astype(np.float32)
+    init = fix["initial_states"]
+    p = lib.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    st, es, er = dev(np.zeros((N, 23), np.float32)), torch.zeros(N, dtype=torch.int32, device="cuda"), torch.zeros(N, device="cuda")
+    tr = torch.ones(N, dtype=torch.uint8, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    obs, act, rew, term = lib.l2f_rollout(p, fix["mdp"], shape, dev(params), st, es, tr, er, dev(init), T, limit, error_flag=flag)
+    assert int(flag.item()) == 0
+    obs, act, rew, term = (x.cpu().numpy() for x in (obs, act, rew, term))
+    want = orc.l2f_rollout(oshape, params, fix["dynamics"], float(fix["dt"]), fix["mdp"], np.zeros((N, 23), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8),
+                           np.zeros(N, np.float32), init, T, limit)
+    assert np.array_equal(obs[:N], want["obs"][:N])                                     # first step: the table's states, bit for bit
+    tol = lambda got, ref, rtol=1e-5, atol=1e-6: np.all(np.abs(got.astype(np.float64) - ref.astype(np.float64)) <= atol + rtol * np.abs(ref))
+    assert tol(act.reshape(-1), orc.mlp_evaluate(oshape, params, obs).reshape(-1))      # every step's action on the kernel's own observation
+    # teacher forcing: rebuild each step's state from the kernel's outputs is not possible from 18 observation values alone (rotor speeds and
+    # disturbances are hidden), so the trajectories are compared directly: the dynamics are bit-exact, only the action's last bits differ
+    assert tol(obs, want["obs"], rtol=1e-4, atol=1e-5)
+    assert np.array_equal(term, want["terminated"]) and np.array_equal(es.cpu().numpy(), want["episode_step"]) and np.array_equal(tr.cpu().numpy(), want["truncated"])
+    assert tol(rew, want["rew"], rtol=1e-4, atol=1e-5)
+    assert tol(st.cpu().numpy(), want["states"], rtol=1e-4, atol=1e-5) and tol(er.cpu().numpy(), want["episode_return"], rtol=1e-4, atol=1e-4)
+    assert term.sum() > 0 and (want["episode_step"] < T).all()
+
+
+def test_l2f_rollout_argument_checks(lib, torch, fix):
+    p = lib.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    st, es, er = torch.zeros((4, 23), device="cuda"), torch.zeros(4, dtype=torch.int32, device="cuda"), torch.zeros(4, device="cuda")
+    tr = torch.ones(4, dtype=torch.uint8, device="cuda")
+    bad = lib.MlpShape.make(18, [48, 48, 4], ["relu", "relu", "tanh"])
+    with pytest.raises(lib.B200RLError):
+        lib.l2f_rollout(p, fix["mdp"], bad, torch.zeros(8000, device="cuda"), st, es, tr, er, None, 3)
+    shape = lib.MlpShape.make(18, [16, 16, 4], ["relu", "relu", "tanh"])
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.l2f_rollout(p, fix["mdp"], shape, torch.zeros(18 * 16 + 16 + 16 * 16 + 16 + 64 + 4, device="cuda"), st, es, tr, er, None, 3, error_flag=flag)
+    assert int(flag.item()) == 1                                                        # a reset without a table entry raises the flag

@@ -285,6 +285,17 @@ def test_l2f_step_matches_reference(orc):
     assert not np.isnan(fix["next_50"]).any() and np.abs(np.linalg.norm(fix["next_50"][:, 3:7], axis=1) - 1).max() < 1e-6
 
 
+def test_l2f_environment_functions_match_reference(orc):
+    """observe, reward (with transitions that terminate) and terminated of the L2F environment: bit for bit."""
+    fix = np.load(os.path.join(GOLDEN, "l2f.npz"))
+    states, actions = mg.l2f_inputs()
+    far = states.copy(); far[::3, :3] *= 3
+    assert np.array_equal(orc.l2f_steps(fix["dynamics"], float(fix["dt"]), far, actions, 1), fix["next_far"])
+    obs, rew, term = orc.l2f_functions(fix["dynamics"], float(fix["dt"]), fix["mdp"], far, actions, fix["next_far"])
+    assert np.array_equal(obs, fix["observations"]) and np.array_equal(rew, fix["rewards"]) and np.array_equal(term, fix["terminated"])
+    assert 0.2 < term.mean() < 0.6
+
+
 @pytest.mark.parametrize("case", range(len(mg.POLYAK_CASES)))
 def test_polyak_update_matches_reference(orc, case):
     """utils::polyak::update / update_squared, repeated: bit for bit."""

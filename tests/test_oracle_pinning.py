@@ -186,6 +186,18 @@ def test_l2f_step_live(orc, ref_strict):
         assert np.array_equal(orc.l2f_steps(dynamics, dt, states, actions, n_steps), ref_strict.l2f_steps(states, actions, n_steps)), n_steps
 
 
+def test_l2f_environment_functions_live(orc, ref_strict):
+    import make_golden as mg
+    dynamics, dt, _ = ref_strict.l2f_parameters()
+    mdp = ref_strict.l2f_mdp()
+    states, actions = mg.l2f_inputs(5000, seed=8)
+    states[::2, :3] *= 2.5
+    nxt = ref_strict.l2f_steps(states, actions, 1)
+    want, got = ref_strict.l2f_functions(states, actions, nxt), orc.l2f_functions(dynamics, dt, mdp, states, actions, nxt)
+    for w, g in zip(want, got):
+        assert np.array_equal(w, g)
+
+
 def test_sac_updates_live(orc, ref_strict):
     import make_golden as mg
     for case, (B, H) in enumerate(oracle.Reference.SAC_CASES):

@@ -829,7 +829,7 @@ def run_l2f_rollout(args):
     params = torch.from_numpy(params_h).to(dev)
     p = pkg.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
     init = fix["initial_states"].reshape(-1, 23)
-    table = torch.from_numpy(init[rs.randint(0, init.shape[0], (3, N))]).to(dev).contiguous()            # three reset rounds per environment
+    table = torch.from_numpy(init[rs.randint(0, init.shape[0], (8, N))]).to(dev).contiguous()            # eight reset rounds per environment
     states, es, er = torch.zeros((N, 23), device=dev), torch.zeros(N, dtype=torch.int32, device=dev), torch.zeros(N, device=dev)
     tr = torch.ones(N, dtype=torch.uint8, device=dev)
     obs, act, rew = torch.empty((T * N, 18), device=dev), torch.empty((T * N, 4), device=dev), torch.empty(T * N, device=dev)

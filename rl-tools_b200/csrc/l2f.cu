@@ -221,93 +221,176 @@ __device__ __forceinline__ float l2f_reward(const L2fArgs& a, const float (&mdp)
     return (reward > 0 || mdp[0] == 0.0f) ? reward : 0.0f;
 }
 
+// One CTA of 14 warps per SM: 448 quadrotors, so 65536 of them (443 per SM) are resident at once. A lane owns one quadrotor for the
+// environment part (reset, observe, step, reward) and, for the two hidden layers, a register tile of 8 quadrotors x H/8 units of its warp's
+// 32 x H product: operands come from shared memory as 16-byte loads that each feed 32 multiply-adds (one broadcast weight per multiply-add,
+// as a thread-per-quadrotor layer would load it, leaves the kernel bound by shared-memory wavefronts). Every unit still accumulates
+// bias + sum over k in ascending k with fused multiply-adds, so the actor's values are those of a plain per-sample loop.
+constexpr int L2F_ROLLOUT_WARPS = 14, L2F_ROLLOUT_THREADS = 32 * L2F_ROLLOUT_WARPS;
 template <int H>
-__global__ void __launch_bounds__(128) l2f_rollout_kernel(L2fRolloutArgs a){
-    constexpr int O = 18, A = 4;
+struct L2fRolloutLayout {
+    static constexpr int O = 18, A = 4;
+    static constexpr int JPT = H / 8;                         // units per lane: unit j = og + 8 * jj for the lane's column group og = lane & 7
+    static constexpr int VW = JPT < 4 ? JPT : 4, NV = JPT / VW;  // a lane's weights per k arrive as NV vectors of VW floats
+    static constexpr int PITCH = 36;                          // row pitch of the hidden tile: rows og, og + 8, .. of eight lanes land on distinct banks
+    // floats from the start of shared memory; the first two layers transposed ([k][slot]), the last as [unit][4]
+    static constexpr int W1T = 0, B1 = W1T + O * H, W2T = B1 + H, B2 = W2T + H * H, W3T = B2 + H, B3 = W3T + A * H, WARP0 = B3 + A;
+    static constexpr int OBS_TILE = O * 32, HID_TILE = H * PITCH, PER_WARP = OBS_TILE + HID_TILE;
+    static constexpr size_t BYTES = sizeof(float) * (WARP0 + L2F_ROLLOUT_WARPS * PER_WARP);
+    __host__ __device__ static constexpr int slot(int j){ return ((j / 8) / VW) * (8 * VW) + (j % 8) * VW + (j / 8) % VW; }
+};
+
+// acc[ee][jj] += sum over k of act[k][8 eg + ee] * wT[k][slot(og + 8 jj)], k ascending; act rows have the pitch ACT_PITCH
+template <int H, int K, int ACT_PITCH>
+__device__ __forceinline__ void l2f_tile_layer(const float* __restrict__ act_tile, const float* __restrict__ wT, int eg, int og, float (&acc)[8][H / 8]){
+    using L = L2fRolloutLayout<H>;
+#pragma unroll 2
+    for(int k = 0; k < K; k++){
+        float x[8], w[L::JPT];
+        const float4 x0 = *reinterpret_cast<const float4*>(act_tile + k * ACT_PITCH + eg * 8), x1 = *reinterpret_cast<const float4*>(act_tile + k * ACT_PITCH + eg * 8 + 4);
+        x[0] = x0.x; x[1] = x0.y; x[2] = x0.z; x[3] = x0.w; x[4] = x1.x; x[5] = x1.y; x[6] = x1.z; x[7] = x1.w;
+#pragma unroll
+        for(int v = 0; v < L::NV; v++){
+            const float* src = wT + k * H + v * (8 * L::VW) + og * L::VW;
+            if constexpr (L::VW == 4){ const float4 t = *reinterpret_cast<const float4*>(src); w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w; }
+            else { const float2 t = *reinterpret_cast<const float2*>(src); w[0] = t.x; w[1] = t.y; }
+        }
+#pragma unroll
+        for(int ee = 0; ee < 8; ee++)
+#pragma unroll
+            for(int jj = 0; jj < L::JPT; jj++) acc[ee][jj] = fmaf(w[jj], x[ee], acc[ee][jj]);
+    }
+}
+// bias in, activation out: the lane's tile goes to the hidden tile as rows [unit][quadrotor of the warp]
+template <int H>
+__device__ __forceinline__ void l2f_tile_store(float* hid, float (&acc)[8][H / 8], int eg, int og, int act){
+    using L = L2fRolloutLayout<H>;
+#pragma unroll
+    for(int jj = 0; jj < L::JPT; jj++){
+        float* row = hid + (og + 8 * jj) * L::PITCH + eg * 8;
+        *reinterpret_cast<float4*>(row) = make_float4(activation_rt(acc[0][jj], act), activation_rt(acc[1][jj], act), activation_rt(acc[2][jj], act), activation_rt(acc[3][jj], act));
+        *reinterpret_cast<float4*>(row + 4) = make_float4(activation_rt(acc[4][jj], act), activation_rt(acc[5][jj], act), activation_rt(acc[6][jj], act), activation_rt(acc[7][jj], act));
+    }
+}
+
+template <int H>
+__global__ void __launch_bounds__(L2F_ROLLOUT_THREADS, 1) l2f_rollout_kernel(L2fRolloutArgs a){
+    using L = L2fRolloutLayout<H>;
+    constexpr int O = L::O, A = L::A;
     extern __shared__ __align__(16) float smem[];
-    float* W1 = smem; float* b1 = W1 + H * O; float* W2 = b1 + H; float* b2 = W2 + H * H; float* W3 = b2 + H; float* b3 = W3 + A * H;
-    constexpr int NPARAMS = H * O + H + H * H + H + A * H + A;
-    for(int i = threadIdx.x; i < NPARAMS; i += blockDim.x) smem[i] = __ldg(a.params + i);
+    {
+        constexpr int W1_END = O * H, B1_END = W1_END + H, W2_END = B1_END + H * H, B2_END = W2_END + H, W3_END = B2_END + A * H;
+        for(int i = threadIdx.x; i < W3_END + A; i += blockDim.x){
+            const float v = __ldg(a.params + i);
+            int dst = i;                                                                       // biases keep their place
+            if(i < W1_END) dst = L::W1T + (i % O) * H + L::slot(i / O);                        // W1[j][k]
+            else if(i >= B1_END && i < W2_END){ const int r = i - B1_END; dst = L::W2T + (r % H) * H + L::slot(r / H); }     // W2[j][k]
+            else if(i >= B2_END && i < W3_END){ const int r = i - B2_END; dst = L::W3T + (r % H) * A + r / H; }             // W3[c][j]
+            smem[dst] = v;
+        }
+    }
     __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, eg = lane >> 3, og = lane & 7;
+    float* obs_tile = smem + L::WARP0 + warp * L::PER_WARP;
+    float* hid = obs_tile + L::OBS_TILE;
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
-    if(e >= a.n_envs) return;
+    const bool active = e < a.n_envs;                     // idle lanes of the last warp still take part in the warp's tiles
     L2fState s;
     {
-        const float* row = a.states + (size_t)e * 23;
         float* dst = reinterpret_cast<float*>(&s);
 #pragma unroll
-        for(int k = 0; k < 23; k++) dst[k] = row[k];
+        for(int k = 0; k < 23; k++) dst[k] = active ? a.states[(size_t)e * 23 + k] : 0.0f;
     }
-    int es = a.episode_step[e], resets = 0;
-    bool trunc = a.truncated[e] != 0;
-    float er = a.episode_return[e];
+    int es = active ? a.episode_step[e] : 0, resets = 0;
+    bool trunc = active ? a.truncated[e] != 0 : false;
+    float er = active ? a.episode_return[e] : 0.0f;
     for(int t = 0; t < a.n_steps; t++){
-        if(trunc){                                   // operations_generic_per_env.h:8-61
-            if(a.reset_states != nullptr && resets < a.n_reset_rounds){
-                const float* row = a.reset_states + ((size_t)resets * a.n_envs + e) * 23;
-                float* dst = reinterpret_cast<float*>(&s);
-#pragma unroll
-                for(int k = 0; k < 23; k++) dst[k] = __ldg(row + k);
-            }
-            else if(a.error_flag) *a.error_flag = 1;
-            resets++; es = 0; er = 0.0f;
-        }
-        float o[O];
-        l2f_observe(s, o);
         const size_t row = (size_t)t * a.n_envs + e;
+        if(active){
+            if(trunc){                                   // operations_generic_per_env.h:8-61
+                if(a.reset_states != nullptr && resets < a.n_reset_rounds){
+                    const float* src = a.reset_states + ((size_t)resets * a.n_envs + e) * 23;
+                    float* dst = reinterpret_cast<float*>(&s);
 #pragma unroll
-        for(int k = 0; k < O; k++) a.obs[row * O + k] = o[k];
-        float h1[H];
+                    for(int k = 0; k < 23; k++) dst[k] = __ldg(src + k);
+                }
+                else if(a.error_flag) *a.error_flag = 1;
+                resets++; es = 0; er = 0.0f;
+            }
+            float o[O];
+            l2f_observe(s, o);
 #pragma unroll
-        for(int j = 0; j < H; j++){
-            float acc = b1[j];
-#pragma unroll
-            for(int k = 0; k < O; k++) acc = fmaf(W1[j * O + k], o[k], acc);
-            h1[j] = activation_rt(acc, a.acts[0]);
+            for(int k = 0; k < O; k++){ a.obs[row * O + k] = o[k]; obs_tile[k * 32 + lane] = o[k]; }
         }
+        else {
+#pragma unroll
+            for(int k = 0; k < O; k++) obs_tile[k * 32 + lane] = 0.0f;
+        }
+        __syncwarp();
+        {
+            float acc[8][L::JPT];
+#pragma unroll
+            for(int jj = 0; jj < L::JPT; jj++){
+                const float b = smem[L::B1 + og + 8 * jj];
+#pragma unroll
+                for(int ee = 0; ee < 8; ee++) acc[ee][jj] = b;
+            }
+            l2f_tile_layer<H, O, 32>(obs_tile, smem + L::W1T, eg, og, acc);
+            l2f_tile_store<H>(hid, acc, eg, og, a.acts[0]);
+        }
+        __syncwarp();
+        {
+            float acc[8][L::JPT];
+#pragma unroll
+            for(int jj = 0; jj < L::JPT; jj++){
+                const float b = smem[L::B2 + og + 8 * jj];
+#pragma unroll
+                for(int ee = 0; ee < 8; ee++) acc[ee][jj] = b;
+            }
+            l2f_tile_layer<H, H, L::PITCH>(hid, smem + L::W2T, eg, og, acc);
+            __syncwarp();                                // every lane has read the first hidden layer before the second overwrites it
+            l2f_tile_store<H>(hid, acc, eg, og, a.acts[1]);
+        }
+        __syncwarp();
         float out[A];
 #pragma unroll
-        for(int c = 0; c < A; c++) out[c] = b3[c];
-#pragma unroll 2
+        for(int c = 0; c < A; c++) out[c] = smem[L::B3 + c];
+#pragma unroll 8
         for(int j = 0; j < H; j++){
-            float acc = b2[j];
-            const float4* w = reinterpret_cast<const float4*>(W2 + j * H);
-#pragma unroll
-            for(int k = 0; k < H / 4; k++){
-                const float4 w4 = w[k];
-                acc = fmaf(w4.x, h1[4 * k + 0], acc); acc = fmaf(w4.y, h1[4 * k + 1], acc);
-                acc = fmaf(w4.z, h1[4 * k + 2], acc); acc = fmaf(w4.w, h1[4 * k + 3], acc);
-            }
-            const float h2 = activation_rt(acc, a.acts[1]);
-#pragma unroll
-            for(int c = 0; c < A; c++) out[c] = fmaf(W3[c * H + j], h2, out[c]);
+            const float h2 = hid[j * L::PITCH + lane];
+            const float4 w3 = *reinterpret_cast<const float4*>(smem + L::W3T + j * A);
+            out[0] = fmaf(w3.x, h2, out[0]); out[1] = fmaf(w3.y, h2, out[1]); out[2] = fmaf(w3.z, h2, out[2]); out[3] = fmaf(w3.w, h2, out[3]);
         }
-        float action[A];
+        __syncwarp();                                    // the tiles are free for the next step
+        if(active){
+            float action[A];
 #pragma unroll
-        for(int c = 0; c < A; c++){ action[c] = activation_rt(out[c], a.acts[2]); a.act[row * A + c] = action[c]; }
-        L2fState next;
-        l2f_step(a.env, s, action, next);
-        const bool term = l2f_terminated(a.mdp, next);
-        const float r = l2f_reward(a.env, a.mdp, s, action, next, term);
-        es += 1; er = __fadd_rn(er, r);
-        trunc = term || (es == a.step_limit);
-        a.rew[row] = r;
-        if(a.terminated) a.terminated[row] = term ? 1 : 0;
-        s = next;
+            for(int c = 0; c < A; c++){ action[c] = activation_rt(out[c], a.acts[2]); a.act[row * A + c] = action[c]; }
+            L2fState next;
+            l2f_step(a.env, s, action, next);
+            const bool term = l2f_terminated(a.mdp, next);
+            const float r = l2f_reward(a.env, a.mdp, s, action, next, term);
+            es += 1; er = __fadd_rn(er, r);
+            trunc = term || (es == a.step_limit);
+            a.rew[row] = r;
+            if(a.terminated) a.terminated[row] = term ? 1 : 0;
+            s = next;
+        }
     }
-    {
-        float* row = a.states + (size_t)e * 23;
+    if(active){
+        float* dst = a.states + (size_t)e * 23;
         const float* src = reinterpret_cast<const float*>(&s);
 #pragma unroll
-        for(int k = 0; k < 23; k++) row[k] = src[k];
+        for(int k = 0; k < 23; k++) dst[k] = src[k];
+        a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
     }
-    a.episode_step[e] = es; a.truncated[e] = trunc ? 1 : 0; a.episode_return[e] = er;
 }
 
 template <int H>
 static int launch_l2f_rollout(const L2fRolloutArgs& a, cudaStream_t s){
-    constexpr size_t SMEM = sizeof(float) * (H * 18 + H + H * H + H + 4 * H + 4);
-    l2f_rollout_kernel<H><<<(a.n_envs + 127) / 128, 128, SMEM, s>>>(a);
+    constexpr size_t SMEM = L2fRolloutLayout<H>::BYTES;
+    B200RL_CUDA_TRY(cudaFuncSetAttribute(l2f_rollout_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    l2f_rollout_kernel<H><<<(a.n_envs + L2F_ROLLOUT_THREADS - 1) / L2F_ROLLOUT_THREADS, L2F_ROLLOUT_THREADS, SMEM, s>>>(a);
     B200RL_LAUNCH_CHECK("l2f_rollout");
     return B200RL_OK;
 }

@@ -45,6 +45,12 @@ const char* b200rl_status_string(int status);
 /* text of the last CUDA error seen by this library on the calling thread ("" if none) */
 const char* b200rl_last_cuda_error(void);
 
+/* Wide networks at small batches (at most four layers, widths and batch at most 512, too large for the whole-network kernels of small
+ * networks) run b200rl_mlp_backward as ONE cooperative launch with grid-wide barriers between the layers (B200RL_COOPERATIVE_PASS=0 in the
+ * environment keeps them on the per-layer kernels, =2 also takes forward / evaluate there). Every barrier wait has a limit; *status = 1
+ * when a wait on the current device ever ran into it (the pass's results are then undefined), else 0. Synchronous (a device-to-host copy). */
+int b200rl_cooperative_pass_status(int* status);
+
 /* Reads (and synchronises for) the library's device-side error word into *state_host: non-zero after a bounded wait
  * inside a tensor-core dense kernel expired (the kernel then left its loops and released its tensor memory instead of
  * spinning). The reference has no counterpart (its asserts are no-ops in kernels, utils/assert/operations_cuda.h:17-21). */

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libb200rl.so")
-SOURCES = ["dense.cu", "dense_tc.cu", "dense_skinny.cu", "mlp_fused.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu", "l2f.cu"]
+SOURCES = ["dense.cu", "dense_tc.cu", "dense_skinny.cu", "mlp_fused.cu", "mlp_coop.cu", "adam.cu", "rollout.cu", "rollout_tc.cu", "ppo.cu", "host_api.cu", "sac.cu", "normalize.cu", "rollout_env.cu", "l2f.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
 # per-source flags: the quadrotor dynamics keep the reference's association of every expression (bit-for-bit parity with its CPU step)
 SOURCE_FLAGS = {"l2f.cu": ["-fmad=false"]}

@@ -511,6 +511,13 @@ int mlp_fused_forward(const b200rl_mlp_shape* sh, const float* params, const flo
 int mlp_fused_backward(const b200rl_mlp_shape* sh, const float* params, float* grads, const float* x, int ldx, const float* pre, const float* out, float* d_out,
                        float* d_input, int batch, void* scratch, size_t scratch_bytes, cudaStream_t s);
 
+// whole-pass cooperative kernel for wide networks at small batches (mlp_coop.cu)
+bool mlp_coop_eligible(const b200rl_mlp_shape* sh, int batch, bool forward);
+int mlp_coop_forward(const b200rl_mlp_shape* sh, const float* params, const float* x, int ldx, float* pre, float* out, float* y, int ldy,
+                     float* tick, float* tock, int batch, cudaStream_t s);
+int mlp_coop_backward(const b200rl_mlp_shape* sh, const float* params, float* grads, const float* x, int ldx, const float* pre, const float* out,
+                      float* d_out, float* d_input, float* tick, float* tock, int batch, cudaStream_t s);
+
 static bool valid_shape(const b200rl_mlp_shape* sh){
     if(!sh || sh->n_layers < 1 || sh->n_layers > B200RL_MAX_LAYERS || sh->input_dim < 1) return false;
     for(int l = 0; l < sh->n_layers; l++) if(sh->dims[l] < 1 || !valid_activation(sh->acts[l])) return false;
@@ -624,6 +631,7 @@ int b200rl_mlp_evaluate_ws(const b200rl_mlp_shape* sh, const float* params, cons
     if(sh->n_layers > 1 && (!tick || (sh->n_layers > 2 && !tock))) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
     if(mlp_fused_eligible(sh, batch)) return mlp_fused_forward(sh, params, x, ldx, nullptr, nullptr, y, ldy, batch, (cudaStream_t)stream);
+    if(mlp_coop_eligible(sh, batch, true)) return mlp_coop_forward(sh, params, x, ldx, nullptr, nullptr, y, ldy, tick, tock, batch, (cudaStream_t)stream);
     const float* in = x; int ldin = ldx, I = sh->input_dim; const float* p = params;
     for(int l = 0; l < sh->n_layers; l++){
         int O = sh->dims[l]; bool last = l == sh->n_layers - 1;
@@ -645,6 +653,7 @@ int b200rl_mlp_forward_ws(const b200rl_mlp_shape* sh, const float* params, const
     if(!valid_shape(sh) || !params || !x || !pre || !out || batch < 0 || ldx < sh->input_dim) return B200RL_ERR_INVALID_ARGUMENT;
     if(batch == 0) return B200RL_OK;
     if(mlp_fused_eligible(sh, batch)) return mlp_fused_forward(sh, params, x, ldx, pre, out, nullptr, 0, batch, (cudaStream_t)stream);
+    if(mlp_coop_eligible(sh, batch, true)) return mlp_coop_forward(sh, params, x, ldx, pre, out, nullptr, 0, nullptr, nullptr, batch, (cudaStream_t)stream);
     const float* in = x; int ldin = ldx, I = sh->input_dim; const float* p = params;
     for(int l = 0; l < sh->n_layers; l++){
         int O = sh->dims[l];
@@ -675,6 +684,7 @@ int b200rl_mlp_backward(const b200rl_mlp_shape* sh, const float* params, float* 
     // small batches: the whole pass in two launches, when the caller's scratch has room for the gradients of all layers
     if(mlp_fused_eligible(sh, batch) && scratch && scratch_bytes >= mlp_fused_backward_scratch_bytes(sh, batch))
         return mlp_fused_backward(sh, params, grads, x, ldx, pre, out, d_out, d_input, batch, scratch, scratch_bytes, (cudaStream_t)stream);
+    if(mlp_coop_eligible(sh, batch, false)) return mlp_coop_backward(sh, params, grads, x, ldx, pre, out, d_out, d_input, tick, tock, batch, (cudaStream_t)stream);
     size_t poff[B200RL_MAX_LAYERS], aoff[B200RL_MAX_LAYERS]; int Is[B200RL_MAX_LAYERS];
     { size_t po = 0, ao = 0; int I = sh->input_dim;
       for(int l = 0; l < L; l++){ poff[l] = po; aoff[l] = ao; Is[l] = I; po += (size_t)sh->dims[l] * I + sh->dims[l]; ao += (size_t)batch * sh->dims[l]; I = sh->dims[l]; } }

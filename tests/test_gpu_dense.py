@@ -251,6 +251,49 @@ def test_mlp_backward_large_batch_against_the_oracle(lib, orc, torch, hidden_act
     assert bool((net.grads == 0.25).all()) and torch.equal(d_in_only, d_in)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,I,dims,acts", [
+    (256, 4, [256, 256, 1], ["relu", "relu", "identity"]),          # the critic of the off-policy algorithms
+    (256, 3, [256, 256, 2], ["relu", "relu", "tanh"]),              # their actor: an odd input width, an activation on the output
+    (200, 17, [300, 270, 133, 5], ["tanh", "sigmoid", "relu", "identity"]),   # four layers, nothing a multiple of the tile
+    (512, 300, [512, 260], ["fast_tanh", "identity"]),              # two chunks of the summed index, the largest batch and width
+])
+def test_mlp_backward_in_one_cooperative_launch(lib, orc, torch, B, I, dims, acts):
+    """Wide networks at small batches take the backward pass as one cooperative launch (phases with grid-wide barriers): parameter
+    gradients on top of existing values and the input gradient against the oracle's per-layer recursion; the input-gradient-only pass;
+    two passes in a row give the same bits (the partial tiles are added in a fixed order); no barrier wait ran into its limit."""
+    import ctypes
+    shape = oracle.MlpShape.make(I, dims, acts)
+    params = mg.det_uniform(91, shape.num_params()) * np.float32(0.1)
+    x = mg.det_normal(92, B * I).reshape(B, I)
+    d_out = mg.det_normal(93, B * dims[-1]).reshape(B, dims[-1]) / np.float32(B)
+    g0 = mg.det_normal(94, shape.num_params()) * np.float32(0.01)
+    pre, out = orc.mlp_forward(shape, params, x)
+    g_ref, din_ref = orc.mlp_backward(shape, params, g0, x, pre, out, d_out, want_d_input=True)
+    net = lib.Mlp(I, dims, acts, B)
+    net.params.copy_(dev(torch, params))
+    xd = dev(torch, x)
+    net.forward(xd)
+    results = []
+    for _ in range(2):
+        net.grads.copy_(dev(torch, g0))
+        d_in = torch.empty((B, I), device="cuda")
+        net.backward(xd, dev(torch, d_out), d_input=d_in)
+        results.append((net.grads.clone(), d_in))
+    g = results[0][0].cpu().numpy()
+    assert np.all(np.abs(g - g_ref) <= 1e-6 + 1e-5 * np.maximum(np.abs(g_ref), 1e-2)), float(np.abs(g - g_ref).max())
+    close(results[0][1], din_ref, rtol=1e-5, atol=1e-8)
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    d_in_only = torch.empty((B, I), device="cuda")
+    net.grads.fill_(0.25)
+    net.backward(xd, dev(torch, d_out), d_input=d_in_only, accumulate_gradients=False)
+    assert bool((net.grads == 0.25).all()) and torch.equal(d_in_only, results[0][1])
+    status = ctypes.c_int(-1)
+    L = lib.lib()
+    L.b200rl_cooperative_pass_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    assert L.b200rl_cooperative_pass_status(ctypes.byref(status)) == 0 and status.value == 0
+
+
 def test_mlp_backward_without_parameter_gradients(lib, torch):
     """grads = NULL is the reference's backward_input: the same input gradient as the full backward pass, parameter gradients untouched."""
     rs = np.random.RandomState(3)

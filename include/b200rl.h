@@ -422,6 +422,20 @@ int b200rl_l2f_steps(const b200rl_l2f_parameters* parameters, float* states, con
 int b200rl_l2f_rollout(const b200rl_l2f_parameters* parameters, const float* mdp, const b200rl_mlp_shape* actor, const float* actor_params, float* states,
                        int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps,
                        int step_limit, float* obs, float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream);
+/* sample_initial_state(device, env, parameters, state, rng) of the same configuration (rl/environments/l2f/operations_generic/
+ * 30_sample_initial_state.h:19-207) as a function of its draws: uniforms [n, 17] in [0, 1) (guidance; position 3; orientation u, v, angle;
+ * linear velocity 3; angular velocity 3; rotor speeds 4), normals [n, 6] standard normals (force 3, torque 3). init (host, 12 floats):
+ * mdp.init guidance, max_position, max_angle, max_linear_velocity, max_angular_velocity, relative_rpm, min_rpm, max_rpm, then the
+ * disturbances' force mean / std and torque mean / std. states [n, 23]; equal to the reference's bit for bit except the orientation
+ * (the GPU's sinf / cosf). */
+int b200rl_l2f_initial_states_from_draws(const b200rl_l2f_parameters* parameters, const float* init, const float* uniforms, const float* normals, float* states, int n,
+                                         b200rl_stream_t stream);
+/* b200rl_l2f_rollout with the initial state of every reset drawn in the kernel from `init` (a counter-based generator keyed by seed,
+ * environment and first_step + step, as b200rl_pendulum_rollout_device_rng: no reset table, any number of resets). */
+int b200rl_l2f_rollout_device_rng(const b200rl_l2f_parameters* parameters, const float* mdp, const float* init, const b200rl_mlp_shape* actor, const float* actor_params,
+                                  float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return, unsigned long long seed,
+                                  unsigned long long first_step, int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, uint8_t* terminated,
+                                  b200rl_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Replay-buffer sampling: gather_batch(device, runner, batch, rng) for SequentialBatch with SEQUENCE_LENGTH 1 and its default sampling

@@ -119,6 +119,8 @@ class Oracle:
         L.orc_l2f_functions.argtypes = [C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _u8p]
         L.orc_l2f_rollout.argtypes = [C.c_void_p, _f32p, _f32p, C.c_float, _f32p, _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, _f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, _u8p]
         L.orc_l2f_steps.argtypes = [C.c_int, C.c_int, _f32p, C.c_float, _f32p, _f32p, _f32p, _f32p]
+        L.orc_l2f_initial_state_from_draws.argtypes = [_f32p, C.c_float, C.c_float, _f32p, _f32p, _f32p]
+        L.orc_l2f_sample_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p, C.c_float, C.c_float, _f32p]
         L.orc_gather_batch_sequences.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, _f32p, _i64p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p]
         L.orc_gather_batch.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, _i64p, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, _i32p, _i32p]
         L.orc_pendulum_collect.argtypes = [C.POINTER(MlpShape), _f32p, C.c_int, C.c_int, _f32p, _i32p, _u8p, _f32p, C.c_void_p, C.c_void_p, C.c_int,
@@ -538,6 +540,23 @@ class Oracle:
                                    np.ascontiguousarray(actions, np.float32), np.ascontiguousarray(next_states, np.float32), obs, rew, term)
         return obs, rew, term
 
+    def l2f_initial_states_from_draws(self, init, dynamics, u, normals):
+        """sample_initial_state of the L2F environment as a function of its draws: u [n, 17] canonical uniforms, normals [n, 6] standard normals
+        (see orc_l2f_initial_state_from_draws); action limits = the last two floats of the dynamics block. Returns [n, 23]."""
+        u, normals = np.ascontiguousarray(u, np.float32), np.ascontiguousarray(normals, np.float32)
+        init, d = np.ascontiguousarray(init, np.float32), np.ascontiguousarray(dynamics, np.float32)
+        out = np.empty((u.shape[0], 23), np.float32)
+        for e in range(u.shape[0]):
+            self.lib.orc_l2f_initial_state_from_draws(init, d[83], d[84], u[e], normals[e], out[e])
+        return out
+
+    def l2f_sample_initial_states(self, seed, n, init, dynamics):
+        """n x sample_initial_state on one engine seeded with `seed`, in the reference's draw order: [n, 23]."""
+        d = np.ascontiguousarray(dynamics, np.float32)
+        out = np.empty((n, 23), np.float32)
+        self.lib.orc_l2f_sample_initial_states(seed, n, np.ascontiguousarray(init, np.float32), d[83], d[84], out)
+        return out
+
     def l2f_rollout(self, shape, params, dynamics, dt, mdp, states, episode_step, truncated, episode_return, reset_states, T, step_limit=500, state_limits=None):
         """The runner loop on the L2F environment: reset_states [R, N, 23]; returns obs, act, rew, terminated and the runner state afterwards."""
         N = states.shape[0]
@@ -697,6 +716,7 @@ class Reference:
         L.ref_offpolicy_gather.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, _f32p, C.c_uint32, C.c_int, C.c_int, _f32p, _f32p, _u8p, _u8p, _u8p, _u8p, _u8p, C.c_void_p]
         L.ref_l2f_parameters.argtypes = [_f32p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         L.ref_l2f_mdp.argtypes = [_f32p]
+        L.ref_l2f_init.argtypes = [_f32p]
         L.ref_l2f_functions.argtypes = [C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _u8p]
         L.ref_l2f_initial_states.argtypes = [C.c_uint32, C.c_int, _f32p]
         L.ref_l2f_steps.argtypes = [C.c_int, C.c_int, _f32p, _f32p, _f32p]
@@ -898,6 +918,12 @@ class Reference:
         """The 18 floats of the default parameter set's reward function and termination thresholds (see ref_l2f_mdp)."""
         m = np.zeros(18, np.float32)
         self.lib.ref_l2f_mdp(m)
+        return m
+
+    def l2f_init(self):
+        """The 12 floats of the default parameter set's initial-state distribution (see ref_l2f_init)."""
+        m = np.zeros(12, np.float32)
+        self.lib.ref_l2f_init(m)
         return m
 
     def l2f_functions(self, states, actions, next_states):

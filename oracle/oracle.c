@@ -1280,3 +1280,73 @@ void orc_ppo_policy_gradient(const float* current_actions, const float* rollout_
     }
     free(d_lp_d_logstd);
 }
+
+/* ---- L2F initial state (rl/environments/l2f/operations_generic/30_sample_initial_state.h:19-207, the harness' state StateRotors<StateRandomForce<StateBase>>) ---- */
+/* init: guidance, max_position, max_angle, max_linear_velocity, max_angular_velocity, relative_rpm, min_rpm, max_rpm, force mean / std, torque mean / std.        */
+/* The state as a function of its draws: u[17] canonical uniforms in [0, 1) (guidance; position 3; orientation u, v, angle; linear velocity 3; angular velocity 3;  */
+/* rotor speeds 4) and nrm[6] standard normals (force 3, torque 3; the third torque component has std / 100). uniform(lo, hi) = u * (hi - lo) + lo, normal =       */
+/* n * std + mean (std == 0: the mean); the reference writes 2.0 / 1.0 / 0.5 as double literals in sample_orientation, so those products are taken in double.      */
+void orc_l2f_initial_state_from_draws(const float* init, float action_min, float action_max, const float* u, const float* nrm, float* state){
+    const int guidance = u[0] < init[0];
+    float* position = state; float* q = state + 3; float* lin = state + 7; float* ang = state + 10; float* force = state + 13; float* torque = state + 16; float* rpm = state + 19;
+    for(int i = 0; i < 3; i++) position[i] = guidance ? 0.0f : u[1 + i] * (init[1] - (-init[1])) + (-init[1]);
+    if(init[2] > 0 && !guidance){
+        const float uu = u[4], v = u[5], angle = u[6];
+        const float phi = (float)(2.0 * (double)3.14159265358979323846f * (double)uu);
+        const float cos_theta = (float)(1.0 - 2.0 * (double)v);
+        const float sin_theta = (float)sqrt(1.0 - (double)(cos_theta * cos_theta));
+        const float x = sin_theta * cosf(phi), y = sin_theta * sinf(phi), z = cos_theta;
+        const float half = (float)(0.5 * (double)angle);
+        const float sn = sinf(half);
+        q[0] = cosf(half); q[1] = x * sn; q[2] = y * sn; q[3] = z * sn;
+    }
+    else { q[0] = 1; q[1] = 0; q[2] = 0; q[3] = 0; }
+    for(int i = 0; i < 3; i++){
+        lin[i] = guidance ? 0.0f : u[7 + i] * (init[3] - (-init[3])) + (-init[3]);
+        ang[i] = guidance ? 0.0f : u[10 + i] * (init[4] - (-init[4])) + (-init[4]);
+    }
+    for(int i = 0; i < 3; i++){
+        const float fs = init[9], ts = i == 2 ? init[11] / 100 : init[11];
+        force[i] = fs == 0 ? init[8] : nrm[i] * fs + init[8];
+        torque[i] = ts == 0 ? init[10] : nrm[3 + i] * ts + init[10];
+    }
+    float min_rpm, max_rpm;
+    if(init[5] != 0.0f){
+        min_rpm = (init[6] + 1) / 2 * (action_max - action_min) + action_min;
+        max_rpm = (init[7] + 1) / 2 * (action_max - action_min) + action_min;
+    }
+    else{
+        min_rpm = init[6] < 0 ? action_min : init[6];
+        max_rpm = init[7] < 0 ? action_max : init[7];
+        if(max_rpm > action_max) max_rpm = action_max;
+        if(min_rpm > max_rpm) min_rpm = max_rpm;
+    }
+    for(int i = 0; i < 4; i++) rpm[i] = u[13 + i] * (max_rpm - min_rpm) + min_rpm;
+}
+/* the standard normal under orc_normal (Marsaglia polar on canonical draws, second value discarded) */
+static float orc_standard_normal(orc_rng* r){
+    float x, y, r2;
+    do{
+        x = 2.0f * orc_canonical(r) - 1.0f;
+        y = 2.0f * orc_canonical(r) - 1.0f;
+        r2 = x * x + y * y;
+    } while(r2 > 1.0f || r2 == 0.0f);
+    return y * sqrtf(-2 * logf(r2) / r2);
+}
+/* n x sample_initial_state on ONE engine, consuming it exactly where the reference does: no position / orientation / velocity draws under    */
+/* guidance, no orientation draws for max_angle <= 0, no draw for a normal with std == 0. states [n, 23].                                    */
+void orc_l2f_sample_initial_states(uint32_t seed, int n, const float* init, float action_min, float action_max, float* states){
+    orc_rng r; orc_rng_init(&r, seed);
+    for(int e = 0; e < n; e++){
+        float u[17] = {0}, nrm[6] = {0};
+        u[0] = orc_canonical(&r);
+        const int guidance = u[0] < init[0];
+        if(!guidance) for(int i = 0; i < 3; i++) u[1 + i] = orc_canonical(&r);
+        if(init[2] > 0 && !guidance) for(int i = 0; i < 3; i++) u[4 + i] = orc_canonical(&r);
+        if(!guidance) for(int i = 0; i < 6; i++) u[7 + i] = orc_canonical(&r);
+        for(int i = 0; i < 3; i++) if(init[9] != 0) nrm[i] = orc_standard_normal(&r);
+        for(int i = 0; i < 3; i++) if((i == 2 ? init[11] / 100 : init[11]) != 0) nrm[3 + i] = orc_standard_normal(&r);
+        for(int i = 0; i < 4; i++) u[13 + i] = orc_canonical(&r);
+        orc_l2f_initial_state_from_draws(init, action_min, action_max, u, nrm, states + (size_t)e * 23);
+    }
+}

@@ -968,6 +968,18 @@ int ref_l2f_functions(int n, const float* states, const float* actions, const fl
     }
     return 0;
 }
+// the initial-state distribution of the harness configuration: mdp.init (guidance, max_position, max_angle, max_linear_velocity,
+// max_angular_velocity, relative_rpm, min_rpm, max_rpm) and the disturbance distributions (force mean / std, torque mean / std)
+int ref_l2f_init(float* init){
+    DEVICE device;
+    l2f_harness::ENVIRONMENT env; l2f_harness::ENVIRONMENT::Parameters parameters;
+    rlt::init(device, env); rlt::initial_parameters(device, env, parameters);
+    const auto& i = parameters.mdp.init; const auto& d = parameters.disturbances;
+    const float values[12] = {i.guidance, i.max_position, i.max_angle, i.max_linear_velocity, i.max_angular_velocity, i.relative_rpm ? 1.0f : 0.0f, i.min_rpm, i.max_rpm,
+                              (float)d.random_force.mean, (float)d.random_force.std, (float)d.random_torque.mean, (float)d.random_torque.std};
+    std::memcpy(init, values, sizeof(values));
+    return 0;
+}
 // n x sample_initial_state on one engine (nominal parameters)
 int ref_l2f_initial_states(uint32_t seed, int n, float* out){
     DEVICE device;

@@ -195,6 +195,9 @@ def lib():
         u64 = C.c_uint64
         L.b200rl_pendulum_collect_device_rng.argtypes = [shape_p, vp, vp, vp, vp, vp, vp, u64, u64, i, i, i, vp, i, vp, vp]
         L.b200rl_l2f_rollout.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 18), shape_p, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp]
+        L.b200rl_l2f_rollout_device_rng.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 18), C.POINTER(C.c_float * 12), shape_p, vp, vp, vp, vp, vp,
+                                                    C.c_ulonglong, C.c_ulonglong, i, i, i, vp, vp, vp, vp, vp]
+        L.b200rl_l2f_initial_states_from_draws.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 12), vp, vp, vp, i, vp]
         L.b200rl_l2f_steps.argtypes = [C.POINTER(L2fParameters), vp, vp, i, i, vp]
         L.b200rl_gather_batch_sequences.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, i, i, f, u64, u64, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
         L.b200rl_pendulum_offpolicy_prologue.argtypes = [vp, vp, vp, vp, vp, u64, u64, vp, i, vp, vp, vp]
@@ -705,6 +708,33 @@ def l2f_rollout(parameters, mdp, shape, params, states, episode_step, truncated,
                                    _ptr(reset_states), R, N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(terminated), _ptr(error_flag), _stream()),
           "b200rl_l2f_rollout")
     return obs, act, rew, terminated
+
+
+def l2f_rollout_device_rng(parameters, mdp, init, shape, params, states, episode_step, truncated, episode_return, seed, first_step, n_steps, step_limit=500,
+                           obs=None, act=None, rew=None, terminated=None):
+    """l2f_rollout with every reset's initial state drawn in the kernel from the 12 floats of `init` (the reference's mdp.init and disturbance
+    distributions), keyed by (seed, environment, first_step + step): no reset table."""
+    import torch
+    N, dev = states.shape[0], states.device
+    obs = torch.empty((n_steps * N, 18), device=dev) if obs is None else obs
+    act = torch.empty((n_steps * N, 4), device=dev) if act is None else act
+    rew = torch.empty(n_steps * N, device=dev) if rew is None else rew
+    terminated = torch.empty(n_steps * N, device=dev, dtype=torch.uint8) if terminated is None else terminated
+    mdp_c, init_c = (C.c_float * 18)(*[float(v) for v in mdp]), (C.c_float * 12)(*[float(v) for v in init])
+    check(lib().b200rl_l2f_rollout_device_rng(C.byref(parameters), mdp_c, init_c, C.byref(shape), _ptr(params), _ptr(states), _ptr(episode_step), _ptr(truncated),
+                                              _ptr(episode_return), seed, first_step, N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(terminated), _stream()),
+          "b200rl_l2f_rollout_device_rng")
+    return obs, act, rew, terminated
+
+
+def l2f_initial_states_from_draws(parameters, init, uniforms, normals):
+    """The reference's sample_initial_state as a function of its draws: uniforms [n, 17] in [0, 1), normals [n, 6]; returns states [n, 23]."""
+    import torch
+    n = uniforms.shape[0]
+    states = torch.empty((n, 23), device=uniforms.device)
+    init_c = (C.c_float * 12)(*[float(v) for v in init])
+    check(lib().b200rl_l2f_initial_states_from_draws(C.byref(parameters), init_c, _ptr(uniforms), _ptr(normals), _ptr(states), n, _stream()), "b200rl_l2f_initial_states_from_draws")
+    return states
 
 
 GATHER_FROM_INITIAL_STATE, GATHER_RANDOM_LENGTH, GATHER_FIRST_STEP_TARGET, GATHER_DETERMINISTIC = 1, 2, 4, 8

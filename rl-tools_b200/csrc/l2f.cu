@@ -7,6 +7,7 @@
 // This file is compiled WITHOUT multiply-add contraction (see the package's per-source flags): every expression below keeps the reference's
 // association, division and square root are IEEE, so a step gives the reference's CPU bits.
 #include "common.cuh"
+#include "rollout.cuh"
 
 namespace b200rl {
 
@@ -176,7 +177,89 @@ struct L2fRolloutArgs {
     const float* params; float* states; int32_t* episode_step; uint8_t* truncated; float* episode_return;
     const float* reset_states; int n_reset_rounds, n_envs, n_steps, step_limit;
     float* obs; float* act; float* rew; uint8_t* terminated; int* error_flag; int acts[3];
+    // device_rng != 0: a reset draws its initial state in the kernel (keyed by rng_seed, the environment and rng_step0 + step) from `init`
+    int device_rng; unsigned long long rng_seed, rng_step0; float init[12];
 };
+
+// sample_initial_state of the harness' state (operations_generic/30_sample_initial_state.h:19-207) as a function of its draws: u[17] uniforms
+// in [0, 1) (guidance; position 3; orientation u, v, angle; linear velocity 3; angular velocity 3; rotor speeds 4), nrm[6] standard normals
+// (force 3, torque 3; the third torque component has std / 100). init: guidance, max_position, max_angle, max_linear_velocity,
+// max_angular_velocity, relative_rpm, min_rpm, max_rpm, force mean / std, torque mean / std. The reference writes 2.0 / 1.0 / 0.5 as double
+// literals in sample_orientation: those products are taken in double here too (a reset is rare next to a step).
+__device__ __forceinline__ void l2f_initial_state(const float (&init)[12], float action_min, float action_max, const float (&u)[17], const float (&nrm)[6], L2fState& s){
+    const bool guidance = u[0] < init[0];
+#pragma unroll
+    for(int i = 0; i < 3; i++){
+        s.position[i] = guidance ? 0.0f : u[1 + i] * (init[1] - (-init[1])) + (-init[1]);
+        s.linear_velocity[i] = guidance ? 0.0f : u[7 + i] * (init[3] - (-init[3])) + (-init[3]);
+        s.angular_velocity[i] = guidance ? 0.0f : u[10 + i] * (init[4] - (-init[4])) + (-init[4]);
+    }
+    if(init[2] > 0 && !guidance){
+        const float phi = (float)(2.0 * (double)3.14159265358979323846f * (double)u[4]);
+        const float cos_theta = (float)(1.0 - 2.0 * (double)u[5]);
+        const float sin_theta = (float)sqrt(1.0 - (double)(cos_theta * cos_theta));
+        const float x = sin_theta * cosf(phi), y = sin_theta * sinf(phi), z = cos_theta;
+        const float half = (float)(0.5 * (double)u[6]);
+        const float sn = sinf(half);
+        s.orientation[0] = cosf(half); s.orientation[1] = x * sn; s.orientation[2] = y * sn; s.orientation[3] = z * sn;
+    }
+    else { s.orientation[0] = 1; s.orientation[1] = 0; s.orientation[2] = 0; s.orientation[3] = 0; }
+#pragma unroll
+    for(int i = 0; i < 3; i++){
+        const float fs = init[9], ts = i == 2 ? init[11] / 100 : init[11];
+        s.force[i] = fs == 0 ? init[8] : nrm[i] * fs + init[8];
+        s.torque[i] = ts == 0 ? init[10] : nrm[3 + i] * ts + init[10];
+    }
+    float min_rpm, max_rpm;
+    if(init[5] != 0.0f){
+        min_rpm = (init[6] + 1) / 2 * (action_max - action_min) + action_min;
+        max_rpm = (init[7] + 1) / 2 * (action_max - action_min) + action_min;
+    }
+    else{
+        min_rpm = init[6] < 0 ? action_min : init[6];
+        max_rpm = init[7] < 0 ? action_max : init[7];
+        if(max_rpm > action_max) max_rpm = action_max;
+        if(min_rpm > max_rpm) min_rpm = max_rpm;
+    }
+#pragma unroll
+    for(int i = 0; i < 4; i++) s.rpm[i] = u[13 + i] * (max_rpm - min_rpm) + min_rpm;
+}
+// The draws of one reset: six Philox-4x32-10 blocks keyed by the seed, counter (environment, step, block + 1): words 0-16 the uniforms,
+// words 17-22 three Box-Muller pairs (both branches) for the six normals, which are only evaluated when a disturbance has a spread.
+__device__ __forceinline__ void l2f_reset_draws(unsigned long long seed, unsigned long long step, uint32_t env, bool want_normals, float (&u)[17], float (&nrm)[6]){
+    uint32_t w[24];
+#pragma unroll
+    for(int b = 0; b < 6; b++){
+        uint32_t c[4] = {env, (uint32_t)step, (uint32_t)(step >> 32), (uint32_t)(b + 1)};
+        Philox::block(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+#pragma unroll
+        for(int k = 0; k < 4; k++) w[4 * b + k] = c[k];
+    }
+#pragma unroll
+    for(int i = 0; i < 17; i++) u[i] = unit_uniform(w[i]);
+#pragma unroll
+    for(int i = 0; i < 3; i++){
+        if(want_normals){
+            const float r = sqrtf(-2.0f * logf(unit_uniform(w[17 + 2 * i]))), a = 2.0f * unit_uniform(w[18 + 2 * i]);
+            nrm[2 * i] = r * cospif(a); nrm[2 * i + 1] = r * sinpif(a);
+        }
+        else { nrm[2 * i] = 0.0f; nrm[2 * i + 1] = 0.0f; }
+    }
+}
+__global__ void l2f_initial_states_kernel(L2fRolloutArgs a, const float* __restrict__ u, const float* __restrict__ nrm, float* __restrict__ states, int n){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= n) return;
+    float uu[17], nn[6];
+#pragma unroll
+    for(int i = 0; i < 17; i++) uu[i] = u[(size_t)e * 17 + i];
+#pragma unroll
+    for(int i = 0; i < 6; i++) nn[i] = nrm[(size_t)e * 6 + i];
+    L2fState s;
+    l2f_initial_state(a.init, a.env.p.action_min, a.env.p.action_max, uu, nn, s);
+    const float* src = reinterpret_cast<const float*>(&s);
+#pragma unroll
+    for(int k = 0; k < 23; k++) states[(size_t)e * 23 + k] = src[k];
+}
 __device__ __forceinline__ void l2f_observe(const L2fState& s, float (&o)[18]){
     const float* q = s.orientation;
 #pragma unroll
@@ -308,7 +391,12 @@ __global__ void __launch_bounds__(L2F_ROLLOUT_THREADS, 1) l2f_rollout_kernel(L2f
         const size_t row = (size_t)t * a.n_envs + e;
         if(active){
             if(trunc){                                   // operations_generic_per_env.h:8-61
-                if(a.reset_states != nullptr && resets < a.n_reset_rounds){
+                if(a.device_rng){
+                    float uu[17], nn[6];
+                    l2f_reset_draws(a.rng_seed, a.rng_step0 + (unsigned long long)t, (uint32_t)e, a.init[9] != 0.0f || a.init[11] != 0.0f, uu, nn);
+                    l2f_initial_state(a.init, a.env.p.action_min, a.env.p.action_max, uu, nn, s);
+                }
+                else if(a.reset_states != nullptr && resets < a.n_reset_rounds){
                     const float* src = a.reset_states + ((size_t)resets * a.n_envs + e) * 23;
                     float* dst = reinterpret_cast<float*>(&s);
 #pragma unroll
@@ -412,10 +500,11 @@ extern "C" int b200rl_l2f_steps(const b200rl_l2f_parameters* parameters, float* 
     return B200RL_OK;
 }
 
-extern "C" int b200rl_l2f_rollout(const b200rl_l2f_parameters* parameters, const float* mdp, const b200rl_mlp_shape* actor, const float* actor_params, float* states,
-                                  int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps,
-                                  int step_limit, float* obs, float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream){
-    if(!parameters || !mdp || !actor) return B200RL_ERR_INVALID_ARGUMENT;
+static int l2f_rollout_impl(const b200rl_l2f_parameters* parameters, const float* mdp, const float* init, const b200rl_mlp_shape* actor, const float* actor_params, float* states,
+                            int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, int device_rng,
+                            unsigned long long seed, unsigned long long first_step, int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew,
+                            uint8_t* terminated, int* error_flag, cudaStream_t stream){
+    if(!parameters || !mdp || !actor || (device_rng && !init)) return B200RL_ERR_INVALID_ARGUMENT;
     if(actor->n_layers != 3 || actor->input_dim != 18 || actor->dims[0] != actor->dims[1] || actor->dims[2] != 4) return B200RL_ERR_UNSUPPORTED;
     const int H = actor->dims[0];
     if(H != 16 && H != 32 && H != 64) return B200RL_ERR_UNSUPPORTED;
@@ -431,8 +520,39 @@ extern "C" int b200rl_l2f_rollout(const b200rl_l2f_parameters* parameters, const
     a.params = actor_params; a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return;
     a.reset_states = reset_states; a.n_reset_rounds = n_reset_rounds; a.n_envs = n_envs; a.n_steps = n_steps; a.step_limit = step_limit;
     a.obs = obs; a.act = act; a.rew = rew; a.terminated = terminated; a.error_flag = error_flag;
+    a.device_rng = device_rng; a.rng_seed = seed; a.rng_step0 = first_step;
+    if(init) memcpy(a.init, init, sizeof(a.init));
     for(int l = 0; l < 3; l++) a.acts[l] = actor->acts[l];
-    if(H == 16) return launch_l2f_rollout<16>(a, (cudaStream_t)stream);
-    if(H == 32) return launch_l2f_rollout<32>(a, (cudaStream_t)stream);
-    return launch_l2f_rollout<64>(a, (cudaStream_t)stream);
+    if(H == 16) return launch_l2f_rollout<16>(a, stream);
+    if(H == 32) return launch_l2f_rollout<32>(a, stream);
+    return launch_l2f_rollout<64>(a, stream);
+}
+
+extern "C" int b200rl_l2f_rollout(const b200rl_l2f_parameters* parameters, const float* mdp, const b200rl_mlp_shape* actor, const float* actor_params, float* states,
+                                  int32_t* episode_step, uint8_t* truncated, float* episode_return, const float* reset_states, int n_reset_rounds, int n_envs, int n_steps,
+                                  int step_limit, float* obs, float* act, float* rew, uint8_t* terminated, int* error_flag, b200rl_stream_t stream){
+    return l2f_rollout_impl(parameters, mdp, nullptr, actor, actor_params, states, episode_step, truncated, episode_return, reset_states, n_reset_rounds, 0, 0, 0, n_envs, n_steps,
+                            step_limit, obs, act, rew, terminated, error_flag, (cudaStream_t)stream);
+}
+
+extern "C" int b200rl_l2f_rollout_device_rng(const b200rl_l2f_parameters* parameters, const float* mdp, const float* init, const b200rl_mlp_shape* actor, const float* actor_params,
+                                             float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return, unsigned long long seed,
+                                             unsigned long long first_step, int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, uint8_t* terminated,
+                                             b200rl_stream_t stream){
+    if(!init) return B200RL_ERR_INVALID_ARGUMENT;
+    return l2f_rollout_impl(parameters, mdp, init, actor, actor_params, states, episode_step, truncated, episode_return, nullptr, 0, 1, seed, first_step, n_envs, n_steps,
+                            step_limit, obs, act, rew, terminated, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int b200rl_l2f_initial_states_from_draws(const b200rl_l2f_parameters* parameters, const float* init, const float* uniforms, const float* normals, float* states, int n,
+                                                    b200rl_stream_t stream){
+    if(!parameters || !init || n < 0) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n == 0) return B200RL_OK;
+    if(!uniforms || !normals || !states) return B200RL_ERR_INVALID_ARGUMENT;
+    L2fRolloutArgs a{};
+    memcpy(&a.env.p, parameters->dynamics, sizeof(L2fDynamics));
+    memcpy(a.init, init, sizeof(a.init));
+    l2f_initial_states_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(a, uniforms, normals, states, n);
+    B200RL_LAUNCH_CHECK("l2f_initial_states");
+    return B200RL_OK;
 }

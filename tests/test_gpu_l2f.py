@@ -110,3 +110,62 @@ def test_l2f_rollout_argument_checks(lib, torch, fix):
     flag = torch.zeros(1, dtype=torch.int32, device="cuda")
     lib.l2f_rollout(p, fix["mdp"], shape, torch.zeros(18 * 16 + 16 + 16 * 16 + 16 + 64 + 4, device="cuda"), st, es, tr, er, None, 3, error_flag=flag)
     assert int(flag.item()) == 1                                                        # a reset without a table entry raises the flag
+
+
+def test_l2f_initial_states_from_draws_vs_oracle(lib, orc, torch, fix):
+    """sample_initial_state as a function of its draws on the device against the oracle (which equals the reference bit for bit): everything
+    but the orientation bit for bit, the orientation within the GPU's sinf / cosf; the default distribution, one whose disturbances have a
+    spread, and absolute rotor-speed bounds."""
+    rs = np.random.RandomState(12)
+    n = 5000
+    u, nrm = rs.uniform(0, 1, (n, 17)).astype(np.float32), rs.randn(n, 6).astype(np.float32)
+    p = lib.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    spread = fix["init"].copy(); spread[8:12] = (0.01, 0.02, -0.001, 0.003)
+    absolute = spread.copy(); absolute[5:8] = (0.0, 0.2, 3.0); absolute[2] = 0.0        # rpm 0.2 .. min(3, action max), no orientation draw
+    for init in (fix["init"], spread, absolute):
+        want = orc.l2f_initial_states_from_draws(init, fix["dynamics"], u, nrm)
+        got = lib.l2f_initial_states_from_draws(p, init, torch.from_numpy(u).cuda(), torch.from_numpy(nrm).cuda()).cpu().numpy()
+        rest = [c for c in range(23) if not 3 <= c < 7]
+        assert np.array_equal(got[:, rest], want[:, rest])
+        assert np.abs(got[:, 3:7] - want[:, 3:7]).max() <= 1e-6
+
+
+def test_l2f_rollout_with_device_side_resets(lib, torch, fix):
+    """Resets drawn in the kernel: the first observations follow the reference's initial-state distribution (a tenth of the quadrotors start
+    at the origin at rest, the others inside the position / velocity bounds with a proper rotation matrix, moments of a uniform
+    distribution); the draws are a function of (seed, environment, first_step + step) only: the same seed repeats, another seed differs,
+    and a call starting at step 10 resets to the states the first call drew at its step 10."""
+    N, T, limit, H = 8192, 12, 10, 32
+    rs = np.random.RandomState(5)
+    shape = lib.MlpShape.make(18, [H, H, 4], ["relu", "relu", "tanh"])
+    params = torch.from_numpy((rs.uniform(-1, 1, shape.num_params()) * 0.02).astype(np.float32)).cuda()
+    p = lib.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    init = fix["init"]
+
+    def run(seed, first_step, steps):
+        st, es, er = torch.zeros((N, 23), device="cuda"), torch.zeros(N, dtype=torch.int32, device="cuda"), torch.zeros(N, device="cuda")
+        tr = torch.ones(N, dtype=torch.uint8, device="cuda")
+        obs, act, rew, term = lib.l2f_rollout_device_rng(p, fix["mdp"], init, shape, params, st, es, tr, er, seed, first_step, steps, limit)
+        return obs.cpu().numpy().reshape(steps, N, 18), term.cpu().numpy().reshape(steps, N)
+
+    obs, term = run(77, 0, T)
+    first = obs[0]
+    guided = np.all(first[:, :3] == 0, axis=1)
+    assert 0.08 < guided.mean() < 0.12
+    assert np.all(first[guided, 12:] == 0) and np.all(first[guided, 3:12] == np.eye(3, dtype=np.float32).reshape(-1))
+    free = first[~guided]
+    assert np.all(np.abs(free[:, :3]) <= init[1]) and np.all(np.abs(free[:, 12:15]) <= init[3]) and np.all(np.abs(free[:, 15:]) <= init[4])
+    R = free[:, 3:12].reshape(-1, 3, 3).astype(np.float64)
+    assert np.abs(R @ R.transpose(0, 2, 1) - np.eye(3)).max() < 1e-5
+    assert np.abs(free[:, :3].mean(axis=0)).max() < 0.02 and np.abs(free[:, :3].var(axis=0) - init[1] ** 2 / 3).max() < 0.01
+    # rotation angle uniform in [0, 1) rad about a uniform axis: trace = 1 + 2 cos(angle)
+    angle = np.arccos(np.clip((np.trace(R, axis1=1, axis2=2) - 1) / 2, -1, 1))
+    assert angle.max() <= 1.0 + 1e-3 and abs(angle.mean() - 0.5) < 0.02
+    again, _ = run(77, 0, T)
+    other, _ = run(78, 0, T)
+    assert np.array_equal(obs, again) and not np.array_equal(obs[0], other[0])
+    whole = ~term[:limit].any(axis=0)                     # no termination in the first episode: these reset exactly at step 10
+    assert whole.sum() > N // 2
+    shifted, _ = run(77, limit, 1)
+    assert np.array_equal(shifted[0][whole], obs[limit][whole])
+

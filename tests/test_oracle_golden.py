@@ -385,3 +385,25 @@ def test_c5_chunk_65536_forward_rows_match_reference(orc):
         assert np.array_equal(pre[off:off + rows.size * d].reshape(rows.size, d), fix[f"pre_{l}"])
         assert np.array_equal(out[off:off + rows.size * d].reshape(rows.size, d), fix[f"out_{l}"])
         off += rows.size * d
+
+
+def test_l2f_initial_state_sampler_matches_reference(orc):
+    """sample_initial_state restated with the engine's draws: 1,800 consecutive calls on one engine equal the fixture written by the reference
+    bit for bit (position, orientation, velocities, rotor speeds; the default disturbances have no spread and draw nothing), and the state
+    as a function of explicit draws agrees with it where the draw decides nothing else (guidance off: positions inside +-max_position ...)."""
+    fix = np.load(os.path.join(GOLDEN, "l2f.npz"))
+    got = orc.l2f_sample_initial_states(mg.L2F_INIT_SEED, 1800, fix["init"], fix["dynamics"])
+    assert np.array_equal(got.reshape(3, 600, 23), fix["initial_states"])
+    rs = np.random.RandomState(2)
+    u, nrm = rs.uniform(0, 1, (500, 17)).astype(np.float32), rs.randn(500, 6).astype(np.float32)
+    init = fix["init"].copy(); init[8:12] = (0.01, 0.02, -0.001, 0.003)       # disturbances with a spread
+    st = orc.l2f_initial_states_from_draws(init, fix["dynamics"], u, nrm)
+    guided = u[:, 0] < init[0]
+    assert 20 < guided.sum() < 90 and np.all(st[guided, :3] == 0) and np.all(st[guided, 3] == 1) and np.all(st[guided, 7:13] == 0)
+    free = ~guided
+    assert np.all(np.abs(st[free, :3]) <= init[1]) and np.all(np.abs(st[free, 7:10]) <= init[3]) and np.all(np.abs(st[free, 10:13]) <= init[4])
+    assert np.allclose(np.linalg.norm(st[:, 3:7], axis=1), 1.0, atol=1e-6)
+    assert np.array_equal(st[:, 13:16], nrm[:, :3] * np.float32(0.02) + np.float32(0.01))
+    assert np.array_equal(st[:, 18], nrm[:, 5] * (np.float32(0.003) / np.float32(100)) + np.float32(-0.001))
+    assert np.all(st[:, 19:] >= 0) and np.all(st[:, 19:] <= 0.5)             # relative rotor speeds -1 .. 0 of the action range 0 .. 1
+

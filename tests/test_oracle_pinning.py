@@ -248,3 +248,13 @@ def test_acrobot_live(orc, ref_strict):
     want, got = ref_strict.acrobot_terminating_rollout(params, *zero(), table, T, limit), orc.acrobot_terminating_rollout(shape, params, *zero(), table, T, limit)
     for k in want:
         assert np.array_equal(want[k], got[k]), k
+
+
+def test_l2f_initial_state_sampler_live(orc, ref_strict):
+    """sample_initial_state of the L2F environment: the oracle's restatement with the engine's draws against the reference for several seeds,
+    3,000 consecutive states each, bit for bit."""
+    dynamics, _, _ = ref_strict.l2f_parameters()
+    init = ref_strict.l2f_init()
+    for seed in (0, 7, 1234567):
+        assert np.array_equal(orc.l2f_sample_initial_states(seed, 3000, init, dynamics), ref_strict.l2f_initial_states(seed, 3000)), seed
+

@@ -17,13 +17,18 @@
 #include "common.cuh"
 #include <cstdlib>
 #include <mutex>
+#include <vector>
 
 namespace b200rl {
 
 constexpr int CO_T = 32, CO_KC = 256, CO_PITCH = 36, CO_THREADS = 256, CO_WARPS = 8;
 constexpr size_t CO_SMEM = sizeof(float) * 2 * CO_KC * CO_PITCH;          // both operand tiles; the eight partial tiles (32 KB) reuse the space
 constexpr unsigned CO_SPIN_LIMIT = 1000000u;                              // polls of the barrier words (two L2 round trips each): about a second
-constexpr int CO_SLOTS = 256;                                             // barrier words per device, handed out round-robin per launch
+// Barrier words per device, handed out round-robin per launch (a captured launch keeps the slot it got at capture time). Two launches may
+// share a slot as long as they never run at the same time: launches on one stream never do, and the parallel branches of one captured graph
+// get consecutive slots. What is not supported: two launches whose slots coincide after a wrap of the ring (4,096 launches apart) running
+// concurrently on different streams.
+constexpr int CO_SLOTS = 4096;
 
 enum { CO_EPI_FORWARD = 0, CO_EPI_DX = 1, CO_EPI_DW = 2 };
 struct CoopGemm {                    // C(m, n) = sum_k A(m, k) B(n, k); *_kcontig: the summed index is the contiguous one in memory
@@ -386,8 +391,8 @@ extern "C" int b200rl_cooperative_pass_status(int* status){
     if(!status) return B200RL_ERR_INVALID_ARGUMENT;
     void* p = nullptr;
     B200RL_CUDA_TRY(cudaGetSymbolAddress(&p, g_coop_barriers));
-    static unsigned host[CO_SLOTS * 4];
-    B200RL_CUDA_TRY(cudaMemcpy(host, p, sizeof(host), cudaMemcpyDeviceToHost));
+    std::vector<unsigned> host(CO_SLOTS * 4);
+    B200RL_CUDA_TRY(cudaMemcpy(host.data(), p, host.size() * sizeof(unsigned), cudaMemcpyDeviceToHost));
     *status = 0;
     for(int i = 0; i < CO_SLOTS; i++) if(host[4 * i + 2] != 0u) *status = 1;
     return B200RL_OK;

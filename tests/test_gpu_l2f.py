@@ -99,6 +99,38 @@ def test_l2f_rollout_vs_oracle(lib, orc, torch, fix, hidden):
     assert term.sum() > 0 and (want["episode_step"] < T).all()
 
 
+@pytest.mark.parametrize("N", [1, 31, 449])
+def test_l2f_rollout_ragged_environment_counts(lib, orc, torch, fix, N):
+    """Environment counts that leave most of a warp, or of the second CTA, idle: the idle lanes take part in their warp's tiles without
+    touching memory. Same checks as the full-size case, 8 steps with an episode limit of 5."""
+    import oracle
+    T, limit, hidden = 8, 5, 16
+    rs = np.random.RandomState(N)
+    acts = ["relu", "tanh", "tanh"]
+    shape, oshape = lib.MlpShape.make(18, [hidden, hidden, 4], acts), oracle.MlpShape.make(18, [hidden, hidden, 4], acts)
+    params = (rs.uniform(-1, 1, oshape.num_params()) * 0.25).astype(np.float32)
+    init = np.ascontiguousarray(fix["initial_states"][:2, :N])
+    p = lib.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    guard = 64                                                    # rows behind the outputs must stay untouched
+    obs = torch.full((T * N + guard, 18), 7.0, device="cuda"); act = torch.full((T * N + guard, 4), 7.0, device="cuda")
+    rew = torch.full((T * N + guard,), 7.0, device="cuda"); term = torch.full((T * N + guard,), 7, dtype=torch.uint8, device="cuda")
+    st, es, er = torch.zeros((N, 23), device="cuda"), torch.zeros(N, dtype=torch.int32, device="cuda"), torch.zeros(N, device="cuda")
+    tr = torch.ones(N, dtype=torch.uint8, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.l2f_rollout(p, fix["mdp"], shape, torch.from_numpy(params).cuda(), st, es, tr, er, torch.from_numpy(init).cuda(), T, limit, obs=obs, act=act, rew=rew, terminated=term,
+                    error_flag=flag)
+    assert int(flag.item()) == 0
+    assert bool((obs[T * N:] == 7).all()) and bool((act[T * N:] == 7).all()) and bool((rew[T * N:] == 7).all()) and bool((term[T * N:] == 7).all())
+    want = orc.l2f_rollout(oshape, params, fix["dynamics"], float(fix["dt"]), fix["mdp"], np.zeros((N, 23), np.float32), np.zeros(N, np.int32), np.ones(N, np.uint8),
+                           np.zeros(N, np.float32), init, T, limit)
+    o, a_ = obs[:T * N].cpu().numpy(), act[:T * N].cpu().numpy()
+    assert np.array_equal(o[:N], want["obs"][:N])
+    ref_act = orc.mlp_evaluate(oshape, params, o)
+    assert np.all(np.abs(a_.astype(np.float64) - ref_act) <= 1e-6 + 1e-5 * np.abs(ref_act))
+    assert np.all(np.abs(o.astype(np.float64) - want["obs"]) <= 1e-5 + 1e-4 * np.abs(want["obs"]))
+    assert np.array_equal(term[:T * N].cpu().numpy(), want["terminated"]) and np.array_equal(es.cpu().numpy(), want["episode_step"])
+
+
 def test_l2f_rollout_argument_checks(lib, torch, fix):
     p = lib.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
     st, es, er = torch.zeros((4, 23), device="cuda"), torch.zeros(4, dtype=torch.int32, device="cuda"), torch.zeros(4, device="cuda")

@@ -323,36 +323,43 @@ struct L2fRolloutLayout {
     __host__ __device__ static constexpr int slot(int j){ return ((j / 8) / VW) * (8 * VW) + (j % 8) * VW + (j / 8) % VW; }
 };
 
-// acc[ee][jj] += sum over k of act[k][8 eg + ee] * wT[k][slot(og + 8 jj)], k ascending; act rows have the pitch ACT_PITCH
+// acc[ee][jj] += sum over k of act[k][8 eg + ee] * wT[k][slot(og + 8 jj)], k ascending; act rows have the pitch ACT_PITCH. Two units advance
+// with one packed multiply-add (each half is the same fused multiply-add as before; the kernel is bound by instruction issue).
 template <int H, int K, int ACT_PITCH>
-__device__ __forceinline__ void l2f_tile_layer(const float* __restrict__ act_tile, const float* __restrict__ wT, int eg, int og, float (&acc)[8][H / 8]){
+__device__ __forceinline__ void l2f_tile_layer(const float* __restrict__ act_tile, const float* __restrict__ wT, int eg, int og, float2 (&acc)[8][H / 16]){
     using L = L2fRolloutLayout<H>;
 #pragma unroll 2
     for(int k = 0; k < K; k++){
-        float x[8], w[L::JPT];
+        float x[8];
+        float2 w[L::JPT / 2];
         const float4 x0 = *reinterpret_cast<const float4*>(act_tile + k * ACT_PITCH + eg * 8), x1 = *reinterpret_cast<const float4*>(act_tile + k * ACT_PITCH + eg * 8 + 4);
         x[0] = x0.x; x[1] = x0.y; x[2] = x0.z; x[3] = x0.w; x[4] = x1.x; x[5] = x1.y; x[6] = x1.z; x[7] = x1.w;
 #pragma unroll
         for(int v = 0; v < L::NV; v++){
             const float* src = wT + k * H + v * (8 * L::VW) + og * L::VW;
-            if constexpr (L::VW == 4){ const float4 t = *reinterpret_cast<const float4*>(src); w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w; }
-            else { const float2 t = *reinterpret_cast<const float2*>(src); w[0] = t.x; w[1] = t.y; }
+            if constexpr (L::VW == 4){ const float4 t = *reinterpret_cast<const float4*>(src); w[2 * v] = make_float2(t.x, t.y); w[2 * v + 1] = make_float2(t.z, t.w); }
+            else w[0] = *reinterpret_cast<const float2*>(src);
         }
 #pragma unroll
-        for(int ee = 0; ee < 8; ee++)
+        for(int ee = 0; ee < 8; ee++){
+            const float2 xx = make_float2(x[ee], x[ee]);
 #pragma unroll
-            for(int jj = 0; jj < L::JPT; jj++) acc[ee][jj] = fmaf(w[jj], x[ee], acc[ee][jj]);
+            for(int jp = 0; jp < L::JPT / 2; jp++) acc[ee][jp] = __ffma2_rn(w[jp], xx, acc[ee][jp]);
+        }
     }
 }
 // bias in, activation out: the lane's tile goes to the hidden tile as rows [unit][quadrotor of the warp]
 template <int H>
-__device__ __forceinline__ void l2f_tile_store(float* hid, float (&acc)[8][H / 8], int eg, int og, int act){
+__device__ __forceinline__ void l2f_tile_store(float* hid, float2 (&acc)[8][H / 16], int eg, int og, int act){
     using L = L2fRolloutLayout<H>;
 #pragma unroll
     for(int jj = 0; jj < L::JPT; jj++){
         float* row = hid + (og + 8 * jj) * L::PITCH + eg * 8;
-        *reinterpret_cast<float4*>(row) = make_float4(activation_rt(acc[0][jj], act), activation_rt(acc[1][jj], act), activation_rt(acc[2][jj], act), activation_rt(acc[3][jj], act));
-        *reinterpret_cast<float4*>(row + 4) = make_float4(activation_rt(acc[4][jj], act), activation_rt(acc[5][jj], act), activation_rt(acc[6][jj], act), activation_rt(acc[7][jj], act));
+        float v[8];
+#pragma unroll
+        for(int ee = 0; ee < 8; ee++) v[ee] = activation_rt((jj & 1) ? acc[ee][jj / 2].y : acc[ee][jj / 2].x, act);
+        *reinterpret_cast<float4*>(row) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(row + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
 }
 
@@ -416,24 +423,24 @@ __global__ void __launch_bounds__(L2F_ROLLOUT_THREADS, 1) l2f_rollout_kernel(L2f
         }
         __syncwarp();
         {
-            float acc[8][L::JPT];
+            float2 acc[8][L::JPT / 2];
 #pragma unroll
-            for(int jj = 0; jj < L::JPT; jj++){
-                const float b = smem[L::B1 + og + 8 * jj];
+            for(int jp = 0; jp < L::JPT / 2; jp++){
+                const float2 b = make_float2(smem[L::B1 + og + 16 * jp], smem[L::B1 + og + 16 * jp + 8]);
 #pragma unroll
-                for(int ee = 0; ee < 8; ee++) acc[ee][jj] = b;
+                for(int ee = 0; ee < 8; ee++) acc[ee][jp] = b;
             }
             l2f_tile_layer<H, O, 32>(obs_tile, smem + L::W1T, eg, og, acc);
             l2f_tile_store<H>(hid, acc, eg, og, a.acts[0]);
         }
         __syncwarp();
         {
-            float acc[8][L::JPT];
+            float2 acc[8][L::JPT / 2];
 #pragma unroll
-            for(int jj = 0; jj < L::JPT; jj++){
-                const float b = smem[L::B2 + og + 8 * jj];
+            for(int jp = 0; jp < L::JPT / 2; jp++){
+                const float2 b = make_float2(smem[L::B2 + og + 16 * jp], smem[L::B2 + og + 16 * jp + 8]);
 #pragma unroll
-                for(int ee = 0; ee < 8; ee++) acc[ee][jj] = b;
+                for(int ee = 0; ee < 8; ee++) acc[ee][jp] = b;
             }
             l2f_tile_layer<H, H, L::PITCH>(hid, smem + L::W2T, eg, og, acc);
             __syncwarp();                                // every lane has read the first hidden layer before the second overwrites it

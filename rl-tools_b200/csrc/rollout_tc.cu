@@ -73,7 +73,17 @@ constexpr int C_COUNT_MAX = H * MAX_OBS + 3 * H + 1;
 // of the FMA instructions they cost no load instruction and no shared-memory bandwidth (a warp-wide broadcast LDS.128
 // occupies the 128 B/clk shared pipe for 4 cycles, which made the table look-ups the bottleneck of the CUDA-core
 // phase). Filled by a device-to-device copy on the launch stream; launches are ordered by an event (see launch_tc).
-__constant__ float c_actor[C_COUNT_MAX + 3];
+__constant__ __align__(16) float c_actor[C_COUNT_MAX + 3];
+// The first layer's weights once more, as pairs of neighbouring units: c_w1_pairs[(j / 2) * OBS + k] = (W1[j][k], W1[j + 1][k]), j even, so
+// that two units advance with one packed multiply-add (the issue slots, not the arithmetic pipes, bound this kernel). Written by
+// pack_w1_pairs_kernel on the launch stream.
+__constant__ __align__(16) float2 c_w1_pairs[(H / 2) * MAX_OBS];
+__global__ void pack_w1_pairs_kernel(const float* __restrict__ params, int obs_dim, float2* __restrict__ dst){
+    for(int i = threadIdx.x; i < (H / 2) * obs_dim; i += blockDim.x){
+        const int pair = i / obs_dim, k = i % obs_dim;
+        dst[i] = make_float2(params[(2 * pair) * obs_dim + k], params[(2 * pair + 1) * obs_dim + k]);
+    }
+}
 
 // x = lead + rest + O(2^-24 x): lead = fp16(x) (11 significant bits), rest = fp16(x - lead). Two values per register, the lower index in
 // the low half. Conversions saturate at +-65504 instead of producing infinities.
@@ -283,20 +293,22 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
 
             // ---- layer 1 (CUDA cores, weights as constant-bank operands); leading fp16 parts -> TMEM, remainder parts -> swizzled smem tile ----
             uint32_t lead_all[32];
+            float2 o2[O];
+#pragma unroll
+            for(int k = 0; k < O; k++) o2[k] = make_float2(o[k], o[k]);
 #pragma unroll
             for(int c = 0; c < 8; c++){                  // 16-byte chunk c of the row: units 8c .. 8c+7
                 uint32_t lead[4], rest[4];
 #pragma unroll
                 for(int q = 0; q < 4; q++){
                     float h[2];
+                    {
+                        const int pair = c * 4 + q;                                          // units 2 pair, 2 pair + 1
+                        float2 acc = *reinterpret_cast<const float2*>(&c_actor[C_B1 + 2 * pair]);            // bias first, inputs ascending: the reference's order
 #pragma unroll
-                    for(int z = 0; z < 2; z++){
-                        const int j = c * 8 + q * 2 + z;
-                        float acc = c_actor[C_B1 + j];                                       // bias first, inputs ascending: the reference's order
-#pragma unroll
-                        for(int k = 0; k < O; k++) acc = fmaf(c_actor[C_W1 + O * j + k], o[k], acc);
-                        if constexpr(A1 == B200RL_ACT_RELU) h[z] = acc;             // the ReLU rides on the conversions below
-                        else h[z] = act_or_rt<A1>(acc, act1);
+                        for(int k = 0; k < O; k++) acc = __ffma2_rn(c_w1_pairs[pair * O + k], o2[k], acc);
+                        if constexpr(A1 == B200RL_ACT_RELU){ h[0] = acc.x; h[1] = acc.y; }       // the ReLU rides on the conversions below
+                        else { h[0] = act_or_rt<A1>(acc.x, act1); h[1] = act_or_rt<A1>(acc.y, act1); }
                     }
                     if constexpr(A1 == B200RL_ACT_RELU) split_f16_pair_relu(h[0], h[1], lead[q], rest[q]);
                     else split_f16_pair(h[0], h[1], lead[q], rest[q]);
@@ -343,7 +355,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             tc::fence_after_thread_sync();
 
             // ---- epilogue: activation of layer 2 (bias came through the MMA), output layer 64 -> 1 (four partial sums) ----
-            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+            float2 oa = make_float2(0.0f, 0.0f), ob = make_float2(0.0f, 0.0f);      // partial sums of units j = 0, 1 (mod 4) and j = 2, 3 (mod 4)
 #pragma unroll
             for(int half = 0; half < 2; half++){
                 uint32_t d[32];
@@ -355,13 +367,13 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                     // ReLU commutes with the positive scale: it is taken out once after the sum; other activations scale each unit back first
                     constexpr bool HOMOGENEOUS = A2 == B200RL_ACT_RELU || A2 == B200RL_ACT_IDENTITY;
                     const float back = HOMOGENEOUS ? 1.0f : w_unscale;
-                    o0 = fmaf(c_actor[C_W3 + j + 0], act_or_rt<A2>(__uint_as_float(d[p * 4 + 0]) * back, act2), o0);
-                    o1 = fmaf(c_actor[C_W3 + j + 1], act_or_rt<A2>(__uint_as_float(d[p * 4 + 1]) * back, act2), o1);
-                    o2 = fmaf(c_actor[C_W3 + j + 2], act_or_rt<A2>(__uint_as_float(d[p * 4 + 2]) * back, act2), o2);
-                    o3 = fmaf(c_actor[C_W3 + j + 3], act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]) * back, act2), o3);
+                    const float2 ha = make_float2(act_or_rt<A2>(__uint_as_float(d[p * 4 + 0]) * back, act2), act_or_rt<A2>(__uint_as_float(d[p * 4 + 1]) * back, act2));
+                    const float2 hb = make_float2(act_or_rt<A2>(__uint_as_float(d[p * 4 + 2]) * back, act2), act_or_rt<A2>(__uint_as_float(d[p * 4 + 3]) * back, act2));
+                    oa = __ffma2_rn(*reinterpret_cast<const float2*>(&c_actor[C_W3 + j]), ha, oa);
+                    ob = __ffma2_rn(*reinterpret_cast<const float2*>(&c_actor[C_W3 + j + 2]), hb, ob);
                 }
             }
-            const float osum = (o0 + o1) + (o2 + o3);
+            const float osum = (oa.x + oa.y) + (ob.x + ob.y);
             float action = activation_rt(c_actor[C_B3] + ((A2 == B200RL_ACT_RELU || A2 == B200RL_ACT_IDENTITY) ? osum * w_unscale : osum), act3);
             if constexpr(COLLECT){
                 const float mean = action;
@@ -430,7 +442,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
 // The kernel fills every SM, so this ordering costs no concurrency. The event, like the kernel's shared-memory attribute, belongs
 // to a device: both are kept per device ordinal.
 namespace {
-struct TcDeviceState { cudaEvent_t order = nullptr; bool configured[3][16] = {}; };
+struct TcDeviceState { cudaEvent_t order = nullptr; bool configured[3][16] = {}; float2* w1_pairs = nullptr; };
 TcDeviceState g_tc_state[MAX_DEVICES];
 std::mutex g_tc_mutex;
 }
@@ -444,6 +456,13 @@ static int upload_small_layers(TcDeviceState& st, const float* params, int obs_d
     if(*order_event) B200RL_CUDA_TRY(cudaStreamWaitEvent(s, st.order, 0));
     B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params, sizeof(float) * (size_t)L.P_W2, 0, cudaMemcpyDeviceToDevice, s));                           // W1, b1
     B200RL_CUDA_TRY(cudaMemcpyToSymbolAsync(c_actor, params + L.P_B2, sizeof(float) * (2 * H + 1), sizeof(float) * (size_t)L.C_B2, cudaMemcpyDeviceToDevice, s));   // b2, W3, b3
+    if(!st.w1_pairs){                                            // the symbol's address on this device
+        void* p = nullptr;
+        B200RL_CUDA_TRY(cudaGetSymbolAddress(&p, c_w1_pairs));
+        st.w1_pairs = static_cast<float2*>(p);
+    }
+    pack_w1_pairs_kernel<<<1, 128, 0, s>>>(params, obs_dim, st.w1_pairs);
+    B200RL_LAUNCH_CHECK("pack_w1_pairs");
     return B200RL_OK;
 }
 

@@ -19,37 +19,39 @@ constexpr int BM = 64, BN = 64, BK = 16, GEMM_THREADS = 256, PADM = 4;
 
 // One k-step of an operand tile travels global -> registers -> shared memory, so that the loads of step k+1 are in flight while
 // step k is multiplied (the batch-256 and 64-wide problems run on few CTAs and are bound by this latency, not by bandwidth).
-// Tile element (k, r) = P(row0 + r, k0 + k), zero outside [0, rows) x [k0, k_end); T / 16 elements per thread (T = tile edge).
-template <int T, bool KCONTIG>
-__device__ __forceinline__ void fetch_tile(float (&reg)[T / 16], const float* __restrict__ P, long long ld, int row0, int rows, int k0, int k_end, int tid){
+// Tile element (k, r) = P(row0 + r, k0 + k), zero outside [0, rows) x [k0, k_end); T * KS / 256 elements per thread (T = tile edge, KS = k
+// step). The 32-wide tiles take k steps of 64: they exist for problems that fill few SMs, where a tile's time is (number of k steps) x
+// (one L2 round trip), so four times fewer, four times larger steps (8 loads in flight per thread and operand instead of 2).
+template <int T, int KS, bool KCONTIG>
+__device__ __forceinline__ void fetch_tile(float (&reg)[T * KS / GEMM_THREADS], const float* __restrict__ P, long long ld, int row0, int rows, int k0, int k_end, int tid){
     if constexpr(KCONTIG){
-        const int k = tid % BK, r = tid / BK;            // 16 consecutive k per row -> 64-byte segments
+        const int k = tid % KS, r = tid / KS;            // KS consecutive k per row -> 64- or 256-byte segments
 #pragma unroll
-        for(int j = 0; j < T / 16; j++){
-            const int gr = row0 + r + j * (GEMM_THREADS / BK), gk = k0 + k;
+        for(int j = 0; j < T * KS / GEMM_THREADS; j++){
+            const int gr = row0 + r + j * (GEMM_THREADS / KS), gk = k0 + k;
             reg[j] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gr * ld + gk) : 0.0f;
         }
     }
     else{
         const int r = tid % T, k = tid / T;              // T consecutive rows (contiguous in memory) per k
 #pragma unroll
-        for(int j = 0; j < T / 16; j++){
+        for(int j = 0; j < T * KS / GEMM_THREADS; j++){
             const int gr = row0 + r, gk = k0 + k + j * (GEMM_THREADS / T);
             reg[j] = (gr < rows && gk < k_end) ? __ldg(P + (long long)gk * ld + gr) : 0.0f;
         }
     }
 }
-template <int T, bool KCONTIG>
-__device__ __forceinline__ void store_tile(float (*S)[T + PADM], const float (&reg)[T / 16], int tid){
+template <int T, int KS, bool KCONTIG>
+__device__ __forceinline__ void store_tile(float (*S)[T + PADM], const float (&reg)[T * KS / GEMM_THREADS], int tid){
     if constexpr(KCONTIG){
-        const int k = tid % BK, r = tid / BK;
+        const int k = tid % KS, r = tid / KS;
 #pragma unroll
-        for(int j = 0; j < T / 16; j++) S[k][r + j * (GEMM_THREADS / BK)] = reg[j];
+        for(int j = 0; j < T * KS / GEMM_THREADS; j++) S[k][r + j * (GEMM_THREADS / KS)] = reg[j];
     }
     else{
         const int r = tid % T, k = tid / T;
 #pragma unroll
-        for(int j = 0; j < T / 16; j++) S[k + j * (GEMM_THREADS / T)][r] = reg[j];
+        for(int j = 0; j < T * KS / GEMM_THREADS; j++) S[k + j * (GEMM_THREADS / T)][r] = reg[j];
     }
 }
 
@@ -57,9 +59,9 @@ __device__ __forceinline__ void store_tile(float (*S)[T + PADM], const float (&r
 template <int T, bool A_KCONTIG, bool B_KCONTIG, int EPI, int ACT>
 __global__ void __launch_bounds__(GEMM_THREADS) gemm_kernel(GemmArgs a){
     static_assert(T == 64 || T == 32);
-    constexpr int R = T / 16;
-    __shared__ __align__(16) float As[BK][T + PADM];
-    __shared__ __align__(16) float Bs[BK][T + PADM];
+    constexpr int R = T / 16, KS = T == 64 ? BK : 4 * BK, NREG = T * KS / GEMM_THREADS;
+    __shared__ __align__(16) float As[KS][T + PADM];
+    __shared__ __align__(16) float Bs[KS][T + PADM];
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * T, n0 = blockIdx.x * T;
     const int k_begin = blockIdx.z * a.k_per_split;
@@ -71,19 +73,19 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_kernel(GemmArgs a){
 #pragma unroll
         for(int j = 0; j < R; j++) acc[i][j] = 0.0f;
 
-    float ra[R], rb[R];
-    fetch_tile<T, A_KCONTIG>(ra, a.A, a.lda, m0, a.M, k_begin, k_end, tid);
-    fetch_tile<T, B_KCONTIG>(rb, a.B, a.ldb, n0, a.N, k_begin, k_end, tid);
-    for(int k0 = k_begin; k0 < k_end; k0 += BK){
-        store_tile<T, A_KCONTIG>(As, ra, tid);
-        store_tile<T, B_KCONTIG>(Bs, rb, tid);
+    float ra[NREG], rb[NREG];
+    fetch_tile<T, KS, A_KCONTIG>(ra, a.A, a.lda, m0, a.M, k_begin, k_end, tid);
+    fetch_tile<T, KS, B_KCONTIG>(rb, a.B, a.ldb, n0, a.N, k_begin, k_end, tid);
+    for(int k0 = k_begin; k0 < k_end; k0 += KS){
+        store_tile<T, KS, A_KCONTIG>(As, ra, tid);
+        store_tile<T, KS, B_KCONTIG>(Bs, rb, tid);
         __syncthreads();
-        if(k0 + BK < k_end){
-            fetch_tile<T, A_KCONTIG>(ra, a.A, a.lda, m0, a.M, k0 + BK, k_end, tid);
-            fetch_tile<T, B_KCONTIG>(rb, a.B, a.ldb, n0, a.N, k0 + BK, k_end, tid);
+        if(k0 + KS < k_end){
+            fetch_tile<T, KS, A_KCONTIG>(ra, a.A, a.lda, m0, a.M, k0 + KS, k_end, tid);
+            fetch_tile<T, KS, B_KCONTIG>(rb, a.B, a.ldb, n0, a.N, k0 + KS, k_end, tid);
         }
 #pragma unroll
-        for(int k = 0; k < BK; k++){
+        for(int k = 0; k < KS; k++){
             float am[R], bn[R];
             if constexpr(R == 4){
                 const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);

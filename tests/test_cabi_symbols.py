@@ -123,6 +123,23 @@ def test_argument_validation_of_the_later_entry_points(lib):
     assert L.b200rl_env_rollout(lib.ENV_ACROBOT_SWINGUP, C.byref(shape3), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None) == 2
     assert L.b200rl_env_rollout(lib.ENV_ACROBOT_SWINGUP, C.byref(shape6), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None) == 1
     assert (L.b200rl_env_observation_dim(0), L.b200rl_env_state_dim(0), L.b200rl_env_observation_dim(1), L.b200rl_env_state_dim(1)) == (3, 2, 6, 4)
+    # the L2F entry points: missing parameter blocks, an actor that is not 18 -> H -> H -> 4 with H in {16, 32, 64}, missing outputs
+    p = lib.L2fParameters.make(np.zeros(85, np.float32), 0.01)
+    mdp, init = (C.c_float * 18)(), (C.c_float * 12)()
+    good, wide = lib.MlpShape.make(18, [32, 32, 4], ["relu", "relu", "tanh"]), lib.MlpShape.make(18, [48, 48, 4], ["relu", "relu", "tanh"])
+    assert L.b200rl_l2f_steps(None, None, None, 4, 1, None) == 1 and L.b200rl_l2f_steps(C.byref(p), None, None, 4, 1, None) == 1
+    assert L.b200rl_l2f_steps(C.byref(p), None, None, 0, 1, None) == 0                                          # nothing to do
+    assert L.b200rl_l2f_rollout(C.byref(p), None, C.byref(good), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None, None) == 1
+    assert L.b200rl_l2f_rollout(C.byref(p), mdp, C.byref(wide), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None, None) == 2
+    assert L.b200rl_l2f_rollout(C.byref(p), mdp, C.byref(good), None, None, None, None, None, None, 0, 4, 4, 10, None, None, None, None, None, None) == 1
+    assert L.b200rl_l2f_rollout_device_rng(C.byref(p), mdp, None, C.byref(good), None, None, None, None, None, 1, 0, 4, 4, 10, None, None, None, None, None) == 1
+    assert L.b200rl_l2f_rollout_device_rng(C.byref(p), mdp, init, C.byref(wide), None, None, None, None, None, 1, 0, 4, 4, 10, None, None, None, None, None) == 2
+    assert L.b200rl_l2f_rollout_device_rng(C.byref(p), mdp, init, C.byref(good), None, None, None, None, None, 1, 0, 4, 0, 10, None, None, None, None, None) == 0
+    assert L.b200rl_l2f_initial_states_from_draws(C.byref(p), None, None, None, None, 4, None) == 1
+    assert L.b200rl_l2f_initial_states_from_draws(C.byref(p), init, None, None, None, 4, None) == 1
+    assert L.b200rl_l2f_initial_states_from_draws(C.byref(p), init, None, None, None, 0, None) == 0
+    L.b200rl_cooperative_pass_status.argtypes = [C.POINTER(C.c_int)]
+    assert L.b200rl_cooperative_pass_status(None) == 1
     # host-side draws of gather_batch: an empty replay buffer is refused, like the reference's assertion
     state = lib.rng_init_host(3)
     out = np.zeros(4, np.int32)

@@ -224,11 +224,18 @@ __global__ void __launch_bounds__(FUSED_THREADS) mlp_fused_backward_chain_kernel
 // ---------------------------------------------------------------------------------------------------------------------------------------
 // backward, part 2: dW_l += d_pre_l^T in_l and db_l += column sums of d_pre_l, all layers in one grid. A tile is 32 outputs x 32 columns
 // of the row-extended matrix [in_l | 1] (the column of ones yields the bias gradient); blockIdx.y is the batch slice.
+// A CTA brings 128 rows of both operands into shared memory per round (16 loads in flight per thread and operand: two L2 round trips per
+// 256-row slice instead of eight), its eight warps take interleaved rows with a 4 x 8 patch of the tile per lane (three 16-byte
+// shared-memory loads per 32 multiply-adds), and the eight partial tiles are added in warp order.
 // ---------------------------------------------------------------------------------------------------------------------------------------
+constexpr int GRADS_ROWS = 128, GRADS_PITCH = 36;
 __global__ void __launch_bounds__(256) mlp_fused_grads_kernel(FusedShape sh, const float* __restrict__ x, long long ldx, const float* __restrict__ outs,
                                                               const float* __restrict__ dpre, float* grads, float* partial, unsigned int* counters, int n_slices){
-    __shared__ float s_d[32][33], s_in[32][33];
+    __shared__ __align__(16) float s_all[2 * GRADS_ROWS * GRADS_PITCH];          // d_pre rows, then input rows; the eight partial tiles reuse it
     __shared__ bool is_last;
+    float (*s_d)[GRADS_PITCH] = reinterpret_cast<float (*)[GRADS_PITCH]>(s_all);
+    float (*s_in)[GRADS_PITCH] = s_d + GRADS_ROWS;
+    static_assert(8 * 32 * 32 <= 2 * GRADS_ROWS * GRADS_PITCH, "partial tiles");
     const int tile = blockIdx.x, slice = blockIdx.y;
     int l = 0;
     while(l + 1 < sh.n_layers && tile >= sh.tile_begin[l + 1]) l++;
@@ -239,45 +246,71 @@ __global__ void __launch_bounds__(256) mlp_fused_grads_kernel(FusedShape sh, con
     const float* in = l ? outs + sh.aoff[l - 1] : x;
     const long long ldin = l ? I : ldx;
     const float* dp = dpre + sh.aoff[l];
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // thread: outputs o_base + ty, + 16; columns i_base + tx, + 16
-    float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rg = lane >> 2, cg = lane & 3;      // lane: outputs 4 rg .. + 3, columns 8 cg .. + 7
+    float acc[4][8];
+#pragma unroll
+    for(int p = 0; p < 4; p++)
+#pragma unroll
+        for(int q = 0; q < 8; q++) acc[p][q] = 0.0f;
     const int b_begin = slice * FUSED_SLICE, b_end = min(sh.batch, b_begin + FUSED_SLICE);
-    for(int b0 = b_begin; b0 < b_end; b0 += 32){
-        for(int idx = threadIdx.x; idx < 32 * 32; idx += 256){
-            const int bb = idx >> 5, c = idx & 31;
-            const int b = b0 + bb;
-            s_d[bb][c] = (b < b_end && o_base + c < O) ? dp[(long long)b * O + o_base + c] : 0.0f;
-            const int i = i_base + c;
-            s_in[bb][c] = b < b_end ? (i < I ? in[(long long)b * ldin + i] : (i == I ? 1.0f : 0.0f)) : 0.0f;
+    for(int b0 = b_begin; b0 < b_end; b0 += GRADS_ROWS){
+        float rd[GRADS_ROWS * 32 / 256], ri[GRADS_ROWS * 32 / 256];
+#pragma unroll
+        for(int u = 0; u < GRADS_ROWS * 32 / 256; u++){
+            const int idx = threadIdx.x + u * 256, bb = idx >> 5, c = idx & 31, b = b0 + bb, i = i_base + c;
+            rd[u] = (b < b_end && o_base + c < O) ? dp[(long long)b * O + o_base + c] : 0.0f;
+            ri[u] = b < b_end ? (i < I ? in[(long long)b * ldin + i] : (i == I ? 1.0f : 0.0f)) : 0.0f;
+        }
+        __syncthreads();                                  // the previous round's rows have been read
+#pragma unroll
+        for(int u = 0; u < GRADS_ROWS * 32 / 256; u++){
+            const int idx = threadIdx.x + u * 256, bb = idx >> 5, c = idx & 31;
+            s_d[bb][c] = rd[u]; s_in[bb][c] = ri[u];
         }
         __syncthreads();
-#pragma unroll 8
-        for(int bb = 0; bb < 32; bb++){
-            const float d0 = s_d[bb][ty], d1 = s_d[bb][ty + 16], v0 = s_in[bb][tx], v1 = s_in[bb][tx + 16];
-            acc[0][0] = fmaf(d0, v0, acc[0][0]); acc[0][1] = fmaf(d0, v1, acc[0][1]);
-            acc[1][0] = fmaf(d1, v0, acc[1][0]); acc[1][1] = fmaf(d1, v1, acc[1][1]);
+#pragma unroll 4
+        for(int bb = warp; bb < GRADS_ROWS; bb += 8){
+            const float4 d = *reinterpret_cast<const float4*>(&s_d[bb][4 * rg]);
+            const float4 v0 = *reinterpret_cast<const float4*>(&s_in[bb][8 * cg]), v1 = *reinterpret_cast<const float4*>(&s_in[bb][8 * cg + 4]);
+            const float dv[4] = {d.x, d.y, d.z, d.w}, vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+            for(int p = 0; p < 4; p++)
+#pragma unroll
+                for(int q = 0; q < 8; q++) acc[p][q] = fmaf(dv[p], vv[q], acc[p][q]);
         }
-        __syncthreads();
+    }
+    __syncthreads();
+    float* R = s_all;                                     // [warp][32 outputs][32 columns]
+#pragma unroll
+    for(int p = 0; p < 4; p++){
+        float* row = R + (warp * 32 + 4 * rg + p) * 32 + 8 * cg;
+        *reinterpret_cast<float4*>(row) = make_float4(acc[p][0], acc[p][1], acc[p][2], acc[p][3]);
+        *reinterpret_cast<float4*>(row + 4) = make_float4(acc[p][4], acc[p][5], acc[p][6], acc[p][7]);
+    }
+    __syncthreads();
+    const int to = threadIdx.x >> 3, ti = (threadIdx.x & 7) * 4;          // thread: output o_base + to, columns i_base + ti .. + 3
+    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for(int w = 0; w < 8; w++){
+        const float4 t = *reinterpret_cast<const float4*>(R + (w * 32 + to) * 32 + ti);
+        sum[0] += t.x; sum[1] += t.y; sum[2] += t.z; sum[3] += t.w;
     }
     float* gW = grads + sh.poff[l];
     float* gb = gW + (long long)O * I;
     auto target = [&](int o, int i) -> float* { return i < I ? gW + (long long)o * I + i : gb + o; };
+    const int o = o_base + to;
     if(n_slices == 1){
 #pragma unroll
-        for(int p = 0; p < 2; p++)
-#pragma unroll
-            for(int q = 0; q < 2; q++){
-                const int o = o_base + ty + 16 * p, i = i_base + tx + 16 * q;
-                if(o < O && i <= I) *target(o, i) += acc[p][q];
-            }
+        for(int q = 0; q < 4; q++){
+            const int i = i_base + ti + q;
+            if(o < O && i <= I) *target(o, i) += sum[q];
+        }
         return;
     }
     // several slices: park the partial tile, the last CTA to arrive for this tile adds the slices in order
     float* mine = partial + ((long long)tile * n_slices + slice) * 1024;
 #pragma unroll
-    for(int p = 0; p < 2; p++)
-#pragma unroll
-        for(int q = 0; q < 2; q++) mine[(ty + 16 * p) * 32 + tx + 16 * q] = acc[p][q];
+    for(int q = 0; q < 4; q++) mine[to * 32 + ti + q] = sum[q];          // scalar: the caller's scratch need not be 16-byte aligned
     __threadfence();
     __syncthreads();
     if(threadIdx.x == 0) is_last = atomicAdd(&counters[tile], 1u) == (unsigned int)(n_slices - 1);
@@ -285,17 +318,16 @@ __global__ void __launch_bounds__(256) mlp_fused_grads_kernel(FusedShape sh, con
     if(!is_last) return;
     __threadfence();
     const float* all = partial + (long long)tile * n_slices * 1024;
+    float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for(int sl = 0; sl < n_slices; sl++){
 #pragma unroll
-    for(int p = 0; p < 2; p++)
+        for(int q = 0; q < 4; q++) t[q] += __ldcg(all + (long long)sl * 1024 + to * 32 + ti + q);
+    }
 #pragma unroll
-        for(int q = 0; q < 2; q++){
-            const int o = o_base + ty + 16 * p, i = i_base + tx + 16 * q;
-            if(o < O && i <= I){
-                float t = 0.0f;
-                for(int s = 0; s < n_slices; s++) t += __ldcg(all + (long long)s * 1024 + (ty + 16 * p) * 32 + tx + 16 * q);
-                *target(o, i) += t;
-            }
-        }
+    for(int q = 0; q < 4; q++){
+        const int i = i_base + ti + q;
+        if(o < O && i <= I) *target(o, i) += t[q];
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------------

@@ -44,6 +44,18 @@ __device__ __forceinline__ GaussianTerms gaussian_terms(float mean, float log_st
     return t;
 }
 
+// the same d_mean and d_log_std without the log-probability (no double-precision instruction)
+__device__ __forceinline__ GaussianTerms gaussian_derivatives(float mean, float log_std, float value){
+    const float diff = __fsub_rn(value, mean);
+    const float std = expf(log_std);
+    const float pre_square = __fdiv_rn(diff, std);
+    GaussianTerms t;
+    t.log_prob = 0.0f;
+    t.d_mean = __fdiv_rn(pre_square, std);
+    t.d_log_std = __fadd_rn(-1.0f, __fmul_rn(pre_square, pre_square));
+    return t;
+}
+
 // :173-184: mean and std of the minibatch advantages -> stats[0], stats[1]
 __global__ void __launch_bounds__(1024) ppo_adv_stats_kernel(const float* __restrict__ adv, long long ld, int B, float* stats){
     __shared__ float s_sum[32], s_sq[32];
@@ -75,7 +87,7 @@ constexpr int PPO_THREADS = 256, PPO_MAX_ACTION_DIM = 64;
 
 // :214-296, one thread per sample; per-block partial sums of the log_std gradient (warp shuffle + shared memory)
 __global__ void __launch_bounds__(PPO_THREADS) ppo_gradient_kernel(PpoArgs a){
-    __shared__ float s_part[PPO_THREADS / 32];
+    __shared__ float s_part[PPO_MAX_ACTION_DIM][PPO_THREADS / 32];
     const int b = blockIdx.x * PPO_THREADS + threadIdx.x;
     const bool valid = b < a.B;
     float d_loss_d_lp = 0.0f;
@@ -95,23 +107,26 @@ __global__ void __launch_bounds__(PPO_THREADS) ppo_gradient_kernel(PpoArgs a){
         const float d_surrogate_d_ratio = ratio_min_switch ? advantage : (clipped ? 0.0f : advantage);
         d_loss_d_lp = __fmul_rn(__fmul_rn(-1.0f / (float)a.B, d_surrogate_d_ratio), ratio);
     }
+    // second pass over the actions: only the float terms of the Gaussian (the double-precision log-probability is not needed again); the
+    // warps' sums of the log_std gradient meet in shared memory once, after the loop
     for(int i = 0; i < a.A; i++){
         float contrib = 0.0f;
         if(valid){
-            const GaussianTerms t = gaussian_terms(a.current_actions[b * a.ld_cur + i], a.log_std[i], a.rollout_actions[b * a.ld_roll + i]);
+            const GaussianTerms t = gaussian_derivatives(a.current_actions[b * a.ld_cur + i], a.log_std[i], a.rollout_actions[b * a.ld_roll + i]);
             a.d_actions[b * a.ld_d + i] = __fmul_rn(t.d_mean, d_loss_d_lp);
             contrib = __fmul_rn(d_loss_d_lp, t.d_log_std);
         }
         if(a.learn_action_std){
             for(int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
-            if((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = contrib;
-            __syncthreads();
-            if(threadIdx.x == 0){
-                float t = 0.0f;
-                for(int w = 0; w < PPO_THREADS / 32; w++) t += s_part[w];
-                a.partial[(long long)blockIdx.x * a.A + i] = t;
-            }
-            __syncthreads();
+            if((threadIdx.x & 31) == 0) s_part[i][threadIdx.x >> 5] = contrib;
+        }
+    }
+    if(a.learn_action_std){
+        __syncthreads();
+        for(int i = threadIdx.x; i < a.A; i += PPO_THREADS){
+            float t = 0.0f;
+            for(int w = 0; w < PPO_THREADS / 32; w++) t += s_part[i][w];
+            a.partial[(long long)blockIdx.x * a.A + i] = t;
         }
     }
 }

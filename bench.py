@@ -1133,7 +1133,8 @@ def main():
                 "roofline": roofline, "cpu_baseline": cpu, "cuda_reference": cuda_reference, "clocks": clocks.summary(),
                 "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
                         "copy_only_value": copy_only_value, "copy_only_note": "the same device-to-host bytes copied by all ranks at once and nothing else: the host link's ceiling for this call"},
-                "gpu_launches": 2 * args.steps, "wall_s_timed_region": wall,
+                "gpu_launches": 2 * args.steps,          # per timed step: pack_w1_pairs_kernel and rollout_tc_kernel (the constant-bank fills are copies)
+                "wall_s_timed_region": wall,
                 "secondary": {"mlp_train": mlp, "rollout_strong": strong}}
         print(json.dumps(line))
     if dist is not None:

@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
             for(int k = 0; k < O; k++) o2[k] = make_float2(o[k], o[k]);
 #pragma unroll
             for(int c = 0; c < 8; c++){                  // 16-byte chunk c of the row: units 8c .. 8c+7
-                uint32_t lead[4], rest[4];
+                uint32_t rest[4];
 #pragma unroll
                 for(int q = 0; q < 4; q++){
                     float h[2];
@@ -310,11 +310,9 @@ __global__ void __launch_bounds__(THREADS, 1) rollout_tc_kernel(RolloutArgs a, i
                         if constexpr(A1 == B200RL_ACT_RELU){ h[0] = acc.x; h[1] = acc.y; }       // the ReLU rides on the conversions below
                         else { h[0] = act_or_rt<A1>(acc.x, act1); h[1] = act_or_rt<A1>(acc.y, act1); }
                     }
-                    if constexpr(A1 == B200RL_ACT_RELU) split_f16_pair_relu(h[0], h[1], lead[q], rest[q]);
-                    else split_f16_pair(h[0], h[1], lead[q], rest[q]);
+                    if constexpr(A1 == B200RL_ACT_RELU) split_f16_pair_relu(h[0], h[1], lead_all[c * 4 + q], rest[q]);
+                    else split_f16_pair(h[0], h[1], lead_all[c * 4 + q], rest[q]);
                 }
-#pragma unroll
-                for(int q = 0; q < 4; q++) lead_all[c * 4 + q] = lead[q];
                 *reinterpret_cast<uint4*>(my_row_rest + (((uint32_t)c ^ swz) << 4)) = make_uint4(rest[0], rest[1], rest[2], rest[3]);
             }
             tc::tmem_st_32x32(tmem_a + lane_off, lead_all);

@@ -38,7 +38,16 @@ __device__ __forceinline__ GaussianTerms gaussian_terms(float mean, float log_st
     const float std = expf(log_std);
     const float pre_square = __fdiv_rn(diff, std);
     GaussianTerms t;
-    t.log_prob = (float)__dsub_rn((double)__fsub_rn(neg_log_sqrt_pi, log_std), __dmul_rn(__dmul_rn(0.5, (double)pre_square), (double)pre_square));
+    // (neg_log_sqrt_pi - log_std) - 0.5 * pre_square^2, which the reference takes in double and rounds to float: here the square is an exact
+    // float pair and the difference is rounded to float once (no double-precision instruction: they issue at 1/64 rate on this part and were
+    // most of this kernel's time), as in the rollout's Gaussian head
+    {
+        const float h = __fmul_rn(pre_square, pre_square), l = __fmaf_rn(pre_square, pre_square, -h);          // pre_square^2 = h + l exactly
+        const float a = __fsub_rn(neg_log_sqrt_pi, log_std), hh = __fmul_rn(0.5f, h);
+        const float d = __fsub_rn(a, hh), db = __fsub_rn(d, a);
+        const float de = __fsub_rn(__fsub_rn(a, __fsub_rn(d, db)), __fadd_rn(hh, db));                         // a - hh = d + de exactly
+        t.log_prob = __fadd_rn(d, __fmaf_rn(-0.5f, l, de));
+    }
     t.d_mean = __fdiv_rn(pre_square, std);
     t.d_log_std = __fadd_rn(-1.0f, __fmul_rn(pre_square, pre_square));
     return t;

@@ -436,6 +436,20 @@ int b200rl_l2f_rollout_device_rng(const b200rl_l2f_parameters* parameters, const
                                   float* states, int32_t* episode_step, uint8_t* truncated, float* episode_return, unsigned long long seed,
                                   unsigned long long first_step, int n_envs, int n_steps, int step_limit, float* obs, float* act, float* rew, uint8_t* terminated,
                                   b200rl_stream_t stream);
+/* The off-policy runner step on this environment in two halves around ANY policy, like b200rl_pendulum_offpolicy_prologue / _epilogue
+ * (rl/components/off_policy_runner/operations_cuda.h:184-204 around operations_generic_per_env.h:8-61 and :62-108). Prologue: environments
+ * whose truncated flag is set are reset -- from reset_states [n, 23] when given, else drawn in the kernel from `init` (12 floats, see
+ * b200rl_l2f_initial_states_from_draws) with the generator keyed by (seed, environment, call + *call_counter) -- and start a fresh episode;
+ * observations [n, 18]; was_truncated_scratch [n] remembers the flags for the epilogue. Epilogue: step with actions [n, 4], reward,
+ * terminated on the next state, counters (an episode ends at termination or at step_limit), next_observations [n, 18], and the transition
+ * appended to the environment's replay buffer (row = observation 18 | action 4 | reward | next observation 18 | terminated | truncated:
+ * layout->ld_data >= 43; rl/components/replay_buffer/operations_generic.h:54-79). */
+int b200rl_l2f_offpolicy_prologue(const b200rl_l2f_parameters* parameters, const float* init, float* states, int32_t* episode_step, const uint8_t* truncated,
+                                  float* episode_return, const float* reset_states, unsigned long long seed, unsigned long long call,
+                                  const unsigned long long* call_counter, int n_envs, float* observations, uint8_t* was_truncated_scratch, b200rl_stream_t stream);
+int b200rl_l2f_offpolicy_epilogue(const b200rl_l2f_parameters* parameters, const float* mdp, float* states, int32_t* episode_step, uint8_t* truncated,
+                                  float* episode_return, int n_envs, int step_limit, const float* actions, float* next_observations, void* replay_buffers,
+                                  const b200rl_replay_layout* layout, const uint8_t* was_truncated_scratch, b200rl_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Replay-buffer sampling: gather_batch(device, runner, batch, rng) for SequentialBatch with SEQUENCE_LENGTH 1 and its default sampling

@@ -29,13 +29,16 @@ class ReplayLayout(C.Structure):
                 ("off_full", C.c_size_t), ("off_current_episode_start", C.c_size_t), ("capacity", C.c_int), ("ld_data", C.c_int), ("index_bytes", C.c_int)]
 
     @staticmethod
-    def packed(capacity):
-        """data [capacity, 10] f32 | episode_start [capacity] u32 | position u32 | current_episode_start u32 | full u8 (+3 pad)."""
+    def packed(capacity, obs_dim=3, action_dim=1):
+        """data [capacity, 2 obs + action + 3] f32 | episode_start [capacity] u32 | position u32 | current_episode_start u32 | full u8 (+3 pad);
+        the Pendulum's row of 10 floats by default."""
         L = ReplayLayout()
-        L.capacity, L.ld_data, L.index_bytes = capacity, 10, 4
-        L.off_data, L.off_episode_start = 0, 40 * capacity
-        L.off_position, L.off_current_episode_start, L.off_full = 44 * capacity, 44 * capacity + 4, 44 * capacity + 8
-        L.env_stride = 44 * capacity + 12
+        ld = 2 * obs_dim + action_dim + 3
+        L.capacity, L.ld_data, L.index_bytes = capacity, ld, 4
+        L.off_data, L.off_episode_start = 0, 4 * ld * capacity
+        base = 4 * (ld + 1) * capacity
+        L.off_position, L.off_current_episode_start, L.off_full = base, base + 4, base + 8
+        L.env_stride = base + 12
         return L
 
 
@@ -198,6 +201,8 @@ def lib():
         L.b200rl_l2f_rollout_device_rng.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 18), C.POINTER(C.c_float * 12), shape_p, vp, vp, vp, vp, vp,
                                                     C.c_ulonglong, C.c_ulonglong, i, i, i, vp, vp, vp, vp, vp]
         L.b200rl_l2f_initial_states_from_draws.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 12), vp, vp, vp, i, vp]
+        L.b200rl_l2f_offpolicy_prologue.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 12), vp, vp, vp, vp, vp, C.c_ulonglong, C.c_ulonglong, vp, i, vp, vp, vp]
+        L.b200rl_l2f_offpolicy_epilogue.argtypes = [C.POINTER(L2fParameters), C.POINTER(C.c_float * 18), vp, vp, vp, vp, i, i, vp, vp, vp, C.POINTER(ReplayLayout), vp, vp]
         L.b200rl_l2f_steps.argtypes = [C.POINTER(L2fParameters), vp, vp, i, i, vp]
         L.b200rl_gather_batch_sequences.argtypes = [vp, C.POINTER(ReplayLayout), i, i, i, i, i, i, f, u64, u64, vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp]
         L.b200rl_pendulum_offpolicy_prologue.argtypes = [vp, vp, vp, vp, vp, u64, u64, vp, i, vp, vp, vp]
@@ -725,6 +730,22 @@ def l2f_rollout_device_rng(parameters, mdp, init, shape, params, states, episode
                                               _ptr(episode_return), seed, first_step, N, n_steps, step_limit, _ptr(obs), _ptr(act), _ptr(rew), _ptr(terminated), _stream()),
           "b200rl_l2f_rollout_device_rng")
     return obs, act, rew, terminated
+
+
+def l2f_offpolicy_prologue(parameters, states, episode_step, truncated, episode_return, observations, was_truncated, reset_states=None, init=None, seed=0, call_index=0,
+                           call_counter=None):
+    """First half of the off-policy runner step on the L2F quadrotor: reset-if-truncated (reset_states [n, 23], or drawn in the kernel from the
+    12 floats of `init`), observations [n, 18]."""
+    init_c = None if init is None else (C.c_float * 12)(*[float(v) for v in init])
+    check(lib().b200rl_l2f_offpolicy_prologue(C.byref(parameters), init_c, _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return), _ptr(reset_states), seed,
+                                              call_index, _ptr(call_counter), states.shape[0], _ptr(observations), _ptr(was_truncated), _stream()), "b200rl_l2f_offpolicy_prologue")
+
+
+def l2f_offpolicy_epilogue(parameters, mdp, states, episode_step, truncated, episode_return, step_limit, actions, next_observations, replay, layout, was_truncated):
+    """Second half: step with actions [n, 4], reward, termination, counters, next_observations [n, 18], replay-buffer append (rows of 43 floats)."""
+    mdp_c = (C.c_float * 18)(*[float(v) for v in mdp])
+    check(lib().b200rl_l2f_offpolicy_epilogue(C.byref(parameters), mdp_c, _ptr(states), _ptr(episode_step), _ptr(truncated), _ptr(episode_return), states.shape[0], step_limit,
+                                              _ptr(actions), _ptr(next_observations), _ptr(replay), C.byref(layout), _ptr(was_truncated), _stream()), "b200rl_l2f_offpolicy_epilogue")
 
 
 def l2f_initial_states_from_draws(parameters, init, uniforms, normals):

@@ -490,6 +490,101 @@ static int launch_l2f_rollout(const L2fRolloutArgs& a, cudaStream_t s){
     return B200RL_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The off-policy runner step on this environment in two halves around ANY policy, like the Pendulum's (the reference's CUDA runner:
+// prologue kernel, evaluate(policy), epilogue kernel; rl/components/off_policy_runner/operations_cuda.h:184-204 around
+// operations_generic_per_env.h:8-61 and :62-108), with the replay-buffer append of rl/components/replay_buffer/operations_generic.h:54-79:
+// row = observation 18 | action 4 | reward | next observation 18 | terminated | truncated.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename INDEX>
+__device__ __forceinline__ void l2f_replay_append(int e, const float (&obs)[18], const float (&action)[4], float reward, const float (&next_obs)[18], bool term, bool trunc,
+                                                  bool was_truncated, unsigned char* replay, const b200rl_replay_layout& L){
+    constexpr int O = 18, A = 4, COL_REWARD = O + A, COL_NEXT = O + A + 1, COL_TERMINATED = 2 * O + A + 1, COL_TRUNCATED = 2 * O + A + 2;
+    unsigned char* rb = replay + (size_t)e * L.env_stride;
+    float* data = reinterpret_cast<float*>(rb + L.off_data);
+    INDEX* episode_start = reinterpret_cast<INDEX*>(rb + L.off_episode_start);
+    INDEX& position_ref = *reinterpret_cast<INDEX*>(rb + L.off_position);
+    INDEX& ces_ref = *reinterpret_cast<INDEX*>(rb + L.off_current_episode_start);
+    unsigned char& full_ref = *(rb + L.off_full);
+    INDEX position = position_ref, ces = ces_ref;
+    bool full = full_ref != 0;
+    if(was_truncated && (full || position > 0)){               // the environment was reset at the start of this step (operations_generic_per_env.h:41-52)
+        const INDEX prev = position == 0 ? (INDEX)(L.capacity - 1) : position - 1;
+        data[(size_t)prev * L.ld_data + COL_TRUNCATED] = 1.0f;
+        ces = position;
+    }
+    float* row = data + (size_t)position * L.ld_data;
+#pragma unroll
+    for(int k = 0; k < O; k++){ row[k] = obs[k]; row[COL_NEXT + k] = next_obs[k]; }
+#pragma unroll
+    for(int k = 0; k < A; k++) row[O + k] = action[k];
+    row[COL_REWARD] = reward; row[COL_TERMINATED] = term ? 1.0f : 0.0f; row[COL_TRUNCATED] = trunc ? 1.0f : 0.0f;
+    episode_start[position] = ces;
+    position = (position + 1) % (INDEX)L.capacity;
+    if(trunc) ces = position;
+    if(position == 0 && !full) full = true;
+    position_ref = position; ces_ref = ces; full_ref = full ? 1 : 0;
+}
+
+// prologue: reset-if-truncated (from reset_states [n, 23], or drawn in the kernel from `init`), counters of a fresh episode, observation
+__global__ void __launch_bounds__(128) l2f_offpolicy_prologue_kernel(L2fRolloutArgs a, const unsigned long long* __restrict__ call_counter, float* __restrict__ observations,
+                                                                     uint8_t* __restrict__ was_truncated){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= a.n_envs) return;
+    L2fState s;
+    float* sf = reinterpret_cast<float*>(&s);
+#pragma unroll
+    for(int k = 0; k < 23; k++) sf[k] = a.states[(size_t)e * 23 + k];
+    const bool trunc = a.truncated[e] != 0;
+    was_truncated[e] = trunc ? 1 : 0;
+    if(trunc){
+        if(a.reset_states){
+#pragma unroll
+            for(int k = 0; k < 23; k++) sf[k] = __ldg(a.reset_states + (size_t)e * 23 + k);
+        }
+        else{
+            float uu[17], nn[6];
+            l2f_reset_draws(a.rng_seed, a.rng_step0 + (call_counter ? *call_counter : 0ull), (uint32_t)e, a.init[9] != 0.0f || a.init[11] != 0.0f, uu, nn);
+            l2f_initial_state(a.init, a.env.p.action_min, a.env.p.action_max, uu, nn, s);
+        }
+#pragma unroll
+        for(int k = 0; k < 23; k++) a.states[(size_t)e * 23 + k] = sf[k];
+        a.episode_step[e] = 0; a.episode_return[e] = 0.0f;
+    }
+    float o[18];
+    l2f_observe(s, o);
+#pragma unroll
+    for(int k = 0; k < 18; k++) observations[(size_t)e * 18 + k] = o[k];
+}
+// epilogue: step with the given actions, reward, termination, counters, next observation, replay-buffer append
+template <typename INDEX>
+__global__ void __launch_bounds__(128) l2f_offpolicy_epilogue_kernel(L2fRolloutArgs a, const float* __restrict__ actions, float* __restrict__ next_observations,
+                                                                     const uint8_t* __restrict__ was_truncated, unsigned char* replay, b200rl_replay_layout L){
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if(e >= a.n_envs) return;
+    L2fState s, next;
+    float* sf = reinterpret_cast<float*>(&s);
+#pragma unroll
+    for(int k = 0; k < 23; k++) sf[k] = a.states[(size_t)e * 23 + k];
+    float action[4], o[18], no[18];
+#pragma unroll
+    for(int k = 0; k < 4; k++) action[k] = actions[(size_t)e * 4 + k];
+    l2f_observe(s, o);
+    l2f_step(a.env, s, action, next);
+    const bool term = l2f_terminated(a.mdp, next);
+    const float r = l2f_reward(a.env, a.mdp, s, action, next, term);
+    const int es = a.episode_step[e] + 1;
+    const bool trunc = term || es == a.step_limit;             // operations_generic_per_env.h:93-97
+    l2f_observe(next, no);
+    const float* nf = reinterpret_cast<const float*>(&next);
+#pragma unroll
+    for(int k = 0; k < 23; k++) a.states[(size_t)e * 23 + k] = nf[k];
+#pragma unroll
+    for(int k = 0; k < 18; k++) next_observations[(size_t)e * 18 + k] = no[k];
+    a.episode_step[e] = es; a.episode_return[e] = __fadd_rn(a.episode_return[e], r); a.truncated[e] = trunc ? 1 : 0;
+    l2f_replay_append<INDEX>(e, o, action, r, no, term, trunc, was_truncated[e] != 0, replay, L);
+}
+
 }  // namespace b200rl
 using namespace b200rl;
 
@@ -561,5 +656,49 @@ extern "C" int b200rl_l2f_initial_states_from_draws(const b200rl_l2f_parameters*
     memcpy(a.init, init, sizeof(a.init));
     l2f_initial_states_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(a, uniforms, normals, states, n);
     B200RL_LAUNCH_CHECK("l2f_initial_states");
+    return B200RL_OK;
+}
+
+static void l2f_fill_args(L2fRolloutArgs& a, const b200rl_l2f_parameters* parameters){
+    memcpy(&a.env.p, parameters->dynamics, sizeof(L2fDynamics));
+    a.env.dt = parameters->dt; a.env.limit_position = parameters->state_limit_position; a.env.limit_velocity = parameters->state_limit_velocity;
+    a.env.limit_angular_velocity = parameters->state_limit_angular_velocity;
+}
+
+extern "C" int b200rl_l2f_offpolicy_prologue(const b200rl_l2f_parameters* parameters, const float* init, float* states, int32_t* episode_step, const uint8_t* truncated,
+                                             float* episode_return, const float* reset_states, unsigned long long seed, unsigned long long call,
+                                             const unsigned long long* call_counter, int n_envs, float* observations, uint8_t* was_truncated_scratch, b200rl_stream_t stream){
+    if(!parameters || (!init && !reset_states) || !states || !episode_step || !truncated || !episode_return || !observations || !was_truncated_scratch || n_envs < 0)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0) return B200RL_OK;
+    L2fRolloutArgs a{};
+    l2f_fill_args(a, parameters);
+    if(init) memcpy(a.init, init, sizeof(a.init));
+    a.states = states; a.episode_step = episode_step; a.truncated = const_cast<uint8_t*>(truncated); a.episode_return = episode_return; a.reset_states = reset_states;
+    a.n_envs = n_envs; a.rng_seed = seed; a.rng_step0 = call;
+    l2f_offpolicy_prologue_kernel<<<(n_envs + 127) / 128, 128, 0, (cudaStream_t)stream>>>(a, call_counter, observations, was_truncated_scratch);
+    B200RL_LAUNCH_CHECK("l2f_offpolicy_prologue");
+    return B200RL_OK;
+}
+
+extern "C" int b200rl_l2f_offpolicy_epilogue(const b200rl_l2f_parameters* parameters, const float* mdp, float* states, int32_t* episode_step, uint8_t* truncated,
+                                             float* episode_return, int n_envs, int step_limit, const float* actions, float* next_observations, void* replay_buffers,
+                                             const b200rl_replay_layout* layout, const uint8_t* was_truncated_scratch, b200rl_stream_t stream){
+    if(!parameters || !mdp || !states || !episode_step || !truncated || !episode_return || !actions || !next_observations || !replay_buffers || !layout ||
+       !was_truncated_scratch || n_envs < 0 || step_limit < 1)
+        return B200RL_ERR_INVALID_ARGUMENT;
+    if(layout->capacity < 1 || layout->ld_data < 2 * 18 + 4 + 3 || (layout->index_bytes != 4 && layout->index_bytes != 8)) return B200RL_ERR_INVALID_ARGUMENT;
+    if(n_envs == 0) return B200RL_OK;
+    L2fRolloutArgs a{};
+    l2f_fill_args(a, parameters);
+    memcpy(a.mdp, mdp, sizeof(a.mdp));
+    a.states = states; a.episode_step = episode_step; a.truncated = truncated; a.episode_return = episode_return; a.n_envs = n_envs; a.step_limit = step_limit;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int blocks = (n_envs + 127) / 128;
+    if(layout->index_bytes == 4)
+        l2f_offpolicy_epilogue_kernel<uint32_t><<<blocks, 128, 0, s>>>(a, actions, next_observations, was_truncated_scratch, static_cast<unsigned char*>(replay_buffers), *layout);
+    else
+        l2f_offpolicy_epilogue_kernel<unsigned long long><<<blocks, 128, 0, s>>>(a, actions, next_observations, was_truncated_scratch, static_cast<unsigned char*>(replay_buffers), *layout);
+    B200RL_LAUNCH_CHECK("l2f_offpolicy_epilogue");
     return B200RL_OK;
 }

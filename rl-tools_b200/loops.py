@@ -82,18 +82,21 @@ class PendulumSacLoop:
     (reset states, exploration noise, batch indices, update noise) comes from the counter-based generator keyed by a device-resident step counter
     that the graph's last node advances, so nothing returns to the host between steps."""
 
+    OBS_DIM, ACTION_DIM, STATE_DIM = 3, 1, 2
+
     def __init__(self, n_envs=1, batch_size=100, hidden_dim=64, step_limit=10000, n_warmup_steps=100, episode_step_limit=200, replay_capacity=None, seed=0,
                  use_graph=True, device="cuda"):
         import torch
         from . import sac, ReplayLayout, new_batch
+        O, A, S = self.OBS_DIM, self.ACTION_DIM, self.STATE_DIM
         assert n_warmup_steps * n_envs >= batch_size, "config.h:25"
         self.n_envs, self.batch_size, self.step_limit, self.n_warmup_steps, self.episode_step_limit = n_envs, batch_size, step_limit, n_warmup_steps, episode_step_limit
         self.seed, self.step_index, self.use_graph, self.device = seed, 0, use_graph, device
-        self.agent = sac.ActorCritic(3, 1, hidden_dim, batch_size, device=device)
+        self.agent = sac.ActorCritic(O, A, hidden_dim, batch_size, device=device)
         self.hidden_dim = hidden_dim
         # init(device, actor_critic, rng) (rl/algorithms/sac/operations_generic.h:112-131): init_weights of the actor and the two critics on one engine
         self.rng = rng_init_host(seed)
-        for net, fan_in0, out in ((self.agent.actor, 3, 2), (self.agent.critics[0], 4, 1), (self.agent.critics[1], 4, 1)):
+        for net, fan_in0, out in ((self.agent.actor, O, 2 * A), (self.agent.critics[0], O + A, 1), (self.agent.critics[1], O + A, 1)):
             off, fan_in = 0, fan_in0
             for d in (hidden_dim, hidden_dim, out):
                 dense_init_weights(self.rng, net.params[off:off + d * fan_in].view(d, fan_in), net.params[off + d * fan_in:off + d * fan_in + d])
@@ -103,14 +106,14 @@ class PendulumSacLoop:
         z = lambda *s, dtype=torch.float32: torch.zeros(*s, device=device, dtype=dtype)
         # init(device, off_policy_runner): every environment starts truncated (reset by the first step), empty replay buffers
         N = n_envs
-        self.layout = ReplayLayout.packed(step_limit if replay_capacity is None else replay_capacity)
+        self.layout = ReplayLayout.packed(step_limit if replay_capacity is None else replay_capacity, O, A)
         self.replay = z(N * self.layout.env_stride, dtype=torch.uint8)
-        self.states, self.episode_step, self.episode_return = z(N, 2), z(N, dtype=torch.int32), z(N)
+        self.states, self.episode_step, self.episode_return = z(N, S), z(N, dtype=torch.int32), z(N)
         self.truncated, self.was_truncated = torch.ones(N, device=device, dtype=torch.uint8), z(N, dtype=torch.uint8)
-        self.observations, self.actions, self.next_observations = z(N, 3), z(N, 1), z(N, 3)
-        self.head_input, self.explore_noise = z(N, 2), z(N, 1)
-        self.explore_pre, self.explore_log_prob = z(N, 1), z(N)
-        self.batch, self.update_noise = new_batch(batch_size, device=device), z(3, batch_size, 1)
+        self.observations, self.actions, self.next_observations = z(N, O), z(N, A), z(N, O)
+        self.head_input, self.explore_noise = z(N, 2 * A), z(N, A)
+        self.explore_pre, self.explore_log_prob = z(N, A), z(N)
+        self.batch, self.update_noise = new_batch(batch_size, O, A, device=device), z(3, batch_size, A)
         self.counter = z(1, dtype=torch.int64)                      # the loop's step index on the device
         self.error_flag = z(1, dtype=torch.int32)
         self.graph = None
@@ -145,7 +148,7 @@ class PendulumSacLoop:
         sample_and_squash_forward(self.head_input, self.explore_noise, output=self.actions, pre_squashing=self.explore_pre, log_probs=self.explore_log_prob)
         self._epilogue()
         gather_batch(self.replay, self.layout, self.n_envs, self.batch, seed=self.seed, call_counter=self.counter, max_episode_length=self.episode_step_limit,
-                     error_flag=self.error_flag)
+                     obs_dim=self.OBS_DIM, action_dim=self.ACTION_DIM, error_flag=self.error_flag)
         randn_device_rng(self.update_noise, self.seed, stream_id=1, call_counter=self.counter)
         a.update(self.batch, self.update_noise[0], self.update_noise[1], self.update_noise[2])
         counter_advance(self.counter, 1)
@@ -194,3 +197,54 @@ class PendulumSacLoop:
         tr = torch.ones(n_episodes, device=self.device, dtype=torch.uint8)
         _, _, rew = pendulum_rollout_device_rng(shape, arena, st, es, tr, er, seed, 0, self.episode_step_limit, self.episode_step_limit)
         return float(rew.view(self.episode_step_limit, n_episodes).sum(0).mean().item())
+
+
+class L2fSacLoop(PendulumSacLoop):
+    """The same loop on the L2F quadrotor (rl::environments::Multirotor in the configuration of the reference's GPU harness: 18 observations,
+    4 rotor commands, episodes of at most 500 steps that end early when the quadrotor leaves the termination bounds): the runner's halves are
+    b200rl_l2f_offpolicy_prologue / _epilogue with every reset drawn in the kernel from the environment's own initial-state distribution;
+    actor 18 -> H -> H -> 8 with the sample-and-squash head, critics 22 -> H -> H -> 1. `parameters` is an L2fParameters, `mdp` the 18 floats of
+    the reward function and termination thresholds, `init` the 12 floats of the initial-state distribution (all read out of the reference's
+    structs when the fixtures are written)."""
+    OBS_DIM, ACTION_DIM, STATE_DIM = 18, 4, 23
+
+    def __init__(self, parameters, mdp, init, n_envs=16, batch_size=256, hidden_dim=64, step_limit=100000, n_warmup_steps=None, episode_step_limit=500,
+                 replay_capacity=None, seed=0, use_graph=True, device="cuda"):
+        self.parameters, self.mdp, self.init = parameters, [float(v) for v in mdp], [float(v) for v in init]
+        warm = n_warmup_steps if n_warmup_steps is not None else max(100, -(-batch_size // n_envs))
+        super().__init__(n_envs=n_envs, batch_size=batch_size, hidden_dim=hidden_dim, step_limit=step_limit, n_warmup_steps=warm, episode_step_limit=episode_step_limit,
+                         replay_capacity=replay_capacity, seed=seed, use_graph=use_graph, device=device)
+
+    def _prologue(self):
+        from . import l2f_offpolicy_prologue
+        l2f_offpolicy_prologue(self.parameters, self.states, self.episode_step, self.truncated, self.episode_return, self.observations, self.was_truncated,
+                               init=self.init, seed=self.seed, call_counter=self.counter)
+
+    def _epilogue(self):
+        from . import l2f_offpolicy_epilogue
+        l2f_offpolicy_epilogue(self.parameters, self.mdp, self.states, self.episode_step, self.truncated, self.episode_return, self.episode_step_limit, self.actions,
+                               self.next_observations, self.replay, self.layout, self.was_truncated)
+
+    def evaluation_actor(self):
+        """The deterministic evaluation policy, action = tanh(mean): the four mean rows of the actor's output layer as an 18 -> H -> H -> 4 actor."""
+        import torch
+        H, O, A = self.hidden_dim, self.OBS_DIM, self.ACTION_DIM
+        p = self.agent.actor.params
+        body = H * O + H + H * H + H
+        arena = torch.cat([p[:body], p[body:body + A * H], p[body + 2 * A * H:body + 2 * A * H + A]])
+        return MlpShape.make(O, [H, H, A], ["relu", "relu", "tanh"]), arena
+
+    def evaluate(self, n_episodes=256, seed=12345):
+        """(mean return, mean length) of n_episodes evaluation episodes: one fused rollout launch, each environment's first episode."""
+        import torch
+        from . import l2f_rollout_device_rng
+        shape, arena = self.evaluation_actor()
+        T = self.episode_step_limit
+        z = lambda *s, dtype=torch.float32: torch.zeros(*s, device=self.device, dtype=dtype)
+        st, es, er = z(n_episodes, 23), z(n_episodes, dtype=torch.int32), z(n_episodes)
+        tr = torch.ones(n_episodes, device=self.device, dtype=torch.uint8)
+        _, _, rew, term = l2f_rollout_device_rng(self.parameters, self.mdp, self.init, shape, arena, st, es, tr, er, seed, 0, T, T)
+        rew, term = rew.view(T, n_episodes), term.view(T, n_episodes)
+        alive = (term.cumsum(0) - term) == 0                          # steps up to and including the first termination
+        return float((rew * alive).sum(0).mean().item()), float(alive.sum(0).float().mean().item())
+

@@ -138,6 +138,12 @@ def test_argument_validation_of_the_later_entry_points(lib):
     assert L.b200rl_l2f_initial_states_from_draws(C.byref(p), None, None, None, None, 4, None) == 1
     assert L.b200rl_l2f_initial_states_from_draws(C.byref(p), init, None, None, None, 4, None) == 1
     assert L.b200rl_l2f_initial_states_from_draws(C.byref(p), init, None, None, None, 0, None) == 0
+    lay43, lay10 = lib.ReplayLayout.packed(8, 18, 4), lib.ReplayLayout.packed(8)
+    assert (lay43.ld_data, lay10.ld_data, lay10.env_stride) == (43, 10, 44 * 8 + 12)
+    assert L.b200rl_l2f_offpolicy_prologue(C.byref(p), None, None, None, None, None, None, 0, 0, None, 4, None, None, None) == 1
+    assert L.b200rl_l2f_offpolicy_prologue(C.byref(p), init, None, None, None, None, None, 0, 0, None, 4, None, None, None) == 1
+    assert L.b200rl_l2f_offpolicy_epilogue(C.byref(p), None, None, None, None, None, 4, 10, None, None, None, C.byref(lay43), None, None) == 1
+    assert L.b200rl_l2f_offpolicy_epilogue(C.byref(p), mdp, None, None, None, None, 4, 10, None, None, None, C.byref(lay43), None, None) == 1
     L.b200rl_cooperative_pass_status.argtypes = [C.POINTER(C.c_int)]
     assert L.b200rl_cooperative_pass_status(None) == 1
     # host-side draws of gather_batch: an empty replay buffer is refused, like the reference's assertion

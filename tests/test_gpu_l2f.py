@@ -201,3 +201,63 @@ def test_l2f_rollout_with_device_side_resets(lib, torch, fix):
     shifted, _ = run(77, limit, 1)
     assert np.array_equal(shifted[0][whole], obs[limit][whole])
 
+
+def test_l2f_offpolicy_step_halves_with_replay_buffers(lib, orc, torch, fix):
+    """The off-policy runner step on the quadrotor in two halves around given actions, 40 steps of 200 environments with an episode limit of
+    7, replay buffers of 16 rows (they wrap) and some initial states pushed beyond the termination threshold: per step the observations
+    and next observations bit for bit against the oracle's functions under the runner's bookkeeping (restated here in numpy); at the end
+    every replay row (reward column within the GPU's acosf), episode starts, positions, full flags and the runner counters."""
+    N, T, limit, cap = 200, 40, 7, 16
+    rs = np.random.RandomState(3)
+    dyn, dt, mdp = fix["dynamics"], float(fix["dt"]), fix["mdp"]
+    pool = fix["initial_states"].reshape(-1, 23).copy()
+    pool[::5, :3] *= np.float32(4.0)                                   # a fifth of the resets start far out: many of them beyond the position threshold of 1 after one step
+    p = lib.L2fParameters.make(dyn, dt)
+    layout = lib.ReplayLayout.packed(cap, 18, 4)
+    assert layout.ld_data == 43
+    replay = torch.zeros(N * layout.env_stride, dtype=torch.uint8, device="cuda")
+    st, es, er = torch.zeros((N, 23), device="cuda"), torch.zeros(N, dtype=torch.int32, device="cuda"), torch.zeros(N, device="cuda")
+    tr, was = torch.ones(N, dtype=torch.uint8, device="cuda"), torch.zeros(N, dtype=torch.uint8, device="cuda")
+    obs_d, nobs_d = torch.zeros((N, 18), device="cuda"), torch.zeros((N, 18), device="cuda")
+    # the runner's bookkeeping in numpy
+    h_st, h_es, h_er, h_tr = np.zeros((N, 23), np.float32), np.zeros(N, np.int32), np.zeros(N, np.float32), np.ones(N, bool)
+    data, ep_start = np.zeros((N, cap, 43), np.float32), np.zeros((N, cap), np.uint32)
+    pos, ces, full = np.zeros(N, np.int64), np.zeros(N, np.int64), np.zeros(N, bool)
+    terminations = 0
+    for t in range(T):
+        table = pool[(t * N + np.arange(N)) % pool.shape[0]]
+        actions = rs.uniform(-1, 1, (N, 4)).astype(np.float32)
+        lib.l2f_offpolicy_prologue(p, st, es, tr, er, obs_d, was, reset_states=torch.from_numpy(table).cuda())
+        lib.l2f_offpolicy_epilogue(p, mdp, st, es, tr, er, limit, torch.from_numpy(actions).cuda(), nobs_d, replay, layout, was)
+        h_was = h_tr.copy()
+        h_st[h_tr] = table[h_tr]; h_es[h_tr] = 0; h_er[h_tr] = 0
+        nxt = orc.l2f_steps(dyn, dt, h_st, actions, 1)
+        obs, rew, term = orc.l2f_functions(dyn, dt, mdp, h_st, actions, nxt)
+        nobs = orc.l2f_functions(dyn, dt, mdp, nxt, actions, nxt)[0]
+        h_es += 1; h_er += rew
+        term = term.astype(bool); trunc = term | (h_es == limit)
+        terminations += int(term.sum())
+        for e in range(N):
+            if h_was[e] and (full[e] or pos[e] > 0):
+                data[e, (pos[e] - 1) % cap, 42] = 1.0
+                ces[e] = pos[e]
+            data[e, pos[e]] = np.concatenate([obs[e], actions[e], [rew[e]], nobs[e], [float(term[e])], [float(trunc[e])]])
+            ep_start[e, pos[e]] = ces[e]
+            pos[e] = (pos[e] + 1) % cap
+            if trunc[e]: ces[e] = pos[e]
+            if pos[e] == 0 and not full[e]: full[e] = True
+        h_st, h_tr = nxt, trunc
+        assert np.array_equal(obs_d.cpu().numpy(), obs) and np.array_equal(nobs_d.cpu().numpy(), nobs), t
+        assert np.array_equal(tr.cpu().numpy().astype(bool), trunc) and np.array_equal(es.cpu().numpy(), h_es), t
+    assert terminations > 50 and full.all()
+    raw = replay.cpu().numpy().reshape(N, layout.env_stride)
+    g_data = raw[:, layout.off_data:layout.off_data + 4 * 43 * cap].copy().view(np.float32).reshape(N, cap, 43)
+    g_start = raw[:, layout.off_episode_start:layout.off_episode_start + 4 * cap].copy().view(np.uint32).reshape(N, cap)
+    g_pos = raw[:, layout.off_position:layout.off_position + 4].copy().view(np.uint32).reshape(N)
+    g_ces = raw[:, layout.off_current_episode_start:layout.off_current_episode_start + 4].copy().view(np.uint32).reshape(N)
+    exact = [c for c in range(43) if c != 22]
+    assert np.array_equal(g_data[:, :, exact], data[:, :, exact])
+    assert np.abs(g_data[:, :, 22] - data[:, :, 22]).max() <= 1e-5
+    assert np.array_equal(g_start, ep_start) and np.array_equal(g_pos, pos) and np.array_equal(g_ces, ces) and np.all(raw[:, layout.off_full] == 1)
+    assert np.array_equal(st.cpu().numpy(), h_st) and np.abs(er.cpu().numpy() - h_er).max() <= 1e-4
+

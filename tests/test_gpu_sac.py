@@ -315,3 +315,37 @@ def test_sac_loop_learns_the_pendulum(lib, torch):
     assert before < -900 and after > -400, (before, after)
     for net in [loop.agent.actor] + loop.agent.critics + loop.agent.critics_target:
         assert bool(torch.isfinite(net.params).all())
+
+
+def test_sac_loop_on_the_quadrotor(lib, torch):
+    """The same loop on the L2F quadrotor (16 environments, resets drawn in the kernel, 64-wide networks, batch 256): warm-up with uniformly
+    random actions, then captured training steps. Checked: the loop's counters, the replay buffers fill with rows of 43 floats whose
+    observations carry proper rotation matrices, every parameter stays finite, and 6,000 steps move the deterministic evaluation policy
+    (256 evaluation episodes) from leaving the termination bounds after ~30 steps to staying inside them several times longer, at a better
+    reward per step (measured: episode length 29 -> 88, return per step -3.4 -> -1.4)."""
+    import os
+    import numpy as np
+    from rl_tools_b200.loops import L2fSacLoop
+    fix = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "l2f.npz"))
+    torch.manual_seed(0)
+    p = lib.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    loop = L2fSacLoop(p, fix["mdp"], fix["init"], n_envs=16, batch_size=256, step_limit=6000, n_warmup_steps=200, replay_capacity=8192, seed=3)
+    ret0, len0 = loop.evaluate()
+    while not loop.step():
+        pass
+    torch.cuda.synchronize()
+    assert int(loop.error_flag.item()) == 0 and int(loop.counter.item()) == 6000
+    ret1, len1 = loop.evaluate()
+    print(f"SAC L2F: evaluation return {ret0:.1f} -> {ret1:.1f}, episode length {len0:.0f} -> {len1:.0f}, alpha {float(loop.agent.log_alpha.exp().item()):.3f}")
+    for net in [loop.agent.actor] + loop.agent.critics + loop.agent.critics_target:
+        assert bool(torch.isfinite(net.params).all())
+    position, full = lib.replay_counters(loop.replay, loop.layout, 16)
+    assert bool((position == 6000).all()) and not bool(full.any())
+    L = loop.layout
+    raw = loop.replay.cpu().numpy().reshape(16, L.env_stride)
+    rows = raw[:, L.off_data:L.off_data + 4 * 43 * 6000].copy().view(np.float32).reshape(16, 6000, 43)
+    R = rows[:, :, 3:12].reshape(-1, 3, 3).astype(np.float64)
+    assert np.abs(R @ R.transpose(0, 2, 1) - np.eye(3)).max() < 1e-4 and np.abs(rows[:, :, 18:22]).max() <= 1.0
+    assert np.isfinite(rows).all() and (rows[:, :, 41].sum() > 0)            # terminations occurred and were recorded
+    assert len1 > 1.5 * len0 and ret1 / len1 > ret0 / len0, (ret0, ret1, len0, len1)        # it stays inside the bounds longer, at a better reward per step
+

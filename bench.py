@@ -16,7 +16,7 @@ the 64 -> 256 -> 256 -> 256 -> 16 MLP on 2^24 rows split over the ranks with ONE
 step (strong scaling, the all-reduce timed on its own), and `rollout_strong` = the same 65,536 environments split over the
 ranks. `--impl reference` times only the reference CPU implementation, on the same metric and config.
 
-`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout, l2f_step, l2f_rollout}` print secondary lines in the same JSON form (sharded MLP training,
+`--workload {mlp_train, collect, ppo_update, critic_train, actor_eval, sac_update, acrobot_rollout, l2f_step, l2f_rollout, l2f_sac_loop}` print secondary lines in the same JSON form (sharded MLP training,
 on-policy collect, the PPO update on the Ant shapes, batch-256 critic regression steps, batch-256 actor inference, the SAC training step, the generic rollout on AcrobotSwingup); the default workload is the headline rollout.
 """
 import argparse
@@ -869,6 +869,43 @@ def run_l2f_rollout(args):
                       "cpu_baseline": cpu, "gpu_launches": steps}))
 
 
+def run_l2f_sac_loop(args):
+    """Secondary line: the off-policy training loop on the L2F quadrotor (16 environments; per loop step: runner step with resets drawn in the kernel,
+    gather_batch, train_critic x 2, update_critic_targets, train_actor at batch 256), every step one CUDA-graph replay. Single GPU."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from importlib import import_module
+    loops = import_module(pkg.__name__ + ".loops")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    here = os.path.dirname(os.path.abspath(__file__))
+    fix = np.load(os.path.join(here, "tests", "golden", "l2f.npz"))
+    p = pkg.L2fParameters.make(fix["dynamics"], float(fix["dt"]))
+    N_ENVS, BATCH, WARM, STEPS = 16, 256, 200, 5000
+    torch.manual_seed(0)
+    loop = loops.L2fSacLoop(p, fix["mdp"], fix["init"], n_envs=N_ENVS, batch_size=BATCH, step_limit=WARM + 100 + STEPS, n_warmup_steps=WARM, replay_capacity=8192, seed=1)
+    _, len0 = loop.evaluate()
+    for _ in range(WARM + 100):                      # warm-up with random actions, the capture, and the first replays
+        loop.step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(STEPS):
+        loop.step()
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    _, len1 = loop.evaluate()
+    print(json.dumps({"metric": "SAC loop steps/s on the L2F quadrotor (runner step of 16 environments + one update at batch 256)", "value": STEPS / (ms * 1e-3), "unit": "loop-steps/s",
+                      "n_gpus": 1, "steps": STEPS, "warmup": WARM + 100, "ms_per_step": ms / STEPS, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                      "data": "synthetic", "config": {"workload": "l2f_sac_loop_16env_batch256_hidden64", "l2": "working set (a few MB) is L2-resident by design: latency-bound",
+                                                       "parallelism": "single GPU", "evaluation_episode_length_before_after": [len0, len1]},
+                      "roofline": None, "cpu_baseline": None, "gpu_launches": None}))
+
+
 def run_actor_eval(args):
     """Secondary line: the batched actor inference of the CPU-runnable configuration -- fp32 input [256, 3], MLP 3 -> 64 -> 64 -> 2 (ReLU,
     ReLU, identity), evaluate() = three fused dense launches, 1000 calls per timed step, eager and replayed as a CUDA graph.
@@ -944,7 +981,7 @@ def main():
     ap.add_argument("--envs", type=int, default=N_ENVS, help="environments per GPU (default: the benchmark workload)")
     ap.add_argument("--rollout-steps", type=int, default=N_STEPS, help="steps per environment per call (default: the benchmark workload)")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only: do not force 3 warm-up steps")
-    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update", "acrobot_rollout", "l2f_step", "l2f_rollout"],
+    ap.add_argument("--workload", default="rollout", choices=["rollout", "mlp_train", "collect", "ppo_update", "critic_train", "actor_eval", "sac_update", "acrobot_rollout", "l2f_step", "l2f_rollout", "l2f_sac_loop"],
                     help="rollout = the headline benchmark; mlp_train = secondary line: sharded forward+backward+Adam of the 64-256-256-256-16 MLP; "
                          "collect = secondary line: on-policy (PPO) collect into the dataset matrix; ppo_update = secondary line: GAE + PPO train() "
                          "on the Ant shapes; critic_train = secondary line: batch-256 SAC critic regression steps (eager and CUDA graph)")
@@ -967,6 +1004,8 @@ def main():
         return run_l2f_step(args)
     if args.workload == "l2f_rollout":
         return run_l2f_rollout(args)
+    if args.workload == "l2f_sac_loop":
+        return run_l2f_sac_loop(args)
     if args.workload == "ppo_update":
         return run_ppo_update(args)
     if args.workload == "critic_train":

@@ -214,7 +214,7 @@ def run_reference(args):
             rows = args.train_rows
             line["secondary"] = {"mlp_train": {"metric": "MLP fwd+bwd+Adam samples/s", "value": mlp["value"], "unit": "samples/s", "n_gpus": args.gpus, "higher_is_better": True,
                                                "scaling": "strong", "dtype": "f32", "data": "synthetic", "timed_on": "host CPU cores", "cpu_baseline": mlp,
-                                               "config": {"workload": f"mlp_train_64-256-256-256-16_rows{rows}", "rows_per_gpu": rows // max(1, args.gpus), "chunk_rows": 65536,
+                                               "config": {"workload": f"mlp_train_64-256-256-256-16_rows{rows}", "rows_per_gpu": rows // max(1, args.gpus), "chunk_rows": TRAIN_CHUNK_ROWS,
                                                           "parallelism": f"dp{args.gpus}, one NCCL all-reduce of the 609 KB gradient arena per step",
                                                           "l2": "inputs (>= 0.6 GB per pass and GPU) exceed L2"}}}
     print(json.dumps(line))
@@ -255,12 +255,18 @@ def mlp_cpu_reference(params=None):
 MLP_FLOP_PER_SAMPLE = 876544.0          # forward 303,104 + weight gradient 303,104 + input gradient 270,336 (2 M N K each, no padding)
 
 
+# Rows per forward / backward pass of the training step (gradients accumulate over the chunks of a rank's rows). The workload fixes the rows
+# (2^24 over all ranks), not the chunk: per-chunk fixed costs (partial-sum reductions, operand images, tile tails) made 65,536-row chunks 227 ms
+# per step on one GPU against 198 / 187 / 181 / 178 / 177 ms at 2^17 .. 2^21; 2^20 leaves two chunks per rank at eight GPUs (6.6 GB of activations).
+TRAIN_CHUNK_ROWS = 1 << 20
+
+
 def measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=True):
     """Data-parallel training of the MLP 64 -> 256 -> 256 -> 256 -> 16 (ReLU, fp32) on `--train-rows` synthetic N(0,1) rows split over the
-    ranks (strong scaling); one step = forward + MSE gradient + backward over the rank's rows in 65,536-row chunks, ONE all-reduce of
+    ranks (strong scaling); one step = forward + MSE gradient + backward over the rank's rows in chunks of TRAIN_CHUNK_ROWS, ONE all-reduce of
     the flat gradient arena (NCCL), ONE fused Adam launch. Returns the result dictionary on rank 0 (None elsewhere)."""
     from rl_tools_b200 import parallel
-    chunk = 65536
+    chunk = TRAIN_CHUNK_ROWS
     b, e = parallel.shard_range(args.train_rows, rank, world)
     rows = (e - b) // chunk * chunk
     g = torch.Generator(device=dev); g.manual_seed(1234 + rank)
@@ -311,7 +317,7 @@ def measure_mlp_train(args, pkg, torch, dev, dist, world, rank, cpu_baseline=Tru
             torch.cuda.synchronize()
             ref_ms, _, _ = oracle.ReferenceCuda().mlp_train("c5_b65536", net.params.cpu().numpy(), xr.data_ptr(), yr.data_ptr(), rows, steps=2, warmup=1)
             cuda_reference = {"value": rows / (ref_ms * 1e-3), "unit": "samples/s", "ms_per_step": ref_ms, "kind": "reference",
-                              "build": "unmodified reference headers, devices::CUDA (cublasSgemm, fp32), nvcc -O3 sm_100a", "sample": "2 steps after 1 warm-up, same rows and chunking"}
+                              "build": "unmodified reference headers, devices::CUDA (cublasSgemm, fp32), nvcc -O3 sm_100a", "sample": "2 steps after 1 warm-up, same rows, in chunks of its compiled batch of 65,536"}
             del xr, yr
     tf = flop / (ms * 1e-3) / 1e12
     return {"metric": "MLP fwd+bwd+Adam samples/s", "value": rows * world / (ms * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": steps,

@@ -120,3 +120,40 @@ def test_parameters_and_moments_against_the_reference(stepped, fix):
     # first step (alpha = 1e-3): p -= alpha * g / (|g| + eps') with eps' >= eps = 1e-7, so |dp| <= alpha * dg / (|g| + eps) + one rounding of p
     dp = np.abs(stepped["params"][::s].astype(np.float64) - fix["params"])
     assert np.all(dp <= 1e-3 * g_bound / (g + 1e-7) + 1.2e-7 * np.abs(fix["params"]) + 1e-9)
+
+
+@pytest.mark.gpu
+def test_c5_gradients_do_not_depend_on_the_chunk_size():
+    """The training step accumulates gradients over chunks of the rank's rows; the benchmark's chunk is 2^20 rows, the reference fixtures of this
+    file pin chunks of 65,536. One million rows of the C5 network, same parameters and data: the gradient arena accumulated over sixteen
+    65,536-row chunks against the one accumulated in a single 2^20-row chunk (every kernel of the step at sixteen times the batch: tile
+    counts, split ranges, byte offsets beyond 2^31 in the activation arenas) -- equal up to the order of fp32 sums over the batch."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from rl_tools_b200 import parallel
+    rows, dims, acts = 1 << 20, [256, 256, 256, 16], ["relu", "relu", "relu", "identity"]
+    g = torch.Generator(device="cuda"); g.manual_seed(5)
+    x, y = torch.randn((rows, 64), device="cuda", generator=g), torch.randn((rows, 16), device="cuda", generator=g)
+    grads = []
+    for chunk in (65536, rows):
+        net = pkg.Mlp(64, dims, acts, chunk)
+        gp = torch.Generator(device="cuda"); gp.manual_seed(7)
+        off, fan_in = 0, 64
+        for d in dims:
+            n = d * fan_in + d
+            net.params[off:off + n] = (torch.rand(n, device="cuda", generator=gp) * 2 - 1) / fan_in ** 0.5
+            off += n; fan_in = d
+        net.zero_gradient()
+        w = parallel.chunk_loss_weight(chunk, rows)
+        for c in range(0, rows, chunk):
+            out = net.forward(x[c:c + chunk])
+            net.backward(x[c:c + chunk], pkg.mse_gradient(out, y[c:c + chunk], w, d_a=net.d_out_buffer()))
+        grads.append(net.grads.double().cpu().numpy())
+        del net
+    a, b = grads
+    scale = np.abs(a).max()
+    assert scale > 1e-4 and np.isfinite(b).all()
+    assert np.abs(a - b).max() <= 2e-5 * scale, (float(np.abs(a - b).max()), float(scale))
+
